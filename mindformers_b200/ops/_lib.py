@@ -1,0 +1,151 @@
+"""ctypes binding of the in-tree sm_100a kernel library (``lib/libmfb200.so``).
+
+The library exposes plain ``extern "C"`` entry points that take raw device pointers and a CUDA
+stream, so it needs no torch headers and builds in seconds. On a machine with a GPU the library
+must be present: a missing or stale ``.so`` raises instead of silently falling back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+KERNEL_LIB_PATH = os.path.join(_HERE, "lib", "libmfb200.so")
+DATA_LIB_PATH = os.path.join(_HERE, "lib", "libmfb200_data.so")
+ABI_VERSION = 1
+
+_lock = threading.Lock()
+_lib = None
+_launch_count = 0  # kernels launched through this binding (read by the benchmark)
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def _declare(lib):
+    def sig(name, args):
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+        return fn
+
+    P, I, L, F = c_void_p, c_int, c_ll, c_float
+    lib.mfb_last_error.restype = ctypes.c_char_p
+    lib.mfb_abi_version.restype = c_int
+    sig("mfb_gemm_bf16", [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P, I, P, I, P])
+    sig("mfb_rmsnorm_fwd", [P, P, P, P, P, P, I, I, F, P])
+    sig("mfb_rmsnorm_bwd_parts", [I])
+    sig("mfb_rmsnorm_bwd", [P, P, P, P, P, P, P, P, I, P, I, I, P])
+    sig("mfb_headnorm_fwd", [P, P, P, I, I, I, L, F, P])
+    sig("mfb_swiglu_fwd", [P, P, L, I, P])
+    sig("mfb_swiglu_bwd", [P, P, P, L, I, P])
+    sig("mfb_rope", [P, P, P, P, L, I, I, I, L, I, I, I, P])
+    sig("mfb_embedding_fwd", [P, P, P, L, I, I, I, P])
+    sig("mfb_embedding_bwd", [P, P, P, L, I, I, I, P])
+    sig("mfb_accum_bf16_to_f32", [P, P, L, F, I, P])
+    sig("mfb_add_bf16", [P, P, P, L, P])
+    sig("mfb_ce_stats", [P, I, P, P, P, P, L, I, L, I, P])
+    sig("mfb_ce_bwd", [P, P, I, P, P, P, L, I, L, I, P])
+    sig("mfb_grad_sumsq_scratch", [])
+    sig("mfb_grad_sumsq", [P, I, L, P, P, I, P])
+    sig("mfb_adamw", [P, P, P, P, P, I, P, P, L, L, F, F, F, F, F, F, F, F, F, F, P])
+    sig("mfb_split_master", [P, P, P, L, P])
+    sig("mfb_join_master", [P, P, P, L, P])
+    # optional entry points (present once their source file is part of the build)
+    for name, args in _OPTIONAL.items():
+        if hasattr(lib, name):
+            sig(name, args)
+
+
+_OPTIONAL: dict = {}
+
+
+def optional_entry(name, args):
+    """Register the signature of an entry point that later source files add to the library."""
+    _OPTIONAL[name] = args
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def available() -> bool:
+    return os.path.exists(KERNEL_LIB_PATH)
+
+
+def get_lib():
+    """Load (once) and return the kernel library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(KERNEL_LIB_PATH):
+            raise KernelLibraryError(
+                f"{KERNEL_LIB_PATH} is missing: run `python -m mindformers_b200.ops.build` "
+                "(the CUDA path never falls back to PyTorch on a GPU)")
+        lib = ctypes.CDLL(KERNEL_LIB_PATH)
+        got = lib.mfb_abi_version()
+        if got != ABI_VERSION:
+            raise KernelLibraryError(f"kernel library ABI {got} != expected {ABI_VERSION}; rebuild it")
+        _declare(lib)
+        _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = get_lib().mfb_last_error().decode(errors="replace")
+        raise KernelLibraryError(f"{what} failed (code {rc}): {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def count_launch(n: int = 1):
+    global _launch_count
+    _launch_count += n
+
+
+def launch_count() -> int:
+    return _launch_count
+
+
+def reset_launch_count():
+    global _launch_count
+    _launch_count = 0
+
+
+_status_words: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits write their error code to."""
+    key = torch.device(device).index or 0
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = t
+    return t
+
+
+def read_status(device=None) -> int:
+    """Synchronising read of the status word (0 = every bounded wait completed)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return int(status_word(device).item())

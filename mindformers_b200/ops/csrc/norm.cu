@@ -1,0 +1,323 @@
+// RMSNorm forward / backward for sm_100a (bf16 activations, fp32 statistics).
+//
+// forward : h = x (+ residual);  y = h * rsqrt(mean(h^2) + eps) * w ; saves rstd[T]
+//           (the residual add of a pre-LN transformer block is fused: h is written back)
+// backward: dx = rstd * (w*dy) - h * rstd^3 * mean(w*dy*h)   (+ dres, the gradient that
+//           reaches h through the residual stream);   dw = sum_t dy * h * rstd
+// dw is reduced in two deterministic phases through a [parts, H] fp32 scratch buffer.
+//
+// One CTA of 256 threads per row, 16-byte vector accesses, row kept in registers when
+// H <= 8192. A warp-per-row variant serves per-head q/k norms (H <= 256, strided rows).
+#include "common.cuh"
+
+namespace mfb {
+
+constexpr int kNormThreads = 256;
+constexpr int kMaxVec = 4;  // 4 x 8 bf16 per thread => H <= 8192 stays in registers
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < (blockDim.x >> 5)) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+template <bool HAS_RES>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* h_out, float* __restrict__ rstd_out, int T, int H,
+                   float eps) {
+  __shared__ float red[32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * H);
+    const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * H) : nullptr;
+    bf16x8* hr = HAS_RES ? reinterpret_cast<bf16x8*>(h_out + (size_t)row * H) : nullptr;
+    float vals[kMaxVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 a = xr[v];
+        if (HAS_RES) {
+          bf16x8 b = rr[v];
+          bf16x8 o;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 fa = __bfloat1622float2(a.v[j]);
+            float2 fb = __bfloat1622float2(b.v[j]);
+            o.v[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+          }
+          hr[v] = o;
+          a = o;  // normalise the rounded sum, the value the backward pass will read
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __bfloat1622float2(a.v[j]);
+          vals[i][2 * j] = f.x;
+          vals[i][2 * j + 1] = f.y;
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+    // tail for H beyond the register window
+    for (int v = threadIdx.x + kMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
+      bf16x8 a = xr[v];
+      if (HAS_RES) {
+        bf16x8 b = rr[v];
+        bf16x8 o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 fa = __bfloat1622float2(a.v[j]);
+          float2 fb = __bfloat1622float2(b.v[j]);
+          o.v[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+        }
+        hr[v] = o;
+        a = o;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(a.v[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float rstd = rsqrtf(tot / (float)H + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 ww = wr[v];
+        bf16x8 o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 fw = __bfloat1622float2(ww.v[j]);
+          o.v[j] = __floats2bfloat162_rn(vals[i][2 * j] * rstd * fw.x, vals[i][2 * j + 1] * rstd * fw.y);
+        }
+        yr[v] = o;
+      }
+    }
+    const bf16x8* src = HAS_RES ? reinterpret_cast<const bf16x8*>(h_out + (size_t)row * H) : xr;
+    for (int v = threadIdx.x + kMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
+      bf16x8 a = src[v];
+      bf16x8 ww = wr[v];
+      bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(a.v[j]);
+        float2 fw = __bfloat1622float2(ww.v[j]);
+        o.v[j] = __floats2bfloat162_rn(f.x * rstd * fw.x, f.y * rstd * fw.y);
+      }
+      yr[v] = o;
+    }
+  }
+}
+
+// Backward over rows [persistent grid]; each CTA keeps its dw partial in registers (columns owned
+// by the thread) and writes one row of the scratch buffer at the end.
+template <bool HAS_DRES>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int T, int H) {
+  __shared__ float red[32];
+  const int nvec = H / 8;
+  float dw_acc[kMaxVec][8];
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)row * H);
+    const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + (size_t)row * H);
+    const float r = rstd[row];
+    float wdy[kMaxVec][8], hv[kMaxVec][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 a = dyr[v], b = hr[v], ww = wr[v];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 fd = __bfloat1622float2(a.v[j]);
+          float2 fh = __bfloat1622float2(b.v[j]);
+          float2 fw = __bfloat1622float2(ww.v[j]);
+          wdy[i][2 * j] = fd.x * fw.x;
+          wdy[i][2 * j + 1] = fd.y * fw.y;
+          hv[i][2 * j] = fh.x;
+          hv[i][2 * j + 1] = fh.y;
+          dot += wdy[i][2 * j] * fh.x + wdy[i][2 * j + 1] * fh.y;
+          dw_acc[i][2 * j] += fd.x * fh.x * r;
+          dw_acc[i][2 * j + 1] += fd.y * fh.y * r;
+        }
+      }
+    }
+    const float tot = block_sum(dot, red);
+    const float c = tot * r * r * r / (float)H;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + (size_t)row * H);
+    const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * H) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 o;
+        bf16x8 dr;
+        if (HAS_DRES) dr = drr[v];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a0 = wdy[i][2 * j] * r - hv[i][2 * j] * c;
+          float a1 = wdy[i][2 * j + 1] * r - hv[i][2 * j + 1] * c;
+          if (HAS_DRES) {
+            float2 f = __bfloat1622float2(dr.v[j]);
+            a0 += f.x;
+            a1 += f.y;
+          }
+          o.v[j] = __floats2bfloat162_rn(a0, a1);
+        }
+        dxr[v] = o;
+      }
+    }
+  }
+  float* out = dw_partial + (size_t)blockIdx.x * H;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out[v * 8 + j] = dw_acc[i][j];
+    }
+  }
+}
+
+// dw[c] (+)= sum_p partial[p, c]; output fp32 (accumulate) or bf16.
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, int parts, int H,
+                                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * H + c];
+  if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
+  if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
+}
+
+// ---- warp-per-row variant for per-head q/k norm: rows are (token, head) with strides ----
+__global__ void headnorm_fwd_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                    float* __restrict__ rstd_out, int T, int heads, int hd,
+                                    long long token_stride, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (row >= (long long)T * heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = row / heads;
+  const int hh = (int)(row - t * heads);
+  __nv_bfloat16* p = x + t * token_stride + (long long)hh * hd;
+  float v[8];
+  float ss = 0.f;
+  const int per = hd / 32;  // elements per lane (hd in {64,128,256})
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (i < per) {
+      v[i] = __bfloat162float(p[lane * per + i]);
+      ss += v[i] * v[i];
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)hd + eps);
+  if (lane == 0 && rstd_out) rstd_out[row] = r;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (i < per) p[lane * per + i] = __float2bfloat16(v[i] * r * __bfloat162float(w[lane * per + i]));
+  }
+}
+
+}  // namespace mfb
+
+extern "C" {
+
+using namespace mfb;
+
+// y = rmsnorm(x (+res)) * w. `h_out` receives x+res when `res` is given (may alias x or res).
+int mfb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd,
+                    int T, int H, float eps, cudaStream_t stream) {
+  if (H % 8 != 0) {
+    mfb_host::set_error("rmsnorm: H=%d must be a multiple of 8", H);
+    return 1;
+  }
+  if (T <= 0) return 0;
+  const int grid = T;
+  if (res)
+    rmsnorm_fwd_kernel<true><<<grid, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+        (__nv_bfloat16*)h_out, rstd, T, H, eps);
+  else
+    rmsnorm_fwd_kernel<false><<<grid, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr, rstd, T, H,
+        eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Number of scratch rows (of H floats each) that mfb_rmsnorm_bwd needs for a problem of T rows.
+int mfb_rmsnorm_bwd_parts(int T) {
+  int parts = 148 * 4;
+  return T < parts ? T : parts;
+}
+
+// dx = d(rmsnorm)/dh (+ dres); dw (fp32 or bf16, one of them non-null) = or += column sums.
+// `scratch` must hold mfb_rmsnorm_bwd_parts(T) * H floats. H <= 8192.
+int mfb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres,
+                    void* dx, float* dw_f32, void* dw_bf16, int accumulate, float* scratch, int T, int H,
+                    cudaStream_t stream) {
+  if (H % 8 != 0 || H > kNormThreads * kMaxVec * 8) {
+    mfb_host::set_error("rmsnorm_bwd: H=%d must be a multiple of 8 and <= 8192", H);
+    return 1;
+  }
+  if (T <= 0) return 0;
+  const int parts = mfb_rmsnorm_bwd_parts(T);
+  if (dres)
+    rmsnorm_bwd_kernel<true><<<parts, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,
+        (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H);
+  else
+    rmsnorm_bwd_kernel<false><<<parts, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr,
+        (__nv_bfloat16*)dx, scratch, T, H);
+  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32,
+                                                             (__nv_bfloat16*)dw_bf16, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// In-place per-head RMSNorm on x[t, head, :] (rows `token_stride` elements apart).
+int mfb_headnorm_fwd(void* x, const void* w, float* rstd, int T, int heads, int hd, long long token_stride,
+                     float eps, cudaStream_t stream) {
+  if (hd % 32 != 0 || hd > 256) {
+    mfb_host::set_error("headnorm: head_dim=%d unsupported", hd);
+    return 1;
+  }
+  const long long rows = (long long)T * heads;
+  if (rows <= 0) return 0;
+  const int wpb = 8;
+  const int grid = (int)((rows + wpb - 1) / wpb);
+  headnorm_fwd_kernel<<<grid, wpb * 32, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, T,
+                                                     heads, hd, token_stride, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

@@ -1,0 +1,242 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+from mindformers_b200.ops import _lib
+from mindformers_b200.ops import functional as Fn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _status_ok():
+    assert _lib.read_status() == 0, "a bounded device wait ran out"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (4096, 6144, 4096), (300, 384, 200),
+                                   (64, 128, 128), (1000, 3072, 1024), (128, 128, 64)])
+def test_gemm_tn(M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    d = Fn.gemm(a, b)
+    ref = a.float() @ b.float().t()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(d, ref) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (4096, 4096, 6144), (384, 256, 192)])
+def test_gemm_b_mn_major(M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    d = Fn.gemm(a, b, b_mn=True)
+    ref = a.float() @ b.float()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(d, ref) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (6144, 4096, 4096), (384, 256, 320)])
+def test_gemm_both_mn_major(M, N, K):
+    torch.manual_seed(2)
+    a = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    d = Fn.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    ref = a.float().t() @ b.float()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(d, ref) < 5e-3
+    # accumulate twice into an fp32 buffer through the TMA reduce-add epilogue
+    acc = torch.zeros(M, N, device=DEV, dtype=torch.float32)
+    Fn.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    Fn.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    torch.cuda.synchronize()
+    assert _rel_err(acc, 2 * ref) < 5e-3
+
+
+def test_linear_autograd_matches_torch():
+    torch.manual_seed(3)
+    x = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(768, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = Fn.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 5e-3
+    assert _rel_err(x.grad, xr.grad) < 5e-3
+    assert _rel_err(w.grad, wr.grad) < 5e-3
+
+
+def test_grouped_gemm_and_wgrad():
+    torch.manual_seed(4)
+    G, K, N = 4, 256, 384
+    counts = [128, 0, 384, 256]
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + c)
+    R = offs[-1] + 256  # spare rows beyond the used blocks
+    a = torch.randn(R, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(G, N, K, device=DEV, dtype=torch.bfloat16)
+    bg = []
+    for g, c in enumerate(counts):
+        bg += [g] * (c // 128)
+    nb = len(bg)
+    block_group = torch.tensor(bg + [0] * (R // 128 - nb), device=DEV, dtype=torch.int32)
+    num_blocks = torch.tensor([nb], device=DEV, dtype=torch.int32)
+    out = Fn.grouped_gemm(a, b, block_group, num_blocks)
+    torch.cuda.synchronize()
+    _status_ok()
+    for g in range(G):
+        rows = slice(offs[g], offs[g + 1])
+        if counts[g]:
+            assert _rel_err(out[rows], a[rows].float() @ b[g].float().t()) < 5e-3
+    # dgrad: dy [R,N] x W[g] [N,K] -> [R,K]
+    dy = torch.randn(R, N, device=DEV, dtype=torch.bfloat16)
+    dx = Fn.grouped_gemm(dy, b, block_group, num_blocks, b_mn=True)
+    torch.cuda.synchronize()
+    _status_ok()
+    for g in range(G):
+        rows = slice(offs[g], offs[g + 1])
+        if counts[g]:
+            assert _rel_err(dx[rows], dy[rows].float() @ b[g].float()) < 5e-3
+    # wgrad per expert (expert 1 is empty and must come out as zeros)
+    go = torch.tensor(offs, device=DEV, dtype=torch.int32)
+    dw = torch.full((G, N, K), 7.0, device=DEV, dtype=torch.float32)
+    Fn.grouped_wgrad(dy, a, go, G, dw)
+    torch.cuda.synchronize()
+    _status_ok()
+    for g in range(G):
+        rows = slice(offs[g], offs[g + 1])
+        ref = dy[rows].float().t() @ a[rows].float()
+        if counts[g]:
+            assert _rel_err(dw[g], ref) < 5e-3
+        else:
+            assert dw[g].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("T,H", [(64, 4096), (33, 2048), (17, 7168), (5, 512)])
+def test_rmsnorm_fwd_bwd(T, H):
+    torch.manual_seed(5)
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y, h = Fn.rmsnorm(x, w, 1e-5, residual=r)
+    gy, gh = torch.randn_like(y), torch.randn_like(h)
+    (y * gy).sum().backward(retain_graph=True)
+    (h * gh).sum().backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = (xr + rr).to(torch.bfloat16).float() + 0 * (xr + rr)  # value rounded like the kernel, grad identity
+    hr = (xr + rr) + ((xr + rr).to(torch.bfloat16).float() - (xr + rr)).detach()
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    ((yr * gy.float()).sum() + (hr * gh.float()).sum()).backward()
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(r.grad, rr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+
+
+def test_swiglu_fwd_bwd():
+    torch.manual_seed(6)
+    x = torch.randn(257, 2 * 1536, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = Fn.swiglu(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    a, b = xr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope(interleaved):
+    torch.manual_seed(7)
+    T, nq, nkv, hd = 96, 8, 2, 128
+    heads = nq + 2 * nkv
+    x0 = torch.randn(T, heads, hd, device=DEV, dtype=torch.bfloat16)
+    inv = 1.0 / (10000 ** (torch.arange(0, hd, 2, device=DEV).float() / hd))
+    ang = torch.arange(128, device=DEV).float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.randint(0, 128, (T,), device=DEV)
+    x = x0.clone().requires_grad_()
+    y = Fn.rope(x * 1.0, cos, sin, pos, nq + nkv, hd, interleaved)
+    ref = Fn.rope_reference(x0, cos, sin, pos, nq + nkv, hd, interleaved)
+    assert _rel_err(y, ref) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x0.clone().float().requires_grad_()
+    Fn.rope_reference(x2, cos, sin, pos, nq + nkv, hd, interleaved).backward(g.float())
+    assert _rel_err(x.grad, x2.grad) < 1e-2
+
+
+@pytest.mark.parametrize("V", [1024, 128256, 50001])
+def test_cross_entropy(V):
+    torch.manual_seed(8)
+    T = 64
+    logits = (torch.randn(T, V, device=DEV) * 2).to(torch.bfloat16)
+    labels = torch.randint(0, V, (T,), device=DEV)
+    lr = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, labels, reduction="none")
+    w = torch.rand(T, device=DEV)
+    (ref * w).sum().backward()
+    lg = logits.clone().requires_grad_()
+    loss = Fn.cross_entropy(lg, labels)
+    assert torch.allclose(loss, ref, atol=2e-3, rtol=2e-3)
+    (loss * w).sum().backward()
+    assert _rel_err(lg.grad, lr.grad) < 1e-2
+
+
+def test_embedding():
+    torch.manual_seed(9)
+    V, H, T = 1000, 256, 333
+    table = torch.randn(V, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, V, (T,), device=DEV)
+    out = Fn.embedding(ids, table)
+    assert torch.equal(out, table[ids])
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref = torch.zeros(V, H, device=DEV)
+    ref.index_add_(0, ids, g.float())
+    assert _rel_err(table.grad, ref) < 1e-2
+
+
+def test_adamw_matches_reference_and_master_is_exact():
+    torch.manual_seed(10)
+    n = 100003
+    w = torch.randn(n, device=DEV) * 0.02
+    p = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    lo = torch.empty(n, device=DEV, dtype=torch.int16)
+    Fn.split_master(w, p, lo)
+    assert torch.equal(Fn.join_master(p, lo), w)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    wr, mr, vr = w.clone(), m.clone(), v.clone()
+    sumsq = torch.zeros(1, device=DEV)
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV)
+        Fn.grad_sumsq(g, sumsq)
+        assert abs(sumsq.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+        Fn.adamw_step(p, lo, m, v, g, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                      decay_end=n // 2, sumsq=sumsq, max_norm=1.0)
+        nrm = g.norm()
+        gc = g * min(1.0, 1.0 / (nrm.item() + 1e-6))
+        mr = 0.9 * mr + 0.1 * gc
+        vr = 0.95 * vr + 0.05 * gc * gc
+        wr[: n // 2] *= 1 - 1e-3 * 0.1
+        wr -= (1e-3 / (1 - 0.9 ** step)) * mr / ((vr / (1 - 0.95 ** step)).sqrt() + 1e-8)
+    got = Fn.join_master(p, lo)
+    assert torch.allclose(got, wr, atol=1e-6, rtol=1e-4)
+    assert torch.allclose(p.float(), got, atol=0, rtol=2 ** -8)
