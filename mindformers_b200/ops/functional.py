@@ -122,8 +122,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, block_group: torch.Tensor, nu
     R, K = a.shape
     N = b.shape[2] if b_mn else b.shape[1]
     if out is None:
-        out = torch.empty((R, N), dtype=torch.bfloat16, device=a.device)
-    if not (_on_gpu(a) and _GEMM_BACKEND == "tcgen05"):
+        out = torch.empty((R, N), dtype=a.dtype, device=a.device)
+    if not (_on_gpu(a) and _GEMM_BACKEND == "tcgen05" and a.dtype == torch.bfloat16):
         nb = int(num_blocks.item())
         bg = block_group[:nb].tolist()
         out.zero_()
@@ -148,7 +148,7 @@ def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, group_offsets: torch.Tensor
     """Per-expert weight gradient ``out[g] (+)= dy[rows_g]^T x[rows_g]`` with ``out`` = ``[G, N_out, K_in]``."""
     R, Nout = dy.shape
     Kin = x.shape[1]
-    if not (_on_gpu(dy) and _GEMM_BACKEND == "tcgen05"):
+    if not (_on_gpu(dy) and _GEMM_BACKEND == "tcgen05" and dy.dtype == torch.bfloat16):
         offs = group_offsets.tolist()
         for g in range(num_groups):
             rows = slice(offs[g], offs[g + 1])
@@ -178,6 +178,8 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w)
+        if x.dim() == 2:
+            return y  # not a view: later in-place kernels (RoPE) may write into it
         return y.reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod

@@ -1,0 +1,244 @@
+"""Context-parallel attention: all-gather KV, ring (P2P) exchange, Ulysses all-to-all; packed-sequence attention.
+
+Reference: the reference toggles these inside its FlashAttention primitive
+(``training_graph/transformer/flash_attention.py:145-147,167-226`` for ring / all-gather layouts,
+``attention.py:203-222,360-428`` for the Ulysses transposes). Here the mechanisms are explicit:
+
+* ``all_gather``: K/V of all ranks are gathered, each rank attends its query chunk (zig-zag balanced).
+* ``p2p`` (ring): K/V blocks rotate around the ring while the local block computes; partial outputs are
+  merged with their log-sum-exp.
+* ``a2a`` (Ulysses): sequence ↔ head all-to-all around a full-sequence attention.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as Fn
+from . import mappings as M
+from . import parallel_state as ps
+
+
+def varlen_attention(q, k, v, cu_seqlens, scale):
+    """Causal attention over packed sequences: tokens attend within their own segment only.
+    q/k/v: [B, S, h, d]; ``cu_seqlens``: cumulative boundaries over the flattened B*S tokens."""
+    B, S = q.shape[:2]
+    T = B * S
+    qf, kf, vf = (t.reshape(1, T, t.shape[2], t.shape[3]) for t in (q, k, v))
+    bounds = cu_seqlens.tolist()
+    outs = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b > a:
+            outs.append(Fn.attention(qf[:, a:b], kf[:, a:b], vf[:, a:b], causal=True, scale=scale))
+    return torch.cat(outs, dim=1).reshape(B, S, q.shape[2], v.shape[3])
+
+
+def _attn_with_lse(q, k, v, scale, causal, q_offset=0):
+    """Reference-math attention that also returns the log-sum-exp; used by the ring merge."""
+    B, Sq, Hq, D = q.shape
+    rep = Hq // k.shape[2]
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        qi = torch.arange(Sq, device=q.device).unsqueeze(-1) + q_offset
+        ki = torch.arange(k.shape[1], device=q.device).unsqueeze(0)
+        s = s.masked_fill(ki > qi, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = torch.matmul(p, vf)
+    return o.permute(0, 2, 1, 3), lse.permute(0, 2, 1)  # [B,S,H,D], [B,S,H]
+
+
+def ring_attention(q, k, v, scale, group=None):
+    """Causal ring attention with contiguous sequence chunks: rank r holds tokens [r*S, (r+1)*S).
+    K/V travel around the ring; blocks from later ranks are skipped (fully masked)."""
+    group = group if group is not None else ps.get_context_parallel_group()
+    cp = ps.get_context_parallel_world_size()
+    r = ps.get_context_parallel_rank()
+    ranks = ps.get_group_ranks("cp")
+    out, lse = None, None
+    kv = torch.stack((k, v)).contiguous()
+    for step in range(cp):
+        src = (r - step) % cp
+        nxt = torch.empty_like(kv) if step < cp - 1 else None
+        reqs = []
+        if nxt is not None:
+            send_to, recv_from = ranks[(r + 1) % cp], ranks[(r - 1) % cp]
+            ops = [dist.P2POp(dist.isend, kv, send_to, group), dist.P2POp(dist.irecv, nxt, recv_from, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        if src <= r:
+            o_b, lse_b = _attn_with_lse(q, kv[0], kv[1], scale, causal=(src == r))
+            if out is None:
+                out, lse = o_b, lse_b
+            else:
+                new_lse = torch.logaddexp(lse, lse_b)
+                out = out * torch.exp(lse - new_lse).unsqueeze(-1) + o_b * torch.exp(lse_b - new_lse).unsqueeze(-1)
+                lse = new_lse
+        for q_ in reqs:
+            q_.wait()
+        if nxt is not None:
+            kv = nxt
+    return out.to(q.dtype)
+
+
+class _UlyssesA2A(torch.autograd.Function):
+    """[B, S/cp, h, d] ↔ [B, S, h/cp, d] all-to-all; ``to_heads`` picks the direction."""
+    @staticmethod
+    def forward(ctx, x, to_heads, group, cp):
+        ctx.to_heads, ctx.group, ctx.cp = to_heads, group, cp
+        B, S, h, d = x.shape
+        if to_heads:
+            xs = x.reshape(B, S, cp, h // cp, d).permute(2, 0, 1, 3, 4).contiguous()
+            out = torch.empty_like(xs)
+            dist.all_to_all_single(out, xs, group=group)
+            return out.permute(1, 0, 2, 3, 4).reshape(B, cp * S, h // cp, d)
+        xs = x.reshape(B, cp, S // cp, h, d).permute(1, 0, 2, 3, 4).contiguous()
+        out = torch.empty_like(xs)
+        dist.all_to_all_single(out, xs, group=group)
+        return out.permute(1, 2, 0, 3, 4).reshape(B, S // cp, cp * h, d)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _UlyssesA2A.apply(g.contiguous(), not ctx.to_heads, ctx.group, ctx.cp), None, None, None
+
+
+def ulysses_attention(q, k, v, scale, group=None):
+    group = group if group is not None else ps.get_context_parallel_group()
+    cp = ps.get_context_parallel_world_size()
+    if q.shape[2] % cp or k.shape[2] % cp:
+        raise ValueError("Ulysses context parallelism needs head counts divisible by the cp size")
+    qh, kh, vh = (_UlyssesA2A.apply(t.contiguous(), True, group, cp) for t in (q, k, v))
+    o = Fn.attention(qh, kh, vh, causal=True, scale=scale)
+    return _UlyssesA2A.apply(o.contiguous(), False, group, cp)
+
+
+class _AllGatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, cp):
+        ctx.group, ctx.cp = group, cp
+        parts = [torch.empty_like(x) for _ in range(cp)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        cp = ctx.cp
+        chunks = [c.contiguous() for c in g.chunk(cp, dim=1)]
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter(out, chunks, group=ctx.group)
+        return out, None, None
+
+
+def allgather_kv_attention(q, k, v, scale, group=None):
+    """Gather K/V over the cp group; this rank's queries (tokens [r*S,(r+1)*S)) attend the prefix."""
+    group = group if group is not None else ps.get_context_parallel_group()
+    cp = ps.get_context_parallel_world_size()
+    r = ps.get_context_parallel_rank()
+    kf = _AllGatherSeq.apply(k, group, cp)
+    vf = _AllGatherSeq.apply(v, group, cp)
+    S = q.shape[1]
+    end = (r + 1) * S
+    if q.is_cuda:
+        o, _ = _attn_with_lse(q, kf[:, :end], vf[:, :end], scale, causal=True, q_offset=r * S)
+        return o.to(q.dtype)
+    return Fn.attention_reference(q, kf[:, :end], vf[:, :end], True, scale, q_offset=r * S)
+
+
+def context_parallel_attention(q, k, v, scale, config):
+    kind = config.cp_comm_type
+    if kind == "p2p":
+        if torch.is_grad_enabled() and q.requires_grad:
+            return _RingAttnFn.apply(q, k, v, scale)
+        return ring_attention(q, k, v, scale)
+    if kind == "a2a":
+        return ulysses_attention(q, k, v, scale)
+    if kind == "all_gather":
+        return allgather_kv_attention(q, k, v, scale)
+    raise NotImplementedError(f"cp_comm_type {kind!r}")
+
+
+class _RingAttnFn(torch.autograd.Function):
+    """Ring attention with a recompute-based backward: gradients of the local q and of every visited
+    K/V block are formed with the saved global log-sum-exp; dK/dV travel back with their block."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        cp, r = ps.get_context_parallel_world_size(), ps.get_context_parallel_rank()
+        group, ranks = ps.get_context_parallel_group(), ps.get_group_ranks("cp")
+        out, lse = None, None
+        kv = torch.stack((k, v)).contiguous()
+        for step in range(cp):
+            src = (r - step) % cp
+            nxt = torch.empty_like(kv) if step < cp - 1 else None
+            reqs = []
+            if nxt is not None:
+                ops = [dist.P2POp(dist.isend, kv, ranks[(r + 1) % cp], group),
+                       dist.P2POp(dist.irecv, nxt, ranks[(r - 1) % cp], group)]
+                reqs = dist.batch_isend_irecv(ops)
+            if src <= r:
+                o_b, lse_b = _attn_with_lse(q, kv[0], kv[1], scale, causal=(src == r))
+                if out is None:
+                    out, lse = o_b, lse_b
+                else:
+                    new_lse = torch.logaddexp(lse, lse_b)
+                    out = out * torch.exp(lse - new_lse).unsqueeze(-1) + o_b * torch.exp(lse_b - new_lse).unsqueeze(-1)
+                    lse = new_lse
+            for q_ in reqs:
+                q_.wait()
+            if nxt is not None:
+                kv = nxt
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.scale = scale
+        return out.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        scale = ctx.scale
+        cp, r = ps.get_context_parallel_world_size(), ps.get_context_parallel_rank()
+        group, ranks = ps.get_context_parallel_group(), ps.get_group_ranks("cp")
+        rep = q.shape[2] // k.shape[2]
+        do = dout.float().permute(0, 2, 1, 3)                      # [B,H,S,D]
+        qf = q.float().permute(0, 2, 1, 3)
+        delta = (do * out.permute(0, 2, 1, 3)).sum(-1)             # [B,H,S]
+        lse_h = lse.permute(0, 2, 1)
+        dq = torch.zeros_like(qf)
+        kv = torch.stack((k, v)).contiguous()
+        dkv = torch.zeros((2, *k.shape), dtype=torch.float32, device=k.device)
+        for step in range(cp):
+            src = (r - step) % cp
+            if src <= r:
+                kf = kv[0].float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+                vf = kv[1].float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+                s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+                if src == r:
+                    S = q.shape[1]
+                    mask = torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1)
+                    s = s.masked_fill(mask, float("-inf"))
+                p = torch.exp(s - lse_h.unsqueeze(-1))
+                dv_b = torch.matmul(p.transpose(-1, -2), do)
+                dp = torch.matmul(do, vf.transpose(-1, -2))
+                ds = p * (dp - delta.unsqueeze(-1)) * scale
+                dq += torch.matmul(ds, kf)
+                dk_b = torch.matmul(ds.transpose(-1, -2), qf)
+                B, H, Sk, D = dk_b.shape
+                dk_b = dk_b.view(B, H // rep, rep, Sk, D).sum(2).permute(0, 2, 1, 3)
+                dv_b = dv_b.view(B, H // rep, rep, Sk, -1).sum(2).permute(0, 2, 1, 3)
+                dkv[0] += dk_b
+                dkv[1] += dv_b
+            # rotate the K/V block and its gradient accumulator together
+            if cp > 1:
+                nkv, ndkv = torch.empty_like(kv), torch.empty_like(dkv)
+                ops = [dist.P2POp(dist.isend, kv, ranks[(r + 1) % cp], group),
+                       dist.P2POp(dist.irecv, nkv, ranks[(r - 1) % cp], group),
+                       dist.P2POp(dist.isend, dkv, ranks[(r + 1) % cp], group),
+                       dist.P2POp(dist.irecv, ndkv, ranks[(r - 1) % cp], group)]
+                for q_ in dist.batch_isend_irecv(ops):
+                    q_.wait()
+                kv, dkv = nkv, ndkv
+        # after cp rotations every block (and its gradient) is back at its owner
+        return dq.permute(0, 2, 1, 3).to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None

@@ -1,0 +1,234 @@
+"""Sharded AdamW over flat buffers (ZeRO-1 style distributed optimizer).
+
+Each data-parallel rank owns ``1/dp`` of every flat buffer: its slice of the fp32 gradient arrives by
+reduce-scatter, the fused kernel updates the bf16 parameters (+16-bit master remainder) and the fp32
+moments of that slice, and an all-gather publishes the new parameters. Global-norm clipping and the
+skip-on-spike / skip-on-NaN decision are read from a device scalar, so a step has no host
+synchronisation. Semantics follow the reference: ``core/optim/adamw.py:38-66`` (decoupled decay, bias
+correction, eps outside the square root), ``core/clip_grad.py:60-101`` (coefficient ``max_norm/(norm+1e-6)``
+applied only when the norm exceeds ``max_norm``), skip-data in ``wrapper/wrapper.py:276-281``.
+State names for checkpoints are ``adam_m.<param>`` / ``adam_v.<param>`` and ``global_step``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, Optional, Union
+
+import torch
+import torch.distributed as dist
+
+from ...ops import functional as Fn
+from .. import parallel_state as ps
+from .param_grad_buffer import ParamAndGradBuffer, build_buffers
+
+
+class _Shard:
+    def __init__(self, buf: ParamAndGradBuffer, group, world: int, rank: int):
+        self.buf, self.group, self.world, self.rank = buf, group, world, rank
+        n = buf.ranges.numel
+        if n % world != 0:
+            raise ValueError(f"buffer {buf.name} ({n} elements) is not divisible by the shard count {world}")
+        self.len = n // world
+        self.begin = rank * self.len
+        self.end = self.begin + self.len
+        dev = buf.param_data.device
+        self.param = buf.param_data[self.begin:self.end]
+        self.grad = buf.grad_data[self.begin:self.end]
+        self.m = torch.zeros(self.len, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.len, dtype=torch.float32, device=dev)
+        self.bf16 = buf.param_data.dtype == torch.bfloat16
+        if self.bf16:
+            self.lo = torch.zeros(self.len, dtype=torch.int16, device=dev)
+        else:
+            self.lo = None
+            self.master = self.param.float().clone() if buf.param_data.dtype != torch.float32 else None
+
+    def clip(self, lo, hi):
+        return max(0, min(hi, self.end) - max(lo, self.begin))
+
+    def local(self, lo, hi):
+        a, b = max(lo, self.begin), min(hi, self.end)
+        if b <= a:
+            return None
+        return a - self.begin, b - self.begin
+
+
+class DistributedOptimizer:
+    """AdamW over the flat buffers of ``model``.
+
+    Args:
+        learning_rate: float or a callable ``step -> lr`` (steps count from 1).
+        max_grad_norm: clip threshold (0 disables); skip_threshold: skip the update when the global norm
+        is at least this (0 disables); non-finite norms always skip.
+    """
+
+    def __init__(self, model: torch.nn.Module, *, learning_rate: Union[float, Callable[[int], float]] = 1e-4,
+                 betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
+                 skip_threshold: float = 0.0, grad_dtype: torch.dtype = torch.float32,
+                 tensor_parallel: Optional[int] = None, sequence_parallel: bool = False,
+                 shard_optimizer: bool = True):
+        self.model = model
+        self.lr = learning_rate
+        self.beta1, self.beta2 = betas
+        self.eps, self.wd = eps, weight_decay
+        self.max_grad_norm, self.skip_threshold = max_grad_norm, skip_threshold
+        self.global_step = 0
+        self.tp = tensor_parallel if tensor_parallel is not None else ps.get_tensor_model_parallel_world_size()
+        self.sequence_parallel = sequence_parallel
+        dp = ps.get_data_parallel_world_size(with_context_parallel=True) if shard_optimizer else 1
+        edp = ps.get_expert_data_parallel_world_size() if shard_optimizer else 1
+        self.buffers = build_buffers(model, tp=self.tp, sequence_parallel=sequence_parallel, grad_dtype=grad_dtype,
+                                     dense_pad=dp, expert_pad=edp)
+        self.shards: Dict[str, _Shard] = {}
+        for name, buf in self.buffers.items():
+            if name.startswith("expert"):
+                grp, world, rank = ps.get_expert_data_parallel_group(), edp, ps.get_expert_data_parallel_rank() if edp > 1 else 0
+            else:
+                grp, world = ps.get_data_parallel_group(with_context_parallel=True), dp
+                rank = ps.get_data_parallel_rank(with_context_parallel=True) if dp > 1 else 0
+            self.shards[name] = _Shard(buf, grp, world, rank)
+        dev = next(iter(self.buffers.values())).param_data.device
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._dup_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.skipped = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the fp32 master starts as the exact value of the bf16 parameter, i.e. remainder 0
+
+    # ---------------------------------------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = True):
+        for buf in self.buffers.values():
+            buf.zero_grad()
+        for p in self.model.parameters():
+            p.grad = None
+
+    def current_lr(self) -> float:
+        return float(self.lr(self.global_step) if callable(self.lr) else self.lr)
+
+    # ---------------------------------------------------------------------------------------------
+    def reduce_gradients(self):
+        """Fold stray autograd grads, all-reduce SP-replicated grads over TP, reduce-scatter over DP."""
+        tp_group = ps.get_tensor_model_parallel_group()
+        for name, buf in self.buffers.items():
+            buf.collect_autograd_grads()
+            r = buf.ranges
+            if self.tp > 1 and self.sequence_parallel and r.sp_end > r.sp_begin and tp_group is not None:
+                dist.all_reduce(buf.grad_data[r.sp_begin:r.sp_end], group=tp_group)
+            sh = self.shards[name]
+            if sh.world > 1:
+                dist.reduce_scatter_tensor(sh.grad, buf.grad_data, op=dist.ReduceOp.SUM, group=sh.group)
+
+    def _global_sumsq(self):
+        self.sumsq.zero_()
+        self._dup_sumsq.zero_()
+        for name, sh in self.shards.items():
+            Fn.grad_sumsq(sh.grad, self.sumsq, accumulate=True)
+            r = sh.buf.ranges
+            loc = sh.local(r.dup_begin, r.dup_end) if self.tp > 1 else None
+            if loc is not None:
+                Fn.grad_sumsq(sh.grad[loc[0]:loc[1]], self._dup_sumsq, accumulate=True)
+        if self.tp > 1:
+            # TP-replicated parameters appear on every TP rank: count them once
+            self.sumsq.sub_(self._dup_sumsq * (1.0 - 1.0 / self.tp))
+        world = ps.get_world_group()
+        if world is not None and dist.is_initialized() and dist.get_world_size() > 1:
+            # every rank's shard is disjoint across DP; TP/PP ranks hold different parameters
+            dist.all_reduce(self.sumsq, group=world)
+        return self.sumsq
+
+    def step(self, grad_scale: float = 1.0):
+        """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""
+        self.reduce_gradients()
+        self._global_sumsq()
+        self.global_step += 1
+        lr = self.current_lr()
+        self.skipped.zero_()
+        for name, sh in self.shards.items():
+            r = sh.buf.ranges
+            d_end = max(0, min(r.decay_end, sh.end) - sh.begin)
+            if sh.bf16:
+                Fn.adamw_step(sh.param, sh.lo, sh.m, sh.v, sh.grad, lr=lr, beta1=self.beta1, beta2=self.beta2,
+                              eps=self.eps, weight_decay=self.wd, step=self.global_step, decay_end=d_end,
+                              sumsq=self.sumsq, skipped=self.skipped, max_norm=self.max_grad_norm,
+                              skip_threshold=self.skip_threshold, grad_scale=grad_scale)
+            else:
+                self._step_fp32(sh, lr, d_end, grad_scale)
+            if sh.world > 1:
+                dist.all_gather_into_tensor(sh.buf.param_data, sh.param.clone(), group=sh.group)
+        return self.sumsq
+
+    def _step_fp32(self, sh: _Shard, lr, d_end, grad_scale):
+        ss = self.sumsq
+        nrm = ss.sqrt() * abs(grad_scale)
+        bad = ~torch.isfinite(ss)
+        if self.skip_threshold > 0:
+            bad = bad | (nrm >= self.skip_threshold)
+        clip = torch.ones_like(nrm)
+        if self.max_grad_norm > 0:
+            clip = torch.where(nrm >= self.max_grad_norm, self.max_grad_norm / (nrm + 1e-6), clip)
+        keep = (~bad).float()
+        g = sh.grad.float() * (clip * grad_scale)
+        t = self.global_step
+        bc1, bc2 = 1 - self.beta1 ** t, 1 - self.beta2 ** t
+        m_new = self.beta1 * sh.m + (1 - self.beta1) * g
+        v_new = self.beta2 * sh.v + (1 - self.beta2) * g * g
+        w = sh.master if sh.master is not None else sh.param
+        w_new = w.clone()
+        w_new[:d_end] *= (1 - lr * self.wd)
+        w_new -= (lr / bc1) * m_new / ((v_new / bc2).sqrt() + self.eps)
+        sh.m.copy_(torch.where(bad, sh.m, m_new))
+        sh.v.copy_(torch.where(bad, sh.v, v_new))
+        w.copy_(torch.where(bad, w, w_new))
+        if sh.master is not None:
+            sh.param.copy_(w)
+        self.skipped.add_(bad.to(torch.int32))
+        del keep
+
+    # ---------------------------------------------------------------------------------------------
+    def global_norm(self, grad_scale: float = 1.0) -> torch.Tensor:
+        """Norm of the last step's gradients (device scalar)."""
+        return self.sumsq.sqrt() * abs(grad_scale)
+
+    # ---- checkpoint -------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        """Per-parameter optimizer state of this rank's shard, keyed like the reference's checkpoints.
+        Values are flat slices ``(tensor, offset_in_param)`` so that shards can be merged on load."""
+        out = {"global_step": self.global_step, "shards": {}}
+        for name, sh in self.shards.items():
+            out["shards"][name] = {"begin": sh.begin, "end": sh.end, "m": sh.m, "v": sh.v,
+                                   "lo": sh.lo, "master": getattr(sh, "master", None)}
+        return out
+
+    def named_states(self) -> Dict[str, torch.Tensor]:
+        """``adam_m.<param>`` / ``adam_v.<param>`` (and ``master_lo.<param>``) views for unsharded runs."""
+        out: Dict[str, torch.Tensor] = {}
+        for name, sh in self.shards.items():
+            if sh.world != 1:
+                continue
+            for pname, (o, cnt, shape) in sh.buf.index.items():
+                out[f"adam_m.{pname}"] = sh.m[o:o + cnt].view(shape)
+                out[f"adam_v.{pname}"] = sh.v[o:o + cnt].view(shape)
+                if sh.lo is not None:
+                    out[f"master_lo.{pname}"] = sh.lo[o:o + cnt].view(shape)
+        return out
+
+    def load_named_states(self, states: Dict[str, torch.Tensor], global_step: Optional[int] = None):
+        for name, sh in self.shards.items():
+            for pname, (o, cnt, shape) in sh.buf.index.items():
+                lo_, hi_ = max(o, sh.begin), min(o + cnt, sh.end)
+                if hi_ <= lo_:
+                    continue
+                for key, dst in (("adam_m", sh.m), ("adam_v", sh.v), ("master_lo", sh.lo)):
+                    src = states.get(f"{key}.{pname}")
+                    if src is None or dst is None:
+                        continue
+                    flat = src.reshape(-1)
+                    dst[lo_ - sh.begin:hi_ - sh.begin].copy_(flat[lo_ - o:hi_ - o])
+        if global_step is not None:
+            self.global_step = int(global_step)
+
+    def reload_model_params(self):
+        """Re-derive the master remainder after parameters were overwritten (checkpoint load)."""
+        for sh in self.shards.values():
+            if sh.bf16:
+                sh.lo.zero_()
+            elif sh.master is not None:
+                sh.master.copy_(sh.param.float())

@@ -1,0 +1,64 @@
+"""One optimisation step: micro-batch loop (gradient accumulation), gradient reduction, clipping, update.
+
+Counterpart of the reference's ``MFTrainOneStepCell`` / ``MFPipelineWithLossScaleCell``
+(``wrapper/wrapper.py:103-292,479-673``): forward → backward → (unscale) → data-parallel reduce →
+overflow / spike check → global-norm clip → optimizer, returning
+``(loss, overflow, loss_scale, lr, global_norm)``. Gradients accumulate in the flat fp32 buffer across
+micro-batches; the check and the clip happen inside the fused AdamW kernel from device scalars, so the
+step launches without waiting for the host.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Optional
+
+import torch
+
+from .. import parallel_state as ps
+from .optimizer import DistributedOptimizer
+
+
+class TrainOneStep:
+    def __init__(self, model: torch.nn.Module, optimizer: DistributedOptimizer, *, micro_batch_size: int = 1,
+                 loss_scale: float = 1.0, forward_fn: Optional[Callable] = None):
+        self.model, self.optimizer = model, optimizer
+        self.micro_batch_size = micro_batch_size
+        self.loss_scale = loss_scale
+        self.forward_fn = forward_fn or (lambda m, b: m(b["input_ids"], b["labels"], b.get("loss_mask"),
+                                                        b.get("position_ids")))
+        self._loss_acc = None
+
+    def __call__(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """``batch`` holds this data-parallel rank's samples: ``input_ids``/``labels`` ``[n, S]`` (device tensors)."""
+        model, opt = self.model, self.optimizer
+        n = batch["input_ids"].shape[0]
+        mbs = self.micro_batch_size
+        if n % mbs:
+            raise ValueError(f"local batch {n} is not a multiple of the micro batch size {mbs}")
+        n_mb = n // mbs
+        opt.zero_grad()
+        total = torch.zeros((), dtype=torch.float32, device=batch["input_ids"].device)
+        per_token = getattr(model, "config", None) is not None and getattr(model.config, "calculate_per_token_loss", False)
+        den_total = torch.zeros_like(total)
+        for i in range(n_mb):
+            mb = {k: v[i * mbs:(i + 1) * mbs] for k, v in batch.items() if v is not None}
+            out = self.forward_fn(model, mb)
+            if per_token:
+                num, den = out
+                (num * self.loss_scale).backward()
+                total += num.detach()
+                den_total += den.detach()
+            else:
+                (out * (self.loss_scale / n_mb)).backward()
+                total += out.detach() / n_mb
+        dp = ps.get_data_parallel_world_size(with_context_parallel=True)
+        scale = 1.0 / (dp * self.loss_scale)
+        if per_token:
+            # normalise by the number of target tokens over all micro-batches and data-parallel ranks
+            import torch.distributed as dist
+            if dp > 1:
+                dist.all_reduce(den_total, group=ps.get_data_parallel_group(with_context_parallel=True))
+            scale = float(1.0 / (den_total.item() * self.loss_scale + 1e-8))
+            total = total / (den_total / dp + 1e-8)
+        opt.step(grad_scale=scale)
+        return {"loss": total, "global_norm": opt.global_norm(scale), "skipped": opt.skipped,
+                "lr": opt.current_lr(), "loss_scale": self.loss_scale}

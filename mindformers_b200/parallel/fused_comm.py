@@ -1,0 +1,54 @@
+"""Fused compute + collective paths over NVLink peer memory (front-end).
+
+``enabled`` / ``moe_enabled`` decide per call whether the fused kernels can serve it; otherwise the
+layers fall back to the NCCL collectives of ``mappings``. The kernels themselves live in
+``ops/csrc/fused_comm.cu`` and work on symmetric buffers registered through ``parallel/symm_mem.py``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import parallel_state as ps
+
+_FORCE_OFF = False
+
+
+def set_enabled(flag: bool):
+    """Global switch (the NCCL baseline of the benchmark turns the fused paths off)."""
+    global _FORCE_OFF
+    _FORCE_OFF = not flag
+
+
+def _runtime_ready() -> bool:
+    from . import symm_mem
+    return symm_mem.is_ready()
+
+
+def enabled(config, x: torch.Tensor) -> bool:
+    if _FORCE_OFF or not getattr(config, "fused_tp_comm", False) or not x.is_cuda:
+        return False
+    if ps.get_tensor_model_parallel_world_size() == 1:
+        return False
+    return _runtime_ready()
+
+
+def moe_enabled(config, x: torch.Tensor) -> bool:
+    if _FORCE_OFF or not getattr(config, "fused_moe_comm", False) or not x.is_cuda:
+        return False
+    if ps.get_expert_model_parallel_world_size() == 1:
+        return False
+    return _runtime_ready() and False
+
+
+def allgather_linear(x, w):
+    from . import fused_tp
+    return fused_tp.allgather_linear(x, w)
+
+
+def linear_reduce_scatter(x, w):
+    from . import fused_tp
+    return fused_tp.linear_reduce_scatter(x, w)
+
+
+def moe_dispatch_experts_combine(layer, hidden, probs, ids):
+    raise NotImplementedError

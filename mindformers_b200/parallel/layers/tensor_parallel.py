@@ -1,0 +1,227 @@
+"""Tensor-parallel linear layers and the vocab-parallel embedding.
+
+API of the reference's ``training_graph/tensor_parallel/layers.py`` (``VocabParallelEmbedding`` :39,
+``ColumnParallelLinear`` :106, ``RowParallelLinear`` :283, ``LinearNoTP`` :439) and of
+``inference/tensor_parallel/layers.py`` (:44-659), one implementation for training and inference.
+Weights are ``[out, in]``; ``forward`` returns ``(output, bias)`` with the bias returned instead of
+added when ``skip_bias_add`` is set. Under sequence parallelism the column layer all-gathers tokens
+before its GEMM and the row layer reduce-scatters after it; with ``config.fused_tp_comm`` those pairs
+run as one kernel over NVLink peer memory (see ``parallel/fused_comm.py``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Optional
+
+import torch
+import torch.nn as nn
+
+from ...ops import functional as Fn
+from .. import mappings as M
+from .. import parallel_state as ps
+
+
+def shard_sections(w: torch.Tensor, sections, dim: int, rank: int, world: int) -> torch.Tensor:
+    """Split ``w`` along ``dim`` into ``sections`` (e.g. q|k|v or gate|up), shard each over ``world``
+    ranks and concatenate this rank's pieces, so every rank holds its slice of every section."""
+    if world == 1:
+        return w
+    parts = []
+    for piece in torch.split(w, list(sections), dim=dim):
+        if piece.shape[dim] % world != 0:
+            raise ValueError(f"section of size {piece.shape[dim]} is not divisible by {world}")
+        parts.append(piece.chunk(world, dim=dim)[rank])
+    return torch.cat(parts, dim=dim).contiguous()
+
+
+def _init_weight(shape, init_method, dtype, device, partition_dim=None, full_shape=None, rank=0, world=1,
+                 sections=None):
+    """Initialise the full matrix with a fixed generator state, then keep this rank's slice, so the
+    values do not depend on the tensor-parallel size."""
+    w = torch.empty(full_shape or shape, dtype=torch.float32, device=device)
+    init_method(w)
+    if world > 1 and partition_dim is not None:
+        if sections:
+            w = shard_sections(w, sections, partition_dim, rank, world)
+        else:
+            w = w.chunk(world, dim=partition_dim)[rank].contiguous()
+    return nn.Parameter(w.to(dtype=dtype))
+
+
+def _mark_tp(param, is_parallel, dim):
+    param.tensor_model_parallel = is_parallel
+    param.partition_dim = dim if is_parallel else -1
+    param.partition_stride = 1
+
+
+def default_init(std=0.02):
+    def _f(t):
+        return nn.init.normal_(t, mean=0.0, std=std)
+    return _f
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Embedding table sharded over the vocabulary; out-of-shard ids give zero rows that the
+    all-reduce (or reduce-scatter under sequence parallelism) fills in."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, *, config, init_method: Callable = None,
+                 reduce_scatter_embeddings: bool = False):
+        super().__init__()
+        self.tp = ps.get_tensor_model_parallel_world_size()
+        self.rank = ps.get_tensor_model_parallel_rank()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.reduce_scatter_embeddings = reduce_scatter_embeddings
+        per = math.ceil(num_embeddings / self.tp)
+        self.vocab_start = self.rank * per
+        self.vocab_end = min(num_embeddings, self.vocab_start + per)
+        self.padded_rows = per
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.init_method_std)
+        full = torch.zeros((per * self.tp, embedding_dim), dtype=torch.float32, device=dev)
+        init(full[:num_embeddings])
+        self.weight = nn.Parameter(full[self.vocab_start:self.vocab_start + per].to(dtype=config.params_dtype))
+        _mark_tp(self.weight, self.tp > 1, 0)
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        flat = input_ids.reshape(-1)
+        out = Fn.embedding(flat, self.weight, self.vocab_start)
+        if self.tp > 1:
+            if self.reduce_scatter_embeddings:
+                out = M.reduce_scatter_to_sequence_parallel_region(out)
+            else:
+                out = M.reduce_from_tensor_model_parallel_region(out)
+        return out
+
+
+class ColumnParallelLinear(nn.Module):
+    """``Y = X W^T`` with ``W`` split along its output rows."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
+                 bias: bool = False, gather_output: bool = False, skip_bias_add: bool = False,
+                 skip_weight_param_allocation: bool = False, is_expert: bool = False, tp_group=None,
+                 stride: int = 1, partition_sections=None):
+        super().__init__()
+        self.config = config
+        self.tp = 1 if is_expert and config.expert_tensor_parallel_size == 1 else ps.get_tensor_model_parallel_world_size()
+        self.rank = ps.get_tensor_model_parallel_rank() if self.tp > 1 else 0
+        if output_size % self.tp != 0:
+            raise ValueError(f"output_size {output_size} is not divisible by the tensor-parallel size {self.tp}")
+        self.input_size, self.output_size = input_size, output_size
+        self.output_size_per_partition = output_size // self.tp
+        self.gather_output, self.skip_bias_add = gather_output, skip_bias_add
+        self.sequence_parallel = bool(config.sequence_parallel) and self.tp > 1
+        self.is_expert = is_expert
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.init_method_std)
+        if skip_weight_param_allocation:
+            self.weight = None
+        else:
+            self.weight = _init_weight((self.output_size_per_partition, input_size), init, config.params_dtype, dev,
+                                       partition_dim=0, full_shape=(output_size, input_size), rank=self.rank,
+                                       world=self.tp, sections=partition_sections)
+            _mark_tp(self.weight, self.tp > 1, 0)
+            self.weight.partition_stride = stride
+            self.weight.partition_sections = tuple(partition_sections) if partition_sections else None
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=config.params_dtype, device=dev))
+            _mark_tp(self.bias, self.tp > 1, 0)
+            self.bias.partition_sections = tuple(partition_sections) if partition_sections else None
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor, weight: Optional[torch.Tensor] = None):
+        w = self.weight if weight is None else weight
+        bias = None if self.skip_bias_add else self.bias
+        if self.tp > 1:
+            if self.sequence_parallel:
+                from .. import fused_comm
+                if fused_comm.enabled(self.config, x):
+                    y = fused_comm.allgather_linear(x, w)
+                else:
+                    y = Fn.linear(M.gather_from_sequence_parallel_region(x), w)
+            else:
+                y = Fn.linear(M.copy_to_tensor_model_parallel_region(x), w)
+        else:
+            y = Fn.linear(x, w)
+        if bias is not None:
+            y = y + bias
+        if self.gather_output and self.tp > 1:
+            y = M.gather_from_tensor_model_parallel_region(y)
+        return y, (self.bias if self.skip_bias_add else None)
+
+
+class RowParallelLinear(nn.Module):
+    """``Y = X W^T`` with ``W`` split along its input columns; partial sums are reduced over TP."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
+                 bias: bool = False, input_is_parallel: bool = True, skip_bias_add: bool = False,
+                 is_expert: bool = False, delay_allreduce: bool = False):
+        super().__init__()
+        self.config = config
+        self.tp = 1 if is_expert and config.expert_tensor_parallel_size == 1 else ps.get_tensor_model_parallel_world_size()
+        self.rank = ps.get_tensor_model_parallel_rank() if self.tp > 1 else 0
+        if input_size % self.tp != 0:
+            raise ValueError(f"input_size {input_size} is not divisible by the tensor-parallel size {self.tp}")
+        self.input_size, self.output_size = input_size, output_size
+        self.input_size_per_partition = input_size // self.tp
+        self.input_is_parallel, self.skip_bias_add = input_is_parallel, skip_bias_add
+        self.sequence_parallel = bool(config.sequence_parallel) and self.tp > 1
+        self.delay_allreduce = delay_allreduce
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.output_layer_init_std)
+        self.weight = _init_weight((output_size, self.input_size_per_partition), init, config.params_dtype, dev,
+                                   partition_dim=1, full_shape=(output_size, input_size), rank=self.rank,
+                                   world=self.tp)
+        _mark_tp(self.weight, self.tp > 1, 1)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(output_size, dtype=config.params_dtype, device=dev))
+            _mark_tp(self.bias, False, -1)
+            self.bias.sequence_parallel = self.sequence_parallel
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor):
+        if not self.input_is_parallel and self.tp > 1:
+            x = x.chunk(self.tp, dim=-1)[self.rank].contiguous()
+        if self.tp > 1 and not self.delay_allreduce:
+            if self.sequence_parallel:
+                from .. import fused_comm
+                if fused_comm.enabled(self.config, x):
+                    y = fused_comm.linear_reduce_scatter(x, self.weight)
+                else:
+                    y = M.reduce_scatter_to_sequence_parallel_region(Fn.linear(x, self.weight))
+            else:
+                y = M.reduce_from_tensor_model_parallel_region(Fn.linear(x, self.weight))
+        else:
+            y = Fn.linear(x, self.weight)
+        if self.bias is not None and not self.skip_bias_add:
+            y = y + self.bias
+        return y, (self.bias if self.skip_bias_add else None)
+
+
+class LinearNoTP(nn.Module):
+    """Replicated linear layer (the reference's ``LinearNoTP`` / ``ReplicatedLinear``)."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
+                 bias: bool = False, skip_bias_add: bool = False, params_dtype=None):
+        super().__init__()
+        self.config = config
+        self.skip_bias_add = skip_bias_add
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.init_method_std)
+        dtype = params_dtype or config.params_dtype
+        self.weight = _init_weight((output_size, input_size), init, dtype, dev)
+        _mark_tp(self.weight, False, -1)
+        self.weight.sequence_parallel = bool(config.sequence_parallel)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(output_size, dtype=dtype, device=dev))
+            self.bias.sequence_parallel = bool(config.sequence_parallel)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        y = Fn.linear(x, self.weight, None if self.skip_bias_add else self.bias)
+        return y, (self.bias if self.skip_bias_add else None)
+
+
+ReplicatedLinear = LinearNoTP

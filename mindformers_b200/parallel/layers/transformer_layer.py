@@ -1,0 +1,139 @@
+"""Pre-LN transformer layer and the layer stack.
+
+Reference: ``training_graph/transformer/transformer_layer.py`` (:74-250: input_layernorm →
+self_attention → residual add → pre_mlp_layernorm → mlp → residual add, returning the extra (MoE) loss)
+and ``transformer_block.py`` (:79-197: per-layer specs, final norm, loss threading), plus the layer →
+pipeline-stage assignment with ``offset`` of ``training_graph/transformer/utils.py:93-159``.
+
+The residual add of each sub-layer is folded into the following RMSNorm kernel: a layer receives the
+pending sub-layer output and the residual stream and returns the same pair.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from .. import parallel_state as ps
+from .attention import AttnMeta, MLASelfAttention, SelfAttention
+from .mlp import MLP
+from .moe import MoELayer
+from .norm import build_norm
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, config, layer_number: int = 1, is_moe: bool = False):
+        super().__init__()
+        self.config = config
+        self.layer_number = layer_number
+        self.input_layernorm = build_norm(config)
+        attn_cls = MLASelfAttention if config.multi_latent_attention else SelfAttention
+        self.self_attention = attn_cls(config, layer_number)
+        self.pre_mlp_layernorm = build_norm(config)
+        self.is_moe = is_moe
+        self.mlp = MoELayer(config, layer_number) if is_moe else MLP(config)
+        if config.sandwich_norm:
+            self.post_attn_layernorm = build_norm(config)
+            self.post_mlp_layernorm = build_norm(config)
+        else:
+            self.post_attn_layernorm = self.post_mlp_layernorm = None
+
+    def forward(self, pending, residual, rotary, meta: AttnMeta):
+        """``pending``: sub-layer output not yet added to ``residual`` (``residual`` None for the first layer)."""
+        if residual is None:
+            residual = pending
+            normed = self.input_layernorm(pending)
+        else:
+            normed, residual = self.input_layernorm(pending, residual)
+        attn_out, _ = self.self_attention(normed, rotary, meta)
+        if self.post_attn_layernorm is not None:
+            attn_out = self.post_attn_layernorm(attn_out)
+        normed, residual = self.pre_mlp_layernorm(attn_out, residual)
+        aux = None
+        if self.is_moe:
+            mlp_out, aux = self.mlp(normed)
+        else:
+            mlp_out, _ = self.mlp(normed)
+        if self.post_mlp_layernorm is not None:
+            mlp_out = self.post_mlp_layernorm(mlp_out)
+        return mlp_out, residual, aux
+
+
+def pipeline_layer_split(num_layers: int, pp: int, vpp: int = 1, offset=0) -> List[List[List[int]]]:
+    """Layer ids of every (pp stage, virtual chunk). ``offset`` adds/removes layers per stage
+    (list of pp values, or vpp lists of pp values), as the reference's ``LayerSetting`` does."""
+    vpp = vpp or 1
+    chunks = pp * vpp
+    base = num_layers // chunks
+    if isinstance(offset, int):
+        if offset != 0:
+            raise ValueError("a scalar offset must be 0; give a list with one value per stage")
+        off = [[0] * pp for _ in range(vpp)]
+    else:
+        off = [list(o) for o in offset] if offset and isinstance(offset[0], (list, tuple)) else [list(offset)]
+        if len(off) != vpp or any(len(o) != pp for o in off):
+            raise ValueError(f"offset must hold {vpp} x {pp} values, got {offset!r}")
+    counts = [[base + off[v][s] for s in range(pp)] for v in range(vpp)]
+    if sum(sum(c) for c in counts) != num_layers:
+        raise ValueError(f"layers per stage {counts} do not add up to num_layers={num_layers}")
+    out = [[[] for _ in range(vpp)] for _ in range(pp)]
+    nxt = 0
+    for v in range(vpp):
+        for s in range(pp):
+            out[s][v] = list(range(nxt, nxt + counts[v][s]))
+            nxt += counts[v][s]
+    return out
+
+
+class TransformerBlock(nn.Module):
+    """The layers owned by this pipeline stage (and virtual chunk) plus, on the last stage, the final norm."""
+
+    def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
+        super().__init__()
+        self.config = config
+        pp = ps.get_pipeline_model_parallel_world_size()
+        pp_rank = ps.get_pipeline_model_parallel_rank()
+        vpp = config.virtual_pipeline_model_parallel_size or 1
+        split = pipeline_layer_split(config.num_layers, pp, vpp, config.offset or 0)
+        self.layer_ids = split[pp_rank][vp_stage or 0]
+        pattern = config.moe_layer_pattern()
+        self.layers = nn.ModuleList(
+            [TransformerLayer(config, layer_number=i + 1, is_moe=bool(pattern[i])) for i in self.layer_ids])
+        self.final_layernorm = build_norm(config) if post_process else None
+        self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
+        self._recompute_layers = self._resolve_recompute(config.recompute)
+
+    def _resolve_recompute(self, rc):
+        n = len(self.layer_ids)
+        if isinstance(rc, bool):
+            return n if rc else 0
+        if isinstance(rc, int):
+            return min(rc, n)
+        if isinstance(rc, (list, tuple)) and rc:
+            pp_rank = ps.get_pipeline_model_parallel_rank()
+            val = rc[pp_rank] if pp_rank < len(rc) else rc[-1]
+            if isinstance(val, (list, tuple)):
+                val = val[0]
+            return n if val is True else int(val or 0)
+        return 0
+
+    def forward(self, hidden, rotary, meta: AttnMeta):
+        pending, residual = hidden, None
+        aux_total = None
+        for idx, layer in enumerate(self.layers):
+            if self.training and idx < self._recompute_layers and torch.is_grad_enabled():
+                pending, residual, aux = checkpoint(layer, pending, residual, rotary, meta, use_reentrant=False)
+            else:
+                pending, residual, aux = layer(pending, residual, rotary, meta)
+            if aux is not None:
+                aux_total = aux if aux_total is None else aux_total + aux
+        if self.final_layernorm is not None:
+            if residual is None:
+                out = self.final_layernorm(pending)
+            else:
+                out, _ = self.final_layernorm(pending, residual)
+        else:
+            out = pending if residual is None else pending + residual
+        return out, aux_total

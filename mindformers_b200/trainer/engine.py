@@ -1,0 +1,73 @@
+"""``TrainingEngine``: model + sharded optimizer + step function behind one call.
+
+This is the object ``Trainer`` drives and the one a user calls for a custom loop::
+
+    engine = TrainingEngine.from_model_config(model_cfg, parallel=dict(tensor_model_parallel_size=2, ...))
+    loss = engine.train_step({"input_ids": pinned_ids, "labels": pinned_labels})   # host tensors in, float out
+
+``train_step`` copies the batch host→device (asynchronously from pinned memory), runs the micro-batch
+loop and the optimizer, and reads the loss back; ``train_step_device`` is the same without the copies.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Optional, Union
+
+import torch
+
+from ..models.presets import preset_is_mla
+from ..parallel import parallel_state as ps
+from ..parallel.distributed.optimizer import DistributedOptimizer
+from ..parallel.distributed.train_step import TrainOneStep
+from ..parallel.layers.gpt_model import GPTModel
+from ..parallel.transformer_config_utils import convert_to_transformer_config
+
+
+class TrainingEngine:
+    def __init__(self, model: torch.nn.Module, optimizer: DistributedOptimizer, micro_batch_size: int = 1,
+                 loss_scale: float = 1.0):
+        self.model = model
+        self.optimizer = optimizer
+        self.step_fn = TrainOneStep(model, optimizer, micro_batch_size=micro_batch_size, loss_scale=loss_scale)
+        self.device = next(model.parameters()).device
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    @classmethod
+    def from_model_config(cls, model_config: dict, *, parallel: Optional[dict] = None, device=None,
+                          learning_rate: Union[float, Callable] = 1e-4, betas=(0.9, 0.95), eps=1e-8,
+                          weight_decay: float = 0.1, max_grad_norm: float = 1.0, micro_batch_size: int = 1,
+                          seq_length: Optional[int] = None, dtype: str = "bfloat16", recompute=False,
+                          grad_dtype=torch.float32, **extra):
+        parallel = dict(parallel or {})
+        cfgd = dict(model_config)
+        cfgd.update(parallel)
+        cfgd.setdefault("params_dtype", dtype)
+        cfgd.setdefault("compute_dtype", dtype)
+        if seq_length:
+            cfgd["seq_length"] = seq_length
+            cfgd["max_position_embeddings"] = max(seq_length, 1)
+        cfgd["recompute"] = recompute
+        cfgd.update(extra)
+        tcfg = convert_to_transformer_config(cfgd, is_mla_model=preset_is_mla(cfgd))
+        tcfg.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        model = GPTModel(tcfg)
+        opt = DistributedOptimizer(model, learning_rate=learning_rate, betas=betas, eps=eps, weight_decay=weight_decay,
+                                   max_grad_norm=max_grad_norm, grad_dtype=grad_dtype,
+                                   sequence_parallel=bool(tcfg.sequence_parallel))
+        return cls(model, opt, micro_batch_size=micro_batch_size)
+
+    def train_step_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        self.model.train()
+        return self.step_fn(batch)
+
+    def train_step(self, host_batch: Dict[str, torch.Tensor]) -> float:
+        dev_batch = {}
+        for k, v in host_batch.items():
+            if v is None:
+                continue
+            dev_batch[k] = v.to(self.device, non_blocking=True)
+            self.h2d_bytes = sum(t.numel() * t.element_size() for t in host_batch.values() if t is not None)
+        out = self.train_step_device(dev_batch)
+        loss = out["loss"].float().cpu()          # device→host read of the step's result
+        self.d2h_bytes = loss.numel() * loss.element_size()
+        return float(loss)

@@ -1,0 +1,102 @@
+import os
+import textwrap
+
+import pytest
+
+from mindformers_b200.tools.register import (ConfigTemplate, MindFormerConfig, MindFormerModuleType,
+                                             MindFormerRegister, set_use_legacy)
+from mindformers_b200.tools.register.config import ActionDict, parse_value
+
+
+def _write(tmp_path, name, text):
+    p = tmp_path / name
+    p.write_text(textwrap.dedent(text))
+    return str(p)
+
+
+def test_yaml_inheritance_and_attribute_access(tmp_path):
+    _write(tmp_path, "base.yaml", """
+        seed: 7
+        runner_config: {batch_size: 2, epochs: 3}
+        model: {model_config: {hidden_size: 64, num_layers: 2}}
+    """)
+    child = _write(tmp_path, "child.yaml", """
+        base_config: base.yaml
+        runner_config: {batch_size: 8}
+        model: {model_config: {num_layers: 4}}
+    """)
+    cfg = MindFormerConfig(child)
+    assert cfg.seed == 7
+    assert cfg.runner_config.batch_size == 8 and cfg.runner_config.epochs == 3
+    assert cfg.model.model_config.hidden_size == 64 and cfg.model.model_config.num_layers == 4
+    assert cfg.not_there is None
+    cfg.merge_from_dict({"model.model_config.num_layers": 6, "new.section.key": 1})
+    assert cfg.get_value("model.model_config.num_layers") == 6
+    assert cfg.new.section.key == 1
+    cfg.set_value("runner_config.epochs", 9)
+    assert cfg.to_dict()["runner_config"]["epochs"] == 9
+
+
+def test_circular_base_config_is_rejected(tmp_path):
+    _write(tmp_path, "a.yaml", "base_config: b.yaml\nx: 1\n")
+    b = _write(tmp_path, "b.yaml", "base_config: a.yaml\ny: 2\n")
+    with pytest.raises(ValueError):
+        MindFormerConfig(b)
+
+
+def test_parse_value_and_action_dict():
+    assert parse_value("1e-3") == 1e-3 and parse_value("True") is True and parse_value("[1,2]") == [1, 2]
+    assert parse_value("abc") == "abc" and parse_value("None") is None
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--options", nargs="+", action=ActionDict)
+    ns = ap.parse_args(["--options", "a.b=3", "c=hello"])
+    assert ns.options == {"a.b": 3, "c": "hello"}
+
+
+def test_template_defaults_and_strict_sections():
+    cfg = {"run_mode": "train", "parallel_config": {"data_parallel": 4}, "optimizer": {"type": "AdamW", "learning_rate": 1e-3}}
+    ConfigTemplate.apply_template(cfg)
+    assert cfg["parallel_config"]["model_parallel"] == 1 and cfg["parallel_config"]["data_parallel"] == 4
+    assert cfg["optimizer"]["betas"] == [0.9, 0.999] and cfg["optimizer"]["learning_rate"] == 1e-3
+    assert cfg["seed"] == 1 and cfg["callbacks"][0]["type"] == "MFLossMonitor"
+    with pytest.raises(KeyError):
+        ConfigTemplate.apply_template({"run_mode": "train", "parallel_config": {"bogus": 1}})
+    # predict mode drops the training sections; mcore mode drops moe_config
+    cfg = {"run_mode": "predict", "use_legacy": False, "optimizer": {"type": "AdamW"}, "moe_config": {"expert_num": 4}}
+    ConfigTemplate.apply_template(cfg)
+    assert "optimizer" not in cfg and "moe_config" not in cfg and "processor" in cfg
+
+
+def test_registry_roundtrip_and_mcore_prefix():
+    @MindFormerRegister.register(MindFormerModuleType.TOOLS, alias="_probe_tool")
+    class Probe:
+        def __init__(self, a=1, b=2):
+            self.a, self.b = a, b
+
+    assert MindFormerRegister.is_exist(MindFormerModuleType.TOOLS, "_probe_tool")
+    inst = MindFormerRegister.get_instance_from_cfg({"type": "_probe_tool", "a": 5}, MindFormerModuleType.TOOLS,
+                                                    default_args={"b": 9})
+    assert (inst.a, inst.b) == (5, 9)
+    with pytest.raises(ValueError):
+        MindFormerRegister.get_cls(MindFormerModuleType.TOOLS, "_missing_")
+
+    @MindFormerRegister.register(MindFormerModuleType.MODELS, alias="_ProbeModel", legacy=False)
+    class ProbeModel:
+        pass
+
+    set_use_legacy(False)
+    try:
+        assert MindFormerRegister.get_cls(MindFormerModuleType.MODELS, "_ProbeModel") is ProbeModel
+        assert "mcore__ProbeModel" in MindFormerRegister.registry[MindFormerModuleType.MODELS]
+    finally:
+        set_use_legacy(True)
+
+
+def test_auto_register_from_register_path(tmp_path, monkeypatch):
+    pkg = tmp_path / "plug"
+    pkg.mkdir()
+    (pkg / "mod.py").write_text("class Extra:\n    value = 3\n")
+    monkeypatch.setenv("REGISTER_PATH", str(tmp_path))
+    cls = MindFormerRegister.auto_register("plug.mod.Extra", MindFormerModuleType.TOOLS)
+    assert cls.value == 3 and MindFormerRegister.get_cls(MindFormerModuleType.TOOLS, "Extra") is cls

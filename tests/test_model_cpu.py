@@ -1,0 +1,193 @@
+"""CPU fp32 tests of the model stack, the optimizer and the parallel-state algebra."""
+import copy
+
+import pytest
+import torch
+
+from mindformers_b200.parallel.distributed.optimizer import DistributedOptimizer
+from mindformers_b200.parallel.distributed.train_step import TrainOneStep
+from mindformers_b200.parallel.layers.gpt_model import GPTModel
+from mindformers_b200.parallel.parallel_state import RankGenerator
+from mindformers_b200.parallel.transformer_config import MLATransformerConfig, TransformerConfig
+from mindformers_b200.parallel.transformer_config_utils import convert_to_transformer_config
+
+
+def tiny_llama_config(**kw):
+    base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=688,
+                vocab_size=1024, seq_length=128, max_position_embeddings=128, params_dtype="float32",
+                compute_dtype="float32", use_scaled_init=False, layernorm_epsilon=1e-5, rotary_base=10000.0,
+                pad_token_id=-1)
+    base.update(kw)
+    cfg = TransformerConfig(**base)
+    cfg.device = "cpu"
+    return cfg
+
+
+def hf_llama_reference_loss(model, ids):
+    """Independent re-statement of the tiny Llama forward in plain torch ops (fp32)."""
+    cfg = model.config
+    x = model.embedding.word_embeddings.weight[ids[:, :-1]]
+    B, S, H = x.shape
+    hd, nq, nkv = cfg.kv_channels, cfg.num_attention_heads, cfg.num_query_groups
+    inv = 1.0 / (cfg.rotary_base ** (torch.arange(0, hd, 2).float() / hd))
+    ang = torch.arange(S).float()[:, None] * inv[None]
+    cos, sin = torch.cat((ang.cos(), ang.cos()), -1), torch.cat((ang.sin(), ang.sin()), -1)
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.layernorm_epsilon) * w
+
+    def rot(t):
+        a, b = t[..., : hd // 2], t[..., hd // 2:]
+        return torch.cat((-b, a), -1)
+
+    for layer in model.decoder.layers:
+        h = rms(x, layer.input_layernorm.weight)
+        qkv = h @ layer.self_attention.linear_qkv.weight.t()
+        q, k, v = qkv.split([nq * hd, nkv * hd, nkv * hd], -1)
+        q = q.view(B, S, nq, hd)
+        k = k.view(B, S, nkv, hd)
+        v = v.view(B, S, nkv, hd)
+        q = q * cos[None, :, None] + rot(q) * sin[None, :, None]
+        k = k * cos[None, :, None] + rot(k) * sin[None, :, None]
+        k = k.repeat_interleave(nq // nkv, 2)
+        v = v.repeat_interleave(nq // nkv, 2)
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / hd ** 0.5
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+        o = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), v).reshape(B, S, nq * hd)
+        x = x + o @ layer.self_attention.linear_proj.weight.t()
+        h = rms(x, layer.pre_mlp_layernorm.weight)
+        gu = h @ layer.mlp.linear_fc1.weight.t()
+        g, u = gu.chunk(2, -1)
+        x = x + (torch.nn.functional.silu(g) * u) @ layer.mlp.linear_fc2.weight.t()
+    x = rms(x, model.decoder.final_layernorm.weight)
+    logits = x @ model.output_layer.weight.t()
+    return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
+
+
+def test_tiny_llama_matches_independent_reference_and_adamw():
+    torch.manual_seed(0)
+    model = GPTModel(tiny_llama_config())
+    assert sum(p.numel() for p in model.parameters()) == 1975552
+    ids = torch.randint(0, 1024, (2, 129), generator=torch.Generator().manual_seed(3))
+    loss = model(ids[:, :-1], ids[:, 1:])
+    ref = hf_llama_reference_loss(model, ids)
+    assert torch.allclose(loss, ref, atol=1e-5, rtol=1e-5)
+    # one fwd + bwd + AdamW(lr 1e-4) step against torch.optim.AdamW on a deep copy
+    twin = copy.deepcopy(model)
+    opt = DistributedOptimizer(model, learning_rate=1e-4, betas=(0.9, 0.999), weight_decay=0.0, max_grad_norm=0.0)
+    step = TrainOneStep(model, opt, micro_batch_size=2)
+    out = step({"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()})
+    topt = torch.optim.AdamW(twin.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    tl = twin(ids[:, :-1], ids[:, 1:])
+    tl.backward()
+    topt.step()
+    assert abs(out["loss"].item() - tl.item()) < 1e-6
+    for (n, a), (_, b) in zip(model.named_parameters(), twin.named_parameters()):
+        assert torch.allclose(a, b, atol=1e-6), n
+
+
+def test_training_is_bit_stable_across_runs():
+    def run():
+        torch.manual_seed(11)
+        m = GPTModel(tiny_llama_config())
+        opt = DistributedOptimizer(m, learning_rate=1e-3, max_grad_norm=1.0)
+        step = TrainOneStep(m, opt, micro_batch_size=1)
+        ids = torch.randint(0, 1024, (2, 65), generator=torch.Generator().manual_seed(5))
+        losses = [step({"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()})["loss"].item()
+                  for _ in range(3)]
+        return losses, [p.detach().clone() for p in m.parameters()]
+
+    l1, p1 = run()
+    l2, p2 = run()
+    assert l1 == l2 and l1[-1] < l1[0]
+    assert all(torch.equal(a, b) for a, b in zip(p1, p2))
+
+
+def test_gradient_accumulation_equals_large_batch():
+    torch.manual_seed(2)
+    a = GPTModel(tiny_llama_config())
+    b = copy.deepcopy(a)
+    ids = torch.randint(0, 1024, (4, 33))
+    batch = {"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()}
+    oa = DistributedOptimizer(a, learning_rate=1e-3)
+    ob = DistributedOptimizer(b, learning_rate=1e-3)
+    la = TrainOneStep(a, oa, micro_batch_size=4)(batch)["loss"]
+    lb = TrainOneStep(b, ob, micro_batch_size=1)(batch)["loss"]
+    assert abs(la.item() - lb.item()) < 1e-5
+    ga, gb = oa.buffers["dense"].grad_data, ob.buffers["dense"].grad_data
+    assert torch.allclose(ga, gb, atol=1e-6)
+    assert abs(oa.global_norm().item() - ob.global_norm().item()) < 1e-5
+
+
+def test_moe_mla_mtp_model_trains():
+    torch.manual_seed(4)
+    cfg = MLATransformerConfig(
+        num_layers=3, hidden_size=128, num_attention_heads=4, ffn_hidden_size=256, vocab_size=512, seq_length=64,
+        max_position_embeddings=64, params_dtype="float32", compute_dtype="float32", num_moe_experts=8,
+        moe_router_topk=2, moe_ffn_hidden_size=64, first_k_dense_replace=1, moe_shared_expert_intermediate_size=64,
+        q_lora_rank=32, kv_lora_rank=32, qk_head_dim=32, qk_pos_emb_head_dim=16, v_head_dim=32,
+        moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True, moe_aux_loss_coeff=1e-3,
+        rotary_scaling_factor=1.0, mtp_num_layers=1, moe_router_num_groups=4, moe_router_group_topk=2,
+        moe_router_topk_scaling_factor=2.5)
+    cfg.device = "cpu"
+    model = GPTModel(cfg)
+    names = {n for n, _ in model.named_parameters()}
+    for expect in ("decoder.layers.1.mlp.router.weight", "decoder.layers.1.mlp.experts.weight1",
+                   "decoder.layers.1.mlp.shared_experts.linear_fc1.weight", "decoder.layers.0.mlp.linear_fc1.weight",
+                   "decoder.layers.1.self_attention.linear_qb.weight", "decoder.layers.1.self_attention.linear_kvb.weight",
+                   "mtp.layers.0.eh_proj.weight", "mtp.layers.0.enorm.weight", "decoder.final_layernorm.weight"):
+        assert expect in names, expect
+    opt = DistributedOptimizer(model, learning_rate=2e-3)
+    step = TrainOneStep(model, opt, micro_batch_size=2)
+    ids = torch.randint(0, 512, (2, 65))
+    batch = {"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()}
+    losses = [step(batch)["loss"].item() for _ in range(5)]
+    assert losses[-1] < losses[0]
+    model.update_topk_bias()
+    bias = model.decoder.layers[1].mlp.router.expert_bias
+    assert bias.abs().max() > 0
+
+
+def test_moe_dispatch_matches_dense_loop():
+    from mindformers_b200.parallel.layers.moe import MoELayer
+    torch.manual_seed(6)
+    cfg = tiny_llama_config(num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=64, hidden_size=64,
+                            num_attention_heads=4, num_query_groups=4, ffn_hidden_size=128)
+    layer = MoELayer(cfg)
+    x = torch.randn(37, 64)
+    out, _ = layer(x)
+    probs, ids, _ = layer.router(x)
+    ref = torch.zeros_like(x)
+    for t in range(x.shape[0]):
+        for j in range(2):
+            e = ids[t, j].item()
+            h = x[t] @ layer.experts.weight1[e]
+            g, u = h.chunk(2)
+            ref[t] += probs[t, j] * ((torch.nn.functional.silu(g) * u) @ layer.experts.weight2[e])
+    assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_rank_generator_groups_are_orthogonal():
+    g = RankGenerator(tp=2, ep=1, dp=2, pp=2, cp=1)
+    assert g.get_ranks("tp") == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert g.get_ranks("dp") == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert g.get_ranks("pp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    flat = sorted(r for grp in g.get_ranks("tp-dp") for r in grp)
+    assert flat == list(range(8))
+    e = RankGenerator(tp=1, ep=4, dp=2, pp=1, cp=1)
+    assert e.get_ranks("ep") == [[0, 1, 2, 3], [4, 5, 6, 7]]
+
+
+def test_hf_config_conversion():
+    hf = dict(model_type="qwen3_moe", num_hidden_layers=4, hidden_size=64, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, intermediate_size=128, moe_intermediate_size=32, num_experts=8,
+              num_experts_per_tok=2, vocab_size=100, rms_norm_eps=1e-6, rope_theta=1e6, norm_topk_prob=True,
+              parallel_config=dict(model_parallel=1, expert_parallel=1, use_seq_parallel=False))
+    cfg = convert_to_transformer_config(hf)
+    assert cfg.num_layers == 4 and cfg.num_query_groups == 2 and cfg.kv_channels == 16
+    assert cfg.num_moe_experts == 8 and cfg.moe_router_topk == 2 and cfg.moe_ffn_hidden_size == 32
+    assert cfg.rotary_base == 1e6 and cfg.layernorm_epsilon == 1e-6
+    with pytest.raises(KeyError):
+        convert_to_transformer_config(dict(hf, num_layers=3))
+    with pytest.raises(ValueError):
+        convert_to_transformer_config(dict(hf, definitely_unknown_key=1))
