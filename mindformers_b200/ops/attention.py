@@ -1,21 +1,138 @@
-"""Front-end of the hand-written flash-attention kernels (``csrc/flash_attention.cu``)."""
+"""Front-end of the hand-written flash-attention kernels (``csrc/flash_attention.cu``).
+
+``flash_attention_packed`` is the training entry: it takes the packed ``[T, nq + 2·nkv, 128]`` buffer that
+the QKV projection (and the in-place RoPE kernel) produced and returns ``[T, nq·128]``; its backward
+writes one packed gradient buffer, so no concatenation or copy sits between attention and the QKV GEMM.
+"""
 from __future__ import annotations
+
+import math
 
 import torch
 
 from . import _lib
 
+HEAD_DIM = 128
+TILE = 128
+
+
+def _ok(seq: int, hd: int, nq: int, nkv: int, dtype) -> bool:
+    return dtype == torch.bfloat16 and hd == HEAD_DIM and seq % TILE == 0 and nq % nkv == 0
+
 
 def supported(q, k, v, causal) -> bool:
     """True when the native kernel covers this problem (bf16, head dim 128, equal q/k lengths)."""
-    lib = _lib.get_lib()
-    return hasattr(lib, "mfb_flash_attn_fwd") and _shape_ok(q, k, v)
+    return (q.is_cuda and v.shape[-1] == HEAD_DIM and q.shape[1] == k.shape[1]
+            and _ok(q.shape[1], q.shape[-1], q.shape[2], k.shape[2], q.dtype)
+            and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1)
 
 
-def _shape_ok(q, k, v) -> bool:
-    return (q.dtype == torch.bfloat16 and q.shape[-1] == 128 and v.shape[-1] == 128
-            and q.shape[1] == k.shape[1] and q.shape[1] % 128 == 0 and q.shape[2] % k.shape[2] == 0)
+def _scratch(device, nbytes: int) -> torch.Tensor:
+    from .functional import _scratch as _f32
+    return _f32(device, (nbytes + 3) // 4)
+
+
+def _fwd(q, k, v, B, S, nq, nkv, q_ld, k_ld, v_ld, causal, scale, need_lse=True):
+    T = B * S
+    out = torch.empty((T, nq * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, nq, S), dtype=torch.float32, device=q.device) if need_lse else None
+    st = _lib.status_word(q.device)
+    rc = _lib.get_lib().mfb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.ptr(lse),
+                                           B, S, S, nq, nkv, q_ld, k_ld, v_ld, out.stride(0), int(causal),
+                                           float(scale), st.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_flash_attn_fwd")
+    _lib.count_launch()
+    return out, lse
+
+
+class _PackedAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, packed, B, S, nq, nkv, causal, scale):
+        # packed: [T, nq + 2 nkv, 128] contiguous
+        W = packed.shape[1] * HEAD_DIM
+        q = packed
+        k = packed[:, nq:]
+        v = packed[:, nq + nkv:]
+        out, lse = _fwd(q, k, v, B, S, nq, nkv, W, W, W, causal, scale)
+        ctx.save_for_backward(packed, out, lse)
+        ctx.meta = (B, S, nq, nkv, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        packed, out, lse = ctx.saved_tensors
+        B, S, nq, nkv, causal, scale = ctx.meta
+        W = packed.shape[1] * HEAD_DIM
+        dout = dout.contiguous()
+        dpacked = torch.empty_like(packed)
+        lib = _lib.get_lib()
+        scratch = _scratch(packed.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, S, nq))
+        st = _lib.status_word(packed.device)
+        k, v = packed[:, nq:], packed[:, nq + nkv:]
+        dk, dv = dpacked[:, nq:], dpacked[:, nq + nkv:]
+        rc = lib.mfb_flash_attn_bwd(packed.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                    lse.data_ptr(), dpacked.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                    scratch.data_ptr(), B, S, nq, nkv, W, W, W, out.stride(0), dout.stride(0), W, W, W,
+                                    int(causal), float(scale), st.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "mfb_flash_attn_bwd")
+        _lib.count_launch(4)
+        return dpacked, None, None, None, None, None, None
+
+
+def packed_supported(packed: torch.Tensor, S: int, nq: int, nkv: int) -> bool:
+    return (packed.is_cuda and packed.is_contiguous() and packed.dim() == 3
+            and _ok(S, packed.shape[-1], nq, nkv, packed.dtype))
+
+
+def flash_attention_packed(packed: torch.Tensor, B: int, S: int, nq: int, nkv: int, causal: bool = True,
+                           scale: float = None) -> torch.Tensor:
+    """Attention over a packed qkv buffer ``[B·S, nq + 2·nkv, 128]`` → ``[B·S, nq·128]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
+    return _PackedAttnFn.apply(packed, B, S, nq, nkv, causal, scale)
+
+
+class _AttnFn(torch.autograd.Function):
+    """Separate q/k/v tensors ``[B, S, h, 128]`` (any row pitch); used by inference prefill and the ring steps."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        B, S, nq, _ = q.shape
+        nkv = k.shape[2]
+        out, lse = _fwd(q, k, v, B, S, nq, nkv, q.stride(1), k.stride(1), v.stride(1), causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta = (causal, scale)
+        return out.view(B, S, nq, HEAD_DIM)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        causal, scale = ctx.meta
+        B, S, nq, _ = q.shape
+        nkv = k.shape[2]
+        dout = dout.contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if not (dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()):
+            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+            dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        lib = _lib.get_lib()
+        scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, S, nq))
+        st = _lib.status_word(q.device)
+        rc = lib.mfb_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                    lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
+                                    B, S, nq, nkv, q.stride(1), k.stride(1), v.stride(1), out.stride(0),
+                                    nq * HEAD_DIM, dq.stride(1), dk.stride(1), dv.stride(1), int(causal), float(scale),
+                                    st.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "mfb_flash_attn_bwd")
+        _lib.count_launch(4)
+        return dq, dk, dv, None, None
 
 
 def flash_attention(q, k, v, causal=True, scale=None):
-    raise _lib.KernelLibraryError("flash attention kernel is not part of this build")
+    """q: ``[B, S, Hq, 128]``, k/v: ``[B, S, Hkv, 128]`` (views with unit inner stride and the batch and
+    sequence axes mergeable into one row axis) → ``[B, S, Hq, 128]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
+    for t in (q, k, v):
+        if t.stride(0) != t.shape[1] * t.stride(1) or t.stride(2) != HEAD_DIM:
+            return _AttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale)
+    return _AttnFn.apply(q, k, v, causal, scale)

@@ -462,20 +462,39 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> t
 # =================================================================================================
 # Cross-entropy (vocab-parallel aware)
 # =================================================================================================
+class _VocabParallelCERefFn(torch.autograd.Function):
+    """Plain-PyTorch vocab-parallel cross-entropy with an explicit backward (softmax - onehot)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, vocab_start, group):
+        lf = logits.float()
+        m = lf.max(-1).values
+        if group is not None:
+            torch.distributed.all_reduce(m, op=torch.distributed.ReduceOp.MAX, group=group)
+        e = (lf - m.unsqueeze(-1)).exp()
+        s = e.sum(-1)
+        local = labels - vocab_start
+        ok = (local >= 0) & (local < lf.shape[-1])
+        idx = local.clamp(0, lf.shape[-1] - 1)
+        tgt = lf.gather(-1, idx.unsqueeze(-1)).squeeze(-1) * ok
+        if group is not None:
+            torch.distributed.all_reduce(s, group=group)
+            torch.distributed.all_reduce(tgt, group=group)
+        ctx.save_for_backward(e / s.unsqueeze(-1), idx, ok)
+        ctx.in_dtype = logits.dtype
+        return m + s.log() - tgt
+
+    @staticmethod
+    def backward(ctx, g):
+        p, idx, ok = ctx.saved_tensors
+        grad = p.clone()
+        grad.scatter_add_(-1, idx.unsqueeze(-1), -ok.to(grad.dtype).unsqueeze(-1))
+        return (grad * g.unsqueeze(-1)).to(ctx.in_dtype), None, None, None
+
+
 def cross_entropy_reference(logits, labels, vocab_start=0, group=None):
     """Per-token NLL in fp32 from a (possibly vocab-sharded) logits tensor."""
-    lf = logits.float()
-    m = lf.max(-1).values
-    if group is not None:
-        torch.distributed.all_reduce(m, op=torch.distributed.ReduceOp.MAX, group=group)
-    s = (lf - m.unsqueeze(-1)).exp().sum(-1)
-    local = labels - vocab_start
-    ok = (local >= 0) & (local < lf.shape[-1])
-    tgt = lf.gather(-1, local.clamp(0, lf.shape[-1] - 1).unsqueeze(-1)).squeeze(-1) * ok
-    if group is not None:
-        torch.distributed.all_reduce(s, group=group)
-        torch.distributed.all_reduce(tgt, group=group)
-    return m + s.log() - tgt
+    return _VocabParallelCERefFn.apply(logits, labels, vocab_start, group)
 
 
 class _CrossEntropyFn(torch.autograd.Function):

@@ -141,7 +141,17 @@ class SelfAttention(nn.Module):
             packed = Fn.rope(packed if packed.is_contiguous() else packed.contiguous(), cos, sin, pos,
                              self.nq + self.nkv, self.rot_dim, self.config.rotary_interleaved)
             q, k, v = packed[:, :self.nq], packed[:, self.nq:self.nq + self.nkv], packed[:, self.nq + self.nkv:]
-        ctx = self.core_attention(q, k, v, meta)
+        ctx = None
+        if meta.cache is None and meta.cu_seqlens is None and ps.get_context_parallel_world_size() == 1 \
+                and Fn.get_attention_backend() != "sdpa":
+            from ...ops import attention as native
+            T = packed.shape[0]
+            S = T // meta.batch
+            if native.packed_supported(packed, S, self.nq, self.nkv):
+                ctx = native.flash_attention_packed(packed, meta.batch, S, self.nq, self.nkv, True,
+                                                    self.core_attention.scale)
+        if ctx is None:
+            ctx = self.core_attention(q, k, v, meta)
         out, bias = self.linear_proj(ctx)
         return out, bias
 

@@ -204,12 +204,16 @@ class GroupedMLP(nn.Module):
         self.E = num_local_experts
         H, F_ = config.hidden_size, config.moe_ffn_hidden_size
         dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
-        ep_rank = ps.get_expert_model_parallel_rank()
-        g = torch.Generator(device="cpu").manual_seed(1234 + 7919 * ep_rank + torch.initial_seed() % 100003)
-        w1 = torch.randn(self.E, H, 2 * F_, generator=g) * config.init_method_std
-        w2 = torch.randn(self.E, F_, H, generator=g) * config.output_layer_init_std
-        self.weight1 = nn.Parameter(w1.to(device=dev, dtype=config.params_dtype))
-        self.weight2 = nn.Parameter(w2.to(device=dev, dtype=config.params_dtype))
+        # draw the weights of all experts from the shared RNG stream, then keep this rank's slice, so the
+        # model does not depend on the expert-parallel size
+        ep, ep_rank = ps.get_expert_model_parallel_world_size(), ps.get_expert_model_parallel_rank()
+        lo, hi = ep_rank * self.E, (ep_rank + 1) * self.E
+        w1 = torch.empty(self.E * ep, H, 2 * F_, dtype=torch.float32, device=dev).normal_(0.0, config.init_method_std)
+        self.weight1 = nn.Parameter(w1[lo:hi].to(config.params_dtype).contiguous())
+        del w1
+        w2 = torch.empty(self.E * ep, F_, H, dtype=torch.float32, device=dev).normal_(0.0, config.output_layer_init_std)
+        self.weight2 = nn.Parameter(w2[lo:hi].to(config.params_dtype).contiguous())
+        del w2
         for p in (self.weight1, self.weight2):
             p.allreduce = False          # reduced over the expert-data-parallel group only
             p.is_expert = True

@@ -240,3 +240,30 @@ def test_adamw_matches_reference_and_master_is_exact():
     got = Fn.join_master(p, lo)
     assert torch.allclose(got, wr, atol=1e-6, rtol=1e-4)
     assert torch.allclose(p.float(), got, atol=0, rtol=2 ** -8)
+
+
+@pytest.mark.parametrize("B,S,nq,nkv,causal", [(1, 128, 2, 1, True), (2, 512, 4, 2, True), (1, 1024, 8, 2, True),
+                                               (1, 384, 2, 2, False)])
+def test_flash_attention_fwd_bwd(B, S, nq, nkv, causal):
+    from mindformers_b200.ops import attention as A
+    torch.manual_seed(12)
+    hd = 128
+    packed = (torch.randn(B * S, nq + 2 * nkv, hd, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    out = A.flash_attention_packed(packed, B, S, nq, nkv, causal=causal)
+    g = (torch.randn_like(out) * 0.1)
+    out.backward(g)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref_in = packed.detach().float().requires_grad_()
+    q = ref_in[:, :nq].reshape(B, S, nq, hd)
+    k = ref_in[:, nq:nq + nkv].reshape(B, S, nkv, hd)
+    v = ref_in[:, nq + nkv:].reshape(B, S, nkv, hd)
+    ref = Fn.attention_reference(q, k, v, causal=causal).reshape(B * S, nq * hd)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    gq, rq = packed.grad[:, :nq], ref_in.grad[:, :nq]
+    gk, rk = packed.grad[:, nq:nq + nkv], ref_in.grad[:, nq:nq + nkv]
+    gv, rv = packed.grad[:, nq + nkv:], ref_in.grad[:, nq + nkv:]
+    assert _rel_err(gv, rv) < 2e-2
+    assert _rel_err(gk, rk) < 2e-2
+    assert _rel_err(gq, rq) < 2e-2

@@ -1,0 +1,68 @@
+"""Multi-process (gloo, CPU) equivalence tests: every parallel layout must reproduce the single-process
+losses, global gradient norm and parameter updates of the same model, data and seed."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPT = os.path.join(ROOT, "tests", "dist", "run_parallel_equivalence.py")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(tmp_path, nproc, tag, *extra):
+    out = tmp_path / f"{tag}.json"
+    if nproc == 1:
+        cmd = [sys.executable, SCRIPT, "--out", str(out), *extra]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), SCRIPT, "--out", str(out), *extra]
+    env = dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert res.returncode == 0, res.stderr[-3000:]
+    return json.loads(out.read_text())
+
+
+def _close(a, b, tol):
+    assert len(a["losses"]) == len(b["losses"])
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < tol, (a["losses"], b["losses"])
+    assert abs(a["norm"] - b["norm"]) < tol * 10, (a["norm"], b["norm"])
+    for k, v in a["digest"].items():
+        assert abs(v - b["digest"][k]) < tol * 50, k
+
+
+@pytest.fixture(scope="module")
+def dense_ref(tmp_path_factory):
+    return _run(tmp_path_factory.mktemp("ref"), 1, "ref")
+
+
+def test_data_parallel_sharded_optimizer(tmp_path, dense_ref):
+    _close(_run(tmp_path, 2, "dp2"), dense_ref, 2e-5)
+
+
+def test_tensor_parallel(tmp_path, dense_ref):
+    _close(_run(tmp_path, 2, "tp2", "--tp", "2"), dense_ref, 2e-5)
+
+
+def test_tensor_parallel_sequence_parallel_with_dp(tmp_path, dense_ref):
+    _close(_run(tmp_path, 4, "tp2sp_dp2", "--tp", "2", "--sp", "1"), dense_ref, 2e-5)
+
+
+@pytest.mark.parametrize("kind", ["all_gather", "p2p", "a2a"])
+def test_context_parallel(tmp_path, dense_ref, kind):
+    _close(_run(tmp_path, 2, f"cp2_{kind}", "--cp", "2", "--cp-type", kind), dense_ref, 2e-5)
+
+
+def test_expert_parallel(tmp_path):
+    ref = _run(tmp_path, 1, "moe_ref", "--moe", "1")
+    got = _run(tmp_path, 2, "moe_ep2", "--moe", "1", "--ep", "2")
+    _close(got, ref, 5e-5)
