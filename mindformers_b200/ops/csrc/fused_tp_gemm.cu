@@ -1,0 +1,538 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
+//
+//   COMM = 1  all-gather -> GEMM   D[T, N] = gather_rows(A_r)[T, K] x B
+//       Each rank contributes a chunk of T/tp rows of A that lives in peer-mapped ("symmetric")
+//       memory. Four extra warps per CTA pull the remote chunks into a local [T, K] buffer with plain
+//       peer loads (16-byte vectors), publishing a counter per 128-row block; the TMA producer of the
+//       GEMM waits on that counter before it loads tiles of the block. Tiles of the rank's own rows
+//       run first, so the NVLink transfer hides behind them. The gathered A is left complete in the
+//       local buffer for the weight-gradient GEMM of the backward pass.
+//   COMM = 2  GEMM -> reduce-scatter   D_r[T/tp, N] = sum_p (A_p x B_p)[rows of rank r]
+//       Every rank computes all T rows of its partial product, remote-owned row chunks first. The
+//       epilogue of a remote-owned tile stores the bf16 tile straight into the owner's receive buffer
+//       (peer stores) and releases a per-tile flag; the epilogue of an own tile acquires the flags of
+//       all peers, adds their tiles to the accumulator in fp32 and writes the final rows. No separate
+//       reduction pass and no host synchronisation.
+//
+// Cross-rank flags carry a monotonically increasing epoch (the call counter, identical on all ranks),
+// so they never need a reset; receive buffers are double-buffered on the epoch parity. A rank can be at
+// most one call ahead of a peer, because each call waits for data that the peer only produces in the
+// same call. Every wait is bounded and reports through the status word.
+//
+// No TMA load in this file uses cluster multicast, and no TMA load reads peer memory.
+#include "common.cuh"
+
+namespace mfb {
+
+constexpr int kTpBM = 128;
+constexpr int kTpBK = 64;
+constexpr int kTpStaging = 128 * 128;
+constexpr int kTpMaxRanks = 8;
+constexpr int kCopySlices = 8;  // a 128-row block is copied as 8 slices of 16 rows
+
+struct TpArgs {
+  int M, N, K;          // D is [M, N] for COMM 1; the partial product is [M, N] for COMM 2
+  int num_m_blocks, num_n_blocks;
+  int tp, rank, epoch;
+  int rows_per_chunk;   // M / tp, multiple of 128
+  int* status;
+  // ---- COMM 1 ----
+  const __nv_bfloat16* peer_a[kTpMaxRanks];  // chunk [rows_per_chunk, K] of every rank (row pitch lda)
+  long long lda;
+  __nv_bfloat16* a_full;                     // local [M, K], contiguous
+  int* block_flags;                          // [num_m_blocks] local counters, zero before launch
+  int* ready_local;                          // [tp]: entry p is written by rank p
+  int* ready_peer[kTpMaxRanks];              // the same array on every rank
+  // ---- COMM 2 ----
+  __nv_bfloat16* recv_local;                 // [2][tp][rows_per_chunk, N] receive slots of this rank
+  __nv_bfloat16* recv_peer[kTpMaxRanks];
+  int* tile_flags_local;                     // [2][tp][blocks_per_chunk * num_n_blocks]
+  int* tile_flags_peer[kTpMaxRanks];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Bounded spin until *flag >= want (system or gpu scope acquire).
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int want, volatile int* abort_flag, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    const int v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v >= want) return true;
+    if (((++it) & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > MFB_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, kStatusPeerFlagTimeout);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+struct TpTile {
+  int m_blk, n_blk;
+};
+
+// Banded rasterisation with the row blocks rotated so that the chunk order starts at `first_chunk`.
+__device__ __forceinline__ TpTile tp_tile(const TpArgs& a, int tile, int first_chunk) {
+  constexpr int kBand = 16;
+  const int tiles_per_band = kBand * a.num_n_blocks;
+  const int band = tile / tiles_per_band;
+  const int first_m = band * kBand;
+  const int band_h = (a.num_m_blocks - first_m) < kBand ? (a.num_m_blocks - first_m) : kBand;
+  const int r = tile - band * tiles_per_band;
+  int m = first_m + r % band_h;
+  const int bpc = a.rows_per_chunk / kTpBM;
+  m = (m + first_chunk * bpc) % a.num_m_blocks;
+  TpTile t;
+  t.m_blk = m;
+  t.n_blk = r / band_h;
+  return t;
+}
+
+template <int BN, int STAGES, bool B_MN, int COMM>
+__global__ void __launch_bounds__(COMM == 1 ? 320 : 192, 1)
+tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chunk; COMM 2: A [M, K]
+               const __grid_constant__ CUtensorMap tmAfull,  // COMM 1: gathered A [M, K]
+               const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmD,      // COMM 1: D [M, N]; COMM 2: D_r [M/tp, N]
+               const TpArgs args) {
+  constexpr int A_BYTES = kTpBM * kTpBK * 2;
+  constexpr int B_BYTES = BN * kTpBK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;
+  constexpr int NUM_CHUNKS = BN / 64;
+  constexpr uint32_t IDESC = umma_idesc_bf16(kTpBM, BN, 0, B_MN ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * kTpStaging);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bpc = args.rows_per_chunk / kTpBM;  // row blocks per chunk
+  const int k_blocks = (args.K + kTpBK - 1) / kTpBK;
+  const int n_tiles = args.num_m_blocks * args.num_n_blocks;
+  // COMM 1 starts with the rank's own rows, COMM 2 with the rows of the next rank (own rows last)
+  const int first_chunk = (COMM == 1) ? args.rank : (args.rank + 1) % args.tp;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&tfull_bar[s]), 1);
+      mbar_init(smem_u32(&tempty_bar[s]), 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmD);
+    if (COMM == 1) {
+      tma_prefetch_desc(&tmAfull);
+      if (blockIdx.x == 0) {
+        // this rank's chunk was written by earlier work on the stream: tell every peer it may read it
+        for (int p = 0; p < args.tp; ++p)
+          if (p != args.rank) st_release_sys(args.ready_peer[p] + args.rank, args.epoch);
+      }
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TpTile t = tp_tile(args, tile, first_chunk);
+        const int chunk = t.m_blk / bpc;
+        const bool own = (COMM == 1) && (chunk == args.rank);
+        if (COMM == 1 && !own) {
+          ok = wait_flag_ge<false>(args.block_flags + t.m_blk, kCopySlices, abort_flag, args.status);
+          if (!ok) break;
+          // the copy was made with generic-proxy stores; order it before the async-proxy (TMA) reads
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, args.status,
+                         kStatusWaitTimeoutProducer);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, STAGE_BYTES);
+          const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_dst = a_dst + A_BYTES;
+          if (own) tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, (t.m_blk - args.rank * bpc) * kTpBM);
+          else if (COMM == 1) tma_load_2d(a_dst, &tmAfull, fb, kb * kTpBK, t.m_blk * kTpBM);
+          else tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, t.m_blk * kTpBM);
+          if (B_MN) {
+#pragma unroll
+            for (int at = 0; at < BN / 64; ++at)
+              tma_load_2d(b_dst + at * (kTpBK * 128), &tmB, fb, t.n_blk * BN + at * 64, kb * kTpBK);
+          } else {
+            tma_load_2d(b_dst, &tmB, fb, kb * kTpBK, t.n_blk * BN);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, args.status, kStatusWaitTimeoutMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < kTpBK / 16; ++k) {
+            const uint64_t a_desc = umma_desc_kmajor_sw128(a_base + k * 32);
+            const uint64_t b_desc = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 16 * 128, kTpBK * 128)
+                                         : umma_desc_kmajor_sw128(b_base + k * 32);
+            umma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&tfull_bar[acc]));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------ epilogue ------------------------------
+    const int ew = warp & 3;
+    const int row = ew * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    int acc = 0;
+    uint32_t acc_phase = 0, chunk_counter = 0;
+    bool ok = true;
+    const int parity = args.epoch & 1;
+    const size_t slot_elems = static_cast<size_t>(args.rows_per_chunk) * args.N;
+    const int tiles_per_chunk = bpc * args.num_n_blocks;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const TpTile t = tp_tile(args, tile, first_chunk);
+      const int owner = t.m_blk / bpc;
+      const int mb_local = t.m_blk - owner * bpc;
+      const int tile_in_chunk = mb_local * args.num_n_blocks + t.n_blk;
+      ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
+      if (COMM == 2 && ok && owner == args.rank) {
+        // the peers' partial tiles must have landed in this rank's receive slots
+        if (issuer) {
+          for (int p = 0; p < args.tp && ok; ++p) {
+            if (p == args.rank) continue;
+            const int* f = args.tile_flags_local + (static_cast<size_t>(parity) * args.tp + p) * tiles_per_chunk + tile_in_chunk;
+            ok = wait_flag_ge<true>(f, args.epoch, abort_flag, args.status);
+          }
+        }
+      }
+      ok = named_bar_and(2, 128, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
+      const int local_row = mb_local * kTpBM + row;   // row inside the owner's chunk
+#pragma unroll 1
+      for (int c = 0; c < NUM_CHUNKS; ++c) {
+        uint32_t v0[32], v1[32], packed[32];
+        tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+        tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+        tmem_ld_wait();
+        const int col0 = t.n_blk * BN + c * 64;
+        if (COMM == 2 && owner == args.rank) {
+          for (int p = 0; p < args.tp; ++p) {
+            if (p == args.rank) continue;
+            const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * args.tp + p) * slot_elems +
+                                       static_cast<size_t>(local_row) * args.N + col0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 u = ld_cg_v4(src + j * 8);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 f = __bfloat1622float2(h[q]);
+                const int idx = j * 8 + q * 2;
+                if (idx < 32) {
+                  v0[idx] = __float_as_uint(__uint_as_float(v0[idx]) + f.x);
+                  v0[idx + 1] = __float_as_uint(__uint_as_float(v0[idx + 1]) + f.y);
+                } else {
+                  v1[idx - 32] = __float_as_uint(__uint_as_float(v1[idx - 32]) + f.x);
+                  v1[idx - 31] = __float_as_uint(__uint_as_float(v1[idx - 31]) + f.y);
+                }
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          packed[i] = pack_bf16x2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+          packed[16 + i] = pack_bf16x2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+        }
+        if (COMM == 2 && owner != args.rank) {
+          // stage the chunk in shared memory, then store it to the owner with coalesced 128-byte rows
+          // (a warp writes four full rows per instruction; row-per-thread stores would fill only half of
+          // every 32-byte sector on the link)
+          const int buf = chunk_counter & 1;
+          if (issuer) tma_wait_group_read<1>();
+          named_bar_sync(1, 128);
+          uint8_t* sbase = staging + buf * kTpStaging;
+          uint8_t* srow = sbase + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          named_bar_sync(1, 128);
+          if (col0 < args.N) {
+            const int et = threadIdx.x - 64;   // 0..127
+            const int cj = et & 7;             // 16-byte chunk inside the row
+            __nv_bfloat16* dst0 = args.recv_peer[owner] + (static_cast<size_t>(parity) * args.tp + args.rank) * slot_elems +
+                                  static_cast<size_t>(mb_local * kTpBM) * args.N + col0 + cj * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 16 + (et >> 3);
+              const uint4 v = *reinterpret_cast<const uint4*>(sbase + r * 128 + ((cj ^ (r & 7)) << 4));
+              *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r) * args.N) = v;
+            }
+          }
+          ++chunk_counter;
+        } else {
+          const int buf = chunk_counter & 1;
+          if (issuer) tma_wait_group_read<1>();
+          named_bar_sync(1, 128);
+          uint8_t* srow = staging + buf * kTpStaging + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (issuer) {
+            if (col0 < args.N) {
+              const int d_row = (COMM == 2) ? mb_local * kTpBM : t.m_blk * kTpBM;
+              tma_store_2d(&tmD, smem_u32(staging + buf * kTpStaging), col0, d_row);
+            }
+            tma_commit_group();
+          }
+          ++chunk_counter;
+        }
+      }
+      tc_fence_before();
+      if (COMM == 2 && owner != args.rank) {
+        // all 128 threads have issued their peer stores: publish the tile
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (issuer) {
+          int* f = args.tile_flags_peer[owner] + (static_cast<size_t>(parity) * args.tp + args.rank) * tiles_per_chunk + tile_in_chunk;
+          st_release_sys(f, args.epoch);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (issuer) tma_wait_group<0>();
+  } else {
+    // ------------------------------ COMM 1: gather warps ------------------------------
+    if (COMM == 1) {
+      const int ct = threadIdx.x - 192;  // 0..127
+      const int rows_per_item = kTpBM / kCopySlices;  // 16
+      const int vec_per_row = args.K / 8;             // 16-byte vectors per row
+      bool ok = true;
+      // remote chunks in the order the GEMM consumes them, then the own chunk (only needed afterwards)
+      for (int step = 1; step <= args.tp && ok; ++step) {
+        const int p = (args.rank + step) % args.tp;
+        if (p != args.rank) {
+          if (ct == 0) ok = wait_flag_ge<true>(args.ready_local + p, args.epoch, abort_flag, args.status);
+          ok = named_bar_and(3, 128, ok);
+          if (!ok) break;
+        }
+        const __nv_bfloat16* src = args.peer_a[p];
+        const int items = bpc * kCopySlices;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+          const int rb = item / kCopySlices, sl = item - rb * kCopySlices;
+          const int row0 = rb * kTpBM + sl * rows_per_item;          // row inside the chunk
+          const long long total = static_cast<long long>(rows_per_item) * vec_per_row;
+          for (long long i = ct; i < total; i += 128) {
+            const int r = static_cast<int>(i / vec_per_row), cv = static_cast<int>(i - static_cast<long long>(r) * vec_per_row);
+            const uint4 v = ld_cg_v4(src + static_cast<size_t>(row0 + r) * args.lda + cv * 8);
+            *reinterpret_cast<uint4*>(args.a_full + (static_cast<size_t>(p) * args.rows_per_chunk + row0 + r) * args.K + cv * 8) = v;
+          }
+          if (p != args.rank) {
+            __threadfence();
+            named_bar_sync(3, 128);
+            if (ct == 0) red_release_gpu_add(args.block_flags + p * bpc + rb, 1);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace mfb
+
+namespace {
+using namespace mfb;
+
+template <int BN, int STAGES, bool B_MN, int COMM>
+int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& tB, const CUtensorMap& tD,
+              const TpArgs& a, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = kTpBM * kTpBK * 2 + BN * kTpBK * 2;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 2 * kTpStaging + (2 * STAGES + 4) * 8 + 16 + 1024;
+  auto kern = tp_gemm_kernel<BN, STAGES, B_MN, COMM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+      mfb_host::set_error("tp gemm: cannot raise shared memory limit");
+      return 10;
+    }
+    attr_set = true;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = a.num_m_blocks * a.num_n_blocks;
+  // COMM 1 needs the gather warps of every CTA to be resident, whatever the tile count
+  const int grid = (COMM == 1) ? sms : (tiles < sms ? tiles : sms);
+  kern<<<grid, COMM == 1 ? 320 : 192, SMEM, stream>>>(tA, tAf, tB, tD, a);
+  if (cudaGetLastError() != cudaSuccess) {
+    mfb_host::set_error("tp gemm: launch failed");
+    return 11;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// All-gather -> GEMM. `peer_a[p]`: chunk [M/tp, K] (row pitch lda) of rank p, peer-mapped; `a_full`: local
+// contiguous [M, K] buffer that holds the gathered A when the kernel ends; `block_flags`: M/128 ints, zeroed
+// by this call; `ready_local` / `ready_peer[p]`: tp ints per rank in peer-mapped memory, persistent across
+// calls; `epoch`: call counter (>= 1, increasing, identical on all ranks). B: [N, K] (or [K, N] when
+// b_mn_major), row pitch ldb. D: [M, N] bf16, row pitch ldd.
+int mfb_tp_allgather_gemm(const void* const* peer_a, long long lda, void* a_full, const void* B, void* D, int M,
+                          int N, int K, int ldb, int ldd, int b_mn_major, int tp, int rank, int epoch,
+                          int* block_flags, int* ready_local, int* const* ready_peer, int* status,
+                          cudaStream_t stream) {
+  if (tp < 2 || tp > kTpMaxRanks || M % (tp * kTpBM) || K % 8 || N < 128) {
+    mfb_host::set_error("tp_allgather_gemm: unsupported M=%d N=%d K=%d tp=%d", M, N, K, tp);
+    return 1;
+  }
+  TpArgs a = {};
+  a.M = M; a.N = N; a.K = K; a.tp = tp; a.rank = rank; a.epoch = epoch; a.rows_per_chunk = M / tp;
+  a.num_m_blocks = M / kTpBM; a.status = status;
+  a.lda = lda; a.a_full = (__nv_bfloat16*)a_full; a.block_flags = block_flags; a.ready_local = ready_local;
+  for (int p = 0; p < tp; ++p) { a.peer_a[p] = (const __nv_bfloat16*)peer_a[p]; a.ready_peer[p] = ready_peer[p]; }
+  const bool bn256 = N >= 256;
+  const int BN = bn256 ? 256 : 128;
+  a.num_n_blocks = (N + BN - 1) / BN;
+  cudaMemsetAsync(block_flags, 0, sizeof(int) * a.num_m_blocks, stream);
+  CUtensorMap tA, tAf, tB, tD;
+  int rc;
+  const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((rc = mfb_host::make_tmap_2d(&tA, peer_a[rank], 2, BF, a.rows_per_chunk, K, lda, kTpBM, kTpBK))) return 20 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tAf, a_full, 2, BF, M, K, K, kTpBM, kTpBK))) return 30 + rc;
+  if (b_mn_major) rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, K, N, ldb, kTpBK, 64);
+  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, BN, kTpBK);
+  if (rc) return 40 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, M, N, ldd, kTpBM, 64))) return 50 + rc;
+  if (bn256) return b_mn_major ? tp_launch<256, 4, true, 1>(tA, tAf, tB, tD, a, stream)
+                               : tp_launch<256, 4, false, 1>(tA, tAf, tB, tD, a, stream);
+  return b_mn_major ? tp_launch<128, 6, true, 1>(tA, tAf, tB, tD, a, stream)
+                    : tp_launch<128, 6, false, 1>(tA, tAf, tB, tD, a, stream);
+}
+
+// GEMM -> reduce-scatter. A: [M, K] local (row pitch lda); B: [N, K] or [K, N]; D: this rank's [M/tp, N] bf16.
+// `recv_local` / `recv_peer[p]`: peer-mapped receive buffers of 2 * tp * (M/tp) * N bf16; `tile_flags_*`:
+// peer-mapped 2 * tp * (M/tp/128) * ceil(N/BN) ints, persistent across calls, zero at start of the job.
+int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
+                               int b_mn_major, int tp, int rank, int epoch, void* recv_local,
+                               void* const* recv_peer, int* tile_flags_local, int* const* tile_flags_peer,
+                               int* status, cudaStream_t stream) {
+  if (tp < 2 || tp > kTpMaxRanks || M % (tp * kTpBM) || K % 8 || N < 128 || N % 64) {
+    mfb_host::set_error("tp_gemm_reduce_scatter: unsupported M=%d N=%d K=%d tp=%d", M, N, K, tp);
+    return 1;
+  }
+  TpArgs a = {};
+  a.M = M; a.N = N; a.K = K; a.tp = tp; a.rank = rank; a.epoch = epoch; a.rows_per_chunk = M / tp;
+  a.num_m_blocks = M / kTpBM; a.status = status;
+  a.recv_local = (__nv_bfloat16*)recv_local; a.tile_flags_local = tile_flags_local;
+  for (int p = 0; p < tp; ++p) { a.recv_peer[p] = (__nv_bfloat16*)recv_peer[p]; a.tile_flags_peer[p] = tile_flags_peer[p]; }
+  const bool bn256 = N >= 256;
+  const int BN = bn256 ? 256 : 128;
+  a.num_n_blocks = (N + BN - 1) / BN;
+  CUtensorMap tA, tB, tD;
+  int rc;
+  const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((rc = mfb_host::make_tmap_2d(&tA, A, 2, BF, M, K, lda, kTpBM, kTpBK))) return 20 + rc;
+  if (b_mn_major) rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, K, N, ldb, kTpBK, 64);
+  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, BN, kTpBK);
+  if (rc) return 40 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, a.rows_per_chunk, N, ldd, kTpBM, 64))) return 50 + rc;
+  if (bn256) return b_mn_major ? tp_launch<256, 4, true, 2>(tA, tA, tB, tD, a, stream)
+                               : tp_launch<256, 4, false, 2>(tA, tA, tB, tD, a, stream);
+  return b_mn_major ? tp_launch<128, 6, true, 2>(tA, tA, tB, tD, a, stream)
+                    : tp_launch<128, 6, false, 2>(tA, tA, tB, tD, a, stream);
+}
+
+// Upper bound of ceil(N / BN) that the flag arrays must provide room for.
+int mfb_tp_num_n_blocks(int N) { return N >= 256 ? (N + 255) / 256 : (N + 127) / 128; }
+
+}  // extern "C"

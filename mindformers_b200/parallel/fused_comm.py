@@ -25,11 +25,14 @@ def _runtime_ready() -> bool:
 
 
 def enabled(config, x: torch.Tensor) -> bool:
+    """True when the fused tensor-parallel kernels can serve this call (bf16 on CUDA, token count a
+    multiple of 128 per rank); the layers fall back to NCCL collectives + GEMM otherwise."""
     if _FORCE_OFF or not getattr(config, "fused_tp_comm", False) or not x.is_cuda:
         return False
-    if ps.get_tensor_model_parallel_world_size() == 1:
+    tp = ps.get_tensor_model_parallel_world_size()
+    if tp == 1 or x.dtype != torch.bfloat16 or x.dim() != 2:
         return False
-    return _runtime_ready()
+    return x.shape[0] % 128 == 0 and x.shape[1] % 64 == 0
 
 
 def moe_enabled(config, x: torch.Tensor) -> bool:
