@@ -8,7 +8,10 @@
 //
 // One CTA of 256 threads per row, 16-byte vector accesses, row kept in registers when
 // H <= 8192. A warp-per-row variant serves per-head q/k norms (H <= 256, strided rows).
+#include <mutex>
+
 #include "common.cuh"
+#include "rmsnorm_noalloc.h"
 
 namespace mfb {
 
@@ -321,3 +324,83 @@ int mfb_headnorm_fwd(void* x, const void* w, float* rstd, int T, int heads, int 
 }
 
 }  // extern "C"
+
+// =================================================================================================
+// RMSNorm backward without any allocation (declaration and user notes: rmsnorm_noalloc.h)
+// =================================================================================================
+namespace mfb {
+
+// Upper limits of the built-in scratch: one row of partial column sums per resident CTA.
+constexpr int kNoAllocMaxParts = 148;
+constexpr int kNoAllocMaxH = 8192;
+
+// Lives in the device memory of every GPU that loads this library, from load until the process exits
+// (148 * 8192 floats = 4.6 MiB). Host code must not pass this name to a kernel: on the host it is only a
+// handle for cudaGetSymbolAddress.
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[kNoAllocMaxParts * kNoAllocMaxH];
+
+}  // namespace mfb
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    mfb_host::set_error("rmsnorm_bwd_noalloc: cannot identify the current device");
+    return 3;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), mfb::g_rmsnorm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      mfb_host::set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return 4;
+    }
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int mfb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const float* rstd,
+                                       const void* dres, void* dx, float* dw_f32, void* dw_bf16, int accumulate,
+                                       int T, int H, cudaStream_t stream) {
+  using namespace mfb;
+  if (H % 8 != 0 || H <= 0 || H > kNoAllocMaxH) {
+    mfb_host::set_error("rmsnorm_bwd_noalloc: H=%d must be a positive multiple of 8 and at most %d", H, kNoAllocMaxH);
+    return 1;
+  }
+  if (T < 0 || (dw_f32 == nullptr && dw_bf16 == nullptr)) {
+    mfb_host::set_error("rmsnorm_bwd_noalloc: bad arguments (T=%d, no dw output)", T);
+    return 1;
+  }
+  if (T == 0) return 0;
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  // Every launched CTA overwrites its whole row of partial sums and the reduction reads exactly the rows that
+  // were launched, so nothing in the array has to be cleared between calls.
+  const int parts = T < kNoAllocMaxParts ? T : kNoAllocMaxParts;
+  if (dres)
+    rmsnorm_bwd_kernel<true><<<parts, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+        (__nv_bfloat16*)dx, scratch, T, H);
+  else
+    rmsnorm_bwd_kernel<false><<<parts, kNormThreads, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dx,
+        scratch, T, H);
+  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32, (__nv_bfloat16*)dw_bf16,
+                                                             accumulate);
+  if (cudaGetLastError() != cudaSuccess) {
+    mfb_host::set_error("rmsnorm_bwd_noalloc: launch failed");
+    return 2;
+  }
+  return 0;
+}
