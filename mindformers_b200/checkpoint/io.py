@@ -1,0 +1,244 @@
+"""Checkpoint save / load in safetensors with the reference's directory scheme.
+
+Save layout (reference ``core/callback/callback.py:1203-1645``):
+``<dir>/rank_{r}/{prefix}_rank_{r}-{epoch}_{step}.safetensors`` + ``meta.json`` (last file, epoch, step) in the
+same rank directory; network-only copies under ``checkpoint_network``; a JSON strategy file per rank under
+``strategy/``. Saved state: model parameters, optimizer moments ``adam_m.*`` / ``adam_v.*`` (and the 16-bit fp32
+master remainders ``master_lo.*``), plus ``global_step, epoch_num, step_num, loss_scale, global_batch_size``
+as 0-d tensors (reference ``callback.py:1397-1411``).
+
+Load accepts the three layouts of ``utils/load_checkpoint_utils.py:100-122`` (single file, directory of files,
+``rank_N`` directories) and Hugging Face model directories (``config.json`` + ``*.safetensors``), which are
+renamed and fused on the fly and then sliced for this rank.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import shutil
+from typing import Dict, Optional, Tuple
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import load_file, save_file
+
+from ..parallel import parallel_state as ps
+from ..tools.logger import logger
+from ..tools.utils import format_ckpt_name, get_real_rank, parse_ckpt_name
+from . import name_maps
+from .sharding import save_strategy, shard_for_param
+
+TRANSIENT_KEYS = ("accu_grads", "key_cache", "value_cache", "expert_load", "rotary_pos_emb")
+SCALAR_KEYS = ("global_step", "epoch_num", "step_num", "loss_scale", "global_batch_size")
+
+
+def _is_transient(name: str) -> bool:
+    return any(k in name for k in TRANSIENT_KEYS)
+
+
+def model_state(model: torch.nn.Module, trainable_only: bool = False) -> Dict[str, torch.Tensor]:
+    out = {}
+    for n, p in model.named_parameters():
+        if trainable_only and not p.requires_grad:
+            continue
+        out[n] = p.detach()
+    for n, b in model.named_buffers():
+        if not _is_transient(n) and b is not None and n.split(".")[-1] in ("expert_bias",):
+            out[n] = b.detach()
+    return out
+
+
+def save_checkpoint(model: torch.nn.Module, directory: str, *, optimizer=None, prefix: str = "mindformers",
+                    epoch: int = 0, step: int = 0, extra: Optional[dict] = None, keep_max: int = 5,
+                    save_network_only_copy: bool = False, trainable_only: bool = False,
+                    remove_redundancy: bool = False, write_strategy: bool = True) -> str:
+    """Write this rank's checkpoint; returns the file path."""
+    rank = get_real_rank()
+    rank_dir = os.path.join(directory, f"rank_{rank}")
+    os.makedirs(rank_dir, exist_ok=True)
+    tensors = {}
+    for n, t in model_state(model, trainable_only).items():
+        if remove_redundancy and _is_redundant(n, model):
+            continue
+        tensors[n] = t.contiguous().cpu()
+    if optimizer is not None and hasattr(optimizer, "named_states"):
+        for n, t in optimizer.named_states().items():
+            tensors[n] = t.contiguous().cpu()
+        if hasattr(optimizer, "shards"):
+            for sname, sh in optimizer.shards.items():
+                if sh.world > 1:   # sharded optimizer: store the flat slices
+                    tensors[f"__shard__.{sname}.adam_m"] = sh.m.cpu()
+                    tensors[f"__shard__.{sname}.adam_v"] = sh.v.cpu()
+                    if sh.lo is not None:
+                        tensors[f"__shard__.{sname}.master_lo"] = sh.lo.cpu()
+        tensors["global_step"] = torch.tensor(int(getattr(optimizer, "global_step", 0)), dtype=torch.int64)
+    scalars = {"epoch_num": epoch, "step_num": step}
+    scalars.update(extra or {})
+    for k, v in scalars.items():
+        tensors[k] = torch.tensor(v, dtype=torch.float32 if isinstance(v, float) else torch.int64)
+    name = format_ckpt_name(prefix, rank, epoch, step)
+    path = os.path.join(rank_dir, name)
+    tmp = path + ".tmp"
+    save_file(tensors, tmp, metadata={"format": "pt", "remove_redundancy": str(bool(remove_redundancy))})
+    os.replace(tmp, path)
+    meta = {"last_epoch": epoch, "last_step": step, "last_ckpt_file": name}
+    mtmp = os.path.join(rank_dir, "meta.json.tmp")
+    with open(mtmp, "w") as f:
+        json.dump(meta, f)
+    os.replace(mtmp, os.path.join(rank_dir, "meta.json"))
+    _rotate(rank_dir, prefix, keep_max)
+    if write_strategy:
+        sdir = os.path.join(os.path.dirname(directory.rstrip("/")) or ".", "strategy")
+        save_strategy(model, os.path.join(sdir, f"ckpt_strategy_rank_{rank}.json"))
+    if save_network_only_copy:
+        ndir = os.path.join(os.path.dirname(directory.rstrip("/")) or ".", "checkpoint_network", f"rank_{rank}")
+        os.makedirs(ndir, exist_ok=True)
+        save_file({n: t.contiguous().cpu() for n, t in model_state(model).items()}, os.path.join(ndir, name))
+    return path
+
+
+def _is_redundant(name: str, model) -> bool:
+    """A tensor-parallel-replicated parameter is written only by the first rank of its TP group."""
+    p = dict(model.named_parameters()).get(name)
+    if p is None:
+        return False
+    replicated = not getattr(p, "tensor_model_parallel", False) and not getattr(p, "is_expert", False)
+    return replicated and ps.get_tensor_model_parallel_rank() != 0
+
+
+def _rotate(rank_dir: str, prefix: str, keep_max: int):
+    if keep_max is None or keep_max <= 0:
+        return
+    files = []
+    for f in os.listdir(rank_dir):
+        parsed = parse_ckpt_name(f)
+        if parsed and parsed[0] == prefix:
+            files.append(((parsed[2], parsed[3]), f))
+    files.sort()
+    for _, f in files[:-keep_max]:
+        os.remove(os.path.join(rank_dir, f))
+
+
+# --------------------------------------------------------------------------------------------------
+def is_hf_safetensors_dir(path: str) -> bool:
+    return os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")) and \
+        bool(glob.glob(os.path.join(path, "*.safetensors")))
+
+
+def _read_files(files) -> Dict[str, torch.Tensor]:
+    out = {}
+    for f in files:
+        out.update(load_file(f))
+    return out
+
+
+def resolve_checkpoint(path: str, rank: Optional[int] = None) -> Tuple[str, list]:
+    """Classify ``path`` → (kind, files) with kind in {"file", "dir", "rank_dirs", "hf"}."""
+    rank = get_real_rank() if rank is None else rank
+    if os.path.isfile(path):
+        return "file", [path]
+    if is_hf_safetensors_dir(path):
+        return "hf", sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    rdir = os.path.join(path, f"rank_{rank}")
+    if os.path.isdir(rdir):
+        meta = os.path.join(rdir, "meta.json")
+        if os.path.exists(meta):
+            with open(meta) as f:
+                last = json.load(f).get("last_ckpt_file")
+            if last and os.path.exists(os.path.join(rdir, last)):
+                return "rank_dirs", [os.path.join(rdir, last)]
+        files = sorted(glob.glob(os.path.join(rdir, "*.safetensors")), key=lambda f: parse_ckpt_name(f)[2:] if parse_ckpt_name(f) else (0, 0))
+        return "rank_dirs", files[-1:]
+    files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if files:
+        return "dir", files
+    raise FileNotFoundError(f"no safetensors checkpoint found under {path}")
+
+
+def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict: bool = True, family: str = "llama",
+                    sharded: Optional[bool] = None) -> dict:
+    """Load parameters (and optimizer state when given). Returns the scalar entries (epoch, step, ...).
+
+    ``sharded``: the tensors in the file are already this rank's slices (default for ``rank_N`` layouts); full
+    tensors (single files, plain directories, HF directories) are sliced by ``shard_for_param``.
+    """
+    kind, files = resolve_checkpoint(path)
+    sd = _read_files(files)
+    if kind == "hf":
+        sd = name_maps.hf_to_framework(sd, model.config, family)
+    if sharded is None:
+        sharded = kind == "rank_dirs"
+    params = dict(model.named_parameters())
+    buffers = dict(model.named_buffers())
+    missing, used = [], set()
+    with torch.no_grad():
+        for n, p in params.items():
+            src = sd.get(n)
+            if src is None and n == "output_layer.weight" and "embedding.word_embeddings.weight" in sd \
+                    and not getattr(model.config, "untie_embeddings_and_output_weights", True):
+                src = sd["embedding.word_embeddings.weight"]
+            if src is None:
+                missing.append(n)
+                continue
+            used.add(n)
+            t = src if sharded and tuple(src.shape) == tuple(p.shape) else shard_for_param(src, p)
+            p.copy_(t.to(device=p.device, dtype=p.dtype))
+        for n, b in buffers.items():
+            if n in sd and tuple(sd[n].shape) == tuple(b.shape):
+                b.copy_(sd[n].to(device=b.device, dtype=b.dtype))
+                used.add(n)
+    if missing and strict:
+        raise KeyError(f"checkpoint {path} lacks parameters: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
+    if missing:
+        logger.warning("parameters not found in checkpoint: %s", missing[:8])
+    scalars = {k: sd[k].item() for k in SCALAR_KEYS if k in sd}
+    if optimizer is not None:
+        if hasattr(optimizer, "reload_model_params"):
+            optimizer.reload_model_params()
+        states = {k: v for k, v in sd.items() if k.startswith(("adam_m.", "adam_v.", "master_lo."))}
+        if states and hasattr(optimizer, "load_named_states"):
+            optimizer.load_named_states({k: v.to(next(model.parameters()).device) for k, v in states.items()},
+                                        scalars.get("global_step"))
+        elif "global_step" in scalars:
+            optimizer.global_step = int(scalars["global_step"])
+        if hasattr(optimizer, "shards"):
+            for sname, sh in optimizer.shards.items():
+                for key, dst in (("adam_m", sh.m), ("adam_v", sh.v), ("master_lo", sh.lo)):
+                    src = sd.get(f"__shard__.{sname}.{key}")
+                    if src is not None and dst is not None and src.numel() == dst.numel():
+                        dst.copy_(src.to(dst.device))
+    return scalars
+
+
+def save_pretrained_dir(model: torch.nn.Module, directory: str, config_dict: Optional[dict] = None,
+                        max_shard_bytes: int = 5 << 30, hf_names: bool = False, family: str = "llama"):
+    """HF-style directory: ``config.json`` + (sharded) ``model-0000x-of-0000y.safetensors`` + index."""
+    os.makedirs(directory, exist_ok=True)
+    sd = {n: t.contiguous().cpu() for n, t in model_state(model).items()}
+    if hf_names:
+        sd = name_maps.framework_to_hf(sd, model.config, family)
+    shards, cur, size = [], {}, 0
+    for n, t in sd.items():
+        b = t.numel() * t.element_size()
+        if cur and size + b > max_shard_bytes:
+            shards.append(cur)
+            cur, size = {}, 0
+        cur[n] = t
+        size += b
+    if cur:
+        shards.append(cur)
+    if len(shards) == 1:
+        save_file(shards[0], os.path.join(directory, "model.safetensors"), metadata={"format": "pt"})
+    else:
+        weight_map = {}
+        for i, sh in enumerate(shards):
+            fname = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+            save_file(sh, os.path.join(directory, fname), metadata={"format": "pt"})
+            weight_map.update({n: fname for n in sh})
+        with open(os.path.join(directory, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in sd.values())},
+                       "weight_map": weight_map}, f, indent=1)
+    if config_dict is not None:
+        with open(os.path.join(directory, "config.json"), "w") as f:
+            json.dump(config_dict, f, indent=1, default=str)

@@ -1,0 +1,246 @@
+"""Hugging Face ⇄ framework parameter names and layouts.
+
+Step 1 renames HF keys to per-projection framework names (the maps of the reference's
+``models/qwen3/utils.py:31-64``, ``models/qwen2/utils.py:30-57``, ``models/deepseek3/utils.py:32-71``,
+``models/llama/llama.py:682-702``). Step 2 fuses them into the parameters the network owns
+(``inference/model_utils.py:83-114``, ``toolkit/weight_convert/deepseekv3/convert_deepseekv3_hf_weight.py``):
+
+* ``linear_q | linear_k | linear_v``  → ``linear_qkv``  (rows ``[Q; K; V]``, or per-KV-group interleave)
+* ``mlp.gating | mlp.linear_fc1``     → ``mlp.linear_fc1`` (rows ``[gate; up]``)
+* ``experts.N.{gating,linear_fc1}``   → ``experts.weight1`` ``[E, H, 2F]``;  ``experts.N.linear_fc2`` → ``weight2 [E, F, H]``
+* MLA: ``linear_q_down_proj | linear_kv_down_proj`` → ``linear_qkv``; ``linear_q_up_proj`` → ``linear_qb``;
+  ``linear_kv_up_proj`` → ``linear_kvb``; ``kv_layernorm`` → ``k_layernorm``
+* ``router.weight.weight`` → ``router.weight``
+"""
+from __future__ import annotations
+
+import re
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+_COMMON = [
+    ("model.embed_tokens.", "embedding.word_embeddings."),
+    (".self_attn.q_proj.", ".self_attention.linear_q."),
+    (".self_attn.k_proj.", ".self_attention.linear_k."),
+    (".self_attn.v_proj.", ".self_attention.linear_v."),
+    (".self_attn.o_proj.", ".self_attention.linear_proj."),
+    (".self_attn.q_norm.", ".self_attention.q_layernorm."),
+    (".self_attn.k_norm.", ".self_attention.k_layernorm."),
+    (".self_attn.q_a_proj.", ".self_attention.linear_q_down_proj."),
+    (".self_attn.q_a_layernorm.", ".self_attention.q_layernorm."),
+    (".self_attn.q_b_proj.", ".self_attention.linear_q_up_proj."),
+    (".self_attn.kv_a_proj_with_mqa.", ".self_attention.linear_kv_down_proj."),
+    (".self_attn.kv_a_layernorm.", ".self_attention.kv_layernorm."),
+    (".self_attn.kv_b_proj.", ".self_attention.linear_kv_up_proj."),
+    (".mlp.gate.e_score_correction_bias", ".mlp.router.expert_bias"),
+    (".mlp.gate.weight", ".mlp.router.weight.weight"),
+    (".gate_proj.", ".gating."),
+    (".down_proj.", ".linear_fc2."),
+    (".up_proj.", ".linear_fc1."),
+    (".post_attention_layernorm.", ".pre_mlp_layernorm."),
+    ("model.norm.", "decoder.final_layernorm."),
+    ("lm_head.", "output_layer."),
+    ("model.layers.", "decoder.layers."),
+]
+
+# legacy (use_legacy: True) Llama names of the reference: models/llama/llama.py:682-702
+_LEGACY_LLAMA = [
+    ("model.embed_tokens.weight", "model.tok_embeddings.embedding_weight"),
+    (".self_attn.q_proj.", ".attention.wq."),
+    (".self_attn.k_proj.", ".attention.wk."),
+    (".self_attn.v_proj.", ".attention.wv."),
+    (".self_attn.o_proj.", ".attention.wo."),
+    (".mlp.gate_proj.", ".feed_forward.w1."),
+    (".mlp.down_proj.", ".feed_forward.w2."),
+    (".mlp.up_proj.", ".feed_forward.w3."),
+    (".input_layernorm.", ".attention_norm."),
+    (".post_attention_layernorm.", ".ffn_norm."),
+    ("model.norm.", "model.norm_out."),
+]
+
+FAMILIES = ("llama", "qwen2", "qwen2_5", "qwen3", "qwen3_moe", "deepseek_v3", "deepseekv3", "mixtral", "telechat",
+            "glm")
+
+
+def convert_name(hf_name: str, family: str = "llama") -> str:
+    """HF key → per-projection framework key."""
+    out = hf_name
+    for a, b in _COMMON:
+        out = out.replace(a, b)
+    return out
+
+
+def convert_name_legacy(hf_name: str) -> str:
+    out = hf_name
+    for a, b in _LEGACY_LLAMA:
+        out = out.replace(a, b)
+    return out
+
+
+def reverse_name(mf_name: str) -> str:
+    """Per-projection framework key → HF key."""
+    out = mf_name
+    for a, b in reversed(_COMMON):
+        out = out.replace(b, a)
+    return out
+
+
+def qkv_concat(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_heads: int, num_kv_heads: int,
+               contiguous_layout: bool = True) -> torch.Tensor:
+    """Fuse q/k/v weights (rows) or biases. ``contiguous_layout`` gives ``[Q; K; V]``; otherwise the rows are
+    interleaved per KV group as ``[q×rep, k, v]`` (reference ``utils/convert_utils.py:63-92``)."""
+    if contiguous_layout:
+        return torch.cat((q, k, v), dim=0)
+    hd = q.shape[0] // num_heads
+    rep = num_heads // num_kv_heads
+    tail = q.shape[1:]
+    qg = q.reshape(num_kv_heads, rep * hd, *tail)
+    kg = k.reshape(num_kv_heads, hd, *tail)
+    vg = v.reshape(num_kv_heads, hd, *tail)
+    return torch.cat((qg, kg, vg), dim=1).reshape(-1, *tail)
+
+
+def qkv_split(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, contiguous_layout: bool = True):
+    if contiguous_layout:
+        return torch.split(qkv, [num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * head_dim], dim=0)
+    rep = num_heads // num_kv_heads
+    tail = qkv.shape[1:]
+    g = qkv.reshape(num_kv_heads, (rep + 2) * head_dim, *tail)
+    q = g[:, : rep * head_dim].reshape(-1, *tail)
+    k = g[:, rep * head_dim:(rep + 1) * head_dim].reshape(-1, *tail)
+    v = g[:, (rep + 1) * head_dim:].reshape(-1, *tail)
+    return q, k, v
+
+
+_EXPERT_RE = re.compile(r"^(?P<pre>.*\.mlp\.experts)\.(?P<idx>\d+)\.(?P<proj>gating|linear_fc1|linear_fc2)\.weight$")
+
+
+def fuse_state_dict(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tensor]:
+    """Per-projection framework names → the fused parameters of ``GPTModel`` (full, unsharded tensors)."""
+    out: Dict[str, torch.Tensor] = {}
+    nh, nkv = config.num_attention_heads, config.num_query_groups
+    contiguous = getattr(config, "use_contiguous_weight_layout", True)
+    groups: Dict[str, Dict[str, torch.Tensor]] = {}
+    experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = {}
+    for name, t in sd.items():
+        m = _EXPERT_RE.match(name)
+        if m:
+            experts.setdefault(m["pre"], {})[(int(m["idx"]), m["proj"])] = t
+            continue
+        key = None
+        for pat in (r"(.*\.self_attention)\.linear_(q|k|v)\.(weight|bias)$",
+                    r"(.*\.(?:mlp|shared_experts))\.(gating|linear_fc1)\.(weight|bias)$",
+                    r"(.*\.self_attention)\.linear_(q_down_proj|kv_down_proj)\.(weight)$"):
+            mm = re.match(pat, name)
+            if mm:
+                key = (mm.group(1), mm.group(3), pat)
+                groups.setdefault(str(key), {"_key": key})[mm.group(2)] = t
+                break
+        if key is not None:
+            continue
+        new = name
+        new = new.replace(".router.weight.weight", ".router.weight")
+        new = new.replace(".self_attention.linear_q_up_proj.", ".self_attention.linear_qb.")
+        new = new.replace(".self_attention.linear_kv_up_proj.", ".self_attention.linear_kvb.")
+        new = new.replace(".self_attention.kv_layernorm.", ".self_attention.k_layernorm.")
+        out[new] = t
+    for g in groups.values():
+        prefix, kind, _ = g["_key"]
+        if "q" in g and "k" in g and "v" in g:
+            out[f"{prefix}.linear_qkv.{kind}"] = qkv_concat(g["q"], g["k"], g["v"], nh, nkv, contiguous)
+        elif "gating" in g and "linear_fc1" in g:
+            out[f"{prefix}.linear_fc1.{kind}"] = torch.cat((g["gating"], g["linear_fc1"]), dim=0)
+        elif "kv_down_proj" in g:
+            parts = [g["q_down_proj"]] if "q_down_proj" in g else []
+            out[f"{prefix}.linear_qkv.{kind}"] = torch.cat(parts + [g["kv_down_proj"]], dim=0)
+        else:
+            for k2, t in g.items():
+                if k2 != "_key":
+                    name = {"q": "linear_q", "k": "linear_k", "v": "linear_v"}.get(k2, k2)
+                    out[f"{prefix}.{name}.{kind}"] = t
+    for prefix, items in experts.items():
+        n = max(i for i, _ in items) + 1
+        w1 = [torch.cat((items[(e, "gating")], items[(e, "linear_fc1")]), dim=0).t() for e in range(n)]
+        w2 = [items[(e, "linear_fc2")].t() for e in range(n)]
+        out[f"{prefix}.weight1"] = torch.stack(w1).contiguous()     # [E, H, 2F]
+        out[f"{prefix}.weight2"] = torch.stack(w2).contiguous()     # [E, F, H]
+    return out
+
+
+def unfuse_state_dict(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tensor]:
+    """Inverse of ``fuse_state_dict`` (used by the reversed converter)."""
+    out: Dict[str, torch.Tensor] = {}
+    nh, nkv = config.num_attention_heads, config.num_query_groups
+    hd = getattr(config, "kv_channels", None) or config.hidden_size // nh
+    contiguous = getattr(config, "use_contiguous_weight_layout", True)
+    mla = bool(getattr(config, "multi_latent_attention", False))
+    for name, t in sd.items():
+        if name.endswith((".self_attention.linear_qkv.weight", ".self_attention.linear_qkv.bias")):
+            prefix, kind = name.rsplit(".linear_qkv.", 1)
+            if mla:
+                qr = getattr(config, "q_lora_rank", None) or 0
+                if qr:
+                    out[f"{prefix}.linear_q_down_proj.{kind}"] = t[:qr]
+                out[f"{prefix}.linear_kv_down_proj.{kind}"] = t[qr:]
+            else:
+                q, k, v = qkv_split(t, nh, nkv, hd, contiguous)
+                out[f"{prefix}.linear_q.{kind}"], out[f"{prefix}.linear_k.{kind}"], out[f"{prefix}.linear_v.{kind}"] = q, k, v
+        elif re.search(r"\.(mlp|shared_experts)\.linear_fc1\.(weight|bias)$", name) and getattr(config, "gated_linear_unit", True):
+            prefix, kind = name.rsplit(".linear_fc1.", 1)
+            g, u = t.chunk(2, dim=0)
+            out[f"{prefix}.gating.{kind}"], out[f"{prefix}.linear_fc1.{kind}"] = g, u
+        elif name.endswith(".experts.weight1"):
+            prefix = name[: -len(".weight1")]
+            for e in range(t.shape[0]):
+                g, u = t[e].t().chunk(2, dim=0)
+                out[f"{prefix}.{e}.gating.weight"], out[f"{prefix}.{e}.linear_fc1.weight"] = g.contiguous(), u.contiguous()
+        elif name.endswith(".experts.weight2"):
+            prefix = name[: -len(".weight2")]
+            for e in range(t.shape[0]):
+                out[f"{prefix}.{e}.linear_fc2.weight"] = t[e].t().contiguous()
+        else:
+            new = name.replace(".self_attention.linear_qb.", ".self_attention.linear_q_up_proj.")
+            new = new.replace(".self_attention.linear_kvb.", ".self_attention.linear_kv_up_proj.")
+            if mla:
+                new = new.replace(".self_attention.k_layernorm.", ".self_attention.kv_layernorm.")
+            if new.endswith(".router.weight"):
+                new = new + ".weight"
+            out[new] = t
+    return out
+
+
+def weight_dequant(weight: torch.Tensor, scale_inv: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """Block-scaled fp8 (e4m3) weight ``[M, N]`` with fp32 ``scale_inv [ceil(M/128), ceil(N/128)]`` → bf16."""
+    M, N = weight.shape
+    s = scale_inv.float().repeat_interleave(block, dim=0)[:M].repeat_interleave(block, dim=1)[:, :N]
+    return (weight.float() * s).to(torch.bfloat16)
+
+
+def hf_to_framework(hf_sd: Dict[str, torch.Tensor], config, family: str = "llama", dtype=None,
+                    keep_fp8: bool = False) -> Dict[str, torch.Tensor]:
+    """Full conversion of an HF state dict (fp8 block-scaled weights are dequantised unless ``keep_fp8``)."""
+    plain: Dict[str, torch.Tensor] = {}
+    for name, t in hf_sd.items():
+        if name.endswith("_scale_inv"):
+            continue
+        if t.dtype == torch.float8_e4m3fn and not keep_fp8:
+            sc = hf_sd.get(name + "_scale_inv")
+            if sc is None:
+                raise KeyError(f"{name} is fp8 but {name}_scale_inv is missing")
+            t = weight_dequant(t, sc)
+        if "rotary_emb.inv_freq" in name:
+            continue
+        if dtype is not None and t.is_floating_point() and t.dtype != torch.float8_e4m3fn:
+            t = t.to(dtype)
+        plain[convert_name(name, family)] = t
+    return fuse_state_dict(plain, config)
+
+
+def framework_to_hf(sd: Dict[str, torch.Tensor], config, family: str = "llama", dtype=None) -> Dict[str, torch.Tensor]:
+    out = {}
+    for name, t in unfuse_state_dict(sd, config).items():
+        if dtype is not None and t.is_floating_point():
+            t = t.to(dtype)
+        out[reverse_name(name)] = t.contiguous()
+    return out

@@ -1,0 +1,170 @@
+"""Process-wide runtime context: device, seed, determinism, distributed initialisation.
+
+Mirrors the API of the reference's ``core/context/build_context.py`` (``build_context`` :431, ``init_context``,
+``set_context``, ``get_context`` :396-566, ``Context`` singleton :46-91) and ``core/context/parallel.py``
+(``init_communication`` :83-100). Ascend/MindSpore keys are accepted and mapped where a CUDA meaning exists:
+``device_id`` → CUDA device, ``max_device_memory`` → per-process memory fraction, ``train_precision_sync`` /
+``infer_precision_sync`` → deterministic algorithms + ``NCCL_ALGO=Ring``, ``CPU_AFFINITY`` → ``sched_setaffinity``.
+"""
+from __future__ import annotations
+
+import os
+import random
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..parallel import parallel_state as ps
+from ..tools.logger import logger
+from ..tools.register import set_use_legacy
+
+_CONTEXT = None
+
+
+def _parse_mem(value) -> Optional[float]:
+    if value is None:
+        return None
+    s = str(value).strip().upper()
+    if s.endswith("GB"):
+        return float(s[:-2]) * (1 << 30)
+    if s.endswith("MB"):
+        return float(s[:-2]) * (1 << 20)
+    return float(s)
+
+
+class Context:
+    """Singleton holding the effective settings."""
+
+    def __init__(self, config=None):
+        cfg = config or {}
+        self.config = cfg
+        ctx = dict(cfg.get("context") or {})
+        par = dict(cfg.get("parallel_config") or {})
+        self.use_parallel = bool(cfg.get("use_parallel", False))
+        self.run_mode = cfg.get("run_mode")
+        self.seed = cfg.get("seed", 1)
+        self.device_target = str(ctx.get("device_target", "CUDA")).upper()
+        self.local_rank = int(os.environ.get("LOCAL_RANK", ctx.get("device_id", 0) or 0))
+        self.settings = dict(ctx)
+        self.parallel_settings = par
+        set_use_legacy(cfg.get("use_legacy", True))
+        if self.run_mode:
+            os.environ["RUN_MODE"] = str(self.run_mode)
+        self._set_device(ctx)
+        self._set_determinism(cfg)
+        self._set_affinity()
+        self.set_seed(self.seed)
+        self.rank, self.world_size = 0, 1
+        if self.use_parallel:
+            self.init_communication(par)
+
+    # ----------------------------------------------------------------------------------------------
+    def _set_device(self, ctx):
+        if torch.cuda.is_available() and self.device_target not in ("CPU",):
+            torch.cuda.set_device(self.local_rank % torch.cuda.device_count())
+            self.device = torch.device("cuda", torch.cuda.current_device())
+            limit = _parse_mem(ctx.get("max_device_memory"))
+            if limit:
+                total = torch.cuda.get_device_properties(self.device).total_memory
+                torch.cuda.set_per_process_memory_fraction(min(1.0, limit / total), self.device)
+        else:
+            self.device = torch.device("cpu")
+
+    def _set_determinism(self, cfg):
+        train_sync, infer_sync = cfg.get("train_precision_sync"), cfg.get("infer_precision_sync")
+        on = bool(train_sync) or bool(infer_sync)
+        if train_sync is not None or infer_sync is not None:
+            torch.use_deterministic_algorithms(on, warn_only=True)
+            torch.backends.cudnn.deterministic = on
+            torch.backends.cudnn.benchmark = not on
+            if on:
+                os.environ.setdefault("NCCL_ALGO", "Ring")
+                os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        self.deterministic = on
+
+    def _set_affinity(self):
+        if os.environ.get("CPU_AFFINITY", "").lower() in ("1", "true") and hasattr(os, "sched_setaffinity"):
+            n = os.cpu_count() or 1
+            per = max(1, n // max(1, torch.cuda.device_count() or 1))
+            cores = set(range(self.local_rank * per, min(n, (self.local_rank + 1) * per)))
+            if cores:
+                try:
+                    os.sched_setaffinity(0, cores)
+                except OSError as e:  # pragma: no cover - depends on the container
+                    logger.warning("cannot set CPU affinity: %s", e)
+
+    @staticmethod
+    def set_seed(seed: int):
+        random.seed(seed)
+        np.random.seed(seed % (2 ** 32))
+        torch.manual_seed(seed)
+
+    def init_communication(self, par: dict):
+        """Join the job (``torchrun`` environment) and build the model-parallel groups."""
+        if "RANK" not in os.environ:
+            logger.warning("use_parallel is set but no launcher environment was found; running single process")
+            return
+        if not dist.is_initialized():
+            backend = "nccl" if self.device.type == "cuda" else "gloo"
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            kwargs = {"device_id": self.device} if backend == "nccl" else {}
+            dist.init_process_group(backend, **kwargs)
+        self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
+        tp = int(par.get("model_parallel", 1) or 1)
+        pp = int(par.get("pipeline_stage", 1) or 1)
+        cp = int(par.get("context_parallel", 1) or 1)
+        ep = int(par.get("expert_parallel", 1) or 1)
+        dp = par.get("data_parallel")
+        expect = tp * pp * cp * int(dp or self.world_size // (tp * pp * cp))
+        if expect != self.world_size:
+            raise ValueError(f"data_parallel*model_parallel*context_parallel*pipeline_stage = {expect} does not "
+                             f"match the number of devices {self.world_size}")
+        ps.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+                                     context_parallel_size=cp, expert_model_parallel_size=ep,
+                                     expert_tensor_parallel_size=par.get("expert_model_parallel"),
+                                     virtual_pipeline_model_parallel_size=(par.get("pp_interleave_num") or None)
+                                     if (par.get("pp_interleave_num") or 1) > 1 else None)
+
+
+def build_context(config=None) -> Context:
+    """Create (or replace) the process context from a full configuration mapping."""
+    global _CONTEXT
+    _CONTEXT = Context(config)
+    return _CONTEXT
+
+
+def init_context(use_parallel: bool = False, context_config: Optional[dict] = None,
+                 parallel_config: Optional[dict] = None):
+    """Older two-argument form; returns ``(local_rank, world_size)``."""
+    ctx = build_context({"use_parallel": use_parallel, "context": context_config or {},
+                         "parallel_config": parallel_config or {}})
+    return ctx.local_rank, ctx.world_size
+
+
+def get_context(key: Optional[str] = None):
+    if _CONTEXT is None:
+        raise RuntimeError("build_context() has not been called")
+    if key is None:
+        return _CONTEXT
+    if hasattr(_CONTEXT, key):
+        return getattr(_CONTEXT, key)
+    return _CONTEXT.settings.get(key)
+
+
+def set_context(**kwargs):
+    if _CONTEXT is None:
+        raise RuntimeError("build_context() has not been called")
+    for k, v in kwargs.items():
+        if k == "seed":
+            _CONTEXT.set_seed(v)
+            _CONTEXT.seed = v
+        elif k in ("train_precision_sync", "infer_precision_sync"):
+            _CONTEXT._set_determinism({k: v})
+        else:
+            _CONTEXT.settings[k] = v
+
+
+def is_context_built() -> bool:
+    return _CONTEXT is not None
