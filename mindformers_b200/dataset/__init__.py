@@ -1,0 +1,7 @@
+from .causal_language_model_dataset import (BlendedMegatronDatasetDataLoader, CausalLanguageModelDataset,
+                                            CommonDataLoader, GeneralDataset, IndexedDataLoader, KeyWordGenDataset,
+                                            MockDataLoader, MultiTurnDataset, ResumableShardSampler, build_dataset,
+                                            build_dataset_loader)
+from .gpt_dataset import (BlendedDataset, BlendedMegatronDatasetBuilder, GPTDataset, GPTDatasetConfig, MockGPTDataset)
+from .handlers import AlpacaInstructDataHandler, PackingHandler, build_data_handler
+from .indexed_dataset import IndexedDataset, IndexedDatasetBuilder

@@ -1,0 +1,132 @@
+"""Data handlers: turn raw instruction / chat records into token ids, labels and packed sequences.
+
+Reference: ``dataset/handler/*`` (``AlpacaInstructDataHandler``, ``CodeAlpacaInstructDataHandler``,
+``AdgenInstructDataHandler``, ``PackingHandler`` with ``actual_seq_len``).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Iterable, List, Optional
+
+import numpy as np
+
+from ..tools.register import MindFormerModuleType, MindFormerRegister
+
+IGNORE = -100
+
+ALPACA_WITH_INPUT = ("Below is an instruction that describes a task, paired with an input that provides further "
+                     "context. Write a response that appropriately completes the request.\n\n"
+                     "### Instruction:\n{instruction}\n\n### Input:\n{input}\n\n### Response:\n")
+ALPACA_NO_INPUT = ("Below is an instruction that describes a task. Write a response that appropriately completes "
+                   "the request.\n\n### Instruction:\n{instruction}\n\n### Response:\n")
+
+
+class BaseInstructDataHandler:
+    """Tokenise (prompt, answer) pairs; prompt positions are masked out of the loss."""
+
+    def __init__(self, tokenizer=None, seq_length: int = 2048, padding: bool = True, ignore_token_id: int = IGNORE,
+                 prompt_key: str = "instruction", output_columns=None, **kw):
+        self.tokenizer, self.seq_length, self.padding = tokenizer, seq_length, padding
+        self.ignore = ignore_token_id
+
+    def format(self, record: dict):
+        raise NotImplementedError
+
+    def encode(self, text: str) -> List[int]:
+        if callable(getattr(self.tokenizer, "encode", None)):
+            return list(self.tokenizer.encode(text, add_special_tokens=False))
+        return list(self.tokenizer(text))
+
+    def handle_one(self, record: dict) -> Dict[str, np.ndarray]:
+        prompt, answer = self.format(record)
+        p, a = self.encode(prompt), self.encode(answer)
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        if eos is not None:
+            a = a + [eos]
+        ids = (p + a)[: self.seq_length + 1]
+        labels = ([self.ignore] * len(p) + a)[: self.seq_length + 1]
+        if self.padding:
+            pad = getattr(self.tokenizer, "pad_token_id", 0) or 0
+            ids = ids + [pad] * (self.seq_length + 1 - len(ids))
+            labels = labels + [self.ignore] * (self.seq_length + 1 - len(labels))
+        return {"input_ids": np.asarray(ids, dtype=np.int64), "labels": np.asarray(labels, dtype=np.int64)}
+
+    def handle(self, records: Iterable[dict]) -> List[Dict[str, np.ndarray]]:
+        return [self.handle_one(r) for r in records]
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+class AlpacaInstructDataHandler(BaseInstructDataHandler):
+    def format(self, r):
+        tpl = ALPACA_WITH_INPUT if r.get("input") else ALPACA_NO_INPUT
+        return tpl.format(instruction=r.get("instruction", ""), input=r.get("input", "")), r.get("output", "")
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+class CodeAlpacaInstructDataHandler(AlpacaInstructDataHandler):
+    pass
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+class AdgenInstructDataHandler(BaseInstructDataHandler):
+    def format(self, r):
+        return r.get("content", ""), r.get("summary", "")
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+class PackingHandler:
+    """Greedy first-fit packing of tokenised samples into rows of ``seq_length`` tokens.
+
+    Output rows carry ``input_ids``, ``labels`` (first token of every packed sample masked) and
+    ``actual_seq_len`` (cumulative boundaries, padded with ``seq_length``), the inputs of TND-layout attention.
+    """
+
+    def __init__(self, seq_length: int, pack_strategy: str = "pack", pad_token_id: int = 0,
+                 ignore_token_id: int = IGNORE, max_segments: int = 128, **kw):
+        if pack_strategy not in ("pack", "truncate"):
+            raise ValueError("pack_strategy must be 'pack' or 'truncate'")
+        self.seq_length, self.strategy = seq_length, pack_strategy
+        self.pad, self.ignore, self.max_segments = pad_token_id, ignore_token_id, max_segments
+
+    def handle(self, samples: Iterable[Dict[str, np.ndarray]]) -> List[Dict[str, np.ndarray]]:
+        rows: List[List[Dict[str, np.ndarray]]] = []
+        space: List[int] = []
+        for s in samples:
+            ids = np.asarray(s["input_ids"])
+            lab = np.asarray(s.get("labels", ids))
+            n = min(len(ids), self.seq_length)
+            item = {"input_ids": ids[:n], "labels": lab[:n]}
+            placed = False
+            if self.strategy == "pack":
+                for i, free in enumerate(space):
+                    if free >= n and len(rows[i]) < self.max_segments:
+                        rows[i].append(item)
+                        space[i] -= n
+                        placed = True
+                        break
+            if not placed:
+                rows.append([item])
+                space.append(self.seq_length - n)
+        out = []
+        for items in rows:
+            ids = np.full(self.seq_length, self.pad, dtype=np.int64)
+            lab = np.full(self.seq_length, self.ignore, dtype=np.int64)
+            bounds, pos = [], 0
+            for it in items:
+                n = len(it["input_ids"])
+                ids[pos:pos + n] = it["input_ids"]
+                lab[pos:pos + n] = it["labels"]
+                lab[pos] = self.ignore if pos > 0 else lab[pos]
+                pos += n
+                bounds.append(pos)
+            asl = np.full(self.max_segments, self.seq_length, dtype=np.int32)
+            asl[: len(bounds)] = bounds
+            out.append({"input_ids": ids, "labels": lab, "actual_seq_len": asl})
+        return out
+
+
+def build_data_handler(config: Optional[dict] = None, default_args: Optional[dict] = None, **kwargs):
+    if config is None:
+        return None
+    cfg = dict(config)
+    cfg.update(kwargs)
+    return MindFormerRegister.get_instance_from_cfg(cfg, MindFormerModuleType.DATA_HANDLER, default_args=default_args)

@@ -1,0 +1,105 @@
+import numpy as np
+import torch
+
+from mindformers_b200.dataset import (BlendedDataset, CausalLanguageModelDataset, GPTDataset, GPTDatasetConfig,
+                                      IndexedDataset, IndexedDatasetBuilder, MockGPTDataset, PackingHandler)
+from mindformers_b200.dataset import helpers as H
+
+
+def _oracle_sample_idx(sizes, doc_idx, seq, epochs, tokens_per_epoch, extra=1):
+    """Flatten the documents, cut every seq tokens, and report (doc position, offset) of each cut."""
+    starts, pos = [], 0
+    for d in doc_idx:
+        starts.append(pos)
+        pos += sizes[d]
+    n = (epochs * tokens_per_epoch - extra) // seq
+    out = []
+    for s in range(n + 1):
+        tok = s * seq
+        k = max(i for i, st in enumerate(starts) if st <= tok)
+        # a cut that falls exactly on a document end stays in the previous document (offset = size - extra)
+        if s > 0 and tok == starts[k] and k > 0 and extra == 1:
+            pass
+        out.append((k, tok - starts[k]))
+    return out
+
+
+def test_build_sample_idx_walks_the_token_stream():
+    rng = np.random.RandomState(0)
+    sizes = rng.randint(3, 40, size=20).astype(np.int32)
+    doc_idx = np.concatenate([rng.permutation(20), rng.permutation(20)]).astype(np.int32)
+    tpe = int(sizes.sum())
+    got = H.build_sample_idx(sizes, doc_idx, 16, 2, tpe, True, 1)
+    assert got.shape == ((2 * tpe - 1) // 16 + 1, 2)
+    # every sample covers exactly seq+1 tokens of the flattened stream, consecutive samples overlap by one
+    starts = np.concatenate(([0], np.cumsum(sizes[doc_idx])))[:-1]
+    flat = starts[got[:, 0]] + got[:, 1]
+    assert np.all(np.diff(flat) == 16)
+    assert got[0].tolist() == [0, 0]
+
+
+def test_blending_matches_weights_and_exhaustive_counts():
+    di, ds = np.zeros(1000, np.int16), np.zeros(1000, np.int64)
+    H.build_blending_indices(di, ds, [0.2, 0.5, 0.3], 3, 1000)
+    assert abs((di == 0).mean() - 0.2) < 0.01 and abs((di == 1).mean() - 0.5) < 0.01
+    for d in range(3):
+        assert ds[di == d].tolist() == list(range(int((di == d).sum())))
+    di, ds = np.zeros(12, np.int16), np.zeros(12, np.int64)
+    H.build_exhaustive_blending_indices(di, ds, [2, 7, 3], 3)
+    assert [(di == d).sum() for d in range(3)] == [2, 7, 3]
+
+
+def test_build_mapping_rows_cover_documents():
+    docs = np.array([0, 3, 5, 9])
+    sizes = np.array([10, 12, 8, 30, 5, 7, 9, 11, 6], np.int32)
+    rows = H.build_mapping(docs, sizes, 1, 100, 32, 0.0, 1234)
+    assert sorted(rows[:, :2].tolist()) == [[0, 3], [3, 5], [5, 9]]
+    blocks = H.build_blocks_mapping(docs, sizes, np.array([2, 2, 2], np.int32), 1, 100, 32, 1234)
+    assert blocks.shape[1] == 4 and sorted(blocks[:, 2].tolist()) == [0, 1, 2]
+
+
+def _make_indexed(tmp_path, n_docs=30, seed=0):
+    rng = np.random.RandomState(seed)
+    prefix = str(tmp_path / "corpus")
+    b = IndexedDatasetBuilder(prefix + ".bin", dtype=np.uint16)
+    docs = []
+    for _ in range(n_docs):
+        doc = rng.randint(1, 500, size=rng.randint(5, 60))
+        docs.append(doc)
+        b.add_item(doc)
+        b.end_document()
+    b.finalize(prefix + ".idx")
+    return prefix, docs
+
+
+def test_indexed_dataset_roundtrip_and_gpt_dataset(tmp_path):
+    prefix, docs = _make_indexed(tmp_path)
+    ds = IndexedDataset(prefix)
+    assert len(ds) == len(docs)
+    assert all(np.array_equal(ds[i], docs[i]) for i in range(len(docs)))
+    assert ds.get(3, 2, 3).tolist() == docs[3][2:5].tolist()
+    cfg = GPTDatasetConfig(sequence_length=32, random_seed=7, path_to_cache=str(tmp_path / "cache"))
+    g = GPTDataset(ds, prefix, np.arange(len(ds), dtype=np.int32), 40, "train", cfg)
+    assert len(g) >= 40
+    item = g[5]
+    assert item["input_ids"].shape == (32,) and torch.equal(item["input_ids"][1:], item["labels"][:-1])
+    # cached indices are reused and give the same samples
+    g2 = GPTDataset(ds, prefix, np.arange(len(ds), dtype=np.int32), 40, "train", cfg)
+    assert torch.equal(g2[5]["input_ids"], item["input_ids"])
+
+
+def test_mock_blend_loader_and_packing():
+    cfg = GPTDatasetConfig(sequence_length=16, random_seed=1, vocab_size=100)
+    a, b = MockGPTDataset(50, cfg, 100), MockGPTDataset(50, cfg, 100)
+    assert torch.equal(a[3]["input_ids"], b[3]["input_ids"])
+    blend = BlendedDataset([a, b], [0.25, 0.75], 40)
+    assert len(blend) == 40 and int(blend[0]["dataset_id"]) in (0, 1)
+    loader = CausalLanguageModelDataset({"data_loader": {"type": "MockDataLoader", "seq_length": 16, "vocab_size": 100,
+                                                         "num_samples": 20}, "batch_size": 4, "pin_memory": False})
+    batches = list(loader)
+    assert len(batches) == 5 and batches[0]["input_ids"].shape == (4, 16)
+    loader.set_init_step(3)
+    assert len(list(loader)) == 2
+    packed = PackingHandler(seq_length=16, max_segments=4).handle(
+        [{"input_ids": np.arange(1, 8)}, {"input_ids": np.arange(1, 10)}, {"input_ids": np.arange(1, 6)}])
+    assert len(packed) == 2 and packed[0]["actual_seq_len"].tolist() == [7, 16, 16, 16]
