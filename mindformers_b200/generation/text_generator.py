@@ -1,0 +1,280 @@
+"""``GenerationMixin``: prefill/decode loop over the paged KV cache with greedy, sampling and beam search.
+
+Reference: ``generation/text_generator.py`` (``generate`` :731-1128, cache set-up :114-160, mcore input
+preparation :1335-1382, chunked prefill :1541, post-processing :1590-1726, ``chat`` :1727). The loop runs on the
+host, one iteration per generated token; the model sees flattened tokens ``[T]`` with ``positions``,
+``q_seq_lens``, block tables and a slot mapping. Sampling runs on the device (one ``multinomial`` per step).
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..inference.block_manager import BlockTables
+from ..inference.paged_attention import KVCacheContext
+from ..parallel import parallel_state as ps
+from ..parallel.layers.attention import AttnMeta
+from ..tools.logger import logger
+from .beam_search import BeamSearchScorer
+from .generation_config import GenerationConfig
+from .logits_process import LogitsProcessorList, SamplingLogitsProcessor, build_processors
+
+
+class GenerationMixin:
+    """Mixed into ``PreTrainedModel``; expects ``self.config`` (TransformerConfig-like) and ``self.model``
+    (a ``GPTModel``)."""
+
+    generation_config: Optional[GenerationConfig] = None
+
+    # ---- cache --------------------------------------------------------------------------------------
+    def _set_kv_cache(self, batch_size: int, max_len: int, num_blocks: Optional[int] = None):
+        cfg = self.config
+        block_size = int(getattr(cfg, "block_size", 16) or 16)
+        need = batch_size * (-(-max_len // block_size))
+        num_blocks = max(int(num_blocks or 0), need)
+        tp = ps.get_tensor_model_parallel_world_size()
+        device = next(self.parameters()).device
+        dtype = next(self.parameters()).dtype
+        n_layers = len(self.model.decoder.layers)
+        if getattr(cfg, "multi_latent_attention", False):
+            ctx = KVCacheContext(n_layers, num_blocks, block_size, 1, 0, dtype, device,
+                                 mla_latent_dim=cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
+        else:
+            kvh = max(1, cfg.num_query_groups // tp)
+            ctx = KVCacheContext(n_layers, num_blocks, block_size, kvh, cfg.kv_channels, dtype, device)
+        ctx.layer_offset = self.model.decoder.layer_ids[0] if self.model.decoder.layer_ids else 0
+        tables = BlockTables(num_blocks, block_size, max_len)
+        return ctx, tables
+
+    # ---- one model call -------------------------------------------------------------------------------
+    @torch.no_grad()
+    def _forward_step(self, tokens: List[List[int]], starts: List[int], ctx: KVCacheContext, tables: BlockTables,
+                      prefill: bool, active: Optional[List[bool]] = None) -> torch.Tensor:
+        """Run the model on the new ``tokens`` of every sequence (positions start at ``starts``).
+        Returns logits ``[B, V]`` of the last new token of each sequence."""
+        device = next(self.parameters()).device
+        lens = [len(t) for t in tokens]
+        if prefill:
+            table, slots = tables.assemble_pa_full_inputs(lens, active)
+        else:
+            table, slots = tables.assemble_pa_inc_inputs(active, 1)
+        flat = torch.tensor([x for t in tokens for x in t], dtype=torch.int64, device=device)
+        pos = torch.tensor([s + i for t, s in zip(tokens, starts) for i in range(len(t))], dtype=torch.int64, device=device)
+        ctx.set_step(is_prefill=prefill, block_tables=table, slot_mapping=slots, context_lens=tables.context_lens(),
+                     q_seq_lens=lens, device=device)
+        meta = AttnMeta(batch=1, seq_len=int(flat.numel()), positions=pos, cache=ctx)
+        logits = self.model(flat.unsqueeze(0), attn_meta=meta)
+        if not prefill:
+            pass  # decode: one row per sequence already
+        elif logits.shape[0] != len(tokens):
+            logits = logits.index_select(0, ctx.last_token_index)
+        tp = ps.get_tensor_model_parallel_world_size()
+        if tp > 1:
+            parts = [torch.empty_like(logits) for _ in range(tp)]
+            torch.distributed.all_gather(parts, logits.contiguous(), group=ps.get_tensor_model_parallel_group())
+            logits = torch.cat(parts, dim=-1)
+        return logits[:, : self.config.vocab_size]
+
+    # ---- public API -----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]], torch.Tensor],
+                 generation_config: Optional[GenerationConfig] = None, logits_processor: Optional[LogitsProcessorList] = None,
+                 streamer=None, seed: Optional[int] = None, **kwargs):
+        """Returns a list (one per prompt) of token-id lists: prompt followed by the generated tokens."""
+        self.eval()
+        gcfg = GenerationConfig(**(generation_config or self.generation_config or GenerationConfig()).to_dict())
+        gcfg.update(**kwargs)
+        prompts = self._normalise_inputs(input_ids, gcfg.pad_token_id)
+        B = len(prompts)
+        max_prompt = max(len(p) for p in prompts)
+        max_len = gcfg.max_length if gcfg.max_new_tokens is None else max_prompt + gcfg.max_new_tokens
+        max_len = min(int(max_len), int(getattr(self.config, "seq_length", max_len) or max_len)) \
+            if gcfg.max_new_tokens is None else int(max_len)
+        if max_len <= min(len(p) for p in prompts):
+            raise ValueError(f"max_length ({max_len}) must exceed the prompt length")
+        if gcfg.num_beams > 1:
+            return self._beam_search(prompts, gcfg, max_len)
+        device = next(self.parameters()).device
+        gen = torch.Generator(device=device)
+        if seed is not None or gcfg.seed is not None:
+            gen.manual_seed(int(seed if seed is not None else gcfg.seed))
+        processors = build_processors(gcfg, max_prompt)
+        if logits_processor:
+            processors.extend(logits_processor)
+        warper = SamplingLogitsProcessor(True, gcfg.temperature, gcfg.top_k, gcfg.top_p) if gcfg.do_sample else None
+        eos = set(gcfg.eos_ids())
+        ctx, tables = self._set_kv_cache(B, max_len, getattr(self.config, "num_blocks", None))
+        tables.init_cache_engine(B)
+        seqs = [list(p) for p in prompts]
+        finished = [False] * B
+        t0 = time.time()
+        if streamer is not None:
+            streamer.put(seqs if B > 1 else seqs[0])
+        # prefill (optionally in chunks)
+        chunk = gcfg.chunk_prefill_size
+        if chunk and max_prompt > chunk:
+            done = [0] * B
+            logits = None
+            while any(d < len(p) for d, p in zip(done, prompts)):
+                toks = [p[d:d + chunk] for p, d in zip(prompts, done)]
+                act = [len(t) > 0 for t in toks]
+                step_logits = self._forward_step(toks, done, ctx, tables, True, act)
+                if logits is None:
+                    logits = torch.zeros(B, step_logits.shape[-1], device=device)
+                rows = [i for i, a in enumerate(act) if a]
+                for j, i in enumerate(rows):
+                    if done[i] + len(toks[i]) >= len(prompts[i]):
+                        logits[i] = step_logits[j]
+                done = [d + len(t) for d, t in zip(done, toks)]
+        else:
+            logits = self._forward_step(seqs, [0] * B, ctx, tables, True)
+        ttft = time.time() - t0
+        new_tokens = 0
+        while True:
+            nxt = self._select(seqs, logits, processors, warper, gen, gcfg)
+            for i in range(B):
+                if finished[i]:
+                    continue
+                tok = int(nxt[i])
+                seqs[i].append(tok)
+                new_tokens += 1
+                limit = max_len if gcfg.max_new_tokens is None else len(prompts[i]) + gcfg.max_new_tokens
+                if tok in eos or len(seqs[i]) >= limit:
+                    finished[i] = True
+            if streamer is not None:
+                streamer.put([int(nxt[0])] if B == 1 else [[int(t)] for t in nxt])
+            if all(finished):
+                break
+            act = [not f for f in finished]
+            toks = [[s[-1]] for s in seqs]
+            logits = self._forward_step(toks, [len(s) - 1 for s in seqs], ctx, tables, False, act)
+        if streamer is not None:
+            streamer.end()
+        tables.clear_cache()
+        dt = max(time.time() - t0, 1e-9)
+        self.last_generation_stats = {"ttft_s": ttft, "new_tokens": new_tokens, "total_s": dt,
+                                      "tokens_per_s": new_tokens / dt}
+        logger.info("generate: %d new tokens in %.3f s (%.1f tokens/s, first token %.3f s)", new_tokens, dt,
+                    new_tokens / dt, ttft)
+        return seqs
+
+    def _select(self, seqs, logits, processors, warper, gen, gcfg):
+        L = max(len(s) for s in seqs)
+        ids = torch.full((len(seqs), L), -1, dtype=torch.int64, device=logits.device)
+        for i, s in enumerate(seqs):
+            ids[i, : len(s)] = torch.tensor(s, dtype=torch.int64, device=logits.device)
+        scores = logits.float()
+        if len(processors):
+            scores = processors(ids, scores)
+        if warper is None:
+            return scores.argmax(-1).tolist()
+        probs = torch.softmax(warper(ids, scores), dim=-1)
+        return torch.multinomial(probs, 1, generator=gen).squeeze(-1).tolist()
+
+    @staticmethod
+    def _normalise_inputs(input_ids, pad_token_id) -> List[List[int]]:
+        if isinstance(input_ids, torch.Tensor):
+            input_ids = input_ids.tolist()
+        if isinstance(input_ids, np.ndarray):
+            input_ids = input_ids.tolist()
+        if len(input_ids) and not isinstance(input_ids[0], (list, tuple)):
+            input_ids = [list(input_ids)]
+        out = []
+        for row in input_ids:
+            row = [int(x) for x in row]
+            if pad_token_id is not None:
+                while len(row) > 1 and row[-1] == pad_token_id:
+                    row.pop()
+            out.append(row)
+        return out
+
+    # ---- beam search ------------------------------------------------------------------------------------
+    def _beam_search(self, prompts, gcfg, max_len):
+        B, nb = len(prompts), gcfg.num_beams
+        device = next(self.parameters()).device
+        eos = gcfg.eos_ids()
+        pad = gcfg.pad_token_id if gcfg.pad_token_id is not None else 0
+        ctx, tables = self._set_kv_cache(B * nb, max_len, None)
+        tables.init_cache_engine(B * nb)
+        flat = [list(p) for p in prompts for _ in range(nb)]
+        prompt_len = max(len(p) for p in prompts)
+        scorer = BeamSearchScorer(B, nb, gcfg.length_penalty, gcfg.early_stopping, gcfg.num_return_sequences)
+        beam_scores = torch.zeros(B, nb)
+        beam_scores[:, 1:] = -1e9
+        logits = self._forward_step(flat, [0] * (B * nb), ctx, tables, True)
+        processors = build_processors(gcfg, prompt_len)
+        while True:
+            L = max(len(s) for s in flat)
+            ids = torch.full((B * nb, L), -1, dtype=torch.int64, device=device)
+            for i, s in enumerate(flat):
+                ids[i, : len(s)] = torch.tensor(s, device=device)
+            logp = torch.log_softmax(processors(ids, logits.float()) if len(processors) else logits.float(), dim=-1).cpu()
+            V = logp.shape[-1]
+            total = (logp.view(B, nb, V) + beam_scores.unsqueeze(-1)).view(B, nb * V)
+            top_s, top_i = total.topk(2 * nb, dim=-1)
+            seqs = [[flat[b * nb + k] for k in range(nb)] for b in range(B)]
+            beam_scores, toks, idx = scorer.process(seqs, top_s, top_i % V, top_i // V, eos, prompt_len, pad)
+            new_flat, src = [], []
+            for b in range(B):
+                for k in range(nb):
+                    j = int(idx[b, k])
+                    new_flat.append(seqs[b][j] + [int(toks[b, k])])
+                    src.append(b * nb + j)
+            self._reorder_cache(ctx, tables, src)
+            flat = new_flat
+            if scorer.is_done or max(len(s) for s in flat) >= max_len:
+                break
+            logits = self._forward_step([[s[-1]] for s in flat], [len(s) - 1 for s in flat], ctx, tables, False)
+        seqs = [[flat[b * nb + k] for k in range(nb)] for b in range(B)]
+        best = scorer.finalize(seqs, beam_scores, prompt_len)
+        tables.clear_cache()
+        if gcfg.num_return_sequences == 1:
+            return [b[0] for b in best]
+        return [s for b in best for s in b]
+
+    @staticmethod
+    def _reorder_cache(ctx: KVCacheContext, tables: BlockTables, src: List[int]):
+        """Beam ``i`` continues from beam ``src[i]``: copy the cache contents block by block."""
+        if src == list(range(len(src))):
+            return
+        dst_blocks, src_blocks = [], []
+        for i, j in enumerate(src):
+            if i == j:
+                continue
+            n = min(len(tables.engines[i].blocks), len(tables.engines[j].blocks))
+            dst_blocks += tables.engines[i].blocks[:n]
+            src_blocks += tables.engines[j].blocks[:n]
+        if not dst_blocks:
+            return
+        d = torch.tensor(dst_blocks, device=ctx.key_cache[0].device)
+        s = torch.tensor(src_blocks, device=ctx.key_cache[0].device)
+        for layer in range(ctx.num_layers):
+            ctx.key_cache[layer][d] = ctx.key_cache[layer][s].clone()
+            if ctx.value_cache[layer] is not None:
+                ctx.value_cache[layer][d] = ctx.value_cache[layer][s].clone()
+
+    # ---- chat ---------------------------------------------------------------------------------------------
+    def chat(self, tokenizer, query: str, history: Optional[list] = None, system_role_name: str = "system",
+             user_role_name: str = "user", assistant_role_name: str = "assistant", instruction: str = "",
+             max_length: int = 512, do_sample: bool = False, top_k: int = 1, top_p: float = 1.0,
+             temperature: float = 1.0, repetition_penalty: float = 1.0):
+        """One chat turn through the tokenizer's chat template; returns ``(response, history)``."""
+        history = list(history or [])
+        if instruction and not history:
+            history.append({"role": system_role_name, "content": instruction})
+        history.append({"role": user_role_name, "content": query})
+        if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
+            ids = tokenizer.apply_chat_template(history, add_generation_prompt=True, tokenize=True)
+        else:
+            text = "".join(f"<|{m['role']}|>\n{m['content']}\n" for m in history) + f"<|{assistant_role_name}|>\n"
+            ids = tokenizer.encode(text)
+        out = self.generate([ids], max_length=max_length, do_sample=do_sample, top_k=top_k, top_p=top_p,
+                            temperature=temperature, repetition_penalty=repetition_penalty,
+                            eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                            pad_token_id=getattr(tokenizer, "pad_token_id", None))[0]
+        response = tokenizer.decode(out[len(ids):], skip_special_tokens=True)
+        history.append({"role": assistant_role_name, "content": response})
+        return response, history

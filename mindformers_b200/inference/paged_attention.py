@@ -1,0 +1,162 @@
+"""Attention over the paged KV cache: cache allocation, prefill and decode paths.
+
+Reference: ``parallel_core/inference/transformer/flash_attention.py`` (prefill = cache write + varlen flash
+attention :94-107; decode = paged attention :109-145), MLA mode with one latent "head" of width
+``kv_lora_rank + rope_dim`` (``multi_latent_attention.py:401-448``), cache shapes from
+``generation/text_generator.py:114-160``.
+
+``KVCacheContext`` travels in ``AttnMeta.cache``; it owns the per-layer cache tensors and the device copies of
+the block table, slot mapping and lengths for the current step.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..ops import _lib
+from ..ops import functional as Fn
+
+
+class KVCacheContext:
+    def __init__(self, num_layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
+                 dtype=torch.bfloat16, device="cuda", mla_latent_dim: Optional[int] = None):
+        self.num_layers, self.num_blocks, self.block_size = num_layers, num_blocks, block_size
+        self.kv_heads, self.head_dim, self.mla_dim = kv_heads, head_dim, mla_latent_dim
+        if mla_latent_dim:
+            self.key_cache = [torch.zeros(num_blocks, block_size, 1, mla_latent_dim, dtype=dtype, device=device)
+                              for _ in range(num_layers)]
+            self.value_cache = [None] * num_layers
+        else:
+            shape = (num_blocks, block_size, kv_heads, head_dim)
+            self.key_cache = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+            self.value_cache = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.is_prefill = True
+        self.block_tables = None      # int32 [B, max_blocks]
+        self.slot_mapping = None      # int32 [T]
+        self.context_lens = None      # int32 [B] tokens in cache after this step
+        self.q_seq_lens = None        # int32 [B] new tokens of each sequence in this step
+        self.last_token_index = None  # int64 [B] row of the last new token of each sequence
+        self.cu_q = None              # python list of cumulative q lengths
+        self.layer_offset = 0
+
+    def set_step(self, *, is_prefill, block_tables, slot_mapping, context_lens, q_seq_lens, device):
+        self.is_prefill = is_prefill
+        self.block_tables = torch.as_tensor(block_tables, dtype=torch.int32, device=device).contiguous()
+        self.slot_mapping = torch.as_tensor(slot_mapping, dtype=torch.int32, device=device).contiguous()
+        self.context_lens = torch.as_tensor(context_lens, dtype=torch.int32, device=device).contiguous()
+        q = [int(x) for x in q_seq_lens]
+        self.q_seq_lens = torch.as_tensor(q, dtype=torch.int32, device=device)
+        cu = [0]
+        for n in q:
+            cu.append(cu[-1] + n)
+        self.cu_q = cu
+        self.last_token_index = torch.as_tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=device)
+
+
+def _write_cache(cache: KVCacheContext, layer: int, k: torch.Tensor, v: Optional[torch.Tensor]):
+    """k, v: [T, heads, hd] (views with token stride); scatter rows into the layer's cache by slot."""
+    T = k.shape[0]
+    kc, vc = cache.key_cache[layer], cache.value_cache[layer]
+    row = k.shape[1] * k.shape[2]
+    if k.is_cuda and k.dtype == torch.bfloat16 and row % 8 == 0 and k.stride(2) == 1 and k.stride(1) == k.shape[2]:
+        rc = _lib.get_lib().mfb_reshape_and_cache(k.data_ptr(), _lib.ptr(v), kc.data_ptr(), _lib.ptr(vc),
+                                                  cache.slot_mapping.data_ptr(), T, row, k.stride(0),
+                                                  v.stride(0) if v is not None else 0, _lib.stream_ptr())
+        _lib.check(rc, "mfb_reshape_and_cache")
+        _lib.count_launch()
+        return
+    slots = cache.slot_mapping.long()
+    ok = slots >= 0
+    kc.view(-1, row)[slots[ok]] = k.reshape(T, row)[ok].to(kc.dtype)
+    if v is not None:
+        vc.view(-1, row)[slots[ok]] = v.reshape(T, row)[ok].to(vc.dtype)
+
+
+def _gather(cache_t: torch.Tensor, table_row: torch.Tensor, n: int, block_size: int) -> torch.Tensor:
+    nb = -(-n // block_size)
+    blocks = table_row[:nb].long()
+    return cache_t[blocks].reshape(nb * block_size, *cache_t.shape[2:])[:n]
+
+
+def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
+    """q: [T, nq, hd]; k/v: [T, nkv, hd] of the new tokens. Returns [T, nq*hd]."""
+    cache: KVCacheContext = meta.cache
+    layer = layer_number - 1 - cache.layer_offset
+    _write_cache(cache, layer, k, v)
+    T, nq, hd = q.shape
+    nkv = k.shape[1]
+    B = cache.context_lens.shape[0]
+    if not cache.is_prefill and T == B:
+        out = torch.empty((T, nq, hd), dtype=q.dtype, device=q.device)
+        if q.is_cuda and q.dtype == torch.bfloat16 and hd in (64, 128) and nq // nkv <= 16:
+            qc = q.contiguous()
+            rc = _lib.get_lib().mfb_paged_decode_attention(
+                qc.data_ptr(), cache.key_cache[layer].data_ptr(), cache.value_cache[layer].data_ptr(),
+                cache.block_tables.data_ptr(), cache.context_lens.data_ptr(), out.data_ptr(), B, nq, nkv, hd,
+                cache.block_size, cache.block_tables.shape[1], float(scale), _lib.stream_ptr())
+            _lib.check(rc, "mfb_paged_decode_attention")
+            _lib.count_launch()
+            return out.view(T, nq * hd)
+        lens = cache.context_lens.tolist()
+        for b in range(B):
+            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            o = Fn.attention_reference(q[b:b + 1].unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), causal=False, scale=scale)
+            out[b] = o[0, 0]
+        return out.view(T, nq * hd)
+    # prefill (optionally with history, e.g. chunked prefill): per-sequence causal attention
+    outs = []
+    lens = cache.context_lens.tolist()
+    for b in range(B):
+        a, e = cache.cu_q[b], cache.cu_q[b + 1]
+        if e == a:
+            continue
+        nq_tok = e - a
+        if lens[b] == nq_tok:
+            o = Fn.attention(q[a:e].unsqueeze(0), k[a:e].unsqueeze(0), v[a:e].unsqueeze(0), causal=True, scale=scale)
+        else:
+            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            o = Fn.attention_reference(q[a:e].unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), causal=True, scale=scale,
+                                       q_offset=lens[b] - nq_tok)
+        outs.append(o.reshape(nq_tok, nq * v.shape[-1]))
+    return torch.cat(outs, dim=0)
+
+
+def mla_paged_attention_forward(attn, q_nope, q_pe, kv_c, k_pe, meta):
+    """Multi-latent attention with a latent cache ``[kv_lora ‖ k_pe]``.
+
+    Prefill expands K/V from the latent with ``linear_kvb``; decode absorbs the up-projections: queries are
+    mapped into the latent space (``q_nope @ W_UK``), attention runs against the cached latents, and the result is
+    mapped back with ``W_UV`` (reference ``multi_latent_attention.py:219-231,434-448``).
+    """
+    cache: KVCacheContext = meta.cache
+    layer = attn.layer_number - 1 - cache.layer_offset
+    T = q_nope.shape[0]
+    latent = torch.cat((kv_c, k_pe.reshape(T, -1)), dim=-1).unsqueeze(1)     # [T, 1, rank + rope]
+    _write_cache(cache, layer, latent.contiguous(), None)
+    nh, nope, rope_d, vd, rank = attn.nh, attn.nope, attn.rope_d, attn.vd, attn.kv_rank
+    w = attn.linear_kvb.weight.view(nh, nope + vd, rank)
+    w_uk, w_uv = w[:, :nope], w[:, nope:]                                      # [nh, nope, rank], [nh, vd, rank]
+    B = cache.context_lens.shape[0]
+    lens = cache.context_lens.tolist()
+    outs = []
+    for b in range(B):
+        a, e = cache.cu_q[b], cache.cu_q[b + 1]
+        if e == a:
+            continue
+        lat = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size)[:, 0]  # [L, rank+rope]
+        c, pe = lat[:, :rank].float(), lat[:, rank:].float()
+        q_lat = torch.einsum("thn,hnr->thr", q_nope[a:e].float(), w_uk.float())    # absorbed query
+        s = (torch.einsum("thr,lr->htl", q_lat, c) + torch.einsum("thd,ld->htl", q_pe[a:e].float(), pe)) * attn.scale
+        nq_tok, L = e - a, lens[b]
+        qi = torch.arange(nq_tok, device=s.device).unsqueeze(-1) + (L - nq_tok)
+        ki = torch.arange(L, device=s.device).unsqueeze(0)
+        s = s.masked_fill((ki > qi).unsqueeze(0), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        o_lat = torch.einsum("htl,lr->thr", p, c)
+        o = torch.einsum("thr,hvr->thv", o_lat, w_uv.float())
+        outs.append(o.reshape(nq_tok, nh * vd).to(q_nope.dtype))
+    return torch.cat(outs, dim=0)

@@ -1,0 +1,20 @@
+from .auto import AutoConfig, AutoModel, AutoModelForCausalLM, AutoProcessor, AutoTokenizer
+from .configuration_utils import PretrainedConfig
+from .families import (ChatGLM2ForConditionalGeneration, DeepseekV3Config, DeepseekV3ForCausalLM, LlamaConfig,
+                       LlamaForCausalLM, MixtralConfig, MixtralForCausalLM, Qwen2Config, Qwen2ForCausalLM, Qwen3Config,
+                       Qwen3ForCausalLM, Qwen3MoeConfig, Qwen3MoeForCausalLM, TelechatConfig, TelechatForCausalLM)
+from .modeling_utils import PreTrainedModel
+from .presets import PRESETS, get_preset
+from .tokenization import ByteTokenizer, TextProcessor, build_tokenizer
+
+
+def build_network(config: dict, default_args=None):
+    """Model from the YAML ``model`` section: ``{"arch": {"type": ...}, "model_config": {...}}``."""
+    mc = dict(config.get("model_config") or {})
+    if default_args:
+        mc.update(default_args)
+    arch = (config.get("arch") or {}).get("type")
+    if arch and "architectures" not in mc:
+        mc["architectures"] = [arch]
+    mc.pop("type", None)
+    return AutoModel.from_config(mc)

@@ -1,0 +1,83 @@
+"""Model families: configuration classes and ``…ForCausalLM`` classes, registered for YAML and Auto lookup.
+
+Reference: ``models/llama`` (legacy), ``models/qwen2``, ``models/qwen3``, ``models/qwen3_moe``,
+``models/deepseek3`` (mcore shims) and the research families (Llama-3.1, Qwen2.5, Mixtral, TeleChat2, GLM-4),
+which here differ only in configuration defaults: all of them are instances of the same ``GPTModel``.
+"""
+from __future__ import annotations
+
+from ..tools.register import MindFormerModuleType, MindFormerRegister
+from .configuration_utils import PretrainedConfig
+from .modeling_utils import PreTrainedModel
+
+_BASE = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32,
+             num_key_value_heads=None, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=4096,
+             tie_word_embeddings=False, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+
+
+def _config(name, model_type, defaults, is_mla=False):
+    base = dict(_BASE)
+    base.update(defaults)
+
+    class _Cfg(PretrainedConfig):
+        @classmethod
+        def default_values(cls):
+            return dict(base)
+
+    _Cfg.__name__ = _Cfg.__qualname__ = name
+    _Cfg.model_type = model_type
+    _Cfg.is_mla = is_mla
+    MindFormerRegister.register_cls(_Cfg, MindFormerModuleType.CONFIG, alias=name)
+    MindFormerRegister.register_cls(_Cfg, MindFormerModuleType.CONFIG, alias=name, legacy=False)
+    return _Cfg
+
+
+def _model(name, cfg_cls, family):
+    class _M(PreTrainedModel):
+        config_class = cfg_cls
+        weight_family = family
+
+    _M.__name__ = _M.__qualname__ = name
+    MindFormerRegister.register_cls(_M, MindFormerModuleType.MODELS, alias=name)
+    MindFormerRegister.register_cls(_M, MindFormerModuleType.MODELS, alias=name, legacy=False)
+    return _M
+
+
+LlamaConfig = _config("LlamaConfig", "llama", dict(rms_norm_eps=1e-5))
+Qwen2Config = _config("Qwen2Config", "qwen2", dict(vocab_size=152064, attention_bias=True, rope_theta=1e6))
+Qwen3Config = _config("Qwen3Config", "qwen3", dict(vocab_size=151936, qk_layernorm=True, head_dim=128, rope_theta=1e6))
+Qwen3MoeConfig = _config("Qwen3MoeConfig", "qwen3_moe",
+                         dict(vocab_size=151936, qk_layernorm=True, head_dim=128, rope_theta=1e6, num_experts=128,
+                              num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
+                              first_k_dense_replace=0, moe_router_score_function="softmax"))
+DeepseekV3Config = _config("DeepseekV3Config", "deepseek_v3",
+                           dict(vocab_size=129280, hidden_size=7168, intermediate_size=18432, num_hidden_layers=61,
+                                num_attention_heads=128, num_key_value_heads=128, n_routed_experts=256,
+                                n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, n_group=8,
+                                topk_group=4, routed_scaling_factor=2.5, norm_topk_prob=True, scoring_func="sigmoid",
+                                first_k_dense_replace=3, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                                qk_rope_head_dim=64, v_head_dim=128, moe_router_enable_expert_bias=True,
+                                rope_interleave=True), is_mla=True)
+MixtralConfig = _config("MixtralConfig", "mixtral",
+                        dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=14336, norm_topk_prob=True,
+                             first_k_dense_replace=0, num_key_value_heads=8, rope_theta=1e6))
+TelechatConfig = _config("TelechatConfig", "telechat", dict(vocab_size=131072))
+ChatGLM4Config = _config("ChatGLM2Config", "glm", dict(vocab_size=151552, attention_bias=True, num_key_value_heads=2))
+
+LlamaForCausalLM = _model("LlamaForCausalLM", LlamaConfig, "llama")
+Qwen2ForCausalLM = _model("Qwen2ForCausalLM", Qwen2Config, "qwen2")
+Qwen3ForCausalLM = _model("Qwen3ForCausalLM", Qwen3Config, "qwen3")
+Qwen3MoeForCausalLM = _model("Qwen3MoeForCausalLM", Qwen3MoeConfig, "qwen3_moe")
+DeepseekV3ForCausalLM = _model("DeepseekV3ForCausalLM", DeepseekV3Config, "deepseek_v3")
+MixtralForCausalLM = _model("MixtralForCausalLM", MixtralConfig, "mixtral")
+TelechatForCausalLM = _model("TelechatForCausalLM", TelechatConfig, "telechat")
+ChatGLM2ForConditionalGeneration = _model("ChatGLM2ForConditionalGeneration", ChatGLM4Config, "glm")
+
+MODEL_TYPE_TO_CLASSES = {
+    "llama": (LlamaConfig, LlamaForCausalLM), "qwen2": (Qwen2Config, Qwen2ForCausalLM),
+    "qwen2_5": (Qwen2Config, Qwen2ForCausalLM), "qwen3": (Qwen3Config, Qwen3ForCausalLM),
+    "qwen3_moe": (Qwen3MoeConfig, Qwen3MoeForCausalLM), "deepseek_v3": (DeepseekV3Config, DeepseekV3ForCausalLM),
+    "deepseekv3": (DeepseekV3Config, DeepseekV3ForCausalLM), "mixtral": (MixtralConfig, MixtralForCausalLM),
+    "telechat": (TelechatConfig, TelechatForCausalLM), "glm": (ChatGLM4Config, ChatGLM2ForConditionalGeneration),
+    "chatglm": (ChatGLM4Config, ChatGLM2ForConditionalGeneration),
+}

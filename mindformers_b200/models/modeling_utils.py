@@ -1,0 +1,111 @@
+"""``PreTrainedModel``: base of every causal-LM class (build, load, save, generate).
+
+Reference: ``models/modeling_utils.py`` (``PreTrainedModel`` :216, ``from_pretrained`` :855-1266,
+``save_pretrained`` with sharding :87, name-conversion hooks :1507-1522) and the per-model shims
+(``qwen3/modeling_qwen3.py:27-54`` etc.). Unlike the reference there is one network class for training and
+inference; ``RUN_MODE=predict`` only changes defaults (eval mode, no optimizer).
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..checkpoint import io as ckpt_io
+from ..checkpoint import name_maps
+from ..generation import GenerationConfig, GenerationMixin
+from ..parallel.layers.gpt_model import GPTModel
+from ..parallel.transformer_config_utils import convert_to_transformer_config
+from ..tools.logger import logger
+from .configuration_utils import PretrainedConfig
+
+
+class PreTrainedModel(nn.Module, GenerationMixin):
+    config_class = PretrainedConfig
+    base_model_prefix = "model"
+    weight_family = "llama"
+
+    def __init__(self, config: PretrainedConfig, device=None, dtype=None, **kwargs):
+        super().__init__()
+        if isinstance(config, dict):
+            config = self.config_class(**config)
+        self.model_config = config
+        d = config.to_dict()
+        d.update(kwargs)
+        if dtype is not None:
+            d["params_dtype"] = d["compute_dtype"] = dtype
+        d.setdefault("params_dtype", d.get("torch_dtype") or d.get("dtype") or "bfloat16")
+        d.setdefault("compute_dtype", d["params_dtype"])
+        if d.get("seq_length") is None and d.get("max_position_embeddings"):
+            d["seq_length"] = min(int(d["max_position_embeddings"]), 8192)
+        tcfg = convert_to_transformer_config(d, is_mla_model=type(config).is_mla or "kv_lora_rank" in d, strict=False)
+        tcfg.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        self.config = tcfg
+        self.model = GPTModel(tcfg)
+        self.generation_config = GenerationConfig.from_model_config(config)
+
+    # ---- forward ----------------------------------------------------------------------------------------
+    def forward(self, input_ids, labels=None, loss_mask=None, position_ids=None, attn_meta=None, **kw):
+        return self.model(input_ids, labels, loss_mask, position_ids, attn_meta)
+
+    # make checkpoints carry the network's own names (no "model." prefix)
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):
+        for n, p in super().named_parameters(prefix, recurse, remove_duplicate):
+            yield (n[len("model."):] if n.startswith("model.") else n), p
+
+    def named_buffers(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):
+        for n, b in super().named_buffers(prefix, recurse, remove_duplicate):
+            yield (n[len("model."):] if n.startswith("model.") else n), b
+
+    # ---- name conversion hooks ----------------------------------------------------------------------------
+    def convert_name(self, weight_name: str) -> str:
+        return name_maps.convert_name(weight_name, self.weight_family)
+
+    def convert_weight_dict(self, source_dict: dict, **kwargs) -> dict:
+        return name_maps.hf_to_framework(source_dict, self.config, self.weight_family)
+
+    def obtain_name_map(self, hf_keys) -> dict:
+        return {k: self.convert_name(k) for k in hf_keys}
+
+    # ---- load / save ------------------------------------------------------------------------------------------
+    def load_weights(self, path: str, strict: bool = True):
+        return ckpt_io.load_checkpoint(self, path, strict=strict, family=self.weight_family)
+
+    load_checkpoint = load_weights
+
+    @classmethod
+    def from_pretrained(cls, pretrained_model_name_or_dir: str, *, config: Optional[PretrainedConfig] = None,
+                        load_weights: bool = True, strict: bool = False, **kwargs) -> "PreTrainedModel":
+        path = pretrained_model_name_or_dir
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} does not exist (hub download is not available offline)")
+        if config is None:
+            config = cls.config_class.from_pretrained(path)
+        model = cls(config, **kwargs)
+        if load_weights:
+            try:
+                ckpt_io.resolve_checkpoint(path)
+                model.load_weights(path, strict=strict)
+            except FileNotFoundError:
+                logger.warning("no weights found under %s: the model keeps its random initialisation", path)
+        return model
+
+    def save_pretrained(self, save_directory: str, max_shard_size: str = "5GB", hf_names: bool = False, **kw):
+        size = _parse_size(max_shard_size)
+        ckpt_io.save_pretrained_dir(self, save_directory, self.model_config.to_dict(), size, hf_names, self.weight_family)
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+
+def _parse_size(s) -> int:
+    if isinstance(s, int):
+        return s
+    s = str(s).upper()
+    for unit, mul in (("GB", 1 << 30), ("MB", 1 << 20), ("KB", 1 << 10)):
+        if s.endswith(unit):
+            return int(float(s[:-2]) * mul)
+    return int(s)
