@@ -187,6 +187,14 @@ class DistributedOptimizer:
         """Norm of the last step's gradients (device scalar)."""
         return self.sumsq.sqrt() * abs(grad_scale)
 
+    def state_norms(self) -> Dict[str, float]:
+        """L2 norms of this rank's moment shards (for ``TrainingStateMonitor``)."""
+        out = {}
+        for name, sh in self.shards.items():
+            out[f"{name}.adam_m"] = float(sh.m.norm())
+            out[f"{name}.adam_v"] = float(sh.v.norm())
+        return out
+
     # ---- checkpoint -------------------------------------------------------------------------------
     def state_dict(self) -> dict:
         """Per-parameter optimizer state of this rank's shard, keyed like the reference's checkpoints.

@@ -1,0 +1,125 @@
+"""``pipeline(task, model, tokenizer)`` factory and the text-generation pipelines.
+
+Reference: ``mindformers/pipeline/pipeline.py:59-149`` (factory), ``base_pipeline.py:53-325`` (batching of
+list / dataset inputs, preprocess → forward → postprocess) and ``text_generation_pipeline.py:31``.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Iterable, List, Optional, Union
+
+import torch
+
+from ..tools.register.register import MindFormerModuleType, MindFormerRegister
+
+SUPPORTED_TASKS = ("text_generation", "multi_modal_to_text_generation")
+
+
+class Pipeline:
+    """Batches the inputs and runs ``preprocess → _forward → postprocess`` per batch."""
+
+    def __init__(self, model, tokenizer=None, image_processor=None, **kwargs):
+        self.model, self.tokenizer, self.image_processor = model, tokenizer, image_processor
+        self.default_kwargs = kwargs
+
+    def _sanitize_parameters(self, **kw):
+        pre = {k: kw[k] for k in ("add_special_tokens", "max_length_input") if k in kw}
+        post = {k: kw[k] for k in ("skip_special_tokens", "return_full_text") if k in kw}
+        fwd = {k: v for k, v in kw.items() if k not in pre and k not in post and k != "batch_size"}
+        return pre, fwd, post
+
+    def __call__(self, inputs, batch_size: Optional[int] = None, **kwargs):
+        merged = dict(self.default_kwargs)
+        merged.update(kwargs)
+        pre_kw, fwd_kw, post_kw = self._sanitize_parameters(**merged)
+        single = isinstance(inputs, (str, dict))
+        items = [inputs] if single else list(inputs)
+        bs = batch_size or 1
+        out: List[Any] = []
+        for i in range(0, len(items), bs):
+            chunk = items[i:i + bs]
+            model_in = self.preprocess(chunk, **pre_kw)
+            model_out = self._forward(model_in, **fwd_kw)
+            out.extend(self.postprocess(model_out, **post_kw))
+        return out[0] if single else out
+
+    def preprocess(self, inputs, **kw):
+        raise NotImplementedError
+
+    def _forward(self, model_inputs, **kw):
+        raise NotImplementedError
+
+    def postprocess(self, model_outputs, **kw):
+        raise NotImplementedError
+
+
+@MindFormerRegister.register(MindFormerModuleType.PIPELINE, alias="text_generation")
+class TextGenerationPipeline(Pipeline):
+    """Prompt text (or token ids) in, ``{"text_generation_text": [...]}`` out."""
+
+    def preprocess(self, inputs, add_special_tokens: bool = True, max_length_input: Optional[int] = None, **kw):
+        ids = []
+        for x in inputs:
+            if isinstance(x, str):
+                if self.tokenizer is None:
+                    raise ValueError("a tokenizer is required for text inputs")
+                t = self.tokenizer.encode(x, add_special_tokens=add_special_tokens)
+            elif torch.is_tensor(x):
+                t = x.tolist()
+            else:
+                t = list(x)
+            ids.append(t[-max_length_input:] if max_length_input else t)
+        return {"input_ids": ids}
+
+    @torch.no_grad()
+    def _forward(self, model_inputs, **generate_kwargs):
+        self.model.eval()
+        if self.tokenizer is not None:
+            generate_kwargs.setdefault("eos_token_id", getattr(self.tokenizer, "eos_token_id", None))
+            generate_kwargs.setdefault("pad_token_id", getattr(self.tokenizer, "pad_token_id", 0) or 0)
+        out = self.model.generate(model_inputs["input_ids"], **generate_kwargs)
+        return {"output_ids": out, "input_ids": model_inputs["input_ids"]}
+
+    def postprocess(self, model_outputs, skip_special_tokens: bool = True, return_full_text: bool = True, **kw):
+        res = []
+        for full, prompt in zip(model_outputs["output_ids"], model_outputs["input_ids"]):
+            ids = full if return_full_text else full[len(prompt):]
+            text = self.tokenizer.decode(ids, skip_special_tokens=skip_special_tokens) if self.tokenizer is not None else ids
+            res.append({"text_generation_text": [text]})
+        return res
+
+
+@MindFormerRegister.register(MindFormerModuleType.PIPELINE, alias="multi_modal_to_text_generation")
+class MultiModalToTextPipeline(TextGenerationPipeline):
+    """Inputs are lists of ``{"text": ...}`` / ``{"image": ...}`` parts. The text parts are concatenated into the
+    prompt; image parts go through ``image_processor`` when the model takes ``pixel_values`` (the language models
+    in this package do not, so images raise unless a processor and such a model are supplied)."""
+
+    def preprocess(self, inputs, **kw):
+        texts = []
+        for sample in inputs:
+            parts = sample if isinstance(sample, list) else [sample]
+            txt = "".join(p.get("text", "") if isinstance(p, dict) else str(p) for p in parts)
+            if any(isinstance(p, dict) and "image" in p for p in parts) and self.image_processor is None:
+                raise ValueError("image parts need an image_processor and a model that accepts pixel_values")
+            texts.append(txt)
+        return super().preprocess(texts, **kw)
+
+
+def pipeline(task: Optional[str] = None, model=None, tokenizer=None, image_processor=None, audio_processor=None,
+             backend: str = "ms", **kwargs):
+    """Build the pipeline for ``task``. ``model`` is a model object, a directory (``from_pretrained``) or a preset name."""
+    if task not in SUPPORTED_TASKS:
+        raise KeyError(f"task {task!r} is not supported; choose from {SUPPORTED_TASKS}")
+    if isinstance(model, str):
+        from ..models import AutoModel, AutoTokenizer
+        path = model
+        model = AutoModel.from_pretrained(path)
+        if tokenizer is None:
+            try:
+                tokenizer = AutoTokenizer.from_pretrained(path)
+            except Exception:
+                tokenizer = None
+    if model is None:
+        raise ValueError("pipeline() needs a model")
+    cls = MindFormerRegister.get_cls(MindFormerModuleType.PIPELINE, task)
+    return cls(model=model, tokenizer=tokenizer, image_processor=image_processor, **kwargs)

@@ -1,0 +1,363 @@
+"""Task trainer: builds dataset / network / optimizer / callbacks from a configuration and runs the loops.
+
+Counterpart of ``mindformers/trainer/base_trainer.py`` (``training_process`` :882-1214, ``evaluate_process``
+:1216, ``predict_process`` :1290) and ``trainer/causal_language_modeling/causal_language_modeling.py:47-439``.
+Where the reference compiles one graph per step and sinks it to the device, this loop launches the step's
+kernels asynchronously and reads the loss back once per step (the read is what ``MFLossMonitor`` prints);
+step time comes from CUDA events on the compute stream.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..checkpoint.io import load_checkpoint
+from ..checkpoint.resume import get_resume_checkpoint, rescale_resume_step
+from ..core.callback import (Callback, CheckpointMonitor, EvalCallBack, GracefulExitCallback, MFLossMonitor, ProfileMonitor,
+                             RunContext, TrainingStateMonitor, build_callback)
+from ..core.lr import build_lr
+from ..core.metric import build_metric
+from ..dataset import build_dataset
+from ..models import build_network
+from ..parallel import parallel_state as ps
+from ..tools.check_rules import check_rules
+from ..tools.logger import get_logger
+from ..tools.register.register import MindFormerModuleType, MindFormerRegister
+from ..tools.utils import get_output_root_path, get_real_group_size
+from .engine import TrainingEngine
+
+logger = get_logger()
+
+
+def _model_dict(config) -> dict:
+    model = config.get("model") or {}
+    mc = dict(model.get("model_config") or {})
+    arch = (model.get("arch") or {}).get("type")
+    if arch and "architectures" not in mc:
+        mc["architectures"] = [arch]
+    mc.pop("type", None)
+    return mc
+
+
+def parallel_kwargs(config) -> dict:
+    """YAML ``parallel_config`` → model-parallel fields of the transformer configuration."""
+    pc = dict(config.get("parallel_config") or {})
+    tp = int(pc.get("model_parallel", 1) or 1)
+    out = dict(tensor_model_parallel_size=tp, pipeline_model_parallel_size=int(pc.get("pipeline_stage", 1) or 1),
+               context_parallel_size=int(pc.get("context_parallel", 1) or 1),
+               expert_model_parallel_size=int(pc.get("expert_parallel", 1) or 1),
+               sequence_parallel=bool(pc.get("use_seq_parallel")) and tp > 1)
+    algo = pc.get("context_parallel_algo")
+    if algo:
+        out["context_parallel_algo"] = algo
+    if pc.get("ulysses_degree_in_cp"):
+        out["ulysses_degree_in_cp"] = pc["ulysses_degree_in_cp"]
+    if (pc.get("pp_interleave_num") or 1) > 1:
+        out["virtual_pipeline_model_parallel_size"] = pc["pp_interleave_num"]
+    return out
+
+
+class BaseTrainer:
+    """Builds the pieces and owns the loops; task trainers override ``forward_batch`` where they differ."""
+
+    task = "general"
+
+    def __init__(self, task: Optional[str] = None, model_name: Optional[str] = None):
+        self.task_name, self.model_name = task or self.task, model_name
+        self.config = None
+        self.engine: Optional[TrainingEngine] = None
+        self.callbacks: List[Callback] = []
+        self.loss_history: List[float] = []
+
+    # ------------------------------------------------------------------ global batch bookkeeping
+    @staticmethod
+    def global_batch_size(config) -> int:
+        rc, pc = config.get("runner_config") or {}, config.get("parallel_config") or {}
+        bs = int(rc.get("batch_size", 1))
+        if ps.model_parallel_is_initialized():
+            dp = ps.get_data_parallel_world_size()
+        else:
+            dp = int(pc.get("data_parallel", 1) or 1) if config.get("use_parallel") else 1
+        pp = int(pc.get("pipeline_stage", 1) or 1)
+        interleave = int(config.get("micro_batch_interleave_num", 1) or 1)
+        if pp > 1:
+            return bs * dp * int(pc.get("micro_batch_num", 1) or 1) * interleave
+        return bs * dp * interleave * int(rc.get("gradient_accumulation_steps", 1) or 1)
+
+    # ------------------------------------------------------------------ builders
+    def create_dataset(self, config, which: str = "train"):
+        task_cfg = config.get(f"{which}_dataset_task")
+        ds_cfg = dict(config.get(f"{which}_dataset") or {})
+        if not task_cfg:
+            task_cfg = {"type": "CausalLanguageModelDataset"}
+        task_cfg = dict(task_cfg)
+        inner = dict(task_cfg.get("dataset_config") or {})
+        inner.update(ds_cfg)
+        rc = config.get("runner_config") or {}
+        accum = int(rc.get("gradient_accumulation_steps", 1) or 1)
+        micro = int((config.get("parallel_config") or {}).get("micro_batch_num", 1) or 1)
+        pp = int((config.get("parallel_config") or {}).get("pipeline_stage", 1) or 1)
+        per_step = int(rc.get("batch_size", 1)) * (micro if pp > 1 else accum)
+        inner["batch_size"] = per_step if which == "train" else int(rc.get("batch_size", 1))
+        loader = inner.get("data_loader")
+        if isinstance(loader, dict) and loader.get("type") == "MockDataLoader":
+            mc = _model_dict(config)
+            loader.setdefault("seq_length", mc.get("seq_length", 2048))
+            loader.setdefault("vocab_size", mc.get("vocab_size", 32000))
+        task_cfg["dataset_config"] = inner
+        return build_dataset(task_cfg)
+
+    def create_engine(self, config, total_steps: int, model=None) -> TrainingEngine:
+        opt_cfg = dict(config.get("optimizer") or {"type": "AdamW"})
+        lr_cfg = dict(config.get("lr_schedule") or {})
+        lr = opt_cfg.get("learning_rate", 5e-5)
+        if lr_cfg.get("type"):
+            lr_cfg.setdefault("learning_rate", lr)
+            if lr_cfg.get("total_steps", -1) in (-1, None):
+                lr_cfg["total_steps"] = total_steps
+            lr = build_lr(lr_cfg)
+        wrapper = dict(config.get("runner_wrapper") or {})
+        clip = wrapper.get("use_clip_grad", True)
+        max_norm = float(wrapper.get("max_grad_norm", 1.0)) if clip else 0.0
+        scale = wrapper.get("scale_sense", 1.0)
+        loss_scale = float(scale) if isinstance(scale, (int, float)) else 1.0   # bf16 needs no dynamic scaling
+        rc = config.get("runner_config") or {}
+        mc = _model_dict(config)
+        recompute = bool((config.get("recompute_config") or {}).get("recompute"))
+        skip = float(wrapper.get("global_norm_spike_threshold", 0) or 0) if wrapper.get("use_skip_data_by_global_norm") else 0.0
+        if model is not None:
+            from ..parallel.distributed.optimizer import DistributedOptimizer
+            tcfg = model.config if hasattr(model.config, "sequence_parallel") else model.model.config
+            net = model if hasattr(model.config, "sequence_parallel") else model.model
+            opt = DistributedOptimizer(net, learning_rate=lr, betas=tuple(opt_cfg.get("betas", (0.9, 0.999))),
+                                       eps=opt_cfg.get("eps", 1e-8), weight_decay=opt_cfg.get("weight_decay", 0.0),
+                                       max_grad_norm=max_norm, skip_threshold=skip,
+                                       sequence_parallel=bool(tcfg.sequence_parallel))
+            return TrainingEngine(net, opt, micro_batch_size=int(rc.get("batch_size", 1)), loss_scale=loss_scale)
+        return TrainingEngine.from_model_config(
+            mc, parallel=parallel_kwargs(config), learning_rate=lr, betas=tuple(opt_cfg.get("betas", (0.9, 0.999))),
+            eps=opt_cfg.get("eps", 1e-8), weight_decay=opt_cfg.get("weight_decay", 0.0), max_grad_norm=max_norm,
+            micro_batch_size=int(rc.get("batch_size", 1)), recompute=recompute,
+            dtype=mc.get("compute_dtype", "bfloat16") if torch.cuda.is_available() else mc.get("compute_dtype", "float32"))
+
+    def create_callbacks(self, config, default: Dict[str, Any]) -> List[Callback]:
+        cbs: List[Callback] = []
+        for c in config.get("callbacks") or [dict(type="MFLossMonitor")]:
+            c = dict(c)
+            if c.get("type") == "ObsMonitor":
+                continue
+            cbs.append(build_callback(c, default_args=None) if c["type"] not in ("MFLossMonitor", "CheckpointMonitor")
+                       else build_callback(c, default_args={k: v for k, v in default.items()
+                                                            if k in ("global_batch_size",)}))
+        mon = config.get("monitor_config") or {}
+        if mon.get("monitor_on"):
+            cbs.append(TrainingStateMonitor(config=mon, global_batch_size=default.get("global_batch_size", 0)))
+        if config.get("profile"):
+            cbs.append(ProfileMonitor(start_step=config.get("profile_start_step", 1), stop_step=config.get("profile_stop_step", 10),
+                                      profile_rank_ids=config.get("profile_rank_ids"), profile_pipeline=config.get("profile_pipeline", False),
+                                      profile_memory=config.get("profile_memory", False), mstx=config.get("mstx", False),
+                                      config=config.get("parallel_config")))
+        if config.get("use_graceful_exit"):
+            cbs.append(GracefulExitCallback((config.get("graceful_exit_config") or {}).get("graceful_exit_path")))
+        # monitors first, checkpoint last: a checkpoint is written only after the step's checks passed
+        cbs.sort(key=lambda c: isinstance(c, CheckpointMonitor))
+        return cbs
+
+    # ------------------------------------------------------------------ training
+    def training_process(self, config, network=None, dataset=None, callbacks: Optional[List[Callback]] = None, **kwargs):
+        self.config = config
+        check_rules(config, mode="train")
+        loader = dataset if dataset is not None else self.create_dataset(config, "train")
+        rc = config.get("runner_config") or {}
+        epochs = int(rc.get("epochs", 1))
+        steps_per_epoch = len(loader)
+        if int(rc.get("sink_size", -1) or -1) > 0 and rc.get("sink_mode") and rc.get("sink_size", 1) > 1:
+            steps_per_epoch = min(steps_per_epoch, int(rc["sink_size"]))
+        total_steps = epochs * steps_per_epoch
+        stop_step = int(rc.get("stop_step", 0) or 0)
+        if stop_step:
+            total_steps = min(total_steps, stop_step)
+        gbs = self.global_batch_size(config)
+        self.engine = engine = self.create_engine(config, total_steps, model=network)
+        seq_len = int(getattr(engine.model.config, "seq_length", 0) or 0)
+        ctx = RunContext(engine=engine, config=config, epochs=epochs, steps_per_epoch=steps_per_epoch, total_steps=total_steps,
+                         global_batch_size=gbs, seq_length=seq_len)
+        self.callbacks = cbs = list(callbacks) if callbacks is not None else self.create_callbacks(config, {"global_batch_size": gbs})
+        start_epoch, start_step = self._maybe_load(config, engine, gbs, steps_per_epoch)
+        ctx.global_step = start_epoch * steps_per_epoch + start_step
+        if ctx.global_step and not config.get("ignore_data_skip") and hasattr(loader, "set_init_step"):
+            skip = config.get("data_skip_steps")
+            loader.set_init_step(int(skip) if skip is not None else start_step)
+        for cb in cbs:
+            cb.on_train_begin(ctx)
+        use_cuda = torch.cuda.is_available() and engine.device.type == "cuda"
+        try:
+            for epoch in range(start_epoch, epochs):
+                ctx.epoch = epoch
+                if hasattr(loader, "shard_sampler"):
+                    loader.shard_sampler.set_epoch(epoch)
+                ctx.step_in_epoch = start_step if epoch == start_epoch else 0
+                for batch in loader:
+                    if ctx.step_in_epoch >= steps_per_epoch or ctx.global_step >= total_steps:
+                        break
+                    for cb in cbs:
+                        cb.on_step_begin(ctx)
+                    if use_cuda:
+                        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        ev0.record()
+                    t0 = time.perf_counter()
+                    out = engine.train_step_full(batch)
+                    if use_cuda:
+                        ev1.record()
+                        ev1.synchronize()
+                        ctx.step_ms = ev0.elapsed_time(ev1)
+                    else:
+                        ctx.step_ms = (time.perf_counter() - t0) * 1e3
+                    ctx.global_step += 1
+                    ctx.step_in_epoch += 1
+                    ctx.loss, ctx.lr, ctx.global_norm, ctx.skipped = out["loss"], out["lr"], out["global_norm"], out["skipped"]
+                    self.loss_history.append(ctx.loss)
+                    for cb in cbs:
+                        cb.on_step_end(ctx)
+                    if ctx.request_stop:
+                        break
+                if ctx.request_stop or ctx.global_step >= total_steps:
+                    break
+                for cb in cbs:
+                    cb.on_epoch_end(ctx)
+        except BaseException as exc:
+            for cb in cbs:
+                cb.on_exception(ctx, exc)
+            raise
+        for cb in cbs:
+            cb.on_train_end(ctx)
+        return ctx
+
+    def _maybe_load(self, config, engine, gbs, steps_per_epoch):
+        path = config.get("load_checkpoint")
+        resume = config.get("resume_training")
+        start_epoch = start_step = 0
+        if not path and config.get("pretrained_model_dir") and config.get("run_mode") == "finetune":
+            path = config["pretrained_model_dir"]
+        if not path:
+            return 0, 0
+        fam = _model_dict(config).get("model_type", "llama")
+        if resume:
+            point = get_resume_checkpoint(path, resume) if os.path.isdir(path) else None
+            scalars = load_checkpoint(engine.model, path, optimizer=engine.optimizer, strict=True, family=fam)
+            epoch = int(scalars.get("epoch_num", point[0] if point else 1))
+            step = int(scalars.get("step_num", point[1] if point else 0))
+            step = rescale_resume_step(step, scalars.get("global_batch_size"), gbs)
+            start_epoch, start_step = max(epoch - 1, 0), step
+            if start_step >= steps_per_epoch:
+                start_epoch, start_step = start_epoch + start_step // steps_per_epoch, start_step % steps_per_epoch
+            logger.info("resumed from %s at epoch %d step %d", path, start_epoch + 1, start_step)
+        else:
+            load_checkpoint(engine.model, path, strict=False, family=fam)
+            if hasattr(engine.optimizer, "reload_model_params"):
+                engine.optimizer.reload_model_params()
+        return start_epoch, start_step
+
+    # ------------------------------------------------------------------ evaluation / prediction
+    @torch.no_grad()
+    def evaluate_process(self, config, network=None, dataset=None, metric=None, **kwargs):
+        self.config = config
+        loader = dataset if dataset is not None else self.create_dataset(config, "eval")
+        model = network if network is not None else (self.engine.model if self.engine else build_network(config.get("model") or {}))
+        if config.get("load_checkpoint") and network is None and self.engine is None:
+            load_checkpoint(getattr(model, "model", model), config["load_checkpoint"], strict=False)
+        metric = metric or build_metric(config.get("metric") or {"type": "PerplexityMetric"})
+        metrics = metric if isinstance(metric, list) else [metric]
+        for m in metrics:
+            m.clear()
+        model.eval()
+        dev = next(model.parameters()).device
+        for batch in loader:
+            ids = batch["input_ids"].to(dev)
+            labels = batch.get("labels")
+            labels = labels.to(dev) if labels is not None else ids
+            mask = batch.get("loss_mask")
+            loss = model(ids, labels, mask.to(dev) if mask is not None else None)
+            for m in metrics:
+                m.update(loss)
+        out = {}
+        for m in metrics:
+            out.update(m.eval())
+        logger.info("evaluation: %s", out)
+        return out
+
+    @torch.no_grad()
+    def predict_process(self, config, input_data=None, network=None, tokenizer=None, **kwargs):
+        from ..models import build_tokenizer
+        from ..pipeline import pipeline
+        self.config = config
+        model = network if network is not None else build_network(config.get("model") or {})
+        path = config.get("load_checkpoint") or config.get("pretrained_model_dir")
+        if path and network is None:
+            model.load_weights(path, strict=False)
+        if tokenizer is None:
+            tok_cfg = (config.get("processor") or {}).get("tokenizer")
+            tokenizer = build_tokenizer(tok_cfg) if tok_cfg else build_tokenizer({"type": "ByteTokenizer"})
+        pipe = pipeline(task="text_generation", model=model, tokenizer=tokenizer)
+        data = input_data if input_data is not None else config.get("input_data")
+        if isinstance(data, str) and os.path.isfile(data):
+            with open(data) as f:
+                data = [line.rstrip("\n") for line in f if line.strip()]
+        gen_kw = {k: kwargs[k] for k in ("max_new_tokens", "max_length", "do_sample", "top_k", "top_p", "temperature",
+                                          "repetition_penalty", "num_beams") if k in kwargs}
+        result = pipe(data, batch_size=config.get("predict_batch_size") or 1, **gen_kw)
+        save = config.get("save_file") or os.path.join(get_output_root_path(), "text_generation_result.txt")
+        os.makedirs(os.path.dirname(save) or ".", exist_ok=True)
+        with open(save, "w") as f:
+            for r in result if isinstance(result, list) else [result]:
+                f.write(str(r) + "\n")
+        return result
+
+
+@MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["text_generation"])
+class CausalLanguageModelingTrainer(BaseTrainer):
+    task = "text_generation"
+
+    def train(self, config, **kw):
+        return self.training_process(config, **kw)
+
+    def evaluate(self, config, **kw):
+        return self.evaluate_process(config, **kw)
+
+    def predict(self, config, **kw):
+        return self.predict_process(config, **kw)
+
+    def generate_evaluate(self, config, network=None, dataset=None, metric=None, tokenizer=None, max_new_tokens: int = 32, **kw):
+        """Generate from each prompt, then score the text against the reference answers (EM/F1, ROUGE ...)."""
+        from ..core.metric import EmF1Metric
+        model = network if network is not None else self.engine.model
+        metric = metric or EmF1Metric()
+        metric.clear()
+        for batch in dataset:
+            prompts, answers = batch["prompt"], batch["answer"]
+            ids = [tokenizer.encode(p) for p in prompts]
+            outs = model.generate(ids, max_new_tokens=max_new_tokens)
+            texts = [tokenizer.decode(o[len(i):]) for o, i in zip(outs, ids)]
+            metric.update(texts, answers)
+        return metric.eval()
+
+
+@MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["general"])
+class GeneralTaskTrainer(CausalLanguageModelingTrainer):
+    """Any network that maps a batch to a loss (``trainer/general_task_trainer``)."""
+    task = "general"
+
+
+@MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["multi_modal_to_text_generation"])
+class MultiModalToTextGenerationTrainer(CausalLanguageModelingTrainer):
+    task = "multi_modal_to_text_generation"
+
+
+def build_trainer(config: Optional[dict] = None, default_args=None, **kwargs):
+    cfg = dict(config or {"type": "CausalLanguageModelingTrainer"})
+    cfg.setdefault("type", "CausalLanguageModelingTrainer")
+    cls = MindFormerRegister.get_cls(MindFormerModuleType.TRAINER, cfg["type"])
+    return cls(task=cfg.get("task"), model_name=cfg.get("model_name"))

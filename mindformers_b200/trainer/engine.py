@@ -60,6 +60,17 @@ class TrainingEngine:
         self.model.train()
         return self.step_fn(batch)
 
+    def train_step_full(self, host_batch: Dict[str, torch.Tensor]) -> Dict[str, float]:
+        """Like ``train_step`` but returns ``loss``, ``lr``, ``global_norm`` and ``skipped`` as Python values
+        (one device→host read of three scalars)."""
+        dev_batch = {k: v.to(self.device, non_blocking=True) for k, v in host_batch.items()
+                     if torch.is_tensor(v) and k in ("input_ids", "labels", "loss_mask", "position_ids")}
+        out = self.train_step_device(dev_batch)
+        packed = torch.stack([out["loss"].float().reshape(()), out["global_norm"].float().reshape(()),
+                              out["skipped"].float().reshape(())]).cpu()
+        return {"loss": float(packed[0]), "global_norm": float(packed[1]), "skipped": bool(packed[2] > 0),
+                "lr": float(out["lr"])}
+
     def train_step(self, host_batch: Dict[str, torch.Tensor]) -> float:
         dev_batch = {}
         for k, v in host_batch.items():

@@ -1,0 +1,153 @@
+"""Trainer / callbacks / metrics / CLI entry points on CPU (tiny 2-layer model, synthetic tokens)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+MODEL = dict(arch=dict(type="LlamaForCausalLM"),
+             model_config=dict(model_type="llama", vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, seq_length=32, max_position_embeddings=32,
+                               params_dtype="float32", compute_dtype="float32"))
+
+
+def _cfg(out, **over):
+    cfg = dict(output_dir=str(out), run_mode="train", use_legacy=False, seed=3, model=MODEL,
+               runner_config=dict(epochs=1, batch_size=2),
+               train_dataset=dict(data_loader=dict(type="MockDataLoader", num_samples=16, seq_length=32, vocab_size=128, seed=5)),
+               train_dataset_task=dict(type="CausalLanguageModelDataset"),
+               optimizer=dict(type="AdamW", learning_rate=1e-3, betas=[0.9, 0.95]),
+               lr_schedule=dict(type="ConstantWarmUpLR", learning_rate=1e-3, warmup_steps=0, total_steps=-1),
+               context=dict(device_target="CPU"),
+               callbacks=[dict(type="MFLossMonitor"), dict(type="CheckpointMonitor", save_checkpoint_steps=4, prefix="t")])
+    cfg.update(over)
+    return cfg
+
+
+def _fresh():
+    from mindformers_b200.core import context
+    context._CONTEXT = None
+
+
+def test_train_saves_and_resume_reproduces_losses(tmp_path):
+    from mindformers_b200.trainer import Trainer
+    _fresh()
+    full = Trainer(args=_cfg(tmp_path / "a"))
+    full.train()
+    ref = full.trainer.loss_history
+    assert len(ref) == 8
+    ck = tmp_path / "a" / "checkpoint"
+    assert sorted(os.listdir(ck / "rank_0")) == ["meta.json", "t_rank_0-1_4.safetensors", "t_rank_0-1_8.safetensors"]
+    assert json.load(open(ck / "rank_0" / "meta.json"))["last_step"] == 8
+    # drop the final checkpoint so that the resume point is step 4, then continue: losses 5..8 must match
+    os.remove(ck / "rank_0" / "t_rank_0-1_8.safetensors")
+    json.dump({"last_epoch": 1, "last_step": 4, "last_ckpt_file": "t_rank_0-1_4.safetensors"}, open(ck / "rank_0" / "meta.json", "w"))
+    _fresh()
+    again = Trainer(args=_cfg(tmp_path / "b", load_checkpoint=str(ck), resume_training=True))
+    again.train()
+    got = again.trainer.loss_history
+    assert len(got) == 4
+    for a, b in zip(ref[4:], got):
+        assert abs(a - b) < 5e-3, (ref, got)
+
+
+def test_training_arguments_roundtrip_and_monitors(tmp_path):
+    from mindformers_b200.core.callback import GracefulExitCallback, TrainingStateMonitor
+    from mindformers_b200.trainer import Trainer, TrainingArguments
+    args = TrainingArguments(output_dir=str(tmp_path), num_train_epochs=1, batch_size=2, learning_rate=2e-3, lr_scheduler_type="linear",
+                             warmup_steps=1, save_strategy="no", use_cpu=True)
+    cfg = args.convert_args_to_mindformers_config()
+    assert cfg["lr_schedule"]["type"] == "LinearWithWarmUpLR" and cfg["optimizer"]["learning_rate"] == 2e-3
+    assert cfg["context"]["device_target"] == "CPU"
+    flag = tmp_path / "graceful_exit.json"
+    json.dump({"GracefulExit": 1}, open(flag, "w"))
+    _fresh()
+    c = _cfg(tmp_path / "g", callbacks=[dict(type="MFLossMonitor")])
+    t = Trainer(args=c, callbacks=None)
+    cbs = t.trainer.create_callbacks(t.config, {}) + [GracefulExitCallback(str(flag)),
+                                                      TrainingStateMonitor(config=dict(weight_state_format=["log"], target=["final_layernorm"]))]
+    t.callbacks = cbs
+    st = t.train()
+    assert st.global_step == 1 and st.stop_reason == "graceful_exit"
+    assert any(k.startswith("weight_norm/") for k in cbs[-1].stats[0])
+
+
+def test_spike_and_nan_detection():
+    from mindformers_b200.core.callback import RunContext, TrainingStateMonitor
+    import tempfile
+    d = tempfile.mkdtemp()
+    mon = TrainingStateMonitor(config=dict(global_norm_spike_threshold=2.0, check_for_global_norm=True,
+                                           global_norm_record_path=os.path.join(d, "spike.json")))
+    ctx = RunContext(global_step=7, loss=1.0, global_norm=5.0)
+    with pytest.raises(RuntimeError, match="TREError"):
+        mon.on_step_end(ctx)
+    assert "7" in json.load(open(os.path.join(d, "spike.json")))
+    with pytest.raises(RuntimeError, match="loss is nan"):
+        mon.on_step_end(RunContext(global_step=8, loss=float("nan"), global_norm=1.0))
+
+
+def test_metrics():
+    from mindformers_b200.core.metric import ADGENMetric, EmF1Metric, EntityScore, PerplexityMetric, PromptAccMetric
+    torch.manual_seed(0)
+    logits, labels = torch.randn(2, 6, 11), torch.randint(0, 11, (2, 6))
+    m = PerplexityMetric()
+    m.update(logits, labels, torch.ones(2, 6))
+    want = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 11), labels[:, 1:].reshape(-1))
+    assert abs(m.eval()["loss"] - float(want)) < 1e-5
+    em = EmF1Metric()
+    em.update(["The cat sat."], ["cat sat"])
+    assert em.eval()["Em"] == 100.0
+    ad = ADGENMetric()
+    ad.update(["abcd"], ["abcd"])
+    assert ad.eval()["rouge-l"] == pytest.approx(100.0)
+    es = EntityScore(["O", "B-P", "I-P"])
+    es.update([[0, 1, 2, 0]], [[0, 1, 2, 0]])
+    assert es.eval()["f1"] == 1.0
+    pa = PromptAccMetric()
+    lg = torch.full((2, 3, 5), -5.0)
+    ids = torch.tensor([[0, 1, 2], [0, 3, 4]])
+    lg[0, 0, 1] = lg[0, 1, 2] = 5.0      # candidate 0 is the likely continuation
+    pa.update(lg, ids, torch.ones(2, 3), torch.tensor([0]))
+    assert pa.eval()["Acc"] == 1.0
+
+
+def test_cli_train_eval_predict(tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    base = [sys.executable, os.path.join(ROOT, "run_mindformer.py"), "--config", os.path.join(ROOT, "configs/general/run_general_task.yaml"),
+            "--output_dir", str(tmp_path), "--context.device_target", "CPU"]
+    r = subprocess.run(base + ["--runner_config.stop_step=2"], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "step:[    2/" in r.stderr + r.stdout
+    ck = os.path.join(str(tmp_path), "checkpoint")
+    r = subprocess.run(base + ["--run_mode", "predict", "--load_checkpoint", ck, "--predict_data", "hello", "--use_parallel", "False"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert os.path.exists(os.path.join(str(tmp_path), "text_generation_result.txt"))
+
+
+def test_convert_weight_roundtrip(tmp_path):
+    from safetensors.torch import load_file
+    from mindformers_b200.models import LlamaConfig, LlamaForCausalLM
+    import convert_weight
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, params_dtype="float32", compute_dtype="float32")
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg, device="cpu")
+    m.save_pretrained(str(tmp_path / "hf"), hf_names=True)
+    out = convert_weight.main(["--model", "llama", "--input_path", str(tmp_path / "hf"), "--output_path", str(tmp_path / "mf")])
+    sd = load_file(out)
+    own = dict(m.model.named_parameters())
+    assert set(own) <= set(sd)
+    for k, v in own.items():
+        assert torch.equal(sd[k], v.detach()), k
+    back = convert_weight.main(["--model", "llama", "--reversed", "--input_path", out, "--output_path", str(tmp_path / "hf2"),
+                                "--config", str(tmp_path / "hf" / "config.json")])
+    a, b = load_file(back), {}
+    for f in os.listdir(tmp_path / "hf"):
+        if f.endswith(".safetensors"):
+            b.update(load_file(str(tmp_path / "hf" / f)))
+    assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
