@@ -67,6 +67,12 @@ def _declare(lib):
     sig("mfb_reshape_and_cache", [P, P, P, P, P, L, I, L, L, P])
     sig("mfb_paged_decode_attention", [P, P, P, P, P, P, I, I, I, I, I, I, F, P])
     sig("mfb_gather_cache", [P, P, P, P, I, I, I, I, I, P])
+    sig("mfb_dp_reduce_scratch", [])
+    sig("mfb_dp_flag_words", [])
+    sig("mfb_dp_reduce", [I, I, I, L, L, P, P, P, P, P, I, P, P])
+    sig("mfb_dp_adamw_allgather", [I, I, I, L, L, P, P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, F, F, F, P, P])
+    sig("mfb_router_fwd", [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    sig("mfb_router_bwd", [P, P, P, P, P, I, I, I, I, I, F, P])
     # optional entry points (present once their source file is part of the build)
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

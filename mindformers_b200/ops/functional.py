@@ -592,6 +592,83 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
 
 
 # =================================================================================================
+# MoE router
+# =================================================================================================
+def router_topk_reference(logits, bias, k, sigmoid, norm, scale, groups=0, group_topk=0):
+    """PyTorch oracle of the router kernel: returns ``(probs [T,k], ids [T,k], scores [T,E])``."""
+    scores = torch.sigmoid(logits) if sigmoid else torch.softmax(logits, dim=-1)
+    sel = scores if bias is None else scores + bias
+    T, E = scores.shape
+    if groups and groups > 1 and group_topk and group_topk < groups:
+        grouped = sel.view(T, groups, E // groups)
+        if bias is not None:
+            gscore = grouped.topk(min(2, E // groups), dim=-1).values.sum(-1)
+        else:
+            gscore = grouped.max(-1).values
+        keep = gscore.topk(group_topk, dim=-1).indices
+        mask = torch.zeros(T, groups, dtype=torch.bool, device=scores.device).scatter_(1, keep, True)
+        sel = sel.masked_fill(~mask.unsqueeze(-1).expand(T, groups, E // groups).reshape(T, E), float("-inf"))
+    ids = sel.topk(k, dim=-1).indices
+    probs = scores.gather(1, ids)
+    if norm:
+        probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
+    return probs * scale, ids, scores
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, bias, k, sigmoid, norm, scale, groups, group_topk, need_scores, counts):
+        T, E = logits.shape
+        logits = logits.contiguous()
+        probs = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+        ids = torch.empty(T, k, dtype=torch.int64, device=logits.device)
+        scores = torch.empty(T, E, dtype=torch.float32, device=logits.device) if need_scores else None
+        rc = _lib.get_lib().mfb_router_fwd(logits.data_ptr(), _lib.ptr(bias), probs.data_ptr(), ids.data_ptr(),
+                                           _lib.ptr(scores), _lib.ptr(counts), T, E, k, int(sigmoid), int(norm),
+                                           int(groups or 0), int(group_topk or 0), float(scale), _lib.stream_ptr())
+        _lib.check(rc, "mfb_router_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(logits, ids)
+        ctx.cfg = (k, sigmoid, norm, scale)
+        ctx.mark_non_differentiable(ids)
+        if scores is None:
+            scores = torch.empty(0, device=logits.device)
+            ctx.no_scores = True
+        else:
+            ctx.no_scores = False
+        return probs, ids, scores
+
+    @staticmethod
+    def backward(ctx, dprobs, _dids, dscores):
+        logits, ids = ctx.saved_tensors
+        k, sigmoid, norm, scale = ctx.cfg
+        T, E = logits.shape
+        dlogits = torch.empty_like(logits)
+        ds = None if ctx.no_scores or dscores is None else dscores.contiguous().float()
+        rc = _lib.get_lib().mfb_router_bwd(logits.data_ptr(), ids.data_ptr(), dprobs.contiguous().float().data_ptr(),
+                                           _lib.ptr(ds), dlogits.data_ptr(), T, E, k, int(sigmoid), int(norm),
+                                           float(scale), _lib.stream_ptr())
+        _lib.check(rc, "mfb_router_bwd")
+        _lib.count_launch()
+        return (dlogits,) + (None,) * 9
+
+
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, *, sigmoid: bool = False, norm: bool = True,
+                scale: float = 1.0, groups: int = 0, group_topk: int = 0, need_scores: bool = False,
+                counts: Optional[torch.Tensor] = None):
+    """Fused router: ``(probs [T,k] fp32, ids [T,k] int64, scores [T,E] | None)``; ``counts [E]`` (fp32) is
+    incremented by the number of copies routed to each expert."""
+    E = logits.shape[-1]
+    if _on_gpu(logits) and logits.dtype == torch.float32 and E <= 512 and k <= 32 and (not groups or groups <= 32):
+        probs, ids, scores = _RouterFn.apply(logits, bias, k, sigmoid, norm, scale, groups, group_topk, need_scores, counts)
+        return probs, ids, (scores if need_scores else None)
+    probs, ids, scores = router_topk_reference(logits.float(), bias, k, sigmoid, norm, scale, groups, group_topk)
+    if counts is not None:
+        counts.scatter_add_(0, ids.reshape(-1), torch.ones(ids.numel(), dtype=counts.dtype, device=counts.device))
+    return probs, ids, (scores if need_scores else None)
+
+
+# =================================================================================================
 # Optimizer helpers
 # =================================================================================================
 def grad_sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool = False):

@@ -17,7 +17,9 @@ from typing import Callable, Dict, Optional, Union
 import torch
 import torch.distributed as dist
 
+from ...ops import _lib
 from ...ops import functional as Fn
+from .. import fused_comm, symm_mem
 from .. import parallel_state as ps
 from .param_grad_buffer import ParamAndGradBuffer, build_buffers
 
@@ -66,7 +68,7 @@ class DistributedOptimizer:
                  betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
                  skip_threshold: float = 0.0, grad_dtype: torch.dtype = torch.float32,
                  tensor_parallel: Optional[int] = None, sequence_parallel: bool = False,
-                 shard_optimizer: bool = True):
+                 shard_optimizer: bool = True, fused_dp_comm: Optional[bool] = None):
         self.model = model
         self.lr = learning_rate
         self.beta1, self.beta2 = betas
@@ -77,8 +79,27 @@ class DistributedOptimizer:
         self.sequence_parallel = sequence_parallel
         dp = ps.get_data_parallel_world_size(with_context_parallel=True) if shard_optimizer else 1
         edp = ps.get_expert_data_parallel_world_size() if shard_optimizer else 1
+        first = next(p for p in model.parameters() if p.requires_grad)
+        if fused_dp_comm is None:
+            fused_dp_comm = fused_comm.dp_enabled() and max(dp, edp) > 1
+        self.fused_dp = bool(fused_dp_comm) and first.is_cuda and first.dtype == torch.bfloat16 \
+            and grad_dtype == torch.float32 and max(dp, edp) <= 8
+        self._symm: Dict[str, object] = {}
+
+        def symm_alloc(tag, numel, dt, dev):
+            grp = ps.get_expert_data_parallel_group() if tag.startswith("expert") else \
+                ps.get_data_parallel_group(with_context_parallel=True)
+            world = edp if tag.startswith("expert") else dp
+            if world <= 1:
+                return torch.zeros(numel, dtype=dt, device=dev)
+            buf = symm_mem.allocate(f"dpopt.{tag}.{id(self)}", numel * torch.empty((), dtype=dt).element_size(), grp, dev)
+            t = buf.tensor.view(dt)[:numel]
+            t.zero_()
+            self._symm[tag] = buf
+            return t
+
         self.buffers = build_buffers(model, tp=self.tp, sequence_parallel=sequence_parallel, grad_dtype=grad_dtype,
-                                     dense_pad=dp, expert_pad=edp)
+                                     dense_pad=dp, expert_pad=edp, allocator=symm_alloc if self.fused_dp else None)
         self.shards: Dict[str, _Shard] = {}
         for name, buf in self.buffers.items():
             if name.startswith("expert"):
@@ -92,6 +113,31 @@ class DistributedOptimizer:
         self._dup_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.skipped = torch.zeros(1, dtype=torch.int32, device=dev)
         # the fp32 master starts as the exact value of the bf16 parameter, i.e. remainder 0
+        self._dp_epoch = 0
+        if self.fused_dp:
+            self._setup_fused_dp(dev)
+
+    def _setup_fused_dp(self, dev):
+        """Peer pointer tables and flag words of the fused reduce-scatter / AdamW / all-gather kernels."""
+        import ctypes
+        lib = _lib.get_lib()
+        words = lib.mfb_dp_flag_words()
+        self._dp_scratch = torch.zeros(lib.mfb_dp_reduce_scratch(), dtype=torch.float32, device=dev)
+        for name, sh in self.shards.items():
+            sh.fused = False
+            if sh.world <= 1 or f"{name}.grad" not in self._symm:
+                continue
+            flags = symm_mem.allocate(f"dpopt.{name}.flags.{id(self)}", words * 4, sh.group, dev)
+            flags.tensor.zero_()
+            arr = ctypes.c_longlong * sh.world
+            sh.peer_grad = arr(*[int(p) for p in self._symm[f"{name}.grad"].handle.buffer_ptrs])
+            sh.peer_param = arr(*[int(p) for p in self._symm[f"{name}.param"].handle.buffer_ptrs])
+            sh.peer_flags = arr(*[int(p) for p in flags.handle.buffer_ptrs])
+            sh.flags = flags
+            sh.fused = True
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()      # every rank's flag words are zero before anyone's first step
 
     # ---------------------------------------------------------------------------------------------
     def zero_grad(self, set_to_none: bool = True):
@@ -113,14 +159,23 @@ class DistributedOptimizer:
             if self.tp > 1 and self.sequence_parallel and r.sp_end > r.sp_begin and tp_group is not None:
                 dist.all_reduce(buf.grad_data[r.sp_begin:r.sp_end], group=tp_group)
             sh = self.shards[name]
-            if sh.world > 1:
+            if sh.world > 1 and not getattr(sh, "fused", False):
                 dist.reduce_scatter_tensor(sh.grad, buf.grad_data, op=dist.ReduceOp.SUM, group=sh.group)
 
     def _global_sumsq(self):
         self.sumsq.zero_()
         self._dup_sumsq.zero_()
         for name, sh in self.shards.items():
-            Fn.grad_sumsq(sh.grad, self.sumsq, accumulate=True)
+            if getattr(sh, "fused", False):
+                # reduce-scatter by peer loads; the squared norm of the reduced slice comes out of the same pass
+                rc = _lib.get_lib().mfb_dp_reduce(sh.world, sh.rank, self._dp_epoch, sh.begin, sh.len, sh.peer_grad,
+                                                  sh.peer_flags, sh.grad.data_ptr(), self._dp_scratch.data_ptr(),
+                                                  self.sumsq.data_ptr(), 1, _lib.status_word(sh.grad.device).data_ptr(),
+                                                  _lib.stream_ptr())
+                _lib.check(rc, "mfb_dp_reduce")
+                _lib.count_launch(2)
+            else:
+                Fn.grad_sumsq(sh.grad, self.sumsq, accumulate=True)
             r = sh.buf.ranges
             loc = sh.local(r.dup_begin, r.dup_end) if self.tp > 1 else None
             if loc is not None:
@@ -136,6 +191,7 @@ class DistributedOptimizer:
 
     def step(self, grad_scale: float = 1.0):
         """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""
+        self._dp_epoch += 1
         self.reduce_gradients()
         self._global_sumsq()
         self.global_step += 1
@@ -144,6 +200,16 @@ class DistributedOptimizer:
         for name, sh in self.shards.items():
             r = sh.buf.ranges
             d_end = max(0, min(r.decay_end, sh.end) - sh.begin)
+            if getattr(sh, "fused", False):
+                bc1, bc2 = 1.0 - self.beta1 ** self.global_step, 1.0 - self.beta2 ** self.global_step
+                rc = _lib.get_lib().mfb_dp_adamw_allgather(
+                    sh.world, sh.rank, self._dp_epoch, sh.begin, sh.len, sh.peer_param, sh.peer_flags, sh.lo.data_ptr(),
+                    sh.m.data_ptr(), sh.v.data_ptr(), sh.grad.data_ptr(), self.sumsq.data_ptr(), self.skipped.data_ptr(),
+                    d_end, lr, self.beta1, self.beta2, self.eps, self.wd, bc1, bc2, self.max_grad_norm,
+                    self.skip_threshold, grad_scale, _lib.status_word(sh.grad.device).data_ptr(), _lib.stream_ptr())
+                _lib.check(rc, "mfb_dp_adamw_allgather")
+                _lib.count_launch(2)
+                continue
             if sh.bf16:
                 Fn.adamw_step(sh.param, sh.lo, sh.m, sh.v, sh.grad, lr=lr, beta1=self.beta1, beta2=self.beta2,
                               eps=self.eps, weight_decay=self.wd, step=self.global_step, decay_end=d_end,

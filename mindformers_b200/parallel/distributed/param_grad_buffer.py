@@ -53,7 +53,7 @@ class ParamAndGradBuffer:
 
     def __init__(self, named_params: List[Tuple[str, torch.nn.Parameter]], *, tp: int = 1,
                  sequence_parallel: bool = False, grad_dtype: torch.dtype = torch.float32, pad_to: int = 1,
-                 name: str = "dense"):
+                 name: str = "dense", allocator=None):
         self.name = name
         if not named_params:
             raise ValueError("empty parameter list")
@@ -90,8 +90,10 @@ class ParamAndGradBuffer:
         r.dup_begin, r.dup_end = begin((1, 2, 3, 4), 0), end((1, 2, 3, 4), 0)
         r.sp_begin, r.sp_end = begin((2, 3), 0), end((2, 3), 0)
         self.ranges = r
-        self.param_data = torch.zeros(total, dtype=dtype, device=device)
-        self.grad_data = torch.zeros(total, dtype=grad_dtype, device=device)
+        # ``allocator(tag, numel, dtype, device)`` lets the optimizer place the buffers in peer-mapped memory
+        alloc = allocator or (lambda tag, numel, dt, dev: torch.zeros(numel, dtype=dt, device=dev))
+        self.param_data = alloc(f"{name}.param", total, dtype, device)
+        self.grad_data = alloc(f"{name}.grad", total, grad_dtype, device)
         self.index: Dict[str, Tuple[int, int, torch.Size]] = {}
         for n, p, o, cnt in self.entries:
             view = self.param_data[o:o + cnt].view(p.shape)
@@ -112,7 +114,7 @@ class ParamAndGradBuffer:
 
 
 def build_buffers(model: torch.nn.Module, *, tp: int, sequence_parallel: bool, grad_dtype=torch.float32,
-                  dense_pad: int = 1, expert_pad: int = 1) -> Dict[str, ParamAndGradBuffer]:
+                  dense_pad: int = 1, expert_pad: int = 1, allocator=None) -> Dict[str, ParamAndGradBuffer]:
     """Split trainable parameters into the dense and the expert buffer (they reduce over different groups)."""
     dense, expert = [], []
     for n, p in model.named_parameters():
@@ -128,5 +130,5 @@ def build_buffers(model: torch.nn.Module, *, tp: int, sequence_parallel: bool, g
         for dt, lst in by_dtype.items():
             name = key if len(by_dtype) == 1 else f"{key}_{str(dt).replace('torch.', '')}"
             out[name] = ParamAndGradBuffer(lst, tp=tp, sequence_parallel=sequence_parallel, grad_dtype=grad_dtype,
-                                           pad_to=pad, name=name)
+                                           pad_to=pad, name=name, allocator=allocator)
     return out

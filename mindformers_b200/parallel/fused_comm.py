@@ -19,6 +19,12 @@ def set_enabled(flag: bool):
     _FORCE_OFF = not flag
 
 
+def dp_enabled() -> bool:
+    """Fused data-parallel optimizer path (reduce-scatter by peer loads, AdamW, all-gather by peer stores)."""
+    import os
+    return not _FORCE_OFF and torch.cuda.is_available() and os.environ.get("MFB_FUSED_DP", "1") != "0"
+
+
 def _runtime_ready() -> bool:
     from . import symm_mem
     return symm_mem.is_ready()

@@ -77,25 +77,21 @@ class TopKRouter(nn.Module):
             z = torch.logsumexp(logits, dim=-1).pow(2).mean() * cfg.moe_z_loss_coeff
         else:
             z = None
-        if self.score_fn == "sigmoid":
-            scores = torch.sigmoid(logits)
-        else:
-            scores = torch.softmax(logits, dim=-1)
-        ids = self._select(scores)
-        probs = scores.gather(1, ids)
-        if self.score_fn == "sigmoid" or cfg.norm_topk_prob:
-            if cfg.norm_topk_prob:
-                probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
-        probs = probs * cfg.moe_router_topk_scaling_factor
-        aux = None
         E = cfg.num_moe_experts
+        want_aux = self.training and bool(cfg.moe_aux_loss_coeff)
         counts = None
         if self.training and (cfg.moe_aux_loss_coeff or self.expert_load is not None):
             counts = torch.zeros(E, dtype=torch.float32, device=x.device)
-            counts.scatter_add_(0, ids.reshape(-1), torch.ones(ids.numel(), dtype=torch.float32, device=x.device))
-        if self.training and cfg.moe_aux_loss_coeff:
+        sig = self.score_fn == "sigmoid"
+        norm = bool(cfg.norm_topk_prob)
+        probs, ids, scores = Fn.router_topk(
+            logits, self.expert_bias, self.topk, sigmoid=sig, norm=norm, scale=float(cfg.moe_router_topk_scaling_factor),
+            groups=int(cfg.moe_router_num_groups or 0), group_topk=int(cfg.moe_router_group_topk or 0),
+            need_scores=want_aux, counts=counts)
+        aux = None
+        if want_aux:
             T = x.shape[0]
-            density = scores.mean(0) if self.score_fn == "softmax" else (scores / (scores.sum(-1, keepdim=True) + 1e-20)).mean(0)
+            density = scores.mean(0) if not sig else (scores / (scores.sum(-1, keepdim=True) + 1e-20)).mean(0)
             frac = counts / (T * self.topk)
             aux = cfg.moe_aux_loss_coeff * E * torch.sum(density * frac.detach())
         if z is not None:

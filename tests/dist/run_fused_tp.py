@@ -108,8 +108,11 @@ def main():
         if args.out:
             with open(args.out, "w") as f:
                 json.dump(res, f, indent=1)
+    worst = max(v for key, d in res.items() if isinstance(d, dict) and not key.startswith("bench") for v in d.values())
+    ok = worst < 1e-2 and res.get("status", 0) == 0
     dist.barrier()
     dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,30 @@
+"""Multi-GPU checks (2 ranks): each spawns a ``torchrun`` worker from ``tests/dist`` and asserts on its exit code.
+Skipped on boxes with fewer than two GPUs. NVLS is switched off; the kernels use plain peer loads/stores."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, *args, nproc=2, timeout=900):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", os.path.join(ROOT, "tests", "dist", script), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout)
+    assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
+    return r.stdout
+
+
+def test_fused_tensor_parallel_gemms():
+    _run("run_fused_tp.py", "--bench", "0")
+
+
+def test_fused_data_parallel_optimizer():
+    _run("run_fused_dp.py", "--big", "0")

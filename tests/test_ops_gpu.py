@@ -267,3 +267,29 @@ def test_flash_attention_fwd_bwd(B, S, nq, nkv, causal):
     assert _rel_err(gv, rv) < 2e-2
     assert _rel_err(gk, rk) < 2e-2
     assert _rel_err(gq, rq) < 2e-2
+
+
+@pytest.mark.parametrize("E,k,sig,groups,gk,bias", [(128, 8, False, 0, 0, False), (256, 8, True, 8, 4, True),
+                                                    (64, 6, True, 0, 0, False), (160, 4, False, 4, 2, False)])
+def test_router_topk_fwd_bwd(E, k, sig, groups, gk, bias):
+    torch.manual_seed(E + k)
+    T = 777
+    logits = torch.randn(T, E, device="cuda") * 2.0
+    b = (torch.randn(E, device="cuda") * 0.1) if bias else None
+    la, lb = logits.clone().requires_grad_(), logits.clone().requires_grad_()
+    counts = torch.zeros(E, device="cuda")
+    p, ids, sc = Fn.router_topk(la, b, k, sigmoid=sig, norm=True, scale=2.5, groups=groups, group_topk=gk,
+                               need_scores=True, counts=counts)
+    pr, idr, scr = Fn.router_topk_reference(lb, b, k, sig, True, 2.5, groups, gk)
+    assert torch.equal(ids.sort(-1).values, idr.sort(-1).values)
+    assert torch.allclose(p.sort(-1).values, pr.sort(-1).values, rtol=1e-4, atol=1e-6)
+    assert torch.allclose(sc, scr, rtol=1e-4, atol=1e-7)
+    want = torch.zeros(E, device="cuda").scatter_add_(0, idr.reshape(-1), torch.ones(T * k, device="cuda"))
+    assert torch.equal(counts, want)
+    w = torch.randn(T, k, device="cuda")
+    ws = torch.randn(T, E, device="cuda") * 0.1
+    # same weights on matching experts: order the reference's columns like the kernel's
+    order = torch.argsort(idr, -1).gather(1, torch.argsort(torch.argsort(ids, -1), -1))
+    ((p * w).sum() + (sc * ws).sum()).backward()
+    ((pr.gather(1, order) * w).sum() + (scr * ws).sum()).backward()
+    assert torch.allclose(la.grad, lb.grad, rtol=2e-3, atol=2e-6)
