@@ -73,6 +73,12 @@ def _declare(lib):
     sig("mfb_dp_adamw_allgather", [I, I, I, L, L, P, P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, F, F, F, P, P])
     sig("mfb_router_fwd", [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     sig("mfb_router_bwd", [P, P, P, P, P, I, I, I, I, I, F, P])
+    sig("mfb_moe_flag_words", [])
+    sig("mfb_moe_rank", [P, I, I, P, P, P])
+    sig("mfb_moe_plan", [I, I, I, I, I, I] + [P] * 10)
+    sig("mfb_moe_scatter", [I] * 7 + [P] * 11)
+    sig("mfb_moe_barrier", [I, I, I, I, P, P, P])
+    sig("mfb_moe_gather", [I] * 7 + [P] * 9)
     # optional entry points (present once their source file is part of the build)
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

@@ -42,11 +42,12 @@ def enabled(config, x: torch.Tensor) -> bool:
 
 
 def moe_enabled(config, x: torch.Tensor) -> bool:
+    """True when the device-side MoE exchange (``parallel/fused_moe.py``) can serve this call: bf16 on CUDA,
+    any expert-parallel size up to 8 (size 1 = local permute kernels)."""
     if _FORCE_OFF or not getattr(config, "fused_moe_comm", False) or not x.is_cuda:
         return False
-    if ps.get_expert_model_parallel_world_size() == 1:
-        return False
-    return _runtime_ready() and False
+    from . import fused_moe
+    return fused_moe.supported(config, x)
 
 
 def allgather_linear(x, w):
@@ -60,4 +61,5 @@ def linear_reduce_scatter(x, w):
 
 
 def moe_dispatch_experts_combine(layer, hidden, probs, ids):
-    raise NotImplementedError
+    from . import fused_moe
+    return fused_moe.moe_dispatch_experts_combine(layer, hidden, probs, ids)

@@ -65,6 +65,7 @@ class ModelParallelConfig:
     # B200 additions: which fused compute+collective paths are on
     fused_tp_comm: bool = True
     fused_moe_comm: bool = True
+    moe_ep_buffer_factor: float = 1.25   # row-buffer head-room over the balanced load when ep > 1
 
     def _check_parallel(self):
         if self.sequence_parallel and self.tensor_model_parallel_size <= 1:

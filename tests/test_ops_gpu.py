@@ -293,3 +293,30 @@ def test_router_topk_fwd_bwd(E, k, sig, groups, gk, bias):
     ((p * w).sum() + (sc * ws).sum()).backward()
     ((pr.gather(1, order) * w).sum() + (scr * ws).sum()).backward()
     assert torch.allclose(la.grad, lb.grad, rtol=2e-3, atol=2e-6)
+
+
+def test_moe_exchange_kernels_match_torch_permute_single_rank():
+    """ep = 1: rank/plan/scatter/gather kernels against the index-based PyTorch permutation, forward and backward."""
+    from mindformers_b200.parallel import fused_comm
+    from mindformers_b200.parallel.layers.moe import MoELayer
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    torch.manual_seed(3)
+    cfg = TransformerConfig(num_layers=1, hidden_size=256, num_attention_heads=4, ffn_hidden_size=512, num_moe_experts=8,
+                            moe_router_topk=2, moe_ffn_hidden_size=128, params_dtype=torch.bfloat16, compute_dtype=torch.bfloat16,
+                            moe_aux_loss_coeff=1e-2)
+    cfg.device = "cuda"
+    layer = MoELayer(cfg).train()
+    x = (torch.randn(300, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    outs = []
+    for fused in (True, False):
+        cfg.fused_moe_comm = fused
+        xi = x.clone().requires_grad_()
+        for p in layer.parameters():
+            p.grad = None
+        y, aux = layer(xi)
+        (y.float().pow(2).mean() + aux).backward()
+        outs.append((y.detach().float(), xi.grad.float(), layer.router.weight.grad.float().clone(),
+                     layer.experts.weight1.grad.float().clone()))
+    for a, b in zip(*outs):
+        assert torch.allclose(a, b, rtol=3e-2, atol=3e-3), (a - b).abs().max()
+    assert _lib.read_status() == 0
