@@ -75,8 +75,8 @@ def _declare(lib):
     sig("mfb_router_bwd", [P, P, P, P, P, I, I, I, I, I, F, P])
     sig("mfb_moe_flag_words", [])
     sig("mfb_moe_rank", [P, I, I, P, P, P])
-    sig("mfb_moe_plan", [I, I, I, I, I, I] + [P] * 10)
-    sig("mfb_moe_scatter", [I] * 7 + [P] * 11)
+    sig("mfb_moe_plan", [I, I, I, I, I, I] + [P] * 11)
+    sig("mfb_moe_scatter", [I] * 7 + [P] * 12)
     sig("mfb_moe_barrier", [I, I, I, I, P, P, P])
     sig("mfb_moe_gather", [I] * 7 + [P] * 9)
     # optional entry points (present once their source file is part of the build)

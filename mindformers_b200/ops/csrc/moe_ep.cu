@@ -102,7 +102,8 @@ moe_rank_kernel(const long long* __restrict__ ids, int n, int* __restrict__ rank
 struct MoePlanArgs {
   int world, rank, epoch, E, E_local, rows_cap, nblocks_cap;
   const int* counts;                 // [E] of this rank
-  int* table_peer[kMoeMaxRanks];     // [world][E] count table of every rank (row r written by rank r)
+  int* table_peer[kMoeMaxRanks];     // [world][E + 1] table of every rank: row r = counts of rank r, then its rows_cap
+  int* owner_cap;                    // out [kMoeMaxRanks]: rows_cap of every rank's buffer
   int* flags_peer[kMoeMaxRanks];     // [3][kMoeMaxRanks] flag rows: 0 = counts, 1 / 2 = barriers
   int* write_base;                   // out [E]: first row (in the owner's buffer) for this rank's copies of e
   int* group_offsets;                // out [E_local + 1]: padded segment starts of the local experts
@@ -120,8 +121,10 @@ moe_plan_kernel(MoePlanArgs a) {
   const int e = threadIdx.x;
   int* table_local = a.table_peer[a.rank];
   if (a.world > 1) {
-    if (e < a.E)
-      for (int p = 0; p < a.world; ++p) a.table_peer[p][a.rank * a.E + e] = a.counts[e];
+    for (int p = 0; p < a.world; ++p) {
+      if (e < a.E) a.table_peer[p][a.rank * (a.E + 1) + e] = a.counts[e];
+      if (e == 0) a.table_peer[p][a.rank * (a.E + 1) + a.E] = a.rows_cap;
+    }
     __threadfence_system();
     __syncthreads();
     if (e < a.world) moe_st_release_sys(a.flags_peer[e] + a.rank, a.epoch);
@@ -130,13 +133,15 @@ moe_plan_kernel(MoePlanArgs a) {
   if (e < a.E) {
     int t = 0, b = 0;
     for (int r = 0; r < a.world; ++r) {
-      const int c = a.world > 1 ? moe_ld_acquire_sys(table_local + r * a.E + e) : a.counts[e];
+      const int c = a.world > 1 ? moe_ld_acquire_sys(table_local + r * (a.E + 1) + e) : a.counts[e];
       if (r < a.rank) b += c;
       t += c;
     }
     tot[e] = t;
     mine[e] = b;
   }
+  if (e < kMoeMaxRanks)
+    a.owner_cap[e] = e >= a.world ? 0 : (a.world > 1 ? moe_ld_acquire_sys(table_local + e * (a.E + 1) + a.E) : a.rows_cap);
   __syncthreads();
   // padded segment starts per owner rank (every rank computes all of them: they are the senders' bases)
   if (e < a.world) {
@@ -185,6 +190,7 @@ struct MoeMoveArgs {
   const long long* ids;       // [T, k]
   const int* rank_in_e;       // [T * k]
   const int* write_base;      // [E]
+  const int* owner_cap;       // [kMoeMaxRanks] rows of every rank's buffer
   __nv_bfloat16* buf_peer[kMoeMaxRanks];  // row buffer [rows_cap, H] of every rank
   const float* weights;       // [T, k] or null
   int* dest_row;              // [T * k] out (scatter) / in (gather): row in the owner's buffer, -1 = dropped
@@ -206,7 +212,7 @@ moe_scatter_kernel(MoeMoveArgs a, const __nv_bfloat16* __restrict__ x) {
     const int e = (int)a.ids[c];
     const int owner = e / a.E_local;
     const int row = a.write_base[e] + a.rank_in_e[c];
-    const bool ok = row < a.rows_cap;
+    const bool ok = e >= 0 && owner < a.world && row >= 0 && row < a.owner_cap[owner];
     if (lane == 0) a.dest_row[c] = ok ? row : -1;
     if (!ok) continue;
     const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * a.H);
@@ -282,8 +288,8 @@ moe_gather_kernel(MoeMoveArgs a, __nv_bfloat16* __restrict__ out, const __nv_bfl
         const long long c = t * a.k + j;
         const int row = a.dest_row[c];
         float dot = 0.f;
-        if (row >= 0 && v < vecs) {
-          const int owner = (int)a.ids[c] / a.E_local;
+        const int owner = (int)a.ids[c] / a.E_local;
+        if (row >= 0 && owner >= 0 && owner < a.world && v < vecs) {
           const uint4 q = moe_ld_cg(a.buf_peer[owner] + (long long)row * a.H + 8 * v);
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
           const float w = a.weights ? a.weights[c] : 1.f;
@@ -342,8 +348,9 @@ int mfb_moe_rank(const long long* ids, int n, int E, int* rank_in_e, int* counts
 
 // peer_tables / peer_flags: host arrays of `world` device addresses.
 int mfb_moe_plan(int world, int rank, int epoch, int E, int E_local, int rows_cap, const int* counts,
-                 const long long* peer_tables, const long long* peer_flags, int* write_base, int* group_offsets,
-                 int* seg_fill, int* block_group, int* num_blocks, int* status, cudaStream_t stream) {
+                 const long long* peer_tables, const long long* peer_flags, int* write_base, int* owner_cap,
+                 int* group_offsets, int* seg_fill, int* block_group, int* num_blocks, int* status,
+                 cudaStream_t stream) {
   if (moe_check(world, rank, E, E_local, 8)) return 1;
   MoePlanArgs a;
   a.world = world; a.rank = rank; a.epoch = epoch; a.E = E; a.E_local = E_local; a.rows_cap = rows_cap;
@@ -352,29 +359,38 @@ int mfb_moe_plan(int world, int rank, int epoch, int E, int E_local, int rows_ca
     a.table_peer[p] = peer_tables ? reinterpret_cast<int*>(peer_tables[p]) : nullptr;
     a.flags_peer[p] = peer_flags ? reinterpret_cast<int*>(peer_flags[p]) : nullptr;
   }
-  a.write_base = write_base; a.group_offsets = group_offsets; a.seg_fill = seg_fill; a.block_group = block_group;
+  a.write_base = write_base; a.owner_cap = owner_cap; a.group_offsets = group_offsets; a.seg_fill = seg_fill; a.block_group = block_group;
   a.num_blocks = num_blocks; a.status = status;
   moe_plan_kernel<<<1, kMoeMaxExperts, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
+static int aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 static void fill_move(MoeMoveArgs* a, int world, int rank, int T, int k, int H, int E_local, int rows_cap,
-                      const long long* ids, const int* rank_in_e, const int* write_base, const long long* peer_bufs,
+                      const long long* ids, const int* rank_in_e, const int* write_base, const int* owner_cap,
+                      const long long* peer_bufs,
                       const float* weights, int* dest_row, const int* group_offsets, const int* seg_fill, int* status) {
   a->world = world; a->rank = rank; a->T = T; a->k = k; a->H = H; a->E_local = E_local; a->rows_cap = rows_cap;
-  a->ids = ids; a->rank_in_e = rank_in_e; a->write_base = write_base; a->weights = weights; a->dest_row = dest_row;
+  a->ids = ids; a->rank_in_e = rank_in_e; a->write_base = write_base; a->owner_cap = owner_cap; a->weights = weights;
+  a->dest_row = dest_row;
   a->group_offsets = group_offsets; a->seg_fill = seg_fill; a->status = status;
   for (int p = 0; p < world; ++p) a->buf_peer[p] = reinterpret_cast<__nv_bfloat16*>(peer_bufs[p]);
 }
 
 int mfb_moe_scatter(int world, int rank, int T, int k, int H, int E_local, int rows_cap, const void* x,
-                    const long long* ids, const int* rank_in_e, const int* write_base, const long long* peer_bufs,
-                    const float* weights, int* dest_row, const int* group_offsets, const int* seg_fill, int* status,
-                    cudaStream_t stream) {
+                    const long long* ids, const int* rank_in_e, const int* write_base, const int* owner_cap,
+                    const long long* peer_bufs, const float* weights, int* dest_row, const int* group_offsets,
+                    const int* seg_fill, int* status, cudaStream_t stream) {
   if (moe_check(world, rank, E_local * world, E_local, H)) return 1;
+  for (int p = 0; p < world; ++p)
+    if (!aligned16(reinterpret_cast<const void*>(peer_bufs[p])) || !aligned16(x)) {
+      mfb_host::set_error("moe scatter: row buffers and the source must be 16-byte aligned");
+      return 1;
+    }
   MoeMoveArgs a;
-  fill_move(&a, world, rank, T, k, H, E_local, rows_cap, ids, rank_in_e, write_base, peer_bufs, weights, dest_row,
-            group_offsets, seg_fill, status);
+  fill_move(&a, world, rank, T, k, H, E_local, rows_cap, ids, rank_in_e, write_base, owner_cap, peer_bufs, weights,
+            dest_row, group_offsets, seg_fill, status);
   moe_scatter_kernel<<<148 * 4, 256, 0, stream>>>(a, (const __nv_bfloat16*)x);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
@@ -394,8 +410,13 @@ int mfb_moe_gather(int world, int rank, int T, int k, int H, int E_local, int ro
                    const long long* ids, const int* dest_row, const long long* peer_bufs, const float* weights,
                    const void* g, float* dots, int* status, cudaStream_t stream) {
   if (moe_check(world, rank, E_local * world, E_local, H)) return 1;
+  for (int p = 0; p < world; ++p)
+    if (!aligned16(reinterpret_cast<const void*>(peer_bufs[p])) || !aligned16(out) || !aligned16(g)) {
+      mfb_host::set_error("moe gather: row buffers, the output and the gradient must be 16-byte aligned");
+      return 1;
+    }
   MoeMoveArgs a;
-  fill_move(&a, world, rank, T, k, H, E_local, rows_cap, ids, nullptr, nullptr, peer_bufs, weights,
+  fill_move(&a, world, rank, T, k, H, E_local, rows_cap, ids, nullptr, nullptr, nullptr, peer_bufs, weights,
             const_cast<int*>(dest_row), nullptr, nullptr, status);
   moe_gather_kernel<<<148 * 4, 256, 0, stream>>>(a, (__nv_bfloat16*)out, (const __nv_bfloat16*)g, dots);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

@@ -130,9 +130,9 @@ class DistributedOptimizer:
             flags = symm_mem.allocate(f"dpopt.{name}.flags.{id(self)}", words * 4, sh.group, dev)
             flags.tensor.zero_()
             arr = ctypes.c_longlong * sh.world
-            sh.peer_grad = arr(*[int(p) for p in self._symm[f"{name}.grad"].handle.buffer_ptrs])
-            sh.peer_param = arr(*[int(p) for p in self._symm[f"{name}.param"].handle.buffer_ptrs])
-            sh.peer_flags = arr(*[int(p) for p in flags.handle.buffer_ptrs])
+            sh.peer_grad = arr(*[int(p) for p in self._symm[f"{name}.grad"].ptrs])
+            sh.peer_param = arr(*[int(p) for p in self._symm[f"{name}.param"].ptrs])
+            sh.peer_flags = arr(*[int(p) for p in flags.ptrs])
             sh.flags = flags
             sh.fused = True
         torch.cuda.synchronize()

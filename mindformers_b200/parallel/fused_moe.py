@@ -39,12 +39,12 @@ class _Plan:
 class MoEExchange:
     """Per-group state: flags, count table, shared gradient row buffers, epoch counter."""
 
-    _instances: Dict[int, "MoEExchange"] = {}
+    _instances: Dict[tuple, "MoEExchange"] = {}
 
     @classmethod
     def get(cls, config) -> "MoEExchange":
         grp = ps.get_expert_model_parallel_group()
-        key = id(grp)
+        key = (id(grp), config.hidden_size, config.num_moe_experts, config.moe_router_topk)
         inst = cls._instances.get(key)
         if inst is None:
             inst = cls._instances[key] = cls(config, grp)
@@ -67,13 +67,13 @@ class MoEExchange:
         self._in_flight: Dict[object, set] = {}
         if self.world > 1:
             words = self.lib.mfb_moe_flag_words()
-            flags = symm_mem.allocate(f"moe.flags.{id(group)}", words * 4, group, self.dev)
+            flags = symm_mem.allocate(f"moe.flags.{id(group)}.{self.H}.{self.E}.{self.k}", words * 4, group, self.dev)
             flags.tensor.zero_()
-            table = symm_mem.allocate(f"moe.table.{id(group)}", self.world * self.E * 4, group, self.dev)
+            table = symm_mem.allocate(f"moe.table.{id(group)}.{self.H}.{self.E}.{self.k}", self.world * (self.E + 1) * 4, group, self.dev)
             table.tensor.zero_()
             self.flags, self.table = flags, table
-            self.peer_flags = self._arr(*[int(p) for p in flags.handle.buffer_ptrs])
-            self.peer_table = self._arr(*[int(p) for p in table.handle.buffer_ptrs])
+            self.peer_flags = self._arr(*[int(p) for p in flags.ptrs])
+            self.peer_table = self._arr(*[int(p) for p in table.ptrs])
             torch.cuda.synchronize()
             dist.barrier(group=group)
         else:
@@ -91,9 +91,9 @@ class MoEExchange:
         if hit is not None:
             return hit
         if self.world > 1:
-            buf = symm_mem.allocate(f"moe.{tag}.{rows}.{id(self.group)}", rows * self.H * 2, self.group, self.dev)
+            buf = symm_mem.allocate(f"moe.{tag}.{rows}.{self.H}.{self.E}.{id(self.group)}", rows * self.H * 2, self.group, self.dev)
             t = buf.tensor.view(torch.bfloat16)[:rows * self.H].view(rows, self.H)
-            ptrs = self._arr(*[int(p) for p in buf.handle.buffer_ptrs])
+            ptrs = self._arr(*[int(p) for p in buf.ptrs])
         else:
             t = torch.empty(rows, self.H, dtype=torch.bfloat16, device=self.dev)
             ptrs = self._arr(t.data_ptr())
@@ -131,7 +131,7 @@ class MoEExchange:
         rc = self.lib.mfb_moe_rank(ids.data_ptr(), n, self.E, st.rank_in_e.data_ptr(), st.counts.data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "mfb_moe_rank")
         rc = self.lib.mfb_moe_plan(self.world, self.rank, self.next_epoch(), self.E, self.E_local, rows, st.counts.data_ptr(),
-                                   self.peer_table, self.peer_flags, st.write_base.data_ptr(),
+                                   self.peer_table, self.peer_flags, st.write_base.data_ptr(), st.owner_cap.data_ptr(),
                                    st.plan.group_offsets.data_ptr(), st.plan.seg_fill.data_ptr(),
                                    st.plan.block_group.data_ptr(), st.plan.num_blocks.data_ptr(), self.status(),
                                    _lib.stream_ptr())
@@ -142,7 +142,8 @@ class MoEExchange:
     def scatter(self, st, x, ids, peer_ptrs, weights=None):
         T = x.shape[0]
         rc = self.lib.mfb_moe_scatter(self.world, self.rank, T, self.k, self.H, self.E_local, st.rows, x.data_ptr(),
-                                      ids.data_ptr(), st.rank_in_e.data_ptr(), st.write_base.data_ptr(), peer_ptrs,
+                                      ids.data_ptr(), st.rank_in_e.data_ptr(), st.write_base.data_ptr(),
+                                      st.owner_cap.data_ptr(), peer_ptrs,
                                       _lib.ptr(weights), st.dest_row.data_ptr(), st.plan.group_offsets.data_ptr(),
                                       st.plan.seg_fill.data_ptr(), self.status(), _lib.stream_ptr())
         _lib.check(rc, "mfb_moe_scatter")
@@ -173,6 +174,7 @@ class _PlanState:
         self.rank_in_e = torch.empty(n, dtype=torch.int32, device=dev)
         self.counts = torch.empty(ex.E, dtype=torch.int32, device=dev)
         self.write_base = torch.empty(ex.E, dtype=torch.int32, device=dev)
+        self.owner_cap = torch.zeros(8, dtype=torch.int32, device=dev)
         self.dest_row = torch.empty(n, dtype=torch.int32, device=dev)
         self.plan = _Plan(ex.E_local, rows, dev)
 

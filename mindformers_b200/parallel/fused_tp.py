@@ -73,10 +73,10 @@ class TpCommContext:
 
     # views into the flag buffer (ints)
     def ready_ptrs(self):
-        return [p for p in self.flags.handle.buffer_ptrs]
+        return [p for p in self.flags.ptrs]
 
     def tile_flag_ptrs(self):
-        return [p + self.tp * 4 for p in self.flags.handle.buffer_ptrs]
+        return [p + self.tp * 4 for p in self.flags.ptrs]
 
 
 _CTX: Optional[TpCommContext] = None
@@ -109,7 +109,7 @@ def allgather_gemm(x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False):
     slot = e & 1
     xs_local = ctx.xs.tensor.view(torch.bfloat16)[slot * ctx.x_elems: slot * ctx.x_elems + Tl * K].view(Tl, K)
     xs_local.copy_(x_local)
-    peer = [p + slot * ctx.x_elems * 2 for p in ctx.xs.handle.buffer_ptrs]
+    peer = [p + slot * ctx.x_elems * 2 for p in ctx.xs.ptrs]
     x_full = torch.empty((T, K), dtype=torch.bfloat16, device=x_local.device)
     y = torch.empty((T, N), dtype=torch.bfloat16, device=x_local.device)
     block_flags = torch.empty(T // 128, dtype=torch.int32, device=x_local.device)
@@ -138,7 +138,7 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) ->
     if not x.is_contiguous():
         x = x.contiguous()
     y = torch.empty((Tl, N), dtype=torch.bfloat16, device=x.device)
-    recv = list(ctx.recv.handle.buffer_ptrs)
+    recv = list(ctx.recv.ptrs)
     tf = ctx.tile_flag_ptrs()
     # the receive slots of this call are laid out with the actual slot size
     st = _lib.status_word(x.device)

@@ -24,9 +24,18 @@ class SymmBuffer:
         self.handle = handle
         self.world = handle.world_size
         self.rank = handle.rank
-        self.peer_ptrs = torch.tensor(list(handle.buffer_ptrs), dtype=torch.int64, device=tensor.device)
+        # torch sub-allocates symmetric tensors from pooled blocks: ``buffer_ptrs`` are the block bases on every
+        # rank and ``offset`` is where this tensor starts inside its block (the same on all ranks)
+        off = int(getattr(handle, "offset", 0) or 0)
+        self.offset = off
+        self.ptrs = [int(p) + off for p in handle.buffer_ptrs]
+        if self.ptrs[self.rank] != tensor.data_ptr():
+            raise RuntimeError(f"symmetric buffer: local address {tensor.data_ptr():#x} is not block base + offset "
+                               f"({self.ptrs[self.rank]:#x}); peer pointers cannot be derived")
+        self.peer_ptrs = torch.tensor(self.ptrs, dtype=torch.int64, device=tensor.device)
         self.signal_ptrs = torch.tensor(list(handle.signal_pad_ptrs), dtype=torch.int64, device=tensor.device)
-        self.multicast_ptr = int(getattr(handle, "multicast_ptr", 0) or 0)
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc + off if mc else 0
 
 
 def allocate(name: str, nbytes: int, group, device=None) -> SymmBuffer:

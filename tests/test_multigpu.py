@@ -28,3 +28,7 @@ def test_fused_tensor_parallel_gemms():
 
 def test_fused_data_parallel_optimizer():
     _run("run_fused_dp.py", "--big", "0")
+
+
+def test_fused_moe_expert_parallel_exchange():
+    _run("run_fused_moe.py", "--bench", "0")
