@@ -18,13 +18,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(tmp_path, nproc, tag, *extra):
+def _run(tmp_path, nproc, tag, *extra, script=SCRIPT):
     out = tmp_path / f"{tag}.json"
     if nproc == 1:
-        cmd = [sys.executable, SCRIPT, "--out", str(out), *extra]
+        cmd = [sys.executable, script, "--out", str(out), *extra]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), SCRIPT, "--out", str(out), *extra]
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), script, "--out", str(out), *extra]
     env = dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1")
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stderr[-3000:]
@@ -66,3 +66,23 @@ def test_expert_parallel(tmp_path):
     ref = _run(tmp_path, 1, "moe_ref", "--moe", "1")
     got = _run(tmp_path, 2, "moe_ep2", "--moe", "1", "--ep", "2")
     _close(got, ref, 5e-5)
+
+
+PIPE = os.path.join(ROOT, "tests", "dist", "run_pipeline.py")
+
+
+@pytest.fixture(scope="module")
+def pipe_ref(tmp_path_factory):
+    return _run(tmp_path_factory.mktemp("pref"), 1, "ref", script=PIPE)
+
+
+def test_pipeline_parallel_1f1b(tmp_path, pipe_ref):
+    _close(_run(tmp_path, 2, "pp2", "--pp", "2", script=PIPE), pipe_ref, 2e-5)
+
+
+def test_pipeline_parallel_interleaved(tmp_path, pipe_ref):
+    _close(_run(tmp_path, 2, "pp2v2", "--pp", "2", "--vpp", "2", script=PIPE), pipe_ref, 2e-5)
+
+
+def test_pipeline_parallel_four_stages(tmp_path, pipe_ref):
+    _close(_run(tmp_path, 4, "pp4", "--pp", "4", script=PIPE), pipe_ref, 2e-5)
