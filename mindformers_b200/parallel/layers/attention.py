@@ -143,7 +143,7 @@ class SelfAttention(nn.Module):
             q, k, v = packed[:, :self.nq], packed[:, self.nq:self.nq + self.nkv], packed[:, self.nq + self.nkv:]
         ctx = None
         if meta.cache is None and meta.cu_seqlens is None and ps.get_context_parallel_world_size() == 1 \
-                and Fn.get_attention_backend() != "sdpa":
+                and Fn.get_attention_backend() != "sdpa" and getattr(self, "use_packed_attention", True):
             from ...ops import attention as native
             T = packed.shape[0]
             S = T // meta.batch

@@ -1,0 +1,5 @@
+from .pet_config import LoraConfig, PetConfig, PrefixTuningConfig, Ptuning2Config, SLoraConfig
+from .lora import LoraAdapter, LoraModel, LoRALinear, merge_lora_weights, lora_state_dict
+from .slora import SLoraAdapter, SLoraLinear
+from .prompt import PrefixEncoder, PrefixTuningModel
+from .pet_model import get_pet_model, is_supported_pet_type
