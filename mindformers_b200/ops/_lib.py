@@ -79,6 +79,12 @@ def _declare(lib):
     sig("mfb_moe_scatter", [I] * 7 + [P] * 12)
     sig("mfb_moe_barrier", [I, I, I, I, P, P, P])
     sig("mfb_moe_gather", [I] * 7 + [P] * 9)
+    sig("mfb_flash_attn_fwd_ex", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, I, F, P, P])
+    sig("mfb_flash_attn_bwd_ex", [P] * 10 + [I, I, I, I, I] + [L] * 8 + [I, I, F, P, P])
+    sig("mfb_cp_flag_words", [])
+    sig("mfb_cp_gather", [I, I, I, I, I, L, I, P, P, P, P, P])
+    sig("mfb_cp_reduce_scatter", [I, I, I, I, I, L, I, P, P, P, P, P])
+    sig("mfb_cp_barrier", [I, I, I, I, P, P, P])
     # optional entry points (present once their source file is part of the build)
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

@@ -136,3 +136,68 @@ def flash_attention(q, k, v, causal=True, scale=None):
         if t.stride(0) != t.shape[1] * t.stride(1) or t.stride(2) != HEAD_DIM:
             return _AttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale)
     return _AttnFn.apply(q, k, v, causal, scale)
+
+
+# ---- rectangular causal attention: Sq queries at key positions [q_offset, q_offset + Sq) of Sk keys ------------
+def rect_forward(q, k, v, q_offset: int, causal: bool, scale: float):
+    """Raw forward: q ``[B,Sq,Hq,128]``, k/v ``[B,Sk,Hkv,128]`` contiguous → ``(out [B*Sq, Hq*128], lse [B,Hq,Sq])``."""
+    B, Sq, nq, _ = q.shape
+    Sk, nkv = k.shape[1], k.shape[2]
+    out = torch.empty((B * Sq, nq * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, nq, Sq), dtype=torch.float32, device=q.device)
+    st = _lib.status_word(q.device)
+    rc = _lib.get_lib().mfb_flash_attn_fwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                              B, Sq, Sk, nq, nkv, q.stride(1), k.stride(1), v.stride(1), out.stride(0),
+                                              int(causal), int(q_offset), float(scale), st.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_flash_attn_fwd_ex")
+    _lib.count_launch()
+    return out, lse
+
+
+def rect_backward(q, k, v, out, lse, dout, dk, dv, q_offset: int, causal: bool, scale: float):
+    """Raw backward: returns ``dq``; writes ``dk`` / ``dv`` (``[B,Sk,Hkv,128]``, every key row, zeros where no query looks)."""
+    B, Sq, nq, _ = q.shape
+    Sk, nkv = k.shape[1], k.shape[2]
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lib = _lib.get_lib()
+    scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, Sq, nq))
+    st = _lib.status_word(q.device)
+    rc = lib.mfb_flash_attn_bwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                                   dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), B, Sq, Sk, nq, nkv,
+                                   q.stride(1), k.stride(1), v.stride(1), out.stride(0), nq * HEAD_DIM, dq.stride(1),
+                                   dk.stride(1), dv.stride(1), int(causal), int(q_offset), float(scale), st.data_ptr(),
+                                   _lib.stream_ptr())
+    _lib.check(rc, "mfb_flash_attn_bwd_ex")
+    _lib.count_launch(4)
+    return dq
+
+
+class _RectAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, q_offset, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = rect_forward(q, k, v, q_offset, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta = (q_offset, causal, scale)
+        B, Sq, nq, _ = q.shape
+        return out.view(B, Sq, nq, HEAD_DIM)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        q_offset, causal, scale = ctx.meta
+        dk, dv = torch.empty_like(k), torch.empty_like(v)
+        dq = rect_backward(q, k, v, out, lse, dout.contiguous(), dk, dv, q_offset, causal, scale)
+        return dq, dk, dv, None, None, None
+
+
+def rect_supported(q, k, v) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == HEAD_DIM and v.shape[-1] == HEAD_DIM
+            and q.shape[1] % TILE == 0 and k.shape[1] % TILE == 0 and q.shape[2] % k.shape[2] == 0)
+
+
+def flash_attention_rect(q, k, v, q_offset: int = 0, causal: bool = True, scale=None):
+    """Attention of ``Sq`` queries over ``Sk`` keys, query ``i`` sitting at key position ``q_offset + i``
+    (``q_offset`` a multiple of 128): prefix / chunked-prefill / context-parallel shapes."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
+    return _RectAttnFn.apply(q, k, v, int(q_offset), bool(causal), float(scale))

@@ -43,6 +43,7 @@ __device__ __forceinline__ float ex2_poly(float x) {
 
 struct FaArgs {
   int seq_q, seq_k;      // tokens per sequence
+  int q_off_tiles;       // causal: query row i sits at key position q_off_tiles * 128 + i
   int num_q_heads, group;  // group = q heads per kv head
   int causal;
   float scale_log2;      // softmax scale * log2(e)
@@ -78,7 +79,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int q_tile = gridDim.x - 1 - blockIdx.x;   // heavy (late) tiles first
   const int head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / args.group;
-  const int n_kv = args.causal ? (q_tile + 1) : (args.seq_k / kTile);
+  const int diag_tile = args.q_off_tiles + q_tile;   // key tile that holds the causal diagonal of this query tile
+  const int n_kv_all = args.seq_k / kTile;
+  const int n_kv = args.causal ? (diag_tile + 1 < n_kv_all ? diag_tile + 1 : n_kv_all) : n_kv_all;
   const int q_row0 = batch * args.seq_q + q_tile * kTile;
   const int k_row0 = batch * args.seq_k;
 
@@ -210,7 +213,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       mbar_arrive(smem_u32(&s_empty[st]));
       float* s = reinterpret_cast<float*>(sr);
-      if (args.causal && j == n_kv - 1) {
+      if (args.causal && j == diag_tile) {
 #pragma unroll
         for (int i = 0; i < kTile; ++i)
           if (i > row) s[i] = -INFINITY;
@@ -341,13 +344,15 @@ extern "C" {
 using namespace mfb;
 
 // q: [B*Sq, q_ld] bf16 rows with head h at columns [h*128, h*128+128); k, v likewise with Hkv heads.
-// o: [B*Sq, o_ld]; lse: [B, Hq, Sq] fp32 (may be null). Sq, Sk multiples of 128; causal needs Sq == Sk.
-int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
-                       int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
-                       int causal, float scale, int* status, cudaStream_t stream) {
-  if (Sq % kTile || Sk % kTile || Hq % Hkv || (causal && Sq != Sk) || B <= 0) {
-    mfb_host::set_error("flash_attn_fwd: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d causal=%d", B, Sq, Sk, Hq,
-                        Hkv, causal);
+// o: [B*Sq, o_ld]; lse: [B, Hq, Sq] fp32 (may be null). Sq, Sk multiples of 128. Causal: query i of a sequence sits
+// at key position q_offset + i (q_offset a multiple of 128, q_offset + Sq <= Sk) and sees keys up to itself.
+int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                          int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
+                          int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
+  if (Sq % kTile || Sk % kTile || Hq % Hkv || B <= 0 || q_offset % kTile || q_offset < 0 ||
+      (causal && q_offset + Sq > Sk)) {
+    mfb_host::set_error("flash_attn_fwd: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d causal=%d q_offset=%d", B, Sq,
+                        Sk, Hq, Hkv, causal, q_offset);
     return 1;
   }
   CUtensorMap tQ, tK, tV, tO;
@@ -357,7 +362,8 @@ int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   if ((rc = mfb_host::make_tmap_2d(&tV, v, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sk, (uint64_t)Hkv * kHd, v_ld, kTile, 64))) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tO, o, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sq, (uint64_t)Hq * kHd, o_ld, kTile, 64))) return 50 + rc;
   FaArgs a;
-  a.seq_q = Sq; a.seq_k = Sk; a.num_q_heads = Hq; a.group = Hq / Hkv; a.causal = causal;
+  a.seq_q = Sq; a.seq_k = Sk; a.q_off_tiles = q_offset / kTile; a.num_q_heads = Hq; a.group = Hq / Hkv;
+  a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.lse = lse; a.status = status;
   constexpr int SMEM = 7 * kTileBytes + 18 * 8 + 16 + 1024;
@@ -378,6 +384,17 @@ int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   return 0;
 }
 
+int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                       int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
+                       int causal, float scale, int* status, cudaStream_t stream) {
+  if (causal && Sq != Sk) {
+    mfb_host::set_error("flash_attn_fwd: causal with Sq != Sk needs mfb_flash_attn_fwd_ex and a query offset");
+    return 1;
+  }
+  return mfb_flash_attn_fwd_ex(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, 0, scale, status,
+                               stream);
+}
+
 }  // extern "C"
 
 // =================================================================================================
@@ -394,7 +411,8 @@ int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
 namespace mfb {
 
 struct FaBwdArgs {
-  int seq;               // Sq == Sk
+  int seq_q, seq_k;      // tokens per sequence on the query / key side
+  int q_off_tiles;       // causal: query row i sits at key position q_off_tiles * 128 + i
   int num_q_heads, num_kv_heads, group;
   int causal;
   float scale, scale_log2;
@@ -430,11 +448,14 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
-  const int n_q_tiles = args.seq / kTile;
-  const int first_q = args.causal ? kv_tile : 0;
+  const int n_q_tiles = args.seq_q / kTile;
+  int first_q = args.causal ? kv_tile - args.q_off_tiles : 0;   // first query tile that sees this key tile
+  if (first_q < 0) first_q = 0;
+  if (first_q > n_q_tiles) first_q = n_q_tiles;
   const int iters_per_head = n_q_tiles - first_q;
   const int n_iter = iters_per_head * args.group;
-  const int row_base = batch * args.seq;
+  const int row_base = batch * args.seq_q;       // query-side rows (Q, dO, dQ)
+  const int krow_base = batch * args.seq_k;      // key-side rows (K, V, dK, dV)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -464,7 +485,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (lane == 0) {
       const uint32_t kvb = smem_u32(kv_full);
       mbar_expect_tx(kvb, 2 * kTileBytes);
-      const int krow = row_base + kv_tile * kTile;
+      const int krow = krow_base + kv_tile * kTile;
       tma_load_2d(smem_u32(sK), &tmK, kvb, kv_head * kHd, krow);
       tma_load_2d(smem_u32(sK) + kSubBytes, &tmK, kvb, kv_head * kHd + 64, krow);
       tma_load_2d(smem_u32(sV), &tmV, kvb, kv_head * kHd, krow);
@@ -547,14 +568,14 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint32_t ph = it & 1;
       const int hq = kv_head * args.group + it / iters_per_head;
       const int qi = first_q + it % iters_per_head;
-      const size_t stat_idx = (static_cast<size_t>(batch) * args.num_q_heads + hq) * args.seq + qi * kTile + row;
+      const size_t stat_idx = (static_cast<size_t>(batch) * args.num_q_heads + hq) * args.seq_q + qi * kTile + row;
       const float lse2 = args.lse[stat_idx] * 1.4426950408889634f;
       const float dlt = args.delta[stat_idx];
       ok = mbar_wait(smem_u32(sdp_full), ph, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
       ok = named_bar_and(2, 128, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool diag = args.causal && (qi == kv_tile);
+      const bool diag = args.causal && (qi + args.q_off_tiles == kv_tile);
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sdS + row * 128;
 #pragma unroll
@@ -610,7 +631,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     if (ok) {
       // all MMAs have completed (last qdo_empty wait above); write dK and dV of this tile
-      const int krow = row_base + kv_tile * kTile;
+      const int krow = krow_base + kv_tile * kTile;
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tmem_dK : tmem_dV;
         uint8_t* stage = which == 0 ? sP : sdS;
@@ -631,6 +652,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                              pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
             }
           }
+        } else {
+          // no query tile sees this key tile (keys beyond the last query's diagonal): its gradients are zero
+#pragma unroll
+          for (int chunk = 0; chunk < 16; ++chunk)
+            *reinterpret_cast<uint4*>(orow + (chunk >> 3) * kSubBytes + ((chunk & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       fence_proxy_async_smem();
@@ -703,19 +729,23 @@ long long mfb_flash_attn_bwd_scratch_bytes(int B, int S, int Hq) {
   return static_cast<long long>(B) * S * Hq * kHd * 4 + static_cast<long long>(B) * S * Hq * 4;
 }
 
-// Gradients of causal/full self-attention (Sq == Sk). q/k/v/o/do as in the forward; dq/dk/dv are written with
-// their own row pitches (they may be column ranges of one packed gradient buffer). `scratch` must hold
-// mfb_flash_attn_bwd_scratch_bytes() bytes; this call zeroes the part it accumulates into.
-int mfb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                       const float* lse, void* dq, void* dk, void* dv, void* scratch, int B, int S, int Hq, int Hkv,
-                       long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
-                       long long dq_ld, long long dk_ld, long long dv_ld, int causal, float scale, int* status,
-                       cudaStream_t stream) {
-  if (S % kTile || Hq % Hkv || B <= 0) {
-    mfb_host::set_error("flash_attn_bwd: unsupported shape B=%d S=%d Hq=%d Hkv=%d", B, S, Hq, Hkv);
+// Gradients of attention with Sq queries and Sk keys per sequence (causal: query i at key position q_offset + i).
+// q/k/v/o/do as in the forward; dq/dk/dv are written with their own row pitches (they may be column ranges of one
+// packed gradient buffer); dk/dv cover all Sk keys. `scratch` must hold mfb_flash_attn_bwd_scratch_bytes(B, Sq, Hq)
+// bytes; this call zeroes the part it accumulates into.
+int mfb_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                          const float* lse, void* dq, void* dk, void* dv, void* scratch, int B, int S, int Sk, int Hq,
+                          int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
+                          long long dq_ld, long long dk_ld, long long dv_ld, int causal, int q_offset, float scale,
+                          int* status, cudaStream_t stream) {
+  if (S % kTile || Sk % kTile || Hq % Hkv || B <= 0 || q_offset % kTile || q_offset < 0 ||
+      (causal && q_offset + S > Sk)) {
+    mfb_host::set_error("flash_attn_bwd: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d q_offset=%d", B, S, Sk, Hq, Hkv,
+                        q_offset);
     return 1;
   }
   const long long T = static_cast<long long>(B) * S;
+  const long long Tk = static_cast<long long>(B) * Sk;
   float* dq_accum = reinterpret_cast<float*>(scratch);
   float* delta = dq_accum + T * Hq * kHd;
   cudaMemsetAsync(dq_accum, 0, T * Hq * kHd * sizeof(float), stream);
@@ -730,13 +760,14 @@ int mfb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* 
   int rc;
   const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if ((rc = mfb_host::make_tmap_2d(&tQ, q, 2, BF, T, (uint64_t)Hq * kHd, q_ld, kTile, 64))) return 20 + rc;
-  if ((rc = mfb_host::make_tmap_2d(&tK, k, 2, BF, T, (uint64_t)Hkv * kHd, k_ld, kTile, 64))) return 30 + rc;
-  if ((rc = mfb_host::make_tmap_2d(&tV, v, 2, BF, T, (uint64_t)Hkv * kHd, v_ld, kTile, 64))) return 40 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tK, k, 2, BF, Tk, (uint64_t)Hkv * kHd, k_ld, kTile, 64))) return 30 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tV, v, 2, BF, Tk, (uint64_t)Hkv * kHd, v_ld, kTile, 64))) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tdO, d_o, 2, BF, T, (uint64_t)Hq * kHd, do_ld, kTile, 64))) return 50 + rc;
-  if ((rc = mfb_host::make_tmap_2d(&tdK, dk, 2, BF, T, (uint64_t)Hkv * kHd, dk_ld, kTile, 64))) return 60 + rc;
-  if ((rc = mfb_host::make_tmap_2d(&tdV, dv, 2, BF, T, (uint64_t)Hkv * kHd, dv_ld, kTile, 64))) return 70 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tdK, dk, 2, BF, Tk, (uint64_t)Hkv * kHd, dk_ld, kTile, 64))) return 60 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tdV, dv, 2, BF, Tk, (uint64_t)Hkv * kHd, dv_ld, kTile, 64))) return 70 + rc;
   FaBwdArgs a;
-  a.seq = S; a.num_q_heads = Hq; a.num_kv_heads = Hkv; a.group = Hq / Hkv; a.causal = causal;
+  a.seq_q = S; a.seq_k = Sk; a.q_off_tiles = q_offset / kTile; a.num_q_heads = Hq; a.num_kv_heads = Hkv;
+  a.group = Hq / Hkv; a.causal = causal;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.lse = lse; a.delta = delta; a.dq_accum = dq_accum; a.status = status;
   constexpr int SMEM = 6 * kTileBytes + 8 * 8 + 16 + 1024;
@@ -748,7 +779,7 @@ int mfb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* 
     }
     attr_set = true;
   }
-  dim3 grid(S / kTile, Hkv, B);
+  dim3 grid(Sk / kTile, Hkv, B);
   flash_attn_bwd_kernel<<<grid, kFaThreads, SMEM, stream>>>(tQ, tK, tV, tdO, tdK, tdV, a);
   {
     const long long total = T * (Hq * kHd / 4);
@@ -761,6 +792,15 @@ int mfb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* 
     return 11;
   }
   return 0;
+}
+
+int mfb_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                       const float* lse, void* dq, void* dk, void* dv, void* scratch, int B, int S, int Hq, int Hkv,
+                       long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
+                       long long dq_ld, long long dk_ld, long long dv_ld, int causal, float scale, int* status,
+                       cudaStream_t stream) {
+  return mfb_flash_attn_bwd_ex(q, k, v, o, d_o, lse, dq, dk, dv, scratch, B, S, S, Hq, Hkv, q_ld, k_ld, v_ld, o_ld,
+                               do_ld, dq_ld, dk_ld, dv_ld, causal, 0, scale, status, stream);
 }
 
 }  // extern "C"

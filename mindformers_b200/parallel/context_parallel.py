@@ -150,6 +150,11 @@ def allgather_kv_attention(q, k, v, scale, group=None):
 
 def context_parallel_attention(q, k, v, scale, config):
     kind = config.cp_comm_type
+    if kind in ("p2p", "all_gather") and getattr(config, "fused_cp_comm", True) and q.is_cuda:
+        from . import fused_comm, fused_cp
+        if fused_comm.cp_enabled() and fused_cp.supported(q, k, v):
+            # K/V exchange by peer loads + rectangular flash attention (same result as the ring)
+            return fused_cp.fused_cp_attention(q, k, v, scale, zigzag=bool(getattr(config, "cp_zigzag", False)))
     if kind == "p2p":
         if torch.is_grad_enabled() and q.requires_grad:
             return _RingAttnFn.apply(q, k, v, scale)

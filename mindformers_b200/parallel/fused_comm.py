@@ -25,6 +25,12 @@ def dp_enabled() -> bool:
     return not _FORCE_OFF and torch.cuda.is_available() and os.environ.get("MFB_FUSED_DP", "1") != "0"
 
 
+def cp_enabled() -> bool:
+    """Context-parallel K/V exchange through the peer-memory kernels (``parallel/fused_cp.py``)."""
+    import os
+    return not _FORCE_OFF and torch.cuda.is_available() and os.environ.get("MFB_FUSED_CP", "1") != "0"
+
+
 def _runtime_ready() -> bool:
     from . import symm_mem
     return symm_mem.is_ready()

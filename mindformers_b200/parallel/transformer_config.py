@@ -65,6 +65,8 @@ class ModelParallelConfig:
     # B200 additions: which fused compute+collective paths are on
     fused_tp_comm: bool = True
     fused_moe_comm: bool = True
+    fused_cp_comm: bool = True
+    cp_zigzag: bool = False              # causal load balance: rank r owns sequence chunks r and 2*cp-1-r
     moe_ep_buffer_factor: float = 1.25   # row-buffer head-room over the balanced load when ep > 1
 
     def _check_parallel(self):

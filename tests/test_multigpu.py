@@ -32,3 +32,7 @@ def test_fused_data_parallel_optimizer():
 
 def test_fused_moe_expert_parallel_exchange():
     _run("run_fused_moe.py", "--bench", "0")
+
+
+def test_fused_context_parallel_attention():
+    _run("run_fused_cp.py", "--bench", "0")
