@@ -1,0 +1,135 @@
+"""Launch one kernel family a few times on a small case (inputs larger than L2, a few hundred MB on the device):
+the target of `ncu -k regex:<kernel> -c N`. Usage: python benchmarks/run_kernel_once.py --kernel gemm
+
+Cases: gemm (fc1 forward 4096 x 28672 x 4096, then dgrad and wgrad layouts), fa (forward + backward, S=4096, 32/8
+heads), rmsnorm, swiglu, rope, ce (4096 x 128256 logits), adamw (64 M parameters), router (E=128 top-8 and E=256
+group-limited), paged (decode attention, 64 sequences of 2048 tokens, block 128), moe (single-rank exchange kernels).
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mindformers_b200.ops import functional as Fn  # noqa: E402
+from mindformers_b200.ops import _lib  # noqa: E402
+
+
+def bf(*shape, scale=0.5):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def gemm():
+    x, w = bf(4096, 4096), bf(28672, 4096, scale=0.05)
+    for _ in range(3):
+        y = Fn.gemm(x, w)                                   # forward  [4096, 28672]
+    dy = bf(4096, 28672, scale=0.1)
+    for _ in range(3):
+        Fn.gemm(dy, w, b_mn=True)                           # dgrad    [4096, 4096]
+    out = torch.zeros(28672, 4096, device="cuda")
+    for _ in range(3):
+        Fn.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True)   # wgrad, fp32 accumulate
+    return y
+
+
+def fa():
+    from mindformers_b200.ops import attention as A
+    B, S, nq, nkv = 1, 4096, 32, 8
+    packed = bf(B * S, nq + 2 * nkv, 128).requires_grad_()
+    g = bf(B * S, nq * 128, scale=0.1)
+    for _ in range(3):
+        packed.grad = None
+        A.flash_attention_packed(packed, B, S, nq, nkv, True).backward(g)
+
+
+def rmsnorm():
+    x, w = bf(32768, 4096).requires_grad_(), torch.ones(4096, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    for _ in range(3):
+        Fn.rmsnorm(x, w, 1e-5)[0].backward(bf(32768, 4096, scale=0.1))
+
+
+def swiglu():
+    x = bf(16384, 2 * 14336).requires_grad_()
+    for _ in range(3):
+        Fn.swiglu(x).backward(bf(16384, 14336, scale=0.1))
+
+
+def rope():
+    T, heads = 32768, 40
+    x = bf(T, heads, 128).requires_grad_()
+    inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device="cuda").float() / 128))
+    ang = torch.arange(4096, device="cuda").float()[:, None] * inv[None]
+    cos, sin = torch.cat([ang, ang], -1).cos(), torch.cat([ang, ang], -1).sin()
+    pos = torch.arange(T, device="cuda") % 4096
+    for _ in range(3):
+        Fn.rope(x, cos, sin, pos, heads, 128, False).backward(bf(T, heads, 128, scale=0.1))
+
+
+def ce():
+    logits = bf(4096, 128256, scale=1.0).requires_grad_()
+    labels = torch.randint(0, 128256, (4096,), device="cuda")
+    for _ in range(3):
+        Fn.cross_entropy(logits, labels).sum().backward()
+
+
+def adamw():
+    n = 64 * 1024 * 1024
+    p = bf(n, scale=0.02)
+    lo = torch.zeros(n, dtype=torch.int16, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 1e-3
+    ss = torch.zeros(1, device="cuda")
+    for step in range(1, 4):
+        Fn.grad_sumsq(g, ss)
+        Fn.adamw_step(p, lo, m, v, g, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step, sumsq=ss,
+                      max_norm=1.0)
+
+
+def router():
+    for E, k, sig, groups, gk in ((128, 8, False, 0, 0), (256, 8, True, 8, 4)):
+        logits = (torch.randn(65536, E, device="cuda") * 2).requires_grad_()
+        bias = torch.zeros(E, device="cuda") if sig else None
+        for _ in range(3):
+            p, ids, _ = Fn.router_topk(logits, bias, k, sigmoid=sig, norm=True, scale=1.0, groups=groups, group_topk=gk)
+            p.sum().backward()
+
+
+def paged():
+    lib = _lib.get_lib()
+    B, ctx, blk, nq, nkv, hd = 64, 2048, 128, 32, 8, 128
+    nblocks = B * ctx // blk
+    kc, vc = bf(nblocks, blk, nkv, hd), bf(nblocks, blk, nkv, hd)
+    q = bf(B, nq, hd)
+    out = torch.empty_like(q)
+    tables = torch.arange(nblocks, device="cuda", dtype=torch.int32).view(B, ctx // blk).contiguous()
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    for _ in range(3):
+        rc = lib.mfb_paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), lens.data_ptr(),
+                                            out.data_ptr(), B, nq, nkv, hd, blk, ctx // blk, hd ** -0.5, _lib.stream_ptr())
+        _lib.check(rc, "paged")
+
+
+def moe():
+    from mindformers_b200.parallel.layers.moe import MoELayer
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    cfg = TransformerConfig(num_layers=1, hidden_size=2048, num_attention_heads=16, ffn_hidden_size=8192, num_moe_experts=16,
+                            moe_router_topk=8, moe_ffn_hidden_size=768, params_dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    cfg.device = "cuda"
+    layer = MoELayer(cfg).train()
+    x = bf(16384, 2048).requires_grad_()
+    for _ in range(3):
+        y, _ = layer(x)
+        y.float().mean().backward()
+
+
+CASES = dict(gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, moe=moe)
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=sorted(CASES))
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    CASES[a.kernel]()
+    torch.cuda.synchronize()
+    print("done", a.kernel, "status", _lib.read_status())
