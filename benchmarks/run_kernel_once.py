@@ -104,10 +104,21 @@ def paged():
     out = torch.empty_like(q)
     tables = torch.arange(nblocks, device="cuda", dtype=torch.int32).view(B, ctx // blk).contiguous()
     lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
-    for _ in range(3):
+    splits = lib.mfb_paged_decode_splits(B, nkv, blk, ctx // blk)
+    scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits) // 4, device="cuda")
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for i in range(4):
+        if i == 1:
+            ev[0].record()
         rc = lib.mfb_paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), lens.data_ptr(),
-                                            out.data_ptr(), B, nq, nkv, hd, blk, ctx // blk, hd ** -0.5, _lib.stream_ptr())
+                                            out.data_ptr(), scratch.data_ptr(), splits, B, nq, nkv, hd, blk, ctx // blk,
+                                            hd ** -0.5, _lib.stream_ptr())
         _lib.check(rc, "paged")
+    ev[1].record()
+    torch.cuda.synchronize()
+    ms = ev[0].elapsed_time(ev[1]) / 3
+    kv_bytes = 2 * B * ctx * nkv * hd * 2
+    print(f"paged decode: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of KV ({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), splits {splits}")
 
 
 def moe():

@@ -92,12 +92,19 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
         out = torch.empty((T, nq, hd), dtype=q.dtype, device=q.device)
         if q.is_cuda and q.dtype == torch.bfloat16 and hd in (64, 128) and nq // nkv <= 16:
             qc = q.contiguous()
-            rc = _lib.get_lib().mfb_paged_decode_attention(
+            lib = _lib.get_lib()
+            max_blocks = cache.block_tables.shape[1]
+            splits = lib.mfb_paged_decode_splits(B, nkv, cache.block_size, max_blocks)
+            need = lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits)
+            scratch = getattr(cache, "_decode_scratch", None)
+            if scratch is None or scratch.numel() * 4 < need:
+                scratch = cache._decode_scratch = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
+            rc = lib.mfb_paged_decode_attention(
                 qc.data_ptr(), cache.key_cache[layer].data_ptr(), cache.value_cache[layer].data_ptr(),
-                cache.block_tables.data_ptr(), cache.context_lens.data_ptr(), out.data_ptr(), B, nq, nkv, hd,
-                cache.block_size, cache.block_tables.shape[1], float(scale), _lib.stream_ptr())
+                cache.block_tables.data_ptr(), cache.context_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), splits,
+                B, nq, nkv, hd, cache.block_size, max_blocks, float(scale), _lib.stream_ptr())
             _lib.check(rc, "mfb_paged_decode_attention")
-            _lib.count_launch()
+            _lib.count_launch(2)
             return out.view(T, nq * hd)
         lens = cache.context_lens.tolist()
         for b in range(B):

@@ -65,7 +65,10 @@ def _declare(lib):
     lib.mfb_flash_attn_bwd_scratch_bytes.restype = L
     sig("mfb_flash_attn_bwd", [P] * 10 + [I, I, I, I] + [L] * 8 + [I, F, P, P])
     sig("mfb_reshape_and_cache", [P, P, P, P, P, L, I, L, L, P])
-    sig("mfb_paged_decode_attention", [P, P, P, P, P, P, I, I, I, I, I, I, F, P])
+    sig("mfb_paged_decode_attention", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    sig("mfb_paged_decode_splits", [I, I, I, I])
+    lib.mfb_paged_decode_scratch_bytes.argtypes = [I, I, I, I]
+    lib.mfb_paged_decode_scratch_bytes.restype = L
     sig("mfb_gather_cache", [P, P, P, P, I, I, I, I, I, P])
     sig("mfb_dp_reduce_scratch", [])
     sig("mfb_dp_flag_words", [])

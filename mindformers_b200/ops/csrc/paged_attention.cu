@@ -35,112 +35,158 @@ __global__ void reshape_and_cache_kernel(const __nv_bfloat16* __restrict__ key, 
   }
 }
 
-constexpr int kPaTile = 128;
 constexpr int kPaMaxGroup = 16;
+constexpr int kPaWarps = 4;
+constexpr int kPaHeadsPerPass = 4;   // query heads kept in registers at a time
 
+// Split-KV decode attention ("flash decoding") on the CUDA cores; the kernel is bandwidth-bound.
+//   grid (splits, Hkv, B); CTA = 4 warps. A CTA owns keys [split * chunk, (split + 1) * chunk) of one sequence and
+//   one KV head. A key row of HD bf16 is read by HD/8 lanes with one 16-byte load each, so a warp covers
+//   32 / (HD/8) keys per instruction (2 for head dim 128, 4 for 64); every lane keeps the query slice, the running
+//   (max, sum) and the output slice of its 8 dimensions for up to four query heads. Lane groups never synchronise
+//   inside the loop: each keeps its own online softmax and the partial results are merged once, first inside the
+//   CTA through shared memory, then across splits by paged_combine_kernel.
 template <int HD>
-__global__ void __launch_bounds__(128)
-paged_decode_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq, HD]
-                    const __nv_bfloat16* __restrict__ key_cache, const __nv_bfloat16* __restrict__ value_cache,
-                    const int* __restrict__ block_tables,        // [B, max_blocks]
-                    const int* __restrict__ context_lens,        // [B] tokens to attend (including the new one)
-                    __nv_bfloat16* __restrict__ out,             // [B, Hq, HD]
-                    int Hq, int Hkv, int block_size, int max_blocks, float scale) {
-  const int b = blockIdx.x, kvh = blockIdx.y;
+__global__ void __launch_bounds__(kPaWarps * 32)
+paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq, HD]
+                          const __nv_bfloat16* __restrict__ key_cache, const __nv_bfloat16* __restrict__ value_cache,
+                          const int* __restrict__ block_tables,        // [B, max_blocks]
+                          const int* __restrict__ context_lens,        // [B]
+                          float* __restrict__ part_acc,                // [B, Hq, splits, HD]
+                          float* __restrict__ part_ml,                 // [B, Hq, splits, 2]  (max, sum)
+                          int Hq, int Hkv, int block_size, int max_blocks, int chunk, float scale) {
+  constexpr int LPK = HD / 8;          // lanes per key
+  constexpr int KPW = 32 / LPK;        // keys per warp instruction
+  constexpr int SLOTS = kPaWarps * KPW;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
   const int group = Hq / Hkv;
   const int ctx = context_lens[b];
+  const int k_begin = split * chunk;
+  const int k_end = min(ctx, k_begin + chunk);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int PER_LANE = HD / 32;  // 4 (hd 128) or 2 (hd 64)
-  __shared__ float s_q[kPaMaxGroup][HD];
-  __shared__ float s_p[kPaMaxGroup][kPaTile];
-  __shared__ float s_m[kPaMaxGroup], s_l[kPaMaxGroup], s_alpha[kPaMaxGroup];
-  for (int i = threadIdx.x; i < group * HD; i += 128) {
-    const int h = i / HD, d = i - h * HD;
-    s_q[h][d] = __bfloat162float(q[((size_t)b * Hq + kvh * group + h) * HD + d]) * scale;
-  }
-  if (threadIdx.x < group) { s_m[threadIdx.x] = -INFINITY; s_l[threadIdx.x] = 0.f; }
-  __syncthreads();
-  float acc[kPaMaxGroup];
-#pragma unroll
-  for (int h = 0; h < kPaMaxGroup; ++h) acc[h] = 0.f;
+  const int sub = lane / LPK, dl = lane % LPK;   // key slot within the warp, dimension slice
+  const int slot = warp * KPW + sub;
+  __shared__ float sh_acc[SLOTS][kPaHeadsPerPass][HD];
+  __shared__ float sh_m[SLOTS][kPaHeadsPerPass], sh_l[SLOTS][kPaHeadsPerPass];
   const int* table = block_tables + (size_t)b * max_blocks;
-  const size_t row = (size_t)Hkv * HD;  // elements per cached token
-  for (int t0 = 0; t0 < ctx; t0 += kPaTile) {
-    const int n = min(kPaTile, ctx - t0);
-    // ---- phase 1: scores, one warp per key ----
-    for (int k = warp; k < kPaTile; k += 4) {
-      if (k < n) {
-        const int tok = t0 + k;
-        const int blk = table[tok / block_size];
-        const __nv_bfloat16* kp = key_cache + ((size_t)blk * block_size + tok % block_size) * row + (size_t)kvh * HD + lane * PER_LANE;
-        float kv[PER_LANE];
-        if (PER_LANE == 4) {
-          const uint2 u = *reinterpret_cast<const uint2*>(kp);
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-          const float2 a = __bfloat1622float2(h2[0]), c = __bfloat1622float2(h2[1]);
-          kv[0] = a.x; kv[1] = a.y; kv[2 % PER_LANE] = c.x; kv[3 % PER_LANE] = c.y;
-        } else {
-          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kp));
-          kv[0] = a.x; kv[1] = a.y;
-        }
-        for (int h = 0; h < group; ++h) {
-          float d = 0.f;
+  const size_t row = (size_t)Hkv * HD;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  for (int h0 = 0; h0 < group; h0 += kPaHeadsPerPass) {
+    const int nh = min(kPaHeadsPerPass, group - h0);
+    float qr[kPaHeadsPerPass][8], acc[kPaHeadsPerPass][8], m[kPaHeadsPerPass], l[kPaHeadsPerPass];
 #pragma unroll
-          for (int i = 0; i < PER_LANE; ++i) d += kv[i] * s_q[h][lane * PER_LANE + i];
-          d = warp_sum(d);
-          if (lane == 0) s_p[h][k] = d;
+    for (int h = 0; h < kPaHeadsPerPass; ++h) {
+      m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
+      if (h < nh) {
+        const uint4 u = *reinterpret_cast<const uint4*>(q + ((size_t)b * Hq + kvh * group + h0 + h) * HD + dl * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          qr[h][2 * i] = f.x * scale_log2; qr[h][2 * i + 1] = f.y * scale_log2;
         }
-      } else if (lane == 0) {
-        for (int h = 0; h < group; ++h) s_p[h][k] = -INFINITY;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qr[h][i] = 0.f;
+      }
+    }
+    // the trip count is the same for every lane of a warp (the shuffles below name all 32 lanes); a lane group
+    // whose key lies beyond the end reads the last valid key and discards the result
+    auto fetch = [&](int t0, uint4& ku_, uint4& vu_) {
+      const int tk = (t0 + sub < k_end) ? t0 + sub : k_end - 1;
+      const int blk = table[tk / block_size];
+      const size_t base = ((size_t)blk * block_size + tk % block_size) * row + (size_t)kvh * HD + dl * 8;
+      ku_ = *reinterpret_cast<const uint4*>(key_cache + base);
+      vu_ = *reinterpret_cast<const uint4*>(value_cache + base);
+    };
+    constexpr int DEPTH = 3;           // key rows in flight per lane group: hides HBM latency at 16 warps per SM
+    uint4 kq[DEPTH], vq[DEPTH];
+    const int first = k_begin + warp * KPW;
+#pragma unroll
+    for (int i = 0; i < DEPTH; ++i)
+      if (first + i * SLOTS < k_end) fetch(first + i * SLOTS, kq[i], vq[i]);
+    for (int t0 = first; t0 < k_end; t0 += SLOTS) {
+      const bool valid = t0 + sub < k_end;
+      const uint4 ku = kq[0], vu = vq[0];
+#pragma unroll
+      for (int i = 0; i + 1 < DEPTH; ++i) { kq[i] = kq[i + 1]; vq[i] = vq[i + 1]; }
+      if (t0 + DEPTH * SLOTS < k_end) fetch(t0 + DEPTH * SLOTS, kq[DEPTH - 1], vq[DEPTH - 1]);
+      float kf[8], vf[8];
+      {
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&ku);
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vu);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __bfloat1622float2(k2[i]), c = __bfloat1622float2(v2[i]);
+          kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = c.x; vf[2 * i + 1] = c.y;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < kPaHeadsPerPass; ++h) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(kf[i], qr[h][i], d);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (valid && h < nh) {
+          const float m_new = fmaxf(m[h], d);
+          const float alpha = exp2f(m[h] - m_new);     // 0 on the first key (m = -inf)
+          const float pexp = exp2f(d - m_new);
+          l[h] = l[h] * alpha + pexp;
+          m[h] = m_new;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(acc[h][i], alpha, pexp * vf[i]);
+        }
+      }
+    }
+    // the lanes of a key group hold identical (m, l): merge the SLOTS streams of this CTA through shared memory
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < kPaHeadsPerPass; ++h) {
+      if (h < nh) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sh_acc[slot][h][dl * 8 + i] = acc[h][i];
+        if (dl == 0) { sh_m[slot][h] = m[h]; sh_l[slot][h] = l[h]; }
       }
     }
     __syncthreads();
-    // ---- online softmax update: warp w handles heads w, w+4, ... ----
-    for (int h = warp; h < group; h += 4) {
+    for (int idx = threadIdx.x; idx < nh * HD; idx += kPaWarps * 32) {
+      const int h = idx / HD, d = idx - h * HD;
       float mx = -INFINITY;
-      for (int k = lane; k < kPaTile; k += 32) mx = fmaxf(mx, s_p[h][k]);
-      mx = warp_max(mx);
-      const float m_old = s_m[h];
-      const float m_new = fmaxf(m_old, mx);
-      float sum = 0.f;
-      for (int k = lane; k < kPaTile; k += 32) {
-        const float p = __expf(s_p[h][k] - m_new);
-        s_p[h][k] = p;
-        sum += p;
+#pragma unroll
+      for (int s2 = 0; s2 < SLOTS; ++s2) mx = fmaxf(mx, sh_m[s2][h]);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int s2 = 0; s2 < SLOTS; ++s2) {
+        const float w = sh_m[s2][h] == -INFINITY ? 0.f : exp2f(sh_m[s2][h] - mx);
+        num += w * sh_acc[s2][h][d];
+        den += w * sh_l[s2][h];
       }
-      sum = warp_sum(sum);
-      if (lane == 0) {
-        const float alpha = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
-        s_alpha[h] = alpha;
-        s_l[h] = s_l[h] * alpha + sum;
-        s_m[h] = m_new;
-      }
+      const size_t o = ((size_t)b * Hq + kvh * group + h0 + h) * splits + split;
+      part_acc[o * HD + d] = num;
+      if (d == 0) { part_ml[o * 2] = mx; part_ml[o * 2 + 1] = den; }
     }
-    __syncthreads();
-    // ---- phase 2: acc[h] (dimension = thread) = acc*alpha + sum_k p[h][k] V[k][d] ----
-    for (int d = threadIdx.x; d < HD; d += 128) {
-#pragma unroll
-      for (int h = 0; h < kPaMaxGroup; ++h)
-        if (h < group) acc[h] *= s_alpha[h];
-      for (int k = 0; k < n; ++k) {
-        const int tok = t0 + k;
-        const int blk = table[tok / block_size];
-        const float v = __bfloat162float(value_cache[((size_t)blk * block_size + tok % block_size) * row + (size_t)kvh * HD + d]);
-#pragma unroll
-        for (int h = 0; h < kPaMaxGroup; ++h)
-          if (h < group) acc[h] += s_p[h][k] * v;
-      }
-    }
-    __syncthreads();
   }
-  for (int d = threadIdx.x; d < HD; d += 128) {
-#pragma unroll
-    for (int h = 0; h < kPaMaxGroup; ++h)
-      if (h < group) {
-        const float l = s_l[h];
-        out[((size_t)b * Hq + kvh * group + h) * HD + d] = __float2bfloat16(l > 0.f ? acc[h] / l : 0.f);
-      }
+}
+
+// out[b, h, :] = merge over splits of (acc, max, sum)
+template <int HD>
+__global__ void paged_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                     __nv_bfloat16* __restrict__ out, int splits) {
+  const size_t bh = blockIdx.x;
+  const int d = threadIdx.x;
+  float mx = -INFINITY;
+  for (int s2 = 0; s2 < splits; ++s2) mx = fmaxf(mx, part_ml[(bh * splits + s2) * 2]);
+  float num = 0.f, den = 0.f;
+  for (int s2 = 0; s2 < splits; ++s2) {
+    const float ms = part_ml[(bh * splits + s2) * 2];
+    const float w = ms == -INFINITY ? 0.f : exp2f(ms - mx);
+    num += w * part_acc[(bh * splits + s2) * HD + d];
+    den += w * part_ml[(bh * splits + s2) * 2 + 1];
   }
+  out[bh * HD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }
 
 // out[t, :] = cache[slot(t), :] gathered through the block table: token i of sequence b for i < lens[b],
@@ -178,23 +224,48 @@ int mfb_reshape_and_cache(const void* key, const void* value, void* key_cache, v
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
+// Number of key splits used for a batch of B sequences with at most max_blocks * block_size cached tokens.
+int mfb_paged_decode_splits(int B, int Hkv, int block_size, int max_blocks) {
+  const long long max_ctx = (long long)max_blocks * block_size;
+  const long long ctas = (long long)B * Hkv;
+  long long splits = (148 * 8 + ctas - 1) / ctas;           // aim at ~8 CTAs per SM
+  const long long by_len = (max_ctx + 255) / 256;           // at least 256 keys per split
+  if (splits > by_len) splits = by_len;
+  if (splits > 64) splits = 64;
+  if (splits < 1) splits = 1;
+  return (int)splits;
+}
+
+// fp32 scratch bytes for mfb_paged_decode_attention: partial outputs and (max, sum) per split.
+long long mfb_paged_decode_scratch_bytes(int B, int Hq, int hd, int splits) {
+  return (long long)B * Hq * splits * (hd + 2) * 4;
+}
+
 int mfb_paged_decode_attention(const void* q, const void* key_cache, const void* value_cache, const int* block_tables,
-                               const int* context_lens, void* out, int B, int Hq, int Hkv, int hd, int block_size,
-                               int max_blocks, float scale, cudaStream_t stream) {
-  if (Hq % Hkv || Hq / Hkv > kPaMaxGroup || (hd != 128 && hd != 64)) {
-    mfb_host::set_error("paged_decode_attention: unsupported Hq=%d Hkv=%d hd=%d", Hq, Hkv, hd);
+                               const int* context_lens, void* out, void* scratch, int splits, int B, int Hq, int Hkv,
+                               int hd, int block_size, int max_blocks, float scale, cudaStream_t stream) {
+  if (Hq % Hkv || Hq / Hkv > kPaMaxGroup || (hd != 128 && hd != 64) || splits < 1) {
+    mfb_host::set_error("paged_decode_attention: unsupported Hq=%d Hkv=%d hd=%d splits=%d", Hq, Hkv, hd, splits);
     return 1;
   }
   if (B <= 0) return 0;
-  dim3 grid(B, Hkv);
-  if (hd == 128)
-    paged_decode_kernel<128><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache,
-                                                       (const __nv_bfloat16*)value_cache, block_tables, context_lens,
-                                                       (__nv_bfloat16*)out, Hq, Hkv, block_size, max_blocks, scale);
-  else
-    paged_decode_kernel<64><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache,
-                                                      (const __nv_bfloat16*)value_cache, block_tables, context_lens,
-                                                      (__nv_bfloat16*)out, Hq, Hkv, block_size, max_blocks, scale);
+  const long long max_ctx = (long long)max_blocks * block_size;
+  int chunk = (int)((max_ctx + splits - 1) / splits);
+  chunk = (chunk + 63) / 64 * 64;
+  float* part_acc = reinterpret_cast<float*>(scratch);
+  float* part_ml = part_acc + (size_t)B * Hq * splits * hd;
+  dim3 grid(splits, Hkv, B);
+  if (hd == 128) {
+    paged_decode_split_kernel<128><<<grid, kPaWarps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache, block_tables,
+        context_lens, part_acc, part_ml, Hq, Hkv, block_size, max_blocks, chunk, scale);
+    paged_combine_kernel<128><<<B * Hq, 128, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
+  } else {
+    paged_decode_split_kernel<64><<<grid, kPaWarps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache, block_tables,
+        context_lens, part_acc, part_ml, Hq, Hkv, block_size, max_blocks, chunk, scale);
+    paged_combine_kernel<64><<<B * Hq, 64, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -340,3 +340,30 @@ def test_flash_attention_rectangular_fwd_bwd(Sq, Sk, off, causal):
     for a, b in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
         assert (a.float() - b).norm() / (b.norm() + 1e-9) < 3e-2
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("hd,nq,nkv,block", [(128, 32, 8, 128), (128, 8, 8, 16), (64, 16, 2, 32), (128, 16, 1, 64)])
+def test_paged_decode_attention_split_kv(hd, nq, nkv, block):
+    torch.manual_seed(hd + nq)
+    lib = _lib.get_lib()
+    lens = [1, 37, 700, 1300, 64]
+    B = len(lens)
+    max_blocks = (max(lens) + block - 1) // block + 1
+    nblocks = B * max_blocks + 3
+    kc = (torch.randn(nblocks, block, nkv, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nblocks, block, nkv, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(nblocks)[:B * max_blocks].to(torch.int32).view(B, max_blocks).cuda()
+    q = (torch.randn(B, nq, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    splits = lib.mfb_paged_decode_splits(B, nkv, block, max_blocks)
+    scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits) // 4, device="cuda")
+    rc = lib.mfb_paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), perm.data_ptr(), ctx.data_ptr(), out.data_ptr(),
+                                        scratch.data_ptr(), splits, B, nq, nkv, hd, block, max_blocks, hd ** -0.5, _lib.stream_ptr())
+    _lib.check(rc, "paged decode")
+    for b, n in enumerate(lens):
+        rows = perm[b].long()
+        kk = kc[rows].reshape(-1, nkv, hd)[:n]
+        vv = vc[rows].reshape(-1, nkv, hd)[:n]
+        ref = Fn.attention_reference(q[b:b + 1].unsqueeze(0).float(), kk.unsqueeze(0).float(), vv.unsqueeze(0).float(), causal=False)
+        assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
