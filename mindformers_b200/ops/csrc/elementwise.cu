@@ -90,6 +90,55 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
+// Vector form of rope_kernel: every thread rotates 8 pairs with 16-byte loads and stores.
+//   rotate-half  (INTERLEAVED = 0): elements [8c, 8c+8) of the first half pair with the same slice of the second half
+//   interleaved  (INTERLEAVED = 1): one 16-byte vector holds 4 pairs (2i, 2i+1); a thread takes two vectors
+// Needs rot % 16 == 0, 16-byte aligned rows (hd, token_stride multiples of 8).
+template <int INTERLEAVED>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                const int* __restrict__ positions, long long T, int n_heads, int hd, int rot, long long token_stride,
+                float sign, int seq_len) {
+  const int half = rot / 2;
+  const int chunks = half / 8;                      // 8 pairs per thread
+  const long long total = T * n_heads * chunks;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % chunks);
+    const long long th = i / chunks;
+    const int h = (int)(th % n_heads);
+    const long long t = th / n_heads;
+    const int pos = positions ? positions[t] : (int)(t % seq_len);
+    const float4* cp = reinterpret_cast<const float4*>(cosT + (long long)pos * half + c * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sinT + (long long)pos * half + c * 8);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x * sign, s0.y * sign, s0.z * sign, s0.w * sign, s1.x * sign, s1.y * sign, s1.z * sign, s1.w * sign};
+    __nv_bfloat16* base = x + t * token_stride + (long long)h * hd;
+    bf16x8* pa = reinterpret_cast<bf16x8*>(base + (INTERLEAVED ? c * 16 : c * 8));
+    bf16x8* pb = reinterpret_cast<bf16x8*>(base + (INTERLEAVED ? c * 16 + 8 : half + c * 8));
+    bf16x8 va = *pa, vb = *pb;
+    if (INTERLEAVED) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(va.v[j]);
+        va.v[j] = __floats2bfloat162_rn(f.x * cs[j] - f.y * sn[j], f.y * cs[j] + f.x * sn[j]);
+        float2 g = __bfloat1622float2(vb.v[j]);
+        vb.v[j] = __floats2bfloat162_rn(g.x * cs[4 + j] - g.y * sn[4 + j], g.y * cs[4 + j] + g.x * sn[4 + j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(va.v[j]), b = __bfloat1622float2(vb.v[j]);
+        va.v[j] = __floats2bfloat162_rn(a.x * cs[2 * j] - b.x * sn[2 * j], a.y * cs[2 * j + 1] - b.y * sn[2 * j + 1]);
+        vb.v[j] = __floats2bfloat162_rn(b.x * cs[2 * j] + a.x * sn[2 * j], b.y * cs[2 * j + 1] + a.y * sn[2 * j + 1]);
+      }
+    }
+    *pa = va;
+    *pb = vb;
+  }
+}
+
 // out[t, :] = table[ids[t] - vocab_start, :] (zero row when the id is outside this rank's shard)
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, long long T, int H, int vocab_start,
@@ -214,6 +263,19 @@ int mfb_rope(void* x, const float* cosT, const float* sinT, const int* positions
              cudaStream_t stream) {
   if (rot % 2 || rot > hd) { mfb_host::set_error("rope: rotary dim %d invalid for head dim %d", rot, hd); return 1; }
   if (T <= 0 || n_heads <= 0) return 0;
+  if (rot % 16 == 0 && hd % 8 == 0 && token_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(cosT) & 15) == 0 && (reinterpret_cast<uintptr_t>(sinT) & 15) == 0) {
+    const long long n = T * n_heads * (rot / 16);
+    const float sg = backward ? -1.f : 1.f;
+    const int sl = seq_len > 0 ? seq_len : 1;
+    if (interleaved)
+      rope_vec_kernel<1><<<ew_grid(n, 256), 256, 0, stream>>>((__nv_bfloat16*)x, cosT, sinT, positions, T, n_heads, hd,
+                                                             rot, token_stride, sg, sl);
+    else
+      rope_vec_kernel<0><<<ew_grid(n, 256), 256, 0, stream>>>((__nv_bfloat16*)x, cosT, sinT, positions, T, n_heads, hd,
+                                                             rot, token_stride, sg, sl);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   rope_kernel<<<ew_grid(T * n_heads * (rot / 2), 256), 256, 0, stream>>>(
       (__nv_bfloat16*)x, cosT, sinT, positions, T, n_heads, hd, rot, token_stride, interleaved,
       backward ? -1.f : 1.f, seq_len > 0 ? seq_len : 1);

@@ -426,7 +426,7 @@ __global__ void __launch_bounds__(kFaThreads, 1)
 flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                       const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
-                      const FaBwdArgs args) {
+                      const __grid_constant__ CUtensorMap tmdQ, const FaBwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -436,14 +436,16 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* sdO = sQ + kTileBytes;
   uint8_t* sP = sdO + kTileBytes;
   uint8_t* sdS = sP + kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + kTileBytes);
+  uint8_t* sdQ = sdS + kTileBytes;   // fp32 staging of half a dQ_part tile: two [128 rows][32 floats] swizzled images
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdQ + kTileBytes);
   uint64_t* kv_full = bars;        // K and V of this CTA arrived
   uint64_t* qdo_full = bars + 1;   // Q_i and dO_i arrived
-  uint64_t* qdo_empty = bars + 2;  // second MMA group done: Q/dO/P/dS buffers reusable, dQ_part ready
+  uint64_t* qdo_empty = bars + 2;  // dV and dK MMAs done: the Q / dO buffers are reusable
   uint64_t* sdp_full = bars + 3;   // S and dP ready in tensor memory
   uint64_t* pds_ready = bars + 4;  // P and dS written to shared memory (128 arrivals)
-  uint64_t* s_free = bars + 5;     // dQ_part consumed: S / dP regions reusable (128 arrivals)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* s_free = bars + 5;     // dQ_part consumed: the dP columns are reusable (128 arrivals)
+  uint64_t* dq_ready = bars + 6;   // dQ_part is complete in tensor memory
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -465,11 +467,13 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(sdp_full), 1);
     mbar_init(smem_u32(pds_ready), 128);
     mbar_init(smem_u32(s_free), 128);
+    mbar_init(smem_u32(dq_ready), 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
+    tma_prefetch_desc(&tmdQ);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), 512);
@@ -480,6 +484,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dV = tmem_base + 256, tmem_dK = tmem_base + 384;
+  // dQ_part shares the dP columns, so S of the next iteration can be issued while dQ_part is still being drained
+  const uint32_t tmem_dQ = tmem_dP;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -518,15 +524,18 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t ph = it & 1;
         ok = mbar_wait(smem_u32(qdo_full), ph, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
-        ok = mbar_wait(smem_u32(s_free), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
-        if (!ok) break;
         tc_fence_after();
+        // the S columns were last read by the softmax threads before pds_ready of the previous iteration
 #pragma unroll
         for (int k = 0; k < kHd / 16; ++k) {
           const uint32_t off = (k >> 2) * kSubBytes + (k & 3) * 32;
           umma_f16_ss(tmem_S, umma_desc_kmajor_sw128(qa + off), umma_desc_kmajor_sw128(ka + off), IDESC_KK,
                       k > 0 ? 1u : 0u);
         }
+        // the dP columns hold dQ_part of the previous iteration until the softmax threads have drained it
+        ok = mbar_wait(smem_u32(s_free), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kHd / 16; ++k) {
           const uint32_t off = (k >> 2) * kSubBytes + (k & 3) * 32;
@@ -549,13 +558,14 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           umma_f16_ss(tmem_dK, umma_desc_mnmajor_sw128(dsa + koff, kSubBytes),
                       umma_desc_mnmajor_sw128(qa + koff, kSubBytes), IDESC_MM, (it > 0 || k > 0) ? 1u : 0u);
         }
+        umma_commit(smem_u32(qdo_empty));          // Q and dO can be overwritten by the next loads
 #pragma unroll
         for (int k = 0; k < kTile / 16; ++k) {   // dQ_part = dS K, reduction over the 128 keys
           const uint64_t a_desc = umma_desc_kmajor_sw128(dsa + (k >> 2) * kSubBytes + (k & 3) * 32);
           const uint64_t b_desc = umma_desc_mnmajor_sw128(ka + k * 16 * 128, kSubBytes);
-          umma_f16_ss(tmem_S, a_desc, b_desc, IDESC_KM, k > 0 ? 1u : 0u);
+          umma_f16_ss(tmem_dQ, a_desc, b_desc, IDESC_KM, k > 0 ? 1u : 0u);
         }
-        umma_commit(smem_u32(qdo_empty));
+        umma_commit(smem_u32(dq_ready));
       }
     }
     __syncwarp();
@@ -607,30 +617,42 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(pds_ready));
-      // dQ_part lands in the S region once the second MMA group has completed
-      ok = mbar_wait(smem_u32(qdo_empty), ph, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
+      // dQ_part lands in the dP columns once the last MMA group has completed
+      ok = mbar_wait(smem_u32(dq_ready), ph, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
       ok = named_bar_and(2, 128, ok);
       if (!ok) break;
       tc_fence_after();
-      float* dq_row = args.dq_accum + (static_cast<size_t>(row_base + qi * kTile + row) * args.num_q_heads + hq) * kHd;
+      // dQ_part -> fp32 accumulator in global memory through the TMA reduce-add path: 64 columns at a time are
+      // staged in shared memory (swizzled 128-byte rows) and added by one bulk reduction per 32-column image,
+      // which costs the L2 one full-line reduction per row instead of eight 16-byte atomics per thread
+      const int qrow = row_base + qi * kTile;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_base + c * 32, r);
-        tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+        if (threadIdx.x == 64) tma_wait_group_read<0>();      // the previous reduction has read the staging buffer
+        named_bar_sync(1, 128);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + i * 4),
-                       "f"(__uint_as_float(r[i * 4])), "f"(__uint_as_float(r[i * 4 + 1])),
-                       "f"(__uint_as_float(r[i * 4 + 2])), "f"(__uint_as_float(r[i * 4 + 3]))
-                       : "memory");
+        for (int sub = 0; sub < 2; ++sub) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_dQ + lane_base + half * 64 + sub * 32, r);
+          tmem_ld_wait();
+          uint8_t* drow = sdQ + sub * (kTile * 128) + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            *reinterpret_cast<uint4*>(drow + ((ch ^ (row & 7)) << 4)) = make_uint4(r[ch * 4], r[ch * 4 + 1], r[ch * 4 + 2], r[ch * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          tma_reduce_add_2d(&tmdQ, smem_u32(sdQ), hq * kHd + half * 64, qrow);
+          tma_reduce_add_2d(&tmdQ, smem_u32(sdQ) + kTile * 128, hq * kHd + half * 64 + 32, qrow);
+          tma_commit_group();
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(s_free));
     }
     if (ok) {
-      // all MMAs have completed (last qdo_empty wait above); write dK and dV of this tile
+      // all MMAs have completed (last dq_ready wait above); write dK and dV of this tile
       const int krow = krow_base + kv_tile * kTile;
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tmem_dK : tmem_dV;
@@ -756,9 +778,11 @@ int mfb_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
     fa_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>((const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta,
                                                              B, S, Hq, do_ld, o_ld);
   }
-  CUtensorMap tQ, tK, tV, tdO, tdK, tdV;
+  CUtensorMap tQ, tK, tV, tdO, tdK, tdV, tdQ;
   int rc;
   const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((rc = mfb_host::make_tmap_2d(&tdQ, dq_accum, 4, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, T, (uint64_t)Hq * kHd,
+                                   (uint64_t)Hq * kHd, kTile, 32, true))) return 80 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tQ, q, 2, BF, T, (uint64_t)Hq * kHd, q_ld, kTile, 64))) return 20 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tK, k, 2, BF, Tk, (uint64_t)Hkv * kHd, k_ld, kTile, 64))) return 30 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tV, v, 2, BF, Tk, (uint64_t)Hkv * kHd, v_ld, kTile, 64))) return 40 + rc;
@@ -770,7 +794,7 @@ int mfb_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
   a.group = Hq / Hkv; a.causal = causal;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.lse = lse; a.delta = delta; a.dq_accum = dq_accum; a.status = status;
-  constexpr int SMEM = 6 * kTileBytes + 8 * 8 + 16 + 1024;
+  constexpr int SMEM = 7 * kTileBytes + 9 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
@@ -780,7 +804,7 @@ int mfb_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
     attr_set = true;
   }
   dim3 grid(Sk / kTile, Hkv, B);
-  flash_attn_bwd_kernel<<<grid, kFaThreads, SMEM, stream>>>(tQ, tK, tV, tdO, tdK, tdV, a);
+  flash_attn_bwd_kernel<<<grid, kFaThreads, SMEM, stream>>>(tQ, tK, tV, tdO, tdK, tdV, tdQ, a);
   {
     const long long total = T * (Hq * kHd / 4);
     long long blocks = (total + 255) / 256;
