@@ -134,7 +134,33 @@ def moe():
         y.float().mean().backward()
 
 
-CASES = dict(gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, moe=moe)
+def fp8():
+    for (M, N, K) in ((4096, 4096, 7168), (8192, 7168, 2048), (4096, 18432, 7168)):
+        x = bf(M, K, scale=0.7)
+        w = torch.randn(N, K, device="cuda") * 0.05
+        wq, sb = Fn.quantize_weight_128x128(w)
+        wb = w.to(torch.bfloat16)
+        xq, sa = Fn.quantize_act_1x128(x)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for i in range(6):
+            if i == 1:
+                ev[0].record()
+            Fn.fp8_gemm(xq, sa, wq, sb)
+        ev[1].record()
+        for i in range(6):
+            if i == 1:
+                ev[2].record()
+            Fn.gemm(x, wb)
+        ev[3].record()
+        torch.cuda.synchronize()
+        t8, t16 = ev[0].elapsed_time(ev[1]) / 5, ev[2].elapsed_time(ev[3]) / 5
+        fl = 2.0 * M * N * K
+        print(f"fp8 block-scaled {M}x{N}x{K}: {t8 * 1e3:.1f} us = {fl / t8 / 1e9:.0f} TFLOP/s; bf16 kernel {t16 * 1e3:.1f} us = {fl / t16 / 1e9:.0f} TFLOP/s")
+        for _ in range(2):
+            Fn.quantize_act_1x128(x)
+
+
+CASES = dict(fp8=fp8, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

@@ -88,6 +88,8 @@ def _declare(lib):
     sig("mfb_cp_gather", [I, I, I, I, I, L, I, P, P, P, P, P])
     sig("mfb_cp_reduce_scatter", [I, I, I, I, I, L, I, P, P, P, P, P])
     sig("mfb_cp_barrier", [I, I, I, I, P, P, P])
+    sig("mfb_gemm_fp8_blockscaled", [P, P, P, P, L, P, I, I, I, L, L, L, I, I, P, P, P, P])
+    sig("mfb_quant_act_1x128", [P, L, P, L, P, L, L, I, P])
     # optional entry points (present once their source file is part of the build)
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

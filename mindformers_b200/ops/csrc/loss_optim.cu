@@ -223,7 +223,57 @@ adamw_kernel(__nv_bfloat16* __restrict__ p, unsigned short* __restrict__ lo, flo
   }
   const float lr_t = a.lr / a.bc1;
   const float inv_bc2 = 1.f / a.bc2;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
+  const float decay = 1.f - a.lr * a.wd;
+  // main part: 8 elements per thread and iteration, every stream moved with 16-byte accesses
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(lo) | reinterpret_cast<uintptr_t>(m) |
+                        reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
+  const long long nvec = vec_ok ? (a.n >> 3) : 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long e0 = i * 8;
+    const uint4 pv = *reinterpret_cast<const uint4*>(p + e0);
+    const uint4 lv = *reinterpret_cast<const uint4*>(lo + e0);
+    const unsigned short* ph = reinterpret_cast<const unsigned short*>(&pv);
+    const unsigned short* pl = reinterpret_cast<const unsigned short*>(&lv);
+    float gg[8], mm[8], vv[8];
+    if (sizeof(GT) == 4) {
+      *reinterpret_cast<float4*>(gg) = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + e0);
+      *reinterpret_cast<float4*>(gg + 4) = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + e0 + 4);
+    } else {
+      const uint4 gv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g) + e0);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(g2[j]); gg[2 * j] = f.x; gg[2 * j + 1] = f.y; }
+    }
+    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + e0);
+    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + e0 + 4);
+    *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + e0);
+    *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + e0 + 4);
+    uint4 np, nl;
+    unsigned short* nph = reinterpret_cast<unsigned short*>(&np);
+    unsigned short* npl = reinterpret_cast<unsigned short*>(&nl);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float w = __uint_as_float(((uint32_t)ph[j] << 16) + (uint32_t)(int32_t)(int16_t)pl[j]);
+      const float gr = gg[j] * clip;
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gr;
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gr * gr;
+      if (e0 + j < a.decay_end) w *= decay;
+      w -= lr_t * mm[j] / (sqrtf(vv[j] * inv_bc2) + a.eps);
+      const uint32_t wb = __float_as_uint(w);
+      const uint32_t nhi = (wb + 0x8000u) >> 16;  // nearest bf16, ties up in magnitude
+      nph[j] = (unsigned short)nhi;
+      npl[j] = (unsigned short)((wb - (nhi << 16)) & 0xffffu);
+    }
+    *reinterpret_cast<float4*>(m + e0) = *reinterpret_cast<float4*>(mm);
+    *reinterpret_cast<float4*>(m + e0 + 4) = *reinterpret_cast<float4*>(mm + 4);
+    *reinterpret_cast<float4*>(v + e0) = *reinterpret_cast<float4*>(vv);
+    *reinterpret_cast<float4*>(v + e0 + 4) = *reinterpret_cast<float4*>(vv + 4);
+    *reinterpret_cast<uint4*>(p + e0) = np;
+    *reinterpret_cast<uint4*>(lo + e0) = nl;
+  }
+  // scalar tail (and the whole range when a pointer is not 16-byte aligned)
+  for (long long i = nvec * 8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n;
        i += (long long)gridDim.x * blockDim.x) {
     const uint32_t hi = __bfloat16_as_ushort(p[i]);
     const int32_t lov = (int32_t)(int16_t)lo[i];
@@ -232,12 +282,12 @@ adamw_kernel(__nv_bfloat16* __restrict__ p, unsigned short* __restrict__ lo, flo
     float mm = m[i], vv = v[i];
     mm = a.beta1 * mm + (1.f - a.beta1) * gr;
     vv = a.beta2 * vv + (1.f - a.beta2) * gr * gr;
-    if (i < a.decay_end) w *= (1.f - a.lr * a.wd);
+    if (i < a.decay_end) w *= decay;
     w -= lr_t * mm / (sqrtf(vv * inv_bc2) + a.eps);
     m[i] = mm;
     v[i] = vv;
     const uint32_t wb = __float_as_uint(w);
-    const uint32_t nhi = (wb + 0x8000u) >> 16;  // nearest bf16, ties up in magnitude
+    const uint32_t nhi = (wb + 0x8000u) >> 16;
     p[i] = __ushort_as_bfloat16((unsigned short)nhi);
     lo[i] = (unsigned short)((wb - (nhi << 16)) & 0xffffu);
   }
@@ -327,7 +377,7 @@ int mfb_adamw(void* p, void* lo, float* m, float* v, const void* g, int g_dtype,
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.bc1 = bc1; a.bc2 = bc2;
   a.max_norm = max_norm; a.skip_threshold = skip_threshold; a.grad_scale = grad_scale;
   a.n = n; a.decay_end = decay_end;
-  const int grid = flat_grid(n, 4);
+  const int grid = flat_grid(n, 8);
   if (g_dtype == 0)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)p, (unsigned short*)lo, m, v,
                                                           (const __nv_bfloat16*)g, sumsq, skipped, a);

@@ -592,6 +592,99 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
 
 
 # =================================================================================================
+# Block-scaled fp8 (e4m3) GEMM: 1 x 128 activation scales, 128 x 128 weight scales (DeepSeek-V3 checkpoints)
+# =================================================================================================
+FP8_MAX = 448.0
+
+
+def quantize_weight_128x128(w: torch.Tensor):
+    """``w [N, K]`` (or ``[G, N, K]``) → ``(wq e4m3, scale_inv fp32 [.., N/128, K/128])`` with ``w ≈ wq * scale_inv`` per block
+    (the layout of DeepSeek-V3 checkpoints: ``weight`` + ``weight_scale_inv``)."""
+    lead = w.shape[:-2]
+    N, K = w.shape[-2:]
+    if N % 128 or K % 128:
+        raise ValueError(f"weight [{N}, {K}] must be a multiple of 128 in both dimensions")
+    blocks = w.float().reshape(*lead, N // 128, 128, K // 128, 128)
+    amax = blocks.abs().amax(dim=(-3, -1), keepdim=True).clamp_min(1e-12)
+    scale = amax / FP8_MAX
+    q = (blocks / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).reshape(w.shape)
+    return q, scale.reshape(*lead, N // 128, K // 128).contiguous()
+
+
+def quantize_act_1x128(x: torch.Tensor):
+    """``x [T, K]`` bf16 → ``(xq e4m3 [T, K], sa fp32 [K/128, T_pad])`` with one scale per row and block of 128
+    (``T_pad`` = T rounded up to 128: the GEMM reads scales of whole row blocks)."""
+    T, K = x.shape
+    if K % 128:
+        raise ValueError(f"K={K} must be a multiple of 128")
+    Tp = (T + 127) // 128 * 128
+    if _on_gpu(x) and x.dtype == torch.bfloat16:
+        x = x.contiguous()
+        q = torch.empty(T, K, dtype=torch.float8_e4m3fn, device=x.device)
+        sa = torch.ones(K // 128, Tp, dtype=torch.float32, device=x.device)
+        rc = _lib.get_lib().mfb_quant_act_1x128(x.data_ptr(), x.stride(0), q.data_ptr(), K, sa.data_ptr(), Tp, T, K,
+                                                _lib.stream_ptr())
+        _lib.check(rc, "mfb_quant_act_1x128")
+        _lib.count_launch()
+        return q, sa
+    b = x.float().reshape(T, K // 128, 128)
+    amax = b.abs().amax(-1, keepdim=True)
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (b / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).reshape(T, K)
+    sa = torch.ones(K // 128, Tp, dtype=torch.float32, device=x.device)
+    sa[:, :T] = scale.squeeze(-1).t()
+    return q, sa
+
+
+def fp8_gemm_reference(xq, sa, wq, sb):
+    """fp32 oracle: de-quantise both operands block by block and multiply. ``wq [N, K]``, ``sb [N/128, K/128]``."""
+    T, K = xq.shape
+    x = xq.float().reshape(T, K // 128, 128) * sa[:, :T].t().unsqueeze(-1)
+    N = wq.shape[0]
+    w = wq.float().reshape(N // 128, 128, K // 128, 128) * sb.reshape(N // 128, 1, K // 128, 1)
+    return x.reshape(T, K) @ w.reshape(N, K).t()
+
+
+def fp8_gemm(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, *, block_group=None, num_blocks=None):
+    """``y [T, N] (bf16) = dequant(xq, sa) @ dequant(wq, sb)^T``. Grouped form: ``wq [G, N, K]``, ``sb [G, N/128, K/128]``,
+    rows of ``xq`` sorted by expert in 128-row blocks (``block_group`` / ``num_blocks`` as for ``grouped_gemm``)."""
+    T, K = xq.shape
+    grouped = wq.dim() == 3
+    G = wq.shape[0] if grouped else 1
+    N = wq.shape[-2]
+    if not _on_gpu(xq):
+        if not grouped:
+            return fp8_gemm_reference(xq, sa, wq, sb).to(torch.bfloat16)
+        out = torch.zeros(T, N, dtype=torch.bfloat16, device=xq.device)
+        nb = int(num_blocks.item())
+        for i, g in enumerate(block_group[:nb].tolist()):
+            rows = slice(i * 128, (i + 1) * 128)
+            out[rows] = fp8_gemm_reference(xq[rows], sa[:, rows], wq[g], sb[g]).to(torch.bfloat16)
+        return out
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=xq.device)
+    st = _lib.status_word(xq.device)
+    w2 = wq.reshape(G * N, K)
+    rc = _lib.get_lib().mfb_gemm_fp8_blockscaled(
+        xq.data_ptr(), w2.data_ptr(), out.data_ptr(), sa.data_ptr(), sa.stride(0), sb.contiguous().data_ptr(), T, N, K,
+        xq.stride(0), w2.stride(0), out.stride(0), 1 if grouped else 0, G, _lib.ptr(block_group), _lib.ptr(num_blocks),
+        st.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_gemm_fp8_blockscaled")
+    _lib.count_launch()
+    return out
+
+
+def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inference linear layer on block-scaled fp8 weights: activations are quantised on the fly (1 x 128 blocks)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    xq, sa = quantize_act_1x128(x2.to(torch.bfloat16))
+    y = fp8_gemm(xq, sa, wq, sb)
+    if bias is not None:
+        y = y + bias
+    return y.reshape(*shape[:-1], wq.shape[-2])
+
+
+# =================================================================================================
 # MoE router
 # =================================================================================================
 def router_topk_reference(logits, bias, k, sigmoid, norm, scale, groups=0, group_topk=0):

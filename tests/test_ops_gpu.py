@@ -367,3 +367,44 @@ def test_paged_decode_attention_split_kv(hd, nq, nkv, block):
         vv = vc[rows].reshape(-1, nkv, hd)[:n]
         ref = Fn.attention_reference(q[b:b + 1].unsqueeze(0).float(), kk.unsqueeze(0).float(), vv.unsqueeze(0).float(), causal=False)
         assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
+
+
+@pytest.mark.parametrize("T,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 2048, 7168)])
+def test_fp8_blockscaled_gemm_dense(T, N, K):
+    torch.manual_seed(T + N)
+    x = (torch.randn(T, K, device="cuda") * 0.7).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    wq, sb = Fn.quantize_weight_128x128(w)
+    xq, sa = Fn.quantize_act_1x128(x)
+    # the activation quantiser matches the PyTorch one
+    xq_ref, sa_ref = Fn.quantize_act_1x128(x.cpu())
+    assert torch.allclose(sa[:, :T].cpu(), sa_ref[:, :T], rtol=1e-6)
+    assert (xq.float().cpu() - xq_ref.float()).abs().max() <= 32.0   # at most one e4m3 step at the top of the range
+    y = Fn.fp8_gemm(xq, sa, wq, sb)
+    ref = Fn.fp8_gemm_reference(xq, sa, wq, sb)
+    assert (y.float() - ref).norm() / ref.norm() < 5e-3
+    full = x.float() @ w.t()
+    assert (y.float() - full).norm() / full.norm() < 6e-2     # quantisation error of the format itself
+    assert _lib.read_status() == 0
+
+
+def test_fp8_blockscaled_gemm_grouped():
+    torch.manual_seed(9)
+    G, N, K = 4, 256, 512
+    blocks = [0, 0, 2, 3, 3, 3]            # expert of each 128-row block (expert 1 has no tokens)
+    T = len(blocks) * 128
+    x = (torch.randn(T, K, device="cuda") * 0.7).to(torch.bfloat16)
+    w = torch.randn(G, N, K, device="cuda") * 0.05
+    wq, sb = Fn.quantize_weight_128x128(w)
+    xq, sa = Fn.quantize_act_1x128(x)
+    bg = torch.tensor(blocks + [0, 0], dtype=torch.int32, device="cuda")
+    nb = torch.tensor([len(blocks)], dtype=torch.int32, device="cuda")
+    xq_pad = torch.cat([xq, torch.zeros(256, K, dtype=xq.dtype, device="cuda")])
+    sa_pad = torch.ones(K // 128, T + 256, device="cuda")
+    sa_pad[:, :T] = sa[:, :T]
+    y = Fn.fp8_gemm(xq_pad, sa_pad, wq, sb, block_group=bg, num_blocks=nb)
+    for i, g in enumerate(blocks):
+        rows = slice(i * 128, (i + 1) * 128)
+        ref = Fn.fp8_gemm_reference(xq[rows], sa[:, rows], wq[g], sb[g])
+        assert (y[rows].float() - ref).norm() / ref.norm() < 5e-3, i
+    assert _lib.read_status() == 0
