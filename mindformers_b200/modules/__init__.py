@@ -1,0 +1,8 @@
+"""Building blocks of the older ("legacy") model stack and small shared utilities: plain layers, activations, rotary
+frequency managers with context-extension methods, ALiBi, capacity-based MoE, sequence-pipeline splitting, weight-only
+and W8A8 quantisers, RNG tracker."""
+from .activation import GELU, FastGelu, SiLU, SwiGLU, get_activation
+from .layers import AlibiTensor, Dropout, FreqsMgr, LayerNorm, Linear, LowerTriangularMaskWithDynamic
+from .moe_legacy import MoEConfig, MoEV2, TopkRouterV2
+from .seq_pipe import SequenceSplit
+from .rng import CudaRNGStatesTracker, get_rng_tracker, model_parallel_manual_seed

@@ -681,7 +681,7 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, bias: Option
     y = fp8_gemm(xq, sa, wq, sb)
     if bias is not None:
         y = y + bias
-    return y.reshape(*shape[:-1], wq.shape[-2])
+    return y.reshape(*shape[:-1], wq.shape[-2]).to(x.dtype)
 
 
 # =================================================================================================

@@ -1,0 +1,102 @@
+"""Legacy building blocks, quantisers, loss scale, RNG tracker, sequence-pipeline split (CPU)."""
+import math
+
+import torch
+
+from mindformers_b200.core.loss_scale import AdaptiveLossScaleUpdateCell, DynamicLossScaleUpdateCell
+from mindformers_b200.modules import (AlibiTensor, FreqsMgr, LayerNorm, Linear, MoEConfig, MoEV2, SequenceSplit,
+                                      get_activation, get_rng_tracker, model_parallel_manual_seed)
+from mindformers_b200.modules import quantizers as Q
+
+
+def test_freqs_mgr_extension_methods():
+    base = FreqsMgr(64, 128, 128, theta=10000.0)
+    cos, sin = base()
+    assert cos.shape == (128, 64) and torch.allclose(cos[0], torch.ones(64))
+    pi = FreqsMgr(64, 128, 128, scaling_factor=4.0, extend_method="PI")
+    assert torch.allclose(pi.freqs_cos[4], base.freqs_cos[1], atol=1e-6)        # positions shrink by the factor
+    ntk = FreqsMgr(64, 128, 128, scaling_factor=4.0, extend_method="NTK")
+    assert ntk.freqs_sin[1, 31] < base.freqs_sin[1, 31]                          # lowest frequency slowed down
+    l3 = FreqsMgr(128, 64, 64, theta=500000.0, scaling_factor=8.0, extend_method="LLAMA3", original_max_position=8192)
+    plain = FreqsMgr(128, 64, 64, theta=500000.0)
+    assert torch.allclose(l3.freqs_cos[:, 0], plain.freqs_cos[:, 0])             # high frequencies untouched
+    assert not torch.allclose(l3.freqs_sin[:, 63], plain.freqs_sin[:, 63])
+    yarn = FreqsMgr(64, 64, 64, scaling_factor=4.0, extend_method="YARN", original_max_position=32)
+    assert yarn.mscale > 1.0
+
+
+def test_linear_layernorm_alibi_activation():
+    torch.manual_seed(0)
+    lin = Linear(16, 8, activation="gelu", compute_dtype=torch.float32)
+    x = torch.randn(4, 16)
+    want = torch.nn.functional.gelu(x @ lin.weight.t() + lin.bias, approximate="tanh")
+    assert torch.allclose(lin(x), want, atol=1e-5)
+    ex = Linear(16, 8, expert_num=3, compute_dtype=torch.float32)
+    assert ex(torch.randn(3, 5, 16)).shape == (3, 5, 8)
+    ln = LayerNorm(16)
+    assert torch.allclose(ln(x).mean(-1), torch.zeros(4), atol=1e-5)
+    bias = AlibiTensor(8, 4)(torch.ones(2, 8))
+    assert bias.shape == (2, 4, 1, 8) and bias[0, 0, 0, 7] > bias[0, 0, 0, 0]
+    assert get_activation("swiglu")(torch.randn(3, 8)).shape == (3, 4)
+
+
+def test_capacity_moe_drops_and_aux():
+    torch.manual_seed(1)
+    cfg = MoEConfig(expert_num=4, capacity_factor=0.5, num_experts_chosen=2, moe_intermediate_size=16, aux_loss_types=["expert", "device"],
+                    aux_loss_factors=[0.01, 0.01], devices_per_group=2, shared_expert_num=1)
+    moe = MoEV2(32, 64, cfg)
+    x = torch.randn(2, 16, 32, requires_grad=True)
+    y, aux = moe(x)
+    assert y.shape == x.shape and aux.item() > 0
+    assert 0.0 < float(moe.router.last_drop_rate) < 1.0          # capacity 0.5 must drop something
+    (y.sum() + aux).backward()
+    assert moe.w1.grad is not None and x.grad is not None
+    cfg2 = MoEConfig(expert_num=4, capacity_factor=8.0, num_experts_chosen=2, moe_intermediate_size=16, enable_sdrop=True)
+    moe2 = MoEV2(32, 64, cfg2)
+    moe2(x)
+    assert float(moe2.router.last_drop_rate) == 0.0
+
+
+def test_quantizers_roundtrip_and_model():
+    torch.manual_seed(2)
+    w = torch.randn(64, 128)
+    for dt, tol in (("int8", 0.01), ("int4", 0.15)):
+        q, s = Q.quantize_weight_rtn(w, dt, group_size=32)
+        assert ((Q.dequantize_weight(q, s, torch.float32) - w).norm() / w.norm()) < tol
+    kq, ks = Q.quantize_kv_int8(torch.randn(4, 2, 64))
+    assert kq.dtype == torch.int8 and ks.shape == (4, 2, 1)
+    from mindformers_b200.models import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=64, hidden_size=128, intermediate_size=256, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, params_dtype="float32", compute_dtype="float32")
+    m = LlamaForCausalLM(cfg, device="cpu").eval()
+    ids = torch.randint(0, 64, (1, 16))
+    ref = m(ids)
+    stats = Q.collect_activation_absmax(m, [ids], lambda mod, b: mod(b))
+    n = Q.quantize_model(m, Q.SmoothQuantConfig(), stats)
+    assert n == 4
+    got = m(ids)
+    assert (got - ref).norm() / ref.norm() < 0.08
+    m2 = LlamaForCausalLM(cfg, device="cpu").eval()
+    ref2 = m2(ids)
+    assert Q.quantize_model(m2, Q.Fp8BlockConfig()) == 4
+    assert (m2(ids) - ref2).norm() / ref2.norm() < 0.1
+
+
+def test_loss_scale_rng_and_sequence_split():
+    ls = DynamicLossScaleUpdateCell(1024, 2, 3)
+    assert ls.update(True) == 512 and [ls.update(False) for _ in range(3)][-1] == 1024
+    ad = AdaptiveLossScaleUpdateCell(1024, 2, 100, max_scale_window=100, min_scale_window=25)
+    ad.update(True)
+    assert ad.window == 50
+    model_parallel_manual_seed(5)
+    tr = get_rng_tracker()
+    with tr.fork():
+        a = torch.rand(3)
+    with tr.fork():
+        b = torch.rand(3)
+    assert not torch.equal(a, b)
+    model_parallel_manual_seed(5)
+    with get_rng_tracker().fork():
+        assert torch.equal(torch.rand(3), a)
+    parts = SequenceSplit(4).split({"input_ids": torch.arange(32).view(2, 16), "labels": torch.arange(32).view(2, 16)})
+    assert len(parts) == 4 and parts[2]["input_ids"].shape == (2, 4) and parts[2]["position_ids"][0, 0] == 8
