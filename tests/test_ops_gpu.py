@@ -408,3 +408,26 @@ def test_fp8_blockscaled_gemm_grouped():
         ref = Fn.fp8_gemm_reference(xq[rows], sa[:, rows], wq[g], sb[g])
         assert (y[rows].float() - ref).norm() / ref.norm() < 5e-3, i
     assert _lib.read_status() == 0
+
+
+def test_bounded_peer_wait_reports_status_instead_of_hanging():
+    """A cross-rank barrier whose peer never arrives: the kernel gives up after its time limit, records the timeout in
+    the status word and returns; the context stays usable."""
+    import ctypes
+    import time
+    lib = _lib.get_lib()
+    words = lib.mfb_moe_flag_words()
+    mine = torch.zeros(words, dtype=torch.int32, device="cuda")
+    absent = torch.zeros(words, dtype=torch.int32, device="cuda")     # stands for a peer that never launches
+    flags = (ctypes.c_longlong * 2)(mine.data_ptr(), absent.data_ptr())
+    st = _lib.status_word("cuda")
+    st.zero_()
+    t0 = time.time()
+    rc = lib.mfb_moe_barrier(2, 0, 1, 1, flags, st.data_ptr(), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert int(st.item()) == 4                   # kStatusPeerFlagTimeout
+    assert 1.0 < waited < 10.0
+    st.zero_()
+    assert torch.ones(4, device="cuda").sum().item() == 4.0     # the device still answers
