@@ -52,7 +52,7 @@ class GenerationMixin:
     # ---- one model call -------------------------------------------------------------------------------
     @torch.no_grad()
     def _forward_step(self, tokens: List[List[int]], starts: List[int], ctx: KVCacheContext, tables: BlockTables,
-                      prefill: bool, active: Optional[List[bool]] = None) -> torch.Tensor:
+                      prefill: bool, active: Optional[List[bool]] = None, all_logits: bool = False) -> torch.Tensor:
         """Run the model on the new ``tokens`` of every sequence (positions start at ``starts``).
         Returns logits ``[B, V]`` of the last new token of each sequence."""
         device = next(self.parameters()).device
@@ -65,9 +65,13 @@ class GenerationMixin:
         pos = torch.tensor([s + i for t, s in zip(tokens, starts) for i in range(len(t))], dtype=torch.int64, device=device)
         ctx.set_step(is_prefill=prefill, block_tables=table, slot_mapping=slots, context_lens=tables.context_lens(),
                      q_seq_lens=lens, device=device)
+        if all_logits:       # draft verification: the logits of every new token are needed
+            ctx.last_token_index = torch.arange(int(flat.numel()), dtype=torch.int64, device=device)
         meta = AttnMeta(batch=1, seq_len=int(flat.numel()), positions=pos, cache=ctx)
         logits = self.model(flat.unsqueeze(0), attn_meta=meta)
-        if not prefill:
+        if all_logits:
+            pass
+        elif not prefill:
             pass  # decode: one row per sequence already
         elif logits.shape[0] != len(tokens):
             logits = logits.index_select(0, ctx.last_token_index)
@@ -97,6 +101,10 @@ class GenerationMixin:
             raise ValueError(f"max_length ({max_len}) must exceed the prompt length")
         if gcfg.num_beams > 1:
             return self._beam_search(prompts, gcfg, max_len)
+        plugin = kwargs.get("parallel_decoding") or getattr(gcfg, "parallel_decoding", None)
+        if plugin:
+            from .parallel_decoding import get_plugin
+            return get_plugin(plugin)(self, prompts, gcfg, max_len, **{k: v for k, v in kwargs.items() if k in ("draft_len", "max_ngram")})
         device = next(self.parameters()).device
         gen = torch.Generator(device=device)
         if seed is not None or gcfg.seed is not None:

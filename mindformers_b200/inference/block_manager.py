@@ -48,6 +48,10 @@ class CacheEngine:
         self.pool.release(self.blocks)
         self.blocks, self.num_tokens = [], 0
 
+    def rollback(self, num_tokens: int):
+        """Forget the last ``num_tokens`` cached tokens (rejected draft tokens); their slots are rewritten later."""
+        self.num_tokens = max(0, self.num_tokens - int(num_tokens))
+
 
 class BlockTables:
     """Block tables and slot mappings of a batch."""

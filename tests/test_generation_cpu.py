@@ -83,3 +83,18 @@ def test_save_and_load_pretrained_roundtrip(tmp_path):
                        model.model.decoder.layers[0].self_attention.linear_qkv.weight)
     tok = ByteTokenizer()
     assert tok.decode(tok.encode("héllo")) == "héllo"
+
+
+def test_parallel_decoding_matches_greedy():
+    model = _tiny()
+    prompt = [7, 8, 9, 7, 8, 9, 7, 8, 9, 7, 8]            # repetitive: n-gram drafts get accepted
+    want = model.generate([prompt, [3, 4, 5]], max_new_tokens=12, do_sample=False)
+    for plugin in ("la", "memory_decoding"):
+        got = model.generate([prompt, [3, 4, 5]], max_new_tokens=12, do_sample=False, parallel_decoding=plugin)
+        assert got == want, plugin
+        assert model.last_generation_stats["model_calls"] <= 13
+    shared = [11, 12, 13, 14, 15, 16, 17, 18, 19]
+    a, b = shared + [40, 41], shared + [50]
+    want = model.generate([a, b], max_new_tokens=5, do_sample=False)
+    got = model.generate([a, b], max_new_tokens=5, do_sample=False, parallel_decoding="prefix_cache")
+    assert got == want and model.last_generation_stats["shared_prefix_tokens"] == 8
