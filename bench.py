@@ -85,7 +85,17 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a valid bench)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=None)
+    ap.add_argument("--config", default="llama8b", choices=["llama8b", "qwen3_moe", "qwen25_cp"],
+                    help="llama8b: the headline (Llama-3.1-8B, TP2+SP x DP); qwen3_moe: Qwen3-30B-A3B, expert parallel = N, "
+                         "micro batch 1; qwen25_cp: Qwen2.5-7B, one sequence of --seq-len tokens, context parallel = N")
     args = ap.parse_args()
+    if args.config == "qwen3_moe" and args.model == "llama3_1_8b":
+        args.model = "qwen3_30b_a3b"
+    if args.config == "qwen25_cp" and args.model == "llama3_1_8b":
+        args.model = "qwen2_5_7b"
+        if args.seq_len == 4096:
+            args.seq_len = 131072
+        args.seqs_per_gpu = 1
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -115,24 +125,54 @@ def main():
         fused_comm.set_enabled(False)
 
     tp = args.tp or (2 if world >= 2 else 1)
-    ps.initialize_model_parallel(tensor_model_parallel_size=tp)
-    dp = world // tp
+    cp = ep = 1
+    if args.config == "qwen3_moe":
+        tp, ep = args.tp or 1, world
+    elif args.config == "qwen25_cp":
+        tp, cp = args.tp or 1, world
+    ps.initialize_model_parallel(tensor_model_parallel_size=tp, context_parallel_size=cp, expert_model_parallel_size=ep,
+                                 expert_tensor_parallel_size=1 if ep > 1 else None)
+    dp = world // (tp * cp)
     torch.manual_seed(1234)
     preset = get_preset(args.model)
     if args.layers:
         preset["num_hidden_layers"] = args.layers
+    parallel = dict(tensor_model_parallel_size=tp, sequence_parallel=tp > 1)
+    extra = {}
+    if ep > 1:
+        parallel.update(expert_model_parallel_size=ep, expert_tensor_parallel_size=1)
+    if cp > 1:
+        parallel.update(context_parallel_size=cp)
+        extra.update(cp_comm_type="p2p", cp_zigzag=True)
     engine = TrainingEngine.from_model_config(
-        preset, parallel=dict(tensor_model_parallel_size=tp, sequence_parallel=tp > 1), seq_length=args.seq_len,
-        learning_rate=1e-4, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0, micro_batch_size=1)
-    seqs_local = args.seqs_per_gpu * world // dp          # sequences this data-parallel rank handles per step
+        preset, parallel=parallel, seq_length=args.seq_len, learning_rate=1e-4, betas=(0.9, 0.95), weight_decay=0.1,
+        max_grad_norm=1.0, micro_batch_size=1, **extra)
     S, V = args.seq_len, preset["vocab_size"]
-    g = torch.Generator().manual_seed(100 + ps.get_data_parallel_rank())
     n_batches = args.warmup + args.steps
-    host = [torch.randint(0, V, (seqs_local, S + 1), generator=g, dtype=torch.int64).pin_memory() for _ in range(2)]
+    if cp > 1:
+        # one sequence of S tokens over the context-parallel group, zig-zag chunks (rank r: chunks r and 2cp-1-r)
+        from mindformers_b200.parallel.fused_cp import zigzag_slice
+        seqs_local = args.seqs_per_gpu
+        g = torch.Generator().manual_seed(100 + ps.get_data_parallel_rank())
+        r = ps.get_context_parallel_rank()
+        host = []
+        for _ in range(2):
+            full = torch.randint(0, V, (seqs_local, S + 1), generator=g, dtype=torch.int64)
+            pos = torch.arange(S).unsqueeze(0).expand(seqs_local, S)
+            host.append({"input_ids": zigzag_slice(full[:, :-1], cp, r).contiguous().pin_memory(),
+                         "labels": zigzag_slice(full[:, 1:], cp, r).contiguous().pin_memory(),
+                         "position_ids": zigzag_slice(pos, cp, r).contiguous().pin_memory()})
 
-    def host_batch(i):
-        t = host[i % 2]
-        return {"input_ids": t[:, :-1], "labels": t[:, 1:]}
+        def host_batch(i):
+            return host[i % 2]
+    else:
+        seqs_local = args.seqs_per_gpu * world // dp          # sequences this data-parallel rank handles per step
+        g = torch.Generator().manual_seed(100 + ps.get_data_parallel_rank())
+        host = [torch.randint(0, V, (seqs_local, S + 1), generator=g, dtype=torch.int64).pin_memory() for _ in range(2)]
+
+        def host_batch(i):
+            t = host[i % 2]
+            return {"input_ids": t[:, :-1], "labels": t[:, 1:]}
 
     dev_batches = [{k: v.cuda().contiguous() for k, v in host_batch(i).items()} for i in range(2)]
 
@@ -165,7 +205,7 @@ def main():
         out = engine.train_step_device(dev_batches[i % 2])
     total_ms, clocks, launches, out = timed(lambda i: engine.train_step_device(dev_batches[i % 2]), args.steps)
     loss_val = float(out["loss"])
-    tokens_per_step = args.seqs_per_gpu * world * S
+    tokens_per_step = (args.seqs_per_gpu * S) if cp > 1 else args.seqs_per_gpu * world * S
     ms_per_step = total_ms / args.steps
     value = tokens_per_step / (ms_per_step / 1e3)
 
@@ -186,9 +226,10 @@ def main():
             "scaling": "weak", "vs_baseline": value / (BASELINE_TOKENS_PER_S_PER_DEVICE * world),
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": args.impl,
-            "config": {"model": "Llama-3.1-8B" if args.model == "llama3_1_8b" and not args.layers else f"{args.model}(layers={args.layers})",
-                       "global_batch": args.seqs_per_gpu * world, "seq_len": S,
-                       "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + f" dp{dp} distributed-optimizer",
+            "config": {"model": ("Llama-3.1-8B" if args.model == "llama3_1_8b" else args.model) if not args.layers else f"{args.model}(layers={args.layers})",
+                       "global_batch": args.seqs_per_gpu if cp > 1 else args.seqs_per_gpu * world, "seq_len": S,
+                       "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + (f" cp{cp}(zig-zag)" if cp > 1 else "")
+                                      + (f" ep{ep}" if ep > 1 else "") + f" dp{dp} distributed-optimizer",
                        "micro_batch": 1, "grad_accum_dtype": "fp32",
                        "l2": "working set (weights + activations, >100 GB) far exceeds the 126 MB L2 every step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,

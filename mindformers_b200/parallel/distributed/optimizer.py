@@ -125,8 +125,8 @@ class DistributedOptimizer:
         self._dp_scratch = torch.zeros(lib.mfb_dp_reduce_scratch(), dtype=torch.float32, device=dev)
         for name, sh in self.shards.items():
             sh.fused = False
-            if sh.world <= 1 or f"{name}.grad" not in self._symm:
-                continue
+            if sh.world <= 1 or not sh.bf16 or f"{name}.grad" not in self._symm:
+                continue      # fp32 parameter buffers (router weights) keep the NCCL reduce-scatter / all-gather
             flags = symm_mem.allocate(f"dpopt.{name}.flags.{id(self)}", words * 4, sh.group, dev)
             flags.tensor.zero_()
             arr = ctypes.c_longlong * sh.world
