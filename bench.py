@@ -85,6 +85,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a valid bench)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=None)
+    ap.add_argument("--recompute", type=int, default=0, help="recompute the activations of the first N layers in backward")
     ap.add_argument("--config", default="llama8b", choices=["llama8b", "qwen3_moe", "qwen25_cp"],
                     help="llama8b: the headline (Llama-3.1-8B, TP2+SP x DP); qwen3_moe: Qwen3-30B-A3B, expert parallel = N, "
                          "micro batch 1; qwen25_cp: Qwen2.5-7B, one sequence of --seq-len tokens, context parallel = N")
@@ -146,7 +147,8 @@ def main():
         extra.update(cp_comm_type="p2p", cp_zigzag=True)
     engine = TrainingEngine.from_model_config(
         preset, parallel=parallel, seq_length=args.seq_len, learning_rate=1e-4, betas=(0.9, 0.95), weight_decay=0.1,
-        max_grad_norm=1.0, micro_batch_size=1, **extra)
+        max_grad_norm=1.0, micro_batch_size=1,
+        recompute=([args.recompute] if args.recompute else False), **extra)
     S, V = args.seq_len, preset["vocab_size"]
     n_batches = args.warmup + args.steps
     if cp > 1:
@@ -230,7 +232,7 @@ def main():
                        "global_batch": args.seqs_per_gpu if cp > 1 else args.seqs_per_gpu * world, "seq_len": S,
                        "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + (f" cp{cp}(zig-zag)" if cp > 1 else "")
                                       + (f" ep{ep}" if ep > 1 else "") + f" dp{dp} distributed-optimizer",
-                       "micro_batch": 1, "grad_accum_dtype": "fp32",
+                       "micro_batch": 1, "grad_accum_dtype": "fp32", "recompute_layers": args.recompute,
                        "l2": "working set (weights + activations, >100 GB) far exceeds the 126 MB L2 every step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
             "kernel_status_word": status,

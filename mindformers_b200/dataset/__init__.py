@@ -5,3 +5,5 @@ from .causal_language_model_dataset import (BlendedMegatronDatasetDataLoader, Ca
 from .gpt_dataset import (BlendedDataset, BlendedMegatronDatasetBuilder, GPTDataset, GPTDatasetConfig, MockGPTDataset)
 from .handlers import AlpacaInstructDataHandler, PackingHandler, build_data_handler
 from .indexed_dataset import IndexedDataset, IndexedDatasetBuilder
+from .dataloaders import (ADGenDataLoader, MultiSourceDataLoader, MultiSourceDataset, SFTDataLoader, ToolAlpacaDataLoader,
+                          TrainingDataLoader, TrainingDataset, read_records)

@@ -178,14 +178,169 @@ class CausalLanguageModelDataset:
         return loader
 
 
-@MindFormerRegister.register(MindFormerModuleType.DATASET)
-class KeyWordGenDataset(CausalLanguageModelDataset):
-    """Prompt/answer generation data; batches carry ``input_ids``/``labels`` like the causal dataset."""
+def _batched(dataset, cfg: dict, collate_fn=collate):
+    shards, shard_id = data_shard_info()
+    sampler = ResumableShardSampler(len(dataset), shards, shard_id, bool(cfg.get("shuffle", False)),
+                                    int(cfg.get("seed", 0) or 0))
+    bs = int(cfg.get("batch_size", 1))
+    loader = DataLoader(dataset, batch_size=bs, sampler=sampler, drop_last=bool(cfg.get("drop_remainder", True)),
+                        collate_fn=collate_fn, num_workers=int(cfg.get("num_parallel_workers", 0) or 0),
+                        pin_memory=bool(cfg.get("pin_memory", torch.cuda.is_available())))
+    loader.shard_sampler = sampler
+    loader.set_init_step = lambda steps: sampler.set_skip(steps * bs)
+    return loader
+
+
+def _task_tokenizer(cfg: dict):
+    tok = cfg.get("tokenizer")
+    if isinstance(tok, (dict, str)):
+        from ..models.tokenization import build_tokenizer
+        tok = build_tokenizer({"pretrained_model_dir": tok} if isinstance(tok, str) else tok)
+    if tok is None:
+        raise ValueError("dataset_config.tokenizer is required")
+    return tok
+
+
+class _KeyWordGenRows(Dataset):
+    """Prompt/answer rows → model inputs (reference ``keyword_gen_dataset.py`` train / eval functions)."""
+
+    def __init__(self, rows, tokenizer, cfg: dict):
+        self.rows, self.tok = rows, tokenizer
+        self.src_len = int(cfg.get("max_source_length", 64))
+        self.tgt_len = int(cfg.get("max_target_length", 64))
+        self.phase = cfg.get("phase", "train")
+        self.ignore_pad = bool(cfg.get("ignore_pad_token_for_loss", True))
+        self.prompt_col = cfg.get("prompt_column", "prompt")
+        self.answer_col = cfg.get("response_column", cfg.get("answer_column", "answer"))
+        pid = getattr(tokenizer, "pad_token_id", None)
+        self.pad_id = 0 if pid is None else pid
+
+    def __len__(self):
+        return len(self.rows)
+
+    def _enc(self, text, limit):
+        return list(self.tok.encode(str(text), add_special_tokens=False))[:limit]
+
+    def __getitem__(self, i):
+        r = self.rows[i]
+        prefix = list(self.tok.build_inputs_with_special_tokens([])) if hasattr(
+            self.tok, "build_inputs_with_special_tokens") else []
+        eos = self.tok.eos_token_id
+        prompt = prefix + self._enc(r[self.prompt_col], self.src_len - len(prefix))
+        answer = self._enc(r[self.answer_col], self.tgt_len - 1) + [eos]
+        if self.phase == "train":
+            width = self.src_len + self.tgt_len
+            ids = prompt + answer
+            labels = [-100] * len(prompt) + answer
+            gap = width - len(ids)
+            ids = ids + [self.pad_id] * gap
+            labels = labels + [-100 if self.ignore_pad else self.pad_id] * gap
+            # position t predicts token t+1
+            return {"input_ids": torch.tensor(ids[:-1]), "labels": torch.tensor(labels[1:])}
+        ids = [self.pad_id] * (self.src_len - len(prompt)) + prompt            # left padding for generation
+        lab = answer + [self.pad_id] * (self.tgt_len - len(answer))
+        return {"input_ids": torch.tensor(ids), "labels": torch.tensor(lab)}
 
 
 @MindFormerRegister.register(MindFormerModuleType.DATASET)
-class MultiTurnDataset(CausalLanguageModelDataset):
-    """Multi-turn chat data with per-turn loss masks."""
+class KeyWordGenDataset:
+    """Keyword → text generation data (ADGEN style). ``dataset_config`` keys: ``data_loader`` (rows with
+    ``prompt_column`` / ``response_column``), ``tokenizer``, ``max_source_length``, ``max_target_length``,
+    ``ignore_pad_token_for_loss``, ``phase`` (``train`` rows are prompt+answer with prompt labels ignored; ``eval``
+    rows are the left-padded prompt and the answer), and the batching keys of ``CausalLanguageModelDataset``."""
+
+    def __new__(cls, dataset_config: Optional[dict] = None, **kwargs):
+        cfg = dict(dataset_config or {})
+        cfg.update(kwargs)
+        loader_cfg = cfg["data_loader"]
+        if isinstance(loader_cfg, dict):
+            cfg.setdefault("phase", loader_cfg.get("phase", "train"))
+            rows = build_dataset_loader(loader_cfg)
+        else:
+            rows = loader_cfg
+        return _batched(_KeyWordGenRows(rows, _task_tokenizer(cfg), cfg), cfg)
+
+
+TOOL_DEFINITION_PREFIX = "Answer the following questions as best as you can. You have access to the following tools:\n"
+FUNCTION_CALL_NAME = "tool_call"
+
+
+def format_function_call(name: str, parameters: dict) -> str:
+    """``name(arg='value', …)`` as python source."""
+    return f"{name}(" + ", ".join(f"{k}={v!r}" for k, v in parameters.items()) + ")"
+
+
+class _MultiTurnRows(Dataset):
+    """Conversations → ``input_ids`` / ``labels`` with loss on assistant turns only
+    (reference ``multi_turn_dataset.py:200-268``)."""
+
+    def __init__(self, rows, tokenizer, cfg: dict):
+        self.rows, self.tok = rows, tokenizer
+        self.max_len = int(cfg.get("max_seq_length", 2048))
+        self.conv_key = cfg.get("conversation_key", "conversations")
+        self.tool_key = cfg.get("tool_key", "tools")
+        pid = getattr(tokenizer, "pad_token_id", None)
+        self.pad_id = 0 if pid is None else pid
+
+    def __len__(self):
+        return len(self.rows)
+
+    def _message(self, role, metadata, content):
+        if hasattr(self.tok, "build_single_message"):
+            return list(self.tok.build_single_message(role, metadata, content))
+        return list(self.tok.encode(f"<|{role}|>{metadata}\n{content}", add_special_tokens=False))
+
+    def format(self, item):
+        prefix = list(self.tok.get_prefix_tokens()) if hasattr(self.tok, "get_prefix_tokens") else []
+        tokens, mask = list(prefix), [0] * len(prefix)
+
+        def put(ids, loss):
+            tokens.extend(ids)
+            mask.extend([int(bool(loss))] * len(ids))
+
+        conv = [dict(c) for c in item[self.conv_key]]
+        if self.tool_key in item and item[self.tool_key]:
+            import json
+            conv.insert(0, {"role": "system",
+                            "content": TOOL_DEFINITION_PREFIX + json.dumps(item[self.tool_key], ensure_ascii=False)})
+        for c in conv:
+            loss = c.get("loss", True) and c["role"] not in ("system", "user")
+            if c["role"] == "tool":
+                call = "```python\n" + format_function_call(FUNCTION_CALL_NAME, c.get("parameters", {})) + "\n```"
+                put(self._message("assistant", c.get("name", ""), call), loss)
+                obs = c.get("observation")
+                if not isinstance(obs, str):
+                    import json
+                    obs = json.dumps(obs, ensure_ascii=False)
+                put(self._message("observation", "", obs), False)
+            else:
+                put(self._message(c["role"], "", c["content"]), loss)
+        put([self.tok.eos_token_id], False)
+        return tokens, mask
+
+    def __getitem__(self, i):
+        tokens, mask = self.format(self.rows[i])
+        # a token carries loss if it belongs to an assistant turn; the label of position t is token t+1
+        labels = [(t if m else -100) for t, m in zip(tokens, [0] + mask[:-1])]
+        ids = tokens[:self.max_len]
+        labels = labels[1:self.max_len]
+        ids = ids + [self.pad_id] * (self.max_len - len(ids))
+        labels = labels + [-100] * (self.max_len - len(labels))
+        return {"input_ids": torch.tensor(ids[:-1]), "labels": torch.tensor(labels[:self.max_len - 1])}
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET)
+class MultiTurnDataset:
+    """Multi-turn (tool) chat data. ``dataset_config`` keys: ``data_loader`` (rows with ``conversations`` and
+    optionally ``tools``), ``tokenizer`` (one with ``build_single_message`` formats turns with its role tokens),
+    ``max_seq_length``, plus the batching keys of ``CausalLanguageModelDataset``."""
+
+    def __new__(cls, dataset_config: Optional[dict] = None, **kwargs):
+        cfg = dict(dataset_config or {})
+        cfg.update(kwargs)
+        loader_cfg = cfg["data_loader"]
+        rows = build_dataset_loader(loader_cfg) if isinstance(loader_cfg, dict) else loader_cfg
+        return _batched(_MultiTurnRows(rows, _task_tokenizer(cfg), cfg), cfg)
 
 
 @MindFormerRegister.register(MindFormerModuleType.DATASET)

@@ -1,0 +1,396 @@
+"""Record-level data loaders for supervised fine-tuning and raw-text pre-training.
+
+Each loader is a registry entry (``MindFormerModuleType.DATASET_LOADER``) that returns a map-style (or iterable)
+dataset of dict rows; ``CausalLanguageModelDataset`` / ``KeyWordGenDataset`` / ``MultiTurnDataset`` shard, batch and
+collate them. They cover the reference's ``dataset/dataloader`` package:
+
+* ``SFTDataLoader``        json / jsonl / parquet / csv / tsv records → tokenised ``input_ids`` / ``labels`` through a
+                           named map function (``sft_dataloader.py``, ``sft_map_functions.py``).
+* ``ADGenDataLoader``      AdvertiseGen ``{"content", "summary"}`` lines (``adgen_dataloader.py``).
+* ``ToolAlpacaDataLoader`` ToolAlpaca conversations with validity checks (``toolaplaca_dataloader.py``).
+* ``MultiSourceDataLoader`` several sub-loaders mixed by sample counts or ratios, with an optional shuffle buffer
+                           (``multi_source_dataloader.py``).
+* ``TrainingDataLoader``   text files → tokenise → concatenate → fixed-length samples (``training_dataloader.py``).
+"""
+from __future__ import annotations
+
+import csv
+import glob
+import json
+import os
+import random
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset, IterableDataset
+
+from ..tools.register import MindFormerModuleType, MindFormerRegister
+
+IGNORE_INDEX = -100
+
+
+# ---- file readers ----------------------------------------------------------------------------------
+def read_records(path: str, file_format: Optional[str] = None) -> List[dict]:
+    """Rows of one file as dicts. ``json`` holds a list or one object per line; parquet/csv/tsv go through pyarrow."""
+    fmt = (file_format or os.path.splitext(path)[1].lstrip(".")).lower()
+    if fmt in ("json", "jsonl"):
+        with open(path, "r", encoding="utf-8") as f:
+            text = f.read().strip()
+        if not text:
+            return []
+        if text[0] == "[":
+            return list(json.loads(text))
+        return [json.loads(line) for line in text.splitlines() if line.strip()]
+    if fmt == "parquet":
+        import pyarrow.parquet as pq
+        return pq.read_table(path).to_pylist()
+    if fmt in ("csv", "tsv"):
+        with open(path, "r", encoding="utf-8", newline="") as f:
+            return list(csv.DictReader(f, delimiter="\t" if fmt == "tsv" else ","))
+    if fmt in ("txt", "text"):
+        with open(path, "r", encoding="utf-8") as f:
+            return [{"text": line.rstrip("\n")} for line in f if line.strip()]
+    raise ValueError(f"unsupported file format {fmt!r} for {path}")
+
+
+def list_files(dataset_dir: str, file_format: Optional[str] = None) -> List[str]:
+    if os.path.isfile(dataset_dir):
+        return [dataset_dir]
+    exts = [file_format] if file_format else ["json", "jsonl", "parquet", "csv", "tsv", "txt"]
+    files: List[str] = []
+    for e in exts:
+        files += glob.glob(os.path.join(dataset_dir, "**", f"*.{e}"), recursive=True)
+    if not files:
+        raise FileNotFoundError(f"no {exts} files under {dataset_dir}")
+    return sorted(files)
+
+
+def cmrc2018_reader(path: str) -> List[dict]:
+    """SQuAD-style CMRC2018 json → ``{"prompt", "answer"}`` rows (reference ``datareaders.py:21``)."""
+    with open(path, "r", encoding="utf-8") as f:
+        data = json.load(f)["data"]
+    rows = []
+    for doc in data:
+        for para in doc["paragraphs"]:
+            for qa in para["qas"]:
+                rows.append({"prompt": f"阅读文章：{para['context']}\n问：{qa['question']}\n答：",
+                             "answer": qa["answers"][0]["text"] if qa["answers"] else ""})
+    return rows
+
+
+def wikitext_reader(path: str) -> List[dict]:
+    """WikiText raw file → one row per article, spacing around punctuation repaired (``datareaders.py:40``)."""
+    import re
+    with open(path, "r", encoding="utf-8") as f:
+        text = f.read()
+    for a, b in ((" @-@ ", "-"), (" @,@ ", ","), (" @.@ ", "."), (" , ", ", "), (" . ", ". "), (" ; ", "; "),
+                 (" : ", ": "), (" 's", "'s"), ("( ", "("), (" )", ")"), (" n't", "n't")):
+        text = text.replace(a, b)
+    parts = re.split(r"\n \= [^=\n]+ \= \n", "\n" + text)
+    return [{"text": p.strip()} for p in parts if p.strip()]
+
+
+DATA_READERS: Dict[str, Callable[[str], List[dict]]] = {"cmrc2018": cmrc2018_reader, "wikitext": wikitext_reader}
+
+
+# ---- map functions ---------------------------------------------------------------------------------
+def _ids(tokenizer, text: str) -> List[int]:
+    return list(tokenizer.encode(text, add_special_tokens=False))
+
+
+def prepare_for_model(tokenizer, max_length: int, prompt: str, answer: Optional[str] = None) -> Dict[str, List[int]]:
+    """``bos + prompt + answer + eos`` cut to ``max_length``; labels ignore the prompt."""
+    bos = [tokenizer.bos_token_id] if getattr(tokenizer, "bos_token_id", None) is not None and getattr(
+        tokenizer, "add_bos_token", True) else []
+    p = bos + _ids(tokenizer, prompt)
+    a = (_ids(tokenizer, answer) + [tokenizer.eos_token_id]) if answer is not None else []
+    ids = (p + a)[:max_length]
+    labels = ([IGNORE_INDEX] * len(p) + a)[:max_length]
+    return {"input_ids": ids, "labels": labels}
+
+
+def default_map_fn(example, tokenizer, max_length, prompt_key="prompt", answer_key="answer", **kw):
+    return prepare_for_model(tokenizer, max_length, str(example[prompt_key]), str(example.get(answer_key, "")))
+
+
+ALPACA_WITH_INPUT = ("Below is an instruction that describes a task, paired with an input that provides further context. "
+                     "Write a response that appropriately completes the request.\n\n"
+                     "### Instruction:\n{instruction}\n\n### Input:\n{input}\n\n### Response:\n")
+ALPACA_NO_INPUT = ("Below is an instruction that describes a task. "
+                   "Write a response that appropriately completes the request.\n\n"
+                   "### Instruction:\n{instruction}\n\n### Response:\n")
+
+
+def alpaca_map_fn(example, tokenizer, max_length, **kw):
+    tmpl = ALPACA_WITH_INPUT if example.get("input") else ALPACA_NO_INPUT
+    return prepare_for_model(tokenizer, max_length, tmpl.format(**{"input": "", **example}), str(example["output"]))
+
+
+def advertisegen_map_fn(example, tokenizer, max_length, **kw):
+    return prepare_for_model(tokenizer, max_length, str(example["content"]), str(example["summary"]))
+
+
+def tnews_map_fn(example, tokenizer, max_length, label_names: Optional[Sequence[str]] = None, **kw):
+    label = example.get("label_desc", example.get("label"))
+    if label_names is not None and str(label).isdigit():
+        label = label_names[int(label)]
+    prompt = f"新闻：{example['sentence']}\n这条新闻的类别是："
+    return prepare_for_model(tokenizer, max_length, prompt, str(label))
+
+
+def multi_round_chat_map_fn(example, tokenizer, max_length, user_role="human", assistant_role="gpt",
+                            user_prefix="<|user|>\n", assistant_prefix="<|assistant|>\n", system_prefix="<|system|>\n",
+                            **kw):
+    """``{"conversations": [{"from", "value"}, …]}``; only assistant turns carry loss."""
+    ids: List[int] = []
+    labels: List[int] = []
+    if getattr(tokenizer, "bos_token_id", None) is not None and getattr(tokenizer, "add_bos_token", True):
+        ids.append(tokenizer.bos_token_id)
+        labels.append(IGNORE_INDEX)
+    for turn in example["conversations"]:
+        role, value = turn.get("from", turn.get("role")), turn.get("value", turn.get("content", ""))
+        if role in (assistant_role, "assistant"):
+            head = _ids(tokenizer, assistant_prefix)
+            body = _ids(tokenizer, value) + [tokenizer.eos_token_id]
+            ids += head + body
+            labels += [IGNORE_INDEX] * len(head) + body
+        else:
+            prefix = system_prefix if role == "system" else user_prefix
+            part = _ids(tokenizer, prefix + value + "\n")
+            ids += part
+            labels += [IGNORE_INDEX] * len(part)
+    return {"input_ids": ids[:max_length], "labels": labels[:max_length]}
+
+
+SFT_MAP_FUNCTIONS: Dict[str, Callable] = {
+    "default": default_map_fn, "alpaca": alpaca_map_fn, "advertisegen": advertisegen_map_fn, "tnews": tnews_map_fn,
+    "cmrc2018": default_map_fn, "multi-round-chat": multi_round_chat_map_fn,
+}
+
+
+def _resolve_tokenizer(tokenizer):
+    if isinstance(tokenizer, (dict, str)):
+        from ..models.tokenization import build_tokenizer
+        return build_tokenizer({"pretrained_model_dir": tokenizer} if isinstance(tokenizer, str) else tokenizer)
+    return tokenizer
+
+
+def _finish(row: Dict[str, List[int]], max_length: int, pad_id: int, pad: bool) -> Dict[str, torch.Tensor]:
+    """Shift labels by one (position ``t`` predicts token ``t+1``) and optionally pad to ``max_length - 1``."""
+    ids, labels = row["input_ids"], row["labels"]
+    ids, labels = ids[:-1], labels[1:]
+    if pad:
+        gap = (max_length - 1) - len(ids)
+        ids, labels = ids + [pad_id] * gap, labels + [IGNORE_INDEX] * gap
+    mask = [0 if l == IGNORE_INDEX else 1 for l in labels]
+    return {"input_ids": torch.tensor(ids, dtype=torch.int64), "labels": torch.tensor(labels, dtype=torch.int64),
+            "loss_mask": torch.tensor(mask, dtype=torch.float32)}
+
+
+class _MappedRecords(Dataset):
+    def __init__(self, records: List[dict], fn: Callable, tokenizer, max_length: int, pad: bool, fn_kwargs: dict):
+        self.records, self.fn, self.tokenizer = records, fn, tokenizer
+        self.max_length, self.pad, self.fn_kwargs = max_length, pad, fn_kwargs
+        pid = getattr(tokenizer, "pad_token_id", None)
+        self.pad_id = 0 if pid is None else pid
+
+    def __len__(self):
+        return len(self.records)
+
+    def __getitem__(self, i):
+        row = self.fn(self.records[i], tokenizer=self.tokenizer, max_length=self.max_length, **self.fn_kwargs)
+        return _finish(row, self.max_length, self.pad_id, self.pad)
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class SFTDataLoader:
+    """``max_length`` counts the unshifted sequence: rows come out with ``max_length - 1`` positions."""
+
+    def __new__(cls, dataset_dir: str, tokenizer, dataset_name: str = "", file_format: Optional[str] = None,
+                max_length: int = 1025, read_function: Optional[Callable] = None,
+                map_function: Optional[Callable] = None, map_function_kwargs: Optional[dict] = None,
+                shuffle: bool = False, seed: int = 0, pad_to_max_length: bool = True, column_names=None, **kw):
+        reader = read_function or DATA_READERS.get(dataset_name)
+        records: List[dict] = []
+        for path in list_files(dataset_dir, file_format):
+            records += reader(path) if reader else read_records(path, file_format)
+        if shuffle:
+            random.Random(seed).shuffle(records)
+        fn = map_function or SFT_MAP_FUNCTIONS.get(dataset_name or "default")
+        if fn is None:
+            raise ValueError(f"dataset_name {dataset_name!r}: pass map_function or one of {sorted(SFT_MAP_FUNCTIONS)}")
+        return _MappedRecords(records, fn, _resolve_tokenizer(tokenizer), int(max_length), pad_to_max_length,
+                              dict(map_function_kwargs or {}))
+
+
+class _RawRecords(Dataset):
+    """Untokenised rows; a task dataset (``KeyWordGenDataset`` / ``MultiTurnDataset``) tokenises them."""
+
+    def __init__(self, rows: List[dict]):
+        self.rows = rows
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        return self.rows[i]
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class ADGenDataLoader:
+    """``{"content": prompt, "summary": answer}`` per line → rows ``{"prompt", "answer"}``."""
+
+    def __new__(cls, dataset_dir: str, phase: str = "train", shuffle: bool = False,
+                origin_columns=("content", "summary"), seed: int = 0, **kw):
+        if phase not in ("train", "eval"):
+            raise ValueError(f"phase must be train or eval, got {phase!r}")
+        pk, ak = origin_columns
+        rows = []
+        for path in list_files(dataset_dir):
+            for i, r in enumerate(read_records(path)):
+                if pk not in r or ak not in r:
+                    raise KeyError(f"{path} row {i}: needs columns {pk!r} and {ak!r}")
+                rows.append({"prompt": r[pk], "answer": r[ak]})
+        if shuffle:
+            random.Random(seed).shuffle(rows)
+        return _RawRecords(rows)
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class ToolAlpacaDataLoader:
+    """ToolAlpaca jsonl: ``{"tools": [...], "conversations": [{"role", "content"}, …]}``. Rows must open with a user
+    turn, alternate user → assistant/tool, and close with an assistant turn; others are skipped with a count."""
+
+    def __new__(cls, dataset_dir: str, shuffle: bool = False, seed: int = 0, **kw):
+        rows, bad = [], 0
+        for path in list_files(dataset_dir):
+            for r in read_records(path):
+                conv = r.get("conversations") or []
+                ok = (len(conv) >= 2 and conv[0].get("role") in ("user", "system")
+                      and conv[-1].get("role") == "assistant"
+                      and all(c.get("role") in ("system", "user", "assistant", "tool") for c in conv)
+                      and all("content" in c or c.get("role") == "tool" for c in conv))
+                if ok:
+                    rows.append(r)
+                else:
+                    bad += 1
+        if shuffle:
+            random.Random(seed).shuffle(rows)
+        ds = _RawRecords(rows)
+        ds.skipped = bad
+        return ds
+
+
+class MultiSourceDataset(Dataset):
+    """Samples of several datasets in one index space.
+
+    ``sample_nums[i]`` rows are taken from dataset ``i`` per epoch (over-sampling wraps around). Without shuffle the
+    sources follow one another; with shuffle the order of sources is a seeded permutation over all draws, and rows
+    inside a source are permuted too.
+    """
+
+    def __init__(self, datasets: List[Dataset], sample_nums: List[int], shuffle: bool = False, seed: int = 0):
+        self.datasets = datasets
+        rng = np.random.default_rng(seed)
+        src = np.concatenate([np.full(n, i, dtype=np.int64) for i, n in enumerate(sample_nums)])
+        row = np.concatenate([
+            (rng.permutation(max(n, len(d)))[:n] if shuffle else np.arange(n)) % max(len(d), 1)
+            for d, n in zip(datasets, sample_nums)])
+        if shuffle:
+            order = rng.permutation(len(src))
+            src, row = src[order], row[order]
+        self.src, self.row = src, row
+
+    def __len__(self):
+        return len(self.src)
+
+    def __getitem__(self, i):
+        return self.datasets[int(self.src[i])][int(self.row[i])]
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class MultiSourceDataLoader:
+    """``sub_data_loader``: list of loader configs. Mix by ``samples_count`` + ``dataset_ratios`` or by explicit
+    ``nums_per_dataset``; default is every row of every source once."""
+
+    def __new__(cls, sub_data_loader: List[dict], sub_data_loader_args: Optional[dict] = None,
+                dataset_ratios: Optional[List[float]] = None, samples_count: Optional[int] = None,
+                nums_per_dataset: Optional[List[int]] = None, shuffle: bool = False, seed: int = 0, **kw):
+        subs = []
+        for cfg in sub_data_loader:
+            merged = dict(sub_data_loader_args or {})
+            merged.update(cfg)
+            subs.append(MindFormerRegister.get_instance_from_cfg(merged, MindFormerModuleType.DATASET_LOADER)
+                        if isinstance(cfg, dict) else cfg)
+        if nums_per_dataset is not None:
+            nums = [int(n) for n in nums_per_dataset]
+        elif dataset_ratios is not None:
+            if abs(sum(dataset_ratios) - 1.0) > 1e-6:
+                raise ValueError("dataset_ratios must sum to 1")
+            total = samples_count if samples_count is not None else sum(len(d) for d in subs)
+            nums = [int(total * r) for r in dataset_ratios]
+        else:
+            nums = [len(d) for d in subs]
+        if len(nums) != len(subs):
+            raise ValueError("one sample count per sub loader is required")
+        return MultiSourceDataset(subs, nums, shuffle, seed)
+
+
+class TrainingDataset(IterableDataset):
+    """Raw text → fixed-length token samples.
+
+    Files are visited in order (a seeded shuffle of the file list if ``shuffle``); every document is tokenised,
+    closed with ``eos`` and appended to a token stream that is cut into ``max_length`` pieces. ``samples_num`` bounds
+    the epoch. ``skip_num`` drops the first samples (resume).
+    """
+
+    def __init__(self, dataset_dir: str, tokenizer, column_names=("input_ids",), max_length: int = 1025,
+                 text_col: str = "text", file_format: Optional[str] = None, shuffle: bool = False, seed: int = 0,
+                 samples_num: Optional[int] = None, skip_num: int = 0, file_limit: int = 1,
+                 is_align: bool = True):
+        self.files = list_files(dataset_dir, file_format)
+        if shuffle:
+            random.Random(seed).shuffle(self.files)
+        self.tokenizer, self.max_length, self.text_col = _resolve_tokenizer(tokenizer), int(max_length), text_col
+        self.file_format, self.samples_num, self.skip_num = file_format, samples_num, skip_num
+        self.column = column_names[0]
+        self.is_align = is_align
+
+    def _documents(self) -> Iterable[str]:
+        for path in self.files:
+            for r in read_records(path, self.file_format):
+                text = r.get(self.text_col)
+                if text:
+                    yield text
+
+    def __iter__(self):
+        buf: List[int] = []
+        produced = 0
+        eos = self.tokenizer.eos_token_id
+        for doc in self._documents():
+            buf += list(self.tokenizer.encode(doc, add_special_tokens=False)) + ([eos] if eos is not None else [])
+            while len(buf) >= self.max_length:
+                piece, buf = buf[:self.max_length], buf[self.max_length:]
+                produced += 1
+                if produced <= self.skip_num:
+                    continue
+                yield {self.column: torch.tensor(piece[:-1], dtype=torch.int64),
+                       "labels": torch.tensor(piece[1:], dtype=torch.int64)}
+                if self.samples_num is not None and produced - self.skip_num >= self.samples_num:
+                    return
+        if buf and not self.is_align and len(buf) > 1:
+            pad = [self.tokenizer.pad_token_id or 0] * (self.max_length - len(buf))
+            piece = buf + pad
+            labels = buf[1:] + [IGNORE_INDEX] * (len(pad) + 0)
+            yield {self.column: torch.tensor(piece[:-1], dtype=torch.int64),
+                   "labels": torch.tensor(labels[:self.max_length - 1], dtype=torch.int64)}
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class TrainingDataLoader:
+    def __new__(cls, dataset_dir: str, tokenizer, column_names=("input_ids",), max_length: int = 1025,
+                text_col: str = "text", file_format: Optional[str] = None, shuffle: bool = False,
+                samples_num: Optional[int] = None, skip_num: int = 0, **kw):
+        return TrainingDataset(dataset_dir, tokenizer, column_names, max_length, text_col, file_format, shuffle,
+                               int(kw.get("seed", 0)), samples_num, skip_num, is_align=bool(kw.get("is_align", True)))

@@ -6,6 +6,9 @@ from .families import (ChatGLM2ForConditionalGeneration, DeepseekV3Config, Deeps
 from .modeling_utils import PreTrainedModel
 from .presets import PRESETS, get_preset
 from .tokenization import ByteTokenizer, TextProcessor, build_tokenizer
+from .tokenization_utils import AddedToken, BatchEncoding, BytePairEncoder, PreTrainedTokenizer
+from .tokenizers import (ChatGLM3Tokenizer, ChatGLM4Tokenizer, Llama3Tokenizer, LlamaTokenizer, LlamaTokenizerFast,
+                         Qwen2Tokenizer, TelechatTokenizer)
 
 
 def build_network(config: dict, default_args=None):

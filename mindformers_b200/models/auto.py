@@ -98,23 +98,76 @@ AutoModelForCausalLM = AutoModel
 
 
 class AutoTokenizer:
-    """Loads a tokenizer directory (``tokenizer.json`` / sentencepiece / tiktoken files) through ``transformers``;
-    ``ByteTokenizer`` is the dependency-free fallback used by tests and ``run_check``."""
+    """Picks the tokenizer class of a directory (reference ``models/auto/tokenization_auto.py``).
 
-    @staticmethod
-    def from_pretrained(name_or_dir: str, **kwargs):
+    Order: ``tokenizer_class`` of ``tokenizer_config.json`` → ``model_type`` of ``config.json`` → the vocabulary
+    files present (``tokenizer.json`` → fast, ``vocab.json`` → Qwen2 BPE, ``tokenizer.model`` → sentencepiece, or a
+    tiktoken rank file when it is not a sentencepiece proto). ``use_hf=True`` hands the directory to
+    ``transformers`` instead. ``"byte"`` gives the file-less ``ByteTokenizer``.
+    """
+    _extra: dict = {}
+
+    @classmethod
+    def _resolve(cls, directory: str):
+        from . import tokenizers as T
+        table = dict(T.TOKENIZER_CLASSES)
+        table.update(cls._extra)
+        name = None
+        cfg_path = os.path.join(directory, "tokenizer_config.json")
+        if os.path.exists(cfg_path):
+            with open(cfg_path, "r", encoding="utf-8") as f:
+                name = json.load(f).get("tokenizer_class")
+        has = lambda f: os.path.exists(os.path.join(directory, f))
+        if name in table and all(has(table[name].vocab_files_names[k]) for k in table[name].required_vocab_files()):
+            return table[name]
+        if has("tokenizer.json"):
+            return T.LlamaTokenizerFast
+        model_type = None
+        if has("config.json"):
+            with open(os.path.join(directory, "config.json"), "r", encoding="utf-8") as f:
+                model_type = json.load(f).get("model_type")
+        if model_type in T.TOKENIZER_BY_MODEL_TYPE:
+            cand = table[T.TOKENIZER_BY_MODEL_TYPE[model_type]]
+            if all(has(cand.vocab_files_names[k]) for k in cand.required_vocab_files()):
+                return cand
+        if has("vocab.json"):
+            return T.Qwen2Tokenizer
+        if has("tokenizer.model"):
+            with open(os.path.join(directory, "tokenizer.model"), "rb") as f:
+                head = f.read(64)
+            tiktoken_like = b" " in head and all(32 <= b < 127 or b in (10, 13) for b in head)
+            return T.Llama3Tokenizer if tiktoken_like else T.LlamaTokenizer
+        raise FileNotFoundError(f"{directory}: no tokenizer.json, vocab.json or tokenizer.model")
+
+    @classmethod
+    def from_pretrained(cls, name_or_dir: str, use_hf: bool = False, **kwargs):
         if name_or_dir in ("byte", "ByteTokenizer"):
             from .tokenization import ByteTokenizer
             return ByteTokenizer()
         if not os.path.exists(name_or_dir):
             raise FileNotFoundError(f"tokenizer directory {name_or_dir} does not exist (no hub access offline)")
-        from transformers import AutoTokenizer as _HF
-        return _HF.from_pretrained(name_or_dir, local_files_only=True, **kwargs)
+        if use_hf:
+            from transformers import AutoTokenizer as _HF
+            return _HF.from_pretrained(name_or_dir, local_files_only=True, **kwargs)
+        if os.path.isfile(name_or_dir):
+            directory = os.path.dirname(name_or_dir) or "."
+            return cls._resolve(directory).from_pretrained(name_or_dir, **kwargs)
+        cfg_path = os.path.join(name_or_dir, "tokenizer_config.json")
+        if os.path.exists(cfg_path):
+            with open(cfg_path, "r", encoding="utf-8") as f:
+                if json.load(f).get("tokenizer_class") == "ByteTokenizer":
+                    from .tokenization import ByteTokenizer
+                    return ByteTokenizer()
+        return cls._resolve(name_or_dir).from_pretrained(name_or_dir, **kwargs)
 
-    @staticmethod
-    def register(*args, **kwargs):
-        from transformers import AutoTokenizer as _HF
-        return _HF.register(*args, **kwargs)
+    @classmethod
+    def register(cls, name_or_config, tokenizer_class=None, **kwargs):
+        """``register("MyTokenizer", MyTokenizer)`` or ``register(ConfigClass, MyTokenizer)``."""
+        if tokenizer_class is None:
+            tokenizer_class, name_or_config = name_or_config, name_or_config.__name__
+        key = name_or_config if isinstance(name_or_config, str) else tokenizer_class.__name__
+        cls._extra[key] = tokenizer_class
+        return tokenizer_class
 
 
 class AutoProcessor:
