@@ -205,6 +205,7 @@ def main():
     # ---- device-timed metric ---------------------------------------------------------------------
     for i in range(args.warmup):
         out = engine.train_step_device(dev_batches[i % 2])
+        engine.adapt_moe_capacity()     # expert-parallel receive buffers grow here if routing overflowed them
     total_ms, clocks, launches, out = timed(lambda i: engine.train_step_device(dev_batches[i % 2]), args.steps)
     loss_val = float(out["loss"])
     tokens_per_step = (args.seqs_per_gpu * S) if cp > 1 else args.seqs_per_gpu * world * S

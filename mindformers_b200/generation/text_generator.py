@@ -68,7 +68,12 @@ class GenerationMixin:
         if all_logits:       # draft verification: the logits of every new token are needed
             ctx.last_token_index = torch.arange(int(flat.numel()), dtype=torch.int64, device=device)
         meta = AttnMeta(batch=1, seq_len=int(flat.numel()), positions=pos, cache=ctx)
-        logits = self.model(flat.unsqueeze(0), attn_meta=meta)
+        hook = getattr(self, "input_embeds_hook", None)     # multimodal models splice encoder outputs in here
+        embeds = hook(flat, pos, prefill) if hook is not None else None
+        if embeds is not None:
+            logits = self.model(flat.unsqueeze(0), attn_meta=meta, input_embeds=embeds)
+        else:
+            logits = self.model(flat.unsqueeze(0), attn_meta=meta)
         if all_logits:
             pass
         elif not prefill:

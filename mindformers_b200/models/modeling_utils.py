@@ -49,7 +49,8 @@ class PreTrainedModel(nn.Module, GenerationMixin):
 
     # ---- forward ----------------------------------------------------------------------------------------
     def forward(self, input_ids, labels=None, loss_mask=None, position_ids=None, attn_meta=None, **kw):
-        return self.model(input_ids, labels, loss_mask, position_ids, attn_meta)
+        return self.model(input_ids, labels, loss_mask, position_ids, attn_meta,
+                          input_embeds=kw.get("input_embeds"))
 
     # make checkpoints carry the network's own names (no "model." prefix)
     def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):

@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from . import parallel_state as ps
+from ..tools.logger import logger
 from . import symm_mem
 
 BLOCK = 128
@@ -34,6 +35,17 @@ class _Plan:
         self.block_group = torch.zeros(rows_cap // BLOCK, dtype=torch.int32, device=dev)
         self.num_blocks = torch.zeros(1, dtype=torch.int32, device=dev)
         self.rows = rows_cap
+
+
+STATUS_MOE_OVERFLOW = 6      # kStatusMoeOverflow of ops/csrc/moe_ep.cu
+
+
+def adapt_capacity() -> bool:
+    """``MoEExchange.adapt_capacity`` of every live exchange (see there)."""
+    grew = False
+    for ex in list(MoEExchange._instances.values()):
+        grew = ex.adapt_capacity() or grew
+    return grew
 
 
 class MoEExchange:
@@ -65,6 +77,7 @@ class MoEExchange:
         self._arr = ctypes.c_longlong * self.world
         self._shared: Dict[tuple, object] = {}
         self._in_flight: Dict[object, set] = {}
+        self._symm_names: list = []
         if self.world > 1:
             words = self.lib.mfb_moe_flag_words()
             flags = symm_mem.allocate(f"moe.flags.{id(group)}.{self.H}.{self.E}.{self.k}", words * 4, group, self.dev)
@@ -91,7 +104,9 @@ class MoEExchange:
         if hit is not None:
             return hit
         if self.world > 1:
-            buf = symm_mem.allocate(f"moe.{tag}.{rows}.{self.H}.{self.E}.{id(self.group)}", rows * self.H * 2, self.group, self.dev)
+            name = f"moe.{tag}.{rows}.{self.H}.{self.E}.{id(self.group)}"
+            self._symm_names.append(name)
+            buf = symm_mem.allocate(name, rows * self.H * 2, self.group, self.dev)
             t = buf.tensor.view(torch.bfloat16)[:rows * self.H].view(rows, self.H)
             ptrs = self._arr(*[int(p) for p in buf.ptrs])
         else:
@@ -122,6 +137,35 @@ class MoEExchange:
 
     def status(self):
         return _lib.status_word(self.dev).data_ptr()
+
+    def adapt_capacity(self) -> bool:
+        """Grow the receive buffers if a rank got more rows than they hold (the plan kernel then set the overflow
+        code in the status word and the scatter skipped the rows that did not fit).
+
+        Collective over the expert-parallel group and synchronising: call it between steps. All ranks grow together
+        because the row buffers are symmetric allocations. Returns True if the factor changed; the dropped rows of
+        the step that overflowed are not recomputed.
+        """
+        if self.world <= 1:
+            return False
+        word = _lib.status_word(self.dev)
+        flag = (word == STATUS_MOE_OVERFLOW).to(torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        if int(flag.item()) == 0:
+            return False
+        word.masked_fill_(word == STATUS_MOE_OVERFLOW, 0)
+        old = self.factor
+        self.factor = min(self.factor * 1.5, float(self.world))
+        if self.factor == old:
+            logger.warning("expert-parallel receive buffers overflow at the maximum factor %.2f", old)
+            return False
+        for name in self._symm_names:
+            symm_mem.free(name, self.group)
+        self._symm_names.clear()
+        self._shared.clear()
+        logger.warning("expert-parallel receive buffers overflowed: moe_ep_buffer_factor %.2f -> %.2f "
+                       "(set it in the model config to avoid the dropped rows of the first steps)", old, self.factor)
+        return True
 
     # ---- kernel wrappers ------------------------------------------------------------------------------
     def plan(self, ids: torch.Tensor, T: int):

@@ -86,8 +86,11 @@ class GPTModel(nn.Module):
     # ---------------------------------------------------------------------------------------------
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 loss_mask: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
-                attn_meta: Optional[AttnMeta] = None, return_hidden: bool = False):
-        """``input_ids``/``labels``: ``[B, S]``. Returns the loss when labels are given, else logits ``[T, V/tp]``."""
+                attn_meta: Optional[AttnMeta] = None, return_hidden: bool = False,
+                input_embeds: Optional[torch.Tensor] = None):
+        """``input_ids``/``labels``: ``[B, S]``. Returns the loss when labels are given, else logits ``[T, V/tp]``.
+        ``input_embeds`` ``[B, S, H]`` (full sequence on every tensor-parallel rank) replaces the embedding lookup;
+        multimodal models use it to splice encoder outputs into the text embeddings."""
         cfg = self.config
         if input_ids.dim() == 1:
             input_ids = input_ids.unsqueeze(0)
@@ -98,7 +101,11 @@ class GPTModel(nn.Module):
         meta.batch = meta.batch or B
         if position_ids is not None and meta.positions is None:
             meta.positions = position_ids.reshape(-1)
-        if self.pre_process:
+        if self.pre_process and input_embeds is not None:
+            hidden = input_embeds.reshape(B * S, -1)
+            if self.embedding.sp:
+                hidden = M.scatter_to_sequence_parallel_region(hidden)
+        elif self.pre_process:
             hidden = self.embedding(input_ids)
         else:
             hidden = self.input_tensor

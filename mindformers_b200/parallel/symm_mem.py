@@ -55,6 +55,12 @@ def allocate(name: str, nbytes: int, group, device=None) -> SymmBuffer:
     return buf
 
 
+def free(name: str, group) -> None:
+    """Drop this module's reference to a buffer. Call it on every rank at the same point of the program, after a
+    collective that orders all peers' reads of the buffer before it."""
+    _BUFFERS.pop(f"{name}:{id(group)}", None)
+
+
 def enable():
     global _READY
     _READY = True

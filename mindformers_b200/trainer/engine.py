@@ -68,6 +68,7 @@ class TrainingEngine:
         out = self.train_step_device(dev_batch)
         packed = torch.stack([out["loss"].float().reshape(()), out["global_norm"].float().reshape(()),
                               out["skipped"].float().reshape(())]).cpu()
+        self.adapt_moe_capacity()
         return {"loss": float(packed[0]), "global_norm": float(packed[1]), "skipped": bool(packed[2] > 0),
                 "lr": float(out["lr"])}
 
@@ -81,4 +82,13 @@ class TrainingEngine:
         out = self.train_step_device(dev_batch)
         loss = out["loss"].float().cpu()          # device→host read of the step's result
         self.d2h_bytes = loss.numel() * loss.element_size()
+        self.adapt_moe_capacity()
         return float(loss)
+
+    def adapt_moe_capacity(self) -> bool:
+        """Grow the expert-parallel receive buffers if the last step overflowed them (collective, synchronising;
+        a no-op without fused expert parallelism)."""
+        from ..parallel import fused_moe
+        if not fused_moe.MoEExchange._instances:
+            return False
+        return fused_moe.adapt_capacity()
