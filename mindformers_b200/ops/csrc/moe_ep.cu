@@ -158,14 +158,19 @@ moe_plan_kernel(MoePlanArgs a) {
   }
   __syncthreads();
   if (e < a.E) a.write_base[e] = seg[e] + mine[e];
+  // on overflow every consumer of the plan (grouped GEMM row blocks, per-expert weight-gradient ranges) stays inside
+  // the buffer: segments are cut at the last whole block that fits
+  int total = seg[a.E];
+  if (total > a.rows_cap) total = a.rows_cap / kMoeBlock * kMoeBlock;
   if (e < a.E_local) {
     const int ge = a.rank * a.E_local + e;
-    a.group_offsets[e] = seg[ge];
-    a.seg_fill[e] = tot[ge];
+    const int start = seg[ge] < total ? seg[ge] : total;
+    int fill = tot[ge];
+    if (fill > total - start) fill = total - start;
+    a.group_offsets[e] = start;
+    a.seg_fill[e] = fill;
   }
   if (e == 0) {
-    int total = seg[a.E];
-    if (total > a.rows_cap) total = a.rows_cap / kMoeBlock * kMoeBlock;
     a.group_offsets[a.E_local] = total;
     a.num_blocks[0] = total / kMoeBlock;
   }

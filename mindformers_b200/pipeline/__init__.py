@@ -90,19 +90,46 @@ class TextGenerationPipeline(Pipeline):
 
 @MindFormerRegister.register(MindFormerModuleType.PIPELINE, alias="multi_modal_to_text_generation")
 class MultiModalToTextPipeline(TextGenerationPipeline):
-    """Inputs are lists of ``{"text": ...}`` / ``{"image": ...}`` parts. The text parts are concatenated into the
-    prompt; image parts go through ``image_processor`` when the model takes ``pixel_values`` (the language models
-    in this package do not, so images raise unless a processor and such a model are supplied)."""
+    """Inputs are queries made of parts, ``[{"image": path_or_array}, {"text": "…"}]``.
+
+    With ``processor`` (a ``BaseXModalToTextProcessor``) the parts are tokenised, image placeholders are expanded and
+    pixel values with their context positions are passed to ``model.generate`` (reference
+    ``pipeline/multi_modal_to_text_generation_pipeline.py``). Without a processor only text parts are accepted and
+    the pipeline behaves like text generation.
+    """
+
+    def __init__(self, *args, processor=None, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.processor = processor
+        if processor is not None and self.tokenizer is None:
+            self.tokenizer = processor.tokenizer
 
     def preprocess(self, inputs, **kw):
+        if self.processor is not None:
+            queries = [list(s) if isinstance(s, (list, tuple)) else [s] for s in inputs]
+            batch = self.processor(queries)
+            out = {"input_ids": batch["input_ids_list"]}
+            for k, v in batch.items():
+                if k not in ("input_ids", "input_ids_list", "raw_query"):
+                    out[k] = v
+            return out
         texts = []
         for sample in inputs:
             parts = sample if isinstance(sample, list) else [sample]
-            txt = "".join(p.get("text", "") if isinstance(p, dict) else str(p) for p in parts)
-            if any(isinstance(p, dict) and "image" in p for p in parts) and self.image_processor is None:
-                raise ValueError("image parts need an image_processor and a model that accepts pixel_values")
-            texts.append(txt)
+            if any(isinstance(p, dict) and "image" in p for p in parts):
+                raise ValueError("image parts need processor= (a BaseXModalToTextProcessor) and a multimodal model")
+            texts.append("".join(p.get("text", "") if isinstance(p, dict) else str(p) for p in parts))
         return super().preprocess(texts, **kw)
+
+    @torch.no_grad()
+    def _forward(self, model_inputs, **generate_kwargs):
+        modal = {k: v for k, v in model_inputs.items() if k != "input_ids"}
+        if not modal:
+            return super()._forward(model_inputs, **generate_kwargs)
+        self.model.eval()
+        generate_kwargs.setdefault("eos_token_id", getattr(self.tokenizer, "eos_token_id", None))
+        out = self.model.generate(model_inputs["input_ids"], **modal, **generate_kwargs)
+        return {"output_ids": out, "input_ids": model_inputs["input_ids"]}
 
 
 def pipeline(task: Optional[str] = None, model=None, tokenizer=None, image_processor=None, audio_processor=None,
