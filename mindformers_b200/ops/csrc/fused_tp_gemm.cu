@@ -14,6 +14,15 @@
 //       all peers, adds their tiles to the accumulator in fp32 and writes the final rows. No separate
 //       reduction pass and no host synchronisation.
 //
+//   COMM = 3  GEMM -> all-reduce (one shot)   D[M, N] = sum_p (A_p x B_p), the same bits on every rank
+//       For tensor-parallel inference, where M is a decode batch or a prefill chunk and no rank owns a row
+//       range. The epilogue of every tile rounds the partial tile to bf16, stores it into the receive slot
+//       [rank] of every peer (coalesced peer stores) and releases the tile's flag there; then it acquires the
+//       flags of all peers for the same tile, adds the tp bf16 partials in rank order (its own rounded one
+//       included, so that all ranks produce identical bits) and writes the tile with a TMA store. All ranks
+//       walk the tiles in the same order, so the wait is for a store that the peer issues before it waits
+//       itself. M needs no alignment: TMA zero-fills rows past M on load and clips them on store.
+//
 // Cross-rank flags carry a monotonically increasing epoch (the call counter, identical on all ranks),
 // so they never need a reset; receive buffers are double-buffered on the epoch parity. A rank can be at
 // most one call ahead of a peer, because each call waits for data that the peer only produces in the
@@ -144,7 +153,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
   const int k_blocks = (args.K + kTpBK - 1) / kTpBK;
   const int n_tiles = args.num_m_blocks * args.num_n_blocks;
   // COMM 1 starts with the rank's own rows, COMM 2 with the rows of the next rank (own rows last)
-  const int first_chunk = (COMM == 1) ? args.rank : (args.rank + 1) % args.tp;
+  const int first_chunk = (COMM == 1) ? args.rank : (COMM == 2 ? (args.rank + 1) % args.tp : 0);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -282,6 +291,127 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
       const int local_row = mb_local * kTpBM + row;   // row inside the owner's chunk
+      if (COMM == 3) {
+        // ---- push the bf16 partial tile to every peer ----
+        const int et = threadIdx.x - 64;   // 0..127
+        const int cj = et & 7;             // 16-byte chunk inside a 128-byte staging row
+        if (issuer) tma_wait_group_read<0>();   // the stores of the previous tile have read the staging buffers
+#pragma unroll 1
+        for (int c = 0; c < NUM_CHUNKS; ++c) {
+          uint32_t v0[32], v1[32], packed[32];
+          tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+          tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            packed[i] = pack_bf16x2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+            packed[16 + i] = pack_bf16x2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+          }
+          const int col0 = t.n_blk * BN + c * 64;
+          const int buf = chunk_counter & 1;
+          named_bar_sync(1, 128);
+          uint8_t* sbase = staging + buf * kTpStaging;
+          uint8_t* srow = sbase + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          named_bar_sync(1, 128);
+          if (col0 < args.N) {
+            uint4 vals[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 16 + (et >> 3);
+              vals[i] = *reinterpret_cast<const uint4*>(sbase + r * 128 + ((cj ^ (r & 7)) << 4));
+            }
+            for (int p = 0; p < args.tp; ++p) {
+              if (p == args.rank) continue;
+              __nv_bfloat16* dst0 = args.recv_peer[p] + (static_cast<size_t>(parity) * args.tp + args.rank) * slot_elems +
+                                    static_cast<size_t>(t.m_blk * kTpBM) * args.N + col0 + cj * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = i * 16 + (et >> 3);
+                *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r) * args.N) = vals[i];
+              }
+            }
+          }
+          ++chunk_counter;
+        }
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (issuer) {
+          for (int p = 0; p < args.tp; ++p) {
+            if (p == args.rank) continue;
+            st_release_sys(args.tile_flags_peer[p] + (static_cast<size_t>(parity) * args.tp + args.rank) * tiles_per_chunk + tile_in_chunk,
+                           args.epoch);
+          }
+          // ---- the peers' partial tiles ----
+          for (int p = 0; p < args.tp && ok; ++p) {
+            if (p == args.rank) continue;
+            ok = wait_flag_ge<true>(args.tile_flags_local + (static_cast<size_t>(parity) * args.tp + p) * tiles_per_chunk + tile_in_chunk,
+                                    args.epoch, abort_flag, args.status);
+          }
+        }
+        ok = named_bar_and(2, 128, ok);
+        if (!ok) break;
+        // ---- sum in rank order and store ----
+#pragma unroll 1
+        for (int c = 0; c < NUM_CHUNKS; ++c) {
+          uint32_t packed[32];
+          const int col0 = t.n_blk * BN + c * 64;
+#pragma unroll 1
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t v[32];
+            float sum[32];
+            tmem_ld_32x32b_x32(t_addr + c * 64 + hf * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sum[i] = 0.f;
+            for (int p = 0; p < args.tp; ++p) {
+              if (p == args.rank) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum[i] += __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+              } else if (col0 < args.N) {
+                const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * args.tp + p) * slot_elems +
+                                           static_cast<size_t>(t.m_blk * kTpBM + row) * args.N + col0 + hf * 32;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 u = ld_cg_v4(src + j * 8);
+                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(h[q]);
+                    sum[j * 8 + q * 2] += f.x;
+                    sum[j * 8 + q * 2 + 1] += f.y;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) packed[hf * 16 + i] = pack_bf16x2(sum[2 * i], sum[2 * i + 1]);
+          }
+          const int buf = chunk_counter & 1;
+          if (issuer) tma_wait_group_read<1>();
+          named_bar_sync(1, 128);
+          uint8_t* srow = staging + buf * kTpStaging + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) =
+                make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (issuer) {
+            if (col0 < args.N) tma_store_2d(&tmD, smem_u32(staging + buf * kTpStaging), col0, t.m_blk * kTpBM);
+            tma_commit_group();
+          }
+          ++chunk_counter;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < NUM_CHUNKS; ++c) {
         uint32_t v0[32], v1[32], packed[32];
@@ -530,6 +660,50 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
                                : tp_launch<256, 4, false, 2>(tA, tA, tB, tD, a, stream);
   return b_mn_major ? tp_launch<128, 6, true, 2>(tA, tA, tB, tD, a, stream)
                     : tp_launch<128, 6, false, 2>(tA, tA, tB, tD, a, stream);
+}
+
+// GEMM -> all-reduce (one shot). A: [M, K] local (row pitch lda); B: [N, K] or [K, N]; D: [M, N] bf16, the full sum
+// on every rank. `recv_local` / `recv_peer[p]`: peer-mapped 2 * tp * ceil(M/128)*128 * N bf16; `tile_flags_*`:
+// peer-mapped 2 * tp * flag_tiles ints, persistent across calls, zero at the start of the job. Any M >= 1.
+int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
+                          int b_mn_major, int tp, int rank, int epoch, void* recv_local, void* const* recv_peer,
+                          int* tile_flags_local, int* const* tile_flags_peer, int flag_tiles, int* status,
+                          cudaStream_t stream) {
+  if (tp < 2 || tp > kTpMaxRanks || M < 1 || K % 8 || N < 128 || N % 64 || lda % 8 || ldd % 8) {
+    mfb_host::set_error("tp_gemm_allreduce: unsupported M=%d N=%d K=%d tp=%d", M, N, K, tp);
+    return 1;
+  }
+  TpArgs a = {};
+  a.M = M; a.N = N; a.K = K; a.tp = tp; a.rank = rank; a.epoch = epoch;
+  a.num_m_blocks = (M + kTpBM - 1) / kTpBM; a.rows_per_chunk = a.num_m_blocks * kTpBM; a.status = status;
+  a.recv_local = (__nv_bfloat16*)recv_local; a.tile_flags_local = tile_flags_local;
+  for (int p = 0; p < tp; ++p) {
+    a.recv_peer[p] = (__nv_bfloat16*)recv_peer[p]; a.tile_flags_peer[p] = tile_flags_peer[p];
+    if ((reinterpret_cast<uintptr_t>(recv_peer[p]) & 15) || (reinterpret_cast<uintptr_t>(tile_flags_peer[p]) & 3)) {
+      mfb_host::set_error("tp_gemm_allreduce: receive buffers must be 16-byte aligned");
+      return 1;
+    }
+  }
+  // few row blocks (decode): narrower tiles put more SMs to work
+  const bool bn256 = N >= 256 && a.num_m_blocks * ((N + 255) / 256) >= 96;
+  const int BN = bn256 ? 256 : 128;
+  a.num_n_blocks = (N + BN - 1) / BN;
+  if (a.num_m_blocks * a.num_n_blocks > flag_tiles) {
+    mfb_host::set_error("tp_gemm_allreduce: %d tiles exceed the %d flags provided", a.num_m_blocks * a.num_n_blocks, flag_tiles);
+    return 1;
+  }
+  CUtensorMap tA, tB, tD;
+  int rc;
+  const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((rc = mfb_host::make_tmap_2d(&tA, A, 2, BF, M, K, lda, kTpBM, kTpBK))) return 20 + rc;
+  if (b_mn_major) rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, K, N, ldb, kTpBK, 64);
+  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, BN, kTpBK);
+  if (rc) return 40 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, M, N, ldd, kTpBM, 64))) return 50 + rc;
+  if (bn256) return b_mn_major ? tp_launch<256, 4, true, 3>(tA, tA, tB, tD, a, stream)
+                               : tp_launch<256, 4, false, 3>(tA, tA, tB, tD, a, stream);
+  return b_mn_major ? tp_launch<128, 6, true, 3>(tA, tA, tB, tD, a, stream)
+                    : tp_launch<128, 6, false, 3>(tA, tA, tB, tD, a, stream);
 }
 
 // Upper bound of ceil(N / BN) that the flag arrays must provide room for.

@@ -47,6 +47,19 @@ def enabled(config, x: torch.Tensor) -> bool:
     return x.shape[0] % 128 == 0 and x.shape[1] % 64 == 0
 
 
+def allreduce_enabled(config, x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """True when the one-shot GEMM -> all-reduce kernel can serve a row-parallel layer without sequence parallelism
+    (tensor-parallel inference): bf16 on CUDA, no gradient needed, at most ``fused_tp.AR_MAX_ROWS`` tokens."""
+    if _FORCE_OFF or not getattr(config, "fused_tp_comm", False) or not x.is_cuda or x.dim() != 2:
+        return False
+    if ps.get_tensor_model_parallel_world_size() == 1 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return False
+    if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+        return False
+    from . import fused_tp
+    return fused_tp.allreduce_shapes_ok(x.shape[0], x.shape[1], weight.shape[0])
+
+
 def moe_enabled(config, x: torch.Tensor) -> bool:
     """True when the device-side MoE exchange (``parallel/fused_moe.py``) can serve this call: bf16 on CUDA,
     any expert-parallel size up to 8 (size 1 = local permute kernels)."""
@@ -64,6 +77,11 @@ def allgather_linear(x, w):
 def linear_reduce_scatter(x, w):
     from . import fused_tp
     return fused_tp.linear_reduce_scatter(x, w)
+
+
+def linear_all_reduce(x, w):
+    from . import fused_tp
+    return fused_tp.gemm_all_reduce(x, w)
 
 
 def moe_dispatch_experts_combine(layer, hidden, probs, ids):

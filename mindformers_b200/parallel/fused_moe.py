@@ -78,6 +78,7 @@ class MoEExchange:
         self._shared: Dict[tuple, object] = {}
         self._in_flight: Dict[object, set] = {}
         self._symm_names: list = []
+        self.alloc_rows = None      # rows of the symmetric row buffers, agreed over the group
         if self.world > 1:
             words = self.lib.mfb_moe_flag_words()
             flags = symm_mem.allocate(f"moe.flags.{id(group)}.{self.H}.{self.E}.{self.k}", words * 4, group, self.dev)
@@ -94,26 +95,39 @@ class MoEExchange:
 
     # ------------------------------------------------------------------------------------------------
     def rows_cap(self, T: int) -> int:
+        """Rows of this rank's receive buffers for ``T`` local tokens.
+
+        Symmetric allocations must have one size on all ranks, so the first call (and the first one after a growth)
+        agrees on the largest request of the group with one all-reduce and a host read; later requests are cut to
+        that size. A rank that then needs more rows than agreed overflows, which ``adapt_capacity`` repairs."""
         cap = int(T * self.k * (self.factor if self.world > 1 else 1.0)) + self.E_local * (BLOCK - 1)
-        return (cap + BLOCK - 1) // BLOCK * BLOCK
+        cap = (cap + BLOCK - 1) // BLOCK * BLOCK
+        if self.world <= 1:
+            return cap
+        if self.alloc_rows is None:
+            t = torch.tensor([cap], dtype=torch.int64, device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            self.alloc_rows = int(t.item())
+        return min(cap, self.alloc_rows)
 
     def row_buffer(self, tag: str, rows: int):
-        """``(tensor [rows, H] bf16, peer pointer array)``; peer-mapped when the group has more than one rank."""
-        key = (tag, rows)
-        hit = self._shared.get(key)
-        if hit is not None:
-            return hit
+        """``(tensor [rows, H] bf16, peer pointer array)``; peer-mapped when the group has more than one rank (then
+        the allocation has ``alloc_rows`` rows on every rank and the first ``rows`` are returned)."""
+        hit = self._shared.get(tag)
+        if hit is not None and hit[0].shape[0] >= rows:
+            return hit[0][:rows], hit[1]
         if self.world > 1:
-            name = f"moe.{tag}.{rows}.{self.H}.{self.E}.{id(self.group)}"
+            full = max(self.alloc_rows or rows, rows)
+            name = f"moe.{tag}.{full}.{self.H}.{self.E}.{id(self.group)}"
             self._symm_names.append(name)
-            buf = symm_mem.allocate(name, rows * self.H * 2, self.group, self.dev)
-            t = buf.tensor.view(torch.bfloat16)[:rows * self.H].view(rows, self.H)
+            buf = symm_mem.allocate(name, full * self.H * 2, self.group, self.dev)
+            t = buf.tensor.view(torch.bfloat16)[:full * self.H].view(full, self.H)
             ptrs = self._arr(*[int(p) for p in buf.ptrs])
         else:
             t = torch.empty(rows, self.H, dtype=torch.bfloat16, device=self.dev)
             ptrs = self._arr(t.data_ptr())
-        self._shared[key] = (t, ptrs)
-        return t, ptrs
+        self._shared[tag] = (t, ptrs)
+        return t[:rows], ptrs
 
     def acquire_slot(self, layer_key) -> int:
         """Row buffers of a layer stay in use from its forward to the end of its backward; a second forward of
@@ -163,6 +177,7 @@ class MoEExchange:
             symm_mem.free(name, self.group)
         self._symm_names.clear()
         self._shared.clear()
+        self.alloc_rows = None
         logger.warning("expert-parallel receive buffers overflowed: moe_ep_buffer_factor %.2f -> %.2f "
                        "(set it in the model config to avoid the dropped rows of the first steps)", old, self.factor)
         return True

@@ -32,6 +32,16 @@ _lib.optional_entry("mfb_tp_gemm_reduce_scatter",
                      ctypes.c_void_p, ctypes.c_void_p])
 
 
+_lib.optional_entry("mfb_tp_gemm_allreduce",
+                    [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                     ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                     ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                     ctypes.c_void_p, ctypes.c_void_p])
+
+AR_FLAG_TILES = 8192          # tiles per call that the all-reduce flag arrays have room for
+AR_MAX_ROWS = 4096            # above this the two-step path (reduce-scatter + all-gather) moves fewer bytes
+
+
 class TpCommContext:
     """Symmetric buffers and epochs of one tensor-parallel group."""
 
@@ -45,6 +55,10 @@ class TpCommContext:
         self.xs = None
         self.recv = None
         self.max_tiles = 0
+        self.ar_epoch = 0
+        self.ar_flags = None
+        self.ar_recv = None
+        self.ar_elems = 0
 
     def _ptr_array(self, ptrs):
         arr = (ctypes.c_void_p * 8)()
@@ -70,6 +84,20 @@ class TpCommContext:
             self.recv = symm_mem.allocate(f"tp_recv_{recv_elems}", 2 * self.tp * recv_elems * 2, self.group, self.device)
             torch.cuda.synchronize()
             self.recv.handle.barrier()
+
+    def ensure_allreduce(self, elems: int):
+        """Receive slots (2 parities x tp ranks x ``elems`` bf16) and tile flags of the one-shot all-reduce;
+        collective over the TP group when something has to be allocated."""
+        if self.ar_flags is None:
+            self.ar_flags = symm_mem.allocate("tp_ar_flags", 2 * self.tp * AR_FLAG_TILES * 4, self.group, self.device)
+            self.ar_flags.tensor.zero_()
+            torch.cuda.synchronize()
+            self.ar_flags.handle.barrier()
+        if elems > self.ar_elems:
+            self.ar_elems = elems
+            self.ar_recv = symm_mem.allocate(f"tp_ar_recv_{elems}", 2 * self.tp * elems * 2, self.group, self.device)
+            torch.cuda.synchronize()
+            self.ar_recv.handle.barrier()
 
     # views into the flag buffer (ints)
     def ready_ptrs(self):
@@ -149,6 +177,37 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) ->
     _lib.check(rc, "mfb_tp_gemm_reduce_scatter")
     _lib.count_launch()
     return y
+
+
+def gemm_all_reduce(x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> torch.Tensor:
+    """``all_reduce(x @ W^T)`` with identical bits on every rank: ``x`` ``[T, K_local]`` (any ``T``), ``w``
+    ``[N, K_local]`` (or ``[K_local, N]``). The row-parallel layers of tensor-parallel inference use it
+    (reference: ``parallel_core/inference/tensor_parallel/layers.py`` ``RowParallelLinear`` + all-reduce)."""
+    ctx = context()
+    tp, rank = ctx.tp, ctx.rank
+    T, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    rows = (T + 127) // 128 * 128
+    ctx.ensure_allreduce(rows * N)
+    ctx.ar_epoch += 1
+    if not x.is_contiguous():
+        x = x.contiguous()
+    y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    recv = list(ctx.ar_recv.ptrs)
+    tf = list(ctx.ar_flags.ptrs)
+    st = _lib.status_word(x.device)
+    rc = _lib.get_lib().mfb_tp_gemm_allreduce(x.data_ptr(), w.data_ptr(), y.data_ptr(), T, N, K, x.stride(0),
+                                              w.stride(0), y.stride(0), int(b_mn), tp, rank, ctx.ar_epoch, recv[rank],
+                                              ctx._ptr_array(recv), tf[rank], ctx._ptr_array(tf), AR_FLAG_TILES,
+                                              st.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_tp_gemm_allreduce")
+    _lib.count_launch()
+    return y
+
+
+def allreduce_shapes_ok(T: int, K: int, N: int) -> bool:
+    tiles = ((T + 127) // 128) * ((N + 127) // 128)
+    return 1 <= T <= AR_MAX_ROWS and K % 8 == 0 and N >= 128 and N % 64 == 0 and tiles <= AR_FLAG_TILES
 
 
 class _AllGatherLinearFn(torch.autograd.Function):

@@ -191,7 +191,11 @@ class RowParallelLinear(nn.Module):
                 else:
                     y = M.reduce_scatter_to_sequence_parallel_region(Fn.linear(x, self.weight))
             else:
-                y = M.reduce_from_tensor_model_parallel_region(Fn.linear(x, self.weight))
+                from .. import fused_comm
+                if fused_comm.allreduce_enabled(self.config, x, self.weight):
+                    y = fused_comm.linear_all_reduce(x, self.weight)      # inference: GEMM -> all-reduce in one kernel
+                else:
+                    y = M.reduce_from_tensor_model_parallel_region(Fn.linear(x, self.weight))
         else:
             y = Fn.linear(x, self.weight)
         if self.bias is not None and not self.skip_bias_add:

@@ -80,8 +80,32 @@ def main():
         ref_dx = g_full.float() @ w.detach().float()
         ref_dw = g_full.float().t() @ x.detach().float()
         res[f"rs_{tag}"] = {"y": rel(y, ref_y), "dx": rel(x.grad, ref_dx), "dw": rel(w.grad, ref_dw)}
+    # GEMM -> all-reduce (inference): any token count, identical bits on every rank
+    for (Tq, K, N, tag) in [(1, 1024, 512, "decode1"), (64, 7168 // tp, 2048, "decode64"), (200, 768, 1024, "odd"),
+                            (2048, 14336 // tp, 4096, "prefill")]:
+        torch.manual_seed(8)
+        x = (torch.randn(Tq, K, device="cuda") * 0.5 + 0.1 * rank).to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        y = fused_tp.gemm_all_reduce(x, w)
+        y2 = fused_tp.gemm_all_reduce(x, w)          # the next call lands in the other parity
+        part = x.float() @ w.float().t()
+        dist.all_reduce(part, group=grp)
+        same = [torch.empty_like(y) for _ in range(tp)]
+        dist.all_gather(same, y, group=grp)
+        res[f"ar_{tag}"] = {"y": rel(y, part), "repeat": rel(y2, part),
+                            "rank_mismatch": float(max((s - same[0]).abs().max().item() for s in same))}
     res["status"] = _lib.read_status()
     if args.bench:
+        for (Tq, K3, N3, tag) in [(64, 14336 // tp, 4096, "decode64_fc2"), (1024, 14336 // tp, 4096, "chunk1024_fc2")]:
+            x3 = torch.randn(Tq, K3, device="cuda").to(torch.bfloat16)
+            w3 = (torch.randn(N3, K3, device="cuda") * 0.05).to(torch.bfloat16)
+            t_f = timeit(lambda: fused_tp.gemm_all_reduce(x3, w3), iters=50)
+            t_n = timeit(lambda: M.all_reduce(torch.matmul(x3, w3.t()), grp, tp), iters=50)
+            res[f"bench_ar_{tag}"] = {"fused_ms": t_f, "nccl_cublas_ms": t_n,
+                                      "bytes_over_nvlink": (tp - 1) * Tq * N3 * 2,
+                                      "nvlink_floor_ms": (tp - 1) * Tq * N3 * 2 / 770e9 * 1e3,
+                                      "gemm_floor_ms": 2.0 * Tq * N3 * K3 / 1415.7e12 * 1e3,
+                                      "weight_read_floor_ms": N3 * K3 * 2 / 6523.7e9 * 1e3}
         K, N = 4096, 14336 * 2 // tp
         x_local = (torch.randn(T // tp, K, device="cuda")).to(torch.bfloat16)
         w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
