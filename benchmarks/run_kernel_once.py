@@ -3,7 +3,7 @@ the target of `ncu -k regex:<kernel> -c N`. Usage: python benchmarks/run_kernel_
 
 Cases: gemm (fc1 forward 4096 x 28672 x 4096, then dgrad and wgrad layouts), fa (forward + backward, S=4096, 32/8
 heads), rmsnorm, swiglu, rope, ce (4096 x 128256 logits), adamw (64 M parameters), router (E=128 top-8 and E=256
-group-limited), paged (decode attention, 64 sequences of 2048 tokens, block 128), moe (single-rank exchange kernels).
+group-limited), paged (decode attention, 64 sequences of 2048 tokens, block 128), mla (latent-cache decode, 64 x 2304 tokens), moe (single-rank exchange kernels).
 """
 import argparse
 import os
@@ -121,6 +121,36 @@ def paged():
     print(f"paged decode: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of KV ({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), splits {splits}")
 
 
+def mla():
+    """MLA decode: 64 sequences of 2304 cached tokens, 16 heads per rank (128 heads over tp 8) and all 128 heads."""
+    from mindformers_b200.inference.paged_attention import mla_decode_attention
+    B, ctx, blk = 64, 2304, 128
+    nblocks = B * ctx // blk
+    cache = bf(nblocks, blk, 1, 576)
+    tables = torch.arange(nblocks, device="cuda", dtype=torch.int32).view(B, ctx // blk).contiguous()
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+
+    class Holder:
+        pass
+
+    for nh in (16, 128):
+        q = bf(B, nh, 576, scale=0.3)
+        h = Holder()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for i in range(5):
+            if i == 2:
+                ev[0].record()
+            out = mla_decode_attention(q, cache, tables, lens, blk, 192 ** -0.5, h)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / 3
+        kv_bytes = B * ctx * 576 * 2
+        flops = 2.0 * B * ctx * nh * (576 + 512)
+        print(f"mla decode heads={nh}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of latent cache "
+              f"({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), "
+              f"{flops / ms / 1e9:.0f} TFLOP/s, status {_lib.read_status()}")
+
+
 def moe():
     from mindformers_b200.parallel.layers.moe import MoELayer
     from mindformers_b200.parallel.transformer_config import TransformerConfig
@@ -160,7 +190,7 @@ def fp8():
             Fn.quantize_act_1x128(x)
 
 
-CASES = dict(fp8=fp8, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, moe=moe)
+CASES = dict(fp8=fp8, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

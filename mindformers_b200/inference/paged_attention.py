@@ -132,6 +132,34 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
     return torch.cat(outs, dim=0)
 
 
+def mla_decode_attention(q_cat: torch.Tensor, latent_cache: torch.Tensor, block_tables: torch.Tensor,
+                         context_lens: torch.Tensor, block_size: int, scale: float, holder=None) -> torch.Tensor:
+    """``q_cat [B, heads, 576]`` (absorbed query ‖ rope query) against the paged latent cache
+    ``[num_blocks, block_size, (1,) 576]`` → latent-space output ``[B, heads, 512]``; ``context_lens`` counts the
+    tokens in the cache, the current one included. ``holder`` keeps the scratch buffer between calls."""
+    B, nh, dim = q_cat.shape
+    if dim != 576 or q_cat.dtype != torch.bfloat16 or latent_cache.dtype != torch.bfloat16:
+        raise ValueError("mla_decode_attention: bf16 tensors with a latent width of 512 + 64 are required")
+    lib = _lib.get_lib()
+    max_blocks = block_tables.shape[1]
+    splits = lib.mfb_mla_decode_splits(B, nh, max_blocks * block_size)
+    need = lib.mfb_mla_decode_scratch_bytes(B, nh, splits)
+    scratch = getattr(holder, "_mla_scratch", None) if holder is not None else None
+    if scratch is None or scratch.numel() * 4 < need:
+        scratch = torch.empty((need + 3) // 4, dtype=torch.float32, device=q_cat.device)
+        if holder is not None:
+            holder._mla_scratch = scratch
+    out = torch.empty((B, nh, 512), dtype=torch.bfloat16, device=q_cat.device)
+    num_blocks = latent_cache.shape[0]
+    rc = lib.mfb_mla_decode_attention(q_cat.data_ptr(), latent_cache.data_ptr(), block_tables.data_ptr(),
+                                      context_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), splits, B, nh,
+                                      num_blocks, block_size, max_blocks, float(scale),
+                                      _lib.status_word(q_cat.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_mla_decode_attention")
+    _lib.count_launch(2)
+    return out
+
+
 def mla_paged_attention_forward(attn, q_nope, q_pe, kv_c, k_pe, meta):
     """Multi-latent attention with a latent cache ``[kv_lora ‖ k_pe]``.
 
@@ -148,6 +176,14 @@ def mla_paged_attention_forward(attn, q_nope, q_pe, kv_c, k_pe, meta):
     w = attn.linear_kvb.weight.view(nh, nope + vd, rank)
     w_uk, w_uv = w[:, :nope], w[:, nope:]                                      # [nh, nope, rank], [nh, vd, rank]
     B = cache.context_lens.shape[0]
+    if (not cache.is_prefill and T == B and q_nope.is_cuda and q_nope.dtype == torch.bfloat16 and rank == 512
+            and rope_d == 64 and cache.block_size in (16, 32, 64, 128)):
+        # decode: absorbed queries against the latent cache in one tcgen05 kernel (ops/csrc/mla_decode.cu)
+        q_lat = torch.einsum("bhn,hnr->bhr", q_nope, w_uk)
+        q_cat = torch.cat((q_lat, q_pe.reshape(B, nh, rope_d)), dim=-1).contiguous()
+        o_lat = mla_decode_attention(q_cat, cache.key_cache[layer], cache.block_tables, cache.context_lens,
+                                     cache.block_size, attn.scale, cache)
+        return torch.einsum("bhr,hvr->bhv", o_lat, w_uv).reshape(B, nh * vd)
     lens = cache.context_lens.tolist()
     outs = []
     for b in range(B):

@@ -69,6 +69,10 @@ def _declare(lib):
     sig("mfb_paged_decode_splits", [I, I, I, I])
     lib.mfb_paged_decode_scratch_bytes.argtypes = [I, I, I, I]
     lib.mfb_paged_decode_scratch_bytes.restype = L
+    sig("mfb_mla_decode_attention", [P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
+    sig("mfb_mla_decode_splits", [I, I, I])
+    lib.mfb_mla_decode_scratch_bytes.argtypes = [I, I, I]
+    lib.mfb_mla_decode_scratch_bytes.restype = L
     sig("mfb_gather_cache", [P, P, P, P, I, I, I, I, I, P])
     sig("mfb_dp_reduce_scratch", [])
     sig("mfb_dp_flag_words", [])

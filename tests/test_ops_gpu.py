@@ -369,6 +369,31 @@ def test_paged_decode_attention_split_kv(hd, nq, nkv, block):
         assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
 
 
+@pytest.mark.parametrize("nh,block", [(16, 128), (128, 128), (20, 16), (16, 64)])
+def test_mla_decode_attention(nh, block):
+    """Absorbed-query MLA decode over the paged latent cache against an fp32 reference."""
+    from mindformers_b200.inference.paged_attention import mla_decode_attention
+    torch.manual_seed(nh + block)
+    lens = [1, 127, 128, 300, 2304, 129]
+    B = len(lens)
+    max_blocks = (max(lens) + block - 1) // block + 1
+    nblocks = B * max_blocks + 3
+    cache = (torch.randn(nblocks, block, 1, 576, device="cuda") * 0.5).to(torch.bfloat16)
+    tables = torch.randperm(nblocks)[:B * max_blocks].to(torch.int32).view(B, max_blocks).cuda()
+    q = (torch.randn(B, nh, 576, device="cuda") * 0.3).to(torch.bfloat16)
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = 192 ** -0.5
+    out = mla_decode_attention(q, cache, tables, ctx, block, scale)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    for b, n in enumerate(lens):
+        lat = cache[tables[b].long()].reshape(-1, 576)[:n].float()
+        s = (q[b].float() @ lat.t()) * scale
+        ref = torch.softmax(s, dim=-1) @ lat[:, :512]
+        err = (out[b].float() - ref).abs().max().item()
+        assert err < 2e-2, (b, n, err)
+
+
 @pytest.mark.parametrize("T,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 2048, 7168)])
 def test_fp8_blockscaled_gemm_dense(T, N, K):
     torch.manual_seed(T + N)
