@@ -185,6 +185,25 @@ def mla_paged_attention_forward(attn, q_nope, q_pe, kv_c, k_pe, meta):
                                      cache.block_size, attn.scale, cache)
         return torch.einsum("bhr,hvr->bhv", o_lat, w_uv).reshape(B, nh * vd)
     lens = cache.context_lens.tolist()
+    q_lens = [cache.cu_q[b + 1] - cache.cu_q[b] for b in range(B)]
+    if (cache.is_prefill and q_nope.is_cuda and q_nope.dtype == torch.bfloat16 and nope == 128 and rope_d == 64
+            and vd == 128 and all(ql == n and ql % 128 == 0 and ql > 0 for ql, n in zip(q_lens, lens))):
+        # prefill without history: expand K / V from the latents and run the flash-attention kernel (192 / 128 heads)
+        from ..ops import attention as native
+        kv = attn._col_nosp(attn.linear_kvb, kv_c).view(T, nh, nope + vd)
+        k = torch.cat((kv[..., :nope], k_pe.reshape(T, 1, rope_d).expand(T, nh, rope_d)), dim=-1)
+        v = kv[..., nope:]
+        qf = torch.cat((q_nope, q_pe), dim=-1)
+        if len(set(q_lens)) == 1:
+            S = q_lens[0]
+            o = native.mla_forward(qf.view(B, S, nh, -1), k.view(B, S, nh, -1), v.reshape(B, S, nh, vd), True, attn.scale)
+            return o.reshape(T, nh * vd)
+        outs = []
+        for b in range(B):
+            a, e = cache.cu_q[b], cache.cu_q[b + 1]
+            o = native.mla_forward(qf[a:e].unsqueeze(0), k[a:e].unsqueeze(0), v[a:e].unsqueeze(0), True, attn.scale)
+            outs.append(o.reshape(e - a, nh * vd))
+        return torch.cat(outs, dim=0)
     outs = []
     for b in range(B):
         a, e = cache.cu_q[b], cache.cu_q[b + 1]

@@ -61,6 +61,7 @@ def _declare(lib):
     sig("mfb_split_master", [P, P, P, L, P])
     sig("mfb_join_master", [P, P, P, L, P])
     sig("mfb_flash_attn_fwd", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, F, P, P])
+    sig("mfb_flash_attn_fwd_mla", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, I, F, P, P])
     lib.mfb_flash_attn_bwd_scratch_bytes.argtypes = [I, I, I]
     lib.mfb_flash_attn_bwd_scratch_bytes.restype = L
     sig("mfb_flash_attn_bwd", [P] * 10 + [I, I, I, I] + [L] * 8 + [I, F, P, P])

@@ -138,6 +138,31 @@ def flash_attention(q, k, v, causal=True, scale=None):
     return _AttnFn.apply(q, k, v, causal, scale)
 
 
+def mla_supported(q, k, v) -> bool:
+    """Forward-only kernel for the multi-latent-attention shape: q/k heads of 192, v heads of 128, bf16, sequence a
+    multiple of 128, the same number of q and k heads."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 192 and k.shape[-1] == 192
+            and v.shape[-1] == HEAD_DIM and q.shape[1] % TILE == 0 and q.shape[1] == k.shape[1]
+            and q.shape[2] % k.shape[2] == 0 and k.shape[2] == v.shape[2])
+
+
+def mla_forward(q, k, v, causal: bool = True, scale=None):
+    """q, k ``[B, S, h, 192]``, v ``[B, S, h, 128]`` → ``[B, S, h, 128]``. Inference only (no backward kernel for this
+    shape: training takes the autograd path of ``functional.attention``)."""
+    B, S, nq, dq = q.shape
+    nkv = k.shape[2]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    scale = scale if scale is not None else 1.0 / math.sqrt(dq)
+    out = torch.empty((B * S, nq * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
+    st = _lib.status_word(q.device)
+    rc = _lib.get_lib().mfb_flash_attn_fwd_mla(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, B, S, S,
+                                               nq, nkv, nq * dq, nkv * dq, nkv * HEAD_DIM, out.stride(0), int(causal), 0,
+                                               float(scale), st.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_flash_attn_fwd_mla")
+    _lib.count_launch()
+    return out.view(B, S, nq, HEAD_DIM)
+
+
 # ---- rectangular causal attention: Sq queries at key positions [q_offset, q_offset + Sq) of Sk keys ------------
 def rect_forward(q, k, v, q_offset: int, causal: bool, scale: float):
     """Raw forward: q ``[B,Sq,Hq,128]``, k/v ``[B,Sk,Hkv,128]`` contiguous → ``(out [B*Sq, Hq*128], lse [B,Hq,Sq])``."""

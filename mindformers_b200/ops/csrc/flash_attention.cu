@@ -1,4 +1,5 @@
-// Flash attention forward for sm_100a (head dim 128, bf16, GQA, causal or full), tcgen05 + TMA.
+// Flash attention forward for sm_100a (bf16, GQA, causal or full), tcgen05 + TMA. Head dim 128, or the
+// multi-latent-attention shape: 192 for Q/K (128 + 64 rope columns) with 128 for V and the output.
 //
 // One CTA owns a tile of 128 query rows of one head and walks over the key/value tiles:
 //   S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S in tensor memory
@@ -51,6 +52,9 @@ struct FaArgs {
   int* status;
 };
 
+// HDQK: width of a Q / K head (128 or 192). With 192 the K tile is single-buffered so that everything still fits
+// in shared memory; the next K tile then loads while the softmax of the current one runs.
+template <int HDQK>
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -58,9 +62,12 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr int QK_SUBS = HDQK / 64;                 // 64-column sub-tiles of a Q / K tile
+  constexpr int QK_BYTES = QK_SUBS * kSubBytes;
+  constexpr int KST = (HDQK == 128) ? 2 : 1;         // K stages
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kTileBytes;             // 2 stages
-  uint8_t* sV = sK + 2 * kTileBytes;         // 2 stages
+  uint8_t* sK = sQ + QK_BYTES;               // KST stages
+  uint8_t* sV = sK + KST * QK_BYTES;         // 2 stages
   uint8_t* sP = sV + 2 * kTileBytes;         // 2 P tiles; the first doubles as the O staging buffer
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kTileBytes);
   uint64_t* q_full = bars;          // 1
@@ -118,20 +125,24 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t qb = smem_u32(q_full);
-      mbar_expect_tx(qb, kTileBytes);
-      tma_load_2d(smem_u32(sQ), &tmQ, qb, head * kHd, q_row0);
-      tma_load_2d(smem_u32(sQ) + kSubBytes, &tmQ, qb, head * kHd + 64, q_row0);
+      mbar_expect_tx(qb, QK_BYTES);
+#pragma unroll
+      for (int i = 0; i < QK_SUBS; ++i)
+        tma_load_2d(smem_u32(sQ) + i * kSubBytes, &tmQ, qb, head * HDQK + 64 * i, q_row0);
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(smem_u32(&k_empty[st]), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
+        const int kst = j % KST;
+        const uint32_t kph = (j / KST) & 1;
+        ok = mbar_wait(smem_u32(&k_empty[kst]), kph ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
         if (!ok) break;
-        const uint32_t kb = smem_u32(&k_full[st]);
-        mbar_expect_tx(kb, kTileBytes);
-        const uint32_t kd = smem_u32(sK + st * kTileBytes);
-        tma_load_2d(kd, &tmK, kb, kv_head * kHd, k_row0 + j * kTile);
-        tma_load_2d(kd + kSubBytes, &tmK, kb, kv_head * kHd + 64, k_row0 + j * kTile);
+        const uint32_t kb = smem_u32(&k_full[kst]);
+        mbar_expect_tx(kb, QK_BYTES);
+        const uint32_t kd = smem_u32(sK + kst * QK_BYTES);
+#pragma unroll
+        for (int i = 0; i < QK_SUBS; ++i)
+          tma_load_2d(kd + i * kSubBytes, &tmK, kb, kv_head * HDQK + 64 * i, k_row0 + j * kTile);
         ok = mbar_wait(smem_u32(&v_empty[st]), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
         if (!ok) break;
         const uint32_t vb = smem_u32(&v_full[st]);
@@ -150,18 +161,20 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&k_full[st]), ph, abort_flag, args.status, kStatusWaitTimeoutMma)) return false;
+        const int kst = j % KST;
+        const uint32_t kph = (j / KST) & 1;
+        if (!mbar_wait(smem_u32(&k_full[kst]), kph, abort_flag, args.status, kStatusWaitTimeoutMma)) return false;
         if (!mbar_wait(smem_u32(&s_empty[st]), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * kTileBytes);
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + kst * QK_BYTES);
 #pragma unroll
-        for (int k = 0; k < kHd / 16; ++k) {
+        for (int k = 0; k < HDQK / 16; ++k) {
           const uint32_t off = (k >> 2) * kSubBytes + (k & 3) * 32;
           umma_f16_ss(tmem_S + st * kTile, umma_desc_kmajor_sw128(qa + off), umma_desc_kmajor_sw128(ka + off),
                       IDESC_QK, k > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&s_full[st]));
-        umma_commit(smem_u32(&k_empty[st]));
+        umma_commit(smem_u32(&k_empty[kst]));
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -340,15 +353,16 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 }  // namespace mfb
 
-extern "C" {
+namespace {
 using namespace mfb;
 
 // q: [B*Sq, q_ld] bf16 rows with head h at columns [h*128, h*128+128); k, v likewise with Hkv heads.
 // o: [B*Sq, o_ld]; lse: [B, Hq, Sq] fp32 (may be null). Sq, Sk multiples of 128. Causal: query i of a sequence sits
 // at key position q_offset + i (q_offset a multiple of 128, q_offset + Sq <= Sk) and sees keys up to itself.
-int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
-                          int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
-                          int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
+template <int HDQK>
+int fa_fwd_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                         int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
+                         int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
   if (Sq % kTile || Sk % kTile || Hq % Hkv || B <= 0 || q_offset % kTile || q_offset < 0 ||
       (causal && q_offset + Sq > Sk)) {
     mfb_host::set_error("flash_attn_fwd: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d causal=%d q_offset=%d", B, Sq,
@@ -357,8 +371,8 @@ int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, 
   }
   CUtensorMap tQ, tK, tV, tO;
   int rc;
-  if ((rc = mfb_host::make_tmap_2d(&tQ, q, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sq, (uint64_t)Hq * kHd, q_ld, kTile, 64))) return 20 + rc;
-  if ((rc = mfb_host::make_tmap_2d(&tK, k, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sk, (uint64_t)Hkv * kHd, k_ld, kTile, 64))) return 30 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tQ, q, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sq, (uint64_t)Hq * HDQK, q_ld, kTile, 64))) return 20 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tK, k, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sk, (uint64_t)Hkv * HDQK, k_ld, kTile, 64))) return 30 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tV, v, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sk, (uint64_t)Hkv * kHd, v_ld, kTile, 64))) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tO, o, 2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)B * Sq, (uint64_t)Hq * kHd, o_ld, kTile, 64))) return 50 + rc;
   FaArgs a;
@@ -366,22 +380,43 @@ int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, 
   a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.lse = lse; a.status = status;
-  constexpr int SMEM = 7 * kTileBytes + 18 * 8 + 16 + 1024;
+  constexpr int QK_BYTES = (HDQK / 64) * kSubBytes;
+  constexpr int SMEM = (1 + (HDQK == 128 ? 2 : 1)) * QK_BYTES + 4 * kTileBytes + 18 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(flash_attn_fwd_kernel<HDQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
       mfb_host::set_error("flash_attn_fwd: cannot raise shared memory limit");
       return 10;
     }
     attr_set = true;
   }
   dim3 grid(Sq / kTile, Hq, B);
-  flash_attn_fwd_kernel<<<grid, kFaThreads, SMEM, stream>>>(tQ, tK, tV, tO, a);
+  flash_attn_fwd_kernel<HDQK><<<grid, kFaThreads, SMEM, stream>>>(tQ, tK, tV, tO, a);
   if (cudaGetLastError() != cudaSuccess) {
     mfb_host::set_error("flash_attn_fwd: launch failed");
     return 11;
   }
   return 0;
+}
+
+}  // namespace
+
+extern "C" {
+using namespace mfb;
+
+int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                          int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
+                          int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
+  return fa_fwd_launch<128>(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, q_offset, scale, status,
+                            stream);
+}
+
+// Multi-latent-attention shape: q, k heads of 192 columns (head h at columns [h*192, h*192+192)), v and o heads of 128.
+int mfb_flash_attn_fwd_mla(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                           int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
+                           int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
+  return fa_fwd_launch<192>(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, q_offset, scale, status,
+                            stream);
 }
 
 int mfb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,

@@ -7,16 +7,16 @@
 // A CTA handles (split of the sequence, chunk of 16 heads, sequence). The products are laid out TRANSPOSED so
 // that the token dimension, not the (small) head count, fills the 128 rows of the tensor core:
 //     S^T [128 tokens x 16 heads]   = C_tile [128 x 576] (A, K-major) . Q^T (B, K-major)          -> TMEM, 16 columns
-//     O^T [512 x 64]  (4 x M=128)  += C_tile^T (A, MN-major: the same bytes) . P^T [128 tokens x 64] (B, MN-major)
-// P^T has 16 real head columns; columns 16..63 stay zero, which keeps its rows at the 128 bytes of one swizzle atom.
+//     O^T [512 x 16]  (4 x M=128)  += C_tile^T (A, MN-major: the same bytes) . P^T [16 heads x 128 tokens] (B, K-major)
 // Softmax threads own one token row each; the per-head maximum over the 128 tokens of a tile is a shuffle
 // + shared-memory reduction, per-head sums stay thread-local until the end. O^T is rescaled in TMEM only when
 // a head's maximum grew by more than 2^8 (as in the flash-attention kernel).
 //
-// A tile of 128 tokens is 147 KB, so two tiles do not fit in shared memory. The cache tile is therefore streamed
-// twice through one ring of five 32 KB slots: first as five units for S^T (four column pairs + the rope columns),
-// then as four units for O^T (the second pass hits L2). The producer runs up to five units ahead, which covers the
-// softmax of the current tile.
+// A tile of 128 tokens is 147 KB, so a second tile cannot be prefetched while one is resident, and the chain
+// S^T -> softmax -> O^T of a tile leaves the memory system idle. Instead the cache tile is STREAMED twice through a
+// small ring of 32 KB slots (first five units for S^T: four column pairs + the rope columns; then the four pairs
+// again for O^T, which hit L2), and the kernel is sized so that TWO CTAs share an SM (88 KB of shared memory and
+// 256 TMEM columns each): while one CTA sits in its softmax, the other one streams.
 //
 // Roles (192 threads): warp 0 = TMA producer (block-table lookups), warp 1 = MMA issuer + TMEM owner,
 // warps 2..5 = softmax / rescale / epilogue. Every wait is bounded (see common.cuh). Partial results of the splits
@@ -33,7 +33,9 @@ constexpr int kMlaRope = 64;
 constexpr int kMlaDim = kMlaRank + kMlaRope;
 constexpr int kMlaSub = kMlaTile * 128;    // [128 tokens][64 columns] swizzled sub-tile, 16 KB
 constexpr int kMlaUnit = 2 * kMlaSub;      // ring slot: a pair of sub-tiles (128 columns)
-constexpr int kMlaSlots = 5;
+constexpr int kMlaSlots = 2;
+constexpr int kMlaPBytes = 2 * kMlaHeads * 128;   // P^T: two [16 heads][64 tokens] K-major sub-tiles
+constexpr int kMlaTmemCols = 256;
 constexpr int kMlaQSub = kMlaHeads * 128;  // [16 heads][64 columns], 2 KB
 constexpr int kMlaQBytes = 9 * kMlaQSub;
 constexpr float kMlaRescale = 8.0f;
@@ -54,19 +56,19 @@ __device__ __forceinline__ float mla_ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kMlaThreads, 1)
+__global__ void __launch_bounds__(kMlaThreads, 2)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmC, const MlaArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sRing = smem;                               // 5 x 32 KB
-  uint8_t* sP = sRing + kMlaSlots * kMlaUnit;          // 16 KB
-  uint8_t* sQ = sP + kMlaSub;                          // 18 KB
+  uint8_t* sRing = smem;                               // 2 x 32 KB
+  uint8_t* sP = sRing + kMlaSlots * kMlaUnit;          // 4 KB
+  uint8_t* sQ = sP + kMlaPBytes;                       // 18 KB
   float* red = reinterpret_cast<float*>(sQ + kMlaQBytes);          // [4 warps][16]
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 4 * kMlaHeads);
   uint64_t* q_full = bars;                  // 1
-  uint64_t* full = bars + 1;                // 5
-  uint64_t* empty = bars + 6;               // 5
+  uint64_t* full = bars + 1;                // up to 5
+  uint64_t* empty = bars + 6;               // up to 5
   uint64_t* s_full = bars + 11;             // 2
   uint64_t* s_empty = bars + 13;            // 2
   uint64_t* p_ready = bars + 15;            // 1
@@ -84,9 +86,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int n_tiles = t1 > t0 ? t1 - t0 : 0;
   const int head0 = chunk * kMlaHeads;
 
-  // P^T columns 16..63 are never written: zero the buffer once
-  for (int i = threadIdx.x; i < kMlaSub / 16; i += kMlaThreads)
-    reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(smem_u32(q_full), 1);
@@ -105,7 +104,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_alloc(smem_u32(tmem_holder), kMlaTmemCols);
     tmem_relinquish();
   }
   fence_proxy_async_smem();
@@ -113,8 +112,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_O = tmem_base;              // 4 blocks of 64 columns
-  const uint32_t tmem_S = tmem_base + 256;        // 2 buffers of 16 columns, 32 apart
+  const uint32_t tmem_O = tmem_base;              // 4 blocks of 16 columns, 32 apart
+  const uint32_t tmem_S = tmem_base + 128;        // 2 buffers of 16 columns, 32 apart
 
   if (warp == 0) {
     // ------------------------------------ producer ------------------------------------
@@ -137,6 +136,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const int pg = (tok0 + i * bs < len) ? table[tok0 / bs + i] : first_page;
           page_row[i] = pg * bs;
         }
+        // two passes: [P0 P1 P2 P3 R] for S^T, then [P0 P1 P2 P3] again for O^T
         for (int u = 0; u < 9 && ok; ++u) {
           const int slot = unit % kMlaSlots;
           const uint32_t ph = (unit / kMlaSlots) & 1;
@@ -160,7 +160,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // ------------------------------------ MMA issuer ------------------------------------
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t IDESC_S = umma_idesc_bf16(kMlaTile, kMlaHeads, 0, 0);   // A = cache K-major, B = Q K-major
-      constexpr uint32_t IDESC_PV = umma_idesc_bf16(kMlaTile, 64, 1, 1);         // A = cache MN-major, B = P^T MN-major
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(kMlaTile, kMlaHeads, 1, 0);  // A = cache MN-major, B = P^T K-major
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, args.status, kStatusWaitTimeoutMma);
       const uint32_t qa = smem_u32(sQ), pa = smem_u32(sP);
       uint32_t unit = 0;
@@ -177,8 +177,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!ok) break;
           tc_fence_after();
           const uint32_t ca = smem_u32(sRing + slot * kMlaUnit);
-          const int ksteps = (u == 4) ? 4 : 8;
-          const int qsub0 = (u == 4) ? 8 : 2 * u;
+          const bool rope = (u == 4);
+          const int ksteps = rope ? 4 : 8;
+          const int qsub0 = rope ? 8 : 2 * u;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             if (k < ksteps) {
@@ -205,8 +206,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int k = 0; k < kMlaTile / 16; ++k) {
             const uint64_t a_desc = umma_desc_mnmajor_sw128(ca + k * 16 * 128, kMlaSub);
-            const uint64_t b_desc = umma_desc_mnmajor_sw128(pa + k * 16 * 128, kMlaSub);
-            umma_f16_ss(tmem_O + m * 64, a_desc, b_desc, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+            const uint64_t b_desc = umma_desc_kmajor_sw128(pa + (k >> 2) * (kMlaHeads * 128) + (k & 3) * 32);
+            umma_f16_ss(tmem_O + m * 32, a_desc, b_desc, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty[slot]));
           ++unit;
@@ -276,22 +277,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int m = 0; m < 4; ++m) {
             uint32_t r[16];
-            tmem_ld_32x32b_x16(tmem_O + lane_base + m * 64, r);
+            tmem_ld_32x32b_x16(tmem_O + lane_base + m * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int h = 0; h < kMlaHeads; ++h) r[h] = __float_as_uint(__uint_as_float(r[h]) * alpha[h]);
-            tmem_st_32x32b_x16(tmem_O + lane_base + m * 64, r);
+            tmem_st_32x32b_x16(tmem_O + lane_base + m * 32, r);
           }
           tmem_st_wait();
         }
       }
       ok = named_bar_and(2, 128, ok);               // also orders the reads of `red` before the next tile's writes
       if (!ok) break;
-      uint8_t* prow = sP + row * 128;
-      *reinterpret_cast<uint4*>(prow + ((0 ^ (row & 7)) << 4)) =
-          make_uint4(pack_bf16x2(s[0], s[1]), pack_bf16x2(s[2], s[3]), pack_bf16x2(s[4], s[5]), pack_bf16x2(s[6], s[7]));
-      *reinterpret_cast<uint4*>(prow + ((1 ^ (row & 7)) << 4)) =
-          make_uint4(pack_bf16x2(s[8], s[9]), pack_bf16x2(s[10], s[11]), pack_bf16x2(s[12], s[13]), pack_bf16x2(s[14], s[15]));
+      // P^T[h][token] as a K-major operand: sub-tile of 64 tokens, row h of 128 bytes, 16-byte chunks swizzled by row
+      {
+        uint8_t* pcol = sP + (row >> 6) * (kMlaHeads * 128) + (row & 7) * 2;
+        const int chunk = (row & 63) >> 3;
+#pragma unroll
+        for (int h = 0; h < kMlaHeads; ++h)
+          *reinterpret_cast<__nv_bfloat16*>(pcol + h * 128 + ((chunk ^ (h & 7)) << 4)) = __float2bfloat16_rn(s[h]);
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(p_ready));
@@ -327,7 +331,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
         uint32_t r[16];
-        tmem_ld_32x32b_x16(tmem_O + lane_base + m * 64, r);
+        tmem_ld_32x32b_x16(tmem_O + lane_base + m * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int h = 0; h < kMlaHeads; ++h) {
@@ -341,7 +345,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, kMlaTmemCols);
   }
 }
 
@@ -379,12 +383,18 @@ using namespace mfb;
 
 // Number of sequence splits that fills the GPU for a batch of B sequences of up to max_len tokens.
 int mfb_mla_decode_splits(int B, int num_heads, int max_len) {
+  // cost of a choice = waves of CTAs over the 2 x 148 resident CTAs x (tiles per CTA + about one tile of fixed work per CTA)
   const int chunks = (num_heads + kMlaHeads - 1) / kMlaHeads;
   const int tiles = (max_len + kMlaTile - 1) / kMlaTile;
-  int s = (2 * 148 + B * chunks - 1) / (B * chunks);
-  if (s > tiles) s = tiles;
-  if (s > 32) s = 32;
-  return s < 1 ? 1 : s;
+  int best = 1;
+  long long best_cost = -1;
+  for (int s = 1; s <= tiles && s <= 32; ++s) {
+    const long long ctas = static_cast<long long>(B) * chunks * s;
+    const long long waves = (ctas + 295) / 296;          // two CTAs per SM
+    const long long cost = waves * ((tiles + s - 1) / s + 1);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
 }
 
 long long mfb_mla_decode_scratch_bytes(int B, int num_heads, int splits) {
@@ -412,7 +422,7 @@ int mfb_mla_decode_attention(const void* q, const void* cache, const int* block_
   a.part_o = reinterpret_cast<float*>(scratch);
   a.part_ml = a.part_o + static_cast<size_t>(B) * splits * num_heads * kMlaRank;
   a.status = status;
-  constexpr int SMEM = kMlaSlots * kMlaUnit + kMlaSub + kMlaQBytes + 4 * kMlaHeads * 4 + 18 * 8 + 16 + 1024;
+  constexpr int SMEM = kMlaSlots * kMlaUnit + kMlaPBytes + kMlaQBytes + 4 * kMlaHeads * 4 + 18 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {

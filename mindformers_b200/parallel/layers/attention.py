@@ -250,7 +250,7 @@ class MLASelfAttention(nn.Module):
         if layer.tp > 1:
             from .. import mappings as M
             x = M.copy_to_tensor_model_parallel_region(x)
-        y = Fn.linear(x, layer.weight)
+        y = layer._mm(x)
         if layer.bias is not None:
             y = y + layer.bias
         return y

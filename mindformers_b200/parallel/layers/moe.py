@@ -214,7 +214,30 @@ class GroupedMLP(nn.Module):
             p.allreduce = False          # reduced over the expert-data-parallel group only
             p.is_expert = True
 
+    w1_fp8 = w2_fp8 = w1_scale_inv = w2_scale_inv = None
+
+    def quantize_fp8_(self) -> bool:
+        """Inference: replace the bf16 expert weights by block-scaled fp8 ones (``[E, out, in]`` e4m3 with one fp32
+        scale per 128 x 128 block, the DeepSeek-V3 checkpoint format)."""
+        H, F2 = self.weight1.shape[1], self.weight1.shape[2]
+        Fh = self.weight2.shape[1]
+        if H % 128 or F2 % 128 or Fh % 128:
+            return False
+        self.w1_fp8, self.w1_scale_inv = Fn.quantize_weight_128x128(self.weight1.detach().transpose(1, 2).contiguous())
+        self.w2_fp8, self.w2_scale_inv = Fn.quantize_weight_128x128(self.weight2.detach().transpose(1, 2).contiguous())
+        self._parameters.pop("weight1", None)
+        self._parameters.pop("weight2", None)
+        self.weight1 = self.weight2 = None
+        return True
+
     def forward(self, x, plan: PermutePlan):
+        if self.w1_fp8 is not None:
+            xq, sa = Fn.quantize_act_1x128(x)
+            h = Fn.fp8_gemm(xq, sa, self.w1_fp8, self.w1_scale_inv, block_group=plan.block_group,
+                            num_blocks=plan.num_blocks)
+            hq, sh = Fn.quantize_act_1x128(Fn.swiglu(h))
+            return Fn.fp8_gemm(hq, sh, self.w2_fp8, self.w2_scale_inv, block_group=plan.block_group,
+                               num_blocks=plan.num_blocks)
         h = _GroupedLinearFn.apply(x, self.weight1, plan.block_group, plan.num_blocks, plan.group_offsets)
         h = Fn.swiglu(h)
         return _GroupedLinearFn.apply(h, self.weight2, plan.block_group, plan.num_blocks, plan.group_offsets)
@@ -309,7 +332,33 @@ class MoELayer(nn.Module):
         self.shared_experts = SharedExpertMLP(config) if config.moe_shared_expert_intermediate_size else None
         self.dispatcher = MoEAlltoAllTokenDispatcher(config)
 
+    def _tp_sliced(self, hidden):
+        """Tensor-parallel attention + expert-parallel MoE without sequence parallelism (the inference layout of the
+        reference's DeepSeek-V3 model, ``research/deepseek3/deepseek3_model_infer.py``): every tensor-parallel rank
+        holds all tokens, so each one routes only its 1/tp slice of them through the experts and the slices are
+        all-gathered afterwards. Tokens are padded to a multiple of tp."""
+        tp, rank = ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank()
+        T = hidden.shape[0]
+        per = -(-T // tp)
+        pad = per * tp - T
+        x = torch.nn.functional.pad(hidden, (0, 0, 0, pad)) if pad else hidden
+        mine = x[rank * per:(rank + 1) * per].contiguous()
+        out, aux = self._forward_local(mine, with_shared=False)
+        full = torch.empty((per * tp, out.shape[1]), dtype=out.dtype, device=out.device)
+        dist.all_gather_into_tensor(full, out.contiguous(), group=ps.get_tensor_model_parallel_group())
+        full = full[:T]
+        if self.shared_experts is not None:       # tensor-parallel MLP: runs on all tokens of every rank
+            full = full + self.shared_experts(hidden)
+        return full, aux
+
     def forward(self, hidden):
+        cfg = self.config
+        if (ps.get_tensor_model_parallel_world_size() > 1 and not cfg.sequence_parallel
+                and ps.get_expert_model_parallel_world_size() > 1 and not torch.is_grad_enabled()):
+            return self._tp_sliced(hidden)
+        return self._forward_local(hidden)
+
+    def _forward_local(self, hidden, with_shared: bool = True):
         probs, ids, aux = self.router(hidden)
         from .. import fused_comm
         if fused_comm.moe_enabled(self.config, hidden):
@@ -318,6 +367,6 @@ class MoELayer(nn.Module):
             x, plan, ctx = self.dispatcher.dispatch(hidden, ids)
             y = self.experts(x, plan)
             out = self.dispatcher.combine(y, plan, ctx, probs.to(hidden.dtype))
-        if self.shared_experts is not None:
+        if with_shared and self.shared_experts is not None:
             out = out + self.shared_experts(hidden)
         return out, aux

@@ -93,7 +93,38 @@ class VocabParallelEmbedding(nn.Module):
         return out
 
 
-class ColumnParallelLinear(nn.Module):
+class _Fp8WeightMixin:
+    """Inference-time block-scaled fp8 weights (DeepSeek-V3 checkpoint format: e4m3 values with one fp32
+    ``weight_scale_inv`` per 128 x 128 block, reference ``toolkit/weight_convert/deepseekv3`` ``weight_dequant``).
+
+    ``quantize_fp8_()`` replaces the bf16 parameter by the buffers ``weight_fp8`` / ``weight_scale_inv``;
+    ``load_fp8_(w, s)`` installs checkpoint tensors directly. ``_mm`` then runs the fp8 GEMM with activations
+    quantised per 1 x 128 block on the fly. Layers whose shape is not a multiple of 128 stay in bf16.
+    """
+    weight_fp8 = None
+    weight_scale_inv = None
+
+    def quantize_fp8_(self) -> bool:
+        w = self.weight
+        if w is None or w.dim() != 2 or w.shape[0] % 128 or w.shape[1] % 128:
+            return False
+        wq, scale = Fn.quantize_weight_128x128(w.detach())
+        return self.load_fp8_(wq, scale)
+
+    def load_fp8_(self, wq: torch.Tensor, scale_inv: torch.Tensor) -> bool:
+        self._parameters.pop("weight", None)
+        self.weight = None
+        self.weight_fp8 = wq
+        self.weight_scale_inv = scale_inv.float().contiguous()
+        return True
+
+    def _mm(self, x: torch.Tensor, w: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if w is None and self.weight_fp8 is not None:
+            return Fn.fp8_linear(x, self.weight_fp8, self.weight_scale_inv)
+        return Fn.linear(x, self.weight if w is None else w)
+
+
+class ColumnParallelLinear(_Fp8WeightMixin, nn.Module):
     """``Y = X W^T`` with ``W`` split along its output rows."""
 
     def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
@@ -131,18 +162,19 @@ class ColumnParallelLinear(nn.Module):
 
     def forward(self, x: torch.Tensor, weight: Optional[torch.Tensor] = None):
         w = self.weight if weight is None else weight
+        fp8 = weight is None and self.weight_fp8 is not None
         bias = None if self.skip_bias_add else self.bias
         if self.tp > 1:
             if self.sequence_parallel:
                 from .. import fused_comm
-                if fused_comm.enabled(self.config, x):
+                if not fp8 and fused_comm.enabled(self.config, x):
                     y = fused_comm.allgather_linear(x, w)
                 else:
-                    y = Fn.linear(M.gather_from_sequence_parallel_region(x), w)
+                    y = self._mm(M.gather_from_sequence_parallel_region(x), weight)
             else:
-                y = Fn.linear(M.copy_to_tensor_model_parallel_region(x), w)
+                y = self._mm(M.copy_to_tensor_model_parallel_region(x), weight)
         else:
-            y = Fn.linear(x, w)
+            y = self._mm(x, weight)
         if bias is not None:
             y = y + bias
         if self.gather_output and self.tp > 1:
@@ -150,7 +182,7 @@ class ColumnParallelLinear(nn.Module):
         return y, (self.bias if self.skip_bias_add else None)
 
 
-class RowParallelLinear(nn.Module):
+class RowParallelLinear(_Fp8WeightMixin, nn.Module):
     """``Y = X W^T`` with ``W`` split along its input columns; partial sums are reduced over TP."""
 
     def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
@@ -183,27 +215,27 @@ class RowParallelLinear(nn.Module):
     def forward(self, x: torch.Tensor):
         if not self.input_is_parallel and self.tp > 1:
             x = x.chunk(self.tp, dim=-1)[self.rank].contiguous()
+        fp8 = self.weight_fp8 is not None
         if self.tp > 1 and not self.delay_allreduce:
+            from .. import fused_comm
             if self.sequence_parallel:
-                from .. import fused_comm
-                if fused_comm.enabled(self.config, x):
+                if not fp8 and fused_comm.enabled(self.config, x):
                     y = fused_comm.linear_reduce_scatter(x, self.weight)
                 else:
-                    y = M.reduce_scatter_to_sequence_parallel_region(Fn.linear(x, self.weight))
+                    y = M.reduce_scatter_to_sequence_parallel_region(self._mm(x))
             else:
-                from .. import fused_comm
-                if fused_comm.allreduce_enabled(self.config, x, self.weight):
+                if not fp8 and fused_comm.allreduce_enabled(self.config, x, self.weight):
                     y = fused_comm.linear_all_reduce(x, self.weight)      # inference: GEMM -> all-reduce in one kernel
                 else:
-                    y = M.reduce_from_tensor_model_parallel_region(Fn.linear(x, self.weight))
+                    y = M.reduce_from_tensor_model_parallel_region(self._mm(x))
         else:
-            y = Fn.linear(x, self.weight)
+            y = self._mm(x)
         if self.bias is not None and not self.skip_bias_add:
             y = y + self.bias
         return y, (self.bias if self.skip_bias_add else None)
 
 
-class LinearNoTP(nn.Module):
+class LinearNoTP(_Fp8WeightMixin, nn.Module):
     """Replicated linear layer (the reference's ``LinearNoTP`` / ``ReplicatedLinear``)."""
 
     def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
@@ -224,7 +256,9 @@ class LinearNoTP(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, x):
-        y = Fn.linear(x, self.weight, None if self.skip_bias_add else self.bias)
+        y = self._mm(x)
+        if self.bias is not None and not self.skip_bias_add:
+            y = y + self.bias
         return y, (self.bias if self.skip_bias_add else None)
 
 

@@ -1,0 +1,38 @@
+"""Block-scaled fp8 inference weights: quantised model close to the bf16 one, generation still runs."""
+import torch
+
+from mindformers_b200.inference.fp8 import quantize_model_fp8
+from mindformers_b200.models import AutoModel
+
+
+def tiny_deepseek():
+    cfg = dict(model_type="deepseek_v3", num_hidden_layers=3, hidden_size=256, num_attention_heads=4,
+               num_key_value_heads=4, intermediate_size=512, moe_intermediate_size=128, n_routed_experts=8,
+               n_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, routed_scaling_factor=1.0,
+               norm_topk_prob=True, scoring_func="sigmoid", first_k_dense_replace=1, vocab_size=512,
+               q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+               max_position_embeddings=256, params_dtype="float32", moe_router_enable_expert_bias=True)
+    torch.manual_seed(0)
+    return AutoModel.from_config(cfg, device="cpu").eval()
+
+
+def test_quantize_model_fp8_matches_full_precision():
+    model = tiny_deepseek()
+    ids = torch.randint(3, 512, (2, 32))
+    with torch.no_grad():
+        ref = model(ids).float()
+    stats = quantize_model_fp8(model)
+    assert stats["linear"] >= 6 and stats["grouped"] == 2 and stats["kept"] >= 1
+    assert stats["bytes_after"] < 0.3 * stats["bytes_before"]          # fp32 -> fp8 + scales
+    names = dict(model.named_modules())
+    dense = names["model.decoder.layers.0.mlp.linear_fc1"]
+    assert dense.weight is None and dense.weight_fp8.dtype == torch.float8_e4m3fn
+    assert dense.weight_scale_inv.shape == (dense.weight_fp8.shape[0] // 128, dense.weight_fp8.shape[1] // 128)
+    assert names["model.output_layer"].weight is not None              # kept in full precision
+    with torch.no_grad():
+        out = model(ids).float()
+    rel = ((out - ref).norm() / ref.norm()).item()
+    assert rel < 0.08, rel
+    assert (out.argmax(-1) == ref.argmax(-1)).float().mean() > 0.7
+    seqs = model.generate(ids[:, :8].tolist(), max_new_tokens=4, do_sample=False)
+    assert all(len(s) == 12 for s in seqs)

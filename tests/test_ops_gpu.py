@@ -369,6 +369,26 @@ def test_paged_decode_attention_split_kv(hd, nq, nkv, block):
         assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
 
 
+@pytest.mark.parametrize("B,S,nh,causal", [(1, 128, 2, True), (2, 512, 4, True), (1, 1024, 16, True), (1, 384, 3, False)])
+def test_flash_attention_mla_shape_forward(B, S, nh, causal):
+    """Forward kernel with 192-wide q/k heads and 128-wide v heads against fp32 softmax attention."""
+    from mindformers_b200.ops import attention as native
+    torch.manual_seed(S + nh)
+    q = (torch.randn(B, S, nh, 192, device="cuda") * 0.5).to(torch.bfloat16)
+    k = (torch.randn(B, S, nh, 192, device="cuda") * 0.5).to(torch.bfloat16)
+    v = (torch.randn(B, S, nh, 128, device="cuda") * 0.5).to(torch.bfloat16)
+    assert native.mla_supported(q, k, v)
+    scale = 192 ** -0.5
+    out = native.mla_forward(q, k, v, causal, scale)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(S, S, device="cuda", dtype=torch.bool), 1), float("-inf"))
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.float())
+    assert (out.float() - ref).abs().max().item() < 2e-2
+
+
 @pytest.mark.parametrize("nh,block", [(16, 128), (128, 128), (20, 16), (16, 64)])
 def test_mla_decode_attention(nh, block):
     """Absorbed-query MLA decode over the paged latent cache against an fp32 reference."""
