@@ -97,14 +97,21 @@ class MoEExchange:
     def rows_cap(self, T: int) -> int:
         """Rows of this rank's receive buffers for ``T`` local tokens.
 
-        Symmetric allocations must have one size on all ranks, so the first call (and the first one after a growth)
-        agrees on the largest request of the group with one all-reduce and a host read; later requests are cut to
-        that size. A rank that then needs more rows than agreed overflows, which ``adapt_capacity`` repairs."""
-        cap = int(T * self.k * (self.factor if self.world > 1 else 1.0)) + self.E_local * (BLOCK - 1)
+        Symmetric allocations must have one size on all ranks, so the first call, the first one after a growth and
+        every call that asks for more rows than were agreed so far settle the size with one all-reduce and a host
+        read. Routing that still overflows the buffers is repaired by ``adapt_capacity``."""
+        factor = self.factor
+        if not torch.is_grad_enabled():
+            # inference has no step boundary at which to grow the buffers and holds one pair of them for all layers,
+            # so it starts from a roomier bound
+            factor = max(factor, min(float(self.world), 2.5))
+        cap = int(T * self.k * (factor if self.world > 1 else 1.0)) + self.E_local * (BLOCK - 1)
         cap = (cap + BLOCK - 1) // BLOCK * BLOCK
         if self.world <= 1:
             return cap
-        if self.alloc_rows is None:
+        if self.alloc_rows is None or cap > self.alloc_rows:
+            # a larger token count than ever before (first call, or a longer prefill): all ranks reach this point in
+            # the same call because the token count per rank is the same over the group
             t = torch.tensor([cap], dtype=torch.int64, device=self.dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
             self.alloc_rows = int(t.item())
@@ -320,10 +327,13 @@ def moe_dispatch_experts_combine(layer, hidden: torch.Tensor, probs: torch.Tenso
     ex = MoEExchange.get(layer.config)
     ids = ids.contiguous()
     st = ex.plan(ids, hidden.shape[0])
-    slot = ex.acquire_slot(layer.layer_number)
-    st.slot = (layer.layer_number, slot)
-    key = f"{layer.layer_number}.{slot}"
     needs_grad = torch.is_grad_enabled() and (hidden.requires_grad or probs.requires_grad)
+    # forward-only calls share one pair of row buffers between all layers: a layer's combine barrier orders every
+    # peer's reads before the next layer's writes. With gradients the buffers live until the layer's backward.
+    layer_key = layer.layer_number if needs_grad else "nograd"
+    slot = ex.acquire_slot(layer_key)
+    st.slot = (layer_key, slot)
+    key = f"{layer_key}.{slot}"
     xin = _Dispatch.apply(hidden, ids, ex, st, key)
     layer.last_tokens_per_expert = st.counts
     y = layer.experts(xin, st.plan)
