@@ -51,9 +51,30 @@ def _classes_for(d: dict):
     raise ValueError(f"cannot determine the model family of configuration with model_type={mt!r}")
 
 
+def _auto_map_classes(path: str):
+    """``(config class, model class)`` named by the ``auto_map`` of a model directory's ``config.json`` (classes that
+    live in Python files of that directory), or None. Either entry may be None when the map does not name it."""
+    if not isinstance(path, str) or not os.path.isdir(path) or not os.path.exists(os.path.join(path, "config.json")):
+        return None
+    amap = _read_config_dict(path).get("auto_map") or {}
+    if not amap:
+        return None
+    from ..tools.hub import get_class_from_dynamic_module
+    cfg_ref = amap.get("AutoConfig")
+    model_ref = amap.get("AutoModelForCausalLM") or amap.get("AutoModel")
+    cfg_cls = get_class_from_dynamic_module(cfg_ref, path) if cfg_ref else None
+    model_cls = get_class_from_dynamic_module(model_ref, path) if model_ref else None
+    if cfg_cls is None and model_cls is not None:
+        cfg_cls = getattr(model_cls, "config_class", None)
+    return cfg_cls, model_cls
+
+
 class AutoConfig:
     @staticmethod
     def from_pretrained(name_or_path: str, **kwargs) -> PretrainedConfig:
+        dyn = _auto_map_classes(name_or_path)
+        if dyn is not None and dyn[0] is not None:
+            return dyn[0].from_dict(_read_config_dict(name_or_path), **kwargs)
         if name_or_path in PRESETS:
             d = get_preset(name_or_path)
         else:
@@ -83,6 +104,12 @@ class AutoModel:
 
     @staticmethod
     def from_pretrained(name_or_dir: str, **kwargs):
+        dyn = _auto_map_classes(name_or_dir)
+        if dyn is not None and dyn[1] is not None:
+            cfg_cls, model_cls = dyn
+            config = kwargs.pop("config", None) or cfg_cls.from_dict(_read_config_dict(name_or_dir))
+            return model_cls.from_pretrained(name_or_dir, config=config, **kwargs) if hasattr(
+                model_cls, "from_pretrained") else model_cls(config, **kwargs)
         config = kwargs.pop("config", None) or AutoConfig.from_pretrained(name_or_dir)
         _, model_cls = _classes_for(config.to_dict())
         if name_or_dir in PRESETS:

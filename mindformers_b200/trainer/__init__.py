@@ -2,3 +2,6 @@ from .base_trainer import BaseTrainer, CausalLanguageModelingTrainer, GeneralTas
 from .engine import TrainingEngine
 from .trainer import Trainer
 from .training_args import TrainingArguments
+from .config_args import (BaseArgsConfig, CheckpointConfig, CloudConfig, ConfigArguments, ContextConfig, DataLoaderConfig,
+                          DatasetConfig, LRConfig, MFContextConfig, OptimizerConfig, ParallelConfig,
+                          ParallelContextConfig, RunnerConfig, WrapperConfig)

@@ -21,6 +21,7 @@ from ..tools.register.config import MindFormerConfig
 from ..tools.register.template import ConfigTemplate
 from ..tools.utils import get_output_root_path, set_output_path
 from .base_trainer import build_trainer
+from .config_args import ConfigArguments
 from .training_args import TrainingArguments
 
 logger = get_logger()
@@ -62,6 +63,9 @@ class Trainer:
         if isinstance(args, TrainingArguments):
             cfg = MindFormerConfig(copy.deepcopy(DEFAULT_TASK_CONFIG))
             args.convert_args_to_mindformers_config(cfg)
+        elif isinstance(args, ConfigArguments):
+            cfg = MindFormerConfig(copy.deepcopy(DEFAULT_TASK_CONFIG))
+            cfg.merge_from_dict(args.to_config())
         elif isinstance(args, str):
             cfg = MindFormerConfig(args)
         elif isinstance(args, dict):

@@ -151,3 +151,27 @@ def test_convert_weight_roundtrip(tmp_path):
         if f.endswith(".safetensors"):
             b.update(load_file(str(tmp_path / "hf" / f)))
     assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+
+
+def test_config_arguments_sections():
+    from mindformers_b200.trainer import (CheckpointConfig, ConfigArguments, LRConfig, OptimizerConfig, ParallelConfig,
+                                          RunnerConfig, Trainer)
+    import pytest as _pytest
+    args = ConfigArguments(
+        output_dir="./out_cfg", seed=7, runner_config=RunnerConfig(epochs=2, batch_size=4),
+        optimizer=OptimizerConfig(optim_type="AdamW", learning_rate=3e-4, weight_decay=0.05),
+        lr_schedule=LRConfig(lr_type="CosineWithWarmUpLR", warmup_steps=10),
+        parallel_config=ParallelConfig(data_parallel=1, model_parallel=1),
+        save_checkpoint=CheckpointConfig(save_checkpoint_steps=50, keep_checkpoint_max=2))
+    cfg = args.to_config()
+    assert cfg["runner_config"] == {"epochs": 2, "batch_size": 4}
+    assert cfg["optimizer"]["type"] == "AdamW" and cfg["optimizer"]["learning_rate"] == 3e-4
+    assert cfg["lr_schedule"] == {"type": "CosineWithWarmUpLR", "warmup_steps": 10}
+    assert cfg["callbacks"][-1]["type"] == "CheckpointMonitor" and cfg["callbacks"][-1]["save_checkpoint_steps"] == 50
+    assert "save_checkpoint" not in cfg
+    with _pytest.raises(KeyError):
+        RunnerConfig(epoch=3)
+    assert RunnerConfig.filter_kwargs(epochs=1, bogus=2) == {"epochs": 1}
+    trainer = Trainer(args=args, task="general")
+    assert trainer.config.runner_config.epochs == 2 and trainer.config.optimizer.weight_decay == 0.05
+    assert trainer.config.seed == 7
