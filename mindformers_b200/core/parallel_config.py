@@ -1,0 +1,123 @@
+"""YAML ``parallel_config`` / ``recompute_config`` / ``swap_config`` / ``moe_config`` sections as objects.
+
+Reference: ``mindformers/core/parallel_config.py:28-76`` (``build_parallel_config``: dict sections →
+``TransformerOpParallelConfig`` / ``TransformerRecomputeConfig`` / ``TransformerSwapConfig`` / ``MoEConfig``; a
+pipeline of more than one stage forces ``vocab_emb_dp=False``) and ``modules/transformer/op_parallel_config.py``.
+The objects carry the reference's field names; ``to_parallel_state_kwargs`` maps them onto
+``parallel_state.initialize_model_parallel``.
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field
+from typing import Any, Dict, List, Optional, Union
+
+
+@dataclass
+class TransformerRecomputeConfig:
+    recompute: Union[bool, list] = False
+    select_recompute: Union[bool, list] = False
+    parallel_optimizer_comm_recompute: bool = False
+    select_comm_recompute: Union[bool, list] = False
+    mp_comm_recompute: bool = True
+    recompute_slice_activation: bool = False
+    select_recompute_exclude: Union[bool, list] = False
+    select_comm_recompute_exclude: Union[bool, list] = False
+
+
+@dataclass
+class TransformerSwapConfig:
+    swap: bool = False
+    default_prefetch: int = 1
+    layer_swap: Optional[list] = None
+    op_swap: Optional[list] = None
+
+
+@dataclass
+class MoEParallelConfig:
+    data_parallel: int = 1
+    model_parallel: int = 1
+    expert_parallel: int = 1
+    context_parallel: int = 1
+
+
+@dataclass
+class TransformerOpParallelConfig:
+    data_parallel: int = 1
+    model_parallel: int = 1
+    context_parallel: int = 1
+    expert_parallel: int = 1
+    pipeline_stage: int = 1
+    micro_batch_num: int = 1
+    seq_split_num: int = 1
+    use_seq_parallel: bool = False
+    optimizer_shard: Optional[bool] = None
+    gradient_aggregation_group: int = 4
+    vocab_emb_dp: bool = True
+    context_parallel_algo: str = "colossalai_cp"
+    ulysses_degree_in_cp: int = 1
+    mem_coeff: float = 0.1
+    virtual_pipeline_stage: Optional[int] = None
+    recompute: TransformerRecomputeConfig = field(default_factory=TransformerRecomputeConfig)
+    swap: TransformerSwapConfig = field(default_factory=TransformerSwapConfig)
+
+    def __post_init__(self):
+        for name in ("data_parallel", "model_parallel", "context_parallel", "expert_parallel", "pipeline_stage",
+                     "micro_batch_num", "seq_split_num", "ulysses_degree_in_cp"):
+            v = getattr(self, name)
+            if not isinstance(v, int) or v < 1:
+                raise ValueError(f"parallel_config.{name} must be a positive integer, got {v!r}")
+        if self.context_parallel_algo not in ("colossalai_cp", "ulysses_cp", "hybrid_cp"):
+            raise ValueError(f"context_parallel_algo {self.context_parallel_algo!r} is not one of "
+                             "colossalai_cp / ulysses_cp / hybrid_cp")
+        if self.pipeline_stage > 1:
+            self.vocab_emb_dp = False           # the embedding is model-parallel once the model is staged
+
+    @property
+    def moe_parallel_config(self) -> MoEParallelConfig:
+        return MoEParallelConfig(self.data_parallel, self.model_parallel, self.expert_parallel, self.context_parallel)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+    def to_parallel_state_kwargs(self) -> Dict[str, Any]:
+        """Arguments of ``parallel_state.initialize_model_parallel`` for these degrees."""
+        kw = dict(tensor_model_parallel_size=self.model_parallel, pipeline_model_parallel_size=self.pipeline_stage,
+                  context_parallel_size=self.context_parallel, expert_model_parallel_size=self.expert_parallel)
+        if self.virtual_pipeline_stage and self.virtual_pipeline_stage > 1:
+            kw["virtual_pipeline_model_parallel_size"] = self.virtual_pipeline_stage
+        return kw
+
+    def cp_comm_type(self) -> str:
+        return {"colossalai_cp": "p2p", "ulysses_cp": "a2a", "hybrid_cp": "a2a+p2p"}[self.context_parallel_algo]
+
+
+default_transformer_config = TransformerOpParallelConfig()
+default_recompute_config = TransformerRecomputeConfig()
+default_moe_parallel_config = MoEParallelConfig()
+
+
+def build_parallel_config(config) -> TransformerOpParallelConfig:
+    """Replace the dict sections of ``config`` (a ``MindFormerConfig`` or dict) by objects and return the parallel one.
+    Sets ``config.parallel_config``, ``config.recompute_config``, ``config.swap_config`` in place."""
+    get = (lambda k: config.get(k)) if hasattr(config, "get") else (lambda k: getattr(config, k, None))
+    rc = get("recompute_config")
+    recompute = rc if isinstance(rc, TransformerRecomputeConfig) else TransformerRecomputeConfig(
+        **{k: v for k, v in dict(rc or {}).items() if k in TransformerRecomputeConfig.__dataclass_fields__})
+    sc = get("swap_config")
+    swap = sc if isinstance(sc, TransformerSwapConfig) else TransformerSwapConfig(
+        **{k: v for k, v in dict(sc or {}).items() if k in TransformerSwapConfig.__dataclass_fields__})
+    pc = get("parallel_config")
+    if isinstance(pc, TransformerOpParallelConfig):
+        par = pc
+        par.recompute, par.swap = recompute, swap
+    else:
+        fields = TransformerOpParallelConfig.__dataclass_fields__
+        par = TransformerOpParallelConfig(recompute=recompute, swap=swap,
+                                          **{k: v for k, v in dict(pc or {}).items()
+                                             if k in fields and k not in ("recompute", "swap") and v is not None})
+    for key, val in (("parallel_config", par), ("recompute_config", recompute), ("swap_config", swap)):
+        if isinstance(config, dict):
+            config[key] = val
+        else:
+            setattr(config, key, val)
+    return par

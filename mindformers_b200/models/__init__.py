@@ -21,3 +21,4 @@ def build_network(config: dict, default_args=None):
         mc["architectures"] = [arch]
     mc.pop("type", None)
     return AutoModel.from_config(mc)
+from .processing_utils import BaseProcessor, GLMProcessor, LlamaProcessor, ProcessorMixin, build_processor

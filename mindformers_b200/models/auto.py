@@ -198,7 +198,19 @@ class AutoTokenizer:
 
 
 class AutoProcessor:
+    """Processor of a directory: the class named in ``preprocessor_config.json`` (registry lookup), else a text
+    processor around the directory's tokenizer."""
+
     @staticmethod
     def from_pretrained(name_or_dir: str, **kwargs):
-        from .tokenization import TextProcessor
-        return TextProcessor(AutoTokenizer.from_pretrained(name_or_dir, **kwargs), **kwargs)
+        path = os.path.join(name_or_dir, "preprocessor_config.json")
+        if os.path.exists(path):
+            with open(path, "r", encoding="utf-8") as f:
+                name = json.load(f).get("processor_class")
+            if name and MindFormerRegister.is_exist(MindFormerModuleType.PROCESSOR, name):
+                return MindFormerRegister.get_cls(MindFormerModuleType.PROCESSOR, name).from_pretrained(name_or_dir, **kwargs)
+        from .processing_utils import LlamaProcessor
+        return LlamaProcessor(AutoTokenizer.from_pretrained(name_or_dir), **kwargs)
+
+
+AutoImageProcessor = AutoProcessor

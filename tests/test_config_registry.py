@@ -100,3 +100,27 @@ def test_auto_register_from_register_path(tmp_path, monkeypatch):
     monkeypatch.setenv("REGISTER_PATH", str(tmp_path))
     cls = MindFormerRegister.auto_register("plug.mod.Extra", MindFormerModuleType.TOOLS)
     assert cls.value == 3 and MindFormerRegister.get_cls(MindFormerModuleType.TOOLS, "Extra") is cls
+
+
+def test_parallel_config_objects_and_cpu_masks():
+    from mindformers_b200.core.parallel_config import build_parallel_config
+    from mindformers_b200.utils.bit_array import BitArray
+    from mindformers_b200.utils.cpu_affinity import cores_for_rank, format_cpu_list, parse_cpu_list
+    import pytest as _pytest
+    cfg = {"parallel_config": {"data_parallel": 2, "model_parallel": 4, "pipeline_stage": 2, "micro_batch_num": 8,
+                               "use_seq_parallel": True, "context_parallel_algo": "ulysses_cp"},
+           "recompute_config": {"recompute": [2, 1], "select_recompute": False}}
+    par = build_parallel_config(cfg)
+    assert par.model_parallel == 4 and par.vocab_emb_dp is False            # staged model: model-parallel embedding
+    assert par.recompute.recompute == [2, 1] and cfg["recompute_config"] is par.recompute
+    assert par.to_parallel_state_kwargs()["pipeline_model_parallel_size"] == 2 and par.cp_comm_type() == "a2a"
+    with _pytest.raises(ValueError):
+        build_parallel_config({"parallel_config": {"model_parallel": 0}})
+    bits = BitArray(64).load_from_str("0000000f,000000f0")
+    assert bits.get_marked_index() == [4, 5, 6, 7, 32, 33, 34, 35] and bits.to_mask_str() == "0000000f,000000f0"
+    assert (bits - BitArray.from_indices([4, 32])).count() == 6
+    assert parse_cpu_list("0-3,8,10-11") == [0, 1, 2, 3, 8, 10, 11] and format_cpu_list([0, 1, 2, 3, 8, 10, 11]) == "0-3,8,10-11"
+    numa = {0: list(range(0, 16)), 1: list(range(16, 32))}
+    assert cores_for_rank(1, 4, range(32), reserved=[0], numa=numa, gpu_node=0) == list(range(8, 15))
+    assert cores_for_rank(3, 4, range(32)) == list(range(24, 32))
+    assert cores_for_rank(2, 4, range(32), numa=numa, gpu_node=1) == list(range(16, 24))

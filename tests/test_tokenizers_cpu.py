@@ -214,3 +214,19 @@ def test_glm4_chat_input(tmp_path, ranks):
     batch = tok(["hello", "hello world the quick fox"], padding=True)
     assert batch["attention_mask"][0][0] == 0                       # left padding
     assert batch["position_ids"][0][-1] == len([i for i in batch["attention_mask"][0] if i]) - 1
+
+
+def test_processor_roundtrip(tmp_path, ranks):
+    from mindformers_b200.models import AutoProcessor, LlamaProcessor, build_processor
+    path = str(tmp_path / "tokenizer.model")
+    save_tiktoken_ranks(ranks, path)
+    tok = Llama3Tokenizer(path)
+    proc = LlamaProcessor(tok, max_length=16)
+    out = proc(text_input=["hello world", "the fox"])
+    assert out["text"].shape == (2, 16) and out["attention_mask"].shape == (2, 16)
+    proc.save_pretrained(str(tmp_path / "p"))
+    again = AutoProcessor.from_pretrained(str(tmp_path / "p"))
+    assert type(again).__name__ == "LlamaProcessor" and again.max_length == 16
+    assert torch.equal(again(text_input=["hello world", "the fox"])["text"], out["text"])
+    built = build_processor({"type": "LlamaProcessor", "tokenizer": {"type": "ByteTokenizer"}, "max_length": 8})
+    assert built(text_input="abc")["text"].shape[-1] == 8
