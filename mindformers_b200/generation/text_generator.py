@@ -175,11 +175,14 @@ class GenerationMixin:
         return seqs
 
     def _select(self, seqs, logits, processors, warper, gen, gcfg):
-        L = max(len(s) for s in seqs)
-        ids = torch.full((len(seqs), L), -1, dtype=torch.int64, device=logits.device)
-        for i, s in enumerate(seqs):
-            ids[i, : len(s)] = torch.tensor(s, dtype=torch.int64, device=logits.device)
         scores = logits.float()
+        if not len(processors) and warper is None:
+            return scores.argmax(-1).tolist()          # greedy without penalties: the token history is not needed
+        L = max(len(s) for s in seqs)
+        host = np.full((len(seqs), L), -1, dtype=np.int64)
+        for i, s in enumerate(seqs):
+            host[i, : len(s)] = s
+        ids = torch.from_numpy(host).to(logits.device)  # one host-to-device copy for the whole batch
         if len(processors):
             scores = processors(ids, scores)
         if warper is None:
