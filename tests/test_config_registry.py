@@ -124,3 +124,30 @@ def test_parallel_config_objects_and_cpu_masks():
     assert cores_for_rank(1, 4, range(32), reserved=[0], numa=numa, gpu_node=0) == list(range(8, 15))
     assert cores_for_rank(3, 4, range(32)) == list(range(24, 32))
     assert cores_for_rank(2, 4, range(32), numa=numa, gpu_node=1) == list(range(16, 24))
+
+
+def test_misc_utils(tmp_path):
+    import warnings
+    from mindformers_b200.tools.generic import add_model_info_to_auto_map, is_experimental_mode
+    from mindformers_b200.utils.decorators import deprecated
+    from mindformers_b200.utils.import_utils import is_package_available, requires_backends
+    import pytest as _pytest
+
+    @deprecated("use g", version="1.2")
+    def f(x):
+        return x + 1
+
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        assert f(1) == 2
+    assert "deprecated since 1.2: use g" in str(w[0].message)
+    assert is_package_available("torch") and not is_package_available("surely_not_installed_pkg")
+    with _pytest.raises(ImportError):
+        requires_backends(f, ["surely_not_installed_pkg"])
+    (tmp_path / "hf").mkdir()
+    (tmp_path / "hf" / "config.json").write_text("{}")
+    (tmp_path / "origin").mkdir()
+    (tmp_path / "origin" / "model.yaml").write_text("a: 1")
+    assert is_experimental_mode(str(tmp_path / "hf")) and not is_experimental_mode(str(tmp_path / "origin"))
+    assert is_experimental_mode("org/model") and not is_experimental_mode("llama2_7b")
+    assert add_model_info_to_auto_map({"AutoModel": "m.C"}, "org/r") == {"AutoModel": "org/r--m.C"}
