@@ -394,3 +394,86 @@ class TrainingDataLoader:
                 samples_num: Optional[int] = None, skip_num: int = 0, **kw):
         return TrainingDataset(dataset_dir, tokenizer, column_names, max_length, text_col, file_format, shuffle,
                                int(kw.get("seed", 0)), samples_num, skip_num, is_align=bool(kw.get("is_align", True)))
+
+
+class _SampleList(Dataset):
+    """Tokenised samples (dicts of int lists / arrays) as tensors, padded or cut to ``seq_length + 1`` and shifted."""
+
+    def __init__(self, samples: List[dict], seq_length: Optional[int], pad_token_id: int = 0):
+        self.samples, self.seq_length, self.pad = samples, seq_length, pad_token_id
+
+    def __len__(self):
+        return len(self.samples)
+
+    def __getitem__(self, i):
+        s = self.samples[i]
+        ids = list(s["input_ids"])
+        labels = list(s["labels"]) if "labels" in s else list(ids)
+        if self.seq_length:
+            width = self.seq_length + 1
+            ids, labels = ids[:width], labels[:width]
+            gap = width - len(ids)
+            ids, labels = ids + [self.pad] * gap, labels + [IGNORE_INDEX] * gap
+        out = {"input_ids": torch.tensor(ids[:-1], dtype=torch.int64), "labels": torch.tensor(labels[1:], dtype=torch.int64)}
+        out["loss_mask"] = (out["labels"] != IGNORE_INDEX).float()
+        for key in ("actual_seq_len", "position_ids"):
+            if key in s:
+                out[key] = torch.as_tensor(np.asarray(s[key]))
+        return out
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class HFDataLoader:
+    """Local files or directories through the Hugging Face ``datasets`` library, then data handlers.
+
+    ``path``: a builder name (``json``, ``parquet``, ``csv``, ``text``) with ``data_files``, or a directory written by
+    ``Dataset.save_to_disk``. ``handler``: list of handler configs (``AlpacaInstructDataHandler``, ``PackingHandler``
+    …) applied in order to the records; without handlers the rows must already carry ``input_ids``. This is the
+    reference's ``CommonDataLoader`` + ``ms_ds_convertor`` pair (``dataset/dataloader/common_dataloader.py``), with
+    torch tensors at the end instead of a MindSpore dataset. No hub access: names that are not local raise.
+    """
+
+    def __new__(cls, path: str, data_files=None, split: str = "train", handler: Optional[List[dict]] = None,
+                tokenizer=None, seq_length: Optional[int] = None, shuffle: bool = False, seed: int = 0,
+                num_samples: Optional[int] = None, pad_token_id: int = 0, **kw):
+        import datasets
+        if os.path.isdir(path) and os.path.exists(os.path.join(path, "dataset_info.json")):
+            ds = datasets.load_from_disk(path)
+            if isinstance(ds, datasets.DatasetDict):
+                ds = ds[split]
+        elif path in ("json", "parquet", "csv", "text", "arrow"):
+            if not data_files:
+                raise ValueError(f"path={path!r} needs data_files")
+            ds = datasets.load_dataset(path, data_files=data_files, split=split)
+        elif os.path.exists(path):
+            ext = os.path.splitext(path)[1].lstrip(".")
+            builder = {"jsonl": "json", "json": "json", "parquet": "parquet", "csv": "csv", "txt": "text"}.get(ext)
+            if os.path.isdir(path):
+                files = list_files(path)
+                ext = os.path.splitext(files[0])[1].lstrip(".")
+                builder = {"jsonl": "json", "json": "json", "parquet": "parquet", "csv": "csv", "txt": "text"}[ext]
+                ds = datasets.load_dataset(builder, data_files=files, split=split)
+            else:
+                ds = datasets.load_dataset(builder, data_files=path, split=split)
+        else:
+            raise FileNotFoundError(f"{path} is neither a local file / directory nor a builder name "
+                                    f"(the hub cannot be reached from here)")
+        if shuffle:
+            ds = ds.shuffle(seed=seed)
+        if num_samples:
+            ds = ds.select(range(min(int(num_samples), len(ds))))
+        records: List[dict] = list(ds)
+        tok = _resolve_tokenizer(tokenizer) if tokenizer is not None else None
+        if handler:
+            from .handlers import build_data_handler
+            for h in handler:
+                cfg = dict(h)
+                if tok is not None:
+                    cfg.setdefault("tokenizer", tok)
+                if seq_length:
+                    cfg.setdefault("seq_length", seq_length)
+                records = build_data_handler(cfg).handle(records)
+        if records and "input_ids" not in records[0]:
+            raise KeyError("rows carry no input_ids: add a tokenising handler")
+        pid = getattr(tok, "pad_token_id", None)
+        return _SampleList(records, seq_length, pad_token_id if pid is None else pid)

@@ -129,3 +129,23 @@ def test_training_dataloader_packs_text(tmp_path):
     resumed = list(TrainingDataLoader(str(tmp_path), tok, max_length=9, skip_num=1))
     assert torch.equal(resumed[0]["input_ids"], samples[1]["input_ids"])
     assert len(list(TrainingDataLoader(str(tmp_path), tok, max_length=9, samples_num=2))) == 2
+
+
+def test_hf_dataloader_with_handlers(tmp_path):
+    from mindformers_b200.dataset.dataloaders import HFDataLoader
+    write_jsonl(tmp_path / "alpaca.jsonl", [{"instruction": "Add", "input": "1 2", "output": "3"},
+                                            {"instruction": "Say hi", "input": "", "output": "hi"}])
+    tok = ByteTokenizer()
+    ds = HFDataLoader(str(tmp_path / "alpaca.jsonl"), handler=[{"type": "AlpacaInstructDataHandler"}], tokenizer=tok,
+                      seq_length=300)
+    assert len(ds) == 2
+    row = ds[1]
+    assert row["input_ids"].shape == row["labels"].shape == (300,)
+    kept = row["labels"][row["labels"] != -100].tolist()
+    assert kept == tok.encode("hi", add_special_tokens=False) + [tok.eos_token_id]
+    ds2 = HFDataLoader("json", data_files=str(tmp_path / "alpaca.jsonl"), handler=[{"type": "AlpacaInstructDataHandler"}],
+                       tokenizer=tok, seq_length=300, num_samples=1)
+    assert len(ds2) == 1
+    import pytest as _pytest
+    with _pytest.raises(FileNotFoundError):
+        HFDataLoader("org/some_dataset")
