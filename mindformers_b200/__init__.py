@@ -1,0 +1,53 @@
+"""mindformers_b200: Blackwell-native large-model training and inference with the MindFormers API surface.
+
+The names a user of the reference imports from the package root resolve here too; they are imported on first access so
+that ``import mindformers_b200`` stays cheap (no torch extension is loaded until something needs it).
+"""
+from __future__ import annotations
+
+import importlib
+
+__version__ = "0.1.0"
+
+_EXPORTS = {
+    # models
+    "AutoConfig": "models", "AutoModel": "models", "AutoModelForCausalLM": "models", "AutoTokenizer": "models",
+    "AutoProcessor": "models", "PretrainedConfig": "models", "PreTrainedModel": "models",
+    "PreTrainedTokenizer": "models", "LlamaConfig": "models", "LlamaForCausalLM": "models", "LlamaTokenizer": "models",
+    "LlamaTokenizerFast": "models", "ChatGLM3Tokenizer": "models", "ChatGLM4Tokenizer": "models",
+    "ChatGLM2ForConditionalGeneration": "models", "Qwen2Tokenizer": "models", "Llama3Tokenizer": "models",
+    "build_network": "models", "build_tokenizer": "models", "build_processor": "models",
+    # trainer / pipeline / generation
+    "Trainer": "trainer", "TrainingArguments": "trainer", "ConfigArguments": "trainer", "TrainingEngine": "trainer",
+    "pipeline": "pipeline", "TextGenerationPipeline": "pipeline", "MultiModalToTextPipeline": "pipeline",
+    "GenerationConfig": "generation", "GenerationMixin": "generation", "TextStreamer": "generation",
+    # registry / config
+    "MindFormerConfig": "tools.register", "MindFormerRegister": "tools.register",
+    "MindFormerModuleType": "tools.register",
+    # runtime
+    "ModelRunner": "model_runner", "run_check": "run_check", "MindFormerBook": "mindformer_book",
+    "build_context": "core.context", "init_context": "core.context", "set_context": "core.context",
+    "get_context": "core.context",
+    # data
+    "CausalLanguageModelDataset": "dataset", "KeyWordGenDataset": "dataset", "MultiTurnDataset": "dataset",
+    "build_dataset": "dataset",
+    # PEFT
+    "LoraConfig": "pet", "LoraModel": "pet", "PetConfig": "pet", "get_pet_model": "pet",
+    # wrappers
+    "MFTrainOneStepCell": "wrapper", "MFPipelineWithLossScaleCell": "wrapper",
+}
+
+__all__ = sorted(_EXPORTS) + ["__version__"]
+
+
+def __getattr__(name: str):
+    mod = _EXPORTS.get(name)
+    if mod is None:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    value = getattr(importlib.import_module(f"{__name__}.{mod}"), name)
+    globals()[name] = value
+    return value
+
+
+def __dir__():
+    return __all__

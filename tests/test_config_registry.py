@@ -151,3 +151,18 @@ def test_misc_utils(tmp_path):
     assert is_experimental_mode(str(tmp_path / "hf")) and not is_experimental_mode(str(tmp_path / "origin"))
     assert is_experimental_mode("org/model") and not is_experimental_mode("llama2_7b")
     assert add_model_info_to_auto_map({"AutoModel": "m.C"}, "org/r") == {"AutoModel": "org/r--m.C"}
+
+
+def test_top_level_api_surface():
+    """The names the reference documents at the package root (docs/api/api_python) resolve."""
+    import mindformers_b200 as mf
+    for name in ("AutoConfig", "AutoModel", "AutoModelForCausalLM", "AutoProcessor", "AutoTokenizer", "ModelRunner",
+                 "Trainer", "TrainingArguments", "pipeline", "run_check", "MindFormerConfig", "MindFormerRegister",
+                 "MindFormerModuleType", "GenerationConfig", "GenerationMixin", "LlamaConfig", "LlamaForCausalLM",
+                 "LlamaTokenizer", "LlamaTokenizerFast", "ChatGLM3Tokenizer", "ChatGLM4Tokenizer", "PreTrainedModel",
+                 "PretrainedConfig", "CausalLanguageModelDataset", "KeyWordGenDataset", "MultiTurnDataset", "LoraConfig",
+                 "LoraModel", "PetConfig", "MultiModalToTextPipeline", "MFTrainOneStepCell", "MFPipelineWithLossScaleCell"):
+        assert getattr(mf, name) is not None, name
+    from mindformers_b200.core import AdamW, CosineWithWarmUpLR, CrossEntropyLoss, MFLossMonitor, PerplexityMetric  # noqa: F401
+    from mindformers_b200.wrapper import MFTrainOneStepCell
+    assert MFTrainOneStepCell.__name__ == "TrainOneStep"
