@@ -44,6 +44,7 @@ struct TpArgs {
   int num_m_blocks, num_n_blocks;
   int tp, rank, epoch;
   int rows_per_chunk;   // M / tp, multiple of 128
+  int ksplit;           // COMM 3: CTAs that share the K range of one tile (1 = no split); otherwise 1
   int* status;
   // ---- COMM 1 ----
   const __nv_bfloat16* peer_a[kTpMaxRanks];  // chunk [rows_per_chunk, K] of every rank (row pitch lda)
@@ -152,6 +153,9 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
   const int bpc = args.rows_per_chunk / kTpBM;  // row blocks per chunk
   const int k_blocks = (args.K + kTpBK - 1) / kTpBK;
   const int n_tiles = args.num_m_blocks * args.num_n_blocks;
+  const int ksplit = (COMM == 3 && args.ksplit > 1) ? args.ksplit : 1;
+  const int k_per_split = (k_blocks + ksplit - 1) / ksplit;
+  const int n_items = n_tiles * ksplit;
   // COMM 1 starts with the rank's own rows, COMM 2 with the rows of the next rank (own rows last)
   const int first_chunk = (COMM == 1) ? args.rank : (COMM == 2 ? (args.rank + 1) % args.tp : 0);
 
@@ -193,7 +197,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int tile = item / ksplit;
+        const int kb0 = (item - tile * ksplit) * k_per_split;
+        const int kb1 = (kb0 + k_per_split < k_blocks) ? kb0 + k_per_split : k_blocks;
         const TpTile t = tp_tile(args, tile, first_chunk);
         const int chunk = t.m_blk / bpc;
         const bool own = (COMM == 1) && (chunk == args.rank);
@@ -203,7 +210,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
           // the copy was made with generic-proxy stores; order it before the async-proxy (TMA) reads
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, args.status,
                          kStatusWaitTimeoutProducer);
           if (!ok) break;
@@ -232,12 +239,14 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int kb0 = (item % ksplit) * k_per_split;
+        const int kb1 = (kb0 + k_per_split < k_blocks) ? kb0 + k_per_split : k_blocks;
         ok = mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, args.status, kStatusWaitTimeoutMma);
           if (!ok) break;
           tc_fence_after();
@@ -248,7 +257,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
             const uint64_t a_desc = umma_desc_kmajor_sw128(a_base + k * 32);
             const uint64_t b_desc = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 16 * 128, kTpBK * 128)
                                          : umma_desc_kmajor_sw128(b_base + k * 32);
-            umma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -270,7 +279,9 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     const int parity = args.epoch & 1;
     const size_t slot_elems = static_cast<size_t>(args.rows_per_chunk) * args.N;
     const int tiles_per_chunk = bpc * args.num_n_blocks;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int tile = item / ksplit;
+      const int ks = item - tile * ksplit;
       const TpTile t = tp_tile(args, tile, first_chunk);
       const int owner = t.m_blk / bpc;
       const int mb_local = t.m_blk - owner * bpc;
@@ -292,7 +303,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
       const int local_row = mb_local * kTpBM + row;   // row inside the owner's chunk
       if (COMM == 3) {
-        // ---- push the bf16 partial tile to every peer ----
+        // slot (rank, K-split) of every partial; the sum runs over slots in index order on every rank
+        const int n_slots = args.tp * ksplit;
+        const int my_slot = args.rank * ksplit + ks;
+        // ---- push the bf16 partial tile to every peer (a K-split helper also to its own rank) ----
         const int et = threadIdx.x - 64;   // 0..127
         const int cj = et & 7;             // 16-byte chunk inside a 128-byte staging row
         if (issuer) tma_wait_group_read<0>();   // the stores of the previous tile have read the staging buffers
@@ -325,8 +339,8 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
               vals[i] = *reinterpret_cast<const uint4*>(sbase + r * 128 + ((cj ^ (r & 7)) << 4));
             }
             for (int p = 0; p < args.tp; ++p) {
-              if (p == args.rank) continue;
-              __nv_bfloat16* dst0 = args.recv_peer[p] + (static_cast<size_t>(parity) * args.tp + args.rank) * slot_elems +
+              if (p == args.rank && ks == 0) continue;     // the reducing CTA keeps its own partial in registers
+              __nv_bfloat16* dst0 = args.recv_peer[p] + (static_cast<size_t>(parity) * n_slots + my_slot) * slot_elems +
                                     static_cast<size_t>(t.m_blk * kTpBM) * args.N + col0 + cj * 8;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -341,14 +355,24 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
         named_bar_sync(1, 128);
         if (issuer) {
           for (int p = 0; p < args.tp; ++p) {
-            if (p == args.rank) continue;
-            st_release_sys(args.tile_flags_peer[p] + (static_cast<size_t>(parity) * args.tp + args.rank) * tiles_per_chunk + tile_in_chunk,
+            if (p == args.rank && ks == 0) continue;
+            st_release_sys(args.tile_flags_peer[p] + (static_cast<size_t>(parity) * n_slots + my_slot) * tiles_per_chunk + tile_in_chunk,
                            args.epoch);
           }
-          // ---- the peers' partial tiles ----
-          for (int p = 0; p < args.tp && ok; ++p) {
-            if (p == args.rank) continue;
-            ok = wait_flag_ge<true>(args.tile_flags_local + (static_cast<size_t>(parity) * args.tp + p) * tiles_per_chunk + tile_in_chunk,
+        }
+        if (ks != 0) {
+          // a K-split helper is done once its partial is published; the CTA with ks == 0 reduces the tile
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
+        if (issuer) {
+          // ---- the other partial tiles: every rank's K-splits ----
+          for (int sl = 0; sl < n_slots && ok; ++sl) {
+            if (sl == my_slot) continue;
+            ok = wait_flag_ge<true>(args.tile_flags_local + (static_cast<size_t>(parity) * n_slots + sl) * tiles_per_chunk + tile_in_chunk,
                                     args.epoch, abort_flag, args.status);
           }
         }
@@ -367,12 +391,12 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) sum[i] = 0.f;
-            for (int p = 0; p < args.tp; ++p) {
-              if (p == args.rank) {
+            for (int sl = 0; sl < n_slots; ++sl) {
+              if (sl == my_slot) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sum[i] += __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
               } else if (col0 < args.N) {
-                const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * args.tp + p) * slot_elems +
+                const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * n_slots + sl) * slot_elems +
                                            static_cast<size_t>(t.m_blk * kTpBM + row) * args.N + col0 + hf * 32;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -577,7 +601,7 @@ int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int tiles = a.num_m_blocks * a.num_n_blocks;
+  const int tiles = a.num_m_blocks * a.num_n_blocks * (COMM == 3 && a.ksplit > 1 ? a.ksplit : 1);
   // COMM 1 needs the gather warps of every CTA to be resident, whatever the tile count
   const int grid = (COMM == 1) ? sms : (tiles < sms ? tiles : sms);
   kern<<<grid, COMM == 1 ? 320 : 192, SMEM, stream>>>(tA, tAf, tB, tD, a);
@@ -663,8 +687,21 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
 }
 
 // GEMM -> all-reduce (one shot). A: [M, K] local (row pitch lda); B: [N, K] or [K, N]; D: [M, N] bf16, the full sum
-// on every rank. `recv_local` / `recv_peer[p]`: peer-mapped 2 * tp * ceil(M/128)*128 * N bf16; `tile_flags_*`:
-// peer-mapped 2 * tp * flag_tiles ints, persistent across calls, zero at the start of the job. Any M >= 1.
+// on every rank. `recv_local` / `recv_peer[p]`: peer-mapped 2 * tp * ksplit * ceil(M/128)*128 * N bf16 with
+// ksplit = mfb_tp_allreduce_ksplit(M, N, K); `tile_flags_*`: peer-mapped 2 * tp * 8 * flag_tiles ints, persistent
+// across calls, zero at the start of the job. Any M >= 1.
+// K-split used for a problem: more than 1 only with a single row block (decode), when all tile x split CTAs are
+// resident at once (the reducing CTA of a tile waits for its helpers) and every split keeps at least 8 K blocks.
+int mfb_tp_allreduce_ksplit(int M, int N, int K) {
+  if (M > kTpBM) return 1;
+  const int tiles = (N + 127) / 128;
+  const int k_blocks = (K + kTpBK - 1) / kTpBK;
+  int ks = 148 / tiles;
+  if (ks > 8) ks = 8;
+  while (ks > 1 && (k_blocks / ks < 8 || ((k_blocks + ks - 1) / ks) * (ks - 1) >= k_blocks)) --ks;
+  return ks < 1 ? 1 : ks;
+}
+
 int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
                           int b_mn_major, int tp, int rank, int epoch, void* recv_local, void* const* recv_peer,
                           int* tile_flags_local, int* const* tile_flags_peer, int flag_tiles, int* status,
@@ -684,8 +721,9 @@ int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, i
       return 1;
     }
   }
+  a.ksplit = mfb_tp_allreduce_ksplit(M, N, K);
   // few row blocks (decode): narrower tiles put more SMs to work
-  const bool bn256 = N >= 256 && a.num_m_blocks * ((N + 255) / 256) >= 96;
+  const bool bn256 = a.ksplit == 1 && N >= 256 && a.num_m_blocks * ((N + 255) / 256) >= 96;
   const int BN = bn256 ? 256 : 128;
   a.num_n_blocks = (N + BN - 1) / BN;
   if (a.num_m_blocks * a.num_n_blocks > flag_tiles) {

@@ -32,6 +32,7 @@ _lib.optional_entry("mfb_tp_gemm_reduce_scatter",
                      ctypes.c_void_p, ctypes.c_void_p])
 
 
+_lib.optional_entry("mfb_tp_allreduce_ksplit", [ctypes.c_int, ctypes.c_int, ctypes.c_int])
 _lib.optional_entry("mfb_tp_gemm_allreduce",
                     [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                      ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
@@ -89,7 +90,7 @@ class TpCommContext:
         """Receive slots (2 parities x tp ranks x ``elems`` bf16) and tile flags of the one-shot all-reduce;
         collective over the TP group when something has to be allocated."""
         if self.ar_flags is None:
-            self.ar_flags = symm_mem.allocate("tp_ar_flags", 2 * self.tp * AR_FLAG_TILES * 4, self.group, self.device)
+            self.ar_flags = symm_mem.allocate("tp_ar_flags", 2 * self.tp * 8 * AR_FLAG_TILES * 4, self.group, self.device)
             self.ar_flags.tensor.zero_()
             torch.cuda.synchronize()
             self.ar_flags.handle.barrier()
@@ -188,7 +189,8 @@ def gemm_all_reduce(x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> tor
     T, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     rows = (T + 127) // 128 * 128
-    ctx.ensure_allreduce(rows * N)
+    ksplit = _lib.get_lib().mfb_tp_allreduce_ksplit(T, N, K)     # decode: several CTAs share the K range of a tile
+    ctx.ensure_allreduce(ksplit * rows * N)
     ctx.ar_epoch += 1
     if not x.is_contiguous():
         x = x.contiguous()
