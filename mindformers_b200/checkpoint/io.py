@@ -172,9 +172,21 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
     params = dict(model.named_parameters())
     buffers = dict(model.named_buffers())
     missing, used = [], set()
+    fp8_modules = []
     with torch.no_grad():
         for n, p in params.items():
             src = sd.get(n)
+            if src is not None and src.dtype == torch.float8_e4m3fn:
+                # block-scaled fp8 weight: de-quantise, load (and shard) like any other tensor, then re-quantise the
+                # local shard in place once everything is loaded (shard boundaries are multiples of the 128 block)
+                scale = sd.get(n + "_scale_inv")
+                if scale is None:
+                    raise KeyError(f"{n} is fp8 but {n}_scale_inv is missing from {path}")
+                src = name_maps.weight_dequant(src, scale)
+                used.add(n + "_scale_inv")
+                owner = model.get_submodule(_owner_path(model, n))
+                if hasattr(owner, "quantize_fp8_"):
+                    fp8_modules.append(owner)
             if src is None and n == "output_layer.weight" and "embedding.word_embeddings.weight" in sd \
                     and not getattr(model.config, "untie_embeddings_and_output_weights", True):
                 src = sd["embedding.word_embeddings.weight"]
@@ -188,6 +200,8 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
             if n in sd and tuple(sd[n].shape) == tuple(b.shape):
                 b.copy_(sd[n].to(device=b.device, dtype=b.dtype))
                 used.add(n)
+        for mod in fp8_modules:
+            mod.quantize_fp8_()
     if missing and strict:
         raise KeyError(f"checkpoint {path} lacks parameters: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
     if missing:
@@ -209,6 +223,17 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
                     if src is not None and dst is not None and src.numel() == dst.numel():
                         dst.copy_(src.to(dst.device))
     return scalars
+
+
+def _owner_path(model: torch.nn.Module, param_name: str) -> str:
+    """Module path of a parameter name as ``named_parameters`` of the model reports it (wrappers that strip a
+    ``model.`` prefix from their parameter names are looked through)."""
+    mod_path = param_name.rsplit(".", 1)[0] if "." in param_name else ""
+    try:
+        model.get_submodule(mod_path)
+        return mod_path
+    except AttributeError:
+        return "model." + mod_path if mod_path else "model"
 
 
 def save_pretrained_dir(model: torch.nn.Module, directory: str, config_dict: Optional[dict] = None,

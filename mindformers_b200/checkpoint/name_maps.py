@@ -221,20 +221,46 @@ def hf_to_framework(hf_sd: Dict[str, torch.Tensor], config, family: str = "llama
                     keep_fp8: bool = False) -> Dict[str, torch.Tensor]:
     """Full conversion of an HF state dict (fp8 block-scaled weights are dequantised unless ``keep_fp8``)."""
     plain: Dict[str, torch.Tensor] = {}
+    any_fp8 = False
     for name, t in hf_sd.items():
         if name.endswith("_scale_inv"):
             continue
-        if t.dtype == torch.float8_e4m3fn and not keep_fp8:
+        if t.dtype == torch.float8_e4m3fn:
             sc = hf_sd.get(name + "_scale_inv")
             if sc is None:
                 raise KeyError(f"{name} is fp8 but {name}_scale_inv is missing")
-            t = weight_dequant(t, sc)
+            t = weight_dequant(t, sc)           # the fused layouts are built from full-precision tensors
+            any_fp8 = True
         if "rotary_emb.inv_freq" in name:
             continue
-        if dtype is not None and t.is_floating_point() and t.dtype != torch.float8_e4m3fn:
+        if dtype is not None and t.is_floating_point():
             t = t.to(dtype)
         plain[convert_name(name, family)] = t
-    return fuse_state_dict(plain, config)
+    out = fuse_state_dict(plain, config)
+    if keep_fp8 and any_fp8:
+        out = requantize_linear_weights(out)
+    return out
+
+
+FP8_KEEP_FULL_PRECISION = ("embedding", "output_layer", "router", "linear_kvb", "layernorm", "norm")
+
+
+def requantize_linear_weights(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Fused 2-D ``linear_*`` weights back to block-scaled fp8: ``X.weight`` (e4m3) + ``X.weight_scale_inv`` (fp32, one
+    per 128 x 128 block). Blocks of the fused tensors coincide with the blocks of their fp8 sources whenever the
+    fused parts are multiples of 128 rows, so the values survive the round trip. Weights whose shape is not a
+    multiple of 128, expert stacks and the layers in ``FP8_KEEP_FULL_PRECISION`` stay as they are."""
+    from ..ops.functional import quantize_weight_128x128
+    out: Dict[str, torch.Tensor] = {}
+    for name, t in sd.items():
+        if (name.endswith(".weight") and t.dim() == 2 and ".linear_" in name and t.shape[0] % 128 == 0
+                and t.shape[1] % 128 == 0 and not any(k in name for k in FP8_KEEP_FULL_PRECISION)):
+            q, scale = quantize_weight_128x128(t)
+            out[name] = q
+            out[name + "_scale_inv"] = scale
+        else:
+            out[name] = t
+    return out
 
 
 def framework_to_hf(sd: Dict[str, torch.Tensor], config, family: str = "llama", dtype=None) -> Dict[str, torch.Tensor]:

@@ -36,3 +36,35 @@ def test_quantize_model_fp8_matches_full_precision():
     assert (out.argmax(-1) == ref.argmax(-1)).float().mean() > 0.7
     seqs = model.generate(ids[:, :8].tolist(), max_new_tokens=4, do_sample=False)
     assert all(len(s) == 12 for s in seqs)
+
+
+def test_fp8_checkpoint_roundtrip(tmp_path):
+    """A checkpoint with block-scaled fp8 linear weights loads into a model and leaves fp8 layers behind."""
+    from safetensors.torch import save_file
+    from mindformers_b200.checkpoint import name_maps
+    from mindformers_b200.checkpoint.io import load_checkpoint
+    model = tiny_deepseek()
+    ids = torch.randint(3, 512, (1, 16))
+    with torch.no_grad():
+        ref = model(ids).float()
+    sd = {k: v.detach().clone() for k, v in model.named_parameters()}
+    q = name_maps.requantize_linear_weights(sd)
+    fp8_names = [k for k, v in q.items() if v.dtype == torch.float8_e4m3fn]
+    assert fp8_names and all(k + "_scale_inv" in q for k in fp8_names)
+    assert not any("linear_kvb" in k or "router" in k for k in fp8_names)
+    # values survive de-quantise -> re-quantise exactly (same blocks, same scales)
+    name = fp8_names[0]
+    again, scale2 = __import__("mindformers_b200.ops.functional", fromlist=["x"]).quantize_weight_128x128(
+        name_maps.weight_dequant(q[name], q[name + "_scale_inv"]).float())
+    assert torch.equal(again.view(torch.uint8), q[name].view(torch.uint8))
+    save_file({k: v.contiguous() for k, v in q.items()}, str(tmp_path / "model.safetensors"))
+    fresh = tiny_deepseek()
+    with torch.no_grad():
+        for p in fresh.parameters():
+            p.add_(1.0)                       # make sure the values come from the file
+    load_checkpoint(fresh, str(tmp_path / "model.safetensors"), strict=True, family="deepseek_v3")
+    mods = dict(fresh.named_modules())
+    assert mods["model.decoder.layers.0.mlp.linear_fc1"].weight_fp8 is not None
+    with torch.no_grad():
+        out = fresh(ids).float()
+    assert ((out - ref).norm() / ref.norm()).item() < 0.08
