@@ -60,6 +60,7 @@ class TpCommContext:
         self.ar_flags = None
         self.ar_recv = None
         self.ar_elems = 0
+        self.ar_arrays = None
 
     def _ptr_array(self, ptrs):
         arr = (ctypes.c_void_p * 8)()
@@ -195,12 +196,15 @@ def gemm_all_reduce(x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> tor
     if not x.is_contiguous():
         x = x.contiguous()
     y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
-    recv = list(ctx.ar_recv.ptrs)
-    tf = list(ctx.ar_flags.ptrs)
+    cached = ctx.ar_arrays
+    if cached is None or cached[0] is not ctx.ar_recv:
+        recv, tf = list(ctx.ar_recv.ptrs), list(ctx.ar_flags.ptrs)
+        cached = ctx.ar_arrays = (ctx.ar_recv, recv[rank], ctx._ptr_array(recv), tf[rank], ctx._ptr_array(tf))
+    _, recv_local, recv_arr, tf_local, tf_arr = cached
     st = _lib.status_word(x.device)
     rc = _lib.get_lib().mfb_tp_gemm_allreduce(x.data_ptr(), w.data_ptr(), y.data_ptr(), T, N, K, x.stride(0),
-                                              w.stride(0), y.stride(0), int(b_mn), tp, rank, ctx.ar_epoch, recv[rank],
-                                              ctx._ptr_array(recv), tf[rank], ctx._ptr_array(tf), AR_FLAG_TILES,
+                                              w.stride(0), y.stride(0), int(b_mn), tp, rank, ctx.ar_epoch, recv_local,
+                                              recv_arr, tf_local, tf_arr, AR_FLAG_TILES,
                                               st.data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "mfb_tp_gemm_allreduce")
     _lib.count_launch()

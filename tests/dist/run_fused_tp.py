@@ -35,6 +35,25 @@ def timeit(fn, iters=10):
     return t.item()
 
 
+def timeit_queued(fn, iters=50):
+    """Device time per call with the launches queued behind a spin kernel, so that host-side launch cost does not
+    show: what the call costs inside a step whose host runs ahead of the GPU."""
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(40_000_000)          # about 20 ms: the host enqueues all calls meanwhile
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
@@ -102,6 +121,9 @@ def main():
             t_f = timeit(lambda: fused_tp.gemm_all_reduce(x3, w3), iters=50)
             t_n = timeit(lambda: M.all_reduce(torch.matmul(x3, w3.t()), grp, tp), iters=50)
             res[f"bench_ar_{tag}"] = {"fused_ms": t_f, "nccl_cublas_ms": t_n,
+                                      "fused_queued_ms": timeit_queued(lambda: fused_tp.gemm_all_reduce(x3, w3)),
+                                      "nccl_cublas_queued_ms": timeit_queued(
+                                          lambda: M.all_reduce(torch.matmul(x3, w3.t()), grp, tp)),
                                       "bytes_over_nvlink": (tp - 1) * Tq * N3 * 2,
                                       "nvlink_floor_ms": (tp - 1) * Tq * N3 * 2 / 770e9 * 1e3,
                                       "gemm_floor_ms": 2.0 * Tq * N3 * K3 / 1415.7e12 * 1e3,
