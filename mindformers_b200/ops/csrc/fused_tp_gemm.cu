@@ -368,21 +368,24 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
           if (++acc == 2) { acc = 0; acc_phase ^= 1; }
           continue;
         }
-        if (issuer) {
-          // ---- the other partial tiles: every rank's K-splits ----
-          for (int sl = 0; sl < n_slots && ok; ++sl) {
+        if (warp == 2) {
+          // ---- the other partial tiles: every rank's K-splits; the lanes of one warp poll the flags side by side ----
+          bool okl = ok;
+          for (int sl = lane; sl < n_slots && okl; sl += 32) {
             if (sl == my_slot) continue;
-            ok = wait_flag_ge<true>(args.tile_flags_local + (static_cast<size_t>(parity) * n_slots + sl) * tiles_per_chunk + tile_in_chunk,
-                                    args.epoch, abort_flag, args.status);
+            okl = wait_flag_ge<true>(args.tile_flags_local + (static_cast<size_t>(parity) * n_slots + sl) * tiles_per_chunk + tile_in_chunk,
+                                     args.epoch, abort_flag, args.status);
           }
+          ok = __all_sync(0xffffffffu, okl);
         }
         ok = named_bar_and(2, 128, ok);
         if (!ok) break;
-        // ---- sum in rank order and store ----
+        // ---- sum in slot order and store ----
 #pragma unroll 1
         for (int c = 0; c < NUM_CHUNKS; ++c) {
           uint32_t packed[32];
           const int col0 = t.n_blk * BN + c * 64;
+          const bool in_range = col0 < args.N;
 #pragma unroll 1
           for (int hf = 0; hf < 2; ++hf) {
             uint32_t v[32];
@@ -391,22 +394,38 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) sum[i] = 0.f;
-            for (int sl = 0; sl < n_slots; ++sl) {
-              if (sl == my_slot) {
+            const __nv_bfloat16* src0 = args.recv_local + static_cast<size_t>(parity) * n_slots * slot_elems +
+                                        static_cast<size_t>(t.m_blk * kTpBM + row) * args.N + col0 + hf * 32;
+            // the loads of up to four slots are in flight together; the additions keep the slot order
+#pragma unroll 1
+            for (int base = 0; base < n_slots; base += 4) {
+              uint4 buf[4][4];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sum[i] += __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
-              } else if (col0 < args.N) {
-                const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * n_slots + sl) * slot_elems +
-                                           static_cast<size_t>(t.m_blk * kTpBM + row) * args.N + col0 + hf * 32;
+              for (int u = 0; u < 4; ++u) {
+                const int sl = base + u;
+                if (sl < n_slots && sl != my_slot && in_range) {
+                  const __nv_bfloat16* src = src0 + static_cast<size_t>(sl) * slot_elems;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint4 u = ld_cg_v4(src + j * 8);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+                  for (int j = 0; j < 4; ++j) buf[u][j] = ld_cg_v4(src + j * 8);
+                }
+              }
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    const float2 f = __bfloat1622float2(h[q]);
-                    sum[j * 8 + q * 2] += f.x;
-                    sum[j * 8 + q * 2 + 1] += f.y;
+              for (int u = 0; u < 4; ++u) {
+                const int sl = base + u;
+                if (sl >= n_slots) continue;
+                if (sl == my_slot) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) sum[i] += __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+                } else if (in_range) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&buf[u][j]);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                      const float2 f = __bfloat1622float2(h[q]);
+                      sum[j * 8 + q * 2] += f.x;
+                      sum[j * 8 + q * 2 + 1] += f.y;
+                    }
                   }
                 }
               }
