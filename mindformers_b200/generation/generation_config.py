@@ -34,6 +34,8 @@ class GenerationConfig:
         self.eos_token_id: Optional[Union[int, List[int]]] = kwargs.pop("eos_token_id", None)
         self.parallel_decoding = kwargs.pop("parallel_decoding", None)
         self.chunk_prefill_size = kwargs.pop("chunk_prefill_size", None)
+        # capture the decode step in a CUDA graph (single-GPU models; falls back to eager launches otherwise)
+        self.use_cuda_graph = kwargs.pop("use_cuda_graph", False)
         self.seed = kwargs.pop("seed", None)
         self._extra = dict(kwargs)
 

@@ -87,6 +87,71 @@ class GenerationMixin:
             logits = torch.cat(parts, dim=-1)
         return logits[:, : self.config.vocab_size]
 
+    # ---- decode step as a CUDA graph ---------------------------------------------------------------------
+    def _graph_decoder(self, B: int, ctx: KVCacheContext, tables: BlockTables):
+        """Build a callable ``step(tokens, starts, active) -> logits [B, V]`` that replays one captured decode step.
+
+        Everything the step reads lives in static device tensors (token ids, positions, block tables, slot mapping,
+        context lengths); a step copies the new values in and replays. Only for models on one GPU: the fused
+        communication kernels take a per-call epoch argument and cannot be replayed. Returns None when the step
+        cannot be captured (the caller then launches eagerly)."""
+        device = next(self.parameters()).device
+        if device.type != "cuda" or ps.get_tensor_model_parallel_world_size() > 1 \
+                or ps.get_expert_model_parallel_world_size() > 1 or ps.get_pipeline_model_parallel_world_size() > 1:
+            return None
+        width = tables.max_blocks_per_seq
+        st_tok = torch.zeros(1, B, dtype=torch.int64, device=device)
+        st_pos = torch.zeros(B, dtype=torch.int64, device=device)
+        st_table = torch.zeros(B, width, dtype=torch.int32, device=device)
+        st_slots = torch.zeros(B, dtype=torch.int32, device=device)
+        st_lens = torch.ones(B, dtype=torch.int32, device=device)
+        host = {k: torch.empty(t.shape, dtype=t.dtype).pin_memory() for k, t in
+                (("tok", st_tok), ("pos", st_pos), ("table", st_table), ("slots", st_slots), ("lens", st_lens))}
+
+        def bind():
+            ctx.is_prefill = False
+            ctx.block_tables, ctx.slot_mapping, ctx.context_lens = st_table, st_slots, st_lens
+            ctx.q_seq_lens = torch.ones(B, dtype=torch.int32, device=device)
+            ctx.cu_q = list(range(B + 1))
+            ctx.last_token_index = torch.arange(B, dtype=torch.int64, device=device)
+
+        def fill(tokens, starts, active):
+            table, slots = tables.assemble_pa_inc_inputs(active, 1)
+            host["tok"][0].copy_(torch.tensor([t[0] for t in tokens], dtype=torch.int64))
+            host["pos"].copy_(torch.tensor(starts, dtype=torch.int64))
+            host["table"].copy_(torch.from_numpy(table))
+            host["slots"].copy_(torch.from_numpy(slots))
+            host["lens"].copy_(torch.from_numpy(tables.context_lens()))
+            for k, dst in (("tok", st_tok), ("pos", st_pos), ("table", st_table), ("slots", st_slots), ("lens", st_lens)):
+                dst.copy_(host[k], non_blocking=True)
+
+        def forward():
+            meta = AttnMeta(batch=1, seq_len=B, positions=st_pos, cache=ctx)
+            return self.model(st_tok, attn_meta=meta)
+
+        state = {"graph": None, "out": None}
+
+        def step(tokens, starts, active):
+            fill(tokens, starts, active)
+            bind()
+            if state["graph"] is None:
+                # the first call runs eagerly twice on a side stream (lazy allocations, kernel attributes), then captures
+                side = torch.cuda.Stream(device=device)
+                side.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(side):
+                    forward()
+                    forward()
+                torch.cuda.current_stream(device).wait_stream(side)
+                torch.cuda.synchronize(device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    state["out"] = forward()
+                state["graph"] = graph
+            state["graph"].replay()
+            return state["out"][:, : self.config.vocab_size]
+
+        return step
+
     # ---- public API -----------------------------------------------------------------------------------
     @torch.no_grad()
     def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]], torch.Tensor],
@@ -146,6 +211,7 @@ class GenerationMixin:
             logits = self._forward_step(seqs, [0] * B, ctx, tables, True)
         ttft = time.time() - t0
         new_tokens = 0
+        graph_step = self._graph_decoder(B, ctx, tables) if getattr(gcfg, "use_cuda_graph", False) else None
         while True:
             nxt = self._select(seqs, logits, processors, warper, gen, gcfg)
             for i in range(B):
@@ -163,7 +229,10 @@ class GenerationMixin:
                 break
             act = [not f for f in finished]
             toks = [[s[-1]] for s in seqs]
-            logits = self._forward_step(toks, [len(s) - 1 for s in seqs], ctx, tables, False, act)
+            if graph_step is not None:
+                logits = graph_step(toks, [len(s) - 1 for s in seqs], act)
+            else:
+                logits = self._forward_step(toks, [len(s) - 1 for s in seqs], ctx, tables, False, act)
         if streamer is not None:
             streamer.end()
         tables.clear_cache()

@@ -476,3 +476,27 @@ def test_bounded_peer_wait_reports_status_instead_of_hanging():
     assert 1.0 < waited < 10.0
     st.zero_()
     assert torch.ones(4, device="cuda").sum().item() == 4.0     # the device still answers
+
+
+@pytest.mark.parametrize("family", ["llama", "deepseek"])
+def test_generate_with_cuda_graph_matches_eager(family):
+    """The decode step replayed from a CUDA graph yields the same greedy tokens as eager launches."""
+    from mindformers_b200.models import AutoModel
+    if family == "llama":
+        cfg = dict(model_type="llama", num_hidden_layers=2, hidden_size=512, num_attention_heads=4, num_key_value_heads=2,
+                   intermediate_size=1024, vocab_size=1024, max_position_embeddings=512, head_dim=128, block_size=16)
+    else:
+        cfg = dict(model_type="deepseek_v3", num_hidden_layers=3, hidden_size=512, num_attention_heads=4,
+                   num_key_value_heads=4, intermediate_size=1024, moe_intermediate_size=256, n_routed_experts=8,
+                   n_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, routed_scaling_factor=1.0,
+                   norm_topk_prob=True, scoring_func="sigmoid", first_k_dense_replace=1, vocab_size=1024,
+                   q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                   max_position_embeddings=512, moe_router_enable_expert_bias=True, block_size=128)
+    torch.manual_seed(0)
+    model = AutoModel.from_config(cfg, device="cuda").eval()
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(3, 1024, (3, 128), generator=g).tolist()
+    eager = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None)
+    graphed = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None, use_cuda_graph=True)
+    assert eager == graphed
+    assert _lib.read_status() == 0
