@@ -26,7 +26,8 @@ def param_layout(name: str, p: torch.Tensor) -> dict:
         lay.update(ep=ep, ep_rank=ps.get_expert_model_parallel_rank())
     if getattr(p, "tensor_model_parallel", False) and tp > 1:
         lay.update(tp=tp, dim=int(getattr(p, "partition_dim", 0)), tp_rank=ps.get_tensor_model_parallel_rank(),
-                   sections=list(getattr(p, "partition_sections", None) or []) or None)
+                   sections=list(getattr(p, "partition_sections", None) or []) or None,
+                   groups=list(getattr(p, "partition_groups", None) or []) or None)
     return lay
 
 
@@ -40,7 +41,7 @@ def shard_for_param(full: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
     if lay["tp"] > 1:
         dim, rank, tp = lay["dim"], lay["tp_rank"], lay["tp"]
         if lay["sections"]:
-            t = shard_sections(t, lay["sections"], dim, rank, tp)
+            t = shard_sections(t, lay["sections"], dim, rank, tp, lay.get("groups"))
         else:
             n = t.shape[dim]
             per = p.shape[dim]
@@ -73,9 +74,17 @@ def merge_shards(shards: List[torch.Tensor], layout: dict, full_rows: Optional[i
     if tp <= 1 or dim < 0:
         return shards[0]
     if sections:
-        per = [s // tp for s in sections]
+        groups = layout.get("groups")
+        from ..parallel.layers.tensor_parallel import section_local_sizes
+        per = section_local_sizes(sections, tp, groups)
         pieces = [torch.split(s, per, dim=dim) for s in shards]
-        return torch.cat([torch.cat([pieces[r][i] for r in range(tp)], dim=dim) for i in range(len(sections))], dim=dim)
+        out = []
+        for i in range(len(sections)):
+            g = groups[i] if groups else None
+            # a replicated section: one copy of each group, taken from the first rank that holds it
+            ranks = [j * tp // g for j in range(g)] if g and g < tp else range(tp)
+            out.append(torch.cat([pieces[r][i] for r in ranks], dim=dim))
+        return torch.cat(out, dim=dim)
     out = torch.cat(shards, dim=dim)
     if full_rows is not None and out.shape[dim] > full_rows:
         out = out.narrow(dim, 0, full_rows)

@@ -96,12 +96,18 @@ class SelfAttention(nn.Module):
         q_size, kv_size = self.nq_total * self.hd, self.nkv_total * self.hd
         sections = (q_size, kv_size, kv_size) if self.contiguous_layout else None
         tp = ps.get_tensor_model_parallel_world_size()
+        groups = None
         if self.nkv_total < tp:
-            raise NotImplementedError("tensor parallel size above the number of KV heads needs KV replication "
-                                      "at load time; use tp <= num_query_groups")
+            # more ranks than KV heads: every rank keeps one whole KV head, replicated over tp / kv_heads ranks
+            # (reference: QKVParallelLinear of the inference stack, tensor_parallel/layers.py:262-275). Inference only:
+            # the gradients of the replicas are not summed between them.
+            if not self.contiguous_layout or tp % self.nkv_total:
+                raise NotImplementedError("a tensor-parallel size above the number of KV heads needs the contiguous "
+                                          "[Q; K; V] weight layout and tp divisible by the number of KV heads")
+            groups = (self.nq_total, self.nkv_total, self.nkv_total)
         self.linear_qkv = ColumnParallelLinear(config.hidden_size, q_size + 2 * kv_size, config=config,
                                                bias=config.add_qkv_bias or config.add_bias_linear,
-                                               partition_sections=sections)
+                                               partition_sections=sections, partition_groups=groups)
         if config.qk_layernorm:
             self.q_layernorm = RMSNorm(config, self.hd, config.layernorm_epsilon)
             self.k_layernorm = RMSNorm(config, self.hd, config.layernorm_epsilon)

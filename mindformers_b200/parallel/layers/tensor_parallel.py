@@ -21,13 +21,38 @@ from .. import mappings as M
 from .. import parallel_state as ps
 
 
-def shard_sections(w: torch.Tensor, sections, dim: int, rank: int, world: int) -> torch.Tensor:
+def section_local_sizes(sections, world: int, groups=None):
+    """Rows of each section that one rank holds. ``groups[i]`` is the number of indivisible groups (heads) of
+    section ``i``; a section with fewer groups than ranks is replicated: each rank holds one whole group."""
+    out = []
+    for i, size in enumerate(sections):
+        g = groups[i] if groups else None
+        if g and g < world:
+            if world % g or size % g:
+                raise ValueError(f"section of {g} groups cannot be replicated over {world} ranks")
+            out.append(size // g)
+        else:
+            if size % world:
+                raise ValueError(f"section of size {size} is not divisible by {world}")
+            out.append(size // world)
+    return out
+
+
+def shard_sections(w: torch.Tensor, sections, dim: int, rank: int, world: int, groups=None) -> torch.Tensor:
     """Split ``w`` along ``dim`` into ``sections`` (e.g. q|k|v or gate|up), shard each over ``world``
-    ranks and concatenate this rank's pieces, so every rank holds its slice of every section."""
+    ranks and concatenate this rank's pieces, so every rank holds its slice of every section. A section with
+    fewer ``groups`` than ranks (K/V heads under a tensor-parallel size above their number) is replicated: rank
+    ``r`` takes group ``r * groups // world``."""
     if world == 1:
         return w
     parts = []
-    for piece in torch.split(w, list(sections), dim=dim):
+    for i, piece in enumerate(torch.split(w, list(sections), dim=dim)):
+        g = groups[i] if groups else None
+        if g and g < world:
+            if world % g or piece.shape[dim] % g:
+                raise ValueError(f"section of {g} groups cannot be replicated over {world} ranks")
+            parts.append(piece.chunk(g, dim=dim)[rank * g // world])
+            continue
         if piece.shape[dim] % world != 0:
             raise ValueError(f"section of size {piece.shape[dim]} is not divisible by {world}")
         parts.append(piece.chunk(world, dim=dim)[rank])
@@ -35,14 +60,14 @@ def shard_sections(w: torch.Tensor, sections, dim: int, rank: int, world: int) -
 
 
 def _init_weight(shape, init_method, dtype, device, partition_dim=None, full_shape=None, rank=0, world=1,
-                 sections=None):
+                 sections=None, groups=None):
     """Initialise the full matrix with a fixed generator state, then keep this rank's slice, so the
     values do not depend on the tensor-parallel size."""
     w = torch.empty(full_shape or shape, dtype=torch.float32, device=device)
     init_method(w)
     if world > 1 and partition_dim is not None:
         if sections:
-            w = shard_sections(w, sections, partition_dim, rank, world)
+            w = shard_sections(w, sections, partition_dim, rank, world, groups)
         else:
             w = w.chunk(world, dim=partition_dim)[rank].contiguous()
     return nn.Parameter(w.to(dtype=dtype))
@@ -130,15 +155,20 @@ class ColumnParallelLinear(_Fp8WeightMixin, nn.Module):
     def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
                  bias: bool = False, gather_output: bool = False, skip_bias_add: bool = False,
                  skip_weight_param_allocation: bool = False, is_expert: bool = False, tp_group=None,
-                 stride: int = 1, partition_sections=None):
+                 stride: int = 1, partition_sections=None, partition_groups=None):
         super().__init__()
         self.config = config
         self.tp = 1 if is_expert and config.expert_tensor_parallel_size == 1 else ps.get_tensor_model_parallel_world_size()
         self.rank = ps.get_tensor_model_parallel_rank() if self.tp > 1 else 0
-        if output_size % self.tp != 0:
-            raise ValueError(f"output_size {output_size} is not divisible by the tensor-parallel size {self.tp}")
         self.input_size, self.output_size = input_size, output_size
-        self.output_size_per_partition = output_size // self.tp
+        if partition_sections and partition_groups and self.tp > 1:
+            # sections with fewer groups than ranks (K/V heads) are replicated, so a rank holds more than 1/tp of the rows
+            self.output_size_per_partition = sum(section_local_sizes(partition_sections, self.tp, partition_groups))
+        else:
+            partition_groups = None
+            if output_size % self.tp != 0:
+                raise ValueError(f"output_size {output_size} is not divisible by the tensor-parallel size {self.tp}")
+            self.output_size_per_partition = output_size // self.tp
         self.gather_output, self.skip_bias_add = gather_output, skip_bias_add
         self.sequence_parallel = bool(config.sequence_parallel) and self.tp > 1
         self.is_expert = is_expert
@@ -149,14 +179,16 @@ class ColumnParallelLinear(_Fp8WeightMixin, nn.Module):
         else:
             self.weight = _init_weight((self.output_size_per_partition, input_size), init, config.params_dtype, dev,
                                        partition_dim=0, full_shape=(output_size, input_size), rank=self.rank,
-                                       world=self.tp, sections=partition_sections)
+                                       world=self.tp, sections=partition_sections, groups=partition_groups)
             _mark_tp(self.weight, self.tp > 1, 0)
             self.weight.partition_stride = stride
             self.weight.partition_sections = tuple(partition_sections) if partition_sections else None
+            self.weight.partition_groups = tuple(partition_groups) if partition_groups else None
         if bias:
             self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=config.params_dtype, device=dev))
             _mark_tp(self.bias, self.tp > 1, 0)
             self.bias.partition_sections = tuple(partition_sections) if partition_sections else None
+            self.bias.partition_groups = tuple(partition_groups) if partition_groups else None
         else:
             self.register_parameter("bias", None)
 

@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--moe", type=int, default=0)
     ap.add_argument("--cp-type", default="all_gather")
     ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--kv-groups", type=int, default=2)
+    ap.add_argument("--forward-only", type=int, default=0, help="no training: write the loss of one forward pass")
     ap.add_argument("--out", required=True)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -36,7 +38,7 @@ def main():
     ps.initialize_model_parallel(tensor_model_parallel_size=args.tp, context_parallel_size=args.cp,
                                  expert_model_parallel_size=args.ep, expert_tensor_parallel_size=1 if args.moe else None)
     torch.manual_seed(7)
-    kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=128,
+    kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=args.kv_groups, ffn_hidden_size=128,
               vocab_size=256, seq_length=32, max_position_embeddings=32, params_dtype="float32",
               compute_dtype="float32", use_scaled_init=False, pad_token_id=-1,
               tensor_model_parallel_size=args.tp, sequence_parallel=bool(args.sp), context_parallel_size=args.cp,
@@ -47,6 +49,17 @@ def main():
     cfg = TransformerConfig(**kw)
     cfg.device = "cpu"
     model = GPTModel(cfg)
+    if args.forward_only:
+        g = torch.Generator().manual_seed(99)
+        ids = torch.randint(0, 256, (4, 33), generator=g)
+        with torch.no_grad():
+            loss = model.eval()(ids[:, :-1].contiguous(), labels=ids[:, 1:].contiguous())
+        if int(os.environ.get("RANK", "0")) == 0:
+            with open(args.out, "w") as f:
+                json.dump({"losses": [float(loss)], "digest": {}, "norm": 0.0}, f)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     opt = DistributedOptimizer(model, learning_rate=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0,
                                sequence_parallel=bool(args.sp))
     step = TrainOneStep(model, opt, micro_batch_size=1)

@@ -53,6 +53,14 @@ def test_tensor_parallel(tmp_path, dense_ref):
     _close(_run(tmp_path, 2, "tp2", "--tp", "2"), dense_ref, 2e-5)
 
 
+def test_tensor_parallel_above_kv_heads_replicates_kv(tmp_path):
+    """tp = 4 with 2 KV heads (and tp = 2 with 1): every rank keeps one whole KV head; the forward pass matches tp = 1."""
+    for groups, tp in ((2, 4), (1, 2)):
+        ref = _run(tmp_path, 1, f"ref_g{groups}", "--forward-only", "1", "--kv-groups", str(groups))
+        got = _run(tmp_path, tp, f"tp{tp}_g{groups}", "--tp", str(tp), "--forward-only", "1", "--kv-groups", str(groups))
+        assert abs(ref["losses"][0] - got["losses"][0]) < 2e-5, (groups, tp, ref["losses"], got["losses"])
+
+
 def test_tensor_parallel_sequence_parallel_with_dp(tmp_path, dense_ref):
     _close(_run(tmp_path, 4, "tp2sp_dp2", "--tp", "2", "--sp", "1"), dense_ref, 2e-5)
 
@@ -86,3 +94,19 @@ def test_pipeline_parallel_interleaved(tmp_path, pipe_ref):
 
 def test_pipeline_parallel_four_stages(tmp_path, pipe_ref):
     _close(_run(tmp_path, 4, "pp4", "--pp", "4", script=PIPE), pipe_ref, 2e-5)
+
+
+def test_replicated_section_shard_and_merge_roundtrip():
+    import torch
+    from mindformers_b200.checkpoint.sharding import merge_shards
+    from mindformers_b200.parallel.layers.tensor_parallel import section_local_sizes, shard_sections
+    hd, nq, nkv, tp = 4, 8, 2, 4
+    sections, groups = (nq * hd, nkv * hd, nkv * hd), (nq, nkv, nkv)
+    full = torch.arange(sum(sections) * 3, dtype=torch.float32).view(sum(sections), 3)
+    assert section_local_sizes(sections, tp, groups) == [8, 4, 4]
+    shards = [shard_sections(full, sections, 0, r, tp, groups) for r in range(tp)]
+    assert all(s.shape == (16, 3) for s in shards)
+    k = full[nq * hd:nq * hd + nkv * hd]
+    assert torch.equal(shards[0][8:12], k[:4]) and torch.equal(shards[1][8:12], k[:4]) and torch.equal(shards[2][8:12], k[4:])
+    merged = merge_shards(shards, {"tp": tp, "dim": 0, "sections": list(sections), "groups": list(groups)})
+    assert torch.equal(merged, full)
