@@ -102,6 +102,26 @@ class LoRALinear(nn.Module):
             self.merged = False
 
 
+class ColumnParallelLinearWithLoRA(LoRALinear):
+    """Column-parallel linear layer with a LoRA branch: ``lora_a`` replicated, ``lora_b`` split like the weight
+    (reference ``training_graph/tensor_parallel/lora_layers.py:56``). Builds the base layer itself."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, lora_rank: int = 8, lora_alpha: float = 16,
+                 lora_dropout: float = 0.0, lora_a_init: str = "normal", **base_kwargs):
+        super().__init__(ColumnParallelLinear(input_size, output_size, config=config, **base_kwargs), lora_rank,
+                         lora_alpha, lora_dropout, a_init=lora_a_init)
+
+
+class RowParallelLinearWithLoRA(LoRALinear):
+    """Row-parallel linear layer with a LoRA branch: ``lora_a`` split like the weight, ``lora_b`` replicated
+    (reference ``training_graph/tensor_parallel/lora_layers.py:234``)."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, lora_rank: int = 8, lora_alpha: float = 16,
+                 lora_dropout: float = 0.0, lora_a_init: str = "normal", **base_kwargs):
+        super().__init__(RowParallelLinear(input_size, output_size, config=config, **base_kwargs), lora_rank,
+                         lora_alpha, lora_dropout, a_init=lora_a_init)
+
+
 class LoraAdapter:
     @staticmethod
     def recursive_replace_dense_cell(module: nn.Module, config: LoraConfig, prefix: str = "") -> int:
