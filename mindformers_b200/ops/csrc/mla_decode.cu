@@ -5,21 +5,18 @@
 //     s[t]   = scale * <q[h, 0:576], c[t, 0:576]>          t < len
 //     o[h,:] = sum_t softmax(s)[t] * c[t, 0:512]
 // A CTA handles (split of the sequence, chunk of 16 heads, sequence). The products are laid out TRANSPOSED so
-// that the token dimension, not the (small) head count, sits on the rows of the tensor core:
-//     S^T [tokens x 16 heads]       = C_tile [tokens x 576] (A, K-major) . Q^T (B, K-major)       -> TMEM, 16 columns
-//     O^T [512 x 16]  (4 x M=128)  += C_tile^T (A, MN-major: the same bytes) . P^T [16 heads x tokens] (B, K-major)
+// that the token dimension, not the (small) head count, fills the 128 rows of the tensor core:
+//     S^T [128 tokens x 16 heads]   = C_tile [128 x 576] (A, K-major) . Q^T (B, K-major)          -> TMEM, 16 columns
+//     O^T [512 x 16]  (4 x M=128)  += C_tile^T (A, MN-major: the same bytes) . P^T [16 heads x 128 tokens] (B, K-major)
 // Softmax threads own one token row each; the per-head maximum over the 128 tokens of a tile is a shuffle
 // + shared-memory reduction, per-head sums stay thread-local until the end. O^T is rescaled in TMEM only when
 // a head's maximum grew by more than 2^8 (as in the flash-attention kernel).
 //
-// Memory latency, not bandwidth, bounds this kernel: what counts is how many bytes an SM keeps in flight while a tile
-// goes through its chain S^T -> softmax -> O^T. A tile is therefore 64 tokens (74 KB): it stays resident for both
-// products (one pass over the cache), and the kernel is sized so that TWO CTAs share an SM (100 KB of shared memory
-// and 256 TMEM columns each), so one CTA loads while the other one computes. The tensor core still runs M = 128: for
-// S^T the rows 64..127 of the A operand are whatever follows the tile in shared memory and give rows of S^T that
-// nobody reads; O^T contracts over the 64 tokens only. Units of a tile: the rope columns first, then four pairs of
-// 64 columns; S^T releases the rope slot, O^T releases each pair as soon as it has used it, and the producer refills
-// the slots in the same order with the next tile.
+// A tile of 128 tokens is 147 KB, so a second tile cannot be prefetched while one is resident, and the chain
+// S^T -> softmax -> O^T of a tile leaves the memory system idle. Instead the cache tile is STREAMED twice through a
+// small ring of 32 KB slots (first five units for S^T: four column pairs + the rope columns; then the four pairs
+// again for O^T, which hit L2), and the kernel is sized so that TWO CTAs share an SM (88 KB of shared memory and
+// 256 TMEM columns each): while one CTA sits in its softmax, the other one streams.
 //
 // Roles (192 threads): warp 0 = TMA producer (block-table lookups), warp 1 = MMA issuer + TMEM owner,
 // warps 2..5 = softmax / rescale / epilogue. Every wait is bounded (see common.cuh). Partial results of the splits
@@ -29,16 +26,15 @@
 namespace mfb {
 
 constexpr int kMlaThreads = 192;
-constexpr int kMlaTile = 64;               // tokens per tile
-constexpr int kMlaM = 128;                 // rows of every MMA
+constexpr int kMlaTile = 128;              // tokens per tile
 constexpr int kMlaHeads = 16;              // heads per CTA
 constexpr int kMlaRank = 512;
 constexpr int kMlaRope = 64;
 constexpr int kMlaDim = kMlaRank + kMlaRope;
-constexpr int kMlaSub = kMlaTile * 128;    // [64 tokens][64 columns] swizzled sub-tile, 8 KB
+constexpr int kMlaSub = kMlaTile * 128;    // [128 tokens][64 columns] swizzled sub-tile, 16 KB
 constexpr int kMlaUnit = 2 * kMlaSub;      // ring slot: a pair of sub-tiles (128 columns)
-constexpr int kMlaSlots = 5;               // rope + four column pairs: one resident tile
-constexpr int kMlaPBytes = kMlaHeads * 128;       // P^T: [16 heads][64 tokens] K-major
+constexpr int kMlaSlots = 2;
+constexpr int kMlaPBytes = 2 * kMlaHeads * 128;   // P^T: two [16 heads][64 tokens] K-major sub-tiles
 constexpr int kMlaTmemCols = 256;
 constexpr int kMlaQSub = kMlaHeads * 128;  // [16 heads][64 columns], 2 KB
 constexpr int kMlaQBytes = 9 * kMlaQSub;
@@ -65,8 +61,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sRing = smem;                               // 5 x 16 KB (+ 8 KB that the M = 128 S^T operand of the last slot overlaps)
-  uint8_t* sP = sRing + kMlaSlots * kMlaUnit + kMlaSub; // 2 KB
+  uint8_t* sRing = smem;                               // 2 x 32 KB
+  uint8_t* sP = sRing + kMlaSlots * kMlaUnit;          // 4 KB
   uint8_t* sQ = sP + kMlaPBytes;                       // 18 KB
   float* red = reinterpret_cast<float*>(sQ + kMlaQBytes);          // [4 warps][16]
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 4 * kMlaHeads);
@@ -127,34 +123,33 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       for (int c = 0; c < 9; ++c)
         tma_load_2d(smem_u32(sQ) + c * kMlaQSub, &tmQ, qb, c * 64, b * args.num_heads + head0);
       const int bs = args.block_size;
-      const int box = bs < kMlaTile ? bs : kMlaTile;     // rows of one TMA box
-      const int pages = kMlaTile / box;                  // boxes per sub-tile
+      const int pages = kMlaTile / bs;            // pages per tile (block_size divides 128)
       const int* table = args.block_tables + static_cast<size_t>(b) * args.max_blocks;
       uint32_t unit = 0;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int tok0 = (t0 + j) * kMlaTile;
-        int page_row[4];
-        const int first_row = table[tok0 / bs] * bs + tok0 % bs;
+        int page_row[8];
+        const int first_page = table[tok0 / bs];
         for (int i = 0; i < pages; ++i) {
-          // boxes past the end of the sequence may lie in unallocated pages: read the tile's first box instead (masked)
-          const int tk = tok0 + i * box;
-          page_row[i] = (tk < len) ? table[tk / bs] * bs + tk % bs : first_row;
+          // pages past the end of the sequence may be unallocated: read the tile's first page instead (masked)
+          const int pg = (tok0 + i * bs < len) ? table[tok0 / bs + i] : first_page;
+          page_row[i] = pg * bs;
         }
-        // one pass: [R P0 P1 P2 P3]; a pair stays in its slot until O^T has used it
-        for (int u = 0; u < 5 && ok; ++u) {
+        // two passes: [P0 P1 P2 P3 R] for S^T, then [P0 P1 P2 P3] again for O^T
+        for (int u = 0; u < 9 && ok; ++u) {
           const int slot = unit % kMlaSlots;
           const uint32_t ph = (unit / kMlaSlots) & 1;
           ok = mbar_wait(smem_u32(&empty[slot]), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full[slot]);
           const uint32_t dst = smem_u32(sRing + slot * kMlaUnit);
-          const bool rope = (u == 0);
-          const int col0 = rope ? kMlaRank : (u - 1) * 128;
+          const bool rope = (u == 4);
+          const int col0 = rope ? kMlaRank : (u < 4 ? u : u - 5) * 128;
           mbar_expect_tx(fb, rope ? kMlaSub : kMlaUnit);
           for (int i = 0; i < pages; ++i) {
-            tma_load_2d(dst + i * box * 128, &tmC, fb, col0, page_row[i]);
-            if (!rope) tma_load_2d(dst + kMlaSub + i * box * 128, &tmC, fb, col0 + 64, page_row[i]);
+            tma_load_2d(dst + i * bs * 128, &tmC, fb, col0, page_row[i]);
+            if (!rope) tma_load_2d(dst + kMlaSub + i * bs * 128, &tmC, fb, col0 + 64, page_row[i]);
           }
           ++unit;
         }
@@ -164,8 +159,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------ MMA issuer ------------------------------------
     if (lane == 0 && n_tiles > 0) {
-      constexpr uint32_t IDESC_S = umma_idesc_bf16(kMlaM, kMlaHeads, 0, 0);   // A = cache K-major, B = Q K-major
-      constexpr uint32_t IDESC_PV = umma_idesc_bf16(kMlaM, kMlaHeads, 1, 0);  // A = cache MN-major, B = P^T K-major
+      constexpr uint32_t IDESC_S = umma_idesc_bf16(kMlaTile, kMlaHeads, 0, 0);   // A = cache K-major, B = Q K-major
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(kMlaTile, kMlaHeads, 1, 0);  // A = cache MN-major, B = P^T K-major
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, args.status, kStatusWaitTimeoutMma);
       const uint32_t qa = smem_u32(sQ), pa = smem_u32(sP);
       uint32_t unit = 0;
@@ -174,8 +169,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t sph = (j >> 1) & 1;
         ok = mbar_wait(smem_u32(&s_empty[sb]), sph ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
-        // ---- S^T = C . Q^T over the five units ----
-        const uint32_t tile_unit0 = unit;
+        // ---- S^T = C . Q^T over the five units of the first pass ----
         for (int u = 0; u < 5 && ok; ++u) {
           const int slot = unit % kMlaSlots;
           const uint32_t ph = (unit / kMlaSlots) & 1;
@@ -183,9 +177,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!ok) break;
           tc_fence_after();
           const uint32_t ca = smem_u32(sRing + slot * kMlaUnit);
-          const bool rope = (u == 0);
+          const bool rope = (u == 4);
           const int ksteps = rope ? 4 : 8;
-          const int qsub0 = rope ? 8 : 2 * (u - 1);
+          const int qsub0 = rope ? 8 : 2 * u;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             if (k < ksteps) {
@@ -194,25 +188,29 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
               umma_f16_ss(tmem_S + sb * 32, a_desc, b_desc, IDESC_S, (u > 0 || k > 0) ? 1u : 0u);
             }
           }
-          if (rope) umma_commit(smem_u32(&empty[slot]));
+          umma_commit(smem_u32(&empty[slot]));
           ++unit;
         }
         if (!ok) break;
         umma_commit(smem_u32(&s_full[sb]));
-        // ---- O^T += C^T . P^T: the four pairs, each released after use ----
+        // ---- O^T += C^T . P^T over the four units of the second pass ----
         ok = mbar_wait(smem_u32(p_ready), j & 1, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
-        tc_fence_after();
-        for (int m = 0; m < 4; ++m) {
-          const int slot = (tile_unit0 + 1 + m) % kMlaSlots;
+        for (int m = 0; m < 4 && ok; ++m) {
+          const int slot = unit % kMlaSlots;
+          const uint32_t ph = (unit / kMlaSlots) & 1;
+          ok = mbar_wait(smem_u32(&full[slot]), ph, abort_flag, args.status, kStatusWaitTimeoutMma);
+          if (!ok) break;
+          tc_fence_after();
           const uint32_t ca = smem_u32(sRing + slot * kMlaUnit);
 #pragma unroll
           for (int k = 0; k < kMlaTile / 16; ++k) {
             const uint64_t a_desc = umma_desc_mnmajor_sw128(ca + k * 16 * 128, kMlaSub);
-            const uint64_t b_desc = umma_desc_kmajor_sw128(pa + (k & 3) * 32);
+            const uint64_t b_desc = umma_desc_kmajor_sw128(pa + (k >> 2) * (kMlaHeads * 128) + (k & 3) * 32);
             umma_f16_ss(tmem_O + m * 32, a_desc, b_desc, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty[slot]));
+          ++unit;
         }
         if (!ok) break;
         umma_commit(smem_u32(pv_done));
@@ -241,7 +239,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_before();
       mbar_arrive(smem_u32(&s_empty[sb]));
       float s[kMlaHeads];
-      const bool valid = row < kMlaTile && (t0 + j) * kMlaTile + row < len;
+      const bool valid = (t0 + j) * kMlaTile + row < len;
 #pragma unroll
       for (int h = 0; h < kMlaHeads; ++h) s[h] = valid ? __uint_as_float(sr[h]) * args.scale_log2 : -INFINITY;
       // per-head maximum over the 128 tokens of the tile
@@ -290,10 +288,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       ok = named_bar_and(2, 128, ok);               // also orders the reads of `red` before the next tile's writes
       if (!ok) break;
-      // P^T[h][token] as a K-major operand: row h of 128 bytes (64 tokens), 16-byte chunks swizzled by row
-      if (row < kMlaTile) {
-        uint8_t* pcol = sP + (row & 7) * 2;
-        const int chunk = row >> 3;
+      // P^T[h][token] as a K-major operand: sub-tile of 64 tokens, row h of 128 bytes, 16-byte chunks swizzled by row
+      {
+        uint8_t* pcol = sP + (row >> 6) * (kMlaHeads * 128) + (row & 7) * 2;
+        const int chunk = (row & 63) >> 3;
 #pragma unroll
         for (int h = 0; h < kMlaHeads; ++h)
           *reinterpret_cast<__nv_bfloat16*>(pcol + h * 128 + ((chunk ^ (h & 7)) << 4)) = __float2bfloat16_rn(s[h]);
@@ -417,15 +415,14 @@ int mfb_mla_decode_attention(const void* q, const void* cache, const int* block_
   int rc;
   const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if ((rc = mfb_host::make_tmap_2d(&tQ, q, 2, BF, (uint64_t)B * num_heads, kMlaDim, kMlaDim, kMlaHeads, 64))) return 20 + rc;
-  const int box_rows = block_size < kMlaTile ? block_size : kMlaTile;
-  if ((rc = mfb_host::make_tmap_2d(&tC, cache, 2, BF, (uint64_t)num_blocks * block_size, kMlaDim, kMlaDim, box_rows, 64))) return 30 + rc;
+  if ((rc = mfb_host::make_tmap_2d(&tC, cache, 2, BF, (uint64_t)num_blocks * block_size, kMlaDim, kMlaDim, block_size, 64))) return 30 + rc;
   MlaArgs a;
   a.block_tables = block_tables; a.context_lens = context_lens; a.max_blocks = max_blocks; a.block_size = block_size;
   a.num_heads = num_heads; a.splits = splits; a.scale_log2 = scale * 1.4426950408889634f;
   a.part_o = reinterpret_cast<float*>(scratch);
   a.part_ml = a.part_o + static_cast<size_t>(B) * splits * num_heads * kMlaRank;
   a.status = status;
-  constexpr int SMEM = kMlaSlots * kMlaUnit + kMlaSub + kMlaPBytes + kMlaQBytes + 4 * kMlaHeads * 4 + 18 * 8 + 16 + 1024;
+  constexpr int SMEM = kMlaSlots * kMlaUnit + kMlaPBytes + kMlaQBytes + 4 * kMlaHeads * 4 + 18 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
