@@ -36,3 +36,7 @@ def test_fused_moe_expert_parallel_exchange():
 
 def test_fused_context_parallel_attention():
     _run("run_fused_cp.py", "--bench", "0")
+
+
+def test_tp_attention_ep_moe_inference_bf16_and_fp8():
+    _run("run_tp_ep_inference.py")
