@@ -6,8 +6,9 @@
 //           reaches h through the residual stream);   dw = sum_t dy * h * rstd
 // dw is reduced in two deterministic phases through a [parts, H] fp32 scratch buffer.
 //
-// One CTA of 256 threads per row, 16-byte vector accesses, row kept in registers when
-// H <= 8192. A warp-per-row variant serves per-head q/k norms (H <= 256, strided rows).
+// CTAs of 256 threads walk rows (persistent grid), 16-byte vector accesses, the row kept in registers (H <= 8192) and
+// the next row's loads issued before the current row is reduced. A warp-per-row variant serves per-head q/k norms
+// (H <= 256, strided rows).
 #include <mutex>
 
 #include "common.cuh"
@@ -33,7 +34,10 @@ struct alignas(16) bf16x8 {
   __nv_bfloat162 v[4];
 };
 
-template <bool HAS_RES>
+// NVEC: 16-byte vectors per thread that cover a row (H <= NVEC * 256 * 8). The grid is persistent: a CTA walks rows
+// blockIdx.x, blockIdx.x + gridDim.x, ... and issues the loads of its next row before it reduces the current one, so
+// that the two block barriers of a row do not leave the memory system idle.
+template <bool HAS_RES, int NVEC>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
@@ -41,24 +45,43 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* res,
                    float eps) {
   __shared__ float red[32];
   const int nvec = H / 8;
-  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 wv[NVEC];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) wv[i] = wr[v];
+  }
+  bf16x8 nx[NVEC], nr[NVEC];
+  auto load_row = [&](int row) {
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * H);
     const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * H) : nullptr;
-    bf16x8* hr = HAS_RES ? reinterpret_cast<bf16x8*>(h_out + (size_t)row * H) : nullptr;
-    float vals[kMaxVec][8];
-    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        bf16x8 a = xr[v];
+        nx[i] = xr[v];
+        if (HAS_RES) nr[i] = rr[v];
+      }
+    }
+  };
+  int row = blockIdx.x;
+  if (row < T) load_row(row);
+  for (; row < T; row += gridDim.x) {
+    bf16x8* hr = HAS_RES ? reinterpret_cast<bf16x8*>(h_out + (size_t)row * H) : nullptr;
+    float vals[NVEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 a = nx[i];
         if (HAS_RES) {
-          bf16x8 b = rr[v];
           bf16x8 o;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float2 fa = __bfloat1622float2(a.v[j]);
-            float2 fb = __bfloat1622float2(b.v[j]);
+            float2 fb = __bfloat1622float2(nr[i].v[j]);
             o.v[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
           }
           hr[v] = o;
@@ -73,65 +96,31 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* res,
         }
       }
     }
-    // tail for H beyond the register window
-    for (int v = threadIdx.x + kMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
-      bf16x8 a = xr[v];
-      if (HAS_RES) {
-        bf16x8 b = rr[v];
-        bf16x8 o;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 fa = __bfloat1622float2(a.v[j]);
-          float2 fb = __bfloat1622float2(b.v[j]);
-          o.v[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
-        }
-        hr[v] = o;
-        a = o;
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(a.v[j]);
-        ss += f.x * f.x + f.y * f.y;
-      }
-    }
+    const int next = row + gridDim.x;
+    if (next < T) load_row(next);          // in flight during the reduction and the stores below
     const float tot = block_sum(ss, red);
     const float rstd = rsqrtf(tot / (float)H + eps);
     if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
-    const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
     bf16x8* yr = reinterpret_cast<bf16x8*>(y + (size_t)row * H);
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        bf16x8 ww = wr[v];
         bf16x8 o;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 fw = __bfloat1622float2(ww.v[j]);
+          float2 fw = __bfloat1622float2(wv[i].v[j]);
           o.v[j] = __floats2bfloat162_rn(vals[i][2 * j] * rstd * fw.x, vals[i][2 * j + 1] * rstd * fw.y);
         }
         yr[v] = o;
       }
-    }
-    const bf16x8* src = HAS_RES ? reinterpret_cast<const bf16x8*>(h_out + (size_t)row * H) : xr;
-    for (int v = threadIdx.x + kMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
-      bf16x8 a = src[v];
-      bf16x8 ww = wr[v];
-      bf16x8 o;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __bfloat1622float2(a.v[j]);
-        float2 fw = __bfloat1622float2(ww.v[j]);
-        o.v[j] = __floats2bfloat162_rn(f.x * rstd * fw.x, f.y * rstd * fw.y);
-      }
-      yr[v] = o;
     }
   }
 }
 
 // Backward over rows [persistent grid]; each CTA keeps its dw partial in registers (columns owned
 // by the thread) and writes one row of the scratch buffer at the end.
-template <bool HAS_DRES>
+template <bool HAS_DRES, int NVEC>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -139,58 +128,87 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    float* __restrict__ dw_partial, int T, int H) {
   __shared__ float red[32];
   const int nvec = H / 8;
-  float dw_acc[kMaxVec][8];
-#pragma unroll
-  for (int i = 0; i < kMaxVec; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
-
+  float dw_acc[NVEC][8];
+  float wf[NVEC][8];
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dw_acc[i][j] = 0.f; wf[i][j] = 0.f; }
+    if (v < nvec) {
+      const bf16x8 ww = wr[v];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(ww.v[j]);
+        wf[i][2 * j] = f.x;
+        wf[i][2 * j + 1] = f.y;
+      }
+    }
+  }
+  bf16x8 ndy[NVEC], nh[NVEC], ndr[NVEC];
+  float nrstd = 0.f;
+  auto load_row = [&](int row) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)row * H);
     const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + (size_t)row * H);
-    const float r = rstd[row];
-    float wdy[kMaxVec][8], hv[kMaxVec][8];
-    float dot = 0.f;
+    const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * H) : nullptr;
+    nrstd = rstd[row];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        bf16x8 a = dyr[v], b = hr[v], ww = wr[v];
+        ndy[i] = dyr[v];
+        nh[i] = hr[v];
+        if (HAS_DRES) ndr[i] = drr[v];
+      }
+    }
+  };
+  int row = blockIdx.x;
+  if (row < T) load_row(row);
+  for (; row < T; row += gridDim.x) {
+    const float r = nrstd;
+    float wdy[NVEC][8], hv[NVEC][8], dr[NVEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 fd = __bfloat1622float2(a.v[j]);
-          float2 fh = __bfloat1622float2(b.v[j]);
-          float2 fw = __bfloat1622float2(ww.v[j]);
-          wdy[i][2 * j] = fd.x * fw.x;
-          wdy[i][2 * j + 1] = fd.y * fw.y;
+          const float2 fd = __bfloat1622float2(ndy[i].v[j]);
+          const float2 fh = __bfloat1622float2(nh[i].v[j]);
+          wdy[i][2 * j] = fd.x * wf[i][2 * j];
+          wdy[i][2 * j + 1] = fd.y * wf[i][2 * j + 1];
           hv[i][2 * j] = fh.x;
           hv[i][2 * j + 1] = fh.y;
           dot += wdy[i][2 * j] * fh.x + wdy[i][2 * j + 1] * fh.y;
           dw_acc[i][2 * j] += fd.x * fh.x * r;
           dw_acc[i][2 * j + 1] += fd.y * fh.y * r;
+          if (HAS_DRES) {
+            const float2 f = __bfloat1622float2(ndr[i].v[j]);
+            dr[i][2 * j] = f.x;
+            dr[i][2 * j + 1] = f.y;
+          }
         }
       }
     }
+    const int next = row + gridDim.x;
+    if (next < T) load_row(next);          // in flight during the reduction and the stores below
     const float tot = block_sum(dot, red);
     const float c = tot * r * r * r / (float)H;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + (size_t)row * H);
-    const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * H) : nullptr;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         bf16x8 o;
-        bf16x8 dr;
-        if (HAS_DRES) dr = drr[v];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float a0 = wdy[i][2 * j] * r - hv[i][2 * j] * c;
           float a1 = wdy[i][2 * j + 1] * r - hv[i][2 * j + 1] * c;
           if (HAS_DRES) {
-            float2 f = __bfloat1622float2(dr.v[j]);
-            a0 += f.x;
-            a1 += f.y;
+            a0 += dr[i][2 * j];
+            a1 += dr[i][2 * j + 1];
           }
           o.v[j] = __floats2bfloat162_rn(a0, a1);
         }
@@ -200,7 +218,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
   float* out = dw_partial + (size_t)blockIdx.x * H;
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
 #pragma unroll
@@ -265,15 +283,25 @@ int mfb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void
     return 1;
   }
   if (T <= 0) return 0;
-  const int grid = T;
-  if (res)
-    rmsnorm_fwd_kernel<true><<<grid, kNormThreads, 0, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-        (__nv_bfloat16*)h_out, rstd, T, H, eps);
-  else
-    rmsnorm_fwd_kernel<false><<<grid, kNormThreads, 0, stream>>>(
-        (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr, rstd, T, H,
-        eps);
+  if (H > kNormThreads * kMaxVec * 8) {
+    mfb_host::set_error("rmsnorm: H=%d above %d is not supported", H, kNormThreads * kMaxVec * 8);
+    return 1;
+  }
+  const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;      // vectors per thread: 1..4
+  const int cap = 148 * (nv <= 2 ? 8 : 4);
+  const int grid = T < cap ? T : cap;
+#define MFB_RMS_FWD(RES, NV)                                                                              \
+  rmsnorm_fwd_kernel<RES, NV><<<grid, kNormThreads, 0, stream>>>(                                          \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,      \
+      (__nv_bfloat16*)h_out, rstd, T, H, eps)
+  if (res) {
+    if (nv == 1) MFB_RMS_FWD(true, 1); else if (nv == 2) MFB_RMS_FWD(true, 2);
+    else if (nv == 3) MFB_RMS_FWD(true, 3); else MFB_RMS_FWD(true, 4);
+  } else {
+    if (nv == 1) MFB_RMS_FWD(false, 1); else if (nv == 2) MFB_RMS_FWD(false, 2);
+    else if (nv == 3) MFB_RMS_FWD(false, 3); else MFB_RMS_FWD(false, 4);
+  }
+#undef MFB_RMS_FWD
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -294,14 +322,19 @@ int mfb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* r
   }
   if (T <= 0) return 0;
   const int parts = mfb_rmsnorm_bwd_parts(T);
-  if (dres)
-    rmsnorm_bwd_kernel<true><<<parts, kNormThreads, 0, stream>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,
-        (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H);
-  else
-    rmsnorm_bwd_kernel<false><<<parts, kNormThreads, 0, stream>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr,
-        (__nv_bfloat16*)dx, scratch, T, H);
+  const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
+#define MFB_RMS_BWD(DRES, NV)                                                                            \
+  rmsnorm_bwd_kernel<DRES, NV><<<parts, kNormThreads, 0, stream>>>(                                       \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,                   \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H)
+  if (dres) {
+    if (nv == 1) MFB_RMS_BWD(true, 1); else if (nv == 2) MFB_RMS_BWD(true, 2);
+    else if (nv == 3) MFB_RMS_BWD(true, 3); else MFB_RMS_BWD(true, 4);
+  } else {
+    if (nv == 1) MFB_RMS_BWD(false, 1); else if (nv == 2) MFB_RMS_BWD(false, 2);
+    else if (nv == 3) MFB_RMS_BWD(false, 3); else MFB_RMS_BWD(false, 4);
+  }
+#undef MFB_RMS_BWD
   colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32,
                                                              (__nv_bfloat16*)dw_bf16, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
@@ -388,12 +421,13 @@ extern "C" int mfb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void
   // Every launched CTA overwrites its whole row of partial sums and the reduction reads exactly the rows that
   // were launched, so nothing in the array has to be cleared between calls.
   const int parts = T < kNoAllocMaxParts ? T : kNoAllocMaxParts;
+  // the widest register window serves every supported H here (one code path for this entry point)
   if (dres)
-    rmsnorm_bwd_kernel<true><<<parts, kNormThreads, 0, stream>>>(
+    rmsnorm_bwd_kernel<true, kMaxVec><<<parts, kNormThreads, 0, stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
         (__nv_bfloat16*)dx, scratch, T, H);
   else
-    rmsnorm_bwd_kernel<false><<<parts, kNormThreads, 0, stream>>>(
+    rmsnorm_bwd_kernel<false, kMaxVec><<<parts, kNormThreads, 0, stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dx,
         scratch, T, H);
   colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32, (__nv_bfloat16*)dw_bf16,
