@@ -44,9 +44,33 @@ def fa():
 
 
 def rmsnorm():
-    x, w = bf(32768, 4096).requires_grad_(), torch.ones(4096, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    T, H = 32768, 4096
+    x, w = bf(T, H).requires_grad_(), torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    res = bf(T, H)
+    dy = bf(T, H, scale=0.1)
     for _ in range(3):
-        Fn.rmsnorm(x, w, 1e-5)[0].backward(bf(32768, 4096, scale=0.1))
+        Fn.rmsnorm(x, w, 1e-5)[0].backward(dy)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    with torch.no_grad():
+        ev[0].record()
+        for _ in range(5):
+            Fn.rmsnorm(x, w, 1e-5)
+        ev[1].record()
+        for _ in range(5):
+            Fn.rmsnorm(x, w, 1e-5, residual=res)
+        ev[2].record()
+    y = Fn.rmsnorm(x, w, 1e-5)[0]
+    torch.cuda.synchronize()
+    ev[2].record()
+    for _ in range(5):
+        y.backward(dy, retain_graph=True)
+    ev[3].record()
+    torch.cuda.synchronize()
+    row = T * H * 2
+    t_f, t_r, t_b = ev[0].elapsed_time(ev[1]) / 5, ev[1].elapsed_time(ev[2]) / 5, ev[2].elapsed_time(ev[3]) / 5
+    bw = lambda nbytes, ms: nbytes / ms / 1e6 / 6523.7
+    print(f"rmsnorm fwd {t_f * 1e3:.1f} us ({bw(2 * row, t_f):.2f} of measured HBM), fwd+residual {t_r * 1e3:.1f} us "
+          f"({bw(4 * row, t_r):.2f}), bwd incl. dw reduction {t_b * 1e3:.1f} us ({bw(3 * row, t_b):.2f})")
 
 
 def swiglu():
