@@ -73,6 +73,11 @@ def main():
     # activation bytes one stage boundary carries per step: forward + backward, every micro-batch
     bytes_per_step = 2 * args.microbatches * args.seq * args.hidden * 2
     buf = torch.empty(args.seq * args.hidden, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):                      # the first transfer sets up the point-to-point channel
+        if rank == 0:
+            dist.send(buf, 1)
+        elif rank == 1:
+            dist.recv(buf, 0)
     dist.barrier()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
