@@ -4,7 +4,9 @@
 //           (the residual add of a pre-LN transformer block is fused: h is written back)
 // backward: dx = rstd * (w*dy) - h * rstd^3 * mean(w*dy*h)   (+ dres, the gradient that
 //           reaches h through the residual stream);   dw = sum_t dy * h * rstd
-// dw is reduced in two deterministic phases through a [parts, H] fp32 scratch buffer.
+// dx and dw come from two kernels: carrying the dw partial sums through the dx loop costs so many registers that
+// the loop loses more to low occupancy than the second read of dy and h costs. dw is reduced in two deterministic
+// phases through a [parts, H] fp32 scratch buffer.
 //
 // CTAs of 256 threads walk rows (persistent grid), 16-byte vector accesses, the row kept in registers (H <= 8192) and
 // the next row's loads issued before the current row is reduced. A warp-per-row variant serves per-head q/k norms
@@ -227,16 +229,153 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// dw[c] (+)= sum_p partial[p, c]; output fp32 (accumulate) or bf16.
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, int parts, int H,
-                                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// dx alone (the regular entry point computes dw in a second kernel, which keeps this one light on registers):
+// the row and its successor are held as raw bf16 vectors, floats are formed on the fly.
+template <bool HAS_DRES, int NVEC>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                      const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                      const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int T, int H) {
+  __shared__ float red[32];
+  const int nvec = H / 8;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 wv[NVEC];
+#pragma unroll
+  for (int i = 0; i < NVEC; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    if (v < nvec) wv[i] = wr[v];
+  }
+  bf16x8 ndy[NVEC], nh[NVEC], ndr[NVEC];
+  float nrstd = 0.f;
+  auto load_row = [&](int row) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)row * H);
+    const bf16x8* hr = reinterpret_cast<const bf16x8*>(h + (size_t)row * H);
+    const bf16x8* drr = HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * H) : nullptr;
+    nrstd = rstd[row];
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        ndy[i] = dyr[v];
+        nh[i] = hr[v];
+        if (HAS_DRES) ndr[i] = drr[v];
+      }
+    }
+  };
+  int row = blockIdx.x;
+  if (row < T) load_row(row);
+  for (; row < T; row += gridDim.x) {
+    const float r = nrstd;
+    bf16x8 cdy[NVEC], ch[NVEC], cdr[NVEC];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      cdy[i] = ndy[i];
+      ch[i] = nh[i];
+      if (HAS_DRES) cdr[i] = ndr[i];
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fd = __bfloat1622float2(cdy[i].v[j]);
+          const float2 fh = __bfloat1622float2(ch[i].v[j]);
+          const float2 fw = __bfloat1622float2(wv[i].v[j]);
+          dot += fd.x * fw.x * fh.x + fd.y * fw.y * fh.y;
+        }
+      }
+    }
+    const int next = row + gridDim.x;
+    if (next < T) load_row(next);          // in flight during the reduction and the stores below
+    const float tot = block_sum(dot, red);
+    const float c = tot * r * r * r / (float)H;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        bf16x8 o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fd = __bfloat1622float2(cdy[i].v[j]);
+          const float2 fh = __bfloat1622float2(ch[i].v[j]);
+          const float2 fw = __bfloat1622float2(wv[i].v[j]);
+          float a0 = fd.x * fw.x * r - fh.x * c;
+          float a1 = fd.y * fw.y * r - fh.y * c;
+          if (HAS_DRES) {
+            const float2 f = __bfloat1622float2(cdr[i].v[j]);
+            a0 += f.x;
+            a1 += f.y;
+          }
+          o.v[j] = __floats2bfloat162_rn(a0, a1);
+        }
+        dxr[v] = o;
+      }
+    }
+  }
+}
+
+// dw partial sums: partial[split, c] = sum over the rows of the split of dy * h * rstd. A CTA covers 256 columns
+// (a lane owns 8 of them, one 16-byte vector) and its 8 warps walk the rows of the split side by side.
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                          const float* __restrict__ rstd, float* __restrict__ partial, int T, int H,
+                          int rows_per_split) {
+  __shared__ float sm[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const bool valid = c0 < H;
+  const int r_begin = blockIdx.y * rows_per_split;
+  const int r_end = (r_begin + rows_per_split < T) ? r_begin + rows_per_split : T;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (valid) {
+#pragma unroll 4
+    for (int r = r_begin + warp; r < r_end; r += 8) {
+      const bf16x8 a = *reinterpret_cast<const bf16x8*>(dy + (size_t)r * H + c0);
+      const bf16x8 b = *reinterpret_cast<const bf16x8*>(h + (size_t)r * H + c0);
+      const float rs = rstd[r];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __bfloat1622float2(a.v[j]);
+        const float2 fb = __bfloat1622float2(b.v[j]);
+        acc[2 * j] += fa.x * fb.x * rs;
+        acc[2 * j + 1] += fa.y * fb.y * rs;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < H) {
+    float s = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) s += sm[w8][threadIdx.x];
+    partial[(size_t)blockIdx.y * H + c] = s;
+  }
+}
+
+// dw[c] (+)= sum_p partial[p, c]; output fp32 (accumulate) or bf16. 32 columns per CTA, 8 warps split the parts.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, int parts, int H,
+                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
+                       int accumulate) {
+  __shared__ float sm[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(size_t)p * H + c];
-  if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
-  if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
+  if (c < H)
+    for (int p = warp; p < parts; p += 8) s += partial[(size_t)p * H + c];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) t += sm[w8][lane];
+    if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + t : t;
+    if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + t : t);
+  }
 }
 
 // ---- warp-per-row variant for per-head q/k norm: rows are (token, head) with strides ----
@@ -321,22 +460,34 @@ int mfb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* r
     return 1;
   }
   if (T <= 0) return 0;
-  const int parts = mfb_rmsnorm_bwd_parts(T);
   const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
-#define MFB_RMS_BWD(DRES, NV)                                                                            \
-  rmsnorm_bwd_kernel<DRES, NV><<<parts, kNormThreads, 0, stream>>>(                                       \
+  const int cap = 148 * (nv <= 2 ? 6 : 3);
+  const int grid = T < cap ? T : cap;
+#define MFB_RMS_DX(DRES, NV)                                                                             \
+  rmsnorm_bwd_dx_kernel<DRES, NV><<<grid, kNormThreads, 0, stream>>>(                                     \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,                   \
-      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H)
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, T, H)
   if (dres) {
-    if (nv == 1) MFB_RMS_BWD(true, 1); else if (nv == 2) MFB_RMS_BWD(true, 2);
-    else if (nv == 3) MFB_RMS_BWD(true, 3); else MFB_RMS_BWD(true, 4);
+    if (nv == 1) MFB_RMS_DX(true, 1); else if (nv == 2) MFB_RMS_DX(true, 2);
+    else if (nv == 3) MFB_RMS_DX(true, 3); else MFB_RMS_DX(true, 4);
   } else {
-    if (nv == 1) MFB_RMS_BWD(false, 1); else if (nv == 2) MFB_RMS_BWD(false, 2);
-    else if (nv == 3) MFB_RMS_BWD(false, 3); else MFB_RMS_BWD(false, 4);
+    if (nv == 1) MFB_RMS_DX(false, 1); else if (nv == 2) MFB_RMS_DX(false, 2);
+    else if (nv == 3) MFB_RMS_DX(false, 3); else MFB_RMS_DX(false, 4);
   }
-#undef MFB_RMS_BWD
-  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32,
-                                                             (__nv_bfloat16*)dw_bf16, accumulate);
+#undef MFB_RMS_DX
+  // dw: row splits sized so that (column tiles x splits) fills the GPU a few times over, within the scratch rows
+  const int col_tiles = (H + 255) / 256;
+  int splits = (148 * 6 + col_tiles - 1) / col_tiles;
+  const int max_parts = mfb_rmsnorm_bwd_parts(T);
+  if (splits > max_parts) splits = max_parts;
+  if (splits > (T + 7) / 8) splits = (T + 7) / 8;
+  if (splits < 1) splits = 1;
+  const int rows_per_split = (T + splits - 1) / splits;
+  const int parts = (T + rows_per_split - 1) / rows_per_split;
+  rmsnorm_dw_partial_kernel<<<dim3(col_tiles, parts), 256, 0, stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, rstd, scratch, T, H, rows_per_split);
+  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(scratch, parts, H, dw_f32,
+                                                           (__nv_bfloat16*)dw_bf16, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -430,8 +581,8 @@ extern "C" int mfb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void
     rmsnorm_bwd_kernel<false, kMaxVec><<<parts, kNormThreads, 0, stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd, nullptr, (__nv_bfloat16*)dx,
         scratch, T, H);
-  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, parts, H, dw_f32, (__nv_bfloat16*)dw_bf16,
-                                                             accumulate);
+  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(scratch, parts, H, dw_f32, (__nv_bfloat16*)dw_bf16,
+                                                           accumulate);
   if (cudaGetLastError() != cudaSuccess) {
     mfb_host::set_error("rmsnorm_bwd_noalloc: launch failed");
     return 2;
