@@ -168,7 +168,7 @@ def paged():
 
 def mla():
     """MLA decode: 64 sequences of 2304 cached tokens, 16 heads per rank (128 heads over tp 8) and all 128 heads."""
-    from mindformers_b200.inference.paged_attention import mla_decode_attention
+    from mindformers_b200.inference.paged_attention import mla_decode_attention, set_mla_decode_variant
     B, ctx, blk = 64, 2304, 128
     nblocks = B * ctx // blk
     cache = bf(nblocks, blk, 1, 576)
@@ -178,7 +178,8 @@ def mla():
     class Holder:
         pass
 
-    for nh in (16, 128):
+    for variant, nh in (("single", 16), ("single", 128), ("cluster", 16), ("cluster", 128)):
+        set_mla_decode_variant(variant)
         q = bf(B, nh, 576, scale=0.3)
         h = Holder()
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -191,9 +192,10 @@ def mla():
         ms = ev[0].elapsed_time(ev[1]) / 3
         kv_bytes = B * ctx * 576 * 2
         flops = 2.0 * B * ctx * nh * (576 + 512)
-        print(f"mla decode heads={nh}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of latent cache "
+        print(f"mla decode ({variant}) heads={nh}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of latent cache "
               f"({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), "
               f"{flops / ms / 1e9:.0f} TFLOP/s, status {_lib.read_status()}")
+    set_mla_decode_variant("single")
 
 
 def moe():

@@ -132,6 +132,14 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
     return torch.cat(outs, dim=0)
 
 
+def set_mla_decode_variant(variant: str) -> None:
+    """Choose the MLA decode kernel: ``"single"`` (one CTA per work item, ``ops/csrc/mla_decode.cu``) or ``"cluster"``
+    (two CTAs of a cluster split the latent columns and read the cache once, ``ops/csrc/mla_decode_cluster.cu``)."""
+    if variant not in ("single", "cluster"):
+        raise ValueError(f"unknown MLA decode variant {variant!r}")
+    _lib.get_lib().mfb_mla_decode_set_variant(1 if variant == "cluster" else 0)
+
+
 def mla_decode_attention(q_cat: torch.Tensor, latent_cache: torch.Tensor, block_tables: torch.Tensor,
                          context_lens: torch.Tensor, block_size: int, scale: float, holder=None) -> torch.Tensor:
     """``q_cat [B, heads, 576]`` (absorbed query ‖ rope query) against the paged latent cache

@@ -72,6 +72,9 @@ def _declare(lib):
     lib.mfb_paged_decode_scratch_bytes.restype = L
     sig("mfb_mla_decode_attention", [P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     sig("mfb_mla_decode_splits", [I, I, I])
+    lib.mfb_mla_decode_set_variant.argtypes = [I]
+    lib.mfb_mla_decode_set_variant.restype = None
+    sig("mfb_mla_decode_get_variant", [])
     lib.mfb_mla_decode_scratch_bytes.argtypes = [I, I, I]
     lib.mfb_mla_decode_scratch_bytes.restype = L
     sig("mfb_gather_cache", [P, P, P, P, I, I, I, I, I, P])

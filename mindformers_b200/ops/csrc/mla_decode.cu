@@ -381,8 +381,19 @@ mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ p
 extern "C" {
 using namespace mfb;
 
+// Kernel variant: 0 = one CTA per (sequence, split, head chunk), two passes over the cache (this file);
+// 1 = a cluster of two CTAs that split the latent columns, one pass (mla_decode_cluster.cu).
+static int g_mla_variant = 0;
+int mfb_mla_cluster_splits(int B, int num_heads, int max_len);
+int mfb_mla_decode_cluster_launch(const void* q, const void* cache, const int* block_tables, const int* context_lens,
+                                  float* part_o, float* part_ml, int splits, int B, int num_heads, int num_blocks,
+                                  int block_size, int max_blocks, float scale, int* status, cudaStream_t stream);
+void mfb_mla_decode_set_variant(int v) { g_mla_variant = v == 1 ? 1 : 0; }
+int mfb_mla_decode_get_variant() { return g_mla_variant; }
+
 // Number of sequence splits that fills the GPU for a batch of B sequences of up to max_len tokens.
 int mfb_mla_decode_splits(int B, int num_heads, int max_len) {
+  if (g_mla_variant == 1) return mfb_mla_cluster_splits(B, num_heads, max_len);
   // cost of a choice = waves of CTAs over the 2 x 148 resident CTAs x (tiles per CTA + about one tile of fixed work per CTA)
   const int chunks = (num_heads + kMlaHeads - 1) / kMlaHeads;
   const int tiles = (max_len + kMlaTile - 1) / kMlaTile;
@@ -422,6 +433,14 @@ int mfb_mla_decode_attention(const void* q, const void* cache, const int* block_
   a.part_o = reinterpret_cast<float*>(scratch);
   a.part_ml = a.part_o + static_cast<size_t>(B) * splits * num_heads * kMlaRank;
   a.status = status;
+  if (g_mla_variant == 1) {
+    rc = mfb_mla_decode_cluster_launch(q, cache, block_tables, context_lens, a.part_o, a.part_ml, splits, B, num_heads,
+                                       num_blocks, block_size, max_blocks, scale, status, stream);
+    if (rc) return rc;
+    mla_combine_kernel<<<dim3(num_heads, B), 128, 0, stream>>>(a.part_o, a.part_ml, reinterpret_cast<__nv_bfloat16*>(out),
+                                                                splits, num_heads);
+    return cudaGetLastError() == cudaSuccess ? 0 : 12;
+  }
   constexpr int SMEM = kMlaSlots * kMlaUnit + kMlaPBytes + kMlaQBytes + 4 * kMlaHeads * 4 + 18 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {

@@ -389,11 +389,14 @@ def test_flash_attention_mla_shape_forward(B, S, nh, causal):
     assert (out.float() - ref).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("variant", ["single", "cluster"])
 @pytest.mark.parametrize("nh,block", [(16, 128), (128, 128), (20, 16), (16, 64)])
-def test_mla_decode_attention(nh, block):
-    """Absorbed-query MLA decode over the paged latent cache against an fp32 reference."""
-    from mindformers_b200.inference.paged_attention import mla_decode_attention
+def test_mla_decode_attention(nh, block, variant):
+    """Absorbed-query MLA decode over the paged latent cache against an fp32 reference, both kernel variants."""
+    from mindformers_b200.inference.paged_attention import mla_decode_attention, set_mla_decode_variant
     torch.manual_seed(nh + block)
+    default = "cluster" if _lib.get_lib().mfb_mla_decode_get_variant() == 1 else "single"
+    set_mla_decode_variant(variant)
     lens = [1, 127, 128, 300, 2304, 129]
     B = len(lens)
     max_blocks = (max(lens) + block - 1) // block + 1
@@ -403,8 +406,11 @@ def test_mla_decode_attention(nh, block):
     q = (torch.randn(B, nh, 576, device="cuda") * 0.3).to(torch.bfloat16)
     ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
     scale = 192 ** -0.5
-    out = mla_decode_attention(q, cache, tables, ctx, block, scale)
-    torch.cuda.synchronize()
+    try:
+        out = mla_decode_attention(q, cache, tables, ctx, block, scale)
+        torch.cuda.synchronize()
+    finally:
+        set_mla_decode_variant(default)
     assert _lib.read_status() == 0
     for b, n in enumerate(lens):
         lat = cache[tables[b].long()].reshape(-1, 576)[:n].float()
