@@ -237,7 +237,46 @@ def fp8():
             Fn.quantize_act_1x128(x)
 
 
-CASES = dict(fp8=fp8, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+def fp8_decode():
+    """Decode-sized fp8 GEMMs (64 tokens): weight streaming with and without the cluster split over K. Several
+    copies of the weight are cycled so that every call reads from HBM, not from L2."""
+    lib = _lib.get_lib()
+    M = 64
+    for (N, K, what) in ((7168, 16384, "o_proj, 1 GPU"), (7168, 18432, "dense fc2, 1 GPU"), (1536, 7168, "q_a"),
+                         (3072, 1536, "q_b, tp 8"), (7168, 2048, "o_proj, tp 8"), (4608, 7168, "dense fc1, tp 8")):
+        copies = max(2, int(400e6 // (N * K)) + 1)
+        ws = []
+        for _ in range(copies):
+            wq, sb = Fn.quantize_weight_128x128(torch.randn(N, K, device="cuda") * 0.05)
+            ws.append((wq, sb))
+        xq, sa = Fn.quantize_act_1x128(bf(M, K, scale=0.7))
+        res = {}
+        for on in (0, 1):
+            lib.mfb_gemm_fp8_enable_ksplit(on)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for i in range(copies):
+                Fn.fp8_gemm(xq, sa, *ws[i])
+            torch.cuda.synchronize()
+            # the calls are replayed from a CUDA graph: at these sizes Python would otherwise be the slower side
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(copies):
+                    Fn.fp8_gemm(xq, sa, *ws[i])
+            g.replay()
+            ev[0].record()
+            for _ in range(4):
+                g.replay()
+            ev[1].record()
+            torch.cuda.synchronize()
+            res[on] = ev[0].elapsed_time(ev[1]) / (4 * copies)
+        lib.mfb_gemm_fp8_enable_ksplit(1)
+        ks = lib.mfb_gemm_fp8_ksplit(M, N, K, 0, N)
+        gbs = N * K / res[1] / 1e6
+        print(f"fp8 decode {M}x{N}x{K} ({what}): one CTA per tile {res[0] * 1e3:.1f} us, cluster split-K x{ks} "
+              f"{res[1] * 1e3:.1f} us = {gbs:.0f} GB/s of weights ({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
+
+
+CASES = dict(fp8=fp8, fp8_decode=fp8_decode, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

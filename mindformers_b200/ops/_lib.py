@@ -70,6 +70,9 @@ def _declare(lib):
     sig("mfb_paged_decode_splits", [I, I, I, I])
     lib.mfb_paged_decode_scratch_bytes.argtypes = [I, I, I, I]
     lib.mfb_paged_decode_scratch_bytes.restype = L
+    lib.mfb_gemm_fp8_enable_ksplit.argtypes = [I]
+    lib.mfb_gemm_fp8_enable_ksplit.restype = None
+    sig("mfb_gemm_fp8_ksplit", [I, I, I, I, L])
     sig("mfb_mla_decode_attention", [P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     sig("mfb_mla_decode_splits", [I, I, I])
     lib.mfb_mla_decode_set_variant.argtypes = [I]
@@ -137,6 +140,11 @@ def get_lib():
         if got != ABI_VERSION:
             raise KernelLibraryError(f"kernel library ABI {got} != expected {ABI_VERSION}; rebuild it")
         _declare(lib)
+        # kernel variants that can be switched for A/B measurements
+        if os.environ.get("MFB_FP8_KSPLIT", "1") == "0":
+            lib.mfb_gemm_fp8_enable_ksplit(0)
+        if os.environ.get("MFB_MLA_DECODE", "single") == "cluster":
+            lib.mfb_mla_decode_set_variant(1)
         _lib = lib
     return _lib
 
@@ -148,7 +156,16 @@ def check(rc: int, what: str):
 
 
 def stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current CUDA stream of the current device (the direct binding: building a
+    ``torch.cuda.Stream`` object per kernel launch costs more host time than the launch itself)."""
+    return _raw_stream(torch.cuda.current_device())
+
+
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:          # CPU-only builds of torch
+    def _raw_stream(device_index: int) -> int:
+        return torch.cuda.current_stream(device_index).cuda_stream
 
 
 def ptr(t) -> int:

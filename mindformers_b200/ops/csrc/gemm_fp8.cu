@@ -12,6 +12,13 @@
 // thread) while the tensor core already works on the next block. Tiles are 128 x 128, the grid is persistent,
 // operands arrive by TMA through a 5-stage ring, the bf16 result leaves through swizzled staging and TMA stores.
 //
+// Small M (one row block, few column tiles; the decode regime, where the job is to stream the weights once at HBM
+// speed): the K range of a tile is split over the KS = 2, 4 or 8 CTAs of a thread-block cluster, so KS times as many
+// SMs pull weights. Each CTA accumulates its K slice as above, then the cluster reduce-scatters the 128 x 128 fp32
+// partials through distributed shared memory: CTA c receives columns [c * 128 / KS, (c + 1) * 128 / KS) of every
+// partial into its (now idle) operand ring, adds them in rank order (the same bits on every run) and stores its
+// slice of the bf16 result.
+//
 // mode 0: dense. mode 1: ragged-M grouped (MoE experts): rows of A / D are expert segments padded to 128 rows,
 // `m_block_group[b]` gives the expert of row block b and `num_m_blocks_dev` the number of row blocks in use.
 //
@@ -39,7 +46,27 @@ struct F8Args {
   const int* m_block_group;
   const int* num_m_blocks_dev;
   int* status;
+  __nv_bfloat16* D;              // split-K path stores its column slices with plain stores
+  long long ldd;
 };
+
+__device__ __forceinline__ uint32_t f8_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t f8_mapa(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void f8_st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// every thread of every CTA of the cluster; release / acquire at cluster scope
+__device__ __forceinline__ void f8_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -53,6 +80,7 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+template <int KS>
 __global__ void __launch_bounds__(kF8Threads, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                             const __grid_constant__ CUtensorMap tmD, const F8Args args) {
@@ -69,6 +97,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kF8Stages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // split-K launches have exactly one cluster per tile; a cluster without a tile leaves as a whole (its threads
+  // would otherwise meet the cluster barriers below in unequal numbers)
+  if (KS > 1 && static_cast<int>(blockIdx.x) / KS >= args.num_m_blocks * args.num_n_blocks) return;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -102,18 +133,24 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
   const int n_tiles = mb_total * args.num_n_blocks;
   // tile -> (row block, column block): column-major over row blocks so that a wave shares B tiles through L2
   auto tile_mn = [&](int tile, int& m_blk, int& n_blk) { m_blk = tile % mb_total; n_blk = tile / mb_total; };
+  // KS = 1: persistent over tiles, whole K per tile. KS > 1: one tile per cluster, K blocks [kb_lo, kb_hi) per CTA.
+  const int krank = KS > 1 ? static_cast<int>(f8_cluster_ctarank()) : 0;
+  const int tile_first = KS > 1 ? static_cast<int>(blockIdx.x) / KS : static_cast<int>(blockIdx.x);
+  const int tile_step = KS > 1 ? n_tiles : static_cast<int>(gridDim.x);       // KS > 1: a single iteration
+  const int kb_lo = KS > 1 ? krank * args.kblocks / KS : 0;
+  const int kb_hi = KS > 1 ? (krank + 1) * args.kblocks / KS : args.kblocks;
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
         int m_blk, n_blk;
         tile_mn(tile, m_blk, n_blk);
         const int grp = args.mode == 1 ? args.m_block_group[m_blk] : 0;
         const int b_row = grp * args.N + n_blk * kF8BN;
-        for (int kb = 0; kb < args.kblocks; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
           if (!ok) break;
           const uint32_t fb = smem_u32(&full_bar[stage]);
@@ -126,14 +163,15 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       }
     }
     __syncwarp();
+    if constexpr (KS > 1) { f8_cluster_sync(); f8_cluster_sync(); }
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t blk = 0;      // K blocks issued so far: partial buffer = blk & 1
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        for (int kb = 0; kb < args.kblocks; ++kb, ++blk) {
+      for (int tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++blk) {
           const int buf = blk & 1;
           ok = mbar_wait(smem_u32(&pempty[buf]), ((blk >> 1) & 1) ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
           if (!ok) break;
@@ -153,6 +191,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       }
     }
     __syncwarp();
+    if constexpr (KS > 1) { f8_cluster_sync(); f8_cluster_sync(); }
   } else {
     const int ew = warp & 3;
     const int row = ew * 32 + lane;
@@ -161,7 +200,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     uint32_t blk = 0;
     bool ok = true;
     const int nkb = args.kblocks;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    for (int tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
       int m_blk, n_blk;
       tile_mn(tile, m_blk, n_blk);
       const int grp = args.mode == 1 ? args.m_block_group[m_blk] : 0;
@@ -170,11 +209,16 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       float acc[kF8BN];
 #pragma unroll
       for (int i = 0; i < kF8BN; ++i) acc[i] = 0.f;
-      for (int kb = 0; kb < nkb; ++kb, ++blk) {
+      // the scales of the next two K blocks are fetched ahead: their latency would otherwise sit between two partials
+      float sc0 = kb_lo < kb_hi ? sa[(long long)kb_lo * args.sa_ld] * sb[kb_lo] : 0.f;
+      float sc1 = kb_lo + 1 < kb_hi ? sa[(long long)(kb_lo + 1) * args.sa_ld] * sb[kb_lo + 1] : 0.f;
+      for (int kb = kb_lo; kb < kb_hi; ++kb, ++blk) {
         const int buf = blk & 1;
-        const float scale = sa[(long long)kb * args.sa_ld] * sb[kb];
+        const float scale = sc0;
+        sc0 = sc1;
+        if (kb + 2 < kb_hi) sc1 = sa[(long long)(kb + 2) * args.sa_ld] * sb[kb + 2];
         ok = mbar_wait(smem_u32(&pfull[buf]), (blk >> 1) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
-        ok = named_bar_and(2, 128, ok);
+        ok = __all_sync(0xffffffffu, ok);             // the tensor-memory loads need the whole warp
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -189,6 +233,47 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&pempty[buf]));
       }
+      if constexpr (KS > 1) {
+        // ---- reduce-scatter of the K-slice partials over the cluster ----
+        constexpr int W = kF8BN / KS;                 // columns owned by each CTA
+        ok = named_bar_and(2, 128, ok);
+        f8_cluster_sync();                            // every CTA of the cluster has drained its operand ring
+        const bool live = ok && (m_blk * kF8BM + row < args.M);
+        if (live) {
+#pragma unroll
+          for (int c = 0; c < KS; ++c) {
+            // slot [krank][row][W] of CTA c's receive buffer (the start of its ring)
+            const uint32_t dst = f8_mapa(smem_u32(smem) + ((krank * kF8BM + row) * W) * 4, c);
+#pragma unroll
+            for (int v = 0; v < W / 4; ++v)
+              f8_st_cluster_v4(dst + v * 16, acc[c * W + 4 * v], acc[c * W + 4 * v + 1], acc[c * W + 4 * v + 2],
+                               acc[c * W + 4 * v + 3]);
+          }
+        }
+        f8_cluster_sync();                            // all slices have landed
+        if (live) {
+          float out[W];
+#pragma unroll
+          for (int i = 0; i < W; ++i) out[i] = 0.f;
+          const float4* recv = reinterpret_cast<const float4*>(smem);
+#pragma unroll
+          for (int r = 0; r < KS; ++r) {
+#pragma unroll
+            for (int v = 0; v < W / 4; ++v) {
+              const float4 x = recv[((r * kF8BM + row) * W) / 4 + v];
+              out[4 * v] += x.x; out[4 * v + 1] += x.y; out[4 * v + 2] += x.z; out[4 * v + 3] += x.w;
+            }
+          }
+          __nv_bfloat16* drow = args.D + (long long)(m_blk * kF8BM + row) * args.ldd + n_blk * kF8BN + krank * W;
+#pragma unroll
+          for (int v = 0; v < W / 8; ++v)
+            *reinterpret_cast<uint4*>(drow + v * 8) =
+                make_uint4(pack_bf16x2(out[8 * v], out[8 * v + 1]), pack_bf16x2(out[8 * v + 2], out[8 * v + 3]),
+                           pack_bf16x2(out[8 * v + 4], out[8 * v + 5]), pack_bf16x2(out[8 * v + 6], out[8 * v + 7]));
+        }
+        break;                                        // one tile per cluster
+      }
+      ok = named_bar_and(2, 128, ok);                 // the four warps leave together or not at all
       if (!ok) break;
       // bf16 result -> two swizzled [128][128 B] images -> TMA store
       if (issuer) tma_wait_group_read<0>();
@@ -252,6 +337,21 @@ __global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, long
 extern "C" {
 using namespace mfb;
 
+// CTAs per cluster that share the K range of a tile (1 = no split). Splitting pays when one row block and few column
+// tiles would leave most SMs without weights to stream; a cluster of 8 needs 8 free SMs in one GPC, so at most 128
+// CTAs of such clusters are resident at a time.
+static int g_f8_split_enabled = 1;
+void mfb_gemm_fp8_enable_ksplit(int on) { g_f8_split_enabled = on ? 1 : 0; }   // for A/B timing
+
+int mfb_gemm_fp8_ksplit(int M, int N, int K, int mode, long long ldd) {
+  if (!g_f8_split_enabled || mode != 0 || M > kF8BM || ldd % 8) return 1;
+  const int tiles = N / kF8BN, kblocks = K / kF8BK;
+  if (tiles * 8 <= 128 && kblocks >= 16) return 8;
+  if (tiles * 4 <= 144 && kblocks >= 8) return 4;
+  if (tiles * 2 <= 148 && kblocks >= 4) return 2;
+  return 1;
+}
+
 // See the file header. lda / ldb in bytes (= elements), ldd in bf16 elements. M is the row bound in mode 1.
 int mfb_gemm_fp8_blockscaled(const void* A, const void* B, void* D, const float* sa, long long sa_ld, const float* sb,
                              int M, int N, int K, long long lda, long long ldb, long long ldd, int mode, int num_groups,
@@ -272,18 +372,40 @@ int mfb_gemm_fp8_blockscaled(const void* A, const void* B, void* D, const float*
   a.num_m_blocks = (M + kF8BM - 1) / kF8BM; a.num_n_blocks = N / kF8BN;
   a.mode = mode; a.num_groups = G; a.sa_ld = sa_ld; a.sa = sa; a.sb = sb;
   a.m_block_group = m_block_group; a.num_m_blocks_dev = num_m_blocks_dev; a.status = status;
+  a.D = reinterpret_cast<__nv_bfloat16*>(D); a.ldd = ldd;
   constexpr int SMEM = kF8Stages * 2 * kF8TileBytes + 2 * kF8TileBytes + (2 * kF8Stages + 4) * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
       mfb_host::set_error("gemm_fp8: cannot raise the shared memory limit");
       return 10;
     }
     attr_set = true;
   }
   int tiles = a.num_m_blocks * a.num_n_blocks;
+  const int ks = mfb_gemm_fp8_ksplit(M, N, K, mode, ldd);
+  if (ks > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * ks);
+    cfg.blockDim = dim3(kF8Threads);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ks; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = ks == 2   ? cudaLaunchKernelEx(&cfg, gemm_fp8_blockscaled_kernel<2>, tA, tB, tD, a)
+                    : ks == 4 ? cudaLaunchKernelEx(&cfg, gemm_fp8_blockscaled_kernel<4>, tA, tB, tD, a)
+                              : cudaLaunchKernelEx(&cfg, gemm_fp8_blockscaled_kernel<8>, tA, tB, tD, a);
+    if (e != cudaSuccess) { mfb_host::set_error("gemm_fp8: split-K launch failed: %s", cudaGetErrorString(e)); return 11; }
+    return 0;
+  }
   int grid = tiles < 148 ? tiles : 148;
-  gemm_fp8_blockscaled_kernel<<<grid, kF8Threads, SMEM, stream>>>(tA, tB, tD, a);
+  gemm_fp8_blockscaled_kernel<1><<<grid, kF8Threads, SMEM, stream>>>(tA, tB, tD, a);
   if (cudaGetLastError() != cudaSuccess) { mfb_host::set_error("gemm_fp8: launch failed"); return 11; }
   return 0;
 }

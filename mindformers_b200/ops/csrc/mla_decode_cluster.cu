@@ -18,7 +18,7 @@
 // threads (and the exchange) work on tile j.
 //
 // No TMA load here is a cluster-wide broadcast: every CTA loads its own columns into its own shared memory.
-// Cross-CTA traffic is 64-byte st.shared::cluster rows and mbarrier arrives. Every wait is bounded; both CTAs of a
+// Cross-CTA traffic is the 64-byte st.async rows. Every wait is bounded; both CTAs of a
 // cluster see the same tile count, and both always reach the cluster barriers at the start and the end.
 #include "common.cuh"
 
@@ -64,11 +64,12 @@ __device__ __forceinline__ uint32_t mc_mapa(uint32_t local_addr, uint32_t rank) 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mc_st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void mc_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// 16-byte store into the peer CTA's shared memory that also counts 16 bytes on the peer's mbarrier: the receiver's
+// wait completes when all expected bytes have landed, with no separate arrive from the 128 sending threads
+__device__ __forceinline__ void mc_st_async_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                               uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(remote_bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mc_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -149,7 +150,7 @@ mla_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       mbar_init(smem_u32(&empty[s]), 1);
       mbar_init(smem_u32(&s_full[s]), 1);
       mbar_init(smem_u32(&s_empty[s]), 128);
-      mbar_init(smem_u32(&x_full[s]), 128);
+      mbar_init(smem_u32(&x_full[s]), 1);
     }
     mbar_init(smem_u32(p_ready), 128);
     mbar_init(smem_u32(pv_done), 1);
@@ -234,9 +235,14 @@ mla_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          ok = issue_s(j + 1);          // runs while the softmax threads and the exchange work on tile j
+        // S^T of tile j + 1 goes first when its data is already here (it then runs while the softmax threads and the
+        // exchange work on tile j); otherwise the O^T update of tile j must not wait for that load, whose buffer is
+        // only freed by the O^T update of tile j - 1
+        bool next_issued = j + 1 >= n_tiles;
+        if (!next_issued && mbar_try_wait(smem_u32(&full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
+          ok = issue_s(j + 1);
           if (!ok) break;
+          next_issued = true;
         }
         ok = mbar_wait(smem_u32(p_ready), j & 1, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
@@ -255,6 +261,7 @@ mla_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         }
         umma_commit(smem_u32(&empty[buf]));
         umma_commit(smem_u32(pv_done));
+        if (!next_issued) ok = issue_s(j + 1);
       }
     }
     __syncwarp();
@@ -280,16 +287,17 @@ mla_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         tc_fence_before();
         mbar_arrive(smem_u32(&s_empty[buf]));
       }
-      // ---- exchange: my partial row goes into the peer's sX[buf]; the peer's arrives in mine. The peer's threads
-      // arrive for tile j only after they have read sX[buf] of tile j - 2, and this thread passed that wait in tile
-      // j - 1 (other buffer) only after ALL of them had arrived for j - 1, so the slot it writes is free. ----
+      // ---- exchange: my partial row goes into the peer's sX[buf]; the peer's lands in mine (8 KB per tile, counted
+      // on x_full[buf]). The peer sends tile j only after it has finished tile j - 1, for which it needed this CTA's
+      // rows of tile j - 1, and every thread here sends those only after it has read sX[buf] of tile j - 2 and (for
+      // thread 0) seen that phase complete: the slot is free and the barrier is in its next phase. ----
       if (ok) {
+        if (row == 0) mbar_expect_tx(smem_u32(&x_full[buf]), kMcXBytes);
         const uint32_t dst = mc_mapa(smem_u32(sX + buf * kMcXBytes + row * (kMcHeads * 4)), peer);
+        const uint32_t rbar = mc_mapa(smem_u32(&x_full[buf]), peer);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          mc_st_cluster_v4(dst + q * 16, __uint_as_float(sr[4 * q]), __uint_as_float(sr[4 * q + 1]),
-                           __uint_as_float(sr[4 * q + 2]), __uint_as_float(sr[4 * q + 3]));
-        mc_arrive_remote(mc_mapa(smem_u32(&x_full[buf]), peer));
+          mc_st_async_v4(dst + q * 16, sr[4 * q], sr[4 * q + 1], sr[4 * q + 2], sr[4 * q + 3], rbar);
         ok = mc_wait_cluster(smem_u32(&x_full[buf]), ph, abort_flag, args.status);
       }
       float s[kMcHeads];

@@ -212,42 +212,57 @@ moe_scatter_kernel(MoeMoveArgs a, const __nv_bfloat16* __restrict__ x) {
   const long long nwarps = (long long)gridDim.x * warps_per_cta;
   const int n = a.T * a.k;
   const int vecs = a.H >> 3;
-  for (long long c = gw; c < n; c += nwarps) {
+  // one work item = 128 vectors (2 KB) of one copy: a decode batch of a few hundred copies still fills the GPU
+  const int chunks = (vecs + 127) >> 7;
+  for (long long item = gw; item < (long long)n * chunks; item += nwarps) {
+    const long long c = item / chunks;
+    const int v_lo = (int)(item - c * chunks) << 7;
     const int t = (int)(c / a.k);
     const int e = (int)a.ids[c];
     const int owner = e / a.E_local;
     const int row = a.write_base[e] + a.rank_in_e[c];
     const bool ok = e >= 0 && owner < a.world && row >= 0 && row < a.owner_cap[owner];
-    if (lane == 0) a.dest_row[c] = ok ? row : -1;
+    if (lane == 0 && v_lo == 0) a.dest_row[c] = ok ? row : -1;
     if (!ok) continue;
     const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * a.H);
     uint4* dst = reinterpret_cast<uint4*>(a.buf_peer[owner] + (long long)row * a.H);
+    const float w = a.weights ? a.weights[c] : 1.f;
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v_lo + u * 32 + lane;
+      if (v < vecs) q[u] = src[v];
+    }
     if (a.weights) {
-      const float w = a.weights[c];
-      for (int v = lane; v < vecs; v += 32) {
-        uint4 q = src[v];
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q[u]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float2 f = __bfloat1622float2(h[i]);
           f.x *= w; f.y *= w;
           h[i] = __float22bfloat162_rn(f);
         }
-        dst[v] = q;
       }
-    } else {
-      for (int v = lane; v < vecs; v += 32) dst[v] = src[v];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v_lo + u * 32 + lane;
+      if (v < vecs) dst[v] = q[u];
     }
   }
-  // padding rows of the local segments start as zero
-  const uint4 z = make_uint4(0, 0, 0, 0);
-  for (int le = 0; le < a.E_local; ++le) {
-    const int first = a.group_offsets[le] + a.seg_fill[le];
-    int last = a.group_offsets[le + 1];
-    if (last > a.rows_cap) last = a.rows_cap;
-    for (long long r = first + gw; r < last; r += nwarps) {
-      uint4* dst = reinterpret_cast<uint4*>(a.buf_peer[a.rank] + r * a.H);
-      for (int v = lane; v < vecs; v += 32) dst[v] = z;
+  // padding rows of the local segments start as zero: the weight-gradient GEMM sums over them. Without a plan
+  // (inference: rows are independent and padding rows are never gathered) they are left as they are.
+  if (a.group_offsets) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int le = 0; le < a.E_local; ++le) {
+      const int first = a.group_offsets[le] + a.seg_fill[le];
+      int last = a.group_offsets[le + 1];
+      if (last > a.rows_cap) last = a.rows_cap;
+      for (long long r = first + gw; r < last; r += nwarps) {
+        uint4* dst = reinterpret_cast<uint4*>(a.buf_peer[a.rank] + r * a.H);
+        for (int v = lane; v < vecs; v += 32) dst[v] = z;
+      }
     }
   }
   __threadfence_system();
@@ -276,6 +291,55 @@ moe_gather_kernel(MoeMoveArgs a, __nv_bfloat16* __restrict__ out, const __nv_bfl
   const long long gw = (long long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * warps_per_cta;
   const int vecs = a.H >> 3;
+  if (!g) {
+    // forward / inference: one work item = 32 vectors of one token, the k rows are fetched four at a time
+    if (!out) return;
+    const int chunks = (vecs + 31) >> 5;
+    for (long long item = gw; item < (long long)a.T * chunks; item += nwarps) {
+      const long long t = item / chunks;
+      const int v = ((int)(item - t * chunks) << 5) + lane;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int j0 = 0; j0 < a.k; j0 += 4) {
+        uint4 q[4];
+        float w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          w[u] = 0.f;
+          q[u] = make_uint4(0, 0, 0, 0);
+          const int j = j0 + u;
+          if (j < a.k) {
+            const long long c = t * a.k + j;
+            const int row = a.dest_row[c];
+            const int owner = (int)a.ids[c] / a.E_local;
+            if (row >= 0 && owner >= 0 && owner < a.world && v < vecs) {
+              q[u] = moe_ld_cg(a.buf_peer[owner] + (long long)row * a.H + 8 * v);
+              w[u] = a.weights ? a.weights[c] : 1.f;
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            acc[2 * i] += w[u] * f.x;
+            acc[2 * i + 1] += w[u] * f.y;
+          }
+        }
+      }
+      if (v < vecs) {
+        uint4 q;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __float22bfloat162_rn(make_float2(acc[2 * i], acc[2 * i + 1]));
+        reinterpret_cast<uint4*>(out + t * a.H)[v] = q;
+      }
+    }
+    return;
+  }
   for (long long t = gw; t < a.T; t += nwarps) {
     for (int v0 = 0; v0 < vecs; v0 += 32) {
       const int v = v0 + lane;

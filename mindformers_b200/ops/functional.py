@@ -43,6 +43,34 @@ def get_attention_backend() -> str:
     return _ATTN_BACKEND
 
 
+class _NoGradCtx:
+    """Stand-in for the autograd context of a ``torch.autograd.Function`` when gradients are off: the forward
+    implementation then runs as a plain call (``Function.apply`` costs tens of microseconds of host time per call,
+    which is what bounds a decode step made of small kernels)."""
+    needs_input_grad = ()
+    saved_tensors = ()
+
+    def save_for_backward(self, *tensors):
+        pass
+
+    def mark_non_differentiable(self, *tensors):
+        pass
+
+    def mark_dirty(self, *tensors):
+        pass
+
+    def set_materialize_grads(self, value):
+        pass
+
+
+def apply_fn(fn, *args):
+    """``fn.apply(*args)`` with gradients enabled, ``fn.forward`` on a throw-away context otherwise."""
+    if torch.is_grad_enabled():
+        return fn.apply(*args)
+    return fn.forward(_NoGradCtx(), *args)
+
+
+
 def _on_gpu(t: torch.Tensor) -> bool:
     return t.is_cuda
 
@@ -203,10 +231,10 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not _on_gpu(x) or x.dtype != torch.bfloat16 or _GEMM_BACKEND != "tcgen05":
         if getattr(w, "main_grad", None) is not None and x.is_cuda:
-            y = _LinearFn.apply(x, w)
+            y = apply_fn(_LinearFn, x, w)
             return y if bias is None else y + bias
         return F.linear(x, w, bias)
-    y = _LinearFn.apply(x, w)
+    y = apply_fn(_LinearFn, x, w)
     if bias is not None:
         y = y + bias
     return y
@@ -302,7 +330,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5,
     """Returns ``(norm(x + residual) * w, x + residual)``; the second value is the new residual stream."""
     if _on_gpu(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 \
             and x.shape[-1] <= 8192:
-        return _RMSNormFn.apply(x, residual, w, eps)
+        return apply_fn(_RMSNormFn, x, residual, w, eps)
     return rmsnorm_reference(x, w, eps, residual)
 
 
@@ -346,7 +374,7 @@ class _SwiGLUFn(torch.autograd.Function):
 def swiglu(x: torch.Tensor) -> torch.Tensor:
     """``silu(x[..., :F]) * x[..., F:]``."""
     if _on_gpu(x) and x.dtype == torch.bfloat16 and (x.shape[-1] // 2) % 8 == 0:
-        return _SwiGLUFn.apply(x)
+        return apply_fn(_SwiGLUFn, x)
     return swiglu_reference(x)
 
 
@@ -405,7 +433,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch
     if _on_gpu(x) and x.dtype == torch.bfloat16 and x.is_contiguous():
         if x.requires_grad and x.is_leaf:
             x = x.clone()
-        return _RopeFn.apply(x, cos, sin, positions, n_heads, rot, interleaved)
+        return apply_fn(_RopeFn, x, cos, sin, positions, n_heads, rot, interleaved)
     return rope_reference(x, cos, sin, positions, n_heads, rot, interleaved)
 
 
@@ -452,7 +480,7 @@ class _EmbeddingFn(torch.autograd.Function):
 def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
     """Row gather; ids outside ``[vocab_start, vocab_start + rows)`` give zero rows (vocab-parallel shard)."""
     if _on_gpu(table) and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
-        return _EmbeddingFn.apply(ids, table, vocab_start)
+        return apply_fn(_EmbeddingFn, ids, table, vocab_start)
     local = ids - vocab_start
     ok = (local >= 0) & (local < table.shape[0])
     out = F.embedding(local.clamp(0, table.shape[0] - 1), table)
@@ -621,7 +649,9 @@ def quantize_act_1x128(x: torch.Tensor):
     if _on_gpu(x) and x.dtype == torch.bfloat16:
         x = x.contiguous()
         q = torch.empty(T, K, dtype=torch.float8_e4m3fn, device=x.device)
-        sa = torch.ones(K // 128, Tp, dtype=torch.float32, device=x.device)
+        # scales of the rows between T and T_pad stay unwritten: they only meet the zero-filled operand rows of the
+        # last row block, whose results are never stored
+        sa = torch.empty(K // 128, Tp, dtype=torch.float32, device=x.device)
         rc = _lib.get_lib().mfb_quant_act_1x128(x.data_ptr(), x.stride(0), q.data_ptr(), K, sa.data_ptr(), Tp, T, K,
                                                 _lib.stream_ptr())
         _lib.check(rc, "mfb_quant_act_1x128")
@@ -753,7 +783,7 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, *, s
     incremented by the number of copies routed to each expert."""
     E = logits.shape[-1]
     if _on_gpu(logits) and logits.dtype == torch.float32 and E <= 512 and k <= 32 and (not groups or groups <= 32):
-        probs, ids, scores = _RouterFn.apply(logits, bias, k, sigmoid, norm, scale, groups, group_topk, need_scores, counts)
+        probs, ids, scores = apply_fn(_RouterFn, logits, bias, k, sigmoid, norm, scale, groups, group_topk, need_scores, counts)
         return probs, ids, (scores if need_scores else None)
     probs, ids, scores = router_topk_reference(logits.float(), bias, k, sigmoid, norm, scale, groups, group_topk)
     if counts is not None:

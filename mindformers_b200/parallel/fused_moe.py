@@ -22,6 +22,7 @@ from ..ops import _lib
 from . import parallel_state as ps
 from ..tools.logger import logger
 from . import symm_mem
+from ..ops.functional import apply_fn
 
 BLOCK = 128
 
@@ -205,13 +206,17 @@ class MoEExchange:
         _lib.count_launch(2)
         return st
 
-    def scatter(self, st, x, ids, peer_ptrs, weights=None):
+    def scatter(self, st, x, ids, peer_ptrs, weights=None, zero_pad: bool = True):
+        """``zero_pad=False`` (forward-only calls) leaves the padding rows of the expert segments as they are: rows
+        are independent in every expert operator and padding rows are never gathered; only the weight-gradient
+        GEMM, which sums over rows, needs them to be zero."""
         T = x.shape[0]
         rc = self.lib.mfb_moe_scatter(self.world, self.rank, T, self.k, self.H, self.E_local, st.rows, x.data_ptr(),
                                       ids.data_ptr(), st.rank_in_e.data_ptr(), st.write_base.data_ptr(),
                                       st.owner_cap.data_ptr(), peer_ptrs,
-                                      _lib.ptr(weights), st.dest_row.data_ptr(), st.plan.group_offsets.data_ptr(),
-                                      st.plan.seg_fill.data_ptr(), self.status(), _lib.stream_ptr())
+                                      _lib.ptr(weights), st.dest_row.data_ptr(),
+                                      st.plan.group_offsets.data_ptr() if zero_pad else 0,
+                                      st.plan.seg_fill.data_ptr() if zero_pad else 0, self.status(), _lib.stream_ptr())
         _lib.check(rc, "mfb_moe_scatter")
         _lib.count_launch()
 
@@ -257,7 +262,7 @@ class _Dispatch(torch.autograd.Function):
         else:
             xin = torch.empty(st.rows, ex.H, dtype=torch.bfloat16, device=x.device)
             ptrs = ex.local_ptrs(xin)
-        ex.scatter(st, x, ids, ptrs)
+        ex.scatter(st, x, ids, ptrs, zero_pad=not str(layer_key).startswith("nograd"))
         ex.barrier(1)
         ctx.ex, ctx.st, ctx.T = ex, st, T
         ctx.save_for_backward(ids)
@@ -334,10 +339,10 @@ def moe_dispatch_experts_combine(layer, hidden: torch.Tensor, probs: torch.Tenso
     slot = ex.acquire_slot(layer_key)
     st.slot = (layer_key, slot)
     key = f"{layer_key}.{slot}"
-    xin = _Dispatch.apply(hidden, ids, ex, st, key)
+    xin = apply_fn(_Dispatch, hidden, ids, ex, st, key)
     layer.last_tokens_per_expert = st.counts
     y = layer.experts(xin, st.plan)
-    out = _Combine.apply(y, probs, ids, ex, st, key)
+    out = apply_fn(_Combine, y, probs, ids, ex, st, key)
     if not needs_grad:
         ex.release_slot(*st.slot)
     return out

@@ -24,6 +24,7 @@ from .. import mappings as M
 from .. import parallel_state as ps
 from .mlp import MLP
 from .tensor_parallel import default_init
+from ...ops.functional import apply_fn
 
 BLOCK = 128  # row block of the grouped GEMM
 
@@ -238,9 +239,9 @@ class GroupedMLP(nn.Module):
             hq, sh = Fn.quantize_act_1x128(Fn.swiglu(h))
             return Fn.fp8_gemm(hq, sh, self.w2_fp8, self.w2_scale_inv, block_group=plan.block_group,
                                num_blocks=plan.num_blocks)
-        h = _GroupedLinearFn.apply(x, self.weight1, plan.block_group, plan.num_blocks, plan.group_offsets)
+        h = apply_fn(_GroupedLinearFn, x, self.weight1, plan.block_group, plan.num_blocks, plan.group_offsets)
         h = Fn.swiglu(h)
-        return _GroupedLinearFn.apply(h, self.weight2, plan.block_group, plan.num_blocks, plan.group_offsets)
+        return apply_fn(_GroupedLinearFn, h, self.weight2, plan.block_group, plan.num_blocks, plan.group_offsets)
 
 
 class SharedExpertMLP(MLP):

@@ -124,29 +124,45 @@ class _Fp8WeightMixin:
 
     ``quantize_fp8_()`` replaces the bf16 parameter by the buffers ``weight_fp8`` / ``weight_scale_inv``;
     ``load_fp8_(w, s)`` installs checkpoint tensors directly. ``_mm`` then runs the fp8 GEMM with activations
-    quantised per 1 x 128 block on the fly. Layers whose shape is not a multiple of 128 stay in bf16.
+    quantised per 1 x 128 block on the fly. Output rows that do not fill the last 128-row block are padded with zero
+    rows (the checkpoint format does the same: its scale grid has ``ceil(rows / 128)`` entries) and the padding columns
+    of the result are sliced off; layers whose input width is not a multiple of 128 stay in bf16.
     """
     weight_fp8 = None
     weight_scale_inv = None
+    _fp8_rows = None          # true number of output rows when ``weight_fp8`` carries padding rows
 
     def quantize_fp8_(self) -> bool:
         w = self.weight
-        if w is None or w.dim() != 2 or w.shape[0] % 128 or w.shape[1] % 128:
+        if w is None or w.dim() != 2 or w.shape[0] % 8 or w.shape[1] % 128:
             return False
-        wq, scale = Fn.quantize_weight_128x128(w.detach())
-        return self.load_fp8_(wq, scale)
+        wq, scale = Fn.quantize_weight_128x128(_pad_rows_128(w.detach()))
+        return self.load_fp8_(wq, scale, rows=w.shape[0])
 
-    def load_fp8_(self, wq: torch.Tensor, scale_inv: torch.Tensor) -> bool:
+    def load_fp8_(self, wq: torch.Tensor, scale_inv: torch.Tensor, rows: Optional[int] = None) -> bool:
+        rows = wq.shape[0] if rows is None else rows
         self._parameters.pop("weight", None)
         self.weight = None
-        self.weight_fp8 = wq
+        self.weight_fp8 = _pad_rows_128(wq)
         self.weight_scale_inv = scale_inv.float().contiguous()
+        self._fp8_rows = rows if rows != self.weight_fp8.shape[0] else None
         return True
 
     def _mm(self, x: torch.Tensor, w: Optional[torch.Tensor] = None) -> torch.Tensor:
         if w is None and self.weight_fp8 is not None:
-            return Fn.fp8_linear(x, self.weight_fp8, self.weight_scale_inv)
+            y = Fn.fp8_linear(x, self.weight_fp8, self.weight_scale_inv)
+            return y if self._fp8_rows is None else y[..., :self._fp8_rows]
         return Fn.linear(x, self.weight if w is None else w)
+
+
+def _pad_rows_128(w: torch.Tensor) -> torch.Tensor:
+    """``w [N, K]`` with zero rows appended up to the next multiple of 128 (no copy when N already is one)."""
+    pad = -w.shape[0] % 128
+    if pad == 0:
+        return w
+    out = torch.zeros(w.shape[0] + pad, w.shape[1], dtype=w.dtype, device=w.device)
+    out[:w.shape[0]] = w
+    return out
 
 
 class ColumnParallelLinear(_Fp8WeightMixin, nn.Module):

@@ -14,6 +14,7 @@ import torch
 import torch.distributed as dist
 
 from . import parallel_state as ps
+from ..ops.functional import apply_fn
 
 
 def _tp():
@@ -159,10 +160,10 @@ class _AllToAll(torch.autograd.Function):
         return _AllToAll.apply(g, ctx.in_splits, ctx.out_splits, ctx.group), None, None, None
 
 
-def copy_to_tensor_model_parallel_region(x): return _CopyToTP.apply(x)
-def reduce_from_tensor_model_parallel_region(x): return _ReduceFromTP.apply(x)
-def gather_from_sequence_parallel_region(x, reduce_scatter_grad=True): return _GatherFromSP.apply(x, reduce_scatter_grad)
-def reduce_scatter_to_sequence_parallel_region(x): return _ReduceScatterToSP.apply(x)
-def scatter_to_sequence_parallel_region(x): return _ScatterToSP.apply(x)
-def gather_from_tensor_model_parallel_region(x): return _GatherLastDim.apply(x)
+def copy_to_tensor_model_parallel_region(x): return apply_fn(_CopyToTP, x)
+def reduce_from_tensor_model_parallel_region(x): return apply_fn(_ReduceFromTP, x)
+def gather_from_sequence_parallel_region(x, reduce_scatter_grad=True): return apply_fn(_GatherFromSP, x, reduce_scatter_grad)
+def reduce_scatter_to_sequence_parallel_region(x): return apply_fn(_ReduceScatterToSP, x)
+def scatter_to_sequence_parallel_region(x): return apply_fn(_ScatterToSP, x)
+def gather_from_tensor_model_parallel_region(x): return apply_fn(_GatherLastDim, x)
 def all_to_all(x, out_splits, in_splits, group): return _AllToAll.apply(x, out_splits, in_splits, group)

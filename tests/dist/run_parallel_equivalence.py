@@ -58,6 +58,7 @@ def main():
             with open(args.out, "w") as f:
                 json.dump({"losses": [float(loss)], "digest": {}, "norm": 0.0}, f)
         if world > 1:
+            dist.barrier()          # no rank tears the group down while another is still inside a collective
             dist.destroy_process_group()
         return
     opt = DistributedOptimizer(model, learning_rate=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0,
@@ -97,6 +98,7 @@ def main():
         with open(args.out, "w") as f:
             json.dump({"losses": losses, "digest": digest, "norm": out["global_norm"].item()}, f)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

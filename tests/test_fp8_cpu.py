@@ -68,3 +68,19 @@ def test_fp8_checkpoint_roundtrip(tmp_path):
     with torch.no_grad():
         out = fresh(ids).float()
     assert ((out - ref).norm() / ref.norm()).item() < 0.08
+
+
+def test_fp8_linear_with_ragged_output_rows_is_padded_and_sliced():
+    """An output width that does not fill its last 128-row block (MLA ``linear_qkv``: q_lora + kv_lora + rope) is
+    quantised with zero padding rows; the result has the true width and matches the full-precision layer."""
+    model = tiny_deepseek()
+    quantize_model_fp8(model)
+    lin = dict(model.named_modules())["model.decoder.layers.0.self_attention.linear_qkv"]
+    assert lin.weight is None and lin.weight_fp8.shape[0] == 384 and lin._fp8_rows == 128 + 128 + 16
+    assert lin.weight_scale_inv.shape == (3, 2)
+    ref = tiny_deepseek()
+    ref_lin = dict(ref.named_modules())["model.decoder.layers.0.self_attention.linear_qkv"]
+    x = torch.randn(5, 256)
+    y, y_ref = lin._mm(x), ref_lin._mm(x)
+    assert y.shape == y_ref.shape == (5, 272)
+    assert ((y.float() - y_ref).norm() / y_ref.norm()).item() < 0.06

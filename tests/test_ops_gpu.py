@@ -420,7 +420,9 @@ def test_mla_decode_attention(nh, block, variant):
         assert err < 2e-2, (b, n, err)
 
 
-@pytest.mark.parametrize("T,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 2048, 7168)])
+@pytest.mark.parametrize("T,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 2048, 7168),
+                                   # one row block and few column tiles: K split over a cluster of 8, 4, 2, 4 CTAs
+                                   (64, 1536, 7168), (64, 3072, 1536), (17, 7168, 2048), (128, 4608, 7168), (1, 256, 512)])
 def test_fp8_blockscaled_gemm_dense(T, N, K):
     torch.manual_seed(T + N)
     x = (torch.randn(T, K, device="cuda") * 0.7).to(torch.bfloat16)

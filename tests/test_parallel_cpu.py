@@ -26,7 +26,14 @@ def _run(tmp_path, nproc, tag, *extra, script=SCRIPT):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), script, "--out", str(out), *extra]
     env = dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1")
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    for attempt in range(2):
+        # a port found free can be taken before the rendezvous binds it: that one failure is retried on a new port
+        if nproc > 1:
+            cmd[cmd.index("--master-port") + 1] = str(_free_port())
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        if res.returncode == 0 or attempt == 1 or not any(
+                m in res.stderr for m in ("address already in use", "Address already in use", "EADDRINUSE")):
+            break
     assert res.returncode == 0, res.stderr[-3000:]
     return json.loads(out.read_text())
 
