@@ -31,7 +31,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--block", type=int, default=128)
-    ap.add_argument("--graph", action="store_true", help="capture the decode step in a CUDA graph (single GPU only)")
+    ap.add_argument("--graph", action="store_true", help="capture the decode step in a CUDA graph")
     ap.add_argument("--hidden", type=int, default=None, help="debug only: override the hidden size")
     ap.add_argument("--experts", type=int, default=None, help="debug only: override the number of routed experts")
     args = ap.parse_args()
@@ -80,7 +80,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    gen_kw = dict(do_sample=False, eos_token_id=None, use_cuda_graph=bool(args.graph and world == 1))
+    gen_kw = dict(do_sample=False, eos_token_id=None, use_cuda_graph=bool(args.graph))
     model.generate([p[:128] for p in prompts[:2]], max_new_tokens=4, **gen_kw)       # warm-up (allocations, buffers)
     model.generate(prompts, max_new_tokens=1, **gen_kw)
     sync()
@@ -115,7 +115,7 @@ def main():
             "data": "synthetic uniform token ids, random-init weights", "new_tokens": new_tokens,
             "config": {"model": f"{args.preset}(layers={args.layers})", "batch": args.batch, "prompt": args.prompt,
                        "new": args.new, "block_size": args.block, "parallelism": f"tp{world} ep{ep}"},
-            "decode_cuda_graph": bool(args.graph and world == 1), "weights_gib_per_gpu": round(mem_weights, 2), "fp8": fp8_stats, "gpu_launches": launches,
+            "decode_cuda_graph": bool(args.graph), "weights_gib_per_gpu": round(mem_weights, 2), "fp8": fp8_stats, "gpu_launches": launches,
             "kernel_status_word": _lib.read_status()}))
     if world > 1:
         dist.destroy_process_group()

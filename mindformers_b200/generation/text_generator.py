@@ -92,13 +92,16 @@ class GenerationMixin:
         """Build a callable ``step(tokens, starts, active) -> logits [B, V]`` that replays one captured decode step.
 
         Everything the step reads lives in static device tensors (token ids, positions, block tables, slot mapping,
-        context lengths); a step copies the new values in and replays. Only for models on one GPU: the fused
-        communication kernels take a per-call epoch argument and cannot be replayed. Returns None when the step
-        cannot be captured (the caller then launches eagerly)."""
+        context lengths); a step copies the new values in and replays. With tensor- or expert-parallel ranks the
+        graph holds NCCL collectives and the expert exchange kernels (whose flag epochs are device counters); the
+        one-shot GEMM + all-reduce kernel takes its epoch from the host, so row-parallel layers fall back to NCCL
+        while a stream is capturing. Every rank must take the same decision, so it depends on the layout only.
+        Returns None when the step cannot be captured (the caller then launches eagerly)."""
         device = next(self.parameters()).device
-        if device.type != "cuda" or ps.get_tensor_model_parallel_world_size() > 1 \
-                or ps.get_expert_model_parallel_world_size() > 1 or ps.get_pipeline_model_parallel_world_size() > 1:
+        if device.type != "cuda" or ps.get_pipeline_model_parallel_world_size() > 1 \
+                or ps.get_context_parallel_world_size() > 1:
             return None
+        tp = ps.get_tensor_model_parallel_world_size()
         width = tables.max_blocks_per_seq
         st_tok = torch.zeros(1, B, dtype=torch.int64, device=device)
         st_pos = torch.zeros(B, dtype=torch.int64, device=device)
@@ -127,7 +130,12 @@ class GenerationMixin:
 
         def forward():
             meta = AttnMeta(batch=1, seq_len=B, positions=st_pos, cache=ctx)
-            return self.model(st_tok, attn_meta=meta)
+            logits = self.model(st_tok, attn_meta=meta)
+            if tp > 1:          # vocabulary-parallel head: every rank gets the full row
+                parts = [torch.empty_like(logits) for _ in range(tp)]
+                torch.distributed.all_gather(parts, logits.contiguous(), group=ps.get_tensor_model_parallel_group())
+                logits = torch.cat(parts, dim=-1)
+            return logits
 
         state = {"graph": None, "out": None}
 

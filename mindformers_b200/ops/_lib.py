@@ -15,7 +15,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 KERNEL_LIB_PATH = os.path.join(_HERE, "lib", "libmfb200.so")
 DATA_LIB_PATH = os.path.join(_HERE, "lib", "libmfb200_data.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _lock = threading.Lock()
 _lib = None
@@ -89,9 +89,9 @@ def _declare(lib):
     sig("mfb_router_bwd", [P, P, P, P, P, I, I, I, I, I, F, P])
     sig("mfb_moe_flag_words", [])
     sig("mfb_moe_rank", [P, I, I, P, P, P])
-    sig("mfb_moe_plan", [I, I, I, I, I, I] + [P] * 11)
+    sig("mfb_moe_plan", [I, I, P, I, I, I] + [P] * 11)
     sig("mfb_moe_scatter", [I] * 7 + [P] * 12)
-    sig("mfb_moe_barrier", [I, I, I, I, P, P, P])
+    sig("mfb_moe_barrier", [I, I, P, I, P, P, P])
     sig("mfb_moe_gather", [I] * 7 + [P] * 9)
     sig("mfb_flash_attn_fwd_ex", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, I, F, P, P])
     sig("mfb_flash_attn_bwd_ex", [P] * 10 + [I, I, I, I, I] + [L] * 8 + [I, I, F, P, P])

@@ -77,6 +77,6 @@ extern "C" {
 const char* mfb_last_error() { return mfb_host::last_error(); }
 
 // ABI version of this library; bumped when an entry point changes its arguments.
-int mfb_abi_version() { return 1; }
+int mfb_abi_version() { return 2; }
 
 }  // extern "C"

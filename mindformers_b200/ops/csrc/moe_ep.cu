@@ -19,7 +19,9 @@
 //                       <g[t], row> that the backward pass needs for d(probs)
 //
 // With a single rank the same kernels are the local permute / unpermute (no flags are touched).
-// Flags carry a per-call epoch; every wait is bounded and reports kStatusPeerFlagTimeout in the status word.
+// Flags carry a per-call epoch that the kernels take from a counter in device memory and advance themselves (every
+// rank runs the same sequence of calls, so the counters agree), which lets a CUDA graph replay them; every wait is
+// bounded and reports kStatusPeerFlagTimeout in the status word.
 #include "common.cuh"
 
 namespace mfb {
@@ -100,7 +102,8 @@ moe_rank_kernel(const long long* __restrict__ ids, int n, int* __restrict__ rank
 // count exchange + layout plan
 // ---------------------------------------------------------------------------------------------------------------
 struct MoePlanArgs {
-  int world, rank, epoch, E, E_local, rows_cap, nblocks_cap;
+  int world, rank, E, E_local, rows_cap, nblocks_cap;
+  int* epoch_ctr;                    // device counter of this rank: the call uses *epoch_ctr + 1 and stores it back
   const int* counts;                 // [E] of this rank
   int* table_peer[kMoeMaxRanks];     // [world][E + 1] table of every rank: row r = counts of rank r, then its rows_cap
   int* owner_cap;                    // out [kMoeMaxRanks]: rows_cap of every rank's buffer
@@ -125,10 +128,14 @@ moe_plan_kernel(MoePlanArgs a) {
       if (e < a.E) a.table_peer[p][a.rank * (a.E + 1) + e] = a.counts[e];
       if (e == 0) a.table_peer[p][a.rank * (a.E + 1) + a.E] = a.rows_cap;
     }
+    __shared__ int s_epoch;
+    if (e == 0) s_epoch = *a.epoch_ctr + 1;
     __threadfence_system();
     __syncthreads();
-    if (e < a.world) moe_st_release_sys(a.flags_peer[e] + a.rank, a.epoch);
-    moe_wait_all(a.flags_peer[a.rank], a.world, a.epoch, a.status);
+    const int epoch = s_epoch;
+    if (e < a.world) moe_st_release_sys(a.flags_peer[e] + a.rank, epoch);
+    moe_wait_all(a.flags_peer[a.rank], a.world, epoch, a.status);
+    if (e == 0) *a.epoch_ctr = epoch;
   }
   if (e < a.E) {
     int t = 0, b = 0;
@@ -269,17 +276,23 @@ moe_scatter_kernel(MoeMoveArgs a, const __nv_bfloat16* __restrict__ x) {
 }
 
 struct MoeBarrierArgs {
-  int world, rank, epoch, phase;
+  int world, rank, phase;
+  int* epoch_ctr;
   int* flags_peer[kMoeMaxRanks];
   int* status;
 };
 
 __global__ void moe_barrier_kernel(MoeBarrierArgs a) {
   if (a.world <= 1) return;
+  __shared__ int s_epoch;
+  if (threadIdx.x == 0) s_epoch = *a.epoch_ctr + 1;
   __threadfence_system();
+  __syncthreads();
+  const int epoch = s_epoch;
   if (threadIdx.x < a.world)
-    moe_st_release_sys(a.flags_peer[threadIdx.x] + a.phase * kMoeMaxRanks + a.rank, a.epoch);
-  moe_wait_all(a.flags_peer[a.rank] + a.phase * kMoeMaxRanks, a.world, a.epoch, a.status);
+    moe_st_release_sys(a.flags_peer[threadIdx.x] + a.phase * kMoeMaxRanks + a.rank, epoch);
+  moe_wait_all(a.flags_peer[a.rank] + a.phase * kMoeMaxRanks, a.world, epoch, a.status);
+  if (threadIdx.x == 0) *a.epoch_ctr = epoch;
 }
 
 // out[t] = sum_j w[t,j] * row(t,j)  (w == null: plain sum); dots[t,j] = <g[t], row(t,j)> when g is given
@@ -416,13 +429,14 @@ int mfb_moe_rank(const long long* ids, int n, int E, int* rank_in_e, int* counts
 }
 
 // peer_tables / peer_flags: host arrays of `world` device addresses.
-int mfb_moe_plan(int world, int rank, int epoch, int E, int E_local, int rows_cap, const int* counts,
+int mfb_moe_plan(int world, int rank, int* epoch_ctr, int E, int E_local, int rows_cap, const int* counts,
                  const long long* peer_tables, const long long* peer_flags, int* write_base, int* owner_cap,
                  int* group_offsets, int* seg_fill, int* block_group, int* num_blocks, int* status,
                  cudaStream_t stream) {
   if (moe_check(world, rank, E, E_local, 8)) return 1;
   MoePlanArgs a;
-  a.world = world; a.rank = rank; a.epoch = epoch; a.E = E; a.E_local = E_local; a.rows_cap = rows_cap;
+  if (world > 1 && !epoch_ctr) { mfb_host::set_error("moe plan: the epoch counter is missing"); return 1; }
+  a.world = world; a.rank = rank; a.epoch_ctr = epoch_ctr; a.E = E; a.E_local = E_local; a.rows_cap = rows_cap;
   a.nblocks_cap = rows_cap / kMoeBlock; a.counts = counts;
   for (int p = 0; p < world; ++p) {
     a.table_peer[p] = peer_tables ? reinterpret_cast<int*>(peer_tables[p]) : nullptr;
@@ -464,12 +478,12 @@ int mfb_moe_scatter(int world, int rank, int T, int k, int H, int E_local, int r
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-int mfb_moe_barrier(int world, int rank, int epoch, int phase, const long long* peer_flags, int* status,
+int mfb_moe_barrier(int world, int rank, int* epoch_ctr, int phase, const long long* peer_flags, int* status,
                     cudaStream_t stream) {
   if (world <= 1) return 0;
-  if (world > kMoeMaxRanks || phase < 1 || phase > 2) { mfb_host::set_error("moe barrier: bad world/phase"); return 1; }
+  if (world > kMoeMaxRanks || phase < 1 || phase > 2 || !epoch_ctr) { mfb_host::set_error("moe barrier: bad world/phase/counter"); return 1; }
   MoeBarrierArgs a;
-  a.world = world; a.rank = rank; a.epoch = epoch; a.phase = phase; a.status = status;
+  a.world = world; a.rank = rank; a.epoch_ctr = epoch_ctr; a.phase = phase; a.status = status;
   for (int p = 0; p < world; ++p) a.flags_peer[p] = reinterpret_cast<int*>(peer_flags[p]);
   moe_barrier_kernel<<<1, 32, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

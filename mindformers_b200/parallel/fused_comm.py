@@ -56,6 +56,8 @@ def allreduce_enabled(config, x: torch.Tensor, weight: torch.Tensor) -> bool:
         return False
     if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
         return False
+    if torch.cuda.is_current_stream_capturing():
+        return False            # the kernel's flag epoch comes from the host: a replay would reuse it
     from . import fused_tp
     return fused_tp.allreduce_shapes_ok(x.shape[0], x.shape[1], weight.shape[0])
 

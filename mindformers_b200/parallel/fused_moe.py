@@ -73,7 +73,9 @@ class MoEExchange:
         self.H = config.hidden_size
         self.factor = float(getattr(config, "moe_ep_buffer_factor", 1.25) or 1.25)
         self.dev = torch.device("cuda", torch.cuda.current_device())
-        self.epoch = 0
+        # epoch of the flag protocol: a device counter that the plan / barrier kernels advance themselves, so the
+        # same launches can be replayed from a CUDA graph
+        self.epoch_ctr = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.lib = _lib.get_lib()
         self._arr = ctypes.c_longlong * self.world
         self._shared: Dict[tuple, object] = {}
@@ -153,10 +155,6 @@ class MoEExchange:
     def local_ptrs(self, t: torch.Tensor):
         return self._arr(t.data_ptr())
 
-    def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
-
     def status(self):
         return _lib.status_word(self.dev).data_ptr()
 
@@ -197,7 +195,7 @@ class MoEExchange:
         st = _PlanState(self, rows, n)
         rc = self.lib.mfb_moe_rank(ids.data_ptr(), n, self.E, st.rank_in_e.data_ptr(), st.counts.data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "mfb_moe_rank")
-        rc = self.lib.mfb_moe_plan(self.world, self.rank, self.next_epoch(), self.E, self.E_local, rows, st.counts.data_ptr(),
+        rc = self.lib.mfb_moe_plan(self.world, self.rank, self.epoch_ctr.data_ptr(), self.E, self.E_local, rows, st.counts.data_ptr(),
                                    self.peer_table, self.peer_flags, st.write_base.data_ptr(), st.owner_cap.data_ptr(),
                                    st.plan.group_offsets.data_ptr(), st.plan.seg_fill.data_ptr(),
                                    st.plan.block_group.data_ptr(), st.plan.num_blocks.data_ptr(), self.status(),
@@ -222,7 +220,7 @@ class MoEExchange:
 
     def barrier(self, phase: int):
         if self.world > 1:
-            rc = self.lib.mfb_moe_barrier(self.world, self.rank, self.next_epoch(), phase, self.peer_flags, self.status(),
+            rc = self.lib.mfb_moe_barrier(self.world, self.rank, self.epoch_ctr.data_ptr(), phase, self.peer_flags, self.status(),
                                           _lib.stream_ptr())
             _lib.check(rc, "mfb_moe_barrier")
             _lib.count_launch()

@@ -1,7 +1,8 @@
 """Worker (torchrun, one rank per GPU): a small DeepSeek-V3-shaped model with tensor-parallel attention and
 expert-parallel MoE (both over all ranks), bf16 and block-scaled fp8 weights. Checks that generation runs through the
 tp-sliced MoE path, that every rank produces the same tokens, that fp8 and bf16 agree on most greedy tokens and that
-no bounded device wait ran out."""
+no bounded device wait ran out. The decode step is also replayed from a CUDA graph (NCCL collectives and the expert
+exchange kernels inside the graph) and must give the tokens of the eager run."""
 import json
 import os
 import sys
@@ -38,6 +39,9 @@ def main():
     out_bf16 = model.generate(prompts, **kw)
     stats = quantize_model_fp8(model)
     out_fp8 = model.generate(prompts, **kw)
+    out_graph = model.generate(prompts, use_cuda_graph=True, **kw)
+    out_graph2 = model.generate(prompts, use_cuda_graph=True, **kw)       # a second capture and replay sequence
+    graph_same = out_graph == out_fp8 and out_graph2 == out_fp8
     new_bf16 = torch.tensor([o[256:] for o in out_bf16], device="cuda")
     new_fp8 = torch.tensor([o[256:] for o in out_fp8], device="cuda")
     both = torch.stack([new_bf16, new_fp8])
@@ -47,10 +51,10 @@ def main():
     agree = (new_bf16[:, 0] == new_fp8[:, 0]).float().mean().item()       # first generated token of every prompt
     status = _lib.read_status()
     res = {"same_across_ranks": same_across_ranks, "first_token_agreement_fp8_vs_bf16": agree, "status": status,
-           "fp8_layers": stats["linear"], "fp8_grouped": stats["grouped"]}
+           "fp8_layers": stats["linear"], "fp8_grouped": stats["grouped"], "graph_matches_eager": graph_same}
     if rank == 0:
         print(json.dumps(res))
-    ok = same_across_ranks and status == 0 and stats["linear"] > 0 and stats["grouped"] > 0 and agree >= 0.5
+    ok = graph_same and same_across_ranks and status == 0 and stats["linear"] > 0 and stats["grouped"] > 0 and agree >= 0.5
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
