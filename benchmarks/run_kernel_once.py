@@ -251,8 +251,11 @@ def fp8_decode():
             ws.append((wq, sb))
         xq, sa = Fn.quantize_act_1x128(bf(M, K, scale=0.7))
         res = {}
-        for on in (0, 1):
-            lib.mfb_gemm_fp8_enable_ksplit(on)
+        for mode in ("tile", "split", "decode"):
+            # "tile": 128 token rows per tile, one CTA per tile; "split": the same with K split over a cluster;
+            # "decode": the weight on the MMA rows (gemm_fp8_decode.cu)
+            lib.mfb_gemm_fp8_enable_ksplit(0 if mode == "tile" else 1)
+            Fn._FP8_DECODE_KERNEL = mode == "decode"
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             for i in range(copies):
                 Fn.fp8_gemm(xq, sa, *ws[i])
@@ -268,15 +271,55 @@ def fp8_decode():
                 g.replay()
             ev[1].record()
             torch.cuda.synchronize()
-            res[on] = ev[0].elapsed_time(ev[1]) / (4 * copies)
+            res[mode] = ev[0].elapsed_time(ev[1]) / (4 * copies)
         lib.mfb_gemm_fp8_enable_ksplit(1)
-        ks = lib.mfb_gemm_fp8_ksplit(M, N, K, 0, N)
-        gbs = N * K / res[1] / 1e6
-        print(f"fp8 decode {M}x{N}x{K} ({what}): one CTA per tile {res[0] * 1e3:.1f} us, cluster split-K x{ks} "
-              f"{res[1] * 1e3:.1f} us = {gbs:.0f} GB/s of weights ({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
+        Fn._FP8_DECODE_KERNEL = True
+        gbs = N * K / res["decode"] / 1e6
+        print(f"fp8 decode {M}x{N}x{K} ({what}): 128-row tiles {res['tile'] * 1e3:.1f} us, with cluster split-K "
+              f"{res['split'] * 1e3:.1f} us, weight-on-rows kernel {res['decode'] * 1e3:.1f} us = {gbs:.0f} GB/s of weights "
+              f"({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
 
 
-CASES = dict(fp8=fp8, fp8_decode=fp8_decode, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+def fp8_moe_decode():
+    """Grouped fp8 GEMM at decode size: 32 experts of 4096 x 7168 (fc1 of a DeepSeek-V3 rank at ep 8), two tokens per
+    expert, against the 128-row-tile kernel. Two weight sets are cycled (0.94 GB each: nothing stays in L2)."""
+    G, N, K, per = int(os.environ.get("MFB_BENCH_EXPERTS", "32")), 4096, 7168, 2      # fewer experts for an ncu capture
+    sets = []
+    for _ in range(2):
+        wq = torch.empty(G, N, K, dtype=torch.float8_e4m3fn, device="cuda")
+        for g in range(G):
+            wq[g], _ = Fn.quantize_weight_128x128(torch.randn(N, K, device="cuda") * 0.05)
+        sb = torch.rand(G, N // 128, K // 128, device="cuda") * 1e-3 + 1e-4
+        sets.append((wq, sb))
+    T = G * 128
+    xq, sa = Fn.quantize_act_1x128(bf(T, K, scale=0.7))
+    bg = torch.arange(G, dtype=torch.int32, device="cuda")
+    nb = torch.tensor([G], dtype=torch.int32, device="cuda")
+    offs = (torch.arange(G + 1, dtype=torch.int32, device="cuda") * 128).contiguous()
+    fill = torch.full((G,), per, dtype=torch.int32, device="cuda")
+    res = {}
+    for mode in ("tile", "decode"):
+        kw = dict(block_group=bg, num_blocks=nb)
+        if mode == "decode":
+            kw.update(group_offsets=offs, seg_fill=fill)
+        for wq, sb in sets:
+            Fn.fp8_gemm(xq, sa, wq, sb, **kw)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(3):
+            for wq, sb in sets:
+                Fn.fp8_gemm(xq, sa, wq, sb, **kw)
+        ev[1].record()
+        torch.cuda.synchronize()
+        res[mode] = ev[0].elapsed_time(ev[1]) / 6
+    gbs = G * N * K / res["decode"] / 1e6
+    print(f"fp8 grouped decode {G} experts x {N}x{K}, {per} tokens each: 128-row tiles {res['tile'] * 1e3:.1f} us, "
+          f"weight-on-rows kernel {res['decode'] * 1e3:.1f} us = {gbs:.0f} GB/s of weights "
+          f"({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), status {_lib.read_status()}")
+
+
+CASES = dict(fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

@@ -70,6 +70,8 @@ def _declare(lib):
     sig("mfb_paged_decode_splits", [I, I, I, I])
     lib.mfb_paged_decode_scratch_bytes.argtypes = [I, I, I, I]
     lib.mfb_paged_decode_scratch_bytes.restype = L
+    sig("mfb_gemm_fp8_decode", [P, P, P, P, L, P, I, I, I, L, L, L, I, I, P, P, P, P, P, P])
+    sig("mfb_gemm_fp8_decode_supported", [I, I, I, I])
     lib.mfb_gemm_fp8_enable_ksplit.argtypes = [I]
     lib.mfb_gemm_fp8_enable_ksplit.restype = None
     sig("mfb_gemm_fp8_ksplit", [I, I, I, I, L])

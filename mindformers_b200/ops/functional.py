@@ -8,6 +8,7 @@ which is the library baseline the hand-written tcgen05 kernel is measured agains
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -675,9 +676,18 @@ def fp8_gemm_reference(xq, sa, wq, sb):
     return x.reshape(T, K) @ w.reshape(N, K).t()
 
 
-def fp8_gemm(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, *, block_group=None, num_blocks=None):
+FP8_DECODE_MAX_ROWS_PER_GROUP = 160     # grouped calls with at most this many (padded) rows per expert are "decode"
+_FP8_DECODE_KERNEL = os.environ.get("MFB_FP8_DECODE_KERNEL", "1") != "0"
+
+
+def fp8_gemm(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, *, block_group=None, num_blocks=None,
+             group_offsets=None, seg_fill=None):
     """``y [T, N] (bf16) = dequant(xq, sa) @ dequant(wq, sb)^T``. Grouped form: ``wq [G, N, K]``, ``sb [G, N/128, K/128]``,
-    rows of ``xq`` sorted by expert in 128-row blocks (``block_group`` / ``num_blocks`` as for ``grouped_gemm``)."""
+    rows of ``xq`` sorted by expert in 128-row blocks (``block_group`` / ``num_blocks`` as for ``grouped_gemm``).
+
+    Two kernels: ``gemm_fp8.cu`` (128 token rows per tile) and, for at most 64 tokens or for grouped calls with a
+    few rows per expert whose segment fill is known (``group_offsets`` / ``seg_fill`` of the expert plan),
+    ``gemm_fp8_decode.cu`` (the weight on the MMA rows, 32 or 64 tokens per tile)."""
     T, K = xq.shape
     grouped = wq.dim() == 3
     G = wq.shape[0] if grouped else 1
@@ -694,7 +704,20 @@ def fp8_gemm(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sb: torch.Ten
     out = torch.empty(T, N, dtype=torch.bfloat16, device=xq.device)
     st = _lib.status_word(xq.device)
     w2 = wq.reshape(G * N, K)
-    rc = _lib.get_lib().mfb_gemm_fp8_blockscaled(
+    lib = _lib.get_lib()
+    decode = _FP8_DECODE_KERNEL and sa.stride(0) % 4 == 0 and (
+        (not grouped and T <= 64) or
+        (grouped and group_offsets is not None and seg_fill is not None and T % 128 == 0
+         and T <= FP8_DECODE_MAX_ROWS_PER_GROUP * G))
+    if decode:
+        rc = lib.mfb_gemm_fp8_decode(
+            xq.data_ptr(), w2.data_ptr(), out.data_ptr(), sa.data_ptr(), sa.stride(0), sb.contiguous().data_ptr(), T, N, K,
+            xq.stride(0), w2.stride(0), out.stride(0), 1 if grouped else 0, G, _lib.ptr(block_group), _lib.ptr(num_blocks),
+            _lib.ptr(group_offsets), _lib.ptr(seg_fill), st.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "mfb_gemm_fp8_decode")
+        _lib.count_launch()
+        return out
+    rc = lib.mfb_gemm_fp8_blockscaled(
         xq.data_ptr(), w2.data_ptr(), out.data_ptr(), sa.data_ptr(), sa.stride(0), sb.contiguous().data_ptr(), T, N, K,
         xq.stride(0), w2.stride(0), out.stride(0), 1 if grouped else 0, G, _lib.ptr(block_group), _lib.ptr(num_blocks),
         st.data_ptr(), _lib.stream_ptr())

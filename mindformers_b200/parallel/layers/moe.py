@@ -233,12 +233,14 @@ class GroupedMLP(nn.Module):
 
     def forward(self, x, plan: PermutePlan):
         if self.w1_fp8 is not None:
+            # with the segment fill of the plan a call with few rows per expert (decode) takes the kernel that puts
+            # the weights on the MMA rows and only the rows in use on the columns
+            kw = dict(block_group=plan.block_group, num_blocks=plan.num_blocks,
+                      group_offsets=getattr(plan, "group_offsets", None), seg_fill=getattr(plan, "seg_fill", None))
             xq, sa = Fn.quantize_act_1x128(x)
-            h = Fn.fp8_gemm(xq, sa, self.w1_fp8, self.w1_scale_inv, block_group=plan.block_group,
-                            num_blocks=plan.num_blocks)
+            h = Fn.fp8_gemm(xq, sa, self.w1_fp8, self.w1_scale_inv, **kw)
             hq, sh = Fn.quantize_act_1x128(Fn.swiglu(h))
-            return Fn.fp8_gemm(hq, sh, self.w2_fp8, self.w2_scale_inv, block_group=plan.block_group,
-                               num_blocks=plan.num_blocks)
+            return Fn.fp8_gemm(hq, sh, self.w2_fp8, self.w2_scale_inv, **kw)
         h = apply_fn(_GroupedLinearFn, x, self.weight1, plan.block_group, plan.num_blocks, plan.group_offsets)
         h = Fn.swiglu(h)
         return apply_fn(_GroupedLinearFn, h, self.weight2, plan.block_group, plan.num_blocks, plan.group_offsets)

@@ -421,8 +421,11 @@ def test_mla_decode_attention(nh, block, variant):
 
 
 @pytest.mark.parametrize("T,N,K", [(128, 128, 128), (300, 512, 1024), (4096, 2048, 7168),
-                                   # one row block and few column tiles: K split over a cluster of 8, 4, 2, 4 CTAs
-                                   (64, 1536, 7168), (64, 3072, 1536), (17, 7168, 2048), (128, 4608, 7168), (1, 256, 512)])
+                                   # up to 64 tokens: the kernel with the weight on the MMA rows (32 / 64 token
+                                   # columns), K split over a cluster of 8, 4, 2 CTAs or not at all
+                                   (64, 1536, 7168), (64, 3072, 1536), (17, 7168, 2048), (1, 256, 512), (33, 24576, 256),
+                                   # 65 - 128 tokens: 128-row tiles, K split over a cluster of 8, 2, 4 CTAs
+                                   (100, 1536, 7168), (128, 7168, 2048), (128, 4608, 7168)])
 def test_fp8_blockscaled_gemm_dense(T, N, K):
     torch.manual_seed(T + N)
     x = (torch.randn(T, K, device="cuda") * 0.7).to(torch.bfloat16)
@@ -461,6 +464,21 @@ def test_fp8_blockscaled_gemm_grouped():
         ref = Fn.fp8_gemm_reference(xq[rows], sa[:, rows], wq[g], sb[g])
         assert (y[rows].float() - ref).norm() / ref.norm() < 5e-3, i
     assert _lib.read_status() == 0
+    # the same call with the segment fill known: only the rows in use are computed (few-rows-per-expert kernel)
+    fill = [200, 0, 3, 290]                # rows in use of every expert: blocks 0-1, -, 2, 3-5
+    offs = torch.tensor([0, 256, 256, 384, 768], dtype=torch.int32, device="cuda")
+    limit, Fn.FP8_DECODE_MAX_ROWS_PER_GROUP = Fn.FP8_DECODE_MAX_ROWS_PER_GROUP, 1 << 20
+    try:
+        y2 = Fn.fp8_gemm(xq_pad, sa_pad, wq, sb, block_group=bg, num_blocks=nb, group_offsets=offs,
+                         seg_fill=torch.tensor(fill, dtype=torch.int32, device="cuda"))
+    finally:
+        Fn.FP8_DECODE_MAX_ROWS_PER_GROUP = limit
+    for g, n in enumerate(fill):
+        if n:
+            rows = slice(int(offs[g]), int(offs[g]) + n)
+            ref = Fn.fp8_gemm_reference(xq[rows], sa[:, rows], wq[g], sb[g])
+            assert (y2[rows].float() - ref).norm() / ref.norm() < 5e-3, g
+    assert _lib.read_status() == 0
 
 
 def test_bounded_peer_wait_reports_status_instead_of_hanging():
@@ -476,11 +494,13 @@ def test_bounded_peer_wait_reports_status_instead_of_hanging():
     st = _lib.status_word("cuda")
     st.zero_()
     t0 = time.time()
-    rc = lib.mfb_moe_barrier(2, 0, 1, 1, flags, st.data_ptr(), _lib.stream_ptr())
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")      # the kernel takes epoch + 1 and stores it back
+    rc = lib.mfb_moe_barrier(2, 0, epoch.data_ptr(), 1, flags, st.data_ptr(), _lib.stream_ptr())
     assert rc == 0
     torch.cuda.synchronize()
     waited = time.time() - t0
     assert int(st.item()) == 4                   # kStatusPeerFlagTimeout
+    assert int(epoch.item()) == 1
     assert 1.0 < waited < 10.0
     st.zero_()
     assert torch.ones(4, device="cuda").sum().item() == 4.0     # the device still answers
