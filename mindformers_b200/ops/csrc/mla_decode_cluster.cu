@@ -9,13 +9,14 @@
 //   so each keeps TWO tiles resident (double buffer) and the cache is read from HBM exactly once;
 //   each computes the part of S^T = C . Q^T that its columns contribute (a partial sum over K);
 //   the softmax threads exchange the 128 x 16 partials through distributed shared memory (each thread writes its
-//   row into the peer's exchange buffer and arrives on the peer's mbarrier), add them, and both CTAs run the same
-//   softmax on the same numbers;
+//   row into the peer's exchange buffer with st.async, which counts the bytes on the peer's mbarrier), add them,
+//   and both CTAs run the same softmax on the same numbers;
 //   each accumulates O^T for its own 256 latent rows from the columns it already holds.
 //
-// Per tile and SM that is 36 (CTA 0) or 32 (CTA 1) narrow MMAs instead of 68, one pass over the cache instead of two,
-// and the S^T products of tile j + 1 are issued before the O^T products of tile j, so they run while the softmax
-// threads (and the exchange) work on tile j.
+// Per tile and SM that is 36 (CTA 0) or 32 (CTA 1) narrow MMAs instead of 68 and one pass over the cache instead of
+// two; the S^T products of tile j + 1 are issued before the O^T products of tile j when their data has arrived.
+// Measured slower than the single-CTA kernel (two tile buffers cannot cover the load latency), so it is a selectable
+// variant, not the default.
 //
 // No TMA load here is a cluster-wide broadcast: every CTA loads its own columns into its own shared memory.
 // Cross-CTA traffic is the 64-byte st.async rows. Every wait is bounded; both CTAs of a
