@@ -100,3 +100,34 @@ def test_loss_scale_rng_and_sequence_split():
         assert torch.equal(torch.rand(3), a)
     parts = SequenceSplit(4).split({"input_ids": torch.arange(32).view(2, 16), "labels": torch.arange(32).view(2, 16)})
     assert len(parts) == 4 and parts[2]["input_ids"].shape == (2, 4) and parts[2]["position_ids"][0, 0] == 8
+
+
+def test_apply_fn_runs_forward_directly_without_gradients():
+    """With gradients off an autograd Function's forward runs as a plain call on a throw-away context; with gradients
+    on it goes through ``Function.apply`` and differentiates as usual."""
+    import torch
+    from mindformers_b200.ops.functional import apply_fn
+
+    class Scale(torch.autograd.Function):
+        calls = []
+
+        @staticmethod
+        def forward(ctx, x, k):
+            Scale.calls.append(type(ctx).__name__)
+            ctx.save_for_backward(x)
+            ctx.k = k
+            ctx.mark_non_differentiable()
+            return x * k
+
+        @staticmethod
+        def backward(ctx, g):
+            return g * ctx.k, None
+
+    x = torch.arange(4.0, requires_grad=True)
+    y = apply_fn(Scale, x, 3.0)
+    y.sum().backward()
+    assert torch.equal(x.grad, torch.full((4,), 3.0))
+    with torch.no_grad():
+        z = apply_fn(Scale, x, 3.0)
+    assert torch.equal(z, y.detach()) and not z.requires_grad
+    assert Scale.calls[0] != "_NoGradCtx" and Scale.calls[1] == "_NoGradCtx"
