@@ -1,0 +1,35 @@
+"""Weight initialisers of the parallel layers.
+
+Reference: ``parallel_core/utils/init_method.py`` (:27-50): ``init_method_normal(sigma)``,
+``scaled_init_method_normal(sigma, num_layers)`` = N(0, sigma / sqrt(2 L)) for the layers that write into the residual
+stream (attention output projection and the second MLP matrix), and zeros. Each returns a function that fills a tensor
+in place and returns it, which is what the layers' ``init_method`` arguments take.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable
+
+import torch
+import torch.nn as nn
+
+
+def init_method_normal(sigma: float = 0.02) -> Callable[[torch.Tensor], torch.Tensor]:
+    def init_(tensor: torch.Tensor) -> torch.Tensor:
+        return nn.init.normal_(tensor, mean=0.0, std=sigma)
+    return init_
+
+
+def scaled_init_method_normal(sigma: float, num_layers: int) -> Callable[[torch.Tensor], torch.Tensor]:
+    """N(0, sigma / sqrt(2 * num_layers)): keeps the variance of the residual stream independent of the depth."""
+    std = sigma / math.sqrt(2.0 * max(int(num_layers), 1))
+
+    def init_(tensor: torch.Tensor) -> torch.Tensor:
+        return nn.init.normal_(tensor, mean=0.0, std=std)
+    return init_
+
+
+def init_method_zero() -> Callable[[torch.Tensor], torch.Tensor]:
+    def init_(tensor: torch.Tensor) -> torch.Tensor:
+        return nn.init.zeros_(tensor)
+    return init_

@@ -55,6 +55,10 @@ class CoreAttention(nn.Module):
         self.layer_number = layer_number
         hd = head_dim or config.kv_channels
         self.scale = softmax_scale if softmax_scale is not None else (config.softmax_scale or 1.0 / math.sqrt(hd))
+        self.unfused = None
+        if not getattr(config, "use_flash_attention", True):
+            from .dot_product_attention import DotProductAttention
+            self.unfused = DotProductAttention(config, layer_number, self.scale, hd)
 
     def forward(self, q, k, v, meta: AttnMeta):
         """q: [T, nq, d]; k: [T, nkv, d]; v: [T, nkv, dv] → [T, nq*dv]."""
@@ -72,6 +76,8 @@ class CoreAttention(nn.Module):
         elif meta.cu_seqlens is not None:
             from ..context_parallel import varlen_attention
             o = varlen_attention(q4, k4, v4, meta.cu_seqlens, self.scale)
+        elif self.unfused is not None:       # use_flash_attention=False: explicit mask + softmax
+            o = self.unfused(q4, k4, v4)
         else:
             o = Fn.attention(q4, k4, v4, causal=True, scale=self.scale)
         return o.reshape(T, -1)

@@ -325,14 +325,17 @@ class MoEAlltoAllTokenDispatcher:
 class MoELayer(nn.Module):
     """Router → dispatch → grouped experts → combine (+ shared experts). Returns ``(out, aux_loss)``."""
 
-    def __init__(self, config, layer_number: int = 1):
+    def __init__(self, config, layer_number: int = 1, submodules: Optional[dict] = None):
+        """``submodules`` (from a layer spec): classes for ``router``, ``experts`` and ``shared_experts``."""
         super().__init__()
         self.config = config
         self.layer_number = layer_number
+        sub = submodules or {}
         ep = ps.get_expert_model_parallel_world_size()
-        self.router = TopKRouter(config)
-        self.experts = GroupedMLP(config, config.num_moe_experts // ep)
-        self.shared_experts = SharedExpertMLP(config) if config.moe_shared_expert_intermediate_size else None
+        self.router = sub.get("router", TopKRouter)(config)
+        self.experts = sub.get("experts", GroupedMLP)(config, config.num_moe_experts // ep)
+        self.shared_experts = (sub.get("shared_experts", SharedExpertMLP)(config)
+                               if config.moe_shared_expert_intermediate_size else None)
         self.dispatcher = MoEAlltoAllTokenDispatcher(config)
 
     def _tp_sliced(self, hidden):

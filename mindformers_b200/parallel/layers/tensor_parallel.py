@@ -80,9 +80,8 @@ def _mark_tp(param, is_parallel, dim):
 
 
 def default_init(std=0.02):
-    def _f(t):
-        return nn.init.normal_(t, mean=0.0, std=std)
-    return _f
+    from ..init_method import init_method_normal
+    return init_method_normal(std)
 
 
 class VocabParallelEmbedding(nn.Module):

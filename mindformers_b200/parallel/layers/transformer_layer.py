@@ -10,35 +10,53 @@ pending sub-layer output and the residual stream and returns the same pair.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from dataclasses import dataclass
+from typing import Any, List, Optional
 
 import torch
 import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
 from .. import parallel_state as ps
-from .attention import AttnMeta, MLASelfAttention, SelfAttention
-from .mlp import MLP
+from ..spec_utils import build_module
+from .attention import AttnMeta
 from .moe import MoELayer
 from .norm import build_norm
 
 
+@dataclass
+class TransformerLayerSubmodules:
+    """What a layer is made of, as ``ModuleSpec`` entries (``gpt_layer_specs.py`` fills them in). Norm entries are
+    built with ``(config)``, the attention and an MoE ``mlp`` with ``(config, layer_number)``, a dense ``mlp`` with
+    ``(config)``; ``None`` for a post-norm leaves it out."""
+    input_layernorm: Any = None
+    self_attention: Any = None
+    pre_mlp_layernorm: Any = None
+    mlp: Any = None
+    post_attn_layernorm: Any = None
+    post_mlp_layernorm: Any = None
+
+
 class TransformerLayer(nn.Module):
-    def __init__(self, config, layer_number: int = 1, is_moe: bool = False):
+    def __init__(self, config, layer_number: int = 1, is_moe: bool = False,
+                 submodules: Optional[TransformerLayerSubmodules] = None):
         super().__init__()
         self.config = config
         self.layer_number = layer_number
-        self.input_layernorm = build_norm(config)
-        attn_cls = MLASelfAttention if config.multi_latent_attention else SelfAttention
-        self.self_attention = attn_cls(config, layer_number)
-        self.pre_mlp_layernorm = build_norm(config)
-        self.is_moe = is_moe
-        self.mlp = MoELayer(config, layer_number) if is_moe else MLP(config)
-        if config.sandwich_norm:
-            self.post_attn_layernorm = build_norm(config)
-            self.post_mlp_layernorm = build_norm(config)
-        else:
-            self.post_attn_layernorm = self.post_mlp_layernorm = None
+        if submodules is None:     # the layer that the configuration describes
+            from .gpt_layer_specs import get_gpt_layer_spec_for_config
+            submodules = get_gpt_layer_spec_for_config(config, is_moe).submodules
+        self.input_layernorm = build_module(submodules.input_layernorm, config)
+        self.self_attention = build_module(submodules.self_attention, config, layer_number)
+        self.pre_mlp_layernorm = build_module(submodules.pre_mlp_layernorm, config)
+        mlp_spec = submodules.mlp
+        mlp_cls = getattr(mlp_spec, "module", mlp_spec)
+        self.is_moe = isinstance(mlp_cls, type) and issubclass(mlp_cls, MoELayer)
+        self.mlp = build_module(mlp_spec, config, layer_number) if self.is_moe else build_module(mlp_spec, config)
+        self.post_attn_layernorm = (build_module(submodules.post_attn_layernorm, config)
+                                    if submodules.post_attn_layernorm is not None else None)
+        self.post_mlp_layernorm = (build_module(submodules.post_mlp_layernorm, config)
+                                   if submodules.post_mlp_layernorm is not None else None)
 
     def forward(self, pending, residual, rotary, meta: AttnMeta):
         """``pending``: sub-layer output not yet added to ``residual`` (``residual`` None for the first layer)."""
@@ -98,9 +116,9 @@ class TransformerBlock(nn.Module):
         vpp = config.virtual_pipeline_model_parallel_size or 1
         split = pipeline_layer_split(config.num_layers, pp, vpp, config.offset or 0)
         self.layer_ids = split[pp_rank][vp_stage or 0]
-        pattern = config.moe_layer_pattern()
-        self.layers = nn.ModuleList(
-            [TransformerLayer(config, layer_number=i + 1, is_moe=bool(pattern[i])) for i in self.layer_ids])
+        from .gpt_layer_specs import get_gpt_decoder_block_spec
+        layer_specs = get_gpt_decoder_block_spec(config)      # one spec per layer of the whole model
+        self.layers = nn.ModuleList([build_module(layer_specs[i], config, layer_number=i + 1) for i in self.layer_ids])
         self.final_layernorm = build_norm(config) if post_process else None
         self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
         self._recompute_layers = self._resolve_recompute(config.recompute)

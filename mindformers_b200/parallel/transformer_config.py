@@ -309,6 +309,14 @@ class TransformerConfig(ModelParallelConfig):
             self.output_layer_init_std = self.init_method_std / (2.0 * self.num_layers) ** 0.5
         else:
             self.output_layer_init_std = self.init_method_std
+        # the initialisers themselves, for callers that pass them on (parallel/init_method.py)
+        from .init_method import init_method_normal, scaled_init_method_normal
+        if self.init_method is None:
+            self.init_method = init_method_normal(self.init_method_std)
+        if self.output_layer_init_method is None:
+            self.output_layer_init_method = (scaled_init_method_normal(self.init_method_std, self.num_layers)
+                                             if self.use_scaled_init and self.num_layers
+                                             else init_method_normal(self.init_method_std))
 
     # -------------------------------------------------------------------------------------------
     @property

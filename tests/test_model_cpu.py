@@ -191,3 +191,66 @@ def test_hf_config_conversion():
         convert_to_transformer_config(dict(hf, num_layers=3))
     with pytest.raises(ValueError):
         convert_to_transformer_config(dict(hf, definitely_unknown_key=1))
+
+
+def test_layer_specs_describe_and_drive_the_layers():
+    """The decoder is built from layer specs: dense / MoE pattern, MLA switch, and a replaced sub-module class."""
+    from mindformers_b200.parallel.layers.attention import MLASelfAttention, SelfAttention
+    from mindformers_b200.parallel.layers.gpt_layer_specs import (get_gpt_decoder_block_spec, get_gpt_layer_local_spec,
+                                                                  get_gpt_mtp_block_spec)
+    from mindformers_b200.parallel.layers.mlp import MLP
+    from mindformers_b200.parallel.layers.moe import MoELayer
+    from mindformers_b200.parallel.layers.transformer_layer import TransformerLayer
+    from mindformers_b200.parallel.spec_utils import ModuleSpec, build_module
+
+    dense = get_gpt_layer_local_spec()
+    assert dense.module is TransformerLayer and dense.submodules.self_attention.module is SelfAttention
+    assert dense.submodules.mlp.module is MLP and dense.submodules.post_mlp_layernorm is None
+    moe = get_gpt_layer_local_spec(num_experts=8, multi_latent_attention=True, sandwich_norm=True)
+    assert moe.submodules.self_attention.module is MLASelfAttention and moe.submodules.mlp.module is MoELayer
+    assert moe.submodules.post_attn_layernorm is not None
+
+    cfg = tiny_llama_config(num_layers=3, num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=64,
+                            first_k_dense_replace=1)
+    specs = get_gpt_decoder_block_spec(cfg)
+    assert [s.submodules.mlp.module is MoELayer for s in specs] == [False, True, True]
+    assert get_gpt_mtp_block_spec(cfg) is None
+    model = GPTModel(cfg)
+    assert [layer.is_moe for layer in model.decoder.layers] == [False, True, True]
+
+    class TaggedAttention(SelfAttention):
+        pass
+
+    spec = get_gpt_layer_local_spec()
+    spec.submodules.self_attention = ModuleSpec(module=TaggedAttention)
+    layer = build_module(spec, tiny_llama_config(), layer_number=1)
+    assert type(layer.self_attention) is TaggedAttention and not layer.is_moe
+    assert set(dict(layer.named_parameters())) == set(dict(TransformerLayer(tiny_llama_config()).named_parameters()))
+
+
+def test_unfused_attention_path_and_masks():
+    """``use_flash_attention=False`` goes through mask generation + scale-mask-softmax and gives the same loss; the
+    mask generator separates documents after a position reset and by cumulative segment ends."""
+    from mindformers_b200.parallel.layers.dot_product_attention import (CausalMaskGenerate, DotProductAttention,
+                                                                        FusedScaleMaskSoftmax, LowerTriangularMask)
+    torch.manual_seed(3)
+    ids = torch.randint(0, 1024, (2, 33))
+    a = GPTModel(tiny_llama_config())
+    b = GPTModel(tiny_llama_config(use_flash_attention=False))
+    b.load_state_dict(a.state_dict())
+    assert isinstance(b.decoder.layers[0].self_attention.core_attention.unfused, DotProductAttention)
+    la = a(ids[:, :-1].contiguous(), labels=ids[:, 1:].contiguous())
+    lb = b(ids[:, :-1].contiguous(), labels=ids[:, 1:].contiguous())
+    assert abs(float(la.detach()) - float(lb.detach())) < 1e-5
+    gen = CausalMaskGenerate(8)
+    pos = torch.tensor([[0, 1, 2, 0, 1, 0, 1, 2]])
+    m = gen(position_ids=pos)[0, 0]
+    assert not m[2, 0] and m[3, 2] and m[4, 2] and not m[4, 3] and m[0, 1] and m[7, 4] and not m[7, 5]
+    m2 = gen(position_ids=torch.arange(8).unsqueeze(0), actual_seq_len=torch.tensor([[3, 5, 8]]))[0, 0]
+    assert torch.equal(m, m2)
+    assert CausalMaskGenerate(8, compressed=True)().shape == (2048, 2048)
+    sm = FusedScaleMaskSoftmax(scale=0.5)
+    p = sm(torch.zeros(1, 1, 8, 8, dtype=torch.bfloat16), m)
+    assert p.dtype == torch.bfloat16 and abs(float(p[0, 0, 4].sum()) - 1) < 1e-2 and float(p[0, 0, 4, 2]) == 0.0
+    lt = LowerTriangularMask(torch.float32)
+    assert lt(True).shape == (128, 128) and lt(False).shape == (1, 1)

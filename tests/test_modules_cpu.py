@@ -131,3 +131,13 @@ def test_apply_fn_runs_forward_directly_without_gradients():
         z = apply_fn(Scale, x, 3.0)
     assert torch.equal(z, y.detach()) and not z.requires_grad
     assert Scale.calls[0] != "_NoGradCtx" and Scale.calls[1] == "_NoGradCtx"
+
+
+def test_init_methods():
+    import torch
+    from mindformers_b200.parallel.init_method import init_method_normal, init_method_zero, scaled_init_method_normal
+    torch.manual_seed(0)
+    a = init_method_normal(0.02)(torch.empty(512, 512))
+    b = scaled_init_method_normal(0.02, 8)(torch.empty(512, 512))
+    assert abs(a.std().item() - 0.02) < 1e-3 and abs(b.std().item() - 0.02 / 4.0) < 3e-4
+    assert init_method_zero()(torch.ones(3)).abs().sum() == 0
