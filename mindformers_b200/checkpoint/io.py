@@ -164,6 +164,11 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
     tensors (single files, plain directories, HF directories) are sliced by ``shard_for_param``.
     """
     kind, files = resolve_checkpoint(path)
+    if kind == "hf" and optimizer is None:
+        # a pretrained directory can be far larger than host memory: stream it layer by layer
+        from ..inference.weights_utils import load_weights
+        load_weights(model, path, family=family, strict=strict)
+        return {}
     sd = _read_files(files)
     if kind == "hf":
         sd = name_maps.hf_to_framework(sd, model.config, family)

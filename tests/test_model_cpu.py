@@ -254,3 +254,36 @@ def test_unfused_attention_path_and_masks():
     assert p.dtype == torch.bfloat16 and abs(float(p[0, 0, 4].sum()) - 1) < 1e-2 and float(p[0, 0, 4, 2]) == 0.0
     lt = LowerTriangularMask(torch.float32)
     assert lt(True).shape == (128, 128) and lt(False).shape == (1, 1)
+
+
+def test_weights_loader_streams_an_hf_directory_layer_by_layer(tmp_path):
+    """Sharded Hugging Face style directory → lazy index, row / column slices, and a layer-by-layer load that ends in
+    the same model (dense Llama and an MoE + MLA model)."""
+    from mindformers_b200.checkpoint.io import save_pretrained_dir
+    from mindformers_b200.inference.weights_utils import (WeightsLoader, infer_trans_rope_weight, load_weights,
+                                                          split_by_tp_rank_columns)
+    torch.manual_seed(5)
+    ids = torch.randint(0, 1024, (2, 17))
+    moe_cfg = dict(num_layers=3, num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=64, first_k_dense_replace=1,
+                   moe_shared_expert_intermediate_size=64)
+    for name, family, kw in (("llama", "llama", {}), ("moe", "qwen3_moe", moe_cfg)):
+        src = GPTModel(tiny_llama_config(**kw)).eval()
+        d = tmp_path / name
+        save_pretrained_dir(src, str(d), config_dict={"model_type": family}, max_shard_bytes=400_000, hf_names=True,
+                            family=family)
+        loader = WeightsLoader(str(d))
+        assert len(loader.files) > 2 and loader.has("model.embed_tokens.weight")
+        layers, other = loader.layer_groups()
+        assert sorted(layers) == list(range(src.config.num_layers)) and "model.norm.weight" in other
+        emb = loader.get("model.embed_tokens.weight")
+        assert torch.equal(loader.rows("model.embed_tokens.weight", 1, 4), emb[256:512])
+        assert torch.equal(split_by_tp_rank_columns(loader.get_slice("model.embed_tokens.weight"), 1, 2), emb[:, 128:])
+        dst = GPTModel(tiny_llama_config(**kw)).eval()
+        stats = load_weights(dst, str(d), family=family)
+        assert stats["layers"] == src.config.num_layers and not stats["missing"]
+        total = sum(p.numel() * 4 for p in src.parameters())
+        assert stats["peak_group_bytes"] < 0.7 * total              # never the whole model at once
+        with torch.no_grad():
+            assert torch.equal(src(ids), dst(ids))
+    w = torch.arange(12.0).reshape(6, 2)
+    assert infer_trans_rope_weight(w, 4)[:, 0].tolist() == [0.0, 2.0, 4.0, 8.0, 6.0, 10.0]
