@@ -57,6 +57,8 @@ class GenerationMixin:
         Returns logits ``[B, V]`` of the last new token of each sequence."""
         device = next(self.parameters()).device
         lens = [len(t) for t in tokens]
+        if hasattr(self, "set_phase"):
+            self.set_phase(prefill)
         if prefill:
             table, slots = tables.assemble_pa_full_inputs(lens, active)
         else:

@@ -17,13 +17,14 @@ import torch.nn as nn
 from ..checkpoint import io as ckpt_io
 from ..checkpoint import name_maps
 from ..generation import GenerationConfig, GenerationMixin
+from ..inference.model_utils import InferModelMixin
 from ..parallel.layers.gpt_model import GPTModel
 from ..parallel.transformer_config_utils import convert_to_transformer_config
 from ..tools.logger import logger
 from .configuration_utils import PretrainedConfig
 
 
-class PreTrainedModel(nn.Module, GenerationMixin):
+class PreTrainedModel(nn.Module, GenerationMixin, InferModelMixin):
     config_class = PretrainedConfig
     base_model_prefix = "model"
     weight_family = "llama"

@@ -287,3 +287,30 @@ def test_weights_loader_streams_an_hf_directory_layer_by_layer(tmp_path):
             assert torch.equal(src(ids), dst(ids))
     w = torch.arange(12.0).reshape(6, 2)
     assert infer_trans_rope_weight(w, 4)[:, 0].tolist() == [0.0, 2.0, 4.0, 8.0, 6.0, 10.0]
+
+
+def test_infer_model_mixin_names_strategy_and_name_map(tmp_path):
+    import json
+    from safetensors.torch import save_file
+    from mindformers_b200.inference.model_utils import (convert_net_name, generate_state_dict, save_strategy_file)
+    from mindformers_b200.models import AutoModel
+    assert convert_net_name("decoder.layers.0.self_attention.linear_k.weight") == \
+        "decoder.layers.0.self_attention.linear_qkv.weight"
+    assert convert_net_name("decoder.layers.3.mlp.experts.7.gating.weight") == "decoder.layers.3.mlp.experts.weight1"
+    assert convert_net_name("decoder.layers.3.mlp.router.weight.weight") == "decoder.layers.3.mlp.router.weight"
+    assert convert_net_name("decoder.final_layernorm.weight") == "decoder.final_layernorm.weight"
+    cfg = dict(model_type="llama", num_hidden_layers=1, hidden_size=64, num_attention_heads=2, num_key_value_heads=2,
+               intermediate_size=128, vocab_size=128, max_position_embeddings=64, params_dtype="float32")
+    model = AutoModel.from_config(cfg, device="cpu")
+    model.set_phase(False)
+    assert not model.is_prefill and model.convert_net_name("a.mlp.gating.weight") == "a.mlp.linear_fc1.weight"
+    state = generate_state_dict(model)
+    assert state["total_rank"] == 1 and state["model"]["decoder.final_layernorm.weight"]["shard"] == [1]
+    path = save_strategy_file(state, str(tmp_path / "strategy" / "ckpt_strategy_rank_0.json"))
+    assert json.load(open(path))["model"].keys() == state["model"].keys()
+    # a directory with foreign names + param_name_map.json
+    new_norm = torch.full((64,), 3.0)
+    save_file({"final.norm": new_norm}, str(tmp_path / "w.safetensors"))
+    json.dump({"final.norm": "decoder.final_layernorm.weight"}, open(tmp_path / "param_name_map.json", "w"))
+    res = model.load_weights_from_dir(str(tmp_path))
+    assert res["tensors"] == 1 and torch.equal(dict(model.named_parameters())["decoder.final_layernorm.weight"], new_norm)
