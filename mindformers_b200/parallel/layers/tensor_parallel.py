@@ -310,3 +310,89 @@ class LinearNoTP(_Fp8WeightMixin, nn.Module):
 
 
 ReplicatedLinear = LinearNoTP
+
+
+class ColumnParallelBatchedLinear(nn.Module):
+    """One column-parallel linear per expert, applied as a batched product: ``x [E_local, C, in]`` (the capacity-based
+    expert layout: C token slots per expert) times ``weight [E_local, out / etp, in]``. Experts are split over the
+    expert-parallel group (axis 0) and every expert's output rows over the expert-tensor-parallel group.
+
+    Reference: ``training_graph/tensor_parallel/batched_layers.py:29-226`` (``ColumnParallelBatchedLinear``)."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
+                 bias: bool = False, skip_bias_add: bool = False, is_expert: bool = True):
+        super().__init__()
+        if not is_expert or not config.num_moe_experts or config.num_moe_experts < 2:
+            raise ValueError("batched linears are expert layers: is_expert=True and num_moe_experts > 1 are required")
+        if bias:
+            raise ValueError("batched expert linears carry no bias")
+        ep, etp = ps.get_expert_model_parallel_world_size(), ps.get_expert_tensor_parallel_world_size()
+        E = config.num_moe_experts
+        if E % ep or output_size % etp:
+            raise ValueError(f"experts {E} / output rows {output_size} do not split over ep {ep} / etp {etp}")
+        self.config, self.num_local_experts = config, E // ep
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.init_method_std)
+        full = torch.empty(E, output_size, input_size, dtype=torch.float32, device=dev)
+        init(full)                                       # whole stack first: values do not depend on ep / etp
+        er, tr = ps.get_expert_model_parallel_rank(), ps.get_expert_tensor_parallel_rank()
+        local = full[er * self.num_local_experts:(er + 1) * self.num_local_experts]
+        local = local.chunk(etp, dim=1)[tr].contiguous()
+        self.weight = nn.Parameter(local.to(config.params_dtype))
+        self.weight.is_expert = True
+        _mark_tp(self.weight, etp > 1, 1)
+
+    def forward(self, x: torch.Tensor, weight: Optional[torch.Tensor] = None):
+        w = self.weight if weight is None else weight
+        y = torch.bmm(x.to(w.dtype), w.transpose(1, 2))
+        return y.to(x.dtype), None
+
+
+class RowParallelBatchedLinear(nn.Module):
+    """Per-expert row-parallel linear: ``x [E_local, C, in / etp]`` times ``weight [E_local, out, in / etp]``, partial
+    sums all-reduced over the expert-tensor-parallel group.
+
+    Reference: ``training_graph/tensor_parallel/batched_layers.py:228-399`` (``RowParallelBatchedLinear``)."""
+
+    def __init__(self, input_size: int, output_size: int, *, config, init_method: Callable = None,
+                 bias: bool = False, skip_bias_add: bool = False, is_expert: bool = True):
+        super().__init__()
+        if not is_expert or not config.num_moe_experts or config.num_moe_experts < 2:
+            raise ValueError("batched linears are expert layers: is_expert=True and num_moe_experts > 1 are required")
+        if bias:
+            raise ValueError("batched expert linears carry no bias")
+        ep, etp = ps.get_expert_model_parallel_world_size(), ps.get_expert_tensor_parallel_world_size()
+        E = config.num_moe_experts
+        if E % ep or input_size % etp:
+            raise ValueError(f"experts {E} / input columns {input_size} do not split over ep {ep} / etp {etp}")
+        self.config, self.num_local_experts, self.etp = config, E // ep, etp
+        dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        init = init_method or default_init(config.output_layer_init_std)
+        full = torch.empty(E, output_size, input_size, dtype=torch.float32, device=dev)
+        init(full)
+        er, tr = ps.get_expert_model_parallel_rank(), ps.get_expert_tensor_parallel_rank()
+        local = full[er * self.num_local_experts:(er + 1) * self.num_local_experts]
+        local = local.chunk(etp, dim=2)[tr].contiguous()
+        self.weight = nn.Parameter(local.to(config.params_dtype))
+        self.weight.is_expert = True
+        _mark_tp(self.weight, etp > 1, 2)
+
+    def forward(self, x: torch.Tensor):
+        y = torch.bmm(x.to(self.weight.dtype), self.weight.transpose(1, 2))
+        if self.etp > 1:
+            y = _AllReduceSum.apply(y, ps.get_expert_tensor_parallel_group())
+        return y.to(x.dtype), None
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """Sum over a group in forward, identity in backward (every rank holds the full gradient of the sum)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        torch.distributed.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None

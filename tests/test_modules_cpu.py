@@ -141,3 +141,27 @@ def test_init_methods():
     b = scaled_init_method_normal(0.02, 8)(torch.empty(512, 512))
     assert abs(a.std().item() - 0.02) < 1e-3 and abs(b.std().item() - 0.02 / 4.0) < 3e-4
     assert init_method_zero()(torch.ones(3)).abs().sum() == 0
+
+
+def test_batched_expert_linears_match_a_per_expert_loop():
+    import torch
+    from mindformers_b200.parallel.layers.tensor_parallel import ColumnParallelBatchedLinear, RowParallelBatchedLinear
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=2, ffn_hidden_size=64, vocab_size=64,
+                            num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=48, params_dtype="float32",
+                            compute_dtype="float32")
+    cfg.device = "cpu"
+    torch.manual_seed(0)
+    up = ColumnParallelBatchedLinear(32, 48, config=cfg)
+    down = RowParallelBatchedLinear(48, 32, config=cfg)
+    assert up.weight.shape == (4, 48, 32) and down.weight.shape == (4, 32, 48) and up.weight.is_expert
+    x = torch.randn(4, 5, 32, requires_grad=True)
+    h, _ = up(x)
+    y, _ = down(torch.nn.functional.silu(h))
+    ref = torch.stack([torch.nn.functional.silu(x[e] @ up.weight[e].t()) @ down.weight[e].t() for e in range(4)])
+    assert torch.allclose(y, ref, atol=1e-5)
+    y.sum().backward()
+    assert x.grad is not None and up.weight.grad.shape == up.weight.shape
+    import pytest
+    with pytest.raises(ValueError):
+        ColumnParallelBatchedLinear(32, 48, config=cfg, is_expert=False)
