@@ -17,6 +17,7 @@ from ..inference.block_manager import BlockTables
 from ..inference.paged_attention import KVCacheContext
 from ..parallel import parallel_state as ps
 from ..parallel.layers.attention import AttnMeta
+from ..tools.debug_info import DetailedLatency, Profiling
 from ..tools.logger import logger
 from .beam_search import BeamSearchScorer
 from .generation_config import GenerationConfig
@@ -196,6 +197,12 @@ class GenerationMixin:
         eos = set(gcfg.eos_ids())
         ctx, tables = self._set_kv_cache(B, max_len, getattr(self.config, "num_blocks", None))
         tables.init_cache_engine(B)
+        # latency breakdown (``self.detailed_latency.enabled`` or MF_DETAILED_LATENCY=1) and a profiler window over
+        # token indices (MF_PROFILE_START_TOKEN / MF_PROFILE_STOP_TOKEN), tools/debug_info.py
+        latency = getattr(self, "detailed_latency", None)
+        if latency is None:
+            latency = self.detailed_latency = DetailedLatency()
+        profiling = Profiling()
         seqs = [list(p) for p in prompts]
         finished = [False] * B
         t0 = time.time()
@@ -218,12 +225,17 @@ class GenerationMixin:
                         logits[i] = step_logits[j]
                 done = [d + len(t) for d, t in zip(done, toks)]
         else:
-            logits = self._forward_step(seqs, [0] * B, ctx, tables, True)
+            profiling.step_begin(0)
+            with latency.phase("predict", True):
+                logits = self._forward_step(seqs, [0] * B, ctx, tables, True)
+            profiling.step_end(0)
         ttft = time.time() - t0
         new_tokens = 0
         graph_step = self._graph_decoder(B, ctx, tables) if getattr(gcfg, "use_cuda_graph", False) else None
+        step_index = 0
         while True:
-            nxt = self._select(seqs, logits, processors, warper, gen, gcfg)
+            with latency.phase("postprocess", step_index == 0):
+                nxt = self._select(seqs, logits, processors, warper, gen, gcfg)
             for i in range(B):
                 if finished[i]:
                     continue
@@ -237,12 +249,21 @@ class GenerationMixin:
                 streamer.put([int(nxt[0])] if B == 1 else [[int(t)] for t in nxt])
             if all(finished):
                 break
-            act = [not f for f in finished]
-            toks = [[s[-1]] for s in seqs]
-            if graph_step is not None:
-                logits = graph_step(toks, [len(s) - 1 for s in seqs], act)
-            else:
-                logits = self._forward_step(toks, [len(s) - 1 for s in seqs], ctx, tables, False, act)
+            with latency.phase("preprocess", False):
+                act = [not f for f in finished]
+                toks = [[s[-1]] for s in seqs]
+                starts = [len(s) - 1 for s in seqs]
+            step_index += 1
+            profiling.step_begin(step_index)
+            with latency.phase("predict", False):
+                if graph_step is not None:
+                    logits = graph_step(toks, starts, act)
+                else:
+                    logits = self._forward_step(toks, starts, ctx, tables, False, act)
+            profiling.step_end(step_index)
+        profiling.close()
+        if latency.enabled:
+            latency.print_info()
         if streamer is not None:
             streamer.end()
         tables.clear_cache()

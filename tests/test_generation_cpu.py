@@ -98,3 +98,32 @@ def test_parallel_decoding_matches_greedy():
     want = model.generate([a, b], max_new_tokens=5, do_sample=False)
     got = model.generate([a, b], max_new_tokens=5, do_sample=False, parallel_decoding="prefix_cache")
     assert got == want and model.last_generation_stats["shared_prefix_tokens"] == 8
+
+
+def test_detailed_latency_and_token_window_profiling(monkeypatch):
+    """Phase timers of generate() and the profiler window opened / closed at token indices."""
+    from mindformers_b200.generation import text_generator
+    from mindformers_b200.tools.debug_info import DetailedLatency, Profiling
+    model = _tiny()
+    model.detailed_latency = DetailedLatency(enabled=True)
+    events = []
+
+    class FakeProf:
+        def __enter__(self):
+            events.append("start")
+
+        def __exit__(self, *a):
+            events.append("stop")
+
+    monkeypatch.setattr(text_generator, "Profiling", lambda: Profiling(start=2, stop=3, profiler_factory=FakeProf))
+    out = model.generate([[5, 6, 7, 8]], max_new_tokens=6, do_sample=False, eos_token_id=None)
+    assert len(out[0]) == 10
+    s = model.detailed_latency.summary()
+    assert s["prefill"]["predict"]["count"] == 1 and s["decode"]["predict"]["count"] == 5
+    assert s["decode"]["preprocess"]["count"] == 5 and s["decode"]["postprocess"]["count"] == 5
+    assert s["decode"]["predict"]["mean_ms"] > 0
+    assert events == ["start", "stop"]
+    p = Profiling(start=1, stop=50, profiler_factory=FakeProf)       # generation ends inside the window
+    p.step_begin(1)
+    p.close()
+    assert p.windows == 1 and not Profiling().enabled
