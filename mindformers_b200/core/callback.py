@@ -445,9 +445,13 @@ class TopkBiasBalanceCallback(Callback):
     ``balance_via_topk_bias``' update rate and logs the per-layer load (:2241-2337)."""
 
     def __init__(self, balance_via_topk_bias: bool = False, topk_bias_update_rate: float = 0.0, expert_num: int = 0,
-                 micro_batch_num: int = 1, gradient_accumulation_steps: int = 1, tensorboard_writer=None, **kwargs):
+                 micro_batch_num: int = 1, gradient_accumulation_steps: int = 1, tensorboard_writer=None,
+                 dump_dir: Optional[str] = None, **kwargs):
         self.enabled, self.tb = balance_via_topk_bias, tensorboard_writer
         self.loads: List[Dict[str, List[float]]] = []
+        # ``dump_dir``: one ``layer-<L>-step<N>.npy`` per MoE layer and step, the input of
+        # ``tools/moe_token_distribution_tools.py``
+        self.dump_dir = dump_dir
 
     def on_step_end(self, ctx):
         model = getattr(ctx.engine, "model", None)
@@ -463,6 +467,14 @@ class TopkBiasBalanceCallback(Callback):
                         self.tb.add_scalar(f"expert_load/{n}/{e}", v, ctx.global_step)
         if snap:
             self.loads.append(snap)
+            if self.dump_dir:
+                import numpy as np
+                os.makedirs(self.dump_dir, exist_ok=True)
+                for idx, name in enumerate(sorted(snap)):
+                    m = re.search(r"layers\.(\d+)\.", name)
+                    layer = int(m.group(1)) if m else idx
+                    np.save(os.path.join(self.dump_dir, f"layer-{layer}-step{ctx.global_step}.npy"),
+                            np.asarray(snap[name], dtype=np.float32))
         if self.enabled and hasattr(model, "update_topk_bias"):
             model.update_topk_bias()
 
@@ -546,6 +558,83 @@ class StressDetectCallBack(Callback):
             if not ok:
                 raise RuntimeError(f"stress detection found inconsistent results at step {ctx.global_step}")
             logger.info("stress detection passed at step %d", ctx.global_step)
+
+
+@_reg
+class StressTestModelMonitor(Callback):
+    """Every ``interval_steps`` the training pauses and each rank trains a small fixed model for a few steps on fixed
+    data; the per-step losses and the final gradient norm must agree on all ranks (same seed, same arithmetic), and a
+    rank that deviates by more than ``compare_interval_steps``-step tolerance is reported as a hardware suspect.
+
+    The reference spawns a side training job from a model directory and greps its logs for the global norm and loss of
+    every rank (``callback.py:2408-2700``); here the side job runs in process on the rank's own device, which tests the
+    same thing — the GEMM / attention / optimizer path of this GPU against the other GPUs — without a second launcher.
+    ``stress_model_dir`` / ``stress_dataset_dir`` / ``stress_master_port`` are accepted for configuration parity."""
+
+    def __init__(self, interval_steps: int = 10, stress_model_dir: Optional[str] = None,
+                 stress_dataset_dir: Optional[str] = None, stress_master_port: int = 8338,
+                 compare_interval_steps: Optional[int] = None, check_stresslog_interval_time: int = 60,
+                 stress_steps: int = 4, hidden_size: int = 256, tolerance: float = 0.0, **kwargs):
+        self.interval, self.steps, self.hidden, self.tol = interval_steps, max(1, stress_steps), hidden_size, tolerance
+        self.model_dir, self.dataset_dir = stress_model_dir, stress_dataset_dir
+        self.reports: List[dict] = []
+
+    def run_stress_job(self) -> torch.Tensor:
+        """Losses of the fixed job followed by the last gradient norm: ``[steps + 1]`` fp32 on the CPU."""
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        dtype = torch.bfloat16 if dev == "cuda" else torch.float32
+        state = torch.get_rng_state()
+        cuda_state = torch.cuda.get_rng_state() if dev == "cuda" else None
+        try:
+            g = torch.Generator(device="cpu").manual_seed(20240229)
+            H = self.hidden
+            w1 = (torch.randn(H, 4 * H, generator=g) * 0.02).to(dev, dtype).requires_grad_(True)
+            w2 = (torch.randn(4 * H, H, generator=g) * 0.02).to(dev, dtype).requires_grad_(True)
+            x = torch.randn(512, H, generator=g).to(dev, dtype)
+            y = torch.randn(512, H, generator=g).to(dev, dtype)
+            out = []
+            norm = torch.zeros(())
+            for _ in range(self.steps):
+                loss = ((torch.nn.functional.silu(x @ w1) @ w2 - y).float() ** 2).mean()
+                gw1, gw2 = torch.autograd.grad(loss, (w1, w2))
+                norm = (gw1.float().pow(2).sum() + gw2.float().pow(2).sum()).sqrt()
+                with torch.no_grad():
+                    w1 -= 0.1 * gw1
+                    w2 -= 0.1 * gw2
+                out.append(loss.detach().float().cpu())
+            out.append(norm.detach().float().cpu())
+            return torch.stack(out)
+        finally:
+            torch.set_rng_state(state)
+            if cuda_state is not None:
+                torch.cuda.set_rng_state(cuda_state)
+
+    def compare(self, mine: torch.Tensor) -> dict:
+        """All-gather the results; ``{"ok", "max_spread", "suspects": [ranks that differ from the median]}``."""
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+            return {"ok": bool(torch.isfinite(mine).all()), "max_spread": 0.0, "suspects": []}
+        dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+        rows = [torch.empty_like(mine, device=dev) for _ in range(dist.get_world_size())]
+        dist.all_gather(rows, mine.to(dev))
+        table = torch.stack(rows).cpu()
+        med = table.median(dim=0).values
+        dev_per_rank = (table - med).abs().max(dim=1).values
+        suspects = [r for r, d in enumerate(dev_per_rank.tolist()) if d > self.tol or d != d]
+        return {"ok": not suspects, "max_spread": float(dev_per_rank.max()), "suspects": suspects}
+
+    def on_step_end(self, ctx):
+        if not self.interval or ctx.global_step % self.interval:
+            return
+        report = self.compare(self.run_stress_job())
+        report["step"] = ctx.global_step
+        self.reports.append(report)
+        if report["ok"]:
+            logger.info("stress test at step %d: all ranks agree", ctx.global_step)
+        else:
+            logger.error("stress test at step %d: ranks %s deviate (max spread %.3e)", ctx.global_step,
+                         report["suspects"], report["max_spread"])
+            raise RuntimeError(f"stress test found deviating ranks {report['suspects']} at step {ctx.global_step}")
 
 
 @_reg

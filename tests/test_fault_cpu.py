@@ -54,3 +54,10 @@ def test_heartbeat_with_hash_store():
     with pytest.raises(RankFailure):
         a.check()
     a.stop()
+
+
+def test_stress_test_monitor_names_the_deviating_rank():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", str(_port()), os.path.join(ROOT, "tests", "dist", "run_stress_monitor.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stderr[-2000:]

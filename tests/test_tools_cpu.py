@@ -68,3 +68,52 @@ def test_glm4_preprocess(tmp_path):
     assert sample["input_ids"][:2] == tok.get_prefix_tokens() and len(sample["labels"]) == 64
     text = tok.decode([l for l in sample["labels"] if l != -100])
     assert "cat" in text and "Translate" not in text
+
+
+def test_moe_token_distribution_reports(tmp_path):
+    import os
+    """Expert-load dumps of a callback → merged tables, balance statistics and a chart per layer."""
+    import json
+    import numpy as np
+    import torch
+    from mindformers_b200.core.callback import RunContext, TopkBiasBalanceCallback
+    from mindformers_b200.tools import moe_token_distribution_tools as tool
+
+    class Router(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.expert_load = torch.zeros(8)
+
+    model = torch.nn.Module()
+    model.decoder = torch.nn.Module()
+    model.decoder.layers = torch.nn.ModuleList([torch.nn.Module() for _ in range(3)])
+    for i in (1, 2):
+        model.decoder.layers[i].router = Router()
+
+    class Engine:
+        pass
+
+    eng = Engine()
+    eng.model = model
+    cb = TopkBiasBalanceCallback(dump_dir=str(tmp_path / "dump"))
+    for step in range(1, 6):
+        model.decoder.layers[1].router.expert_load = torch.tensor([step, 1, 1, 1, 1, 1, 1, 0.0])    # expert 0 heats up
+        model.decoder.layers[2].router.expert_load = torch.ones(8)
+        cb.on_step_end(RunContext(engine=eng, global_step=step))
+    files = tool.collect_npy_files(str(tmp_path / "dump"))
+    assert sorted(files) == [1, 2] and len(files[1]) == 5 and files[1][0].endswith("layer-1-step1.npy")
+    table = tool.merge_npy_files(files[1])
+    assert table.shape == (5, 8) and table[4, 0] == 5
+    reports = tool.generate_reports(str(tmp_path / "dump"), str(tmp_path / "charts") + "/", hot_expert_num=2)
+    hot = reports[1]
+    assert hot["hot_experts"][0] == 0 and hot["idle_experts"] == [7] and hot["cold_experts"][0] == 7
+    assert hot["max_over_mean"]["last"] > hot["max_over_mean"]["first"] > 1.0
+    even = reports[2]
+    assert abs(even["max_over_mean"]["worst"] - 1.0) < 1e-9 and even["coefficient_of_variation"]["mean"] < 1e-9
+    svg = open(tmp_path / "charts" / "layer-1.svg").read()
+    assert svg.startswith("<svg") and svg.count("<rect") == 5 * 8
+    assert json.load(open(tmp_path / "charts" / "layer-2.json"))["experts"] == 8
+    assert np.loadtxt(tmp_path / "charts" / "layer-1.csv", delimiter=",").shape == (5, 8)
+    tool.main(["--npy_files_load_path", str(tmp_path / "dump"), "--save_path_prefix", str(tmp_path / "c2") + "/",
+               "--num_layers", "2"])
+    assert os.path.exists(tmp_path / "c2" / "layer-1.svg") and not os.path.exists(tmp_path / "c2" / "layer-2.svg")
