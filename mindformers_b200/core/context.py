@@ -55,12 +55,47 @@ class Context:
         self._set_device(ctx)
         self._set_determinism(cfg)
         self._set_affinity()
+        self.parallel_speed_up = self._load_parallel_speed_up(cfg, ctx)
         self.set_seed(self.seed)
         self.rank, self.world_size = 0, 1
         if self.use_parallel:
             self.init_communication(par)
 
     # ----------------------------------------------------------------------------------------------
+    # keys of a ``parallel_speed_up.json`` that have a counterpart here: overlap of a GEMM with its collective is what
+    # the fused kernels do, so these switch them on (model_config keys) unless the YAML already says otherwise
+    _SPEED_UP_MAP = {"matmul_grad_comm_overlap": "fused_tp_comm", "enable_grad_comm_opt": "fused_tp_comm",
+                     "enable_opt_shard_comm_opt": "fused_tp_comm", "compute_communicate_fusion_level": "fused_tp_comm",
+                     "enable_concat_eliminate_opt": None, "enable_begin_end_inline_opt": None,
+                     "dataset_broadcast_opt_level": None, "recompute_comm_overlap": None}
+
+    def _load_parallel_speed_up(self, cfg, ctx) -> dict:
+        """``context.ascend_config.parallel_speed_up_json_path`` (reference ``configs/qwen3/parallel_speed_up.json``,
+        ``research/qwen2_5/parallel_speed_up_72B_32K.json``): graph-compiler knobs of the reference's backend. Those
+        that mean "overlap this GEMM with its collective" select the fused communication kernels; the others have
+        nothing to steer here and are listed as ignored."""
+        path = (ctx.get("ascend_config") or {}).get("parallel_speed_up_json_path") or ctx.get("parallel_speed_up_json_path")
+        out = {"path": path, "applied": {}, "ignored": []}
+        if not path:
+            return out
+        if not os.path.exists(path):
+            logger.warning("parallel_speed_up_json_path %s does not exist; ignored", path)
+            return out
+        import json
+        with open(path) as f:
+            knobs = json.load(f)
+        model_cfg = ((cfg.get("model") or {}).get("model_config")) if hasattr(cfg, "get") else None
+        for key, value in knobs.items():
+            target = self._SPEED_UP_MAP.get(key)
+            if target and value:
+                out["applied"][key] = target
+                if model_cfg is not None and model_cfg.get(target) is None:
+                    model_cfg[target] = True
+            else:
+                out["ignored"].append(key)
+        logger.info("parallel_speed_up: applied %s, ignored %s", out["applied"], out["ignored"])
+        return out
+
     def _set_device(self, ctx):
         if torch.cuda.is_available() and self.device_target not in ("CPU",):
             torch.cuda.set_device(self.local_rank % torch.cuda.device_count())

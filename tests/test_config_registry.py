@@ -166,3 +166,19 @@ def test_top_level_api_surface():
     from mindformers_b200.core import AdamW, CosineWithWarmUpLR, CrossEntropyLoss, MFLossMonitor, PerplexityMetric  # noqa: F401
     from mindformers_b200.wrapper import MFTrainOneStepCell
     assert MFTrainOneStepCell.__name__ == "TrainOneStep"
+
+
+def test_context_reads_parallel_speed_up_json(tmp_path):
+    """Graph-compiler knobs of the reference's backend: the overlap ones select the fused kernels, the rest is listed."""
+    import json
+    from mindformers_b200.core.context import Context
+    path = tmp_path / "parallel_speed_up.json"
+    json.dump({"matmul_grad_comm_overlap": True, "dataset_broadcast_opt_level": 3, "enable_grad_comm_opt": False,
+               "some_future_knob": 1}, open(path, "w"))
+    cfg = {"context": {"device_target": "CPU", "ascend_config": {"parallel_speed_up_json_path": str(path)}},
+           "model": {"model_config": {"hidden_size": 8}}}
+    ctx = Context(cfg)
+    assert ctx.parallel_speed_up["applied"] == {"matmul_grad_comm_overlap": "fused_tp_comm"}
+    assert set(ctx.parallel_speed_up["ignored"]) == {"dataset_broadcast_opt_level", "enable_grad_comm_opt", "some_future_knob"}
+    assert cfg["model"]["model_config"]["fused_tp_comm"] is True
+    assert Context({"context": {"device_target": "CPU"}}).parallel_speed_up["path"] is None
