@@ -231,6 +231,10 @@ class GenerationMixin:
             profiling.step_end(0)
         ttft = time.time() - t0
         new_tokens = 0
+        lockstep_group = None
+        if ps.get_expert_model_parallel_world_size() > ps.get_tensor_model_parallel_world_size() \
+                and torch.distributed.is_available() and torch.distributed.is_initialized():
+            lockstep_group = ps.get_expert_model_parallel_group()
         graph_step = self._graph_decoder(B, ctx, tables) if getattr(gcfg, "use_cuda_graph", False) else None
         step_index = 0
         while True:
@@ -247,7 +251,15 @@ class GenerationMixin:
                     finished[i] = True
             if streamer is not None:
                 streamer.put([int(nxt[0])] if B == 1 else [[int(t)] for t in nxt])
-            if all(finished):
+            if lockstep_group is not None:
+                # data-parallel attention with expert parallelism across the replicas: every rank of the expert group
+                # takes part in each layer's token exchange, so a rank whose own batch is done keeps stepping (with no
+                # active sequence) until all ranks are done
+                flag = torch.tensor([0 if all(finished) else 1], dtype=torch.int32, device=device)
+                torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX, group=lockstep_group)
+                if int(flag.item()) == 0:
+                    break
+            elif all(finished):
                 break
             with latency.phase("preprocess", False):
                 act = [not f for f in finished]

@@ -117,3 +117,16 @@ def test_replicated_section_shard_and_merge_roundtrip():
     assert torch.equal(shards[0][8:12], k[:4]) and torch.equal(shards[1][8:12], k[:4]) and torch.equal(shards[2][8:12], k[4:])
     merged = merge_shards(shards, {"tp": tp, "dim": 0, "sections": list(sections), "groups": list(groups)})
     assert torch.equal(merged, full)
+
+
+def test_dp_attention_with_ep_moe_generation_runs_in_lockstep(tmp_path):
+    """Attention data-parallel (own prompts and lengths per rank), experts split over the ranks: a rank that is done
+    keeps stepping until all are, and every rank's tokens equal those of the unsharded model."""
+    out = tmp_path / "dpa.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist", "run_dp_attention_ep_moe.py"), str(out)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, res.stderr[-3000:]
+    got = json.loads(out.read_text())
+    assert got["ok"] and got["lens"] == [9, 9]
