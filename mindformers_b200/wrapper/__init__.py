@@ -8,6 +8,7 @@ that name the reference's classes resolve.
 from ..parallel.distributed.train_step import TrainOneStep
 from ..parallel.pipeline import PipelineTrainStep
 from ..tools.register import MindFormerModuleType, MindFormerRegister
+from .micro_batch_interleave import MicroBatchInterleaved
 
 MFTrainOneStepCell = TrainOneStep
 MFPipelineWithLossScaleCell = PipelineTrainStep
@@ -16,4 +17,4 @@ for _name, _cls in (("MFTrainOneStepCell", TrainOneStep), ("MFPipelineWithLossSc
     if not MindFormerRegister.is_exist(MindFormerModuleType.WRAPPER, _name):
         MindFormerRegister.register_cls(_cls, MindFormerModuleType.WRAPPER, alias=_name)
 
-__all__ = ["MFTrainOneStepCell", "MFPipelineWithLossScaleCell", "TrainOneStep", "PipelineTrainStep"]
+__all__ = ["MFTrainOneStepCell", "MFPipelineWithLossScaleCell", "TrainOneStep", "PipelineTrainStep", "MicroBatchInterleaved"]

@@ -314,3 +314,21 @@ def test_infer_model_mixin_names_strategy_and_name_map(tmp_path):
     json.dump({"final.norm": "decoder.final_layernorm.weight"}, open(tmp_path / "param_name_map.json", "w"))
     res = model.load_weights_from_dir(str(tmp_path))
     assert res["tensors"] == 1 and torch.equal(dict(model.named_parameters())["decoder.final_layernorm.weight"], new_norm)
+
+
+def test_micro_batch_interleaved_wrapper():
+    from mindformers_b200.wrapper import MicroBatchInterleaved
+    torch.manual_seed(2)
+    model = GPTModel(tiny_llama_config())
+    ids = torch.randint(0, 1024, (4, 17))
+    inp, lab = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    whole = model(inp, labels=lab)
+    wrapped = MicroBatchInterleaved(model, 2)
+    split = wrapped(inp, labels=lab)
+    assert abs(float(whole.detach()) - float(split.detach())) < 1e-5       # equal token counts per half
+    split.backward()
+    assert model.output_layer.weight.grad is not None
+    with torch.no_grad():
+        assert wrapped(inp).shape == model(inp).shape                       # logits are concatenated again
+    with pytest.raises(ValueError):
+        MicroBatchInterleaved(model, 3)(inp, labels=lab)
