@@ -3,6 +3,7 @@ frequency managers with context-extension methods, ALiBi, capacity-based MoE, se
 and W8A8 quantisers, RNG tracker."""
 from .activation import GELU, FastGelu, SiLU, SwiGLU, get_activation
 from .layers import AlibiTensor, Dropout, FreqsMgr, LayerNorm, Linear, LowerTriangularMaskWithDynamic
-from .moe_legacy import MoEConfig, MoEV2, TopkRouterV2
+from .local_block_sparse_attention import LocalBlockSparseAttention
+from .moe_legacy import MoEConfig, MoEInfer, MoEV2, MoEV3, TopkRouterV2
 from .seq_pipe import SequenceSplit
 from .rng import CudaRNGStatesTracker, get_rng_tracker, model_parallel_manual_seed

@@ -135,3 +135,94 @@ class MoEV2(nn.Module):
                 s = s * torch.sigmoid(self.shared_gate(x2))
             out = out + s
         return out.reshape(shape), aux
+
+
+class MoEV3(nn.Module):
+    """Dropless MoE with explicit collectives (reference ``modules/transformer/moev3.py:57``, ``ffn_forward_func``
+    :491-530): all-to-all of the per-expert counts, all-to-all-v of the token copies sorted by expert, grouped expert
+    MLP on the received rows, all-to-all-v back, weighted un-permute. ``group`` is the expert-parallel process group
+    (None = all experts local); every rank owns ``expert_num / group size`` consecutive experts.
+
+    The reference's hierarchical variant (inter-node all-gather + intra-node all-to-all-v, ``:689-752``) is a topology
+    optimisation for several nodes; on one NVSwitch box every peer is equally far and the flat exchange is used."""
+
+    def __init__(self, hidden_size: int, ffn_hidden_size: int, cfg: MoEConfig, group=None, device=None,
+                 dtype=torch.float32):
+        super().__init__()
+        import torch.distributed as dist
+        self.cfg, self.H, self.group = cfg, hidden_size, group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if cfg.expert_num % self.world:
+            raise ValueError("expert_num must be divisible by the expert-parallel size")
+        self.E_local = cfg.expert_num // self.world
+        F_ = cfg.moe_intermediate_size or ffn_hidden_size
+        self.gate = nn.Linear(hidden_size, cfg.expert_num, bias=False, device=device, dtype=torch.float32)
+        g = torch.Generator().manual_seed(4321)                       # full stacks first: values independent of ep
+        w1 = torch.empty(cfg.expert_num, hidden_size, 2 * F_).normal_(0, 0.02, generator=g)
+        w2 = torch.empty(cfg.expert_num, F_, hidden_size).normal_(0, 0.02, generator=g)
+        lo = self.rank * self.E_local
+        self.w1 = nn.Parameter(w1[lo:lo + self.E_local].to(device=device, dtype=dtype))
+        self.w2 = nn.Parameter(w2[lo:lo + self.E_local].to(device=device, dtype=dtype))
+
+    def route(self, x2: torch.Tensor):
+        c = self.cfg
+        logits = self.gate(x2.float())
+        probs = torch.softmax(logits, dim=-1)
+        top_p, top_e = probs.topk(c.num_experts_chosen, dim=-1)
+        if c.norm_topk_prob and c.num_experts_chosen > 1:
+            top_p = top_p / (top_p.sum(-1, keepdim=True) + 1e-9)
+        frac = F.one_hot(top_e, c.expert_num).sum(1).float().mean(0) / c.num_experts_chosen
+        aux = c.aux_loss_factor * c.expert_num * torch.sum(frac.detach() * probs.mean(0))
+        return top_p * c.routed_scaling_factor, top_e, aux
+
+    def experts(self, rows: torch.Tensor, counts_per_local_expert: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(rows)
+        start = 0
+        for e, n in enumerate(counts_per_local_expert.tolist()):
+            if n:
+                seg = rows[start:start + n]
+                g, u = (seg @ self.w1[e].to(seg.dtype)).chunk(2, dim=-1)
+                out[start:start + n] = (F.silu(g) * u) @ self.w2[e].to(seg.dtype)
+                start += n
+        return out
+
+    def forward(self, x: torch.Tensor):
+        import torch.distributed as dist
+        from ..parallel.mappings import all_to_all
+        shape = x.shape
+        x2 = x.reshape(-1, self.H)
+        T, k, E = x2.shape[0], self.cfg.num_experts_chosen, self.cfg.expert_num
+        probs, ids, aux = self.route(x2)
+        flat_e = ids.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)                    # copies sorted by (global) expert
+        send = x2.repeat_interleave(k, dim=0)[order]
+        counts = torch.bincount(flat_e, minlength=E)
+        if self.world > 1:
+            recv_counts = torch.empty_like(counts)
+            dist.all_to_all_single(recv_counts, counts, group=self.group)              # counts[r*E_local + e] -> rank r
+            in_splits = counts.view(self.world, self.E_local).sum(1).tolist()
+            out_splits = recv_counts.view(self.world, self.E_local).sum(1).tolist()
+            recv = all_to_all(send, out_splits, in_splits, self.group)               # differentiable exchange
+            # received rows are ordered (source rank, local expert): regroup by local expert
+            src_counts = recv_counts.view(self.world, self.E_local)
+            tag = torch.repeat_interleave(torch.arange(self.E_local, device=x.device).repeat(self.world), src_counts.reshape(-1))
+            regroup = torch.argsort(tag, stable=True)
+            y = self.experts(recv[regroup], src_counts.sum(0))
+            back = torch.zeros_like(y).index_copy(0, regroup, y)
+            ret = all_to_all(back, in_splits, out_splits, self.group)
+        else:
+            ret = self.experts(send, counts)
+        unsorted = torch.zeros_like(ret).index_copy(0, order, ret)
+        out = (unsorted.view(T, k, self.H) * probs.unsqueeze(-1).to(ret.dtype)).sum(1)
+        return out.reshape(shape), aux
+
+
+class MoEInfer(MoEV3):
+    """Forward-only MoE of the legacy inference path (``modules/transformer/moe.py:1888``): routing, expert MLPs and
+    the final weighted un-permute (``MoeFinalizeRouting``) without an auxiliary loss."""
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor):
+        out, _ = super().forward(x)
+        return out

@@ -165,3 +165,42 @@ def test_batched_expert_linears_match_a_per_expert_loop():
     import pytest
     with pytest.raises(ValueError):
         ColumnParallelBatchedLinear(32, 48, config=cfg, is_expert=False)
+
+
+def test_local_block_sparse_attention_matches_dense_masked_attention():
+    import torch
+    from mindformers_b200.modules.local_block_sparse_attention import LocalBlockSparseAttention
+    torch.manual_seed(0)
+    att = LocalBlockSparseAttention(seq_len=64, size_per_head=16, local_size=32, block_size=8, dropout_rate=0.0).eval()
+    q, k, v = (torch.randn(2, 3, 64, 16) for _ in range(3))
+    out = att(q, k, v)
+    mask = att.dense_mask()
+    assert mask[40, 40] and mask[40, 16] and not mask[40, 15] and not mask[40, 41]      # window of 4 blocks, causal
+    s = (q @ k.transpose(-1, -2)) / 4.0
+    ref = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v
+    assert torch.allclose(out, ref, atol=1e-5)
+    pad = torch.ones(2, 64, 64)
+    pad[1, :, :5] = 0                                   # batch 1 may not look at its first five tokens
+    out2 = att(q, k, v, pad)
+    ref2 = torch.softmax(s.masked_fill(~(mask & pad.bool()[:, None]), float("-inf")), -1)
+    ref2 = torch.nan_to_num(ref2, nan=0.0) @ v
+    assert torch.allclose(out2, ref2, atol=1e-5) and torch.allclose(out2[0], out[0], atol=1e-6)
+
+
+def test_moe_infer_matches_per_token_loop():
+    import torch
+    from mindformers_b200.modules import MoEConfig, MoEInfer
+    cfg = MoEConfig(expert_num=4, num_experts_chosen=2, moe_intermediate_size=12)
+    torch.manual_seed(1)
+    moe = MoEInfer(8, 12, cfg)
+    x = torch.randn(2, 5, 8)
+    out = moe(x)
+    assert out.shape == x.shape and not out.requires_grad
+    probs, ids, _ = moe.route(x.reshape(-1, 8))
+    ref = torch.zeros(10, 8)
+    for t in range(10):
+        for j in range(2):
+            e = int(ids[t, j])
+            g, u = (x.reshape(-1, 8)[t] @ moe.w1[e]).chunk(2)
+            ref[t] += probs[t, j] * ((torch.nn.functional.silu(g) * u) @ moe.w2[e])
+    assert torch.allclose(out.reshape(-1, 8), ref.detach(), atol=1e-5)

@@ -130,3 +130,11 @@ def test_dp_attention_with_ep_moe_generation_runs_in_lockstep(tmp_path):
     assert res.returncode == 0, res.stderr[-3000:]
     got = json.loads(out.read_text())
     assert got["ok"] and got["lens"] == [9, 9]
+
+
+def test_legacy_dropless_moe_over_two_ranks_matches_one_rank():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist", "run_moev3.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, res.stderr[-3000:]
