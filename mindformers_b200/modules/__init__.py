@@ -2,6 +2,7 @@
 frequency managers with context-extension methods, ALiBi, capacity-based MoE, sequence-pipeline splitting, weight-only
 and W8A8 quantisers, RNG tracker."""
 from .activation import GELU, FastGelu, SiLU, SwiGLU, get_activation
+from .infer_attention import InferAttention, KVCacheMgr, PagedAttentionMgr
 from .layers import AlibiTensor, Dropout, FreqsMgr, LayerNorm, Linear, LowerTriangularMaskWithDynamic
 from .local_block_sparse_attention import LocalBlockSparseAttention
 from .moe_legacy import MoEConfig, MoEInfer, MoEV2, MoEV3, TopkRouterV2

@@ -204,3 +204,52 @@ def test_moe_infer_matches_per_token_loop():
             g, u = (x.reshape(-1, 8)[t] @ moe.w1[e]).chunk(2)
             ref[t] += probs[t, j] * ((torch.nn.functional.silu(g) * u) @ moe.w2[e])
     assert torch.allclose(out.reshape(-1, 8), ref.detach(), atol=1e-5)
+
+
+def test_infer_attention_paged_and_contiguous_caches_match_full_attention():
+    """Prefill + two decode steps through the paged cache manager and through the contiguous cache manager give the
+    attention of the whole sequence recomputed from scratch (with RoPE)."""
+    import torch
+    from mindformers_b200.inference.block_manager import BlockTables
+    from mindformers_b200.modules import InferAttention
+    from mindformers_b200.ops import functional as Fn
+    torch.manual_seed(0)
+    nh, nkv, hd, B, S0, steps = 4, 2, 16, 2, 5, 2
+    total = S0 + steps
+    q_all, k_all, v_all = (torch.randn(B, total, n * hd) for n in (nh, nkv, nkv))
+    inv = 1.0 / (10000 ** (torch.arange(0, hd, 2).float() / hd))
+    ang = torch.arange(64).float()[:, None] * inv[None]
+    freqs = (ang.cos(), ang.sin())
+
+    def reference(upto):
+        pos = torch.arange(upto).repeat(B)
+        q = Fn.rope_reference(q_all[:, :upto].reshape(B * upto, nh, hd), *freqs, pos, nh, hd).view(B, upto, nh, hd)
+        k = Fn.rope_reference(k_all[:, :upto].reshape(B * upto, nkv, hd), *freqs, pos, nkv, hd).view(B, upto, nkv, hd)
+        v = v_all[:, :upto].view(B, upto, nkv, hd)
+        return Fn.attention_reference(q, k, v, causal=True).reshape(B, upto, nh * hd)
+
+    paged = InferAttention(nh, hd, nkv, block_size=4, num_blocks=16, compute_dtype=torch.float32, device="cpu")
+    dense = InferAttention(nh, hd, nkv, use_paged_attention=False, max_batch_size=B, max_seq_length=16,
+                           compute_dtype=torch.float32, device="cpu")
+    tables = BlockTables(16, 4, 16)
+    tables.init_cache_engine(B)
+    table, slots = tables.assemble_pa_full_inputs([S0] * B)
+    pos = torch.arange(S0).repeat(B)
+    flat = lambda t, a, b: t[:, a:b].reshape(B * (b - a), -1)
+    out = paged(flat(q_all, 0, S0), flat(k_all, 0, S0), flat(v_all, 0, S0), tables.context_lens(), table, slots, freqs,
+                pos, [S0] * B, True)
+    ref = reference(S0)
+    assert torch.allclose(out.view(B, S0, -1), ref, atol=1e-5)
+    out_d = dense(q_all[:, :S0], k_all[:, :S0], v_all[:, :S0], torch.tensor([S0] * B), freqs_cis=freqs, is_prefill=True)
+    assert torch.allclose(out_d, ref, atol=1e-5)
+    for step in range(steps):
+        t = S0 + step
+        table, slots = tables.assemble_pa_inc_inputs(None, 1)
+        pos = torch.full((B,), t)
+        out = paged(flat(q_all, t, t + 1), flat(k_all, t, t + 1), flat(v_all, t, t + 1), tables.context_lens(), table,
+                    slots, freqs, pos, None, False)
+        ref = reference(t + 1)[:, -1]
+        assert torch.allclose(out, ref, atol=1e-5), step
+        out_d = dense(q_all[:, t:t + 1], k_all[:, t:t + 1], v_all[:, t:t + 1], torch.tensor([t + 1] * B),
+                      freqs_cis=freqs, positions=pos, is_prefill=False)
+        assert torch.allclose(out_d[:, 0], ref, atol=1e-5), step
