@@ -9,7 +9,51 @@ The objects carry the reference's field names; ``to_parallel_state_kwargs`` maps
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass, field
+from enum import Enum
 from typing import Any, Dict, List, Optional, Union
+
+
+class ContextParallelAlgo(Enum):
+    """How the sequence is split over the context-parallel ranks (``op_parallel_config.py:250``): K/V exchange
+    between sequence shards, head all-to-all, or the first inside groups of the second."""
+    COLOSSALAI_CP = "colossalai_cp"
+    ULYSSES_CP = "ulysses_cp"
+    HYBRID_CP = "hybrid_cp"
+
+
+@dataclass
+class OpParallelConfig:
+    """Degrees that a single operator is split by (``op_parallel_config.py:48``): data, model (tensor), context."""
+    data_parallel: int = 1
+    model_parallel: int = 1
+    context_parallel: int = 1
+    use_seq_parallel: bool = False
+    select_recompute: bool = False
+    context_parallel_algo: str = "colossalai_cp"
+
+    def __post_init__(self):
+        for name in ("data_parallel", "model_parallel", "context_parallel"):
+            v = getattr(self, name)
+            if not isinstance(v, int) or v < 1:
+                raise ValueError(f"{name} must be a positive integer, got {v!r}")
+        ContextParallelAlgo(self.context_parallel_algo)          # raises on an unknown name
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+
+@dataclass
+class _PipeLineConfig:
+    """Pipeline degrees (``op_parallel_config.py:132``)."""
+    pipeline_stage: int = 1
+    micro_batch_num: int = 1
+    seq_split_num: int = 1
+
+    def __post_init__(self):
+        for name in ("pipeline_stage", "micro_batch_num", "seq_split_num"):
+            v = getattr(self, name)
+            if not isinstance(v, int) or v < 1:
+                raise ValueError(f"{name} must be a positive integer, got {v!r}")
 
 
 @dataclass
@@ -73,6 +117,15 @@ class TransformerOpParallelConfig:
             self.vocab_emb_dp = False           # the embedding is model-parallel once the model is staged
 
     @property
+    def dp_mp_config(self) -> OpParallelConfig:
+        return OpParallelConfig(self.data_parallel, self.model_parallel, self.context_parallel, self.use_seq_parallel,
+                                bool(self.recompute.select_recompute), self.context_parallel_algo)
+
+    @property
+    def pipeline_config(self) -> _PipeLineConfig:
+        return _PipeLineConfig(self.pipeline_stage, self.micro_batch_num, self.seq_split_num)
+
+    @property
     def moe_parallel_config(self) -> MoEParallelConfig:
         return MoEParallelConfig(self.data_parallel, self.model_parallel, self.expert_parallel, self.context_parallel)
 
@@ -94,6 +147,7 @@ class TransformerOpParallelConfig:
 default_transformer_config = TransformerOpParallelConfig()
 default_recompute_config = TransformerRecomputeConfig()
 default_moe_parallel_config = MoEParallelConfig()
+default_dpmp_config = OpParallelConfig()
 
 
 def build_parallel_config(config) -> TransformerOpParallelConfig:

@@ -182,3 +182,19 @@ def test_context_reads_parallel_speed_up_json(tmp_path):
     assert set(ctx.parallel_speed_up["ignored"]) == {"dataset_broadcast_opt_level", "enable_grad_comm_opt", "some_future_knob"}
     assert cfg["model"]["model_config"]["fused_tp_comm"] is True
     assert Context({"context": {"device_target": "CPU"}}).parallel_speed_up["path"] is None
+
+
+def test_op_parallel_config_objects():
+    import pytest
+    from mindformers_b200.core.parallel_config import (ContextParallelAlgo, OpParallelConfig, TransformerOpParallelConfig,
+                                                       _PipeLineConfig, default_dpmp_config)
+    par = TransformerOpParallelConfig(data_parallel=2, model_parallel=4, context_parallel=2, pipeline_stage=2,
+                                      micro_batch_num=8, context_parallel_algo="ulysses_cp", use_seq_parallel=True)
+    dpmp = par.dp_mp_config
+    assert (dpmp.data_parallel, dpmp.model_parallel, dpmp.context_parallel, dpmp.use_seq_parallel) == (2, 4, 2, True)
+    assert ContextParallelAlgo(dpmp.context_parallel_algo) is ContextParallelAlgo.ULYSSES_CP
+    assert par.pipeline_config == _PipeLineConfig(2, 8, 1) and default_dpmp_config.model_parallel == 1
+    with pytest.raises(ValueError):
+        OpParallelConfig(context_parallel_algo="ring_of_rings")
+    with pytest.raises(ValueError):
+        _PipeLineConfig(pipeline_stage=0)
