@@ -245,20 +245,14 @@ class BaseTrainer:
         if not path:
             return 0, 0
         fam = _model_dict(config).get("model_type", "llama")
+        from .utils import load_resume_context_from_checkpoint, transform_and_load_checkpoint
         if resume:
-            point = get_resume_checkpoint(path, resume) if os.path.isdir(path) else None
-            scalars = load_checkpoint(engine.model, path, optimizer=engine.optimizer, strict=True, family=fam)
-            epoch = int(scalars.get("epoch_num", point[0] if point else 1))
-            step = int(scalars.get("step_num", point[1] if point else 0))
-            step = rescale_resume_step(step, scalars.get("global_batch_size"), gbs)
-            start_epoch, start_step = max(epoch - 1, 0), step
-            if start_step >= steps_per_epoch:
-                start_epoch, start_step = start_epoch + start_step // steps_per_epoch, start_step % steps_per_epoch
+            scalars = transform_and_load_checkpoint(config, engine.model, engine.optimizer, path, family=fam, resume=True)
+            ctx = load_resume_context_from_checkpoint(scalars, path, resume, gbs, steps_per_epoch)
+            start_epoch, start_step = ctx["initial_epoch"], ctx["initial_step"]
             logger.info("resumed from %s at epoch %d step %d", path, start_epoch + 1, start_step)
         else:
-            load_checkpoint(engine.model, path, strict=False, family=fam)
-            if hasattr(engine.optimizer, "reload_model_params"):
-                engine.optimizer.reload_model_params()
+            transform_and_load_checkpoint(config, engine.model, engine.optimizer, path, family=fam, resume=False)
         return start_epoch, start_step
 
     # ------------------------------------------------------------------ evaluation / prediction

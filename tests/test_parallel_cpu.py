@@ -138,3 +138,37 @@ def test_legacy_dropless_moe_over_two_ranks_matches_one_rank():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
                          env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
     assert res.returncode == 0, res.stderr[-3000:]
+
+
+def test_auto_trans_ckpt_loads_a_tp2_checkpoint_into_one_rank(tmp_path):
+    """Per-rank checkpoint + strategy files of a tp = 2 run → merged and loaded by a single-rank model
+    (``auto_trans_ckpt``); the loss of a fixed batch is the one the tp = 2 model had, and the resume context follows
+    the scalars of the checkpoint with the step rescaled for the new global batch size."""
+    import torch
+    from tests.dist.run_save_tp_ckpt import CFG, batch
+    from mindformers_b200.parallel.layers.gpt_model import GPTModel
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    from mindformers_b200.trainer.utils import load_resume_context_from_checkpoint, transform_and_load_checkpoint
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist", "run_save_tp_ckpt.py"), str(tmp_path)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, res.stderr[-3000:]
+    want = json.loads((tmp_path / "loss.json").read_text())["loss"]
+    torch.manual_seed(5)                                            # other initial values than the saved model
+    cfg = TransformerConfig(**CFG)
+    cfg.device = "cpu"
+    model = GPTModel(cfg).eval()
+    inp, lab = batch()
+    with torch.no_grad():
+        before = float(model(inp, labels=lab))
+    config = {"auto_trans_ckpt": True, "src_strategy_path_or_dir": str(tmp_path / "strategy"),
+              "output_dir": str(tmp_path / "out"), "load_checkpoint": str(tmp_path / "checkpoint")}
+    scalars = transform_and_load_checkpoint(config, model)
+    with torch.no_grad():
+        after = float(model(inp, labels=lab))
+    assert abs(before - want) > 1e-3 and abs(after - want) < 1e-5
+    assert os.path.exists(tmp_path / "out" / "transformed_checkpoint" / "model.safetensors")
+    ctx = load_resume_context_from_checkpoint(scalars, str(tmp_path / "checkpoint"), True, global_batch_size=8,
+                                              steps_per_epoch=100)
+    assert ctx["initial_epoch"] == 0 and ctx["initial_step"] == 14            # 7 steps of 16 samples = 14 steps of 8
