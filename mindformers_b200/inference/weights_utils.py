@@ -18,7 +18,7 @@ import glob
 import json
 import os
 import re
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import torch
 from safetensors import safe_open

@@ -15,7 +15,6 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from ..checkpoint.io import load_checkpoint
-from ..checkpoint.resume import get_resume_checkpoint, rescale_resume_step
 from ..core.callback import (Callback, CheckpointMonitor, EvalCallBack, GracefulExitCallback, MFLossMonitor, ProfileMonitor,
                              RunContext, TrainingStateMonitor, build_callback)
 from ..core.lr import build_lr
