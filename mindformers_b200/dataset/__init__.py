@@ -3,7 +3,8 @@ from .causal_language_model_dataset import (BlendedMegatronDatasetDataLoader, Ca
                                             MockDataLoader, MultiTurnDataset, ResumableShardSampler, build_dataset,
                                             build_dataset_loader)
 from .gpt_dataset import (BlendedDataset, BlendedMegatronDatasetBuilder, GPTDataset, GPTDatasetConfig, MockGPTDataset)
-from .handlers import AlpacaInstructDataHandler, PackingHandler, build_data_handler
+from .handlers import AlpacaInstructDataHandler, LlavaInstructDataHandler, PackingHandler, build_data_handler
+from .modal_to_text_sft_dataset import ModalToTextSFTDataset
 from .indexed_dataset import IndexedDataset, IndexedDatasetBuilder
 from .dataloaders import (ADGenDataLoader, MultiSourceDataLoader, MultiSourceDataset, SFTDataLoader, ToolAlpacaDataLoader,
                           TrainingDataLoader, TrainingDataset, read_records)

@@ -5,6 +5,7 @@ Reference: ``dataset/handler/*`` (``AlpacaInstructDataHandler``, ``CodeAlpacaIns
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Dict, Iterable, List, Optional
 
 import numpy as np
@@ -70,6 +71,46 @@ class CodeAlpacaInstructDataHandler(AlpacaInstructDataHandler):
 class AdgenInstructDataHandler(BaseInstructDataHandler):
     def format(self, r):
         return r.get("content", ""), r.get("summary", "")
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+class LlavaInstructDataHandler(BaseInstructDataHandler):
+    """LLaVA-style visual instruction records: ``{"image": "x.jpg", "conversations": [{"from": "human", "value":
+    "<image>\n..."}, {"from": "gpt", "value": "..."}, ...]}`` → multi-turn text with the image tag expanded to
+    ``image_token_num`` placeholder tokens; only the assistant turns carry loss. ``image_dir`` is prepended to the
+    image path, which is kept in the output for the multimodal dataset to load
+    (reference ``dataset/handler/llava_handler.py``)."""
+
+    def __init__(self, tokenizer=None, seq_length: int = 2048, image_dir: str = "", image_token: str = "<image>",
+                 image_token_num: int = 1, user_prefix: str = "USER: ", assistant_prefix: str = " ASSISTANT: ", **kw):
+        super().__init__(tokenizer, seq_length, **kw)
+        self.image_dir, self.image_token, self.image_token_num = image_dir, image_token, max(1, image_token_num)
+        self.user_prefix, self.assistant_prefix = user_prefix, assistant_prefix
+
+    def format(self, r):
+        raise NotImplementedError("multi-turn records are handled as a whole by handle_one")
+
+    def handle_one(self, record: dict) -> Dict[str, np.ndarray]:
+        ids: List[int] = []
+        labels: List[int] = []
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        for turn in record.get("conversations", []):
+            human = turn.get("from") in ("human", "user")
+            text = turn.get("value", "").replace(self.image_token, self.image_token * self.image_token_num)
+            piece = self.encode((self.user_prefix if human else self.assistant_prefix) + text)
+            if not human and eos is not None:
+                piece = piece + [eos]
+            ids += piece
+            labels += [self.ignore] * len(piece) if human else piece
+        ids, labels = ids[: self.seq_length + 1], labels[: self.seq_length + 1]
+        if self.padding:
+            pad = getattr(self.tokenizer, "pad_token_id", 0) or 0
+            ids = ids + [pad] * (self.seq_length + 1 - len(ids))
+            labels = labels + [self.ignore] * (self.seq_length + 1 - len(labels))
+        out = {"input_ids": np.asarray(ids, dtype=np.int64), "labels": np.asarray(labels, dtype=np.int64)}
+        if record.get("image"):
+            out["image_path"] = os.path.join(self.image_dir, record["image"]) if self.image_dir else record["image"]
+        return out
 
 
 @MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)

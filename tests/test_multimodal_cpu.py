@@ -127,3 +127,62 @@ def test_generate_matches_forward_and_pipeline():
     pipe = pipeline("multi_modal_to_text_generation", model=model, processor=proc, max_new_tokens=3, do_sample=False)
     res = pipe([query])
     assert isinstance(res[0]["text_generation_text"][0], str)
+
+
+def test_modal_to_text_sft_dataset_llava_handler_and_s3_paths(tmp_path):
+    import json
+    from mindformers_b200.dataset import LlavaInstructDataHandler, ModalToTextSFTDataset
+    from mindformers_b200.dataset import utils_s3
+    tok = ImgTokenizer(add_bos_token=False)
+    t = template(tok, mode="train", max_length=48)
+    img = np.random.default_rng(0).integers(0, 255, (28, 28, 3), dtype=np.uint8)
+    seen = []
+    t.modal_builders["image"].load_image = lambda item: (seen.append(item), img)[1]
+    records = [{"conversations": [["user", "<img>a.png</img>what?"], ["assistant", "cat"]]},
+               {"image": "b.png", "conversations": [{"from": "human", "value": "<image>\\nand this?"},
+                                                    {"from": "gpt", "value": "dog"}]}]
+    ann = tmp_path / "ann.json"
+    json.dump(records, open(ann, "w"))
+    loader = ModalToTextSFTDataset(dict(annotation_file=str(ann), modal_content_transform_template=t, batch_size=2,
+                                        image_dir=str(tmp_path / "imgs")))
+    batch = next(iter(loader))
+    assert batch["input_ids"].shape == (2, 47) and batch["labels"].shape == (2, 47)
+    assert seen[0] == "a.png" and seen[1] == str(tmp_path / "imgs" / "b.png")
+    pos = batch["image_context_pos"]
+    assert pos.shape[-1] == 2 and set(pos[..., 0].unique().tolist()) == {0, 1}         # rows of the batch
+    kept = [l for l in batch["labels"][1].tolist() if l != -100]
+    assert kept == tok.encode("dog", add_special_tokens=False) + [tok.eos_token_id]
+
+    h = LlavaInstructDataHandler(tok, seq_length=80, image_dir="/data/img", image_token_num=3)
+    out = h.handle_one(records[1])
+    assert out["image_path"] == "/data/img/b.png" and out["input_ids"].shape == (81,)
+    text = tok.decode([i for i in out["input_ids"].tolist() if i != (tok.pad_token_id or 0)])
+    assert text.count("<image>") == 3 and "ASSISTANT: dog" in text
+    assert [l for l in out["labels"].tolist() if l != -100][-1] == tok.eos_token_id
+
+    assert utils_s3.is_s3_path("s3://bucket/a/b.idx") and not utils_s3.is_s3_path("/data/b.idx")
+    assert utils_s3.parse_s3_path("s3://bucket/a/b.idx") == ("bucket", "a/b.idx")
+
+    class FakeS3:
+        store = {("bucket", "a/b.idx"): b"0123456789"}
+        downloads = 0
+
+        def head_object(self, Bucket, Key):
+            return {"ContentLength": len(self.store[(Bucket, Key)])}
+
+        def download_file(self, bucket, key, dst):
+            FakeS3.downloads += 1
+            open(dst, "wb").write(self.store[(bucket, key)])
+
+        def get_object(self, Bucket, Key, Range):
+            a, b = (int(x) for x in Range.split("=")[1].split("-"))
+            return {"Body": self.store[(Bucket, Key)][a:b + 1]}
+
+    cfg = utils_s3.S3Config(path_to_idx_cache=str(tmp_path / "cache"))
+    local = utils_s3.maybe_download_index("s3://bucket/a/b.idx", cfg, FakeS3())
+    assert open(local, "rb").read() == b"0123456789"
+    utils_s3.maybe_download_index("s3://bucket/a/b.idx", cfg, FakeS3())
+    assert FakeS3.downloads == 1                                                       # second call hits the cache
+    assert utils_s3.object_exists("s3://bucket/a/b.idx", FakeS3()) and not utils_s3.object_exists("s3://bucket/x", FakeS3())
+    assert utils_s3.read_range("s3://bucket/a/b.idx", 2, 4, FakeS3()) == b"2345"
+    assert utils_s3.maybe_download_index("/local/file.idx", cfg) == "/local/file.idx"
