@@ -92,15 +92,46 @@ class IndexedDatasetBuilder:
                 f.write(np.asarray(self.modes, dtype=np.int8).tobytes(order="C"))
 
 
+class _S3Bin:
+    """Token data of an object-store ``.bin``: ranged reads of ``chunk`` bytes, the last chunk kept for the next
+    request (sequential access, which is what the samplers mostly do, hits it)."""
+
+    def __init__(self, path: str, chunk: int, client=None):
+        self.path, self.chunk, self.client = path, max(1, int(chunk)), client
+        self._start, self._data = 0, b""
+        self.requests = 0
+
+    def read(self, offset: int, nbytes: int) -> bytes:
+        from . import utils_s3
+        if not (self._start <= offset and offset + nbytes <= self._start + len(self._data)):
+            self._start = offset
+            self._data = utils_s3.read_range(self.path, offset, max(nbytes, self.chunk), self.client)
+            self.requests += 1
+        lo = offset - self._start
+        return self._data[lo:lo + nbytes]
+
+
 class IndexedDataset:
     """Random access to the sequences of a ``prefix.idx`` / ``prefix.bin`` pair."""
 
-    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True):
+    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True, object_storage_config=None,
+                 s3_client=None):
+        """``path_prefix`` may be an ``s3://bucket/key`` prefix: the index is downloaded once into
+        ``object_storage_config.path_to_idx_cache`` and token data is fetched with ranged reads of
+        ``bin_chunk_nbytes`` (``dataset/utils_s3.py``)."""
         self.path_prefix = path_prefix
         self.multimodal = multimodal
-        with open(get_idx_path(path_prefix), "rb") as f:
+        self._s3 = None
+        idx_file = get_idx_path(path_prefix)
+        from . import utils_s3
+        if utils_s3.is_s3_path(path_prefix):
+            if object_storage_config is None:
+                raise ValueError("an s3:// dataset prefix needs object_storage_config (S3Config)")
+            idx_file = utils_s3.maybe_download_index(idx_file, object_storage_config, s3_client)
+            self._s3 = _S3Bin(get_bin_path(path_prefix), object_storage_config.bin_chunk_nbytes, s3_client)
+        with open(idx_file, "rb") as f:
             if f.read(9) != _MAGIC:
-                raise ValueError(f"{get_idx_path(path_prefix)} is not an indexed-dataset index")
+                raise ValueError(f"{idx_file} is not an indexed-dataset index")
             (version,) = struct.unpack("<Q", f.read(8))
             if version != 1:
                 raise ValueError(f"unsupported index version {version}")
@@ -109,7 +140,7 @@ class IndexedDataset:
             (n_seq,) = struct.unpack("<Q", f.read(8))
             (n_doc,) = struct.unpack("<Q", f.read(8))
             offset = f.tell()
-        idx = np.memmap(get_idx_path(path_prefix), mode="r", order="C")
+        idx = np.memmap(idx_file, mode="r", order="C")
         self.sequence_lengths = np.frombuffer(idx, dtype=np.int32, count=n_seq, offset=offset)
         offset += n_seq * 4
         self.sequence_pointers = np.frombuffer(idx, dtype=np.int64, count=n_seq, offset=offset)
@@ -118,7 +149,9 @@ class IndexedDataset:
         offset += n_doc * 8
         self.sequence_modes = np.frombuffer(idx, dtype=np.int8, count=n_seq, offset=offset) if multimodal else None
         self._idx_map = idx
-        if mmap:
+        if self._s3 is not None:
+            self._bin = None
+        elif mmap:
             self._bin = np.memmap(get_bin_path(path_prefix), mode="r", order="C")
         else:
             self._bin = np.fromfile(get_bin_path(path_prefix), dtype=np.uint8)
@@ -131,6 +164,8 @@ class IndexedDataset:
         if length is not None:
             n = min(n, length)
         start = int(self.sequence_pointers[idx]) + offset * self.dtype.itemsize
+        if self._s3 is not None:
+            return np.frombuffer(self._s3.read(start, n * self.dtype.itemsize), dtype=self.dtype, count=n)
         return np.frombuffer(self._bin, dtype=self.dtype, count=n, offset=start)
 
     def __getitem__(self, idx):

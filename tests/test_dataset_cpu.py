@@ -103,3 +103,37 @@ def test_mock_blend_loader_and_packing():
     packed = PackingHandler(seq_length=16, max_segments=4).handle(
         [{"input_ids": np.arange(1, 8)}, {"input_ids": np.arange(1, 10)}, {"input_ids": np.arange(1, 6)}])
     assert len(packed) == 2 and packed[0]["actual_seq_len"].tolist() == [7, 16, 16, 16]
+
+
+def test_indexed_dataset_from_an_object_store_prefix(tmp_path):
+    """``s3://`` prefix: the index is cached locally once, token data comes from ranged reads (stand-in client)."""
+    import numpy as np
+    from mindformers_b200.dataset import IndexedDataset, IndexedDatasetBuilder
+    from mindformers_b200.dataset.utils_s3 import S3Config
+    prefix = str(tmp_path / "corpus")
+    b = IndexedDatasetBuilder(prefix + ".bin", dtype=np.int32)
+    docs = [np.arange(5), np.arange(100, 117), np.arange(7, 9)]
+    for d in docs:
+        b.add_item(d)
+        b.end_document()
+    b.finalize(prefix + ".idx")
+
+    class FakeS3:
+        def __init__(self):
+            self.blobs = {("bkt", "data/corpus.idx"): open(prefix + ".idx", "rb").read(),
+                          ("bkt", "data/corpus.bin"): open(prefix + ".bin", "rb").read()}
+
+        def download_file(self, bucket, key, dst):
+            open(dst, "wb").write(self.blobs[(bucket, key)])
+
+        def get_object(self, Bucket, Key, Range):
+            a, e = (int(x) for x in Range.split("=")[1].split("-"))
+            return {"Body": self.blobs[(Bucket, Key)][a:e + 1]}
+
+    ds = IndexedDataset("s3://bkt/data/corpus", object_storage_config=S3Config(str(tmp_path / "cache"), 64),
+                        s3_client=FakeS3())
+    assert len(ds) == 3
+    for i, d in enumerate(docs):
+        assert ds[i].tolist() == d.tolist()
+    assert ds.get(1, offset=3, length=4).tolist() == [103, 104, 105, 106]
+    assert ds._s3.requests <= 4 and os.path.exists(tmp_path / "cache" / "bkt" / "data" / "corpus.idx")
