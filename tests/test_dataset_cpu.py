@@ -106,6 +106,7 @@ def test_mock_blend_loader_and_packing():
 
 
 def test_indexed_dataset_from_an_object_store_prefix(tmp_path):
+    import os
     """``s3://`` prefix: the index is cached locally once, token data comes from ranged reads (stand-in client)."""
     import numpy as np
     from mindformers_b200.dataset import IndexedDataset, IndexedDatasetBuilder
