@@ -33,6 +33,8 @@ _COMMON = [
     (".self_attn.kv_a_proj_with_mqa.", ".self_attention.linear_kv_down_proj."),
     (".self_attn.kv_a_layernorm.", ".self_attention.kv_layernorm."),
     (".self_attn.kv_b_proj.", ".self_attention.linear_kv_up_proj."),
+    (".mlp.shared_expert_gate.weight", ".mlp.shared_experts.gate_weight"),        # Qwen2-MoE: gated shared expert
+    (".mlp.shared_expert.", ".mlp.shared_experts."),
     (".mlp.gate.e_score_correction_bias", ".mlp.router.expert_bias"),
     (".mlp.gate.weight", ".mlp.router.weight.weight"),
     (".gate_proj.", ".gating."),
@@ -59,8 +61,8 @@ _LEGACY_LLAMA = [
     ("model.norm.", "model.norm_out."),
 ]
 
-FAMILIES = ("llama", "qwen2", "qwen2_5", "qwen3", "qwen3_moe", "deepseek_v3", "deepseekv3", "mixtral", "telechat",
-            "glm")
+FAMILIES = ("llama", "qwen2", "qwen2_5", "qwen2_moe", "qwen3", "qwen3_moe", "deepseek_v2", "deepseek_v3",
+            "deepseekv3", "mixtral", "telechat", "glm")
 
 
 def convert_name(hf_name: str, family: str = "llama") -> str:

@@ -1,6 +1,7 @@
 from .auto import AutoConfig, AutoModel, AutoModelForCausalLM, AutoProcessor, AutoTokenizer
 from .configuration_utils import PretrainedConfig
-from .families import (ChatGLM2ForConditionalGeneration, DeepseekV3Config, DeepseekV3ForCausalLM, LlamaConfig,
+from .families import (ChatGLM2ForConditionalGeneration, DeepseekV2Config, DeepseekV2ForCausalLM, DeepseekV3Config,
+                       DeepseekV3ForCausalLM, LlamaConfig, Qwen2MoeConfig, Qwen2MoeForCausalLM,
                        LlamaForCausalLM, MixtralConfig, MixtralForCausalLM, Qwen2Config, Qwen2ForCausalLM, Qwen3Config,
                        Qwen3ForCausalLM, Qwen3MoeConfig, Qwen3MoeForCausalLM, TelechatConfig, TelechatForCausalLM)
 from .modeling_utils import PreTrainedModel

@@ -58,6 +58,18 @@ DeepseekV3Config = _config("DeepseekV3Config", "deepseek_v3",
                                 first_k_dense_replace=3, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
                                 qk_rope_head_dim=64, v_head_dim=128, moe_router_enable_expert_bias=True,
                                 rope_interleave=True), is_mla=True)
+DeepseekV2Config = _config("DeepseekV2Config", "deepseek_v2",
+                           dict(vocab_size=102400, hidden_size=5120, intermediate_size=12288, num_hidden_layers=60,
+                                num_attention_heads=128, num_key_value_heads=128, n_routed_experts=160,
+                                n_shared_experts=2, num_experts_per_tok=6, moe_intermediate_size=1536, n_group=8,
+                                topk_group=3, routed_scaling_factor=16.0, norm_topk_prob=False, scoring_func="softmax",
+                                first_k_dense_replace=1, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                                qk_rope_head_dim=64, v_head_dim=128, rope_interleave=True), is_mla=True)
+Qwen2MoeConfig = _config("Qwen2MoeConfig", "qwen2_moe",
+                         dict(vocab_size=151936, attention_bias=True, rope_theta=1e6, num_experts=60,
+                              num_experts_per_tok=4, moe_intermediate_size=1408, shared_expert_intermediate_size=5632,
+                              use_shared_expert_gating=True, norm_topk_prob=False, first_k_dense_replace=0,
+                              moe_router_score_function="softmax"))
 MixtralConfig = _config("MixtralConfig", "mixtral",
                         dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=14336, norm_topk_prob=True,
                              first_k_dense_replace=0, num_key_value_heads=8, rope_theta=1e6))
@@ -69,6 +81,8 @@ Qwen2ForCausalLM = _model("Qwen2ForCausalLM", Qwen2Config, "qwen2")
 Qwen3ForCausalLM = _model("Qwen3ForCausalLM", Qwen3Config, "qwen3")
 Qwen3MoeForCausalLM = _model("Qwen3MoeForCausalLM", Qwen3MoeConfig, "qwen3_moe")
 DeepseekV3ForCausalLM = _model("DeepseekV3ForCausalLM", DeepseekV3Config, "deepseek_v3")
+DeepseekV2ForCausalLM = _model("DeepseekV2ForCausalLM", DeepseekV2Config, "deepseek_v2")
+Qwen2MoeForCausalLM = _model("Qwen2MoeForCausalLM", Qwen2MoeConfig, "qwen2_moe")
 MixtralForCausalLM = _model("MixtralForCausalLM", MixtralConfig, "mixtral")
 TelechatForCausalLM = _model("TelechatForCausalLM", TelechatConfig, "telechat")
 ChatGLM2ForConditionalGeneration = _model("ChatGLM2ForConditionalGeneration", ChatGLM4Config, "glm")
@@ -78,6 +92,8 @@ MODEL_TYPE_TO_CLASSES = {
     "qwen2_5": (Qwen2Config, Qwen2ForCausalLM), "qwen3": (Qwen3Config, Qwen3ForCausalLM),
     "qwen3_moe": (Qwen3MoeConfig, Qwen3MoeForCausalLM), "deepseek_v3": (DeepseekV3Config, DeepseekV3ForCausalLM),
     "deepseekv3": (DeepseekV3Config, DeepseekV3ForCausalLM), "mixtral": (MixtralConfig, MixtralForCausalLM),
+    "deepseek_v2": (DeepseekV2Config, DeepseekV2ForCausalLM), "deepseek2": (DeepseekV2Config, DeepseekV2ForCausalLM),
+    "qwen2_moe": (Qwen2MoeConfig, Qwen2MoeForCausalLM),
     "telechat": (TelechatConfig, TelechatForCausalLM), "glm": (ChatGLM4Config, ChatGLM2ForConditionalGeneration),
     "chatglm": (ChatGLM4Config, ChatGLM2ForConditionalGeneration),
 }

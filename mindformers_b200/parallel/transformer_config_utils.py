@@ -86,6 +86,8 @@ _TABLE = [
     ("moe_token_drop_policy", ("enable_sdrop", "moe_token_drop_policy"), _drop_policy),
     ("use_pad_tokens", ("enable_gmm_safe_tokens", "use_pad_tokens"), None),
     ("shared_expert_num", ("n_shared_experts", "shared_expert_num"), None),
+    ("moe_shared_expert_intermediate_size", ("shared_expert_intermediate_size", "moe_shared_expert_intermediate_size"), None),
+    ("use_shared_expert_gating", ("use_shared_expert_gating",), None),
     ("cp_comm_type", ("cp_comm_type",), None),
     ("context_parallel_algo", ("context_parallel_algo",), None),
     ("hierarchical_context_parallel_sizes", ("hierarchical_context_parallel_sizes",), None),

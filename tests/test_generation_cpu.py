@@ -127,3 +127,27 @@ def test_detailed_latency_and_token_window_profiling(monkeypatch):
     p.step_begin(1)
     p.close()
     assert p.windows == 1 and not Profiling().enabled
+
+
+def test_deepseek_v2_and_qwen2_moe_families_build_and_generate():
+    """DeepSeek-V2 (MLA without a query low-rank projection, softmax router) and Qwen2-MoE (gated shared expert)."""
+    from mindformers_b200.models import DeepseekV2ForCausalLM, Qwen2MoeForCausalLM
+    v2 = AutoModel.from_config(dict(
+        model_type="deepseek_v2", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=4,
+        intermediate_size=128, moe_intermediate_size=32, n_routed_experts=4, n_shared_experts=1, num_experts_per_tok=2,
+        n_group=2, topk_group=1, first_k_dense_replace=1, q_lora_rank=None, kv_lora_rank=32, qk_nope_head_dim=16,
+        qk_rope_head_dim=8, v_head_dim=16, vocab_size=128, max_position_embeddings=64, params_dtype="float32"), device="cpu")
+    assert isinstance(v2, DeepseekV2ForCausalLM)
+    names = dict(v2.named_parameters())
+    assert "decoder.layers.0.self_attention.linear_q.weight" in names            # plain query projection
+    assert "decoder.layers.1.mlp.shared_experts.linear_fc1.weight" in names
+    assert len(v2.generate([[3, 4, 5]], max_new_tokens=3, do_sample=False, eos_token_id=None)[0]) == 6
+    q2 = AutoModel.from_config(dict(
+        model_type="qwen2_moe", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+        intermediate_size=128, moe_intermediate_size=32, shared_expert_intermediate_size=96, num_experts=4,
+        num_experts_per_tok=2, vocab_size=128, max_position_embeddings=64, params_dtype="float32"), device="cpu")
+    assert isinstance(q2, Qwen2MoeForCausalLM)
+    names = dict(q2.named_parameters())
+    assert names["decoder.layers.0.mlp.shared_experts.gate_weight"].shape == (1, 64)
+    assert names["decoder.layers.0.mlp.shared_experts.linear_fc2.weight"].shape[1] == 96
+    assert len(q2.generate([[3, 4, 5]], max_new_tokens=2, do_sample=False, eos_token_id=None)[0]) == 5

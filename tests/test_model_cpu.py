@@ -266,7 +266,8 @@ def test_weights_loader_streams_an_hf_directory_layer_by_layer(tmp_path):
     ids = torch.randint(0, 1024, (2, 17))
     moe_cfg = dict(num_layers=3, num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=64, first_k_dense_replace=1,
                    moe_shared_expert_intermediate_size=64)
-    for name, family, kw in (("llama", "llama", {}), ("moe", "qwen3_moe", moe_cfg)):
+    gated = dict(moe_cfg, use_shared_expert_gating=True)            # Qwen2-MoE: sigmoid gate on the shared expert
+    for name, family, kw in (("llama", "llama", {}), ("moe", "qwen3_moe", moe_cfg), ("gated", "qwen2_moe", gated)):
         src = GPTModel(tiny_llama_config(**kw)).eval()
         d = tmp_path / name
         save_pretrained_dir(src, str(d), config_dict={"model_type": family}, max_shard_bytes=400_000, hf_names=True,
