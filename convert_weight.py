@@ -28,7 +28,8 @@ from mindformers_b200.models.presets import preset_is_mla  # noqa: E402
 from mindformers_b200.parallel.transformer_config_utils import convert_to_transformer_config  # noqa: E402
 
 convert_map = {"llama": "llama", "qwen2_5": "qwen2", "qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3_moe",
-               "glm-n": "glm", "glm4": "glm", "mixtral": "mixtral", "telechat": "telechat", "deepseekv3": "deepseek_v3"}
+               "glm-n": "glm", "glm4": "glm", "mixtral": "mixtral", "telechat": "telechat", "deepseekv3": "deepseek_v3",
+               "deepseekv2": "deepseek_v2", "qwen2_moe": "qwen2_moe"}
 reversed_convert_map = dict(convert_map)
 DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 

@@ -17,7 +17,8 @@ class MindFormerBook:
     _PIPELINE_SUPPORT_TASK_LIST = OrderedDict([("text_generation", sorted(PRESETS)), ("multi_modal_to_text_generation", ["common"])])
     _MODEL_SUPPORT_LIST = OrderedDict([
         ("llama", ["llama2_7b", "llama3_1_8b", "llama3_1_70b"]), ("qwen2", ["qwen2_5_7b"]), ("qwen3", ["qwen3_8b", "qwen3_32b"]),
-        ("qwen3_moe", ["qwen3_30b_a3b"]), ("deepseek_v3", ["deepseek_v3"]), ("mixtral", ["mixtral_8x7b"]),
+        ("qwen3_moe", ["qwen3_30b_a3b"]), ("deepseek_v3", ["deepseek_v3"]), ("deepseek_v2", ["deepseek_v2_236b"]),
+        ("qwen2_moe", ["qwen1_5_moe_a2_7b"]), ("mixtral", ["mixtral_8x7b"]),
         ("telechat", ["telechat2_7b"]), ("glm", ["glm4_9b"]),
     ])
 
