@@ -253,3 +253,30 @@ def test_infer_attention_paged_and_contiguous_caches_match_full_attention():
         out_d = dense(q_all[:, t:t + 1], k_all[:, t:t + 1], v_all[:, t:t + 1], torch.tensor([t + 1] * B),
                       freqs_cis=freqs, positions=pos, is_prefill=False)
         assert torch.allclose(out_d[:, 0], ref, atol=1e-5), step
+
+
+def test_double_benchmark_accuracy_criterion():
+    """A result as good as the same-precision baseline passes, one that is clearly worse fails, NaN fails."""
+    import pytest
+    import torch
+    from mindformers_b200.utils.precision import DoubleBenchmarkComparator, error_metrics, precision_check
+    torch.manual_seed(0)
+    a, b = torch.randn(256, 512), torch.randn(512, 128)
+    golden = a.double() @ b.double()
+    baseline = (a.bfloat16() @ b.bfloat16()).float()
+    good = (a.bfloat16().float() @ b.bfloat16().float()).bfloat16().float()          # bf16 inputs, fp32 accumulation
+    cmp_ = DoubleBenchmarkComparator(dtype=torch.bfloat16)
+    ok, report = cmp_.check_pass_or_not(good, baseline, golden)
+    assert ok, report
+    worse = good + 0.05 * golden.float().abs().mean() * torch.randn_like(good)
+    ok, report = cmp_.check_pass_or_not(worse, baseline, golden)
+    assert not ok and not report["rmse"]["passed"]
+    broken = good.clone()
+    broken[3, 5] = float("nan")
+    assert not cmp_.check_pass_or_not(broken, baseline, golden)[0]
+    m = error_metrics(good, golden, cmp_.std)
+    assert 0 < m["mean_rel"] < 5e-2 and m["rmse"] > 0
+    out = precision_check(good, golden.float(), kl_threshold=1e-3)
+    assert out["cosine"] > 0.9999
+    with pytest.raises(AssertionError):
+        precision_check(-good, golden.float())
