@@ -276,7 +276,7 @@ def test_double_benchmark_accuracy_criterion():
     assert not cmp_.check_pass_or_not(broken, baseline, golden)[0]
     m = error_metrics(good, golden, cmp_.std)
     assert 0 < m["mean_rel"] < 5e-2 and m["rmse"] > 0
-    out = precision_check(good, golden.float(), kl_threshold=1e-3)
+    out = precision_check(good, golden.float(), l1_threshold=0.1, kl_threshold=1e-3)
     assert out["cosine"] > 0.9999
     with pytest.raises(AssertionError):
         precision_check(-good, golden.float())
