@@ -53,6 +53,10 @@ def run_with_restarts(train_fn: Callable[[int, Optional[str]], object], checkpoi
 
 
 class ElasticRunner:
+    """Supervises a training function: restarts it from the latest consistent checkpoint after a failure, up to
+    ``max_restarts`` times (the host-side part of the reference's fault-tolerant training,
+    ``core/callback/callback.py`` ``TrainFaultTolerance``)."""
+
     def __init__(self, checkpoint_dir: str, max_restarts: int = 3, backoff_s: float = 1.0):
         self.checkpoint_dir, self.max_restarts, self.backoff_s = checkpoint_dir, max_restarts, backoff_s
         self.restarts = 0

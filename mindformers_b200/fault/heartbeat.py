@@ -17,6 +17,8 @@ import torch.distributed as dist
 
 
 class RankFailure(RuntimeError):
+    """Raised between steps when a peer stopped sending heartbeats or reported an error."""
+
     def __init__(self, ranks: List[int], reason: str):
         super().__init__(f"rank(s) {ranks} failed: {reason}")
         self.ranks, self.reason = ranks, reason

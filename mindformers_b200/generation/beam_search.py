@@ -7,6 +7,8 @@ import torch
 
 
 class BeamHypotheses:
+    """The ``num_beams`` best finished hypotheses of one batch entry, scored by length-penalised log-probability."""
+
     def __init__(self, num_beams: int, length_penalty: float, early_stopping: bool):
         self.num_beams, self.length_penalty, self.early_stopping = num_beams, length_penalty, early_stopping
         self.beams: List[Tuple[float, List[int]]] = []
@@ -30,6 +32,10 @@ class BeamHypotheses:
 
 
 class BeamSearchScorer:
+    """Beam bookkeeping of ``generate(num_beams > 1)`` (reference ``generation/beam_search.py``): picks the next beams
+    from the top ``2 * num_beams`` candidates, moves finished ones into ``BeamHypotheses`` and finalises the best
+    sequence per batch entry."""
+
     def __init__(self, batch_size: int, num_beams: int, length_penalty: float = 1.0, early_stopping: bool = False,
                  num_beam_hyps_to_keep: int = 1):
         self.batch_size, self.num_beams, self.keep = batch_size, num_beams, num_beam_hyps_to_keep

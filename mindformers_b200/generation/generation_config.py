@@ -7,6 +7,11 @@ from typing import List, Optional, Union
 
 
 class GenerationConfig:
+    """Generation settings (reference ``generation/generation_config.py``): ``max_length`` / ``max_new_tokens``,
+    ``do_sample``, ``top_k``, ``top_p``, ``temperature``, repetition / frequency / presence penalties, ``num_beams``,
+    ``eos_token_id`` (int or list), ``pad_token_id``, ``chunk_prefill_size``, ``parallel_decoding``,
+    ``use_cuda_graph``. ``update(**kw)`` overrides fields, ``to_dict()`` / ``from_model_config()`` convert."""
+
     def __init__(self, **kwargs):
         self.max_length = kwargs.pop("max_length", kwargs.pop("max_decode_length", 20))
         self.max_new_tokens = kwargs.pop("max_new_tokens", None)

@@ -12,11 +12,16 @@ import torch
 
 
 class LogitsProcessor:
+    """Base of the score transforms: ``__call__(input_ids, scores) -> scores`` on ``[batch, vocab]`` (reference
+    ``generation/logits_process.py``)."""
+
     def __call__(self, input_ids: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
 class LogitsProcessorList(list):
+    """Applies its processors in order."""
+
     def __call__(self, input_ids, scores, **kw):
         for p in self:
             scores = p(input_ids, scores)
@@ -24,6 +29,8 @@ class LogitsProcessorList(list):
 
 
 class TemperatureLogitsWarper(LogitsProcessor):
+    """Divides the scores by ``temperature``."""
+
     def __init__(self, temperature: float):
         if not temperature > 0:
             raise ValueError(f"temperature must be positive, got {temperature}")
@@ -34,6 +41,9 @@ class TemperatureLogitsWarper(LogitsProcessor):
 
 
 class RepetitionPenaltyLogitsProcessor(LogitsProcessor):
+    """Scales the scores of tokens already in the sequence: positive ones divided, negative ones multiplied by
+    ``repetition_penalty``."""
+
     def __init__(self, repetition_penalty: float):
         if not repetition_penalty > 0:
             raise ValueError("repetition_penalty must be positive")
@@ -48,6 +58,8 @@ class RepetitionPenaltyLogitsProcessor(LogitsProcessor):
 
 
 class FrequencyPenaltyLogitsProcessor(LogitsProcessor):
+    """Subtracts ``frequency_penalty`` times the number of occurrences of every token so far."""
+
     def __init__(self, frequency_penalty: float, output_tokens_counts: Optional[torch.Tensor] = None):
         self.p = float(frequency_penalty)
 
@@ -59,6 +71,8 @@ class FrequencyPenaltyLogitsProcessor(LogitsProcessor):
 
 
 class PresencePenaltyLogitsProcessor(LogitsProcessor):
+    """Subtracts ``presence_penalty`` from every token that occurred at least once."""
+
     def __init__(self, presence_penalty: float):
         self.p = float(presence_penalty)
 
@@ -69,6 +83,8 @@ class PresencePenaltyLogitsProcessor(LogitsProcessor):
 
 
 class TopKLogitsWarper(LogitsProcessor):
+    """Keeps the ``top_k`` highest scores, sets the rest to ``filter_value``."""
+
     def __init__(self, top_k: int, filter_value: float = -float("inf"), min_tokens_to_keep: int = 1):
         if top_k <= 0:
             raise ValueError("top_k must be a positive integer")
@@ -81,6 +97,9 @@ class TopKLogitsWarper(LogitsProcessor):
 
 
 class TopPLogitsWarper(LogitsProcessor):
+    """Nucleus filter: keeps the smallest set of tokens whose probabilities sum to ``top_p`` (at least
+    ``min_tokens_to_keep``)."""
+
     def __init__(self, top_p: float, filter_value: float = -float("inf"), min_tokens_to_keep: int = 1):
         if not 0 <= top_p <= 1.0:
             raise ValueError("top_p must lie in [0, 1]")
@@ -96,6 +115,8 @@ class TopPLogitsWarper(LogitsProcessor):
 
 
 class MinLengthLogitsProcessor(LogitsProcessor):
+    """Forbids the end-of-sequence tokens until the sequence has ``min_length`` tokens."""
+
     def __init__(self, min_length: int, eos_token_id, pad_token_id: Optional[int] = None):
         self.min_length = int(min_length)
         self.eos = list(eos_token_id) if isinstance(eos_token_id, (list, tuple)) else [int(eos_token_id)]
@@ -111,11 +132,15 @@ class MinLengthLogitsProcessor(LogitsProcessor):
 
 
 class MinNewTokensLengthLogitsProcessor(MinLengthLogitsProcessor):
+    """Forbids the end-of-sequence tokens until ``min_new_tokens`` tokens were generated after the prompt."""
+
     def __init__(self, prompt_length_to_skip: int, min_new_tokens: int, eos_token_id, pad_token_id=None):
         super().__init__(prompt_length_to_skip + min_new_tokens, eos_token_id, pad_token_id)
 
 
 class LogitNormalization(LogitsProcessor):
+    """Replaces the scores by their log-softmax (after the other processors, so beam scores stay comparable)."""
+
     def __call__(self, input_ids, scores):
         return scores.log_softmax(dim=-1)
 

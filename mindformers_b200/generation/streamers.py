@@ -6,6 +6,9 @@ from typing import Optional
 
 
 class BaseStreamer:
+    """Receives tokens as ``generate()`` produces them: ``put(token_ids)`` per step, ``end()`` once (reference
+    ``generation/streamers.py``)."""
+
     def put(self, value):
         raise NotImplementedError
 

@@ -12,6 +12,8 @@ import numpy as np
 
 
 class BlockMemPool:
+    """Free list of KV-cache block ids (reference ``modules/block_tables.py:20-60``)."""
+
     def __init__(self, num_blocks: int, block_size: int):
         self.num_blocks, self.block_size = num_blocks, block_size
         self.free: List[int] = list(range(num_blocks - 1, -1, -1))

@@ -20,6 +20,10 @@ from ..ops import functional as Fn
 
 
 class KVCacheContext:
+    """Per-layer paged caches ``[num_blocks, block_size, kv_heads, head_dim]`` (or the 576-wide latent cache of
+    multi-latent attention) plus the metadata of the current step: block tables, slot mapping, context lengths, new
+    tokens per sequence."""
+
     def __init__(self, num_layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
                  dtype=torch.bfloat16, device="cuda", mla_latent_dim: Optional[int] = None):
         self.num_layers, self.num_blocks, self.block_size = num_layers, num_blocks, block_size

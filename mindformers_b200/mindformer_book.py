@@ -8,6 +8,9 @@ from .models.presets import PRESETS
 
 
 class MindFormerBook:
+    """Static catalogue of what the framework supports: trainers and pipelines per task, models per family, and the
+    project paths (reference ``mindformers/mindformer_book.py:59``)."""
+
     _PROJECT_PATH = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     _TRAINER_SUPPORT_TASKS_LIST = OrderedDict([
         ("general", ["common"]),

@@ -50,6 +50,10 @@ class InputBuilder:
 
 
 class ModelRunner:
+    """Serving-side model wrapper (reference ``mindformers/model_runner.py:138,199``): builds the model and tokenizer
+    from a directory and exposes ``forward(input_ids, valid_length_each_example, block_tables, slot_mapping, prefill,
+    ...)`` over the paged KV cache, plus KV block swapping between device and host (``swap``)."""
+
     def __init__(self, model_path: str, npu_mem_size: float, cpu_mem_size: float, block_size: int, rank_id: int = 0,
                  world_size: int = 1, npu_device_ids: Optional[Sequence[int]] = None, plugin_params: Optional[str] = None,
                  model=None, tokenizer=None):

@@ -70,6 +70,9 @@ def _auto_map_classes(path: str):
 
 
 class AutoConfig:
+    """Resolves a configuration class from a directory (``config.json`` ``model_type`` / ``auto_map``), a preset name or a
+    YAML file (reference ``models/auto/configuration_auto.py:189``): ``from_pretrained(name_or_path)``, ``for_model(model_type)``."""
+
     @staticmethod
     def from_pretrained(name_or_path: str, **kwargs) -> PretrainedConfig:
         dyn = _auto_map_classes(name_or_path)
@@ -92,6 +95,10 @@ class AutoConfig:
 
 
 class AutoModel:
+    """Builds the model class registered for a configuration (reference ``models/auto/auto_factory.py:217,764``):
+    ``from_config(config)`` with random weights, ``from_pretrained(directory)`` with the weights of a Hugging Face style
+    or framework directory. ``AutoModelForCausalLM`` is the same class: every registered model is a causal LM."""
+
     @staticmethod
     def from_config(config, **kwargs):
         """``config``: a ``PretrainedConfig``, a dict, a preset name, or a YAML / JSON path."""

@@ -16,6 +16,10 @@ CONFIG_NAME = "config.json"
 
 
 class PretrainedConfig:
+    """Hugging Face compatible model configuration (reference ``models/configuration_utils.py``): attribute access to
+    the keys of ``config.json``, class defaults via ``default_values()``, ``from_pretrained`` / ``from_dict`` /
+    ``from_json_file`` / ``to_dict`` / ``save_pretrained``; unknown keys are kept."""
+
     model_type: str = ""
     is_mla: bool = False
 

@@ -25,6 +25,8 @@ def _config(name, model_type, defaults, is_mla=False):
             return dict(base)
 
     _Cfg.__name__ = _Cfg.__qualname__ = name
+    _Cfg.__doc__ = (f"Configuration of the ``{model_type}`` family with Hugging Face key names; defaults: "
+                    + ", ".join(f"{k}={v!r}" for k, v in sorted(defaults.items())) + ".")
     _Cfg.model_type = model_type
     _Cfg.is_mla = is_mla
     MindFormerRegister.register_cls(_Cfg, MindFormerModuleType.CONFIG, alias=name)
@@ -38,6 +40,8 @@ def _model(name, cfg_cls, family):
         weight_family = family
 
     _M.__name__ = _M.__qualname__ = name
+    _M.__doc__ = (f"Causal language model of the ``{family}`` family: ``{cfg_cls.__name__}`` → ``GPTModel``; Hugging Face "
+                  f"checkpoints are mapped by the ``{family}`` name rules (``checkpoint/name_maps.py``).")
     MindFormerRegister.register_cls(_M, MindFormerModuleType.MODELS, alias=name)
     MindFormerRegister.register_cls(_M, MindFormerModuleType.MODELS, alias=name, legacy=False)
     return _M

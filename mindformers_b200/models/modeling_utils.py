@@ -25,6 +25,11 @@ from .configuration_utils import PretrainedConfig
 
 
 class PreTrainedModel(nn.Module, GenerationMixin, InferModelMixin):
+    """Base of the model classes (reference ``models/modeling_utils.py:216``): holds the Hugging Face keyed
+    ``config``, builds the ``GPTModel`` from it, and provides ``from_pretrained`` / ``save_pretrained`` (sharded
+    safetensors + ``config.json``), the name-conversion hooks (``convert_name``, ``convert_weight_dict``,
+    ``obtain_name_map``), ``generate()`` (``GenerationMixin``) and the serving helpers of ``InferModelMixin``."""
+
     config_class = PretrainedConfig
     base_model_prefix = "model"
     weight_family = "llama"

@@ -96,6 +96,8 @@ class BaseProcessor(ProcessorMixin):
 
 @MindFormerRegister.register(MindFormerModuleType.PROCESSOR)
 class LlamaProcessor(BaseProcessor):
+    """Tokenizer wrapper returning padded ``input_ids`` tensors (reference ``models/llama/llama_processor.py``)."""
+
     attributes = ["tokenizer"]
 
     def __init__(self, tokenizer=None, max_length: int = 128, padding: str = "max_length", return_tensors="pt", **kw):

@@ -93,6 +93,9 @@ class _SentencePieceMixin:
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class LlamaTokenizer(_SentencePieceMixin, PreTrainedTokenizer):
+    """SentencePiece tokenizer of Llama / Llama 2 (reference ``models/llama/llama_tokenizer.py``): ``tokenizer.model``,
+    optional BOS / EOS insertion, the Llama 2 chat template."""
+
     vocab_files_names = {"vocab_file": "tokenizer.model"}
     default_chat_template = LLAMA2_CHAT_TEMPLATE
 
@@ -404,6 +407,10 @@ class ChatGLM3Tokenizer(_GLMChatMixin, _SentencePieceMixin, PreTrainedTokenizer)
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class ChatGLM4Tokenizer(_GLMChatMixin, _TiktokenStyle):
+    """GLM-4 tokenizer (reference ``models/glm2/glm4_tokenizer.py``): tiktoken-style byte-pair ranks in
+    ``tokenizer.model``, the role tokens (``<|system|>``, ``<|user|>``, ...) and ``build_chat_input`` /
+    ``apply_chat_template`` with the ``[gMASK]<sop>`` prefix."""
+
     vocab_files_names = {"vocab_file": "tokenizer.model"}
     ROLE_TOKENS = ["<|endoftext|>", "[MASK]", "[gMASK]", "[sMASK]", "<sop>", "<eop>", "<|system|>", "<|user|>",
                    "<|assistant|>", "<|observation|>", "<|begin_of_image|>", "<|end_of_image|>",

@@ -11,6 +11,8 @@ from ..ops import functional as Fn
 
 
 class GELU(nn.Module):
+    """GELU, exact (erf) or tanh approximation."""
+
     def __init__(self, approximate: bool = True):
         super().__init__()
         self.approximate = "tanh" if approximate else "none"
@@ -27,6 +29,8 @@ class FastGelu(nn.Module):
 
 
 class SiLU(nn.Module):
+    """``x * sigmoid(x)``."""
+
     def forward(self, x):
         return F.silu(x)
 
@@ -39,10 +43,14 @@ class SwiGLU(nn.Module):
 
 
 class LeakyReLU(nn.LeakyReLU):
+    """Leaky ReLU with slope ``alpha`` for negative inputs."""
+
     pass
 
 
 class LogSoftmax(nn.LogSoftmax):
+    """Log-softmax over ``axis``."""
+
     pass
 
 

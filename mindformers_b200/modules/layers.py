@@ -15,7 +15,8 @@ from .activation import get_activation
 
 
 class Linear(nn.Module):
-    """``y = act(x W^T + b)``; with ``expert_num > 1`` the weight is ``[E, out, in]`` and ``x`` is ``[E, tokens, in]``."""
+    """``y = act(x W^T + b)``; with ``expert_num > 1`` the weight is ``[E, out, in]`` and ``x`` is ``[E, tokens, in]``.
+    ``y = act(x W^T + b)``; with ``expert_num > 1`` the weight is ``[E, out, in]`` and ``x`` is ``[E, tokens, in]``."""
 
     def __init__(self, in_channels: int, out_channels: int, has_bias: bool = True, activation=None, expert_num: int = 1,
                  use_gmm: bool = False, transpose_b: bool = True, param_init_type=torch.float32, compute_dtype=torch.bfloat16,
@@ -45,6 +46,9 @@ class Linear(nn.Module):
 
 
 class LayerNorm(nn.Module):
+    """LayerNorm with the legacy stack's argument names (``normalized_shape``, ``eps``, ``param_init_type``); fp32
+    statistics."""
+
     def __init__(self, normalized_shape, eps: float = 1e-5, param_init_type=torch.float32, device=None):
         super().__init__()
         shape = (normalized_shape,) if isinstance(normalized_shape, int) else tuple(normalized_shape)
@@ -57,6 +61,8 @@ class LayerNorm(nn.Module):
 
 
 class Dropout(nn.Module):
+    """Dropout configured by keep probability, as the legacy layers do (``keep_prob=1`` is the identity)."""
+
     def __init__(self, keep_prob: float = 1.0):
         super().__init__()
         self.p = 1.0 - keep_prob
@@ -141,7 +147,8 @@ def apply_rotary(x, cos, sin):
 
 
 class AlibiTensor(nn.Module):
-    """Attention bias ``slope_h * (key_pos - query_pos)`` per head (``AlibiTensorV2`` semantics: computed from positions)."""
+    """Attention bias ``slope_h * (key_pos - query_pos)`` per head (``AlibiTensorV2`` semantics: computed from
+    positions)."""
 
     def __init__(self, seq_length: int, num_heads: int):
         super().__init__()

@@ -15,6 +15,9 @@ import torch.nn.functional as F
 
 @dataclass
 class MoEConfig:
+    """Legacy MoE settings (reference ``modules/transformer/moe.py:88``): expert count, capacity factor, experts per
+    token, drop policy, auxiliary-loss kinds and factors, shared experts, group-limited routing."""
+
     expert_num: int = 1
     capacity_factor: float = 1.1
     aux_loss_factor: float = 0.05

@@ -23,12 +23,17 @@ from ..parallel.layers.tensor_parallel import ColumnParallelLinear, LinearNoTP, 
 
 @dataclass
 class QuantizationConfig:
+    """Base quantisation settings (reference ``utils/quantization_config.py:67``): ``quant_method``, weight / activation
+    / KV-cache dtypes, modules to skip."""
+
     quant_method: str = "rtn"
     modules_to_not_convert: Optional[Iterable[str]] = None
 
 
 @dataclass
 class RtnConfig(QuantizationConfig):
+    """Round-to-nearest weight-only quantisation (int8 / int4, per channel or per group)."""
+
     quant_method: str = "rtn"
     weight_dtype: str = "int8"          # int8 | int4
     group_size: int = 0                 # 0 = one scale per output channel
@@ -36,6 +41,9 @@ class RtnConfig(QuantizationConfig):
 
 @dataclass
 class PtqConfig(QuantizationConfig):
+    """Post-training quantisation: int8 weights and activations with calibrated per-channel scales, optional int8 KV
+    cache."""
+
     quant_method: str = "ptq"
     weight_dtype: str = "int8"
     activation_dtype: str = "int8"
@@ -44,12 +52,17 @@ class PtqConfig(QuantizationConfig):
 
 @dataclass
 class SmoothQuantConfig(PtqConfig):
+    """SmoothQuant W8A8: activation outliers migrated into the weights by a per-channel smoothing factor ``alpha``."""
+
     quant_method: str = "smooth_quant"
     alpha: float = 0.5
 
 
 @dataclass
 class Fp8BlockConfig(QuantizationConfig):
+    """Block-scaled fp8 (e4m3) weights with one scale per 128 x 128 block, activations per 1 x 128 block (the
+    DeepSeek-V3 checkpoint format)."""
+
     quant_method: str = "fp8"
     fmt: str = "e4m3"
     weight_block_size: tuple = (128, 128)

@@ -14,6 +14,10 @@ _DATA_PARALLEL = "data-parallel-rng"
 
 
 class CudaRNGStatesTracker:
+    """Named random-number states (reference ``inference/tensor_parallel/random.py:47``): ``fork(name)`` runs a block
+    under the state registered for ``name`` so that tensor-parallel ranks draw different dropout masks and identical
+    initial weights."""
+
     def __init__(self):
         self.states: Dict[str, torch.Tensor] = {}
         self.seeds = set()
@@ -60,7 +64,8 @@ def get_rng_tracker() -> CudaRNGStatesTracker:
 
 
 def model_parallel_manual_seed(seed: int):
-    """Default generator: ``seed`` (same on all TP ranks); tracked model-parallel generator: ``seed + 2718 + tp_rank``."""
+    """Default generator: ``seed`` (same on all TP ranks); tracked model-parallel generator: ``seed + 2718 + tp_rank``.
+    Default generator: ``seed`` (same on all TP ranks); tracked model-parallel generator: ``seed + 2718 + tp_rank``."""
     _TRACKER.reset()
     torch.manual_seed(seed)
     _TRACKER.add(_DATA_PARALLEL, seed + 1)

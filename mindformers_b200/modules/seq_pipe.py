@@ -9,6 +9,10 @@ import torch
 
 
 class SequenceSplit:
+    """Sequence-pipeline chunking (reference ``modules/seq_pipe.py:21,64-119``): slices the sequence axis into
+    ``seq_split_num`` chunks that flow through the pipeline one after the other, relying on the KV cache of the
+    earlier chunks."""
+
     def __init__(self, seq_split_num: int, seq_dim: int = 1):
         if seq_split_num < 1:
             raise ValueError("seq_split_num must be >= 1")

@@ -28,6 +28,8 @@ c_float = ctypes.c_float
 
 
 class KernelLibraryError(RuntimeError):
+    """The sm_100a kernel library is missing, stale, or one of its entry points returned an error code."""
+
     pass
 
 

@@ -40,6 +40,8 @@ def _category(name: str, p: torch.Tensor, tp: int, sequence_parallel: bool) -> i
 
 @dataclass
 class BufferRanges:
+    """Where a parameter sits inside a flat bucket buffer and which slice of the bucket each data-parallel rank owns."""
+
     numel: int = 0            # padded to a multiple of pad_to
     decay_end: int = 0        # [0, decay_end) gets weight decay
     dup_begin: int = 0        # [dup_begin, dup_end) is replicated over tensor-parallel ranks

@@ -18,6 +18,10 @@ from .optimizer import DistributedOptimizer
 
 
 class TrainOneStep:
+    """Forward + backward over the micro-batches of a step, gradient reduction, overflow / NaN check, global-norm
+    clipping, optimizer step and loss-scale update (reference ``wrapper/wrapper.py:303`` ``MFTrainOneStepCell``).
+    ``__call__(batch)`` returns ``{loss, global_norm, skipped, loss_scale}`` as device tensors."""
+
     def __init__(self, model: torch.nn.Module, optimizer: DistributedOptimizer, *, micro_batch_size: int = 1,
                  loss_scale: float = 1.0, forward_fn: Optional[Callable] = None):
         self.model, self.optimizer = model, optimizer

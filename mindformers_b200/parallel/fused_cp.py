@@ -30,6 +30,9 @@ from . import symm_mem
 
 
 class CPExchange:
+    """Peer-memory state of the context-parallel K/V exchange of one group: symmetric K/V and dK/dV buffers, flag words,
+    epoch counter."""
+
     _instances: Dict[tuple, "CPExchange"] = {}
 
     @classmethod

@@ -27,6 +27,9 @@ from .transformer_layer import TransformerBlock
 
 
 class LanguageModelEmbedding(nn.Module):
+    """Word embedding (vocabulary-parallel), flattened to ``[tokens, hidden]``, scattered over the sequence-parallel
+    ranks when those are on (reference ``base_models/common/embeddings/language_model_embedding.py:31``)."""
+
     def __init__(self, config):
         super().__init__()
         sp = bool(config.sequence_parallel) and ps.get_tensor_model_parallel_world_size() > 1
@@ -39,6 +42,12 @@ class LanguageModelEmbedding(nn.Module):
 
 
 class GPTModel(nn.Module):
+    """The decoder-only model for training and inference (reference ``base_models/gpt/gpt_model.py``): embedding →
+    rotary tables → ``TransformerBlock`` → optional multi-token-prediction block → output layer (tied or untied) →
+    fp32 logits, or the masked cross-entropy when ``labels`` are given. ``forward(input_ids, labels=None,
+    loss_mask=None, position_ids=None, attn_meta=None, input_embeds=None)``; ``update_topk_bias()`` applies the
+    auxiliary-loss-free router balancing."""
+
     def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None,
                  share_embeddings_and_output_weights: Optional[bool] = None):
         super().__init__()

@@ -25,6 +25,10 @@ class VocabParallelCrossEntropy(nn.Module):
 
 
 class CrossEntropyLoss(nn.Module):
+    """Masked vocabulary-parallel cross-entropy (reference ``training_graph/loss_func.py:35-139``): fp32 statistics,
+    returns ``sum(loss * mask) / (sum(mask) + 1e-8)`` or the ``(numerator, denominator)`` pair for pipeline /
+    sequence-pipeline accumulation."""
+
     def __init__(self, calculate_per_token_loss: bool = False, eps: float = 1e-8):
         super().__init__()
         self.per_token = calculate_per_token_loss

@@ -24,6 +24,10 @@ def get_activation(name: str):
 
 
 class MLP(nn.Module):
+    """Gated MLP: ``linear_fc1`` (column-parallel, gate and up projections fused) → SwiGLU → ``linear_fc2``
+    (row-parallel; reduce-scatter under sequence parallelism). Returns ``(output, bias)`` (reference
+    ``training_graph/transformer/mlp.py:38,127-167``)."""
+
     def __init__(self, config, ffn_hidden_size=None, is_expert: bool = False, input_size=None):
         super().__init__()
         self.config = config

@@ -22,6 +22,10 @@ def roll_left(t: torch.Tensor, fill=0):
 
 
 class MultiTokenPredictionLayer(nn.Module):
+    """One multi-token-prediction depth (reference ``training_graph/transformer/multi_token_prediction.py:87``): norms
+    of the shifted embedding and the previous hidden state, ``eh_proj`` (2H → H), one transformer layer, final
+    norm."""
+
     def __init__(self, config):
         super().__init__()
         self.enorm = build_norm(config)
@@ -41,6 +45,9 @@ class MultiTokenPredictionLayer(nn.Module):
 
 
 class MultiTokenPredictionBlock(nn.Module):
+    """Runs the MTP layers on tokens rolled left by one per depth and returns their scaled cross-entropy
+    (``mtp_loss_scaling_factor / mtp_num_layers`` each) through the shared embedding and output head."""
+
     def __init__(self, config):
         super().__init__()
         self.config = config

@@ -15,6 +15,10 @@ from ...ops import functional as Fn
 
 
 class RMSNorm(nn.Module):
+    """Root-mean-square norm with an optional fused residual add: ``forward(x, residual=None)`` returns ``norm(x +
+    residual) * weight`` (and the new residual stream when one was given). fp32 statistics; the CUDA kernel is
+    ``ops/csrc/norm.cu`` (reference ``training_graph/transformer/norm.py:243`` ``FusedRMSNorm``)."""
+
     def __init__(self, config, hidden_size: int, eps: float = 1e-5):
         super().__init__()
         dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -31,6 +35,9 @@ class RMSNorm(nn.Module):
 
 
 class LayerNorm(nn.Module):
+    """LayerNorm with the same calling convention as ``RMSNorm`` (reference
+    ``training_graph/transformer/norm.py:38,115``)."""
+
     def __init__(self, config, hidden_size: int, eps: float = 1e-5):
         super().__init__()
         dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")

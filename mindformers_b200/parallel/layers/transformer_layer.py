@@ -38,6 +38,10 @@ class TransformerLayerSubmodules:
 
 
 class TransformerLayer(nn.Module):
+    """Pre-LN block: ``input_layernorm`` → ``self_attention`` → ``pre_mlp_layernorm`` → ``mlp`` (dense or MoE), optional
+    sandwich norms; the residual adds are folded into the norms. Built from a ``TransformerLayerSubmodules`` spec
+    (reference ``training_graph/transformer/transformer_layer.py:74-250``)."""
+
     def __init__(self, config, layer_number: int = 1, is_moe: bool = False,
                  submodules: Optional[TransformerLayerSubmodules] = None):
         super().__init__()

@@ -13,6 +13,9 @@ from typing import Any, Tuple, Union
 
 @dataclass
 class ModuleSpec:
+    """``module`` (a class, a ``(module path, name)`` pair or a callable) + fixed ``params`` + the specs of its
+    ``submodules``."""
+
     module: Union[type, Tuple[str, str], Any]
     params: dict = field(default_factory=dict)
     submodules: Any = None

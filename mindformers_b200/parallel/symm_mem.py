@@ -19,6 +19,9 @@ def is_ready() -> bool:
 
 
 class SymmBuffer:
+    """A peer-mapped allocation: the local tensor, the device pointers of the same buffer on every rank of the group
+    (``ptrs``) and the handle that keeps the mapping alive."""
+
     def __init__(self, tensor, handle):
         self.tensor = tensor
         self.handle = handle

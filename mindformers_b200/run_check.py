@@ -16,6 +16,9 @@ VERSION = "1.6.0+b200"
 
 
 class MFCheck:
+    """Installation self-check (reference ``mindformers/run_check.py:108``): version line, kernel library, a two-layer
+    Llama trained for a few steps, a short generation; prints one verdict per stage."""
+
     def __init__(self, steps: int = 3, device: str = None):
         self.steps = steps
         self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -92,6 +95,8 @@ class MFCheck:
 
 
 def run_check(log_level: str = "info") -> bool:
+    """Installation self-check (reference ``mindformers/run_check.py:366``): returns True when every stage passed."""
+
     return MFCheck().check()
 
 

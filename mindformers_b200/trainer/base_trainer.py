@@ -312,6 +312,10 @@ class BaseTrainer:
 
 @MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["text_generation"])
 class CausalLanguageModelingTrainer(BaseTrainer):
+    """Task trainer for causal language models (reference
+    ``trainer/causal_language_modeling/causal_language_modeling.py:47-439``): ``train``, ``evaluate`` (perplexity),
+    ``generate_evaluate`` (generate then score) and ``predict``."""
+
     task = "text_generation"
 
     def train(self, config, **kw):
@@ -346,6 +350,9 @@ class GeneralTaskTrainer(CausalLanguageModelingTrainer):
 
 @MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["multi_modal_to_text_generation"])
 class MultiModalToTextGenerationTrainer(CausalLanguageModelingTrainer):
+    """Task trainer for image / multimodal-to-text models (reference ``trainer/multi_modal_to_text_generation/``): the
+    causal-LM flow with a processor that also yields the modality tensors."""
+
     task = "multi_modal_to_text_generation"
 
 

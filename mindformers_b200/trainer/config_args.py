@@ -17,6 +17,9 @@ from typing import Any, Dict, List, Optional
 
 
 class BaseArgsConfig:
+    """Base of the dataclass mirrors of the YAML sections (reference ``trainer/config_args.py``): keeps unknown keys,
+    drops ``None`` values in ``to_dict``."""
+
     _support_kwargs: List[str] = []
     _section: Optional[str] = None          # YAML section this class mirrors
 

@@ -23,6 +23,10 @@ from ..parallel.transformer_config_utils import convert_to_transformer_config
 
 
 class TrainingEngine:
+    """One model + distributed optimizer + train step behind ``train_step(batch) -> {loss, global_norm, ...}``: the unit
+    that ``bench.py`` and the trainers drive (reference ``wrapper/wrapper.py`` ``MFTrainOneStepCell`` plus the model /
+    optimizer construction of ``trainer/base_trainer.py``)."""
+
     def __init__(self, model: torch.nn.Module, optimizer: DistributedOptimizer, micro_batch_size: int = 1,
                  loss_scale: float = 1.0):
         self.model = model

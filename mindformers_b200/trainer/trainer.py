@@ -36,6 +36,11 @@ DEFAULT_TASK_CONFIG = {
 
 
 class Trainer:
+    """High-level entry point (reference ``trainer/trainer.py:180-325``): ``Trainer(args=config file | dict |
+    TrainingArguments, task=..., model=..., train_dataset=..., eval_dataset=..., callbacks=...)`` then ``train()``,
+    ``finetune()``, ``evaluate()``, ``predict()``. Builds the context, the parallel groups, the task trainer
+    registered for ``task`` and hands it the merged configuration."""
+
     def __init__(self, args: Optional[Union[str, dict, MindFormerConfig, TrainingArguments]] = None, task: str = "general",
                  model=None, model_name: Optional[str] = None, tokenizer=None, train_dataset=None, eval_dataset=None,
                  data_collator: Optional[Callable] = None, optimizers=None, compute_metrics=None,

@@ -9,6 +9,10 @@ from typing import List, Optional, Union
 
 @dataclass
 class TrainingArguments:
+    """Hugging Face style training arguments (reference ``trainer/training_args.py``): a dataclass of about 200 fields
+    that ``convert_args_to_mindformers_config`` maps onto the YAML sections (runner, optimizer, schedule, parallel,
+    callbacks, checkpointing)."""
+
     output_dir: str = "./output"
     overwrite_output_dir: bool = False
     seed: int = 42

@@ -1,0 +1,48 @@
+"""The documented public API carries docstrings, and deprecated entry points say so when used."""
+import importlib
+import warnings
+
+import pytest
+
+PUBLIC = {
+    "mindformers_b200": ["AutoConfig", "AutoModel", "AutoModelForCausalLM", "AutoProcessor", "AutoTokenizer", "ModelRunner",
+                         "Trainer", "TrainingArguments", "pipeline", "run_check"],
+    "mindformers_b200.core": ["AdamW", "CrossEntropyLoss", "MFLossMonitor", "CheckpointMonitor", "CosineWithWarmUpLR",
+                              "PerplexityMetric", "build_context"],
+    "mindformers_b200.generation": ["GenerationConfig", "GenerationMixin"],
+    "mindformers_b200.models": ["LlamaConfig", "LlamaForCausalLM", "LlamaTokenizer", "LlamaTokenizerFast",
+                                "PreTrainedModel", "PreTrainedTokenizer", "PretrainedConfig", "ChatGLM4Tokenizer"],
+    "mindformers_b200.core.parallel_config": ["OpParallelConfig"],
+    "mindformers_b200.pet": ["LoraModel", "LoraConfig", "PetConfig"],
+    "mindformers_b200.pipeline": ["MultiModalToTextPipeline"],
+    "mindformers_b200.tools.register": ["MindFormerConfig", "MindFormerRegister", "MindFormerModuleType"],
+    "mindformers_b200.wrapper": ["MFTrainOneStepCell", "MFPipelineWithLossScaleCell"],
+    "mindformers_b200.dataset": ["CausalLanguageModelDataset", "KeyWordGenDataset", "MultiTurnDataset"],
+}
+
+
+@pytest.mark.parametrize("module", sorted(PUBLIC))
+def test_public_api_is_importable_and_documented(module):
+    mod = importlib.import_module(module)
+    missing = []
+    for name in PUBLIC[module]:
+        obj = getattr(mod, name, None)
+        if obj is None:
+            missing.append(f"{name}: not exported")
+        elif not (getattr(obj, "__doc__", None) or "").strip():
+            missing.append(f"{name}: no docstring")
+    assert not missing, missing
+
+
+def test_deprecated_decorator_warns_once_with_the_replacement():
+    from mindformers_b200.utils.decorators import deprecated
+
+    @deprecated("use new_function", version="1.6")
+    def old_function():
+        return 7
+
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        assert old_function() == 7
+    text = " ".join(str(w.message) for w in seen)
+    assert "old_function" in text and "new_function" in text
