@@ -57,6 +57,9 @@ class RunContext:
 
 
 class Callback:
+    """Hooks that the training loop calls: ``on_train_begin/end``, ``on_epoch_begin/end``, ``on_step_begin/end``,
+    each with the ``RunContext``."""
+
     def on_train_begin(self, ctx: RunContext): ...
     def on_step_begin(self, ctx: RunContext): ...
     def on_step_end(self, ctx: RunContext): ...

@@ -8,6 +8,9 @@ import torch
 
 
 class ClipGradNorm:
+    """Global-norm clipping (reference ``core/clip_grad.py:60-101``): ``norm = sqrt(sum ||g||^2)``, gradients scaled
+    by ``min(1, max_norm / (norm + 1e-6))``; returns the gradients and the norm."""
+
     def __init__(self, max_norm: float = 1.0, use_norm=None):
         self.max_norm = float(max_norm)
         self.use_norm = use_norm

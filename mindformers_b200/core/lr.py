@@ -112,6 +112,9 @@ class CosineWithRestartsAndWarmUpLR(CosineWithWarmUpLR):
 
 @MindFormerRegister.register(MindFormerModuleType.LR)
 class PolynomialWithWarmUpLR(_Schedule):
+    """Linear warm-up, then polynomial decay of degree ``power`` to ``lr_end`` at ``total_steps`` (reference
+    ``core/lr/lr_schedule.py``)."""
+
     def __init__(self, learning_rate, total_steps=-1, lr_end: float = 1e-7, power: float = 1.0, **kw):
         super().__init__(learning_rate, total_steps=total_steps, **kw)
         self.lr_end, self.power = lr_end, power
@@ -188,6 +191,8 @@ class CosineAnnealingLR(_Schedule):
 
 @MindFormerRegister.register(MindFormerModuleType.LR)
 class CosineAnnealingWarmRestarts(_Schedule):
+    """Cosine annealing restarted every ``t_0 * t_mult^i`` steps (SGDR)."""
+
     def __init__(self, base_lr, t_0: int, t_mult: int = 1, eta_min: float = 0.0, **kw):
         super().__init__(base_lr, **kw)
         if t_0 <= 0 or t_mult < 1:

@@ -58,6 +58,9 @@ class _PipeLineConfig:
 
 @dataclass
 class TransformerRecomputeConfig:
+    """``recompute_config`` section: full (``recompute``), selective (``select_recompute`` patterns) and
+    communication recomputation switches."""
+
     recompute: Union[bool, list] = False
     select_recompute: Union[bool, list] = False
     parallel_optimizer_comm_recompute: bool = False
@@ -70,6 +73,9 @@ class TransformerRecomputeConfig:
 
 @dataclass
 class TransformerSwapConfig:
+    """``swap_config`` section: which layers / operators keep their activations in host memory and how far ahead they
+    are fetched back."""
+
     swap: bool = False
     default_prefetch: int = 1
     layer_swap: Optional[list] = None
@@ -78,6 +84,8 @@ class TransformerSwapConfig:
 
 @dataclass
 class MoEParallelConfig:
+    """Degrees seen by an MoE layer: data, model, expert, context."""
+
     data_parallel: int = 1
     model_parallel: int = 1
     expert_parallel: int = 1
@@ -86,6 +94,10 @@ class MoEParallelConfig:
 
 @dataclass
 class TransformerOpParallelConfig:
+    """``parallel_config`` section as an object (reference ``modules/transformer/transformer.py:535-700``): data /
+    model / context / expert / pipeline degrees, micro-batches, sequence parallelism, context-parallel algorithm,
+    with the recompute and swap configurations attached."""
+
     data_parallel: int = 1
     model_parallel: int = 1
     context_parallel: int = 1

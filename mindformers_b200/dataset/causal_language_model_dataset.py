@@ -125,6 +125,9 @@ def _is_number(x) -> bool:
 
 @MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
 class IndexedDataLoader:
+    """Samples of ``seq_length + 1`` tokens cut from one ``.bin`` / ``.idx`` prefix (reference
+    ``dataset/dataloader/indexed_dataset.py``)."""
+
     def __new__(cls, path_prefix: str, seq_length: int = 4096, num_samples: Optional[int] = None, seed: int = 1234, **kw):
         from .indexed_dataset import IndexedDataset
         indexed = IndexedDataset(path_prefix)
@@ -143,6 +146,8 @@ class CommonDataLoader:
 
 @MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
 class MockDataLoader:
+    """Uniform random token ids of the configured shape: data for benchmarks and smoke runs."""
+
     def __new__(cls, seq_length: int = 4096, vocab_size: int = 32000, num_samples: int = 1 << 20, seed: int = 1234, **kw):
         return MockGPTDataset(num_samples, GPTDatasetConfig(sequence_length=seq_length, random_seed=seed,
                                                             vocab_size=vocab_size), vocab_size)

@@ -389,6 +389,9 @@ class TrainingDataset(IterableDataset):
 
 @MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
 class TrainingDataLoader:
+    """Text files (plain or JSON lines) tokenised and packed into ``seq_length`` samples on the fly (reference
+    ``dataset/dataloader/training_dataloader.py``)."""
+
     def __new__(cls, dataset_dir: str, tokenizer, column_names=("input_ids",), max_length: int = 1025,
                 text_col: str = "text", file_format: Optional[str] = None, shuffle: bool = False,
                 samples_num: Optional[int] = None, skip_num: int = 0, **kw):

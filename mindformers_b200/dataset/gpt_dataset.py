@@ -23,6 +23,10 @@ from .indexed_dataset import IndexedDataset
 
 @dataclass
 class GPTDatasetConfig:
+    """Settings of the Megatron-style GPT dataset: sequence length, seed, split, blend, end-of-document handling
+    (``reset_position_ids``, ``reset_attention_mask``, ``eod_mask_loss``, ``create_compressed_eod_mask``), cache
+    directory."""
+
     sequence_length: int
     random_seed: int = 1234
     blend: Optional[Tuple[List[str], Optional[List[float]]]] = None

@@ -57,6 +57,9 @@ class BaseInstructDataHandler:
 
 @MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
 class AlpacaInstructDataHandler(BaseInstructDataHandler):
+    """Alpaca records (``instruction``, optional ``input``, ``output``) rendered with the Alpaca prompt; only the
+    response carries loss."""
+
     def format(self, r):
         tpl = ALPACA_WITH_INPUT if r.get("input") else ALPACA_NO_INPUT
         return tpl.format(instruction=r.get("instruction", ""), input=r.get("input", "")), r.get("output", "")
@@ -64,11 +67,15 @@ class AlpacaInstructDataHandler(BaseInstructDataHandler):
 
 @MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
 class CodeAlpacaInstructDataHandler(AlpacaInstructDataHandler):
+    """Code-Alpaca records: the Alpaca format."""
+
     pass
 
 
 @MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
 class AdgenInstructDataHandler(BaseInstructDataHandler):
+    """ADGEN records: ``content`` is the prompt, ``summary`` the target."""
+
     def format(self, r):
         return r.get("content", ""), r.get("summary", "")
 

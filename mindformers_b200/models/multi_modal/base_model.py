@@ -21,6 +21,8 @@ from ..modeling_utils import PreTrainedModel
 
 
 class VisionConfig(PretrainedConfig):
+    """Vision tower settings: image and patch size, width, depth, heads, MLP width."""
+
     model_type = "vit"
 
     @classmethod
@@ -31,6 +33,8 @@ class VisionConfig(PretrainedConfig):
 
 
 class ViTBlock(nn.Module):
+    """Pre-LN vision transformer block (bidirectional attention + GELU MLP)."""
+
     def __init__(self, c: VisionConfig, dtype):
         super().__init__()
         h = c.hidden_size
@@ -90,7 +94,8 @@ class BaseXModalToTextModel(nn.Module):
     @staticmethod
     def update_modal_to_text(modal_embeds: torch.Tensor, text_embeds: torch.Tensor,
                              modal_context_pos: torch.Tensor) -> torch.Tensor:
-        """``modal_embeds [n, L, H]`` go to ``text_embeds[b, p]`` for every ``(b, p)`` of ``modal_context_pos [n, L, 2]``."""
+        """``modal_embeds [n, L, H]`` go to ``text_embeds[b, p]`` for every ``(b, p)`` of ``modal_context_pos [n, L,
+        2]``."""
         pos = modal_context_pos.reshape(-1, 2).to(text_embeds.device)
         out = text_embeds.clone()
         out[pos[:, 0], pos[:, 1]] = modal_embeds.reshape(-1, modal_embeds.shape[-1]).to(out.dtype)
@@ -101,6 +106,9 @@ class BaseXModalToTextModel(nn.Module):
 
 
 class ImageToTextConfig(PretrainedConfig):
+    """Configuration of ``ImageToTextModel``: ``vision_config``, ``text_config`` (any registered causal-LM
+    configuration), projector width and the id of the image placeholder token."""
+
     model_type = "image_to_text"
 
     @classmethod

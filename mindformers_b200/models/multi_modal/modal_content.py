@@ -31,6 +31,10 @@ class DataRecord(dict):
 
 
 class ModalContentBuilder:
+    """Turns the tagged content of one modality (for example ``<img>path</img>``) into model inputs: loads and
+    encodes the content, pads the token sequence with ``context_length`` placeholder tokens per item and reports
+    their positions (reference ``models/multi_modal/modal_content.py:37``)."""
+
     def __init__(self, type_: str, context_pad_token: str, context_length: int, use_custom_token_pos: bool = False,
                  start_token: Optional[str] = None, end_token: Optional[str] = None, tokenizer=None,
                  need_padding_context: bool = True, modal_content_max_size: int = 1, mode: str = "predict",
@@ -127,6 +131,8 @@ class ModalContentBuilder:
 
 
 class BaseTextContentBuilder(ModalContentBuilder):
+    """The text part of a query: passes the string through."""
+
     def __init__(self, **kwargs):
         super().__init__("text", "", 0, need_padding_context=False, **kwargs)
 

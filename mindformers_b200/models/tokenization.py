@@ -13,6 +13,9 @@ from ..tools.register import MindFormerModuleType, MindFormerRegister
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class ByteTokenizer:
+    """Tokenizer without a vocabulary file: UTF-8 bytes shifted past the special ids. Used by tests, ``run_check``
+    and as the fallback when a model directory has no tokenizer."""
+
     pad_token, bos_token, eos_token, unk_token = "<pad>", "<s>", "</s>", "<unk>"
 
     def __init__(self, add_bos_token: bool = True, add_eos_token: bool = False, **kw):

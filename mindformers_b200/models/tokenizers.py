@@ -115,6 +115,9 @@ class LlamaTokenizer(_SentencePieceMixin, PreTrainedTokenizer):
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class TelechatTokenizer(LlamaTokenizer):
+    """SentencePiece tokenizer of TeleChat with its ``<_user>`` / ``<_bot>`` / ``<_system>`` role tokens (reference
+    ``research/telechat2/telechat_tokenizer.py``)."""
+
     def __init__(self, vocab_file: str, unk_token="<unk>", bos_token="<_start>", eos_token="<_end>",
                  pad_token="<_pad>", add_bos_token: bool = False, add_eos_token: bool = False, **kwargs):
         kwargs.setdefault("additional_special_tokens", ["<_user>", "<_bot>", "<_system>"])
@@ -271,6 +274,9 @@ def _ranks_from_tokenizer_json(path: str) -> Dict[bytes, int]:
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class Llama3Tokenizer(_TiktokenStyle):
+    """Llama 3 / 3.1 tokenizer (reference ``research/llama3_1/llama3_1_tokenizer.py``): tiktoken-style byte-pair
+    ranks, the 256 reserved special tokens, the header / end-of-turn chat template."""
+
     vocab_files_names = {"vocab_file": "tokenizer.model"}
     default_chat_template = LLAMA3_CHAT_TEMPLATE
 
@@ -291,6 +297,9 @@ class Llama3Tokenizer(_TiktokenStyle):
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class Qwen2Tokenizer(_TiktokenStyle):
+    """Byte-level BPE tokenizer of Qwen2 / Qwen2.5 / Qwen3 (reference ``research/qwen2_5/qwen2_5_tokenizer.py``):
+    ``vocab.json`` + ``merges.txt``, ``<|im_start|>`` / ``<|im_end|>`` ChatML template."""
+
     vocab_files_names = {"vocab_file": "vocab.json", "merges_file": "merges.txt"}
     pattern = QWEN2_PATTERN
     default_chat_template = CHATML_TEMPLATE
@@ -385,6 +394,9 @@ class _GLMChatMixin:
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class ChatGLM3Tokenizer(_GLMChatMixin, _SentencePieceMixin, PreTrainedTokenizer):
+    """SentencePiece tokenizer of ChatGLM3 (reference ``models/glm2/glm3_tokenizer.py``): role tokens appended after
+    the SentencePiece vocabulary, ``[gMASK] sop`` prefix, ``build_chat_input``."""
+
     vocab_files_names = {"vocab_file": "tokenizer.model"}
     ROLE_TOKENS = ["[MASK]", "[gMASK]", "[sMASK]", "sop", "eop", "<|system|>", "<|user|>", "<|assistant|>",
                    "<|observation|>"]

@@ -21,6 +21,9 @@ import torch.nn.functional as F
 
 
 class LocalBlockSparseAttention(nn.Module):
+    """``forward(q, k, v, attention_mask=None)`` on ``[batch, heads, seq, head_dim]``: every query block attends to
+    the ``local_size / block_size`` key blocks ending with its own, causally inside the diagonal block."""
+
     def __init__(self, seq_len: int, size_per_head: int, local_size: int, block_size: int, dropout_rate: float = 0.1,
                  softmax_compute_type=torch.float32, parallel_config=None):
         super().__init__()

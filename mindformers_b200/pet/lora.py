@@ -123,6 +123,10 @@ class RowParallelLinearWithLoRA(LoRALinear):
 
 
 class LoraAdapter:
+    """``get_pet_model(model, config)``: replaces the linear layers matched by ``target_modules`` with their LoRA
+    versions and freezes everything else (reference ``pet/tuners/lora_adapter.py:59,153``
+    ``recursive_replace_dense_cell``)."""
+
     @staticmethod
     def recursive_replace_dense_cell(module: nn.Module, config: LoraConfig, prefix: str = "") -> int:
         """Replace every linear layer whose qualified name matches ``config.target_modules``; returns the count."""

@@ -9,6 +9,9 @@ from ..tools.register.register import MindFormerModuleType, MindFormerRegister
 
 @dataclass
 class PetConfig:
+    """Base of the parameter-efficient tuning configurations (reference ``pet/pet_config.py``): ``pet_type`` selects
+    the adapter."""
+
     pet_type: Optional[str] = None
 
     def to_dict(self):
@@ -37,6 +40,8 @@ class LoraConfig(PetConfig):
 @MindFormerRegister.register(MindFormerModuleType.CONFIG, alias="SLoraConfig")
 @dataclass
 class SLoraConfig(PetConfig):
+    """Multi-adapter LoRA serving: directory of adapters, maximum rank, target modules."""
+
     pet_type: str = "slora"
     lora_num: int = 1
     lora_rank: int = 8
@@ -49,6 +54,8 @@ class SLoraConfig(PetConfig):
 @MindFormerRegister.register(MindFormerModuleType.CONFIG, alias="PrefixTuningConfig")
 @dataclass
 class PrefixTuningConfig(PetConfig):
+    """Prefix tuning: ``prefix_token_num`` trainable key / value vectors per layer."""
+
     pet_type: str = "prefixtuning"
     prefix_token_num: int = 16
     mid_dim: int = 512
@@ -58,6 +65,8 @@ class PrefixTuningConfig(PetConfig):
 @MindFormerRegister.register(MindFormerModuleType.CONFIG, alias="Ptuning2Config")
 @dataclass
 class Ptuning2Config(PetConfig):
+    """P-Tuning v2: ``pre_seq_len`` trainable prefix tokens through an optional re-parameterisation MLP."""
+
     pet_type: str = "ptuning2"
     pre_seq_len: int = 16
     prefix_projection: bool = False

@@ -65,6 +65,9 @@ class _PrefixCore(nn.Module):
 
 
 class PrefixTuningModel(nn.Module):
+    """Freezes the base model and trains per-layer prefix key / value vectors that are prepended inside attention
+    (reference ``pet/tuners/prefix_tuning_adapter.py``)."""
+
     def __init__(self, config, base_model: nn.Module):
         super().__init__()
         self.pet_config = config

@@ -15,6 +15,9 @@ from .pet_config import SLoraConfig
 
 
 class SLoraLinear(nn.Module):
+    """A linear layer with a bank of LoRA pairs: every row of the batch adds the low-rank update of the adapter its
+    request selected (index 0 = no adapter)."""
+
     def __init__(self, base: nn.Module, num_adapters: int, rank: int, alpha: float):
         super().__init__()
         self.base = base
@@ -42,6 +45,9 @@ class SLoraLinear(nn.Module):
 
 
 class SLoraAdapter:
+    """Loads a directory of LoRA adapters into ``SLoraLinear`` banks and routes requests to them by ``adapter_ids``
+    (reference ``pet/tuners/slora_adapter.py:37-574``)."""
+
     def __init__(self, model: nn.Module, config: SLoraConfig):
         self.model, self.config = model, config
         self.names: Dict[str, int] = {}
@@ -82,7 +88,8 @@ class SLoraAdapter:
         return slot
 
     def set_adapter_ids(self, adapter_names: Sequence[Optional[str]], tokens_per_sequence: Sequence[int]):
-        """``adapter_names[i]`` (``None`` = base model) applies to the ``tokens_per_sequence[i]`` tokens of sequence ``i``."""
+        """``adapter_names[i]`` (``None`` = base model) applies to the ``tokens_per_sequence[i]`` tokens of sequence
+        ``i``."""
         dev = self.layers[0].lora_a.device
         slots = torch.tensor([self.names.get(n, 0) if n else 0 for n in adapter_names], device=dev)
         idx = torch.repeat_interleave(slots, torch.tensor(list(tokens_per_sequence), device=dev))

@@ -11,6 +11,8 @@ from typing import List, Optional, Tuple
 
 
 class SeparatorStyle(Enum):
+    """How the turns of a conversation template are joined."""
+
     ADD_COLON_SINGLE = auto()
     ADD_COLON_TWO = auto()
     LLAMA2 = auto()
@@ -18,6 +20,9 @@ class SeparatorStyle(Enum):
 
 @dataclasses.dataclass
 class Conversation:
+    """A prompt template with its history: system text, role names, messages, separators; ``get_prompt()`` renders it
+    (reference ``tools/dataset_preprocess/llama/conversation.py``)."""
+
     name: str
     system: str
     roles: Tuple[str, str]

@@ -5,6 +5,9 @@ from typing import Iterable, List
 
 
 class BitArray:
+    """Fixed-size bit set over an integer (CPU masks for affinity): ``set``, ``clear``, ``test``, ranges to and from
+    strings like ``0-3,8``."""
+
     def __init__(self, length: int = 0):
         if length < 0:
             raise ValueError("length must be non-negative")
@@ -20,7 +23,8 @@ class BitArray:
         return out
 
     def load_from_str(self, mask: str) -> "BitArray":
-        """Comma-separated hexadecimal words, most significant first (the format of ``/proc/*/status`` ``Cpus_allowed``)."""
+        """Comma-separated hexadecimal words, most significant first (the format of ``/proc/*/status``
+        ``Cpus_allowed``)."""
         words = [w for w in mask.strip().split(",") if w]
         self.bits = int("".join(w.zfill(8) for w in words) or "0", 16)
         self.length = max(self.length, 32 * len(words))

@@ -15,6 +15,9 @@ _WRITER = None
 
 
 class JsonlWriter:
+    """Scalar writer used when neither ``tensorboardX`` nor ``torch.utils.tensorboard`` is importable: one JSON
+    object per ``add_scalar`` / ``add_text`` call."""
+
     def __init__(self, log_dir: str):
         os.makedirs(log_dir, exist_ok=True)
         self.path = os.path.join(log_dir, "scalars.jsonl")

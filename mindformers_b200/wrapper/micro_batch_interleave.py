@@ -23,6 +23,9 @@ def _split(value: Any, n: int, batch: int):
 
 
 class MicroBatchInterleaved(nn.Module):
+    """Wraps a network: the batch is cut into ``interleave_num`` copies along dimension 0, each runs on its own CUDA
+    stream, scalar losses are averaged, ``(numerator, denominator)`` losses summed, other tensors concatenated."""
+
     def __init__(self, network: nn.Module, interleave_num: int = 2):
         super().__init__()
         if interleave_num < 1:
