@@ -117,3 +117,81 @@ def test_moe_token_distribution_reports(tmp_path):
     tool.main(["--npy_files_load_path", str(tmp_path / "dump"), "--save_path_prefix", str(tmp_path / "c2") + "/",
                "--num_layers", "2"])
     assert os.path.exists(tmp_path / "c2" / "layer-1.svg") and not os.path.exists(tmp_path / "c2" / "layer-2.svg")
+
+
+def test_deepseekv3_converter_streams_layers_and_handles_fp8(tmp_path):
+    """Hugging Face style DeepSeek-V3 directory (several shards, one weight stored as block-scaled fp8 + scale_inv) →
+    converter → framework directory that loads into the same model."""
+    import importlib.util
+    import json
+    import os
+    import torch
+    from safetensors.torch import load_file, save_file
+    from mindformers_b200.checkpoint.io import load_checkpoint, save_pretrained_dir
+    from mindformers_b200.models import AutoModel
+    from mindformers_b200.ops.functional import quantize_weight_128x128
+    cfg = dict(model_type="deepseek_v3", num_hidden_layers=3, hidden_size=256, num_attention_heads=4,
+               num_key_value_heads=4, intermediate_size=512, moe_intermediate_size=128, n_routed_experts=4,
+               n_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, routed_scaling_factor=1.0,
+               norm_topk_prob=True, scoring_func="sigmoid", first_k_dense_replace=1, vocab_size=512, q_lora_rank=128,
+               kv_lora_rank=128, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, max_position_embeddings=128,
+               params_dtype="float32", moe_router_enable_expert_bias=True)
+    torch.manual_seed(3)
+    src_model = AutoModel.from_config(cfg, device="cpu").eval()
+    hf = tmp_path / "hf"
+    save_pretrained_dir(src_model, str(hf), config_dict=cfg, max_shard_bytes=600_000, hf_names=True, family="deepseek_v3")
+    assert len([f for f in os.listdir(hf) if f.endswith(".safetensors")]) > 3
+    # store one projection the way the released checkpoint does: e4m3 values + one scale per 128 x 128 block
+    key = "model.layers.1.self_attn.o_proj.weight"
+    index = json.load(open(hf / "model.safetensors.index.json"))["weight_map"]
+    shard = load_file(str(hf / index[key]))
+    q, scale = quantize_weight_128x128(shard[key])
+    shard[key], shard[key + "_scale_inv"] = q, scale
+    save_file(shard, str(hf / index[key]), metadata={"format": "pt"})
+    index[key + "_scale_inv"] = index[key]
+    json.dump({"weight_map": index}, open(hf / "model.safetensors.index.json", "w"))
+    spec = importlib.util.spec_from_file_location(
+        "conv", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "toolkit", "weight_convert",
+                             "deepseekv3", "convert_deepseekv3_hf_weight.py"))
+    conv = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(conv)
+    out = conv.main(["--torch_ckpt_path", str(hf), "--mindspore_ckpt_path", str(tmp_path / "mf"), "--dtype", "fp32"])
+    names = json.load(open(os.path.join(out, "model.safetensors.index.json")))["weight_map"]
+    assert "decoder.layers.1.mlp.experts.weight1" in names and "decoder.layers.0.self_attention.linear_qkv.weight" in names
+    dst_model = AutoModel.from_config(cfg, device="cpu").eval()
+    load_checkpoint(dst_model, out, strict=True, family="deepseek_v3")
+    a, b = dict(src_model.named_parameters()), dict(dst_model.named_parameters())
+    for n in a:
+        if n == "decoder.layers.1.self_attention.linear_proj.weight":
+            rel = (a[n] - b[n]).norm() / a[n].norm()
+            assert 0 < rel < 0.05                                   # went through e4m3
+        else:
+            assert torch.equal(a[n], b[n]), n
+
+
+def test_fp8_cast_bf16_tool(tmp_path):
+    import importlib.util
+    import json
+    import os
+    import torch
+    from safetensors.torch import load_file, save_file
+    from mindformers_b200.ops.functional import quantize_weight_128x128
+    src = tmp_path / "fp8"
+    os.makedirs(src)
+    torch.manual_seed(0)
+    w = torch.randn(256, 128) * 0.1
+    q, scale = quantize_weight_128x128(w)
+    save_file({"a.weight": q, "norm.weight": torch.ones(8)}, str(src / "model-00001-of-00002.safetensors"))
+    save_file({"a.weight_scale_inv": scale}, str(src / "model-00002-of-00002.safetensors"))      # scale in another shard
+    json.dump({"model_type": "deepseek_v3", "quantization_config": {"fmt": "e4m3"}}, open(src / "config.json", "w"))
+    spec = importlib.util.spec_from_file_location(
+        "cast", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "toolkit", "weight_convert",
+                             "deepseekv3", "fp8_cast_bf16.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    dst = mod.main(["--input-fp8-hf-path", str(src), "--output-bf16-hf-path", str(tmp_path / "bf16")])
+    out = load_file(os.path.join(dst, "model-00001-of-00002.safetensors"))
+    assert out["a.weight"].dtype == torch.bfloat16 and (out["a.weight"].float() - w).norm() / w.norm() < 0.05
+    idx = json.load(open(os.path.join(dst, "model.safetensors.index.json")))["weight_map"]
+    assert set(idx) == {"a.weight", "norm.weight"}
+    assert "quantization_config" not in json.load(open(os.path.join(dst, "config.json")))

@@ -18,7 +18,7 @@ import os
 import sys
 
 import torch
-from safetensors.torch import load_file, save_file
+from safetensors.torch import save_file
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 sys.path.insert(0, ROOT)
@@ -27,6 +27,11 @@ from mindformers_b200.checkpoint import name_maps  # noqa: E402
 from mindformers_b200.parallel.transformer_config_utils import convert_to_transformer_config  # noqa: E402
 
 DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+def n_main_full(hf_cfg) -> int:
+    """Index of the first layer that is not a decoder layer of the full model (the MTP layers follow the decoder)."""
+    return int(hf_cfg.get("num_hidden_layers_full", hf_cfg["num_hidden_layers"]))
 
 
 def main(argv=None):
@@ -43,23 +48,15 @@ def main(argv=None):
     with open(os.path.join(src, "config.json")) as f:
         hf_cfg = json.load(f)
     if args.num_layers:
+        hf_cfg["num_hidden_layers_full"] = hf_cfg["num_hidden_layers"]
         hf_cfg["num_hidden_layers"] = args.num_layers
     cfg = convert_to_transformer_config(hf_cfg, is_mla_model=True, strict=False)
-    files = sorted(f for f in os.listdir(src) if f.endswith(".safetensors"))
-    sd = {}
-    for f in files:                       # fused tensors need their partners, which may sit in another shard
-        part = load_file(os.path.join(src, f))
-        if args.num_layers:
-            part = {k: v for k, v in part.items() if ".layers." not in k or int(k.split(".layers.")[1].split(".")[0]) < args.num_layers
-                    or int(k.split(".layers.")[1].split(".")[0]) == hf_cfg.get("num_hidden_layers_full", 10 ** 9)}
-        sd.update(part)
-    out = name_maps.hf_to_framework(sd, cfg, "deepseek_v3", DTYPES[args.dtype], keep_fp8=args.keep_fp8)
-    if args.keep_fp8:
-        for k, v in sd.items():
-            if k.endswith("_scale_inv"):
-                out[name_maps.convert_name(k[:-len("_scale_inv")], "deepseek_v3") + "_scale_inv"] = v
+    from mindformers_b200.inference.weights_utils import WeightsLoader
+    loader = WeightsLoader(src)
+    layers, other = loader.layer_groups()
+    n_main = int(hf_cfg["num_hidden_layers"])
     os.makedirs(dst, exist_ok=True)
-    shard, size, idx, index = {}, 0, 0, {}
+    shard, size, idx, index, total, count = {}, 0, 0, {}, 0, 0
     limit = 5 * (1 << 30)
 
     def flush():
@@ -70,18 +67,44 @@ def main(argv=None):
             for k in shard:
                 index[k] = name
             shard, size, idx = {}, 0, idx + 1
-    for k, v in out.items():
-        nbytes = v.numel() * v.element_size()
-        if size + nbytes > limit:
-            flush()
-        shard[k] = v
-        size += nbytes
+
+    def emit(converted):
+        nonlocal size, total, count
+        for k, v in converted.items():
+            nbytes = v.numel() * v.element_size()
+            if size + nbytes > limit:
+                flush()
+            shard[k] = v
+            size += nbytes
+            total += nbytes
+            count += 1
+
+    # one group at a time: tensors outside the layers, then every layer (fused tensors have all their partners inside
+    # their layer), so the host holds one layer of the source and one output shard at most
+    groups = [sorted(other)]
+    for i in sorted(layers):
+        if args.num_layers and i >= args.num_layers and i < n_main_full(hf_cfg):
+            continue                                   # a truncated conversion keeps the first N layers (and MTP)
+        groups.append(sorted(layers[i]))
+    for names in groups:
+        if not names:
+            continue
+        part = loader.load_group(names)
+        conv = name_maps.hf_to_framework(part, cfg, "deepseek_v3", DTYPES[args.dtype], keep_fp8=args.keep_fp8)
+        if args.keep_fp8:
+            for k, v in part.items():
+                if k.endswith("_scale_inv"):
+                    fw = name_maps.convert_name(k[:-len("_scale_inv")], "deepseek_v3") + "_scale_inv"
+                    conv.setdefault(fw, v)
+        emit(conv)
+        del part, conv
     flush()
+    loader.close()
     with open(os.path.join(dst, "model.safetensors.index.json"), "w") as f:
-        json.dump({"metadata": {"total_size": sum(v.numel() * v.element_size() for v in out.values())}, "weight_map": index}, f, indent=1)
+        json.dump({"metadata": {"total_size": total}, "weight_map": index}, f, indent=1)
     with open(os.path.join(dst, "config.json"), "w") as f:
         json.dump(hf_cfg, f, indent=1)
-    print(f"converted {len(out)} tensors into {dst}")
+    print(f"converted {count} tensors into {dst}")
     return dst
 
 
