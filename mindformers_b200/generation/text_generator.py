@@ -31,7 +31,7 @@ class GenerationMixin:
     generation_config: Optional[GenerationConfig] = None
 
     # ---- cache --------------------------------------------------------------------------------------
-    def _set_kv_cache(self, batch_size: int, max_len: int, num_blocks: Optional[int] = None):
+    def _set_kv_cache(self, batch_size: int, max_len: int, num_blocks: Optional[int] = None, extra_layers: int = 0):
         cfg = self.config
         block_size = int(getattr(cfg, "block_size", 16) or 16)
         need = batch_size * (-(-max_len // block_size))
@@ -39,7 +39,7 @@ class GenerationMixin:
         tp = ps.get_tensor_model_parallel_world_size()
         device = next(self.parameters()).device
         dtype = next(self.parameters()).dtype
-        n_layers = len(self.model.decoder.layers)
+        n_layers = len(self.model.decoder.layers) + extra_layers      # extra: multi-token-prediction layers that draft
         if getattr(cfg, "multi_latent_attention", False):
             ctx = KVCacheContext(n_layers, num_blocks, block_size, 1, 0, dtype, device,
                                  mla_latent_dim=cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
@@ -53,9 +53,11 @@ class GenerationMixin:
     # ---- one model call -------------------------------------------------------------------------------
     @torch.no_grad()
     def _forward_step(self, tokens: List[List[int]], starts: List[int], ctx: KVCacheContext, tables: BlockTables,
-                      prefill: bool, active: Optional[List[bool]] = None, all_logits: bool = False) -> torch.Tensor:
+                      prefill: bool, active: Optional[List[bool]] = None, all_logits: bool = False,
+                      return_hidden: bool = False) -> torch.Tensor:
         """Run the model on the new ``tokens`` of every sequence (positions start at ``starts``).
-        Returns logits ``[B, V]`` of the last new token of each sequence."""
+        Returns logits ``[B, V]`` of the last new token of each sequence (``all_logits``: of every new token). With
+        ``return_hidden`` the result is ``(logits, hidden [T, H] of every new token, flat token ids, positions)``."""
         device = next(self.parameters()).device
         lens = [len(t) for t in tokens]
         if hasattr(self, "set_phase"):
@@ -73,7 +75,12 @@ class GenerationMixin:
         meta = AttnMeta(batch=1, seq_len=int(flat.numel()), positions=pos, cache=ctx)
         hook = getattr(self, "input_embeds_hook", None)     # multimodal models splice encoder outputs in here
         embeds = hook(flat, pos, prefill) if hook is not None else None
-        if embeds is not None:
+        hidden_all = None
+        if return_hidden:
+            hidden_all = self.model(flat.unsqueeze(0), attn_meta=meta, return_hidden=True, input_embeds=embeds)
+            rows = hidden_all if (all_logits or not prefill) else hidden_all.index_select(0, ctx.last_token_index)
+            logits = self.model.logits(rows).float()
+        elif embeds is not None:
             logits = self.model(flat.unsqueeze(0), attn_meta=meta, input_embeds=embeds)
         else:
             logits = self.model(flat.unsqueeze(0), attn_meta=meta)
@@ -88,6 +95,8 @@ class GenerationMixin:
             parts = [torch.empty_like(logits) for _ in range(tp)]
             torch.distributed.all_gather(parts, logits.contiguous(), group=ps.get_tensor_model_parallel_group())
             logits = torch.cat(parts, dim=-1)
+        if return_hidden:
+            return logits[:, : self.config.vocab_size], hidden_all, flat, pos
         return logits[:, : self.config.vocab_size]
 
     # ---- decode step as a CUDA graph ---------------------------------------------------------------------

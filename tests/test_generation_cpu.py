@@ -151,3 +151,38 @@ def test_deepseek_v2_and_qwen2_moe_families_build_and_generate():
     assert names["decoder.layers.0.mlp.shared_experts.gate_weight"].shape == (1, 64)
     assert names["decoder.layers.0.mlp.shared_experts.linear_fc2.weight"].shape[1] == 96
     assert len(q2.generate([[3, 4, 5]], max_new_tokens=2, do_sample=False, eos_token_id=None)[0]) == 5
+
+
+def test_mtp_speculative_decoding_equals_greedy_and_accepts_drafts():
+    """The multi-token-prediction layer drafts one token per step; output is the greedy sequence whether drafts are
+    accepted (after a short training on a periodic pattern they are) or rejected (random weights)."""
+    cfg = dict(model_type="deepseek_v3", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=4,
+               intermediate_size=128, moe_intermediate_size=32, n_routed_experts=4, n_shared_experts=1,
+               num_experts_per_tok=2, n_group=2, topk_group=1, routed_scaling_factor=1.0, norm_topk_prob=True,
+               scoring_func="sigmoid", first_k_dense_replace=1, vocab_size=96, q_lora_rank=32, kv_lora_rank=32,
+               qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, max_position_embeddings=128,
+               params_dtype="float32", num_nextn_predict_layers=1, block_size=4)
+    torch.manual_seed(0)
+    model = AutoModel.from_config(cfg, device="cpu")
+    prompts = [[3, 4, 5, 6, 7], [9, 8, 7]]
+    kw = dict(max_new_tokens=9, do_sample=False, eos_token_id=None)
+    model.eval()
+    assert model.generate(prompts, **kw) == model.generate(prompts, parallel_decoding="mtp", **kw)
+    assert model.last_generation_stats["proposed_draft_tokens"] > 0
+    # teach main model and MTP layer the pattern 10 20 30 10 20 30 ...
+    pattern = torch.tensor([10, 20, 30] * 11)[:32].unsqueeze(0).repeat(4, 1)
+    opt = torch.optim.Adam(model.parameters(), lr=3e-3)
+    model.train()
+    for _ in range(60):
+        loss = model(pattern[:, :-1].contiguous(), labels=pattern[:, 1:].contiguous())
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    model.eval()
+    prompts = [[10, 20, 30, 10, 20], [20, 30, 10]]
+    ref = model.generate(prompts, **kw)
+    assert ref[0][5:8] == [30, 10, 20]                                  # the pattern was learnt
+    out = model.generate(prompts, parallel_decoding="mtp", **kw)
+    stats = model.last_generation_stats
+    assert out == ref
+    assert stats["accepted_draft_tokens"] >= 4 and stats["model_calls"] < 1 + 9      # fewer calls than tokens
