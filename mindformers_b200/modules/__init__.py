@@ -7,4 +7,6 @@ from .layers import AlibiTensor, Dropout, FreqsMgr, LayerNorm, Linear, LowerTria
 from .local_block_sparse_attention import LocalBlockSparseAttention
 from .moe_legacy import MoEConfig, MoEInfer, MoEV2, MoEV3, TopkRouterV2
 from .seq_pipe import SequenceSplit
+from .transformer import (AttentionMask, FeedForward, MultiHeadAttention, Transformer, TransformerDecoder,
+                          TransformerDecoderLayer, TransformerEncoder, TransformerEncoderLayer, VocabEmbedding)
 from .rng import CudaRNGStatesTracker, get_rng_tracker, model_parallel_manual_seed

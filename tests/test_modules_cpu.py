@@ -280,3 +280,41 @@ def test_double_benchmark_accuracy_criterion():
     assert out["cosine"] > 0.9999
     with pytest.raises(AssertionError):
         precision_check(-good, golden.float())
+
+
+def test_generic_transformer_blocks():
+    """Encoder / decoder stacks of the older API: shapes, causal masking, incremental decoding with the returned
+    key / value pairs, cross-attention, post- vs pre-LN."""
+    import torch
+    from mindformers_b200.modules import (AttentionMask, Transformer, TransformerDecoder, TransformerEncoder,
+                                          VocabEmbedding)
+    torch.manual_seed(0)
+    B, S, H = 2, 6, 32
+    emb = VocabEmbedding(50, H)
+    ids = torch.randint(0, 50, (B, S))
+    x, table = emb(ids)
+    assert x.shape == (B, S, H) and table.shape == (50, H)
+    mask = AttentionMask(S)(torch.tensor([[1, 1, 1, 1, 1, 1], [1, 1, 1, 1, 0, 0]]))
+    assert mask.shape == (B, S, S) and mask[0, 2, 3] == 0 and mask[0, 3, 2] == 1 and mask[1, 5, 4] == 0
+    enc = TransformerEncoder(B, 2, H, 64, S, 4, 0.0, 0.0, use_past=True).eval()
+    full, present = enc(x, mask)
+    assert full.shape == (B, S, H) and len(present) == 2 and present[0][0].shape == (B, 4, S, H // 4)
+    # causal: a later token does not change earlier outputs
+    x2 = x.clone()
+    x2[0, 5] += 1.0
+    assert torch.allclose(enc(x2, mask)[0][0, :5], full[0, :5], atol=1e-6)
+    # incremental: last token with the cached keys / values of the first five
+    first, past = enc(x[:, :5], mask[:, :5, :5])
+    step, _ = enc(x[:, 5:6], mask[:, 5:6, :], past=past)
+    assert torch.allclose(step[0, 0], full[0, 5], atol=1e-5)
+    dec = TransformerDecoder(1, B, H, 64, S, 4, 4, 0.0, 0.0, post_layernorm_residual=True).eval()
+    tgt = torch.randn(B, 4, H)
+    out, _ = dec(tgt, torch.tril(torch.ones(4, 4)).expand(B, 4, 4), full, torch.ones(B, 4, S))
+    out_nomem, _ = dec(tgt, torch.tril(torch.ones(4, 4)).expand(B, 4, 4))
+    assert out.shape == (B, 4, H) and not torch.allclose(out, out_nomem)
+    model = Transformer(H, B, 64, S, 4, encoder_layers=1, decoder_layers=1, num_heads=4, attention_dropout_rate=0.0,
+                        hidden_dropout_rate=0.0)
+    y, enc_p, dec_p = model(x, mask, tgt, torch.tril(torch.ones(4, 4)).expand(B, 4, 4), torch.ones(B, 4, S))
+    assert y.shape == (B, 4, H) and len(enc_p) == 1 and len(dec_p) == 1
+    y.sum().backward()
+    assert emb.embedding_table.grad is not None
