@@ -91,6 +91,24 @@ MixtralForCausalLM = _model("MixtralForCausalLM", MixtralConfig, "mixtral")
 TelechatForCausalLM = _model("TelechatForCausalLM", TelechatConfig, "telechat")
 ChatGLM2ForConditionalGeneration = _model("ChatGLM2ForConditionalGeneration", ChatGLM4Config, "glm")
 
+# Names that configurations written for the reference use for the same models: its mcore shims pick a
+# ``Training...`` or ``Inference...`` class by run mode (``qwen3/modeling_qwen3.py:27-54``,
+# ``deepseek3/modeling_deepseek_v3.py:25-42``) and its research directories ship explicit tensor-parallel inference
+# models (``research/llama3_1/llama.py:48`` ``ParallelLlamaForCausalLM``, ``research/qwen2_5`` ``ParallelQwenForCausalLM``,
+# ``research/deepseek3`` ``DeepseekV3ForCausalLM`` / ``InferenceDeepseekV3ForCausalLM``). One class serves training and
+# inference here, so these are aliases.
+_ALIASES = {
+    "ParallelLlamaForCausalLM": LlamaForCausalLM, "ParallelQwenForCausalLM": Qwen2ForCausalLM,
+    "TrainingQwen3ForCausalLM": Qwen3ForCausalLM, "InferenceQwen3ForCausalLM": Qwen3ForCausalLM,
+    "TrainingQwen3MoeForCausalLM": Qwen3MoeForCausalLM, "InferenceQwen3MoeForCausalLM": Qwen3MoeForCausalLM,
+    "TrainingDeepseekV3ForCausalLM": DeepseekV3ForCausalLM, "InferenceDeepseekV3ForCausalLM": DeepseekV3ForCausalLM,
+    "InferenceQwen2ForCausalLM": Qwen2ForCausalLM, "DeepseekV2ForCausalLM_legacy": DeepseekV2ForCausalLM,
+    "TelechatForCausalLM_MoE": TelechatForCausalLM,
+}
+for _alias, _cls in _ALIASES.items():
+    for _legacy in (True, False):
+        MindFormerRegister.register_cls(_cls, MindFormerModuleType.MODELS, alias=_alias, legacy=_legacy)
+
 MODEL_TYPE_TO_CLASSES = {
     "llama": (LlamaConfig, LlamaForCausalLM), "qwen2": (Qwen2Config, Qwen2ForCausalLM),
     "qwen2_5": (Qwen2Config, Qwen2ForCausalLM), "qwen3": (Qwen3Config, Qwen3ForCausalLM),
