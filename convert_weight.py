@@ -84,8 +84,11 @@ def main(argv=None):
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     p.add_argument("--model", required=True, choices=sorted(convert_map))
     p.add_argument("--reversed", action="store_true", help="framework → Hugging Face")
-    p.add_argument("--input_path", required=True)
-    p.add_argument("--output_path", required=True)
+    p.add_argument("--input_path", default=None)
+    p.add_argument("--output_path", default=None)
+    p.add_argument("--convert_config", default=None,
+                   help="YAML with one section per model (input_path, output_path, dtype, ...), e.g. "
+                        "configs/convert_config/run_convert.yaml; command-line values win")
     p.add_argument("--dtype", default=None, choices=sorted(DTYPES))
     p.add_argument("--config", default=None, help="config.json of the model (defaults to <input_path>/config.json)")
     p.add_argument("--qkv_concat", default=True, type=lambda s: s.lower() in ("1", "true"))
@@ -95,6 +98,15 @@ def main(argv=None):
     p.add_argument("--hidden_size", type=int, default=None)
     p.add_argument("--layers", type=int, default=None)
     args = p.parse_args(argv)
+    if args.convert_config:
+        import yaml
+        with open(args.convert_config) as f:
+            section = (yaml.safe_load(f) or {}).get(args.model) or {}
+        for key, value in section.items():
+            if value is not None and hasattr(args, key) and getattr(args, key) in (None, False):
+                setattr(args, key, value)
+    if not args.input_path or not args.output_path:
+        p.error("--input_path and --output_path are required (on the command line or in --convert_config)")
     path = convert(args)
     print(f"converted weights written to {path}")
     return path

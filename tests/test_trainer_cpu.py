@@ -151,6 +151,15 @@ def test_convert_weight_roundtrip(tmp_path):
         if f.endswith(".safetensors"):
             b.update(load_file(str(tmp_path / "hf" / f)))
     assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+    # the same conversion with the paths taken from a convert_config YAML
+    import yaml
+    yml = tmp_path / "run_convert.yaml"
+    yaml.safe_dump({"llama": {"input_path": str(tmp_path / "hf"), "output_path": str(tmp_path / "mf2"), "dtype": None}},
+                   open(yml, "w"))
+    out2 = convert_weight.main(["--model", "llama", "--convert_config", str(yml)])
+    assert all(torch.equal(load_file(out2)[k], sd[k]) for k in sd)
+    shipped = yaml.safe_load(open(os.path.join(ROOT, "configs", "convert_config", "run_convert.yaml")))
+    assert set(shipped) >= {"llama", "qwen3_moe", "deepseekv3"} and set(shipped) <= set(convert_weight.convert_map)
 
 
 def test_config_arguments_sections():
