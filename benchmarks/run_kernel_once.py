@@ -3,7 +3,10 @@ the target of `ncu -k regex:<kernel> -c N`. Usage: python benchmarks/run_kernel_
 
 Cases: gemm (fc1 forward 4096 x 28672 x 4096, then dgrad and wgrad layouts), fa (forward + backward, S=4096, 32/8
 heads), rmsnorm, swiglu, rope, ce (4096 x 128256 logits), adamw (64 M parameters), router (E=128 top-8 and E=256
-group-limited), paged (decode attention, 64 sequences of 2048 tokens, block 128), mla (latent-cache decode, 64 x 2304 tokens), moe (single-rank exchange kernels).
+group-limited), paged (decode attention, 64 sequences of 2048 tokens, block 128), mla (latent-cache decode, 64 x 2304
+tokens, both kernel variants), moe (single-rank exchange kernels), fp8 (block-scaled GEMM at prefill sizes against the
+bf16 kernel), fp8_decode (64-token GEMMs: 128-row tiles, cluster split-K, weight-on-rows kernel; graph replay, weights
+cycled past L2), fp8_moe_decode (32 experts with two tokens each; MFB_BENCH_EXPERTS shrinks it for an ncu capture).
 """
 import argparse
 import os
