@@ -14,22 +14,35 @@ import torch
 import torch.nn as nn
 
 
+class _NormalInit:
+    """Picklable ``tensor -> tensor`` initialiser (configurations that hold one can be copied to worker processes)."""
+
+    def __init__(self, std: float):
+        self.std = float(std)
+
+    def __call__(self, tensor: torch.Tensor) -> torch.Tensor:
+        return nn.init.normal_(tensor, mean=0.0, std=self.std)
+
+    def __repr__(self):
+        return f"normal(std={self.std:g})"
+
+
+class _ZeroInit:
+    def __call__(self, tensor: torch.Tensor) -> torch.Tensor:
+        return nn.init.zeros_(tensor)
+
+    def __repr__(self):
+        return "zeros"
+
+
 def init_method_normal(sigma: float = 0.02) -> Callable[[torch.Tensor], torch.Tensor]:
-    def init_(tensor: torch.Tensor) -> torch.Tensor:
-        return nn.init.normal_(tensor, mean=0.0, std=sigma)
-    return init_
+    return _NormalInit(sigma)
 
 
 def scaled_init_method_normal(sigma: float, num_layers: int) -> Callable[[torch.Tensor], torch.Tensor]:
     """N(0, sigma / sqrt(2 * num_layers)): keeps the variance of the residual stream independent of the depth."""
-    std = sigma / math.sqrt(2.0 * max(int(num_layers), 1))
-
-    def init_(tensor: torch.Tensor) -> torch.Tensor:
-        return nn.init.normal_(tensor, mean=0.0, std=std)
-    return init_
+    return _NormalInit(sigma / math.sqrt(2.0 * max(int(num_layers), 1)))
 
 
 def init_method_zero() -> Callable[[torch.Tensor], torch.Tensor]:
-    def init_(tensor: torch.Tensor) -> torch.Tensor:
-        return nn.init.zeros_(tensor)
-    return init_
+    return _ZeroInit()
