@@ -98,7 +98,20 @@ class PreTrainedModel(nn.Module, GenerationMixin, InferModelMixin):
                 model.load_weights(path, strict=strict)
             except FileNotFoundError:
                 logger.warning("no weights found under %s: the model keeps its random initialisation", path)
+        model.apply_quantization_config()
         return model
+
+    def apply_quantization_config(self, quantization_config: Optional[dict] = None, act_stats=None) -> int:
+        """Quantise the (loaded) model as its configuration's ``quantization_config`` says (``quant_method``: ``rtn``,
+        ``ptq``, ``smooth_quant`` or ``fp8``); returns the number of converted layers. Training modes leave the model
+        as it is: the quantised layers are inference-only."""
+        qc = quantization_config or getattr(self.model_config, "quantization_config", None)
+        if not qc or os.environ.get("RUN_MODE", "predict") in ("train", "finetune"):
+            return 0
+        from ..modules.quantizers import AutoQuantizer
+        n = AutoQuantizer.from_config(dict(qc)).quantize(self, act_stats)
+        logger.info("quantization_config %s: %d layers converted", dict(qc).get("quant_method"), n)
+        return n
 
     def save_pretrained(self, save_directory: str, max_shard_size: str = "5GB", hf_names: bool = False, **kw):
         size = _parse_size(max_shard_size)

@@ -206,3 +206,50 @@ def quantize_kv_int8(x: torch.Tensor):
 
 def dequantize_kv_int8(q: torch.Tensor, s: torch.Tensor, dtype=torch.bfloat16):
     return (q.float() * s).to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# configuration dict -> config object -> quantised model (reference ``modules/quantizers/auto.py:33-39``)
+# ---------------------------------------------------------------------------------------------------------------
+_CONFIG_CLASSES = {"rtn": RtnConfig, "ptq": PtqConfig, "smooth_quant": SmoothQuantConfig, "smoothquant": SmoothQuantConfig,
+                   "fp8": Fp8BlockConfig}
+
+
+class AutoQuantizationConfig:
+    """``from_dict({"quant_method": "ptq", ...})`` → the configuration class of that method; unknown keys of a
+    Hugging Face ``quantization_config`` (for example ``activation_scheme``) are dropped."""
+
+    @staticmethod
+    def from_dict(d: dict) -> QuantizationConfig:
+        d = dict(d or {})
+        method = str(d.get("quant_method", "rtn")).lower()
+        if method not in _CONFIG_CLASSES:
+            raise ValueError(f"quant_method {method!r} is not one of {sorted(set(_CONFIG_CLASSES))}")
+        cls = _CONFIG_CLASSES[method]
+        fields = set(cls.__dataclass_fields__)
+        kw = {k: v for k, v in d.items() if k in fields}
+        kw["quant_method"] = "smooth_quant" if method == "smoothquant" else method
+        if "weight_block_size" in kw:
+            kw["weight_block_size"] = tuple(kw["weight_block_size"])
+        return cls(**kw)
+
+
+class AutoQuantizer:
+    """``AutoQuantizer.from_config(cfg_or_dict).quantize(model)``: applies the method to a built (and loaded) model.
+    Block-scaled fp8 goes through the layers' own fp8 path (``inference/fp8.py``), the integer methods through
+    ``quantize_model``; ``act_stats`` are the activation maxima of a calibration run for the W8A8 methods."""
+
+    def __init__(self, config: QuantizationConfig):
+        self.config = config
+
+    @classmethod
+    def from_config(cls, config) -> "AutoQuantizer":
+        return cls(config if isinstance(config, QuantizationConfig) else AutoQuantizationConfig.from_dict(config))
+
+    def quantize(self, model: nn.Module, act_stats: Optional[Dict[str, torch.Tensor]] = None) -> int:
+        if self.config.quant_method == "fp8":
+            from ..inference.fp8 import quantize_model_fp8
+            skip = tuple(self.config.modules_to_not_convert or ("output_layer", "embedding", "router", "linear_kvb"))
+            stats = quantize_model_fp8(model, skip=skip)
+            return int(stats["linear"]) + int(stats["grouped"])
+        return quantize_model(model, self.config, act_stats)

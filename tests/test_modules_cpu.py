@@ -318,3 +318,40 @@ def test_generic_transformer_blocks():
     assert y.shape == (B, 4, H) and len(enc_p) == 1 and len(dec_p) == 1
     y.sum().backward()
     assert emb.embedding_table.grad is not None
+
+
+def test_quantization_config_of_a_pretrained_directory_is_applied(tmp_path, monkeypatch):
+    """``quantization_config`` in ``config.json`` selects the quantiser when the model is loaded for inference."""
+    import json
+    import pytest
+    import torch
+    from mindformers_b200.models import AutoModel
+    from mindformers_b200.modules.quantizers import (AutoQuantizationConfig, Fp8BlockConfig, QuantLinear, RtnConfig,
+                                                     SmoothQuantConfig)
+    assert isinstance(AutoQuantizationConfig.from_dict({"quant_method": "rtn", "weight_dtype": "int4", "x": 1}), RtnConfig)
+    assert AutoQuantizationConfig.from_dict({"quant_method": "smoothquant", "alpha": 0.7}).alpha == 0.7
+    fp8 = AutoQuantizationConfig.from_dict({"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128],
+                                            "activation_scheme": "dynamic"})
+    assert isinstance(fp8, Fp8BlockConfig) and fp8.weight_block_size == (128, 128)
+    assert isinstance(AutoQuantizationConfig.from_dict({"quant_method": "smooth_quant"}), SmoothQuantConfig)
+    with pytest.raises(ValueError):
+        AutoQuantizationConfig.from_dict({"quant_method": "int3-magic"})
+    cfg = dict(model_type="llama", num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=2,
+               intermediate_size=256, vocab_size=256, max_position_embeddings=64, params_dtype="float32")
+    torch.manual_seed(0)
+    ref = AutoModel.from_config(cfg, device="cpu").eval()
+    ref.save_pretrained(str(tmp_path / "m"))
+    saved = json.load(open(tmp_path / "m" / "config.json"))
+    saved["quantization_config"] = {"quant_method": "rtn", "weight_dtype": "int8"}
+    json.dump(saved, open(tmp_path / "m" / "config.json", "w"))
+    monkeypatch.setenv("RUN_MODE", "predict")
+    q = AutoModel.from_pretrained(str(tmp_path / "m"), device="cpu").eval()
+    n_quant = sum(isinstance(m, QuantLinear) for m in q.modules())
+    assert n_quant == 2 * 4                                           # qkv, proj, fc1, fc2 of both layers
+    ids = torch.randint(0, 256, (1, 12))
+    with torch.no_grad():
+        a, b = ref(ids).float(), q(ids).float()
+    assert ((a - b).norm() / a.norm()).item() < 0.05
+    monkeypatch.setenv("RUN_MODE", "finetune")                        # training keeps full-precision layers
+    t = AutoModel.from_pretrained(str(tmp_path / "m"), device="cpu")
+    assert not any(isinstance(m, QuantLinear) for m in t.modules())
