@@ -291,6 +291,9 @@ class BaseTrainer:
         path = config.get("load_checkpoint") or config.get("pretrained_model_dir")
         if path and network is None:
             model.load_weights(path, strict=False)
+        if network is None and hasattr(model, "apply_quantization_config"):
+            # ``model.model_config.quantization_config`` or a top-level ``quantization_config`` section of the YAML
+            model.apply_quantization_config(config.get("quantization_config"))
         if tokenizer is None:
             tok_cfg = (config.get("processor") or {}).get("tokenizer")
             tokenizer = build_tokenizer(tok_cfg) if tok_cfg else build_tokenizer({"type": "ByteTokenizer"})

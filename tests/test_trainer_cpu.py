@@ -184,3 +184,28 @@ def test_config_arguments_sections():
     trainer = Trainer(args=args, task="general")
     assert trainer.config.runner_config.epochs == 2 and trainer.config.optimizer.weight_decay == 0.05
     assert trainer.config.seed == 7
+
+
+def test_predict_applies_the_yaml_quantization_config(tmp_path, monkeypatch):
+    from mindformers_b200.modules.quantizers import QuantLinear
+    from mindformers_b200.tools.register import MindFormerConfig
+    from mindformers_b200.trainer.base_trainer import CausalLanguageModelingTrainer
+    monkeypatch.setenv("RUN_MODE", "predict")
+    cfg = MindFormerConfig({
+        "run_mode": "predict", "output_dir": str(tmp_path), "save_file": str(tmp_path / "out.txt"),
+        "model": {"model_config": dict(model_type="llama", num_hidden_layers=1, hidden_size=128, num_attention_heads=4,
+                                       num_key_value_heads=2, intermediate_size=256, vocab_size=300,
+                                       max_position_embeddings=64, params_dtype="float32")},
+        "quantization_config": {"quant_method": "rtn", "weight_dtype": "int8"},
+        "processor": {"tokenizer": {"type": "ByteTokenizer"}}})
+    seen = {}
+    import mindformers_b200.pipeline as pl
+    real = pl.pipeline
+
+    def spy(task, model, tokenizer, **kw):
+        seen["model"] = model
+        return real(task=task, model=model, tokenizer=tokenizer, **kw)
+
+    monkeypatch.setattr(pl, "pipeline", spy)
+    out = CausalLanguageModelingTrainer().predict(cfg, input_data=["hello"], max_new_tokens=3)
+    assert out and sum(isinstance(m, QuantLinear) for m in seen["model"].modules()) == 4
