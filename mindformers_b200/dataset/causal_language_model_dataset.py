@@ -180,7 +180,59 @@ class CausalLanguageModelDataset:
                             pin_memory=bool(cfg.get("pin_memory", torch.cuda.is_available())))
         loader.shard_sampler = sampler
         loader.set_init_step = lambda steps, bs=int(cfg.get("batch_size", 1)): sampler.set_skip(steps * bs)
+        if cfg.get("token_monitor"):
+            loader.collate_fn = TokenMonitor(collate, **dict(cfg.get("token_monitor_config") or {}))
+            loader.token_monitor = loader.collate_fn
         return loader
+
+
+class TokenMonitor:
+    """Counts how often every token id is fed to the model (reference ``causal_language_model_dataset.py:448``: the
+    token histogram of the training data, for spotting a tokenizer / corpus mismatch or a dominating token).
+
+    Wraps the collate function, so it sees exactly the batches that the training loop gets (with ``num_workers > 0``
+    each worker counts its own share). ``summary(top_k)`` gives totals and the most frequent ids; every
+    ``dump_interval`` batches the histogram is written to ``<save_dir>/token_counts_rank<r>.npy``."""
+
+    def __init__(self, collate_fn, vocab_size: Optional[int] = None, column: str = "input_ids", pad_token_id=None,
+                 dump_interval: int = 0, save_dir: Optional[str] = None):
+        self.collate_fn, self.column, self.pad = collate_fn, column, pad_token_id
+        self.counts = torch.zeros(int(vocab_size or 0), dtype=torch.int64)
+        self.batches, self.dump_interval, self.save_dir = 0, int(dump_interval or 0), save_dir
+
+    def __call__(self, items):
+        batch = self.collate_fn(items)
+        ids = batch.get(self.column) if isinstance(batch, dict) else None
+        if ids is not None:
+            flat = ids.reshape(-1).to(torch.int64)
+            flat = flat[flat >= 0]
+            if self.pad is not None:
+                flat = flat[flat != self.pad]
+            if flat.numel():
+                c = torch.bincount(flat, minlength=self.counts.numel())
+                if c.numel() > self.counts.numel():
+                    self.counts = torch.nn.functional.pad(self.counts, (0, c.numel() - self.counts.numel()))
+                self.counts[: c.numel()] += c
+            self.batches += 1
+            if self.dump_interval and self.batches % self.dump_interval == 0:
+                self.dump()
+        return batch
+
+    def summary(self, top_k: int = 10) -> dict:
+        total = int(self.counts.sum())
+        k = min(top_k, int((self.counts > 0).sum()))
+        vals, idx = torch.topk(self.counts, k) if k else (torch.zeros(0), torch.zeros(0))
+        return {"batches": self.batches, "tokens": total, "distinct": int((self.counts > 0).sum()),
+                "top": [(int(i), int(v), (int(v) / total if total else 0.0)) for i, v in zip(idx.tolist(), vals.tolist())]}
+
+    def dump(self) -> Optional[str]:
+        import numpy as np
+        from ..tools.utils import get_output_root_path, get_real_rank
+        root = self.save_dir or os.path.join(get_output_root_path(), "token_monitor")
+        os.makedirs(root, exist_ok=True)
+        path = os.path.join(root, f"token_counts_rank{get_real_rank()}.npy")
+        np.save(path, self.counts.numpy())
+        return path
 
 
 def _batched(dataset, cfg: dict, collate_fn=collate):

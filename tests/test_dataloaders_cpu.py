@@ -149,3 +149,20 @@ def test_hf_dataloader_with_handlers(tmp_path):
     import pytest as _pytest
     with _pytest.raises(FileNotFoundError):
         HFDataLoader("org/some_dataset")
+
+
+def test_token_monitor_counts_what_the_loop_receives(tmp_path):
+    import numpy as np
+    import torch
+    from mindformers_b200.dataset import CausalLanguageModelDataset
+    loader = CausalLanguageModelDataset(dict(
+        data_loader=dict(type="MockDataLoader", seq_length=16, vocab_size=50, num_samples=24, seed=3), batch_size=4,
+        token_monitor=True, token_monitor_config=dict(vocab_size=50, dump_interval=2, save_dir=str(tmp_path))))
+    seen = torch.zeros(50, dtype=torch.int64)
+    for batch in loader:
+        seen += torch.bincount(batch["input_ids"].reshape(-1), minlength=50)
+    mon = loader.token_monitor
+    assert torch.equal(mon.counts, seen) and mon.batches == 6
+    s = mon.summary(top_k=3)
+    assert s["tokens"] == int(seen.sum()) and len(s["top"]) == 3 and s["top"][0][1] == int(seen.max())
+    assert np.load(tmp_path / "token_counts_rank0.npy").sum() == int(seen.sum())
