@@ -46,3 +46,18 @@ def test_deprecated_decorator_warns_once_with_the_replacement():
         assert old_function() == 7
     text = " ".join(str(w.message) for w in seen)
     assert "old_function" in text and "new_function" in text
+
+
+def test_every_module_of_the_package_imports():
+    """No module depends on a GPU, a network or an optional package at import time."""
+    import pkgutil
+    import mindformers_b200
+    failed = []
+    for m in pkgutil.walk_packages(mindformers_b200.__path__, "mindformers_b200."):
+        if m.name.endswith(".ops.build"):
+            continue                                   # the build script compiles when run as a module
+        try:
+            importlib.import_module(m.name)
+        except Exception as e:                         # noqa: BLE001 - the test reports every failure at once
+            failed.append(f"{m.name}: {e!r}")
+    assert not failed, failed
