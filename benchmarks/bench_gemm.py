@@ -1,4 +1,5 @@
-"""Time the hand-written tcgen05 bf16 GEMM against torch.matmul (cuBLAS) on Llama-3.1-8B shapes.
+"""Time the hand-written tcgen05 bf16 GEMMs (single-CTA tiles, CTA-pair tiles, CTA pairs with a K split of the
+tail wave) against torch.matmul (cuBLAS) on every Llama-3.1-8B linear shape: forward, dgrad and wgrad.
 
 Usage: python benchmarks/bench_gemm.py [--iters 20] [--out FILE.json]
 Timing: CUDA events, 3 warm-up runs, L2 flushed by writing a 256 MiB buffer between iterations.
@@ -14,15 +15,23 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from mindformers_b200.ops import functional as Fn  # noqa: E402
 from mindformers_b200.ops import _lib  # noqa: E402
 
-SHAPES = [  # (name, M, N, K, a_mn, b_mn)
-    ("qkv_fwd", 4096, 6144, 4096, False, False),
-    ("fc1_fwd", 4096, 28672, 4096, False, False),
-    ("fc2_fwd", 4096, 4096, 14336, False, False),
-    ("proj_fwd", 4096, 4096, 4096, False, False),
-    ("fc1_dgrad", 4096, 4096, 28672, False, True),
-    ("fc1_wgrad", 28672, 4096, 4096, True, True),
-    ("head_fwd", 4096, 128256, 4096, False, False),
-    ("square_8k", 8192, 8192, 8192, False, False),
+SHAPES = [  # (name, M, N, K, a_mn, b_mn, fp32 accumulate into the output)
+    ("qkv_fwd", 4096, 6144, 4096, False, False, False),
+    ("proj_fwd", 4096, 4096, 4096, False, False, False),
+    ("fc1_fwd", 4096, 28672, 4096, False, False, False),
+    ("fc2_fwd", 4096, 4096, 14336, False, False, False),
+    ("head_fwd", 4096, 128256, 4096, False, False, False),
+    ("qkv_dgrad", 4096, 4096, 6144, False, True, False),
+    ("proj_dgrad", 4096, 4096, 4096, False, True, False),
+    ("fc1_dgrad", 4096, 4096, 28672, False, True, False),
+    ("fc2_dgrad", 4096, 14336, 4096, False, True, False),
+    ("head_dgrad", 4096, 4096, 128256, False, True, False),
+    ("qkv_wgrad", 6144, 4096, 4096, True, True, True),
+    ("proj_wgrad", 4096, 4096, 4096, True, True, True),
+    ("fc1_wgrad", 28672, 4096, 4096, True, True, True),
+    ("fc2_wgrad", 4096, 14336, 4096, True, True, True),
+    ("head_wgrad", 128256, 4096, 4096, True, True, True),
+    ("square_8k", 8192, 8192, 8192, False, False, False),
 ]
 
 
@@ -47,27 +56,50 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--only", default=None, help="comma-separated shape names")
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     rows = []
-    for name, M, N, K, a_mn, b_mn in SHAPES:
-        a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
-        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    variants = [("single", False, 1), ("pair", True, 1), ("pair_split", True, 4)]
+    only = set(args.only.split(",")) if args.only else None
+    for name, M, N, K, a_mn, b_mn, acc in SHAPES:
+        if only and name not in only:
+            continue
+        a = (torch.randn((K, M) if a_mn else (M, K), device="cuda") * 0.5).to(torch.bfloat16)
+        b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.5).to(torch.bfloat16)
+        out = torch.zeros(M, N, device="cuda", dtype=torch.float32 if acc else torch.bfloat16)
         am = a.t() if a_mn else a
         bm = b if b_mn else b.t()
-        ours = lambda: Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out)
-        lib = lambda: torch.matmul(am, bm, out=out)
-        t_ours, b_ours = time_fn(ours, args.iters, flush)
-        t_lib, b_lib = time_fn(lib, args.iters, flush)
-        ref = torch.matmul(am, bm)
-        got = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
-        err = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
         fl = 2.0 * M * N * K
-        rows.append({"name": name, "M": M, "N": N, "K": K, "ours_ms": t_ours, "ours_best_ms": b_ours,
-                     "cublas_ms": t_lib, "cublas_best_ms": b_lib, "ours_tflops": fl / t_ours / 1e9,
-                     "cublas_tflops": fl / t_lib / 1e9, "rel_err_vs_cublas": err})
-        print(rows[-1], flush=True)
+        ref = torch.matmul(am, bm)
+        row = {"name": name, "M": M, "N": N, "K": K}
+        for vname, pair, slices in variants:
+            Fn.set_pair_gemm(pair, slices)
+            ours = lambda: Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc)
+            t, best = time_fn(ours, args.iters, flush)
+            out.zero_()
+            got = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc)
+            err = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
+            row[vname + "_ms"] = t
+            row[vname + "_tflops"] = fl / t / 1e9
+            row[vname + "_rel_err"] = err
+        if acc:
+            lib = lambda: out.add_(torch.matmul(am, bm))      # what the library arm does for a weight gradient
+        else:
+            lib = lambda: torch.matmul(am, bm, out=out)
+        t_lib, _ = time_fn(lib, args.iters, flush)
+        row["cublas_ms"] = t_lib
+        row["cublas_tflops"] = fl / t_lib / 1e9
+        if acc:
+            out_bf = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            t_mm, _ = time_fn(lambda: torch.matmul(am, bm, out=out_bf), args.iters, flush)
+            row["cublas_mm_only_tflops"] = fl / t_mm / 1e9
+            del out_bf
+        row["best_vs_cublas"] = max(row[v + "_tflops"] for v, _, _ in variants) / row["cublas_tflops"]
+        rows.append(row)
+        print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()}), flush=True)
+        del a, b, out, ref
+    Fn.set_pair_gemm(True, 4)
     print("status word:", _lib.read_status())
     if args.out:
         with open(args.out, "w") as f:

@@ -131,12 +131,48 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     mode = _OUT_MODES[(out.dtype, bool(accumulate))]
     lib = _lib.get_lib()
     st = _lib.status_word(a.device)
+    if _PAIR_GEMM and M >= 256 and N >= 256 and K >= 64:
+        # 256 x 256 tiles on CTA pairs; the tail wave is split along K through a per-stream workspace
+        ws = _pair_workspace(a.device) if _PAIR_SLICES > 1 and mode < 2 else None
+        rc = lib.mfb_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                    out.stride(0), int(a_mn), int(b_mn), mode, _lib.ptr(ws), _PAIR_SLICES,
+                                    st.data_ptr(), int(sm_limit), _lib.stream_ptr())
+        _lib.check(rc, "mfb_gemm_bf16_pair")
+        _lib.count_launch()
+        return out
     rc = lib.mfb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                            out.stride(0), int(a_mn), int(b_mn), mode, 0, 1, 0, 0, 0, 0, st.data_ptr(),
                            int(sm_limit), _lib.stream_ptr())
     _lib.check(rc, "mfb_gemm_bf16")
     _lib.count_launch()
     return out
+
+
+# Dense GEMMs of at least one 256 x 256 tile run on CTA pairs (``gemm_tcgen05_2cta.cu``); ``MFB_GEMM_PAIR=0``
+# keeps the single-CTA kernel for A/B measurements, ``MFB_GEMM_PAIR_SLICES`` bounds the K split of the tail wave.
+_PAIR_GEMM = os.environ.get("MFB_GEMM_PAIR", "1") != "0"
+_PAIR_SLICES = int(os.environ.get("MFB_GEMM_PAIR_SLICES", "4"))
+_pair_ws_cache: dict = {}
+
+
+def set_pair_gemm(enabled: bool, max_slices: Optional[int] = None):
+    """Switch the CTA-pair GEMM (and the K split of its tail wave) at run time."""
+    global _PAIR_GEMM, _PAIR_SLICES
+    _PAIR_GEMM = bool(enabled)
+    if max_slices is not None:
+        _PAIR_SLICES = int(max_slices)
+
+
+def _pair_workspace(device) -> torch.Tensor:
+    """Zero-initialised workspace of the split tail wave, one per (device, stream): two GEMMs that overlap on
+    the GPU must not share partial tiles or flags."""
+    key = (torch.device(device).index or 0, _lib.stream_ptr())
+    t = _pair_ws_cache.get(key)
+    if t is None:
+        nbytes = int(_lib.get_lib().mfb_gemm_pair_workspace_bytes())
+        t = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _pair_ws_cache[key] = t
+    return t
 
 
 def grouped_gemm(a: torch.Tensor, b: torch.Tensor, block_group: torch.Tensor, num_blocks: torch.Tensor,

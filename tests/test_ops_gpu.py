@@ -63,6 +63,49 @@ def test_gemm_both_mn_major(M, N, K):
     assert _rel_err(acc, 2 * ref) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K,sm_limit", [(4096, 4096, 1024, 0), (1280, 256, 2048, 8), (1304, 520, 2056, 8),
+                                            (768, 768, 512, 4)])
+@pytest.mark.parametrize("layout", ["tn", "nn", "tt_f32"])
+def test_gemm_pair_tail_split_matches_unsplit(M, N, K, sm_limit, layout):
+    """CTA-pair GEMM: the K split of the tail wave (partials through the workspace) against fp32 matmul and
+    against the same kernel without the split; run twice so that the second call meets re-armed flags."""
+    torch.manual_seed(7)
+    a_mn, b_mn = layout == "tt_f32", layout != "tn"
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    odt = torch.float32 if layout == "tt_f32" else torch.bfloat16
+    try:
+        Fn.set_pair_gemm(True, 1)
+        plain = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=odt, sm_limit=sm_limit)
+        Fn.set_pair_gemm(True, 4)
+        for _ in range(2):
+            split = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=odt, sm_limit=sm_limit)
+            torch.cuda.synchronize()
+            _status_ok()
+            assert _rel_err(split, ref) < 5e-3
+            assert _rel_err(split, plain) < 2e-3
+        assert _rel_err(plain, ref) < 5e-3
+    finally:
+        Fn.set_pair_gemm(True, 4)
+
+
+def test_gemm_pair_matches_single_cta_kernel():
+    torch.manual_seed(8)
+    a = torch.randn(1024, 1536, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(2048, 1536, device=DEV, dtype=torch.bfloat16)
+    try:
+        Fn.set_pair_gemm(False)
+        single = Fn.gemm(a, b)
+        Fn.set_pair_gemm(True, 1)
+        pair = Fn.gemm(a, b)
+    finally:
+        Fn.set_pair_gemm(True, 4)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.equal(single, pair), "same K order per output element: the two tilings must agree bitwise"
+
+
 def test_linear_autograd_matches_torch():
     torch.manual_seed(3)
     x = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
