@@ -14,7 +14,10 @@ token ids, random-init weights.
 Prints ONE JSON line on rank 0. ``value`` is device-timed (CUDA events, max over ranks, barrier and
 synchronize on both sides); ``e2e`` repeats the measurement through ``TrainingEngine.train_step`` with
 the host→device copy of the tokens from pinned memory and the device→host read of the loss inside the
-timed region. ``--impl reference`` reports why the reference itself cannot run here.
+timed region. After this repository's own path the same engine is timed again on the library path (cuBLAS GEMMs,
+SDPA attention, NCCL collectives) and reported as ``library_arm`` / ``vs_library`` in the same line; with N >= 2 the
+fused multi-GPU kernels are first checked against the NCCL path on one micro-batch (``multi_gpu_numerics``).
+``--impl reference`` tries to import the reference from ``baseline/_ref`` and reports what stops it.
 """
 import argparse
 import json
@@ -67,9 +70,27 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    why = ("reference needs MindSpore + Ascend CANN: `import mindformers` from baseline/_ref fails with "
-           "ModuleNotFoundError: No module named 'mindspore' (not installable offline; no CUDA backend in the reference)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Try to bring up the unmodified reference from ``baseline/_ref`` and report what stops it."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "mindformers")):
+        why = ("baseline/_ref holds no installed reference (pip install --no-index --no-deps --target baseline/_ref "
+               "<copy of the reference> has not been run on this machine)")
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    sys.path.insert(0, ref_dir)
+    try:
+        import mindformers  # noqa: F401  (the reference package, not this repository's)
+        from mindformers import Trainer  # noqa: F401
+    except BaseException as exc:  # noqa: BLE001  (whatever the import raises is the answer)
+        text = f"{type(exc).__name__}: {exc}".replace("\n", " ")[:300]
+        why = (f"`import mindformers` from baseline/_ref fails with {text}; the reference runs every device op through "
+               "MindSpore + Ascend CANN, which cannot be installed offline, and has no CUDA backend of its own")
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    finally:
+        sys.path.remove(ref_dir)
+    print(json.dumps({"impl": "reference", "unavailable": "the reference imported, but it has no CUDA device target "
+                      "(every YAML sets device_target Ascend): there is no stock code path to run on a B200"}))
     return 0
 
 
@@ -84,6 +105,9 @@ def main():
     ap.add_argument("--model", default="llama3_1_8b")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a valid bench)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-library-arm", action="store_true",
+                    help="skip the cuBLAS + SDPA + NCCL arm that is timed on the same engine after this repository's path")
+    ap.add_argument("--no-numerics-check", action="store_true")
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--recompute", type=int, default=0, help="recompute the activations of the first N layers in backward")
     ap.add_argument("--config", default="llama8b", choices=["llama8b", "qwen3_moe", "qwen25_cp"],
@@ -202,31 +226,90 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item(), clocks, _lib.launch_count(), last
 
-    # ---- device-timed metric ---------------------------------------------------------------------
-    for i in range(args.warmup):
-        out = engine.train_step_device(dev_batches[i % 2])
-        engine.adapt_moe_capacity()     # expert-parallel receive buffers grow here if routing overflowed them
-    total_ms, clocks, launches, out = timed(lambda i: engine.train_step_device(dev_batches[i % 2]), args.steps)
-    loss_val = float(out["loss"])
     tokens_per_step = (args.seqs_per_gpu * S) if cp > 1 else args.seqs_per_gpu * world * S
-    ms_per_step = total_ms / args.steps
-    value = tokens_per_step / (ms_per_step / 1e3)
 
-    # ---- end to end through the public API ---------------------------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        engine.train_step(host_batch(0))
-        e2e_ms, _, _, _ = timed(lambda i: engine.train_step(host_batch(i)), args.steps)
-        e2e = {"value": tokens_per_step / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
-               "h2d_bytes_per_step": engine.h2d_bytes, "d2h_bytes_per_step": engine.d2h_bytes,
-               "api": "mindformers_b200.trainer.engine.TrainingEngine.train_step"}
+    def set_library_path(on: bool):
+        """Library arm: cuBLAS GEMMs, SDPA attention, NCCL collectives through the same model code."""
+        Fn.set_gemm_backend("cublas" if on else "tcgen05")
+        Fn.set_attention_backend("sdpa" if on else "auto")
+        fused_comm.set_enabled(not on)
+        engine.optimizer.set_fused_dp(not on)
 
+    # ---- numerics of the fused multi-GPU paths against the NCCL path, once, before any timing ----
+    numerics = None
+    if world > 1 and args.impl == "ours" and not args.no_numerics_check:
+        mb = {k: v[:1] for k, v in dev_batches[0].items()}
+
+        def grads_of_one_micro_batch():
+            engine.model.train()
+            engine.optimizer.zero_grad()
+            loss = engine.step_fn.forward_fn(engine.model, mb)
+            loss.backward()
+            sumsq = engine.optimizer.reduce_and_norm().clone()
+            shards = {n: sh.grad.clone() for n, sh in engine.optimizer.shards.items()}
+            return loss.detach().float().clone(), sumsq, shards
+
+        loss_f, ss_f, g_f = grads_of_one_micro_batch()
+        set_library_path(True)
+        loss_l, ss_l, g_l = grads_of_one_micro_batch()
+        set_library_path(False)
+        num = sum(float((g_f[n].double() - g_l[n].double()).pow(2).sum()) for n in g_f)
+        den = sum(float(g_l[n].double().pow(2).sum()) for n in g_f)
+        numerics = {"what": "one micro-batch forward + backward + gradient reduction: fused TP / DP kernels and tcgen05 "
+                            "GEMM / attention vs cuBLAS + SDPA + NCCL on the same weights",
+                    "loss_fused": float(loss_f), "loss_library": float(loss_l),
+                    "grad_shard_rel_err": (num / max(den, 1e-30)) ** 0.5,
+                    "grad_norm_fused": float(ss_f.sqrt()), "grad_norm_library": float(ss_l.sqrt())}
+        t = torch.tensor([numerics["grad_shard_rel_err"], abs(numerics["loss_fused"] - numerics["loss_library"])],
+                         device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        numerics["grad_shard_rel_err_max_over_ranks"] = float(t[0])
+        numerics["loss_abs_diff_max_over_ranks"] = float(t[1])
+        if not (float(t[0]) < 5e-2 and float(t[1]) < 5e-2):
+            raise SystemExit(f"fused multi-GPU path disagrees with the NCCL path: {numerics}")
+        del g_f, g_l
+        engine.optimizer.zero_grad()
+
+    def run_arm():
+        """Warm-up, device-timed steps, then the end-to-end measurement through the public API."""
+        for i in range(args.warmup):
+            out = engine.train_step_device(dev_batches[i % 2])
+            engine.adapt_moe_capacity()     # expert-parallel receive buffers grow here if routing overflowed them
+        total_ms, clocks, launches, out = timed(lambda i: engine.train_step_device(dev_batches[i % 2]), args.steps)
+        ms_per_step = total_ms / args.steps
+        res = {"value": tokens_per_step / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "clocks": clocks,
+               "launches": launches, "final_loss": float(out["loss"]), "e2e": None}
+        if not args.no_e2e:
+            engine.train_step(host_batch(0))
+            e2e_ms, _, _, _ = timed(lambda i: engine.train_step(host_batch(i)), args.steps)
+            res["e2e"] = {"value": tokens_per_step / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": engine.h2d_bytes, "d2h_bytes_per_step": engine.d2h_bytes,
+                          "api": "mindformers_b200.trainer.engine.TrainingEngine.train_step"}
+        return res
+
+    mine = run_arm()
     status = _lib.read_status()
+    gemm_backend, attn_backend = Fn.get_gemm_backend(), Fn.get_attention_backend()
+
+    # ---- the library arm on the same engine, same lease, same clocks ----
+    library = None
+    if args.impl == "ours" and not args.no_library_arm:
+        set_library_path(True)
+        lib_res = run_arm()
+        set_library_path(False)
+        library = {"what": "same engine and weights with torch.matmul (cuBLAS), torch SDPA and NCCL collectives; "
+                           "none of this repository's GEMM / attention / fused-collective kernels",
+                   "value": lib_res["value"], "ms_per_step": lib_res["ms_per_step"], "clocks": lib_res["clocks"],
+                   "e2e": lib_res["e2e"]["value"] if lib_res["e2e"] else None, "final_loss": lib_res["final_loss"]}
+
     if rank == 0:
+        value, e2e = mine["value"], mine["e2e"]
         line = {
             "metric": "train tokens/s (box, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": mine["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": value / (BASELINE_TOKENS_PER_S_PER_DEVICE * world),
+            "vs_baseline_is": "value / (2703 tokens/s/device x N): the reference's published Llama-3.1-8B finetune "
+                              "figure on Ascend 910B at seq 8192, another chip and config, quoted for context only",
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": args.impl,
             "config": {"model": ("Llama-3.1-8B" if args.model == "llama3_1_8b" else args.model) if not args.layers else f"{args.model}(layers={args.layers})",
@@ -235,9 +318,13 @@ def main():
                                       + (f" ep{ep}" if ep > 1 else "") + f" dp{dp} distributed-optimizer",
                        "micro_batch": 1, "grad_accum_dtype": "fp32", "recompute_layers": args.recompute,
                        "l2": "working set (weights + activations, >100 GB) far exceeds the 126 MB L2 every step"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            "clocks": mine["clocks"], "e2e": e2e, "gpu_launches": mine["launches"], "final_loss": mine["final_loss"],
             "kernel_status_word": status,
-            "gemm_backend": Fn.get_gemm_backend(), "attention_backend": Fn.get_attention_backend(),
+            "gemm_backend": gemm_backend, "attention_backend": attn_backend,
+            "library_arm": library,
+            "vs_library": (value / library["value"]) if library else None,
+            "vs_library_e2e": (e2e["value"] / library["e2e"]) if library and e2e and library["e2e"] else None,
+            "multi_gpu_numerics": numerics,
         }
         print(json.dumps(line))
     if world > 1:

@@ -28,6 +28,11 @@
 // most one call ahead of a peer, because each call waits for data that the peer only produces in the
 // same call. Every wait is bounded and reports through the status word.
 //
+// PAIR = true runs COMM 1 / 2 on CTA pairs (`cta_group::2`, 256 x 256 MMA tiles, see gemm_tcgen05_2cta.cu):
+// the two CTAs of a cluster take the row blocks 2i and 2i+1 of one tile column, each loads its own A block
+// and its own half of the B tile, the even CTA issues the MMA for both. Everything that crosses ranks
+// (copy warps, block counters, tile flags, receive slots) stays per 128-row block, i.e. per CTA.
+//
 // No TMA load in this file uses cluster multicast, and no TMA load reads peer memory.
 #include "common.cuh"
 
@@ -123,19 +128,40 @@ __device__ __forceinline__ TpTile tp_tile(const TpArgs& a, int tile, int first_c
   return t;
 }
 
-template <int BN, int STAGES, bool B_MN, int COMM>
+// The same walk over pairs of row blocks: tile -> (pair of row blocks, column block); CTA `cta` of the cluster
+// takes row block 2 * pair + cta. Chunks hold an even number of row blocks, so a pair never straddles two ranks.
+__device__ __forceinline__ TpTile tp_tile_pair(const TpArgs& a, int tile, int first_chunk, int cta) {
+  constexpr int kBand = 8;
+  const int num_pairs = a.num_m_blocks >> 1;
+  const int tiles_per_band = kBand * a.num_n_blocks;
+  const int band = tile / tiles_per_band;
+  const int first_m = band * kBand;
+  const int band_h = (num_pairs - first_m) < kBand ? (num_pairs - first_m) : kBand;
+  const int r = tile - band * tiles_per_band;
+  int m = first_m + r % band_h;
+  const int ppc = (a.rows_per_chunk / kTpBM) >> 1;
+  m = (m + first_chunk * ppc) % num_pairs;
+  TpTile t;
+  t.m_blk = 2 * m + cta;
+  t.n_blk = r / band_h;
+  return t;
+}
+
+template <int BN, int STAGES, bool B_MN, int COMM, bool PAIR>
 __global__ void __launch_bounds__(COMM == 1 ? 320 : 192, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chunk; COMM 2: A [M, K]
                const __grid_constant__ CUtensorMap tmAfull,  // COMM 1: gathered A [M, K]
                const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmD,      // COMM 1: D [M, N]; COMM 2: D_r [M/tp, N]
                const TpArgs args) {
+  static_assert(!PAIR || (COMM != 3 && BN == 256), "CTA pairs serve the 256-wide training tiles only");
   constexpr int A_BYTES = kTpBM * kTpBK * 2;
-  constexpr int B_BYTES = BN * kTpBK * 2;
+  constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of B this CTA stages (a pair splits the tile's N)
+  constexpr int B_BYTES = B_ROWS * kTpBK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = 2 * BN;
   constexpr int NUM_CHUNKS = BN / 64;
-  constexpr uint32_t IDESC = umma_idesc_bf16(kTpBM, BN, 0, B_MN ? 1 : 0);
+  constexpr uint32_t IDESC = umma_idesc_bf16(PAIR ? 2 * kTpBM : kTpBM, BN, 0, B_MN ? 1 : 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -152,7 +178,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bpc = args.rows_per_chunk / kTpBM;  // row blocks per chunk
   const int k_blocks = (args.K + kTpBK - 1) / kTpBK;
-  const int n_tiles = args.num_m_blocks * args.num_n_blocks;
+  const int cta = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int wid = PAIR ? (blockIdx.x >> 1) : blockIdx.x;        // work-item walker: one per CTA or per pair
+  const int wstride = PAIR ? (gridDim.x >> 1) : gridDim.x;
+  const int n_tiles = (PAIR ? (args.num_m_blocks >> 1) : args.num_m_blocks) * args.num_n_blocks;
   const int ksplit = (COMM == 3 && args.ksplit > 1) ? args.ksplit : 1;
   const int k_per_split = (k_blocks + ksplit - 1) / ksplit;
   const int n_items = n_tiles * ksplit;
@@ -167,7 +196,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&tfull_bar[s]), 1);
-      mbar_init(smem_u32(&tempty_bar[s]), 4);
+      mbar_init(smem_u32(&tempty_bar[s]), PAIR ? 8 : 4);   // the epilogue warps of both CTAs of a pair
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -183,11 +212,17 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer CTA's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -197,11 +232,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int item = wid; item < n_items && ok; item += wstride) {
         const int tile = item / ksplit;
         const int kb0 = (item - tile * ksplit) * k_per_split;
         const int kb1 = (kb0 + k_per_split < k_blocks) ? kb0 + k_per_split : k_blocks;
-        const TpTile t = tp_tile(args, tile, first_chunk);
+        const TpTile t = PAIR ? tp_tile_pair(args, tile, first_chunk, cta) : tp_tile(args, tile, first_chunk);
         const int chunk = t.m_blk / bpc;
         const bool own = (COMM == 1) && (chunk == args.rank);
         if (COMM == 1 && !own) {
@@ -214,19 +249,37 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, args.status,
                          kStatusWaitTimeoutProducer);
           if (!ok) break;
-          const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, STAGE_BYTES);
+          const uint32_t fb_local = smem_u32(&full_bar[stage]);
           const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_dst = a_dst + A_BYTES;
-          if (own) tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, (t.m_blk - args.rank * bpc) * kTpBM);
-          else if (COMM == 1) tma_load_2d(a_dst, &tmAfull, fb, kb * kTpBK, t.m_blk * kTpBM);
-          else tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, t.m_blk * kTpBM);
-          if (B_MN) {
+          if (PAIR) {
+            // both CTAs' loads count on the even CTA's barrier, which expects the bytes of both
+            const uint32_t fb = mapa_shared(fb_local, 0);
+            if (cta == 0) mbar_expect_tx(fb_local, 2 * STAGE_BYTES);
+            const int b_n0 = t.n_blk * BN + cta * B_ROWS;
+            if (own) tma_load_2d_pair(a_dst, &tmA, fb, kb * kTpBK, (t.m_blk - args.rank * bpc) * kTpBM);
+            else if (COMM == 1) tma_load_2d_pair(a_dst, &tmAfull, fb, kb * kTpBK, t.m_blk * kTpBM);
+            else tma_load_2d_pair(a_dst, &tmA, fb, kb * kTpBK, t.m_blk * kTpBM);
+            if (B_MN) {
 #pragma unroll
-            for (int at = 0; at < BN / 64; ++at)
-              tma_load_2d(b_dst + at * (kTpBK * 128), &tmB, fb, t.n_blk * BN + at * 64, kb * kTpBK);
+              for (int at = 0; at < B_ROWS / 64; ++at)
+                tma_load_2d_pair(b_dst + at * (kTpBK * 128), &tmB, fb, b_n0 + at * 64, kb * kTpBK);
+            } else {
+              tma_load_2d_pair(b_dst, &tmB, fb, kb * kTpBK, b_n0);
+            }
           } else {
-            tma_load_2d(b_dst, &tmB, fb, kb * kTpBK, t.n_blk * BN);
+            const uint32_t fb = fb_local;
+            mbar_expect_tx(fb, STAGE_BYTES);
+            if (own) tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, (t.m_blk - args.rank * bpc) * kTpBM);
+            else if (COMM == 1) tma_load_2d(a_dst, &tmAfull, fb, kb * kTpBK, t.m_blk * kTpBM);
+            else tma_load_2d(a_dst, &tmA, fb, kb * kTpBK, t.m_blk * kTpBM);
+            if (B_MN) {
+#pragma unroll
+              for (int at = 0; at < BN / 64; ++at)
+                tma_load_2d(b_dst + at * (kTpBK * 128), &tmB, fb, t.n_blk * BN + at * 64, kb * kTpBK);
+            } else {
+              tma_load_2d(b_dst, &tmB, fb, kb * kTpBK, t.n_blk * BN);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -235,11 +288,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && cta == 0) {   // in a pair the even CTA issues the MMAs of both
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int item = wid; item < n_items && ok; item += wstride) {
         const int kb0 = (item % ksplit) * k_per_split;
         const int kb1 = (kb0 + k_per_split < k_blocks) ? kb0 + k_per_split : k_blocks;
         ok = mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1, abort_flag, args.status, kStatusWaitTimeoutMma);
@@ -257,13 +310,16 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
             const uint64_t a_desc = umma_desc_kmajor_sw128(a_base + k * 32);
             const uint64_t b_desc = B_MN ? umma_desc_mnmajor_sw128(b_base + k * 16 * 128, kTpBK * 128)
                                          : umma_desc_kmajor_sw128(b_base + k * 32);
-            umma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR) umma_f16_ss_pair(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&empty_bar[stage]));
+          if (PAIR) umma_commit_pair(smem_u32(&empty_bar[stage]));
+          else umma_commit(smem_u32(&empty_bar[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&tfull_bar[acc]));
+        if (PAIR) umma_commit_pair(smem_u32(&tfull_bar[acc]));
+        else umma_commit(smem_u32(&tfull_bar[acc]));
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -279,10 +335,13 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     const int parity = args.epoch & 1;
     const size_t slot_elems = static_cast<size_t>(args.rows_per_chunk) * args.N;
     const int tiles_per_chunk = bpc * args.num_n_blocks;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    // accumulator-drained arrivals go to the even CTA of a pair (its own barrier otherwise)
+    const uint32_t tempty0 = PAIR ? mapa_shared(smem_u32(&tempty_bar[0]), 0) : smem_u32(&tempty_bar[0]);
+    const uint32_t tempty1 = PAIR ? mapa_shared(smem_u32(&tempty_bar[1]), 0) : smem_u32(&tempty_bar[1]);
+    for (int item = wid; item < n_items && ok; item += wstride) {
       const int tile = item / ksplit;
       const int ks = item - tile * ksplit;
-      const TpTile t = tp_tile(args, tile, first_chunk);
+      const TpTile t = PAIR ? tp_tile_pair(args, tile, first_chunk, cta) : tp_tile(args, tile, first_chunk);
       const int owner = t.m_blk / bpc;
       const int mb_local = t.m_blk - owner * bpc;
       const int tile_in_chunk = mb_local * args.num_n_blocks + t.n_blk;
@@ -550,7 +609,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(acc == 0 ? tempty0 : tempty1);
+        else mbar_arrive(smem_u32(&tempty_bar[acc]));
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (issuer) tma_wait_group<0>();
@@ -592,9 +654,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA of a pair leaves while the other may still signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -603,12 +667,15 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
 namespace {
 using namespace mfb;
 
-template <int BN, int STAGES, bool B_MN, int COMM>
+bool g_tp_pair_enabled = true;
+
+template <int BN, int STAGES, bool B_MN, int COMM, bool PAIR = false>
 int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& tB, const CUtensorMap& tD,
               const TpArgs& a, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = kTpBM * kTpBK * 2 + BN * kTpBK * 2;
+  constexpr int STAGE_BYTES = kTpBM * kTpBK * 2 + (PAIR ? BN / 2 : BN) * kTpBK * 2;
   constexpr int SMEM = STAGES * STAGE_BYTES + 2 * kTpStaging + (2 * STAGES + 4) * 8 + 16 + 1024;
-  auto kern = tp_gemm_kernel<BN, STAGES, B_MN, COMM>;
+  static_assert(SMEM <= 232448, "shared memory budget exceeded");
+  auto kern = tp_gemm_kernel<BN, STAGES, B_MN, COMM, PAIR>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
@@ -622,7 +689,28 @@ int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = a.num_m_blocks * a.num_n_blocks * (COMM == 3 && a.ksplit > 1 ? a.ksplit : 1);
   // COMM 1 needs the gather warps of every CTA to be resident, whatever the tile count
-  const int grid = (COMM == 1) ? sms : (tiles < sms ? tiles : sms);
+  int grid = (COMM == 1) ? sms : (tiles < sms ? tiles : sms);
+  if (PAIR) {
+    grid &= ~1;   // whole pairs; `tiles` counts 128-row blocks, i.e. one CTA each
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(COMM == 1 ? 320 : 192);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tA, tAf, tB, tD, a);
+    if (e != cudaSuccess) {
+      mfb_host::set_error("tp gemm (pairs): launch failed: %s", cudaGetErrorString(e));
+      return 11;
+    }
+    return 0;
+  }
   kern<<<grid, COMM == 1 ? 320 : 192, SMEM, stream>>>(tA, tAf, tB, tD, a);
   if (cudaGetLastError() != cudaSuccess) {
     mfb_host::set_error("tp gemm: launch failed");
@@ -655,6 +743,8 @@ int mfb_tp_allgather_gemm(const void* const* peer_a, long long lda, void* a_full
   for (int p = 0; p < tp; ++p) { a.peer_a[p] = (const __nv_bfloat16*)peer_a[p]; a.ready_peer[p] = ready_peer[p]; }
   const bool bn256 = N >= 256;
   const int BN = bn256 ? 256 : 128;
+  // CTA pairs: 256-wide tiles and an even number of 128-row blocks per rank
+  const bool pair = g_tp_pair_enabled && bn256 && (a.rows_per_chunk % (2 * kTpBM) == 0);
   a.num_n_blocks = (N + BN - 1) / BN;
   cudaMemsetAsync(block_flags, 0, sizeof(int) * a.num_m_blocks, stream);
   CUtensorMap tA, tAf, tB, tD;
@@ -663,9 +753,11 @@ int mfb_tp_allgather_gemm(const void* const* peer_a, long long lda, void* a_full
   if ((rc = mfb_host::make_tmap_2d(&tA, peer_a[rank], 2, BF, a.rows_per_chunk, K, lda, kTpBM, kTpBK))) return 20 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tAf, a_full, 2, BF, M, K, K, kTpBM, kTpBK))) return 30 + rc;
   if (b_mn_major) rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, K, N, ldb, kTpBK, 64);
-  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, BN, kTpBK);
+  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, pair ? BN / 2 : BN, kTpBK);
   if (rc) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, M, N, ldd, kTpBM, 64))) return 50 + rc;
+  if (pair) return b_mn_major ? tp_launch<256, 6, true, 1, true>(tA, tAf, tB, tD, a, stream)
+                              : tp_launch<256, 6, false, 1, true>(tA, tAf, tB, tD, a, stream);
   if (bn256) return b_mn_major ? tp_launch<256, 4, true, 1>(tA, tAf, tB, tD, a, stream)
                                : tp_launch<256, 4, false, 1>(tA, tAf, tB, tD, a, stream);
   return b_mn_major ? tp_launch<128, 6, true, 1>(tA, tAf, tB, tD, a, stream)
@@ -690,15 +782,18 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
   for (int p = 0; p < tp; ++p) { a.recv_peer[p] = (__nv_bfloat16*)recv_peer[p]; a.tile_flags_peer[p] = tile_flags_peer[p]; }
   const bool bn256 = N >= 256;
   const int BN = bn256 ? 256 : 128;
+  const bool pair = g_tp_pair_enabled && bn256 && (a.rows_per_chunk % (2 * kTpBM) == 0);
   a.num_n_blocks = (N + BN - 1) / BN;
   CUtensorMap tA, tB, tD;
   int rc;
   const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if ((rc = mfb_host::make_tmap_2d(&tA, A, 2, BF, M, K, lda, kTpBM, kTpBK))) return 20 + rc;
   if (b_mn_major) rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, K, N, ldb, kTpBK, 64);
-  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, BN, kTpBK);
+  else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, pair ? BN / 2 : BN, kTpBK);
   if (rc) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, a.rows_per_chunk, N, ldd, kTpBM, 64))) return 50 + rc;
+  if (pair) return b_mn_major ? tp_launch<256, 6, true, 2, true>(tA, tA, tB, tD, a, stream)
+                              : tp_launch<256, 6, false, 2, true>(tA, tA, tB, tD, a, stream);
   if (bn256) return b_mn_major ? tp_launch<256, 4, true, 2>(tA, tA, tB, tD, a, stream)
                                : tp_launch<256, 4, false, 2>(tA, tA, tB, tD, a, stream);
   return b_mn_major ? tp_launch<128, 6, true, 2>(tA, tA, tB, tD, a, stream)
@@ -762,6 +857,9 @@ int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, i
   return b_mn_major ? tp_launch<128, 6, true, 3>(tA, tA, tB, tD, a, stream)
                     : tp_launch<128, 6, false, 3>(tA, tA, tB, tD, a, stream);
 }
+
+// Switch the CTA-pair variant of the all-gather and reduce-scatter GEMMs (on by default) for A/B measurements.
+void mfb_tp_set_pair(int enabled) { g_tp_pair_enabled = enabled != 0; }
 
 // Upper bound of ceil(N / BN) that the flag arrays must provide room for.
 int mfb_tp_num_n_blocks(int N) { return N >= 256 ? (N + 255) / 256 : (N + 127) / 128; }

@@ -189,11 +189,25 @@ class DistributedOptimizer:
             dist.all_reduce(self.sumsq, group=world)
         return self.sumsq
 
-    def step(self, grad_scale: float = 1.0):
-        """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""
+    def set_fused_dp(self, flag: bool):
+        """Switch the shards that were set up for the peer-memory reduce-scatter / AdamW / all-gather kernels
+        between those kernels and the NCCL collectives (the buffers serve both). Every rank must switch at the
+        same step. Used by the benchmark to time the library path on the same engine."""
+        for sh in self.shards.values():
+            if not hasattr(sh, "_fused_capable"):
+                sh._fused_capable = bool(getattr(sh, "fused", False))
+            sh.fused = bool(flag) and sh._fused_capable
+
+    def reduce_and_norm(self) -> torch.Tensor:
+        """Gradient reduction (tensor-parallel replicas, data-parallel reduce-scatter) and the squared global
+        norm of the reduced gradients, without the parameter update: the first half of ``step``."""
         self._dp_epoch += 1
         self.reduce_gradients()
-        self._global_sumsq()
+        return self._global_sumsq()
+
+    def step(self, grad_scale: float = 1.0):
+        """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""
+        self.reduce_and_norm()
         self.global_step += 1
         lr = self.current_lr()
         self.skipped.zero_()
