@@ -253,8 +253,11 @@ def main():
         set_library_path(True)
         loss_l, ss_l, g_l = grads_of_one_micro_batch()
         set_library_path(False)
-        num = sum(float((g_f[n].double() - g_l[n].double()).pow(2).sum()) for n in g_f)
-        den = sum(float(g_l[n].double().pow(2).sum()) for n in g_f)
+        num = den = 0.0
+        for n in g_f:                       # in pieces: a shard can be tens of GB
+            for a, b in zip(g_f[n].split(1 << 26), g_l[n].split(1 << 26)):
+                num += float((a.float() - b.float()).pow(2).sum(dtype=torch.float64))
+                den += float(b.float().pow(2).sum(dtype=torch.float64))
         numerics = {"what": "one micro-batch forward + backward + gradient reduction: fused TP / DP kernels and tcgen05 "
                             "GEMM / attention vs cuBLAS + SDPA + NCCL on the same weights",
                     "loss_fused": float(loss_f), "loss_library": float(loss_l),

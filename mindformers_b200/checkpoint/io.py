@@ -49,34 +49,49 @@ def model_state(model: torch.nn.Module, trainable_only: bool = False) -> Dict[st
     return out
 
 
-def save_checkpoint(model: torch.nn.Module, directory: str, *, optimizer=None, prefix: str = "mindformers",
-                    epoch: int = 0, step: int = 0, extra: Optional[dict] = None, keep_max: int = 5,
-                    save_network_only_copy: bool = False, trainable_only: bool = False,
-                    remove_redundancy: bool = False, write_strategy: bool = True) -> str:
-    """Write this rank's checkpoint; returns the file path."""
-    rank = get_real_rank()
-    rank_dir = os.path.join(directory, f"rank_{rank}")
-    os.makedirs(rank_dir, exist_ok=True)
-    tensors = {}
+def _to_host(t: torch.Tensor) -> torch.Tensor:
+    """A host copy that no later device work can change. CUDA tensors are copied into pinned memory on the current
+    stream (the caller synchronises once after all copies are queued)."""
+    t = t.detach()
+    if t.is_cuda:
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        host.copy_(t, non_blocking=True)
+        return host
+    return t.contiguous().clone()
+
+
+def snapshot_checkpoint(model: torch.nn.Module, *, optimizer=None, epoch: int = 0, step: int = 0,
+                        extra: Optional[dict] = None, trainable_only: bool = False,
+                        remove_redundancy: bool = False) -> Dict[str, torch.Tensor]:
+    """Host snapshot of everything a checkpoint file holds, taken on the training stream: parameters, this rank's
+    optimizer states and the scalar entries. After this returns the training loop may go on changing the device
+    tensors; ``write_checkpoint`` (possibly on another thread) only sees the copies."""
+    tensors: Dict[str, torch.Tensor] = {}
     for n, t in model_state(model, trainable_only).items():
         if remove_redundancy and _is_redundant(n, model):
             continue
-        tensors[n] = t.contiguous().cpu()
+        tensors[n] = _to_host(t)
     if optimizer is not None and hasattr(optimizer, "named_states"):
         for n, t in optimizer.named_states().items():
-            tensors[n] = t.contiguous().cpu()
-        if hasattr(optimizer, "shards"):
-            for sname, sh in optimizer.shards.items():
-                if sh.world > 1:   # sharded optimizer: store the flat slices
-                    tensors[f"__shard__.{sname}.adam_m"] = sh.m.cpu()
-                    tensors[f"__shard__.{sname}.adam_v"] = sh.v.cpu()
-                    if sh.lo is not None:
-                        tensors[f"__shard__.{sname}.master_lo"] = sh.lo.cpu()
+            tensors[n] = _to_host(t)
         tensors["global_step"] = torch.tensor(int(getattr(optimizer, "global_step", 0)), dtype=torch.int64)
+    if torch.cuda.is_available():
+        torch.cuda.current_stream().synchronize()
     scalars = {"epoch_num": epoch, "step_num": step}
     scalars.update(extra or {})
     for k, v in scalars.items():
         tensors[k] = torch.tensor(v, dtype=torch.float32 if isinstance(v, float) else torch.int64)
+    return tensors
+
+
+def write_checkpoint(tensors: Dict[str, torch.Tensor], directory: str, *, rank: Optional[int] = None,
+                     prefix: str = "mindformers", epoch: int = 0, step: int = 0, keep_max: int = 5,
+                     remove_redundancy: bool = False, network_only_dir: Optional[str] = None) -> str:
+    """Write a snapshot as ``rank_{r}/{prefix}_rank_{r}-{epoch}_{step}.safetensors`` (atomically), update
+    ``meta.json`` and rotate old files. Touches no device memory: safe on a background thread."""
+    rank = get_real_rank() if rank is None else rank
+    rank_dir = os.path.join(directory, f"rank_{rank}")
+    os.makedirs(rank_dir, exist_ok=True)
     name = format_ckpt_name(prefix, rank, epoch, step)
     path = os.path.join(rank_dir, name)
     tmp = path + ".tmp"
@@ -88,14 +103,29 @@ def save_checkpoint(model: torch.nn.Module, directory: str, *, optimizer=None, p
         json.dump(meta, f)
     os.replace(mtmp, os.path.join(rank_dir, "meta.json"))
     _rotate(rank_dir, prefix, keep_max)
-    if write_strategy:
-        sdir = os.path.join(os.path.dirname(directory.rstrip("/")) or ".", "strategy")
-        save_strategy(model, os.path.join(sdir, f"ckpt_strategy_rank_{rank}.json"))
-    if save_network_only_copy:
-        ndir = os.path.join(os.path.dirname(directory.rstrip("/")) or ".", "checkpoint_network", f"rank_{rank}")
+    if network_only_dir:
+        ndir = os.path.join(network_only_dir, f"rank_{rank}")
         os.makedirs(ndir, exist_ok=True)
-        save_file({n: t.contiguous().cpu() for n, t in model_state(model).items()}, os.path.join(ndir, name))
+        skip = ("adam_m.", "adam_v.", "master_lo.", "__slice__.")
+        save_file({n: t for n, t in tensors.items() if not n.startswith(skip) and n not in SCALAR_KEYS},
+                  os.path.join(ndir, name))
     return path
+
+
+def save_checkpoint(model: torch.nn.Module, directory: str, *, optimizer=None, prefix: str = "mindformers",
+                    epoch: int = 0, step: int = 0, extra: Optional[dict] = None, keep_max: int = 5,
+                    save_network_only_copy: bool = False, trainable_only: bool = False,
+                    remove_redundancy: bool = False, write_strategy: bool = True) -> str:
+    """Write this rank's checkpoint (snapshot + write in one call); returns the file path."""
+    tensors = snapshot_checkpoint(model, optimizer=optimizer, epoch=epoch, step=step, extra=extra,
+                                  trainable_only=trainable_only, remove_redundancy=remove_redundancy)
+    rank = get_real_rank()
+    root = os.path.dirname(directory.rstrip("/")) or "."
+    if write_strategy:
+        save_strategy(model, os.path.join(root, "strategy", f"ckpt_strategy_rank_{rank}.json"))
+    return write_checkpoint(tensors, directory, rank=rank, prefix=prefix, epoch=epoch, step=step, keep_max=keep_max,
+                            remove_redundancy=remove_redundancy,
+                            network_only_dir=os.path.join(root, "checkpoint_network") if save_network_only_copy else None)
 
 
 def _is_redundant(name: str, model) -> bool:
@@ -133,14 +163,22 @@ def _read_files(files) -> Dict[str, torch.Tensor]:
     return out
 
 
-def resolve_checkpoint(path: str, rank: Optional[int] = None) -> Tuple[str, list]:
-    """Classify ``path`` → (kind, files) with kind in {"file", "dir", "rank_dirs", "hf"}."""
+def resolve_checkpoint(path: str, rank: Optional[int] = None, point: Optional[Tuple[int, int]] = None) -> Tuple[str, list]:
+    """Classify ``path`` → (kind, files) with kind in {"file", "dir", "rank_dirs", "hf"}. With ``point`` =
+    (epoch, step) the file of exactly that save is taken from the rank directory (the resume point that all ranks
+    agreed on) instead of the rank's own newest file."""
     rank = get_real_rank() if rank is None else rank
     if os.path.isfile(path):
         return "file", [path]
     if is_hf_safetensors_dir(path):
         return "hf", sorted(glob.glob(os.path.join(path, "*.safetensors")))
     rdir = os.path.join(path, f"rank_{rank}")
+    if os.path.isdir(rdir) and point is not None:
+        from .resume import checkpoint_file_for
+        f = checkpoint_file_for(path, rank, int(point[0]), int(point[1]))
+        if f is None:
+            raise FileNotFoundError(f"rank {rank} has no checkpoint of epoch {point[0]} step {point[1]} under {path}")
+        return "rank_dirs", [f]
     if os.path.isdir(rdir):
         meta = os.path.join(rdir, "meta.json")
         if os.path.exists(meta):
@@ -156,22 +194,58 @@ def resolve_checkpoint(path: str, rank: Optional[int] = None) -> Tuple[str, list
     raise FileNotFoundError(f"no safetensors checkpoint found under {path}")
 
 
+def _file_removed_redundancy(path: str) -> bool:
+    try:
+        with safe_open(path, framework="pt") as f:
+            return (f.metadata() or {}).get("remove_redundancy") == "True"
+    except Exception:  # noqa: BLE001  (an unreadable header shows up as a load error right after)
+        return False
+
+
+def _tp_first_rank_file(path: str, own_file: str) -> Optional[str]:
+    """The file of the same save written by the first rank of this rank's tensor-parallel group (same data- and
+    pipeline-parallel position): with ``remove_redundancy`` it alone holds the tensor-parallel-replicated tensors."""
+    parsed = parse_ckpt_name(own_file)
+    if parsed is None or not ps.model_parallel_is_initialized():
+        return None
+    first = ps.get_group_ranks("tp")[0]
+    from .resume import checkpoint_file_for
+    return checkpoint_file_for(path, first, parsed[2], parsed[3])
+
+
 def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict: bool = True, family: str = "llama",
-                    sharded: Optional[bool] = None) -> dict:
+                    sharded: Optional[bool] = None, point: Optional[Tuple[int, int]] = None) -> dict:
     """Load parameters (and optimizer state when given). Returns the scalar entries (epoch, step, ...).
 
     ``sharded``: the tensors in the file are already this rank's slices (default for ``rank_N`` layouts); full
-    tensors (single files, plain directories, HF directories) are sliced by ``shard_for_param``.
+    tensors (single files, plain directories, HF directories) are sliced by ``shard_for_param``. ``point``: the
+    (epoch, step) every rank resumes from (``checkpoint.resume.get_resume_checkpoint``).
     """
-    kind, files = resolve_checkpoint(path)
+    kind, files = resolve_checkpoint(path, point=point)
     if kind == "hf" and optimizer is None:
         # a pretrained directory can be far larger than host memory: stream it layer by layer
         from ..inference.weights_utils import load_weights
         load_weights(model, path, family=family, strict=strict)
         return {}
     sd = _read_files(files)
+    if kind == "rank_dirs" and files and _file_removed_redundancy(files[0]) and ps.get_tensor_model_parallel_rank() != 0:
+        # replicated tensors were written by the first tensor-parallel rank only: take them from its file
+        other = _tp_first_rank_file(path, files[0])
+        if other is None:
+            raise FileNotFoundError(f"{files[0]} was saved with remove_redundancy; the file of the first "
+                                    "tensor-parallel rank, which holds the replicated tensors, is missing")
+        extra_sd = load_file(other)
+        own_params = dict(model.named_parameters())
+        for k, v in extra_sd.items():
+            base = k.split(".", 1)[1] if k.startswith(("adam_m.", "adam_v.", "master_lo.", "__slice__.")) else k
+            p = own_params.get(base)
+            replicated = p is not None and not getattr(p, "tensor_model_parallel", False) and not getattr(p, "is_expert", False)
+            if k not in sd and replicated:
+                sd[k] = v
     if kind == "hf":
         sd = name_maps.hf_to_framework(sd, model.config, family)
+    if kind == "dir" and os.path.exists(os.path.join(path, "hyper_param.safetensors")) and "global_step" not in sd:
+        sd.update(load_file(os.path.join(path, "hyper_param.safetensors")))
     if sharded is None:
         sharded = kind == "rank_dirs"
     params = dict(model.named_parameters())
@@ -215,18 +289,11 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
     if optimizer is not None:
         if hasattr(optimizer, "reload_model_params"):
             optimizer.reload_model_params()
-        states = {k: v for k, v in sd.items() if k.startswith(("adam_m.", "adam_v.", "master_lo."))}
+        states = {k: v for k, v in sd.items() if k.startswith(("adam_m.", "adam_v.", "master_lo.", "__slice__."))}
         if states and hasattr(optimizer, "load_named_states"):
-            optimizer.load_named_states({k: v.to(next(model.parameters()).device) for k, v in states.items()},
-                                        scalars.get("global_step"))
+            optimizer.load_named_states(states, scalars.get("global_step"), strict=strict, model_params=params)
         elif "global_step" in scalars:
             optimizer.global_step = int(scalars["global_step"])
-        if hasattr(optimizer, "shards"):
-            for sname, sh in optimizer.shards.items():
-                for key, dst in (("adam_m", sh.m), ("adam_v", sh.v), ("master_lo", sh.lo)):
-                    src = sd.get(f"__shard__.{sname}.{key}")
-                    if src is not None and dst is not None and src.numel() == dst.numel():
-                        dst.copy_(src.to(dst.device))
     return scalars
 
 

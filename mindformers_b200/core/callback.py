@@ -320,12 +320,21 @@ class CheckpointMonitor(Callback):
                   remove_redundancy=self.remove_redundancy)
         t0 = time.time()
         if self.async_save and not tag_exception:
-            # device→host copies happen here (inside save_checkpoint's .cpu() calls run in the thread after a
-            # stream sync), the file write overlaps the following steps
+            # the state is copied to pinned host memory on the training stream before this returns; the thread only
+            # writes those copies, so steps that run meanwhile cannot leak into the file
             import threading
-            torch.cuda.synchronize() if torch.cuda.is_available() else None
-            snap_model, d = engine.model, self._dir()
-            th = threading.Thread(target=lambda: self.saved.append(save_checkpoint(snap_model, d, **kw)), daemon=True)
+            from ..checkpoint.io import snapshot_checkpoint, write_checkpoint
+            from ..checkpoint.sharding import save_strategy
+            from ..tools.utils import get_real_rank
+            d, rank = self._dir(), get_real_rank()
+            root = os.path.dirname(d.rstrip("/")) or "."
+            snap = snapshot_checkpoint(engine.model, optimizer=kw["optimizer"], epoch=kw["epoch"], step=kw["step"],
+                                       extra=extra, remove_redundancy=self.remove_redundancy)
+            save_strategy(engine.model, os.path.join(root, "strategy", f"ckpt_strategy_rank_{rank}.json"))
+            wkw = dict(rank=rank, prefix=self.prefix, epoch=kw["epoch"], step=kw["step"], keep_max=self.keep_max,
+                       remove_redundancy=self.remove_redundancy,
+                       network_only_dir=os.path.join(root, "checkpoint_network") if self.save_network else None)
+            th = threading.Thread(target=lambda: self.saved.append(write_checkpoint(snap, d, **wkw)), daemon=True)
             th.start()
             self._pending = th
             path = None

@@ -134,6 +134,100 @@ def get_optimizer_grouped_parameters(model: torch.nn.Module, weight_decay: float
     return list(groups.values())
 
 
+class ReplicatedOptimizer:
+    """Runs any ``torch.optim`` style optimizer (``CAME``, ``SGD``, ...) behind the interface the train step expects
+    from the sharded AdamW: ``zero_grad()``, ``step(grad_scale)``, ``global_norm()``, ``skipped``, ``current_lr()``,
+    ``global_step``, ``named_states()``. State is replicated over the data-parallel group: gradients are all-reduced
+    (NCCL / gloo), the global norm is taken over all model-parallel ranks with tensor-parallel replicas counted once,
+    clipping follows ``core/clip_grad.py`` (``max_norm / (norm + 1e-6)`` when the norm exceeds ``max_norm``), and
+    a non-finite norm skips the update. This is how the trainer honours ``optimizer.type`` other than AdamW."""
+
+    def __init__(self, model: torch.nn.Module, inner: torch.optim.Optimizer, learning_rate, max_grad_norm: float = 1.0,
+                 sequence_parallel: bool = False):
+        import torch.distributed as dist
+        from ..parallel import parallel_state as ps
+        self._dist, self._ps = dist, ps
+        self.model, self.inner, self.lr = model, inner, learning_rate
+        self.max_grad_norm, self.sequence_parallel = max_grad_norm, sequence_parallel
+        self.global_step = 0
+        dev = next(model.parameters()).device
+        self.skipped = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._base_lrs = [g.get("lr", 0.0) for g in inner.param_groups]
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.inner.zero_grad(set_to_none=True)
+
+    def current_lr(self) -> float:
+        return float(self.lr(self.global_step) if callable(self.lr) else self.lr)
+
+    def step(self, grad_scale: float = 1.0):
+        dist, ps = self._dist, self._ps
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        dp_group = ps.get_data_parallel_group(with_context_parallel=True) if multi else None
+        tp = ps.get_tensor_model_parallel_world_size()
+        self.sumsq.zero_()
+        for p in self.model.parameters():
+            if p.grad is None:
+                continue
+            if multi and ps.get_data_parallel_world_size(with_context_parallel=True) > 1:
+                dist.all_reduce(p.grad, group=dp_group)
+            if multi and tp > 1 and self.sequence_parallel and getattr(p, "sequence_parallel", False):
+                dist.all_reduce(p.grad, group=ps.get_tensor_model_parallel_group())
+            p.grad.mul_(grad_scale)
+            ss = p.grad.float().pow(2).sum()
+            replicated = tp > 1 and not getattr(p, "tensor_model_parallel", False) and not getattr(p, "is_expert", False)
+            self.sumsq += ss / tp if replicated else ss
+        if multi:
+            dist.all_reduce(self.sumsq, group=ps.get_world_group())
+            dpw = ps.get_data_parallel_world_size(with_context_parallel=True)
+            if dpw > 1:
+                self.sumsq /= dpw               # data-parallel replicas hold the same (already reduced) gradients
+        norm = float(self.sumsq.sqrt())
+        self.global_step += 1
+        bad = not (norm == norm and norm != float("inf"))
+        self.skipped.fill_(int(bad))
+        if bad:
+            return self.sumsq
+        if self.max_grad_norm > 0 and norm >= self.max_grad_norm:
+            coef = self.max_grad_norm / (norm + 1e-6)
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    p.grad.mul_(coef)
+        lr = self.current_lr()
+        for g in self.inner.param_groups:
+            g["lr"] = lr * g.get("lr_scale", 1.0)
+        self.inner.step()
+        return self.sumsq
+
+    def global_norm(self, grad_scale: float = 1.0) -> torch.Tensor:
+        return self.sumsq.sqrt()        # ``step`` scaled the gradients before taking the norm
+
+    def named_states(self):
+        names = {id(p): n for n, p in self.model.named_parameters()}
+        out = {}
+        for p, st in self.inner.state.items():
+            for k, v in st.items():
+                if torch.is_tensor(v):
+                    out[f"{k}.{names.get(id(p), 'param')}"] = v
+        return out
+
+    def load_named_states(self, states, global_step=None, strict: bool = False, model_params=None):
+        by_name = dict(self.model.named_parameters())
+        for key, v in states.items():
+            if key.startswith("__slice__."):
+                continue
+            k, _, pname = key.partition(".")
+            p = by_name.get(pname)
+            if p is not None:
+                self.inner.state.setdefault(p, {})[k] = v.to(p.device)
+        if global_step is not None:
+            self.global_step = int(global_step)
+
+    def state_norms(self):
+        return {}
+
+
 def build_optim(config: dict, default_args: Optional[dict] = None, model: Optional[torch.nn.Module] = None, **kwargs):
     """Instantiate the optimizer named by ``config['type']``; ``model`` is passed as ``params``."""
     cfg = dict(config or {})

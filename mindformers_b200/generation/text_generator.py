@@ -174,6 +174,22 @@ class GenerationMixin:
 
     # ---- public API -----------------------------------------------------------------------------------
     @torch.no_grad()
+    def _check_device_status(self):
+        """After the last token was read back: a kernel whose bounded wait ran out, or an expert-parallel receive
+        buffer that overflowed (token rows dropped), makes the generated text wrong, so both raise here instead of
+        passing silently. Costs one 8-byte read; the sampling of the last token has synchronised already."""
+        dev = next(self.model.parameters()).device
+        if dev.type != "cuda":
+            return
+        from ..ops import _lib
+        code, overflow = _lib.read_status_words(dev)
+        _lib.raise_on_status(code, "during generate()")
+        if overflow:
+            _lib.status_word(dev)[1:2].zero_()
+            raise RuntimeError("expert-parallel receive buffers overflowed during generate(): token rows were dropped. "
+                               "Set moe_ep_buffer_factor in the model configuration to the expert-parallel size "
+                               "(worst case) or generate with fewer tokens per prefill chunk")
+
     def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]], torch.Tensor],
                  generation_config: Optional[GenerationConfig] = None, logits_processor: Optional[LogitsProcessorList] = None,
                  streamer=None, seed: Optional[int] = None, **kwargs):
@@ -288,6 +304,7 @@ class GenerationMixin:
         if streamer is not None:
             streamer.end()
         tables.clear_cache()
+        self._check_device_status()
         dt = max(time.time() - t0, 1e-9)
         self.last_generation_stats = {"ttft_s": ttft, "new_tokens": new_tokens, "total_s": dt,
                                       "tokens_per_s": new_tokens / dt}

@@ -198,17 +198,41 @@ _status_words: dict = {}
 
 
 def status_word(device) -> torch.Tensor:
-    """Per-device int32 word that kernels with bounded waits write their error code to."""
+    """Per-device pair of int32 words that kernels report through. Word 0 takes the code of the first bounded wait
+    that ran out (kernels get its address); word 1, right behind it, is set by the expert-parallel plan kernel when
+    a receive buffer overflowed, so that an earlier time-out code cannot hide an overflow or the other way round."""
     key = torch.device(device).index or 0
     t = _status_words.get(key)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
+        t = torch.zeros(2, dtype=torch.int32, device=device)
         _status_words[key] = t
     return t
 
 
 def read_status(device=None) -> int:
-    """Synchronising read of the status word (0 = every bounded wait completed)."""
+    """Synchronising read of the wait status (0 = every bounded wait completed)."""
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    return int(status_word(device).item())
+    return int(status_word(device)[0].item())
+
+
+def read_status_words(device=None):
+    """Synchronising read of ``(wait status, expert-parallel overflow flag)``."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    a, b = status_word(device).tolist()
+    return int(a), int(b)
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait (mbarrier phase, peer flag) ran out: the step's results are incomplete."""
+
+
+_STATUS_NAMES = {1: "TMA producer wait", 2: "MMA issuer wait", 3: "epilogue wait", 4: "peer flag wait (another rank "
+                 "did not arrive)", 5: "bad kernel argument"}
+
+
+def raise_on_status(code: int, where: str = ""):
+    if code:
+        raise DeviceWaitTimeout(f"device status {code} ({_STATUS_NAMES.get(code, 'unknown')}) {where}: a bounded wait "
+                                "inside a kernel ran out, so its output is incomplete; the run cannot continue on it")

@@ -160,7 +160,8 @@ moe_plan_kernel(MoePlanArgs a) {
     }
     if (e == a.rank) {
       seg[a.E] = off;
-      if (off > a.rows_cap && a.status) atomicCAS(a.status, 0, kStatusMoeOverflow);
+      // overflow has a word of its own right behind the wait status, so neither can hide the other
+      if (off > a.rows_cap && a.status) atomicExch(a.status + 1, 1);
     }
   }
   __syncthreads();

@@ -292,7 +292,12 @@ _scratch_cache: dict = {}
 
 
 def _scratch(device, nfloats: int) -> torch.Tensor:
-    key = (torch.device(device).index or 0)
+    """Reusable fp32 scratch of at least ``nfloats`` elements for the CURRENT stream of ``device``. The cache is keyed
+    by (device, stream): kernels of two streams (``MicroBatchInterleaved`` copies, side-stream reductions) may be in
+    flight together and must not share partial sums. A buffer is allocated while its stream is current, so the caching
+    allocator ties the block to that stream; when a request outgrows the buffer the old one is dropped, which is safe
+    because every user of it was queued on the same stream before the new allocation."""
+    key = (torch.device(device).index or 0, _lib.stream_ptr())
     t = _scratch_cache.get(key)
     if t is None or t.numel() < nfloats:
         t = torch.empty(max(nfloats, 1 << 20), dtype=torch.float32, device=device)

@@ -286,30 +286,73 @@ class DistributedOptimizer:
         return out
 
     def named_states(self) -> Dict[str, torch.Tensor]:
-        """``adam_m.<param>`` / ``adam_v.<param>`` (and ``master_lo.<param>``) views for unsharded runs."""
+        """``adam_m.<param>`` / ``adam_v.<param>`` (and ``master_lo.<param>``) of this rank's share of every parameter.
+        A rank that owns a whole parameter gives views of the parameter's (tensor-parallel local) shape. Under a
+        sharded optimizer a rank owns a flat slice of each buffer, so a parameter that straddles a shard boundary
+        comes as a 1-D slice plus ``__slice__.<param>`` = ``[offset, count, numel]`` (int64): where the slice sits
+        in the flattened local parameter. Parameters outside the rank's slice are left out; the data-parallel
+        peers hold them."""
         out: Dict[str, torch.Tensor] = {}
-        for name, sh in self.shards.items():
-            if sh.world != 1:
-                continue
-            for pname, (o, cnt, shape) in sh.buf.index.items():
-                out[f"adam_m.{pname}"] = sh.m[o:o + cnt].view(shape)
-                out[f"adam_v.{pname}"] = sh.v[o:o + cnt].view(shape)
-                if sh.lo is not None:
-                    out[f"master_lo.{pname}"] = sh.lo[o:o + cnt].view(shape)
-        return out
-
-    def load_named_states(self, states: Dict[str, torch.Tensor], global_step: Optional[int] = None):
         for name, sh in self.shards.items():
             for pname, (o, cnt, shape) in sh.buf.index.items():
                 lo_, hi_ = max(o, sh.begin), min(o + cnt, sh.end)
                 if hi_ <= lo_:
                     continue
+                whole = (lo_ == o and hi_ == o + cnt)
+                a, b = lo_ - sh.begin, hi_ - sh.begin
+                for key, src in (("adam_m", sh.m), ("adam_v", sh.v), ("master_lo", sh.lo)):
+                    if src is None:
+                        continue
+                    out[f"{key}.{pname}"] = src[a:b].view(shape) if whole else src[a:b]
+                if not whole:
+                    out[f"__slice__.{pname}"] = torch.tensor([lo_ - o, hi_ - lo_, cnt], dtype=torch.int64)
+        return out
+
+    def load_named_states(self, states: Dict[str, torch.Tensor], global_step: Optional[int] = None,
+                          strict: bool = False, model_params: Optional[Dict[str, torch.Tensor]] = None):
+        """Restore the moments (and master remainders) of this rank's slice of every buffer from ``states``.
+
+        A state may be (a) of the parameter's local shape, (b) a 1-D slice with its ``__slice__.<param>`` entry, as
+        ``named_states`` of a sharded run writes it, or (c) the full tensor of a merged checkpoint, which is cut for
+        this rank's tensor- / expert-parallel position first (``model_params`` maps names to the parameters that
+        describe that layout). A slice that does not cover what this rank needs (the checkpoint was written under
+        another data-parallel layout and not merged) raises instead of leaving moments at zero."""
+        from ...checkpoint.sharding import shard_for_param
+        missing = []
+        for name, sh in self.shards.items():
+            for pname, (o, cnt, shape) in sh.buf.index.items():
+                lo_, hi_ = max(o, sh.begin), min(o + cnt, sh.end)
+                if hi_ <= lo_:
+                    continue
+                need_a, need_b = lo_ - o, hi_ - o            # range of the flattened local parameter this rank holds
                 for key, dst in (("adam_m", sh.m), ("adam_v", sh.v), ("master_lo", sh.lo)):
                     src = states.get(f"{key}.{pname}")
-                    if src is None or dst is None:
+                    if dst is None:
                         continue
-                    flat = src.reshape(-1)
-                    dst[lo_ - sh.begin:hi_ - sh.begin].copy_(flat[lo_ - o:hi_ - o])
+                    if src is None:
+                        if key != "master_lo":
+                            missing.append(f"{key}.{pname}")
+                        continue
+                    sl = states.get(f"__slice__.{pname}")
+                    if sl is not None and src.dim() == 1 and src.numel() == int(sl[1]):
+                        off, n = int(sl[0]), int(sl[1])
+                    else:
+                        if tuple(src.shape) != tuple(shape):
+                            p = (model_params or {}).get(pname)
+                            if p is None:
+                                raise ValueError(f"optimizer state {key}.{pname} has shape {tuple(src.shape)}, the local "
+                                                 f"parameter {tuple(shape)}: pass the model parameters to re-slice it")
+                            src = shard_for_param(src, p)
+                        off, n = 0, cnt
+                        src = src.reshape(-1)
+                    if off > need_a or off + n < need_b:
+                        raise ValueError(
+                            f"optimizer state {key}.{pname} covers elements [{off}, {off + n}) of the parameter, this rank "
+                            f"needs [{need_a}, {need_b}): the checkpoint was written under another data-parallel layout; "
+                            "merge it first (checkpoint.transform.unify_checkpoints, or auto_trans_ckpt with its strategy files)")
+                    dst[lo_ - sh.begin:hi_ - sh.begin].copy_(src[need_a - off:need_b - off].to(dst.device))
+        if missing and strict:
+            raise KeyError(f"checkpoint lacks optimizer states: {missing[:6]}{' ...' if len(missing) > 6 else ''}")
         if global_step is not None:
             self.global_step = int(global_step)
 

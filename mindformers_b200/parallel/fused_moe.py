@@ -107,7 +107,11 @@ class MoEExchange:
         if not torch.is_grad_enabled():
             # inference has no step boundary at which to grow the buffers and holds one pair of them for all layers,
             # so it starts from a roomier bound
-            factor = max(factor, min(float(self.world), 2.5))
+            # so it takes the worst case (every token of the group routed to this rank: nothing can be dropped)
+            # while that stays within a few GB, and a roomier bound otherwise; ``generate`` checks the overflow
+            # flag at its final synchronisation and raises if rows were dropped
+            worst = float(self.world)
+            factor = worst if T * self.k * worst * self.H * 2 <= (8 << 30) else max(factor, min(worst, 2.5))
         cap = int(T * self.k * (factor if self.world > 1 else 1.0)) + self.E_local * (BLOCK - 1)
         cap = (cap + BLOCK - 1) // BLOCK * BLOCK
         if self.world <= 1:
@@ -169,11 +173,11 @@ class MoEExchange:
         if self.world <= 1:
             return False
         word = _lib.status_word(self.dev)
-        flag = (word == STATUS_MOE_OVERFLOW).to(torch.int32)
+        flag = word[1:2].clone()
         dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
         if int(flag.item()) == 0:
             return False
-        word.masked_fill_(word == STATUS_MOE_OVERFLOW, 0)
+        word[1:2].zero_()
         old = self.factor
         self.factor = min(self.factor * 1.5, float(self.world))
         if self.factor == old:

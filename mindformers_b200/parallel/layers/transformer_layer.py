@@ -109,6 +109,31 @@ def pipeline_layer_split(num_layers: int, pp: int, vpp: int = 1, offset=0) -> Li
     return out
 
 
+class StageLayers(nn.Module):
+    """The layers of one pipeline stage, registered under their GLOBAL layer number: a parameter of the sixth layer of
+    the model is ``layers.5.…`` on whichever stage owns it, so checkpoints, weight loaders and resharding tools see
+    one name space for every pipeline layout (the reference numbers layers globally per stage,
+    ``training_graph/transformer/utils.py:129-159``). Iteration and integer indexing are over the stage's own
+    layers in order (``layers[0]`` is the first layer of this stage), as with a ``ModuleList``."""
+
+    def __init__(self, layer_ids, modules):
+        super().__init__()
+        self.layer_ids = list(layer_ids)
+        for gid, mod in zip(self.layer_ids, modules):
+            self.add_module(str(gid), mod)
+
+    def __len__(self):
+        return len(self.layer_ids)
+
+    def __iter__(self):
+        return (self._modules[str(g)] for g in self.layer_ids)
+
+    def __getitem__(self, idx):
+        if isinstance(idx, slice):
+            return [self._modules[str(g)] for g in self.layer_ids[idx]]
+        return self._modules[str(self.layer_ids[idx])]
+
+
 class TransformerBlock(nn.Module):
     """The layers owned by this pipeline stage (and virtual chunk) plus, on the last stage, the final norm."""
 
@@ -122,7 +147,8 @@ class TransformerBlock(nn.Module):
         self.layer_ids = split[pp_rank][vp_stage or 0]
         from .gpt_layer_specs import get_gpt_decoder_block_spec
         layer_specs = get_gpt_decoder_block_spec(config)      # one spec per layer of the whole model
-        self.layers = nn.ModuleList([build_module(layer_specs[i], config, layer_number=i + 1) for i in self.layer_ids])
+        self.layers = StageLayers(self.layer_ids,
+                                  [build_module(layer_specs[i], config, layer_number=i + 1) for i in self.layer_ids])
         self.final_layernorm = build_norm(config) if post_process else None
         self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
         self._recompute_layers = self._resolve_recompute(config.recompute)

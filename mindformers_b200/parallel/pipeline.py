@@ -3,18 +3,32 @@
 The reference tags layers with ``pipeline_stage`` and lets MindSpore's ``PipelineCell`` schedule micro-batches and
 insert Send/Recv (``trainer/base_trainer.py:506-518``, ``training_graph/transformer/utils.py:129-146``); loss is
 valid on the last stage only and the token-count denominator is all-reduced over the pipeline group
-(``wrapper/wrapper.py:574,607``). Here the schedule is explicit:
+(``wrapper/wrapper.py:574,607``). Here the schedule is explicit and is data: ``build_schedule`` returns, for one
+rank, the list of steps (which virtual micro-batch runs forward, which runs backward, what is sent and received
+after each), and ``run_schedule`` executes it. The same lists feed a blocking-rendezvous simulation in the tests,
+which shows for every rank count and chunk count that no rank waits on a message whose sender waits on it.
 
-* activations ``[T, H]`` travel with ``torch.distributed.batch_isend_irecv``; on CUDA the transfers are issued
-  from a side stream that waits on the producing kernel through an event, so the next micro-batch's compute on the
-  main stream overlaps the transfer; a receive is posted one step ahead of its use;
-* warm-up forwards (``pp - rank - 1``), steady one-forward-one-backward, cool-down backwards;
-* with ``virtual_pipeline_model_parallel_size = v`` every rank owns ``v`` model chunks and micro-batches visit
-  chunk ``c`` of all stages before chunk ``c + 1`` (interleaved 1F1B), which divides the bubble by ``v``;
-* the embedding weight shared by the first and the last stage gets its gradient all-reduced over those two ranks.
+Communication layout, chosen so that the order of operations cannot deadlock:
+
+* activations travel on one communicator, gradients on another (two process groups over the same ranks, so each has
+  its own NCCL stream): a blocked activation send never sits in front of a gradient receive;
+* on each communicator a step issues ONE ``batch_isend_irecv`` that holds the send of what the step produced and the
+  receive of what the rank needs next. Both run concurrently inside the batch, so the wrap-around traffic of the
+  interleaved schedule (last stage -> first stage, next chunk) cannot form a cycle of sends that wait for receives
+  queued behind other sends;
+* the activation batch is issued right after the forward and awaited before the next forward, the gradient batch
+  right after the backward and awaited before the next backward: the transfers overlap the other half of the step;
+* receive buffers are allocated on the compute stream at issue time and the communicator's stream orders itself
+  after that stream, so a recycled block is never written while earlier kernels still read it.
+
+Schedules: warm-up forwards (``pp - rank - 1``; with ``v`` chunks per rank ``2 (pp - rank - 1) + (v - 1) pp``), then
+one-forward-one-backward, then cool-down backwards. Virtual micro-batch ``k`` runs chunk ``(k // pp) % v`` forward and
+chunk ``v - 1 - (k // pp) % v`` backward, which divides the bubble by ``v``. The embedding weight shared by the first
+and the last stage gets its gradient all-reduced over those two ranks.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
@@ -25,88 +39,109 @@ from . import parallel_state as ps
 _EMBED_GROUPS: Dict[tuple, object] = {}
 
 
-class P2PCommunicator:
-    """Send/receive of activations and their gradients to the neighbouring stages."""
+@dataclass
+class Step:
+    """One entry of a rank's schedule. ``fwd`` / ``bwd``: virtual micro-batch to run forward / backward (``None``: none).
+    After the forward the activation batch goes out: ``send_act`` (output of that forward to the next stage) and
+    ``recv_act`` (input of virtual micro-batch ``recv_act`` from the previous stage). After the backward the gradient
+    batch: ``send_grad`` (input gradient to the previous stage), ``recv_grad`` (output gradient of ``recv_grad``)."""
 
-    def __init__(self, shape: Sequence[int], dtype: torch.dtype, device, overlap: bool = True):
+    fwd: Optional[int] = None
+    bwd: Optional[int] = None
+    send_act: Optional[int] = None
+    recv_act: Optional[int] = None
+    send_grad: Optional[int] = None
+    recv_grad: Optional[int] = None
+
+
+def fwd_chunk(k: int, pp: int, v: int) -> int:
+    return (k // pp) % v
+
+
+def bwd_chunk(k: int, pp: int, v: int) -> int:
+    return v - 1 - (k // pp) % v
+
+
+def microbatch_of(k: int, pp: int, v: int) -> int:
+    return (k // (pp * v)) * pp + k % pp
+
+
+def build_schedule(pp: int, v: int, n: int, rank: int) -> List[Step]:
+    """Steps of ``rank`` for ``n`` micro-batches over ``pp`` stages with ``v`` model chunks per rank."""
+    if v > 1 and n % pp != 0:
+        raise ValueError(f"interleaved schedule needs micro-batches ({n}) to be a multiple of pipeline stages ({pp})")
+    total = n * v
+    warm = min((pp - rank - 1) * (2 if v > 1 else 1) + (v - 1) * pp, total)
+
+    def needs_act(k):          # the first chunk of the first stage embeds its own input
+        return 0 <= k < total and not (rank == 0 and fwd_chunk(k, pp, v) == 0)
+
+    def sends_act(k):          # the last chunk of the last stage produces the loss
+        return not (rank == pp - 1 and fwd_chunk(k, pp, v) == v - 1)
+
+    def needs_grad(k):
+        return 0 <= k < total and not (rank == pp - 1 and bwd_chunk(k, pp, v) == v - 1)
+
+    def sends_grad(k):
+        return not (rank == 0 and bwd_chunk(k, pp, v) == 0)
+
+    steps = [Step(recv_act=0 if needs_act(0) else None, recv_grad=0 if (warm == 0 and needs_grad(0)) else None)]
+    for k in range(warm):
+        st = Step(fwd=k, send_act=k if sends_act(k) else None, recv_act=k + 1 if needs_act(k + 1) else None)
+        if k == warm - 1 and needs_grad(0):
+            st.recv_grad = 0
+        steps.append(st)
+    for i in range(total - warm):
+        f, b = warm + i, i
+        steps.append(Step(fwd=f, bwd=b, send_act=f if sends_act(f) else None,
+                          recv_act=f + 1 if needs_act(f + 1) else None,
+                          send_grad=b if sends_grad(b) else None, recv_grad=b + 1 if needs_grad(b + 1) else None))
+    for b in range(total - warm, total):
+        steps.append(Step(bwd=b, send_grad=b if sends_grad(b) else None, recv_grad=b + 1 if needs_grad(b + 1) else None))
+    return steps
+
+
+class P2PCommunicator:
+    """Activation and gradient exchange with the neighbouring stages: one batched send+receive per ring per step."""
+
+    def __init__(self, shape: Sequence[int], dtype: torch.dtype, device):
         self.shape, self.dtype, self.device = tuple(shape), dtype, torch.device(device)
-        # activations and gradients travel on separate communicators: between one pair of ranks each then carries a
-        # single kind of message, whose order is the micro-batch order on both sides (with two stages and virtual
-        # chunks, wrap-around gradients and ordinary activations would otherwise share a queue)
-        self.group = ps.get_pipeline_model_parallel_group()
-        self.bwd_group = backward_group()
+        self.act_group = ps.get_pipeline_model_parallel_group()
+        self.grad_group = backward_group()
         self.pp = ps.get_pipeline_model_parallel_world_size()
-        self.rank = ps.get_pipeline_model_parallel_rank()
         self.next = ps.get_pipeline_model_parallel_next_rank() if self.pp > 1 else None
         self.prev = ps.get_pipeline_model_parallel_prev_rank() if self.pp > 1 else None
-        self.cuda = self.device.type == "cuda"
-        self.stream = torch.cuda.Stream(device=self.device) if (self.cuda and overlap) else None
         self.bytes_sent = 0
-        self._keep: List[torch.Tensor] = []
 
-    def _issue(self, ops, produced: Optional[torch.Tensor] = None):
-        if not ops:
-            return []
-        if self.stream is not None:
-            if produced is not None:
-                self.stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(self.stream):
-                reqs = dist.batch_isend_irecv(ops)
-            return reqs
-        return dist.batch_isend_irecv(ops)
+    def _batch(self, send: Optional[torch.Tensor], dst, recv: bool, src, group):
+        """Issue one batch holding at most one send and one receive; returns (receive buffer or None, requests, the
+        tensors that must stay alive until the requests were awaited)."""
+        ops, keep, buf = [], [], None
+        if send is not None:
+            send = send.contiguous()
+            keep.append(send)
+            self.bytes_sent += send.numel() * send.element_size()
+            ops.append(dist.P2POp(dist.isend, send, dst, group))
+        if recv:
+            buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+            ops.append(dist.P2POp(dist.irecv, buf, src, group))
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        return buf, reqs, keep
 
-    def _wait(self, reqs):
+    def exchange_act(self, send: Optional[torch.Tensor], recv: bool):
+        return self._batch(None if send is None else send.detach(), self.next, recv, self.prev, self.act_group)
+
+    def exchange_grad(self, send: Optional[torch.Tensor], recv: bool):
+        return self._batch(send, self.prev, recv, self.next, self.grad_group)
+
+    @staticmethod
+    def wait(pending):
+        if pending is None:
+            return None
+        buf, reqs, _keep = pending
         for r in reqs:
             r.wait()
-        if self.stream is not None:
-            torch.cuda.current_stream(self.device).wait_stream(self.stream)
-
-    def irecv(self, src, group) -> tuple:
-        buf = torch.empty(self.shape, dtype=self.dtype, device=self.device)
-        if self.stream is not None:
-            buf.record_stream(self.stream)
-        reqs = self._issue([dist.P2POp(dist.irecv, buf, src, group)])
-        return buf, reqs
-
-    def isend(self, t: torch.Tensor, dst, group):
-        t = t.contiguous()
-        if self.stream is not None:
-            t.record_stream(self.stream)
-        self._keep.append(t)
-        if len(self._keep) > 4 * max(self.pp, 2):
-            self._keep = self._keep[-2 * max(self.pp, 2):]
-        self.bytes_sent += t.numel() * t.element_size()
-        return self._issue([dist.P2POp(dist.isend, t, dst, group)], produced=t)
-
-    # blocking forms used by the schedules ------------------------------------------------------------
-    def recv_forward(self, first: bool):
-        if first:
-            return None
-        buf, reqs = self.irecv(self.prev, self.group)
-        self._wait(reqs)
-        return buf.requires_grad_()
-
-    def recv_backward(self, last: bool):
-        if last:
-            return None
-        buf, reqs = self.irecv(self.next, self.bwd_group)
-        self._wait(reqs)
         return buf
-
-    def send_forward(self, t, last: bool):
-        if not last:
-            self._pending = getattr(self, "_pending", []) + self.isend(t.detach(), self.next, self.group)
-
-    def send_backward(self, g, first: bool):
-        if not first:
-            self._pending = getattr(self, "_pending", []) + self.isend(g, self.prev, self.bwd_group)
-
-    def flush(self):
-        for r in getattr(self, "_pending", []):
-            r.wait()
-        self._pending = []
-        if self.stream is not None:
-            torch.cuda.current_stream(self.device).wait_stream(self.stream)
 
 
 def _forward_step(model, mb, input_tensor, num_microbatches, collect, loss_scale):
@@ -148,108 +183,94 @@ def forward_backward_no_pipelining(model, microbatches: List[dict], loss_scale: 
     return losses
 
 
+def run_schedule(chunks: List[torch.nn.Module], microbatches: List[dict], hidden_shape, dtype,
+                 loss_scale: float = 1.0) -> List[torch.Tensor]:
+    """Execute this rank's schedule (``build_schedule``) over its model chunks; returns the micro-batch losses on
+    the rank that holds the last chunk of the last stage."""
+    pp = ps.get_pipeline_model_parallel_world_size()
+    rank = ps.get_pipeline_model_parallel_rank()
+    v, n = len(chunks), len(microbatches)
+    steps = build_schedule(pp, v, n, rank)
+    dev = next(chunks[0].parameters()).device
+    comm = P2PCommunicator(hidden_shape, dtype, dev)
+    losses: List[torch.Tensor] = []
+    inputs = [[] for _ in range(v)]
+    outputs = [[] for _ in range(v)]
+    auxes = [[] for _ in range(v)]
+    act_pending = grad_pending = None       # the batch in flight on each ring
+    act_in: Dict[int, torch.Tensor] = {}    # received inputs / output gradients by virtual micro-batch
+    grad_in: Dict[int, torch.Tensor] = {}
+
+    def finish_act(st_prev):
+        nonlocal act_pending
+        buf = comm.wait(act_pending)
+        act_pending = None
+        if buf is not None:
+            act_in[st_prev.recv_act] = buf.requires_grad_()
+
+    def finish_grad(st_prev):
+        nonlocal grad_pending
+        buf = comm.wait(grad_pending)
+        grad_pending = None
+        if buf is not None:
+            grad_in[st_prev.recv_grad] = buf
+
+    act_owner = grad_owner = None           # the step whose batch is in flight
+    for st in steps:
+        y = gx = None
+        if st.fwd is not None:
+            if act_owner is not None:
+                finish_act(act_owner)
+                act_owner = None
+            k = st.fwd
+            c = fwd_chunk(k, pp, v)
+            if v > 1:
+                ps.set_virtual_pipeline_model_parallel_rank(c)
+            x = act_in.pop(k, None)
+            y, aux = _forward_step(chunks[c], microbatches[microbatch_of(k, pp, v)], x, n, losses, loss_scale)
+            inputs[c].append(x); outputs[c].append(y); auxes[c].append(aux)
+        if st.send_act is not None or st.recv_act is not None:
+            if act_owner is not None:       # a batch of a step without a forward (the first receive) is still in flight
+                finish_act(act_owner)
+            act_pending = comm.exchange_act(y if st.send_act is not None else None, st.recv_act is not None)
+            act_owner = st
+        if st.bwd is not None:
+            if grad_owner is not None:
+                finish_grad(grad_owner)
+                grad_owner = None
+            k = st.bwd
+            c = bwd_chunk(k, pp, v)
+            if v > 1:
+                ps.set_virtual_pipeline_model_parallel_rank(c)
+            g = grad_in.pop(k, None)
+            xi, yo, au = inputs[c].pop(0), outputs[c].pop(0), auxes[c].pop(0)
+            gx = _backward_step(xi, yo, au, g)
+        if st.send_grad is not None or st.recv_grad is not None:
+            if grad_owner is not None:
+                finish_grad(grad_owner)
+            grad_pending = comm.exchange_grad(gx if st.send_grad is not None else None, st.recv_grad is not None)
+            grad_owner = st
+    if act_owner is not None:
+        finish_act(act_owner)
+    if grad_owner is not None:
+        finish_grad(grad_owner)
+    if v > 1:
+        ps.set_virtual_pipeline_model_parallel_rank(0)
+    run_schedule.last_bytes_sent = comm.bytes_sent
+    return losses
+
+
 def forward_backward_pipelining_without_interleaving(model, microbatches: List[dict], hidden_shape, dtype,
                                                      loss_scale: float = 1.0, overlap: bool = True):
     """Non-interleaved 1F1B. ``model`` is this stage's chunk; returns the micro-batch losses on the last stage."""
-    pp = ps.get_pipeline_model_parallel_world_size()
-    rank = ps.get_pipeline_model_parallel_rank()
-    first, last = rank == 0, rank == pp - 1
-    n = len(microbatches)
-    dev = next(model.parameters()).device
-    comm = P2PCommunicator(hidden_shape, dtype, dev, overlap)
-    warm = min(pp - rank - 1, n)
-    steady = n - warm
-    losses: List[torch.Tensor] = []
-    inputs, outputs, auxes = [], [], []
-    k = 0
-    for _ in range(warm):
-        x = comm.recv_forward(first)
-        y, aux = _forward_step(model, microbatches[k], x, n, losses, loss_scale)
-        comm.send_forward(y, last)
-        inputs.append(x); outputs.append(y); auxes.append(aux)
-        k += 1
-    x = comm.recv_forward(first) if steady > 0 else None
-    for i in range(steady):
-        y, aux = _forward_step(model, microbatches[k], x, n, losses, loss_scale)
-        k += 1
-        comm.send_forward(y, last)
-        inputs.append(x); outputs.append(y); auxes.append(aux)
-        g = comm.recv_backward(last)
-        xi, yo, au = inputs.pop(0), outputs.pop(0), auxes.pop(0)
-        gx = _backward_step(xi, yo, au, g)
-        comm.send_backward(gx, first)
-        if i < steady - 1:
-            x = comm.recv_forward(first)
-    for _ in range(warm):
-        g = comm.recv_backward(last)
-        xi, yo, au = inputs.pop(0), outputs.pop(0), auxes.pop(0)
-        gx = _backward_step(xi, yo, au, g)
-        comm.send_backward(gx, first)
-    comm.flush()
-    return losses
+    return run_schedule([model], microbatches, hidden_shape, dtype, loss_scale)
 
 
 def forward_backward_pipelining_with_interleaving(chunks: List[torch.nn.Module], microbatches: List[dict], hidden_shape,
                                                   dtype, loss_scale: float = 1.0, overlap: bool = True):
     """Interleaved 1F1B over ``v = len(chunks)`` model chunks per rank. The number of micro-batches must be a
-    multiple of the pipeline size. Virtual micro-batch ``j`` runs chunk ``(j // pp) % v`` (forward order); the
-    backward order mirrors it from the last chunk."""
-    pp = ps.get_pipeline_model_parallel_world_size()
-    rank = ps.get_pipeline_model_parallel_rank()
-    v = len(chunks)
-    n = len(microbatches)
-    if n % pp != 0:
-        raise ValueError(f"interleaved schedule needs micro-batches ({n}) to be a multiple of pipeline stages ({pp})")
-    total = n * v
-    dev = next(chunks[0].parameters()).device
-    comm = P2PCommunicator(hidden_shape, dtype, dev, overlap)
-    losses: List[torch.Tensor] = []
-
-    def chunk_of(j, forward=True):
-        c = (j // pp) % v
-        return c if forward else v - 1 - c
-
-    def mb_of(j):
-        return (j // (pp * v)) * pp + j % pp
-
-    warm = min((pp - rank - 1) * 2 + (v - 1) * pp, total)
-    steady = total - warm
-    inputs = [[] for _ in range(v)]
-    outputs = [[] for _ in range(v)]
-    auxes = [[] for _ in range(v)]
-
-    def is_first(c):
-        return rank == 0 and c == 0
-
-    def is_last(c):
-        return rank == pp - 1 and c == v - 1
-
-    def fwd(j):
-        c = chunk_of(j)
-        ps.set_virtual_pipeline_model_parallel_rank(c)
-        x = comm.recv_forward(is_first(c))
-        y, aux = _forward_step(chunks[c], microbatches[mb_of(j)], x, n, losses, loss_scale)
-        comm.send_forward(y, is_last(c))
-        inputs[c].append(x); outputs[c].append(y); auxes[c].append(aux)
-
-    def bwd(j):
-        c = chunk_of(j, forward=False)
-        ps.set_virtual_pipeline_model_parallel_rank(c)
-        g = comm.recv_backward(is_last(c))
-        xi, yo, au = inputs[c].pop(0), outputs[c].pop(0), auxes[c].pop(0)
-        gx = _backward_step(xi, yo, au, g)
-        comm.send_backward(gx, is_first(c))
-
-    for j in range(warm):
-        fwd(j)
-    for i in range(steady):
-        fwd(warm + i)
-        bwd(i)
-    for i in range(steady, total):
-        bwd(i)
-    comm.flush()
-    ps.set_virtual_pipeline_model_parallel_rank(0)
-    return losses
+    multiple of the pipeline size."""
+    return run_schedule(list(chunks), microbatches, hidden_shape, dtype, loss_scale)
 
 
 def get_forward_backward_func():

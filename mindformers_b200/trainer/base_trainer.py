@@ -99,7 +99,8 @@ class BaseTrainer:
         accum = int(rc.get("gradient_accumulation_steps", 1) or 1)
         micro = int((config.get("parallel_config") or {}).get("micro_batch_num", 1) or 1)
         pp = int((config.get("parallel_config") or {}).get("pipeline_stage", 1) or 1)
-        per_step = int(rc.get("batch_size", 1)) * (micro if pp > 1 else accum)
+        interleave = int(config.get("micro_batch_interleave_num", 1) or 1)
+        per_step = int(rc.get("batch_size", 1)) * (micro if pp > 1 else accum) * (interleave if pp == 1 else 1)
         inner["batch_size"] = per_step if which == "train" else int(rc.get("batch_size", 1))
         loader = inner.get("data_loader")
         if isinstance(loader, dict) and loader.get("type") == "MockDataLoader":
@@ -127,20 +128,61 @@ class BaseTrainer:
         mc = _model_dict(config)
         recompute = bool((config.get("recompute_config") or {}).get("recompute"))
         skip = float(wrapper.get("global_norm_spike_threshold", 0) or 0) if wrapper.get("use_skip_data_by_global_norm") else 0.0
+        pc = config.get("parallel_config") or {}
+        if int(pc.get("seq_split_num", 1) or 1) > 1:
+            raise NotImplementedError(
+                "parallel_config.seq_split_num > 1 (sequence pipeline: chunks of one sequence flowing through the "
+                "stages with the keys and values of earlier chunks carried along) is not built; use "
+                "context_parallel for long sequences or pp_interleave_num to shrink the pipeline bubble")
+        interleave = int(config.get("micro_batch_interleave_num", 1) or 1)
+        pp = int(pc.get("pipeline_stage", 1) or 1)
+        if interleave > 1 and pp > 1:
+            raise NotImplementedError("micro_batch_interleave_num > 1 cannot be combined with pipeline_stage > 1: the "
+                                      "pipeline schedule already keeps several micro-batches in flight")
+        opt_type = str(opt_cfg.get("type", "AdamW"))
+        sharded_adamw = opt_type.lower() in ("adamw", "fusedadamw", "fused_adamw", "adam_w")
+        betas = tuple(opt_cfg.get("betas", (0.9, 0.999)))
+        mbs = int(rc.get("batch_size", 1))
         if model is not None:
-            from ..parallel.distributed.optimizer import DistributedOptimizer
+            if pp > 1:
+                raise NotImplementedError("pipeline_stage > 1 needs the model built from the configuration (one chunk per "
+                                          "stage); a ready-made network cannot be split")
             tcfg = model.config if hasattr(model.config, "sequence_parallel") else model.model.config
             net = model if hasattr(model.config, "sequence_parallel") else model.model
-            opt = DistributedOptimizer(net, learning_rate=lr, betas=tuple(opt_cfg.get("betas", (0.9, 0.999))),
-                                       eps=opt_cfg.get("eps", 1e-8), weight_decay=opt_cfg.get("weight_decay", 0.0),
-                                       max_grad_norm=max_norm, skip_threshold=skip,
-                                       sequence_parallel=bool(tcfg.sequence_parallel))
-            return TrainingEngine(net, opt, micro_batch_size=int(rc.get("batch_size", 1)), loss_scale=loss_scale)
-        return TrainingEngine.from_model_config(
-            mc, parallel=parallel_kwargs(config), learning_rate=lr, betas=tuple(opt_cfg.get("betas", (0.9, 0.999))),
-            eps=opt_cfg.get("eps", 1e-8), weight_decay=opt_cfg.get("weight_decay", 0.0), max_grad_norm=max_norm,
-            micro_batch_size=int(rc.get("batch_size", 1)), recompute=recompute,
-            dtype=mc.get("compute_dtype", "bfloat16") if torch.cuda.is_available() else mc.get("compute_dtype", "float32"))
+        else:
+            from ..models.presets import preset_is_mla
+            from ..parallel.layers.gpt_model import GPTModel
+            from ..parallel.transformer_config_utils import convert_to_transformer_config
+            from .engine import build_pipeline_chunks
+            cfgd = dict(mc)
+            cfgd.update(parallel_kwargs(config))
+            dtype = mc.get("compute_dtype", "bfloat16") if torch.cuda.is_available() else mc.get("compute_dtype", "float32")
+            cfgd.setdefault("params_dtype", dtype)
+            cfgd.setdefault("compute_dtype", dtype)
+            cfgd["recompute"] = recompute
+            tcfg = convert_to_transformer_config(cfgd, is_mla_model=preset_is_mla(cfgd))
+            tcfg.device = "cuda" if torch.cuda.is_available() else "cpu"
+            net = build_pipeline_chunks(tcfg) if (pp > 1 and ps.model_parallel_is_initialized()
+                                                  and ps.get_pipeline_model_parallel_world_size() > 1) else GPTModel(tcfg)
+        if sharded_adamw:
+            from ..parallel.distributed.optimizer import DistributedOptimizer
+            opt = DistributedOptimizer(net, learning_rate=lr, betas=betas, eps=opt_cfg.get("eps", 1e-8),
+                                       weight_decay=opt_cfg.get("weight_decay", 0.0), max_grad_norm=max_norm,
+                                       skip_threshold=skip, sequence_parallel=bool(tcfg.sequence_parallel))
+        else:
+            # any other registered optimizer (CAME, SGD, ...): replicated state, NCCL gradient all-reduce
+            from ..core.optim import ReplicatedOptimizer, build_optim
+            inner_cfg = {k: v for k, v in opt_cfg.items() if k not in ("learning_rate",)}
+            inner_cfg["learning_rate"] = float(lr(1)) if callable(lr) else float(lr)
+            inner = build_optim(inner_cfg, model=net)
+            opt = ReplicatedOptimizer(net, inner, lr, max_grad_norm=max_norm, sequence_parallel=bool(tcfg.sequence_parallel))
+        forward_fn = None
+        if interleave > 1:
+            from ..wrapper import MicroBatchInterleaved
+            wrapped = MicroBatchInterleaved(net, interleave)
+            forward_fn = lambda m, b: wrapped(b["input_ids"], b["labels"], b.get("loss_mask"), b.get("position_ids"))  # noqa: E731
+            mbs *= interleave                        # one forward call now carries `interleave` copies of the micro-batch
+        return TrainingEngine(net, opt, micro_batch_size=mbs, loss_scale=loss_scale, forward_fn=forward_fn)
 
     def create_callbacks(self, config, default: Dict[str, Any]) -> List[Callback]:
         cbs: List[Callback] = []
@@ -218,6 +260,9 @@ class BaseTrainer:
                     ctx.global_step += 1
                     ctx.step_in_epoch += 1
                     ctx.loss, ctx.lr, ctx.global_norm, ctx.skipped = out["loss"], out["lr"], out["global_norm"], out["skipped"]
+                    if out.get("moe_rows_dropped"):
+                        logger.warning("step %d: expert-parallel receive buffers overflowed and token rows were dropped; "
+                                       "the buffers have been grown for the next step", ctx.global_step)
                     self.loss_history.append(ctx.loss)
                     for cb in cbs:
                         cb.on_step_end(ctx)

@@ -64,22 +64,38 @@ def transform_checkpoint_if_needed(config, path: str) -> str:
         raise ValueError("auto_trans_ckpt needs src_strategy_path_or_dir: the directory with the "
                          "ckpt_strategy_rank_N.json files of the run that wrote the checkpoint")
     dst = os.path.join(config.get("output_dir") or "./output", "transformed_checkpoint")
+    point = get_resume_checkpoint(path, config.get("resume_training") or True)
     if _rank() == 0:
         from ..checkpoint.transform import unify_checkpoints
-        unify_checkpoints(path, strategy, dst, include_optimizer=bool(config.get("resume_training")))
+        unify_checkpoints(path, strategy, dst, include_optimizer=bool(config.get("resume_training")), point=point)
         logger.info("checkpoint %s merged into %s for the current parallel layout", path, dst)
     _barrier()
     return dst
 
 
+def common_resume_point(config, path: str):
+    """(epoch, step) that every rank loads from a ``rank_N`` checkpoint directory: the newest save that all rank
+    directories hold and that is not marked unhealthy (or the save a file name in ``resume_training`` names). Rank 0
+    records it under ``<output>/resume_record`` and all ranks read that record, so they cannot disagree. ``None`` for
+    paths that are not ``rank_N`` layouts."""
+    if not os.path.isdir(path) or not any(d.startswith("rank_") for d in os.listdir(path)):
+        return None
+    from ..checkpoint.resume import record_resume_point
+    point = get_resume_checkpoint(path, config.get("resume_training") or True)
+    if point is None:
+        raise FileNotFoundError(f"no checkpoint under {path} is present (and healthy) in every rank directory")
+    return record_resume_point(config.get("output_dir") or "./output", *point)
+
+
 def load_ckpt(config, model: torch.nn.Module, optimizer=None, path: Optional[str] = None, strict: bool = False,
               family: str = "llama") -> dict:
     """Load weights (and optimizer state when given) from ``path`` or ``config.load_checkpoint``; returns the scalar
-    entries of the checkpoint."""
+    entries of the checkpoint. From a ``rank_N`` directory every rank takes the file of the common resume point."""
     path = path or config.get("load_checkpoint")
     if not path:
         return {}
-    return load_checkpoint(model, path, optimizer=optimizer, strict=strict, family=family)
+    point = common_resume_point(config, path)
+    return load_checkpoint(model, path, optimizer=optimizer, strict=strict, family=family, point=point)
 
 
 def transform_and_load_checkpoint(config, model: torch.nn.Module, optimizer=None, path: Optional[str] = None,

@@ -65,13 +65,7 @@ def main():
     with torch.no_grad():
         for ch in chunks:
             for n, p in ch.named_parameters():
-                if ".layers." in n:
-                    local = int(n.split(".layers.")[1].split(".")[0])
-                    gid = ch.decoder.layer_ids[local]
-                    n_ref = n.replace(f".layers.{local}.", f".layers.{gid}.")
-                else:
-                    n_ref = n
-                p.copy_(ref_sd[n_ref])
+                p.copy_(ref_sd[n])          # layers carry their global number on every stage
     del ref
     net = torch.nn.ModuleList(chunks)
     opt = DistributedOptimizer(net, learning_rate=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
@@ -87,9 +81,7 @@ def main():
     for ch in chunks:
         for n, p in ch.named_parameters():
             if "layernorm" in n and ".layers." in n:
-                local = int(n.split(".layers.")[1].split(".")[0])
-                gid = ch.decoder.layer_ids[local]
-                digest[n.replace(f".layers.{local}.", f".layers.{gid}.")] = p.detach().double().sum().item()
+                digest[n] = p.detach().double().sum().item()
     gathered = [None] * world
     if world > 1:
         dist.all_gather_object(gathered, digest)

@@ -172,3 +172,110 @@ def test_auto_trans_ckpt_loads_a_tp2_checkpoint_into_one_rank(tmp_path):
     ctx = load_resume_context_from_checkpoint(scalars, str(tmp_path / "checkpoint"), True, global_batch_size=8,
                                               steps_per_epoch=100)
     assert ctx["initial_epoch"] == 0 and ctx["initial_step"] == 14            # 7 steps of 16 samples = 14 steps of 8
+
+
+def _simulate_pipeline(pp, v, n):
+    """Blocking-rendezvous model of the pipeline schedule: a batch (at most one send and one receive on one ring) starts
+    when its rank has computed what it sends and the rank's previous batch on that ring has finished; it finishes when
+    both of its operations have met their counterparts, i.e. when the peers' matching batches have STARTED. A forward
+    needs the previous activation batch finished, a backward the previous gradient batch. Returns True when every rank
+    reaches the end of its schedule."""
+    from mindformers_b200.parallel.pipeline import build_schedule
+    sched = [build_schedule(pp, v, n, r) for r in range(pp)]
+    # batches per (rank, ring) in issue order: (step index, send k or None, recv k or None)
+    rings = {}
+    for r in range(pp):
+        for ring, s_attr, r_attr in (("act", "send_act", "recv_act"), ("grad", "send_grad", "recv_grad")):
+            rings[(r, ring)] = [(i, getattr(st, s_attr), getattr(st, r_attr)) for i, st in enumerate(sched[r])
+                                if getattr(st, s_attr) is not None or getattr(st, r_attr) is not None]
+    # message order between a pair must agree: the j-th send r -> peer meets the j-th receive at peer from r
+    for r in range(pp):
+        nxt, prv = (r + 1) % pp, (r - 1) % pp
+        assert len([b for b in rings[(r, "act")] if b[1] is not None]) == \
+            len([b for b in rings[(nxt, "act")] if b[2] is not None]), (pp, v, n, r, "act count")
+        assert len([b for b in rings[(r, "grad")] if b[1] is not None]) == \
+            len([b for b in rings[(prv, "grad")] if b[2] is not None]), (pp, v, n, r, "grad count")
+
+    def counterpart_index(r, ring, bi, kind):
+        """Index (in the peer's batch list) of the batch that holds the counterpart of the send / receive of batch bi."""
+        peer = ((r + 1) if (ring == "act") == (kind == "send") else (r - 1)) % pp
+        mine, theirs = rings[(r, ring)], rings[(peer, ring)]
+        col, pcol = (1, 2) if kind == "send" else (2, 1)
+        j = sum(1 for b in mine[:bi] if b[col] is not None)            # ordinal of this message on the pair
+        seen = -1
+        for pi, b in enumerate(theirs):
+            if b[pcol] is not None:
+                seen += 1
+                if seen == j:
+                    return peer, pi
+        raise AssertionError("no counterpart")
+
+    pos = [0] * pp                                     # next step to compute, per rank
+    started = {key: 0 for key in rings}                # batches started per (rank, ring)
+    finished = {key: 0 for key in rings}
+    issued = {key: 0 for key in rings}                 # batches whose step has been computed (may start in order)
+    progress = True
+    while progress:
+        progress = False
+        for r in range(pp):
+            # compute the next step if its inputs are there
+            while pos[r] < len(sched[r]):
+                st = sched[r][pos[r]]
+                ok = True
+                if st.fwd is not None:                 # all earlier activation batches finished
+                    ok = ok and finished[(r, "act")] == issued[(r, "act")]
+                if st.bwd is not None:
+                    ok = ok and finished[(r, "grad")] == issued[(r, "grad")]
+                # a step that issues a batch while one is still in flight on that ring waits for it too
+                if st.send_act is not None or st.recv_act is not None:
+                    ok = ok and finished[(r, "act")] == issued[(r, "act")]
+                if st.send_grad is not None or st.recv_grad is not None:
+                    ok = ok and (st.bwd is None or True) and finished[(r, "grad")] == issued[(r, "grad")]
+                if not ok:
+                    break
+                if st.send_act is not None or st.recv_act is not None:
+                    issued[(r, "act")] += 1
+                if st.send_grad is not None or st.recv_grad is not None:
+                    issued[(r, "grad")] += 1
+                pos[r] += 1
+                progress = True
+            for ring in ("act", "grad"):
+                key = (r, ring)
+                if started[key] < issued[key] and started[key] == finished[key]:
+                    started[key] += 1
+                    progress = True
+        for key, lst in rings.items():
+            r, ring = key
+            if started[key] > finished[key]:
+                bi = finished[key]
+                _, snd, rcv = lst[bi]
+                ok = True
+                for kind, present in (("send", snd), ("recv", rcv)):
+                    if present is None:
+                        continue
+                    peer, pi = counterpart_index(r, ring, bi, kind)
+                    ok = ok and started[(peer, ring)] > pi
+                if ok:
+                    finished[key] += 1
+                    progress = True
+    return all(pos[r] == len(sched[r]) for r in range(pp)) and all(finished[k] == len(rings[k]) for k in rings)
+
+
+@pytest.mark.parametrize("pp", [2, 3, 4, 8])
+@pytest.mark.parametrize("v", [1, 2, 3])
+def test_pipeline_schedule_has_no_communication_cycle(pp, v):
+    from mindformers_b200.parallel.pipeline import build_schedule, fwd_chunk, bwd_chunk
+    for n in ([pp, 2 * pp, 4 * pp] if v > 1 else [1, 2, pp, pp + 1, 3 * pp]):
+        assert _simulate_pipeline(pp, v, n), f"schedule deadlocks under blocking sends: pp={pp} v={v} n={n}"
+        # every virtual micro-batch runs forward once and backward once on every rank, forward first
+        for r in range(pp):
+            steps = build_schedule(pp, v, n, r)
+            f = [s.fwd for s in steps if s.fwd is not None]
+            b = [s.bwd for s in steps if s.bwd is not None]
+            assert f == list(range(n * v)) and b == list(range(n * v))
+            done_f = set()
+            for s in steps:
+                if s.fwd is not None:
+                    done_f.add((fwd_chunk(s.fwd, pp, v), s.fwd % pp + (s.fwd // (pp * v)) * pp))
+                if s.bwd is not None:
+                    assert (bwd_chunk(s.bwd, pp, v), s.bwd % pp + (s.bwd // (pp * v)) * pp) in done_f
