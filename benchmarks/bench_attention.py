@@ -38,6 +38,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--poly", type=int, default=2, help="eighths of the exponentials on the FMA pipe for the headline rows")
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     rows = []
@@ -69,12 +70,22 @@ def main():
             o.transpose(1, 2).reshape(B * S, nq * hd).backward(g)
 
         fl_fwd = 4.0 * B * nq * S * S * hd / 2
+        lib = _lib.get_lib()
+        variants = {}
+        lib.mfb_flash_attn_set_fwd_variant(1)              # one query tile per CTA
+        variants["one_tile"] = fl_fwd / time_fn(ours_fwd, args.iters, flush) / 1e9
+        lib.mfb_flash_attn_set_fwd_variant(2)              # two query tiles per CTA, 0..4 eighths of exp2 on the FMA pipe
+        for poly in range(5):
+            lib.mfb_flash_attn_fwd2_set_poly(poly)
+            variants[f"two_tiles_poly{poly}"] = fl_fwd / time_fn(ours_fwd, args.iters, flush) / 1e9
+        lib.mfb_flash_attn_fwd2_set_poly(args.poly)
         t1, t2 = time_fn(ours_fwd, args.iters, flush), time_fn(sdpa_fwd, args.iters, flush)
         t3, t4 = time_fn(ours_fb, args.iters, flush), time_fn(sdpa_fb, args.iters, flush)
         rows.append({"B": B, "S": S, "nq": nq, "nkv": nkv, "ours_fwd_ms": t1, "sdpa_fwd_ms": t2,
                      "ours_fwd_tflops": fl_fwd / t1 / 1e9, "sdpa_fwd_tflops": fl_fwd / t2 / 1e9,
                      "ours_fwd_bwd_ms": t3, "sdpa_fwd_bwd_ms": t4,
-                     "ours_fwd_bwd_tflops": 3.5 * fl_fwd / t3 / 1e9, "sdpa_fwd_bwd_tflops": 3.5 * fl_fwd / t4 / 1e9})
+                     "ours_fwd_bwd_tflops": 3.5 * fl_fwd / t3 / 1e9, "sdpa_fwd_bwd_tflops": 3.5 * fl_fwd / t4 / 1e9,
+                     "fwd_variants_tflops": variants})
         print(rows[-1], flush=True)
     print("status word:", _lib.read_status())
     if args.out:

@@ -67,6 +67,10 @@ def _declare(lib):
     sig("mfb_split_master", [P, P, P, L, P])
     sig("mfb_join_master", [P, P, P, L, P])
     sig("mfb_flash_attn_fwd", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, F, P, P])
+    lib.mfb_flash_attn_set_fwd_variant.argtypes = [I]
+    lib.mfb_flash_attn_set_fwd_variant.restype = None
+    lib.mfb_flash_attn_fwd2_set_poly.argtypes = [I]
+    lib.mfb_flash_attn_fwd2_set_poly.restype = None
     sig("mfb_flash_attn_fwd_mla", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, I, F, P, P])
     lib.mfb_flash_attn_bwd_scratch_bytes.argtypes = [I, I, I]
     lib.mfb_flash_attn_bwd_scratch_bytes.restype = L
@@ -151,6 +155,10 @@ def get_lib():
         # kernel variants that can be switched for A/B measurements
         if os.environ.get("MFB_FP8_KSPLIT", "1") == "0":
             lib.mfb_gemm_fp8_enable_ksplit(0)
+        if os.environ.get("MFB_FA_FWD", "2") == "1":
+            lib.mfb_flash_attn_set_fwd_variant(1)
+        if os.environ.get("MFB_FA_POLY"):
+            lib.mfb_flash_attn_fwd2_set_poly(int(os.environ["MFB_FA_POLY"]))
         if os.environ.get("MFB_MLA_DECODE", "single") == "cluster":
             lib.mfb_mla_decode_set_variant(1)
         _lib = lib

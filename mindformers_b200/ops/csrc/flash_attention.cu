@@ -404,9 +404,19 @@ int fa_fwd_launch(const void* q, const void* k, const void* v, void* o, float* l
 extern "C" {
 using namespace mfb;
 
+int mfb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                        int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld, int causal,
+                        int q_offset, float scale, int* status, cudaStream_t stream);
+
+static int g_fa_fwd_variant = 2;   // 2: two query tiles per CTA (flash_attention_fwd2.cu); 1: one tile per CTA
+void mfb_flash_attn_set_fwd_variant(int v) { g_fa_fwd_variant = (v == 1) ? 1 : 2; }
+
 int mfb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
                           int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld,
                           int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
+  if (g_fa_fwd_variant == 2)
+    return mfb_flash_attn_fwd2(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, q_offset, scale,
+                               status, stream);
   return fa_fwd_launch<128>(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, q_offset, scale, status,
                             stream);
 }

@@ -286,7 +286,8 @@ def test_adamw_matches_reference_and_master_is_exact():
 
 
 @pytest.mark.parametrize("B,S,nq,nkv,causal", [(1, 128, 2, 1, True), (2, 512, 4, 2, True), (1, 1024, 8, 2, True),
-                                               (1, 384, 2, 2, False)])
+                                               (1, 384, 2, 2, False), (1, 4096, 32, 8, True), (2, 2048, 16, 4, True),
+                                               (1, 640, 4, 4, True)])
 def test_flash_attention_fwd_bwd(B, S, nq, nkv, causal):
     from mindformers_b200.ops import attention as A
     torch.manual_seed(12)
