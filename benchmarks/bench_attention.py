@@ -38,7 +38,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default=None)
-    ap.add_argument("--poly", type=int, default=2, help="eighths of the exponentials on the FMA pipe for the headline rows")
+    ap.add_argument("--poly", type=int, default=0, help="quarters of the exponentials on the FMA pipe for the headline rows")
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     rows = []
@@ -74,8 +74,8 @@ def main():
         variants = {}
         lib.mfb_flash_attn_set_fwd_variant(1)              # one query tile per CTA
         variants["one_tile"] = fl_fwd / time_fn(ours_fwd, args.iters, flush) / 1e9
-        lib.mfb_flash_attn_set_fwd_variant(2)              # two query tiles per CTA, 0..4 eighths of exp2 on the FMA pipe
-        for poly in range(5):
+        lib.mfb_flash_attn_set_fwd_variant(2)              # two query tiles per CTA, 0..2 quarters of exp2 on the FMA pipe
+        for poly in range(3):
             lib.mfb_flash_attn_fwd2_set_poly(poly)
             variants[f"two_tiles_poly{poly}"] = fl_fwd / time_fn(ours_fwd, args.iters, flush) / 1e9
         lib.mfb_flash_attn_fwd2_set_poly(args.poly)

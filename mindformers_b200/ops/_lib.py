@@ -67,6 +67,12 @@ def _declare(lib):
     sig("mfb_split_master", [P, P, P, L, P])
     sig("mfb_join_master", [P, P, P, L, P])
     sig("mfb_flash_attn_fwd", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, F, P, P])
+    lib.mfb_flash_attn_set_bwd_variant.argtypes = [I]
+    lib.mfb_flash_attn_set_bwd_variant.restype = None
+    lib.mfb_flash_attn_bwd2_set_split.argtypes = [I]
+    lib.mfb_flash_attn_bwd2_set_split.restype = None
+    lib.mfb_flash_attn_bwd_scratch_bytes_ex.argtypes = [I, I, I, I, I]
+    lib.mfb_flash_attn_bwd_scratch_bytes_ex.restype = L
     lib.mfb_flash_attn_set_fwd_variant.argtypes = [I]
     lib.mfb_flash_attn_set_fwd_variant.restype = None
     lib.mfb_flash_attn_fwd2_set_poly.argtypes = [I]
@@ -155,6 +161,8 @@ def get_lib():
         # kernel variants that can be switched for A/B measurements
         if os.environ.get("MFB_FP8_KSPLIT", "1") == "0":
             lib.mfb_gemm_fp8_enable_ksplit(0)
+        if os.environ.get("MFB_FA_BWD", "2") == "1":
+            lib.mfb_flash_attn_set_bwd_variant(1)
         if os.environ.get("MFB_FA_FWD", "2") == "1":
             lib.mfb_flash_attn_set_fwd_variant(1)
         if os.environ.get("MFB_FA_POLY"):

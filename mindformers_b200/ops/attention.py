@@ -66,7 +66,7 @@ class _PackedAttnFn(torch.autograd.Function):
         dout = dout.contiguous()
         dpacked = torch.empty_like(packed)
         lib = _lib.get_lib()
-        scratch = _scratch(packed.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, S, nq))
+        scratch = _scratch(packed.device, lib.mfb_flash_attn_bwd_scratch_bytes_ex(B, S, S, nq, nkv))
         st = _lib.status_word(packed.device)
         k, v = packed[:, nq:], packed[:, nq + nkv:]
         dk, dv = dpacked[:, nq:], dpacked[:, nq + nkv:]
@@ -116,7 +116,7 @@ class _AttnFn(torch.autograd.Function):
             dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
         lib = _lib.get_lib()
-        scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, S, nq))
+        scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes_ex(B, S, S, nq, nkv))
         st = _lib.status_word(q.device)
         rc = lib.mfb_flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
                                     lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
@@ -185,7 +185,7 @@ def rect_backward(q, k, v, out, lse, dout, dk, dv, q_offset: int, causal: bool, 
     Sk, nkv = k.shape[1], k.shape[2]
     dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lib = _lib.get_lib()
-    scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes(B, Sq, nq))
+    scratch = _scratch(q.device, lib.mfb_flash_attn_bwd_scratch_bytes_ex(B, Sq, Sk, nq, nkv))
     st = _lib.status_word(q.device)
     rc = lib.mfb_flash_attn_bwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
                                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), B, Sq, Sk, nq, nkv,

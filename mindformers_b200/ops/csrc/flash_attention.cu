@@ -791,9 +791,24 @@ __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat1
 extern "C" {
 using namespace mfb;
 
-// Number of bytes of zero-initialised scratch that mfb_flash_attn_bwd needs: fp32 dq accumulator plus delta.
+int mfb_flash_attn_bwd2(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                        void* dq, void* dk, void* dv, void* scratch, int B, int S, int Sk, int Hq, int Hkv,
+                        long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
+                        long long dq_ld, long long dk_ld, long long dv_ld, int causal, int q_offset, float scale,
+                        int* status, cudaStream_t stream);
+long long mfb_flash_attn_bwd2_scratch_bytes(int B, int Sq, int Sk, int Hq, int Hkv);
+
+static int g_fa_bwd_variant = 2;   // 2: pipelined kernel with keys on the lanes (flash_attention_bwd2.cu); 1: the serial one
+void mfb_flash_attn_set_bwd_variant(int v) { g_fa_bwd_variant = (v == 1) ? 1 : 2; }
+
+// Number of bytes of scratch that mfb_flash_attn_bwd / _ex need for Sq queries and Sk keys per sequence (either
+// kernel variant): fp32 dQ accumulator, delta, and the fp32 dK / dV accumulators of a split query-head group.
+long long mfb_flash_attn_bwd_scratch_bytes_ex(int B, int Sq, int Sk, int Hq, int Hkv) {
+  return mfb_flash_attn_bwd2_scratch_bytes(B, Sq, Sk, Hq, Hkv);
+}
+// The same for Sq == Sk with the number of KV heads unknown (bounded by the query heads).
 long long mfb_flash_attn_bwd_scratch_bytes(int B, int S, int Hq) {
-  return static_cast<long long>(B) * S * Hq * kHd * 4 + static_cast<long long>(B) * S * Hq * 4;
+  return mfb_flash_attn_bwd2_scratch_bytes(B, S, S, Hq, Hq);
 }
 
 // Gradients of attention with Sq queries and Sk keys per sequence (causal: query i at key position q_offset + i).
@@ -805,6 +820,9 @@ int mfb_flash_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
                           int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
                           long long dq_ld, long long dk_ld, long long dv_ld, int causal, int q_offset, float scale,
                           int* status, cudaStream_t stream) {
+  if (g_fa_bwd_variant == 2)
+    return mfb_flash_attn_bwd2(q, k, v, o, d_o, lse, dq, dk, dv, scratch, B, S, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, do_ld,
+                               dq_ld, dk_ld, dv_ld, causal, q_offset, scale, status, stream);
   if (S % kTile || Sk % kTile || Hq % Hkv || B <= 0 || q_offset % kTile || q_offset < 0 ||
       (causal && q_offset + S > Sk)) {
     mfb_host::set_error("flash_attn_bwd: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d q_offset=%d", B, S, Sk, Hq, Hkv,

@@ -14,8 +14,9 @@
 // Shared memory: Q_A, Q_B, two stages of K, two stages of V (192 KB); the Q buffers stage the output at the end.
 //
 // The running maximum is lazy as in the single-tile kernel: O is rescaled only when a row maximum grows by more
-// than 2^8. A fraction of the exponentials (template POLY, in eighths) is evaluated by a polynomial on the FMA pipe
-// instead of the 16-per-clock MUFU unit, which is the narrowest unit of this loop.
+// than 2^8. A fraction of the exponentials (template POLY, in quarters) is evaluated by a polynomial on the FMA pipe
+// instead of the 16-per-clock MUFU unit (the loop is bound by instruction issue: scores are scaled, summed and
+// converted two at a time with the packed fp32 instructions of sm_100, row maxima use the three-input maximum).
 //
 // Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax of tile A,
 // warps 6..9 softmax of tile B. Every wait is bounded (common.cuh).
@@ -43,8 +44,33 @@ struct Args {
 
 __device__ __forceinline__ float ex2_mufu(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Packed fp32 pairs (one instruction for two lanes of work) and the three-input maximum of sm_100: the softmax
+// loop is bound by instruction issue, not by a single pipe, so halving the instruction count is what pays.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 // 2^x for x <= 0 on the FMA pipe: x = n + f with f in [-0.5, 0.5], cubic for 2^f (max relative error 7.5e-5,
 // below the bf16 rounding of P), n added to the exponent field.
@@ -69,6 +95,9 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       : "memory");
 }
 
+// Warps are given registers in groups of four, so 320 threads are budgeted like 384: 168 registers per thread.
+// The softmax therefore reads its S row from tensor memory twice (once for the maximum, once, in halves, for the
+// exponentials) instead of holding all 128 scores across both passes.
 template <int POLY>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -93,10 +122,15 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = gridDim.x - 1 - blockIdx.x;      // heavy (late) query tiles first
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int kv_head = head / args.group;
+  // one-dimensional grid, heaviest work first over ALL heads and sequences: the late (long) query tiles of every
+  // head are scheduled before any early (short) one, so the last wave is made of short CTAs
   const int n_q_tiles = args.seq_q / kTile;
+  const int n_pairs = (n_q_tiles + 1) / 2;
+  const int per_pair = gridDim.x / n_pairs;          // heads x sequences
+  const int pair = n_pairs - 1 - static_cast<int>(blockIdx.x) / per_pair;
+  const int hb = static_cast<int>(blockIdx.x) % per_pair;
+  const int head = hb % args.num_q_heads, batch = hb / args.num_q_heads;
+  const int kv_head = head / args.group;
   const int n_kv_all = args.seq_k / kTile;
   const int tile_of[2] = {2 * pair, 2 * pair + 1};
   int n_kv_x[2];
@@ -246,34 +280,37 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int diag_tile = args.q_off_tiles + tile_of[x];
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
+    const uint64_t scale2 = pack2(args.scale_log2, args.scale_log2);
     for (int j = 0; j < my_n; ++j) {
       ok = mbar_wait(smem_u32(&s_full[x]), j & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
-      ok = named_bar_and(bar_and, 128, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[kTile];
+      const bool on_diag = args.causal && j == diag_tile;
+      // pass 1: row maximum (four independent chains of three-input maxima); the scores are not kept
+      float mxs[4];
+      {
+        uint32_t sr[kTile];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t (&r)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]);
-        tmem_ld_32x32b_x32(s_tmem + c * 32, r);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&r)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]);
+          tmem_ld_32x32b_x32(s_tmem + c * 32, r);
+        }
+        tmem_ld_wait();
+        float* s = reinterpret_cast<float*>(sr);
+        if (on_diag) {
+#pragma unroll
+          for (int i = 0; i < kTile; ++i)
+            if (i > row) s[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          float m = s[a * 32];
+#pragma unroll
+          for (int i = 1; i + 1 < 32; i += 2) m = fmax3(m, s[a * 32 + i], s[a * 32 + i + 1]);
+          mxs[a] = fmaxf(m, s[a * 32 + 31]);
+        }
       }
-      tmem_ld_wait();
-      float* s = reinterpret_cast<float*>(sr);
-      if (args.causal && j == diag_tile) {
-#pragma unroll
-        for (int i = 0; i < kTile; ++i)
-          if (i > row) s[i] = -INFINITY;
-      }
-      float mxs[8];
-#pragma unroll
-      for (int a = 0; a < 8; ++a) mxs[a] = s[a];
-#pragma unroll
-      for (int i = 8; i < kTile; i += 8) {
-#pragma unroll
-        for (int a = 0; a < 8; ++a) mxs[a] = fmaxf(mxs[a], s[i + a]);
-      }
-      float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
-                       fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       mx *= args.scale_log2;
       float alpha = 1.f;
       if (j == 0) {
@@ -296,34 +333,57 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float rsum[8];
+      const uint64_t negm2 = pack2(neg_m, neg_m);
+      uint64_t rs2[4] = {0, 0, 0, 0};
+      // exp2 of the scaled, shifted scores two at a time; P goes back as bf16 pairs, 64 score columns (32 packed
+      // registers) per store, into the first 64 columns of this tile's S buffer
 #pragma unroll
-      for (int a = 0; a < 8; ++a) rsum[a] = 0.f;
+      for (int h = 0; h < 2; ++h) {
+        // pass 2: 64 scores at a time; the second half is read before the first half's P overwrites columns 0..31
+        uint32_t sr[64];
+        {
+          uint32_t (&ra)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[0]);
+          uint32_t (&rb)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[32]);
+          tmem_ld_32x32b_x32(s_tmem + h * 64, ra);
+          tmem_ld_32x32b_x32(s_tmem + h * 64 + 32, rb);
+          tmem_ld_wait();
+        }
+        float* s = reinterpret_cast<float*>(sr);
+        if (on_diag) {
 #pragma unroll
-      for (int i = 0; i < kTile; i += 8) {
+          for (int i = 0; i < 64; ++i)
+            if (h * 64 + i > row) s[i] = -INFINITY;
+        }
+        uint32_t pk[32];
 #pragma unroll
-        for (int a = 0; a < 8; ++a) {
-          const float t = fmaf(s[i + a], args.scale_log2, neg_m);
-          s[i + a] = (a < POLY) ? ex2_fma(t) : ex2_mufu(t);
-          rsum[a] += s[i + a];
+        for (int i = 0; i < 32; ++i) {
+          float t0, t1;
+          unpack2(fma2(pack2(s[2 * i], s[2 * i + 1]), scale2, negm2), t0, t1);
+          const bool poly = (i & 3) < POLY;
+          const float e0 = poly ? ex2_fma(t0) : ex2_mufu(t0);
+          const float e1 = poly ? ex2_fma(t1) : ex2_mufu(t1);
+          rs2[i & 3] = add2(rs2[i & 3], pack2(e0, e1));
+          pk[i] = pack_bf16x2(e0, e1);
+        }
+        if (h == 0) {
+          // P of scores 0..63 goes to columns 0..31, which still hold scores 0..31 only: already consumed
+          tmem_st_32x32b_x32(s_tmem, pk);
+        } else {
+          tmem_st_32x32b_x32(s_tmem + 32, pk);
         }
       }
-      l_sum = l_sum * alpha + ((rsum[0] + rsum[1]) + (rsum[2] + rsum[3])) + ((rsum[4] + rsum[5]) + (rsum[6] + rsum[7]));
-      // P as bf16 pairs into the first 64 columns of this tile's S buffer
-      uint32_t pk[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) pk[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
-      tmem_st_32x32b_x32(s_tmem, pk);
-      tmem_st_32x32b_x32(s_tmem + 32, pk + 32);
+      float r0, r1, r2, r3;
+      unpack2(add2(rs2[0], rs2[1]), r0, r1);
+      unpack2(add2(rs2[2], rs2[3]), r2, r3);
+      l_sum = l_sum * alpha + ((r0 + r1) + (r2 + r3));
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&p_ready[x]));
     }
     if (my_n > 0) {
-      if (ok) {
-        ok = mbar_wait(smem_u32(&pv_done[x]), (my_n - 1) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
-        ok = named_bar_and(bar_and, 128, ok);
-      }
+      if (ok) ok = mbar_wait(smem_u32(&pv_done[x]), (my_n - 1) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
+      // one decision for the whole warpgroup (a thread that gave up above still arrives here)
+      ok = named_bar_and(bar_and, 128, ok);
       if (ok) {
         tc_fence_after();
         // every MMA that read Q_X has completed: its shared-memory tile now stages the output
@@ -376,7 +436,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
 namespace {
 using namespace mfb;
-int g_fa2_poly = 2;   // eighths of the exponentials evaluated on the FMA pipe
+int g_fa2_poly = 0;   // quarters of the exponentials evaluated on the FMA pipe
 
 template <int POLY>
 int fa2_launch_poly(const CUtensorMap& tQ, const CUtensorMap& tK, const CUtensorMap& tV, const CUtensorMap& tO,
@@ -403,8 +463,8 @@ int fa2_launch_poly(const CUtensorMap& tQ, const CUtensorMap& tK, const CUtensor
 
 extern "C" {
 
-// Fraction (in eighths, 0..4) of the exponentials that the two-tile forward evaluates on the FMA pipe.
-void mfb_flash_attn_fwd2_set_poly(int eighths) { g_fa2_poly = eighths < 0 ? 0 : (eighths > 4 ? 4 : eighths); }
+// Fraction (in quarters, 0..2) of the exponentials that the two-tile forward evaluates on the FMA pipe.
+void mfb_flash_attn_fwd2_set_poly(int quarters) { g_fa2_poly = quarters < 0 ? 0 : (quarters > 2 ? 2 : quarters); }
 
 // Two-tile forward, head dim 128. Arguments as mfb_flash_attn_fwd_ex.
 int mfb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
@@ -429,13 +489,11 @@ int mfb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, fl
   a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.lse = lse; a.status = status;
-  dim3 grid((Sq / T + 1) / 2, Hq, B);
+  dim3 grid(((Sq / T + 1) / 2) * Hq * B);
   switch (g_fa2_poly) {
     case 0: return fa2_launch_poly<0>(tQ, tK, tV, tO, a, grid, stream);
     case 1: return fa2_launch_poly<1>(tQ, tK, tV, tO, a, grid, stream);
-    case 2: return fa2_launch_poly<2>(tQ, tK, tV, tO, a, grid, stream);
-    case 3: return fa2_launch_poly<3>(tQ, tK, tV, tO, a, grid, stream);
-    default: return fa2_launch_poly<4>(tQ, tK, tV, tO, a, grid, stream);
+    default: return fa2_launch_poly<2>(tQ, tK, tV, tO, a, grid, stream);
   }
 }
 

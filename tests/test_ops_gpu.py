@@ -313,6 +313,40 @@ def test_flash_attention_fwd_bwd(B, S, nq, nkv, causal):
     assert _rel_err(gq, rq) < 2e-2
 
 
+@pytest.mark.parametrize("split", [1, 2, 4])
+@pytest.mark.parametrize("variant", [1, 2])
+def test_flash_attention_backward_variants_and_group_split(variant, split):
+    """Both backward kernels, and the pipelined one with a KV head's query-head group cut over 1 / 2 / 4 CTAs (fp32
+    reduce-add of dK / dV), against fp32 attention."""
+    from mindformers_b200.ops import attention as A
+    if variant == 1 and split != 1:
+        pytest.skip("the serial kernel has no group split")
+    lib = _lib.get_lib()
+    torch.manual_seed(40 + split)
+    B, S, nq, nkv, hd = 2, 640, 8, 2, 128
+    packed = (torch.randn(B * S, nq + 2 * nkv, hd, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    try:
+        lib.mfb_flash_attn_set_bwd_variant(variant)
+        lib.mfb_flash_attn_bwd2_set_split(split)
+        out = A.flash_attention_packed(packed, B, S, nq, nkv, causal=True)
+        g = (torch.randn_like(out) * 0.1)
+        out.backward(g)
+        torch.cuda.synchronize()
+    finally:
+        lib.mfb_flash_attn_set_bwd_variant(2)
+        lib.mfb_flash_attn_bwd2_set_split(0)
+    _status_ok()
+    ref_in = packed.detach().float().requires_grad_()
+    q = ref_in[:, :nq].reshape(B, S, nq, hd)
+    k = ref_in[:, nq:nq + nkv].reshape(B, S, nkv, hd)
+    v = ref_in[:, nq + nkv:].reshape(B, S, nkv, hd)
+    ref = Fn.attention_reference(q, k, v, causal=True).reshape(B * S, nq * hd)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    for lo, hi in ((0, nq), (nq, nq + nkv), (nq + nkv, nq + 2 * nkv)):
+        assert _rel_err(packed.grad[:, lo:hi], ref_in.grad[:, lo:hi]) < 2e-2
+
+
 @pytest.mark.parametrize("E,k,sig,groups,gk,bias", [(128, 8, False, 0, 0, False), (256, 8, True, 8, 4, True),
                                                     (64, 6, True, 0, 0, False), (160, 4, False, 4, 2, False)])
 def test_router_topk_fwd_bwd(E, k, sig, groups, gk, bias):
