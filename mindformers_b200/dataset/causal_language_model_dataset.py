@@ -44,8 +44,11 @@ class ResumableShardSampler(Sampler):
             order = np.random.RandomState(self.seed + self.epoch).permutation(self.size)
         else:
             order = np.arange(self.size)
+        # strided shards (sample i of the order goes to shard i % num_shards, as MindSpore's distributed sampler
+        # does): the samples of global step s are order[s*G : (s+1)*G] for every data-parallel size, so a run that
+        # resumes under another layout continues with exactly the data the old layout would have seen
         per = self.size // self.num_shards
-        mine = order[self.shard_id * per:(self.shard_id + 1) * per]
+        mine = order[self.shard_id::self.num_shards][:per]
         start, self.skip = self.skip, 0
         return iter(mine[start:].tolist())
 

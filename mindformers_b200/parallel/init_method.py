@@ -7,6 +7,7 @@ in place and returns it, which is what the layers' ``init_method`` arguments tak
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Callable
 
@@ -46,3 +47,17 @@ def scaled_init_method_normal(sigma: float, num_layers: int) -> Callable[[torch.
 
 def init_method_zero() -> Callable[[torch.Tensor], torch.Tensor]:
     return _ZeroInit()
+
+
+@contextlib.contextmanager
+def module_rng(base_seed: int, tag: int, device=None):
+    """Random-number scope of one building block of a model (embedding, layer ``i``, output layer): the generators are
+    forked and seeded from ``(base_seed, tag)`` alone, so the block's initial weights do not depend on what was built
+    before it. A pipeline stage that builds layers 16..31 therefore draws the same values for them as a process that
+    builds all 32, the same way a tensor-parallel rank initialises the full matrix and keeps its slice. On exit the
+    generators continue where they were."""
+    cuda = torch.cuda.is_available() and device is not None and str(device).startswith("cuda")
+    devices = [torch.cuda.current_device()] if cuda else []
+    with torch.random.fork_rng(devices=devices):
+        torch.manual_seed((int(base_seed) * 1000003 + int(tag) * 7919 + 12345) % (2 ** 63 - 1))
+        yield

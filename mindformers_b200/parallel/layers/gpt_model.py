@@ -56,19 +56,26 @@ class GPTModel(nn.Module):
         self.tied = (not config.untie_embeddings_and_output_weights) if share_embeddings_and_output_weights is None \
             else share_embeddings_and_output_weights
         dev = getattr(config, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu")
+        # every building block draws its initial weights from a generator seeded by (process seed, block): the values
+        # do not depend on which other blocks this pipeline stage builds
+        from ..init_method import module_rng
+        seed0 = torch.initial_seed()
         if pre_process:
-            self.embedding = LanguageModelEmbedding(config)
+            with module_rng(seed0, 1, dev):
+                self.embedding = LanguageModelEmbedding(config)
         self.rotary_pos_emb = get_rope(config, device=dev) if config.position_embedding_type in ("rope", "yarn", "llama3") else None
-        self.decoder = TransformerBlock(config, pre_process, post_process, vp_stage)
+        self.decoder = TransformerBlock(config, pre_process, post_process, vp_stage, base_seed=seed0)
         if post_process:
             if config.mtp_num_layers:
                 from .mtp import MultiTokenPredictionBlock
-                self.mtp = MultiTokenPredictionBlock(config)
+                with module_rng(seed0, 70, dev):
+                    self.mtp = MultiTokenPredictionBlock(config)
             else:
                 self.mtp = None
-            self.output_layer = ColumnParallelLinear(config.hidden_size, config.vocab_size, config=config,
-                                                     bias=False, gather_output=False,
-                                                     skip_weight_param_allocation=self.tied and pre_process)
+            with module_rng(seed0, 60, dev):
+                self.output_layer = ColumnParallelLinear(config.hidden_size, config.vocab_size, config=config,
+                                                         bias=False, gather_output=False,
+                                                         skip_weight_param_allocation=self.tied and pre_process)
             self.loss = CrossEntropyLoss(config.calculate_per_token_loss)
         self.input_tensor = None  # activation received from the previous pipeline stage
 

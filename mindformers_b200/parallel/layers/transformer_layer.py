@@ -137,9 +137,12 @@ class StageLayers(nn.Module):
 class TransformerBlock(nn.Module):
     """The layers owned by this pipeline stage (and virtual chunk) plus, on the last stage, the final norm."""
 
-    def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None):
+    def __init__(self, config, pre_process: bool = True, post_process: bool = True, vp_stage: Optional[int] = None,
+                 base_seed: Optional[int] = None):
         super().__init__()
         self.config = config
+        base_seed = torch.initial_seed() if base_seed is None else base_seed
+        dev = getattr(config, "device", None)
         pp = ps.get_pipeline_model_parallel_world_size()
         pp_rank = ps.get_pipeline_model_parallel_rank()
         vpp = config.virtual_pipeline_model_parallel_size or 1
@@ -147,8 +150,12 @@ class TransformerBlock(nn.Module):
         self.layer_ids = split[pp_rank][vp_stage or 0]
         from .gpt_layer_specs import get_gpt_decoder_block_spec
         layer_specs = get_gpt_decoder_block_spec(config)      # one spec per layer of the whole model
-        self.layers = StageLayers(self.layer_ids,
-                                  [build_module(layer_specs[i], config, layer_number=i + 1) for i in self.layer_ids])
+        from ..init_method import module_rng
+        built = []
+        for i in self.layer_ids:
+            with module_rng(base_seed, 100 + i, dev):     # a layer's initial weights depend on its number only
+                built.append(build_module(layer_specs[i], config, layer_number=i + 1))
+        self.layers = StageLayers(self.layer_ids, built)
         self.final_layernorm = build_norm(config) if post_process else None
         self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
         self._recompute_layers = self._resolve_recompute(config.recompute)

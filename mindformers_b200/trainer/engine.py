@@ -124,7 +124,14 @@ class TrainingEngine:
         dev_batch = {k: v.to(self.device, non_blocking=True) for k, v in host_batch.items()
                      if torch.is_tensor(v) and k in ("input_ids", "labels", "loss_mask", "position_ids")}
         out = self.train_step_device(dev_batch)
-        vals = [out["loss"].float().reshape(()), out["global_norm"].float().reshape(()), out["skipped"].float().reshape(())]
+        loss = out["loss"].float().reshape(())
+        if ps.model_parallel_is_initialized() and ps.get_data_parallel_world_size(with_context_parallel=True) > 1:
+            # the logged loss is the mean over the data-parallel replicas (each saw other samples)
+            import torch.distributed as dist
+            loss = loss.clone()
+            dist.all_reduce(loss, group=ps.get_data_parallel_group(with_context_parallel=True))
+            loss = loss / ps.get_data_parallel_world_size(with_context_parallel=True)
+        vals = [loss, out["global_norm"].float().reshape(()), out["skipped"].float().reshape(())]
         if self.device.type == "cuda":
             from ..ops import _lib
             vals.extend(_lib.status_word(self.device).float().unbind(0))     # wait status, expert-parallel overflow

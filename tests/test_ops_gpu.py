@@ -577,7 +577,7 @@ def test_bounded_peer_wait_reports_status_instead_of_hanging():
     assert rc == 0
     torch.cuda.synchronize()
     waited = time.time() - t0
-    assert int(st.item()) == 4                   # kStatusPeerFlagTimeout
+    assert int(st[0].item()) == 4                # kStatusPeerFlagTimeout (word 0; word 1 is the overflow flag)
     assert int(epoch.item()) == 1
     assert 1.0 < waited < 10.0
     st.zero_()
