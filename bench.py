@@ -104,6 +104,10 @@ def main():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--model", default="llama3_1_8b")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is not a valid bench)")
+    ap.add_argument("--micro-batch", type=int, default=None,
+                    help="sequences per forward/backward pass (default: 1 on one GPU, where the full optimizer state leaves "
+                         "room for one sequence of activations at a time; 2 from two GPUs on, where tensor parallelism "
+                         "halves the state per GPU); the global batch and the tokens per step do not change")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-library-arm", action="store_true",
                     help="skip the cuBLAS + SDPA + NCCL arm that is timed on the same engine after this repository's path")
@@ -169,9 +173,10 @@ def main():
     if cp > 1:
         parallel.update(context_parallel_size=cp)
         extra.update(cp_comm_type="p2p", cp_zigzag=True)
+    micro_batch = args.micro_batch or (2 if (world >= 2 and args.config == "llama8b") else 1)
     engine = TrainingEngine.from_model_config(
         preset, parallel=parallel, seq_length=args.seq_len, learning_rate=1e-4, betas=(0.9, 0.95), weight_decay=0.1,
-        max_grad_norm=1.0, micro_batch_size=1,
+        max_grad_norm=1.0, micro_batch_size=micro_batch,
         recompute=([args.recompute] if args.recompute else False), **extra)
     S, V = args.seq_len, preset["vocab_size"]
     n_batches = args.warmup + args.steps
@@ -238,7 +243,7 @@ def main():
     # ---- numerics of the fused multi-GPU paths against the NCCL path, once, before any timing ----
     numerics = None
     if world > 1 and args.impl == "ours" and not args.no_numerics_check:
-        mb = {k: v[:1] for k, v in dev_batches[0].items()}
+        mb = {k: v[:micro_batch] for k, v in dev_batches[0].items()}
 
         def grads_of_one_micro_batch():
             engine.model.train()
@@ -338,7 +343,7 @@ def main():
                        "global_batch": args.seqs_per_gpu if cp > 1 else args.seqs_per_gpu * world, "seq_len": S,
                        "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + (f" cp{cp}(zig-zag)" if cp > 1 else "")
                                       + (f" ep{ep}" if ep > 1 else "") + f" dp{dp} distributed-optimizer",
-                       "micro_batch": 1, "grad_accum_dtype": "fp32", "recompute_layers": args.recompute,
+                       "micro_batch": micro_batch, "grad_accum_dtype": "fp32", "recompute_layers": args.recompute,
                        "l2": "working set (weights + activations, >100 GB) far exceeds the 126 MB L2 every step"},
             "clocks": mine["clocks"], "e2e": e2e, "gpu_launches": mine["launches"], "final_loss": mine["final_loss"],
             "kernel_status_word": status,

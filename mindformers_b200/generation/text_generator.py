@@ -173,7 +173,6 @@ class GenerationMixin:
         return step
 
     # ---- public API -----------------------------------------------------------------------------------
-    @torch.no_grad()
     def _check_device_status(self):
         """After the last token was read back: a kernel whose bounded wait ran out, or an expert-parallel receive
         buffer that overflowed (token rows dropped), makes the generated text wrong, so both raise here instead of
@@ -190,6 +189,7 @@ class GenerationMixin:
                                "Set moe_ep_buffer_factor in the model configuration to the expert-parallel size "
                                "(worst case) or generate with fewer tokens per prefill chunk")
 
+    @torch.no_grad()
     def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]], torch.Tensor],
                  generation_config: Optional[GenerationConfig] = None, logits_processor: Optional[LogitsProcessorList] = None,
                  streamer=None, seed: Optional[int] = None, **kwargs):

@@ -186,3 +186,22 @@ def test_mtp_speculative_decoding_equals_greedy_and_accepts_drafts():
     stats = model.last_generation_stats
     assert out == ref
     assert stats["accepted_draft_tokens"] >= 4 and stats["model_calls"] < 1 + 9      # fewer calls than tokens
+
+
+def test_generate_runs_with_gradients_off():
+    """``generate`` must run the model under ``no_grad`` (the kernels' autograd wrappers, the per-layer buffers of the
+    expert exchange and the CUDA-graph capture all depend on it)."""
+    from mindformers_b200.models import AutoModel
+    torch.manual_seed(0)
+    model = AutoModel.from_config(dict(model_type="llama", num_hidden_layers=1, hidden_size=64, num_attention_heads=4,
+                                       num_key_value_heads=2, intermediate_size=128, vocab_size=128,
+                                       max_position_embeddings=64, params_dtype="float32", compute_dtype="float32"),
+                                  device="cpu").eval()
+    seen = []
+    inner = model.model if hasattr(model, "model") else model
+    hook = inner.register_forward_pre_hook(lambda m, a: seen.append(torch.is_grad_enabled()))
+    try:
+        model.generate([[1, 2, 3, 4]], max_new_tokens=3, do_sample=False, eos_token_id=None)
+    finally:
+        hook.remove()
+    assert seen and not any(seen)
