@@ -136,6 +136,27 @@ class Context:
         np.random.seed(seed % (2 ** 32))
         torch.manual_seed(seed)
 
+    def choose_pipeline_stages(self, par: dict, auto: bool = False) -> int:
+        """``parallel_config.pipeline_stage``, or with ``parallel.auto_pipeline`` the reference's rule
+        (``core/context/parallel.py:46-64``): ``min(max(stages given, number of servers), micro_batch_num)``, so that a
+        job spread over several nodes pipelines across them (the slow links carry activations only) but never uses more
+        stages than there are micro-batches to fill them. The result must divide the device count left after tensor and
+        context parallelism; the largest such value not above the rule's is taken."""
+        given = int(par.get("pipeline_stage", 1) or 1)
+        if not auto:
+            return given
+        local = int(os.environ.get("LOCAL_WORLD_SIZE", 0) or 0) or max(torch.cuda.device_count(), 1)
+        servers = max(1, self.world_size // max(local, 1))
+        micro = int(par.get("micro_batch_num", 1) or 1)
+        want = min(max(given, servers), micro)
+        rest = self.world_size // (int(par.get("model_parallel", 1) or 1) * int(par.get("context_parallel", 1) or 1))
+        while want > 1 and rest % want:
+            want -= 1
+        if par.get("data_parallel") and want != given:
+            par["data_parallel"] = rest // want
+        logger.info("automatic pipeline stages: %d (given %d, servers %d, micro batches %d)", want, given, servers, micro)
+        return max(want, 1)
+
     def init_communication(self, par: dict):
         """Join the job (``torchrun`` environment) and build the model-parallel groups."""
         if "RANK" not in os.environ:
@@ -148,7 +169,9 @@ class Context:
             dist.init_process_group(backend, **kwargs)
         self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
         tp = int(par.get("model_parallel", 1) or 1)
-        pp = int(par.get("pipeline_stage", 1) or 1)
+        pp = self.choose_pipeline_stages(par, ((self.config or {}).get("parallel") or {}).get("auto_pipeline"))
+        if pp != int(par.get("pipeline_stage", 1) or 1):
+            par["pipeline_stage"] = pp
         cp = int(par.get("context_parallel", 1) or 1)
         ep = int(par.get("expert_parallel", 1) or 1)
         dp = par.get("data_parallel")

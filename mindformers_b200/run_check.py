@@ -34,9 +34,29 @@ class MFCheck:
             self.results[name] = {"ok": False, "error": f"{type(e).__name__}: {e}"}
             logger.error("[run_check] %-18s FAILED: %s", name, e)
 
+    @staticmethod
+    def version_map() -> dict:
+        """``VERSION_MAP.json`` next to the package: framework version -> supported torch / CUDA versions (the
+        reference keeps the same table for MindSpore versions)."""
+        import json
+        import os
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "VERSION_MAP.json")) as f:
+            return json.load(f)["mindformers_b200"]
+
     def check_versions(self):
-        info = {"framework": VERSION, "torch": torch.__version__, "cuda": torch.version.cuda,
+        from . import __version__
+        info = {"framework": VERSION, "package": __version__, "torch": torch.__version__, "cuda": torch.version.cuda,
                 "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"}
+        entry = self.version_map().get(__version__)
+        if entry is None:
+            raise RuntimeError(f"VERSION_MAP.json has no entry for package version {__version__}")
+        tv = ".".join(torch.__version__.split("+")[0].split(".")[:2])
+        info["torch_supported"] = tv in entry["torch"]["support"]
+        if not info["torch_supported"]:
+            logger.warning("[run_check] torch %s is outside the tested range %s (preferred %s)", tv,
+                           entry["torch"]["support"], entry["torch"]["prefer"])
+        if torch.version.cuda and torch.cuda.is_available():
+            info["cuda_supported"] = ".".join(torch.version.cuda.split(".")[:2]) in entry["cuda"]["support"]
         if torch.cuda.is_available():
             major, minor = torch.cuda.get_device_capability(0)
             info["sm"] = f"{major}{minor}"

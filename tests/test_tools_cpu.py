@@ -195,3 +195,30 @@ def test_fp8_cast_bf16_tool(tmp_path):
     idx = json.load(open(os.path.join(dst, "model.safetensors.index.json")))["weight_map"]
     assert set(idx) == {"a.weight", "norm.weight"}
     assert "quantization_config" not in json.load(open(os.path.join(dst, "config.json")))
+
+
+def test_reference_package_name_aliases_the_implementation():
+    import mindformers
+    import mindformers.core.context as alias
+    import mindformers_b200.core.context as real
+    from mindformers import MindFormerConfig, Trainer                      # noqa: F401
+    from mindformers.tools.register import MindFormerRegister
+    from mindformers_b200.tools.register import MindFormerRegister as Real
+    assert alias is real and MindFormerRegister is Real
+    assert "Trainer" in dir(mindformers)
+
+
+def test_version_map_and_automatic_pipeline_stages(monkeypatch):
+    from mindformers_b200 import __version__
+    from mindformers_b200.core.context import Context
+    from mindformers_b200.run_check import MFCheck
+    vm = MFCheck.version_map()
+    assert __version__ in vm and "torch" in vm[__version__] and "sm_100a" in vm[__version__]["arch"]
+    ctx = Context.__new__(Context)
+    ctx.world_size, ctx.config = 32, {}
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")                            # four servers of eight devices
+    par = dict(model_parallel=2, pipeline_stage=1, micro_batch_num=8, data_parallel=16)
+    assert ctx.choose_pipeline_stages(dict(par), auto=False) == 1
+    p2 = dict(par)
+    assert ctx.choose_pipeline_stages(p2, auto=True) == 4 and p2["data_parallel"] == 4
+    assert ctx.choose_pipeline_stages(dict(par, micro_batch_num=2), auto=True) == 2     # never more stages than micro-batches

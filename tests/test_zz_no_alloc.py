@@ -60,6 +60,39 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
         assert err < 1e-2, err
 
 
+def _fp32_reference(dy, h, w, rstd, dres):
+    """dx and dw of RMSNorm in fp32 from the same saved statistics."""
+    dyf, hf, wf = dy.float(), h.float(), w.float()
+    xhat = hf * rstd[:, None]
+    dw = (dyf * xhat).sum(0)
+    g = dyf * wf
+    dx = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    return dx, dw
+
+
+@pytest.mark.parametrize("T,H,with_res", [(300, 8192, True), (5000, 8192, False), (149, 1024, True)])
+def test_noalloc_entry_at_its_widest_row_and_accumulating_against_fp32(T, H, with_res):
+    """H = 8192 is the documented maximum; T > 148 makes every thread block walk several rows; ``accumulate = 1`` adds
+    onto a weight gradient that is already there. Checked against an fp32 evaluation, twice in a row."""
+    lib = _lib.get_lib()
+    noalloc = _bind(lib)
+    stream = _lib.stream_ptr()
+    for seed in (11, 12):
+        dy, h, w, rstd, dres = _case(T, H, seed, with_res)
+        dx = torch.empty_like(h)
+        base = torch.randn(H, device="cuda", dtype=torch.float32)
+        dw = base.clone()
+        rc = noalloc(dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), _lib.ptr(dres), dx.data_ptr(),
+                     dw.data_ptr(), 0, 1, T, H, stream)
+        assert rc == 0, lib.mfb_last_error()
+        torch.cuda.synchronize()
+        dx_ref, dw_ref = _fp32_reference(dy, h, w, rstd, dres)
+        assert ((dx.float() - dx_ref).norm() / dx_ref.norm()).item() < 5e-3          # bf16 rounding of dx
+        assert (((dw - base) - dw_ref).norm() / dw_ref.norm()).item() < 1e-4         # fp32 sums in another order
+
+
 def test_noalloc_entry_rejects_rows_wider_than_its_scratch():
     lib = _lib.get_lib()
     noalloc = _bind(lib)
