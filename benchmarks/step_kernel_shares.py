@@ -1,0 +1,88 @@
+"""Per-kernel device-time shares of one training step (torch.profiler, rank 0), for this repository's path and for the
+library path (cuBLAS + SDPA + NCCL) on the same engine.
+
+    python benchmarks/step_kernel_shares.py --layers 8
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/step_kernel_shares.py --layers 8
+
+The model is Llama-3.1-8B with ``--layers`` layers (shares, not absolute times, are what this is for: the profiler
+serialises little but adds launch overhead). Tensor parallel 2 with sequence parallelism from two ranks on.
+"""
+import argparse
+import json
+import os
+import sys
+from collections import defaultdict
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--seqs", type=int, default=4)
+    ap.add_argument("--micro-batch", type=int, default=None)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from mindformers_b200.models.presets import get_preset
+    from mindformers_b200.ops import functional as Fn
+    from mindformers_b200.parallel import fused_comm, parallel_state as ps
+    from mindformers_b200.trainer.engine import TrainingEngine
+    tp = 2 if world >= 2 else 1
+    ps.initialize_model_parallel(tensor_model_parallel_size=tp)
+    dp = world // tp
+    preset = get_preset("llama3_1_8b")
+    preset["num_hidden_layers"] = args.layers
+    mbs = args.micro_batch or (2 if world >= 2 else 1)
+    engine = TrainingEngine.from_model_config(preset, parallel=dict(tensor_model_parallel_size=tp, sequence_parallel=tp > 1),
+                                              seq_length=4096, micro_batch_size=mbs)
+    n = args.seqs * world // dp
+    ids = torch.randint(0, preset["vocab_size"], (n, 4097), device="cuda")
+    batch = {"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()}
+
+    def shares(label):
+        for _ in range(2):
+            engine.train_step_device(batch)
+        torch.cuda.synchronize()
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+            engine.train_step_device(batch)
+            torch.cuda.synchronize()
+        agg = defaultdict(lambda: [0, 0.0])
+        for ev in prof.events():
+            if ev.device_type == torch.autograd.DeviceType.CUDA:
+                name = ev.name.split("(")[0][:90]
+                agg[name][0] += 1
+                agg[name][1] += ev.device_time if hasattr(ev, "device_time") else ev.cuda_time
+        total = sum(v[1] for v in agg.values())
+        rows = sorted(((k, c, t) for k, (c, t) in agg.items()), key=lambda r: -r[2])
+        if rank == 0:
+            print(f"== {label}: {total / 1e3:.1f} ms of kernel time in one step ({args.layers} layers, tp{tp}, mbs {mbs})")
+            for k, c, t in rows[:28]:
+                print(f"{100 * t / total:6.2f} %  {t / 1e3:9.2f} ms  x{c:<5d} {k}")
+        return {"label": label, "total_ms": total / 1e3, "rows": [(k, c, t / 1e3) for k, c, t in rows[:60]]}
+
+    out = [shares("this repository")]
+    Fn.set_gemm_backend("cublas")
+    Fn.set_attention_backend("sdpa")
+    fused_comm.set_enabled(False)
+    engine.optimizer.set_fused_dp(False)
+    out.append(shares("library path"))
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            json.dump(out, f, indent=1)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

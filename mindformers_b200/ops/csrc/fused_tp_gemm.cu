@@ -50,6 +50,9 @@ struct TpArgs {
   int tp, rank, epoch;
   int rows_per_chunk;   // M / tp, multiple of 128
   int ksplit;           // COMM 3: CTAs that share the K range of one tile (1 = no split); otherwise 1
+  int probe;            // timing probes (results are wrong): bit 0 drops the peer stores and their fence, bit 1 the
+                        // owner's wait for and reads of the peers' partial tiles
+  int rs_lag;           // COMM 2: > 0 interleaves own and remote tiles after this many remote tiles (see rs_order)
   int* status;
   // ---- COMM 1 ----
   const __nv_bfloat16* peer_a[kTpMaxRanks];  // chunk [rows_per_chunk, K] of every rank (row pitch lda)
@@ -147,6 +150,27 @@ __device__ __forceinline__ TpTile tp_tile_pair(const TpArgs& a, int tile, int fi
   return t;
 }
 
+// Work order of the GEMM -> reduce-scatter kernel. In chunk order the tiles of the other ranks' rows (whose
+// epilogues store over NVLink) come first and the rank's own tiles last, which packs all link traffic into the first
+// (tp-1)/tp of the run; with a short reduction dimension that phase is bound by the link, not by the tensor core.
+// This order starts with `lag` remote tiles (so that every partial tile is on its way well before its owner needs
+// it) and then takes one own tile after every tp-1 remote ones, spreading the stores over the whole run. All ranks
+// use the same order, so the rank that produces a partial tile stays `lag` positions ahead of its consumer.
+__device__ __forceinline__ int rs_order(int i, int n_tiles, int tp, int lag) {
+  const int n_o = n_tiles / tp, n_r = n_tiles - n_o;
+  const int L = lag < n_r ? lag : n_r;
+  if (i < L) return i;
+  const int j = i - L;
+  const int rm1 = tp - 1;
+  int n_cyc = (n_r - L) / rm1;
+  if (n_cyc > n_o) n_cyc = n_o;
+  const int cyc = j / tp, pos = j - cyc * tp;
+  if (cyc < n_cyc) return pos == 0 ? n_r + cyc : L + cyc * rm1 + (pos - 1);
+  const int k = j - n_cyc * tp;
+  const int rem_left = (n_r - L) - n_cyc * rm1;
+  return k < rem_left ? L + n_cyc * rm1 + k : n_r + n_cyc + (k - rem_left);
+}
+
 template <int BN, int STAGES, bool B_MN, int COMM, bool PAIR>
 __global__ void __launch_bounds__(COMM == 1 ? 320 : 192, 1)
 tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chunk; COMM 2: A [M, K]
@@ -233,8 +257,8 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
       uint32_t phase = 0;
       bool ok = true;
       for (int item = wid; item < n_items && ok; item += wstride) {
-        const int tile = item / ksplit;
-        const int kb0 = (item - tile * ksplit) * k_per_split;
+        const int tile = (COMM == 2 && args.rs_lag > 0) ? rs_order(item, n_tiles, args.tp, args.rs_lag) : item / ksplit;
+        const int kb0 = (item - (item / ksplit) * ksplit) * k_per_split;
         const int kb1 = (kb0 + k_per_split < k_blocks) ? kb0 + k_per_split : k_blocks;
         const TpTile t = PAIR ? tp_tile_pair(args, tile, first_chunk, cta) : tp_tile(args, tile, first_chunk);
         const int chunk = t.m_blk / bpc;
@@ -339,14 +363,14 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
     const uint32_t tempty0 = PAIR ? mapa_shared(smem_u32(&tempty_bar[0]), 0) : smem_u32(&tempty_bar[0]);
     const uint32_t tempty1 = PAIR ? mapa_shared(smem_u32(&tempty_bar[1]), 0) : smem_u32(&tempty_bar[1]);
     for (int item = wid; item < n_items && ok; item += wstride) {
-      const int tile = item / ksplit;
-      const int ks = item - tile * ksplit;
+      const int tile = (COMM == 2 && args.rs_lag > 0) ? rs_order(item, n_tiles, args.tp, args.rs_lag) : item / ksplit;
+      const int ks = item - (item / ksplit) * ksplit;
       const TpTile t = PAIR ? tp_tile_pair(args, tile, first_chunk, cta) : tp_tile(args, tile, first_chunk);
       const int owner = t.m_blk / bpc;
       const int mb_local = t.m_blk - owner * bpc;
       const int tile_in_chunk = mb_local * args.num_n_blocks + t.n_blk;
       ok = mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
-      if (COMM == 2 && ok && owner == args.rank) {
+      if (COMM == 2 && ok && owner == args.rank && !(args.probe & 2)) {
         // the peers' partial tiles must have landed in this rank's receive slots
         if (issuer) {
           for (int p = 0; p < args.tp && ok; ++p) {
@@ -514,6 +538,21 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
+      // Own tiles add the peers' partial tiles. The 128 bytes a thread needs from the first peer for chunk c + 1 are
+      // requested while chunk c is converted and stored, so their latency (the data was written over NVLink into this
+      // GPU's memory) is not paid once per chunk in sequence.
+      const bool add_partials = (COMM == 2 && owner == args.rank && !(args.probe & 2));
+      const int p_first = (args.rank == 0) ? 1 : 0;
+      uint4 pre[8];
+      auto partial_src = [&](int p, int c) -> const __nv_bfloat16* {
+        return args.recv_local + (static_cast<size_t>(parity) * args.tp + p) * slot_elems +
+               static_cast<size_t>(local_row) * args.N + t.n_blk * BN + c * 64;
+      };
+      if (add_partials && t.n_blk * BN < args.N) {
+        const __nv_bfloat16* src = partial_src(p_first, 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) pre[j] = ld_cg_v4(src + j * 8);
+      }
 #pragma unroll 1
       for (int c = 0; c < NUM_CHUNKS; ++c) {
         uint32_t v0[32], v1[32], packed[32];
@@ -521,14 +560,13 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
         tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
         tmem_ld_wait();
         const int col0 = t.n_blk * BN + c * 64;
-        if (COMM == 2 && owner == args.rank) {
+        if (add_partials && col0 < args.N) {
           for (int p = 0; p < args.tp; ++p) {
             if (p == args.rank) continue;
-            const __nv_bfloat16* src = args.recv_local + (static_cast<size_t>(parity) * args.tp + p) * slot_elems +
-                                       static_cast<size_t>(local_row) * args.N + col0;
+            const __nv_bfloat16* src = partial_src(p, c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const uint4 u = ld_cg_v4(src + j * 8);
+              const uint4 u = (p == p_first) ? pre[j] : ld_cg_v4(src + j * 8);
               const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -543,6 +581,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
                 }
               }
             }
+          }
+          if (c + 1 < NUM_CHUNKS && col0 + 64 < args.N) {
+            const __nv_bfloat16* src = partial_src(p_first, c + 1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pre[j] = ld_cg_v4(src + j * 8);
           }
         }
 #pragma unroll
@@ -564,7 +607,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
             *reinterpret_cast<uint4*>(srow + ((j ^ (row & 7)) << 4)) =
                 make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
           named_bar_sync(1, 128);
-          if (col0 < args.N) {
+          if (col0 < args.N && !(args.probe & 1)) {
             const int et = threadIdx.x - 64;   // 0..127
             const int cj = et & 7;             // 16-byte chunk inside the row
             __nv_bfloat16* dst0 = args.recv_peer[owner] + (static_cast<size_t>(parity) * args.tp + args.rank) * slot_elems +
@@ -598,22 +641,25 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
           ++chunk_counter;
         }
       }
+      // the accumulator has been read out: hand it back to the MMA warp BEFORE the tile is published, so that the
+      // system-scope fence below (a round trip over NVLink) is not on the path of the next tile's main loop
       tc_fence_before();
-      if (COMM == 2 && owner != args.rank) {
-        // all 128 threads have issued their peer stores: publish the tile
-        __threadfence_system();
-        named_bar_sync(1, 128);
-        if (issuer) {
-          int* f = args.tile_flags_peer[owner] + (static_cast<size_t>(parity) * args.tp + args.rank) * tiles_per_chunk + tile_in_chunk;
-          st_release_sys(f, args.epoch);
-        }
-      }
       __syncwarp();
       if (lane == 0) {
         if (PAIR) mbar_arrive_cluster(acc == 0 ? tempty0 : tempty1);
         else mbar_arrive(smem_u32(&tempty_bar[acc]));
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (COMM == 2 && owner != args.rank) {
+        // all 128 threads have issued their peer stores: publish the tile. The barrier orders every thread's stores
+        // before the issuer's release store, whose system scope is cumulative over them; one thread pays the round
+        // trip over the link, not 128
+        named_bar_sync(1, 128);
+        if (issuer) {
+          int* f = args.tile_flags_peer[owner] + (static_cast<size_t>(parity) * args.tp + args.rank) * tiles_per_chunk + tile_in_chunk;
+          st_release_sys(f, args.epoch);
+        }
+      }
     }
     if (issuer) tma_wait_group<0>();
   } else {
@@ -668,6 +714,8 @@ namespace {
 using namespace mfb;
 
 bool g_tp_pair_enabled = true;
+bool g_tp_rs_interleave = true;
+int g_tp_probe = 0;
 
 template <int BN, int STAGES, bool B_MN, int COMM, bool PAIR = false>
 int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& tB, const CUtensorMap& tD,
@@ -792,6 +840,17 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
   else rc = mfb_host::make_tmap_2d(&tB, B, 2, BF, N, K, ldb, pair ? BN / 2 : BN, kTpBK);
   if (rc) return 40 + rc;
   if ((rc = mfb_host::make_tmap_2d(&tD, D, 2, BF, a.rows_per_chunk, N, ldd, kTpBM, 64))) return 50 + rc;
+  a.probe = g_tp_probe;
+  if (g_tp_rs_interleave && tp == 2) {
+    // With two ranks the producer of every partial tile is 2 * lag - 1 positions ahead of its consumer, so the tile
+    // at the smallest unfinished position never waits on a later one and the order cannot deadlock; with more ranks
+    // the last remote chunk would come after the own tiles that need it, so chunk order is kept there.
+    // two waves of remote tiles first. The tile walk goes band by band (8 pairs or 16 row blocks): a chunk must be
+    // whole bands for "the first (tp-1)/tp of the tiles" to be exactly the remote ones; otherwise chunk order is kept
+    const int units = pair ? (a.num_m_blocks / 2) : a.num_m_blocks;
+    const int band = pair ? 8 : 16;
+    if ((units / tp) % band == 0) a.rs_lag = 2 * (148 / (pair ? 2 : 1));
+  }
   if (pair) return b_mn_major ? tp_launch<256, 6, true, 2, true>(tA, tA, tB, tD, a, stream)
                               : tp_launch<256, 6, false, 2, true>(tA, tA, tB, tD, a, stream);
   if (bn256) return b_mn_major ? tp_launch<256, 4, true, 2>(tA, tA, tB, tD, a, stream)
@@ -857,6 +916,12 @@ int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, i
   return b_mn_major ? tp_launch<128, 6, true, 3>(tA, tA, tB, tD, a, stream)
                     : tp_launch<128, 6, false, 3>(tA, tA, tB, tD, a, stream);
 }
+
+// Timing probes of the reduce-scatter GEMM (see TpArgs::probe); results are wrong while a probe is set.
+void mfb_tp_set_probe(int bits) { g_tp_probe = bits; }
+
+// Switch the interleaved work order of the reduce-scatter GEMM (on by default) for A/B measurements.
+void mfb_tp_set_rs_interleave(int enabled) { g_tp_rs_interleave = enabled != 0; }
 
 // Switch the CTA-pair variant of the all-gather and reduce-scatter GEMMs (on by default) for A/B measurements.
 void mfb_tp_set_pair(int enabled) { g_tp_pair_enabled = enabled != 0; }

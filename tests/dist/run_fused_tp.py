@@ -2,6 +2,7 @@
 against NCCL collectives + fp32 matmul, forward and backward, and times both paths with CUDA events.
 Writes a JSON summary from rank 0 to --out. NVLS is not used (plain peer loads/stores)."""
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -148,6 +149,28 @@ def main():
         res["bench_rs_fc2"] = {"fused_ms": t_f, "nccl_cublas_ms": t_n, "gemm_only_ms": t_g,
                                "fused_tflops": fl / t_f / 1e9, "bytes_over_nvlink": (T - T // tp) * N2 * 2,
                                "nvlink_floor_ms": (T - T // tp) * N2 * 2 / 770e9 * 1e3}
+        # short reduction dimensions (attention output projection, dgrad of the QKV projection): the link-bound cases
+        lib = _lib.get_lib()
+        for tag, K4, N4, bmn in (("rs_proj", 4096 // tp, 4096, False), ("rs_qkv_dgrad", 6144 // tp, 4096, True)):
+            x4 = torch.randn(T, K4, device="cuda").to(torch.bfloat16)
+            w4 = (torch.randn((K4, N4) if bmn else (N4, K4), device="cuda") * 0.05).to(torch.bfloat16)
+            row = {}
+            for mode in (0, 1):
+                lib.mfb_tp_set_rs_interleave(mode)
+                row["interleaved_ms" if mode else "chunk_order_ms"] = timeit(lambda: fused_tp.gemm_reduce_scatter(x4, w4, b_mn=bmn))
+            if hasattr(lib, "mfb_tp_set_probe"):
+                lib.mfb_tp_set_probe.argtypes = [ctypes.c_int]
+                lib.mfb_tp_set_probe.restype = None
+                for bits, name in ((1, "probe_no_peer_stores_ms"), (2, "probe_no_partial_reads_ms"), (3, "probe_neither_ms")):
+                    lib.mfb_tp_set_probe(bits)
+                    row[name] = timeit(lambda: fused_tp.gemm_reduce_scatter(x4, w4, b_mn=bmn))
+                lib.mfb_tp_set_probe(0)
+            row["nccl_cublas_ms"] = timeit(lambda: M.reduce_scatter_first_dim(torch.matmul(x4, w4 if bmn else w4.t()), grp, tp))
+            row["gemm_only_ms"] = timeit(lambda: Fn.gemm(x4, w4, b_mn=bmn))
+            res[f"bench_{tag}"] = row
+        lib.mfb_tp_set_rs_interleave(0)
+        res["bench_rs_fc2"]["chunk_order_ms"] = timeit(lambda: fused_tp.gemm_reduce_scatter(x2, w2))
+        lib.mfb_tp_set_rs_interleave(1)
         res["status_after_bench"] = _lib.read_status()
     if rank == 0:
         print(json.dumps(res, indent=1))
