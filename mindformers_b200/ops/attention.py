@@ -53,7 +53,8 @@ class _PackedAttnFn(torch.autograd.Function):
         q = packed
         k = packed[:, nq:]
         v = packed[:, nq + nkv:]
-        out, lse = _fwd(q, k, v, B, S, nq, nkv, W, W, W, causal, scale)
+        from ..parallel.recompute import cached_output
+        out, lse = cached_output(lambda: _fwd(q, k, v, B, S, nq, nkv, W, W, W, causal, scale))
         ctx.save_for_backward(packed, out, lse)
         ctx.meta = (B, S, nq, nkv, causal, scale)
         return out
@@ -98,7 +99,8 @@ class _AttnFn(torch.autograd.Function):
     def forward(ctx, q, k, v, causal, scale):
         B, S, nq, _ = q.shape
         nkv = k.shape[2]
-        out, lse = _fwd(q, k, v, B, S, nq, nkv, q.stride(1), k.stride(1), v.stride(1), causal, scale)
+        from ..parallel.recompute import cached_output
+        out, lse = cached_output(lambda: _fwd(q, k, v, B, S, nq, nkv, q.stride(1), k.stride(1), v.stride(1), causal, scale))
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.meta = (causal, scale)
         return out.view(B, S, nq, HEAD_DIM)

@@ -72,6 +72,11 @@ def apply_fn(fn, *args):
 
 
 
+def _cached_output(compute):
+    from ..parallel.recompute import cached_output
+    return cached_output(compute)
+
+
 def _on_gpu(t: torch.Tensor) -> bool:
     return t.is_cuda
 
@@ -242,7 +247,7 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        y = _cached_output(lambda: gemm(x2, w, out_dtype=x.dtype))   # a selective-recompute region runs the product once only
         if x.dim() == 2:
             return y  # not a view: later in-place kernels (RoPE) may write into it
         return y.reshape(*x.shape[:-1], w.shape[0])
@@ -254,7 +259,7 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).reshape(x.shape)
+            dx = gemm(dy2, w, b_mn=True, out_dtype=x.dtype).reshape(x.shape)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, "main_grad", None)
             if main_grad is not None:
@@ -266,6 +271,11 @@ class _LinearFn(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    from ..parallel.recompute import current_cache
+    if current_cache() is not None and torch.is_grad_enabled():
+        # inside a selective-recompute region every product goes through the function that knows the output cache
+        y = _LinearFn.apply(x, w)
+        return y if bias is None else y + bias
     if not _on_gpu(x) or x.dtype != torch.bfloat16 or _GEMM_BACKEND != "tcgen05":
         if getattr(w, "main_grad", None) is not None and x.is_cuda:
             y = apply_fn(_LinearFn, x, w)

@@ -219,7 +219,8 @@ def allreduce_shapes_ok(T: int, K: int, N: int) -> bool:
 class _AllGatherLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, w):
-        y, x_full = allgather_gemm(x_local, w)
+        from .recompute import cached_output
+        y, x_full = cached_output(lambda: allgather_gemm(x_local, w))    # no second exchange in a recomputation
         ctx.save_for_backward(x_full, w)
         return y
 
@@ -241,8 +242,9 @@ class _AllGatherLinearFn(torch.autograd.Function):
 class _LinearReduceScatterFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
+        from .recompute import cached_output
         ctx.save_for_backward(x, w)
-        return gemm_reduce_scatter(x, w)
+        return cached_output(lambda: gemm_reduce_scatter(x, w))
 
     @staticmethod
     def backward(ctx, dy_local):

@@ -170,8 +170,9 @@ class _GroupedLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, block_group, num_blocks, group_offsets):
+        from ..recompute import cached_output
         ctx.save_for_backward(x, w, block_group, num_blocks, group_offsets)
-        return Fn.grouped_gemm(x, w, block_group, num_blocks, b_mn=True)
+        return cached_output(lambda: Fn.grouped_gemm(x, w, block_group, num_blocks, b_mn=True))
 
     @staticmethod
     def backward(ctx, dy):

@@ -159,6 +159,53 @@ class TransformerBlock(nn.Module):
         self.final_layernorm = build_norm(config) if post_process else None
         self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
         self._recompute_layers = self._resolve_recompute(config.recompute)
+        self._setup_selective_recompute_and_offload(config)
+
+    # reference defaults of ``select_recompute: true`` (``training_graph/transformer/utils.py:107-110``): the gated
+    # activation of the MLP and of the shared experts; here these, the norms and the rotary embedding are what a
+    # selectively recomputed layer runs twice, whatever the patterns say, because nothing else is cheap
+    _DEFAULT_SELECT = (r"mlp\.mul", r"mlp\.activation_func\.silu", r"mlp\.shared_experts\.mul",
+                       r"mlp\.shared_experts\.activation_func\.silu", r".*\.norm")
+
+    def _setup_selective_recompute_and_offload(self, config):
+        from ..recompute import ActivationOffloader, mark_recompute_modules
+        n = len(self.layer_ids)
+        sel = getattr(config, "select_recompute", False)
+        patterns, count = [], 0
+        if isinstance(sel, dict):                       # {pattern: layers per stage}
+            patterns, count = list(sel.keys()), n
+            counts = [self._resolve_recompute(v) for v in sel.values()]
+            count = max(counts) if counts else 0
+        elif isinstance(sel, (list, tuple)) and sel and all(isinstance(x, str) for x in sel):
+            patterns, count = list(sel), n
+        else:
+            count = self._resolve_recompute(sel)
+        self._select_layers = count
+        extra = [p for p in patterns if p not in self._DEFAULT_SELECT]
+        self._select_matched = []
+        for layer in self.layers[:count]:
+            self._select_matched += mark_recompute_modules(layer, extra)
+        ignored = [k for k in ("recompute_slice_activation", "select_comm_recompute", "parallel_optimizer_comm_recompute")
+                   if getattr(config, k, False)]
+        if ignored:
+            from ...tools.logger import logger
+            logger.warning("recompute options without effect here: %s (the fused GEMM + collective kernels leave no "
+                           "separate communication output to recompute, activations are not sliced)", ignored)
+        # offload: ``swap: true`` with ``layer_swap`` = number of layers (or a list of {layers, backward_prefetch})
+        self._offload = None
+        self._offload_layers = set()
+        if getattr(config, "cpu_offloading", False):
+            spec = getattr(config, "cpu_offloading_num_layers", None)
+            prefetch = int(getattr(config, "default_prefetch", 1) or 1)
+            if isinstance(spec, (list, tuple)) and spec and isinstance(spec[0], dict):
+                for entry in spec:
+                    ids = entry.get("layers", True)
+                    prefetch = int(entry.get("backward_prefetch", prefetch) or prefetch)
+                    self._offload_layers |= set(range(n)) if ids is True else {int(i) for i in ids if int(i) < n}
+            else:
+                k = n if spec in (None, True) else min(int(spec), n)
+                self._offload_layers = set(range(k))
+            self._offload = ActivationOffloader(prefetch=prefetch)
 
     def _resolve_recompute(self, rc):
         n = len(self.layer_ids)
@@ -177,11 +224,22 @@ class TransformerBlock(nn.Module):
     def forward(self, hidden, rotary, meta: AttnMeta):
         pending, residual = hidden, None
         aux_total = None
+        training = self.training and torch.is_grad_enabled()
+        if training and self._offload is not None:
+            self._offload.prune()
         for idx, layer in enumerate(self.layers):
-            if self.training and idx < self._recompute_layers and torch.is_grad_enabled():
-                pending, residual, aux = checkpoint(layer, pending, residual, rotary, meta, use_reentrant=False)
+            run = layer
+            if training and self._offload is not None and idx in self._offload_layers:
+                def run(p, r, ro, m, _layer=layer, _idx=idx):     # saved tensors of this layer go to pinned host memory
+                    with self._offload.layer(_idx):
+                        return _layer(p, r, ro, m)
+            if training and idx < self._recompute_layers:
+                pending, residual, aux = checkpoint(run, pending, residual, rotary, meta, use_reentrant=False)
+            elif training and idx < self._select_layers:
+                from ..recompute import selective_checkpoint
+                pending, residual, aux = selective_checkpoint(run, pending, residual, rotary, meta)
             else:
-                pending, residual, aux = layer(pending, residual, rotary, meta)
+                pending, residual, aux = run(pending, residual, rotary, meta)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
         if self.final_layernorm is not None:

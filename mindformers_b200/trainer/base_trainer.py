@@ -126,7 +126,8 @@ class BaseTrainer:
         loss_scale = float(scale) if isinstance(scale, (int, float)) else 1.0   # bf16 needs no dynamic scaling
         rc = config.get("runner_config") or {}
         mc = _model_dict(config)
-        recompute = bool((config.get("recompute_config") or {}).get("recompute"))
+        rcfg = dict(config.get("recompute_config") or {})
+        recompute = rcfg.get("recompute") or False          # bool, or layers per pipeline stage
         skip = float(wrapper.get("global_norm_spike_threshold", 0) or 0) if wrapper.get("use_skip_data_by_global_norm") else 0.0
         pc = config.get("parallel_config") or {}
         if int(pc.get("seq_split_num", 1) or 1) > 1:
@@ -160,6 +161,14 @@ class BaseTrainer:
             cfgd.setdefault("params_dtype", dtype)
             cfgd.setdefault("compute_dtype", dtype)
             cfgd["recompute"] = recompute
+            for key in ("select_recompute", "recompute_slice_activation", "select_comm_recompute",
+                        "parallel_optimizer_comm_recompute"):
+                if rcfg.get(key):
+                    cfgd[key] = rcfg[key]
+            swap = dict(config.get("swap_config") or {})
+            if swap.get("swap"):
+                cfgd.update(cpu_offloading=True, cpu_offloading_num_layers=swap.get("layer_swap"),
+                            default_prefetch=int(swap.get("default_prefetch", 1) or 1))
             tcfg = convert_to_transformer_config(cfgd, is_mla_model=preset_is_mla(cfgd))
             tcfg.device = "cuda" if torch.cuda.is_available() else "cpu"
             net = build_pipeline_chunks(tcfg) if (pp > 1 and ps.model_parallel_is_initialized()
