@@ -214,6 +214,44 @@ def moe():
         y.float().mean().backward()
 
 
+def grouped():
+    """Grouped expert GEMMs at the Qwen3-30B-A3B shapes of one expert-parallel rank out of 8: 16 local experts, hidden
+    2048, expert FFN 768 (fc1 N = 1536, fc2 K = 768), 4096 tokens x top-8 / 8 ranks = 4096 rows on average."""
+    E, H, F_ = 16, 2048, 768
+    rows_per = [256] * E                              # balanced routing, segments padded to 128
+    R = sum(rows_per)
+    x = bf(R, H)
+    w1 = bf(E, H, 2 * F_, scale=0.05)                 # [E, in, out]
+    w2 = bf(E, F_, H, scale=0.05)
+    block_group = torch.tensor([e for e, r in enumerate(rows_per) for _ in range(r // 128)], dtype=torch.int32, device="cuda")
+    num_blocks = torch.tensor([block_group.numel()], dtype=torch.int32, device="cuda")
+    offs = torch.tensor([0] + list(torch.tensor(rows_per).cumsum(0)), dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        h = Fn.grouped_gemm(x, w1, block_group, num_blocks, b_mn=True)          # fc1  [R, 1536]
+    a = bf(R, F_)
+    for _ in range(3):
+        y = Fn.grouped_gemm(a, w2, block_group, num_blocks, b_mn=True)          # fc2  [R, 2048]
+    dw = torch.zeros(E, H, 2 * F_, device="cuda")
+    for _ in range(3):
+        Fn.grouped_wgrad(x, h, offs, E, dw, accumulate=True)                    # wgrad of fc1
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record()
+    for _ in range(10):
+        Fn.grouped_gemm(x, w1, block_group, num_blocks, b_mn=True)
+    ev[1].record()
+    for _ in range(10):
+        Fn.grouped_gemm(a, w2, block_group, num_blocks, b_mn=True)
+    ev[2].record()
+    for _ in range(10):
+        Fn.grouped_wgrad(x, h, offs, E, dw, accumulate=True)
+    ev[3].record()
+    torch.cuda.synchronize()
+    for name, i, fl in (("fc1", 0, 2.0 * R * H * 2 * F_), ("fc2", 1, 2.0 * R * F_ * H), ("wgrad fc1", 2, 2.0 * R * H * 2 * F_)):
+        ms = ev[i].elapsed_time(ev[i + 1]) / 10
+        print(f"grouped {name}: {ms * 1e3:.1f} us, {fl / ms / 1e9:.0f} TFLOP/s")
+    return y
+
+
 def fp8():
     for (M, N, K) in ((4096, 4096, 7168), (8192, 7168, 2048), (4096, 18432, 7168)):
         x = bf(M, K, scale=0.7)
@@ -322,7 +360,7 @@ def fp8_moe_decode():
           f"({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), status {_lib.read_status()}")
 
 
-CASES = dict(fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+CASES = dict(fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

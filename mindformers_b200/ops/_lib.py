@@ -67,6 +67,8 @@ def _declare(lib):
     sig("mfb_split_master", [P, P, P, L, P])
     sig("mfb_join_master", [P, P, P, L, P])
     sig("mfb_flash_attn_fwd", [P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, F, P, P])
+    sig("mfb_flash_attn_fwd2_varlen", [P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, I, I, F, P, P])
+    sig("mfb_flash_attn_bwd2_varlen", [P] * 12 + [I, I, I, I, I] + [L] * 8 + [I, I, F, P, P])
     lib.mfb_tp_set_rs_interleave.argtypes = [I]
     lib.mfb_tp_set_rs_interleave.restype = None
     lib.mfb_tp_set_pair.argtypes = [I]

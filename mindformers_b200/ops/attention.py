@@ -32,11 +32,39 @@ def _scratch(device, nbytes: int) -> torch.Tensor:
     return _f32(device, (nbytes + 3) // 4)
 
 
-def _fwd(q, k, v, B, S, nq, nkv, q_ld, k_ld, v_ld, causal, scale, need_lse=True):
+def document_tables(cu_seqlens: torch.Tensor = None, actual_seq_len: torch.Tensor = None, B: int = 1, S: int = 0):
+    """``(doc_start, doc_end)`` int32 ``[B, S]`` tables the packed-sequence kernels take: for every token the first
+    position of its document inside its row and one past the last. From ``cu_seqlens`` (``[n + 1]`` boundaries of one
+    packed row, ``B`` must be 1) or from ``actual_seq_len`` (``[B, P]`` cumulative document ends per row, padded with
+    ``S``, as the datasets emit them with ``create_compressed_eod_mask``)."""
+    if cu_seqlens is not None:
+        ends = cu_seqlens[1:].reshape(1, -1).to(torch.int64)
+    else:
+        ends = actual_seq_len.reshape(B, -1).to(torch.int64)
+    dev = ends.device
+    ends, _ = torch.sort(torch.clamp(ends, max=S), dim=1)
+    pos = torch.arange(S, device=dev, dtype=torch.int64).unsqueeze(0).expand(ends.shape[0], S).contiguous()
+    idx = torch.searchsorted(ends, pos, right=True)                      # first end > position
+    padded = torch.cat([ends, torch.full((ends.shape[0], 1), S, dtype=torch.int64, device=dev)], dim=1)
+    doc_end = padded.gather(1, idx)
+    starts = torch.cat([torch.zeros((ends.shape[0], 1), dtype=torch.int64, device=dev), ends], dim=1)
+    doc_start = starts.gather(1, idx)
+    return doc_start.to(torch.int32).contiguous(), doc_end.to(torch.int32).contiguous()
+
+
+def _fwd(q, k, v, B, S, nq, nkv, q_ld, k_ld, v_ld, causal, scale, need_lse=True, doc_start=None):
     T = B * S
     out = torch.empty((T, nq * HEAD_DIM), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((B, nq, S), dtype=torch.float32, device=q.device) if need_lse else None
     st = _lib.status_word(q.device)
+    if doc_start is not None:
+        rc = _lib.get_lib().mfb_flash_attn_fwd2_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                                       _lib.ptr(lse), doc_start.data_ptr(), B, S, S, nq, nkv, q_ld, k_ld,
+                                                       v_ld, out.stride(0), int(causal), 0, float(scale), st.data_ptr(),
+                                                       _lib.stream_ptr())
+        _lib.check(rc, "mfb_flash_attn_fwd2_varlen")
+        _lib.count_launch()
+        return out, lse
     rc = _lib.get_lib().mfb_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.ptr(lse),
                                            B, S, S, nq, nkv, q_ld, k_ld, v_ld, out.stride(0), int(causal),
                                            float(scale), st.data_ptr(), _lib.stream_ptr())
@@ -47,16 +75,17 @@ def _fwd(q, k, v, B, S, nq, nkv, q_ld, k_ld, v_ld, causal, scale, need_lse=True)
 
 class _PackedAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, packed, B, S, nq, nkv, causal, scale):
+    def forward(ctx, packed, B, S, nq, nkv, causal, scale, doc_start=None, doc_end=None):
         # packed: [T, nq + 2 nkv, 128] contiguous
         W = packed.shape[1] * HEAD_DIM
         q = packed
         k = packed[:, nq:]
         v = packed[:, nq + nkv:]
         from ..parallel.recompute import cached_output
-        out, lse = cached_output(lambda: _fwd(q, k, v, B, S, nq, nkv, W, W, W, causal, scale))
+        out, lse = cached_output(lambda: _fwd(q, k, v, B, S, nq, nkv, W, W, W, causal, scale, doc_start=doc_start))
         ctx.save_for_backward(packed, out, lse)
         ctx.meta = (B, S, nq, nkv, causal, scale)
+        ctx.docs = (doc_start, doc_end)
         return out
 
     @staticmethod
@@ -71,13 +100,23 @@ class _PackedAttnFn(torch.autograd.Function):
         st = _lib.status_word(packed.device)
         k, v = packed[:, nq:], packed[:, nq + nkv:]
         dk, dv = dpacked[:, nq:], dpacked[:, nq + nkv:]
+        doc_start, doc_end = ctx.docs
+        if doc_start is not None:
+            rc = lib.mfb_flash_attn_bwd2_varlen(packed.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                                lse.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), dpacked.data_ptr(),
+                                                dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(), B, S, S, nq, nkv, W, W, W,
+                                                out.stride(0), dout.stride(0), W, W, W, int(causal), 0, float(scale),
+                                                st.data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "mfb_flash_attn_bwd2_varlen")
+            _lib.count_launch(4)
+            return dpacked, None, None, None, None, None, None, None, None
         rc = lib.mfb_flash_attn_bwd(packed.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
                                     lse.data_ptr(), dpacked.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                     scratch.data_ptr(), B, S, nq, nkv, W, W, W, out.stride(0), dout.stride(0), W, W, W,
                                     int(causal), float(scale), st.data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "mfb_flash_attn_bwd")
         _lib.count_launch(4)
-        return dpacked, None, None, None, None, None, None
+        return dpacked, None, None, None, None, None, None, None, None
 
 
 def packed_supported(packed: torch.Tensor, S: int, nq: int, nkv: int) -> bool:
@@ -86,10 +125,11 @@ def packed_supported(packed: torch.Tensor, S: int, nq: int, nkv: int) -> bool:
 
 
 def flash_attention_packed(packed: torch.Tensor, B: int, S: int, nq: int, nkv: int, causal: bool = True,
-                           scale: float = None) -> torch.Tensor:
-    """Attention over a packed qkv buffer ``[B·S, nq + 2·nkv, 128]`` → ``[B·S, nq·128]``."""
+                           scale: float = None, doc_start: torch.Tensor = None, doc_end: torch.Tensor = None) -> torch.Tensor:
+    """Attention over a packed qkv buffer ``[B·S, nq + 2·nkv, 128]`` → ``[B·S, nq·128]``. With ``doc_start`` /
+    ``doc_end`` (``document_tables``) every row holds several documents and a token attends inside its own only."""
     scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
-    return _PackedAttnFn.apply(packed, B, S, nq, nkv, causal, scale)
+    return _PackedAttnFn.apply(packed, B, S, nq, nkv, causal, scale, doc_start, doc_end)
 
 
 class _AttnFn(torch.autograd.Function):

@@ -43,6 +43,8 @@ struct Args {
   float scale, scale_log2;
   const float* lse;        // [B, Hq, Sq]
   const float* delta;      // [B, Hq, Sq]
+  const int* doc_start;    // [B, Sq] packed sequences: start of each token's document (null: one document per row)
+  const int* doc_end;      // [B, Sq] one past the last position of each token's document
   int* status;
 };
 
@@ -84,7 +86,8 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint8_t* sdQ = sdS + kTileBytes;          // 16 KB: one [128 rows][32 floats] image of a dQ quarter
   float* s_lse = reinterpret_cast<float*>(sdQ + kSubBytes);   // [2][128], log2 units
   float* s_dlt = s_lse + 2 * kTile;                           // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + 2 * kTile);
+  int* s_doc = reinterpret_cast<int*>(s_dlt + 2 * kTile);     // [2][128] document start of the query columns
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_doc + 2 * kTile);
   uint64_t* kv_full = bars;         // 1
   uint64_t* q_full = bars + 1;      // 2
   uint64_t* q_empty = bars + 3;     // 2
@@ -111,9 +114,17 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int head0 = kv_head * args.group + part * heads_here;
   const int n_q_tiles = args.seq_q / kTile;
   int first_q = args.causal ? kv_tile - args.q_off_tiles : 0;
+  int end_q = n_q_tiles;                      // one past the last query tile that sees this key tile
+  if (args.doc_start) {
+    // packed sequences (Sq == Sk, no offset): the queries that see a key are those of the key's document
+    const size_t k0 = static_cast<size_t>(batch) * args.seq_q + kv_tile * kTile;
+    if (!args.causal) first_q = args.doc_start[k0] / kTile;
+    end_q = (args.doc_end[k0 + kTile - 1] - 1) / kTile + 1;
+    if (end_q > n_q_tiles) end_q = n_q_tiles;
+  }
   if (first_q < 0) first_q = 0;
-  if (first_q > n_q_tiles) first_q = n_q_tiles;
-  const int iters_per_head = n_q_tiles - first_q;
+  if (first_q > end_q) first_q = end_q;
+  const int iters_per_head = end_q - first_q;
   const int n_iter = iters_per_head * heads_here;
   const int row_base = batch * args.seq_q;
   const int krow = batch * args.seq_k + kv_tile * kTile;
@@ -277,12 +288,20 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const int qi = first_q + it % iters_per_head;
       {
         const size_t idx = (static_cast<size_t>(batch) * args.num_q_heads + hq) * args.seq_q + qi * kTile + tid;
-        if (h == 0) s_lse[ph * kTile + tid] = args.lse[idx] * 1.4426950408889634f;
-        else s_dlt[ph * kTile + tid] = args.delta[idx];
+        if (h == 0) {
+          s_lse[ph * kTile + tid] = args.lse[idx] * 1.4426950408889634f;
+        } else {
+          s_dlt[ph * kTile + tid] = args.delta[idx];
+          if (args.doc_start)
+            s_doc[ph * kTile + tid] = args.doc_start[static_cast<size_t>(batch) * args.seq_q + qi * kTile + tid];
+        }
       }
       ok = named_bar_and(kBarStats, 256, ok);          // the table is complete; one decision for both warpgroups
       if (!ok) break;
       const bool diag = args.causal && (qi + args.q_off_tiles == kv_tile);
+      // some query of the tile belongs to a document that starts after the first key of this key tile
+      const int kpos = kv_tile * kTile + row;
+      const bool doc_mask = args.doc_start && (s_doc[ph * kTile + kTile - 1] > kv_tile * kTile);
       uint32_t pk[32];                                 // P^T of this thread's 64 queries as bf16 pairs
       // ---- P^T ----
       if (ok) ok = mbar_wait(smem_u32(s_full), ph, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
@@ -307,6 +326,13 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               if (q0 + 1 < row) p1 = 0.f;
               if (q0 + 2 < row) p2 = 0.f;
               if (q0 + 3 < row) p3 = 0.f;
+            }
+            if (doc_mask) {                            // and none before the start of its document
+              const int4 d = *reinterpret_cast<const int4*>(s_doc + ph * kTile + q0);
+              if (d.x > kpos) p0 = 0.f;
+              if (d.y > kpos) p1 = 0.f;
+              if (d.z > kpos) p2 = 0.f;
+              if (d.w > kpos) p3 = 0.f;
             }
             pk[c * 16 + g * 2] = pack_bf16x2(p0, p1);
             pk[c * 16 + g * 2 + 1] = pack_bf16x2(p2, p3);
@@ -550,13 +576,34 @@ long long mfb_flash_attn_bwd2_scratch_bytes(int B, int Sq, int Sk, int Hq, int H
   return dq + dl + dkv;
 }
 
+int mfb_flash_attn_bwd2_varlen(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                               const float* lse, const int* doc_start, const int* doc_end, void* dq, void* dk, void* dv,
+                               void* scratch, int B, int S, int Sk, int Hq, int Hkv, long long q_ld, long long k_ld,
+                               long long v_ld, long long o_ld, long long do_ld, long long dq_ld, long long dk_ld,
+                               long long dv_ld, int causal, int q_offset, float scale, int* status, cudaStream_t stream);
+
 // Arguments as mfb_flash_attn_bwd_ex; `scratch` holds mfb_flash_attn_bwd2_scratch_bytes(B, Sq, Sk, Hq, Hkv) bytes.
 int mfb_flash_attn_bwd2(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                         void* dq, void* dk, void* dv, void* scratch, int B, int S, int Sk, int Hq, int Hkv,
                         long long q_ld, long long k_ld, long long v_ld, long long o_ld, long long do_ld,
                         long long dq_ld, long long dk_ld, long long dv_ld, int causal, int q_offset, float scale,
                         int* status, cudaStream_t stream) {
+  return mfb_flash_attn_bwd2_varlen(q, k, v, o, d_o, lse, nullptr, nullptr, dq, dk, dv, scratch, B, S, Sk, Hq, Hkv, q_ld,
+                                    k_ld, v_ld, o_ld, do_ld, dq_ld, dk_ld, dv_ld, causal, q_offset, scale, status, stream);
+}
+
+// The same with packed sequences: `doc_start` / `doc_end` [B, S] int32 (device) give for every token the first position
+// of its document and one past its last. Needs S == Sk and q_offset == 0. Both null = one document per row.
+int mfb_flash_attn_bwd2_varlen(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                               const float* lse, const int* doc_start, const int* doc_end, void* dq, void* dk, void* dv,
+                               void* scratch, int B, int S, int Sk, int Hq, int Hkv, long long q_ld, long long k_ld,
+                               long long v_ld, long long o_ld, long long do_ld, long long dq_ld, long long dk_ld,
+                               long long dv_ld, int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
   constexpr int T128 = fb2::kTile, HD = fb2::kHd;
+  if ((doc_start != nullptr) != (doc_end != nullptr) || (doc_start && (S != Sk || q_offset != 0))) {
+    mfb_host::set_error("flash_attn_bwd2: packed sequences need both document tables, Sq == Sk and no query offset");
+    return 1;
+  }
   if (S % T128 || Sk % T128 || Hq % Hkv || B <= 0 || q_offset % T128 || q_offset < 0 || (causal && q_offset + S > Sk)) {
     mfb_host::set_error("flash_attn_bwd2: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d q_offset=%d", B, S, Sk, Hq, Hkv,
                         q_offset);
@@ -594,8 +641,8 @@ int mfb_flash_attn_bwd2(const void* q, const void* k, const void* v, const void*
   a.seq_q = S; a.seq_k = Sk; a.q_off_tiles = q_offset / T128; a.num_q_heads = Hq; a.num_kv_heads = Hkv;
   a.group = Hq / Hkv; a.split = split; a.causal = causal;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
-  a.lse = lse; a.delta = delta; a.status = status;
-  constexpr int SMEM = 6 * fb2::kTileBytes + fb2::kSubBytes + 4 * T128 * 4 + 14 * 8 + 16 + 1024;
+  a.lse = lse; a.delta = delta; a.status = status; a.doc_start = doc_start; a.doc_end = doc_end;
+  constexpr int SMEM = 6 * fb2::kTileBytes + fb2::kSubBytes + 6 * T128 * 4 + 14 * 8 + 16 + 1024;
   static_assert(SMEM <= 232448, "shared memory budget exceeded");
   static bool attr_set = false;
   if (!attr_set) {

@@ -39,6 +39,8 @@ struct Args {
   int causal;
   float scale_log2;
   float* lse;              // [B, Hq, Sq] natural-log LSE (may be null)
+  const int* doc_start;    // [B, Sq] packed sequences: position at which the document of each token starts
+                           // (null: every sequence is one document). Needs Sq == Sk and no query offset.
   int* status;
 };
 
@@ -133,15 +135,21 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int kv_head = head / args.group;
   const int n_kv_all = args.seq_k / kTile;
   const int tile_of[2] = {2 * pair, 2 * pair + 1};
-  int n_kv_x[2];
+  int n_kv_x[2], lo_x[2];   // tile x works on key tiles lo_x[x] .. n_kv_x[x] - 1
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
     const int diag = args.q_off_tiles + tile_of[x];
     int n = args.causal ? (diag + 1 < n_kv_all ? diag + 1 : n_kv_all) : n_kv_all;
     if (tile_of[x] >= n_q_tiles) n = 0;              // odd number of query tiles: the last CTA has tile A only
     n_kv_x[x] = n;
+    lo_x[x] = 0;
+    if (args.doc_start && n > 0) {
+      // documents are contiguous, so no row of the tile starts earlier than its first row's document
+      lo_x[x] = args.doc_start[static_cast<size_t>(batch) * args.seq_q + tile_of[x] * kTile] / kTile;
+    }
   }
   const int n_kv = n_kv_x[0] > n_kv_x[1] ? n_kv_x[0] : n_kv_x[1];
+  const int lo = (n_kv_x[1] > 0 && lo_x[1] < lo_x[0]) ? lo_x[1] : lo_x[0];   // first key tile this CTA loads
   const int k_row0 = batch * args.seq_k;
 
   if (threadIdx.x == 0) {
@@ -183,9 +191,9 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tma_load_2d(smem_u32(sQ) + x * kTileBytes + kSubBytes, &tmQ, qb, head * kHd + 64, q_row);
       }
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      for (int j = lo; j < n_kv && ok; ++j) {
+        const int st = (j - lo) & 1;
+        const uint32_t ph = ((j - lo) >> 1) & 1;
         ok = mbar_wait(smem_u32(&k_empty[st]), ph ^ 1, abort_flag, args.status, kStatusWaitTimeoutProducer);
         if (!ok) break;
         const uint32_t kb = smem_u32(&k_full[st]);
@@ -210,7 +218,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       constexpr uint32_t IDESC_PV = umma_idesc_bf16(kTile, kHd, 0, 1);    // A = P (tensor memory), B = V MN-major
       auto issue_qk = [&](int x, int j) {
         const uint32_t qa = smem_u32(sQ) + x * kTileBytes;
-        const uint32_t ka = smem_u32(sK) + (j & 1) * kTileBytes;
+        const uint32_t ka = smem_u32(sK) + ((j - lo) & 1) * kTileBytes;
 #pragma unroll
         for (int k = 0; k < kHd / 16; ++k) {
           const uint32_t off = (k >> 2) * kSubBytes + (k & 3) * 32;
@@ -220,25 +228,27 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         umma_commit(smem_u32(&s_full[x]));
       };
       bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, args.status, kStatusWaitTimeoutMma);
-      if (ok && n_kv > 0) {
+      auto active = [&](int x, int j) { return j >= lo_x[x] && j < n_kv_x[x]; };
+      if (ok && n_kv > lo) {
         ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (ok) {
           tc_fence_after();
-          if (n_kv_x[0] > 0) issue_qk(0, 0);
-          if (n_kv_x[1] > 0) issue_qk(1, 0);
+          if (active(0, lo)) issue_qk(0, lo);
+          if (active(1, lo)) issue_qk(1, lo);
           umma_commit(smem_u32(&k_empty[0]));
         }
       }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      for (int j = lo; j < n_kv && ok; ++j) {
+        const int st = (j - lo) & 1;
+        const uint32_t ph = ((j - lo) >> 1) & 1;
         ok = mbar_wait(smem_u32(&v_full[st]), ph, abort_flag, args.status, kStatusWaitTimeoutMma);
         if (!ok) break;
         bool k_next_waited = false;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (j >= n_kv_x[x]) continue;
-          ok = mbar_wait(smem_u32(&p_ready[x]), j & 1, abort_flag, args.status, kStatusWaitTimeoutMma);
+          const bool pv_now = active(x, j), qk_next = active(x, j + 1);
+          if (pv_now) {
+          ok = mbar_wait(smem_u32(&p_ready[x]), (j - lo_x[x]) & 1, abort_flag, args.status, kStatusWaitTimeoutMma);
           if (!ok) break;
           tc_fence_after();
           const uint32_t va = smem_u32(sV) + st * kTileBytes;
@@ -247,12 +257,13 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
           for (int k = 0; k < kTile / 16; ++k) {
             const uint64_t b_desc = umma_desc_mnmajor_sw128(va + k * 16 * 128, kSubBytes);
-            umma_f16_ts(o_tmem, p_tmem + k * 8, b_desc, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+            umma_f16_ts(o_tmem, p_tmem + k * 8, b_desc, IDESC_PV, (j > lo_x[x] || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&pv_done[x]));
-          if (j + 1 < n_kv_x[x]) {
+          }
+          if (qk_next) {
             if (!k_next_waited) {
-              ok = mbar_wait(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1, abort_flag, args.status,
+              ok = mbar_wait(smem_u32(&k_full[(j + 1 - lo) & 1]), ((j + 1 - lo) >> 1) & 1, abort_flag, args.status,
                              kStatusWaitTimeoutMma);
               if (!ok) break;
               tc_fence_after();
@@ -263,7 +274,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         if (!ok) break;
         umma_commit(smem_u32(&v_empty[st]));
-        if (k_next_waited) umma_commit(smem_u32(&k_empty[(j + 1) & 1]));
+        if (k_next_waited) umma_commit(smem_u32(&k_empty[(j + 1 - lo) & 1]));
       }
     }
     __syncwarp();
@@ -276,16 +287,23 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const uint32_t s_tmem = tmem_base + x * kTile + lane_base;
     const uint32_t o_tmem = tmem_base + 256 + x * kTile + lane_base;
     const uint32_t bar_and = 2 + x, bar_sync = 4 + x;
-    const int my_n = n_kv_x[x];
+    const int my_n = n_kv_x[x], my_lo = lo_x[x];
     const int diag_tile = args.q_off_tiles + tile_of[x];
+    // first key this row may see (its document's start); 0 without packed sequences
+    const int my_doc = (args.doc_start && my_n > 0)
+                           ? args.doc_start[static_cast<size_t>(batch) * args.seq_q + tile_of[x] * kTile + row] : 0;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     const uint64_t scale2 = pack2(args.scale_log2, args.scale_log2);
-    for (int j = 0; j < my_n; ++j) {
-      ok = mbar_wait(smem_u32(&s_full[x]), j & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
+    for (int j = my_lo; j < my_n; ++j) {
+      ok = mbar_wait(smem_u32(&s_full[x]), (j - my_lo) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
       if (!ok) break;
       tc_fence_after();
-      const bool on_diag = args.causal && j == diag_tile;
+      // columns [col_lo, col_hi] of this key tile are visible to the row; the tile is masked only where some row
+      // of the warp needs it (the diagonal tile, and tiles that hold the start of a row's document)
+      const int col_lo = my_doc - j * kTile;
+      const int col_hi = (args.causal && j == diag_tile) ? row : kTile - 1;
+      const bool on_diag = __any_sync(0xffffffffu, col_lo > 0 || col_hi < kTile - 1);
       // pass 1: row maximum (four independent chains of three-input maxima); the scores are not kept
       float mxs[4];
       {
@@ -300,7 +318,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (on_diag) {
 #pragma unroll
           for (int i = 0; i < kTile; ++i)
-            if (i > row) s[i] = -INFINITY;
+            if (i > col_hi || i < col_lo) s[i] = -INFINITY;
         }
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
@@ -313,13 +331,13 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       mx *= args.scale_log2;
       float alpha = 1.f;
-      if (j == 0) {
+      if (j == my_lo) {
         m_used = mx;
       } else if (mx > m_used + kRescaleThreshold) {
         alpha = ex2_mufu(m_used - mx);
         m_used = mx;
       }
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (j > my_lo && __any_sync(0xffffffffu, alpha != 1.f)) {
         // S(j) is complete, so every earlier P V product has finished; the next one waits for p_ready below:
         // nobody else touches O now
 #pragma unroll
@@ -352,7 +370,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (on_diag) {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
-            if (h * 64 + i > row) s[i] = -INFINITY;
+            if (h * 64 + i > col_hi || h * 64 + i < col_lo) s[i] = -INFINITY;
         }
         uint32_t pk[32];
 #pragma unroll
@@ -381,7 +399,7 @@ flash_attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       mbar_arrive(smem_u32(&p_ready[x]));
     }
     if (my_n > 0) {
-      if (ok) ok = mbar_wait(smem_u32(&pv_done[x]), (my_n - 1) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
+      if (ok) ok = mbar_wait(smem_u32(&pv_done[x]), (my_n - 1 - my_lo) & 1, abort_flag, args.status, kStatusWaitTimeoutEpilogue);
       // one decision for the whole warpgroup (a thread that gave up above still arrives here)
       ok = named_bar_and(bar_and, 128, ok);
       if (ok) {
@@ -466,12 +484,30 @@ extern "C" {
 // Fraction (in quarters, 0..2) of the exponentials that the two-tile forward evaluates on the FMA pipe.
 void mfb_flash_attn_fwd2_set_poly(int quarters) { g_fa2_poly = quarters < 0 ? 0 : (quarters > 2 ? 2 : quarters); }
 
+int mfb_flash_attn_fwd2_varlen(const void* q, const void* k, const void* v, void* o, float* lse, const int* doc_start,
+                               int B, int Sq, int Sk, int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld,
+                               long long o_ld, int causal, int q_offset, float scale, int* status, cudaStream_t stream);
+
 // Two-tile forward, head dim 128. Arguments as mfb_flash_attn_fwd_ex.
 int mfb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
                         int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld, long long o_ld, int causal,
                         int q_offset, float scale, int* status, cudaStream_t stream) {
+  return mfb_flash_attn_fwd2_varlen(q, k, v, o, lse, nullptr, B, Sq, Sk, Hq, Hkv, q_ld, k_ld, v_ld, o_ld, causal, q_offset,
+                                    scale, status, stream);
+}
+
+// The same with packed sequences: `doc_start` [B, Sq] int32 (device) gives, for every token, the position inside its
+// row at which its document starts; a token attends to the keys of its own document only (and, with `causal`, not to
+// later ones). Needs Sq == Sk and q_offset == 0. Null `doc_start` = one document per row.
+int mfb_flash_attn_fwd2_varlen(const void* q, const void* k, const void* v, void* o, float* lse, const int* doc_start,
+                               int B, int Sq, int Sk, int Hq, int Hkv, long long q_ld, long long k_ld, long long v_ld,
+                               long long o_ld, int causal, int q_offset, float scale, int* status, cudaStream_t stream) {
   using namespace mfb;
   constexpr int T = fa2::kTile, HD = fa2::kHd;
+  if (doc_start && (Sq != Sk || q_offset != 0)) {
+    mfb_host::set_error("flash_attn_fwd2: packed sequences need Sq == Sk and no query offset");
+    return 1;
+  }
   if (Sq % T || Sk % T || Hq % Hkv || B <= 0 || q_offset % T || q_offset < 0 || (causal && q_offset + Sq > Sk)) {
     mfb_host::set_error("flash_attn_fwd2: unsupported shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d causal=%d q_offset=%d", B,
                         Sq, Sk, Hq, Hkv, causal, q_offset);
@@ -488,7 +524,7 @@ int mfb_flash_attn_fwd2(const void* q, const void* k, const void* v, void* o, fl
   a.seq_q = Sq; a.seq_k = Sk; a.q_off_tiles = q_offset / T; a.num_q_heads = Hq; a.group = Hq / Hkv;
   a.causal = causal;
   a.scale_log2 = scale * 1.4426950408889634f;
-  a.lse = lse; a.status = status;
+  a.lse = lse; a.status = status; a.doc_start = doc_start;
   dim3 grid(((Sq / T + 1) / 2) * Hq * B);
   switch (g_fa2_poly) {
     case 0: return fa2_launch_poly<0>(tQ, tK, tV, tO, a, grid, stream);

@@ -28,7 +28,9 @@ class TrainOneStep:
         self.micro_batch_size = micro_batch_size
         self.loss_scale = loss_scale
         self.forward_fn = forward_fn or (lambda m, b: m(b["input_ids"], b["labels"], b.get("loss_mask"),
-                                                        b.get("position_ids")))
+                                                        b.get("position_ids"), actual_seq_len=b.get("actual_seq_len"))
+                                         if b.get("actual_seq_len") is not None else
+                                         m(b["input_ids"], b["labels"], b.get("loss_mask"), b.get("position_ids")))
         self._loss_acc = None
 
     def __call__(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:

@@ -32,6 +32,8 @@ class AttnMeta:
     positions: Optional[torch.Tensor] = None   # [T] int position ids (None: t % seq_len)
     cu_seqlens: Optional[torch.Tensor] = None  # [n+1] packed-sequence boundaries (TND layout)
     max_seqlen: int = 0
+    actual_seq_len: Optional[torch.Tensor] = None   # [B, P] cumulative document ends per row (EOD-reset batches)
+    doc_tables: Optional[tuple] = None    # (doc_start, doc_end) int32 [B, S], built once per forward from the above
     cache: Optional[object] = None        # inference.KVCacheContext for paged attention
     cp_rank_positions: bool = False       # positions already hold the context-parallel offsets
 
@@ -73,9 +75,15 @@ class CoreAttention(nn.Module):
         if cp > 1:
             from ..context_parallel import context_parallel_attention
             o = context_parallel_attention(q4, k4, v4, self.scale, self.config)
-        elif meta.cu_seqlens is not None:
+        elif meta.cu_seqlens is not None or meta.actual_seq_len is not None:
             from ..context_parallel import varlen_attention
-            o = varlen_attention(q4, k4, v4, meta.cu_seqlens, self.scale)
+            cu = meta.cu_seqlens
+            if cu is None:       # cumulative ends per row -> boundaries of the flattened token axis
+                ends = meta.actual_seq_len.reshape(B, -1).to(torch.int64).clamp(max=S)
+                flat = (ends + torch.arange(B, device=ends.device).unsqueeze(1) * S).reshape(-1)
+                cu = torch.unique(torch.cat([flat.new_zeros(1), flat]))
+                q4, k4, v4 = (t.reshape(1, B * S, t.shape[2], t.shape[3]) for t in (q4, k4, v4))
+            o = varlen_attention(q4, k4, v4, cu, self.scale)
         elif self.unfused is not None:       # use_flash_attention=False: explicit mask + softmax
             o = self.unfused(q4, k4, v4)
         else:
@@ -154,14 +162,20 @@ class SelfAttention(nn.Module):
                              self.nq + self.nkv, self.rot_dim, self.config.rotary_interleaved)
             q, k, v = packed[:, :self.nq], packed[:, self.nq:self.nq + self.nkv], packed[:, self.nq + self.nkv:]
         ctx = None
-        if meta.cache is None and meta.cu_seqlens is None and ps.get_context_parallel_world_size() == 1 \
+        if meta.cache is None and ps.get_context_parallel_world_size() == 1 \
                 and Fn.get_attention_backend() != "sdpa" and getattr(self, "use_packed_attention", True):
             from ...ops import attention as native
             T = packed.shape[0]
             S = T // meta.batch
             if native.packed_supported(packed, S, self.nq, self.nkv):
+                docs = (None, None)
+                if meta.cu_seqlens is not None or meta.actual_seq_len is not None:
+                    # packed rows (EOD-reset data, TND batches): the kernels take per-token document tables
+                    if meta.doc_tables is None:
+                        meta.doc_tables = native.document_tables(meta.cu_seqlens, meta.actual_seq_len, meta.batch, S)
+                    docs = meta.doc_tables
                 ctx = native.flash_attention_packed(packed, meta.batch, S, self.nq, self.nkv, True,
-                                                    self.core_attention.scale)
+                                                    self.core_attention.scale, docs[0], docs[1])
         if ctx is None:
             ctx = self.core_attention(q, k, v, meta)
         out, bias = self.linear_proj(ctx)

@@ -103,7 +103,7 @@ class GPTModel(nn.Module):
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 loss_mask: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
                 attn_meta: Optional[AttnMeta] = None, return_hidden: bool = False,
-                input_embeds: Optional[torch.Tensor] = None):
+                input_embeds: Optional[torch.Tensor] = None, actual_seq_len: Optional[torch.Tensor] = None):
         """``input_ids``/``labels``: ``[B, S]``. Returns the loss when labels are given, else logits ``[T, V/tp]``.
         ``input_embeds`` ``[B, S, H]`` (full sequence on every tensor-parallel rank) replaces the embedding lookup;
         multimodal models use it to splice encoder outputs into the text embeddings."""
@@ -117,6 +117,10 @@ class GPTModel(nn.Module):
         meta.batch = meta.batch or B
         if position_ids is not None and meta.positions is None:
             meta.positions = position_ids.reshape(-1)
+        if actual_seq_len is not None and meta.actual_seq_len is None:
+            # packed rows: cumulative document ends per row, as datasets with ``create_compressed_eod_mask`` emit them
+            # (reference ``transformer_config.py:466-487`` / ``gpt_dataset.py:612-636``); attention stays inside documents
+            meta.actual_seq_len = actual_seq_len
         if self.pre_process and input_embeds is not None:
             hidden = input_embeds.reshape(B * S, -1)
             if self.embedding.sp:

@@ -122,7 +122,7 @@ class TrainingEngine:
         that ran out raises ``DeviceWaitTimeout``; an expert-parallel receive-buffer overflow sets
         ``moe_rows_dropped`` (the buffers are grown before the next step and the trainer logs the event)."""
         dev_batch = {k: v.to(self.device, non_blocking=True) for k, v in host_batch.items()
-                     if torch.is_tensor(v) and k in ("input_ids", "labels", "loss_mask", "position_ids")}
+                     if torch.is_tensor(v) and k in ("input_ids", "labels", "loss_mask", "position_ids", "actual_seq_len")}
         out = self.train_step_device(dev_batch)
         loss = out["loss"].float().reshape(())
         if ps.model_parallel_is_initialized() and ps.get_data_parallel_world_size(with_context_parallel=True) > 1:

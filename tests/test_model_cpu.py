@@ -369,3 +369,30 @@ def test_selective_and_full_recompute_and_offload_do_not_change_the_training_cur
         seen[name] = dict(R.STATS)
     assert seen["selective"]["computed"] == seen["selective"]["replayed"] > 0, seen
     assert 0 < seen["selective_fc1"]["replayed"] < seen["selective"]["replayed"], seen
+
+
+def test_packed_rows_attend_inside_their_documents_only():
+    """``actual_seq_len`` (cumulative document ends per row, what the GPT dataset emits with the compressed EOD mask)
+    reaches the attention layers: the logits of the second document of a packed row equal those of the same tokens fed
+    alone, with position ids reset at the boundary."""
+    import torch
+    from mindformers_b200.parallel.layers.gpt_model import GPTModel
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    torch.manual_seed(0)
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=128,
+                            vocab_size=97, seq_length=16, max_position_embeddings=16, params_dtype="float32",
+                            compute_dtype="float32")
+    cfg.device = "cpu"
+    model = GPTModel(cfg).eval()
+    ids = torch.randint(1, 97, (2, 16))
+    cut = [6, 11]                                        # row 0: documents [0,6) and [6,16); row 1: [0,11), [11,16)
+    asl = torch.tensor([[6, 16, 16, 16], [11, 16, 16, 16]], dtype=torch.int32)
+    pos = torch.stack([torch.cat([torch.arange(c), torch.arange(16 - c)]) for c in cut])
+    with torch.no_grad():
+        packed = model(ids, position_ids=pos, actual_seq_len=asl).view(2, 16, -1)
+        plain = model(ids, position_ids=pos).view(2, 16, -1)
+        for b, c in enumerate(cut):
+            alone = model(ids[b:b + 1, c:], position_ids=torch.arange(16 - c).unsqueeze(0)).view(16 - c, -1)
+            assert torch.allclose(packed[b, c:], alone, atol=1e-5)
+            assert not torch.allclose(plain[b, c:], alone, atol=1e-3)      # without the table the documents leak
+            assert torch.allclose(packed[b, :c], plain[b, :c], atol=1e-5)  # the first document never sees the second

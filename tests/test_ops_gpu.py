@@ -313,6 +313,45 @@ def test_flash_attention_fwd_bwd(B, S, nq, nkv, causal):
     assert _rel_err(gq, rq) < 2e-2
 
 
+@pytest.mark.parametrize("B,S,nq,nkv,bounds", [
+    (1, 1024, 4, 2, [0, 100, 130, 600, 1024]),          # documents that start and end inside tiles
+    (2, 512, 4, 4, [0, 128, 256, 512]),                 # boundaries on tile edges
+    (1, 640, 8, 2, [0, 640]),                           # one document: must equal the plain kernel
+    (1, 2048, 8, 2, [0, 7, 8, 900, 1500, 1501, 2048]),  # very short documents next to long ones
+])
+def test_flash_attention_packed_sequences_match_per_document_attention(B, S, nq, nkv, bounds):
+    """Packed rows (several documents per sequence, the layout of EOD-reset pre-training data): forward and backward of
+    the kernels with document tables against fp32 attention evaluated separately on every document."""
+    from mindformers_b200.ops import attention as A
+    torch.manual_seed(len(bounds) + S)
+    hd = 128
+    packed = (torch.randn(B * S, nq + 2 * nkv, hd, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    cu = torch.tensor(bounds, device=DEV, dtype=torch.int32)
+    asl = torch.full((B, 8), S, device=DEV, dtype=torch.int32)
+    asl[:, :len(bounds) - 1] = cu[1:]
+    doc_start, doc_end = A.document_tables(actual_seq_len=asl, B=B, S=S)
+    out = A.flash_attention_packed(packed, B, S, nq, nkv, causal=True, doc_start=doc_start, doc_end=doc_end)
+    g = (torch.randn_like(out) * 0.1)
+    out.backward(g)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref_in = packed.detach().float().requires_grad_()
+    r3 = ref_in.view(B, S, nq + 2 * nkv, hd)
+    pieces = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b > a:
+            q, k, v = r3[:, a:b, :nq], r3[:, a:b, nq:nq + nkv], r3[:, a:b, nq + nkv:]
+            pieces.append(Fn.attention_reference(q, k, v, causal=True))
+    ref = torch.cat(pieces, dim=1).reshape(B * S, nq * hd)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    for lo, hi in ((0, nq), (nq, nq + nkv), (nq + nkv, nq + 2 * nkv)):
+        assert _rel_err(packed.grad[:, lo:hi], ref_in.grad[:, lo:hi]) < 2e-2
+    if len(bounds) == 2:
+        plain = A.flash_attention_packed(packed.detach(), B, S, nq, nkv, causal=True)
+        assert torch.equal(plain, out.detach())
+
+
 @pytest.mark.parametrize("split", [1, 2, 4])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_flash_attention_backward_variants_and_group_split(variant, split):
