@@ -244,6 +244,11 @@ def load_checkpoint(model: torch.nn.Module, path: str, *, optimizer=None, strict
                 sd[k] = v
     if kind == "hf":
         sd = name_maps.hf_to_framework(sd, model.config, family)
+    elif any(name_maps.is_legacy_llama_name(k) for k in sd):
+        # a checkpoint written by the reference's legacy Llama (model.layers.N.attention.wq ...): keep the scalars
+        legacy = {k: v for k, v in sd.items() if k.startswith(("model.", "lm_head."))}
+        rest = {k: v for k, v in sd.items() if k not in legacy}
+        sd = dict(rest, **name_maps.legacy_llama_to_framework(legacy, model.config))
     if kind == "dir" and os.path.exists(os.path.join(path, "hyper_param.safetensors")) and "global_step" not in sd:
         sd.update(load_file(os.path.join(path, "hyper_param.safetensors")))
     if sharded is None:

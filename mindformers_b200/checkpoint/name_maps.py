@@ -61,12 +61,61 @@ _LEGACY_LLAMA = [
     ("model.norm.", "model.norm_out."),
 ]
 
+# ChatGLM2/3 and GLM-4 checkpoints (Hugging Face ``THUDM/glm-4-9b`` key names, which the reference's GLM model keeps:
+# models/glm2/convert_weight.py:60-160). ``query_key_value`` rows are ``[Q; K; V]`` and ``dense_h_to_4h`` rows are
+# ``[gate; up]``: the fused layouts of ``linear_qkv`` and ``linear_fc1``, so they map without splitting. The second
+# block covers the reference's split MindSpore names (``qkv_concat`` / ``mlp_concat`` off).
+_GLM = [
+    ("transformer.embedding.word_embeddings.", "embedding.word_embeddings."),
+    ("transformer.embedding.embedding_weight", "embedding.word_embeddings.weight"),
+    ("transformer.encoder.final_layernorm.", "decoder.final_layernorm."),
+    ("transformer.encoder.layers.", "decoder.layers."),
+    ("transformer.output_layer.", "output_layer."),
+    (".self_attention.query_key_value.", ".self_attention.linear_qkv."),
+    (".self_attention.dense.", ".self_attention.linear_proj."),
+    (".mlp.dense_h_to_4h.", ".mlp.linear_fc1."),
+    (".mlp.dense_4h_to_h.", ".mlp.linear_fc2."),
+    (".post_attention_layernorm.", ".pre_mlp_layernorm."),
+]
+_GLM_SPLIT = [
+    (".self_attention.wq.", ".self_attention.linear_q."),
+    (".self_attention.wk.", ".self_attention.linear_k."),
+    (".self_attention.wv.", ".self_attention.linear_v."),
+    (".mlp.dense_left.", ".mlp.gating."),
+    (".mlp.dense_right.", ".mlp.linear_fc1."),
+]
+
+
+def is_glm_name(name: str) -> bool:
+    return name.startswith("transformer.")
+
+
+def convert_name_glm(name: str) -> str:
+    """ChatGLM / GLM-4 key → framework key (fused ``linear_qkv`` / ``linear_fc1`` names for the concatenated tensors,
+    per-projection names for the split ones)."""
+    out = name
+    for a, b in _GLM_SPLIT + _GLM:
+        out = out.replace(a, b)
+    return out
+
+
+def reverse_name_glm(name: str) -> str:
+    """Framework key (fused names) → ChatGLM / GLM-4 key."""
+    out = name
+    for a, b in _GLM:
+        if not a.endswith("embedding_weight"):        # the reference's MindSpore-only spelling: read, never written
+            out = out.replace(b, a)
+    return out
+
+
 FAMILIES = ("llama", "qwen2", "qwen2_5", "qwen2_moe", "qwen3", "qwen3_moe", "deepseek_v2", "deepseek_v3",
             "deepseekv3", "mixtral", "telechat", "glm")
 
 
 def convert_name(hf_name: str, family: str = "llama") -> str:
     """HF key → per-projection framework key."""
+    if family == "glm" and is_glm_name(hf_name):
+        return convert_name_glm(hf_name)
     out = hf_name
     for a, b in _COMMON:
         out = out.replace(a, b)
@@ -77,6 +126,62 @@ def convert_name_legacy(hf_name: str) -> str:
     out = hf_name
     for a, b in _LEGACY_LLAMA:
         out = out.replace(a, b)
+    return out
+
+
+_LEGACY_MARKS = (".attention.wq.", ".attention.wk.", ".attention.wv.", ".attention.wo.", ".attention.w_qkv.",
+                 ".feed_forward.w", "tok_embeddings.", ".attention_norm.", ".ffn_norm.", "model.norm_out.")
+
+
+def is_legacy_llama_name(name: str) -> bool:
+    return any(m in name for m in _LEGACY_MARKS)
+
+
+def legacy_llama_to_hf_name(name: str) -> str:
+    """Legacy Llama key → Hugging Face key (the inverse of ``convert_name_legacy``); the fused ``w_qkv`` /
+    ``w_gate_hidden`` keys have no Hugging Face spelling and are handled by ``legacy_llama_to_framework``."""
+    out = name
+    for hf, legacy in _LEGACY_LLAMA:
+        out = out.replace(legacy, hf)
+    return out
+
+
+def legacy_llama_to_framework(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tensor]:
+    """State dict with the reference's legacy Llama names → fused framework names. ``attention.w_qkv`` (rows
+    ``[Q; K; V]``) and ``feed_forward.w_gate_hidden`` (rows ``[gate; up]``) are the fused layouts already."""
+    direct: Dict[str, torch.Tensor] = {}
+    per_proj: Dict[str, torch.Tensor] = {}
+    for name, t in sd.items():
+        if ".attention.w_qkv." in name:
+            new = name.replace("model.layers.", "decoder.layers.").replace(".attention.w_qkv.", ".self_attention.linear_qkv.")
+            direct[new] = t
+        elif ".feed_forward.w_gate_hidden." in name:
+            new = name.replace("model.layers.", "decoder.layers.").replace(".feed_forward.w_gate_hidden.", ".mlp.linear_fc1.")
+            direct[new] = t
+        else:
+            per_proj[convert_name(legacy_llama_to_hf_name(name))] = t
+    out = fuse_state_dict(per_proj, config)
+    out.update(direct)
+    return out
+
+
+def framework_to_legacy_llama(sd: Dict[str, torch.Tensor], config, qkv_concat: bool = False) -> Dict[str, torch.Tensor]:
+    """Fused framework names → the reference's legacy Llama names; slices are views of the fused tensors."""
+    out: Dict[str, torch.Tensor] = {}
+    fused = {}
+    if qkv_concat:
+        for name in list(sd):
+            if name.endswith((".self_attention.linear_qkv.weight", ".self_attention.linear_qkv.bias")):
+                new = name.replace("decoder.layers.", "model.layers.").replace(".self_attention.linear_qkv.", ".attention.w_qkv.")
+                fused[name] = new
+            elif re.search(r"\.mlp\.linear_fc1\.(weight|bias)$", name):
+                new = name.replace("decoder.layers.", "model.layers.").replace(".mlp.linear_fc1.", ".feed_forward.w_gate_hidden.")
+                fused[name] = new
+    rest = {k: v for k, v in sd.items() if k not in fused}
+    for name, t in unfuse_state_dict(rest, config).items():
+        out[convert_name_legacy(reverse_name(name))] = t
+    for name, new in fused.items():
+        out[new] = sd[name]
     return out
 
 
@@ -125,15 +230,19 @@ def fuse_state_dict(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tens
     contiguous = getattr(config, "use_contiguous_weight_layout", True)
     groups: Dict[str, Dict[str, torch.Tensor]] = {}
     experts: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = {}
+    # a model built with one module per MLA projection keeps the per-projection names as they are
+    split_mla = bool(getattr(config, "multi_latent_attention", False)) and not getattr(config, "mla_qkv_concat", True)
+    pats = [r"(.*\.self_attention)\.linear_(q|k|v)\.(weight|bias)$",
+            r"(.*\.(?:mlp|shared_experts))\.(gating|linear_fc1)\.(weight|bias)$"]
+    if not split_mla:
+        pats.append(r"(.*\.self_attention)\.linear_(q_down_proj|kv_down_proj)\.(weight)$")
     for name, t in sd.items():
         m = _EXPERT_RE.match(name)
         if m:
             experts.setdefault(m["pre"], {})[(int(m["idx"]), m["proj"])] = t
             continue
         key = None
-        for pat in (r"(.*\.self_attention)\.linear_(q|k|v)\.(weight|bias)$",
-                    r"(.*\.(?:mlp|shared_experts))\.(gating|linear_fc1)\.(weight|bias)$",
-                    r"(.*\.self_attention)\.linear_(q_down_proj|kv_down_proj)\.(weight)$"):
+        for pat in pats:
             mm = re.match(pat, name)
             if mm:
                 key = (mm.group(1), mm.group(3), pat)
@@ -143,9 +252,11 @@ def fuse_state_dict(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tens
             continue
         new = name
         new = new.replace(".router.weight.weight", ".router.weight")
-        new = new.replace(".self_attention.linear_q_up_proj.", ".self_attention.linear_qb.")
-        new = new.replace(".self_attention.linear_kv_up_proj.", ".self_attention.linear_kvb.")
-        new = new.replace(".self_attention.kv_layernorm.", ".self_attention.k_layernorm.")
+        if not split_mla:
+            new = new.replace(".self_attention.linear_q_up_proj.", ".self_attention.linear_qb.")
+            new = new.replace(".self_attention.linear_q_proj.", ".self_attention.linear_q.")
+            new = new.replace(".self_attention.linear_kv_up_proj.", ".self_attention.linear_kvb.")
+            new = new.replace(".self_attention.kv_layernorm.", ".self_attention.k_layernorm.")
         out[new] = t
     for g in groups.values():
         prefix, kind, _ = g["_key"]
@@ -159,7 +270,7 @@ def fuse_state_dict(sd: Dict[str, torch.Tensor], config) -> Dict[str, torch.Tens
         else:
             for k2, t in g.items():
                 if k2 != "_key":
-                    name = {"q": "linear_q", "k": "linear_k", "v": "linear_v"}.get(k2, k2)
+                    name = {"q": "linear_q_proj" if split_mla else "linear_q", "k": "linear_k", "v": "linear_v"}.get(k2, k2)
                     out[f"{prefix}.{name}.{kind}"] = t
     for prefix, items in experts.items():
         n = max(i for i, _ in items) + 1
@@ -233,7 +344,7 @@ def hf_to_framework(hf_sd: Dict[str, torch.Tensor], config, family: str = "llama
                 raise KeyError(f"{name} is fp8 but {name}_scale_inv is missing")
             t = weight_dequant(t, sc)           # the fused layouts are built from full-precision tensors
             any_fp8 = True
-        if "rotary_emb.inv_freq" in name:
+        if "rotary_emb.inv_freq" in name or "rotary_pos_emb.inv_freq" in name:
             continue
         if dtype is not None and t.is_floating_point():
             t = t.to(dtype)
@@ -267,6 +378,12 @@ def requantize_linear_weights(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Te
 
 def framework_to_hf(sd: Dict[str, torch.Tensor], config, family: str = "llama", dtype=None) -> Dict[str, torch.Tensor]:
     out = {}
+    if family == "glm":       # GLM checkpoints keep the fused query_key_value / dense_h_to_4h tensors
+        for name, t in sd.items():
+            if dtype is not None and t.is_floating_point():
+                t = t.to(dtype)
+            out[reverse_name_glm(name)] = t.contiguous()
+        return out
     for name, t in unfuse_state_dict(sd, config).items():
         if dtype is not None and t.is_floating_point():
             t = t.to(dtype)

@@ -27,7 +27,7 @@ from ..checkpoint import name_maps
 from ..checkpoint.sharding import shard_for_param
 from ..tools.logger import logger
 
-_LAYER_RE = re.compile(r"^(?:model\.)?(?:decoder\.)?layers\.(\d+)\.")
+_LAYER_RE = re.compile(r"^(?:model\.|transformer\.encoder\.)?(?:decoder\.)?layers\.(\d+)\.")
 
 
 def split_by_tp_rank_rows(sl, rank: int, world: int) -> torch.Tensor:
@@ -165,7 +165,7 @@ def load_weights(model: torch.nn.Module, path: str, family: str = "llama", stric
     layers, other = loader.layer_groups()
     params = dict(model.named_parameters())
     buffers = dict(model.named_buffers())
-    is_hf = any(k.startswith("model.") or k.startswith("lm_head") for k in loader.keys())
+    is_hf = any(k.startswith(("model.", "lm_head", "transformer.")) for k in loader.keys())
     used: set = set()
     fp8_modules: list = []
     peak = 0

@@ -4,7 +4,9 @@ from .families import (ChatGLM2ForConditionalGeneration, DeepseekV2Config, Deeps
                        DeepseekV3ForCausalLM, LlamaConfig, Qwen2MoeConfig, Qwen2MoeForCausalLM,
                        LlamaForCausalLM, MixtralConfig, MixtralForCausalLM, Qwen2Config, Qwen2ForCausalLM, Qwen3Config,
                        Qwen3ForCausalLM, Qwen3MoeConfig, Qwen3MoeForCausalLM, TelechatConfig, TelechatForCausalLM)
+from .families import ChatGLM2Config
 from .modeling_utils import PreTrainedModel
+from .llama_legacy import LegacyLlamaForCausalLM, LlamaLegacyConfig
 from .presets import PRESETS, get_preset
 from .tokenization import ByteTokenizer, TextProcessor, build_tokenizer
 from .tokenization_utils import AddedToken, BatchEncoding, BytePairEncoder, PreTrainedTokenizer

@@ -78,7 +78,68 @@ MixtralConfig = _config("MixtralConfig", "mixtral",
                         dict(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=14336, norm_topk_prob=True,
                              first_k_dense_replace=0, num_key_value_heads=8, rope_theta=1e6))
 TelechatConfig = _config("TelechatConfig", "telechat", dict(vocab_size=131072))
-ChatGLM4Config = _config("ChatGLM2Config", "glm", dict(vocab_size=151552, attention_bias=True, num_key_value_heads=2))
+
+
+class ChatGLM2Config(PretrainedConfig):
+    """ChatGLM2 / ChatGLM3 / GLM-4 configuration with the keys of the reference's class and of the published
+    ``config.json`` files (``models/glm2/glm2_config.py:125-240``: ``padded_vocab_size``, ``num_layers``,
+    ``ffn_hidden_size``, ``kv_channels``, ``multi_query_attention`` / ``multi_query_group_num``, ``rope_ratio``,
+    ``rmsnorm``, ``add_qkv_bias`` …); defaults are GLM-4-9B.
+
+    What makes the family differ from Llama is expressed in ``to_transformer_dict``: the rotary embedding covers the
+    first half of every head and rotates adjacent pairs (``glm2_modules.py`` rotary: ``rope_cache`` over
+    ``kv_channels // 2`` dims, pairs ``(2i, 2i+1)``), its base is ``10000 * rope_ratio``, Q/K/V carry a bias while the
+    other projections do not, and there are ``multi_query_group_num`` KV heads."""
+
+    model_type = "glm"
+
+    @classmethod
+    def default_values(cls):
+        return dict(num_layers=40, padded_vocab_size=151552, hidden_size=4096, ffn_hidden_size=13696, kv_channels=128,
+                    num_attention_heads=32, seq_length=8192, layernorm_epsilon=1.5625e-07, rope_ratio=1.0, rmsnorm=True,
+                    post_layer_norm=True, add_bias_linear=False, add_qkv_bias=True, multi_query_attention=True,
+                    multi_query_group_num=2, tie_word_embeddings=False, pad_token_id=151329, eos_token_id=151329,
+                    max_position_embeddings=None)
+
+    _PAIRS = (("num_layers", "num_hidden_layers"), ("padded_vocab_size", "vocab_size"),
+              ("ffn_hidden_size", "intermediate_size"), ("kv_channels", "head_dim"),
+              ("multi_query_group_num", "num_key_value_heads"), ("layernorm_epsilon", "rms_norm_eps"),
+              ("add_qkv_bias", "attention_bias"), ("rope_ratio", "rope_theta"), ("rope_ratio", "rotary_base"))
+
+    def __init__(self, **kwargs):
+        self._explicit = set(kwargs)
+        super().__init__(**kwargs)
+
+    def to_transformer_dict(self) -> dict:
+        d = self.to_dict()
+        # a configuration written with Hugging Face keys (the GLM-4-0414 ``config.json`` spelling) wins over this
+        # class's ChatGLM-keyed defaults
+        for glm_key, hf_key in self._PAIRS:
+            if d.get(hf_key) is not None and glm_key not in self._explicit:
+                d.pop(glm_key, None)
+        if "rope_ratio" not in d:
+            d.pop("multi_query_attention", None)
+            if "partial_rotary_factor" not in d:
+                d.setdefault("rotary_percent", 0.5)
+            d.setdefault("rotary_interleaved", True)
+            d["normalization"] = "RMSNorm" if d.pop("rmsnorm", True) else "LayerNorm"
+            return d
+        if not d.pop("multi_query_attention", True):
+            d["multi_query_group_num"] = d["num_attention_heads"]
+        d["rotary_base"] = 10000.0 * float(d.pop("rope_ratio", 1.0) or 1.0)
+        d.setdefault("rotary_percent", 0.5)
+        d.setdefault("rotary_interleaved", True)
+        d["normalization"] = "RMSNorm" if d.pop("rmsnorm", True) else "LayerNorm"
+        if d.get("max_position_embeddings") is None:
+            d["max_position_embeddings"] = d.get("seq_length")
+        if "vocab_size" in d and "padded_vocab_size" in d:
+            d.pop("vocab_size")
+        return d
+
+
+MindFormerRegister.register_cls(ChatGLM2Config, MindFormerModuleType.CONFIG, alias="ChatGLM2Config")
+MindFormerRegister.register_cls(ChatGLM2Config, MindFormerModuleType.CONFIG, alias="ChatGLM2Config", legacy=False)
+ChatGLM4Config = ChatGLM2Config
 
 LlamaForCausalLM = _model("LlamaForCausalLM", LlamaConfig, "llama")
 Qwen2ForCausalLM = _model("Qwen2ForCausalLM", Qwen2Config, "qwen2")

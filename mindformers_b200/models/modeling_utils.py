@@ -39,12 +39,18 @@ class PreTrainedModel(nn.Module, GenerationMixin, InferModelMixin):
         if isinstance(config, dict):
             config = self.config_class(**config)
         self.model_config = config
-        d = config.to_dict()
+        # a family whose keys do not map one to one (GLM: rope_ratio, multi_query_attention) translates them itself
+        d = config.to_transformer_dict() if hasattr(config, "to_transformer_dict") else config.to_dict()
         d.update(kwargs)
         if dtype is not None:
             d["params_dtype"] = d["compute_dtype"] = dtype
         d.setdefault("params_dtype", d.get("torch_dtype") or d.get("dtype") or "bfloat16")
         d.setdefault("compute_dtype", d["params_dtype"])
+        if d.get("intermediate_size") is None and d.get("ffn_hidden_size") is None and d.get("multiple_of"):
+            # legacy Llama configurations size the feed-forward from multiple_of / ffn_dim_multiplier
+            from .llama_legacy import legacy_ffn_hidden_size
+            d["intermediate_size"] = legacy_ffn_hidden_size(d["hidden_size"], None, d["multiple_of"],
+                                                            d.get("ffn_dim_multiplier"))
         if d.get("seq_length") is None and d.get("max_position_embeddings"):
             d["seq_length"] = min(int(d["max_position_embeddings"]), 8192)
         tcfg = convert_to_transformer_config(d, is_mla_model=type(config).is_mla or "kv_lora_rank" in d, strict=False)

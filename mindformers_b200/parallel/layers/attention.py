@@ -202,6 +202,23 @@ class MLASelfAttention(nn.Module):
         self.qd = self.nope + self.rope_d
         self.q_rank, self.kv_rank = config.q_lora_rank, config.kv_lora_rank
         H = config.hidden_size
+        replicated = self._build_projections(config, H)
+        self.linear_proj = RowParallelLinear(config.num_attention_heads * self.vd, H, config=config,
+                                             bias=config.add_bias_linear)
+        # these run on the gathered sequence: their gradients are already complete on every rank
+        for mod in replicated:
+            if mod is not None:
+                for prm in mod.parameters():
+                    prm.sequence_parallel = False
+        mscale = 1.0
+        if config.rope_type == "yarn" and config.rotary_scaling_factor > 1 and config.mscale_all_dim:
+            from .rotary import yarn_get_mscale
+            mscale = yarn_get_mscale(config.rotary_scaling_factor, config.mscale_all_dim)
+        self.scale = config.softmax_scale or (mscale * mscale / math.sqrt(self.qd))
+        self.core_attention = CoreAttention(config, layer_number, softmax_scale=self.scale, head_dim=self.qd)
+
+    def _build_projections(self, config, H):
+        """Create the query / kv projections and norms; returns the modules that run replicated on the full sequence."""
         down = (self.q_rank or 0) + self.kv_rank + self.rope_d
         if self.q_rank:
             self.linear_qkv = LinearNoTP(H, down, config=config)
@@ -214,19 +231,7 @@ class MLASelfAttention(nn.Module):
         self.k_layernorm = RMSNorm(config, self.kv_rank, config.layernorm_epsilon)
         self.linear_kvb = ColumnParallelLinear(self.kv_rank, config.num_attention_heads * (self.nope + self.vd),
                                                config=config)
-        self.linear_proj = RowParallelLinear(config.num_attention_heads * self.vd, H, config=config,
-                                             bias=config.add_bias_linear)
-        # these run on the gathered sequence: their gradients are already complete on every rank
-        for mod in (self.linear_qkv, self.q_layernorm, self.k_layernorm):
-            if mod is not None:
-                for prm in mod.parameters():
-                    prm.sequence_parallel = False
-        mscale = 1.0
-        if config.rope_type == "yarn" and config.rotary_scaling_factor > 1 and config.mscale_all_dim:
-            from .rotary import yarn_get_mscale
-            mscale = yarn_get_mscale(config.rotary_scaling_factor, config.mscale_all_dim)
-        self.scale = config.softmax_scale or (mscale * mscale / math.sqrt(self.qd))
-        self.core_attention = CoreAttention(config, layer_number, softmax_scale=self.scale, head_dim=self.qd)
+        return self.linear_qkv, self.q_layernorm, self.k_layernorm
 
     def _rope(self, x, rotary, meta, heads):
         cos, sin = rotary
@@ -245,13 +250,7 @@ class MLASelfAttention(nn.Module):
         else:
             hidden_full = hidden
         T = hidden_full.shape[0]
-        comp, _ = self.linear_qkv(hidden_full)
-        if self.q_rank:
-            q_c, kv_c, k_pe = torch.split(comp, [self.q_rank, self.kv_rank, self.rope_d], dim=-1)
-            q = self._col_nosp(self.linear_qb, self.q_layernorm(q_c))
-        else:
-            kv_c, k_pe = torch.split(comp, [self.kv_rank, self.rope_d], dim=-1)
-            q = self._col_nosp(self.linear_q, hidden_full)
+        q, kv_c, k_pe = self._project(hidden_full)
         q = q.view(T, self.nh, self.qd)
         q_nope, q_pe = q[..., :self.nope], q[..., self.nope:]
         kv_c = self.k_layernorm(kv_c)
@@ -271,6 +270,18 @@ class MLASelfAttention(nn.Module):
         out, bias = self.linear_proj(ctx)
         return out, bias
 
+    def _project(self, hidden_full):
+        """Full-sequence hidden states → (query ``[T, nh·qd]``, compressed kv ``[T, kv_rank]``, shared rotary key
+        ``[T, rope_d]``), before the kv norm and the rotary embedding."""
+        comp, _ = self.linear_qkv(hidden_full)
+        if self.q_rank:
+            q_c, kv_c, k_pe = torch.split(comp, [self.q_rank, self.kv_rank, self.rope_d], dim=-1)
+            q = self._col_nosp(self.linear_qb, self.q_layernorm(q_c))
+        else:
+            kv_c, k_pe = torch.split(comp, [self.kv_rank, self.rope_d], dim=-1)
+            q = self._col_nosp(self.linear_q, hidden_full)
+        return q, kv_c, k_pe
+
     def _col_nosp(self, layer, x):
         """Column-parallel projection of an input that is already full-sequence on every rank."""
         if layer.tp > 1:
@@ -280,3 +291,87 @@ class MLASelfAttention(nn.Module):
         if layer.bias is not None:
             y = y + layer.bias
         return y
+
+
+class MLASelfAttentionMegatron(MLASelfAttention):
+    """Multi-latent attention with one module per projection, under the names Megatron checkpoints use
+    (reference ``training_graph/transformer/multi_latent_attention.py:345-520``, selected by
+    ``mla_qkv_concat=False``): ``linear_q_proj`` (no query compression) or ``linear_q_down_proj`` → ``q_layernorm``
+    → ``linear_q_up_proj``; ``linear_kv_down_proj`` (``[kv_lora ‖ k_pe]``) → ``kv_layernorm`` →
+    ``linear_kv_up_proj``; ``linear_proj``. The arithmetic, the paged decode path and the weight absorption are those
+    of ``MLASelfAttention``; only the parameter layout differs, so a checkpoint in this layout loads without the
+    down-projections being concatenated."""
+
+    def _build_projections(self, config, H):
+        nhq = config.num_attention_heads * self.qd
+        if self.q_rank:
+            self.linear_q_down_proj = LinearNoTP(H, self.q_rank, config=config)
+            self.q_layernorm = RMSNorm(config, self.q_rank, config.layernorm_epsilon)
+            self.linear_q_up_proj = ColumnParallelLinear(self.q_rank, nhq, config=config)
+        else:
+            self.linear_q_proj = ColumnParallelLinear(H, nhq, config=config)
+            self.q_layernorm = None
+        self.linear_kv_down_proj = LinearNoTP(H, self.kv_rank + self.rope_d, config=config)
+        self.kv_layernorm = RMSNorm(config, self.kv_rank, config.layernorm_epsilon)
+        self.linear_kv_up_proj = ColumnParallelLinear(self.kv_rank, config.num_attention_heads * (self.nope + self.vd),
+                                                      config=config)
+        return (getattr(self, "linear_q_down_proj", None), self.linear_kv_down_proj, self.q_layernorm,
+                self.kv_layernorm)
+
+    # the shared forward and the paged decode path address the kv norm and up-projection by the concatenated
+    # layout's names
+    @property
+    def k_layernorm(self):
+        return self.kv_layernorm
+
+    @property
+    def linear_kvb(self):
+        return self.linear_kv_up_proj
+
+    def _project(self, hidden_full):
+        kv, _ = self.linear_kv_down_proj(hidden_full)
+        kv_c, k_pe = torch.split(kv, [self.kv_rank, self.rope_d], dim=-1)
+        if self.q_rank:
+            q_c, _ = self.linear_q_down_proj(hidden_full)
+            q = self._col_nosp(self.linear_q_up_proj, self.q_layernorm(q_c))
+        else:
+            q = self._col_nosp(self.linear_q_proj, hidden_full)
+        return q, kv_c, k_pe
+
+
+class CrossAttention(nn.Module):
+    """Attention whose queries come from the layer input and whose keys and values come from another sequence
+    (an encoder's output): ``linear_q`` (hidden → heads·hd, column-parallel), ``linear_kv`` (hidden → 2·heads·hd,
+    column-parallel, rows ``[K; V]`` per rank), non-causal softmax attention, ``linear_proj`` (row-parallel).
+    Reference ``training_graph/transformer/attention.py:670-760``: like there, the number of query groups must equal
+    the number of heads, and no rotary embedding is applied.
+
+    ``forward(hidden [Tq, H], key_value_states [Tk, H], meta, kv_batch_seq=None)``: both inputs are token-major with
+    ``meta.batch`` sequences of equal length each."""
+
+    def __init__(self, config, layer_number: int = 1):
+        super().__init__()
+        if config.num_query_groups != config.num_attention_heads:
+            raise ValueError("cross attention needs num_query_groups == num_attention_heads")
+        self.config, self.layer_number = config, layer_number
+        self.hd = config.kv_channels
+        tp = ps.get_tensor_model_parallel_world_size()
+        self.nh = config.num_attention_heads // tp
+        width = config.num_attention_heads * self.hd
+        bias = config.add_qkv_bias or config.add_bias_linear
+        self.linear_q = ColumnParallelLinear(config.hidden_size, width, config=config, bias=bias)
+        self.linear_kv = ColumnParallelLinear(config.hidden_size, 2 * width, config=config, bias=bias,
+                                              partition_sections=(width, width))
+        self.linear_proj = RowParallelLinear(width, config.hidden_size, config=config, bias=config.add_bias_linear,
+                                             skip_bias_add=False)
+        self.scale = config.softmax_scale or 1.0 / math.sqrt(self.hd)
+
+    def forward(self, hidden, key_value_states, meta: AttnMeta, rotary=None):
+        q, _ = self.linear_q(hidden)
+        kv, _ = self.linear_kv(key_value_states)
+        B = meta.batch
+        Tq, Tk = q.shape[0], kv.shape[0]
+        q4 = q.view(B, Tq // B, self.nh, self.hd)
+        kv5 = kv.view(B, Tk // B, 2, self.nh, self.hd)
+        o = Fn.attention(q4, kv5[:, :, 0], kv5[:, :, 1], causal=False, scale=self.scale)
+        return self.linear_proj(o.reshape(Tq, self.nh * self.hd))

@@ -12,7 +12,7 @@ from __future__ import annotations
 from typing import List, Optional
 
 from ..spec_utils import ModuleSpec
-from .attention import MLASelfAttention, SelfAttention
+from .attention import CrossAttention, MLASelfAttention, MLASelfAttentionMegatron, SelfAttention
 from .mlp import MLP
 from .moe import GroupedMLP, MoELayer, SharedExpertMLP, TopKRouter
 from .mtp import MultiTokenPredictionBlock, MultiTokenPredictionLayer
@@ -40,11 +40,13 @@ def get_gpt_layer_local_spec(num_experts: Optional[int] = None, moe_grouped_gemm
                              mla_qkv_concat: bool = True) -> ModuleSpec:
     """Spec of one pre-LN transformer layer.
 
-    ``qk_layernorm`` lives in the configuration that the attention reads, the fused ``[Q|K|V]`` weight layout and the
-    concatenated MLA down-projection are the only layouts, so those three switches select nothing here; they are kept
-    so that callers of the reference's function keep working."""
+    ``qk_layernorm`` and the ``[Q|K|V]`` row layout live in the configuration that the attention reads, so those two
+    switches select nothing here. ``mla_qkv_concat=False`` selects the multi-latent attention with one module per
+    projection (``linear_q_down_proj`` / ``linear_q_up_proj`` / ``linear_kv_down_proj`` / ``linear_kv_up_proj``)
+    instead of the concatenated down-projection."""
     norm = ModuleSpec(module=build_norm)
-    attn = ModuleSpec(module=MLASelfAttention if multi_latent_attention else SelfAttention)
+    mla = MLASelfAttention if mla_qkv_concat else MLASelfAttentionMegatron
+    attn = ModuleSpec(module=mla if multi_latent_attention else SelfAttention)
     return ModuleSpec(module=TransformerLayer, submodules=TransformerLayerSubmodules(
         input_layernorm=norm, self_attention=attn, pre_mlp_layernorm=norm,
         mlp=get_mlp_module_spec(num_experts, moe_grouped_gemm),
@@ -56,7 +58,8 @@ def get_gpt_layer_spec_for_config(config, is_moe: bool) -> ModuleSpec:
     return get_gpt_layer_local_spec(
         num_experts=config.num_moe_experts if is_moe else None, moe_grouped_gemm=True,
         qk_layernorm=bool(getattr(config, "qk_layernorm", False)),
-        multi_latent_attention=bool(config.multi_latent_attention), sandwich_norm=bool(config.sandwich_norm))
+        multi_latent_attention=bool(config.multi_latent_attention), sandwich_norm=bool(config.sandwich_norm),
+        mla_qkv_concat=bool(getattr(config, "mla_qkv_concat", True)))
 
 
 def get_gpt_decoder_block_spec(config) -> List[ModuleSpec]:

@@ -53,7 +53,8 @@ _TABLE = [
     ("mtp_num_layers", ("mtp_depth", "num_nextn_predict_layers", "mtp_num_layers"), None),
     ("mtp_loss_scaling_factor", ("mtp_loss_factor", "mtp_loss_scaling_factor"), None),
     ("num_attention_heads", ("num_heads", "num_attention_heads"), None),
-    ("num_query_groups", ("n_kv_heads", "num_key_value_heads", "num_query_groups"), None),
+    ("num_query_groups", ("n_kv_heads", "num_key_value_heads", "multi_query_group_num", "num_query_groups"), None),
+    ("vocab_size", ("padded_vocab_size", "vocab_size"), None),
     ("ffn_hidden_size", ("intermediate_size", "ffn_hidden_size"), None),
     ("kv_channels", ("head_dim", "kv_channels"), None),
     ("fp32_residual_connection", ("fp32_residual_connection",), None),
@@ -95,6 +96,7 @@ _TABLE = [
     ("qk_head_dim", ("qk_nope_head_dim", "qk_head_dim"), None),
     ("qk_pos_emb_head_dim", ("qk_rope_head_dim", "qk_pos_emb_head_dim"), None),
     ("rotary_base", ("theta", "rope_theta", "rotary_base"), None),
+    ("rotary_percent", ("partial_rotary_factor", "rotary_percent"), None),
     ("rotary_scaling_factor", ("scaling_factor", "factor", "rotary_scaling_factor"), None),
     ("max_position_embeddings", ("max_position_embeddings",), None),
     ("original_max_position_embeddings", ("original_max_position_embeddings",), None),
@@ -122,6 +124,10 @@ DEFAULT_WHITE_KEYS = {
     "prefix", "finetuning_task", "task_specific_params", "tf_legacy_loss", "torchscript",
     "pruned_heads", "sep_token_id", "decoder_start_token_id", "_attn_implementation_autoset",
     "attn_implementation", "_attn_implementation", "use_bfloat16", "tokenizer",
+    # ChatGLM / GLM-4 keys that the family's configuration class folds into other fields
+    "rmsnorm", "post_layer_norm", "multi_query_attention", "apply_query_key_layer_scaling", "rope_ratio",
+    "bias_dropout_fusion", "apply_residual_connection_post_layernorm", "original_rope", "classifier_dropout",
+    "mlp_concat", "use_rearrange_rope", "quantization_bit", "pre_seq_len", "prefix_projection", "gmask_token_id",
 }
 
 _FIELDS = {f.name for f in dataclasses.fields(MLATransformerConfig)}

@@ -396,3 +396,212 @@ def test_packed_rows_attend_inside_their_documents_only():
             assert torch.allclose(packed[b, c:], alone, atol=1e-5)
             assert not torch.allclose(plain[b, c:], alone, atol=1e-3)      # without the table the documents leak
             assert torch.allclose(packed[b, :c], plain[b, :c], atol=1e-5)  # the first document never sees the second
+
+
+def _tiny_mla_config(**kw):
+    base = dict(num_layers=2, hidden_size=128, num_attention_heads=4, ffn_hidden_size=256, vocab_size=512,
+                seq_length=64, max_position_embeddings=64, params_dtype="float32", compute_dtype="float32",
+                q_lora_rank=32, kv_lora_rank=32, qk_head_dim=32, qk_pos_emb_head_dim=16, v_head_dim=32,
+                rotary_scaling_factor=1.0)
+    base.update(kw)
+    cfg = MLATransformerConfig(**base)
+    cfg.device = "cpu"
+    return cfg
+
+
+@pytest.mark.parametrize("q_rank", [32, None])
+def test_mla_with_one_module_per_projection_matches_the_concatenated_layout(q_rank):
+    """``mla_qkv_concat=False`` builds ``linear_q_down_proj / linear_q_up_proj / linear_kv_down_proj /
+    linear_kv_up_proj / kv_layernorm`` (``linear_q_proj`` without query compression). A state dict of the
+    concatenated model, split into per-projection names and loaded into that model, gives the same logits and
+    gradients."""
+    from mindformers_b200.checkpoint.name_maps import fuse_state_dict, unfuse_state_dict
+    from mindformers_b200.parallel.layers.attention import MLASelfAttentionMegatron
+    torch.manual_seed(21)
+    a = GPTModel(_tiny_mla_config(q_lora_rank=q_rank))
+    b = GPTModel(_tiny_mla_config(q_lora_rank=q_rank, mla_qkv_concat=False))
+    attn = b.decoder.layers[0].self_attention
+    assert isinstance(attn, MLASelfAttentionMegatron)
+    names = {n for n, _ in b.named_parameters()}
+    want = ["linear_kv_down_proj.weight", "linear_kv_up_proj.weight", "kv_layernorm.weight", "linear_proj.weight"]
+    want += ["linear_q_down_proj.weight", "linear_q_up_proj.weight", "q_layernorm.weight"] if q_rank else ["linear_q_proj.weight"]
+    for w in want:
+        assert f"decoder.layers.0.self_attention.{w}" in names, w
+    assert not any("linear_qkv" in n or "linear_kvb" in n or ".k_layernorm" in n for n in names)
+    per_proj = unfuse_state_dict(a.state_dict(), a.config)
+    fused_for_b = fuse_state_dict(per_proj, b.config)
+    missing, unexpected = b.load_state_dict(fused_for_b, strict=False)
+    assert not [m for m in missing if "rotary" not in m] and not unexpected, (missing, unexpected)
+    ids = torch.randint(0, 512, (2, 33))
+    la = a(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+    lb = b(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+    assert torch.allclose(la, lb, atol=1e-5)
+    la.backward(), lb.backward()
+    ga = a.decoder.layers[1].self_attention.linear_kvb.weight.grad
+    gb = b.decoder.layers[1].self_attention.linear_kv_up_proj.weight.grad
+    assert torch.allclose(ga, gb, atol=1e-5)
+    # and back: the per-projection model's own state dict fuses into the concatenated layout
+    back = fuse_state_dict(b.state_dict(), a.config)
+    assert set(back) == set(a.state_dict())
+
+
+def test_cross_attention_matches_an_fp32_reference():
+    """Queries from the decoder states, keys / values from an encoder sequence of another length; no mask."""
+    from mindformers_b200.parallel.layers.attention import AttnMeta, CrossAttention
+    torch.manual_seed(22)
+    cfg = tiny_llama_config(hidden_size=64, num_attention_heads=4, num_query_groups=4, add_qkv_bias=True)
+    ca = CrossAttention(cfg)
+    names = {n for n, _ in ca.named_parameters()}
+    assert {"linear_q.weight", "linear_kv.weight", "linear_proj.weight", "linear_q.bias", "linear_kv.bias"} <= names
+    assert ca.linear_kv.weight.shape == (128, 64)
+    B, Sq, Sk, H, nh, hd = 2, 5, 9, 64, 4, 16
+    x = torch.randn(B * Sq, H, requires_grad=True)
+    mem = torch.randn(B * Sk, H)
+    out, _ = ca(x, mem, AttnMeta(batch=B, seq_len=Sq))
+    q = (x @ ca.linear_q.weight.t() + ca.linear_q.bias).view(B, Sq, nh, hd).transpose(1, 2)
+    kv = mem @ ca.linear_kv.weight.t() + ca.linear_kv.bias
+    k = kv[:, :H].reshape(B, Sk, nh, hd).transpose(1, 2)
+    v = kv[:, H:].reshape(B, Sk, nh, hd).transpose(1, 2)
+    p = torch.softmax(q @ k.transpose(-1, -2) / hd ** 0.5, dim=-1)
+    ref = (p @ v).transpose(1, 2).reshape(B * Sq, H) @ ca.linear_proj.weight.t()
+    assert torch.allclose(out, ref, atol=1e-5)
+    out.sum().backward()
+    assert x.grad is not None and ca.linear_kv.weight.grad.abs().sum() > 0
+    with pytest.raises(ValueError):
+        CrossAttention(tiny_llama_config(hidden_size=64, num_attention_heads=4, num_query_groups=2))
+
+
+def test_legacy_llama_emits_and_takes_the_legacy_parameter_names(tmp_path):
+    """Built from legacy keys (``num_heads``, ``n_kv_heads``, ``multiple_of``), it lists its weights as
+    ``model.layers.N.attention.wq`` … (views of the fused tensors), loads such a dict (also through the checkpoint
+    reader, and in the ``qkv_concat`` spelling) and then computes what the source model computes."""
+    from safetensors.torch import save_file
+    from mindformers_b200.checkpoint.io import load_checkpoint
+    from mindformers_b200.models import LegacyLlamaForCausalLM, LlamaLegacyConfig
+    from mindformers_b200.models.llama_legacy import legacy_ffn_hidden_size
+    assert legacy_ffn_hidden_size(4096, None, 256, None) == 11008           # Llama-2 7B
+    assert legacy_ffn_hidden_size(4096, None, 1024, 1.3) == 14336           # Llama-3 8B
+    torch.manual_seed(23)
+    kw = dict(num_layers=2, num_heads=4, n_kv_heads=2, hidden_size=64, multiple_of=32, vocab_size=256, seq_length=32,
+              params_dtype="float32")
+    src = LegacyLlamaForCausalLM(LlamaLegacyConfig(**kw), device="cpu").eval()
+    assert src.config.ffn_hidden_size == 192 and src.config.num_query_groups == 2
+    sd = src.state_dict()
+    for k in ("model.tok_embeddings.embedding_weight", "model.layers.1.attention.wq.weight",
+              "model.layers.1.attention.wk.weight", "model.layers.0.attention.wo.weight",
+              "model.layers.0.feed_forward.w1.weight", "model.layers.0.feed_forward.w2.weight",
+              "model.layers.0.feed_forward.w3.weight", "model.layers.0.attention_norm.weight",
+              "model.layers.0.ffn_norm.weight", "model.norm_out.weight", "lm_head.weight"):
+        assert k in sd, (k, sorted(sd)[:12])
+    assert sd["model.layers.1.attention.wk.weight"].shape == (32, 64)
+    fused = src.model.decoder.layers[1].self_attention.linear_qkv.weight
+    assert sd["model.layers.1.attention.wq.weight"].data_ptr() == fused.data_ptr()          # a view, not a copy
+    ids = torch.randint(0, 256, (2, 16))
+    with torch.no_grad():
+        want = src(ids)
+    dst = LegacyLlamaForCausalLM(LlamaLegacyConfig(**kw), device="cpu").eval()
+    dst.load_state_dict({k: v.clone() for k, v in sd.items()})
+    with torch.no_grad():
+        assert torch.equal(dst(ids), want)
+    # the fused legacy spelling (qkv_concat) and the generic checkpoint reader
+    cat = LegacyLlamaForCausalLM(LlamaLegacyConfig(qkv_concat=True, **kw), device="cpu").eval()
+    cat.load_state_dict({k: v.clone() for k, v in sd.items()})
+    sd_cat = cat.state_dict()
+    assert "model.layers.0.attention.w_qkv.weight" in sd_cat and "model.layers.0.feed_forward.w_gate_hidden.weight" in sd_cat
+    assert not any(".attention.wq." in k for k in sd_cat)
+    save_file({k: v.contiguous() for k, v in sd_cat.items()}, str(tmp_path / "legacy.safetensors"))
+    plain = GPTModel(tiny_llama_config(num_layers=2, num_attention_heads=4, num_query_groups=2, hidden_size=64,
+                                       ffn_hidden_size=192, vocab_size=256, seq_length=32)).eval()
+    load_checkpoint(plain, str(tmp_path / "legacy.safetensors"), strict=True)
+    with torch.no_grad():
+        assert torch.allclose(plain(ids), want, atol=1e-6)
+
+
+def _chatglm_reference_forward(sd, ids, nh, nkv, hd, eps, base):
+    """ChatGLM / GLM-4 forward written from the published architecture: fused query_key_value with bias, rotary on the
+    first half of each head over adjacent pairs, grouped KV heads, RMSNorm, SwiGLU from one fused projection."""
+    B, S = ids.shape
+    x = sd["transformer.embedding.word_embeddings.weight"][ids]
+    rot = hd // 2
+    theta = 1.0 / (base ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    ang = torch.outer(torch.arange(S, dtype=torch.float32), theta)              # [S, rot/2]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+
+    def rope(t):                                                                # t [B, S, h, hd]
+        r, p = t[..., :rot], t[..., rot:]
+        r = r.reshape(*r.shape[:-1], rot // 2, 2)
+        a, b = r[..., 0], r[..., 1]
+        out = torch.stack((a * cos - b * sin, b * cos + a * sin), dim=-1).flatten(-2)
+        return torch.cat((out, p), dim=-1)
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    n_layers = 1 + max(int(k.split(".")[3]) for k in sd if k.startswith("transformer.encoder.layers."))
+    for i in range(n_layers):
+        pre = f"transformer.encoder.layers.{i}."
+        h = rms(x, sd[pre + "input_layernorm.weight"])
+        qkv = h @ sd[pre + "self_attention.query_key_value.weight"].t() + sd[pre + "self_attention.query_key_value.bias"]
+        q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+        q, k, v = q.view(B, S, nh, hd), k.view(B, S, nkv, hd), v.view(B, S, nkv, hd)
+        q, k = rope(q), rope(k)
+        k, v = (t.repeat_interleave(nh // nkv, dim=2) for t in (k, v))
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / hd ** 0.5
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+        o = torch.einsum("bhqk,bkhd->bqhd", s.softmax(-1), v).reshape(B, S, nh * hd)
+        x = x + o @ sd[pre + "self_attention.dense.weight"].t()
+        h = rms(x, sd[pre + "post_attention_layernorm.weight"])
+        gate, up = (h @ sd[pre + "mlp.dense_h_to_4h.weight"].t()).chunk(2, dim=-1)
+        x = x + (torch.nn.functional.silu(gate) * up) @ sd[pre + "mlp.dense_4h_to_h.weight"].t()
+    x = rms(x, sd["transformer.encoder.final_layernorm.weight"])
+    return x @ sd["transformer.output_layer.weight"].t()
+
+
+def test_glm4_checkpoint_loads_and_reproduces_the_published_architecture(tmp_path):
+    """A checkpoint with GLM-4's own key names and tensor layouts, written as a pretrained directory, loads into
+    ``ChatGLM2ForConditionalGeneration``; the logits equal an independent forward of the GLM architecture (partial,
+    pair-wise rotary embedding, QKV bias, 2 KV groups), and saving with the family's names gives the tensors back."""
+    import json
+    from safetensors.torch import save_file
+    from mindformers_b200.checkpoint import name_maps
+    from mindformers_b200.models import ChatGLM2Config, ChatGLM2ForConditionalGeneration
+    torch.manual_seed(24)
+    H, F, nh, nkv, hd, V, L = 64, 96, 4, 2, 16, 128, 2
+    sd = {"transformer.embedding.word_embeddings.weight": torch.randn(V, H) * 0.1,
+          "transformer.encoder.final_layernorm.weight": 1 + 0.1 * torch.randn(H),
+          "transformer.output_layer.weight": torch.randn(V, H) * 0.1,
+          "transformer.rotary_pos_emb.inv_freq": torch.zeros(hd // 4)}
+    for i in range(L):
+        pre = f"transformer.encoder.layers.{i}."
+        sd[pre + "input_layernorm.weight"] = 1 + 0.1 * torch.randn(H)
+        sd[pre + "post_attention_layernorm.weight"] = 1 + 0.1 * torch.randn(H)
+        sd[pre + "self_attention.query_key_value.weight"] = torch.randn((nh + 2 * nkv) * hd, H) * 0.1
+        sd[pre + "self_attention.query_key_value.bias"] = torch.randn((nh + 2 * nkv) * hd) * 0.1
+        sd[pre + "self_attention.dense.weight"] = torch.randn(H, nh * hd) * 0.1
+        sd[pre + "mlp.dense_h_to_4h.weight"] = torch.randn(2 * F, H) * 0.1
+        sd[pre + "mlp.dense_4h_to_h.weight"] = torch.randn(H, F) * 0.1
+    cfg_json = dict(model_type="chatglm", num_layers=L, padded_vocab_size=V, hidden_size=H, ffn_hidden_size=F,
+                    kv_channels=hd, num_attention_heads=nh, multi_query_attention=True, multi_query_group_num=nkv,
+                    seq_length=32, layernorm_epsilon=1e-5, rope_ratio=50.0, rmsnorm=True, add_qkv_bias=True,
+                    add_bias_linear=False, torch_dtype="float32", post_layer_norm=True,
+                    apply_query_key_layer_scaling=True)
+    d = tmp_path / "glm4"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg_json))
+    save_file(sd, str(d / "model.safetensors"))
+    model = ChatGLM2ForConditionalGeneration.from_pretrained(str(d), strict=True, device="cpu").eval()
+    c = model.config
+    assert (c.num_query_groups, c.rotary_percent, c.rotary_interleaved, c.add_qkv_bias, c.add_bias_linear) == \
+        (nkv, 0.5, True, True, False)
+    assert c.rotary_base == 500000.0 and c.vocab_size == V and c.normalization == "RMSNorm"
+    ids = torch.randint(0, V, (2, 24))
+    with torch.no_grad():
+        got = model(ids)
+    ref = _chatglm_reference_forward(sd, ids, nh, nkv, hd, 1e-5, 500000.0)
+    got = got.reshape(ref.shape)
+    assert torch.allclose(got, ref, atol=2e-5), (got - ref).abs().max()
+    back = name_maps.framework_to_hf(dict(model.named_parameters()), model.config, "glm")
+    assert set(back) == set(sd) - {"transformer.rotary_pos_emb.inv_freq"}
+    for k, v in back.items():
+        assert torch.equal(v, sd[k]), k
+    assert ChatGLM2Config().to_transformer_dict()["multi_query_group_num"] == 2
