@@ -682,11 +682,31 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA,      // COMM 1: own chun
         for (int item = blockIdx.x; item < items; item += gridDim.x) {
           const int rb = item / kCopySlices, sl = item - rb * kCopySlices;
           const int row0 = rb * kTpBM + sl * rows_per_item;          // row inside the chunk
-          const long long total = static_cast<long long>(rows_per_item) * vec_per_row;
-          for (long long i = ct; i < total; i += 128) {
-            const int r = static_cast<int>(i / vec_per_row), cv = static_cast<int>(i - static_cast<long long>(r) * vec_per_row);
-            const uint4 v = ld_cg_v4(src + static_cast<size_t>(row0 + r) * args.lda + cv * 8);
-            *reinterpret_cast<uint4*>(args.a_full + (static_cast<size_t>(p) * args.rows_per_chunk + row0 + r) * args.K + cv * 8) = v;
+          const int total = rows_per_item * vec_per_row;
+          // A load over NVLink takes a few microseconds to come back; with one load in flight per thread the link
+          // idles (about 150 GB/s for the whole GPU). Eight independent loads per thread before the first store keep
+          // 2.4 MB in flight over the 148 CTAs, which covers the round trip at the link's rate.
+          constexpr int kInFlight = 8;
+          const __nv_bfloat16* src_rows = src + static_cast<size_t>(row0) * args.lda;
+          __nv_bfloat16* dst_rows = args.a_full + (static_cast<size_t>(p) * args.rows_per_chunk + row0) * args.K;
+          for (int base = ct; base < total; base += 128 * kInFlight) {
+            uint4 v[kInFlight];
+#pragma unroll
+            for (int j = 0; j < kInFlight; ++j) {
+              const int i = base + j * 128;
+              if (i < total) {
+                const int r = i / vec_per_row, cv = i - r * vec_per_row;
+                v[j] = ld_cg_v4(src_rows + static_cast<size_t>(r) * args.lda + cv * 8);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < kInFlight; ++j) {
+              const int i = base + j * 128;
+              if (i < total) {
+                const int r = i / vec_per_row, cv = i - r * vec_per_row;
+                *reinterpret_cast<uint4*>(dst_rows + static_cast<size_t>(r) * args.K + cv * 8) = v[j];
+              }
+            }
           }
           if (p != args.rank) {
             __threadfence();

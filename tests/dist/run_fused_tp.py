@@ -168,6 +168,18 @@ def main():
             row["nccl_cublas_ms"] = timeit(lambda: M.reduce_scatter_first_dim(torch.matmul(x4, w4 if bmn else w4.t()), grp, tp))
             row["gemm_only_ms"] = timeit(lambda: Fn.gemm(x4, w4, b_mn=bmn))
             res[f"bench_{tag}"] = row
+        # all-gather -> GEMM where the GEMM is short against the transfer: the QKV projection and the two input-gradient
+        # GEMMs behind a row-parallel layer (gathered output gradient times the weight)
+        for tag, K5, N5, bmn in (("ag_qkv", 4096, 6144 // tp, False), ("ag_proj_dgrad", 4096, 4096 // tp, True),
+                                 ("ag_fc2_dgrad", 4096, 14336 // tp, True)):
+            x5 = torch.randn(T // tp, K5, device="cuda").to(torch.bfloat16)
+            w5 = (torch.randn((K5, N5) if bmn else (N5, K5), device="cuda") * 0.05).to(torch.bfloat16)
+            x5_full = torch.empty(T, K5, device="cuda", dtype=torch.bfloat16)
+            res[f"bench_{tag}"] = {
+                "fused_ms": timeit(lambda: fused_tp.allgather_gemm(x5, w5, b_mn=bmn)),
+                "nccl_cublas_ms": timeit(lambda: torch.matmul(M.all_gather_first_dim(x5, grp, tp), w5 if bmn else w5.t())),
+                "gemm_only_ms": timeit(lambda: Fn.gemm(x5_full, w5, b_mn=bmn)),
+                "bytes_over_nvlink": (T - T // tp) * K5 * 2, "nvlink_floor_ms": (T - T // tp) * K5 * 2 / 770e9 * 1e3}
         lib.mfb_tp_set_rs_interleave(0)
         res["bench_rs_fc2"]["chunk_order_ms"] = timeit(lambda: fused_tp.gemm_reduce_scatter(x2, w2))
         lib.mfb_tp_set_rs_interleave(1)
