@@ -367,27 +367,47 @@ moe_gather_kernel(MoeMoveArgs a, __nv_bfloat16* __restrict__ out, const __nv_bfl
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); gv[2 * i] = f.x; gv[2 * i + 1] = f.y; }
       }
-      for (int j = 0; j < a.k; ++j) {
-        const long long c = t * a.k + j;
-        const int row = a.dest_row[c];
-        float dot = 0.f;
-        const int owner = (int)a.ids[c] / a.E_local;
-        if (row >= 0 && owner >= 0 && owner < a.world && v < vecs) {
-          const uint4 q = moe_ld_cg(a.buf_peer[owner] + (long long)row * a.H + 8 * v);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-          const float w = a.weights ? a.weights[c] : 1.f;
+      // the k rows of a token sit on up to k peers: four loads in flight before the first is used, since one peer
+      // load takes microseconds to return
+      for (int j0 = 0; j0 < a.k; j0 += 4) {
+        uint4 q4[4];
+        bool have[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(h[i]);
-            acc[2 * i] += w * f.x;
-            acc[2 * i + 1] += w * f.y;
-            if (g) dot += gv[2 * i] * f.x + gv[2 * i + 1] * f.y;
+        for (int u = 0; u < 4; ++u) {
+          have[u] = false;
+          const int j = j0 + u;
+          if (j < a.k) {
+            const long long c = t * a.k + j;
+            const int row = a.dest_row[c];
+            const int owner = (int)a.ids[c] / a.E_local;
+            if (row >= 0 && owner >= 0 && owner < a.world && v < vecs) {
+              q4[u] = moe_ld_cg(a.buf_peer[owner] + (long long)row * a.H + 8 * v);
+              have[u] = true;
+            }
           }
         }
-        if (g) {
-          dot = warp_sum(dot);
-          if (lane == 0) {
-            if (v0 == 0) dots[c] = dot; else dots[c] += dot;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u;
+          if (j >= a.k) break;
+          const long long c = t * a.k + j;
+          float dot = 0.f;
+          if (have[u]) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q4[u]);
+            const float w = a.weights ? a.weights[c] : 1.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(h[i]);
+              acc[2 * i] += w * f.x;
+              acc[2 * i + 1] += w * f.y;
+              if (g) dot += gv[2 * i] * f.x + gv[2 * i + 1] * f.y;
+            }
+          }
+          if (g) {
+            dot = warp_sum(dot);
+            if (lane == 0) {
+              if (v0 == 0) dots[c] = dot; else dots[c] += dot;
+            }
           }
         }
       }

@@ -206,15 +206,35 @@ class GroupedMLP(nn.Module):
         # model does not depend on the expert-parallel size
         ep, ep_rank = ps.get_expert_model_parallel_world_size(), ps.get_expert_model_parallel_rank()
         lo, hi = ep_rank * self.E, (ep_rank + 1) * self.E
+        # expert tensor parallelism: every expert's FFN width is split over the expert-tensor-parallel ranks (gate and
+        # up halves separately); the dispatcher gathers the rows of those ranks before the experts and reduce-scatters
+        # the partial outputs after (reference ``modules/transformer/moev3.py:758-850``)
+        etp, er = ps.get_expert_tensor_parallel_world_size(), ps.get_expert_tensor_parallel_rank()
+        if etp > 1 and F_ % etp:
+            raise ValueError(f"moe_ffn_hidden_size {F_} is not divisible by the expert tensor parallel size {etp}")
+        self.etp = etp
+        Fl = F_ // etp
         w1 = torch.empty(self.E * ep, H, 2 * F_, dtype=torch.float32, device=dev).normal_(0.0, config.init_method_std)
-        self.weight1 = nn.Parameter(w1[lo:hi].to(config.params_dtype).contiguous())
+        w1 = w1[lo:hi]
+        if etp > 1:
+            w1 = torch.cat((w1[..., er * Fl:(er + 1) * Fl], w1[..., F_ + er * Fl:F_ + (er + 1) * Fl]), dim=-1)
+        self.weight1 = nn.Parameter(w1.to(config.params_dtype).contiguous())
         del w1
         w2 = torch.empty(self.E * ep, F_, H, dtype=torch.float32, device=dev).normal_(0.0, config.output_layer_init_std)
-        self.weight2 = nn.Parameter(w2[lo:hi].to(config.params_dtype).contiguous())
+        w2 = w2[lo:hi]
+        if etp > 1:
+            w2 = w2[:, er * Fl:(er + 1) * Fl]
+        self.weight2 = nn.Parameter(w2.to(config.params_dtype).contiguous())
         del w2
         for p in (self.weight1, self.weight2):
             p.allreduce = False          # reduced over the expert-data-parallel group only
             p.is_expert = True
+        if etp > 1:
+            self.weight1.tensor_model_parallel, self.weight1.partition_dim = True, 2
+            self.weight1.partition_sections = (F_, F_)
+            self.weight2.tensor_model_parallel, self.weight2.partition_dim = True, 1
+            for p in (self.weight1, self.weight2):
+                p.partition_stride = 1
 
     w1_fp8 = w2_fp8 = w1_scale_inv = w2_scale_inv = None
 
@@ -337,7 +357,20 @@ class MoELayer(nn.Module):
         self.experts = sub.get("experts", GroupedMLP)(config, config.num_moe_experts // ep)
         self.shared_experts = (sub.get("shared_experts", SharedExpertMLP)(config)
                                if config.moe_shared_expert_intermediate_size else None)
-        self.dispatcher = MoEAlltoAllTokenDispatcher(config)
+        # the plain all-to-all dispatcher is the default; the all-gather and two-level ("deredundency") dispatchers,
+        # safe-token padding and tensor-parallel experts go through the staged dispatcher
+        kind = getattr(config, "moe_token_dispatcher_type", "alltoall") or "alltoall"
+        if getattr(config, "use_allgather_dispatcher", False):
+            kind = "allgather"
+        if getattr(config, "enable_deredundency", False):
+            kind = "deredundency"
+        self.expert_tp = getattr(self.experts, "etp", 1) > 1
+        self.staged = kind != "alltoall" or self.expert_tp or bool(getattr(config, "use_pad_tokens", False))
+        if self.staged:
+            from .moe_dispatchers import StagedTokenDispatcher
+            self.dispatcher = StagedTokenDispatcher(config, kind, expert_tp=self.expert_tp)
+        else:
+            self.dispatcher = MoEAlltoAllTokenDispatcher(config)
 
     def _tp_sliced(self, hidden):
         """Tensor-parallel attention + expert-parallel MoE without sequence parallelism (the inference layout of the
@@ -360,7 +393,7 @@ class MoELayer(nn.Module):
 
     def forward(self, hidden):
         cfg = self.config
-        if (ps.get_tensor_model_parallel_world_size() > 1 and not cfg.sequence_parallel
+        if (ps.get_tensor_model_parallel_world_size() > 1 and not cfg.sequence_parallel and not self.expert_tp
                 and ps.get_expert_model_parallel_world_size() > 1 and not torch.is_grad_enabled()):
             return self._tp_sliced(hidden)
         return self._forward_local(hidden)
@@ -368,7 +401,7 @@ class MoELayer(nn.Module):
     def _forward_local(self, hidden, with_shared: bool = True):
         probs, ids, aux = self.router(hidden)
         from .. import fused_comm
-        if fused_comm.moe_enabled(self.config, hidden):
+        if not self.staged and fused_comm.moe_enabled(self.config, hidden):
             out = fused_comm.moe_dispatch_experts_combine(self, hidden, probs, ids)
         else:
             x, plan, ctx = self.dispatcher.dispatch(hidden, ids)

@@ -88,6 +88,8 @@ class ParallelState:
         self.sizes = dict(tp=1, cp=1, ep=1, dp=1, pp=1, etp=1, edp=1)
         self.virtual_pp_size: Optional[int] = None
         self.virtual_pp_rank: Optional[int] = None
+        self.rank_lists: Dict[str, list] = {}       # name -> the rank lists of every group of that kind in the job
+        self.subgroups: Dict[tuple, tuple] = {}
 
     def get(self, name: str) -> _Group:
         return self.groups.get(name) or _Group([self.rank])
@@ -144,6 +146,7 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
         "ep": expert.get_ranks("ep"), "etp": expert.get_ranks("tp"), "edp": expert.get_ranks("dp"),
         "etp_ep": expert.get_ranks("tp-ep"),
     }
+    st.rank_lists = {name: [list(r) for r in lists] for name, lists in plan.items()}
     for name, lists in plan.items():
         mine = None
         for ranks in lists:
@@ -154,6 +157,33 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, pipeline_mode
     st.groups["world"] = _Group(list(range(world)), dist.group.WORLD if world > 1 else None)
     st.initialized = True
     return st
+
+
+def split_group(name: str, inner: int):
+    """Two-level split of the groups called ``name``: ``inner`` consecutive members form an inner group (the ranks of one
+    node, say) and the members with the same position inside their inner group form an outer group. Returns
+    ``(inner_group, inner_ranks, outer_group, outer_ranks)`` for this rank; process-group handles are ``None`` for
+    single-member groups. Every rank of the job must call this with the same arguments (groups are created
+    collectively), and the result is cached."""
+    st = _STATE
+    key = (name, inner)
+    if key in st.subgroups:
+        return st.subgroups[key]
+    lists = st.rank_lists.get(name) or [[st.rank]]
+    mine = [None, [st.rank], None, [st.rank]]
+    for ranks in lists:
+        n = len(ranks)
+        if n % inner:
+            raise ValueError(f"group {name!r} of size {n} cannot be split into inner groups of {inner}")
+        inners = [ranks[i:i + inner] for i in range(0, n, inner)]
+        outers = [ranks[i::inner] for i in range(inner)]
+        for slot, groups in ((0, inners), (2, outers)):
+            for g in groups:
+                handle = _new_group(g) if (st.world_size > 1 and len(g) > 1) else None
+                if st.rank in g:
+                    mine[slot], mine[slot + 1] = handle, list(g)
+    st.subgroups[key] = tuple(mine)
+    return st.subgroups[key]
 
 
 def destroy_model_parallel():

@@ -201,6 +201,8 @@ class TransformerConfig(ModelParallelConfig):
     moe_apply_probs_on_input: bool = False
     moe_token_dispatcher_type: str = "alltoall"
     use_allgather_dispatcher: bool = False
+    enable_deredundency: bool = False       # two-level dispatch: all-gather across nodes, all-to-all inside a node
+    npu_nums_per_device: int = 1            # ranks per node for the two-level dispatch (the reference's key name)
     group_wise_a2a: bool = False
     moe_enable_deepep: bool = False
     moe_per_layer_logging: bool = False

@@ -279,3 +279,16 @@ def test_pipeline_schedule_has_no_communication_cycle(pp, v):
                     done_f.add((fwd_chunk(s.fwd, pp, v), s.fwd % pp + (s.fwd // (pp * v)) * pp))
                 if s.bwd is not None:
                     assert (bwd_chunk(s.bwd, pp, v), s.bwd % pp + (s.bwd // (pp * v)) * pp) in done_f
+
+
+@pytest.mark.parametrize("mode", ["ep", "etp"])
+def test_moe_dispatcher_variants_match_a_dense_loop_over_experts(mode):
+    """4 gloo ranks. ``ep``: expert parallel 4 with the all-to-all, all-gather and two-level (2 ranks per node)
+    dispatchers, each with and without safe tokens. ``etp``: tensor parallel 2 x expert parallel 2 with every expert's
+    FFN split over the tensor-parallel pair. Output, input gradient, expert-weight and router gradients equal those
+    of a dense loop over whole experts."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist", "run_moe_dispatchers.py"), "--mode", mode]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, (res.stdout[-2000:], res.stderr[-3000:])
