@@ -45,7 +45,8 @@ class GenerationMixin:
                                  mla_latent_dim=cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
         else:
             kvh = max(1, cfg.num_query_groups // tp)
-            ctx = KVCacheContext(n_layers, num_blocks, block_size, kvh, cfg.kv_channels, dtype, device)
+            ctx = KVCacheContext(n_layers, num_blocks, block_size, kvh, cfg.kv_channels, dtype, device,
+                                 kv_cache_dtype=getattr(cfg, "kv_cache_dtype", None))
         ctx.layer_offset = self.model.decoder.layer_ids[0] if self.model.decoder.layer_ids else 0
         tables = BlockTables(num_blocks, block_size, max_len)
         return ctx, tables

@@ -25,10 +25,25 @@ class KVCacheContext:
     tokens per sequence."""
 
     def __init__(self, num_layers: int, num_blocks: int, block_size: int, kv_heads: int, head_dim: int,
-                 dtype=torch.bfloat16, device="cuda", mla_latent_dim: Optional[int] = None):
+                 dtype=torch.bfloat16, device="cuda", mla_latent_dim: Optional[int] = None,
+                 kv_cache_dtype: Optional[str] = None):
+        """``kv_cache_dtype="int8"`` stores keys and values as int8 codes with one fp32 scale per token and KV head
+        (``key_scale`` / ``value_scale`` ``[num_blocks, block_size, kv_heads]``): half the bytes per cached token, read
+        back by the decode kernel and by prefill with history. Not available for the multi-latent cache."""
         self.num_layers, self.num_blocks, self.block_size = num_layers, num_blocks, block_size
         self.kv_heads, self.head_dim, self.mla_dim = kv_heads, head_dim, mla_latent_dim
-        if mla_latent_dim:
+        self.int8 = str(kv_cache_dtype or "").lower() in ("int8", "torch.int8")
+        self.key_scale = self.value_scale = None
+        self.compute_dtype = dtype
+        if self.int8 and mla_latent_dim:
+            raise ValueError("an int8 KV cache is not available for multi-latent attention")
+        if self.int8:
+            shape = (num_blocks, block_size, kv_heads, head_dim)
+            self.key_cache = [torch.zeros(shape, dtype=torch.int8, device=device) for _ in range(num_layers)]
+            self.value_cache = [torch.zeros(shape, dtype=torch.int8, device=device) for _ in range(num_layers)]
+            self.key_scale = [torch.ones(shape[:3], dtype=torch.float32, device=device) for _ in range(num_layers)]
+            self.value_scale = [torch.ones(shape[:3], dtype=torch.float32, device=device) for _ in range(num_layers)]
+        elif mla_latent_dim:
             self.key_cache = [torch.zeros(num_blocks, block_size, 1, mla_latent_dim, dtype=dtype, device=device)
                               for _ in range(num_layers)]
             self.value_cache = [None] * num_layers
@@ -64,6 +79,26 @@ def _write_cache(cache: KVCacheContext, layer: int, k: torch.Tensor, v: Optional
     T = k.shape[0]
     kc, vc = cache.key_cache[layer], cache.value_cache[layer]
     row = k.shape[1] * k.shape[2]
+    if getattr(cache, "int8", False):
+        ks, vs = cache.key_scale[layer], cache.value_scale[layer]
+        if k.is_cuda and k.dtype == torch.bfloat16 and k.stride(2) == 1 and k.stride(1) == k.shape[2] \
+                and v.stride(2) == 1 and v.stride(1) == v.shape[2]:
+            rc = _lib.get_lib().mfb_reshape_and_cache_int8(
+                k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(),
+                cache.slot_mapping.data_ptr(), T, k.shape[1], k.shape[2], k.stride(0), v.stride(0), _lib.stream_ptr())
+            _lib.check(rc, "mfb_reshape_and_cache_int8")
+            _lib.count_launch()
+            return
+        slots = cache.slot_mapping.long()
+        ok = slots >= 0
+        for src, dst, sc in ((k, kc, ks), (v, vc, vs)):
+            x = src.reshape(T, src.shape[1], src.shape[2])[ok].float()
+            amax = x.abs().amax(-1)
+            scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+            q = torch.round(x / scale.unsqueeze(-1)).clamp(-127, 127).to(torch.int8)
+            dst.view(-1, src.shape[1], src.shape[2])[slots[ok]] = q
+            sc.view(-1, src.shape[1])[slots[ok]] = scale
+        return
     if k.is_cuda and k.dtype == torch.bfloat16 and row % 8 == 0 and k.stride(2) == 1 and k.stride(1) == k.shape[2]:
         rc = _lib.get_lib().mfb_reshape_and_cache(k.data_ptr(), _lib.ptr(v), kc.data_ptr(), _lib.ptr(vc),
                                                   cache.slot_mapping.data_ptr(), T, row, k.stride(0),
@@ -78,10 +113,22 @@ def _write_cache(cache: KVCacheContext, layer: int, k: torch.Tensor, v: Optional
         vc.view(-1, row)[slots[ok]] = v.reshape(T, row)[ok].to(vc.dtype)
 
 
-def _gather(cache_t: torch.Tensor, table_row: torch.Tensor, n: int, block_size: int) -> torch.Tensor:
+def _gather(cache_t: torch.Tensor, table_row: torch.Tensor, n: int, block_size: int,
+            scale_t: Optional[torch.Tensor] = None, dtype=None) -> torch.Tensor:
+    """The first ``n`` cached rows of one sequence as a contiguous tensor (de-quantised when ``scale_t`` is given)."""
     nb = -(-n // block_size)
     blocks = table_row[:nb].long()
-    return cache_t[blocks].reshape(nb * block_size, *cache_t.shape[2:])[:n]
+    rows = cache_t[blocks].reshape(nb * block_size, *cache_t.shape[2:])[:n]
+    if scale_t is not None:
+        sc = scale_t[blocks].reshape(nb * block_size, -1)[:n]
+        rows = (rows.float() * sc.unsqueeze(-1)).to(dtype or torch.bfloat16)
+    return rows
+
+
+def _layer_scales(cache, layer):
+    if getattr(cache, "int8", False):
+        return cache.key_scale[layer], cache.value_scale[layer]
+    return None, None
 
 
 def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
@@ -103,17 +150,20 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
             scratch = getattr(cache, "_decode_scratch", None)
             if scratch is None or scratch.numel() * 4 < need:
                 scratch = cache._decode_scratch = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
-            rc = lib.mfb_paged_decode_attention(
+            ksc, vsc = _layer_scales(cache, layer)
+            rc = lib.mfb_paged_decode_attention_ex(
                 qc.data_ptr(), cache.key_cache[layer].data_ptr(), cache.value_cache[layer].data_ptr(),
+                _lib.ptr(ksc), _lib.ptr(vsc),
                 cache.block_tables.data_ptr(), cache.context_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), splits,
                 B, nq, nkv, hd, cache.block_size, max_blocks, float(scale), _lib.stream_ptr())
-            _lib.check(rc, "mfb_paged_decode_attention")
+            _lib.check(rc, "mfb_paged_decode_attention_ex")
             _lib.count_launch(2)
             return out.view(T, nq * hd)
         lens = cache.context_lens.tolist()
+        ksc, vsc = _layer_scales(cache, layer)
         for b in range(B):
-            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
-            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size, ksc, q.dtype)
+            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size, vsc, q.dtype)
             o = Fn.attention_reference(q[b:b + 1].unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), causal=False, scale=scale)
             out[b] = o[0, 0]
         return out.view(T, nq * hd)
@@ -128,8 +178,9 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
         if lens[b] == nq_tok:
             o = Fn.attention(q[a:e].unsqueeze(0), k[a:e].unsqueeze(0), v[a:e].unsqueeze(0), causal=True, scale=scale)
         else:
-            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
-            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size)
+            ksc, vsc = _layer_scales(cache, layer)
+            kk = _gather(cache.key_cache[layer], cache.block_tables[b], lens[b], cache.block_size, ksc, q.dtype)
+            vv = _gather(cache.value_cache[layer], cache.block_tables[b], lens[b], cache.block_size, vsc, q.dtype)
             o = Fn.attention_reference(q[a:e].unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), causal=True, scale=scale,
                                        q_offset=lens[b] - nq_tok)
         outs.append(o.reshape(nq_tok, nq * v.shape[-1]))

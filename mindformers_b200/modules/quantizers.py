@@ -123,16 +123,14 @@ class QuantLinear(nn.Module):
     def _matmul(self, x):
         if self.method == "fp8":
             return Fn.fp8_linear(x, self.qweight, self.scale)
+        if self.act_int8 and self.scale.shape[1] == 1 and self.smooth is not None:
+            return Fn.w8a8_linear(x, self.qweight, self.scale[:, 0], smooth=self.smooth)   # division fused into the quantiser
         if self.smooth is not None:
             x = x / self.smooth.to(x.dtype)
-        if self.act_int8:
-            # W8A8 with per-token dynamic activation scales; int32 accumulation emulated in fp32 (exact for |sum| < 2^24)
-            xs = x.float().abs().amax(-1, keepdim=True).clamp_min(1e-8) / 127.0
-            xq = torch.round(x.float() / xs).clamp(-128, 127)
-            groups = self.scale.shape[1]
-            if groups == 1:
-                y = (xq @ self.qweight.float().t()) * xs * self.scale.t()
-                return y.to(x.dtype)
+        if self.act_int8 and self.scale.shape[1] == 1:
+            # W8A8: per-token dynamic activation scales, per-channel weight scales, the product on the integer tensor
+            # cores with an int32 accumulator (the fp32 emulation that stood here was exact only for |sum| < 2^24)
+            return Fn.w8a8_linear(x, self.qweight, self.scale[:, 0])
         return F.linear(x, dequantize_weight(self.qweight, self.scale, x.dtype))
 
     def forward(self, x, *a, **kw):
@@ -252,4 +250,8 @@ class AutoQuantizer:
             skip = tuple(self.config.modules_to_not_convert or ("output_layer", "embedding", "router", "linear_kvb"))
             stats = quantize_model_fp8(model, skip=skip)
             return int(stats["linear"]) + int(stats["grouped"])
-        return quantize_model(model, self.config, act_stats)
+        n = quantize_model(model, self.config, act_stats)
+        kv = getattr(self.config, "kvcache_dtype", None)
+        if kv and getattr(model, "config", None) is not None:
+            model.config.kv_cache_dtype = str(kv)        # picked up when the generation code allocates the paged cache
+        return n

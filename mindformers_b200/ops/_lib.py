@@ -125,6 +125,11 @@ def _declare(lib):
     sig("mfb_cp_barrier", [I, I, I, I, P, P, P])
     sig("mfb_gemm_fp8_blockscaled", [P, P, P, P, L, P, I, I, I, L, L, L, I, I, P, P, P, P])
     sig("mfb_quant_act_1x128", [P, L, P, L, P, L, L, I, P])
+    sig("mfb_reshape_and_cache_int8", [P, P, P, P, P, P, P, L, I, I, L, L, P])
+    sig("mfb_gather_cache_int8", [P, P, P, P, P, I, I, I, I, I, I, P])
+    sig("mfb_paged_decode_attention_ex", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    sig("mfb_gemm_w8a8", [P, P, P, P, P, P, I, I, I, L, L, L, P, P])
+    sig("mfb_quant_act_int8", [P, L, P, L, P, P, L, I, P])
     # optional entry points (present once their source file is part of the build)
     for name, args in _OPTIONAL.items():
         if hasattr(lib, name):

@@ -9,6 +9,11 @@
 // (lanes split the head dimension, shuffle reduction), phase 2 accumulates P·V with one thread per output
 // dimension so that V rows are read coalesced. Online softmax keeps running (max, sum) per head.
 // The kernel is bandwidth-bound: its roofline is KV bytes / HBM bandwidth.
+//
+// int8 cache (kv_cache_dtype int8; reference utils/quantization_config.py kv-cache quantisation): rows are stored as
+// int8 with one fp32 scale per (token, KV head) in a side array [num_blocks, block_size, kv_heads]; the write kernel
+// quantises (absmax / 127), the decode kernel reads 8 bytes per lane instead of 16 and multiplies by the scale, so
+// the bytes per cached token halve.
 #include "common.cuh"
 
 namespace mfb {
@@ -35,6 +40,38 @@ __global__ void reshape_and_cache_kernel(const __nv_bfloat16* __restrict__ key, 
   }
 }
 
+// One warp per (token, head): scale = absmax / 127, codes = round(x / scale).
+__global__ void reshape_and_cache_int8_kernel(const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* __restrict__ value,
+                                              int8_t* __restrict__ key_cache, int8_t* __restrict__ value_cache,
+                                              float* __restrict__ key_scale, float* __restrict__ value_scale,
+                                              const int* __restrict__ slot_mapping, long long T, int heads, int hd,
+                                              long long k_stride, long long v_stride) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= T * heads) return;
+  const long long t = w / heads;
+  const int h = (int)(w - t * heads);
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* src = which == 0 ? key + t * k_stride + (long long)h * hd
+                                          : (value ? value + t * v_stride + (long long)h * hd : nullptr);
+    if (!src) break;
+    float m = 0.f;
+    for (int d = lane; d < hd; d += 32) m = fmaxf(m, fabsf(__bfloat162float(src[d])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float sc = m > 0.f ? m / 127.f : 1.f;
+    const float inv = 1.f / sc;
+    int8_t* dst = (which == 0 ? key_cache : value_cache) + ((long long)slot * heads + h) * hd;
+    for (int d = lane; d < hd; d += 32) {
+      int r = __float2int_rn(__bfloat162float(src[d]) * inv);
+      dst[d] = (int8_t)(r > 127 ? 127 : (r < -127 ? -127 : r));
+    }
+    if (lane == 0) (which == 0 ? key_scale : value_scale)[(long long)slot * heads + h] = sc;
+  }
+}
+
 constexpr int kPaMaxGroup = 16;
 constexpr int kPaWarps = 4;
 constexpr int kPaHeadsPerPass = 4;   // query heads kept in registers at a time
@@ -46,10 +83,11 @@ constexpr int kPaHeadsPerPass = 4;   // query heads kept in registers at a time
 //   (max, sum) and the output slice of its 8 dimensions for up to four query heads. Lane groups never synchronise
 //   inside the loop: each keeps its own online softmax and the partial results are merged once, first inside the
 //   CTA through shared memory, then across splits by paged_combine_kernel.
-template <int HD>
+template <int HD, bool INT8>
 __global__ void __launch_bounds__(kPaWarps * 32)
 paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq, HD]
-                          const __nv_bfloat16* __restrict__ key_cache, const __nv_bfloat16* __restrict__ value_cache,
+                          const void* __restrict__ key_cache_v, const void* __restrict__ value_cache_v,
+                          const float* __restrict__ key_scale, const float* __restrict__ value_scale,   // INT8 only
                           const int* __restrict__ block_tables,        // [B, max_blocks]
                           const int* __restrict__ context_lens,        // [B]
                           float* __restrict__ part_acc,                // [B, Hq, splits, HD]
@@ -94,29 +132,49 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq,
     }
     // the trip count is the same for every lane of a warp (the shuffles below name all 32 lanes); a lane group
     // whose key lies beyond the end reads the last valid key and discards the result
-    auto fetch = [&](int t0, uint4& ku_, uint4& vu_) {
+    // a fetched key / value slice: 16 bytes of bf16, or 8 bytes of int8 codes (in .x, .y) and the row's scale
+    struct Slice { uint4 k, v; float ks, vs; };
+    auto fetch = [&](int t0, Slice& s_) {
       const int tk = (t0 + sub < k_end) ? t0 + sub : k_end - 1;
       const int blk = table[tk / block_size];
-      const size_t base = ((size_t)blk * block_size + tk % block_size) * row + (size_t)kvh * HD + dl * 8;
-      ku_ = *reinterpret_cast<const uint4*>(key_cache + base);
-      vu_ = *reinterpret_cast<const uint4*>(value_cache + base);
+      const size_t tok = (size_t)blk * block_size + tk % block_size;
+      const size_t base = tok * row + (size_t)kvh * HD + dl * 8;
+      if (INT8) {
+        const uint2 a = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(key_cache_v) + base);
+        const uint2 c = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(value_cache_v) + base);
+        s_.k = make_uint4(a.x, a.y, 0, 0);
+        s_.v = make_uint4(c.x, c.y, 0, 0);
+        s_.ks = key_scale[tok * Hkv + kvh];
+        s_.vs = value_scale[tok * Hkv + kvh];
+      } else {
+        s_.k = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(key_cache_v) + base);
+        s_.v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(value_cache_v) + base);
+      }
     };
     constexpr int DEPTH = 3;           // key rows in flight per lane group: hides HBM latency at 16 warps per SM
-    uint4 kq[DEPTH], vq[DEPTH];
+    Slice pipe[DEPTH];
     const int first = k_begin + warp * KPW;
 #pragma unroll
     for (int i = 0; i < DEPTH; ++i)
-      if (first + i * SLOTS < k_end) fetch(first + i * SLOTS, kq[i], vq[i]);
+      if (first + i * SLOTS < k_end) fetch(first + i * SLOTS, pipe[i]);
     for (int t0 = first; t0 < k_end; t0 += SLOTS) {
       const bool valid = t0 + sub < k_end;
-      const uint4 ku = kq[0], vu = vq[0];
+      const Slice cur = pipe[0];
 #pragma unroll
-      for (int i = 0; i + 1 < DEPTH; ++i) { kq[i] = kq[i + 1]; vq[i] = vq[i + 1]; }
-      if (t0 + DEPTH * SLOTS < k_end) fetch(t0 + DEPTH * SLOTS, kq[DEPTH - 1], vq[DEPTH - 1]);
+      for (int i = 0; i + 1 < DEPTH; ++i) pipe[i] = pipe[i + 1];
+      if (t0 + DEPTH * SLOTS < k_end) fetch(t0 + DEPTH * SLOTS, pipe[DEPTH - 1]);
       float kf[8], vf[8];
-      {
-        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&ku);
-        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vu);
+      if (INT8) {
+        const int8_t* kb = reinterpret_cast<const int8_t*>(&cur.k);
+        const int8_t* vb = reinterpret_cast<const int8_t*>(&cur.v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          kf[i] = static_cast<float>(kb[i]) * cur.ks;
+          vf[i] = static_cast<float>(vb[i]) * cur.vs;
+        }
+      } else {
+        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&cur.k);
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&cur.v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 a = __bfloat1622float2(k2[i]), c = __bfloat1622float2(v2[i]);
@@ -206,10 +264,52 @@ __global__ void gather_cache_kernel(const __nv_bfloat16* __restrict__ cache, con
   }
 }
 
+// The same gather out of an int8 cache, de-quantised to bf16: one warp per (token, head).
+__global__ void gather_cache_int8_kernel(const int8_t* __restrict__ cache, const float* __restrict__ scale,
+                                         const int* __restrict__ block_tables, const int* __restrict__ cu_lens,
+                                         __nv_bfloat16* __restrict__ out, int block_size, int max_blocks, int heads, int hd) {
+  const int b = blockIdx.y;
+  const int start = cu_lens[b], n = cu_lens[b + 1] - start;
+  const int lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < (long long)n * heads; w += warps) {
+    const int tok = (int)(w / heads), h = (int)(w - (long long)tok * heads);
+    const int blk = block_tables[(size_t)b * max_blocks + tok / block_size];
+    const size_t slot = (size_t)blk * block_size + tok % block_size;
+    const float sc = scale[slot * heads + h];
+    const int8_t* src = cache + (slot * heads + h) * hd;
+    __nv_bfloat16* dst = out + ((size_t)(start + tok) * heads + h) * hd;
+    for (int d = lane; d < hd; d += 32) dst[d] = __float2bfloat16(static_cast<float>(src[d]) * sc);
+  }
+}
+
 }  // namespace mfb
 
 extern "C" {
 using namespace mfb;
+
+// key / value [T, heads, hd] bf16 -> int8 caches [slots, heads, hd] + scales [slots, heads]
+int mfb_reshape_and_cache_int8(const void* key, const void* value, void* key_cache, void* value_cache, float* key_scale,
+                               float* value_scale, const int* slot_mapping, long long T, int heads, int hd,
+                               long long k_stride, long long v_stride, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long blocks = (T * heads * 32 + 255) / 256;
+  reshape_and_cache_int8_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+      (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, (int8_t*)key_cache, (int8_t*)value_cache, key_scale,
+      value_scale, slot_mapping, T, heads, hd, k_stride, v_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int mfb_gather_cache_int8(const void* cache, const float* scale, const int* block_tables, const int* cu_lens, void* out,
+                          int B, int max_len, int block_size, int max_blocks, int heads, int hd, cudaStream_t stream) {
+  if (B <= 0 || max_len <= 0) return 0;
+  long long per = ((long long)max_len * heads * 32 + 255) / 256;
+  if (per > 1024) per = 1024;
+  dim3 grid((unsigned)per, B);
+  gather_cache_int8_kernel<<<grid, 256, 0, stream>>>((const int8_t*)cache, scale, block_tables, cu_lens,
+                                                     (__nv_bfloat16*)out, block_size, max_blocks, heads, hd);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
 
 int mfb_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
                           const int* slot_mapping, long long T, int row_elems, long long k_stride, long long v_stride,
@@ -241,9 +341,11 @@ long long mfb_paged_decode_scratch_bytes(int B, int Hq, int hd, int splits) {
   return (long long)B * Hq * splits * (hd + 2) * 4;
 }
 
-int mfb_paged_decode_attention(const void* q, const void* key_cache, const void* value_cache, const int* block_tables,
-                               const int* context_lens, void* out, void* scratch, int splits, int B, int Hq, int Hkv,
-                               int hd, int block_size, int max_blocks, float scale, cudaStream_t stream) {
+// key_scale / value_scale non-null: the caches hold int8 codes with one fp32 scale per (slot, KV head).
+int mfb_paged_decode_attention_ex(const void* q, const void* key_cache, const void* value_cache, const float* key_scale,
+                                  const float* value_scale, const int* block_tables, const int* context_lens, void* out,
+                                  void* scratch, int splits, int B, int Hq, int Hkv, int hd, int block_size, int max_blocks,
+                                  float scale, cudaStream_t stream) {
   if (Hq % Hkv || Hq / Hkv > kPaMaxGroup || (hd != 128 && hd != 64) || splits < 1) {
     mfb_host::set_error("paged_decode_attention: unsupported Hq=%d Hkv=%d hd=%d splits=%d", Hq, Hkv, hd, splits);
     return 1;
@@ -255,18 +357,28 @@ int mfb_paged_decode_attention(const void* q, const void* key_cache, const void*
   float* part_acc = reinterpret_cast<float*>(scratch);
   float* part_ml = part_acc + (size_t)B * Hq * splits * hd;
   dim3 grid(splits, Hkv, B);
+  const bool i8 = key_scale != nullptr;
+  if (i8 && !value_scale) { mfb_host::set_error("paged_decode_attention: int8 cache needs both scale arrays"); return 1; }
+#define MFB_PA_LAUNCH(HD_, I8_)                                                                                       \
+  paged_decode_split_kernel<HD_, I8_><<<grid, kPaWarps * 32, 0, stream>>>(                                            \
+      (const __nv_bfloat16*)q, key_cache, value_cache, key_scale, value_scale, block_tables, context_lens, part_acc,  \
+      part_ml, Hq, Hkv, block_size, max_blocks, chunk, scale)
   if (hd == 128) {
-    paged_decode_split_kernel<128><<<grid, kPaWarps * 32, 0, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache, block_tables,
-        context_lens, part_acc, part_ml, Hq, Hkv, block_size, max_blocks, chunk, scale);
+    if (i8) MFB_PA_LAUNCH(128, true); else MFB_PA_LAUNCH(128, false);
     paged_combine_kernel<128><<<B * Hq, 128, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
   } else {
-    paged_decode_split_kernel<64><<<grid, kPaWarps * 32, 0, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache, block_tables,
-        context_lens, part_acc, part_ml, Hq, Hkv, block_size, max_blocks, chunk, scale);
+    if (i8) MFB_PA_LAUNCH(64, true); else MFB_PA_LAUNCH(64, false);
     paged_combine_kernel<64><<<B * Hq, 64, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
   }
+#undef MFB_PA_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int mfb_paged_decode_attention(const void* q, const void* key_cache, const void* value_cache, const int* block_tables,
+                               const int* context_lens, void* out, void* scratch, int splits, int B, int Hq, int Hkv,
+                               int hd, int block_size, int max_blocks, float scale, cudaStream_t stream) {
+  return mfb_paged_decode_attention_ex(q, key_cache, value_cache, nullptr, nullptr, block_tables, context_lens, out,
+                                       scratch, splits, B, Hq, Hkv, hd, block_size, max_blocks, scale, stream);
 }
 
 int mfb_gather_cache(const void* cache, const int* block_tables, const int* cu_lens, void* out, int B, int max_len,

@@ -789,6 +789,64 @@ def fp8_linear(x: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, bias: Option
 
 
 # =================================================================================================
+# W8A8: int8 activations x int8 weights on the integer tensor-core path
+# =================================================================================================
+def quantize_act_int8(x: torch.Tensor, smooth: Optional[torch.Tensor] = None):
+    """``x [T, K]`` → ``(int8 [T, K], scale fp32 [T])``: one scale per token, ``absmax / 127``; ``smooth [K]`` divides
+    the activations first (SmoothQuant)."""
+    T, K = x.shape
+    if _on_gpu(x) and x.dtype == torch.bfloat16:
+        x = x.contiguous()
+        q = torch.empty(T, K, dtype=torch.int8, device=x.device)
+        scale = torch.empty(T, dtype=torch.float32, device=x.device)
+        sm = smooth.float().contiguous() if smooth is not None else None
+        rc = _lib.get_lib().mfb_quant_act_int8(x.data_ptr(), x.stride(0), q.data_ptr(), K, scale.data_ptr(), _lib.ptr(sm),
+                                               T, K, _lib.stream_ptr())
+        _lib.check(rc, "mfb_quant_act_int8")
+        _lib.count_launch()
+        return q, scale
+    xf = x.float() / smooth.float() if smooth is not None else x.float()
+    amax = xf.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    q = torch.round(xf / scale.unsqueeze(-1)).clamp(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def w8a8_gemm(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor,
+              bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``bf16(sa[m] * sb[n] * (xq @ wq^T)[m, n] + bias[n])`` with ``xq [M, K]``, ``wq [N, K]`` int8, int32 accumulation."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    if _on_gpu(xq) and K % 16 == 0 and N % 8 == 0:
+        xq, wq = xq.contiguous(), wq.contiguous()
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+        b = bias.to(torch.bfloat16).contiguous() if bias is not None else None
+        st = _lib.status_word(xq.device)
+        rc = _lib.get_lib().mfb_gemm_w8a8(xq.data_ptr(), wq.data_ptr(), out.data_ptr(), sa.float().contiguous().data_ptr(),
+                                          sb.float().contiguous().data_ptr(), _lib.ptr(b), M, N, K, K, K, N,
+                                          st.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "mfb_gemm_w8a8")
+        _lib.count_launch()
+        return out
+    # integer matmul on the CPU, double on a GPU whose shape the kernel does not take: both exact
+    acc = (xq.double() @ wq.double().t()) if xq.is_cuda else (xq.to(torch.int64) @ wq.to(torch.int64).t())
+    y = acc.float() * sa.float().unsqueeze(-1) * sb.float().unsqueeze(0)
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(torch.bfloat16)
+
+
+def w8a8_linear(x: torch.Tensor, wq: torch.Tensor, sb: torch.Tensor, smooth: Optional[torch.Tensor] = None,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Linear layer on int8 weights with dynamically quantised int8 activations (per token)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    xq, sa = quantize_act_int8(x2.to(torch.bfloat16) if x2.is_cuda else x2, smooth)
+    y = w8a8_gemm(xq, sa, wq, sb.reshape(-1), bias)
+    return y.reshape(*shape[:-1], wq.shape[0]).to(x.dtype)
+
+
+# =================================================================================================
 # MoE router
 # =================================================================================================
 def router_topk_reference(logits, bias, k, sigmoid, norm, scale, groups=0, group_topk=0):

@@ -201,6 +201,7 @@ class TransformerConfig(ModelParallelConfig):
     moe_apply_probs_on_input: bool = False
     moe_token_dispatcher_type: str = "alltoall"
     use_allgather_dispatcher: bool = False
+    kv_cache_dtype: Optional[str] = None    # "int8": paged KV cache in int8 with per-token, per-head scales
     enable_deredundency: bool = False       # two-level dispatch: all-gather across nodes, all-to-all inside a node
     npu_nums_per_device: int = 1            # ranks per node for the two-level dispatch (the reference's key name)
     group_wise_a2a: bool = False

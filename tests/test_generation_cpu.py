@@ -205,3 +205,38 @@ def test_generate_runs_with_gradients_off():
     finally:
         hook.remove()
     assert seen and not any(seen)
+
+
+def test_int8_kv_cache_stores_codes_and_scales_and_tracks_the_bf16_cache():
+    """``kv_cache_dtype="int8"``: the paged cache holds int8 codes plus one scale per token and KV head; decode and
+    chunked prefill read it back. Logits stay within the quantisation error of the exact cache and a ``ptq``
+    quantisation config with ``kvcache_dtype: int8`` switches it on."""
+    from mindformers_b200.inference.paged_attention import KVCacheContext
+    model = _tiny()
+    prompts = [[5, 9, 33, 7, 100, 2, 8], [12, 250, 3]]
+
+    def prefill_then_one_decode_step():
+        ctx, tables = model._set_kv_cache(2, 16)
+        tables.init_cache_engine(2)
+        first = model._forward_step(prompts, [0, 0], ctx, tables, True)
+        nxt = [[int(r.argmax())] for r in first]
+        second = model._forward_step(nxt, [len(p) for p in prompts], ctx, tables, False)
+        tables.clear_cache()
+        return ctx, first.float(), second.float()
+
+    _, e1, e2 = prefill_then_one_decode_step()
+    model.config.kv_cache_dtype = "int8"
+    ctx, q1, q2 = prefill_then_one_decode_step()
+    assert isinstance(ctx, KVCacheContext) and ctx.int8 and ctx.key_cache[0].dtype == torch.int8
+    assert ctx.key_scale[0].shape == ctx.key_cache[0].shape[:3] and int(ctx.key_cache[0].abs().max()) == 127
+    assert torch.equal(e1, q1)                    # prefill attends to the new tokens themselves, not to the cache
+    worst, spread = (e2 - q2).abs().max().item(), e2.abs().max().item()
+    assert 0 < worst < 0.05 * spread, (worst, spread)          # decode reads the quantised cache: close, not equal
+    chunked = model.generate(prompts, max_new_tokens=5, do_sample=False, chunk_prefill_size=3)
+    assert [len(x) for x in chunked] == [len(p) + 5 for p in prompts]
+    # the quantiser's kvcache_dtype reaches the cache
+    model2 = _tiny()
+    model2.apply_quantization_config({"quant_method": "ptq", "kvcache_dtype": "int8"})
+    assert model2.config.kv_cache_dtype == "int8"
+    out = model2.generate(prompts, max_new_tokens=3, do_sample=False)
+    assert [len(x) for x in out] == [len(p) + 3 for p in prompts]

@@ -355,3 +355,23 @@ def test_quantization_config_of_a_pretrained_directory_is_applied(tmp_path, monk
     monkeypatch.setenv("RUN_MODE", "finetune")                        # training keeps full-precision layers
     t = AutoModel.from_pretrained(str(tmp_path / "m"), device="cpu")
     assert not any(isinstance(m, QuantLinear) for m in t.modules())
+
+
+def test_w8a8_linear_is_exact_integer_arithmetic_and_close_to_the_float_product():
+    """Per-token activation scales x per-channel weight scales around an exact integer product."""
+    from mindformers_b200.ops import functional as Fn
+    torch.manual_seed(31)
+    x = torch.randn(37, 96)
+    w = torch.randn(40, 96) * 0.1
+    wq, ws = Q.quantize_weight_rtn(w, "int8", 0)
+    xq, xs = Fn.quantize_act_int8(x)
+    assert xq.dtype == torch.int8 and xs.shape == (37,) and int(xq.abs().max()) == 127
+    y = Fn.w8a8_gemm(xq, xs, wq, ws[:, 0]).float()
+    exact = (xq.double() @ wq.double().t()).float() * xs[:, None] * ws[:, 0][None, :]
+    assert torch.allclose(y, exact.to(torch.bfloat16).float())
+    ref = x @ w.t()
+    assert ((y - ref).norm() / ref.norm()).item() < 0.03
+    smooth = torch.rand(96) + 0.5
+    y2 = Fn.w8a8_linear(x, Q.quantize_weight_rtn(w * smooth, "int8", 0)[0], Q.quantize_weight_rtn(w * smooth, "int8", 0)[1][:, 0],
+                        smooth=smooth)
+    assert ((y2.float() - ref).norm() / ref.norm()).item() < 0.03

@@ -645,3 +645,101 @@ def test_generate_with_cuda_graph_matches_eager(family):
     graphed = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None, use_cuda_graph=True)
     assert eager == graphed
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1024, 4096), (2048, 6144, 4096), (64, 520, 208), (4096, 4096, 14336)])
+def test_w8a8_gemm_matches_exact_integer_product(M, N, K):
+    """int8 x int8 on the integer tensor-core path with an int32 accumulator: the result is the exactly computed integer
+    product times the scales (plus bias), rounded to bf16 once; ragged M, N and K tails included."""
+    torch.manual_seed(M + N)
+    a = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+    sa = torch.rand(M, device="cuda") * 0.02 + 0.001
+    sb = torch.rand(N, device="cuda") * 0.02 + 0.001
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    for use_bias in (False, True):
+        y = Fn.w8a8_gemm(a, sa, b, sb, bias if use_bias else None)
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        acc = (a.double() @ b.double().t())                              # exact: |sum| < 2^53
+        ref = acc * sa.double()[:, None] * sb.double()[None, :]
+        if use_bias:
+            ref = ref + bias.double()
+        err = (y.double() - ref).abs().max().item()
+        assert err <= ref.abs().max().item() * 2 ** -8 + 1e-6, err        # one bf16 rounding
+
+
+def test_quantize_act_int8_and_w8a8_linear_against_fp32():
+    torch.manual_seed(77)
+    x = (torch.randn(1000, 4096, device="cuda") * 2).to(torch.bfloat16)
+    w = torch.randn(1024, 4096, device="cuda") * 0.05
+    smooth = torch.rand(4096, device="cuda") + 0.5
+    for sm in (None, smooth):
+        xq, xs = Fn.quantize_act_int8(x, sm)
+        xf = x.float() / sm if sm is not None else x.float()
+        amax = xf.abs().amax(-1)
+        assert torch.allclose(xs, amax / 127.0, rtol=1e-6)
+        ref_q = torch.round(xf / xs[:, None]).clamp(-127, 127)
+        assert (xq.float() - ref_q).abs().max().item() <= 1                # ties may round either way
+        assert ((xq.float() - ref_q).abs() > 0).float().mean().item() < 1e-3
+    from mindformers_b200.modules import quantizers as Q
+    wq, ws = Q.quantize_weight_rtn(w, "int8", 0)
+    y = Fn.w8a8_linear(x, wq, ws[:, 0])
+    ref = x.float() @ w.t()
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 0.02
+
+
+@pytest.mark.parametrize("hd,nq,nkv,block", [(128, 32, 8, 16), (64, 8, 2, 128), (128, 4, 4, 32)])
+def test_int8_kv_cache_write_decode_and_gather(hd, nq, nkv, block):
+    """Keys and values go into the int8 paged cache through the quantising write kernel; the decode kernel and the
+    de-quantising gather read them back. Reference: fp32 attention over the de-quantised cache contents."""
+    from mindformers_b200.inference.paged_attention import KVCacheContext, _write_cache
+    torch.manual_seed(hd + nq)
+    lib = _lib.get_lib()
+    lens = [1, 37, 700, 1300, 64]
+    B = len(lens)
+    max_blocks = (max(lens) + block - 1) // block + 1
+    nblocks = B * max_blocks + 3
+    cache = KVCacheContext(1, nblocks, block, nkv, hd, torch.bfloat16, "cuda", kv_cache_dtype="int8")
+    perm = torch.randperm(nblocks)[:B * max_blocks].to(torch.int32).view(B, max_blocks).cuda()
+    ks, vs, slots = [], [], []
+    for b, n in enumerate(lens):
+        ks.append((torch.randn(n, nkv, hd, device="cuda") * (0.2 + b)).to(torch.bfloat16))
+        vs.append((torch.randn(n, nkv, hd, device="cuda") * 0.5).to(torch.bfloat16))
+        t = torch.arange(n, device="cuda")
+        slots.append(perm[b].long()[t // block] * block + t % block)
+    k_all, v_all = torch.cat(ks), torch.cat(vs)
+    cache.slot_mapping = torch.cat(slots).to(torch.int32)
+    _write_cache(cache, 0, k_all, v_all)
+    torch.cuda.synchronize()
+    kc, vc = cache.key_cache[0], cache.value_cache[0]
+    sl = cache.slot_mapping.long()
+    kd = kc.view(-1, nkv, hd)[sl].float() * cache.key_scale[0].view(-1, nkv)[sl].unsqueeze(-1)
+    vd = vc.view(-1, nkv, hd)[sl].float() * cache.value_scale[0].view(-1, nkv)[sl].unsqueeze(-1)
+    # the stored codes reproduce the inputs to within half a quantisation step
+    step = k_all.float().abs().amax(-1, keepdim=True) / 127.0
+    assert ((kd - k_all.float()).abs() <= 0.51 * step + 1e-6).all()
+    assert int(kc.view(-1, nkv, hd)[sl].abs().max()) == 127
+    q = (torch.randn(B, nq, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    splits = lib.mfb_paged_decode_splits(B, nkv, block, max_blocks)
+    scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits) // 4, device="cuda")
+    rc = lib.mfb_paged_decode_attention_ex(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), cache.key_scale[0].data_ptr(),
+                                           cache.value_scale[0].data_ptr(), perm.data_ptr(), ctx.data_ptr(), out.data_ptr(),
+                                           scratch.data_ptr(), splits, B, nq, nkv, hd, block, max_blocks, hd ** -0.5,
+                                           _lib.stream_ptr())
+    _lib.check(rc, "paged decode int8")
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    gathered = torch.empty(sum(lens), nkv, hd, device="cuda", dtype=torch.bfloat16)
+    rc = lib.mfb_gather_cache_int8(kc.data_ptr(), cache.key_scale[0].data_ptr(), perm.data_ptr(), cu.data_ptr(),
+                                   gathered.data_ptr(), B, max(lens), block, max_blocks, nkv, hd, _lib.stream_ptr())
+    _lib.check(rc, "gather int8")
+    torch.cuda.synchronize()
+    assert torch.allclose(gathered.float(), kd.to(torch.bfloat16).float())
+    o = 0
+    for b, n in enumerate(lens):
+        ref = Fn.attention_reference(q[b:b + 1].unsqueeze(0).float(), kd[o:o + n].unsqueeze(0), vd[o:o + n].unsqueeze(0),
+                                     causal=False)
+        assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
+        o += n
