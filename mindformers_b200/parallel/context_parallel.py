@@ -8,6 +8,10 @@ Reference: the reference toggles these inside its FlashAttention primitive
 * ``p2p`` (ring): K/V blocks rotate around the ring while the local block computes; partial outputs are
   merged with their log-sum-exp.
 * ``a2a`` (Ulysses): sequence ↔ head all-to-all around a full-sequence attention.
+* ``a2a+p2p`` (hybrid): Ulysses inside groups of ``ulysses_degree_in_cp`` ranks, the ring across the groups.
+
+The ring and the hybrid live in ``ring_attention.py``. On a GPU ``p2p`` and ``all_gather`` take the fused peer-memory
+path (K/V pulled by peer loads into one buffer, O(S) memory) unless ``fused_cp_comm`` is off.
 """
 from __future__ import annotations
 
@@ -51,38 +55,6 @@ def _attn_with_lse(q, k, v, scale, causal, q_offset=0):
     p = torch.exp(s - lse.unsqueeze(-1))
     o = torch.matmul(p, vf)
     return o.permute(0, 2, 1, 3), lse.permute(0, 2, 1)  # [B,S,H,D], [B,S,H]
-
-
-def ring_attention(q, k, v, scale, group=None):
-    """Causal ring attention with contiguous sequence chunks: rank r holds tokens [r*S, (r+1)*S).
-    K/V travel around the ring; blocks from later ranks are skipped (fully masked)."""
-    group = group if group is not None else ps.get_context_parallel_group()
-    cp = ps.get_context_parallel_world_size()
-    r = ps.get_context_parallel_rank()
-    ranks = ps.get_group_ranks("cp")
-    out, lse = None, None
-    kv = torch.stack((k, v)).contiguous()
-    for step in range(cp):
-        src = (r - step) % cp
-        nxt = torch.empty_like(kv) if step < cp - 1 else None
-        reqs = []
-        if nxt is not None:
-            send_to, recv_from = ranks[(r + 1) % cp], ranks[(r - 1) % cp]
-            ops = [dist.P2POp(dist.isend, kv, send_to, group), dist.P2POp(dist.irecv, nxt, recv_from, group)]
-            reqs = dist.batch_isend_irecv(ops)
-        if src <= r:
-            o_b, lse_b = _attn_with_lse(q, kv[0], kv[1], scale, causal=(src == r))
-            if out is None:
-                out, lse = o_b, lse_b
-            else:
-                new_lse = torch.logaddexp(lse, lse_b)
-                out = out * torch.exp(lse - new_lse).unsqueeze(-1) + o_b * torch.exp(lse_b - new_lse).unsqueeze(-1)
-                lse = new_lse
-        for q_ in reqs:
-            q_.wait()
-        if nxt is not None:
-            kv = nxt
-    return out.to(q.dtype)
 
 
 class _UlyssesA2A(torch.autograd.Function):
@@ -156,94 +128,20 @@ def context_parallel_attention(q, k, v, scale, config):
             # K/V exchange by peer loads + rectangular flash attention (same result as the ring)
             return fused_cp.fused_cp_attention(q, k, v, scale, zigzag=bool(getattr(config, "cp_zigzag", False)))
     if kind == "p2p":
-        if torch.is_grad_enabled() and q.requires_grad:
-            return _RingAttnFn.apply(q, k, v, scale)
-        return ring_attention(q, k, v, scale)
+        # K/V blocks travel the ring under the compute, memory O(S / cp); zig-zag balances the causal work
+        from .ring_attention import ring_attention
+        return ring_attention(q, k, v, scale, zigzag=bool(getattr(config, "cp_zigzag", False)))
     if kind == "a2a":
         return ulysses_attention(q, k, v, scale)
+    if kind == "a2a+p2p":
+        from .ring_attention import hybrid_attention
+        if getattr(config, "cp_zigzag", False):
+            raise ValueError("a2a+p2p context parallelism uses contiguous sequence chunks: switch cp_zigzag off")
+        u = int(getattr(config, "ulysses_degree_in_cp", 0) or 0)
+        sizes = getattr(config, "hierarchical_context_parallel_sizes", None)
+        if not u and sizes:
+            u = int(sizes[0])
+        return hybrid_attention(q, k, v, scale, u or 1)
     if kind == "all_gather":
         return allgather_kv_attention(q, k, v, scale)
     raise NotImplementedError(f"cp_comm_type {kind!r}")
-
-
-class _RingAttnFn(torch.autograd.Function):
-    """Ring attention with a recompute-based backward: gradients of the local q and of every visited
-    K/V block are formed with the saved global log-sum-exp; dK/dV travel back with their block."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, scale):
-        cp, r = ps.get_context_parallel_world_size(), ps.get_context_parallel_rank()
-        group, ranks = ps.get_context_parallel_group(), ps.get_group_ranks("cp")
-        out, lse = None, None
-        kv = torch.stack((k, v)).contiguous()
-        for step in range(cp):
-            src = (r - step) % cp
-            nxt = torch.empty_like(kv) if step < cp - 1 else None
-            reqs = []
-            if nxt is not None:
-                ops = [dist.P2POp(dist.isend, kv, ranks[(r + 1) % cp], group),
-                       dist.P2POp(dist.irecv, nxt, ranks[(r - 1) % cp], group)]
-                reqs = dist.batch_isend_irecv(ops)
-            if src <= r:
-                o_b, lse_b = _attn_with_lse(q, kv[0], kv[1], scale, causal=(src == r))
-                if out is None:
-                    out, lse = o_b, lse_b
-                else:
-                    new_lse = torch.logaddexp(lse, lse_b)
-                    out = out * torch.exp(lse - new_lse).unsqueeze(-1) + o_b * torch.exp(lse_b - new_lse).unsqueeze(-1)
-                    lse = new_lse
-            for q_ in reqs:
-                q_.wait()
-            if nxt is not None:
-                kv = nxt
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.scale = scale
-        return out.to(q.dtype)
-
-    @staticmethod
-    def backward(ctx, dout):
-        q, k, v, out, lse = ctx.saved_tensors
-        scale = ctx.scale
-        cp, r = ps.get_context_parallel_world_size(), ps.get_context_parallel_rank()
-        group, ranks = ps.get_context_parallel_group(), ps.get_group_ranks("cp")
-        rep = q.shape[2] // k.shape[2]
-        do = dout.float().permute(0, 2, 1, 3)                      # [B,H,S,D]
-        qf = q.float().permute(0, 2, 1, 3)
-        delta = (do * out.permute(0, 2, 1, 3)).sum(-1)             # [B,H,S]
-        lse_h = lse.permute(0, 2, 1)
-        dq = torch.zeros_like(qf)
-        kv = torch.stack((k, v)).contiguous()
-        dkv = torch.zeros((2, *k.shape), dtype=torch.float32, device=k.device)
-        for step in range(cp):
-            src = (r - step) % cp
-            if src <= r:
-                kf = kv[0].float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
-                vf = kv[1].float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
-                s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-                if src == r:
-                    S = q.shape[1]
-                    mask = torch.ones(S, S, dtype=torch.bool, device=q.device).triu(1)
-                    s = s.masked_fill(mask, float("-inf"))
-                p = torch.exp(s - lse_h.unsqueeze(-1))
-                dv_b = torch.matmul(p.transpose(-1, -2), do)
-                dp = torch.matmul(do, vf.transpose(-1, -2))
-                ds = p * (dp - delta.unsqueeze(-1)) * scale
-                dq += torch.matmul(ds, kf)
-                dk_b = torch.matmul(ds.transpose(-1, -2), qf)
-                B, H, Sk, D = dk_b.shape
-                dk_b = dk_b.view(B, H // rep, rep, Sk, D).sum(2).permute(0, 2, 1, 3)
-                dv_b = dv_b.view(B, H // rep, rep, Sk, -1).sum(2).permute(0, 2, 1, 3)
-                dkv[0] += dk_b
-                dkv[1] += dv_b
-            # rotate the K/V block and its gradient accumulator together
-            if cp > 1:
-                nkv, ndkv = torch.empty_like(kv), torch.empty_like(dkv)
-                ops = [dist.P2POp(dist.isend, kv, ranks[(r + 1) % cp], group),
-                       dist.P2POp(dist.irecv, nkv, ranks[(r - 1) % cp], group),
-                       dist.P2POp(dist.isend, dkv, ranks[(r + 1) % cp], group),
-                       dist.P2POp(dist.irecv, ndkv, ranks[(r - 1) % cp], group)]
-                for q_ in dist.batch_isend_irecv(ops):
-                    q_.wait()
-                kv, dkv = nkv, ndkv
-        # after cp rotations every block (and its gradient) is back at its owner
-        return dq.permute(0, 2, 1, 3).to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None

@@ -50,6 +50,15 @@ def main():
                 "dv": rel(v.grad, cut(vr.grad))}
         res["zigzag" if zigzag else "contiguous"] = errs
         worst = max(worst, max(errs.values()))
+        # the ring: K/V blocks over NCCL send / recv under the flash kernels of the block at hand, memory O(S / cp)
+        from mindformers_b200.parallel.ring_attention import ring_attention
+        q2, k2, v2 = (cut(t).contiguous().requires_grad_() for t in (qf, kf, vf))
+        o2 = ring_attention(q2, k2, v2, 128 ** -0.5, zigzag=zigzag)
+        o2.backward(cut(gf).contiguous())
+        errs2 = {"o": rel(o2, cut(ref)), "dq": rel(q2.grad, cut(qr.grad)), "dk": rel(k2.grad, cut(kr.grad)),
+                 "dv": rel(v2.grad, cut(vr.grad))}
+        res["ring_zigzag" if zigzag else "ring_contiguous"] = errs2
+        worst = max(worst, max(errs2.values()))
     res["status"] = _lib.read_status()
     if args.bench:
         S, nq, nkv = args.bench_seq, 28, 4        # Qwen2.5-7B heads; S tokens per rank
@@ -80,7 +89,14 @@ def main():
         flops_total = 4 * St * St / 2 * 128 * nq * 3.5       # fwd + bwd (2.5x) causal, whole sequence
         kv_bytes = 2 * S * nkv * 128 * 2 * (world - 1)        # inbound K,V per gather (two gathers + one reduce-scatter)
         t_c, t_z = timeit(lambda: run(False)), timeit(lambda: run(True))
+        from mindformers_b200.parallel.ring_attention import ring_attention
+
+        def run_ring(zz):
+            o = ring_attention(q, k, v, 128 ** -0.5, zigzag=zz)
+            o.backward(g)
+        t_rc, t_rz = timeit(lambda: run_ring(False)), timeit(lambda: run_ring(True))
         res["bench"] = {"tokens_per_rank": S, "contiguous_ms": t_c, "zigzag_ms": t_z,
+                        "ring_contiguous_ms": t_rc, "ring_zigzag_ms": t_rz,
                         "attn_floor_ms_per_rank": flops_total / world / 1415.7e12 * 1e3,
                         "nvlink_floor_ms": 3 * kv_bytes / 770e9 * 1e3,
                         "zigzag_tflops_per_rank": flops_total / world / t_z / 1e9}

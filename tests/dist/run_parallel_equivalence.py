@@ -27,6 +27,8 @@ def main():
     ap.add_argument("--sp", type=int, default=0)
     ap.add_argument("--moe", type=int, default=0)
     ap.add_argument("--cp-type", default="all_gather")
+    ap.add_argument("--zigzag", type=int, default=0, help="rank r holds sequence chunks r and 2*cp-1-r")
+    ap.add_argument("--ulysses", type=int, default=1, help="ulysses_degree_in_cp of the a2a+p2p layout")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--kv-groups", type=int, default=2)
     ap.add_argument("--forward-only", type=int, default=0, help="no training: write the loss of one forward pass")
@@ -42,7 +44,8 @@ def main():
               vocab_size=256, seq_length=32, max_position_embeddings=32, params_dtype="float32",
               compute_dtype="float32", use_scaled_init=False, pad_token_id=-1,
               tensor_model_parallel_size=args.tp, sequence_parallel=bool(args.sp), context_parallel_size=args.cp,
-              expert_model_parallel_size=args.ep, cp_comm_type=args.cp_type if args.cp > 1 else None)
+              expert_model_parallel_size=args.ep, cp_comm_type=args.cp_type if args.cp > 1 else None,
+              cp_zigzag=bool(args.zigzag), ulysses_degree_in_cp=args.ulysses)
     if args.moe:
         kw.update(num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_aux_loss_coeff=1e-2,
                   expert_tensor_parallel_size=1)
@@ -76,8 +79,14 @@ def main():
     if args.cp > 1:
         cpr = ps.get_context_parallel_rank()
         S = inp.shape[1] // args.cp
-        pos = torch.arange(cpr * S, (cpr + 1) * S).unsqueeze(0).expand(per, S).contiguous()
-        inp, lab = inp[:, cpr * S:(cpr + 1) * S].contiguous(), lab[:, cpr * S:(cpr + 1) * S].contiguous()
+        if args.zigzag:
+            half = S // 2
+            idx = torch.cat((torch.arange(cpr * half, (cpr + 1) * half),
+                             torch.arange((2 * args.cp - 1 - cpr) * half, (2 * args.cp - cpr) * half)))
+        else:
+            idx = torch.arange(cpr * S, (cpr + 1) * S)
+        pos = idx.unsqueeze(0).expand(per, S).contiguous()
+        inp, lab = inp[:, idx].contiguous(), lab[:, idx].contiguous()
     losses = []
     for _ in range(args.steps):
         batch = {"input_ids": inp, "labels": lab}

@@ -77,6 +77,17 @@ def test_context_parallel(tmp_path, dense_ref, kind):
     _close(_run(tmp_path, 2, f"cp2_{kind}", "--cp", "2", "--cp-type", kind), dense_ref, 2e-5)
 
 
+@pytest.mark.parametrize("name,extra", [
+    ("ring4", ["--cp-type", "p2p"]),
+    ("ring4_zigzag", ["--cp-type", "p2p", "--zigzag", "1"]),
+    ("hybrid_u2_ring2", ["--cp-type", "a2a+p2p", "--ulysses", "2"]),
+])
+def test_ring_and_hybrid_context_parallel_over_four_ranks(tmp_path, dense_ref, name, extra):
+    """cp = 4: the ring with contiguous chunks (K/V and their gradients travel the ring), the zig-zag balanced ring
+    (half blocks per step) and Ulysses-in-pairs x ring-across-pairs all train like the unsharded model."""
+    _close(_run(tmp_path, 4, name, "--cp", "4", *extra), dense_ref, 2e-5)
+
+
 def test_expert_parallel(tmp_path):
     ref = _run(tmp_path, 1, "moe_ref", "--moe", "1")
     got = _run(tmp_path, 2, "moe_ep2", "--moe", "1", "--ep", "2")
