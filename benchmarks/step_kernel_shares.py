@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--profiled-steps", type=int, default=1, help="consecutive steps inside one profiler session")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -53,8 +54,17 @@ def main():
         for _ in range(2):
             engine.train_step_device(batch)
         torch.cuda.synchronize()
-        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        # wall time of a step on the device without the profiler: kernel time / this = how busy the GPU is
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
             engine.train_step_device(batch)
+        e1.record()
+        torch.cuda.synchronize()
+        step_ms = e0.elapsed_time(e1) / 3
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+            for _ in range(args.profiled_steps):
+                engine.train_step_device(batch)
             torch.cuda.synchronize()
         agg = defaultdict(lambda: [0, 0.0])
         for ev in prof.events():
@@ -63,12 +73,36 @@ def main():
                 agg[name][0] += 1
                 agg[name][1] += ev.device_time if hasattr(ev, "device_time") else ev.cuda_time
         total = sum(v[1] for v in agg.values())
+        # idle time between consecutive kernels, by the kernel that follows the gap: where the host falls behind
+        devs = sorted((ev for ev in prof.events() if ev.device_type == torch.autograd.DeviceType.CUDA),
+                      key=lambda ev: ev.time_range.start)
+        gaps = defaultdict(lambda: [0, 0.0])
+        end_prev, name_prev = None, None
+        for ev in devs:
+            if end_prev is not None:
+                gap = ev.time_range.start - end_prev
+                if gap > 3.0:
+                    key = f"{name_prev.split('(')[0][:50]} -> {ev.name.split('(')[0][:50]}"
+                    gaps[key][0] += 1
+                    gaps[key][1] += gap
+            if end_prev is None or ev.time_range.end > end_prev:
+                end_prev, name_prev = ev.time_range.end, ev.name
+        gap_rows = sorted(((k, c, t) for k, (c, t) in gaps.items()), key=lambda r: -r[2])
+        span_ms = (max(ev.time_range.end for ev in devs) - devs[0].time_range.start) / 1e3
         rows = sorted(((k, c, t) for k, (c, t) in agg.items()), key=lambda r: -r[2])
         if rank == 0:
-            print(f"== {label}: {total / 1e3:.1f} ms of kernel time in one step ({args.layers} layers, tp{tp}, mbs {mbs})")
+            print(f"== {label}: {total / 1e3:.1f} ms of kernel time in one step of {step_ms:.1f} ms "
+                  f"({args.layers} layers, tp{tp}, mbs {mbs})")
             for k, c, t in rows[:28]:
                 print(f"{100 * t / total:6.2f} %  {t / 1e3:9.2f} ms  x{c:<5d} {k}")
-        return {"label": label, "total_ms": total / 1e3, "rows": [(k, c, t / 1e3) for k, c, t in rows[:60]]}
+        if rank == 0:
+            print(f"-- {args.profiled_steps} profiled step(s): first kernel start to last kernel end {span_ms:.1f} ms, "
+                  f"kernel time {total / 1e3:.1f} ms")
+            print(f"-- idle gaps > 3 us: {sum(t for _, _, t in gap_rows) / 1e3:.1f} ms in {sum(c for _, c, _ in gap_rows)} gaps")
+            for k, c, t in gap_rows[:14]:
+                print(f"   {t / 1e3:7.2f} ms  x{c:<4d} {k}")
+        return {"label": label, "total_ms": total / 1e3, "step_ms": step_ms, "profiled_steps": args.profiled_steps, "span_ms": span_ms,
+                "gaps": [(k, c, t / 1e3) for k, c, t in gap_rows[:40]], "rows": [(k, c, t / 1e3) for k, c, t in rows[:60]]}
 
     out = [shares("this repository")]
     Fn.set_gemm_backend("cublas")

@@ -89,8 +89,8 @@ class GenerationMixin:
             pass
         elif not prefill:
             pass  # decode: one row per sequence already
-        elif logits.shape[0] != len(tokens):
-            logits = logits.index_select(0, ctx.last_token_index)
+        elif logits.shape[0] == int(flat.numel()) and logits.shape[0] != int(ctx.last_token_index.numel()):
+            logits = logits.index_select(0, ctx.last_token_index)      # a forward that returned a row per token
         tp = ps.get_tensor_model_parallel_world_size()
         if tp > 1:
             parts = [torch.empty_like(logits) for _ in range(tp)]

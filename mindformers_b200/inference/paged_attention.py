@@ -71,7 +71,10 @@ class KVCacheContext:
         for n in q:
             cu.append(cu[-1] + n)
         self.cu_q = cu
-        self.last_token_index = torch.as_tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=device)
+        # sequences without new tokens in this step (finished prompts of a chunked prefill, idle serving slots) have
+        # no row of their own: one entry per sequence that has tokens
+        self.last_token_index = torch.as_tensor([c - 1 for c, n in zip(cu[1:], q) if n > 0], dtype=torch.int64,
+                                                device=device)
 
 
 def _write_cache(cache: KVCacheContext, layer: int, k: torch.Tensor, v: Optional[torch.Tensor]):

@@ -30,6 +30,9 @@ def test_paged_greedy_generation_matches_full_recompute():
     # chunked prefill gives the same continuation
     out2 = model.generate(prompts, max_new_tokens=6, do_sample=False, chunk_prefill_size=3)
     assert out2 == out
+    # ... also when the shorter prompt comes first (it has no tokens in the later chunks)
+    rev = model.generate(prompts[::-1], max_new_tokens=6, do_sample=False, chunk_prefill_size=3)
+    assert rev == out[::-1]
 
 
 def test_sampling_is_seeded_and_eos_stops():
