@@ -222,3 +222,59 @@ def test_version_map_and_automatic_pipeline_stages(monkeypatch):
     p2 = dict(par)
     assert ctx.choose_pipeline_stages(p2, auto=True) == 4 and p2["data_parallel"] == 4
     assert ctx.choose_pipeline_stages(dict(par, micro_batch_num=2), auto=True) == 2     # never more stages than micro-batches
+
+
+def test_benchmark_tools_resolve_models_prepare_data_and_train(tmp_path, monkeypatch):
+    """``scripts/benchmark``: a preset name, a shipped configuration name and a model directory resolve; overrides
+    reach the configuration; a raw text file and an Alpaca file are turned into datasets; weights in the model
+    directory switch the run to fine-tuning."""
+    import importlib.util
+    import json as _json
+    import os
+    import shutil
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    bench_dir = os.path.join(root, "scripts", "benchmark")
+    monkeypatch.syspath_prepend(bench_dir)
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(bench_dir, name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+        return mod
+    base = load("base_init_model")
+    pre = load("run_pretrain")
+    assert pre.build_args(["a=1", "b=0.5", "c=true", "d=none", "e=x"]) == {"a": 1, "b": 0.5, "c": True, "d": None, "e": "x"}
+    named = base.BaseInitModel("llama3_1_8b", {"model_num_layers": 2, "data_seq_len": 256, "data_parallel": 1,
+                                               "model_parallel": 1, "hidden_size": 128}, build_model=False)
+    mc = named.config["model"]["model_config"]
+    assert mc["num_hidden_layers"] == 2 and mc["seq_length"] == 256 and mc["hidden_size"] == 128 and named.custom_model
+    assert named.config["parallel_config"]["model_parallel"] == 1 and not named.finetune
+    with pytest.raises(ValueError):
+        base.BaseInitModel("no_such_model", {}, build_model=False)
+    # a model directory: yaml (+ later weights)
+    mdir = tmp_path / "model"
+    mdir.mkdir()
+    shutil.copy(os.path.join(root, "configs", "general", "run_general_task.yaml"), mdir / "run.yaml")
+    text = tmp_path / "wiki.train.tokens"
+    text.write_text(" = Title = \n" + ("The quick brown fox jumps over the lazy dog . " * 400) + "\n")
+    args = {"data_seq_len": 64, "data_batch_size": 2, "vocab_size": 300}
+    run = pre.ModelPretrain(str(mdir), dict(args))
+    assert not run.finetune
+    res = run.train(str(text), steps=6, output_dir=str(tmp_path / "out"))
+    assert res["mode"] == "train" and res["steps"] == 6 and res["tokens_per_s"] > 0 and res["final_loss"] < 6.0
+    built = base.BaseInitModel(str(mdir), dict(args))
+    assert built.network is not None and built.network.config.seq_length == 64
+    # alpaca records, and weights in the directory -> fine-tuning
+    alpaca = tmp_path / "alpaca_data.json"
+    alpaca.write_text(_json.dumps([{"instruction": "add", "input": "1 2", "output": "3"},
+                                   {"instruction": "say hi", "input": "", "output": "hi there"}] * 8))
+    from mindformers_b200.checkpoint.io import save_checkpoint
+    save_checkpoint(built.network, str(mdir / "weights.safetensors"))
+    run2 = pre.ModelPretrain(str(mdir), dict(args))
+    assert run2.finetune and run2.config["load_checkpoint"].endswith("weights.safetensors")
+    res2 = run2.train(str(alpaca), steps=3, output_dir=str(tmp_path / "out2"))
+    assert res2["mode"] == "finetune" and res2["steps"] == 3
+    off = pre.ModelPretrain(str(mdir), dict(args, load_checkpoint=""))
+    assert not off.finetune and off.config["load_checkpoint"] == ""
