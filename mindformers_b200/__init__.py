@@ -44,7 +44,10 @@ def __getattr__(name: str):
     mod = _EXPORTS.get(name)
     if mod is None:
         raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
-    value = getattr(importlib.import_module(f"{__name__}.{mod}"), name)
+    module = importlib.import_module(f"{__name__}.{mod}")
+    if mod == name:
+        return module          # the sub-package of the same name is callable and stands for the function too
+    value = getattr(module, name)
     globals()[name] = value
     return value
 

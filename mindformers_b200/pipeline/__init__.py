@@ -150,3 +150,18 @@ def pipeline(task: Optional[str] = None, model=None, tokenizer=None, image_proce
         raise ValueError("pipeline() needs a model")
     cls = MindFormerRegister.get_cls(MindFormerModuleType.PIPELINE, task)
     return cls(model=model, tokenizer=tokenizer, image_processor=image_processor, **kwargs)
+
+
+# ``mindformers_b200.pipeline`` names both this package and the factory function above. Calling the package calls the
+# function, so ``from mindformers_b200 import pipeline; pipeline("text_generation", ...)`` works whichever of the two
+# the import machinery hands out, and ``import mindformers_b200.pipeline as pl; pl.pipeline`` keeps meaning the module.
+import sys as _sys
+import types as _types
+
+
+class _CallablePackage(_types.ModuleType):
+    def __call__(self, *args, **kwargs):
+        return pipeline(*args, **kwargs)
+
+
+_sys.modules[__name__].__class__ = _CallablePackage

@@ -91,7 +91,10 @@ class MindFormerConfig(dict):
         if path in _seen:
             raise ValueError(f"circular base_config chain through {filename}")
         with open(path, encoding="utf-8") as f:
-            data = yaml.safe_load(f) or {}
+            text = f.read()
+        from ..check_rules import check_yaml_depth_before_loading
+        check_yaml_depth_before_loading(text)          # on the node tree, before any object is built
+        data = yaml.safe_load(text) or {}
         if not isinstance(data, dict):
             raise ValueError(f"{filename}: top level of a configuration must be a mapping")
         _depth(data)

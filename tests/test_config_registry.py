@@ -255,3 +255,54 @@ def test_every_shipped_yaml_loads_validates_and_builds_a_shrunk_model(path, monk
     with torch.no_grad():
         logits = model(torch.randint(0, 256, (1, 8)))
     assert logits.shape[-1] >= 256 and torch.isfinite(logits).all()
+
+
+def test_cross_field_rules_of_modes_datasets_recompute_and_swap():
+    from mindformers_b200.tools.check_rules import (check_compatibility, check_keyword_gen_dataset, check_mode,
+                                                    check_recompute_shapes, check_yaml_depth_before_loading)
+    base = {"parallel_config": {"data_parallel": 2, "pipeline_stage": 2}, "use_parallel": True,
+            "model": {"model_config": {"seq_length": 64, "batch_size": 3}}}
+    with pytest.raises(ValueError, match="training layout"):
+        check_mode(base, "predict")
+    flat = {"parallel_config": {"data_parallel": 2}, "use_parallel": True, "model": {"model_config": {"batch_size": 3}}}
+    with pytest.raises(ValueError, match="divisible by data_parallel"):
+        check_mode(flat, "predict")
+    check_mode(flat, "train")
+    # keyword-generation data: seq_length = source + target + 1 in training, = source for the generation metric
+    adgen = {"model": {"model_config": {"seq_length": 193}}, "do_eval": True, "metric": [{"type": "ADGENMetric"}],
+             "train_dataset": {"data_loader": {"type": "ADGenDataLoader"}, "max_source_length": 64, "max_target_length": 128},
+             "eval_dataset": {"data_loader": {"type": "ADGenDataLoader"}, "max_source_length": 64, "max_target_length": 128}}
+    with pytest.raises(ValueError, match="eval_dataset"):
+        check_keyword_gen_dataset(adgen, "train")
+    adgen["eval_dataset"]["max_source_length"] = 193
+    check_keyword_gen_dataset(adgen, "train")
+    adgen["train_dataset"]["max_target_length"] = 100
+    with pytest.raises(ValueError, match="train_dataset"):
+        check_keyword_gen_dataset(adgen, "train")
+    ppl = {"model": {"model_config": {"seq_length": 8}}, "metric": {"type": "PerplexityMetric"},
+           "eval_dataset": {"data_loader": {"type": "X", "phase": "eval"}}}
+    check_keyword_gen_dataset(ppl, "eval")
+    assert ppl["eval_dataset"]["data_loader"]["phase"] == "train"
+    # recompute / swap shapes
+    ok = {"parallel_config": {"pipeline_stage": 2}, "recompute_config": {"recompute": [3, 2], "select_recompute": ["mlp"]},
+          "swap_config": {"swap": True, "default_prefetch": 1,
+                          "layer_swap": [{"layers": [0, 1], "backward_prefetch": 2}], "op_swap": {"mlp": [{"layers": [1], "backward_prefetch": 1}]}}}
+    check_recompute_shapes(ok)
+    for bad, msg in (({"recompute_config": {"recompute": [1, 2, 3]}, "parallel_config": {"pipeline_stage": 2}}, "at most one per stage"),
+                     ({"recompute_config": {"select_recompute": [1, "mlp"]}}, "all be int"),
+                     ({"swap_config": {"swap": "yes"}}, "must be a bool"),
+                     ({"swap_config": {"swap": True, "default_prefetch": 0}}, "positive int"),
+                     ({"swap_config": {"swap": True, "layer_swap": {"layers": [0]}}}, "list of mappings"),
+                     ({"swap_config": {"swap": True, "layer_swap": [{"layers": [0], "backward_prefetch": 0}]}}, "backward_prefetch")):
+        with pytest.raises(ValueError, match=msg):
+            check_recompute_shapes(bad)
+    with pytest.raises(ValueError, match="use_seq_parallel"):
+        check_compatibility({"model": {"model_config": {"fine_grain_interleave": 2}}, "parallel_config": {}})
+    with pytest.raises(ValueError, match="divisible by expert_parallel"):
+        check_compatibility({"model": {"model_config": {"num_experts": 6}}, "parallel_config": {"expert_parallel": 4}})
+    with pytest.raises(ValueError, match="pipeline_stage > 1"):
+        check_compatibility({"parallel_config": {"seq_split_num": 2}})
+    check_yaml_depth_before_loading("a: {b: {c: [1, 2, {d: 3}]}}")
+    deep = "a: " + "{x: " * 12 + "1" + "}" * 12
+    with pytest.raises(ValueError, match="nested deeper"):
+        check_yaml_depth_before_loading(deep)
