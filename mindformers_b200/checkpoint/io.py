@@ -313,6 +313,42 @@ def _owner_path(model: torch.nn.Module, param_name: str) -> str:
         return "model." + mod_path if mod_path else "model"
 
 
+def shard_checkpoint(state_dict: Dict[str, torch.Tensor], max_shard_size=5 << 30, weights_name: str = "model.safetensors"):
+    """Cut a state dict into files of at most ``max_shard_size`` bytes, walking the keys in order (no bin packing; a
+    tensor larger than the limit gets a file of its own). Returns ``(shards, index)``: ``{file name: {key: tensor}}`` and
+    ``{"metadata": {"total_size"}, "weight_map": {key: file name}}`` — ``index`` is ``None`` for a single file, which
+    then carries ``weights_name`` (reference ``models/modeling_utils.py:87-155``)."""
+    limit = max_shard_size if isinstance(max_shard_size, int) else _size_to_int(max_shard_size)
+    groups, cur, size, total = [], {}, 0, 0
+    for n, t in state_dict.items():
+        b = t.numel() * t.element_size()
+        if cur and size + b > limit:
+            groups.append(cur)
+            cur, size = {}, 0
+        cur[n] = t
+        size += b
+        total += b
+    if cur or not groups:
+        groups.append(cur)
+    if len(groups) == 1:
+        return {weights_name: groups[0]}, None
+    stem, ext = os.path.splitext(weights_name)
+    shards, weight_map = {}, {}
+    for i, g in enumerate(groups):
+        fname = f"{stem}-{i + 1:05d}-of-{len(groups):05d}{ext}"
+        shards[fname] = g
+        weight_map.update({n: fname for n in g})
+    return shards, {"metadata": {"total_size": total}, "weight_map": weight_map}
+
+
+def _size_to_int(text) -> int:
+    s = str(text).strip().upper()
+    for unit, mul in (("GIB", 1 << 30), ("MIB", 1 << 20), ("KIB", 1 << 10), ("GB", 10 ** 9), ("MB", 10 ** 6), ("KB", 10 ** 3)):
+        if s.endswith(unit):
+            return int(float(s[:-len(unit)]) * mul)
+    return int(s)
+
+
 def save_pretrained_dir(model: torch.nn.Module, directory: str, config_dict: Optional[dict] = None,
                         max_shard_bytes: int = 5 << 30, hf_names: bool = False, family: str = "llama"):
     """HF-style directory: ``config.json`` + (sharded) ``model-0000x-of-0000y.safetensors`` + index."""
@@ -320,27 +356,12 @@ def save_pretrained_dir(model: torch.nn.Module, directory: str, config_dict: Opt
     sd = {n: t.contiguous().cpu() for n, t in model_state(model).items()}
     if hf_names:
         sd = name_maps.framework_to_hf(sd, model.config, family)
-    shards, cur, size = [], {}, 0
-    for n, t in sd.items():
-        b = t.numel() * t.element_size()
-        if cur and size + b > max_shard_bytes:
-            shards.append(cur)
-            cur, size = {}, 0
-        cur[n] = t
-        size += b
-    if cur:
-        shards.append(cur)
-    if len(shards) == 1:
-        save_file(shards[0], os.path.join(directory, "model.safetensors"), metadata={"format": "pt"})
-    else:
-        weight_map = {}
-        for i, sh in enumerate(shards):
-            fname = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
-            save_file(sh, os.path.join(directory, fname), metadata={"format": "pt"})
-            weight_map.update({n: fname for n in sh})
+    shards, index = shard_checkpoint(sd, max_shard_bytes, "model.safetensors")
+    for fname, part in shards.items():
+        save_file(part, os.path.join(directory, fname), metadata={"format": "pt"})
+    if index is not None:
         with open(os.path.join(directory, "model.safetensors.index.json"), "w") as f:
-            json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in sd.values())},
-                       "weight_map": weight_map}, f, indent=1)
+            json.dump(index, f, indent=1)
     if config_dict is not None:
         with open(os.path.join(directory, "config.json"), "w") as f:
             json.dump(config_dict, f, indent=1, default=str)

@@ -123,6 +123,23 @@ class PreTrainedModel(nn.Module, GenerationMixin, InferModelMixin):
         size = _parse_size(max_shard_size)
         ckpt_io.save_pretrained_dir(self, save_directory, self.model_config.to_dict(), size, hf_names, self.weight_family)
 
+    def check_pipeline_stage(self, pipeline_stage: Optional[int] = None, pp_interleave_num: Optional[int] = None):
+        """A pipeline layout needs at least one layer per stage, and per virtual stage when interleaved (reference
+        ``models/modeling_utils.py:317-341``). Sizes default to the model's configuration."""
+        cfg = self.config
+        pp = int(pipeline_stage or getattr(cfg, "pipeline_model_parallel_size", 1) or 1)
+        vpp = int(pp_interleave_num or getattr(cfg, "virtual_pipeline_model_parallel_size", None) or 1)
+        if pp <= 1:
+            return
+        layers = getattr(cfg, "num_layers", None)
+        if layers is None:
+            raise ValueError("num_layers is not set: the pipeline_stage check needs it")
+        if layers < pp:
+            raise ValueError(f"num_layers must be at least pipeline_stage, got num_layers ({layers}) < pp ({pp})")
+        if vpp > 1 and pp * vpp > layers:
+            raise ValueError(f"num_layers must be at least pp * pp_interleave_num, got num_layers {layers} and "
+                             f"pp * pp_interleave_num = {pp * vpp}")
+
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.parameters())
 
@@ -135,3 +152,6 @@ def _parse_size(s) -> int:
         if s.endswith(unit):
             return int(float(s[:-2]) * mul)
     return int(s)
+
+
+shard_checkpoint = ckpt_io.shard_checkpoint

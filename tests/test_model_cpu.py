@@ -605,3 +605,25 @@ def test_glm4_checkpoint_loads_and_reproduces_the_published_architecture(tmp_pat
     for k, v in back.items():
         assert torch.equal(v, sd[k]), k
     assert ChatGLM2Config().to_transformer_dict()["multi_query_group_num"] == 2
+
+
+def test_shard_checkpoint_and_pipeline_stage_check():
+    from mindformers_b200.models import LlamaConfig, LlamaForCausalLM
+    from mindformers_b200.models.modeling_utils import shard_checkpoint
+    sd = {f"w{i}": torch.zeros(n, dtype=torch.float32) for i, n in enumerate([1500, 1500, 500, 1500, 500, 500])}
+    shards, index = shard_checkpoint(sd, max_shard_size=10000, weights_name="model.safetensors")
+    assert [sorted(v) for v in shards.values()] == [["w0"], ["w1", "w2"], ["w3", "w4", "w5"]]     # in key order, no packing
+    assert list(shards)[0] == "model-00001-of-00003.safetensors" and index["weight_map"]["w4"] == "model-00003-of-00003.safetensors"
+    assert index["metadata"]["total_size"] == 6000 * 4
+    one, idx = shard_checkpoint(sd, "1MB")
+    assert list(one) == ["model.safetensors"] and idx is None
+    big, _ = shard_checkpoint({"a": torch.zeros(10), "huge": torch.zeros(10000), "b": torch.zeros(10)}, 1000)
+    assert [sorted(v) for v in big.values()] == [["a"], ["huge"], ["b"]]
+    model = LlamaForCausalLM(LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=3,
+                                         num_attention_heads=2, params_dtype="float32"), device="cpu")
+    model.check_pipeline_stage(2)
+    model.check_pipeline_stage(1, 8)
+    with pytest.raises(ValueError, match="at least pipeline_stage"):
+        model.check_pipeline_stage(4)
+    with pytest.raises(ValueError, match="pp_interleave_num"):
+        model.check_pipeline_stage(2, 2)
