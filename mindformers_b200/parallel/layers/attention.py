@@ -86,6 +86,12 @@ class CoreAttention(nn.Module):
             o = varlen_attention(q4, k4, v4, cu, self.scale)
         elif self.unfused is not None:       # use_flash_attention=False: explicit mask + softmax
             o = self.unfused(q4, k4, v4)
+        elif self.training and float(getattr(self.config, "attention_dropout", 0.0) or 0.0) > 0.0:
+            # dropout on the attention probabilities: the flash kernels have no dropout, the library kernel does
+            nq_, nkv_ = q4.shape[2], k4.shape[2]
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q4.transpose(1, 2), k4.transpose(1, 2), v4.transpose(1, 2), dropout_p=float(self.config.attention_dropout),
+                is_causal=True, scale=self.scale, enable_gqa=(nq_ != nkv_)).transpose(1, 2)
         else:
             o = Fn.attention(q4, k4, v4, causal=True, scale=self.scale)
         return o.reshape(T, -1)
@@ -162,7 +168,8 @@ class SelfAttention(nn.Module):
                              self.nq + self.nkv, self.rot_dim, self.config.rotary_interleaved)
             q, k, v = packed[:, :self.nq], packed[:, self.nq:self.nq + self.nkv], packed[:, self.nq + self.nkv:]
         ctx = None
-        if meta.cache is None and ps.get_context_parallel_world_size() == 1 \
+        drop = self.training and float(getattr(self.config, "attention_dropout", 0.0) or 0.0) > 0.0
+        if meta.cache is None and ps.get_context_parallel_world_size() == 1 and not drop \
                 and Fn.get_attention_backend() != "sdpa" and getattr(self, "use_packed_attention", True):
             from ...ops import attention as native
             T = packed.shape[0]

@@ -61,6 +61,23 @@ class TransformerLayer(nn.Module):
                                     if submodules.post_attn_layernorm is not None else None)
         self.post_mlp_layernorm = (build_module(submodules.post_mlp_layernorm, config)
                                    if submodules.post_mlp_layernorm is not None else None)
+        self.hidden_dropout = float(getattr(config, "hidden_dropout", 0.0) or 0.0)
+
+    def _dropout(self, x):
+        """Hidden dropout on a sub-layer output before it joins the residual (reference ``bias_dropout_add``,
+        ``transformer_layer.py:215-250``). Under sequence parallelism every tensor-parallel rank holds other tokens, so
+        the mask comes from the tensor-parallel random stream (different per rank); otherwise the ranks hold the same
+        activations and draw the same mask from the default stream."""
+        if self.hidden_dropout <= 0.0 or not self.training:
+            return x
+        cfg = self.config
+        if cfg.sequence_parallel and ps.get_tensor_model_parallel_world_size() > 1:
+            from ...modules.rng import get_rng_tracker
+            tracker = get_rng_tracker()
+            if "model-parallel-rng" in tracker.states:
+                with tracker.fork():
+                    return torch.nn.functional.dropout(x, self.hidden_dropout, True)
+        return torch.nn.functional.dropout(x, self.hidden_dropout, True)
 
     def forward(self, pending, residual, rotary, meta: AttnMeta):
         """``pending``: sub-layer output not yet added to ``residual`` (``residual`` None for the first layer)."""
@@ -72,6 +89,7 @@ class TransformerLayer(nn.Module):
         attn_out, _ = self.self_attention(normed, rotary, meta)
         if self.post_attn_layernorm is not None:
             attn_out = self.post_attn_layernorm(attn_out)
+        attn_out = self._dropout(attn_out)
         normed, residual = self.pre_mlp_layernorm(attn_out, residual)
         aux = None
         if self.is_moe:
@@ -80,7 +98,7 @@ class TransformerLayer(nn.Module):
             mlp_out, _ = self.mlp(normed)
         if self.post_mlp_layernorm is not None:
             mlp_out = self.post_mlp_layernorm(mlp_out)
-        return mlp_out, residual, aux
+        return self._dropout(mlp_out), residual, aux
 
 
 def pipeline_layer_split(num_layers: int, pp: int, vpp: int = 1, offset=0) -> List[List[List[int]]]:

@@ -627,3 +627,26 @@ def test_shard_checkpoint_and_pipeline_stage_check():
         model.check_pipeline_stage(4)
     with pytest.raises(ValueError, match="pp_interleave_num"):
         model.check_pipeline_stage(2, 2)
+
+
+def test_hidden_and_attention_dropout_act_in_training_only():
+    """``hidden_dropout`` masks the sub-layer outputs before the residual add and ``attention_dropout`` the attention
+    probabilities: two training passes differ, evaluation is deterministic and equals the model without dropout."""
+    torch.manual_seed(41)
+    plain = GPTModel(tiny_llama_config())
+    torch.manual_seed(41)
+    drop = GPTModel(tiny_llama_config(hidden_dropout=0.2, attention_dropout=0.1))
+    drop.load_state_dict(plain.state_dict())
+    ids = torch.randint(0, 1024, (2, 33))
+    inp, lab = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    drop.train()
+    a, b = drop(inp, lab), drop(inp, lab)
+    assert abs(float(a) - float(b)) > 1e-6
+    a.backward()
+    assert all(p.grad is not None for p in drop.parameters())
+    drop.eval(), plain.eval()
+    with torch.no_grad():
+        assert torch.equal(drop(inp, lab), plain(inp, lab))
+    only_hidden = GPTModel(tiny_llama_config(hidden_dropout=0.5)).train()
+    x = only_hidden(inp, lab)
+    assert torch.isfinite(x)
