@@ -24,6 +24,7 @@ from ..models import build_network
 from ..parallel import parallel_state as ps
 from ..tools.check_rules import check_rules
 from ..tools.logger import get_logger
+from ..tools.register.config import MindFormerConfig
 from ..tools.register.register import MindFormerModuleType, MindFormerRegister
 from ..tools.utils import get_output_root_path, get_real_group_size
 from .engine import TrainingEngine
@@ -232,7 +233,7 @@ class BaseTrainer:
             total_steps = min(total_steps, stop_step)
         gbs = self.global_batch_size(config)
         self.engine = engine = self.create_engine(config, total_steps, model=network)
-        seq_len = int(getattr(engine.model.config, "seq_length", 0) or 0)
+        seq_len = int(getattr(getattr(engine.model, "config", None), "seq_length", 0) or 0)
         ctx = RunContext(engine=engine, config=config, epochs=epochs, steps_per_epoch=steps_per_epoch, total_steps=total_steps,
                          global_batch_size=gbs, seq_length=seq_len)
         self.callbacks = cbs = list(callbacks) if callbacks is not None else self.create_callbacks(config, {"global_batch_size": gbs})
@@ -399,18 +400,188 @@ class CausalLanguageModelingTrainer(BaseTrainer):
         return metric.eval()
 
 
+class GeneralEngine:
+    """The minimum a training loop needs, around an arbitrary network: ``train_step_full(batch)`` → ``{loss, lr,
+    global_norm, skipped}``. ``network(batch)`` (a mapping is passed as keyword arguments, a tuple as positional ones)
+    returns the loss or a tuple whose first element is the loss. Either ``wrapper`` — a callable that does forward,
+    backward and the update itself and returns the loss, the counterpart of a ``TrainOneStepCell`` handed to the
+    reference's general trainer — or ``optimizer`` (any ``torch.optim.Optimizer``) drives the update."""
+
+    def __init__(self, network: torch.nn.Module, optimizer=None, wrapper=None, max_grad_norm: float = 0.0,
+                 lr_scheduler=None, device=None):
+        self.model, self.optimizer, self.wrapper = network, optimizer, wrapper
+        self.max_grad_norm, self.lr_scheduler = float(max_grad_norm or 0.0), lr_scheduler
+        first = next(network.parameters(), None)
+        self.device = device or (first.device if first is not None else torch.device("cpu"))
+        self.global_step = 0
+
+    def _to_device(self, batch):
+        move = lambda t: t.to(self.device, non_blocking=True) if isinstance(t, torch.Tensor) else t   # noqa: E731
+        if isinstance(batch, dict):
+            return {k: move(v) for k, v in batch.items()}
+        if isinstance(batch, (list, tuple)):
+            return type(batch)(move(v) for v in batch)
+        return move(batch)
+
+    def forward(self, batch):
+        batch = self._to_device(batch)
+        out = self.model(**batch) if isinstance(batch, dict) else (self.model(*batch) if isinstance(batch, (list, tuple))
+                                                                    else self.model(batch))
+        return out
+
+    @staticmethod
+    def loss_of(out):
+        return out[0] if isinstance(out, (list, tuple)) else out
+
+    def train_step_full(self, batch):
+        self.model.train()
+        if self.wrapper is not None:
+            loss = self.loss_of(self.wrapper(self._to_device(batch)))
+            norm = float("nan")
+        else:
+            self.optimizer.zero_grad(set_to_none=True)
+            loss = self.loss_of(self.forward(batch))
+            loss.backward()
+            params = [p for g in self.optimizer.param_groups for p in g["params"] if p.grad is not None]
+            if self.max_grad_norm > 0:
+                norm = float(torch.nn.utils.clip_grad_norm_(params, self.max_grad_norm))
+            else:
+                norm = float(torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(p.grad.float())
+                                                                   for p in params]))) if params else 0.0
+            self.optimizer.step()
+            if self.lr_scheduler is not None:
+                self.lr_scheduler.step()
+        self.global_step += 1
+        lr = self.optimizer.param_groups[0]["lr"] if self.optimizer is not None else float("nan")
+        return {"loss": float(loss.detach()), "lr": float(lr), "global_norm": norm, "skipped": False}
+
+
 @MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["general"])
-class GeneralTaskTrainer(CausalLanguageModelingTrainer):
-    """Any network that maps a batch to a loss (``trainer/general_task_trainer``)."""
+class GeneralTaskTrainer(BaseTrainer):
+    """Trainer for a task this package has no dedicated flow for (reference
+    ``trainer/general_task_trainer/general_task_trainer.py:32-240``): the caller brings the network and the dataset —
+    and optionally the optimizer, a one-step ``wrapper``, callbacks and metric objects — and gets the common loop
+    (callbacks, step timing, stop step) around them. Unlike the language-model trainers nothing is built from the
+    model section of the configuration, so a missing network or dataset is an error, as in the reference."""
+
     task = "general"
+
+    def create_engine(self, config, total_steps: int, model=None):
+        from ..core.optim import build_optim
+        kw = getattr(self, "_general_kwargs", {})
+        optimizer, wrapper = kw.get("optimizer"), kw.get("wrapper")
+        if optimizer is None and wrapper is None:
+            opt_cfg = dict((config or {}).get("optimizer") or {"type": "AdamW", "learning_rate": 1e-3})
+            if opt_cfg.get("type") in ("AdamW", "adamw", "FusedAdamW"):        # the sharded optimizer needs a GPT-style model
+                lr = float(opt_cfg.get("learning_rate", 1e-3))
+                optimizer = torch.optim.AdamW([p for p in model.parameters() if p.requires_grad], lr=lr,
+                                              betas=tuple(opt_cfg.get("betas", (0.9, 0.999))), eps=float(opt_cfg.get("eps", 1e-8)),
+                                              weight_decay=float(opt_cfg.get("weight_decay", 0.0)))
+            else:
+                optimizer = build_optim(opt_cfg, model=model)
+        wrap_cfg = dict((config or {}).get("runner_wrapper") or {})
+        clip = float(wrap_cfg.get("max_grad_norm", 0.0)) if wrap_cfg.get("use_clip_grad") else 0.0
+        return GeneralEngine(model, optimizer, wrapper, clip, kw.get("lr_scheduler"))
+
+    def global_batch_size(self, config):
+        return int(((config or {}).get("runner_config") or {}).get("batch_size", 1) or 1)
+
+    def _maybe_load(self, config, engine, gbs, steps_per_epoch):
+        path = (config or {}).get("load_checkpoint")
+        if path:
+            from safetensors.torch import load_file
+            state = load_file(path) if str(path).endswith(".safetensors") else torch.load(path, map_location="cpu")
+            engine.model.load_state_dict(state, strict=False)
+        return 0, 0
+
+    def train(self, config=None, network=None, dataset=None, wrapper=None, optimizer=None, callbacks=None, **kwargs):
+        if network is None:
+            raise NotImplementedError("the general trainer needs the network to train, got None")
+        if dataset is None:
+            raise NotImplementedError("the general trainer needs the training dataset, got None")
+        self._general_kwargs = dict(optimizer=optimizer, wrapper=wrapper, lr_scheduler=kwargs.pop("lr_scheduler", None))
+        cfg = config if config is not None else MindFormerConfig({"runner_config": {"epochs": 1}})
+        if callbacks is None:
+            callbacks = [MFLossMonitor()] if not (cfg.get("callbacks") or []) else None
+        return self.training_process(cfg, network=network, dataset=dataset, callbacks=callbacks, **kwargs)
+
+    @torch.no_grad()
+    def evaluate(self, config=None, network=None, dataset=None, compute_metrics=None, callbacks=None, **kwargs):
+        """``compute_metrics``: ``{name: metric}`` with ``clear()`` / ``update(*outputs)`` / ``eval()``; the network's
+        evaluation output (a tensor or a tuple) is what ``update`` receives, batch by batch."""
+        if network is None:
+            raise NotImplementedError("the general trainer needs the network to evaluate, got None")
+        if dataset is None:
+            raise NotImplementedError("the general trainer needs the evaluation dataset, got None")
+        if not compute_metrics:
+            raise NotImplementedError("the general trainer needs compute_metrics = {name: metric object}")
+        engine = GeneralEngine(network)
+        network.eval()
+        for m in compute_metrics.values():
+            m.clear()
+        for batch in dataset:
+            out = engine.forward(batch)
+            out = out if isinstance(out, (list, tuple)) else (out,)
+            for m in compute_metrics.values():
+                m.update(*out)
+        result = {name: m.eval() for name, m in compute_metrics.items()}
+        logger.info("evaluation: %s", result)
+        return result
+
+    @torch.no_grad()
+    def predict(self, config=None, input_data=None, network=None, **kwargs):
+        """Runs ``network`` in evaluation mode on ``input_data`` (one batch, or a list of batches) and returns its raw
+        outputs: what a prediction *means* belongs to the task, which this trainer does not know."""
+        if network is None:
+            raise NotImplementedError("the general trainer needs the network to predict with, got None")
+        engine = GeneralEngine(network)
+        network.eval()
+        if isinstance(input_data, list) and input_data and isinstance(input_data[0], (dict, tuple, list, torch.Tensor)):
+            return [engine.forward(b) for b in input_data]
+        return engine.forward(input_data)
 
 
 @MindFormerRegister.register(MindFormerModuleType.TRAINER, search_names=["multi_modal_to_text_generation"])
 class MultiModalToTextGenerationTrainer(CausalLanguageModelingTrainer):
-    """Task trainer for image / multimodal-to-text models (reference ``trainer/multi_modal_to_text_generation/``): the
-    causal-LM flow with a processor that also yields the modality tensors."""
+    """Task trainer for image / multimodal-to-text models (reference
+    ``trainer/multi_modal_to_text_generation/multi_modal_to_text_generation.py:35-260``): training and evaluation are
+    the causal-LM flow on batches that also carry the modality tensors; ``predict`` turns conversation records
+    (``[{"image": path}, {"text": ...}]`` per query) into tensors with the model's processor, generates and decodes."""
 
     task = "multi_modal_to_text_generation"
+
+    def predict(self, config, input_data=None, network=None, tokenizer=None, processor=None, **kwargs):
+        from ..models import build_processor, build_tokenizer
+        from ..pipeline import pipeline
+        self.config = config
+        model = network if network is not None else build_network(config.get("model") or {})
+        path = config.get("load_checkpoint") or config.get("pretrained_model_dir")
+        if path and network is None:
+            model.load_weights(path, strict=False)
+        proc_cfg = config.get("processor") or {}
+        if tokenizer is None:
+            tok_cfg = proc_cfg.get("tokenizer")
+            tokenizer = build_tokenizer(tok_cfg) if tok_cfg else build_tokenizer({"type": "ByteTokenizer"})
+        if processor is None and proc_cfg.get("type"):
+            processor = build_processor(proc_cfg, default_args={"tokenizer": tokenizer})
+        data = input_data if input_data is not None else config.get("input_data")
+        if isinstance(data, str) and os.path.isfile(data):
+            import json as _json
+            with open(data) as f:
+                data = [_json.loads(line) for line in f if line.strip()]
+        if isinstance(data, dict) or (isinstance(data, list) and data and isinstance(data[0], dict) and
+                                      not any(isinstance(v, list) for v in data[0].values())):
+            data = [data] if isinstance(data, dict) else [data]     # one query given as its list of segments
+        pipe = pipeline(task="multi_modal_to_text_generation", model=model, tokenizer=tokenizer, processor=processor)
+        gen_kw = {k: kwargs[k] for k in ("max_new_tokens", "max_length", "do_sample", "top_k", "top_p", "temperature",
+                                          "repetition_penalty") if k in kwargs}
+        result = pipe(data, batch_size=config.get("predict_batch_size") or 1, **gen_kw)
+        save = config.get("save_file") or os.path.join(get_output_root_path(), "multi_modal_to_text_generation_result.txt")
+        os.makedirs(os.path.dirname(save) or ".", exist_ok=True)
+        with open(save, "w") as f:
+            for r in result if isinstance(result, list) else [result]:
+                f.write(str(r) + "\n")
+        return result
 
 
 def build_trainer(config: Optional[dict] = None, default_args=None, **kwargs):

@@ -186,3 +186,22 @@ def test_modal_to_text_sft_dataset_llava_handler_and_s3_paths(tmp_path):
     assert utils_s3.object_exists("s3://bucket/a/b.idx", FakeS3()) and not utils_s3.object_exists("s3://bucket/x", FakeS3())
     assert utils_s3.read_range("s3://bucket/a/b.idx", 2, 4, FakeS3()) == b"2345"
     assert utils_s3.maybe_download_index("/local/file.idx", cfg) == "/local/file.idx"
+
+
+def test_multimodal_trainer_predict_from_records(tmp_path):
+    """The task trainer turns conversation records into tensors with the processor, generates and writes the texts."""
+    from mindformers_b200.tools.register import MindFormerConfig
+    from mindformers_b200.trainer.base_trainer import MultiModalToTextGenerationTrainer
+    tok = ImgTokenizer()
+    model = tiny_model().eval()
+    proc = BaseXModalToTextProcessor(template(tok), tokenizer=tok)
+    img = np.random.default_rng(2).integers(0, 255, (28, 28, 3), dtype=np.uint8)
+    cfg = MindFormerConfig({"run_mode": "predict", "save_file": str(tmp_path / "out.txt")})
+    trainer = MultiModalToTextGenerationTrainer(model_name="tiny")
+    res = trainer.predict(cfg, input_data=[[{"image": img}, {"text": "what is this"}]], network=model, tokenizer=tok,
+                          processor=proc, max_new_tokens=3, do_sample=False)
+    assert isinstance(res[0]["text_generation_text"][0], str)
+    assert (tmp_path / "out.txt").read_text().strip()
+    one = trainer.predict(cfg, input_data=[{"image": img}, {"text": "and this"}], network=model, tokenizer=tok,
+                          processor=proc, max_new_tokens=2, do_sample=False)
+    assert len(one) == 1

@@ -209,3 +209,80 @@ def test_predict_applies_the_yaml_quantization_config(tmp_path, monkeypatch):
     monkeypatch.setattr(pl, "pipeline", spy)
     out = CausalLanguageModelingTrainer().predict(cfg, input_data=["hello"], max_new_tokens=3)
     assert out and sum(isinstance(m, QuantLinear) for m in seen["model"].modules()) == 4
+
+
+def test_general_task_trainer_trains_and_scores_a_caller_supplied_network(tmp_path):
+    """Any module that maps a batch to a loss: the caller's network, dataset, optimizer (or one-step wrapper) and
+    metric objects go through the common loop; a missing network or dataset is an error."""
+    import torch
+    from mindformers_b200.core.callback import Callback
+    from mindformers_b200.trainer.base_trainer import GeneralTaskTrainer
+
+    class Classifier(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 3))
+
+        def forward(self, x, label=None):
+            logits = self.body(x)
+            if self.training:
+                return torch.nn.functional.cross_entropy(logits, label)
+            return logits, label
+
+    class Accuracy:
+        def clear(self):
+            self.hit = self.n = 0
+
+        def update(self, logits, label):
+            self.hit += int((logits.argmax(-1) == label).sum())
+            self.n += int(label.numel())
+
+        def eval(self):
+            return self.hit / max(self.n, 1)
+
+    torch.manual_seed(0)
+    w = torch.randn(8, 3)
+    xs = torch.randn(256, 8)
+    ys = (xs @ w).argmax(-1)
+    data = [{"x": xs[i:i + 32], "label": ys[i:i + 32]} for i in range(0, 256, 32)]
+    net = Classifier()
+    seen = []
+
+    class Spy(Callback):
+        def on_step_end(self, ctx):
+            seen.append(ctx.loss)
+    trainer = GeneralTaskTrainer(model_name="common")
+    metrics = {"Accuracy": Accuracy()}
+    before = trainer.evaluate(network=net, dataset=data, compute_metrics=metrics)["Accuracy"]
+    cfg = {"runner_config": {"epochs": 12}, "optimizer": {"type": "AdamW", "learning_rate": 0.03},
+           "runner_wrapper": {"use_clip_grad": True, "max_grad_norm": 1.0}}
+    from mindformers_b200.tools.register import MindFormerConfig
+    ctx = trainer.train(config=MindFormerConfig(cfg), network=net, dataset=data, callbacks=[Spy()])
+    assert ctx.global_step == 96 and len(seen) == 96 and seen[-1] < 0.5 * seen[0]
+    after = trainer.evaluate(network=net, dataset=data, compute_metrics=metrics)["Accuracy"]
+    assert after > max(before, 0.85)
+    logits, _ = trainer.predict(input_data={"x": xs[:4], "label": ys[:4]}, network=net)
+    assert logits.shape == (4, 3)
+    # a caller-supplied optimizer, and a wrapper that does the whole step itself
+    net2 = Classifier()
+    opt = torch.optim.SGD(net2.parameters(), lr=0.1)
+    trainer.train(network=net2, dataset=data, optimizer=opt)
+    net3 = Classifier()
+    opt3 = torch.optim.SGD(net3.parameters(), lr=0.1)
+    calls = []
+
+    def one_step(batch):
+        opt3.zero_grad()
+        loss = net3(**batch)
+        loss.backward()
+        opt3.step()
+        calls.append(1)
+        return loss
+    trainer.train(network=net3, dataset=data, wrapper=one_step)
+    assert len(calls) == len(data)
+    with pytest.raises(NotImplementedError):
+        trainer.train(dataset=data)
+    with pytest.raises(NotImplementedError):
+        trainer.train(network=net)
+    with pytest.raises(NotImplementedError):
+        trainer.evaluate(network=net, dataset=data)
