@@ -35,6 +35,7 @@ class AttnMeta:
     actual_seq_len: Optional[torch.Tensor] = None   # [B, P] cumulative document ends per row (EOD-reset batches)
     doc_tables: Optional[tuple] = None    # (doc_start, doc_end) int32 [B, S], built once per forward from the above
     cache: Optional[object] = None        # inference.KVCacheContext for paged attention
+    kv_carry: Optional[object] = None     # modules.seq_pipe.KVCarry: keys / values of the earlier sequence chunks
     cp_rank_positions: bool = False       # positions already hold the context-parallel offsets
 
 
@@ -168,8 +169,25 @@ class SelfAttention(nn.Module):
                              self.nq + self.nkv, self.rot_dim, self.config.rotary_interleaved)
             q, k, v = packed[:, :self.nq], packed[:, self.nq:self.nq + self.nkv], packed[:, self.nq + self.nkv:]
         ctx = None
+        if meta.kv_carry is not None:
+            # sequence pipeline: this call holds one chunk of every sequence; attend to the chunks before it as well
+            carry = meta.kv_carry
+            T = packed.shape[0]
+            B, S = meta.batch, T // meta.batch
+            k4, v4 = k.reshape(B, S, self.nkv, self.hd), v.reshape(B, S, self.nkv, self.hd)
+            k_all, v_all = carry.extend(self.layer_number, k4, v4)
+            q4 = q.reshape(B, S, self.nq, self.hd)
+            from ...ops import attention as native
+            if k_all.shape[1] == S:
+                o = Fn.attention(q4, k_all, v_all, causal=True, scale=self.core_attention.scale)
+            elif native.rect_supported(q4, k_all, v_all) and Fn.get_attention_backend() != "sdpa":
+                o = native.flash_attention_rect(q4.contiguous(), k_all.contiguous(), v_all.contiguous(), carry.start, True,
+                                                self.core_attention.scale)
+            else:
+                o = Fn.attention_reference(q4, k_all, v_all, True, self.core_attention.scale, q_offset=carry.start)
+            ctx = o.reshape(T, self.nq * self.hd)
         drop = self.training and float(getattr(self.config, "attention_dropout", 0.0) or 0.0) > 0.0
-        if meta.cache is None and ps.get_context_parallel_world_size() == 1 and not drop \
+        if ctx is None and meta.cache is None and ps.get_context_parallel_world_size() == 1 and not drop \
                 and Fn.get_attention_backend() != "sdpa" and getattr(self, "use_packed_attention", True):
             from ...ops import attention as native
             T = packed.shape[0]

@@ -66,12 +66,26 @@ def microbatch_of(k: int, pp: int, v: int) -> int:
     return (k // (pp * v)) * pp + k % pp
 
 
-def build_schedule(pp: int, v: int, n: int, rank: int) -> List[Step]:
-    """Steps of ``rank`` for ``n`` micro-batches over ``pp`` stages with ``v`` model chunks per rank."""
+def seq_bwd_unit(b: int, seq_split: int) -> int:
+    """Sequence pipeline: the forward unit (micro-batch, chunk) = ``m * C + c`` that the ``b``-th backward handles. The
+    chunks of a micro-batch run backward in reverse, because a chunk's keys and values are read by the chunks after
+    it and their gradients must be complete first."""
+    m, r = divmod(b, seq_split)
+    return m * seq_split + (seq_split - 1 - r)
+
+
+def build_schedule(pp: int, v: int, n: int, rank: int, seq_split: int = 1) -> List[Step]:
+    """Steps of ``rank`` for ``n`` micro-batches over ``pp`` stages with ``v`` model chunks per rank. With
+    ``seq_split = C > 1`` (``v`` must be 1) every micro-batch is ``C`` sequence chunks: forward units are numbered
+    ``m * C + c``, the ``b``-th backward handles unit ``seq_bwd_unit(b, C)``, and the warm-up grows by ``C - 1``
+    forwards so that the last chunk of a micro-batch has run forward before its first backward is due."""
     if v > 1 and n % pp != 0:
         raise ValueError(f"interleaved schedule needs micro-batches ({n}) to be a multiple of pipeline stages ({pp})")
+    if seq_split > 1 and v > 1:
+        raise ValueError("the sequence pipeline does not combine with interleaved model chunks")
+    n = n * seq_split
     total = n * v
-    warm = min((pp - rank - 1) * (2 if v > 1 else 1) + (v - 1) * pp, total)
+    warm = min((pp - rank - 1) * (2 if v > 1 else 1) + (v - 1) * pp + (seq_split - 1), total)
 
     def needs_act(k):          # the first chunk of the first stage embeds its own input
         return 0 <= k < total and not (rank == 0 and fwd_chunk(k, pp, v) == 0)
@@ -144,11 +158,19 @@ class P2PCommunicator:
         return buf
 
 
-def _forward_step(model, mb, input_tensor, num_microbatches, collect, loss_scale):
-    """One micro-batch forward on one model chunk; returns what must be sent on / differentiated."""
+def _forward_step(model, mb, input_tensor, num_microbatches, collect, loss_scale, carry=None):
+    """One micro-batch forward on one model chunk; returns what must be sent on / differentiated. ``carry``: the
+    ``KVCarry`` of this micro-batch when ``mb`` is one sequence chunk of it."""
     if input_tensor is not None:
         model.set_input_tensor(input_tensor)
-    out = model(mb["input_ids"], mb.get("labels"), mb.get("loss_mask"), mb.get("position_ids"))
+    if carry is not None:
+        from .layers.attention import AttnMeta
+        B, S = mb["input_ids"].shape
+        carry.begin_chunk(int(mb["seq_chunk"]), int(mb["seq_chunk"]) * S)
+        meta = AttnMeta(batch=B, seq_len=S, kv_carry=carry)
+        out = model(mb["input_ids"], mb.get("labels"), mb.get("loss_mask"), mb.get("position_ids"), attn_meta=meta)
+    else:
+        out = model(mb["input_ids"], mb.get("labels"), mb.get("loss_mask"), mb.get("position_ids"))
     aux = None
     if model.post_process:
         loss = out
@@ -160,36 +182,68 @@ def _forward_step(model, mb, input_tensor, num_microbatches, collect, loss_scale
     return out, aux
 
 
-def _backward_step(input_tensor, output, aux, output_grad):
+def _backward_step(input_tensor, output, aux, output_grad, carry=None, chunk: int = 0):
     if input_tensor is not None and input_tensor.grad is not None:
         input_tensor.grad = None
-    if output_grad is None:        # last stage: output is the scaled loss
+    tensors, grads = [output], [output_grad]          # last stage: the output is the scaled loss, its gradient is 1
+    if aux is not None and output_grad is not None:
+        tensors.append(aux)
+        grads.append(torch.ones_like(aux))
+    if carry is not None:
+        # gradients that the later chunks of this micro-batch left for this chunk's keys and values
+        roots, root_grads = carry.roots_and_grads(chunk)
+        tensors += roots
+        grads += root_grads
+    if output_grad is None and len(tensors) == 1:
         output.backward()
     else:
-        tensors, grads = [output], [output_grad]
-        if aux is not None:
-            tensors.append(aux)
-            grads.append(torch.ones_like(aux))
+        if grads[0] is None:
+            grads[0] = torch.ones_like(output)
         torch.autograd.backward(tensors, grads)
+    if carry is not None:
+        carry.release(chunk)
     return None if input_tensor is None else input_tensor.grad
 
 
-def forward_backward_no_pipelining(model, microbatches: List[dict], loss_scale: float = 1.0):
+def forward_backward_no_pipelining(model, microbatches: List[dict], loss_scale: float = 1.0, seq_split: int = 1):
+    """All micro-batches on one stage. With ``seq_split = C > 1`` each micro-batch runs as ``C`` sequence chunks: all
+    chunks forward (keys / values carried along), then backward last chunk first; activation memory of everything but
+    the keys and values is that of one chunk."""
     losses: List[torch.Tensor] = []
     n = len(microbatches)
+    if seq_split <= 1:
+        for mb in microbatches:
+            out, _ = _forward_step(model, mb, None, n, losses, loss_scale)
+            out.backward()
+        return losses
+    from ..modules.seq_pipe import KVCarry, SequenceSplit
+    splitter = SequenceSplit(seq_split)
     for mb in microbatches:
-        out, _ = _forward_step(model, mb, None, n, losses, loss_scale)
-        out.backward()
+        carry, outs, parts = KVCarry(), [], []
+        for part in splitter.split(mb):
+            out, _ = _forward_step(model, part, None, n * seq_split, parts, loss_scale, carry)
+            outs.append(out)
+        for c in reversed(range(seq_split)):
+            _backward_step(None, outs[c], None, None, carry, c)
+        losses.append(torch.stack(parts).mean())
     return losses
 
 
 def run_schedule(chunks: List[torch.nn.Module], microbatches: List[dict], hidden_shape, dtype,
-                 loss_scale: float = 1.0) -> List[torch.Tensor]:
+                 loss_scale: float = 1.0, seq_split: int = 1) -> List[torch.Tensor]:
     """Execute this rank's schedule (``build_schedule``) over its model chunks; returns the micro-batch losses on
-    the rank that holds the last chunk of the last stage."""
+    the rank that holds the last chunk of the last stage. ``seq_split = C > 1``: sequence pipeline — every micro-batch
+    enters as ``C`` sequence chunks (``hidden_shape`` is that of one chunk), each stage keeps the keys and values of
+    the chunks it has seen, and a micro-batch's chunks run backward in reverse order."""
     pp = ps.get_pipeline_model_parallel_world_size()
     rank = ps.get_pipeline_model_parallel_rank()
     v, n = len(chunks), len(microbatches)
+    if seq_split > 1:
+        from ..modules.seq_pipe import KVCarry, SequenceSplit
+        splitter = SequenceSplit(seq_split)
+        units = [part for mb in microbatches for part in splitter.split(mb)]
+        carries = [KVCarry() for _ in microbatches]
+        return _run_seq_schedule(chunks[0], units, carries, hidden_shape, dtype, loss_scale, seq_split, pp, rank)
     steps = build_schedule(pp, v, n, rank)
     dev = next(chunks[0].parameters()).device
     comm = P2PCommunicator(hidden_shape, dtype, dev)
@@ -258,6 +312,75 @@ def run_schedule(chunks: List[torch.nn.Module], microbatches: List[dict], hidden
         ps.set_virtual_pipeline_model_parallel_rank(0)
     run_schedule.last_bytes_sent = comm.bytes_sent
     return losses
+
+
+def _run_seq_schedule(model, units, carries, hidden_shape, dtype, loss_scale, C, pp, rank) -> List[torch.Tensor]:
+    """``run_schedule`` for the sequence pipeline (one model chunk per rank). Forward unit ``u`` is chunk ``u % C`` of
+    micro-batch ``u // C``; the ``b``-th backward handles unit ``seq_bwd_unit(b, C)``. Returns one loss per micro-batch
+    (the mean of its chunk losses) on the last stage."""
+    n_units = len(units)
+    steps = build_schedule(pp, 1, n_units // C, rank, seq_split=C)
+    dev = next(model.parameters()).device
+    comm = P2PCommunicator(hidden_shape, dtype, dev)
+    parts: List[torch.Tensor] = []
+    kept: Dict[int, tuple] = {}             # forward unit -> (input, output, aux)
+    act_pending = grad_pending = None
+    act_in: Dict[int, torch.Tensor] = {}
+    grad_in: Dict[int, torch.Tensor] = {}
+    act_owner = grad_owner = None
+
+    def finish_act(st_prev):
+        nonlocal act_pending
+        buf = comm.wait(act_pending)
+        act_pending = None
+        if buf is not None:
+            act_in[st_prev.recv_act] = buf.requires_grad_()
+
+    def finish_grad(st_prev):
+        nonlocal grad_pending
+        buf = comm.wait(grad_pending)
+        grad_pending = None
+        if buf is not None:
+            grad_in[st_prev.recv_grad] = buf
+
+    for st in steps:
+        y = gx = None
+        if st.fwd is not None:
+            if act_owner is not None:
+                finish_act(act_owner)
+                act_owner = None
+            u = st.fwd
+            x = act_in.pop(u, None)
+            y, aux = _forward_step(model, units[u], x, n_units, parts, loss_scale, carries[u // C])
+            kept[u] = (x, y, aux)
+        if st.send_act is not None or st.recv_act is not None:
+            if act_owner is not None:
+                finish_act(act_owner)
+            act_pending = comm.exchange_act(y if st.send_act is not None else None, st.recv_act is not None)
+            act_owner = st
+        if st.bwd is not None:
+            if grad_owner is not None:
+                finish_grad(grad_owner)
+                grad_owner = None
+            b = st.bwd
+            u = seq_bwd_unit(b, C)
+            g = grad_in.pop(b, None)
+            xi, yo, au = kept.pop(u)
+            gx = _backward_step(xi, yo, au, g, carries[u // C], u % C)
+        if st.send_grad is not None or st.recv_grad is not None:
+            if grad_owner is not None:
+                finish_grad(grad_owner)
+            grad_pending = comm.exchange_grad(gx if st.send_grad is not None else None, st.recv_grad is not None)
+            grad_owner = st
+    if act_owner is not None:
+        finish_act(act_owner)
+    if grad_owner is not None:
+        finish_grad(grad_owner)
+    run_schedule.last_bytes_sent = comm.bytes_sent
+    if not parts:
+        return []
+    per_mb = torch.stack(parts).view(-1, C).mean(dim=1)
+    return list(per_mb)
 
 
 def forward_backward_pipelining_without_interleaving(model, microbatches: List[dict], hidden_shape, dtype,
@@ -345,9 +468,14 @@ class PipelineTrainStep:
     """
 
     def __init__(self, chunks: Sequence[torch.nn.Module], optimizer, micro_batch_size: int = 1, loss_scale: float = 1.0,
-                 overlap: bool = True):
+                 overlap: bool = True, seq_split_num: int = 1):
         self.chunks = list(chunks)
         self.optimizer, self.mbs, self.loss_scale, self.overlap = optimizer, micro_batch_size, loss_scale, overlap
+        self.seq_split = int(seq_split_num or 1)
+        if self.seq_split > 1 and len(self.chunks) > 1:
+            raise ValueError("seq_split_num > 1 (sequence pipeline) does not combine with pp_interleave_num > 1")
+        if self.seq_split > 1 and ps.get_context_parallel_world_size() > 1:
+            raise ValueError("seq_split_num > 1 (sequence pipeline) does not combine with context parallelism")
 
     def __call__(self, batch: Dict[str, torch.Tensor]):
         cfg = self.chunks[0].config
@@ -355,17 +483,18 @@ class PipelineTrainStep:
         mbs = [{k: v[i * self.mbs:(i + 1) * self.mbs] for k, v in batch.items() if v is not None} for i in range(n)]
         S = batch["input_ids"].shape[1]
         tp = ps.get_tensor_model_parallel_world_size()
-        T = self.mbs * S // (tp if cfg.sequence_parallel else 1)
+        if S % self.seq_split:
+            raise ValueError(f"sequence length {S} is not divisible by seq_split_num {self.seq_split}")
+        T = self.mbs * (S // self.seq_split) // (tp if cfg.sequence_parallel else 1)
         shape = (T, cfg.hidden_size)
         dtype = cfg.compute_dtype if isinstance(cfg.compute_dtype, torch.dtype) else getattr(torch, str(cfg.compute_dtype))
         self.optimizer.zero_grad()
         if len(self.chunks) > 1:
             losses = forward_backward_pipelining_with_interleaving(self.chunks, mbs, shape, dtype, self.loss_scale, self.overlap)
         elif ps.get_pipeline_model_parallel_world_size() > 1:
-            losses = forward_backward_pipelining_without_interleaving(self.chunks[0], mbs, shape, dtype, self.loss_scale,
-                                                                     self.overlap)
+            losses = run_schedule([self.chunks[0]], mbs, shape, dtype, self.loss_scale, self.seq_split)
         else:
-            losses = forward_backward_no_pipelining(self.chunks[0], mbs, self.loss_scale)
+            losses = forward_backward_no_pipelining(self.chunks[0], mbs, self.loss_scale, self.seq_split)
         sync_shared_embedding_grads(self.chunks)
         dp = ps.get_data_parallel_world_size(with_context_parallel=True)
         scale = 1.0 / (dp * self.loss_scale)

@@ -131,11 +131,9 @@ class BaseTrainer:
         recompute = rcfg.get("recompute") or False          # bool, or layers per pipeline stage
         skip = float(wrapper.get("global_norm_spike_threshold", 0) or 0) if wrapper.get("use_skip_data_by_global_norm") else 0.0
         pc = config.get("parallel_config") or {}
-        if int(pc.get("seq_split_num", 1) or 1) > 1:
-            raise NotImplementedError(
-                "parallel_config.seq_split_num > 1 (sequence pipeline: chunks of one sequence flowing through the "
-                "stages with the keys and values of earlier chunks carried along) is not built; use "
-                "context_parallel for long sequences or pp_interleave_num to shrink the pipeline bubble")
+        seq_split = int(pc.get("seq_split_num", 1) or 1)
+        if seq_split > 1 and int(pc.get("pp_interleave_num", 1) or 1) > 1:
+            raise NotImplementedError("seq_split_num > 1 (sequence pipeline) cannot be combined with pp_interleave_num > 1")
         interleave = int(config.get("micro_batch_interleave_num", 1) or 1)
         pp = int(pc.get("pipeline_stage", 1) or 1)
         if interleave > 1 and pp > 1:
@@ -192,7 +190,8 @@ class BaseTrainer:
             wrapped = MicroBatchInterleaved(net, interleave)
             forward_fn = lambda m, b: wrapped(b["input_ids"], b["labels"], b.get("loss_mask"), b.get("position_ids"))  # noqa: E731
             mbs *= interleave                        # one forward call now carries `interleave` copies of the micro-batch
-        return TrainingEngine(net, opt, micro_batch_size=mbs, loss_scale=loss_scale, forward_fn=forward_fn)
+        return TrainingEngine(net, opt, micro_batch_size=mbs, loss_scale=loss_scale, forward_fn=forward_fn,
+                              seq_split_num=seq_split)
 
     def create_callbacks(self, config, default: Dict[str, Any]) -> List[Callback]:
         cbs: List[Callback] = []

@@ -70,14 +70,16 @@ class TrainingEngine:
     optimizer construction of ``trainer/base_trainer.py``)."""
 
     def __init__(self, model: torch.nn.Module, optimizer: DistributedOptimizer, micro_batch_size: int = 1,
-                 loss_scale: float = 1.0, forward_fn: Optional[Callable] = None):
+                 loss_scale: float = 1.0, forward_fn: Optional[Callable] = None, seq_split_num: int = 1):
         self.model = model
         self.optimizer = optimizer
-        if isinstance(model, PipelineChunks):
-            # pipeline stages: 1F1B (interleaved when the rank owns several chunks) over NCCL point-to-point
+        if isinstance(model, PipelineChunks) or int(seq_split_num or 1) > 1:
+            # pipeline stages: 1F1B (interleaved when the rank owns several chunks) over NCCL point-to-point; with
+            # seq_split_num > 1 the sequence pipeline (chunks of a sequence as pipeline units, keys / values carried)
             from ..parallel.pipeline import PipelineTrainStep
-            self.step_fn = PipelineTrainStep(list(model.chunks), optimizer, micro_batch_size=micro_batch_size,
-                                             loss_scale=loss_scale)
+            chunks = list(model.chunks) if isinstance(model, PipelineChunks) else [model]
+            self.step_fn = PipelineTrainStep(chunks, optimizer, micro_batch_size=micro_batch_size,
+                                             loss_scale=loss_scale, seq_split_num=seq_split_num)
         else:
             self.step_fn = TrainOneStep(model, optimizer, micro_batch_size=micro_batch_size, loss_scale=loss_scale,
                                         forward_fn=forward_fn)

@@ -185,14 +185,14 @@ def test_auto_trans_ckpt_loads_a_tp2_checkpoint_into_one_rank(tmp_path):
     assert ctx["initial_epoch"] == 0 and ctx["initial_step"] == 14            # 7 steps of 16 samples = 14 steps of 8
 
 
-def _simulate_pipeline(pp, v, n):
+def _simulate_pipeline(pp, v, n, seq_split=1):
     """Blocking-rendezvous model of the pipeline schedule: a batch (at most one send and one receive on one ring) starts
     when its rank has computed what it sends and the rank's previous batch on that ring has finished; it finishes when
     both of its operations have met their counterparts, i.e. when the peers' matching batches have STARTED. A forward
     needs the previous activation batch finished, a backward the previous gradient batch. Returns True when every rank
     reaches the end of its schedule."""
     from mindformers_b200.parallel.pipeline import build_schedule
-    sched = [build_schedule(pp, v, n, r) for r in range(pp)]
+    sched = [build_schedule(pp, v, n, r, seq_split) for r in range(pp)]
     # batches per (rank, ring) in issue order: (step index, send k or None, recv k or None)
     rings = {}
     for r in range(pp):
@@ -290,6 +290,58 @@ def test_pipeline_schedule_has_no_communication_cycle(pp, v):
                     done_f.add((fwd_chunk(s.fwd, pp, v), s.fwd % pp + (s.fwd // (pp * v)) * pp))
                 if s.bwd is not None:
                     assert (bwd_chunk(s.bwd, pp, v), s.bwd % pp + (s.bwd // (pp * v)) * pp) in done_f
+
+
+def test_sequence_pipeline_schedule_orders_chunks_and_never_deadlocks():
+    """``seq_split = C``: forward units (micro-batch, chunk) in order, backward with the chunks of a micro-batch reversed;
+    a backward never comes before the forward of its unit, nor before the backward of a later chunk of its micro-batch;
+    the rings meet without a cycle for every stage count."""
+    from mindformers_b200.parallel.pipeline import build_schedule, seq_bwd_unit
+    assert [seq_bwd_unit(b, 3) for b in range(6)] == [2, 1, 0, 5, 4, 3]
+    for pp, n, C in [(2, 2, 2), (2, 3, 4), (3, 4, 2), (4, 4, 3), (4, 8, 2), (8, 8, 4), (2, 1, 8)]:
+        assert _simulate_pipeline(pp, 1, n, C), f"sequence pipeline deadlocks: pp={pp} n={n} C={C}"
+        for r in range(pp):
+            steps = build_schedule(pp, 1, n, r, C)
+            assert [s.fwd for s in steps if s.fwd is not None] == list(range(n * C))
+            assert [s.bwd for s in steps if s.bwd is not None] == list(range(n * C))
+            done_f, done_b = set(), set()
+            for s in steps:
+                if s.fwd is not None:
+                    done_f.add(s.fwd)
+                if s.bwd is not None:
+                    u = seq_bwd_unit(s.bwd, C)
+                    m, c = divmod(u, C)
+                    assert u in done_f, (pp, n, C, r, "backward before its forward")
+                    assert all(m * C + later in done_b for later in range(c + 1, C)), "a later chunk must go first"
+                    done_b.add(u)
+    with pytest.raises(ValueError):
+        build_schedule(2, 2, 4, 0, 2)
+
+
+def test_sequence_chunks_with_carried_keys_and_values_match_the_whole_sequence():
+    """One stage: a micro-batch run as 4 sequence chunks (keys / values carried forward, chunks backward in reverse with
+    the gradients of the carried tensors fed back) gives the loss and the gradients of the whole-sequence run."""
+    import torch
+    from mindformers_b200.parallel import parallel_state as ps
+    from mindformers_b200.parallel.layers.gpt_model import GPTModel
+    from mindformers_b200.parallel.pipeline import forward_backward_no_pipelining
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    ps.initialize_model_parallel()
+    torch.manual_seed(3)
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=128,
+                            vocab_size=128, seq_length=32, max_position_embeddings=32, params_dtype="float32",
+                            compute_dtype="float32", pad_token_id=-1)
+    cfg.device = "cpu"
+    model = GPTModel(cfg)
+    ids = torch.randint(0, 128, (3, 33))
+    mbs = [{"input_ids": ids[i:i + 1, :-1].contiguous(), "labels": ids[i:i + 1, 1:].contiguous()} for i in range(3)]
+    whole = forward_backward_no_pipelining(model, mbs)
+    ref = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    chunked = forward_backward_no_pipelining(model, mbs, seq_split=4)
+    assert torch.allclose(torch.stack(whole), torch.stack(chunked), atol=1e-6)
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, ref[n], atol=2e-6), n
 
 
 @pytest.mark.parametrize("mode", ["ep", "etp"])

@@ -69,6 +69,21 @@ def test_pipeline_two_stages_from_the_configuration_matches_one_process(tmp_path
         assert abs(a - b) < 2e-4, (got, single_losses)
 
 
+def test_sequence_pipeline_from_the_configuration_matches_one_process(tmp_path, single_losses):
+    """``seq_split_num: 2`` over two stages: every micro-batch flows through the pipeline as two sequence chunks, each
+    stage carries the keys and values of the first chunk to the second, chunks run backward in reverse; with data
+    parallel 2 next to it. The losses are those of the unsharded run."""
+    par = dict(data_parallel=1, model_parallel=1, pipeline_stage=2, micro_batch_num=4, seq_split_num=2)
+    got = _launch(tmp_path, "pp2seq2", _cfg(tmp_path / "o", parallel=par, use_parallel=True), 2)
+    assert len(got) == len(single_losses) == 4
+    for a, b in zip(got, single_losses):
+        assert abs(a - b) < 2e-4, (got, single_losses)
+    par = dict(data_parallel=2, model_parallel=1, pipeline_stage=2, micro_batch_num=2, seq_split_num=4)
+    got = _launch(tmp_path, "pp2dp2seq4", _cfg(tmp_path / "o2", parallel=par, use_parallel=True), 4)
+    for a, b in zip(got, single_losses):
+        assert abs(a - b) < 2e-4, (got, single_losses)
+
+
 def test_pipeline_interleaved_with_data_parallel_matches_one_process(tmp_path, single_losses):
     par = dict(data_parallel=2, model_parallel=1, pipeline_stage=2, micro_batch_num=2, pp_interleave_num=2)
     got = _launch(tmp_path, "pp2dp2", _cfg(tmp_path / "o", parallel=par, use_parallel=True), 4)
@@ -178,8 +193,8 @@ def test_trainer_honours_optimizer_type_and_rejects_unbuilt_modes(tmp_path):
     assert len(hist) == 3 and all(x == x and x < 10 for x in hist)
     assert opt.global_step == 3 and any("exp_avg" in k for k in opt.named_states())     # CAME's factored moments exist
     context._CONTEXT = None
-    bad = _cfg(tmp_path / "d", steps=1, parallel=dict(seq_split_num=2))
-    with pytest.raises(NotImplementedError):
+    bad = _cfg(tmp_path / "d", steps=1, parallel=dict(seq_split_num=2))      # the sequence pipeline needs stages
+    with pytest.raises(ValueError, match="pipeline_stage > 1"):
         Trainer(args=bad).train()
     context._CONTEXT = None
     cfg = _cfg(tmp_path / "e", steps=2, batch_size=2, micro_batch_interleave_num=2)
