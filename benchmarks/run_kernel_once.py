@@ -112,6 +112,10 @@ def rope():
     pos = torch.arange(T, device="cuda") % 4096
     for _ in range(3):
         Fn.rope(x, cos, sin, pos, heads, 128, False).backward(bf(T, heads, 128, scale=0.1))
+    with torch.no_grad():
+        ms = _timed(lambda: Fn.rope(x, cos, sin, pos, heads, 128, False))
+    nbytes = 2 * T * heads * 128 * 2
+    print(f"rope forward: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s ({nbytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
 
 
 def ce():
@@ -132,6 +136,10 @@ def adamw():
         Fn.grad_sumsq(g, ss)
         Fn.adamw_step(p, lo, m, v, g, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step, sumsq=ss,
                       max_norm=1.0)
+    ms = _timed(lambda: Fn.adamw_step(p, lo, m, v, g, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=5,
+                                      sumsq=ss, max_norm=1.0))
+    nbytes = n * (4 + 2 * 2 + 2 * 2 + 4 * 2 + 4 * 2)      # grad read; bf16 param, int16 remainder, m, v read + written
+    print(f"adamw: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s ({nbytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
 
 
 def router():
@@ -360,7 +368,71 @@ def fp8_moe_decode():
           f"({gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth), status {_lib.read_status()}")
 
 
-CASES = dict(fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+def _timed(fn, iters=5, warm=2):
+    for _ in range(warm):
+        fn()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(iters):
+        fn()
+    ev[1].record()
+    torch.cuda.synchronize()
+    return ev[0].elapsed_time(ev[1]) / iters
+
+
+def w8a8():
+    """W8A8 GEMM (int8 x int8 -> int32 in tensor memory, scales in the epilogue) at the Llama-8B linear shapes, 8192
+    tokens; beside it the bf16 product of the same shape on this repository's kernel and on cuBLAS."""
+    T = 8192
+    for N, K, tag in ((6144, 4096, "qkv"), (4096, 4096, "proj"), (28672, 4096, "fc1"), (4096, 14336, "fc2")):
+        a = torch.randint(-127, 128, (T, K), device="cuda", dtype=torch.int8)
+        b = torch.randint(-127, 128, (N, K), device="cuda", dtype=torch.int8)
+        sa, sb = torch.rand(T, device="cuda") * 0.01, torch.rand(N, device="cuda") * 0.01
+        x, w = bf(T, K), bf(N, K, scale=0.05)
+        t_i8 = _timed(lambda: Fn.w8a8_gemm(a, sa, b, sb))
+        t_q = _timed(lambda: Fn.quantize_act_int8(x))
+        t_bf = _timed(lambda: Fn.gemm(x, w))
+        t_cb = _timed(lambda: torch.matmul(x, w.t()))
+        ops = 2.0 * T * N * K
+        print(f"w8a8 {tag}: T {T} N {N} K {K}: int8 {t_i8 * 1e3:.1f} us = {ops / t_i8 / 1e9:.0f} TOP/s; activation quantiser "
+              f"{t_q * 1e3:.1f} us; bf16 this repository {t_bf * 1e3:.1f} us = {ops / t_bf / 1e9:.0f} TFLOP/s; cuBLAS bf16 "
+              f"{t_cb * 1e3:.1f} us")
+
+
+def paged_int8():
+    """Paged decode attention over the int8 KV cache against the bf16 cache (same shapes as ``paged``)."""
+    lib = _lib.get_lib()
+    B, ctx, blk, nq, nkv, hd = 64, 2048, 128, 32, 8, 128
+    nblocks = B * ctx // blk
+    q = bf(B, nq, hd)
+    out = torch.empty_like(q)
+    tables = torch.arange(nblocks, device="cuda", dtype=torch.int32).view(B, ctx // blk).contiguous()
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    splits = lib.mfb_paged_decode_splits(B, nkv, blk, ctx // blk)
+    scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits) // 4, device="cuda")
+    for kind in ("bf16", "int8"):
+        if kind == "bf16":
+            kc, vc, ks, vs = bf(nblocks, blk, nkv, hd), bf(nblocks, blk, nkv, hd), None, None
+            kv_bytes = 2 * B * ctx * nkv * hd * 2
+        else:
+            kc = torch.randint(-127, 128, (nblocks, blk, nkv, hd), device="cuda", dtype=torch.int8)
+            vc = torch.randint(-127, 128, (nblocks, blk, nkv, hd), device="cuda", dtype=torch.int8)
+            ks = torch.rand(nblocks, blk, nkv, device="cuda") * 0.01
+            vs = torch.rand(nblocks, blk, nkv, device="cuda") * 0.01
+            kv_bytes = 2 * B * ctx * nkv * (hd + 4)
+
+        def call():
+            rc = lib.mfb_paged_decode_attention_ex(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), _lib.ptr(ks), _lib.ptr(vs),
+                                                   tables.data_ptr(), lens.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                                   splits, B, nq, nkv, hd, blk, ctx // blk, hd ** -0.5, _lib.stream_ptr())
+            _lib.check(rc, "paged")
+        ms = _timed(call, iters=5)
+        print(f"paged decode, {kind} cache: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of cache "
+              f"({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
+
+
+CASES = dict(w8a8=w8a8, paged_int8=paged_int8, fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

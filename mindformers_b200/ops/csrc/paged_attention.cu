@@ -14,6 +14,8 @@
 // int8 with one fp32 scale per (token, KV head) in a side array [num_blocks, block_size, kv_heads]; the write kernel
 // quantises (absmax / 127), the decode kernel reads 8 bytes per lane instead of 16 and multiplies by the scale, so
 // the bytes per cached token halve.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace mfb {
@@ -132,26 +134,28 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq,
     }
     // the trip count is the same for every lane of a warp (the shuffles below name all 32 lanes); a lane group
     // whose key lies beyond the end reads the last valid key and discards the result
-    // a fetched key / value slice: 16 bytes of bf16, or 8 bytes of int8 codes (in .x, .y) and the row's scale
-    struct Slice { uint4 k, v; float ks, vs; };
+    // a fetched key / value slice: 16 bytes of bf16, or 8 bytes of int8 codes and the row's scales
+    struct SliceBf { uint4 k, v; };
+    struct SliceI8 { uint2 k, v; float ks, vs; };
+    using Slice = typename std::conditional<INT8, SliceI8, SliceBf>::type;
     auto fetch = [&](int t0, Slice& s_) {
       const int tk = (t0 + sub < k_end) ? t0 + sub : k_end - 1;
       const int blk = table[tk / block_size];
       const size_t tok = (size_t)blk * block_size + tk % block_size;
       const size_t base = tok * row + (size_t)kvh * HD + dl * 8;
-      if (INT8) {
-        const uint2 a = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(key_cache_v) + base);
-        const uint2 c = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(value_cache_v) + base);
-        s_.k = make_uint4(a.x, a.y, 0, 0);
-        s_.v = make_uint4(c.x, c.y, 0, 0);
-        s_.ks = key_scale[tok * Hkv + kvh];
-        s_.vs = value_scale[tok * Hkv + kvh];
+      if constexpr (INT8) {
+        s_.k = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(key_cache_v) + base);
+        s_.v = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(value_cache_v) + base);
+        s_.ks = __ldg(key_scale + tok * Hkv + kvh);
+        s_.vs = __ldg(value_scale + tok * Hkv + kvh);
       } else {
         s_.k = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(key_cache_v) + base);
         s_.v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(value_cache_v) + base);
       }
     };
-    constexpr int DEPTH = 3;           // key rows in flight per lane group: hides HBM latency at 16 warps per SM
+    // key rows in flight per lane group: hides HBM latency at 16 warps per SM. The int8 rows are half as long, so twice
+    // as many are kept in flight for the same bytes on the wire.
+    constexpr int DEPTH = INT8 ? 6 : 3;
     Slice pipe[DEPTH];
     const int first = k_begin + warp * KPW;
 #pragma unroll
@@ -164,7 +168,7 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q,        // [B, Hq,
       for (int i = 0; i + 1 < DEPTH; ++i) pipe[i] = pipe[i + 1];
       if (t0 + DEPTH * SLOTS < k_end) fetch(t0 + DEPTH * SLOTS, pipe[DEPTH - 1]);
       float kf[8], vf[8];
-      if (INT8) {
+      if constexpr (INT8) {
         const int8_t* kb = reinterpret_cast<const int8_t*>(&cur.k);
         const int8_t* vb = reinterpret_cast<const int8_t*>(&cur.v);
 #pragma unroll
