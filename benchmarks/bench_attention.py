@@ -38,6 +38,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--probes", type=int, default=0, help="also time the backward kernel with its timing probes set")
     ap.add_argument("--poly", type=int, default=0, help="quarters of the exponentials on the FMA pipe for the headline rows")
     args = ap.parse_args()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -81,11 +82,19 @@ def main():
         lib.mfb_flash_attn_fwd2_set_poly(args.poly)
         t1, t2 = time_fn(ours_fwd, args.iters, flush), time_fn(sdpa_fwd, args.iters, flush)
         t3, t4 = time_fn(ours_fb, args.iters, flush), time_fn(sdpa_fb, args.iters, flush)
+        probes = {}
+        if args.probes and hasattr(lib, "mfb_flash_attn_bwd2_set_probe"):
+            # where the backward kernel's time goes (results are wrong while a probe is set): 1 = the dQ drain drops its
+            # staging and reduce-add, 2 = the compute warpgroups drop the exponentials, 3 = both
+            for bits in (1, 2, 3):
+                lib.mfb_flash_attn_bwd2_set_probe(bits)
+                probes[f"fwd_bwd_ms_probe{bits}"] = time_fn(ours_fb, args.iters, flush)
+            lib.mfb_flash_attn_bwd2_set_probe(0)
         rows.append({"B": B, "S": S, "nq": nq, "nkv": nkv, "ours_fwd_ms": t1, "sdpa_fwd_ms": t2,
                      "ours_fwd_tflops": fl_fwd / t1 / 1e9, "sdpa_fwd_tflops": fl_fwd / t2 / 1e9,
                      "ours_fwd_bwd_ms": t3, "sdpa_fwd_bwd_ms": t4,
                      "ours_fwd_bwd_tflops": 3.5 * fl_fwd / t3 / 1e9, "sdpa_fwd_bwd_tflops": 3.5 * fl_fwd / t4 / 1e9,
-                     "fwd_variants_tflops": variants})
+                     "fwd_variants_tflops": variants, **probes})
         print(rows[-1], flush=True)
     print("status word:", _lib.read_status())
     if args.out:

@@ -125,6 +125,9 @@ def _declare(lib):
     sig("mfb_cp_barrier", [I, I, I, I, P, P, P])
     sig("mfb_gemm_fp8_blockscaled", [P, P, P, P, L, P, I, I, I, L, L, L, I, I, P, P, P, P])
     sig("mfb_quant_act_1x128", [P, L, P, L, P, L, L, I, P])
+    if hasattr(lib, "mfb_flash_attn_bwd2_set_probe"):
+        lib.mfb_flash_attn_bwd2_set_probe.argtypes = [I]
+        lib.mfb_flash_attn_bwd2_set_probe.restype = None
     sig("mfb_reshape_and_cache_int8", [P, P, P, P, P, P, P, L, I, I, L, L, P])
     sig("mfb_gather_cache_int8", [P, P, P, P, P, I, I, I, I, I, I, P])
     sig("mfb_paged_decode_attention_ex", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])

@@ -46,6 +46,8 @@ struct Args {
   const int* doc_start;    // [B, Sq] packed sequences: start of each token's document (null: one document per row)
   const int* doc_end;      // [B, Sq] one past the last position of each token's document
   int* status;
+  int probe;               // timing probes (results are wrong): bit 0 the drain drops its staging and reduce-add,
+                           // bit 1 the compute warpgroups drop the exponentials and the dS arithmetic
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -317,10 +319,16 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           for (int g = 0; g < 8; ++g) {
             const float4 l = l4[g];
             const int q0 = h * 64 + c * 32 + g * 4;
-            float p0 = ex2f(fmaf(__uint_as_float(r[g * 4 + 0]), args.scale_log2, -l.x));
-            float p1 = ex2f(fmaf(__uint_as_float(r[g * 4 + 1]), args.scale_log2, -l.y));
-            float p2 = ex2f(fmaf(__uint_as_float(r[g * 4 + 2]), args.scale_log2, -l.z));
-            float p3 = ex2f(fmaf(__uint_as_float(r[g * 4 + 3]), args.scale_log2, -l.w));
+            float p0, p1, p2, p3;
+            if (args.probe & 2) {
+              p0 = __uint_as_float(r[g * 4 + 0]); p1 = __uint_as_float(r[g * 4 + 1]);
+              p2 = __uint_as_float(r[g * 4 + 2]); p3 = __uint_as_float(r[g * 4 + 3]);
+            } else {
+              p0 = ex2f(fmaf(__uint_as_float(r[g * 4 + 0]), args.scale_log2, -l.x));
+              p1 = ex2f(fmaf(__uint_as_float(r[g * 4 + 1]), args.scale_log2, -l.y));
+              p2 = ex2f(fmaf(__uint_as_float(r[g * 4 + 2]), args.scale_log2, -l.z));
+              p3 = ex2f(fmaf(__uint_as_float(r[g * 4 + 3]), args.scale_log2, -l.w));
+            }
             if (diag) {                                // a query sees keys up to its own position
               if (q0 + 0 < row) p0 = 0.f;
               if (q0 + 1 < row) p1 = 0.f;
@@ -480,6 +488,7 @@ flash_attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
+          if (args.probe & 1) continue;
           if (issuer) tma_wait_group_read<0>();         // the previous reduction has read the staging image
           named_bar_sync(kBarDrain, 128);
           uint8_t* irow = sdQ + row * 128;
@@ -550,6 +559,7 @@ __global__ void fb2_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __n
 
 namespace {
 int g_fb2_split = 0;   // 0 = choose from the problem size
+int g_fb2_probe = 0;
 }
 
 extern "C" {
@@ -557,6 +567,8 @@ using namespace mfb;
 
 // Split of a KV head's query-head group over CTAs: 0 lets the launcher choose, 1 / 2 / 4 force it.
 void mfb_flash_attn_bwd2_set_split(int split) { g_fb2_split = split; }
+// Timing probes for benchmarks (the results are wrong while one is set); see Args::probe.
+void mfb_flash_attn_bwd2_set_probe(int bits) { g_fb2_probe = bits; }
 
 static int fb2_choose_split(int B, int Sk, int Hq, int Hkv) {
   const int group = Hq / Hkv;
@@ -641,7 +653,7 @@ int mfb_flash_attn_bwd2_varlen(const void* q, const void* k, const void* v, cons
   a.seq_q = S; a.seq_k = Sk; a.q_off_tiles = q_offset / T128; a.num_q_heads = Hq; a.num_kv_heads = Hkv;
   a.group = Hq / Hkv; a.split = split; a.causal = causal;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
-  a.lse = lse; a.delta = delta; a.status = status; a.doc_start = doc_start; a.doc_end = doc_end;
+  a.lse = lse; a.delta = delta; a.status = status; a.doc_start = doc_start; a.doc_end = doc_end; a.probe = g_fb2_probe;
   constexpr int SMEM = 6 * fb2::kTileBytes + fb2::kSubBytes + 6 * T128 * 4 + 14 * 8 + 16 + 1024;
   static_assert(SMEM <= 232448, "shared memory budget exceeded");
   static bool attr_set = false;
