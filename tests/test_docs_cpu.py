@@ -61,3 +61,14 @@ def test_every_module_of_the_package_imports():
         except Exception as e:                         # noqa: BLE001 - the test reports every failure at once
             failed.append(f"{m.name}: {e!r}")
     assert not failed, failed
+
+
+def test_api_reference_pages_match_the_docstrings():
+    """``docs/api`` is generated from the docstrings; regenerate with ``python docs/build_api_docs.py`` after changing one."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "docs", "build_api_docs.py"), "--check"], capture_output=True,
+                         text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
