@@ -110,6 +110,58 @@ class TrainingArguments:
     profile_communication: bool = False
     profile_memory: bool = True
     push_to_hub: bool = False
+    # ---- context / parallel details ----
+    max_call_depth: int = 10000              # accepted for configuration compatibility (graph-compiler recursion limit)
+    save_graphs: bool = False                # no graph compiler here: kept so that existing argument files load
+    save_graphs_path: str = "./graph"
+    gradients_mean: bool = False
+    loss_repeated_mean: bool = True
+    enable_alltoall: bool = False
+    dataset_strategy: str = "full_batch"
+    search_mode: str = "sharding_propagation"
+    gradient_accumulation_shard: bool = False
+    parallel_optimizer_threshold: int = 64
+    optimizer_weight_shard_size: int = -1
+    strategy_ckpt_save_file: str = "./ckpt_strategy.ckpt"
+    gradient_aggregation_group: int = 4
+    micro_batch_interleave_num: int = 1
+    # ---- mixture of experts ----
+    expert_num: int = 1
+    capacity_factor: float = 1.05
+    aux_loss_factor: float = 0.05
+    num_experts_chosen: int = 1
+    # ---- recompute details ----
+    parallel_optimizer_comm_recompute: bool = False
+    mp_comm_recompute: bool = True
+    recompute_slice_activation: bool = False
+    # ---- dataset columns / loader ----
+    train_dataset_in_columns: Optional[List[str]] = None
+    train_dataset_out_columns: Optional[List[str]] = None
+    eval_dataset_in_columns: Optional[List[str]] = None
+    eval_dataset_out_columns: Optional[List[str]] = None
+    repeat: int = 1
+    prediction_loss_only: bool = False
+    python_multiprocessing: bool = False
+    numa_enable: bool = False
+    prefetch_size: int = 1
+    # ---- dynamic loss scale ----
+    loss_scale_factor: int = 2
+    loss_scale_window: int = 1000
+    max_scale_window: int = 1000
+    min_scale_window: int = 20
+    # ---- checkpoint / profiling / tuning ----
+    keep_checkpoint_per_n_minutes: int = 0
+    profile_end_step: Optional[int] = None
+    init_start_profile: bool = False
+    auto_tune: bool = False
+    filepath_prefix: str = "./autotune"
+    autotune_per_step: int = 10
+    # ---- hub ----
+    hub_model_id: Optional[str] = None
+    hub_strategy: str = "every_save"
+    hub_token: Optional[str] = None
+    hub_private_repo: bool = False
+    hub_always_push: bool = False
 
     _SCHEDULES = {"cosine": "CosineWithWarmUpLR", "linear": "LinearWithWarmUpLR", "constant": "ConstantWarmUpLR",
                   "constant_with_warmup": "ConstantWarmUpLR", "polynomial": "PolynomialWithWarmUpLR",
@@ -165,7 +217,33 @@ class TrainingArguments:
                                            pipeline_stage=self.pipeline_stage, micro_batch_num=self.micro_batch_num,
                                            use_seq_parallel=self.use_seq_parallel, optimizer_shard=self.optimizer_shard,
                                            vocab_emb_dp=self.vocab_emb_dp))
-        sec("recompute_config").update(dict(recompute=self.recompute, select_recompute=self.select_recompute))
+        sec("parallel_config").update(dict(gradient_aggregation_group=self.gradient_aggregation_group))
+        sec("parallel").update(dict(gradients_mean=self.gradients_mean, loss_repeated_mean=self.loss_repeated_mean,
+                                    enable_alltoall=self.enable_alltoall, search_mode=self.search_mode,
+                                    strategy_ckpt_save_file=self.strategy_ckpt_save_file,
+                                    parallel_optimizer_config=dict(
+                                        gradient_accumulation_shard=self.gradient_accumulation_shard,
+                                        parallel_optimizer_threshold=self.parallel_optimizer_threshold,
+                                        optimizer_weight_shard_size=self.optimizer_weight_shard_size)))
+        sec("context").update(dict(max_call_depth=self.max_call_depth, save_graphs=self.save_graphs,
+                                   save_graphs_path=self.save_graphs_path))
+        cfg["micro_batch_interleave_num"] = self.micro_batch_interleave_num
+        if self.expert_num > 1:
+            sec("moe_config").update(dict(expert_num=self.expert_num, capacity_factor=self.capacity_factor,
+                                          aux_loss_factor=self.aux_loss_factor, num_experts_chosen=self.num_experts_chosen))
+        sec("recompute_config").update(dict(recompute=self.recompute, select_recompute=self.select_recompute,
+                                            parallel_optimizer_comm_recompute=self.parallel_optimizer_comm_recompute,
+                                            mp_comm_recompute=self.mp_comm_recompute,
+                                            recompute_slice_activation=self.recompute_slice_activation))
+        if self.auto_tune:
+            cfg["auto_tune"], cfg["filepath_prefix"], cfg["autotune_per_step"] = True, self.filepath_prefix, self.autotune_per_step
+        if self.profile_end_step is not None:
+            cfg["profile_stop_step"] = self.profile_end_step
+        cfg["init_start_profile"] = self.init_start_profile
+        if self.push_to_hub or self.hub_model_id:
+            cfg["hub"] = dict(push_to_hub=self.push_to_hub, hub_model_id=self.hub_model_id, hub_strategy=self.hub_strategy,
+                              hub_token=self.hub_token, hub_private_repo=self.hub_private_repo,
+                              hub_always_push=self.hub_always_push)
         cfg["optimizer"] = dict(type=self._OPTIMS[self.optim.lower()], betas=[self.adam_beta1, self.adam_beta2],
                                 eps=self.adam_epsilon, weight_decay=self.weight_decay, learning_rate=self.learning_rate)
         lr = dict(type=self._SCHEDULES[self.lr_scheduler_type], learning_rate=self.learning_rate,
@@ -177,7 +255,15 @@ class TrainingArguments:
         else:
             lr["warmup_steps"] = self.warmup_steps
         cfg["lr_schedule"] = lr
-        cfg["runner_wrapper"] = dict(type=self.wrapper_type, scale_sense=self.scale_sense, use_clip_grad=self.use_clip_grad,
+        scale = self.scale_sense
+        if isinstance(scale, str) and scale.lower().startswith("dynamic"):
+            scale = dict(type="DynamicLossScaleUpdateCell", loss_scale_value=self.loss_scale_value,
+                         scale_factor=self.loss_scale_factor, scale_window=self.loss_scale_window)
+        elif isinstance(scale, str) and scale.lower().startswith("adaptive"):
+            scale = dict(type="AdaptiveLossScaleUpdateCell", loss_scale_value=self.loss_scale_value,
+                         scale_factor=self.loss_scale_factor, scale_window=self.loss_scale_window,
+                         max_scale_window=self.max_scale_window, min_scale_window=self.min_scale_window)
+        cfg["runner_wrapper"] = dict(type=self.wrapper_type, scale_sense=scale, use_clip_grad=self.use_clip_grad,
                                      max_grad_norm=self.max_grad_norm)
         metrics = self.metric_type if isinstance(self.metric_type, list) else [self.metric_type]
         cfg["metric"] = dict(type=metrics[0])
@@ -187,7 +273,8 @@ class TrainingArguments:
             cbs.append(dict(type="CheckpointMonitor", prefix=self.save_prefix, directory=self.save_directory,
                             save_checkpoint_steps=self.save_steps, save_checkpoint_seconds=self.save_seconds or 0,
                             keep_checkpoint_max=self.save_total_limit, save_network_params=self.save_network_params,
-                            save_trainable_params=self.save_trainable_params, async_save=self.async_save))
+                            save_trainable_params=self.save_trainable_params, async_save=self.async_save,
+                            keep_checkpoint_per_n_minutes=self.keep_checkpoint_per_n_minutes))
         cfg["callbacks"] = cbs
         if self.evaluation_strategy != "no":
             cfg["do_eval"] = True
@@ -200,6 +287,14 @@ class TrainingArguments:
                 sec(which).update(dict(data_loader=dict(type=self.dataset_type or "CommonDataLoader", path=path),
                                        shuffle=self.shuffle, drop_remainder=self.dataloader_drop_last,
                                        num_parallel_workers=self.dataloader_num_workers,
-                                       seed=self.data_seed if self.data_seed is not None else self.seed))
+                                       seed=self.data_seed if self.data_seed is not None else self.seed,
+                                       repeat=self.repeat, python_multiprocessing=self.python_multiprocessing,
+                                       numa_enable=self.numa_enable, prefetch_size=self.prefetch_size))
+                in_cols = self.train_dataset_in_columns if which == "train_dataset" else self.eval_dataset_in_columns
+                out_cols = self.train_dataset_out_columns if which == "train_dataset" else self.eval_dataset_out_columns
+                if in_cols:
+                    cfg[which]["input_columns"] = list(in_cols)
+                if out_cols:
+                    cfg[which]["output_columns"] = list(out_cols)
                 cfg[f"{which}_task"] = dict(type=self.dataset_task or "CausalLanguageModelDataset")
         return cfg

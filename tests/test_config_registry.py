@@ -306,3 +306,27 @@ def test_cross_field_rules_of_modes_datasets_recompute_and_swap():
     deep = "a: " + "{x: " * 12 + "1" + "}" * 12
     with pytest.raises(ValueError, match="nested deeper"):
         check_yaml_depth_before_loading(deep)
+
+
+def test_training_arguments_cover_the_reference_fields_and_map_to_sections():
+    import re
+    from mindformers_b200.trainer import TrainingArguments
+    a = TrainingArguments(expert_num=8, num_experts_chosen=2, capacity_factor=1.2, aux_loss_factor=0.01, scale_sense="dynamic",
+                          loss_scale_value=4096, loss_scale_window=500, micro_batch_interleave_num=2, mp_comm_recompute=False,
+                          train_dataset="/data/x.jsonl", train_dataset_in_columns=["input_ids", "labels"], repeat=2,
+                          keep_checkpoint_per_n_minutes=30, profile_end_step=7, hub_model_id="org/model",
+                          gradient_aggregation_group=8)
+    cfg = a.convert_args_to_mindformers_config()
+    assert cfg["moe_config"] == dict(expert_num=8, capacity_factor=1.2, aux_loss_factor=0.01, num_experts_chosen=2)
+    assert cfg["runner_wrapper"]["scale_sense"]["type"] == "DynamicLossScaleUpdateCell"
+    assert cfg["runner_wrapper"]["scale_sense"]["scale_window"] == 500
+    assert cfg["micro_batch_interleave_num"] == 2 and cfg["recompute_config"]["mp_comm_recompute"] is False
+    assert cfg["train_dataset"]["input_columns"] == ["input_ids", "labels"] and cfg["train_dataset"]["repeat"] == 2
+    ck = [c for c in cfg["callbacks"] if c["type"] == "CheckpointMonitor"][0]
+    assert ck["keep_checkpoint_per_n_minutes"] == 30 and cfg["profile_stop_step"] == 7
+    assert cfg["hub"]["hub_model_id"] == "org/model" and cfg["parallel_config"]["gradient_aggregation_group"] == 8
+    fields = set(TrainingArguments.__dataclass_fields__)
+    for name in ("max_call_depth", "gradients_mean", "enable_alltoall", "dataset_strategy", "parallel_optimizer_threshold",
+                 "recompute_slice_activation", "eval_dataset_out_columns", "prediction_loss_only", "max_scale_window",
+                 "auto_tune", "hub_always_push", "strategy_ckpt_save_file"):
+        assert name in fields, name
