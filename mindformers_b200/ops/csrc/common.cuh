@@ -74,16 +74,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One try: the thread is suspended by the hardware until the phase completes or the time hint (nanoseconds) runs
+// out, whichever comes first. Without a hint the suspension is short and a waiting warp keeps re-issuing the
+// instruction, which costs issue slots and, with a hundred waiting threads per SM, measurable power under the cap.
+constexpr uint32_t kMbarSuspendHintNs = 1000000u;   // 1 ms per try; the callers bound the total wait
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kMbarSuspendHintNs)
       : "memory");
   return ok;
 }
@@ -96,7 +100,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (((++it) & 0xff) == 0) {
+    if (((++it) & 0xf) == 0) {        // a try may last up to the suspend hint: look at the clock every 16 tries
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > MFB_WAIT_LIMIT_NS) {
         *abort_flag = 1;
