@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=4)
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--bands", type=int, default=0, help="also time the step with fixed raster bands (A/B)")
     ap.add_argument("--profiled-steps", type=int, default=1, help="consecutive steps inside one profiler session")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -104,7 +105,21 @@ def main():
         return {"label": label, "total_ms": total / 1e3, "step_ms": step_ms, "profiled_steps": args.profiled_steps, "span_ms": span_ms,
                 "gaps": [(k, c, t / 1e3) for k, c, t in gap_rows[:40]], "rows": [(k, c, t / 1e3) for k, c, t in rows[:60]]}
 
-    out = [shares("this repository")]
+    out = []
+    if args.bands:
+        # A/B of the raster band (plain CTA-pair GEMM, tensor-parallel GEMMs) inside the same process and clocks
+        import ctypes
+        from mindformers_b200.ops import _lib
+        lib = _lib.get_lib()
+        lib.mfb_tp_set_band.argtypes = [ctypes.c_int]
+        lib.mfb_tp_set_band.restype = None
+        for plain, tpb in ((8, 8), (16, 8), (0, 8), (0, 16), (0, 0), (8, 8)):
+            lib.mfb_gemm_pair_set_band(plain)
+            lib.mfb_tp_set_band(tpb)
+            out.append(shares(f"this repository, band plain={plain} tp={tpb} (0 = chosen from K)"))
+        lib.mfb_gemm_pair_set_band(0)
+        lib.mfb_tp_set_band(0)
+    out.append(shares("this repository"))
     Fn.set_gemm_backend("cublas")
     Fn.set_attention_backend("sdpa")
     fused_comm.set_enabled(False)

@@ -125,6 +125,9 @@ def _declare(lib):
     sig("mfb_cp_barrier", [I, I, I, I, P, P, P])
     sig("mfb_gemm_fp8_blockscaled", [P, P, P, P, L, P, I, I, I, L, L, L, I, I, P, P, P, P])
     sig("mfb_quant_act_1x128", [P, L, P, L, P, L, L, I, P])
+    if hasattr(lib, "mfb_gemm_pair_set_band"):
+        lib.mfb_gemm_pair_set_band.argtypes = [I]
+        lib.mfb_gemm_pair_set_band.restype = None
     if hasattr(lib, "mfb_flash_attn_bwd2_set_probe"):
         lib.mfb_flash_attn_bwd2_set_probe.argtypes = [I]
         lib.mfb_flash_attn_bwd2_set_probe.restype = None

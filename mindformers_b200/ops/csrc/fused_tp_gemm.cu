@@ -53,6 +53,7 @@ struct TpArgs {
   int probe;            // timing probes (results are wrong): bit 0 drops the peer stores and their fence, bit 1 the
                         // owner's wait for and reads of the peers' partial tiles
   int rs_lag;           // COMM 2: > 0 interleaves own and remote tiles after this many remote tiles (see rs_order)
+  int band;             // raster band of the CTA-pair walk, in pairs of row blocks
   int* status;
   // ---- COMM 1 ----
   const __nv_bfloat16* peer_a[kTpMaxRanks];  // chunk [rows_per_chunk, K] of every rank (row pitch lda)
@@ -134,7 +135,7 @@ __device__ __forceinline__ TpTile tp_tile(const TpArgs& a, int tile, int first_c
 // The same walk over pairs of row blocks: tile -> (pair of row blocks, column block); CTA `cta` of the cluster
 // takes row block 2 * pair + cta. Chunks hold an even number of row blocks, so a pair never straddles two ranks.
 __device__ __forceinline__ TpTile tp_tile_pair(const TpArgs& a, int tile, int first_chunk, int cta) {
-  constexpr int kBand = 8;
+  const int kBand = a.band;     // pairs of row blocks per raster band: 16 for K <= 4096, else 8 (see gemm_tcgen05_2cta.cu)
   const int num_pairs = a.num_m_blocks >> 1;
   const int tiles_per_band = kBand * a.num_n_blocks;
   const int band = tile / tiles_per_band;
@@ -737,6 +738,18 @@ bool g_tp_pair_enabled = true;
 bool g_tp_rs_interleave = true;
 int g_tp_probe = 0;
 
+// Raster band of the CTA-pair walk (pairs of row blocks): 16 for K <= 4096, else 8, cut down to a divisor of the pairs
+// per chunk so that a band never straddles two ranks' rows (the chunk order of the walk is what makes the waits safe).
+int g_tp_band = 0;   // > 0: fixed band (benchmarks)
+
+int tp_pair_band(int K, int rows_per_chunk) {
+  const int ppc = rows_per_chunk / (2 * mfb::kTpBM);
+  int band = (K <= 4096) ? 16 : 8;
+  if (g_tp_band > 0) band = g_tp_band;
+  while (band > 1 && (ppc < band || ppc % band)) band >>= 1;
+  return band;
+}
+
 template <int BN, int STAGES, bool B_MN, int COMM, bool PAIR = false>
 int tp_launch(const CUtensorMap& tA, const CUtensorMap& tAf, const CUtensorMap& tB, const CUtensorMap& tD,
               const TpArgs& a, cudaStream_t stream) {
@@ -814,6 +827,7 @@ int mfb_tp_allgather_gemm(const void* const* peer_a, long long lda, void* a_full
   // CTA pairs: 256-wide tiles and an even number of 128-row blocks per rank
   const bool pair = g_tp_pair_enabled && bn256 && (a.rows_per_chunk % (2 * kTpBM) == 0);
   a.num_n_blocks = (N + BN - 1) / BN;
+  a.band = tp_pair_band(K, a.rows_per_chunk);
   cudaMemsetAsync(block_flags, 0, sizeof(int) * a.num_m_blocks, stream);
   CUtensorMap tA, tAf, tB, tD;
   int rc;
@@ -852,6 +866,7 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
   const int BN = bn256 ? 256 : 128;
   const bool pair = g_tp_pair_enabled && bn256 && (a.rows_per_chunk % (2 * kTpBM) == 0);
   a.num_n_blocks = (N + BN - 1) / BN;
+  a.band = tp_pair_band(K, a.rows_per_chunk);
   CUtensorMap tA, tB, tD;
   int rc;
   const CUtensorMapDataType BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -868,7 +883,7 @@ int mfb_tp_gemm_reduce_scatter(const void* A, const void* B, void* D, int M, int
     // two waves of remote tiles first. The tile walk goes band by band (8 pairs or 16 row blocks): a chunk must be
     // whole bands for "the first (tp-1)/tp of the tiles" to be exactly the remote ones; otherwise chunk order is kept
     const int units = pair ? (a.num_m_blocks / 2) : a.num_m_blocks;
-    const int band = pair ? 8 : 16;
+    const int band = pair ? a.band : 16;
     if ((units / tp) % band == 0) a.rs_lag = 2 * (148 / (pair ? 2 : 1));
   }
   if (pair) return b_mn_major ? tp_launch<256, 6, true, 2, true>(tA, tA, tB, tD, a, stream)
@@ -937,6 +952,8 @@ int mfb_tp_gemm_allreduce(const void* A, const void* B, void* D, int M, int N, i
                     : tp_launch<128, 6, false, 3>(tA, tA, tB, tD, a, stream);
 }
 
+// Fix the raster band of the CTA-pair walk (0 = choose from K) for A/B measurements.
+void mfb_tp_set_band(int band) { g_tp_band = band; }
 // Timing probes of the reduce-scatter GEMM (see TpArgs::probe); results are wrong while a probe is set.
 void mfb_tp_set_probe(int bits) { g_tp_probe = bits; }
 

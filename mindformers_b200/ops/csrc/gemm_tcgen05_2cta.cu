@@ -45,6 +45,7 @@ struct Args {
   float* partials;    // [split_tiles][slices-1][2 CTAs][256 cols][128 rows] fp32
   int* flags;         // [split_tiles][slices-1][2 CTAs]
   int* status;
+  int band;           // tile rows per raster band (see get_unit)
 };
 
 struct Unit {
@@ -76,8 +77,10 @@ __device__ __forceinline__ Unit get_unit(const Args& g, int u) {
     w.kbn = kb1 - w.kb0;
     w.role = (w.slice == g.slices - 1) ? 2 : 1;
   }
-  // banded rasterisation: 8 tile rows share their B tiles through L2
-  constexpr int kBand = 8;
+  // banded rasterisation: the tile rows of a band share their B tiles through L2, and the band's A rows stay resident
+  // while the walk crosses all columns, so B is streamed from HBM once per band. The launcher picks the band as tall as
+  // keeps the band's rows of A (band x 256 x K bf16) within a third of L2.
+  const int kBand = g.band;
   const int tiles_per_band = kBand * g.num_n_tiles;
   const int band = tile / tiles_per_band;
   const int first_m = band * kBand;
@@ -479,7 +482,15 @@ int dispatch_pair(int a_mn, int b_mn, int out_mode, const CUtensorMap& tA, const
 
 }  // namespace
 
+namespace {
+int g_pair_band = 0;
+}
+
 extern "C" {
+
+// Raster band of the CTA-pair GEMM in tile rows: 0 = chosen from K (see the launcher), > 0 = fixed (for benchmarks).
+void mfb_gemm_pair_set_band(int band) { g_pair_band = band; }
+
 
 // Bytes of workspace `mfb_gemm_bf16_pair` may use for the split tail wave (partials, then flags).
 // The caller allocates it once, zero-filled, and passes the same buffer to every call on one stream;
@@ -557,6 +568,15 @@ int mfb_gemm_bf16_pair(const void* A, const void* B, void* D, int M, int N, int 
   args.partials = reinterpret_cast<float*>(workspace);
   args.flags = workspace ? reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + partial_bytes) : nullptr;
   args.status = status;
+  {
+    // 16 tile rows per band while the band's rows of A stay near 32 MB (K <= 4096), else 8. Measured under the power
+    // cap at 8192 x 28672 x 4096: 1337 / 1372 / 1266 TFLOP/s for bands of 8 / 16 / 32 (cuBLAS 1366); at K = 14336 a
+    // band of 8 is best. `g_pair_band` > 0 overrides the choice (benchmarks).
+    long long band = (K <= 4096) ? 16 : 8;
+    if (g_pair_band > 0) band = g_pair_band;
+    if (band > args.num_m_tiles) band = args.num_m_tiles;
+    args.band = static_cast<int>(band);
+  }
   return dispatch_pair(a_mn_major, b_mn_major, out_mode, tA, tB, tD, args, clusters, stream);
 }
 
