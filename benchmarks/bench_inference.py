@@ -100,21 +100,28 @@ def main():
     wall = time.perf_counter() - t0
     total_ms = ev[2].elapsed_time(ev[3])
     launches = _lib.launch_count()
-    graph_ms = 0.0
+    graph_ms = loop_ms = loop2_ms = 0.0
     if args.graph:
         # the same generation with the decode step replayed from a CUDA graph (captured inside the call: its cost is
-        # part of the time)
-        evg = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        evg[0].record()
-        out_g = model.generate(prompts, max_new_tokens=args.new, use_cuda_graph=True, **gen_kw)
-        evg[1].record()
-        sync()
-        graph_ms = evg[0].elapsed_time(evg[1])
+        # part of the time): first with the token selection on the host after every step, then with the selection and
+        # the state update on the device (tokens read back once per burst), whose second call reuses the capture
+        def timed(**kw):
+            evg = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            evg[0].record()
+            res = model.generate(prompts, max_new_tokens=args.new, use_cuda_graph=True, **kw, **gen_kw)
+            evg[1].record()
+            sync()
+            return evg[0].elapsed_time(evg[1]), res
+        graph_ms, out_g = timed(device_loop=False)
         graph_same = sum(a == b for a, b in zip(out, out_g)) / len(out)
-    t = torch.tensor([ttft_ms, total_ms, graph_ms], device="cuda")
+        loop_ms, out_l = timed(device_loop=True)
+        loop2_ms, out_l2 = timed(device_loop=True)
+        loop_same = sum(a == b for a, b in zip(out, out_l)) / len(out)
+        loop_same2 = sum(a == b for a, b in zip(out, out_l2)) / len(out)
+    t = torch.tensor([ttft_ms, total_ms, graph_ms, loop_ms, loop2_ms], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ttft_ms, total_ms, graph_ms = t.tolist()
+    ttft_ms, total_ms, graph_ms, loop_ms, loop2_ms = t.tolist()
     new_tokens = sum(len(o) - args.prompt for o in out)
     decode_ms = max(total_ms - ttft_ms, 1e-6)
     if rank == 0:
@@ -130,6 +137,11 @@ def main():
                 "decode_tokens_per_s": (new_tokens - args.batch) / max(graph_ms - ttft_ms, 1e-6) * 1e3,
                 "ms_per_decode_step": max(graph_ms - ttft_ms, 1e-6) / max(args.new - 1, 1),
                 "sequences_equal_to_eager": graph_same},
+            "device_loop_decode": None if not args.graph else {
+                "decode_tokens_per_s_first_call": (new_tokens - args.batch) / max(loop_ms - ttft_ms, 1e-6) * 1e3,
+                "decode_tokens_per_s": (new_tokens - args.batch) / max(loop2_ms - ttft_ms, 1e-6) * 1e3,
+                "ms_per_decode_step": max(loop2_ms - ttft_ms, 1e-6) / max(args.new - 1, 1),
+                "sequences_equal_to_eager": [loop_same, loop_same2]},
             "weights_gib_per_gpu": round(mem_weights, 2), "fp8": fp8_stats, "gpu_launches": launches,
             "kernel_status_word": _lib.read_status()}))
     if world > 1:

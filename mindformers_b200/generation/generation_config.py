@@ -41,6 +41,10 @@ class GenerationConfig:
         self.chunk_prefill_size = kwargs.pop("chunk_prefill_size", None)
         # capture the decode step in a CUDA graph (single-GPU models; falls back to eager launches otherwise)
         self.use_cuda_graph = kwargs.pop("use_cuda_graph", False)
+        # with use_cuda_graph: pick the tokens and advance the decode state on the device and read the tokens back once
+        # per ``device_loop_steps`` steps (greedy and plain temperature sampling; other settings keep the host loop)
+        self.device_loop = kwargs.pop("device_loop", True)
+        self.device_loop_steps = kwargs.pop("device_loop_steps", 16)
         self.seed = kwargs.pop("seed", None)
         self._extra = dict(kwargs)
 

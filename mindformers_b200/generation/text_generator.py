@@ -173,6 +173,124 @@ class GenerationMixin:
 
         return step
 
+    # ---- decode loop on the device -------------------------------------------------------------------------
+    def _device_loop(self, B: int, max_len: int, num_blocks: Optional[int]):
+        """KV cache, block tables and captured step of the device-side decode loop (``generation/device_loop.py``),
+        kept on the model per geometry: a later ``generate`` call of the same batch size and length class reuses the
+        cache memory and replays the graph captured by the first one. ``release_device_loops()`` frees them."""
+        alloc_len = -(-int(max_len) // 256) * 256
+        pool = self.__dict__.setdefault("_device_loops", {})
+        key = (B, alloc_len, int(num_blocks or 0))
+        entry = pool.get(key)
+        if entry is None:
+            while len(pool) >= 2:                       # each entry pins a KV cache: keep the two latest geometries
+                pool.pop(next(iter(pool)))
+            ctx, tables = self._set_kv_cache(B, alloc_len, num_blocks)
+            entry = pool[key] = {"ctx": ctx, "geometry": (tables.pool.num_blocks, tables.block_size, alloc_len),
+                                 "loop": None, "captures": 0}
+        return entry, entry["ctx"], BlockTables(*entry["geometry"])
+
+    def release_device_loops(self):
+        """Drop the KV caches and graphs kept by the device-side decode loop."""
+        self.__dict__.pop("_device_loops", None)
+
+    def _build_device_loop(self, entry, B: int, width: int, block_size: int, cap: int):
+        """Captures ``forward pass -> token selection -> state update`` of one decode step over static tensors."""
+        from .device_loop import DecodeState, decode_advance
+        ctx = entry["ctx"]
+        device = next(self.parameters()).device
+        tp = ps.get_tensor_model_parallel_world_size()
+        st = DecodeState.allocate(B, width, block_size, cap, device)
+        vocab = int(self.config.vocab_size)
+
+        def bind():
+            ctx.is_prefill = False
+            ctx.block_tables, ctx.slot_mapping, ctx.context_lens = st.table, st.slots, st.lens
+            ctx.q_seq_lens = torch.ones(B, dtype=torch.int32, device=device)
+            ctx.cu_q = list(range(B + 1))
+            ctx.last_token_index = torch.arange(B, dtype=torch.int64, device=device)
+
+        def step():
+            meta = AttnMeta(batch=1, seq_len=B, positions=st.pos, cache=ctx)
+            logits = self.model(st.tok, attn_meta=meta)
+            if tp > 1:          # vocabulary-parallel head: every rank gets the full row and picks the same token
+                parts = [torch.empty_like(logits) for _ in range(tp)]
+                torch.distributed.all_gather(parts, logits.contiguous(), group=ps.get_tensor_model_parallel_group())
+                logits = torch.cat(parts, dim=-1)
+            decode_advance(logits[:, :vocab].float(), st)
+
+        class _Eager:                 # CPU tensors: the "graph" is the step itself
+            replay = staticmethod(lambda: step())
+
+        def capture():
+            """Called with the state loaded for a real step: the warm-up runs advance it, so it is restored after."""
+            bind()
+            if device.type != "cuda":
+                entry["captures"] += 1
+                return _Eager
+            keep = {k: getattr(st, k).clone() for k in ("tok", "pos", "lens", "slots", "count", "finished", "hist")}
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                step()
+                step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            for k, v in keep.items():
+                getattr(st, k).copy_(v)
+            entry["captures"] += 1
+            return graph
+
+        return {"state": st, "capture": capture, "bind": bind, "graph": None, "cap": cap}
+
+    def _run_device_loop(self, entry, tables: BlockTables, seqs, prompts, finished, gcfg, eos, max_len, streamer, seed):
+        """Decode bursts until every sequence is finished. ``seqs`` already hold the first generated token."""
+        from .device_loop import read_burst
+        B = len(seqs)
+        burst = max(1, int(getattr(gcfg, "device_loop_steps", 16) or 16))
+        limits = [max_len if gcfg.max_new_tokens is None else len(p) + gcfg.max_new_tokens for p in prompts]
+        active = [not f for f in finished]
+        tables.reserve(limits, active)
+        table, slots = tables.assemble_pa_inc_inputs(active, 1)
+        loop = entry["loop"]
+        if loop is None or loop["cap"] < burst:
+            loop = entry["loop"] = self._build_device_loop(entry, B, tables.max_blocks_per_seq, tables.block_size, burst)
+        st = loop["state"]
+        st.load([s[-1] for s in seqs], [len(s) - 1 for s in seqs], table, slots, finished, limits)
+        temperature = float(gcfg.temperature) if gcfg.do_sample else 0.0
+        base_seed = int(seed if seed is not None else (gcfg.seed if gcfg.seed is not None else torch.initial_seed()))
+        st.set_sampling(eos, temperature, base_seed)
+        if loop["graph"] is None:
+            loop["graph"] = loop["capture"]()
+        loop["bind"]()          # the prefill pointed the cache context at its own tensors (matters to eager replays only)
+        new_tokens, bursts = 0, 0
+        while not all(finished):
+            if temperature > 0 and bursts:
+                st.set_sampling(eos, temperature, base_seed + 0x9E3779B1 * bursts)   # the history index restarts per burst
+            for _ in range(burst):
+                loop["graph"].replay()
+            got = read_burst(st, burst)
+            bursts += 1
+            for i, toks in enumerate(got):
+                if finished[i]:
+                    continue
+                for t in toks:
+                    seqs[i].append(t)
+                    new_tokens += 1
+                    if t in eos or len(seqs[i]) >= limits[i]:
+                        finished[i] = True
+                        break
+            if streamer is not None:
+                if B == 1:
+                    streamer.put(got[0])
+                else:
+                    for j in range(max(len(g) for g in got)):
+                        streamer.put([[g[j]] if j < len(g) else [gcfg.pad_token_id or 0] for g in got])
+        return new_tokens
+
     # ---- public API -----------------------------------------------------------------------------------
     def _check_device_status(self):
         """After the last token was read back: a kernel whose bounded wait ran out, or an expert-parallel receive
@@ -221,7 +339,16 @@ class GenerationMixin:
             processors.extend(logits_processor)
         warper = SamplingLogitsProcessor(True, gcfg.temperature, gcfg.top_k, gcfg.top_p) if gcfg.do_sample else None
         eos = set(gcfg.eos_ids())
-        ctx, tables = self._set_kv_cache(B, max_len, getattr(self.config, "num_blocks", None))
+        lockstep = ps.get_expert_model_parallel_world_size() > ps.get_tensor_model_parallel_world_size() \
+            and torch.distributed.is_available() and torch.distributed.is_initialized()
+        from .device_loop import fast_path_ok
+        loop_entry = None
+        if getattr(gcfg, "use_cuda_graph", False) and getattr(gcfg, "device_loop", True) \
+                and ps.get_pipeline_model_parallel_world_size() == 1 and ps.get_context_parallel_world_size() == 1 \
+                and fast_path_ok(gcfg, processors, B, lockstep):
+            loop_entry, ctx, tables = self._device_loop(B, max_len, getattr(self.config, "num_blocks", None))
+        else:
+            ctx, tables = self._set_kv_cache(B, max_len, getattr(self.config, "num_blocks", None))
         tables.init_cache_engine(B)
         # latency breakdown (``self.detailed_latency.enabled`` or MF_DETAILED_LATENCY=1) and a profiler window over
         # token indices (MF_PROFILE_START_TOKEN / MF_PROFILE_STOP_TOKEN), tools/debug_info.py
@@ -261,7 +388,8 @@ class GenerationMixin:
         if ps.get_expert_model_parallel_world_size() > ps.get_tensor_model_parallel_world_size() \
                 and torch.distributed.is_available() and torch.distributed.is_initialized():
             lockstep_group = ps.get_expert_model_parallel_group()
-        graph_step = self._graph_decoder(B, ctx, tables) if getattr(gcfg, "use_cuda_graph", False) else None
+        graph_step = self._graph_decoder(B, ctx, tables) \
+            if getattr(gcfg, "use_cuda_graph", False) and loop_entry is None else None
         step_index = 0
         while True:
             with latency.phase("postprocess", step_index == 0):
@@ -286,6 +414,13 @@ class GenerationMixin:
                 if int(flag.item()) == 0:
                     break
             elif all(finished):
+                break
+            if loop_entry is not None:
+                # the first token came from the prefill logits on the host; the rest of the generation runs as bursts
+                # of graph replays with the selection and the state update on the device
+                with latency.phase("predict", False):
+                    new_tokens += self._run_device_loop(loop_entry, tables, seqs, prompts, finished, gcfg, eos, max_len,
+                                                        streamer, seed)
                 break
             with latency.phase("preprocess", False):
                 act = [not f for f in finished]

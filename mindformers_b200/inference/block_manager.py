@@ -46,6 +46,13 @@ class CacheEngine:
             self.blocks.extend(self.pool.allocate(need))
         self.num_tokens = total
 
+    def reserve(self, total_tokens: int):
+        """Own enough blocks for ``total_tokens`` cached tokens without caching any: the block table of a sequence
+        then stays fixed while a device-side loop appends tokens."""
+        need = -(-int(total_tokens) // self.pool.block_size) - len(self.blocks)
+        if need > 0:
+            self.blocks.extend(self.pool.allocate(need))
+
     def release(self):
         self.pool.release(self.blocks)
         self.blocks, self.num_tokens = [], 0
@@ -107,6 +114,13 @@ class BlockTables:
             blocks = np.asarray(e.blocks, dtype=np.int64)
             slots.append(blocks[pos // self.block_size] * self.block_size + pos % self.block_size)
         return self._table(), np.concatenate(slots).astype(np.int32)
+
+    def reserve(self, totals, active=None):
+        """Reserve blocks for ``totals[i]`` tokens of every (active) sequence; returns the block tables."""
+        for i, e in enumerate(self.engines):
+            if active is None or active[i]:
+                e.reserve(int(totals[i]))
+        return self._table()
 
     def context_lens(self) -> np.ndarray:
         return np.asarray([e.num_tokens for e in self.engines], dtype=np.int32)

@@ -108,6 +108,9 @@ def _declare(lib):
     sig("mfb_dp_reduce_scratch", [])
     sig("mfb_dp_flag_words", [])
     sig("mfb_dp_reduce", [I, I, I, L, L, P, P, P, P, P, I, P, P])
+    sig("mfb_dp_bucket_rows", [])
+    sig("mfb_dp_announce", [I, I, I, I, P, P])
+    sig("mfb_dp_reduce_bucket", [I, I, I, I, L, L, P, P, P, P, P, I, P, P])
     sig("mfb_dp_adamw_allgather", [I, I, I, L, L, P, P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, F, F, F, P, P])
     sig("mfb_router_fwd", [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     sig("mfb_router_bwd", [P, P, P, P, P, I, I, I, I, I, F, P])
@@ -133,6 +136,7 @@ def _declare(lib):
         lib.mfb_flash_attn_bwd2_set_probe.restype = None
     sig("mfb_reshape_and_cache_int8", [P, P, P, P, P, P, P, L, I, I, L, L, P])
     sig("mfb_gather_cache_int8", [P, P, P, P, P, I, I, I, I, I, I, P])
+    sig("mfb_decode_advance", [P, I, I, I, P, P, P, P, P, I, I, P, I, P, P, P, P, P])
     sig("mfb_paged_decode_attention_ex", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     sig("mfb_gemm_w8a8", [P, P, P, P, P, P, I, I, I, L, L, L, P, P])
     sig("mfb_quant_act_int8", [P, L, P, L, P, P, L, I, P])

@@ -14,6 +14,14 @@
 //   dp_wait_kernel     one CTA that waits (bounded) for the "published" flags of all peers, so the next
 //                      forward pass on this stream sees complete parameters.
 //
+// Overlap with the backward pass: the layers' gradient ranges are reduced in buckets while the backward pass of
+// the last micro-batch is still running. After the backward kernels of a bucket, dp_announce_kernel (launching
+// stream) releases this rank's "bucket final" flag on every peer; on a side stream dp_wait_row_kernel (one warp,
+// bounded) waits for all peers' flags of that bucket and a dp_reduce_kernel without announce / wait sums the part
+// of the bucket that this rank owns. Only the one-warp wait kernel ever waits for another GPU, so the reduce
+// kernel cannot hold resources while waiting and the compute stream never waits for the side stream before the
+// end of the backward pass.
+//
 // Flags carry the step number (identical on all ranks), so they never need a reset. A rank cannot run ahead:
 // dp_wait of step t needs every peer's dp_adamw of step t, and a peer's dp_reduce of step t + 1 (the only
 // reader of this rank's gradients) comes after that in its stream. Every wait gives up after
@@ -73,12 +81,24 @@ __device__ bool dp_wait_all(const int* flags, int world, int want, int* status) 
   return ok != 0;
 }
 
+constexpr int kDpBucketRows = 64;      // bucket flag rows per step
+constexpr int kDpBucketFlagBase = 32;  // first int of the bucket rows inside a rank's flag array
+
+// SYNC: announce "gradients final" and wait for all peers inside the kernel (the pass after the backward pass).
+// !SYNC: the caller has already waited (dp_wait_row_kernel earlier in the stream); a wait that timed out left its
+// code in the status word, and the kernel then reads nothing.
+template <bool SYNC>
 __global__ void __launch_bounds__(kDpThreads)
 dp_reduce_kernel(DpArgs a, float* __restrict__ reduced, float* __restrict__ partials) {
-  // announce: this rank's gradients are final (they were written by earlier kernels of this stream)
-  if (blockIdx.x == 0 && threadIdx.x < a.world)
-    dp_st_release_sys(a.flags_peer[threadIdx.x] + a.rank, a.epoch);
-  const bool ok = dp_wait_all(a.flags_local, a.world, a.epoch, a.status);
+  bool ok;
+  if (SYNC) {
+    // announce: this rank's gradients are final (they were written by earlier kernels of this stream)
+    if (blockIdx.x == 0 && threadIdx.x < a.world)
+      dp_st_release_sys(a.flags_peer[threadIdx.x] + a.rank, a.epoch);
+    ok = dp_wait_all(a.flags_local, a.world, a.epoch, a.status);
+  } else {
+    ok = a.status == nullptr || *reinterpret_cast<volatile int*>(a.status) == 0;
+  }
   float acc = 0.f;
   if (ok) {
     const long long nvec = a.n >> 2;
@@ -205,9 +225,18 @@ __global__ void dp_wait_kernel(DpArgs a) {
   dp_wait_all(a.flags_local + kDpMaxRanks, a.world, a.epoch, a.status);
 }
 
-static inline int dp_grid(long long nvec) {
+// Bucket protocol: row `row` of the bucket flags. The announce follows the bucket's backward kernels in its stream.
+__global__ void dp_announce_kernel(DpArgs a, int row) {
+  if (threadIdx.x < a.world)
+    dp_st_release_sys(a.flags_peer[threadIdx.x] + kDpBucketFlagBase + row * kDpMaxRanks + a.rank, a.epoch);
+}
+__global__ void dp_wait_row_kernel(DpArgs a, int row) {
+  dp_wait_all(a.flags_local + kDpBucketFlagBase + row * kDpMaxRanks, a.world, a.epoch, a.status);
+}
+
+static inline int dp_grid(long long nvec, int max_ctas = 148 * 4) {
   long long blocks = (nvec + kDpThreads - 1) / kDpThreads;
-  const long long cap = 148 * 4;
+  const long long cap = max_ctas > 0 && max_ctas < 148 * 4 ? max_ctas : 148 * 4;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
@@ -221,7 +250,9 @@ using namespace mfb;
 // Number of floats of scratch that mfb_dp_reduce needs (block partials of the squared norm).
 int mfb_dp_reduce_scratch() { return 148 * 4; }
 // Number of ints in the per-rank flag array (two rows of kDpMaxRanks) plus the ticket word.
-int mfb_dp_flag_words() { return 2 * kDpMaxRanks + 8; }
+int mfb_dp_flag_words() { return kDpBucketFlagBase + kDpBucketRows * kDpMaxRanks; }
+// Number of gradient buckets per step that the bucket flag rows can tell apart.
+int mfb_dp_bucket_rows() { return kDpBucketRows; }
 
 static int fill_dp_args(DpArgs* a, int world, int rank, int epoch, long long begin, long long n,
                         const long long* peer_grad, const long long* peer_param, const long long* peer_flags,
@@ -253,8 +284,40 @@ int mfb_dp_reduce(int world, int rank, int epoch, long long begin, long long n, 
   DpArgs a;
   if (fill_dp_args(&a, world, rank, epoch, begin, n, peer_grad, nullptr, peer_flags, status)) return 1;
   const int grid = dp_grid(n >> 2);
-  dp_reduce_kernel<<<grid, kDpThreads, 0, stream>>>(a, reduced, scratch);
+  dp_reduce_kernel<true><<<grid, kDpThreads, 0, stream>>>(a, reduced, scratch);
   dp_sum_partials_kernel<<<1, 256, 0, stream>>>(scratch, grid, sumsq, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Bucket `row` of step `epoch`: this rank's gradients of the bucket are final (stream order) -> tell every peer.
+int mfb_dp_announce(int world, int rank, int epoch, int row, const long long* peer_flags, cudaStream_t stream) {
+  DpArgs a;
+  if (fill_dp_args(&a, world, rank, epoch, 0, 0, nullptr, nullptr, peer_flags, nullptr)) return 1;
+  if (row < 0 || row >= kDpBucketRows) {
+    mfb_host::set_error("dp optimizer: bucket row %d out of range (%d rows)", row, kDpBucketRows);
+    return 1;
+  }
+  dp_announce_kernel<<<1, 32, 0, stream>>>(a, row);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Waits (one warp, bounded) until every peer has announced bucket `row`, then reduces [begin, begin + n) of it
+// (the part this rank owns; n may be 0: wait only) and adds the squared norm of the result to *sumsq.
+int mfb_dp_reduce_bucket(int world, int rank, int epoch, int row, long long begin, long long n,
+                         const long long* peer_grad, const long long* peer_flags, float* reduced, float* scratch,
+                         float* sumsq, int max_ctas, int* status, cudaStream_t stream) {
+  DpArgs a;
+  if (fill_dp_args(&a, world, rank, epoch, begin, n, peer_grad, nullptr, peer_flags, status)) return 1;
+  if (row < 0 || row >= kDpBucketRows) {
+    mfb_host::set_error("dp optimizer: bucket row %d out of range (%d rows)", row, kDpBucketRows);
+    return 1;
+  }
+  dp_wait_row_kernel<<<1, 32, 0, stream>>>(a, row);
+  if (n > 0) {
+    const int grid = dp_grid(n >> 2, max_ctas);
+    dp_reduce_kernel<false><<<grid, kDpThreads, 0, stream>>>(a, reduced, scratch);
+    dp_sum_partials_kernel<<<1, 256, 0, stream>>>(scratch, grid, sumsq, 1);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -12,6 +12,8 @@ State names for checkpoints are ``adam_m.<param>`` / ``adam_v.<param>`` and ``gl
 from __future__ import annotations
 
 import math
+import os
+import re
 from typing import Callable, Dict, Optional, Union
 
 import torch
@@ -114,8 +116,11 @@ class DistributedOptimizer:
         self.skipped = torch.zeros(1, dtype=torch.int32, device=dev)
         # the fp32 master starts as the exact value of the bf16 parameter, i.e. remainder 0
         self._dp_epoch = 0
+        self._overlap = None          # state of the bucketed reduction that runs under the backward pass
+        self.overlap_grad_reduce = os.environ.get("MFB_DP_OVERLAP", "1") != "0"
         if self.fused_dp:
             self._setup_fused_dp(dev)
+            self._setup_overlap(dev)
 
     def _setup_fused_dp(self, dev):
         """Peer pointer tables and flag words of the fused reduce-scatter / AdamW / all-gather kernels."""
@@ -140,6 +145,114 @@ class DistributedOptimizer:
             dist.barrier()      # every rank's flag words are zero before anyone's first step
 
     # ---------------------------------------------------------------------------------------------
+    # Gradient reduction under the backward pass (the reference overlaps the data-parallel gradient reduction with
+    # the backward pass through MindSpore's ``enable_parallel_optimizer`` + ``parallel_speed_up.json``
+    # ``enable_grad_comm_opt``; wrapper/wrapper.py:255,560).
+    def _setup_overlap(self, dev):
+        """Finds, per fused buffer, the flat-buffer range of every decoder layer. The weight matrices of a layer are
+        consecutive in the buffer (same category, registration order), so a layer's range is final as soon as the
+        backward pass has left the layer. Everything else (embedding, head, norms, biases) stays with the pass
+        that follows the backward pass."""
+        from ..layers.transformer_layer import TransformerBlock
+        blocks = [(n, m) for n, m in self.model.named_modules() if isinstance(m, TransformerBlock) and len(m.layers)]
+        self._ov_blocks, self._ov_layers = [], {}
+        if len(blocks) != 1:
+            return
+        prefix, block = blocks[0]
+        pat = re.compile(r"^" + re.escape(prefix + "." if prefix else "") + r"layers\.(\d+)\.")
+        rows = _lib.get_lib().mfb_dp_bucket_rows()
+        for name, sh in self.shards.items():
+            if not getattr(sh, "fused", False):
+                continue
+            span: Dict[int, list] = {}
+            main_end = min(sh.buf.ranges.dup_begin, sh.buf.ranges.decay_end) if self.tp > 1 else sh.buf.ranges.decay_end
+            for pname, _, off, cnt in sh.buf.entries:
+                mt = pat.match(pname)
+                if mt is None or off >= main_end:
+                    continue
+                gid = int(mt.group(1))
+                end = (off + cnt + 127) // 128 * 128
+                lo_hi = span.setdefault(gid, [off, end])
+                lo_hi[0], lo_hi[1] = min(lo_hi[0], off), max(lo_hi[1], end)
+            ids = sorted(span)
+            # the ranges must tile one interval in layer order, otherwise a "final" range could hold other gradients
+            ok = bool(ids) and all(span[a][1] == span[b][0] for a, b in zip(ids, ids[1:]))
+            inside = sum(cnt for pname, _, off, cnt in sh.buf.entries
+                         if ids and span[ids[0]][0] <= off < span[ids[-1]][1] and pat.match(pname) is None)
+            if not ok or inside:
+                continue
+            group = max(1, -(-len(ids) // rows))              # layers per bucket, so that the rows suffice
+            self._ov_layers[name] = {"span": span, "ids": ids, "group": group}
+        if self._ov_layers:
+            self._ov_blocks = [block]
+            self._ov_stream = torch.cuda.Stream(device=dev)
+            self._ov_scratch = torch.zeros(_lib.get_lib().mfb_dp_reduce_scratch(), dtype=torch.float32, device=dev)
+            self._ov_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def begin_grad_overlap(self):
+        """Call before the forward pass of the step's last micro-batch: from then on each decoder layer's gradient
+        range is reduced over the data-parallel group as soon as the backward pass has finished the layer."""
+        self._overlap = None
+        if not (self.fused_dp and self.overlap_grad_reduce and getattr(self, "_ov_layers", None)):
+            return
+        if not all(getattr(self.shards[n], "fused", False) for n in self._ov_layers):
+            return                            # the shards are on the NCCL path (set_fused_dp(False))
+        self._dp_epoch += 1
+        self._ov_sumsq.zero_()
+        self._overlap = {"row": 0, "low": {n: None for n in self._ov_layers}, "pending": {n: [] for n in self._ov_layers},
+                         "event": None}
+        for b in self._ov_blocks:
+            b.grads_final_hook = self._layer_grads_final
+
+    def _layer_grads_final(self, gid: int):
+        ov = self._overlap
+        if ov is None or ov.get("stopped"):
+            return
+        lib = _lib.get_lib()
+        for name, info in self._ov_layers.items():
+            if gid not in info["span"]:
+                continue
+            pend = ov["pending"][name]
+            pend.append(gid)
+            first = gid == info["ids"][0]
+            if len(pend) < info["group"] and not first:
+                continue
+            lo = min(info["span"][g][0] for g in pend)
+            hi = max(info["span"][g][1] for g in pend)
+            pend.clear()
+            if ov["low"][name] is not None and hi != ov["low"][name]:
+                ov["stopped"] = True          # layers finished out of order: leave the rest to the closing pass
+                return
+            sh = self.shards[name]
+            row = ov["row"]
+            ov["row"] += 1
+            rc = lib.mfb_dp_announce(sh.world, sh.rank, self._dp_epoch, row, sh.peer_flags, _lib.stream_ptr())
+            _lib.check(rc, "mfb_dp_announce")
+            ev = torch.cuda.Event()
+            ev.record()
+            a, b = max(lo, sh.begin), min(hi, sh.end)
+            n = max(0, b - a)
+            self._ov_stream.wait_event(ev)
+            with torch.cuda.stream(self._ov_stream):
+                rc = lib.mfb_dp_reduce_bucket(sh.world, sh.rank, self._dp_epoch, row, a if n else 0, n, sh.peer_grad,
+                                              sh.peer_flags, sh.buf.grad_data.data_ptr() + 4 * (a if n else 0),
+                                              self._ov_scratch.data_ptr(), self._ov_sumsq.data_ptr(), 148,
+                                              _lib.status_word(sh.grad.device).data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "mfb_dp_reduce_bucket")
+            _lib.count_launch(4 if n else 2)
+            ov["low"][name] = lo
+            ov.setdefault("high", {}).setdefault(name, hi)
+
+    def _end_grad_overlap(self):
+        """Joins the side stream and returns, per buffer, the range that the buckets have covered."""
+        ov, self._overlap = self._overlap, None
+        for b in getattr(self, "_ov_blocks", []):
+            b.grads_final_hook = None
+        if ov is None:
+            return {}
+        torch.cuda.current_stream().wait_stream(self._ov_stream)
+        return {n: (lo, ov["high"][n]) for n, lo in ov["low"].items() if lo is not None}
+
     def zero_grad(self, set_to_none: bool = True):
         for buf in self.buffers.values():
             buf.zero_grad()
@@ -162,18 +275,24 @@ class DistributedOptimizer:
             if sh.world > 1 and not getattr(sh, "fused", False):
                 dist.reduce_scatter_tensor(sh.grad, buf.grad_data, op=dist.ReduceOp.SUM, group=sh.group)
 
-    def _global_sumsq(self):
+    def _global_sumsq(self, covered=None):
         self.sumsq.zero_()
         self._dup_sumsq.zero_()
+        if covered:
+            self.sumsq.add_(self._ov_sumsq)      # squared norm of the ranges that were reduced under the backward pass
         for name, sh in self.shards.items():
             if getattr(sh, "fused", False):
                 # reduce-scatter by peer loads; the squared norm of the reduced slice comes out of the same pass
-                rc = _lib.get_lib().mfb_dp_reduce(sh.world, sh.rank, self._dp_epoch, sh.begin, sh.len, sh.peer_grad,
-                                                  sh.peer_flags, sh.grad.data_ptr(), self._dp_scratch.data_ptr(),
-                                                  self.sumsq.data_ptr(), 1, _lib.status_word(sh.grad.device).data_ptr(),
-                                                  _lib.stream_ptr())
-                _lib.check(rc, "mfb_dp_reduce")
-                _lib.count_launch(2)
+                lo, hi = (covered or {}).get(name, (sh.end, sh.end))
+                pieces = [(sh.begin, min(sh.end, lo)), (max(sh.begin, hi), sh.end)] if lo < hi else [(sh.begin, sh.end)]
+                pieces = [(a, b) for a, b in pieces if b > a] or [(sh.begin, sh.begin)]    # the announce must still go out
+                for a, b in pieces:
+                    rc = _lib.get_lib().mfb_dp_reduce(sh.world, sh.rank, self._dp_epoch, a, b - a, sh.peer_grad,
+                                                      sh.peer_flags, sh.buf.grad_data.data_ptr() + 4 * a,
+                                                      self._dp_scratch.data_ptr(), self.sumsq.data_ptr(), 1,
+                                                      _lib.status_word(sh.grad.device).data_ptr(), _lib.stream_ptr())
+                    _lib.check(rc, "mfb_dp_reduce")
+                    _lib.count_launch(2)
             else:
                 Fn.grad_sumsq(sh.grad, self.sumsq, accumulate=True)
             r = sh.buf.ranges
@@ -201,9 +320,12 @@ class DistributedOptimizer:
     def reduce_and_norm(self) -> torch.Tensor:
         """Gradient reduction (tensor-parallel replicas, data-parallel reduce-scatter) and the squared global
         norm of the reduced gradients, without the parameter update: the first half of ``step``."""
-        self._dp_epoch += 1
+        started = self._overlap is not None      # begin_grad_overlap has already opened this step's epoch
+        covered = self._end_grad_overlap()
+        if not started:
+            self._dp_epoch += 1
         self.reduce_gradients()
-        return self._global_sumsq()
+        return self._global_sumsq(covered)
 
     def step(self, grad_scale: float = 1.0):
         """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""

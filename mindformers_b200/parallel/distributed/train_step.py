@@ -47,6 +47,8 @@ class TrainOneStep:
         den_total = torch.zeros_like(total)
         for i in range(n_mb):
             mb = {k: v[i * mbs:(i + 1) * mbs] for k, v in batch.items() if v is not None}
+            if i == n_mb - 1 and hasattr(opt, "begin_grad_overlap"):
+                opt.begin_grad_overlap()      # the last backward pass: layer gradients are reduced as they become final
             out = self.forward_fn(model, mb)
             if per_token:
                 num, den = out

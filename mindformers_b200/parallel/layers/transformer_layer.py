@@ -178,6 +178,9 @@ class TransformerBlock(nn.Module):
         self.recompute = bool(config.recompute) if not isinstance(config.recompute, (list, tuple)) else True
         self._recompute_layers = self._resolve_recompute(config.recompute)
         self._setup_selective_recompute_and_offload(config)
+        # ``grads_final_hook(layer_id)``: set by the optimizer for the forward pass of a step's last micro-batch; it is
+        # called during the backward pass as soon as every gradient of that layer's parameters has been written
+        self.grads_final_hook = None
 
     # reference defaults of ``select_recompute: true`` (``training_graph/transformer/utils.py:107-110``): the gated
     # activation of the MLP and of the shared experts; here these, the norms and the rotary embedding are what a
@@ -247,6 +250,11 @@ class TransformerBlock(nn.Module):
             self._offload.prune()
         for idx, layer in enumerate(self.layers):
             run = layer
+            if training and self.grads_final_hook is not None and pending.requires_grad:
+                # the gradient of a layer's input is the last thing its backward pass produces
+                def fire(_grad, _cb=self.grads_final_hook, _gid=self.layer_ids[idx]):
+                    _cb(_gid)
+                pending.register_hook(fire)
             if training and self._offload is not None and idx in self._offload_layers:
                 def run(p, r, ro, m, _layer=layer, _idx=idx):     # saved tensors of this layer go to pinned host memory
                     with self._offload.layer(_idx):

@@ -243,3 +243,60 @@ def test_int8_kv_cache_stores_codes_and_scales_and_tracks_the_bf16_cache():
     assert model2.config.kv_cache_dtype == "int8"
     out = model2.generate(prompts, max_new_tokens=3, do_sample=False)
     assert [len(x) for x in out] == [len(p) + 3 for p in prompts]
+
+
+def test_device_loop_matches_the_host_loop_and_reuses_its_capture():
+    """Token selection and state update as the last operation of the decode step (eager replays on CPU): same tokens
+    as the per-token host loop for prompts of different lengths, with an end token that stops one sequence early and
+    a length limit that falls inside a burst; the second call reuses the first call's cache and captured step."""
+    model = _tiny()
+    prompts = [[5, 9, 33, 7, 100, 2, 8], [12, 250, 3], [7]]
+    host = model.generate(prompts, max_new_tokens=11, do_sample=False)
+    loop = model.generate(prompts, max_new_tokens=11, do_sample=False, use_cuda_graph=True, device_loop_steps=4)
+    assert loop == host
+    eos = host[1][len(prompts[1]) + 5]                      # sixth generated token of the second sequence
+    host_e = model.generate(prompts, max_new_tokens=11, do_sample=False, eos_token_id=eos)
+    loop_e = model.generate(prompts, max_new_tokens=11, do_sample=False, eos_token_id=eos, use_cuda_graph=True,
+                            device_loop_steps=4)
+    assert loop_e == host_e and len(loop_e[1]) <= len(prompts[1]) + 6
+    entries = list(model._device_loops.values())
+    assert len(entries) == 1 and entries[0]["captures"] == 1
+    # a single new token never enters the loop; a burst longer than the generation is cut by the limit
+    assert model.generate(prompts, max_new_tokens=1, use_cuda_graph=True) == model.generate(prompts, max_new_tokens=1)
+    assert model.generate(prompts, max_new_tokens=3, use_cuda_graph=True, device_loop_steps=16) == \
+        model.generate(prompts, max_new_tokens=3)
+    model.release_device_loops()
+    assert not getattr(model, "_device_loops", None)
+
+
+def test_device_loop_sampling_is_seeded_and_follows_the_distribution():
+    from mindformers_b200.generation.device_loop import DecodeState, decode_advance
+    model = _tiny()
+    kw = dict(max_new_tokens=9, do_sample=True, top_k=0, top_p=1.0, temperature=0.7, use_cuda_graph=True,
+              device_loop_steps=4)
+    a = model.generate([[1, 2, 3], [9, 8]], seed=5, **kw)
+    b = model.generate([[1, 2, 3], [9, 8]], seed=5, **kw)
+    c = model.generate([[1, 2, 3], [9, 8]], seed=6, **kw)
+    assert a == b and a != c and [len(x) for x in a] == [12, 11]
+    # Gumbel-max draws follow softmax(logits / T)
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(1, 1)
+    counts = torch.zeros(4)
+    for s in range(600):
+        st = DecodeState.allocate(1, 8, 4, 4, "cpu")
+        st.table.copy_(torch.arange(8, dtype=torch.int32)[None])
+        st.limit.fill_(30)
+        st.set_sampling((), 0.5, seed=s)
+        decode_advance(logits, st)
+        counts[int(st.hist[0, 0])] += 1
+    want = torch.softmax(logits[0] / 0.5, -1)
+    assert (counts / 600 - want).abs().max() < 0.06
+    # state after one greedy step: token, position, length and slot move together; the end token freezes the sequence
+    st = DecodeState.allocate(2, 8, 4, 4, "cpu")
+    st.table.copy_(torch.tensor([[3, 5, 7, 9, 11, 13, 15, 17], [2, 4, 6, 8, 10, 12, 14, 16]], dtype=torch.int32))
+    st.load([10, 11], [6, 2], st.table.numpy(), [0, 0], [False, False], [30, 30])
+    st.set_sampling([1], 0.0, 0)
+    decode_advance(torch.tensor([[0.0, 0.0, 3.0, 0.0], [0.0, 9.0, 0.0, 0.0]]), st)
+    assert st.tok.tolist() == [[2, 11]] and st.pos.tolist() == [7, 2] and st.lens.tolist() == [8, 3]
+    assert st.slots.tolist() == [5 * 4 + 3, -1] and st.finished.tolist() == [0, 1] and st.hist[:, 0].tolist() == [2, 1]
+    decode_advance(torch.tensor([[0.0, 0.0, 3.0, 0.0], [0.0, 9.0, 0.0, 0.0]]), st)
+    assert st.hist[:, 1].tolist() == [2, -1] and st.pos.tolist() == [8, 2] and st.slots[0].item() == 7 * 4 + 0

@@ -642,9 +642,71 @@ def test_generate_with_cuda_graph_matches_eager(family):
     g = torch.Generator().manual_seed(1)
     prompts = torch.randint(3, 1024, (3, 128), generator=g).tolist()
     eager = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None)
-    graphed = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None, use_cuda_graph=True)
+    graphed = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None, use_cuda_graph=True,
+                             device_loop=False)
     assert eager == graphed
+    # selection and state update on the device, tokens read back once per burst of 5 steps; the second call replays the
+    # graph that the first one captured
+    for _ in range(2):
+        looped = model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=None, use_cuda_graph=True,
+                                device_loop_steps=5)
+        assert looped == eager
+    stop = eager[1][128 + 4]
+    assert model.generate(prompts, max_new_tokens=12, do_sample=False, eos_token_id=stop, use_cuda_graph=True,
+                          device_loop_steps=5) == model.generate(prompts, max_new_tokens=12, do_sample=False,
+                                                                 eos_token_id=stop)
+    entries = list(model._device_loops.values())
+    assert len(entries) == 1 and entries[0]["captures"] == 1
     assert _lib.read_status() == 0
+
+
+def test_decode_advance_kernel_matches_the_reference_and_samples_the_softmax():
+    from mindformers_b200.generation.device_loop import DecodeState, decode_advance
+    torch.manual_seed(3)
+    B, V, width, bs, cap = 37, 32003, 9, 16, 4
+
+    def fresh(device):
+        st = DecodeState.allocate(B, width, bs, cap, device)
+        g = torch.Generator().manual_seed(1)
+        table = torch.randint(0, 500, (B, width), generator=g, dtype=torch.int32)
+        table[5, 3:] = -1
+        pos = torch.randint(0, width * bs - 2, (B,), generator=g)
+        pos[7] = width * bs - 1                       # the next position is outside the table
+        fin = [i % 11 == 0 for i in range(B)]
+        lim = [int(p) + (2 if i % 5 == 0 else 40) for i, p in enumerate(pos)]
+        st.load(list(range(B)), pos.tolist(), table.numpy(), [0] * B, fin, lim)
+        st.set_sampling([17, 4242], 0.0, 0)
+        return st
+    logits = torch.randn(B, V + 5).to(torch.bfloat16).float()      # bf16-rounded values: ties at the maximum do occur
+    logits[3, 17] = 50.0
+    logits[9, 4242] = 50.0
+    logits[12, 100] = logits[12, 30000] = 60.0                      # a tie: the lower index wins
+    cpu, dev = fresh("cpu"), fresh("cuda")
+    for _ in range(3):
+        decode_advance(logits[:, :V], cpu)
+        decode_advance(logits.cuda()[:, :V], dev)
+    torch.cuda.synchronize()
+    for name in ("tok", "pos", "lens", "slots", "hist", "count", "finished"):
+        assert torch.equal(getattr(cpu, name), getattr(dev, name).cpu()), name
+    assert dev.hist[12, 0].item() == 100 and dev.finished[3].item() == 1 and dev.finished[7].item() == 1
+    # sampling: 4096 rows with the same logits, one draw each
+    n = 4096
+    st = DecodeState.allocate(n, 4, 16, 2, "cuda")
+    st.limit.fill_(60)
+    st.set_sampling((), 0.5, seed=11)
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0, -30.0], device="cuda")
+    decode_advance(row[None].repeat(n, 1), st)
+    first = st.hist[:, 0].clone()
+    freq = torch.bincount(first, minlength=5).float().cpu() / n
+    assert (freq - torch.softmax(row.cpu() / 0.5, -1)).abs().max() < 0.03
+    st.count.zero_()
+    st.pos.zero_()
+    decode_advance(row[None].repeat(n, 1), st)
+    assert torch.equal(st.hist[:, 0], first)                        # same seed, same history index: same draws
+    st.count.zero_()
+    st.set_sampling((), 0.5, seed=12)
+    decode_advance(row[None].repeat(n, 1), st)
+    assert not torch.equal(st.hist[:, 0], first)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 1024, 4096), (2048, 6144, 4096), (64, 520, 208), (4096, 4096, 14336)])

@@ -355,3 +355,44 @@ def test_moe_dispatcher_variants_match_a_dense_loop_over_experts(mode):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
                          env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
     assert res.returncode == 0, (res.stdout[-2000:], res.stderr[-3000:])
+
+
+def test_layer_gradients_are_final_when_the_layer_hook_fires():
+    """The hook that drives the bucketed data-parallel reduction fires once per layer, last layer first, and at that
+    moment the layer's weight gradients already hold their value for the step (the last micro-batch included)."""
+    import torch
+    from mindformers_b200.trainer.engine import TrainingEngine
+    cfg = dict(model_type="llama", num_hidden_layers=3, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+               intermediate_size=128, vocab_size=128, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=32)
+    torch.manual_seed(0)
+    eng = TrainingEngine.from_model_config(cfg, seq_length=32, device="cpu", dtype="float32", micro_batch_size=1)
+    opt, block = eng.optimizer, eng.model.decoder
+    ids = torch.randint(0, 128, (2, 33))
+    batch = {"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous()}
+    seen = {}
+
+    def record(gid):
+        layer = block.layers._modules[str(gid)]
+        seen[gid] = {n: p.main_grad.clone() if p.grad is None else p.main_grad + p.grad
+                     for n, p in layer.named_parameters()}
+
+    armed = []
+    opt.begin_grad_overlap = lambda: (armed.append(1), setattr(block, "grads_final_hook", record))
+    opt.max_grad_norm = 0.0
+    final = {}
+    orig = opt.reduce_and_norm
+
+    def spy():
+        block.grads_final_hook = None
+        out = orig()
+        for gid in block.layer_ids:
+            final[gid] = {n: p.main_grad.clone() for n, p in block.layers._modules[str(gid)].named_parameters()}
+        return out
+    opt.reduce_and_norm = spy
+    eng.train_step_device(batch)
+    assert armed == [1]                                   # armed once, for the last of the two micro-batches
+    assert list(seen) == [2, 1, 0]
+    for gid, grads in seen.items():
+        for n, g in grads.items():
+            assert g.abs().sum() > 0
+            torch.testing.assert_close(g, final[gid][n], rtol=0, atol=0)
