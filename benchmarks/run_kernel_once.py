@@ -432,7 +432,53 @@ def paged_int8():
               f"({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
 
 
-CASES = dict(w8a8=w8a8, paged_int8=paged_int8, fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+def bf16_decode():
+    """bf16 product with a few rows of activations (decode) at the Llama-3.1-8B linear shapes: the weight-on-rows
+    kernel against the general tcgen05 kernels and cuBLAS, with the weight bytes per second that each reaches. The
+    weights of the shapes together (1.3 GB) exceed L2, and the calls rotate over them, so every call reads HBM."""
+    shapes = ((6144, 4096, "qkv"), (4096, 4096, "proj"), (28672, 4096, "fc1"), (4096, 14336, "fc2"), (128256, 4096, "head"))
+    ws = {tag: bf(N, K, scale=0.05) for N, K, tag in shapes}
+    flush = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8)
+
+    def timed_cold(fn, iters=6):
+        fn()
+        tot = 0.0
+        for _ in range(iters):
+            flush.zero_()                                  # evict the weight from L2
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            fn()
+            ev[1].record()
+            torch.cuda.synchronize()
+            tot += ev[0].elapsed_time(ev[1])
+        return tot / iters
+    for T in (1, 8, 32, 64):
+        for N, K, tag in shapes:
+            x, w = bf(T, K), ws[tag]
+            res = {}
+            for name, ks in (("auto", 0), ("ks1", 1), ("ks2", 2), ("ks4", 4), ("ks8", 8), ("occ2", 16)):
+                if ks == 8 and T <= 16:
+                    continue
+                Fn.set_decode_gemm(True, ks)
+                res[name] = timed_cold(lambda: Fn.gemm(x, w))
+            Fn.set_decode_gemm(False)
+            res["general"] = timed_cold(lambda: Fn.gemm(x, w))
+            Fn.set_decode_gemm(True, 0)
+            res["cublas"] = timed_cold(lambda: torch.matmul(x, w.t()))
+            gbs = N * K * 2 / res["auto"] / 1e6
+            print(f"T={T:3d} {tag:5s} N={N:6d} K={K:5d}: " + "  ".join(f"{k} {v * 1e3:7.1f} us" for k, v in res.items())
+                  + f"   auto: {gbs:6.0f} GB/s = {gbs / 6523.7 * 100:.0f} % of measured HBM copy bandwidth")
+
+
+def bf16_decode_one():
+    """Three launches of the weight-on-rows product on one shape (8 tokens x the 28672 x 4096 up-projection, 235 MB of
+    weights: larger than L2), for a profiler capture."""
+    x, w = bf(8, 4096), bf(28672, 4096, scale=0.05)
+    for _ in range(3):
+        Fn.gemm(x, w)
+
+
+CASES = dict(bf16_decode=bf16_decode, bf16_decode_one=bf16_decode_one, w8a8=w8a8, paged_int8=paged_int8, fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

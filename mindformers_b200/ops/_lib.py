@@ -44,6 +44,8 @@ def _declare(lib):
     lib.mfb_last_error.restype = ctypes.c_char_p
     lib.mfb_abi_version.restype = c_int
     sig("mfb_gemm_bf16", [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P, I, P, I, P])
+    sig("mfb_gemm_bf16_decode_supported", [I, I, I])
+    sig("mfb_gemm_bf16_decode", [P, P, P, P, I, I, I, L, L, L, I, P, P])
     sig("mfb_gemm_bf16_pair", [P, P, P, I, I, I, I, I, I, I, I, I, P, I, P, I, P])
     lib.mfb_gemm_pair_workspace_bytes.argtypes = []
     lib.mfb_gemm_pair_workspace_bytes.restype = L

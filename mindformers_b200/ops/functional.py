@@ -136,6 +136,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     mode = _OUT_MODES[(out.dtype, bool(accumulate))]
     lib = _lib.get_lib()
     st = _lib.status_word(a.device)
+    if _DECODE_GEMM and M <= 64 and mode == 0 and not a_mn and not b_mn and K >= 64 and K % 8 == 0 \
+            and b.dtype == torch.bfloat16:
+        # a few rows of activations: the weight rows go on the MMA rows and every weight is streamed once
+        rc = lib.mfb_gemm_bf16_decode(a.data_ptr(), b.data_ptr(), out.data_ptr(), None, M, N, K, a.stride(0), b.stride(0),
+                                      out.stride(0), _DECODE_GEMM_KS, st.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "mfb_gemm_bf16_decode")
+        _lib.count_launch()
+        return out
     if _PAIR_GEMM and M >= 256 and N >= 256 and K >= 64:
         # 256 x 256 tiles on CTA pairs; the tail wave is split along K through a per-stream workspace
         ws = _pair_workspace(a.device) if _PAIR_SLICES > 1 and mode < 2 else None
@@ -156,6 +164,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 # Dense GEMMs of at least one 256 x 256 tile run on CTA pairs (``gemm_tcgen05_2cta.cu``); ``MFB_GEMM_PAIR=0``
 # keeps the single-CTA kernel for A/B measurements, ``MFB_GEMM_PAIR_SLICES`` bounds the K split of the tail wave.
 _PAIR_GEMM = os.environ.get("MFB_GEMM_PAIR", "1") != "0"
+# Products with at most 64 rows of activations (decode steps) take ``gemm_bf16_decode.cu``; ``MFB_BF16_DECODE_KERNEL=0``
+# keeps the general kernels, ``MFB_BF16_DECODE_KS`` fixes its K split (1, 2, 4, 8; 16 = two CTAs per SM) for measurements.
+_DECODE_GEMM = os.environ.get("MFB_BF16_DECODE_KERNEL", "1") != "0"
+_DECODE_GEMM_KS = int(os.environ.get("MFB_BF16_DECODE_KS", "0"))
+
+
+def set_decode_gemm(enabled: bool, force_ks: int = 0):
+    """Switch the small-row-count GEMM kernel (and fix its K split) at run time."""
+    global _DECODE_GEMM, _DECODE_GEMM_KS
+    _DECODE_GEMM, _DECODE_GEMM_KS = bool(enabled), int(force_ks)
+
 _PAIR_SLICES = int(os.environ.get("MFB_GEMM_PAIR_SLICES", "4"))
 _pair_ws_cache: dict = {}
 

@@ -805,3 +805,29 @@ def test_int8_kv_cache_write_decode_and_gather(hd, nq, nkv, block):
                                      causal=False)
         assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
         o += n
+
+
+@pytest.mark.parametrize("T", [1, 7, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 14336), (1000, 520), (28672, 1024), (256, 64), (20000, 2048)])
+def test_bf16_decode_gemm_matches_fp32_reference(T, N, K):
+    """Weight-on-rows product for 1 - 64 rows of activations: every K split (cluster reduce-scatter through distributed
+    shared memory), the two-CTAs-per-SM variant and the launcher's own choice, ragged N and K included; canary rows
+    around the output stay untouched."""
+    torch.manual_seed(T * 131 + N)
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    tol = 2e-2 * ref.abs().max().item() + 1e-3
+    try:
+        for ks in (0, 1, 2, 4, 8, 16):
+            Fn.set_decode_gemm(True, ks)
+            buf = torch.full((T + 2, N), 7.0, device="cuda", dtype=torch.bfloat16)
+            y = Fn.gemm(x, w, out=buf[1:T + 1])
+            torch.cuda.synchronize()
+            assert _lib.read_status() == 0
+            assert (y.float() - ref).abs().max().item() < tol, (ks, (y.float() - ref).abs().max().item())
+            assert torch.all(buf[0] == 7.0) and torch.all(buf[T + 1] == 7.0)
+            again = Fn.gemm(x, w)
+            assert torch.equal(again, y)                       # same bits on every run (fixed summation order)
+    finally:
+        Fn.set_decode_gemm(True, 0)
