@@ -478,7 +478,60 @@ def bf16_decode_one():
         Fn.gemm(x, w)
 
 
-CASES = dict(bf16_decode=bf16_decode, bf16_decode_one=bf16_decode_one, w8a8=w8a8, paged_int8=paged_int8, fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
+def paged_tc():
+    """Decode attention over the paged bf16 cache: tensor-core kernel against the CUDA-core split-KV kernel, 64 sequences
+    x 2048 cached tokens (0.54 GB of K/V, larger than L2) and a short-context case (8 x 640)."""
+    lib = _lib.get_lib()
+    for B, ctx, blk, nq, nkv in ((64, 2048, 128, 32, 8), (64, 2048, 16, 32, 8), (8, 640, 128, 32, 8), (16, 8192, 128, 32, 8)):
+        hd = 128
+        per = (ctx + blk - 1) // blk
+        nblocks = B * per
+        q = bf(B, nq, hd)
+        out = torch.empty_like(q)
+        kc, vc = bf(nblocks, blk, nkv, hd), bf(nblocks, blk, nkv, hd)
+        tables = torch.randperm(nblocks, device="cuda").to(torch.int32).view(B, per).contiguous()
+        lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        kv_bytes = 2 * B * ctx * nkv * hd * 2
+        s_tc = lib.mfb_paged_decode_tc_splits(B, nkv, per * blk)
+        s_cc = lib.mfb_paged_decode_splits(B, nkv, blk, per)
+        scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, max(s_tc, s_cc)) // 4, device="cuda")
+
+        def tc():
+            rc = lib.mfb_paged_decode_attention_tc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), lens.data_ptr(),
+                                                   out.data_ptr(), scratch.data_ptr(), s_tc, B, nq, nkv, nblocks, blk, per,
+                                                   hd ** -0.5, _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "paged tc")
+
+        def cc():
+            rc = lib.mfb_paged_decode_attention(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), lens.data_ptr(),
+                                                out.data_ptr(), scratch.data_ptr(), s_cc, B, nq, nkv, hd, blk, per,
+                                                hd ** -0.5, _lib.stream_ptr())
+            _lib.check(rc, "paged")
+        for name, fn, sp in (("tensor cores", tc, s_tc), ("CUDA cores", cc, s_cc)):
+            ms = _timed(fn, iters=5)
+            print(f"B={B} ctx={ctx} block={blk}: {name:12s} splits {sp:2d}: {ms * 1e3:7.1f} us, {kv_bytes / ms / 1e6:6.0f} GB/s of "
+                  f"cache ({kv_bytes / ms / 1e6 / 6523.7 * 100:.0f} % of measured HBM copy bandwidth)")
+
+
+def paged_tc_one():
+    """Three launches of the tensor-core paged decode kernel (64 x 2048 tokens, block 128), for a profiler capture."""
+    lib = _lib.get_lib()
+    B, ctx, blk, nq, nkv, hd = 64, 2048, 128, 32, 8, 128
+    per = ctx // blk
+    q, out = bf(B, nq, hd), torch.empty(B, nq, hd, device="cuda", dtype=torch.bfloat16)
+    kc, vc = bf(B * per, blk, nkv, hd), bf(B * per, blk, nkv, hd)
+    tables = torch.arange(B * per, device="cuda", dtype=torch.int32).view(B, per).contiguous()
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    sp = lib.mfb_paged_decode_tc_splits(B, nkv, ctx)
+    scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, sp) // 4, device="cuda")
+    for _ in range(3):
+        rc = lib.mfb_paged_decode_attention_tc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), tables.data_ptr(), lens.data_ptr(),
+                                               out.data_ptr(), scratch.data_ptr(), sp, B, nq, nkv, B * per, blk, per,
+                                               hd ** -0.5, _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "paged tc")
+
+
+CASES = dict(paged_tc=paged_tc, paged_tc_one=paged_tc_one, bf16_decode=bf16_decode, bf16_decode_one=bf16_decode_one, w8a8=w8a8, paged_int8=paged_int8, fp8=fp8, fp8_decode=fp8_decode, fp8_moe_decode=fp8_moe_decode, gemm=gemm, grouped=grouped, fa=fa, rmsnorm=rmsnorm, swiglu=swiglu, rope=rope, ce=ce, adamw=adamw, router=router, paged=paged, mla=mla, moe=moe)
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()

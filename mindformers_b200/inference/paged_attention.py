@@ -10,6 +10,8 @@ the block table, slot mapping and lengths for the current step.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import List, Optional
 
@@ -134,6 +136,19 @@ def _layer_scales(cache, layer):
     return None, None
 
 
+# Decode attention over a bf16 cache with head dim 128 runs on the tensor cores (``paged_decode_tc.cu``);
+# ``MFB_PAGED_DECODE=cuda_core`` (or ``set_paged_decode_kernel``) keeps the split-KV kernel on the CUDA cores, which also
+# serves head dim 64 and the int8 cache.
+_DECODE_KERNEL = "cuda_core" if os.environ.get("MFB_PAGED_DECODE", "tensor_core") == "cuda_core" else "tensor_core"
+
+
+def set_paged_decode_kernel(kind: str) -> None:
+    global _DECODE_KERNEL
+    if kind not in ("tensor_core", "cuda_core"):
+        raise ValueError("kind must be 'tensor_core' or 'cuda_core'")
+    _DECODE_KERNEL = kind
+
+
 def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
     """q: [T, nq, hd]; k/v: [T, nkv, hd] of the new tokens. Returns [T, nq*hd]."""
     cache: KVCacheContext = meta.cache
@@ -148,12 +163,28 @@ def paged_attention_forward(q, k, v, meta, layer_number: int, scale: float):
             qc = q.contiguous()
             lib = _lib.get_lib()
             max_blocks = cache.block_tables.shape[1]
+            ksc, vsc = _layer_scales(cache, layer)
+            if ksc is None and _DECODE_KERNEL == "tensor_core" \
+                    and lib.mfb_paged_decode_tc_supported(nq, nkv, hd, cache.block_size):
+                # bf16 cache, head dim 128: Q K^T and P V on the tensor cores, K / V tiles streamed by TMA
+                splits = lib.mfb_paged_decode_tc_splits(B, nkv, max_blocks * cache.block_size)
+                need = lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits)
+                scratch = getattr(cache, "_decode_scratch", None)
+                if scratch is None or scratch.numel() * 4 < need:
+                    scratch = cache._decode_scratch = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
+                kc = cache.key_cache[layer]
+                rc = lib.mfb_paged_decode_attention_tc(
+                    qc.data_ptr(), kc.data_ptr(), cache.value_cache[layer].data_ptr(), cache.block_tables.data_ptr(),
+                    cache.context_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), splits, B, nq, nkv, kc.shape[0],
+                    cache.block_size, max_blocks, float(scale), _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+                _lib.check(rc, "mfb_paged_decode_attention_tc")
+                _lib.count_launch(2)
+                return out.view(T, nq * hd)
             splits = lib.mfb_paged_decode_splits(B, nkv, cache.block_size, max_blocks)
             need = lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits)
             scratch = getattr(cache, "_decode_scratch", None)
             if scratch is None or scratch.numel() * 4 < need:
                 scratch = cache._decode_scratch = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
-            ksc, vsc = _layer_scales(cache, layer)
             rc = lib.mfb_paged_decode_attention_ex(
                 qc.data_ptr(), cache.key_cache[layer].data_ptr(), cache.value_cache[layer].data_ptr(),
                 _lib.ptr(ksc), _lib.ptr(vsc),

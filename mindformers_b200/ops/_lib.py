@@ -139,6 +139,9 @@ def _declare(lib):
     sig("mfb_reshape_and_cache_int8", [P, P, P, P, P, P, P, L, I, I, L, L, P])
     sig("mfb_gather_cache_int8", [P, P, P, P, P, I, I, I, I, I, I, P])
     sig("mfb_decode_advance", [P, I, I, I, P, P, P, P, P, I, I, P, I, P, P, P, P, P])
+    sig("mfb_paged_decode_tc_supported", [I, I, I, I])
+    sig("mfb_paged_decode_tc_splits", [I, I, I])
+    sig("mfb_paged_decode_attention_tc", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P])
     sig("mfb_paged_decode_attention_ex", [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     sig("mfb_gemm_w8a8", [P, P, P, P, P, P, I, I, I, L, L, L, P, P])
     sig("mfb_quant_act_int8", [P, L, P, L, P, P, L, I, P])

@@ -378,6 +378,15 @@ int mfb_paged_decode_attention_ex(const void* q, const void* key_cache, const vo
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
+// out[row, :] = merge of the `splits` partial results of every (sequence, query head) row.
+int mfb_paged_combine(const float* part_acc, const float* part_ml, void* out, int splits, int rows, int hd,
+                      cudaStream_t stream) {
+  if (hd == 128) paged_combine_kernel<128><<<rows, 128, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
+  else if (hd == 64) paged_combine_kernel<64><<<rows, 64, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, splits);
+  else { mfb_host::set_error("paged_combine: head dim %d", hd); return 1; }
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
 int mfb_paged_decode_attention(const void* q, const void* key_cache, const void* value_cache, const int* block_tables,
                                const int* context_lens, void* out, void* scratch, int splits, int B, int Hq, int Hkv,
                                int hd, int block_size, int max_blocks, float scale, cudaStream_t stream) {

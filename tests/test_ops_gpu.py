@@ -486,6 +486,52 @@ def test_paged_decode_attention_split_kv(hd, nq, nkv, block):
         assert torch.allclose(out[b].float(), ref[0, 0], rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref[0, 0]).abs().max())
 
 
+@pytest.mark.parametrize("nq,nkv,block", [(32, 8, 128), (8, 8, 16), (16, 1, 64), (28, 4, 32), (6, 2, 128)])
+def test_paged_decode_attention_on_tensor_cores(nq, nkv, block):
+    """tcgen05 decode attention over the paged bf16 cache against fp32 attention: ragged lengths (one token, a full
+    tile, several tiles + a tail), random block tables with unallocated (-1) tail entries, groups of 1 - 16 query
+    heads per KV head, every block size; forced split counts; same bits on a second run."""
+    torch.manual_seed(nq * 7 + block)
+    lib = _lib.get_lib()
+    hd = 128
+    assert lib.mfb_paged_decode_tc_supported(nq, nkv, hd, block)
+    lens = [1, 37, 128, 700, 1300, 129]
+    B = len(lens)
+    max_blocks = (max(lens) + block - 1) // block + 2
+    nblocks = B * max_blocks + 3
+    kc = (torch.randn(nblocks, block, nkv, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nblocks, block, nkv, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(nblocks)[:B * max_blocks].to(torch.int32).view(B, max_blocks).cuda()
+    table = perm.clone()
+    for b, n in enumerate(lens):
+        table[b, (n + block - 1) // block:] = -1          # blocks that were never allocated
+    q = (torch.randn(B, nq, hd, device="cuda") * 0.5).to(torch.bfloat16)
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    auto = lib.mfb_paged_decode_tc_splits(B, nkv, max_blocks * block)
+    outs = []
+    for splits in (auto, 1, 3, auto):
+        out = torch.full((B + 2, nq, hd), 9.0, device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(lib.mfb_paged_decode_scratch_bytes(B, nq, hd, splits) // 4, device="cuda")
+        rc = lib.mfb_paged_decode_attention_tc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), ctx.data_ptr(),
+                                               out[1:].data_ptr(), scratch.data_ptr(), splits, B, nq, nkv, nblocks, block,
+                                               max_blocks, hd ** -0.5, _lib.status_word(q.device).data_ptr(),
+                                               _lib.stream_ptr())
+        _lib.check(rc, "paged decode tc")
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        assert torch.all(out[0] == 9.0) and torch.all(out[B + 1] == 9.0)
+        outs.append(out[1:B + 1].clone())
+        for b, n in enumerate(lens):
+            rows = perm[b].long()
+            kk = kc[rows].reshape(-1, nkv, hd)[:n]
+            vv = vc[rows].reshape(-1, nkv, hd)[:n]
+            ref = Fn.attention_reference(q[b:b + 1].unsqueeze(0).float(), kk.unsqueeze(0).float(), vv.unsqueeze(0).float(),
+                                         causal=False)
+            err = (outs[-1][b].float() - ref[0, 0]).abs().max().item()
+            assert err < 2e-2, (splits, b, err)
+    assert torch.equal(outs[0], outs[3])
+
+
 @pytest.mark.parametrize("B,S,nh,causal", [(1, 128, 2, True), (2, 512, 4, True), (1, 1024, 16, True), (1, 384, 3, False)])
 def test_flash_attention_mla_shape_forward(B, S, nh, causal):
     """Forward kernel with 192-wide q/k heads and 128-wide v heads against fp32 softmax attention."""
