@@ -34,6 +34,33 @@ def _parse_mem(value) -> Optional[float]:
     return float(s)
 
 
+def resolve_3d_tensor_parallel(par, model_cfg) -> Optional[dict]:
+    """``use_3d_tensor_parallel`` with ``tp_x``, ``tp_y``, ``tp_z`` (reference ``modules/flash_attention.py:148-164,
+    352-353`` and ``modules/layers.py:1549-1551``): the model-parallel devices form a ``z x x x y`` grid on which an
+    activation ``[batch, heads, sequence, head_dim]`` is laid out with the heads over ``y`` and the sequence over
+    ``(cp, z, x)``. The same layout here is tensor parallelism of size ``tp_y`` (heads, and the rows / columns of the
+    linear layers) with context parallelism of size ``cp * tp_z * tp_x`` (the sequence); both settings are rewritten
+    in place, so every later reader of ``parallel_config`` (group construction, model configuration) sees the
+    two-level layout. Returns the resolved sizes, or None when the model does not ask for it."""
+    if model_cfg is None or not hasattr(model_cfg, "get") or not model_cfg.get("use_3d_tensor_parallel"):
+        return None
+    x, y, z = (int(model_cfg.get(k, 1) or 1) for k in ("tp_x", "tp_y", "tp_z"))
+    mp = int(par.get("model_parallel", 1) or 1)
+    done = par.get("_tensor_parallel_3d")
+    if done:
+        return dict(done)
+    if min(x, y, z) < 1 or x * y * z != mp:
+        raise ValueError(f"use_3d_tensor_parallel: tp_x * tp_y * tp_z = {x} * {y} * {z} must equal model_parallel = {mp}")
+    if model_cfg.get("use_seq_parallel") or par.get("use_seq_parallel"):
+        raise ValueError("use_3d_tensor_parallel cannot be combined with use_seq_parallel (the reference rejects it too)")
+    cp = int(par.get("context_parallel", 1) or 1)
+    out = {"tp_x": x, "tp_y": y, "tp_z": z, "model_parallel": y, "context_parallel": cp * x * z}
+    par["model_parallel"], par["context_parallel"] = out["model_parallel"], out["context_parallel"]
+    par["_tensor_parallel_3d"] = dict(out)
+    logger.info("3-D tensor parallelism %d x %d x %d: heads over %d devices, sequence over %d", x, y, z, y, cp * x * z)
+    return out
+
+
 class Context:
     """Singleton holding the effective settings."""
 
@@ -41,7 +68,14 @@ class Context:
         cfg = config or {}
         self.config = cfg
         ctx = dict(cfg.get("context") or {})
-        par = dict(cfg.get("parallel_config") or {})
+        raw_par = cfg.get("parallel_config") if hasattr(cfg, "get") else None
+        model_cfg = (cfg.get("model") or {}).get("model_config") if hasattr(cfg, "get") and cfg.get("model") else None
+        if raw_par is not None and hasattr(raw_par, "get"):
+            # rewrites model_parallel / context_parallel in the configuration itself: the model builder reads them too
+            self.tensor_parallel_3d = resolve_3d_tensor_parallel(raw_par, model_cfg)
+        else:
+            self.tensor_parallel_3d = None
+        par = dict(raw_par or {})
         self.use_parallel = bool(cfg.get("use_parallel", False))
         self.run_mode = cfg.get("run_mode")
         self.seed = cfg.get("seed", 1)

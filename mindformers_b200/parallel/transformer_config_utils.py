@@ -110,6 +110,8 @@ for _target, _aliases, _fn in _TABLE:
 
 # keys that a model configuration may carry without a TransformerConfig counterpart
 DEFAULT_WHITE_KEYS = {
+    # resolved into model_parallel / context_parallel before the model is built (core/context.py)
+    "use_3d_tensor_parallel", "tp_x", "tp_y", "tp_z",
     "model_type", "architectures", "type", "torch_dtype", "dtype", "transformers_version", "auto_map",
     "bos_token_id", "eos_token_id", "use_cache", "use_sliding_window", "sliding_window",
     "max_window_layers", "attention_bias_", "pretraining_tp", "mlp_bias", "monitor_config",

@@ -330,3 +330,27 @@ def test_training_arguments_cover_the_reference_fields_and_map_to_sections():
                  "recompute_slice_activation", "eval_dataset_out_columns", "prediction_loss_only", "max_scale_window",
                  "auto_tune", "hub_always_push", "strategy_ckpt_save_file"):
         assert name in fields, name
+
+
+def test_3d_tensor_parallel_maps_onto_tensor_and_context_parallel():
+    """``use_3d_tensor_parallel`` with tp_x / tp_y / tp_z: heads over y, sequence over (cp, z, x); the sizes must
+    multiply to model_parallel and sequence parallelism is rejected, as in the reference."""
+    import pytest
+    from mindformers_b200.core.context import build_context, resolve_3d_tensor_parallel
+    par = {"data_parallel": 1, "model_parallel": 8, "context_parallel": 2}
+    mc = {"use_3d_tensor_parallel": True, "tp_x": 2, "tp_y": 2, "tp_z": 2}
+    out = resolve_3d_tensor_parallel(par, mc)
+    assert out["model_parallel"] == 2 and out["context_parallel"] == 8
+    assert par["model_parallel"] == 2 and par["context_parallel"] == 8
+    assert resolve_3d_tensor_parallel(par, mc) == out                      # a second reader changes nothing
+    with pytest.raises(ValueError):
+        resolve_3d_tensor_parallel({"model_parallel": 8}, {"use_3d_tensor_parallel": True, "tp_x": 2, "tp_y": 2, "tp_z": 1})
+    with pytest.raises(ValueError):
+        resolve_3d_tensor_parallel({"model_parallel": 4, "use_seq_parallel": True},
+                                   {"use_3d_tensor_parallel": True, "tp_x": 2, "tp_y": 2, "tp_z": 1})
+    assert resolve_3d_tensor_parallel({"model_parallel": 4}, {"tp_x": 2}) is None
+    cfg = {"use_parallel": False, "context": {"device_target": "CPU"},
+           "parallel_config": {"model_parallel": 4}, "model": {"model_config": {"use_3d_tensor_parallel": True, "tp_x": 2,
+                                                                                 "tp_y": 2, "tp_z": 1}}}
+    ctx = build_context(cfg)
+    assert ctx.tensor_parallel_3d["context_parallel"] == 2 and cfg["parallel_config"]["model_parallel"] == 2
