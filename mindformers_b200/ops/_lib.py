@@ -107,6 +107,11 @@ def _declare(lib):
     lib.mfb_mla_decode_scratch_bytes.argtypes = [I, I, I]
     lib.mfb_mla_decode_scratch_bytes.restype = L
     sig("mfb_gather_cache", [P, P, P, P, I, I, I, I, I, P])
+    lib.mfb_ll_allreduce_buffer_bytes.argtypes = [I, L]
+    lib.mfb_ll_allreduce_buffer_bytes.restype = L
+    sig("mfb_ll_allreduce_state_words", [])
+    sig("mfb_ll_allreduce_init", [P, L, P])
+    sig("mfb_ll_allreduce", [P, P, L, L, I, I, P, P, P, P])
     sig("mfb_dp_reduce_scratch", [])
     sig("mfb_dp_flag_words", [])
     sig("mfb_dp_reduce", [I, I, I, L, L, P, P, P, P, P, I, P, P])

@@ -274,7 +274,15 @@ class RowParallelLinear(_Fp8WeightMixin, nn.Module):
                 if not fp8 and fused_comm.allreduce_enabled(self.config, x, self.weight):
                     y = fused_comm.linear_all_reduce(x, self.weight)      # inference: GEMM -> all-reduce in one kernel
                 else:
-                    y = M.reduce_from_tensor_model_parallel_region(self._mm(x))
+                    y = self._mm(x)
+                    from .. import ll_allreduce
+                    group = ps.get_tensor_model_parallel_group()
+                    if getattr(self.config, "fused_tp_comm", False) and ll_allreduce.usable(group, y):
+                        # decode-sized output (also of fp8 layers, also under CUDA-graph capture): one launch in which
+                        # the data carries its own arrival
+                        y = ll_allreduce.get(group)(y, out=y)
+                    else:
+                        y = M.reduce_from_tensor_model_parallel_region(y)
         else:
             y = self._mm(x)
         if self.bias is not None and not self.skip_bias_add:

@@ -40,3 +40,7 @@ def test_fused_context_parallel_attention():
 
 def test_tp_attention_ep_moe_inference_bf16_and_fp8():
     _run("run_tp_ep_inference.py")
+
+
+def test_low_latency_all_reduce():
+    _run("run_ll_allreduce.py")
