@@ -191,8 +191,17 @@ class GenerationMixin:
         return entry, entry["ctx"], BlockTables(*entry["geometry"])
 
     def release_device_loops(self):
-        """Drop the KV caches and graphs kept by the device-side decode loop."""
-        self.__dict__.pop("_device_loops", None)
+        """Drop the KV caches and graphs kept by the device-side decode loop. The capture closures refer back to their
+        entry, so the references are cut by hand: the graphs are destroyed now, not at some later garbage collection
+        (a live graph that holds collectives keeps ``destroy_process_group`` from returning)."""
+        pool = self.__dict__.pop("_device_loops", None) or {}
+        for entry in pool.values():
+            loop = entry.get("loop")
+            if loop:
+                loop["graph"] = None
+                loop.clear()
+            entry.clear()
+        pool.clear()
 
     def _build_device_loop(self, entry, B: int, width: int, block_size: int, cap: int):
         """Captures ``forward pass -> token selection -> state update`` of one decode step over static tensors."""
@@ -421,6 +430,13 @@ class GenerationMixin:
                 with latency.phase("predict", False):
                     new_tokens += self._run_device_loop(loop_entry, tables, seqs, prompts, finished, gcfg, eos, max_len,
                                                         streamer, seed)
+                if torch.distributed.is_available() and torch.distributed.is_initialized() \
+                        and torch.distributed.get_world_size() > 1:
+                    # the captured step holds collectives of the process groups: a graph that outlives the call keeps
+                    # their communicators busy (destroy_process_group then never returns), so it is dropped here and
+                    # only single-process generation reuses its capture
+                    torch.cuda.synchronize(device)
+                    self.release_device_loops()
                 break
             with latency.phase("preprocess", False):
                 act = [not f for f in finished]
