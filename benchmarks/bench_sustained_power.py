@@ -7,7 +7,7 @@ benchmark (a few launches after an idle gap) does not see that. This script loop
 ``nvidia-smi`` (SM clock, power draw) ten times a second and reports TFLOP/s, TFLOP/s per GHz and joules per PFLOP over
 the settled part of the run, for this repository's CTA-pair GEMM at several raster bands and for cuBLAS.
 
-    python benchmarks/bench_sustained_power.py --tokens 8192 --seconds 3 --out gpurun_out/sustained.json
+    python benchmarks/bench_sustained_power.py --tokens 8192 --seconds 3 --out sustained.json
 
 It reads clocks and power only; it changes no GPU setting."""
 import argparse
