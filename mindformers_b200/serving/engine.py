@@ -13,6 +13,11 @@ One iteration (``step()``):
 3. if requests were admitted, one prefill call runs their prompts (long prompts in chunks of ``max_prefill_tokens``);
    otherwise one decode call advances every running request by a token — before it, the newest requests are
    preempted while the pool cannot give every running request the block its next token may need;
+   When every running request decodes greedily (or at one common temperature without top-k / top-p / penalties) and
+   shares its stop tokens, the decode call is a BURST instead (``decode_burst`` steps, default 8): the step was
+   captured in a CUDA graph together with the token selection and the update of positions and cache slots
+   (``generation/device_loop.py``), the graph is replayed ``decode_burst`` times without host work in between, and
+   the tokens are read back once. Requests that finish inside a burst stop there; new arrivals wait for its end;
 4. the next token of every request that was served is chosen (greedy, or temperature / top-k / top-p / penalties with
    a per-request seeded generator), stop conditions are checked and the ``on_token`` callbacks are called.
 
@@ -116,8 +121,10 @@ class ServingEngine:
     prefill call."""
 
     def __init__(self, model, max_num_seqs: int = 8, max_model_len: Optional[int] = None, num_blocks: Optional[int] = None,
-                 max_prefill_tokens: int = 8192, eos_token_id=None):
+                 max_prefill_tokens: int = 8192, eos_token_id=None, decode_burst: int = 8):
         self.model = model.eval()
+        self.decode_burst = int(decode_burst)         # < 2: every decode step returns to the host
+        self._loop = None                             # captured step + its static tensors (built by the first burst)
         cfg = model.config
         self.max_num_seqs = int(max_num_seqs)
         self.max_model_len = int(max_model_len or getattr(cfg, "seq_length", 2048))
@@ -143,7 +150,7 @@ class ServingEngine:
         self._thread: Optional[threading.Thread] = None
         self.finished_metrics: Deque[Dict[str, float]] = deque(maxlen=4096)
         self.counters = {"requests": 0, "finished": 0, "aborted": 0, "preempted": 0, "prefill_tokens": 0,
-                         "decode_tokens": 0, "steps": 0}
+                         "decode_tokens": 0, "steps": 0, "bursts": 0}
         self._by_id: Dict[str, Request] = {}
 
     # ---- submission (any thread) ---------------------------------------------------------------------------------
@@ -273,9 +280,109 @@ class ServingEngine:
                 return need > self.tables.pool.num_free
             while short() and len(self._admit_order) > 1:
                 self._preempt(self._admit_order[-1])
+            burst = self._burst_length()
+            if burst >= 2:
+                return self._decode_burst(burst)
             served = self._decode()
         self._choose_tokens(served)
         return served
+
+    # ---- decode bursts on the device --------------------------------------------------------------------------------
+    def _stop_ids(self, r: Request):
+        ids = set(r.params.stop_token_ids)
+        if not r.params.ignore_eos:
+            ids |= self.eos_ids
+        return ids
+
+    def _burst_length(self) -> int:
+        """Steps the running batch may take without the host: 0 unless every running request can be served by the
+        device-side selection with ONE setting, nobody waits for a slot that a finishing request would free, and the
+        pool can hold the burst's tokens."""
+        if self.decode_burst < 2 or self.waiting or self._incoming or self._aborts:
+            return 0
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            return 0                 # a graph that holds collectives must not outlive its process group
+        live = [r for r in self.running if r is not None]
+        first = live[0]
+        stops = self._stop_ids(first)
+        if len(stops) > 8:
+            return 0
+        for r in live:
+            if len(r.processors) or self._stop_ids(r) != stops:
+                return 0
+            if r.params.greedy != first.params.greedy:
+                return 0
+            if not r.params.greedy and (r.params.top_k not in (0, None) or (r.params.top_p or 1.0) < 1.0
+                                        or r.params.temperature != first.params.temperature):
+                return 0
+        steps = min(self.decode_burst, max(self._limit(r) - len(r.tokens) for r in live))
+        steps = max(steps, 0)
+        # blocks for the burst (the capture's warm-up runs may write three positions ahead)
+        reach = max(steps, 3 if self._loop is None or self._loop["graph"] is None else steps)
+        need = sum(max(0, self._blocks_for(min(r.cached + 1 + reach, self.max_model_len)) - len(self.tables.engines[r.slot].blocks))
+                   for r in live)
+        if need > self.tables.pool.num_free:
+            return 0
+        return steps if steps >= 2 else 0
+
+    def _limit(self, r: Request) -> int:
+        return min(len(r.prompt) + r.params.max_tokens, self.max_model_len)
+
+    def _decode_burst(self, steps: int) -> List[Request]:
+        from ..generation.device_loop import read_burst
+        B = self.max_num_seqs
+        live = [r for r in self.running if r is not None]
+        first = live[0]
+        if self._loop is None or self._loop["cap"] < self.decode_burst:
+            entry = {"ctx": self.ctx, "captures": 0}
+            self._loop = self.model._build_device_loop(entry, B, self.tables.max_blocks_per_seq, self.block_size,
+                                                       self.decode_burst)
+            self._loop["entry"] = entry
+        loop = self._loop
+        reach = max(steps, 3) if loop["graph"] is None else steps
+        active = [r is not None for r in self.running]
+        for r in live:
+            self.tables.engines[r.slot].reserve(min(r.cached + 1 + reach, self.max_model_len))
+        table, slots = self.tables.assemble_pa_inc_inputs(active, 1)
+        st = loop["state"]
+        toks = [self.running[i].tokens[-1] if active[i] else 0 for i in range(B)]
+        pos = [self.running[i].cached if active[i] else 0 for i in range(B)]
+        limits = [self._limit(self.running[i]) if active[i] else 1 for i in range(B)]
+        st.load(toks, pos, table, slots, [not a for a in active], limits)
+        seed = first.params.seed if first.params.seed is not None else hash(first.request_id) & 0x7FFFFFFF
+        st.set_sampling(sorted(self._stop_ids(first)), 0.0 if first.params.greedy else float(first.params.temperature),
+                        int(seed) + 7919 * self.counters["steps"])
+        if loop["graph"] is None:
+            loop["graph"] = loop["capture"]()
+        loop["bind"]()
+        for _ in range(steps):
+            loop["graph"].replay()
+        got = read_burst(st, steps)
+        self.counters["bursts"] += 1
+        now = time.perf_counter()
+        for r in live:
+            new = got[r.slot]
+            stops = self._stop_ids(r)
+            for tok in new:
+                r.output.append(tok)
+                r.cached += 1
+                self.counters["decode_tokens"] += 1
+                if r.t_first is None:
+                    r.t_first = now
+                if r.on_token is not None:
+                    r.on_token(r, tok)
+                if tok in stops:
+                    self.tables.engines[r.slot].num_tokens = r.cached
+                    self._release(r, "stop")
+                    break
+                if len(r.output) >= r.params.max_tokens or len(r.tokens) >= self.max_model_len:
+                    self.tables.engines[r.slot].num_tokens = r.cached
+                    self._release(r, "length")
+                    break
+            else:
+                self.tables.engines[r.slot].num_tokens = r.cached      # the device advanced without the host's bookkeeping
+        return live
 
     def _prefill(self, reqs: List[Request]) -> List[Request]:
         B = self.max_num_seqs

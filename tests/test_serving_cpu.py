@@ -128,3 +128,40 @@ def test_openai_style_http_endpoints_blocking_and_streaming():
             assert "mfb_serving_finished" in m and "mfb_serving_ttft_s_p50" in m
     finally:
         engine.shutdown()
+
+
+def test_decode_bursts_on_the_device_give_the_host_loop_tokens():
+    """With every running request greedy, decode runs as bursts of captured steps (eager replays on CPU) with the token
+    selection on the device: same tokens, same finish reasons, same streamed callbacks as with one host step per token,
+    for requests that finish inside a burst (length and stop token), join between bursts and differ in prompt length;
+    a request with a penalty or its own stop token sends the batch back to the host loop."""
+    model = _tiny()
+    budgets = [6, 9, 4, 12, 5]
+    free = model.generate([PROMPTS[1]], max_new_tokens=9, do_sample=False)[0][len(PROMPTS[1]):]
+    stop_tok = free[4]
+
+    def run(burst, extra=None):
+        eng = ServingEngine(model, max_num_seqs=3, max_model_len=48, max_prefill_tokens=8, eos_token_id=stop_tok,
+                            decode_burst=burst)
+        seen = {}
+        reqs = []
+        for i, (p, n) in enumerate(zip(PROMPTS, budgets)):
+            sp = SamplingParams(max_tokens=n, temperature=0.0)
+            if extra and i in extra:
+                sp = SamplingParams(max_tokens=n, temperature=0.0, **extra[i])
+            reqs.append(eng.add_request(f"r{i}", p, sp, on_token=lambda r, t: seen.setdefault(r.request_id, []).append(t)))
+        eng.run_until_idle()
+        st = eng.stats()
+        assert st["running"] == 0 and st["free_blocks"] == st["total_blocks"]
+        return [(r.output, r.finish_reason) for r in reqs], seen, eng.counters
+
+    host, host_seen, c0 = run(0)
+    dev, dev_seen, c1 = run(5)
+    assert c0["bursts"] == 0 and c1["bursts"] >= 2
+    assert dev == host and dev_seen == host_seen
+    assert any(reason == "stop" for _, reason in host) and any(reason == "length" for _, reason in host)
+    assert c1["decode_tokens"] == c0["decode_tokens"] and c1["steps"] < c0["steps"]
+    # ineligible companions: a repetition penalty, a private stop token
+    mixed_host, _, _ = run(0, {0: dict(repetition_penalty=1.3), 3: dict(stop_token_ids=[free[2]])})
+    mixed_dev, _, c2 = run(5, {0: dict(repetition_penalty=1.3), 3: dict(stop_token_ids=[free[2]])})
+    assert mixed_dev == mixed_host

@@ -33,3 +33,33 @@ def test_engine_matches_offline_generation_on_gpu(kv_dtype):
     assert all(r.output[:4] == w[:4] for r, w in zip(reqs, want)), [(r.output, w) for r, w in zip(reqs, want)]
     assert agree >= 3, agree
     assert engine.stats()["free_blocks"] == engine.stats()["total_blocks"]
+
+
+def test_engine_decode_bursts_replay_a_captured_step_on_gpu():
+    """Greedy requests through the engine with decode bursts (captured step + device-side token selection, eight replays
+    per host visit) and with one host step per token: same tokens for every request, fewer host iterations, one capture
+    for the whole run, no bounded wait ran out."""
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, max_position_embeddings=256, seq_length=256,
+                      params_dtype="bfloat16", compute_dtype="bfloat16", block_size=16)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg, device="cuda")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (37, 5, 130, 64, 9)]
+    budgets = [12, 20, 6, 9, 16]
+
+    def run(burst):
+        engine = ServingEngine(model, max_num_seqs=3, max_model_len=192, max_prefill_tokens=96, eos_token_id=None,
+                               decode_burst=burst)
+        reqs = [engine.add_request(f"r{i}", p, SamplingParams(max_tokens=n, temperature=0.0))
+                for i, (p, n) in enumerate(zip(prompts, budgets))]
+        engine.run_until_idle()
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        assert engine.stats()["free_blocks"] == engine.stats()["total_blocks"]
+        return [r.output for r in reqs], engine
+    host, e0 = run(0)
+    dev, e1 = run(8)
+    assert dev == host
+    assert e1.counters["bursts"] >= 2 and e1.counters["steps"] < e0.counters["steps"]
+    assert e1._loop["entry"]["captures"] == 1
