@@ -296,9 +296,8 @@ class ServingEngine:
 
     def _burst_length(self) -> int:
         """Steps the running batch may take without the host: 0 unless every running request can be served by the
-        device-side selection with ONE setting, nobody waits for a slot that a finishing request would free, and the
-        pool can hold the burst's tokens."""
-        if self.decode_burst < 2 or self.waiting or self._incoming or self._aborts:
+        device-side selection with ONE setting and the pool can hold the burst's tokens."""
+        if self.decode_burst < 2 or self._incoming or self._aborts:
             return 0
         import torch.distributed as dist
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
@@ -317,6 +316,10 @@ class ServingEngine:
                                         or r.params.temperature != first.params.temperature):
                 return 0
         steps = min(self.decode_burst, max(self._limit(r) - len(r.tokens) for r in live))
+        if self.waiting:
+            # requests queue for a slot: the burst ends when the first running request reaches its length limit, so
+            # the slot it frees is handed over at once
+            steps = min(steps, min(self._limit(r) - len(r.tokens) for r in live))
         steps = max(steps, 0)
         # blocks for the burst (the capture's warm-up runs may write three positions ahead)
         reach = max(steps, 3 if self._loop is None or self._loop["graph"] is None else steps)
