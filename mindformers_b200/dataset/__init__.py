@@ -8,3 +8,5 @@ from .modal_to_text_sft_dataset import ModalToTextSFTDataset
 from .indexed_dataset import IndexedDataset, IndexedDatasetBuilder
 from .dataloaders import (ADGenDataLoader, MultiSourceDataLoader, MultiSourceDataset, SFTDataLoader, ToolAlpacaDataLoader,
                           TrainingDataLoader, TrainingDataset, read_records)
+from .sampler import build_sampler
+from .transforms import build_transforms

@@ -240,14 +240,29 @@ class TokenMonitor:
 
 def _batched(dataset, cfg: dict, collate_fn=collate):
     shards, shard_id = data_shard_info()
-    sampler = ResumableShardSampler(len(dataset), shards, shard_id, bool(cfg.get("shuffle", False)),
-                                    int(cfg.get("seed", 0) or 0))
+    custom = (cfg.get("data_loader") or {}).get("sampler") if isinstance(cfg.get("data_loader"), dict) else None
+    custom = custom or cfg.get("sampler")
+    if custom:
+        # ``sampler: {type: ..., ...}`` in the dataset section (reference dataset/sampler/build_sampler.py): the named
+        # sampler replaces the resumable shard sampler; samplers that ask for it get the dataset size and the shard
+        from .sampler import build_sampler
+        import inspect
+        spec = dict(custom)
+        from ..tools.register import MindFormerModuleType, MindFormerRegister
+        params = inspect.signature(MindFormerRegister.get_cls(MindFormerModuleType.DATASET_SAMPLER, spec["type"]).__init__).parameters
+        for key, val in (("dataset_size", len(dataset)), ("num_shards", shards), ("shard_id", shard_id)):
+            if key in params and key not in spec:
+                spec[key] = val
+        sampler = build_sampler(spec)
+    else:
+        sampler = ResumableShardSampler(len(dataset), shards, shard_id, bool(cfg.get("shuffle", False)),
+                                        int(cfg.get("seed", 0) or 0))
     bs = int(cfg.get("batch_size", 1))
     loader = DataLoader(dataset, batch_size=bs, sampler=sampler, drop_last=bool(cfg.get("drop_remainder", True)),
                         collate_fn=collate_fn, num_workers=int(cfg.get("num_parallel_workers", 0) or 0),
                         pin_memory=bool(cfg.get("pin_memory", torch.cuda.is_available())))
     loader.shard_sampler = sampler
-    loader.set_init_step = lambda steps: sampler.set_skip(steps * bs)
+    loader.set_init_step = (lambda steps: sampler.set_skip(steps * bs)) if hasattr(sampler, "set_skip") else (lambda steps: None)
     return loader
 
 
