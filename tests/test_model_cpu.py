@@ -650,3 +650,26 @@ def test_hidden_and_attention_dropout_act_in_training_only():
     only_hidden = GPTModel(tiny_llama_config(hidden_dropout=0.5)).train()
     x = only_hidden(inp, lab)
     assert torch.isfinite(x)
+
+
+def test_build_model_config_and_base_model_alias(tmp_path):
+    """YAML-style builders: a configuration by registered class name or by model type, a network from the ``model``
+    section, and the older ``BaseModel`` base with ``load_checkpoint`` from ``checkpoint_name_or_path``."""
+    from mindformers_b200.models import BaseModel, LlamaConfig, LlamaForCausalLM, build_model, build_model_config
+    kw = dict(hidden_size=64, num_hidden_layers=1, num_attention_heads=4, vocab_size=96, intermediate_size=128)
+    assert isinstance(build_model_config({"type": "LlamaConfig", **kw}), LlamaConfig)
+    assert type(build_model_config({"model_type": "qwen2", **kw})).__name__ == "Qwen2Config"
+    assert build_model_config(None) is None
+    section = {"arch": {"type": "LlamaForCausalLM"},
+               "model_config": {"type": "LlamaConfig", "params_dtype": "float32", "compute_dtype": "float32", **kw}}
+    net = build_model(section, default_args={"device": "cpu"})
+    assert isinstance(net, LlamaForCausalLM)
+    net.save_pretrained(str(tmp_path / "m"))
+
+    class Mine(BaseModel):
+        config_class = LlamaConfig
+    cfg = LlamaConfig(params_dtype="float32", compute_dtype="float32", checkpoint_name_or_path=str(tmp_path / "m"), **kw)
+    other = Mine(cfg, device="cpu")
+    other.load_checkpoint(cfg)
+    for (n, a), (_, b) in zip(net.state_dict().items(), other.state_dict().items()):
+        assert torch.equal(a, b), n

@@ -104,3 +104,51 @@ def test_samplers_from_configuration():
     assert build_sampler() is None
     with pytest.raises(ValueError):
         build_sampler({"type": "DistributedSampler", "num_shards": 2, "shard_id": 2, "dataset_size": 4})
+
+
+def test_image_layout_helpers_and_array_transforms(tmp_path):
+    import base64
+    import io
+    from mindformers_b200.tools.image_tools import load_image
+    from mindformers_b200.utils.image_transforms import (center_crop, get_resize_output_image_size, normalize, pad, rescale,
+                                                         resize, to_channel_dimension_format, to_pil_image)
+    from mindformers_b200.utils.image_utils import (ChannelDimension, divide_to_patches, get_image_size,
+                                                    infer_channel_dimension_format, select_best_resolution)
+    rng = np.random.default_rng(2)
+    hwc = rng.integers(0, 256, (40, 60, 3), dtype=np.uint8)
+    chw = hwc.transpose(2, 0, 1)
+    assert infer_channel_dimension_format(hwc) == ChannelDimension.LAST and infer_channel_dimension_format(chw) == ChannelDimension.FIRST
+    assert get_image_size(hwc) == (40, 60) == get_image_size(chw)
+    np.testing.assert_array_equal(to_channel_dimension_format(hwc, "channels_first"), chw)
+    # any-resolution: a 40 x 60 image fits a 2 x 3 canvas of 20-pixel tiles best
+    assert select_best_resolution((40, 60), [(20, 20), (40, 40), (40, 60), (60, 40)]) == (40, 60)
+    assert select_best_resolution((500, 1000), [(336, 672), (672, 336), (336, 336)]) == (336, 672)
+    assert select_best_resolution((100, 300), [(336, 672), (672, 336), (336, 336)]) == (336, 336)      # nothing to gain: least waste
+    tiles = divide_to_patches(chw, 20)
+    assert len(tiles) == 6 and all(t.shape == (3, 20, 20) for t in tiles)
+    np.testing.assert_array_equal(tiles[4], chw[:, 20:40, 20:40])
+    np.testing.assert_allclose(rescale(hwc, 1 / 255.0), hwc / 255.0, atol=1e-6)
+    n = normalize(hwc / 255.0, [0.5, 0.4, 0.3], [0.2, 0.2, 0.2])
+    np.testing.assert_allclose(n[..., 1], (hwc[..., 1] / 255.0 - 0.4) / 0.2, atol=1e-6)
+    np.testing.assert_array_equal(center_crop(hwc, (20, 30)), hwc[10:30, 15:45])
+    big = center_crop(hwc, (50, 70))
+    assert big.shape == (50, 70, 3) and big[:5].sum() == 0 and np.array_equal(big[5:45, 5:65], hwc)
+    assert pad(chw, ((1, 2), (3, 4))).shape == (3, 43, 67) and pad(hwc, 2, mode="reflect").shape == (44, 64, 3)
+    assert get_resize_output_image_size(hwc, 20, default_to_square=False) == (20, 30)
+    assert get_resize_output_image_size(hwc, 20) == (20, 20) and get_resize_output_image_size(hwc, (7, 9)) == (7, 9)
+    assert get_resize_output_image_size(hwc, 30, default_to_square=False, max_size=40) == (26, 40)
+    small = resize(hwc, (20, 30))
+    assert small.shape == (20, 30, 3) and small.dtype == np.uint8
+    fl = resize(chw.astype(np.float32) / 255.0, (20, 30))
+    assert fl.shape == (3, 20, 30) and 0.0 <= fl.min() and fl.max() <= 1.0
+    pil = to_pil_image(chw)
+    np.testing.assert_array_equal(np.asarray(pil), hwc)
+    path = tmp_path / "a.png"
+    pil.save(path)
+    buf = io.BytesIO()
+    pil.save(buf, format="PNG")
+    for src in (str(path), buf.getvalue(), base64.b64encode(buf.getvalue()).decode(),
+                "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode(), pil):
+        np.testing.assert_array_equal(np.asarray(load_image(src)), hwc)
+    with pytest.raises(ValueError):
+        load_image("not an image")
