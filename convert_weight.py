@@ -61,6 +61,16 @@ def _config_for(args, input_dir):
 def convert(args):
     family = convert_map[args.model]
     dtype = DTYPES[args.dtype] if args.dtype else None
+    if args.workers and args.workers > 1 and not args.reversed and not args.legacy_names and os.path.isdir(args.input_path):
+        # one process per group of layers, one output file each + an index (a directory, not a single file)
+        from mindformers_b200.utils.safetensors import convert_hf_safetensors_multiprocess
+        cfg_path = args.config or os.path.join(args.input_path, "config.json")
+        with open(cfg_path) as f:
+            cfg_dict = json.load(f)
+        cfg_dict.setdefault("model_type", family)
+        return convert_hf_safetensors_multiprocess(args.input_path, args.output_path, cfg_dict, family,
+                                                   {"fp32": "float32", "bf16": "bfloat16", "fp16": "float16"}.get(args.dtype),
+                                                   workers=args.workers, keep_fp8=args.keep_fp8)
     sd = _load_any(args.input_path)
     cfg = _config_for(args, args.input_path)
     if args.reversed:
@@ -94,6 +104,9 @@ def main(argv=None):
     p.add_argument("--qkv_concat", default=True, type=lambda s: s.lower() in ("1", "true"))
     p.add_argument("--legacy_names", action="store_true")
     p.add_argument("--keep_fp8", action="store_true")
+    p.add_argument("--workers", type=int, default=1,
+                   help="> 1: convert a Hugging Face directory with this many processes (output_path becomes a directory "
+                        "of files + model.safetensors.index.json)")
     p.add_argument("--n_head", type=int, default=None)
     p.add_argument("--hidden_size", type=int, default=None)
     p.add_argument("--layers", type=int, default=None)

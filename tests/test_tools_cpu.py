@@ -278,3 +278,51 @@ def test_benchmark_tools_resolve_models_prepare_data_and_train(tmp_path, monkeyp
     assert res2["mode"] == "finetune" and res2["steps"] == 3
     off = pre.ModelPretrain(str(mdir), dict(args, load_checkpoint=""))
     assert not off.finetune and off.config["load_checkpoint"] == ""
+
+
+def test_multiprocess_safetensors_conversion_equals_the_single_process_one(tmp_path):
+    """A Hugging Face directory whose shards cut a layer in two, converted by worker processes (the unit of work is a
+    layer): same tensors as the single-process conversion, an index that names every tensor once, and the directory
+    loads into a model."""
+    import json
+    import os
+    import sys
+    import torch
+    from safetensors.torch import load_file, save_file
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import convert_weight
+    from mindformers_b200.models import Qwen3MoeConfig, AutoModel, LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=5, num_attention_heads=4,
+                      num_key_value_heads=2, params_dtype="float32", compute_dtype="float32")
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg, device="cpu")
+    m.save_pretrained(str(tmp_path / "hf_one"), hf_names=True)
+    full = {}
+    for f in os.listdir(tmp_path / "hf_one"):
+        if f.endswith(".safetensors"):
+            full.update(load_file(str(tmp_path / "hf_one" / f)))
+    keys = sorted(full)
+    os.makedirs(tmp_path / "hf")
+    cut = len(keys) // 3 + 1                                   # boundaries fall inside layers
+    weight_map = {}
+    for i in range(3):
+        part = {k: full[k] for k in keys[i * cut:(i + 1) * cut]}
+        save_file(part, str(tmp_path / "hf" / f"model-{i}.safetensors"))
+        weight_map.update({k: f"model-{i}.safetensors" for k in part})
+    json.dump({"weight_map": weight_map}, open(tmp_path / "hf" / "model.safetensors.index.json", "w"))
+    json.dump(json.load(open(tmp_path / "hf_one" / "config.json")), open(tmp_path / "hf" / "config.json", "w"))
+    single = load_file(convert_weight.main(["--model", "llama", "--input_path", str(tmp_path / "hf"),
+                                            "--output_path", str(tmp_path / "one")]))
+    index = convert_weight.main(["--model", "llama", "--input_path", str(tmp_path / "hf"), "--output_path",
+                                 str(tmp_path / "many"), "--workers", "3"])
+    wm = json.load(open(index))["weight_map"]
+    assert len(set(wm.values())) >= 3 and set(wm) == set(single)
+    merged = {}
+    for f in set(wm.values()):
+        merged.update(load_file(os.path.join(os.path.dirname(index), f)))
+    assert all(torch.equal(merged[k], single[k]) for k in single)
+    fresh = LlamaForCausalLM(cfg, device="cpu")
+    from mindformers_b200.checkpoint.io import load_checkpoint
+    load_checkpoint(fresh.model, os.path.dirname(index), strict=True)
+    for (n, a), (_, b) in zip(m.model.named_parameters(), fresh.model.named_parameters()):
+        assert torch.equal(a, b), n
