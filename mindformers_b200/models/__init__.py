@@ -11,7 +11,7 @@ from .presets import PRESETS, get_preset
 from .tokenization import ByteTokenizer, TextProcessor, build_tokenizer
 from .tokenization_utils import AddedToken, BatchEncoding, BytePairEncoder, PreTrainedTokenizer
 from .tokenizers import (ChatGLM3Tokenizer, ChatGLM4Tokenizer, Llama3Tokenizer, LlamaTokenizer, LlamaTokenizerFast,
-                         Qwen2Tokenizer, TelechatTokenizer)
+                         PreTrainedTokenizerFast, Qwen2Tokenizer, TelechatTokenizer, convert_slow_tokenizer)
 
 
 class BaseModel(PreTrainedModel):

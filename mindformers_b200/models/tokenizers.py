@@ -134,16 +134,30 @@ class TelechatTokenizer(LlamaTokenizer):
         return self(text, add_special_tokens=False)
 
 
-@MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
-class LlamaTokenizerFast(PreTrainedTokenizer):
-    """``tokenizer.json`` run by the ``tokenizers`` library."""
+class PreTrainedTokenizerFast(PreTrainedTokenizer):
+    """Base of the tokenizers that run on the ``tokenizers`` library (reference ``models/tokenization_utils_fast.py``):
+    built from a ``tokenizer.json`` file, from a ``tokenizers.Tokenizer`` object, or from a slow tokenizer through
+    ``convert_slow_tokenizer`` (``slow_tokenizer=``)."""
     vocab_files_names = {"tokenizer_file": "tokenizer.json"}
+    slow_tokenizer_class = None
 
-    def __init__(self, tokenizer_file: str, bos_token=None, eos_token=None, unk_token=None, pad_token=None,
-                 add_bos_token: bool = False, add_eos_token: bool = False, **kwargs):
+    def __init__(self, tokenizer_file: Optional[str] = None, bos_token=None, eos_token=None, unk_token=None, pad_token=None,
+                 add_bos_token: bool = False, add_eos_token: bool = False, tokenizer_object=None, slow_tokenizer=None,
+                 **kwargs):
         from tokenizers import Tokenizer
         self.tokenizer_file = tokenizer_file
-        self.backend = Tokenizer.from_file(tokenizer_file)
+        if tokenizer_object is not None:
+            self.backend = tokenizer_object
+        elif slow_tokenizer is not None:
+            self.backend = convert_slow_tokenizer(slow_tokenizer)
+            bos_token = bos_token or slow_tokenizer.bos_token
+            eos_token = eos_token or slow_tokenizer.eos_token
+            unk_token = unk_token or slow_tokenizer.unk_token
+            pad_token = pad_token or slow_tokenizer.pad_token
+        elif tokenizer_file is not None:
+            self.backend = Tokenizer.from_file(tokenizer_file)
+        else:
+            raise ValueError("one of tokenizer_file, tokenizer_object or slow_tokenizer is required")
         super().__init__(tokenizer_file=tokenizer_file, bos_token=bos_token, eos_token=eos_token, unk_token=unk_token,
                          pad_token=pad_token, add_bos_token=add_bos_token, add_eos_token=add_eos_token, **kwargs)
 
@@ -194,6 +208,67 @@ class LlamaTokenizerFast(PreTrainedTokenizer):
         dst = os.path.join(save_directory, name)
         self.backend.save(dst)
         return (dst,)
+
+
+@MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
+class LlamaTokenizerFast(PreTrainedTokenizerFast):
+    """``tokenizer.json`` of the Llama family run by the ``tokenizers`` library."""
+
+
+def merges_from_ranks(ranks: Dict[bytes, int]):
+    """The merge list that a rank table implies: a token of two or more bytes was formed by joining the two parts that
+    byte-pair encoding yields for it when only lower-ranked merges are allowed. Returned in rank order."""
+    merges = []
+    for token, rank in sorted(ranks.items(), key=lambda kv: kv[1]):
+        if len(token) < 2:
+            continue
+        parts = [bytes([b]) for b in token]
+        while len(parts) > 2:
+            best, best_rank = None, None
+            for i in range(len(parts) - 1):
+                r = ranks.get(parts[i] + parts[i + 1])
+                if r is not None and r < rank and (best_rank is None or r < best_rank):
+                    best, best_rank = i, r
+            if best is None:
+                break
+            parts[best:best + 2] = [parts[best] + parts[best + 1]]
+        if len(parts) == 2:
+            merges.append((parts[0], parts[1]))
+    return merges
+
+
+def convert_slow_tokenizer(slow):
+    """A ``tokenizers.Tokenizer`` that encodes like ``slow`` (reference ``models/convert_slow_tokenizer.py``).
+
+    Byte-level BPE tokenizers (rank table + split pattern: Llama-3, Qwen2, GLM-4 styles) become a ``BPE`` model over
+    the printable-character alphabet with a regex ``Split`` + ``ByteLevel`` pre-tokenizer and their special tokens
+    added; sentencepiece-backed tokenizers are converted from their ``.model`` file by the library's own importer."""
+    from tokenizers import AddedToken as FastAdded, Regex, Tokenizer, decoders, models, pre_tokenizers
+    if isinstance(slow, _TiktokenStyle):
+        table = bytes_to_unicode()
+        uni = lambda tok: "".join(table[b] for b in tok)
+        vocab = {uni(tok): idx for tok, idx in slow.mergeable_ranks.items()}
+        merges = [(uni(a), uni(b)) for a, b in merges_from_ranks(slow.mergeable_ranks)]
+        backend = Tokenizer(models.BPE(vocab=vocab, merges=merges, fuse_unk=False, byte_fallback=False,
+                                       ignore_merges=False))
+        backend.pre_tokenizer = pre_tokenizers.Sequence([
+            pre_tokenizers.Split(Regex(slow.pattern), behavior="isolated", invert=False),
+            pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+        backend.decoder = decoders.ByteLevel()
+        specials = sorted(slow.special_tokens.items(), key=lambda kv: kv[1])
+        next_id = len(vocab)
+        for tok, idx in specials:
+            if idx != next_id:
+                raise ValueError(f"special token {tok!r} has id {idx}, but the fast vocabulary would give it {next_id}: "
+                                 "special tokens must follow the ordinary ones without gaps")
+            next_id += 1
+        backend.add_special_tokens([FastAdded(t, special=True, normalized=False) for t, _ in specials])
+        return backend
+    sp_file = getattr(slow, "vocab_file", None)
+    if sp_file and str(sp_file).endswith(".model"):
+        from tokenizers.implementations import SentencePieceUnigramTokenizer
+        return SentencePieceUnigramTokenizer.from_spm(sp_file)._tokenizer
+    raise TypeError(f"no conversion for {type(slow).__name__}")
 
 
 class _TiktokenStyle(PreTrainedTokenizer):

@@ -230,3 +230,33 @@ def test_processor_roundtrip(tmp_path, ranks):
     assert torch.equal(again(text_input=["hello world", "the fox"])["text"], out["text"])
     built = build_processor({"type": "LlamaProcessor", "tokenizer": {"type": "ByteTokenizer"}, "max_length": 8})
     assert built(text_input="abc")["text"].shape[-1] == 8
+
+
+def test_slow_to_fast_conversion_encodes_alike(tmp_path, ranks):
+    """``convert_slow_tokenizer``: the byte-level BPE tokenizers (Qwen2 and Llama-3 styles) rebuilt on the ``tokenizers``
+    library give the same ids and round-trip the same texts, special tokens included; the merge list recovered from
+    the rank table reproduces every multi-byte token."""
+    from mindformers_b200.models import PreTrainedTokenizerFast, convert_slow_tokenizer
+    from mindformers_b200.models.tokenizers import merges_from_ranks
+    merges = merges_from_ranks(ranks)
+    assert len(merges) == sum(len(t) > 1 for t in ranks) and all(a + b in ranks for a, b in merges)
+    table = bytes_to_unicode()
+    vocab = {"".join(table[b] for b in tok): idx for tok, idx in ranks.items()}
+    (tmp_path / "vocab.json").write_text(json.dumps(vocab), encoding="utf-8")
+    (tmp_path / "merges.txt").write_text("#version: 0.2\n" + "\n".join(
+        "".join(table[x] for x in a) + " " + "".join(table[x] for x in b) for a, b in merges), encoding="utf-8")
+    slow = Qwen2Tokenizer(str(tmp_path / "vocab.json"), str(tmp_path / "merges.txt"))
+    fast = PreTrainedTokenizerFast(slow_tokenizer=slow)
+    assert fast.vocab_size == slow.vocab_size and fast.eos_token == slow.eos_token
+    texts = CORPUS[:7] + ["<|im_start|>user\nhello  world<|im_end|>\n", "tabs\tand\n\nnewlines   ", "数字 123 and ünï"]
+    for t in texts:
+        a, b = slow.encode(t), fast.encode(t)
+        assert a == b, (t, a, b)
+        assert fast.decode(b) == slow.decode(a) == t
+    fast.save_pretrained(str(tmp_path / "fast"))
+    again = AutoTokenizer.from_pretrained(str(tmp_path / "fast"))
+    assert again.encode(texts[0]) == slow.encode(texts[0])
+    backend = convert_slow_tokenizer(slow)
+    assert backend.token_to_id("<|im_end|>") == slow.im_end_id
+    with pytest.raises(TypeError):
+        convert_slow_tokenizer(object())
