@@ -205,3 +205,39 @@ def test_multimodal_trainer_predict_from_records(tmp_path):
     one = trainer.predict(cfg, input_data=[{"image": img}, {"text": "and this"}], network=model, tokenizer=tok,
                           processor=proc, max_new_tokens=2, do_sample=False)
     assert len(one) == 1
+
+
+def test_features_travel_through_shared_memory_as_two_negative_ids(tmp_path):
+    """The serving front end parks an array in shared memory and sends (encoded name, encoded shape); the worker gets
+    the same array back; corrupted or ordinary negative values are rejected; the clean-up file unlinks leftovers."""
+    import numpy as np
+    import pytest
+    from mindformers_b200.models.multi_modal.shm_utils import (SHM_NAME_PREFIX, decode_shape_from_int64,
+                                                               decode_shm_name_from_int64, encode_shape_to_int64,
+                                                               encode_shm_name_to_int64, get_data_from_shm, put_data_to_shm,
+                                                               release_shared_memory)
+    from mindformers_b200.models.multi_modal.utils import DataRecord
+    for shape in ((7,), (2, 3), (4, 3, 336, 336), (2, 5, 3, 224, 224), (1, 2, 3, 4, 5, 6)):
+        code = encode_shape_to_int64(shape)
+        assert code < 0 and -code < 2 ** 63 and decode_shape_from_int64(code) == shape
+    for name in (SHM_NAME_PREFIX + "1a2b3c4d", SHM_NAME_PREFIX + "00ff00ff00", SHM_NAME_PREFIX + "7"):
+        code = encode_shm_name_to_int64(name)
+        assert code < 0 and -code < 2 ** 63 and decode_shm_name_from_int64(code) == name
+    with pytest.raises(ValueError):
+        decode_shape_from_int64(encode_shape_to_int64((2, 3)) - 1)
+    with pytest.raises(ValueError):
+        decode_shm_name_from_int64(-123456)
+    with pytest.raises(ValueError):
+        encode_shape_to_int64((1 << 30, 1 << 30, 3))
+    feats = np.random.default_rng(0).standard_normal((2, 3, 8, 8)).astype(np.float32)
+    book = str(tmp_path / "segments.txt")
+    name_id, shape_id = put_data_to_shm(feats, book)
+    assert name_id < 0 and shape_id < 0
+    np.testing.assert_array_equal(get_data_from_shm(name_id, shape_id, np.float32), feats)
+    put_data_to_shm(feats, book)                        # a segment nobody fetches
+    assert release_shared_memory(book) == 1             # the first one is gone already, the second is unlinked here
+    rec = DataRecord()
+    rec.put("ids", 1, append=True)
+    rec.put("ids", 2, append=True)
+    rec.put_from_dict({"n": 3})
+    assert rec.output(["ids", "n"], "tuple") == ([1, 2], 3) and rec.has_key("n") and rec.output(["n"]) == {"n": 3}
