@@ -37,7 +37,15 @@ def _is_transient(name: str) -> bool:
     return any(k in name for k in TRANSIENT_KEYS)
 
 
+def _sync_params(model):
+    """An optimizer that still publishes updated parameters on a side stream leaves a hook on the model: wait for it."""
+    fn = getattr(model, "_mfb_param_sync", None)
+    if callable(fn):
+        fn()
+
+
 def model_state(model: torch.nn.Module, trainable_only: bool = False) -> Dict[str, torch.Tensor]:
+    _sync_params(model)
     out = {}
     for n, p in model.named_parameters():
         if trainable_only and not p.requires_grad:

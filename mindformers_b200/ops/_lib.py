@@ -116,6 +116,8 @@ def _declare(lib):
     sig("mfb_dp_flag_words", [])
     sig("mfb_dp_reduce", [I, I, I, L, L, P, P, P, P, P, I, P, P])
     sig("mfb_dp_bucket_rows", [])
+    sig("mfb_dp_adamw_publish", [I, I, I, I, L, L, L, P, P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, F, F, F, P, P])
+    sig("mfb_dp_wait_published", [I, I, I, I, P, P, P])
     sig("mfb_dp_announce", [I, I, I, I, P, P])
     sig("mfb_dp_reduce_bucket", [I, I, I, I, L, L, P, P, P, P, P, I, P, P])
     sig("mfb_dp_adamw_allgather", [I, I, I, L, L, P, P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, F, F, F, P, P])

@@ -82,7 +82,8 @@ __device__ bool dp_wait_all(const int* flags, int world, int want, int* status) 
 }
 
 constexpr int kDpBucketRows = 64;      // bucket flag rows per step
-constexpr int kDpBucketFlagBase = 32;  // first int of the bucket rows inside a rank's flag array
+constexpr int kDpBucketFlagBase = 32;  // first int of the "gradients final" bucket rows inside a rank's flag array
+constexpr int kDpPublishFlagBase = kDpBucketFlagBase + kDpBucketRows * kDpMaxRanks;   // "parameters published" rows
 
 // SYNC: announce "gradients final" and wait for all peers inside the kernel (the pass after the backward pass).
 // !SYNC: the caller has already waited (dp_wait_row_kernel earlier in the stream); a wait that timed out left its
@@ -145,11 +146,13 @@ __global__ void dp_sum_partials_kernel(const float* __restrict__ partials, int p
 struct DpAdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2, max_norm, skip_threshold, grad_scale;
   long long decay_end;  // elements [0, decay_end) of the slice get weight decay
+  int publish_row;      // >= 0: release this row of the "parameters published" bucket flags instead of the step's one flag
+  int zero_grads;       // the kernel leaves zeros in the gradients it consumed (the next step's accumulation starts there)
 };
 
 __global__ void __launch_bounds__(kDpThreads)
 dp_adamw_kernel(DpArgs a, DpAdamArgs h, unsigned short* __restrict__ lo, float* __restrict__ m,
-                float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ sumsq,
+                float* __restrict__ v, float* __restrict__ g, const float* __restrict__ sumsq,
                 int* __restrict__ skipped) {
   float clip = h.grad_scale;
   bool bad = false;
@@ -201,12 +204,22 @@ dp_adamw_kernel(DpArgs a, DpAdamArgs h, unsigned short* __restrict__ lo, float* 
       *reinterpret_cast<float4*>(v + e0) = *reinterpret_cast<float4*>(vv);
       *reinterpret_cast<float4*>(v + e0 + 4) = *reinterpret_cast<float4*>(vv + 4);
       *reinterpret_cast<uint4*>(lo + e0) = nl;
+      if (h.zero_grads) {
+        *reinterpret_cast<float4*>(g + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(g + e0 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       // publish: own copy first, then every peer's copy of this slice
       for (int p = 0; p < a.world; ++p) {
         const int q = (a.rank + p) % a.world;
         *reinterpret_cast<uint4*>(a.peer_param[q] + a.begin + e0) = np;
       }
     }
+  }
+  if (bad && h.zero_grads) {
+    const long long nvec = a.n >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x)
+      reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   // completion: the last CTA releases the "published" flag on every peer
   __threadfence_system();
@@ -216,7 +229,8 @@ dp_adamw_kernel(DpArgs a, DpAdamArgs h, unsigned short* __restrict__ lo, float* 
   __syncthreads();
   if (last) {
     __threadfence_system();
-    if (threadIdx.x < a.world) dp_st_release_sys(a.flags_peer[threadIdx.x] + kDpMaxRanks + a.rank, a.epoch);
+    const int off = h.publish_row >= 0 ? kDpPublishFlagBase + h.publish_row * kDpMaxRanks : kDpMaxRanks;
+    if (threadIdx.x < a.world) dp_st_release_sys(a.flags_peer[threadIdx.x] + off + a.rank, a.epoch);
     if (threadIdx.x == 0) *a.ticket = 0;
   }
 }
@@ -232,6 +246,9 @@ __global__ void dp_announce_kernel(DpArgs a, int row) {
 }
 __global__ void dp_wait_row_kernel(DpArgs a, int row) {
   dp_wait_all(a.flags_local + kDpBucketFlagBase + row * kDpMaxRanks, a.world, a.epoch, a.status);
+}
+__global__ void dp_wait_published_row_kernel(DpArgs a, int row) {
+  dp_wait_all(a.flags_local + kDpPublishFlagBase + row * kDpMaxRanks, a.world, a.epoch, a.status);
 }
 
 static inline int dp_grid(long long nvec, int max_ctas = 148 * 4) {
@@ -250,7 +267,7 @@ using namespace mfb;
 // Number of floats of scratch that mfb_dp_reduce needs (block partials of the squared norm).
 int mfb_dp_reduce_scratch() { return 148 * 4; }
 // Number of ints in the per-rank flag array (two rows of kDpMaxRanks) plus the ticket word.
-int mfb_dp_flag_words() { return kDpBucketFlagBase + kDpBucketRows * kDpMaxRanks; }
+int mfb_dp_flag_words() { return kDpPublishFlagBase + kDpBucketRows * kDpMaxRanks; }
 // Number of gradient buckets per step that the bucket flag rows can tell apart.
 int mfb_dp_bucket_rows() { return kDpBucketRows; }
 
@@ -332,8 +349,45 @@ int mfb_dp_adamw_allgather(int world, int rank, int epoch, long long begin, long
   DpAdamArgs h;
   h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd; h.bc1 = bc1; h.bc2 = bc2;
   h.max_norm = max_norm; h.skip_threshold = skip_threshold; h.grad_scale = grad_scale; h.decay_end = decay_end;
-  dp_adamw_kernel<<<dp_grid(n >> 3), kDpThreads, 0, stream>>>(a, h, (unsigned short*)lo, m, v, reduced, sumsq, skipped);
+  h.publish_row = -1; h.zero_grads = 0;
+  dp_adamw_kernel<<<dp_grid(n >> 3), kDpThreads, 0, stream>>>(a, h, (unsigned short*)lo, m, v, const_cast<float*>(reduced),
+                                                              sumsq, skipped);
   dp_wait_kernel<<<1, 32, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// One piece [begin, begin + n) of this rank's slice (n may be 0: publish only): AdamW, publication of the new
+// parameters to every rank, zeros left in the consumed gradients, then release of row `row` of the "parameters
+// published" flags on every rank. No wait: the consumer waits per row with mfb_dp_wait_published.
+// piece_off: offset of the piece inside the rank's slice (index into lo / m / v / reduced, and into decay_end's frame).
+int mfb_dp_adamw_publish(int world, int rank, int epoch, int row, long long begin, long long n, long long piece_off,
+                         const long long* peer_param, const long long* peer_flags, void* lo, float* m, float* v,
+                         float* reduced, const float* sumsq, int* skipped, long long decay_end, float lr, float beta1,
+                         float beta2, float eps, float wd, float bc1, float bc2, float max_norm, float skip_threshold,
+                         float grad_scale, int* status, cudaStream_t stream) {
+  DpArgs a;
+  if (fill_dp_args(&a, world, rank, epoch, begin, n, nullptr, peer_param, peer_flags, status)) return 1;
+  if (row < 0 || row >= kDpBucketRows || (piece_off & 7)) {
+    mfb_host::set_error("dp optimizer: publish row %d / piece offset %lld", row, piece_off);
+    return 1;
+  }
+  DpAdamArgs h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd; h.bc1 = bc1; h.bc2 = bc2;
+  h.max_norm = max_norm; h.skip_threshold = skip_threshold; h.grad_scale = grad_scale;
+  h.decay_end = decay_end - piece_off;          // the kernel indexes the piece from 0
+  h.publish_row = row; h.zero_grads = 1;
+  dp_adamw_kernel<<<dp_grid(n >> 3), kDpThreads, 0, stream>>>(a, h, (unsigned short*)lo + piece_off, m + piece_off,
+                                                              v + piece_off, reduced + piece_off, sumsq, skipped);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Waits (one warp, bounded) until every rank has published row `row` of step `epoch`.
+int mfb_dp_wait_published(int world, int rank, int epoch, int row, const long long* peer_flags, int* status,
+                          cudaStream_t stream) {
+  DpArgs a;
+  if (fill_dp_args(&a, world, rank, epoch, 0, 0, nullptr, nullptr, peer_flags, status)) return 1;
+  if (row < 0 || row >= kDpBucketRows) { mfb_host::set_error("dp optimizer: publish row %d", row); return 1; }
+  dp_wait_published_row_kernel<<<1, 32, 0, stream>>>(a, row);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -118,6 +118,10 @@ class DistributedOptimizer:
         self._dp_epoch = 0
         self._overlap = None          # state of the bucketed reduction that runs under the backward pass
         self.overlap_grad_reduce = os.environ.get("MFB_DP_OVERLAP", "1") != "0"
+        # opt-in: AdamW + publication of the new parameters run on the side stream in the order the next forward pass
+        # needs them, and that forward pass waits per group of layers instead of at the end of the step
+        self.overlap_param_gather = os.environ.get("MFB_DP_PARAM_OVERLAP", "0") == "1"
+        self._pub = None              # pending publication: events per row, rows already waited for
         if self.fused_dp:
             self._setup_fused_dp(dev)
             self._setup_overlap(dev)
@@ -156,6 +160,11 @@ class DistributedOptimizer:
         from ..layers.transformer_layer import TransformerBlock
         blocks = [(n, m) for n, m in self.model.named_modules() if isinstance(m, TransformerBlock) and len(m.layers)]
         self._ov_blocks, self._ov_layers = [], {}
+        self._ov_stream = torch.cuda.Stream(device=dev)
+        self._pub_skipped = torch.zeros(1, dtype=torch.int32, device=dev)
+        # whoever reads the parameters next (a forward pass, a checkpoint) first waits for a publication in flight
+        self.model._mfb_param_sync = self.finish_param_gather
+        self.model.register_forward_pre_hook(lambda _m, _a: self._before_model_forward())
         if len(blocks) != 1:
             return
         prefix, block = blocks[0]
@@ -185,9 +194,19 @@ class DistributedOptimizer:
             self._ov_layers[name] = {"span": span, "ids": ids, "group": group}
         if self._ov_layers:
             self._ov_blocks = [block]
-            self._ov_stream = torch.cuda.Stream(device=dev)
             self._ov_scratch = torch.zeros(_lib.get_lib().mfb_dp_reduce_scratch(), dtype=torch.float32, device=dev)
             self._ov_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def _before_model_forward(self):
+        """A forward pass that starts while parameters are still being published: the parameters outside the decoder
+        layers are needed at once, the layers wait one by one (a forward pass outside the training step included)."""
+        if self._pub is None:
+            return
+        self._wait_published(0)
+        self._wait_published(1)
+        if self._pub is not None:
+            for b in getattr(self, "_ov_blocks", []):
+                b.params_ready_hook = self._layer_params_needed
 
     def begin_grad_overlap(self):
         """Call before the forward pass of the step's last micro-batch: from then on each decoder layer's gradient
@@ -254,10 +273,132 @@ class DistributedOptimizer:
         return {n: (lo, ov["high"][n]) for n, lo in ov["low"].items() if lo is not None}
 
     def zero_grad(self, set_to_none: bool = True):
-        for buf in self.buffers.values():
-            buf.zero_grad()
+        pub = self._pub
+        if pub is not None:
+            # the embedding, head and norm parameters are needed first, and their publication by every rank also says
+            # that every rank has finished reading this rank's gradients: only now may they be overwritten
+            self._wait_published(0)
+            self._wait_published(1)
+            for name, buf in self.buffers.items():
+                sh = self.shards[name]
+                if name in pub["shards"]:
+                    buf.grad_data[:sh.begin].zero_()      # this rank's own slice is zeroed by its AdamW pieces
+                    buf.grad_data[sh.end:].zero_()
+                else:
+                    buf.zero_grad()
+            for b in getattr(self, "_ov_blocks", []):
+                b.params_ready_hook = self._layer_params_needed
+        else:
+            for buf in self.buffers.values():
+                buf.zero_grad()
         for p in self.model.parameters():
             p.grad = None
+
+    # ---- parameter publication under the next forward pass ----------------------------------------------------------
+    def _publish_rows(self, name):
+        """``[(row, lo, hi)]`` in the order the forward pass needs the parameters: rows 0 / 1 = everything outside the
+        decoder layers (below / above their range), rows 2.. = groups of layers in ascending order."""
+        sh = self.shards[name]
+        info = getattr(self, "_ov_layers", {}).get(name)
+        if info is None:
+            return [(0, sh.begin, sh.end), (1, sh.end, sh.end)]
+        ids, span = info["ids"], info["span"]
+        d0, d1 = span[ids[0]][0], span[ids[-1]][1]
+        rows = [(0, 0, d0), (1, d1, sh.buf.ranges.numel)]
+        per = max(1, -(-len(ids) // 60))
+        for gi, i in enumerate(range(0, len(ids), per)):
+            grp = ids[i:i + per]
+            rows.append((2 + gi, span[grp[0]][0], span[grp[-1]][1]))
+        return rows
+
+    def _row_of_layer(self, name, gid):
+        info = self._ov_layers[name]
+        per = max(1, -(-len(info["ids"]) // 60))
+        return 2 + info["ids"].index(gid) // per
+
+    def _wait_published(self, row: int):
+        pub = self._pub
+        if pub is None or row in pub["waited"]:
+            return
+        pub["waited"].add(row)
+        lib = _lib.get_lib()
+        for name in pub["shards"]:
+            ev = pub["events"][name].get(row)
+            if ev is None:
+                continue
+            torch.cuda.current_stream().wait_event(ev)        # this GPU's own pieces: ordered by the event
+            sh = self.shards[name]
+            rc = lib.mfb_dp_wait_published(sh.world, sh.rank, pub["epoch"], row, sh.peer_flags,
+                                           _lib.status_word(sh.grad.device).data_ptr(), _lib.stream_ptr())
+            _lib.check(rc, "mfb_dp_wait_published")
+            _lib.count_launch(1)
+        if len(pub["waited"]) >= pub["rows"]:
+            self._pub = None
+            for b in getattr(self, "_ov_blocks", []):
+                b.params_ready_hook = None
+
+    def _layer_params_needed(self, gid: int):
+        pub = self._pub
+        if pub is None:
+            return
+        for name in pub["shards"]:
+            if name in self._ov_layers and gid in self._ov_layers[name]["span"]:
+                self._wait_published(self._row_of_layer(name, gid))
+
+    def finish_param_gather(self):
+        """Make the current stream wait for every parameter that is still being published (call before anything other
+        than the next training step reads the parameters: evaluation, generation, a checkpoint)."""
+        pub = self._pub
+        if pub is None:
+            return
+        for row in range(pub["rows"]):
+            self._wait_published(row)
+        self._pub = None
+        for b in getattr(self, "_ov_blocks", []):
+            b.params_ready_hook = None
+
+    def _step_published(self, lr, grad_scale):
+        """AdamW and publication of the fused shards piece by piece on the side stream (see ``overlap_param_gather``)."""
+        lib = _lib.get_lib()
+        main = torch.cuda.current_stream()
+        # the skip decision of the step, on the compute stream (the pieces reach the same verdict from the same scalar)
+        nrm = self.sumsq.sqrt() * abs(grad_scale)
+        bad = ~torch.isfinite(self.sumsq)
+        if self.skip_threshold > 0:
+            bad = bad | (nrm >= self.skip_threshold)
+        self.skipped.copy_(bad.to(torch.int32))
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self._ov_stream.wait_event(ready)
+        pub = {"epoch": self._dp_epoch, "events": {}, "waited": set(), "shards": [], "rows": 0}
+        bc1, bc2 = 1.0 - self.beta1 ** self.global_step, 1.0 - self.beta2 ** self.global_step
+        scratch_skipped = self._pub_skipped
+        with torch.cuda.stream(self._ov_stream):
+            for name, sh in self.shards.items():
+                if not getattr(sh, "fused", False):
+                    continue
+                pub["shards"].append(name)
+                pub["events"][name] = {}
+                r = sh.buf.ranges
+                d_end = max(0, min(r.decay_end, sh.end) - sh.begin)
+                rows = self._publish_rows(name)
+                pub["rows"] = max(pub["rows"], len(rows))
+                for row, lo, hi in rows:
+                    a, b = max(lo, sh.begin), min(hi, sh.end)
+                    n = max(0, b - a)
+                    off = a - sh.begin if n else 0
+                    rc = lib.mfb_dp_adamw_publish(
+                        sh.world, sh.rank, self._dp_epoch, row, a if n else sh.begin, n, off, sh.peer_param, sh.peer_flags,
+                        sh.lo.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), sh.grad.data_ptr(), self.sumsq.data_ptr(),
+                        scratch_skipped.data_ptr(), d_end, lr, self.beta1, self.beta2, self.eps, self.wd, bc1, bc2,
+                        self.max_grad_norm, self.skip_threshold, grad_scale, _lib.status_word(sh.grad.device).data_ptr(),
+                        _lib.stream_ptr())
+                    _lib.check(rc, "mfb_dp_adamw_publish")
+                    _lib.count_launch(1)
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    pub["events"][name][row] = ev
+        self._pub = pub
 
     def current_lr(self) -> float:
         return float(self.lr(self.global_step) if callable(self.lr) else self.lr)
@@ -329,13 +470,20 @@ class DistributedOptimizer:
 
     def step(self, grad_scale: float = 1.0):
         """One optimizer step. ``grad_scale`` multiplies the gradients (1/dp averaging, loss-scale inverse)."""
+        self.finish_param_gather()          # a step whose forward pass never ran (tests) still owes the waits
         self.reduce_and_norm()
         self.global_step += 1
         lr = self.current_lr()
         self.skipped.zero_()
+        deferred = self.overlap_param_gather and self.fused_dp and hasattr(self, "_ov_stream") \
+            and any(getattr(sh, "fused", False) for sh in self.shards.values())
+        if deferred:
+            self._step_published(lr, grad_scale)
         for name, sh in self.shards.items():
             r = sh.buf.ranges
             d_end = max(0, min(r.decay_end, sh.end) - sh.begin)
+            if getattr(sh, "fused", False) and deferred:
+                continue
             if getattr(sh, "fused", False):
                 bc1, bc2 = 1.0 - self.beta1 ** self.global_step, 1.0 - self.beta2 ** self.global_step
                 rc = _lib.get_lib().mfb_dp_adamw_allgather(

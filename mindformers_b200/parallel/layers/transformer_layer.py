@@ -181,6 +181,9 @@ class TransformerBlock(nn.Module):
         # ``grads_final_hook(layer_id)``: set by the optimizer for the forward pass of a step's last micro-batch; it is
         # called during the backward pass as soon as every gradient of that layer's parameters has been written
         self.grads_final_hook = None
+        # ``params_ready_hook(layer_id)``: set by the optimizer while it still publishes updated parameters; called
+        # before a layer runs, it makes the stream wait for that layer's parameters
+        self.params_ready_hook = None
 
     # reference defaults of ``select_recompute: true`` (``training_graph/transformer/utils.py:107-110``): the gated
     # activation of the MLP and of the shared experts; here these, the norms and the rotary embedding are what a
@@ -250,6 +253,8 @@ class TransformerBlock(nn.Module):
             self._offload.prune()
         for idx, layer in enumerate(self.layers):
             run = layer
+            if self.params_ready_hook is not None:
+                self.params_ready_hook(self.layer_ids[idx])
             if training and self.grads_final_hook is not None and pending.requires_grad:
                 # the gradient of a layer's input is the last thing its backward pass produces
                 def fire(_grad, _cb=self.grads_final_hook, _gid=self.layer_ids[idx]):

@@ -19,10 +19,11 @@ TINY = dict(model_type="llama", num_hidden_layers=2, hidden_size=256, num_attent
             intermediate_size=512, vocab_size=1024, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=256)
 
 
-def build(fused, overlap=True, cfg=None, seq=256, **kw):
+def build(fused, overlap=True, cfg=None, seq=256, publish=False, **kw):
     torch.manual_seed(11)
     os.environ["MFB_FUSED_DP"] = "1" if fused else "0"
     os.environ["MFB_DP_OVERLAP"] = "1" if overlap else "0"
+    os.environ["MFB_DP_PARAM_OVERLAP"] = "1" if publish else "0"
     kw.setdefault("max_grad_norm", 1.0)
     return TrainingEngine.from_model_config(cfg or TINY, seq_length=seq, learning_rate=1e-3, weight_decay=0.1, **kw)
 
@@ -102,6 +103,9 @@ def main():
     res = {"dp": world}
     four = dict(TINY, num_hidden_layers=4)
     fused, plain, serial = build(True, cfg=four), build(False, cfg=four), build(True, overlap=False, cfg=four)
+    deferred = build(True, cfg=four, publish=True)      # AdamW + publication under the next forward pass
+    assert deferred.optimizer.overlap_param_gather and not fused.optimizer.overlap_param_gather
+    deferred_diff = 0.0
     assert fused.optimizer.fused_dp and not plain.optimizer.fused_dp and serial.optimizer.fused_dp
     assert fused.optimizer._ov_layers and fused.optimizer.overlap_grad_reduce and not serial.optimizer.overlap_grad_reduce
     grad_mismatch, serial_param_diff = 0.0, 0.0
@@ -120,6 +124,21 @@ def main():
         a = fused.train_step_device(batch)
         b = plain.train_step_device(batch)
         c = serial.train_step_device(batch)
+        d = deferred.train_step_device(batch)
+        assert deferred.optimizer._pub is not None          # the publication is still pending after the step
+        if step == 1:
+            with torch.no_grad():                           # a forward pass outside the training step waits by itself
+                deferred.model(batch["input_ids"][:1], batch["labels"][:1])
+        elif step == 2:
+            deferred.optimizer.finish_param_gather()
+        # step 0: nothing waits here, the next training step's zero_grad / forward pass pick the waits up;
+        # step 3: model_state (what a checkpoint calls) waits
+        deferred_diff = max(deferred_diff, abs(float(d["loss"]) - float(a["loss"])))
+        if step:
+            from mindformers_b200.checkpoint.io import model_state
+            got = model_state(deferred.model)
+            for (n, p) in fused.model.named_parameters():
+                deferred_diff = max(deferred_diff, (p.float() - got[n].float()).abs().max().item())
         for (_, s1), (_, s2) in zip(serial.optimizer.shards.items(), fused.optimizer.shards.items()):
             grad_mismatch = max(grad_mismatch, (s1.grad - s2.grad).abs().max().item())
         for p, q in zip(serial.model.parameters(), fused.model.parameters()):
@@ -137,6 +156,7 @@ def main():
     res["max_param_diff_vs_nccl"] = worst
     res["bucketed_vs_single_pass_grad_mismatch"] = grad_mismatch
     res["bucketed_vs_single_pass_param_diff"] = serial_param_diff
+    res["deferred_publication_param_and_loss_diff"] = deferred_diff
     if args.timeline:
         res["timeline"] = overlap_timeline(rank, world)
     res["losses"] = losses
@@ -169,7 +189,8 @@ def main():
             with open(args.out, "w") as f:
                 json.dump(res, f, indent=1)
     ok = res["status"] == 0 and res["replica_mismatch"] == 0.0 and res["max_param_diff_vs_nccl"] < 1e-2 \
-        and res["bucketed_vs_single_pass_grad_mismatch"] == 0.0 and res["bucketed_vs_single_pass_param_diff"] < 1e-3
+        and res["bucketed_vs_single_pass_grad_mismatch"] == 0.0 and res["bucketed_vs_single_pass_param_diff"] < 1e-3 \
+        and res["deferred_publication_param_and_loss_diff"] == 0.0
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
 
