@@ -237,7 +237,14 @@ def build_optim(config: dict, default_args: Optional[dict] = None, model: Option
         args.setdefault("params", model)
     target = MindFormerRegister.get_cls(MindFormerModuleType.OPTIMIZER, cfg["type"])
     if not issubclass(target, DistributedOptimizer) and isinstance(args.get("params"), torch.nn.Module):
-        args["params"] = [p for p in args["params"].parameters() if p.requires_grad]
+        layer_scale, layer_decay = bool(cfg.pop("layer_scale", False)), float(cfg.pop("layer_decay", 1.0))
+        if layer_scale or cfg.get("weight_decay"):
+            # decay / no-decay groups (and a learning rate that decays from the top layer down with layer_scale)
+            from ..trainer.optimizer_grouped_parameters import get_optimizer_grouped_parameters
+            args["params"] = get_optimizer_grouped_parameters(args["params"], float(cfg.get("weight_decay") or 0.0),
+                                                              layer_scale=layer_scale, layer_decay=layer_decay)
+        else:
+            args["params"] = [p for p in args["params"].parameters() if p.requires_grad]
         if "learning_rate" in cfg and target.__module__.startswith("torch.optim"):
             cfg["lr"] = cfg.pop("learning_rate")
     return MindFormerRegister.get_instance_from_cfg(cfg, MindFormerModuleType.OPTIMIZER, default_args=args)

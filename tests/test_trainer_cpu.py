@@ -286,3 +286,34 @@ def test_general_task_trainer_trains_and_scores_a_caller_supplied_network(tmp_pa
         trainer.train(network=net)
     with pytest.raises(NotImplementedError):
         trainer.evaluate(network=net, dataset=data)
+
+
+def test_grouped_parameters_decay_exemptions_and_layer_wise_learning_rate():
+    """Groups for group-style optimizers: 1-D parameters and biases get no weight decay; with ``layer_scale`` the learning
+    rate falls by ``layer_decay`` per layer from the head down, and the replicated optimizer applies it."""
+    from mindformers_b200.core.optim import ReplicatedOptimizer, build_optim
+    from mindformers_b200.models import LlamaConfig, LlamaForCausalLM
+    from mindformers_b200.trainer.optimizer_grouped_parameters import get_optimizer_grouped_parameters
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, params_dtype="float32", compute_dtype="float32")
+    torch.manual_seed(0)
+    m = LlamaForCausalLM(cfg, device="cpu").model
+    plain = get_optimizer_grouped_parameters(m, weight_decay=0.1)
+    by_name = {g["name"]: g for g in plain}
+    assert set(by_name) == {"decay", "no_decay"} and by_name["decay"]["weight_decay"] == 0.1
+    assert all(p.dim() <= 1 for p in by_name["no_decay"]["params"]) and all(p.dim() > 1 for p in by_name["decay"]["params"])
+    assert sum(len(g["params"]) for g in plain) == len(list(m.parameters()))
+    scaled = {g["name"]: g for g in get_optimizer_grouped_parameters(m, 0.1, layer_scale=True, layer_decay=0.5)}
+    assert abs(scaled["layer_0_decay"]["lr_scale"] - 0.5 ** 4) < 1e-12          # embedding
+    assert abs(scaled["layer_1_decay"]["lr_scale"] - 0.5 ** 3) < 1e-12 and abs(scaled["layer_3_decay"]["lr_scale"] - 0.5) < 1e-12
+    assert scaled["layer_4_decay"]["lr_scale"] == 1.0                            # output layer
+    inner = build_optim({"type": "SGD", "learning_rate": 1.0, "weight_decay": 0.0, "layer_scale": True, "layer_decay": 0.5},
+                        model=m)
+    opt = ReplicatedOptimizer(m, inner, learning_rate=1.0, max_grad_norm=0.0)
+    before = {n: p.detach().clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = torch.ones_like(p)
+    opt.step()
+    moved = {n: float((before[n] - p.detach()).abs().max()) for n, p in m.named_parameters()}
+    assert abs(moved["embedding.word_embeddings.weight"] - 0.5 ** 4) < 1e-6
+    assert abs(moved["decoder.layers.2.mlp.linear_fc2.weight"] - 0.5) < 1e-6 and abs(moved["output_layer.weight"] - 1.0) < 1e-6
