@@ -92,6 +92,30 @@ _OUT_MODES = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.floa
               (torch.bfloat16, True): 3}
 
 
+def _decode_gemm_ok(M: int, K: int, a: torch.Tensor, b: torch.Tensor) -> bool:
+    return _DECODE_GEMM and M <= 64 and K >= 64 and K % 8 == 0 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+
+
+def decode_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``x W^T + bias`` for 1 - 64 rows of ``x`` on the weight-on-rows kernel with the bias added in its epilogue; None
+    when the kernel does not serve the call (the caller then takes the general path)."""
+    if not (_on_gpu(x) and _GEMM_BACKEND == "tcgen05" and x.dim() == 2 and w.dim() == 2 and _decode_gemm_ok(x.shape[0], x.shape[1], x, w)):
+        return None
+    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous() or bias.numel() != w.shape[0]):
+        return None
+    if not _aligned(x):
+        x = x.contiguous()
+    if not _aligned(w):
+        w = w.contiguous()
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+    rc = _lib.get_lib().mfb_gemm_bf16_decode(x.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(bias), x.shape[0], w.shape[0],
+                                             x.shape[1], x.stride(0), w.stride(0), out.stride(0), _DECODE_GEMM_KS,
+                                             _lib.status_word(x.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "mfb_gemm_bf16_decode")
+    _lib.count_launch()
+    return out
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          accumulate: bool = False, sm_limit: int = 0) -> torch.Tensor:
@@ -300,6 +324,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             y = apply_fn(_LinearFn, x, w)
             return y if bias is None else y + bias
         return F.linear(x, w, bias)
+    if bias is not None and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or bias.requires_grad)):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = decode_linear(x2, w, bias) if x2.shape[0] <= 64 else None      # decode step: bias added by the GEMM's epilogue
+        if y is not None:
+            return y if x.dim() == 2 else y.reshape(*x.shape[:-1], w.shape[0])
     y = apply_fn(_LinearFn, x, w)
     if bias is not None:
         y = y + bias

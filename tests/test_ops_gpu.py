@@ -875,5 +875,10 @@ def test_bf16_decode_gemm_matches_fp32_reference(T, N, K):
             assert torch.all(buf[0] == 7.0) and torch.all(buf[T + 1] == 7.0)
             again = Fn.gemm(x, w)
             assert torch.equal(again, y)                       # same bits on every run (fixed summation order)
+            bias = (torch.randn(N, device="cuda") * 0.5).to(torch.bfloat16)
+            with torch.no_grad():
+                yb = Fn.linear(x, w, bias)                     # bias in the kernel's epilogue
+            assert (yb.float() - (ref + bias.float())).abs().max().item() < tol + 4e-3 * bias.abs().max().item()
+            assert (yb.float() - y.float() - bias.float()).abs().max().item() <= 2 ** -7 * (ref.abs().max().item() + 2.0)
     finally:
         Fn.set_decode_gemm(True, 0)
