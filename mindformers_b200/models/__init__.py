@@ -14,6 +14,44 @@ from .tokenizers import (ChatGLM3Tokenizer, ChatGLM4Tokenizer, Llama3Tokenizer, 
                          PreTrainedTokenizerFast, Qwen2Tokenizer, TelechatTokenizer, convert_slow_tokenizer)
 
 
+# keys of the older top-level ``moe_config`` YAML section that steer MindSpore's MoE implementation only (routing class
+# names, graph-fusion switches, drop-rate callbacks): nothing to translate
+_MOE_LEGACY_ONLY = {"routing_policy", "enable_sdrop", "use_fused_ops_topkrouter", "use_fused_ops_permute", "group_wise_a2a",
+                    "comp_comm_parallel", "comp_comm_parallel_degree", "ep_extend_tp", "callback_moe_droprate",
+                    "save_token_distribution", "cur_layer", "enable_cold_hot_expert", "hot_expert_num", "cold_token_percent",
+                    "moe_module_name", "enable_gmm_safe_tokens", "use_3d_tensor_parallel", "tp_x", "tp_y", "tp_z",
+                    "moe_shared_expert_overlap", "use_shared_expert_gating", "max_router_load", "expert_group_size",
+                    "enable_delay_allreduce"}
+
+
+def merge_moe_config(model_config: dict, moe_config) -> dict:
+    """Fold the older ``moe_config`` section (reference ``modules/transformer/moe.py:88`` ``MoEConfig``; top level of the
+    legacy YAMLs, e.g. ``research/telechat2/telechat2-39b-a12b/finetune_telechat_39b_a12b.yaml:34-50``) into the model
+    configuration: ``expert_num`` / ``num_experts_chosen`` / ``capacity_factor`` / ... are aliases the configuration
+    converter knows; ``aux_loss_factors`` + ``aux_loss_types`` become the one load-balancing coefficient; keys that only
+    select MindSpore code paths are dropped. Keys already present in the model configuration win."""
+    if not moe_config:
+        return model_config
+    moe = dict(moe_config.to_dict() if hasattr(moe_config, "to_dict") and not isinstance(moe_config, dict) else moe_config)
+    out = dict(model_config)
+    factors, types = moe.pop("aux_loss_factors", None), moe.pop("aux_loss_types", None)
+    if factors:
+        types = list(types or ["expert"] * len(factors))
+        coeff = next((f for f, t in zip(factors, types) if t == "expert"), factors[0])
+        if coeff:
+            moe.setdefault("router_aux_loss_coef", coeff)
+    if int(moe.get("expert_num", 1) or 1) <= 1:
+        return out                                        # a dense model that carries the section's defaults
+    if moe.get("shared_expert_num") in (0, None):
+        moe.pop("shared_expert_num", None)
+    moe.pop("capacity_factor", None)                      # the expert layers here are dropless: no token is cut off
+    for k, v in moe.items():
+        if k in _MOE_LEGACY_ONLY or v is None:
+            continue
+        out.setdefault(k, v)
+    return out
+
+
 class BaseModel(PreTrainedModel):
     """Name of the reference's older model base class (``models/base_model.py:39``: a cell with the generation mixin,
     ``load_checkpoint`` from ``checkpoint_name_or_path`` in the configuration and the ``from_pretrained`` family).
@@ -65,6 +103,7 @@ def build_network(config: dict, default_args=None):
     mc = dict(config.get("model_config") or {})
     if default_args:
         mc.update(default_args)
+    mc = merge_moe_config(mc, mc.pop("moe_config", None) or config.get("moe_config"))
     arch = (config.get("arch") or {}).get("type")
     if arch and "architectures" not in mc:
         mc["architectures"] = [arch]

@@ -39,7 +39,9 @@ def _model_dict(config) -> dict:
     if arch and "architectures" not in mc:
         mc["architectures"] = [arch]
     mc.pop("type", None)
-    return mc
+    from ..models import merge_moe_config
+    # the older YAMLs describe the experts in a top-level ``moe_config`` section
+    return merge_moe_config(mc, mc.pop("moe_config", None) or config.get("moe_config"))
 
 
 def parallel_kwargs(config) -> dict:

@@ -673,3 +673,40 @@ def test_build_model_config_and_base_model_alias(tmp_path):
     other.load_checkpoint(cfg)
     for (n, a), (_, b) in zip(net.state_dict().items(), other.state_dict().items()):
         assert torch.equal(a, b), n
+
+
+def test_legacy_moe_config_section_builds_the_experts():
+    """The older top-level ``moe_config`` section (TeleChat2-39B-A12B style YAML) reaches the model: expert count, top-k,
+    router dtype and the load-balancing coefficient; keys that only select the reference's code paths are dropped; a
+    dense model that carries the section's defaults stays dense."""
+    import os
+    import yaml
+    from mindformers_b200.models import build_network, merge_moe_config
+    from mindformers_b200.trainer.base_trainer import _model_dict
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = yaml.safe_load(open(os.path.join(root, "configs", "telechat2", "finetune_telechat2_39b_a12b.yaml")))
+    mc = _model_dict(cfg)
+    assert mc["expert_num"] == 16 and mc["num_experts_chosen"] == 4 and mc["router_aux_loss_coef"] == 0.01
+    assert "routing_policy" not in mc and "capacity_factor" not in mc and "shared_expert_num" not in mc
+    assert merge_moe_config({"hidden_size": 8}, {"expert_num": 1, "num_experts_chosen": 1}) == {"hidden_size": 8}
+    assert merge_moe_config({"expert_num": 4}, {"expert_num": 8})["expert_num"] == 4          # the model section wins
+    small = dict(mc, num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=4, intermediate_size=96,
+                 moe_intermediate_size=48, vocab_size=128, max_position_embeddings=64, seq_length=64, params_dtype="float32",
+                 compute_dtype="float32", device="cpu", fused_moe_comm=False)
+    net = build_network({"model_config": small})
+    tc = net.model.config
+    assert tc.num_moe_experts == 16 and tc.moe_router_topk == 4 and abs(tc.moe_aux_loss_coeff - 0.01) < 1e-12
+    names = [n for n, _ in net.named_parameters()]
+    assert any("experts" in n for n in names) and any("router" in n for n in names)
+    ids = torch.randint(0, 128, (2, 16))
+    loss = net.model(ids, ids)
+    loss = loss[0] if isinstance(loss, tuple) else loss
+    loss.float().mean().backward()
+    # the section nested under model_config works as well
+    nested = build_network({"model_config": dict({k: v for k, v in small.items() if k not in ("expert_num", "num_experts_chosen",
+                                                                                               "router_aux_loss_coef",
+                                                                                               "router_dense_type",
+                                                                                               "balance_via_topk_bias",
+                                                                                               "topk_bias_update_rate")},
+                                                 moe_config={"expert_num": 8, "num_experts_chosen": 2})})
+    assert nested.model.config.num_moe_experts == 8 and nested.model.config.moe_router_topk == 2
