@@ -326,3 +326,80 @@ def test_multiprocess_safetensors_conversion_equals_the_single_process_one(tmp_p
     load_checkpoint(fresh.model, os.path.dirname(index), strict=True)
     for (n, a), (_, b) in zip(m.model.named_parameters(), fresh.model.named_parameters()):
         assert torch.equal(a, b), n
+
+
+def test_harness_adapter_serves_the_three_request_kinds(monkeypatch):
+    """``MFLM`` under a stand-in for the lm-eval package (its ``TemplateLM`` base class and ``Instance`` requests): the
+    adapter registers as model "mf", ``loglikelihood`` equals the summed log-probabilities of the continuation under
+    the model, the greedy flag is right, rolling likelihoods add up over windows, ``generate_until`` cuts at the stop
+    string, and a two-choice task scored from these numbers picks the likelier continuation."""
+    import importlib
+    import os
+    import sys
+    import types
+    import torch
+    registry = {}
+    api = types.ModuleType("lm_eval.api")
+    model_mod = types.ModuleType("lm_eval.api.model")
+    reg_mod = types.ModuleType("lm_eval.api.registry")
+
+    class TemplateLM:                                   # what the harness's base class provides
+        def __init__(self):
+            self.cache_hook = None
+
+        def loglikelihood(self, requests, disable_tqdm=False):
+            new = []
+            for r in requests:
+                context, continuation = r.args
+                ctx = self.tok_encode(context) if context else [self.eot_token_id]
+                new.append(((context, continuation), ctx, self.tok_encode(continuation)))
+            return self._loglikelihood_tokens(new, disable_tqdm=disable_tqdm)
+
+    model_mod.TemplateLM = TemplateLM
+    reg_mod.register_model = lambda *names: (lambda cls: [registry.__setitem__(n, cls) for n in names] and cls)
+    pkg = types.ModuleType("lm_eval")
+    for name, mod in (("lm_eval", pkg), ("lm_eval.api", api), ("lm_eval.api.model", model_mod), ("lm_eval.api.registry", reg_mod)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.syspath_prepend(os.path.join(root, "toolkit", "benchmarks"))
+    sys.modules.pop("eval_with_harness", None)
+    ewh = importlib.import_module("eval_with_harness")
+    assert registry.get("mf") is ewh.MFLM and issubclass(ewh.MFLM, TemplateLM)
+
+    from mindformers_b200.models import ByteTokenizer, LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=260, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=128, seq_length=128, params_dtype="float32",
+                      compute_dtype="float32", block_size=4)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg, device="cpu")
+    tok = ByteTokenizer()
+    lm = ewh.MFLM(model=model, tokenizer=tok, max_length=64, max_gen_toks=8)
+
+    class Instance:
+        def __init__(self, *args):
+            self.args = args
+
+    ctx, a, b = "The capital of", " France", " Xq#z"
+    (ll_a, g_a), (ll_b, g_b) = lm.loglikelihood([Instance(ctx, a), Instance(ctx, b)])
+    ids = tok.encode(ctx, add_special_tokens=False) + tok.encode(a, add_special_tokens=False)
+    with torch.no_grad():
+        logp = torch.log_softmax(model.model(torch.tensor([ids])).float(), -1)
+    n = len(tok.encode(a, add_special_tokens=False))
+    want = sum(float(logp[i - 1, ids[i]]) for i in range(len(ids) - n, len(ids)))
+    assert abs(ll_a - want) < 1e-4 and isinstance(g_a, bool)
+    best = int(torch.tensor([ll_a, ll_b]).argmax())            # a two-choice task scored the harness way
+    assert best == (0 if ll_a >= ll_b else 1)
+    ctx_ids = tok.encode(ctx, add_special_tokens=False)
+    greedy_ids = model.generate([ctx_ids], max_new_tokens=3, do_sample=False)[0][len(ctx_ids):]
+    assert lm._loglikelihood_tokens([((ctx, ""), ctx_ids, greedy_ids)])[0][1] is True       # the model's own continuation
+    assert lm._loglikelihood_tokens([((ctx, ""), ctx_ids, [(greedy_ids[0] + 1) % 256] + greedy_ids[1:])])[0][1] is False
+    text = "abcdefghij" * 12                                    # longer than one window of 63 tokens
+    rolling = lm.loglikelihood_rolling([Instance(text)])[0]
+    short = lm.loglikelihood_rolling([Instance(text[:20])])[0]
+    assert rolling < short < 0
+    outs = lm.generate_until([Instance(ctx, {"until": ["\n"], "max_gen_toks": 6}), Instance(ctx, {"until": []})])
+    assert len(outs) == 2 and all(isinstance(o, str) for o in outs) and "\n" not in outs[0]
+    full = outs[1]
+    if len(full) > 2:
+        cut = lm.generate_until([Instance(ctx, {"until": [full[2]]})])[0]
+        assert cut == full.split(full[2])[0]
