@@ -709,6 +709,53 @@ class GracefulExitCallback(Callback):
 
 
 @_reg
+class StepPauseCallback(Callback):
+    """Training step pause (the TSP role of the reference's fault-tolerance runtime, ``version_control.py:412``
+    ``check_tsp_valid``): while ``<path>`` contains ``{"Pause": 1}`` every rank waits at a step boundary, with no
+    kernel or collective in flight, until the file is cleared (or says ``{"Pause": 0}``) or ``max_pause_seconds`` have
+    passed. The ranks agree on pausing and on resuming through one all-reduce per poll, so none runs ahead; the time
+    spent is recorded in ``paused_seconds``. An operator can use it to hold a job while a neighbour is serviced."""
+
+    def __init__(self, pause_path: Optional[str] = None, poll_steps: int = 1, poll_seconds: float = 1.0,
+                 max_pause_seconds: float = 3600.0, **kwargs):
+        self.path = pause_path or os.path.join(get_output_root_path(), "step_pause.json")
+        self.poll, self.poll_seconds, self.max_pause = max(1, poll_steps), float(poll_seconds), float(max_pause_seconds)
+        self.paused_seconds, self.pauses = 0.0, 0
+
+    def requested(self) -> bool:
+        try:
+            with open(self.path) as f:
+                return bool(json.load(f).get("Pause"))
+        except (OSError, ValueError):
+            return False
+
+    @staticmethod
+    def _agree(flag: bool) -> bool:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            t = torch.tensor([int(flag)], device="cuda" if dist.get_backend() == "nccl" else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return bool(t.item())
+        return flag
+
+    def on_step_end(self, ctx):
+        if ctx.global_step % self.poll or not self._agree(self.requested()):
+            return
+        import time as _time
+        logger.warning("step pause requested: holding at step %d", ctx.global_step)
+        self.pauses += 1
+        t0 = _time.time()
+        while True:
+            _time.sleep(self.poll_seconds)
+            waited = _time.time() - t0
+            # a rank keeps pausing while ANY rank still sees the request, and all give up together at the limit
+            if not self._agree(self.requested() and waited < self.max_pause):
+                break
+        self.paused_seconds += _time.time() - t0
+        logger.warning("step pause over after %.1f s, resuming at step %d", _time.time() - t0, ctx.global_step)
+
+
+@_reg
 class TrainFaultTolerance(Callback):
     """Host-side fault handling around the step loop (the reference delegates to MindIO TFT,
     ``trainer/base_trainer.py:1095-1125``): on an exception it calls ``ckpt_save_fn`` (try-to-persist) once

@@ -61,3 +61,30 @@ def test_stress_test_monitor_names_the_deviating_rank():
            "--master-port", str(_port()), os.path.join(ROOT, "tests", "dist", "run_stress_monitor.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, OMP_NUM_THREADS="1"))
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_step_pause_holds_the_loop_until_the_request_is_cleared(tmp_path):
+    """TSP: a ``{"Pause": 1}`` file holds training at a step boundary; clearing it (from another thread, as an operator
+    would) resumes; a request that is never cleared ends at ``max_pause_seconds``."""
+    import json
+    import threading
+    import time
+    from types import SimpleNamespace
+    from mindformers_b200.core.callback import StepPauseCallback
+    path = tmp_path / "step_pause.json"
+    cb = StepPauseCallback(pause_path=str(path), poll_seconds=0.05, max_pause_seconds=5.0)
+    ctx = SimpleNamespace(global_step=3)
+    t0 = time.time()
+    cb.on_step_end(ctx)                                   # no file: nothing happens
+    assert time.time() - t0 < 0.05 and cb.pauses == 0
+    path.write_text(json.dumps({"Pause": 1}))
+    threading.Timer(0.3, lambda: path.write_text(json.dumps({"Pause": 0}))).start()
+    t0 = time.time()
+    cb.on_step_end(ctx)
+    held = time.time() - t0
+    assert 0.25 < held < 2.0 and cb.pauses == 1 and abs(cb.paused_seconds - held) < 0.1
+    path.write_text(json.dumps({"Pause": 1}))
+    short = StepPauseCallback(pause_path=str(path), poll_seconds=0.05, max_pause_seconds=0.2)
+    t0 = time.time()
+    short.on_step_end(ctx)
+    assert 0.15 < time.time() - t0 < 1.0
