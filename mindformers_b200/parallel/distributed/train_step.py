@@ -45,6 +45,22 @@ class TrainOneStep:
         total = torch.zeros((), dtype=torch.float32, device=batch["input_ids"].device)
         per_token = getattr(model, "config", None) is not None and getattr(model.config, "calculate_per_token_loss", False)
         den_total = torch.zeros_like(total)
+        inv_den = None
+        if per_token and "labels" in batch and batch["labels"] is not None:
+            # the number of target tokens of the whole step is known before any forward pass (it is the model's own
+            # mask rule applied to the batch): every micro-batch's numerator is divided by it ON THE DEVICE, so the
+            # step needs no host read of the denominator
+            cfg = model.config
+            labels = batch["labels"]
+            if batch.get("loss_mask") is not None:
+                mask = batch["loss_mask"].to(torch.bool) & (labels != cfg.ignore_token_id)
+            else:
+                mask = (batch["input_ids"] != cfg.pad_token_id) & (labels != cfg.ignore_token_id)
+            den_all = mask.sum().to(torch.float32)
+            if ps.get_data_parallel_world_size(with_context_parallel=True) > 1:
+                import torch.distributed as dist
+                dist.all_reduce(den_all, group=ps.get_data_parallel_group(with_context_parallel=True))
+            inv_den = 1.0 / (den_all + 1e-8)
         for i in range(n_mb):
             mb = {k: v[i * mbs:(i + 1) * mbs] for k, v in batch.items() if v is not None}
             if i == n_mb - 1 and hasattr(opt, "begin_grad_overlap"):
@@ -52,7 +68,7 @@ class TrainOneStep:
             out = self.forward_fn(model, mb)
             if per_token:
                 num, den = out
-                (num * self.loss_scale).backward()
+                (num * (self.loss_scale if inv_den is None else self.loss_scale * inv_den)).backward()
                 total += num.detach()
                 den_total += den.detach()
             else:
@@ -60,8 +76,11 @@ class TrainOneStep:
                 total += out.detach() / n_mb
         dp = ps.get_data_parallel_world_size(with_context_parallel=True)
         scale = 1.0 / (dp * self.loss_scale)
-        if per_token:
-            # normalise by the number of target tokens over all micro-batches and data-parallel ranks
+        if per_token and inv_den is not None:
+            scale = 1.0 / self.loss_scale                     # the gradients already carry 1 / (target tokens of the step)
+            total = total / (den_total + 1e-8)                # this rank's mean loss per target token (a device value)
+        elif per_token:
+            # no labels in the batch to count from: normalise by the denominators the model returned (one host read)
             import torch.distributed as dist
             if dp > 1:
                 dist.all_reduce(den_total, group=ps.get_data_parallel_group(with_context_parallel=True))

@@ -317,3 +317,41 @@ def test_grouped_parameters_decay_exemptions_and_layer_wise_learning_rate():
     moved = {n: float((before[n] - p.detach()).abs().max()) for n, p in m.named_parameters()}
     assert abs(moved["embedding.word_embeddings.weight"] - 0.5 ** 4) < 1e-6
     assert abs(moved["decoder.layers.2.mlp.linear_fc2.weight"] - 0.5) < 1e-6 and abs(moved["output_layer.weight"] - 1.0) < 1e-6
+
+
+def test_per_token_loss_over_micro_batches_matches_one_big_batch():
+    """``calculate_per_token_loss``: micro-batches with very different numbers of target tokens; the step's gradients are
+    those of (sum of token losses) / (number of target tokens of the whole step), i.e. of one big batch, and the
+    denominator is taken from the batch on the device (no host read inside the step)."""
+    from mindformers_b200.trainer.engine import TrainingEngine
+    cfg = dict(model_type="llama", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+               intermediate_size=128, vocab_size=128, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=32)
+    ids = torch.randint(1, 128, (2, 33), generator=torch.Generator().manual_seed(0))
+    mask = torch.ones(2, 32, dtype=torch.int32)
+    mask[1, 5:] = 0                                            # the second sample has 5 target tokens, the first 32
+    batch = {"input_ids": ids[:, :-1].contiguous(), "labels": ids[:, 1:].contiguous(), "loss_mask": mask}
+
+    def run(mbs, per_token):
+        torch.manual_seed(3)
+        eng = TrainingEngine.from_model_config(cfg, seq_length=32, device="cpu", dtype="float32", micro_batch_size=mbs,
+                                               learning_rate=1e-2, max_grad_norm=0.0, calculate_per_token_loss=per_token)
+        out = eng.train_step_device(batch)
+        return {n: p.detach().clone() for n, p in eng.model.named_parameters()}, float(out["loss"]), eng
+
+    split, loss_split, eng = run(1, True)
+    whole, loss_whole, _ = run(2, True)
+    for n in split:
+        torch.testing.assert_close(split[n], whole[n], rtol=2e-5, atol=2e-6)
+    assert abs(loss_split - loss_whole) < 1e-5
+    # it is NOT the mean of the per-sample means (which the default loss computes with micro batch 1)
+    mean_of_means, _, _ = run(1, False)
+    assert max(float((mean_of_means[n] - split[n]).abs().max()) for n in split) > 1e-5
+    # the denominator stays on the device: the step never calls .item() on a tensor
+    calls = []
+    orig = torch.Tensor.item
+    torch.Tensor.item = lambda self: (calls.append(1), orig(self))[1]
+    try:
+        eng.train_step_device(batch)
+    finally:
+        torch.Tensor.item = orig
+    assert not calls
