@@ -396,3 +396,45 @@ def test_layer_gradients_are_final_when_the_layer_hook_fires():
         for n, g in grads.items():
             assert g.abs().sum() > 0
             torch.testing.assert_close(g, final[gid][n], rtol=0, atol=0)
+
+
+def test_gradient_bucket_and_publication_plans_tile_the_flat_buffer(monkeypatch):
+    """Host-side plans of the overlapped data-parallel paths, on a CPU model with the peer-memory state faked: the
+    per-layer gradient ranges tile one interval of the flat buffer in layer order and hold only that layer's weight
+    matrices; the publication rows (outside-the-layers below / above, then groups of layers) cover every element once;
+    a model with more layers than flag rows groups its layers."""
+    import torch
+    from mindformers_b200.trainer.engine import TrainingEngine
+
+    def plans(layers):
+        cfg = dict(model_type="llama", num_hidden_layers=layers, hidden_size=32, num_attention_heads=4, num_key_value_heads=2,
+                   intermediate_size=64, vocab_size=64, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=16)
+        eng = TrainingEngine.from_model_config(cfg, seq_length=16, device="cpu", dtype="float32")
+        opt = eng.optimizer
+        for sh in opt.shards.values():
+            sh.fused = True
+        monkeypatch.setattr(torch.cuda, "Stream", lambda device=None: None)
+        opt._setup_overlap("cpu")
+        return opt
+
+    opt = plans(3)
+    info = opt._ov_layers["dense"]
+    buf = opt.buffers["dense"]
+    assert info["ids"] == [0, 1, 2] and info["group"] == 1
+    for gid in info["ids"]:
+        lo, hi = info["span"][gid]
+        inside = [n for n, _, off, cnt in buf.entries if lo <= off < hi]
+        assert inside and all(f"layers.{gid}." in n for n in inside) and all("norm" not in n for n in inside)
+    assert all(info["span"][a][1] == info["span"][b][0] for a, b in zip(info["ids"], info["ids"][1:]))
+    rows = opt._publish_rows("dense")
+    assert [r for r, _, _ in rows] == list(range(len(rows))) and len(rows) == 2 + 3
+    covered = sorted((lo, hi) for _, lo, hi in rows if hi > lo)
+    assert covered[0][0] == 0 and covered[-1][1] == buf.ranges.numel
+    assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+    assert [opt._row_of_layer("dense", g) for g in info["ids"]] == [2, 3, 4]
+    big = plans(130)
+    info = big._ov_layers["dense"]
+    assert info["group"] == 3                                   # 130 layers over 64 gradient-bucket rows
+    rows = big._publish_rows("dense")
+    assert len(rows) <= 62 and big._row_of_layer("dense", 129) == rows[-1][0]
+    assert sorted({big._row_of_layer("dense", g) for g in info["ids"]}) == [r for r, _, _ in rows[2:]]
