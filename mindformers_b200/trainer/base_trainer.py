@@ -234,6 +234,16 @@ class BaseTrainer:
             total_steps = min(total_steps, stop_step)
         gbs = self.global_batch_size(config)
         self.engine = engine = self.create_engine(config, total_steps, model=network)
+        if config.get("only_save_strategy"):
+            # build the model under this job's layout, write its slicing description and stop: the files are the
+            # destination strategy of an offline checkpoint transformation (reference trainer/base_trainer.py)
+            from ..checkpoint.sharding import save_strategy
+            from ..tools.utils import get_real_rank
+            path = os.path.join(config.get("output_dir") or get_output_root_path(), "strategy",
+                                f"ckpt_strategy_rank_{get_real_rank()}.json")
+            save_strategy(engine.model, path)
+            logger.info("only_save_strategy: wrote %s, no training", path)
+            return {"strategy_file": path}
         seq_len = int(getattr(getattr(engine.model, "config", None), "seq_length", 0) or 0)
         ctx = RunContext(engine=engine, config=config, epochs=epochs, steps_per_epoch=steps_per_epoch, total_steps=total_steps,
                          global_batch_size=gbs, seq_length=seq_len)

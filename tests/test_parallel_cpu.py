@@ -438,3 +438,53 @@ def test_gradient_bucket_and_publication_plans_tile_the_flat_buffer(monkeypatch)
     rows = big._publish_rows("dense")
     assert len(rows) <= 62 and big._row_of_layer("dense", 129) == rows[-1][0]
     assert sorted({big._row_of_layer("dense", g) for g in info["ids"]}) == [r for r, _, _ in rows[2:]]
+
+
+def test_offline_transform_between_layouts_round_trips(tmp_path):
+    """``TransformCkpt`` / ``tools.transform_ckpt``: a tp = 2 checkpoint (per-rank files + strategy files) becomes (a) one
+    complete checkpoint, (b) the rank file of a single-rank layout whose loss matches, and (c), transformed back with
+    the tp = 2 strategy as destination, per-rank files whose tensors equal the original ones."""
+    import glob
+    import torch
+    from safetensors.torch import load_file
+    from tests.dist.run_save_tp_ckpt import CFG, batch
+    from mindformers_b200.checkpoint.sharding import save_strategy
+    from mindformers_b200.parallel.layers.gpt_model import GPTModel
+    from mindformers_b200.parallel.transformer_config import TransformerConfig
+    from mindformers_b200.tools import transform_ckpt
+    from mindformers_b200.tools.resume_ckpt import get_resume_checkpoint
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "dist", "run_save_tp_ckpt.py"), str(tmp_path)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, res.stderr[-3000:]
+    want = json.loads((tmp_path / "loss.json").read_text())["loss"]
+    src, strat = str(tmp_path / "checkpoint"), str(tmp_path / "strategy")
+    name = get_resume_checkpoint(src)
+    assert name and name.endswith(".safetensors") and get_resume_checkpoint(src, "mine.safetensors") == "mine.safetensors"
+    # (a) merge only
+    merged = transform_ckpt.main(["--src_ckpt_dir", src, "--src_ckpt_strategy", strat, "--dst_ckpt_dir", str(tmp_path / "full")])
+    full = load_file(os.path.join(merged, "model.safetensors"))
+    # (b) single-rank destination
+    torch.manual_seed(5)
+    cfg = TransformerConfig(**CFG)
+    cfg.device = "cpu"
+    model = GPTModel(cfg).eval()
+    save_strategy(model, str(tmp_path / "one" / "ckpt_strategy_rank_0.json"))
+    out = transform_ckpt.main(["--src_ckpt_dir", src, "--src_ckpt_strategy", strat, "--dst_ckpt_strategy", str(tmp_path / "one"),
+                               "--dst_ckpt_dir", str(tmp_path / "to_one"), "--prefix", "llama_"])
+    one = load_file(os.path.join(out, "rank_0", "llama_rank_0.safetensors"))
+    assert all(torch.equal(one[k], full[k]) for k in full)
+    sd = {n: one[n] for n, _ in model.named_parameters()}
+    model.load_state_dict(sd, strict=False)
+    inp, lab = batch()
+    with torch.no_grad():
+        assert abs(float(model(inp, labels=lab)) - want) < 1e-5
+    # (c) back to the source layout: the original shards come out again (weights and Adam moments)
+    back = transform_ckpt.main(["--src_ckpt_dir", merged, "--dst_ckpt_strategy", strat, "--dst_ckpt_dir", str(tmp_path / "back")])
+    for r in range(2):
+        orig = load_file(sorted(glob.glob(os.path.join(src, f"rank_{r}", "*.safetensors")))[-1])
+        again = load_file(os.path.join(back, f"rank_{r}", f"checkpoint_rank_{r}.safetensors"))
+        params = json.load(open(os.path.join(strat, f"ckpt_strategy_rank_{r}.json")))["params"]
+        for n in params:
+            assert torch.equal(again[n], orig[n]), (r, n)

@@ -355,3 +355,14 @@ def test_per_token_loss_over_micro_batches_matches_one_big_batch():
     finally:
         torch.Tensor.item = orig
     assert not calls
+
+
+def test_only_save_strategy_writes_the_layout_and_does_not_train(tmp_path):
+    from mindformers_b200.trainer import Trainer
+    _fresh()
+    t = Trainer(args=_cfg(tmp_path / "s", only_save_strategy=True))
+    t.train()
+    path = tmp_path / "s" / "strategy" / "ckpt_strategy_rank_0.json"
+    info = json.load(open(path))
+    assert info["tp"] == 1 and any("linear_qkv" in n for n in info["params"])
+    assert not t.trainer.loss_history and not os.path.exists(tmp_path / "s" / "checkpoint")
