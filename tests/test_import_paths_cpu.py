@@ -1,0 +1,93 @@
+"""Scripts written against the reference import their classes from its module paths: those paths resolve here too."""
+import importlib
+
+import pytest
+
+PATHS = {
+    "mindformers.auto_class": ["AutoModel", "AutoTokenizer"],
+    "mindformers.models.base_config": ["BaseConfig"],
+    "mindformers.models.base_model": ["BaseModel"],
+    "mindformers.models.build_config": ["build_model_config"],
+    "mindformers.models.build_model": ["build_model", "build_network"],
+    "mindformers.models.build_tokenizer": ["build_tokenizer"],
+    "mindformers.models.build_processor": ["build_processor"],
+    "mindformers.models.convert_slow_tokenizer": ["convert_slow_tokenizer"],
+    "mindformers.models.image_processing_utils": ["BaseImageProcessor"],
+    "mindformers.models.tokenization_utils_base": ["PreTrainedTokenizerBase", "BatchEncoding"],
+    "mindformers.models.tokenization_utils_fast": ["PreTrainedTokenizerFast"],
+    "mindformers.models.llama": ["LlamaConfig", "LlamaForCausalLM", "LlamaTokenizer", "LlamaTokenizerFast", "LlamaProcessor"],
+    "mindformers.models.llama.llama_config": ["LlamaConfig"],
+    "mindformers.models.llama.llama": ["LlamaForCausalLM"],
+    "mindformers.models.glm2": ["ChatGLM2Config", "ChatGLM2ForConditionalGeneration", "ChatGLM4Tokenizer"],
+    "mindformers.models.qwen2": ["Qwen2Config", "Qwen2ForCausalLM"],
+    "mindformers.models.qwen3": ["Qwen3Config", "Qwen3ForCausalLM"],
+    "mindformers.models.qwen3_moe": ["Qwen3MoeConfig", "Qwen3MoeForCausalLM"],
+    "mindformers.models.deepseek3": ["DeepseekV3Config", "DeepseekV3ForCausalLM"],
+    "mindformers.modules.block_tables": ["BlockTables"],
+    "mindformers.modules.cache_engine": ["BlockMemPool", "CacheEngine"],
+    "mindformers.modules.kvcache_mgr": ["KVCacheMgr"],
+    "mindformers.modules.paged_attention_mgr": ["PagedAttentionMgr"],
+    "mindformers.parallel_core.transformer_config": ["TransformerConfig"],
+    "mindformers.parallel_core.model_parallel_config": ["ModelParallelConfig"],
+    "mindformers.parallel_core.mf_model_config": ["MFModelConfig"],
+    "mindformers.parallel_core.transformer_config_utils": ["convert_to_transformer_config"],
+    "mindformers.parallel_core.process_group_config": ["ModelCommProcessGroups"],
+    "mindformers.parallel_core.utils.spec_utils": ["ModuleSpec", "build_module"],
+    "mindformers.parallel_core.utils.init_method": ["init_method_normal", "scaled_init_method_normal"],
+    "mindformers.parallel_core.training_graph": ["GPTModel", "ColumnParallelLinear", "RowParallelLinear"],
+    "mindformers.parallel_core.inference": ["GPTModel", "WeightsLoader"],
+    "mindformers.parallel_core.inference.parallel_state": ["initialize_model_parallel"],
+    "mindformers.pet.constants": ["PetType"],
+    "mindformers.pet.models": ["LoraModel"],
+    "mindformers.pet.tuners": ["LoraAdapter"],
+    "mindformers.pipeline.base_pipeline": ["BasePipeline"],
+    "mindformers.pipeline.pipeline": ["pipeline"],
+    "mindformers.pipeline.build_pipeline": ["build_pipeline"],
+    "mindformers.pipeline.text_generation_pipeline": ["TextGenerationPipeline"],
+    "mindformers.trainer.build_trainer": ["build_trainer"],
+    "mindformers.trainer.causal_language_modeling": ["CausalLanguageModelingTrainer"],
+    "mindformers.trainer.general_task_trainer": ["GeneralTaskTrainer"],
+    "mindformers.trainer.multi_modal_to_text_generation": ["MultiModalToTextGenerationTrainer"],
+    "mindformers.utils.load_checkpoint_utils": ["load_checkpoint", "is_hf_safetensors_dir"],
+    "mindformers.utils.resume_ckpt_utils": ["load_resume_context_from_checkpoint", "get_resume_checkpoint"],
+    "mindformers.utils.quantization_config": ["RtnConfig", "PtqConfig", "SmoothQuantConfig"],
+    "mindformers.wrapper.wrapper": ["MFTrainOneStepCell", "MFPipelineWithLossScaleCell"],
+    "mindformers.wrapper.adaptive_loss_scale": ["AdaptiveLossScaleUpdateCell"],
+    "mindformers.wrapper.build_wrapper": ["build_wrapper"],
+    "mindformers.dataset.build_dataset": ["build_dataset"],
+    "mindformers.dataset.dataloader": ["SFTDataLoader", "CommonDataLoader"],
+    "mindformers.dataset.handler": ["AlpacaInstructDataHandler", "PackingHandler"],
+    "mindformers.dataset.blended_datasets": ["GPTDataset", "IndexedDataset"],
+    "mindformers.dataset.keyword_gen_dataset": ["KeyWordGenDataset"],
+    "mindformers.dataset.multi_turn_dataset": ["MultiTurnDataset"],
+    "mindformers.generation.utils": ["softmax", "topk"],
+    "mindformers.tools.resume_ckpt": ["get_resume_checkpoint"],
+    "mindformers.tools.transform_ckpt": ["main"],
+    "mindformers.tools.ckpt_transform": ["TransformCkpt"],
+    "mindformers.core.callback": ["MFLossMonitor", "CheckpointMonitor"],
+    "mindformers.core.optim": ["AdamW", "FusedAdamW"],
+    "mindformers.core.lr": ["CosineWithWarmUpLR"],
+    "mindformers.core.context": ["build_context"],
+}
+
+
+@pytest.mark.parametrize("module", sorted(PATHS))
+def test_reference_import_path_resolves(module):
+    mod = importlib.import_module(module)
+    for name in PATHS[module]:
+        assert hasattr(mod, name), (module, name)
+
+
+def test_shims_are_the_same_objects_and_builders_work():
+    import numpy as np
+    from mindformers.models.llama import LlamaConfig as A
+    from mindformers_b200.models import LlamaConfig as B
+    assert A is B
+    from mindformers.pipeline.build_pipeline import build_pipeline
+    from mindformers.wrapper.build_wrapper import build_wrapper
+    assert build_pipeline() is None and build_wrapper() is None
+    from mindformers.generation.utils import log_softmax, softmax, topk
+    x = np.array([[1.0, 3.0, 2.0]])
+    assert abs(softmax(x).sum() - 1) < 1e-12 and np.allclose(np.exp(log_softmax(x)), softmax(x))
+    v, i = topk(x, 2)
+    assert v.tolist() == [[3.0, 2.0]] and i.tolist() == [[1, 2]]
