@@ -39,11 +39,41 @@ _EXPORTS = {
 
 __all__ = sorted(_EXPORTS) + ["__version__"]
 
+# Every other public name of these modules is reachable from the package root as well (the reference's root package
+# re-exports its sub-packages wholesale, ``mindformers/__init__.py:20-245``); they are searched in this order on first use.
+_SEARCH = ("core.callback", "core.lr", "core.optim", "core.loss", "core.metric", "core.clip_grad", "core.loss_scale",
+           "core.parallel_config", "core.context", "dataset", "dataset.dataloaders", "dataset.handlers",
+           "dataset.causal_language_model_dataset", "dataset.transforms", "dataset.sampler", "dataset.base_dataset",
+           "dataset.dataloader", "generation", "generation.logits_process", "models", "models.base_config",
+           "models.tokenization_utils_base", "models.auto", "models.families", "models.base_processor",
+           "models.image_processing_utils", "models.multi_modal", "models.processing_utils", "models.tokenizers",
+           "models.tokenization_utils", "modules", "modules.layers", "modules.transformer", "modules.activation",
+           "modules.local_block_sparse_attention", "modules.moe_legacy", "pet", "pet.adapters", "pipeline", "trainer",
+           "trainer.base_trainer", "tools.register", "tools.register.config", "tools.logger", "tools.utils", "wrapper",
+           "utils", "model_runner", "_root_aliases")
+_SUBPACKAGES = ("core", "dataset", "generation", "models", "modules", "pet", "pipeline", "trainer", "tools", "wrapper", "utils",
+                "model_runner", "inference", "parallel", "checkpoint", "serving", "fault", "ops")
+
+
+def _search(name: str):
+    for mod in _SEARCH:
+        try:
+            module = importlib.import_module(f"{__name__}.{mod}")
+        except ImportError:
+            continue
+        if name in getattr(module, "__dict__", {}) and not name.startswith("_"):
+            return getattr(module, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
 
 def __getattr__(name: str):
     mod = _EXPORTS.get(name)
     if mod is None:
-        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+        if name in _SUBPACKAGES:
+            return importlib.import_module(f"{__name__}.{name}")
+        value = _search(name)
+        globals()[name] = value
+        return value
     module = importlib.import_module(f"{__name__}.{mod}")
     if mod == name:
         return module          # the sub-package of the same name is callable and stands for the function too

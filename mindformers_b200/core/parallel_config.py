@@ -8,7 +8,7 @@ The objects carry the reference's field names; ``to_parallel_state_kwargs`` maps
 """
 from __future__ import annotations
 
-from dataclasses import asdict, dataclass, field
+from dataclasses import asdict, dataclass, field, is_dataclass
 from enum import Enum
 from typing import Any, Dict, List, Optional, Union
 
@@ -156,6 +156,31 @@ class TransformerOpParallelConfig:
         return {"colossalai_cp": "p2p", "ulysses_cp": "a2a", "hybrid_cp": "a2a+p2p"}[self.context_parallel_algo]
 
 
+@dataclass
+class EmbeddingOpParallelConfig:
+    """Degrees of the vocabulary embedding (reference ``modules/transformer/transformer.py:87``): with ``vocab_emb_dp``
+    the table is replicated and the lookup is data-parallel, otherwise its rows are split ``model_parallel`` ways."""
+    data_parallel: int = 1
+    model_parallel: int = 1
+    context_parallel: int = 1
+    use_seq_parallel: bool = False
+    select_recompute: bool = False
+    vocab_emb_dp: bool = True
+
+    def __post_init__(self):
+        if not isinstance(self.vocab_emb_dp, bool):
+            raise TypeError(f"vocab_emb_dp must be a bool, got {type(self.vocab_emb_dp).__name__}")
+        self.dp_mp_config                                   # validates the degrees
+
+    @property
+    def dp_mp_config(self) -> OpParallelConfig:
+        return OpParallelConfig(self.data_parallel, self.model_parallel, self.context_parallel, self.use_seq_parallel,
+                                self.select_recompute)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+
 default_transformer_config = TransformerOpParallelConfig()
 default_recompute_config = TransformerRecomputeConfig()
 default_moe_parallel_config = MoEParallelConfig()
@@ -187,3 +212,39 @@ def build_parallel_config(config) -> TransformerOpParallelConfig:
         else:
             setattr(config, key, val)
     return par
+
+
+def _as_dict(obj) -> Dict[str, Any]:
+    return obj.to_dict() if hasattr(obj, "to_dict") else asdict(obj)
+
+
+def _diff_dict(obj) -> Dict[str, Any]:
+    """The fields of a configuration object that differ from its class defaults."""
+    if hasattr(obj, "to_diff_dict"):
+        return obj.to_diff_dict()
+    full, base = _as_dict(obj), _as_dict(type(obj)())
+    return {k: v for k, v in full.items() if base.get(k) != v}
+
+
+def reset_parallel_config(config, reset_diff_config: bool = True):
+    """Inverse of ``build_parallel_config``: turn the ``moe_config`` / ``recompute_config`` / ``parallel_config`` objects
+    of ``config`` back into plain dicts (only the non-default fields with ``reset_diff_config``), so that the
+    configuration can be written to YAML or rebuilt (reference ``core/parallel_config.py:79``)."""
+    get = (lambda k: config.get(k)) if hasattr(config, "get") else (lambda k: getattr(config, k, None))
+
+    def put(k, v):
+        if hasattr(config, "__setitem__"):
+            config[k] = v
+        else:
+            setattr(config, k, v)
+
+    for key in ("moe_config", "recompute_config", "swap_config", "parallel_config"):
+        obj = get(key)
+        if obj is None or isinstance(obj, dict) or not (hasattr(obj, "to_dict") or is_dataclass(obj)):
+            continue
+        d = _diff_dict(obj) if reset_diff_config else _as_dict(obj)
+        if key == "parallel_config":
+            d.pop("recompute", None)
+            d.pop("swap", None)
+        put(key, d)
+    return config

@@ -480,3 +480,26 @@ class HFDataLoader:
             raise KeyError("rows carry no input_ids: add a tokenising handler")
         pid = getattr(tok, "pad_token_id", None)
         return _SampleList(records, seq_length, pad_token_id if pid is None else pid)
+
+
+@MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
+class BaseMultiModalDataLoader:
+    """Conversation-format annotation file → rows ``{"conversations": [[role, text], ...]}`` (reference
+    ``dataset/dataloader/multi_modal_dataloader.py:30``). ``extra_kwargs``: ``data_field`` (default "conversations"),
+    ``from_keyword`` ("from"), ``value_keyword`` ("value"), ``read_function`` (path → list of records)."""
+
+    def __new__(cls, annotation_file: str, shuffle: Optional[bool] = True, extra_kwargs: Optional[dict] = None, seed: int = 0,
+                **kwargs):
+        if not os.path.exists(annotation_file):
+            raise FileExistsError(f"The annotation_file {annotation_file} is not exist.")
+        extra = dict(extra_kwargs or {})
+        mk = dict(extra.get("map_function_kwargs") or {})
+        field = mk.get("data_field", extra.get("data_field", "conversations"))
+        fk = mk.get("from_keyword", extra.get("from_keyword", "from"))
+        vk = mk.get("value_keyword", extra.get("value_keyword", "value"))
+        reader = extra.get("read_function")
+        records = reader(annotation_file) if reader else read_records(annotation_file, "json" if annotation_file.endswith(".json") else None)
+        rows = [{"conversations": [[m[fk], m[vk]] for m in rec[field]]} for rec in records]
+        if shuffle:
+            random.Random(seed).shuffle(rows)
+        return _RawRecords(rows)

@@ -49,6 +49,30 @@ class InputBuilder:
         return ids
 
 
+def get_model(model_name_or_path: str, revision: Optional[str] = None, trust_remote_code: Optional[bool] = False, **kwargs):
+    """What a serving front end needs before any weights are loaded (reference ``model_runner.py:93``): the tokenizer
+    of the model directory and an ``InputBuilder`` that turns chat conversations into token ids. A directory whose
+    configuration names a multimodal processor gets ``(processor, processor)`` instead."""
+    if not os.path.isdir(model_name_or_path):
+        raise ValueError(f"{model_name_or_path} does not exist or is not a directory.")
+    from .models import AutoTokenizer
+    proc_cfg = None
+    for name in sorted(os.listdir(model_name_or_path)):
+        if name.endswith((".yaml", ".yml")):
+            from .tools.register import MindFormerConfig
+            cfg = MindFormerConfig(os.path.join(model_name_or_path, name))
+            p = cfg.get("processor")
+            if p and (p.get("image_processor") or p.get("modal_transform") or p.get("model_transform_template")):
+                proc_cfg = p
+            break
+    if proc_cfg is not None:
+        from .models.processing_utils import build_processor
+        processor = build_processor(proc_cfg)
+        return processor, processor
+    tokenizer = AutoTokenizer.from_pretrained(model_name_or_path, **{k: v for k, v in kwargs.items() if k != "use_fast"})
+    return tokenizer, InputBuilder(tokenizer)
+
+
 class ModelRunner:
     """Serving-side model wrapper (reference ``mindformers/model_runner.py:138,199``): builds the model and tokenizer
     from a directory and exposes ``forward(input_ids, valid_length_each_example, block_tables, slot_mapping, prefill,

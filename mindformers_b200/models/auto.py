@@ -129,6 +129,12 @@ class AutoModel:
 
 
 AutoModelForCausalLM = AutoModel
+# The reference keeps one factory per head type (``models/auto/modeling_auto.py``: ``AutoModelForPreTraining``,
+# ``AutoModelWithLMHead``, ``AutoModelForMaskGeneration`` ...). Every registered architecture is a causal language model,
+# so the head-specific factories resolve to the same classes.
+AutoModelForPreTraining = AutoModel
+AutoModelWithLMHead = AutoModel
+AutoModelForMaskGeneration = AutoModel
 
 
 class AutoTokenizer:
@@ -221,3 +227,62 @@ class AutoProcessor:
 
 
 AutoImageProcessor = AutoProcessor
+
+
+class _LazyMapping(dict):
+    """Read-only view ``key -> class`` over the family table and the user registrations, evaluated at lookup time
+    (reference ``models/auto/configuration_auto.py`` ``_LazyConfigMapping``, ``auto_factory.py`` ``_LazyAutoMapping``)."""
+
+    def __init__(self, pick):
+        super().__init__()
+        self._pick = pick
+
+    def _table(self):
+        out = {}
+        for key, pair in {**MODEL_TYPE_TO_CLASSES, **_EXTRA}.items():
+            val = self._pick(key, pair)
+            if val is not None:
+                out[key] = val
+        return out
+
+    def __getitem__(self, key):
+        return self._table()[key]
+
+    def __contains__(self, key):
+        return key in self._table()
+
+    def __iter__(self):
+        return iter(self._table())
+
+    def __len__(self):
+        return len(self._table())
+
+    def keys(self):
+        return self._table().keys()
+
+    def values(self):
+        return self._table().values()
+
+    def items(self):
+        return self._table().items()
+
+    def get(self, key, default=None):
+        return self._table().get(key, default)
+
+    def register(self, key, value, exist_ok: bool = False):
+        if key in self._table() and not exist_ok:
+            raise ValueError(f"{key!r} is already registered")
+        cfg, model = _EXTRA.get(key, MODEL_TYPE_TO_CLASSES.get(key, (None, None)))
+        _EXTRA[key] = (value, model) if self._pick(key, (value, None)) is value else (cfg, model)
+
+
+def _tokenizer_for(key, pair):
+    from . import tokenizers as T
+    name = T.TOKENIZER_BY_MODEL_TYPE.get(key)
+    return T.TOKENIZER_CLASSES.get(name) if name else None
+
+
+CONFIG_MAPPING = _LazyMapping(lambda key, pair: pair[0])
+CONFIG_MAPPING_NAMES = {k: v[0].__name__ for k, v in MODEL_TYPE_TO_CLASSES.items()}
+TOKENIZER_MAPPING = _LazyMapping(_tokenizer_for)
+from .image_processing_utils import IMAGE_PROCESSOR_MAPPING, AutoImageProcessor  # noqa: E402,F401

@@ -152,6 +152,46 @@ MixtralForCausalLM = _model("MixtralForCausalLM", MixtralConfig, "mixtral")
 TelechatForCausalLM = _model("TelechatForCausalLM", TelechatConfig, "telechat")
 ChatGLM2ForConditionalGeneration = _model("ChatGLM2ForConditionalGeneration", ChatGLM4Config, "glm")
 
+def _backbone(name, causal_cls):
+    class _B(causal_cls):
+        def forward(self, input_ids, position_ids=None, attn_meta=None, **kw):
+            return self.model(input_ids, None, None, position_ids, attn_meta, return_hidden=True,
+                              input_embeds=kw.get("input_embeds"))
+
+    _B.__name__ = _B.__qualname__ = name
+    _B.__doc__ = (f"The ``{causal_cls.__name__}`` network without its language-model head: ``forward(input_ids)`` returns the "
+                  f"final-norm hidden states ``[B * S, hidden]`` (reference ``models/llama/llama.py`` ``LlamaModel``, "
+                  f"``models/glm2/glm2.py`` ``ChatGLM2Model``). The head's weights are still built so that a causal-LM "
+                  f"checkpoint loads without missing keys.")
+    return _B
+
+
+LlamaModel = _backbone("LlamaModel", LlamaForCausalLM)
+ChatGLM2Model = _backbone("ChatGLM2Model", ChatGLM2ForConditionalGeneration)
+
+
+class ChatGLM2WithPtuning2(ChatGLM2ForConditionalGeneration):
+    """ChatGLM2 with P-Tuning v2 (reference ``models/glm2/glm2.py`` ``ChatGLM2WithPtuning2``): the base weights are frozen
+    and a per-layer key / value prefix of ``config.pet_config.pre_seq_len`` virtual tokens is trained."""
+
+    def __init__(self, config, **kwargs):
+        super().__init__(config, **kwargs)
+        from ..pet.pet_config import Ptuning2Config
+        from ..pet.prompt import PrefixTuningModel
+        pet = getattr(config, "pet_config", None) or {}
+        if not isinstance(pet, Ptuning2Config):
+            pet = dict(pet)
+            pet.pop("pet_type", None)
+            pet = Ptuning2Config(**pet)
+        tuned = PrefixTuningModel(pet, self)
+        object.__setattr__(self, "_tuned", tuned)           # not a sub-module: it holds this module already
+        self.prefix_encoder = tuned.prefix_encoder
+
+    def forward(self, *args, **kwargs):
+        self._tuned.current = self.prefix_encoder()
+        return super().forward(*args, **kwargs)
+
+
 # Names that configurations written for the reference use for the same models: its mcore shims pick a
 # ``Training...`` or ``Inference...`` class by run mode (``qwen3/modeling_qwen3.py:27-54``,
 # ``deepseek3/modeling_deepseek_v3.py:25-42``) and its research directories ship explicit tensor-parallel inference

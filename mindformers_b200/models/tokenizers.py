@@ -493,6 +493,27 @@ class ChatGLM3Tokenizer(_GLMChatMixin, _SentencePieceMixin, PreTrainedTokenizer)
 
 
 @MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
+class ChatGLM2Tokenizer(ChatGLM3Tokenizer):
+    """SentencePiece tokenizer of ChatGLM2 (reference ``models/glm2/glm2_tokenizer.py``): the five command tokens
+    ``[MASK] [gMASK] [sMASK] sop eop`` follow the SentencePiece vocabulary (no role tokens), inputs start with
+    ``[gMASK] sop``, and a chat is written as numbered rounds by ``build_prompt``."""
+
+    ROLE_TOKENS = ["[MASK]", "[gMASK]", "[sMASK]", "sop", "eop"]
+
+    def build_prompt(self, query: str, history=None) -> str:
+        prompt = ""
+        history = history or []
+        for i, (old_query, response) in enumerate(history):
+            prompt += "[Round {}]\n\n问：{}\n\n答：{}\n\n".format(i + 1, old_query, response)
+        return prompt + "[Round {}]\n\n问：{}\n\n答：".format(len(history) + 1, query)
+
+    def build_chat_input(self, query: str, history=None, role: str = "user", return_tensors: Optional[str] = "pt"):
+        ids = self.get_prefix_tokens() + self._to_ids(self.build_prompt(query, history))
+        row = {"input_ids": ids, "attention_mask": [1] * len(ids), "position_ids": list(range(len(ids)))}
+        return self._tensors(type(self).pad(self, [row], padding=False), return_tensors)
+
+
+@MindFormerRegister.register(MindFormerModuleType.TOKENIZER)
 class ChatGLM4Tokenizer(_GLMChatMixin, _TiktokenStyle):
     """GLM-4 tokenizer (reference ``models/glm2/glm4_tokenizer.py``): tiktoken-style byte-pair ranks in
     ``tokenizer.model``, the role tokens (``<|system|>``, ``<|user|>``, ...) and ``build_chat_input`` /
@@ -518,10 +539,10 @@ class ChatGLM4Tokenizer(_GLMChatMixin, _TiktokenStyle):
 TOKENIZER_BY_MODEL_TYPE = {
     "llama": "LlamaTokenizer", "llama2": "LlamaTokenizer", "llama3": "Llama3Tokenizer", "llama3_1": "Llama3Tokenizer",
     "qwen2": "Qwen2Tokenizer", "qwen2_5": "Qwen2Tokenizer", "qwen3": "Qwen2Tokenizer", "qwen3_moe": "Qwen2Tokenizer",
-    "chatglm": "ChatGLM3Tokenizer", "glm3": "ChatGLM3Tokenizer", "glm4": "ChatGLM4Tokenizer",
+    "chatglm2": "ChatGLM2Tokenizer", "glm2": "ChatGLM2Tokenizer", "chatglm": "ChatGLM3Tokenizer", "glm3": "ChatGLM3Tokenizer", "glm4": "ChatGLM4Tokenizer",
     "telechat": "TelechatTokenizer", "deepseek_v3": "LlamaTokenizerFast", "mixtral": "LlamaTokenizer",
 }
 TOKENIZER_CLASSES = {c.__name__: c for c in (LlamaTokenizer, LlamaTokenizerFast, Llama3Tokenizer, Qwen2Tokenizer,
-                                             ChatGLM3Tokenizer, ChatGLM4Tokenizer, TelechatTokenizer)}
+                                             ChatGLM2Tokenizer, ChatGLM3Tokenizer, ChatGLM4Tokenizer, TelechatTokenizer)}
 TOKENIZER_CLASSES["PreTrainedTokenizerFast"] = LlamaTokenizerFast
 TOKENIZER_CLASSES["Qwen2TokenizerFast"] = LlamaTokenizerFast

@@ -164,3 +164,64 @@ class AlibiTensor(nn.Module):
         """``attention_mask [B, S]`` (1 = token) → bias ``[B, H, 1, S]``."""
         pos = ((attention_mask.cumsum(-1) - 1) * attention_mask).to(torch.float32)
         return (self.slopes.to(pos.device) * pos[:, None, None, :]).to(dtype)
+
+
+class AlibiTensorV2(nn.Module):
+    """ALiBi bias from a token mask (reference ``modules/layers.py`` ``AlibiTensorV2``): ``attention_mask [B, S]`` (1 = token)
+    gives ``[B, num_heads, 1, S]`` with ``slope_h * (number of earlier tokens)`` at every token and 0 at padding, so
+    left- or right-padded batches get the distances of their real tokens."""
+
+    def __init__(self, num_heads: int):
+        super().__init__()
+        self.num_heads = num_heads
+        closest = 2 ** math.floor(math.log2(num_heads))
+        base = 2.0 ** (-(2.0 ** -(math.log2(closest) - 3)))
+        slopes = [base ** (i + 1) for i in range(closest)]
+        if closest != num_heads:
+            extra = 2.0 ** (-(2.0 ** -(math.log2(2 * closest) - 3)))
+            slopes += [extra ** (i + 1) for i in range(0, 2 * (num_heads - closest), 2)]
+        self.register_buffer("slopes", torch.tensor(slopes, dtype=torch.float32), persistent=False)
+
+    def forward(self, attention_mask: torch.Tensor, dtype=torch.float32):
+        m = attention_mask.to(torch.float32)
+        position = (m.cumsum(-1) - 1.0) * m                                   # [B, S]
+        return (self.slopes.to(m.device)[None, :, None, None] * position[:, None, None, :]).to(dtype)
+
+
+class AttentionMaskHF(nn.Module):
+    """Causal mask in the convention of the older attention cells (reference ``modules/transformer/transformer.py``
+    ``AttentionMaskHF``): ``input_mask [B, S]`` (1 = token) gives ``[B, S, S]`` with 1 where query i may attend key j
+    (j <= i and both are tokens)."""
+
+    def __init__(self, seq_length: int, compute_dtype=torch.float32):
+        super().__init__()
+        self.seq_length, self.dtype = seq_length, compute_dtype
+        self.register_buffer("tril", torch.tril(torch.ones(seq_length, seq_length)), persistent=False)
+
+    def forward(self, input_mask: torch.Tensor):
+        m = input_mask.to(self.dtype)
+        s = m.shape[-1]
+        return m[:, :, None] * m[:, None, :] * self.tril[:s, :s].to(m.device, self.dtype)
+
+
+class RotaryEmbedding(nn.Module):
+    """Applies rotary position embedding to query and key (reference ``modules/layers.py:1461``): ``xq, xk`` are
+    ``[B, heads, S, head_dim]``, ``freqs_cis = (cos, sin, swap_mask)`` as ``FreqsMgr`` returns them (``cos`` / ``sin``
+    ``[S, head_dim]``; the third entry is unused, the half rotation is done by slicing)."""
+
+    def __init__(self, head_dim: int = 128, compute_dtype=torch.float32, use_rope_slice: bool = False, **kwargs):
+        super().__init__()
+        self.head_dim, self.dtype = head_dim, compute_dtype
+
+    @staticmethod
+    def rotate_half(x):
+        a, b = x.chunk(2, dim=-1)
+        return torch.cat((-b, a), dim=-1)
+
+    def forward(self, xq: torch.Tensor, xk: torch.Tensor, freqs_cis):
+        cos, sin = freqs_cis[0], freqs_cis[1]
+        out = []
+        for x in (xq, xk):
+            xf = x.to(self.dtype)
+            out.append((xf * cos.to(self.dtype) + self.rotate_half(xf) * sin.to(self.dtype)).to(x.dtype))
+        return out[0], out[1]

@@ -83,3 +83,41 @@ class LocalBlockSparseAttention(nn.Module):
         probs = self.dropout(probs).to(v.dtype).reshape(B, H, nb, b, w, b)
         out = torch.einsum("bhnqwk,bhnwkd->bhnqd", probs, vb)
         return out.reshape(B, H, S, D)
+
+
+class FixedSparseAttention(nn.Module):
+    """Fixed-pattern sparse attention of the Sparse Transformer (reference ``modules/layers.py`` ``FixedSparseAttention``):
+    a query attends (causally) to the keys of its own block of ``block_size`` positions and to the last
+    ``num_different_global_patterns``-th ... "summary" column group of every earlier block: with ``g`` global patterns,
+    head ``h`` uses the ``block_size // g`` columns of slot ``g - 1 - (h % g)`` counted from the end of each block.
+    ``q, k, v``: ``[batch, seq, heads * size_per_head]``; ``attention_mask``: ``[batch, seq, seq]`` (1 = may attend).
+    Computed densely with the pattern as a mask (the pattern is what the layer defines, not how it is scheduled)."""
+
+    def __init__(self, batch_size=None, num_heads: int = 8, size_per_head: int = 64, block_size: int = 64,
+                 seq_length: int = 1024, num_different_global_patterns: int = 4, parallel_config=None):
+        super().__init__()
+        if seq_length % block_size or block_size % num_different_global_patterns:
+            raise ValueError("seq_length must be a multiple of block_size and block_size of num_different_global_patterns")
+        self.heads, self.hd, self.block, self.seq, self.g = num_heads, size_per_head, block_size, seq_length, num_different_global_patterns
+        pos = torch.arange(seq_length)
+        same_block = (pos[:, None] // block_size) == (pos[None, :] // block_size)
+        width = block_size // num_different_global_patterns
+        masks = []
+        for h in range(num_heads):
+            slot = num_different_global_patterns - 1 - (h % num_different_global_patterns)
+            col = pos % block_size
+            summary = (col >= slot * width) & (col < (slot + 1) * width)
+            masks.append(same_block | summary[None, :])
+        self.register_buffer("pattern", torch.stack(masks) & torch.tril(torch.ones(seq_length, seq_length, dtype=torch.bool)),
+                             persistent=False)
+
+    def forward(self, q, k, v, attention_mask=None):
+        B, S, _ = q.shape
+        qh, kh, vh = (t.view(B, S, self.heads, self.hd).transpose(1, 2).float() for t in (q, k, v))
+        scores = qh @ kh.transpose(-1, -2) * self.hd ** -0.5
+        allow = self.pattern[None, :, :S, :S].to(q.device)
+        if attention_mask is not None:
+            allow = allow & attention_mask[:, None].to(torch.bool)
+        scores = scores.masked_fill(~allow, float("-inf"))
+        probs = torch.nan_to_num(torch.softmax(scores, dim=-1))
+        return (probs @ vh).transpose(1, 2).reshape(B, S, self.heads * self.hd).to(q.dtype)

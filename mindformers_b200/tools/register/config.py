@@ -41,6 +41,32 @@ def _depth(obj, level=0):
             _depth(v, level + 1)
 
 
+class DictConfig(dict):
+    """A dict whose keys are also attributes (reference ``tools/register/config.py:31``); missing attributes read None.
+    ``to_dict`` gives back plain nested dicts."""
+
+    def __getattr__(self, key):
+        return self.get(key)
+
+    def __setattr__(self, key, value):
+        self[key] = value
+
+    def __delattr__(self, key):
+        del self[key]
+
+    def __deepcopy__(self, memo=None):
+        out = DictConfig()
+        for k, v in self.items():
+            out[copy.deepcopy(k, memo)] = copy.deepcopy(v, memo)
+        return out
+
+    def to_dict(self):
+        out = {}
+        for k, v in self.items():
+            out[k] = v.to_dict() if isinstance(v, DictConfig) else copy.deepcopy(v)
+        return out
+
+
 class MindFormerConfig(dict):
     """Nested attribute dictionary. ``MindFormerConfig("a.yaml", "b.yaml", key=value)``."""
 
