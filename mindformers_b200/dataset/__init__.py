@@ -10,3 +10,7 @@ from .dataloaders import (ADGenDataLoader, MultiSourceDataLoader, MultiSourceDat
                           TrainingDataLoader, TrainingDataset, read_records)
 from .sampler import build_sampler
 from .transforms import build_transforms
+
+from .._submodules import keep_functions as _keep_functions  # noqa: E402
+
+_keep_functions(__name__, ('build_dataset',))

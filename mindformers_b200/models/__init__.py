@@ -110,3 +110,7 @@ def build_network(config: dict, default_args=None):
     mc.pop("type", None)
     return AutoModel.from_config(mc)
 from .processing_utils import BaseProcessor, GLMProcessor, LlamaProcessor, ProcessorMixin, build_processor
+
+from .._submodules import keep_functions as _keep_functions  # noqa: E402
+
+_keep_functions(__name__, ('build_model', 'build_processor', 'build_tokenizer', 'convert_slow_tokenizer'))

@@ -165,3 +165,7 @@ class _CallablePackage(_types.ModuleType):
 
 
 _sys.modules[__name__].__class__ = _CallablePackage
+
+from .._submodules import keep_functions as _keep_functions  # noqa: E402
+
+_keep_functions(__name__, ('pipeline',))

@@ -91,3 +91,20 @@ def test_shims_are_the_same_objects_and_builders_work():
     assert abs(softmax(x).sum() - 1) < 1e-12 and np.allclose(np.exp(log_softmax(x)), softmax(x))
     v, i = topk(x, 2)
     assert v.tolist() == [[3.0, 2.0]] and i.tolist() == [[1, 2]]
+
+
+def test_function_names_survive_importing_their_modules():
+    """``models.build_processor`` is a function and also a module path of the reference; importing the module (under
+    either package name) must not replace the function."""
+    import mindformers_b200.dataset as ds
+    import mindformers_b200.models as models
+    import mindformers_b200.pipeline as pl
+    import mindformers_b200.trainer as tr
+    for name in ("mindformers.models.build_processor", "mindformers_b200.models.build_model", "mindformers.models.build_tokenizer",
+                 "mindformers.models.convert_slow_tokenizer", "mindformers.pipeline.pipeline", "mindformers.trainer.build_trainer",
+                 "mindformers_b200.dataset.build_dataset", "mindformers.dataset.transforms.build_transforms"):
+        mod = importlib.import_module(name)
+        assert callable(getattr(mod, name.rsplit(".", 1)[1]))
+    for fn in (models.build_processor, models.build_model, models.build_tokenizer, models.convert_slow_tokenizer,
+               pl.pipeline, tr.build_trainer, ds.build_dataset, ds.transforms.build_transforms):
+        assert callable(fn) and not isinstance(fn, type(importlib))
