@@ -12,7 +12,8 @@ import types
 
 class _Package(types.ModuleType):
     def __setattr__(self, name, value):
-        if isinstance(value, types.ModuleType) and name in self.__dict__.get("_kept_functions", ()):
+        if isinstance(value, types.ModuleType) and (name in self.__dict__.get("_kept_functions", ()) or (
+                name in self.__dict__ and not isinstance(self.__dict__[name], types.ModuleType))):
             return
         super().__setattr__(name, value)
 
@@ -24,3 +25,49 @@ def keep_functions(package_name: str, names):
             raise ImportError(f"{package_name}.{name} is not bound to a function")
     pkg.__dict__["_kept_functions"] = tuple(names)
     pkg.__class__ = _Package
+
+
+# ---- reference paths below a module that is a single file here -------------------------------------------------------
+# The reference splits some packages over several files (``core/callback/callback.py`` + ``build_callback.py``) that
+# are one module here (``core/callback.py``). ``alias_children(module, children)`` lets ``import module.child``
+# resolve: the module gets an empty ``__path__`` (which is what makes the import system look for children at all) and
+# a finder returns, for each listed child, the module itself (or another module given by name).
+import importlib
+import importlib.abc
+import importlib.util
+
+_CHILDREN = {}
+
+
+class _SameModuleLoader(importlib.abc.Loader):
+    def __init__(self, target: str):
+        self.target = target
+
+    def create_module(self, spec):
+        return importlib.import_module(self.target)
+
+    def exec_module(self, module):
+        pass
+
+
+class _ChildFinder(importlib.abc.MetaPathFinder):
+    def find_spec(self, fullname, path=None, target=None):
+        real = _CHILDREN.get(fullname)
+        if real is None:
+            return None
+        return importlib.util.spec_from_loader(fullname, _SameModuleLoader(real))
+
+
+def alias_children(module_name: str, children):
+    """``children``: names (resolve to ``module_name`` itself) or ``(name, target module)`` pairs."""
+    mod = sys.modules[module_name]
+    if not hasattr(mod, "__path__"):
+        mod.__path__ = []
+    for child in children:
+        name, target = (child, module_name) if isinstance(child, str) else child
+        _CHILDREN[f"{module_name}.{name}"] = target
+    if not any(isinstance(f, _ChildFinder) for f in sys.meta_path):
+        sys.meta_path.append(_ChildFinder())
+    if not isinstance(mod, _Package):
+        mod.__dict__.setdefault("_kept_functions", ())
+        mod.__class__ = _Package

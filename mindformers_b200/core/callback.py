@@ -787,3 +787,8 @@ def build_callback(config=None, default_args: Optional[dict] = None, **kwargs):
     if isinstance(config, Callback):
         return config
     return MindFormerRegister.get_instance_from_cfg(dict(config), MindFormerModuleType.CALLBACK, default_args=default_args)
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['callback', 'build_callback'])

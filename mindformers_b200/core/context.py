@@ -260,3 +260,8 @@ def set_context(**kwargs):
 
 def is_context_built() -> bool:
     return _CONTEXT is not None
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['build_context', 'parallel', 'validators'])

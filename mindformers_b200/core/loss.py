@@ -19,3 +19,8 @@ def build_loss(config=None, default_args=None, **kwargs):
 
 
 __all__ = ["CrossEntropyLoss", "VocabParallelCrossEntropy", "build_loss"]
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['loss', 'build_loss'])

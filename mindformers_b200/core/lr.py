@@ -232,3 +232,8 @@ def build_lr(config: Optional[dict] = None, default_args: Optional[dict] = None,
     if "type" not in cfg:
         return float(cfg["learning_rate"])
     return MindFormerRegister.get_instance_from_cfg(cfg, MindFormerModuleType.LR, default_args=default_args)
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['lr_schedule', 'build_lr'])

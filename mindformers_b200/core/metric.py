@@ -225,3 +225,8 @@ def build_metric(config=None, default_args=None, **kwargs):
     if isinstance(config, (list, tuple)):
         return [build_metric(c, default_args) for c in config]
     return MindFormerRegister.get_instance_from_cfg(dict(config), MindFormerModuleType.METRIC, default_args=default_args)
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['metric', 'build_metric', 'utils'])

@@ -248,3 +248,8 @@ def build_optim(config: dict, default_args: Optional[dict] = None, model: Option
         if "learning_rate" in cfg and target.__module__.startswith("torch.optim"):
             cfg["lr"] = cfg.pop("learning_rate")
     return MindFormerRegister.get_instance_from_cfg(cfg, MindFormerModuleType.OPTIMIZER, default_args=args)
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['adamw', 'build_optim', 'came', 'fused_adamw'])

@@ -161,3 +161,8 @@ def build_sampler(config=None, default_args: Optional[dict] = None, module_type:
         return MindFormerRegister.get_instance_from_cfg(dict(config), MindFormerModuleType.DATASET_SAMPLER,
                                                         default_args=default_args)
     return MindFormerRegister.get_instance(module_type, class_name, **kwargs)
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['build_sampler'])

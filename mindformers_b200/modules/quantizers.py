@@ -255,3 +255,8 @@ class AutoQuantizer:
         if kv and getattr(model, "config", None) is not None:
             model.config.kv_cache_dtype = str(kv)        # picked up when the generation code allocates the paged cache
         return n
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['auto', 'base', 'ptq_quantizer', 'rtn_quantizer', 'smooth_quant_quantizer'])

@@ -236,3 +236,13 @@ class Transformer(nn.Module):
         out, dec_present = self.decoder(decoder_inputs, decoder_masks, enc_out if self.encoder is not None else None,
                                         memory_mask)
         return out, enc_present, dec_present
+
+
+# the parallel configuration objects live in ``core/parallel_config.py``; the reference exports them from here too
+# (``modules/transformer/__init__.py``)
+from ..core.parallel_config import (EmbeddingOpParallelConfig, MoEParallelConfig, OpParallelConfig,  # noqa: E402,F401
+                                    TransformerOpParallelConfig, TransformerRecomputeConfig, TransformerSwapConfig)
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ['transformer', 'op_parallel_config', ('moe', 'mindformers_b200.modules.moe_legacy'), ('moev3', 'mindformers_b200.modules.moe_legacy'), ('moe_utils', 'mindformers_b200.modules.moe_legacy')])

@@ -108,3 +108,35 @@ def test_function_names_survive_importing_their_modules():
     for fn in (models.build_processor, models.build_model, models.build_tokenizer, models.convert_slow_tokenizer,
                pl.pipeline, tr.build_trainer, ds.build_dataset, ds.transforms.build_transforms):
         assert callable(fn) and not isinstance(fn, type(importlib))
+
+
+CHILD_PATHS = {
+    "mindformers.core.callback.callback": ["MFLossMonitor", "CheckpointMonitor"],
+    "mindformers.core.callback.build_callback": ["build_callback"],
+    "mindformers.core.context.build_context": ["build_context"],
+    "mindformers.core.loss.loss": ["CrossEntropyLoss"],
+    "mindformers.core.lr.lr_schedule": ["CosineWithWarmUpLR"],
+    "mindformers.core.lr.build_lr": ["build_lr"],
+    "mindformers.core.metric.metric": ["PerplexityMetric"],
+    "mindformers.core.optim.adamw": ["AdamW"],
+    "mindformers.core.optim.came": ["CAME"],
+    "mindformers.core.optim.build_optim": ["build_optim"],
+    "mindformers.modules.transformer.transformer": ["TransformerOpParallelConfig", "EmbeddingOpParallelConfig"],
+    "mindformers.modules.transformer.op_parallel_config": ["OpParallelConfig"],
+    "mindformers.modules.transformer.moe": ["MoEConfig"],
+    "mindformers.modules.quantizers.rtn_quantizer": ["AutoQuantizer"],
+    "mindformers.dataset.sampler.build_sampler": ["build_sampler"],
+    "mindformers.dataset.utils": ["check_dataset_config"],
+    "mindformers.tools.ckpt_transform.utils": ["is_power_of_two", "make_soft_link"],
+    "mindformers.generation.parallel_decoding_mcore": ["la_pre_process"],
+    "mindformers.modules.flash_attention": ["FlashAttention"],
+}
+
+
+@pytest.mark.parametrize("path", sorted(CHILD_PATHS))
+def test_reference_paths_below_single_file_modules(path):
+    mod = importlib.import_module(path)
+    for name in CHILD_PATHS[path]:
+        assert hasattr(mod, name), f"{path} lacks {name}"
+    import mindformers_b200.core.context as ctx
+    assert callable(ctx.build_context) and not isinstance(ctx.build_context, type(importlib))

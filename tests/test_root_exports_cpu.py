@@ -264,3 +264,80 @@ def test_get_model_returns_tokenizer_and_builder(tmp_path):
     assert tokenizer.encode("hello world")[-2:] == [1, 2]
     ids = builder.make_context(0, [{"role": "user", "content": "hello"}])
     assert 1 in ids
+
+
+def _dense_attention(q, k, v, scale, discard=None, bias=None):
+    rep = q.shape[1] // k.shape[1]
+    s = (q.float() @ k.float().repeat_interleave(rep, 1).transpose(-1, -2)) * scale
+    if bias is not None:
+        s = s + bias
+    if discard is not None:
+        s = s.masked_fill(discard, float("-inf"))
+    return torch.softmax(s, -1) @ v.float().repeat_interleave(rep, 1)
+
+
+def test_flash_attention_layer_layouts_and_sparse_modes():
+    from mindformers_b200.modules.flash_attention import FlashAttention
+    torch.manual_seed(0)
+    B, S, N, Nkv, D = 2, 12, 4, 2, 8
+    q, k, v = torch.randn(B, N, S, D), torch.randn(B, Nkv, S, D), torch.randn(B, Nkv, S, D)
+    scale = D ** -0.5
+    causal = torch.triu(torch.ones(S, S, dtype=torch.bool), 1)
+    want = _dense_attention(q, k, v, scale, causal)
+    # BNSD, causal by sparse_mode
+    out = FlashAttention(N, scale_value=scale, input_layout="BNSD", sparse_mode=2)(q, k, v)
+    assert torch.allclose(out, want, atol=1e-5)
+    # BSH, causal by an explicit mask (1 = discard)
+    flat = lambda t: t.transpose(1, 2).reshape(B, S, -1)
+    out = FlashAttention(N, scale_value=scale, input_layout="BSH", sparse_mode=0)(flat(q), flat(k), flat(v), causal.to(torch.uint8))
+    assert torch.allclose(out, flat(want), atol=1e-5)
+    # band: 3 tokens back, none ahead
+    qi, ki = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    band = (ki > qi) | (ki < qi - 3)
+    out = FlashAttention(N, scale_value=scale, input_layout="BNSD", sparse_mode=4, pre_tokens=3, next_tokens=0)(q, k, v)
+    assert torch.allclose(out, _dense_attention(q, k, v, scale, band), atol=1e-5)
+    # alibi bias
+    bias = mf.AlibiTensorV2(N)(torch.ones(B, S))
+    out = FlashAttention(N, scale_value=scale, input_layout="BNSD", sparse_mode=2, use_alibi_mask=True)(q, k, v, alibi_mask=bias)
+    assert torch.allclose(out, _dense_attention(q, k, v, scale, causal, bias), atol=1e-5)
+    # packed documents
+    T = 10
+    pq, pk, pv = torch.randn(T, N * D), torch.randn(T, Nkv * D), torch.randn(T, Nkv * D)
+    out = FlashAttention(N, scale_value=scale, input_layout="TH", sparse_mode=3)(pq, pk, pv, actual_seq_qlen=[4, 10],
+                                                                              actual_seq_kvlen=[4, 10])
+    for a, b in ((0, 4), (4, 10)):
+        qs = pq[a:b].view(1, b - a, N, D).transpose(1, 2)
+        ks = pk[a:b].view(1, b - a, Nkv, D).transpose(1, 2)
+        vs = pv[a:b].view(1, b - a, Nkv, D).transpose(1, 2)
+        w = _dense_attention(qs, ks, vs, scale, torch.triu(torch.ones(b - a, b - a, dtype=torch.bool), 1))
+        assert torch.allclose(out[a:b], w.transpose(1, 2).reshape(b - a, -1), atol=1e-5)
+
+
+def test_la_pre_process_drops_padding_slots():
+    import numpy as np
+    from mindformers_b200.generation.parallel_decoding_mcore import compact_padded_tokens, la_pre_process
+    slots = np.arange(12).reshape(3, 4)                # 3 sequences padded to 4 tokens
+    out, mask = la_pre_process(None, slots, q_seq_lens=[2, 4, 1])
+    assert out.tolist() == [0, 1, 4, 5, 6, 7, 8] and mask.shape == (1, 1)
+    same, m2 = la_pre_process(None, np.arange(7), q_seq_lens=[2, 4, 1], spec_mask=np.ones((7, 7)))
+    assert same.tolist() == list(range(7)) and m2.shape == (7, 7)
+    assert la_pre_process(None, np.arange(3), q_seq_lens=1)[0].tolist() == [0, 1, 2]
+    assert compact_padded_tokens(np.arange(12).reshape(3, 4) + 100, [2, 4, 1]).tolist() == [100, 101, 104, 105, 106, 107, 108]
+
+
+def test_ckpt_transform_utils(tmp_path, capsys):
+    from mindformers_b200.tools.ckpt_transform.utils import (check_ckpt_file_exist, check_path, check_rank_folders,
+                                                             is_power_of_two, make_soft_link, show_progress)
+    assert is_power_of_two(8) and not is_power_of_two(6) and not is_power_of_two(0)
+    (tmp_path / "rank_0").mkdir()
+    (tmp_path / "rank_0" / "a.safetensors").write_bytes(b"x")
+    assert check_rank_folders(str(tmp_path), 0) and not check_rank_folders(str(tmp_path), 1)
+    assert check_ckpt_file_exist(str(tmp_path / "rank_0")) and not check_ckpt_file_exist(str(tmp_path))
+    link = tmp_path / "links" / "latest"
+    make_soft_link(str(link), str(tmp_path / "rank_0"), target_is_directory=True)
+    make_soft_link(str(link), str(tmp_path / "rank_0"), target_is_directory=True)        # replaces the link
+    assert os.path.islink(link) and os.path.exists(link / "a.safetensors")
+    with pytest.raises(FileNotFoundError):
+        check_path(str(tmp_path / "nope"))
+    show_progress(1.0, "transform")
+    assert "100.00%" in capsys.readouterr().out
