@@ -26,10 +26,12 @@ class _AliasLoader(importlib.abc.Loader):
         self.target = target
 
     def create_module(self, spec):
-        return importlib.import_module(self.target)      # the very module object of the implementation
+        module = importlib.import_module(self.target)    # the very module object of the implementation
+        self._spec = module.__spec__                     # the import system rebinds ``__spec__`` to the alias's
+        return module
 
     def exec_module(self, module):
-        pass
+        module.__spec__ = self._spec
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):

@@ -84,3 +84,8 @@ def __getattr__(name: str):
 
 def __dir__():
     return __all__
+
+from ._reference_paths import PATHS as _REFERENCE_PATHS  # noqa: E402
+from ._submodules import register_paths as _register_paths  # noqa: E402
+
+_register_paths(__name__, _REFERENCE_PATHS)

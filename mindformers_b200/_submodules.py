@@ -24,7 +24,15 @@ def keep_functions(package_name: str, names):
         if isinstance(pkg.__dict__.get(name), types.ModuleType) or name not in pkg.__dict__:
             raise ImportError(f"{package_name}.{name} is not bound to a function")
     pkg.__dict__["_kept_functions"] = tuple(names)
-    pkg.__class__ = _Package
+    _guard(pkg)
+
+
+def _guard(mod):
+    """Gives ``mod`` the guarded attribute assignment, keeping what its current module class adds (e.g. ``__call__``)."""
+    cls = type(mod)
+    if issubclass(cls, _Package):
+        return
+    mod.__class__ = _Package if cls is types.ModuleType else type(cls.__name__, (_Package, cls), {})
 
 
 # ---- reference paths below a module that is a single file here -------------------------------------------------------
@@ -44,18 +52,49 @@ class _SameModuleLoader(importlib.abc.Loader):
         self.target = target
 
     def create_module(self, spec):
-        return importlib.import_module(self.target)
+        module = importlib.import_module(self.target)
+        self._spec = module.__spec__          # the import system rebinds ``__spec__`` to the alias's; put it back
+        return module
 
     def exec_module(self, module):
-        pass
+        module.__spec__ = self._spec
+
+
+_NODES = set()
+
+
+class _EmptyPackageLoader(importlib.abc.Loader):
+    def create_module(self, spec):
+        return None
+
+    def exec_module(self, module):
+        module.__doc__ = "Directory level of a reference module path; the leaves below it resolve to modules of this package."
 
 
 class _ChildFinder(importlib.abc.MetaPathFinder):
     def find_spec(self, fullname, path=None, target=None):
         real = _CHILDREN.get(fullname)
-        if real is None:
-            return None
-        return importlib.util.spec_from_loader(fullname, _SameModuleLoader(real))
+        if real is not None:
+            return importlib.util.spec_from_loader(fullname, _SameModuleLoader(real))
+        if fullname in _NODES:
+            return importlib.util.spec_from_loader(fullname, _EmptyPackageLoader(), is_package=True)
+        return None
+
+
+def _install_finder():
+    if not any(isinstance(f, _ChildFinder) for f in sys.meta_path):
+        sys.meta_path.append(_ChildFinder())
+
+
+def register_paths(root: str, table):
+    """``table``: ``{"a.b.leaf": "x.y"}`` relative to package ``root``: ``root.a.b.leaf`` resolves to module ``root.x.y``;
+    directory levels that do not exist (``root.a.b``) become empty packages."""
+    for rel, target in table.items():
+        _CHILDREN.setdefault(f"{root}.{rel}", f"{root}.{target}")
+        parts = rel.split(".")
+        for i in range(1, len(parts)):
+            _NODES.add(f"{root}." + ".".join(parts[:i]))
+    _install_finder()
 
 
 def alias_children(module_name: str, children):
@@ -66,8 +105,6 @@ def alias_children(module_name: str, children):
     for child in children:
         name, target = (child, module_name) if isinstance(child, str) else child
         _CHILDREN[f"{module_name}.{name}"] = target
-    if not any(isinstance(f, _ChildFinder) for f in sys.meta_path):
-        sys.meta_path.append(_ChildFinder())
-    if not isinstance(mod, _Package):
-        mod.__dict__.setdefault("_kept_functions", ())
-        mod.__class__ = _Package
+    _install_finder()
+    mod.__dict__.setdefault("_kept_functions", ())
+    _guard(mod)

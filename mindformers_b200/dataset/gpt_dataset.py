@@ -8,6 +8,7 @@ not in the model.
 """
 from __future__ import annotations
 
+import enum
 import hashlib
 import json
 import os
@@ -53,6 +54,61 @@ def parse_split(split: str) -> List[float]:
     if s <= 0:
         raise ValueError(f"split {split!r} has no positive entry")
     return [p / s for p in parts[:3]]
+
+
+class Split(enum.Enum):
+    train = 0
+    valid = 1
+    test = 2
+
+
+def normalize(weights: Sequence[float]) -> List[float]:
+    """Weights divided by their sum (float64)."""
+    w = np.asarray(weights, dtype=np.float64)
+    return (w / w.sum()).tolist()
+
+
+def parse_and_normalize_split(split: str) -> List[float]:
+    """``"99,1,0"`` / ``"99/1"`` → three fractions that sum to 1."""
+    return parse_split(split)
+
+
+def convert_split_vector_to_split_matrix(vector_a: Sequence[float], vector_b: Optional[Sequence[float]] = None):
+    """Fractions → ``[(begin, end) or None]`` bookends on [0, 1] per split; with a second vector, the overlap of the two
+    layouts per split (used to carve a retrieval corpus from the same documents)."""
+    def bookends(v):
+        edges = np.concatenate([[0.0], np.cumsum(np.asarray(v, dtype=np.float64))])
+        return [(float(edges[i]), float(edges[i + 1])) if edges[i + 1] > edges[i] else None for i in range(len(v))]
+
+    a = bookends(vector_a)
+    if vector_b is None:
+        return a
+    out = []
+    for x, y in zip(a, bookends(vector_b)):
+        if x is None or y is None:
+            out.append(None)
+            continue
+        lo, hi = max(x[0], y[0]), min(x[1], y[1])
+        out.append((lo, hi) if hi > lo else None)
+    return out
+
+
+def get_blend_from_list(blend: Optional[Sequence[str]]):
+    """``["30", "a_prefix", "70", "b_prefix"]`` → ``(["a_prefix", "b_prefix"], [30.0, 70.0])``; a plain list of prefixes →
+    ``(prefixes, None)``; None → None."""
+    if blend is None:
+        return None
+    items = [str(b).strip() for b in blend]
+    if len(items) % 2 == 0:
+        try:
+            weights = [float(w) for w in items[0::2]]
+            return items[1::2], weights
+        except ValueError:
+            pass
+    return items, None
+
+
+BlendedMegatronDatasetConfig = GPTDatasetConfig
 
 
 class GPTDataset(torch.utils.data.Dataset):

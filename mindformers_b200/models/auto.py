@@ -286,3 +286,61 @@ CONFIG_MAPPING = _LazyMapping(lambda key, pair: pair[0])
 CONFIG_MAPPING_NAMES = {k: v[0].__name__ for k, v in MODEL_TYPE_TO_CLASSES.items()}
 TOKENIZER_MAPPING = _LazyMapping(_tokenizer_for)
 from .image_processing_utils import IMAGE_PROCESSOR_MAPPING, AutoImageProcessor  # noqa: E402,F401
+
+
+def is_experimental_mode(path) -> bool:
+    """Whether ``path`` is a model directory / repository name (the ``from_pretrained`` route of the reference that reads
+    ``config.json``) rather than a YAML file or a name of the built-in support list."""
+    if not isinstance(path, str):
+        return False
+    if os.path.isdir(path):
+        return not any(f.endswith((".yaml", ".yml")) for f in os.listdir(path))
+    return not path.endswith((".yaml", ".yml")) and path not in PRESETS and "/" in path
+
+
+def config_class_to_model_type(config_class_name: str):
+    """``"LlamaConfig"`` → ``"llama"``; None for an unknown class name."""
+    for key, pair in {**MODEL_TYPE_TO_CLASSES, **_EXTRA}.items():
+        if pair[0] is not None and pair[0].__name__ == config_class_name:
+            return key
+    return None
+
+
+def tokenizer_class_from_name(class_name: str):
+    from . import tokenizers as T
+    return T.TOKENIZER_CLASSES.get(class_name) or (
+        MindFormerRegister.get_cls(MindFormerModuleType.TOKENIZER, class_name)
+        if MindFormerRegister.is_exist(MindFormerModuleType.TOKENIZER, class_name) else None)
+
+
+def image_processor_class_from_name(class_name: str):
+    return IMAGE_PROCESSOR_MAPPING.get(class_name)
+
+
+def processor_class_from_name(class_name: str):
+    return (MindFormerRegister.get_cls(MindFormerModuleType.PROCESSOR, class_name)
+            if MindFormerRegister.is_exist(MindFormerModuleType.PROCESSOR, class_name) else None)
+
+
+def _json_of(directory: str, name: str) -> dict:
+    path = os.path.join(directory, name)
+    if not os.path.isfile(path):
+        return {}
+    with open(path, encoding="utf-8") as f:
+        return json.load(f)
+
+
+def get_tokenizer_config(name_or_dir: str, **kwargs) -> dict:
+    """Contents of ``tokenizer_config.json`` of a model directory ({} when there is none)."""
+    return _json_of(name_or_dir, "tokenizer_config.json")
+
+
+def get_image_processor_config(name_or_dir: str, **kwargs) -> dict:
+    """Contents of ``preprocessor_config.json`` of a model directory ({} when there is none)."""
+    return _json_of(name_or_dir, "preprocessor_config.json")
+
+
+from .._submodules import alias_children as _alias_children  # noqa: E402
+
+_alias_children(__name__, ("auto_factory", "configuration_auto", "image_processing_auto", "modeling_auto", "processing_auto",
+                           "tokenization_auto"))

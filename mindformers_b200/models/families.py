@@ -206,6 +206,7 @@ _ALIASES = {
     "InferenceQwen2ForCausalLM": Qwen2ForCausalLM, "DeepseekV2ForCausalLM_legacy": DeepseekV2ForCausalLM,
     "TelechatForCausalLM_MoE": TelechatForCausalLM,
 }
+globals().update(_ALIASES)
 for _alias, _cls in _ALIASES.items():
     for _legacy in (True, False):
         MindFormerRegister.register_cls(_cls, MindFormerModuleType.MODELS, alias=_alias, legacy=_legacy)

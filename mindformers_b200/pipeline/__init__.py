@@ -132,9 +132,52 @@ class MultiModalToTextPipeline(TextGenerationPipeline):
         return {"output_ids": out, "input_ids": model_inputs["input_ids"]}
 
 
+class PipelineRegistry:
+    """Task table of ``pipeline()`` (reference ``pipeline/pipeline_registry.py:22``): ``supported_tasks`` maps a task name
+    to ``{"impl": pipeline class, "ms": model classes, "default": {...}, "type": ...}``, ``task_aliases`` maps other
+    spellings to a task name. ``register_pipeline`` adds a task and registers its class for ``pipeline()``."""
+
+    def __init__(self, supported_tasks=None, task_aliases=None):
+        self.supported_tasks = dict(supported_tasks or {})
+        self.task_aliases = dict(task_aliases or {})
+
+    def get_supported_tasks(self):
+        return sorted(set(self.supported_tasks) | set(self.task_aliases))
+
+    def check_task(self, task: str):
+        """``(normalised task name, its table entry, None)``; raises ``KeyError`` for an unknown task."""
+        task = self.task_aliases.get(task, task)
+        if task in self.supported_tasks:
+            return task, self.supported_tasks[task], None
+        raise KeyError(f"Unknown task {task}, available tasks are {self.get_supported_tasks()}")
+
+    def register_pipeline(self, task: str, pipeline_class, ms_model=None, default=None, task_type=None):
+        global SUPPORTED_TASKS
+        models = () if ms_model is None else (tuple(ms_model) if isinstance(ms_model, (list, tuple)) else (ms_model,))
+        entry = {"impl": pipeline_class, "ms": models}
+        if default is not None:
+            entry["default"] = default if ("model" in default or "ms" in default) else {"model": default}
+        if task_type is not None:
+            entry["type"] = task_type
+        self.supported_tasks[task] = entry
+        pipeline_class.registered_impl = {task: entry}
+        bucket = MindFormerRegister.registry.setdefault(MindFormerModuleType.PIPELINE, {})
+        bucket[task] = pipeline_class
+        if task not in SUPPORTED_TASKS:
+            SUPPORTED_TASKS = tuple(SUPPORTED_TASKS) + (task,)
+
+    def to_dict(self):
+        return self.supported_tasks
+
+
+TASK_ALIASES = {"text-generation": "text_generation", "image-to-text": "multi_modal_to_text_generation",
+                "image_to_text_generation": "multi_modal_to_text_generation"}
+
+
 def pipeline(task: Optional[str] = None, model=None, tokenizer=None, image_processor=None, audio_processor=None,
              backend: str = "ms", **kwargs):
     """Build the pipeline for ``task``. ``model`` is a model object, a directory (``from_pretrained``) or a preset name."""
+    task = TASK_ALIASES.get(task, task)
     if task not in SUPPORTED_TASKS:
         raise KeyError(f"task {task!r} is not supported; choose from {SUPPORTED_TASKS}")
     if isinstance(model, str):
@@ -150,6 +193,11 @@ def pipeline(task: Optional[str] = None, model=None, tokenizer=None, image_proce
         raise ValueError("pipeline() needs a model")
     cls = MindFormerRegister.get_cls(MindFormerModuleType.PIPELINE, task)
     return cls(model=model, tokenizer=tokenizer, image_processor=image_processor, **kwargs)
+
+
+PIPELINE_REGISTRY = PipelineRegistry(
+    {"text_generation": {"impl": TextGenerationPipeline, "ms": (), "type": "text"},
+     "multi_modal_to_text_generation": {"impl": MultiModalToTextPipeline, "ms": (), "type": "multimodal"}}, TASK_ALIASES)
 
 
 # ``mindformers_b200.pipeline`` names both this package and the factory function above. Calling the package calls the

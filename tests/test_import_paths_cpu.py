@@ -140,3 +140,73 @@ def test_reference_paths_below_single_file_modules(path):
         assert hasattr(mod, name), f"{path} lacks {name}"
     import mindformers_b200.core.context as ctx
     assert callable(ctx.build_context) and not isinstance(ctx.build_context, type(importlib))
+
+
+def _table():
+    from mindformers_b200._reference_paths import PATHS
+    return PATHS
+
+
+@pytest.mark.parametrize("rel", sorted(_table()))
+def test_reference_leaf_paths_resolve_to_their_module(rel):
+    mod = importlib.import_module("mindformers." + rel)
+    assert mod is importlib.import_module("mindformers_b200." + _table()[rel])
+    assert importlib.import_module("mindformers_b200." + rel) is mod
+
+
+def test_deep_reference_imports():
+    from mindformers.dataset.blended_datasets.utils import Split, get_blend_from_list, normalize
+    from mindformers.dataset.dataloader.sft_dataloader import SFTDataLoader  # noqa: F401
+    from mindformers.models.auto.tokenization_auto import AutoTokenizer, tokenizer_class_from_name
+    from mindformers.models.qwen3.modeling_qwen3_infer import InferenceQwen3ForCausalLM
+    from mindformers.models.qwen3.utils import Qwen3PreTrainedModel
+    from mindformers.parallel_core.inference.tensor_parallel.mappings import ReduceFromModelParallelRegion
+    from mindformers.parallel_core.inference.transformer.moe.router import Router, TopKRouter
+    from mindformers.parallel_core.training_graph.transformer.identity_op import IdentityOp
+    from mindformers.parallel_core.training_graph.transformer.norm import FusedNorm, get_norm_cls
+    from mindformers.pet.models.slora import SLoraModel  # noqa: F401
+    from mindformers.pipeline.pipeline_registry import PipelineRegistry
+    import mindformers_b200 as mf
+    import torch
+    assert InferenceQwen3ForCausalLM is mf.Qwen3ForCausalLM and Qwen3PreTrainedModel.config_class is mf.Qwen3Config
+    assert tokenizer_class_from_name("LlamaTokenizer") is mf.LlamaTokenizer and AutoTokenizer is mf.AutoTokenizer
+    assert get_blend_from_list(["30", "a", "70", "b"]) == (["a", "b"], [30.0, 70.0])
+    assert get_blend_from_list(["a", "b", "c"]) == (["a", "b", "c"], None) and get_blend_from_list(["a", "b"]) == (["a", "b"], None)
+    assert normalize([1, 3]) == [0.25, 0.75] and Split.valid.value == 1
+    x = torch.randn(3, 4)
+    assert IdentityOp()(x) is x and ReduceFromModelParallelRegion()(x) is x
+    assert get_norm_cls("RMSNorm") is FusedNorm and issubclass(TopKRouter, torch.nn.Module) and Router is not None
+    reg = PipelineRegistry({"text_generation": {"impl": mf.TextGenerationPipeline, "ms": ()}}, {"text-generation": "text_generation"})
+    assert reg.check_task("text-generation")[0] == "text_generation" and "text_generation" in reg.get_supported_tasks()
+    with pytest.raises(KeyError):
+        reg.check_task("translation")
+    with pytest.raises(ImportError):
+        importlib.import_module("mindformers.dataset.dataloader.ms_ds_convertor")
+
+
+def test_split_matrix_and_building_blocks():
+    import torch
+    from mindformers.dataset.blended_datasets.blended_megatron_dataset_config import convert_split_vector_to_split_matrix
+    from mindformers.parallel_core.training_graph.base_models.common.embeddings.rope_utils import ApplyRotaryPosEmb
+    from mindformers.parallel_core.training_graph.transformer.utils import get_attn_mask_func
+    from mindformers.parallel_core.inference.transformer.activation import get_act_func
+    m = convert_split_vector_to_split_matrix([0.9, 0.1, 0.0])
+    assert m[2] is None and m[0][0] == 0.0 and abs(m[0][1] - 0.9) < 1e-12 and abs(m[1][1] - 1.0) < 1e-12
+    both = convert_split_vector_to_split_matrix([0.9, 0.1, 0.0], [0.5, 0.5, 0.0])
+    assert both[0] == (0.0, 0.5) and abs(both[1][0] - 0.9) < 1e-12
+    scores, mask = torch.zeros(2, 2), torch.tensor([[0, 1], [0, 0]])
+    assert get_attn_mask_func("attn_mask_fill")(scores, mask)[0, 1] == -10000 and get_attn_mask_func("attn_mask_add")(scores, mask)[0, 0] == 0
+    x = torch.randn(4, 6)
+    assert torch.allclose(get_act_func("swiglu")(x), torch.nn.functional.silu(x[:, :3]) * x[:, 3:], atol=1e-6)
+    assert torch.allclose(get_act_func("squared_relu")(x), torch.relu(x) ** 2)
+    # rotary: angles in the "halves" layout [f, f]; position 0 is the identity, norms are kept
+    S, B, H, D = 5, 2, 3, 8
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D))
+    f = torch.outer(torch.arange(S).float(), inv)
+    freqs = torch.cat([f, f], -1).view(S, 1, 1, D)
+    t = torch.randn(S, B, H, D)
+    out = ApplyRotaryPosEmb()(t, freqs)
+    assert torch.allclose(out[0], t[0], atol=1e-6) and torch.allclose(out.norm(dim=-1), t.norm(dim=-1), atol=1e-5)
+    a, b = t[..., : D // 2], t[..., D // 2:]
+    want = torch.cat([a * f.cos()[:, None, None] - b * f.sin()[:, None, None], b * f.cos()[:, None, None] + a * f.sin()[:, None, None]], -1)
+    assert torch.allclose(out, want, atol=1e-5)

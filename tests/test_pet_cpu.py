@@ -80,3 +80,38 @@ def test_prefix_tuning_trains_prefix_only():
         loss.backward()
         opt.step()
     assert loss.item() < first
+
+
+def test_slora_model_loads_adapter_table_and_routes(tmp_path):
+    import json
+
+    from safetensors.torch import save_file
+
+    from mindformers_b200.pet.models import Ptuning2Model, SLoraModel
+    from mindformers_b200.pet.pet_config import SLoraConfig as _Cfg
+    torch.manual_seed(0)
+    base = _tiny_model() if "_tiny_model" in globals() else None
+    if base is None:
+        from mindformers_b200.models import LlamaConfig, LlamaForCausalLM
+        base = LlamaForCausalLM(LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                            num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32,
+                                            params_dtype="float32", compute_dtype="float32")).eval()
+    ids = torch.randint(0, 64, (2, 8))
+    with torch.no_grad():
+        plain = base(ids).clone()
+    net = SLoraModel(_Cfg(lora_num=2, lora_rank=4, lora_alpha=8, target_modules=".*linear_proj"), base)
+    state = {}
+    for layer in net.slora.layers:
+        state[f"{layer.qualified_name}.lora_a"] = torch.randn(4, layer.lora_a.shape[-1]) * 0.1
+        state[f"{layer.qualified_name}.lora_b"] = torch.randn(layer.lora_b.shape[-2], 4) * 0.1
+    (tmp_path / "math").mkdir()
+    save_file(state, str(tmp_path / "math" / "adapter_model.safetensors"))
+    (tmp_path / "lora_adapter.json").write_text(json.dumps({"math": "math"}))
+    assert net.load_adapters(str(tmp_path)) == ["math"]
+    with torch.no_grad():
+        routed = net(ids, adapter_names=[None, "math"]).view(2, 8, -1)
+        again = net(ids).view(2, 8, -1)
+    plain = plain.view(2, 8, -1)
+    assert torch.allclose(routed[0], plain[0], atol=1e-5) and not torch.allclose(routed[1], plain[1], atol=1e-4)
+    assert torch.allclose(again, plain, atol=1e-5)                      # routing does not outlive the call
+    assert issubclass(Ptuning2Model, torch.nn.Module)
