@@ -1,4 +1,7 @@
 """Data handlers under the reference's ``dataset/handler`` path."""
-from ...dataset.handlers import AdgenInstructDataHandler, AlpacaInstructDataHandler, BaseInstructDataHandler, CodeAlpacaInstructDataHandler, LlavaInstructDataHandler, PackingHandler, build_data_handler  # noqa: F401
+from ...dataset.handlers import (AdgenInstructDataHandler, AlpacaInstructDataHandler, BaseInstructDataHandler,  # noqa: F401
+                                 CodeAlpacaInstructDataHandler, LlavaInstructDataHandler, PackingConfig, PackingHandler,
+                                 build_data_handler, pack_examples, truncate_examples)
 
-__all__ = ["AdgenInstructDataHandler", "AlpacaInstructDataHandler", "BaseInstructDataHandler", "CodeAlpacaInstructDataHandler", "LlavaInstructDataHandler", "PackingHandler", "build_data_handler"]
+__all__ = ["AdgenInstructDataHandler", "AlpacaInstructDataHandler", "BaseInstructDataHandler", "CodeAlpacaInstructDataHandler",
+           "LlavaInstructDataHandler", "PackingConfig", "PackingHandler", "build_data_handler", "pack_examples", "truncate_examples"]

@@ -6,7 +6,8 @@ Reference: ``dataset/handler/*`` (``AlpacaInstructDataHandler``, ``CodeAlpacaIns
 from __future__ import annotations
 
 import os
-from typing import Callable, Dict, Iterable, List, Optional
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterable, List, Optional, Sequence
 
 import numpy as np
 
@@ -121,8 +122,86 @@ class LlavaInstructDataHandler(BaseInstructDataHandler):
 
 
 @MindFormerRegister.register(MindFormerModuleType.DATA_HANDLER)
+@dataclass
+class PackingConfig:
+    """Settings of the packing functions (reference ``dataset/handler/packing_handler.py:24``)."""
+    seq_length: int = None
+    pad_token: int = 0
+    ignore_token: int = IGNORE
+    seed: int = 42
+    dataset_shuffle: bool = False
+
+    def __post_init__(self):
+        if self.seq_length is None:
+            raise ValueError("seq_length must be set in PackingHandler.")
+
+
+def pack_examples(dataset: Iterable[Dict[str, Sequence[int]]], config: PackingConfig) -> Dict[str, list]:
+    """Sequential packing: samples are appended to the current row until the next one would not fit; samples longer
+    than ``seq_length`` are skipped. Inside a row every sample's labels are its own next tokens (``labels[1:]`` plus one
+    pad), so no label crosses a sample boundary. Columns: ``input_ids``, ``labels`` (padded to ``seq_length``),
+    ``actual_seq_len`` (cumulative sample ends of the row)."""
+    out = {"input_ids": [], "labels": [], "actual_seq_len": []}
+    ids: List[int] = []
+    lab: List[int] = []
+    ends: List[int] = []
+
+    def flush():
+        gap = config.seq_length - len(ids)
+        out["input_ids"].append(ids + [config.pad_token] * gap)
+        out["labels"].append(lab + [config.ignore_token] * gap)
+        out["actual_seq_len"].append(list(ends))
+
+    for sample in dataset:
+        tokens, labels = list(sample["input_ids"]), list(sample["labels"])
+        n = len(tokens)
+        if n > config.seq_length:
+            continue
+        if len(ids) + n > config.seq_length:
+            flush()
+            ids, lab, ends = [], [], []
+        ids += tokens
+        lab += labels[1:] + [config.pad_token]
+        ends.append((ends[-1] if ends else 0) + n)
+    if ids:
+        flush()
+    return out
+
+
+def truncate_examples(examples: Dict[str, List[Sequence[int]]], config: PackingConfig) -> Dict[str, list]:
+    """Truncate mode: all samples of the batch are joined into one stream per column and cut into rows of
+    ``seq_length`` (a sample may continue in the next row); the last row is padded. ``actual_seq_len`` lists, per row,
+    the lengths of the pieces it holds."""
+    L = config.seq_length
+    first = next(iter(examples))
+    pieces: List[List[int]] = [[]]
+    used = 0
+    for n in (len(x) for x in examples[first]):
+        while used + n > L:
+            part = L - used
+            if part:
+                pieces[-1].append(part)
+            pieces.append([])
+            n -= part
+            used = 0
+        if n:
+            pieces[-1].append(n)
+            used += n
+    out = {}
+    for key, column in examples.items():
+        stream = [t for row in column for t in row]
+        rows = [stream[i:i + L] for i in range(0, len(stream), L)] or [[]]
+        fill = config.pad_token if key == "input_ids" else config.ignore_token
+        rows[-1] = rows[-1] + [fill] * (L - len(rows[-1]))
+        out[key] = rows
+    out["actual_seq_len"] = [p for p in pieces if p][: len(out[first])]
+    return out
+
+
 class PackingHandler:
-    """Greedy first-fit packing of tokenised samples into rows of ``seq_length`` tokens.
+    """Packing of tokenised samples into rows of ``seq_length`` tokens: ``pack_strategy="pack"`` places every sample
+    whole into the first row with room (first fit; the reference fills rows in order, ``pack_examples`` above does that),
+    ``"truncate"`` joins all samples and cuts the stream into rows (``truncate_examples``).
 
     Output rows carry ``input_ids``, ``labels`` (first token of every packed sample masked) and
     ``actual_seq_len`` (cumulative boundaries, padded with ``seq_length``), the inputs of TND-layout attention.
@@ -135,7 +214,27 @@ class PackingHandler:
         self.seq_length, self.strategy = seq_length, pack_strategy
         self.pad, self.ignore, self.max_segments = pad_token_id, ignore_token_id, max_segments
 
+    def _handle_truncate(self, samples):
+        cfg = PackingConfig(seq_length=self.seq_length, pad_token=self.pad, ignore_token=self.ignore)
+        cols = {"input_ids": [], "labels": []}
+        for s in samples:
+            ids = [int(t) for t in s["input_ids"]]
+            cols["input_ids"].append(ids)
+            cols["labels"].append([int(t) for t in s.get("labels", ids)])
+        if not cols["input_ids"]:
+            return []
+        cut = truncate_examples(cols, cfg)
+        out = []
+        for ids, lab, lens in zip(cut["input_ids"], cut["labels"], cut["actual_seq_len"]):
+            asl = np.full(self.max_segments, self.seq_length, dtype=np.int32)
+            bounds = np.cumsum(lens)[: self.max_segments]
+            asl[: len(bounds)] = bounds
+            out.append({"input_ids": np.asarray(ids, dtype=np.int64), "labels": np.asarray(lab, dtype=np.int64), "actual_seq_len": asl})
+        return out
+
     def handle(self, samples: Iterable[Dict[str, np.ndarray]]) -> List[Dict[str, np.ndarray]]:
+        if self.strategy == "truncate":
+            return self._handle_truncate(samples)
         rows: List[List[Dict[str, np.ndarray]]] = []
         space: List[int] = []
         for s in samples:

@@ -138,3 +138,24 @@ def test_indexed_dataset_from_an_object_store_prefix(tmp_path):
         assert ds[i].tolist() == d.tolist()
     assert ds.get(1, offset=3, length=4).tolist() == [103, 104, 105, 106]
     assert ds._s3.requests <= 4 and os.path.exists(tmp_path / "cache" / "bkt" / "data" / "corpus.idx")
+
+
+def test_pack_and_truncate_examples():
+    from mindformers_b200.dataset.handler.packing_handler import PackingConfig, PackingHandler, pack_examples, truncate_examples
+    cfg = PackingConfig(seq_length=8, pad_token=0, ignore_token=-100)
+    samples = [{"input_ids": [1, 2, 3], "labels": [1, 2, 3]}, {"input_ids": [4, 5, 6, 7], "labels": [4, 5, 6, 7]},
+               {"input_ids": [8, 9], "labels": [8, 9]}, {"input_ids": list(range(20, 30)), "labels": list(range(20, 30))}]
+    packed = pack_examples(samples, cfg)
+    # rows fill in order; the 10-token sample does not fit a row of 8 and is skipped
+    assert packed["input_ids"] == [[1, 2, 3, 4, 5, 6, 7, 0], [8, 9, 0, 0, 0, 0, 0, 0]]
+    assert packed["labels"][0] == [2, 3, 0, 5, 6, 7, 0, -100] and packed["actual_seq_len"] == [[3, 7], [2]]
+    cols = {"input_ids": [[1, 2, 3], [4, 5, 6, 7], [8, 9, 10]], "labels": [[1, 2, 3], [4, 5, 6, 7], [8, 9, 10]]}
+    cut = truncate_examples(cols, PackingConfig(seq_length=4))
+    assert cut["input_ids"] == [[1, 2, 3, 4], [5, 6, 7, 8], [9, 10, 0, 0]]
+    assert cut["labels"][-1] == [9, 10, -100, -100] and cut["actual_seq_len"] == [[3, 1], [3, 1], [2]]
+    rows = PackingHandler(seq_length=4, pack_strategy="truncate", max_segments=4).handle(
+        [{"input_ids": r, "labels": r} for r in cols["input_ids"]])
+    assert [r["input_ids"].tolist() for r in rows] == cut["input_ids"]
+    assert rows[0]["actual_seq_len"].tolist() == [3, 4, 4, 4] and rows[2]["actual_seq_len"].tolist() == [2, 4, 4, 4]
+    with __import__("pytest").raises(ValueError):
+        PackingConfig()
