@@ -6,6 +6,7 @@ int32 sequence lengths, int64 byte pointers, int64 document boundaries, optional
 """
 from __future__ import annotations
 
+import enum
 import os
 import struct
 from typing import List, Optional, Sequence
@@ -15,6 +16,38 @@ import numpy as np
 _MAGIC = b"MMIDIDX\x00\x00"
 _DTYPES = {1: np.uint8, 2: np.int8, 3: np.int16, 4: np.int32, 5: np.int64, 6: np.float64, 7: np.float32, 8: np.uint16}
 _CODES = {np.dtype(v): k for k, v in _DTYPES.items()}
+
+
+class DType(enum.Enum):
+    """Element-type codes of the ``.idx`` header (the Megatron on-disk format)."""
+    uint8 = 1
+    int8 = 2
+    int16 = 3
+    int32 = 4
+    int64 = 5
+    float64 = 6
+    float32 = 7
+    uint16 = 8
+
+    @classmethod
+    def code_from_dtype(cls, value) -> int:
+        return cls[np.dtype(value).name].value
+
+    @classmethod
+    def dtype_from_code(cls, value: int):
+        return getattr(np, cls(value).name)
+
+    @staticmethod
+    def size(key) -> int:
+        """Bytes per element of a code or a dtype."""
+        if isinstance(key, int):
+            return np.dtype(DType.dtype_from_code(key)).itemsize
+        return np.dtype(key).itemsize
+
+    @staticmethod
+    def optimal_dtype(cardinality: Optional[int]):
+        """uint16 when every token id fits, else int32."""
+        return np.uint16 if cardinality is not None and cardinality < 65500 else np.int32
 
 
 def get_idx_path(prefix: str) -> str:

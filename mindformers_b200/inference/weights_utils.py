@@ -193,3 +193,33 @@ def load_weights(model: torch.nn.Module, path: str, family: str = "llama", stric
     if missing:
         logger.warning("parameters not found in %s: %s", path, missing[:8])
     return {"layers": len(layers), "tensors": len(loader.key_to_file), "peak_group_bytes": peak, "missing": missing}
+
+
+def split_weight_by_tp_rank(weight, split_axis: int, tp_rank_id: int, tp_group_size: int) -> torch.Tensor:
+    """This rank's equal share of ``weight`` (a tensor or a lazy safetensors slice) along ``split_axis`` (0 = rows,
+    1 = columns); reference ``parallel_core/inference/weights_utils.py:252``."""
+    if split_axis == 0:
+        return split_by_tp_rank_rows(weight, tp_rank_id, tp_group_size)
+    if split_axis == 1:
+        return split_by_tp_rank_columns(weight, tp_rank_id, tp_group_size)
+    raise ValueError(f"split_axis must be 0 or 1, got {split_axis}")
+
+
+def handle_training_ffn_weight(ffn_value: torch.Tensor):
+    """Packed ``[gate; up]`` first projection of a training checkpoint → ``(gate, up)`` halves along the rows."""
+    gate, up = ffn_value.chunk(2, dim=0)
+    return gate.contiguous(), up.contiguous()
+
+
+def handle_training_qkv_weight(qkv_weight_value: torch.Tensor, config):
+    """Group-interleaved packed QKV of a training checkpoint (per KV group: its ``heads / groups`` query heads, then its
+    key, then its value) → ``(q, k, v)`` in head order."""
+    heads = config.num_attention_heads
+    groups = getattr(config, "num_query_groups", None) or heads
+    hd = getattr(config, "kv_channels", None) or config.hidden_size // heads
+    rep = heads // groups
+    w = qkv_weight_value.reshape(groups, (rep + 2) * hd, -1)
+    q = w[:, : rep * hd].reshape(heads * hd, -1)
+    k = w[:, rep * hd: (rep + 1) * hd].reshape(groups * hd, -1)
+    v = w[:, (rep + 1) * hd:].reshape(groups * hd, -1)
+    return q.contiguous(), k.contiguous(), v.contiguous()

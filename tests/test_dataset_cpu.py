@@ -159,3 +159,25 @@ def test_pack_and_truncate_examples():
     assert rows[0]["actual_seq_len"].tolist() == [3, 4, 4, 4] and rows[2]["actual_seq_len"].tolist() == [2, 4, 4, 4]
     with __import__("pytest").raises(ValueError):
         PackingConfig()
+
+
+def test_indexed_dataset_dtype_codes_and_weight_split_helpers():
+    import numpy as np
+    import torch
+    from mindformers_b200.dataset.indexed_dataset import DType
+    from mindformers_b200.inference.weights_utils import (handle_training_ffn_weight, handle_training_qkv_weight,
+                                                          split_weight_by_tp_rank)
+    assert DType.code_from_dtype(np.int32) == 4 and DType.dtype_from_code(8) is np.uint16 and DType.size(5) == 8
+    assert DType.optimal_dtype(32000) is np.uint16 and DType.optimal_dtype(152064) is np.int32
+    w = torch.arange(24.).reshape(6, 4)
+    assert torch.equal(split_weight_by_tp_rank(w, 0, 1, 2), w[3:]) and torch.equal(split_weight_by_tp_rank(w, 1, 0, 2), w[:, :2])
+
+    class Cfg:
+        num_attention_heads, num_query_groups, kv_channels, hidden_size = 4, 2, 2, 8
+
+    q, k, v = torch.randn(8, 8), torch.randn(4, 8), torch.randn(4, 8)
+    packed = torch.cat([torch.cat([q[g * 4:(g + 1) * 4], k[g * 2:(g + 1) * 2], v[g * 2:(g + 1) * 2]]) for g in range(2)])
+    a, b, c = handle_training_qkv_weight(packed, Cfg)
+    assert torch.equal(a, q) and torch.equal(b, k) and torch.equal(c, v)
+    gate, up = handle_training_ffn_weight(torch.arange(12.).reshape(6, 2))
+    assert gate.shape == (3, 2) and up[0, 0] == 6
