@@ -163,9 +163,76 @@ def multi_round_chat_map_fn(example, tokenizer, max_length, user_role="human", a
     return {"input_ids": ids[:max_length], "labels": labels[:max_length]}
 
 
+def _dyn_row(ids: List[int], labels: List[int], tokenizer, max_length: int) -> Dict[str, List[int]]:
+    """Close a dynamic-length row: append the end token, cut at ``max_length``; no padding (the batch collator pads)."""
+    ids, labels = ids + [tokenizer.eos_token_id], labels + [tokenizer.eos_token_id]
+    ids, labels = ids[:max_length], labels[:max_length]
+    return {"input_ids": ids, "attention_mask": [1] * len(ids), "labels": labels}
+
+
+def _chat_turns(example, kw):
+    field = kw.get("data_field", "conversations")
+    fk, vk = kw.get("from_keyword", "from"), kw.get("value_keyword", "value")
+    user, assistant = kw.get("user_role_name", "human"), kw.get("assistant_role_name", "gpt")
+    for message in example[field]:
+        role = message[fk]
+        if role not in (user, assistant):
+            raise ValueError(f"Incorrect role name: {role}. Check the values of `user_role_name` and `assistant_role_name` "
+                             f"in `map_function_kwargs`.")
+        yield role == user, message[vk]
+
+
+def multi_round_chat_dyn_map_fn(example, tokenizer=None, max_length=None, **kw):
+    """Multi-round chat without padding (reference ``sft_map_functions.py:119``): a user turn is ``bos_token + user_prompt
+    + user_prompt_role + text`` followed by ``assistant_prompt + assistant_prompt_role`` (no loss); an assistant turn is
+    ``sep_token + text`` (loss on all of it); one end token closes the row."""
+    ignore = kw.get("ignore_token_id", IGNORE_INDEX)
+    bos, sep = kw.get("bos_token", "<s>"), kw.get("sep_token", "")
+    ids: List[int] = []
+    labels: List[int] = []
+    for is_user, text in _chat_turns(example, kw):
+        if is_user:
+            part = _ids(tokenizer, bos + kw.get("user_prompt", "") + kw.get("user_prompt_role", "") + text) + \
+                _ids(tokenizer, kw.get("assistant_prompt", "") + kw.get("assistant_prompt_role", ""))
+            ids += part
+            labels += [ignore] * len(part)
+        else:
+            part = _ids(tokenizer, sep + text)
+            ids += part
+            labels += part
+    return _dyn_row(ids, labels, tokenizer, max_length)
+
+
+def multi_instruct_dyn_map_fn(example, tokenizer=None, max_length=None, **kw):
+    """Instruction / input / output records without padding (reference ``sft_map_functions.py:166``): the prompt
+    ``user_prompt_role + instruction + input + assistant_prompt_role`` carries no loss, the output does."""
+    ignore = kw.get("ignore_token_id", IGNORE_INDEX)
+    prompt = _ids(tokenizer, kw.get("user_prompt_role", "") + example[kw.get("instruction_keyword", "instruction")]
+                  + example[kw.get("from_keyword", "input")] + kw.get("assistant_prompt_role", ""))
+    answer = _ids(tokenizer, example[kw.get("value_keyword", "output")])
+    return _dyn_row(prompt + answer, [ignore] * len(prompt) + answer, tokenizer, max_length)
+
+
+def multi_round_chat_dyn_map_fn_alpaca(example, tokenizer=None, max_length=None, **kw):
+    """ChatML-formatted multi-round chat without padding (reference ``sft_map_functions.py:204``): user turns are
+    ``bos + user_prompt + sep + user_prompt_role + text + sep`` + the assistant prompt, assistant turns end with
+    ``<|im_end|>\\n``; every token carries loss (continued pre-training on chat transcripts)."""
+    bos, sep = kw.get("bos_token", "<|im_start|>"), kw.get("sep_token", "<|im_end|>\n<|im_start|>")
+    ids: List[int] = []
+    for is_user, text in _chat_turns(example, kw):
+        if is_user:
+            ids += _ids(tokenizer, bos + kw.get("user_prompt", "") + sep + kw.get("user_prompt_role", "") + text + sep)
+            ids += _ids(tokenizer, kw.get("assistant_prompt", "") + kw.get("assistant_prompt_role", ""))
+        else:
+            ids += _ids(tokenizer, text + "<|im_end|>\n")
+    return _dyn_row(ids, list(ids), tokenizer, max_length)
+
+
 SFT_MAP_FUNCTIONS: Dict[str, Callable] = {
     "default": default_map_fn, "alpaca": alpaca_map_fn, "advertisegen": advertisegen_map_fn, "tnews": tnews_map_fn,
     "cmrc2018": default_map_fn, "multi-round-chat": multi_round_chat_map_fn,
+    "multi-round-chat-dyn": multi_round_chat_dyn_map_fn, "multi-instruct-dyn": multi_instruct_dyn_map_fn,
+    "multi-round-chat-dyn-alpaca": multi_round_chat_dyn_map_fn_alpaca,
 }
 
 

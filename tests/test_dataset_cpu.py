@@ -181,3 +181,29 @@ def test_indexed_dataset_dtype_codes_and_weight_split_helpers():
     assert torch.equal(a, q) and torch.equal(b, k) and torch.equal(c, v)
     gate, up = handle_training_ffn_weight(torch.arange(12.).reshape(6, 2))
     assert gate.shape == (3, 2) and up[0, 0] == 6
+
+
+def test_dynamic_length_sft_map_functions():
+    from mindformers_b200.dataset.dataloader.sft_map_functions import (multi_instruct_dyn_map_fn, multi_round_chat_dyn_map_fn,
+                                                                       multi_round_chat_dyn_map_fn_alpaca)
+
+    class Tok:
+        eos_token_id = 2
+
+        def encode(self, text, add_special_tokens=False):
+            return [10 + (ord(c) % 50) for c in text]
+
+    tok = Tok()
+    ex = {"conversations": [{"from": "human", "value": "hi"}, {"from": "gpt", "value": "yo"}]}
+    row = multi_round_chat_dyn_map_fn(ex, tokenizer=tok, max_length=64, bos_token="", user_prompt_role="U:", assistant_prompt_role="A:")
+    user = tok.encode("U:hi") + tok.encode("A:")
+    assert row["input_ids"] == user + tok.encode("yo") + [2]
+    assert row["labels"] == [-100] * len(user) + tok.encode("yo") + [2] and row["attention_mask"] == [1] * len(row["input_ids"])
+    cut = multi_round_chat_dyn_map_fn(ex, tokenizer=tok, max_length=3, bos_token="")
+    assert len(cut["input_ids"]) == 3 and len(cut["labels"]) == 3
+    with __import__("pytest").raises(ValueError):
+        multi_round_chat_dyn_map_fn({"conversations": [{"from": "bot", "value": "x"}]}, tokenizer=tok, max_length=8)
+    ins = multi_instruct_dyn_map_fn({"instruction": "do ", "input": "x", "output": "ok"}, tokenizer=tok, max_length=64)
+    assert ins["input_ids"] == tok.encode("do x") + tok.encode("ok") + [2] and ins["labels"][:4] == [-100] * 4
+    al = multi_round_chat_dyn_map_fn_alpaca(ex, tokenizer=tok, max_length=256, bos_token="<s>", sep_token="|")
+    assert al["input_ids"] == tok.encode("<s>|hi|") + tok.encode("yo<|im_end|>\n") + [2] and al["labels"] == al["input_ids"]
