@@ -134,6 +134,11 @@ def get_optimizer_grouped_parameters(model: torch.nn.Module, weight_decay: float
     return list(groups.values())
 
 
+# the reference registers this optimizer as ``Came`` (``core/optim/came.py``); YAMLs written for it say ``type: Came``
+Came = CAME
+MindFormerRegister.register_cls(CAME, MindFormerModuleType.OPTIMIZER, alias="Came")
+
+
 class ReplicatedOptimizer:
     """Runs any ``torch.optim`` style optimizer (``CAME``, ``SGD``, ...) behind the interface the train step expects
     from the sharded AdamW: ``zero_grad()``, ``step(grad_scale)``, ``global_norm()``, ``skipped``, ``current_lr()``,
