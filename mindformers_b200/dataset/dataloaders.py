@@ -549,24 +549,47 @@ class HFDataLoader:
         return _SampleList(records, seq_length, pad_token_id if pid is None else pid)
 
 
+class MultiModalSFTDataLoader(Dataset):
+    """Random-access view of a conversation-format annotation file (reference
+    ``dataset/dataloader/multi_modal_dataloader.py:48``): item ``i`` is a 1-tuple holding the conversation as
+    ``[[role, text], ...]``. ``map_function_kwargs``: ``data_field`` ("conversations"), ``from_keyword`` ("from"),
+    ``value_keyword`` ("value"); ``read_function``: path → list of records (default: JSON / JSON lines)."""
+
+    def __init__(self, annotation_file: str, max_length: int = 1025, read_function: Optional[Callable] = None,
+                 map_function_kwargs: Optional[dict] = None, max_chunk_size: int = 1024, **kw):
+        if not os.path.exists(annotation_file):
+            raise FileExistsError(f"The annotation_file {annotation_file} is not exist.")
+        self.max_length, self.kwargs = max_length, dict(map_function_kwargs or {})
+        self.records = read_function(annotation_file) if read_function else read_records(
+            annotation_file, "json" if annotation_file.endswith(".json") else None)
+
+    def __len__(self):
+        return len(self.records)
+
+    def conversation(self, record: dict) -> List[List[str]]:
+        field = self.kwargs.get("data_field", "conversations")
+        fk, vk = self.kwargs.get("from_keyword", "from"), self.kwargs.get("value_keyword", "value")
+        return [[m[fk], m[vk]] for m in record[field]]
+
+    def __getitem__(self, i):
+        return (self.conversation(self.records[i]),)
+
+
 @MindFormerRegister.register(MindFormerModuleType.DATASET_LOADER)
 class BaseMultiModalDataLoader:
     """Conversation-format annotation file → rows ``{"conversations": [[role, text], ...]}`` (reference
-    ``dataset/dataloader/multi_modal_dataloader.py:30``). ``extra_kwargs``: ``data_field`` (default "conversations"),
-    ``from_keyword`` ("from"), ``value_keyword`` ("value"), ``read_function`` (path → list of records)."""
+    ``dataset/dataloader/multi_modal_dataloader.py:30``). ``extra_kwargs`` are the arguments of
+    ``MultiModalSFTDataLoader`` (``map_function_kwargs``, ``read_function``, ``max_length``)."""
 
     def __new__(cls, annotation_file: str, shuffle: Optional[bool] = True, extra_kwargs: Optional[dict] = None, seed: int = 0,
                 **kwargs):
-        if not os.path.exists(annotation_file):
-            raise FileExistsError(f"The annotation_file {annotation_file} is not exist.")
         extra = dict(extra_kwargs or {})
-        mk = dict(extra.get("map_function_kwargs") or {})
-        field = mk.get("data_field", extra.get("data_field", "conversations"))
-        fk = mk.get("from_keyword", extra.get("from_keyword", "from"))
-        vk = mk.get("value_keyword", extra.get("value_keyword", "value"))
-        reader = extra.get("read_function")
-        records = reader(annotation_file) if reader else read_records(annotation_file, "json" if annotation_file.endswith(".json") else None)
-        rows = [{"conversations": [[m[fk], m[vk]] for m in rec[field]]} for rec in records]
+        mk = dict(extra.pop("map_function_kwargs", None) or {})
+        for key in ("data_field", "from_keyword", "value_keyword"):
+            if key in extra:
+                mk.setdefault(key, extra.pop(key))
+        source = MultiModalSFTDataLoader(annotation_file, map_function_kwargs=mk, **extra)
+        rows = [{"conversations": source[i][0]} for i in range(len(source))]
         if shuffle:
             random.Random(seed).shuffle(rows)
         return _RawRecords(rows)

@@ -56,7 +56,7 @@ class BaseImageToTextImageProcessor(BaseImageProcessor):
             arr = np.stack([arr] * 3, axis=-1)
         if arr.ndim != 3 or arr.shape[-1] not in (3, 4):
             raise ValueError(f"expected an HWC image, got shape {arr.shape}")
-        t = torch.from_numpy(np.ascontiguousarray(arr[..., :3])).permute(2, 0, 1).float()
+        t = torch.from_numpy(np.array(arr[..., :3], copy=True)).permute(2, 0, 1).float()
         return t / 255.0 if arr.dtype == np.uint8 or t.max() > 1.5 else t
 
     def preprocess(self, images, **kwargs) -> torch.Tensor:
